@@ -1,0 +1,612 @@
+// TEST INFRASTRUCTURE (CPU oracle). Not part of the shipped library.
+//
+// CPU restatement of the dense-preset transformer of the reference: inference
+// forward over a KV cache (model/transformer.go:243-342, model/attention.go:
+// 235-324, model/kvcache.go:69-140,383-448), training forward that saves
+// activations (model/train_transformer.go:63-142, model/train.go:55-192,
+// 490-552) and the analytic backward (model/train_transformer.go:147-320,
+// model/train.go:198-427,505-572, tensors/backward.go:57-116,
+// model/layers/linear.go:45-104).
+#pragma once
+#include <map>
+#include <string>
+#include <memory>
+#include <cstdio>
+#include "backend.h"
+
+namespace gnor {
+
+static const float kNormEps = 1e-6f;      // model/attention.go:11
+static const float kQKScale = 1.2f;       // model/attention.go:14
+static const int kVeGateChannels = 12;    // model/attention.go:18
+static const float kVeGateScale = 3.0f;   // model/attention.go:21
+static const int kSmearChannels = 24;     // model/helpers.go:13
+static const float kSoftcap = 15.0f;      // model/transformer.go:11
+static const int kRotaryOvercompute = 10; // model/transformer.go:15
+static const double kRotaryBase = 100000; // model/rotary.go:10
+
+struct Config {
+  int sequence_len = 0, vocab = 0, n_layer = 0, n_head = 0, n_kv_head = 0, embed_dim = 0, rotary_dims = 0;
+  std::string window_pattern = "L";
+  int head_dim() const { return embed_dim / n_head; }
+  int rotary_dimension() const { return rotary_dims <= 0 ? head_dim() : rotary_dims; }  // model/config.go:430-444
+  int padded_vocab() const { return ((vocab + 63) / 64) * 64; }                         // model/config.go:619-624
+  // model/config.go:629-645 (integer division truncates toward zero, as in Go).
+  std::vector<int> windows() const {
+    int longw = sequence_len;
+    int shortw = -((-sequence_len / 4) / 128) * 128;
+    std::vector<int> w(n_layer, longw);
+    for (int l = 0; l < n_layer; ++l) {
+      char c = window_pattern[l % window_pattern.size()];
+      w[l] = (c == 'S' || c == 's') ? shortw : longw;
+    }
+    w[n_layer - 1] = longw;
+    return w;
+  }
+};
+
+struct Param {
+  std::vector<float> w, g;
+  int rows = 0, cols = 0;
+};
+
+static inline bool has_value_embedding(int layer, int n_layer) { return layer % 2 == (n_layer - 1) % 2; }  // model/helpers.go:69-71
+
+struct KVCache {
+  int batch = 0, max_seq = 0, pos = 0;
+  // [layer][row*Hkv+head] -> [max_seq, D]
+  std::vector<std::vector<std::vector<float>>> k, v;
+  std::vector<float> prev;  // [batch, d] pre-smear embedding of the last token
+  bool has_prev = false;
+};
+
+struct LayerCtx {
+  std::vector<float> prev_x;      // activations before combineResidual
+  std::vector<float> x_in;        // block input (after combineResidual)
+  std::vector<float> h;           // norm(x_in)
+  std::vector<float> q_rot, k_rot;// [B,T,H,D] post-rotary, pre-norm
+  std::vector<float> q_hm, k_hm, v_hm;  // head-major post-norm q,k; final v
+  std::vector<float> lse;         // [B,Hq,T]
+  std::vector<float> o_hm;        // [B,Hq,T,D]
+  std::vector<float> ve_sig;      // [B,T,Hkv] sigmoid gate (pre *3)
+  std::vector<float> ve;          // [B,T,Hkv*D] value embedding rows
+  std::vector<float> mid;         // x_in + attention output
+  std::vector<float> m;           // norm(mid)
+  std::vector<float> u;           // c_fc output (pre activation)
+  std::vector<float> hid;         // relu(u)^2
+};
+
+struct TrainCtx {
+  int B = 0, T = 0;
+  std::vector<int32_t> ids;
+  std::vector<float> raw;          // wte rows
+  std::vector<float> e_alias;      // see note in train_forward on aliasing
+  std::vector<float> smear_slice;  // [B,T-1,24]
+  std::vector<float> smear_sig;    // [B,T-1]
+  std::vector<float> x0;           // after smear
+  std::vector<LayerCtx> layers;
+  std::vector<float> backout;
+  std::vector<float> final_pre, final_norm;
+  std::vector<float> logits;       // [B*T, V] softcapped
+};
+
+struct Model {
+  Config cfg;
+  Backend bk;
+  std::map<std::string, Param> params;
+  std::vector<float> cosv, sinv;  // [sequence_len*10, R/2]
+  std::vector<int> windows;
+  int D = 0, R = 0, Vp = 0, KV = 0;
+
+  explicit Model(const Config& c, int mode) : cfg(c) {
+    bk.mode = mode;
+    D = cfg.head_dim(); R = cfg.rotary_dimension(); Vp = cfg.padded_vocab(); KV = cfg.n_kv_head * D;
+    windows = cfg.windows();
+    auto add = [&](const std::string& name, int rows, int cols) {
+      Param p; p.rows = rows; p.cols = cols; p.w.assign((size_t)rows * cols, 0.0f); p.g.assign((size_t)rows * cols, 0.0f);
+      params[name] = std::move(p);
+    };
+    int d = cfg.embed_dim;
+    // model/params.go:14-74 names; shapes from model/transformer.go:49-83.
+    add("transformer.wte.weight", Vp, d);
+    add("lm_head.weight", Vp, d);
+    for (int l = 0; l < cfg.n_layer; ++l) {
+      std::string p = "transformer.h." + std::to_string(l) + ".";
+      add(p + "attn.c_q.weight", cfg.n_head * D, d);
+      add(p + "attn.c_k.weight", KV, d);
+      add(p + "attn.c_v.weight", KV, d);
+      add(p + "attn.c_proj.weight", d, d);
+      if (has_value_embedding(l, cfg.n_layer)) {
+        add(p + "attn.ve_gate.weight", cfg.n_kv_head, kVeGateChannels);
+        add("value_embeds." + std::to_string(l) + ".weight", Vp, KV);
+      }
+      add(p + "mlp.c_fc.weight", 4 * d, d);
+      add(p + "mlp.c_proj.weight", d, 4 * d);
+    }
+    add("resid_lambdas", 1, cfg.n_layer);
+    add("x0_lambdas", 1, cfg.n_layer);
+    add("smear_gate.weight", 1, kSmearChannels);
+    add("smear_lambda", 1, 1);
+    add("backout_lambda", 1, 1);
+    // model/rotary.go:16-30
+    int half = R / 2, seq = cfg.sequence_len * kRotaryOvercompute;
+    cosv.resize((size_t)seq * half); sinv.resize((size_t)seq * half);
+    for (int p = 0; p < seq; ++p)
+      for (int j = 0; j < half; ++j) {
+        double inv = std::pow(kRotaryBase, -2.0 * (double)j / (double)R);
+        double f = (double)p * inv;
+        cosv[(size_t)p * half + j] = (float)std::cos(f);
+        sinv[(size_t)p * half + j] = (float)std::sin(f);
+      }
+  }
+  Param& P(const std::string& n) { return params.at(n); }
+  std::string LP(int l, const char* s) const { return "transformer.h." + std::to_string(l) + "." + s; }
+  void zero_grad() { for (auto& kv : params) std::fill(kv.second.g.begin(), kv.second.g.end(), 0.0f); }
+
+  // ------------------------------------------------------------ primitives
+  void linear(std::vector<float>& out, const std::vector<float>& in, const Param& w, int64_t rows) const {
+    out.resize((size_t)rows * w.rows);
+    bk.matmul_t(out.data(), in.data(), w.w.data(), (int)rows, w.rows, w.cols);
+  }
+  // model/layers/linear.go:45-53: dW += dY^T X ; returns dX = dY W.
+  void linear_backward(std::vector<float>& dx, const std::vector<float>& x, const std::vector<float>& dy, Param& w, int64_t rows) const {
+    int out = w.rows, in = w.cols;
+    std::vector<float> dyT((size_t)out * rows), gw((size_t)out * in);
+    for (int64_t r = 0; r < rows; ++r) for (int o = 0; o < out; ++o) dyT[(size_t)o * rows + r] = dy[(size_t)r * out + o];
+    bk.matmul(gw.data(), dyT.data(), x.data(), out, in, (int)rows);
+    for (size_t i = 0; i < gw.size(); ++i) w.g[i] += gw[i];
+    dx.resize((size_t)rows * in);
+    bk.matmul(dx.data(), dy.data(), w.w.data(), (int)rows, in, out);
+  }
+  void norm(std::vector<float>& out, const std::vector<float>& in, int cols) const {
+    out.resize(in.size());
+    bk.rmsnorm_lastdim(out.data(), in.data(), (int64_t)(in.size() / cols), cols, kNormEps);
+  }
+  // tensors/backward.go:81-104
+  static void norm_backward(std::vector<float>& dx, const std::vector<float>& x, const std::vector<float>& dy, int cols) {
+    dx.resize(x.size());
+    int64_t rows = (int64_t)(x.size() / cols);
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; ++r) {
+      const float* xr = x.data() + r * cols; const float* gr = dy.data() + r * cols; float* o = dx.data() + r * cols;
+      double ss = 0, dp = 0;
+      for (int c = 0; c < cols; ++c) { ss += (double)xr[c] * (double)xr[c]; dp += (double)gr[c] * (double)xr[c]; }
+      double ms = ss / (double)cols;
+      double rms = std::sqrt(ms + (double)kNormEps);
+      double inv = 1.0 / rms;
+      double coef = dp / ((double)cols * rms * rms * rms);
+      for (int c = 0; c < cols; ++c) o[c] = (float)((double)gr[c] * inv - coef * (double)xr[c]);
+    }
+  }
+  void embedding(std::vector<float>& out, const Param& w, const int32_t* ids, int64_t n) const {
+    out.resize((size_t)n * w.cols);
+    for (int64_t i = 0; i < n; ++i) std::memcpy(out.data() + i * w.cols, w.w.data() + (int64_t)ids[i] * w.cols, sizeof(float) * w.cols);
+  }
+  // model/rotary.go:43-75 on [B,T,H,D]; sign = +1 forward, -1 backward (negated sine table, model/train.go:14-20).
+  void rotary(std::vector<float>& x, int B, int T, int H, int offset, float sign) const {
+    int half = R / 2, off = D - R;
+    for (int b = 0; b < B; ++b) for (int t = 0; t < T; ++t) {
+      int pos = offset + t;
+      const float* cw = cosv.data() + (size_t)pos * half; const float* sw = sinv.data() + (size_t)pos * half;
+      for (int h = 0; h < H; ++h) {
+        float* p = x.data() + (((size_t)b * T + t) * H + h) * D + off;
+        for (int j = 0; j < half; ++j) {
+          float a = p[j], c = p[half + j];
+          float s = sign * sw[j];
+          p[j] = a * cw[j] + c * s;
+          p[half + j] = -a * s + c * cw[j];
+        }
+      }
+    }
+  }
+  static void to_head_major(std::vector<float>& out, const std::vector<float>& in, int B, int T, int H, int D) {
+    out.resize(in.size());
+    for (int b = 0; b < B; ++b) for (int t = 0; t < T; ++t) for (int h = 0; h < H; ++h)
+      std::memcpy(out.data() + (((size_t)b * H + h) * T + t) * D, in.data() + (((size_t)b * T + t) * H + h) * D, sizeof(float) * D);
+  }
+  static void to_seq_major(std::vector<float>& out, const std::vector<float>& in, int B, int T, int H, int D) {
+    out.resize(in.size());
+    for (int b = 0; b < B; ++b) for (int t = 0; t < T; ++t) for (int h = 0; h < H; ++h)
+      std::memcpy(out.data() + (((size_t)b * T + t) * H + h) * D, in.data() + (((size_t)b * H + h) * T + t) * D, sizeof(float) * D);
+  }
+  // gate[b,t] = lambda * sigmoid(W_s . e[b,t][0:24])
+  float smear_gate_value(const float* e_row, float* sig_out) const {
+    const Param& ws = params.at("smear_gate.weight");
+    float pre = bk.dot(e_row, ws.w.data(), kSmearChannels);
+    float sig = (float)(1.0 / (1.0 + std::exp((double)(-pre))));
+    if (sig_out) *sig_out = sig;
+    return sig * params.at("smear_lambda").w[0];
+  }
+  // logits = softcap * tanh((y W_lm^T)[:, :V] / softcap)   (model/transformer.go:338-341, tensors/math.go:38-45)
+  void lm_head(std::vector<float>& logits, const std::vector<float>& y, int64_t rows) const {
+    const Param& w = params.at("lm_head.weight");
+    int V = cfg.vocab;
+    logits.resize((size_t)rows * V);
+    bk.matmul_t(logits.data(), y.data(), w.w.data(), (int)rows, V, cfg.embed_dim);  // first V rows of W = trimVocab
+    float inv = 1.0f / kSoftcap;
+    int64_t n = rows * V;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) {
+      float s = logits[i] * inv;
+      s = (float)std::tanh((double)s);
+      logits[i] = s * kSoftcap;
+    }
+  }
+
+  // ------------------------------------------------- inference forward
+  void cache_init(KVCache& c, int batch, int max_seq) const {
+    c.batch = batch; c.max_seq = max_seq; c.pos = 0; c.has_prev = false;
+    c.k.assign(cfg.n_layer, {}); c.v.assign(cfg.n_layer, {});
+    for (int l = 0; l < cfg.n_layer; ++l) {
+      c.k[l].assign((size_t)batch * cfg.n_kv_head, std::vector<float>((size_t)max_seq * D, 0.0f));
+      c.v[l].assign((size_t)batch * cfg.n_kv_head, std::vector<float>((size_t)max_seq * D, 0.0f));
+    }
+  }
+  // model/kvcache.go:383-448 (dense part)
+  void cache_replicate(KVCache& dst, const KVCache& src) const {
+    int pos = src.pos;
+    for (int l = 0; l < cfg.n_layer; ++l)
+      for (int row = 0; row < dst.batch; ++row)
+        for (int h = 0; h < cfg.n_kv_head; ++h) {
+          std::copy(src.k[l][h].begin(), src.k[l][h].begin() + (size_t)pos * D, dst.k[l][(size_t)row * cfg.n_kv_head + h].begin());
+          std::copy(src.v[l][h].begin(), src.v[l][h].begin() + (size_t)pos * D, dst.v[l][(size_t)row * cfg.n_kv_head + h].begin());
+        }
+    dst.pos = pos;
+    if (src.has_prev) {
+      int d = cfg.embed_dim;
+      dst.prev.resize((size_t)dst.batch * d);
+      for (int row = 0; row < dst.batch; ++row) std::copy(src.prev.begin(), src.prev.begin() + d, dst.prev.begin() + (size_t)row * d);
+      dst.has_prev = true;
+    }
+  }
+
+  // Returns logits [B,T,V].  cache may be null (then T must be > 1).
+  void forward(std::vector<float>& logits, const int32_t* ids, int B, int T, KVCache* cache) const {
+    int d = cfg.embed_dim, Hq = cfg.n_head, Hkv = cfg.n_kv_head, L = cfg.n_layer;
+    int64_t rows = (int64_t)B * T;
+    std::vector<float> raw, x;
+    embedding(raw, params.at("transformer.wte.weight"), ids, rows);
+    norm(x, raw, d);
+    int offset = cache ? cache->pos : 0;
+    // ---- smear (model/transformer.go:266-301)
+    std::vector<float> prev_in;
+    bool had_prev = false;
+    if (cache) {
+      had_prev = cache->has_prev;
+      if (had_prev) prev_in = cache->prev;
+      cache->prev.resize((size_t)B * d);
+      for (int b = 0; b < B; ++b) std::copy(x.begin() + ((size_t)b * T + T - 1) * d, x.begin() + ((size_t)b * T + T) * d, cache->prev.begin() + (size_t)b * d);
+      cache->has_prev = true;
+    }
+    if (T > 1) {
+      std::vector<float> gates((size_t)B * T, 0.0f);  // gate for t>=1 ; t=0 seed gate when had_prev
+      for (int b = 0; b < B; ++b) for (int t = 0; t < T; ++t)
+        if (t >= 1 || had_prev) gates[(size_t)b * T + t] = smear_gate_value(x.data() + ((size_t)b * T + t) * d, nullptr);
+      for (int b = 0; b < B; ++b) {
+        for (int t = T - 1; t >= 1; --t) {
+          float g = gates[(size_t)b * T + t];
+          float* cur = x.data() + ((size_t)b * T + t) * d; const float* pv = x.data() + ((size_t)b * T + t - 1) * d;
+          for (int c = 0; c < d; ++c) cur[c] += g * pv[c];
+        }
+        if (had_prev) {
+          float g = gates[(size_t)b * T];
+          float* cur = x.data() + (size_t)b * T * d; const float* pv = prev_in.data() + (size_t)b * d;
+          for (int c = 0; c < d; ++c) cur[c] += g * pv[c];
+        }
+      }
+    } else if (cache && had_prev) {
+      for (int b = 0; b < B; ++b) {
+        float g = smear_gate_value(x.data() + (size_t)b * d, nullptr);
+        float* cur = x.data() + (size_t)b * d; const float* pv = prev_in.data() + (size_t)b * d;
+        for (int c = 0; c < d; ++c) cur[c] += g * pv[c];
+      }
+    }
+    std::vector<float> x0 = x, backout;
+    const Param& rl = params.at("resid_lambdas"); const Param& xl = params.at("x0_lambdas");
+    for (int l = 0; l < L; ++l) {
+      for (size_t i = 0; i < x.size(); ++i) x[i] = rl.w[l] * x[i] + xl.w[l] * x0[i];
+      // ---- attention (model/attention.go:235-324)
+      std::vector<float> h, q, k, v;
+      norm(h, x, d);
+      linear(q, h, params.at(LP(l, "attn.c_q.weight")), rows);
+      linear(k, h, params.at(LP(l, "attn.c_k.weight")), rows);
+      linear(v, h, params.at(LP(l, "attn.c_v.weight")), rows);
+      if (has_value_embedding(l, L)) {
+        std::vector<float> ve;
+        embedding(ve, params.at("value_embeds." + std::to_string(l) + ".weight"), ids, rows);
+        const Param& wg = params.at(LP(l, "attn.ve_gate.weight"));
+        for (int64_t r = 0; r < rows; ++r) for (int hh = 0; hh < Hkv; ++hh) {
+          float pre = bk.dot(h.data() + r * d, wg.w.data() + (size_t)hh * kVeGateChannels, kVeGateChannels);
+          float gate = (float)(1.0 / (1.0 + std::exp((double)(-pre)))) * kVeGateScale;
+          float* vr = v.data() + (r * Hkv + hh) * D; const float* er = ve.data() + (r * Hkv + hh) * D;
+          for (int c = 0; c < D; ++c) vr[c] += gate * er[c];
+        }
+      }
+      rotary(q, B, T, Hq, offset, 1.0f);
+      rotary(k, B, T, Hkv, offset, 1.0f);
+      std::vector<float> qn, kn;
+      norm(qn, q, D); norm(kn, k, D);
+      for (auto& e : qn) e *= kQKScale;
+      for (auto& e : kn) e *= kQKScale;
+      std::vector<float> qh, kh, vh, oh((size_t)rows * Hq * D);
+      to_head_major(qh, qn, B, T, Hq, D); to_head_major(kh, kn, B, T, Hkv, D); to_head_major(vh, v, B, T, Hkv, D);
+      int klen = T;
+      if (cache) {
+        for (int b = 0; b < B; ++b) for (int hh = 0; hh < Hkv; ++hh) {
+          size_t slot = (size_t)b * Hkv + hh;
+          std::copy(kh.begin() + slot * T * D, kh.begin() + (slot + 1) * T * D, cache->k[l][slot].begin() + (size_t)offset * D);
+          std::copy(vh.begin() + slot * T * D, vh.begin() + (slot + 1) * T * D, cache->v[l][slot].begin() + (size_t)offset * D);
+        }
+        klen = offset + T;
+      }
+      int ratio = Hq / Hkv;
+#pragma omp parallel for schedule(static)
+      for (int idx = 0; idx < B * Hq; ++idx) {
+        int b = idx / Hq, hq = idx % Hq, hk = hq / ratio;
+        size_t slot = (size_t)b * Hkv + hk;
+        const float* kp = cache ? cache->k[l][slot].data() : kh.data() + slot * T * D;
+        const float* vp = cache ? cache->v[l][slot].data() : vh.data() + slot * T * D;
+        bk.attention_forward(qh.data() + (size_t)idx * T * D, kp, vp, T, klen, D, offset, windows[l], nullptr, 0,
+                             oh.data() + (size_t)idx * T * D, nullptr);
+      }
+      std::vector<float> os, ao;
+      to_seq_major(os, oh, B, T, Hq, D);
+      linear(ao, os, params.at(LP(l, "attn.c_proj.weight")), rows);
+      for (size_t i = 0; i < x.size(); ++i) x[i] = x[i] + ao[i];
+      // ---- MLP (model/mlp.go:62-76)
+      std::vector<float> m, u, fo;
+      norm(m, x, d);
+      linear(u, m, params.at(LP(l, "mlp.c_fc.weight")), rows);
+      bk.relu_squared(u.data(), u.data(), (int64_t)u.size());
+      linear(fo, u, params.at(LP(l, "mlp.c_proj.weight")), rows);
+      for (size_t i = 0; i < x.size(); ++i) x[i] = x[i] + fo[i];
+      if (l == L / 2) backout = x;
+    }
+    if (cache) cache->pos += T;
+    if (!backout.empty()) {
+      float lam = -params.at("backout_lambda").w[0];
+      for (size_t i = 0; i < x.size(); ++i) x[i] = x[i] + lam * backout[i];
+    }
+    std::vector<float> y;
+    norm(y, x, d);
+    lm_head(logits, y, rows);
+  }
+
+  // ------------------------------------------------- training forward
+  void train_forward(TrainCtx& ctx, const int32_t* ids, int B, int T) const {
+    int d = cfg.embed_dim, Hq = cfg.n_head, Hkv = cfg.n_kv_head, L = cfg.n_layer;
+    int64_t rows = (int64_t)B * T;
+    ctx.B = B; ctx.T = T; ctx.ids.assign(ids, ids + rows);
+    embedding(ctx.raw, params.at("transformer.wte.weight"), ids, rows);
+    std::vector<float> x;
+    norm(x, ctx.raw, d);
+    // smear gate input: channels 0..23 of rows 1..T-1 (pre-smear)
+    ctx.smear_slice.resize((size_t)B * (T - 1) * kSmearChannels);
+    ctx.smear_sig.resize((size_t)B * (T - 1));
+    std::vector<float> gates((size_t)B * (T - 1));
+    for (int b = 0; b < B; ++b) for (int t = 1; t < T; ++t) {
+      const float* er = x.data() + ((size_t)b * T + t) * d;
+      size_t gi = (size_t)b * (T - 1) + (t - 1);
+      std::copy(er, er + kSmearChannels, ctx.smear_slice.begin() + gi * kSmearChannels);
+      gates[gi] = smear_gate_value(er, &ctx.smear_sig[gi]);
+    }
+    for (int b = 0; b < B; ++b) for (int t = T - 1; t >= 1; --t) {
+      float g = gates[(size_t)b * (T - 1) + (t - 1)];
+      float* cur = x.data() + ((size_t)b * T + t) * d; const float* pv = x.data() + ((size_t)b * T + t - 1) * d;
+      for (int c = 0; c < d; ++c) cur[c] += g * pv[c];
+    }
+    // The reference stores `embeddedNormalized` as the same tensor object that
+    // smearAdd then modifies in place (model/train_transformer.go:75-83), so
+    // what smearBackward later reads as the "embedded" activations is the
+    // POST-smear tensor.  The oracle keeps that behaviour.
+    ctx.e_alias = x;
+    ctx.x0 = x;
+    ctx.layers.assign(L, LayerCtx());
+    const Param& rl = params.at("resid_lambdas"); const Param& xl = params.at("x0_lambdas");
+    int ratio = Hq / Hkv;
+    for (int l = 0; l < L; ++l) {
+      LayerCtx& c = ctx.layers[l];
+      c.prev_x = x;
+      for (size_t i = 0; i < x.size(); ++i) x[i] = rl.w[l] * x[i] + xl.w[l] * ctx.x0[i];
+      c.x_in = x;
+      norm(c.h, x, d);
+      std::vector<float> q, k, v;
+      linear(q, c.h, params.at(LP(l, "attn.c_q.weight")), rows);
+      linear(k, c.h, params.at(LP(l, "attn.c_k.weight")), rows);
+      linear(v, c.h, params.at(LP(l, "attn.c_v.weight")), rows);
+      if (has_value_embedding(l, L)) {
+        embedding(c.ve, params.at("value_embeds." + std::to_string(l) + ".weight"), ids, rows);
+        const Param& wg = params.at(LP(l, "attn.ve_gate.weight"));
+        c.ve_sig.resize((size_t)rows * Hkv);
+        for (int64_t r = 0; r < rows; ++r) for (int hh = 0; hh < Hkv; ++hh) {
+          float pre = bk.dot(c.h.data() + r * d, wg.w.data() + (size_t)hh * kVeGateChannels, kVeGateChannels);
+          float sig = (float)(1.0 / (1.0 + std::exp((double)(-pre))));
+          c.ve_sig[r * Hkv + hh] = sig;
+          float gate = sig * kVeGateScale;
+          float* vr = v.data() + (r * Hkv + hh) * D; const float* er = c.ve.data() + (r * Hkv + hh) * D;
+          for (int cc = 0; cc < D; ++cc) vr[cc] += gate * er[cc];
+        }
+      }
+      rotary(q, B, T, Hq, 0, 1.0f);
+      rotary(k, B, T, Hkv, 0, 1.0f);
+      c.q_rot = q; c.k_rot = k;
+      std::vector<float> qn, kn;
+      norm(qn, q, D); norm(kn, k, D);
+      for (auto& e : qn) e *= kQKScale;
+      for (auto& e : kn) e *= kQKScale;
+      to_head_major(c.q_hm, qn, B, T, Hq, D); to_head_major(c.k_hm, kn, B, T, Hkv, D); to_head_major(c.v_hm, v, B, T, Hkv, D);
+      c.o_hm.assign((size_t)rows * Hq * D, 0.0f);
+      c.lse.assign((size_t)B * Hq * T, 0.0f);
+#pragma omp parallel for schedule(static)
+      for (int idx = 0; idx < B * Hq; ++idx) {
+        int b = idx / Hq, hq = idx % Hq, hk = hq / ratio;
+        size_t slot = (size_t)b * Hkv + hk;
+        bk.attention_forward(c.q_hm.data() + (size_t)idx * T * D, c.k_hm.data() + slot * T * D, c.v_hm.data() + slot * T * D,
+                             T, T, D, 0, windows[l], nullptr, 0, c.o_hm.data() + (size_t)idx * T * D, c.lse.data() + (size_t)idx * T);
+      }
+      std::vector<float> os, ao;
+      to_seq_major(os, c.o_hm, B, T, Hq, D);
+      linear(ao, os, params.at(LP(l, "attn.c_proj.weight")), rows);
+      c.mid.resize(x.size());
+      for (size_t i = 0; i < x.size(); ++i) c.mid[i] = x[i] + ao[i];
+      norm(c.m, c.mid, d);
+      linear(c.u, c.m, params.at(LP(l, "mlp.c_fc.weight")), rows);
+      c.hid.resize(c.u.size());
+      bk.relu_squared(c.hid.data(), c.u.data(), (int64_t)c.u.size());
+      std::vector<float> fo;
+      linear(fo, c.hid, params.at(LP(l, "mlp.c_proj.weight")), rows);
+      for (size_t i = 0; i < x.size(); ++i) x[i] = c.mid[i] + fo[i];
+      if (l == L / 2) ctx.backout = x;
+    }
+    if (!ctx.backout.empty()) {
+      float lam = -params.at("backout_lambda").w[0];
+      for (size_t i = 0; i < x.size(); ++i) x[i] = x[i] + lam * ctx.backout[i];
+    }
+    ctx.final_pre = x;
+    norm(ctx.final_norm, x, d);
+    lm_head(ctx.logits, ctx.final_norm, rows);
+  }
+
+  // ------------------------------------------------- training backward
+  // dlogits: [B*T, V] gradient at the softcapped logits.
+  void train_backward(TrainCtx& ctx, const std::vector<float>& dlogits) {
+    int d = cfg.embed_dim, Hq = cfg.n_head, Hkv = cfg.n_kv_head, L = cfg.n_layer, V = cfg.vocab, B = ctx.B, T = ctx.T;
+    int64_t rows = (int64_t)B * T;
+    int ratio = Hq / Hkv;
+    // SoftcapBackward (tensors/backward.go:108-116) then zero-pad to Vp (train_transformer.go:149-153)
+    std::vector<float> gpad((size_t)rows * Vp, 0.0f);
+    float invcap = 1.0f / kSoftcap;
+    for (int64_t r = 0; r < rows; ++r) for (int v = 0; v < V; ++v) {
+      double sc = (double)ctx.logits[(size_t)r * V + v] * (double)invcap;
+      gpad[(size_t)r * Vp + v] = dlogits[(size_t)r * V + v] * (float)(1 - sc * sc);
+    }
+    std::vector<float> dy, dx;
+    linear_backward(dy, ctx.final_norm, gpad, P("lm_head.weight"), rows);
+    norm_backward(dx, ctx.final_pre, dy, d);
+    std::vector<float> dbackout;
+    if (!ctx.backout.empty()) {
+      float lam = P("backout_lambda").w[0];
+      dbackout.resize(dx.size());
+      double dot = 0;
+      for (size_t i = 0; i < dx.size(); ++i) { dbackout[i] = dx[i] * (-lam); dot += (double)dx[i] * (double)(-ctx.backout[i]); }
+      P("backout_lambda").g[0] += (float)dot;
+    }
+    std::vector<float> dx0((size_t)rows * d, 0.0f);
+    for (int l = L - 1; l >= 0; --l) {
+      LayerCtx& c = ctx.layers[l];
+      std::vector<float> dout = dx;
+      if (l == L / 2 && !dbackout.empty()) for (size_t i = 0; i < dout.size(); ++i) dout[i] = dx[i] + dbackout[i];
+      // ---- block backward (model/train.go:554-572)
+      // MLP backward (model/train.go:505-514)
+      std::vector<float> dhid, dm, dmid;
+      linear_backward(dhid, c.hid, dout, P(LP(l, "mlp.c_proj.weight")), rows);
+      std::vector<float> du(dhid.size(), 0.0f);
+      for (size_t i = 0; i < du.size(); ++i) if (c.u[i] > 0) du[i] = dhid[i] * 2 * c.u[i];   // tensors/backward.go:57-65
+      linear_backward(dm, c.m, du, P(LP(l, "mlp.c_fc.weight")), rows);
+      std::vector<float> nb;
+      norm_backward(nb, c.mid, dm, d);
+      dmid.resize(dout.size());
+      for (size_t i = 0; i < dmid.size(); ++i) dmid[i] = dout[i] + nb[i];
+      // ---- attention backward (model/train.go:198-427)
+      std::vector<float> os, dos, doh;
+      to_seq_major(os, c.o_hm, B, T, Hq, D);
+      linear_backward(dos, os, dmid, P(LP(l, "attn.c_proj.weight")), rows);
+      to_head_major(doh, dos, B, T, Hq, D);
+      std::vector<float> dq((size_t)rows * Hq * D, 0.0f), dk((size_t)rows * Hkv * D, 0.0f), dv((size_t)rows * Hkv * D, 0.0f);
+      // Sequential over (batch, head) as in the reference: K/V gradients of a
+      // shared kv head accumulate in query-head order.
+      for (int b = 0; b < B; ++b) for (int hq = 0; hq < Hq; ++hq) {
+        int hk = hq / ratio; size_t idx = (size_t)b * Hq + hq, slot = (size_t)b * Hkv + hk;
+        bk.attention_backward(c.q_hm.data() + idx * T * D, c.k_hm.data() + slot * T * D, c.v_hm.data() + slot * T * D,
+                              doh.data() + idx * T * D, c.lse.data() + idx * T, nullptr, T, T, D, 0, windows[l], nullptr, 0,
+                              dq.data() + idx * T * D, dk.data() + slot * T * D, dv.data() + slot * T * D);
+      }
+      for (auto& e : dq) e *= kQKScale;
+      for (auto& e : dk) e *= kQKScale;
+      std::vector<float> dqs, dks, dvs, dqp, dkp;
+      to_seq_major(dqs, dq, B, T, Hq, D); to_seq_major(dks, dk, B, T, Hkv, D); to_seq_major(dvs, dv, B, T, Hkv, D);
+      norm_backward(dqp, c.q_rot, dqs, D);
+      norm_backward(dkp, c.k_rot, dks, D);
+      rotary(dqp, B, T, Hq, 0, -1.0f);
+      rotary(dkp, B, T, Hkv, 0, -1.0f);
+      std::vector<float> dh, t1;
+      linear_backward(dh, c.h, dqp, P(LP(l, "attn.c_q.weight")), rows);
+      linear_backward(t1, c.h, dkp, P(LP(l, "attn.c_k.weight")), rows);
+      for (size_t i = 0; i < dh.size(); ++i) dh[i] = dh[i] + t1[i];
+      linear_backward(t1, c.h, dvs, P(LP(l, "attn.c_v.weight")), rows);
+      for (size_t i = 0; i < dh.size(); ++i) dh[i] = dh[i] + t1[i];
+      if (!c.ve.empty()) {
+        // model/train.go:375-409
+        Param& wg = P(LP(l, "attn.ve_gate.weight"));
+        Param& vew = P("value_embeds." + std::to_string(l) + ".weight");
+        std::vector<float> dve((size_t)rows * KV), dpre((size_t)rows * Hkv);
+        for (int64_t r = 0; r < rows * Hkv; ++r) {
+          float scale = c.ve_sig[r] * kVeGateScale;
+          double dp = 0;
+          for (int cc = 0; cc < D; ++cc) {
+            dve[(size_t)r * D + cc] = dvs[(size_t)r * D + cc] * scale;
+            dp += (double)dvs[(size_t)r * D + cc] * (double)c.ve[(size_t)r * D + cc];
+          }
+          float dgate = (float)dp;
+          float dsig = dgate * kVeGateScale;
+          float sig = c.ve_sig[r];
+          dpre[r] = dsig * sig * (1 - sig);
+        }
+        std::vector<float> slice((size_t)rows * kVeGateChannels), dslice;
+        for (int64_t r = 0; r < rows; ++r) std::copy(c.h.begin() + r * d, c.h.begin() + r * d + kVeGateChannels, slice.begin() + r * kVeGateChannels);
+        linear_backward(dslice, slice, dpre, wg, rows);
+        for (int64_t r = 0; r < rows; ++r) for (int cc = 0; cc < kVeGateChannels; ++cc) dh[(size_t)r * d + cc] = dh[(size_t)r * d + cc] + dslice[(size_t)r * kVeGateChannels + cc];
+        // value_embeds scatter-add by token id (train_transformer.go:213-216, layers/linear.go:90-104)
+        for (int64_t r = 0; r < rows; ++r) {
+          float* gr = vew.g.data() + (size_t)ctx.ids[r] * KV;
+          for (int cc = 0; cc < KV; ++cc) gr[cc] += dve[(size_t)r * KV + cc];
+        }
+      }
+      std::vector<float> din;
+      norm_backward(din, c.x_in, dh, d);
+      for (size_t i = 0; i < din.size(); ++i) din[i] = din[i] + dmid[i];
+      // ---- residual mix (train_transformer.go:218-242)
+      float rw = P("resid_lambdas").w[l], xw = P("x0_lambdas").w[l];
+      double rdot = 0, xdot = 0;
+      for (size_t i = 0; i < din.size(); ++i) { rdot += (double)din[i] * (double)c.prev_x[i]; xdot += (double)din[i] * (double)ctx.x0[i]; }
+      P("resid_lambdas").g[l] += (float)rdot;
+      P("x0_lambdas").g[l] += (float)xdot;
+      dx.resize(din.size());
+      for (size_t i = 0; i < din.size(); ++i) { dx[i] = din[i] * rw; dx0[i] = dx0[i] + xw * din[i]; }
+    }
+    for (size_t i = 0; i < dx.size(); ++i) dx[i] = dx[i] + dx0[i];
+    // ---- smear backward (train_transformer.go:269-305)
+    float lam = P("smear_lambda").w[0];
+    std::vector<float> de((size_t)rows * d, 0.0f), dgate((size_t)B * (T - 1), 0.0f);
+    double dlam = 0;
+    for (int b = 0; b < B; ++b) for (int t = 0; t < T; ++t) {
+      size_t base = ((size_t)b * T + t) * d;
+      if (t == 0) { for (int c = 0; c < d; ++c) de[base + c] += dx[base + c]; continue; }
+      size_t gi = (size_t)b * (T - 1) + (t - 1), pb = base - d;
+      float gv = lam * ctx.smear_sig[gi];
+      double gs = 0;
+      for (int c = 0; c < d; ++c) {
+        de[base + c] += dx[base + c];
+        de[pb + c] += dx[base + c] * gv;
+        gs += (double)dx[base + c] * (double)ctx.e_alias[pb + c];
+      }
+      float sg = ctx.smear_sig[gi];
+      dlam += gs * (double)sg;
+      dgate[gi] = (float)(gs * (double)lam) * sg * (1 - sg);
+    }
+    P("smear_lambda").g[0] += (float)dlam;
+    std::vector<float> dslice;
+    linear_backward(dslice, ctx.smear_slice, dgate, P("smear_gate.weight"), (int64_t)B * (T - 1));
+    for (int b = 0; b < B; ++b) for (int t = 1; t < T; ++t) for (int c = 0; c < kSmearChannels; ++c)
+      de[((size_t)b * T + t) * d + c] += dslice[((size_t)b * (T - 1) + (t - 1)) * kSmearChannels + c];
+    std::vector<float> draw;
+    norm_backward(draw, ctx.raw, de, d);
+    Param& wte = P("transformer.wte.weight");
+    for (int64_t r = 0; r < rows; ++r) {
+      float* gr = wte.g.data() + (size_t)ctx.ids[r] * d;
+      for (int c = 0; c < d; ++c) gr[c] += draw[(size_t)r * d + c];
+    }
+  }
+};
+
+}  // namespace gnor

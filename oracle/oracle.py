@@ -1,0 +1,474 @@
+"""ctypes binding of the CPU oracle (``oracle/gn_oracle.cpp``).
+
+TEST INFRASTRUCTURE ONLY: imported by tests, by the smoke check and by the
+benchmark's CPU-baseline leg, never by the product package.
+
+``mode`` selects the flavour everywhere: 0 = restatement of the reference's
+``kernels/scalar`` backend (float64 accumulation; the parity oracle), 1 =
+restatement of the structure of ``kernels/simd`` (float32 lanes, polynomial
+exp; the timed CPU baseline).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+_HERE = Path(__file__).resolve().parent
+_BUILD = _HERE / "_build"
+
+f32p = C.POINTER(C.c_float)
+i32p = C.POINTER(C.c_int32)
+u64p = C.POINTER(C.c_uint64)
+
+
+def build(force: bool = False) -> None:
+    """Compile the oracle with the committed Makefile (g++, OpenMP)."""
+    if force:
+        subprocess.run(["make", "-C", str(_HERE), "clean"], check=True, capture_output=True)
+    subprocess.run(["make", "-C", str(_HERE)], check=True, capture_output=True)
+
+
+def _has_avx512() -> bool:
+    try:
+        with open("/proc/cpuinfo") as handle:
+            for line in handle:
+                if line.startswith("flags"):
+                    flags = set(line.split(":", 1)[1].split())
+                    return {"avx512f", "avx512bw", "avx512dq", "avx512vl", "avx512cd"} <= flags
+    except OSError:
+        pass
+    return False
+
+
+def isa() -> str:
+    return "avx512" if _has_avx512() else "avx2"
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    name = "libgnoracle_v4.so" if _has_avx512() else "libgnoracle_v3.so"
+    path = _BUILD / name
+    if not path.exists():
+        build()
+    _lib = C.CDLL(str(path))
+    _declare(_lib)
+    return _lib
+
+
+class OrConfig(C.Structure):
+    _fields_ = [
+        ("sequence_len", C.c_int32), ("vocab_size", C.c_int32), ("n_layer", C.c_int32), ("n_head", C.c_int32),
+        ("n_kv_head", C.c_int32), ("embed_dim", C.c_int32), ("rotary_dims", C.c_int32), ("window_pattern", C.c_char * 16),
+    ]
+
+
+def _declare(l: C.CDLL) -> None:
+    l.or_num_threads.restype = C.c_int
+    l.or_sum.restype = C.c_float
+    l.or_max.restype = C.c_float
+    l.or_dot.restype = C.c_float
+    l.or_argmax.restype = C.c_int64
+    l.or_kth_largest.restype = C.c_float
+    l.or_sampler_uniform.restype = C.c_float
+    l.or_sampler_uniform.argtypes = [C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32]
+    l.or_reward_uniform.restype = C.c_float
+    l.or_reward_uniform.argtypes = [C.c_uint64, C.c_uint32]
+    l.or_cross_entropy_per_position.restype = C.c_int64
+    l.or_model_create.restype = C.c_void_p
+    l.or_model_param_name.restype = C.c_char_p
+    l.or_model_param_numel.restype = C.c_int64
+    l.or_model_param_data.restype = f32p
+    l.or_model_param_grad.restype = f32p
+    l.or_cache_create.restype = C.c_void_p
+    l.or_policy_gradient_step.restype = C.c_float
+    l.or_pg_loss_backward.restype = C.c_double
+
+
+def _f(a):
+    return a.ctypes.data_as(f32p)
+
+
+def _i(a):
+    return a.ctypes.data_as(i32p)
+
+
+def f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def i32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+def num_threads() -> int:
+    return int(lib().or_num_threads())
+
+
+def set_threads(n: int) -> None:
+    lib().or_set_threads(C.c_int(n))
+
+
+# --------------------------------------------------------------------------
+# kerneltest fixtures (kernels/kerneltest/compare.go:12-51)
+# --------------------------------------------------------------------------
+def kt_data(count: int) -> np.ndarray:
+    idx = np.arange(count)
+    return ((idx % 7).astype(np.float32) - np.float32(3.5) + np.float32(0.1) * (idx % 3).astype(np.float32)).astype(np.float32)
+
+
+def kt_data_b(count: int) -> np.ndarray:
+    idx = np.arange(count)
+    return ((idx % 5).astype(np.float32) + np.float32(0.5)).astype(np.float32)
+
+
+def kt_close(got, want, rel, floor) -> np.ndarray:
+    got = np.asarray(got, dtype=np.float32)
+    want = np.asarray(want, dtype=np.float32)
+    diff = np.abs(got - want)
+    scale = np.maximum(np.abs(want), 1.0)
+    return diff <= floor + rel * scale
+
+
+# --------------------------------------------------------------------------
+# Backend (kernels/backend.go).  Names follow the Go methods in snake case.
+# --------------------------------------------------------------------------
+class Backend:
+    def __init__(self, mode: int = 0):
+        self.mode = mode
+        self.l = lib()
+
+    def _binary(self, fn, a, b):
+        a, b = f32(a), f32(b)
+        d = np.empty_like(a)
+        fn(self.mode, _f(d), _f(a), _f(b), C.c_int64(a.size))
+        return d
+
+    def _unary(self, fn, a):
+        a = f32(a)
+        d = np.empty_like(a)
+        fn(self.mode, _f(d), _f(a), C.c_int64(a.size))
+        return d
+
+    def add(self, a, b): return self._binary(self.l.or_add, a, b)
+    def subtract(self, a, b): return self._binary(self.l.or_subtract, a, b)
+    def multiply(self, a, b): return self._binary(self.l.or_multiply, a, b)
+    def divide(self, a, b): return self._binary(self.l.or_divide, a, b)
+    def negate(self, a): return self._unary(self.l.or_negate, a)
+    def abs(self, a): return self._unary(self.l.or_abs, a)
+    def square(self, a): return self._unary(self.l.or_square, a)
+    def relu_squared(self, a): return self._unary(self.l.or_relu_squared, a)
+    def exp(self, a): return self._unary(self.l.or_exp, a)
+    def sigmoid(self, a): return self._unary(self.l.or_sigmoid, a)
+    def tanh(self, a): return self._unary(self.l.or_tanh, a)
+    def rsqrt(self, a): return self._unary(self.l.or_rsqrt, a)
+
+    def scale(self, a, factor):
+        a = f32(a); d = np.empty_like(a)
+        self.l.or_scale(self.mode, _f(d), _f(a), C.c_float(factor), C.c_int64(a.size)); return d
+
+    def add_scaled(self, base, scaled, factor):
+        base, scaled = f32(base), f32(scaled); d = np.empty_like(base)
+        self.l.or_add_scaled(self.mode, _f(d), _f(base), _f(scaled), C.c_float(factor), C.c_int64(base.size)); return d
+
+    def swiglu(self, gate, up, clamp):
+        gate, up = f32(gate), f32(up); d = np.empty_like(gate)
+        self.l.or_swiglu(self.mode, _f(d), _f(gate), _f(up), C.c_float(clamp), C.c_int64(gate.size)); return d
+
+    def swiglu_backward(self, gate, up, out_grad, clamp):
+        gate, up, out_grad = f32(gate), f32(up), f32(out_grad)
+        gg, ug = np.empty_like(gate), np.empty_like(gate)
+        self.l.or_swiglu_backward(self.mode, _f(gg), _f(ug), _f(gate), _f(up), _f(out_grad), C.c_float(clamp), C.c_int64(gate.size))
+        return gg, ug
+
+    def sum(self, v): v = f32(v); return float(self.l.or_sum(self.mode, _f(v), C.c_int64(v.size)))
+    def max(self, v): v = f32(v); return float(self.l.or_max(self.mode, _f(v), C.c_int64(v.size)))
+    def argmax(self, v): v = f32(v); return int(self.l.or_argmax(self.mode, _f(v), C.c_int64(v.size)))
+
+    def dot_product(self, a, b):
+        a, b = f32(a), f32(b)
+        return float(self.l.or_dot(self.mode, _f(a), _f(b), C.c_int64(min(a.size, b.size))))
+
+    def matmul(self, left, right, rows, cols, inner):
+        left, right = f32(left), f32(right); d = np.empty(rows * cols, np.float32)
+        self.l.or_matmul(self.mode, _f(d), _f(left), _f(right), rows, cols, inner); return d
+
+    def matmul_transposed(self, left, right, rows, cols, inner):
+        left, right = f32(left), f32(right); d = np.empty(rows * cols, np.float32)
+        self.l.or_matmul_transposed(self.mode, _f(d), _f(left), _f(right), rows, cols, inner); return d
+
+    def softmax_last_dim(self, src, rows, cols):
+        src = f32(src); d = np.empty(rows * cols, np.float32)
+        self.l.or_softmax_lastdim(self.mode, _f(d), _f(src), C.c_int64(rows), cols); return d
+
+    def rmsnorm_last_dim(self, src, rows, cols, eps):
+        src = f32(src); d = np.empty(rows * cols, np.float32)
+        self.l.or_rmsnorm_lastdim(self.mode, _f(d), _f(src), C.c_int64(rows), cols, C.c_float(eps)); return d
+
+    def topk_indices(self, scores, rows, count, k):
+        scores = f32(scores); d = np.zeros(rows * k, np.int32)
+        self.l.or_topk_indices(self.mode, _i(d), _f(scores), rows, count, k); return d
+
+    def moe_gate_topk(self, logits, bias, rows, experts, k):
+        logits, bias = f32(logits), f32(bias)
+        probs = np.empty(rows * experts, np.float32); sel = np.zeros(rows * k, np.int32); w = np.zeros(rows * k, np.float32)
+        self.l.or_moe_gate_topk(self.mode, _f(logits), _f(bias), _f(probs), _i(sel), _f(w), rows, experts, k)
+        return probs, sel, w
+
+    def grouped_matmul_transposed(self, inp, weight, counts, experts, cols, inner):
+        inp, weight, counts = f32(inp), f32(weight), i32(counts)
+        d = np.zeros(int(counts.sum()) * cols, np.float32)
+        self.l.or_grouped_matmul_transposed(self.mode, _f(d), _f(inp), _f(weight), _i(counts), experts, cols, inner); return d
+
+    def indexer_scores(self, q, k, w, rows, blocks, heads, dim):
+        q, k, w = f32(q), f32(k), f32(w); d = np.empty(rows * blocks, np.float32)
+        self.l.or_indexer_scores(self.mode, _f(d), _f(q), _f(k), _f(w), rows, blocks, heads, dim); return d
+
+    def indexer_block_max(self, scores, rows, blocks, group):
+        scores = f32(scores); groups = (blocks + max(group, 1) - 1) // max(group, 1)
+        d = np.empty(rows * groups, np.float32)
+        self.l.or_indexer_block_max(self.mode, _f(d), _f(scores), rows, blocks, group); return d
+
+    def attention_forward(self, q, k, v, ql, kl, hd, offset, window, segments=None):
+        q, k, v = f32(q), f32(k), f32(v)
+        out = np.empty(ql * hd, np.float32); lse = np.empty(ql, np.float32)
+        seg = i32(segments) if segments is not None else None
+        self.l.or_attention_forward(self.mode, _f(q), _f(k), _f(v), ql, kl, hd, offset, window,
+                                    _i(seg) if seg is not None else None, 0 if seg is None else seg.size, _f(out), _f(lse))
+        return out, lse
+
+    def attention_forward_split(self, q, k, v, ql, kl, hd, offset, window, kstart, kend, segments=None):
+        q, k, v = f32(q), f32(k), f32(v)
+        acc = np.empty(ql * hd, np.float32); mx = np.empty(ql, np.float32); sm = np.empty(ql, np.float32)
+        seg = i32(segments) if segments is not None else None
+        self.l.or_attention_forward_split(self.mode, _f(q), _f(k), _f(v), ql, kl, hd, offset, window, kstart, kend,
+                                          _i(seg) if seg is not None else None, 0 if seg is None else seg.size, _f(acc), _f(mx), _f(sm))
+        return acc, mx, sm
+
+    def attention_combine(self, accs, mxs, sms, ql, hd):
+        acc = f32(np.stack(accs)); mx = f32(np.stack(mxs)); sm = f32(np.stack(sms))
+        out = np.empty(ql * hd, np.float32); lse = np.empty(ql, np.float32)
+        self.l.or_attention_combine(self.mode, _f(acc), _f(mx), _f(sm), len(accs), ql, hd, _f(out), _f(lse))
+        return out, lse
+
+    def attention_backward(self, q, k, v, dout, lse, ql, kl, hd, offset, window, row_correction=None, segments=None,
+                           dq=None, dk=None, dv=None):
+        q, k, v, dout, lse = f32(q), f32(k), f32(v), f32(dout), f32(lse)
+        dq = np.zeros(ql * hd, np.float32) if dq is None else f32(dq).copy()
+        dk = np.zeros(kl * hd, np.float32) if dk is None else f32(dk).copy()
+        dv = np.zeros(kl * hd, np.float32) if dv is None else f32(dv).copy()
+        rc = f32(row_correction) if row_correction is not None else None
+        seg = i32(segments) if segments is not None else None
+        self.l.or_attention_backward(self.mode, _f(q), _f(k), _f(v), _f(dout), _f(lse), _f(rc) if rc is not None else None,
+                                     ql, kl, hd, offset, window, _i(seg) if seg is not None else None,
+                                     0 if seg is None else seg.size, _f(dq), _f(dk), _f(dv))
+        return dq, dk, dv
+
+
+# --------------------------------------------------------------------------
+# tensors-level functions
+# --------------------------------------------------------------------------
+def cross_entropy_per_position(logits, targets, ignore=-1, mode=0):
+    logits = f32(logits); targets = i32(targets)
+    rows, vocab = logits.shape
+    losses = np.empty(rows, np.float32)
+    valid = lib().or_cross_entropy_per_position(mode, _f(logits), _i(targets), C.c_int64(rows), vocab, ignore, _f(losses))
+    return losses, int(valid)
+
+
+def cross_entropy_grad(logits, targets, ignore=-1, scale=1.0, mode=0):
+    logits = f32(logits); targets = i32(targets)
+    rows, vocab = logits.shape
+    grad = np.empty((rows, vocab), np.float32)
+    lib().or_cross_entropy_grad(mode, _f(logits), _i(targets), C.c_int64(rows), vocab, ignore, C.c_float(scale), _f(grad))
+    return grad
+
+
+def softcap(x, cap=15.0):
+    x = f32(x); d = np.empty_like(x); lib().or_softcap(_f(d), _f(x), C.c_float(cap), C.c_int64(x.size)); return d
+
+
+def softcap_backward(out, gout, cap=15.0):
+    out, gout = f32(out), f32(gout); d = np.empty_like(out)
+    lib().or_softcap_backward(_f(d), _f(out), _f(gout), C.c_float(cap), C.c_int64(out.size)); return d
+
+
+def relu_squared_backward(inp, gout):
+    inp, gout = f32(inp), f32(gout); d = np.empty_like(inp)
+    lib().or_relu_squared_backward(_f(d), _f(inp), _f(gout), C.c_int64(inp.size)); return d
+
+
+def rmsnorm_backward(inp, gout, eps=1e-6):
+    inp, gout = f32(inp), f32(gout); d = np.empty_like(inp)
+    rows, cols = inp.reshape(-1, inp.shape[-1]).shape
+    lib().or_rmsnorm_backward(_f(d), _f(inp), _f(gout), C.c_int64(rows), cols, C.c_float(eps)); return d
+
+
+def sigmoid_backward(out, gout):
+    out, gout = f32(out), f32(gout); d = np.empty_like(out)
+    lib().or_sigmoid_backward(_f(d), _f(out), _f(gout), C.c_int64(out.size)); return d
+
+
+def sample_next_token(logits, temperature, top_k, uniforms=None, seeds=None, group=1, step=0):
+    logits = f32(logits)
+    rows, vocab = logits.shape
+    out = np.empty(rows, np.int32)
+    u = f32(uniforms) if uniforms is not None else None
+    s = np.ascontiguousarray(seeds, dtype=np.uint64) if seeds is not None else None
+    lib().or_sample_next_token(_f(logits), rows, vocab, _f(u) if u is not None else None,
+                               s.ctypes.data_as(u64p) if s is not None else None, group, C.c_uint32(step),
+                               C.c_float(temperature), top_k, _i(out))
+    return out
+
+
+def kth_largest(values, rank):
+    values = f32(values)
+    return float(lib().or_kth_largest(_f(values), values.size, rank))
+
+
+def sampler_uniform(seed, step, row, col):
+    return float(lib().or_sampler_uniform(seed, step, row, col))
+
+
+def reward_uniform(seed, rollout):
+    return float(lib().or_reward_uniform(seed, rollout))
+
+
+def philox(c, k):
+    out = (C.c_uint32 * 4)()
+    lib().or_philox(C.c_uint32(c[0]), C.c_uint32(c[1]), C.c_uint32(c[2]), C.c_uint32(c[3]), C.c_uint32(k[0]), C.c_uint32(k[1]), out)
+    return [int(x) for x in out]
+
+
+def rotary_tables(x, cos, sin, B, T, H, D, offset):
+    x = f32(x).copy(); cos, sin = f32(cos), f32(sin)
+    half = cos.shape[-1]
+    lib().or_rotary_tables(_f(x), _f(cos), _f(sin), half, B, T, H, D, offset)
+    return x
+
+
+def advantage(rewards, group, mode=0):
+    rewards = f32(rewards); adv = np.empty_like(rewards)
+    lib().or_advantage(_f(rewards), rewards.size // group, group, mode, _f(adv)); return adv
+
+
+def build_batch(tokens, lengths, prompt_lengths, pad_token):
+    tokens = i32(tokens); lengths = i32(lengths); prompt_lengths = i32(prompt_lengths)
+    n, stride = tokens.shape
+    max_len = int(lengths.max())
+    inputs = np.empty((n, max_len - 1), np.int32); targets = np.empty((n, max_len - 1), np.int32)
+    got = lib().or_build_batch(_i(tokens), _i(lengths), _i(prompt_lengths), n, stride, pad_token, _i(inputs), _i(targets))
+    assert got == max_len
+    return inputs, targets, max_len
+
+
+def pg_loss_backward(logits, targets, adv, seq_len, norm, mode=0, want_grad=True):
+    logits = f32(logits); targets = i32(targets); adv = f32(adv)
+    rows, vocab = logits.shape
+    nll = np.empty(rows, np.float32)
+    grad = np.empty((rows, vocab), np.float32) if want_grad else None
+    loss = lib().or_pg_loss_backward(mode, _f(logits), _i(targets), _f(adv), C.c_int64(rows), vocab, seq_len, C.c_float(norm),
+                                     _f(nll), _f(grad) if want_grad else None)
+    return float(loss), nll, grad
+
+
+# --------------------------------------------------------------------------
+# Model
+# --------------------------------------------------------------------------
+class Model:
+    def __init__(self, sequence_len, vocab_size, n_layer, n_head, n_kv_head, embed_dim, rotary_dims=0, window_pattern="L", mode=0):
+        self.l = lib()
+        self.cfg = OrConfig(sequence_len, vocab_size, n_layer, n_head, n_kv_head, embed_dim, rotary_dims, window_pattern.encode())
+        self.h = C.c_void_p(self.l.or_model_create(C.byref(self.cfg), mode))
+        self.vocab = vocab_size
+        self.names = [self.l.or_model_param_name(self.h, i).decode() for i in range(self.l.or_model_param_count(self.h))]
+
+    def __del__(self):
+        try:
+            self.l.or_model_destroy(self.h)
+        except Exception:
+            pass
+
+    def shape(self, name):
+        r, c = C.c_int(), C.c_int()
+        self.l.or_model_param_shape(self.h, name.encode(), C.byref(r), C.byref(c))
+        return r.value, c.value
+
+    def param(self, name) -> np.ndarray:
+        n = self.l.or_model_param_numel(self.h, name.encode())
+        return np.ctypeslib.as_array(self.l.or_model_param_data(self.h, name.encode()), shape=(n,))
+
+    def grad(self, name) -> np.ndarray:
+        n = self.l.or_model_param_numel(self.h, name.encode())
+        return np.ctypeslib.as_array(self.l.or_model_param_grad(self.h, name.encode()), shape=(n,))
+
+    def zero_grad(self):
+        self.l.or_model_zero_grad(self.h)
+
+    def window_sizes(self):
+        out = np.zeros(self.cfg.n_layer, np.int32); self.l.or_model_window_sizes(self.h, _i(out)); return out
+
+    def padded_vocab(self):
+        return int(self.l.or_model_padded_vocab(self.h))
+
+    def forward(self, ids):
+        ids = i32(ids); B, T = ids.shape
+        logits = np.empty((B, T, self.vocab), np.float32)
+        self.l.or_model_forward(self.h, _i(ids), B, T, _f(logits)); return logits
+
+    def train_forward(self, ids):
+        ids = i32(ids); B, T = ids.shape
+        logits = np.empty((B * T, self.vocab), np.float32)
+        self.l.or_train_forward(self.h, _i(ids), B, T, _f(logits)); return logits
+
+    def cache(self, batch, max_seq):
+        return Cache(self, batch, max_seq)
+
+    def forward_cached(self, cache, ids):
+        ids = i32(ids); B, T = ids.shape
+        logits = np.empty((B, T, self.vocab), np.float32)
+        self.l.or_model_forward_cached(self.h, cache.h, _i(ids), B, T, _f(logits)); return logits
+
+    def generate(self, prompt, group, max_tokens, temperature, top_k, seed, want_logits=False):
+        prompt = i32(prompt)
+        toks = np.zeros((group, max_tokens), np.int32); lens = np.zeros(group, np.int32)
+        sl = np.zeros((max_tokens, group, self.vocab), np.float32) if want_logits else None
+        steps = self.l.or_generate(self.h, _i(prompt), prompt.size, group, max_tokens, C.c_float(temperature), top_k,
+                                   C.c_uint64(seed), _i(toks), _i(lens), _f(sl) if want_logits else None)
+        return toks, lens, int(steps), sl
+
+    def policy_gradient_step(self, inputs, targets, adv, norm, taps=False):
+        inputs, targets, adv = i32(inputs), i32(targets), f32(adv)
+        B, T = inputs.shape
+        nll = np.empty(B * T, np.float32) if taps else None
+        dl = np.empty((B * T, self.vocab), np.float32) if taps else None
+        lg = np.empty((B * T, self.vocab), np.float32) if taps else None
+        loss = self.l.or_policy_gradient_step(self.h, _i(inputs), _i(targets), _f(adv), B, T, C.c_float(norm),
+                                              _f(nll) if taps else None, _f(dl) if taps else None, _f(lg) if taps else None)
+        return float(loss), nll, dl, lg
+
+
+class Cache:
+    def __init__(self, model: Model, batch, max_seq):
+        self.model = model
+        self.h = C.c_void_p(model.l.or_cache_create(model.h, batch, max_seq))
+
+    def __del__(self):
+        try:
+            self.model.l.or_cache_destroy(self.h)
+        except Exception:
+            pass
+
+    def position(self):
+        return int(self.model.l.or_cache_position(self.h))
+
+    def replicate_from(self, src: "Cache"):
+        self.model.l.or_cache_replicate(self.model.h, self.h, src.h)

@@ -1,0 +1,214 @@
+"""Pins the CPU oracle against the known answers held by the reference's own tests.
+
+Each test names the reference test whose expectation it restates.
+"""
+import math
+
+import numpy as np
+import pytest
+
+
+def close(got, want, rel, floor):
+    got = np.asarray(got, np.float32); want = np.asarray(want, np.float32)
+    return bool(np.all(np.abs(got - want) <= floor + rel * np.maximum(np.abs(want), 1.0)))
+
+
+# kernels/scalar/scalar_test.go:12-38
+def test_elementwise(oracle):
+    bk = oracle.Backend(0)
+    l, r = [1, 2, 3], [4, 5, 6]
+    assert close(bk.add(l, r), [5, 7, 9], 1e-6, 1e-6)
+    assert close(bk.subtract(r, l), [3, 3, 3], 1e-6, 1e-6)
+    assert close(bk.multiply(l, r), [4, 10, 18], 1e-6, 1e-6)
+    assert close(bk.divide(r, l), [4, 2.5, 2], 1e-6, 1e-6)
+    assert close(bk.scale(l, 2), [2, 4, 6], 1e-6, 1e-6)
+    assert close(bk.add_scaled(l, r, 0.5), [3, 4.5, 6], 1e-6, 1e-6)
+    assert close(bk.negate(l), [-1, -2, -3], 1e-6, 1e-6)
+    assert close(bk.abs([-1, 2, -3]), [1, 2, 3], 1e-6, 1e-6)
+    assert close(bk.square(l), [1, 4, 9], 1e-6, 1e-6)
+    assert close(bk.relu_squared([-1, 2, -3]), [0, 4, 0], 1e-6, 1e-6)
+
+
+# kernels/scalar/scalar_test.go:40-94
+def test_swiglu(oracle):
+    bk = oracle.Backend(0)
+    silu = lambda x: np.float32(x) / (np.float32(1) + np.float32(math.exp(-x)))
+    got = bk.swiglu([0, 1, -1, 2], [1, 1, 2, -3], 0)
+    assert close(got, [silu(0) * 1, silu(1) * 1, silu(-1) * 2, silu(2) * -3], 1e-5, 1e-6)
+    got = bk.swiglu([20, 1, 1, 2], [1, 20, -20, 1], 10)
+    assert close(got, [silu(10) * 1, silu(1) * 10, silu(1) * -10, silu(2) * 1], 1e-5, 1e-6)
+    gate, up, og = [0.5, 1.5], [2.0, -1.0], [1.0, 2.0]
+    gg, ug = bk.swiglu_backward(gate, up, og, 10)
+    for i in range(2):
+        g, u, d = gate[i], up[i], og[i]
+        s = 1.0 / (1.0 + math.exp(-g))
+        assert close(gg[i], d * u * s * (1 + g * (1 - s)), 1e-5, 1e-6)
+        assert close(ug[i], d * g * s, 1e-5, 1e-6)
+
+
+# kernels/scalar/scalar_test.go:96-108
+def test_transcendentals(oracle):
+    bk = oracle.Backend(0)
+    assert close(bk.exp([1]), [math.e], 1e-6, 1e-6)
+    assert close(bk.sigmoid([0]), [0.5], 1e-6, 1e-6)
+    assert close(bk.tanh([0]), [0], 1e-6, 1e-6)
+    assert close(bk.rsqrt([4]), [0.5], 1e-6, 1e-6)
+
+
+# kernels/scalar/scalar_test.go:110-137
+def test_reductions_and_linear_algebra(oracle):
+    bk = oracle.Backend(0)
+    assert bk.sum([1, 2, 3, 4]) == 10
+    assert bk.max([1, 9, 3]) == 9
+    assert bk.max([]) == 0
+    assert bk.argmax([1, 9, 3]) == 1
+    left, right = [1, 2, 3, 4, 5, 6], [7, 8, 9, 10, 11, 12]
+    assert close(bk.matmul(left, right, 2, 2, 3), [58, 64, 139, 154], 1e-5, 1e-5)
+    assert close(bk.matmul_transposed(left, right, 2, 2, 3), [50, 68, 122, 167], 1e-5, 1e-5)
+    assert close(bk.dot_product([1, 2, 3], [4, 5, 6]), 32, 1e-6, 1e-6)
+
+
+# kernels/scalar/scalar_test.go:139-151
+def test_rows(oracle):
+    bk = oracle.Backend(0)
+    sm = bk.softmax_last_dim([1, 2, 3, 4], 2, 2)
+    assert abs(float(sm.astype(np.float64).sum()) - 2) < 1e-6
+    assert close(bk.rmsnorm_last_dim([1, 1, 1, 1], 2, 2, 1e-6), [1, 1, 1, 1], 1e-5, 1e-5)
+
+
+# kernels/scalar/scalar_test.go:153-186
+def test_attention_reference(oracle):
+    bk = oracle.Backend(0)
+    q = k = v = [1, 0, 0, 1]
+    out, lse = bk.attention_forward(q, k, v, 2, 2, 2, 0, -1)
+    assert close(out[:2], [1, 0], 1e-5, 1e-6)
+    dq, dk, dv = bk.attention_backward(q, k, v, [1, 1, 1, 1], lse, 2, 2, 2, 0, -1)
+    assert np.all(np.isfinite(dq)) and np.all(np.isfinite(dk)) and np.all(np.isfinite(dv))
+
+
+# kernels/scalar/scalar_test.go:188-205
+def test_moe_gate_topk(oracle):
+    bk = oracle.Backend(0)
+    probs, sel, w = bk.moe_gate_topk([0, 0, 0], [0, 1, 2], 1, 3, 2)
+    assert close(probs, [1 / 3] * 3, 1e-6, 1e-6)
+    assert list(sel) == [2, 1]
+    assert close(w, [1 / 3, 1 / 3], 1e-6, 1e-6)
+
+
+# kernels/scalar/scalar_test.go:207-222
+def test_topk_indices(oracle):
+    bk = oracle.Backend(0)
+    got = bk.topk_indices([0.1, 0.9, 0.3, 0.7, 0.5, 0.2, 0.5, 0.2], 2, 4, 3)
+    assert list(got) == [1, 3, 2, 0, 2, 1]
+
+
+# kernels/scalar/scalar_test.go:224-235
+def test_grouped_matmul_transposed(oracle):
+    bk = oracle.Backend(0)
+    got = bk.grouped_matmul_transposed([1, 2, 3, 4, 5, 6], [1, 0, 0, 1, 2, 0, 0, 3], [2, 1], 2, 2, 2)
+    assert close(got, [1, 2, 3, 4, 10, 18], 1e-6, 1e-6)
+
+
+# tensors/loss_test.go:8-32
+def test_cross_entropy_per_position(oracle):
+    logits = np.array([[0, 0, 5, 0], [1, 1, 1, 1], [2, 0, 0, 0]], np.float32)
+    losses, valid = oracle.cross_entropy_per_position(logits, [2, -1, 0])
+    assert valid == 2
+    assert losses[1] == 0
+    assert abs(losses[0] - np.float32(math.log(math.exp(5) + 3) - 5)) <= 1e-5
+    assert abs(losses[2] - np.float32(math.log(math.exp(2) + 3) - 2)) <= 1e-5
+
+
+# tensors/loss_test.go:34-64
+def test_cross_entropy_known_values(oracle):
+    losses, valid = oracle.cross_entropy_per_position(np.ones((1, 4), np.float32), [0])
+    assert abs(losses.sum() / valid - np.float32(math.log(4))) <= 1e-5
+    losses, _ = oracle.cross_entropy_per_position(np.ones((2, 4), np.float32), [0, 1])
+    assert abs(losses.sum() - 2 * np.float32(math.log(4))) <= 1e-4
+    losses, valid = oracle.cross_entropy_per_position(np.ones((2, 4), np.float32), [-1, -1])
+    assert valid == 0 and losses.sum() == 0
+
+
+# tensors/backward_test.go:70-89
+def test_cross_entropy_grad(oracle):
+    g = oracle.cross_entropy_grad(np.zeros((1, 3), np.float32), [1], -1, 1.0)
+    assert close(g[0], [1 / 3, -2 / 3, 1 / 3], 1e-5, 1e-6)
+    g = oracle.cross_entropy_grad(np.zeros((2, 3), np.float32), [-1, 0], -1, 1.0)
+    assert np.all(g[0] == 0)
+
+
+# tensors/backward_test.go:118-158
+def test_backward_primitives(oracle):
+    assert close(oracle.relu_squared_backward([-1, 2, -3, 4], [1, 1, 1, 1]), [0, 4, 0, 8], 1e-5, 1e-6)
+    g = oracle.rmsnorm_backward(np.array([[1, 2, 3, 4]], np.float32), np.ones((1, 4), np.float32), 1e-6)
+    assert g.size == 4 and np.all(np.isfinite(g))
+    assert np.all(np.isfinite(oracle.softcap_backward([0.5, -0.5], [1, 1], 15)))
+    assert close(oracle.sigmoid_backward([0.5, -0.5], [1, 1])[0], 0.25, 1e-5, 1e-6)
+
+
+# inference/inference_test.go:11-30
+def test_sample_next_token(oracle):
+    logits = np.array([[1, 9, 3, 5], [7, 2, 8, 1]], np.float32)
+    assert list(oracle.sample_next_token(logits, 0.0, 0)) == [1, 2]
+    logits = np.array([[1, 2, 3, 4, 5, 6, 7, 8]], np.float32)
+    for seed in range(64):
+        got = oracle.sample_next_token(logits, 1.0, 3, seeds=[seed], group=1, step=seed % 5)
+        assert got[0] >= 5
+
+
+# tensors/random_test.go:67-86 (the Gumbel sampler favours a dominant logit; argmax at T<=0)
+def test_sample_multinomial_statistics(oracle):
+    logits = np.array([[0, 0, 10, 0]], np.float32)
+    hits = sum(int(oracle.sample_next_token(logits, 1.0, 0, seeds=[s], group=1)[0] == 2) for s in range(200))
+    assert hits > 180
+    assert oracle.sample_next_token(np.array([[0.1, 0.7, 0.2]], np.float32), 0.0, 0)[0] == 1
+
+
+# model/model_test.go:196-211, 283-301
+def test_rotary_quarter_turn(oracle):
+    cos = np.array([[1], [0]], np.float32); sin = np.array([[0], [1]], np.float32)
+    assert list(oracle.rotary_tables([3, 4], cos, sin, 1, 1, 1, 2, 1)) == [4, -3]
+    assert list(oracle.rotary_tables([10, 20, 3, 4], cos, sin, 1, 1, 1, 4, 1)) == [10, 20, 4, -3]
+
+
+# model/model_test.go:158-194
+def test_window_sizes_and_padded_vocab(oracle):
+    m = oracle.Model(2048, 32, 4, 2, 2, 8, 0, "SSSL")
+    assert list(m.window_sizes()) == [512, 512, 512, 2048]
+    assert m.padded_vocab() == 64
+    assert oracle.Model(64, 65, 2, 2, 2, 8).padded_vocab() == 128
+
+
+# kernels/simd/parity_test.go:263-310 and model/model_test.go:232-253: split-K shards recombine to the full pass
+@pytest.mark.parametrize("ql,kl,hd,off,win", [(6, 6, 8, 0, -1), (1, 10, 8, 9, -1), (6, 6, 8, 0, 2), (1, 10, 4, 9, 3), (1, 700, 16, 699, -1)])
+@pytest.mark.parametrize("splits", [1, 2, 3, 5])
+def test_attention_split_combines_to_full(oracle, ql, kl, hd, off, win, splits):
+    bk = oracle.Backend(0)
+    q, k, v = oracle.kt_data(ql * hd), oracle.kt_data(kl * hd), oracle.kt_data_b(kl * hd)
+    want_o, want_l = bk.attention_forward(q, k, v, ql, kl, hd, off, win)
+    per = (kl + splits - 1) // splits
+    parts = [bk.attention_forward_split(q, k, v, ql, kl, hd, off, win, s * per, min((s + 1) * per, kl)) for s in range(splits)]
+    got_o, got_l = bk.attention_combine([p[0] for p in parts], [p[1] for p in parts], [p[2] for p in parts], ql, hd)
+    assert close(got_o, want_o, 2e-3, 1e-5)
+    assert close(got_l, want_l, 2e-3, 1e-5)
+
+
+# kernels/simd/parity_test.go:15-223: the SIMD-structured port stays within the
+# reference's own simd-vs-scalar tolerances.
+def test_simd_port_within_reference_tolerances(oracle):
+    sc, sp = oracle.Backend(0), oracle.Backend(1)
+    for rows, cols, inner in [(3, 5, 17), (4, 6, 13), (64, 129, 200), (97, 131, 256), (400, 128, 512)]:
+        left = oracle.kt_data(rows * inner)
+        assert close(sp.matmul(left, oracle.kt_data_b(inner * cols), rows, cols, inner),
+                     sc.matmul(left, oracle.kt_data_b(inner * cols), rows, cols, inner), 2e-3, 1e-4)
+        assert close(sp.matmul_transposed(left, oracle.kt_data_b(cols * inner), rows, cols, inner),
+                     sc.matmul_transposed(left, oracle.kt_data_b(cols * inner), rows, cols, inner), 2e-3, 1e-4)
+    for n in [1, 7, 31, 64, 513, 1031]:
+        x = oracle.kt_data(n)
+        assert close(sp.softmax_last_dim(x, 1, n), sc.softmax_last_dim(x, 1, n), 1e-4, 1e-6)
+        assert close(sp.rmsnorm_last_dim(x, 1, n, 1e-6), sc.rmsnorm_last_dim(x, 1, n, 1e-6), 1e-5, 1e-6)
+    ql = kl = 200; hd = 32
+    q, k, v = oracle.kt_data(ql * hd), oracle.kt_data(kl * hd), oracle.kt_data_b(kl * hd)
+    o1, l1 = sp.attention_forward(q, k, v, ql, kl, hd, 0, -1)
+    o0, l0 = sc.attention_forward(q, k, v, ql, kl, hd, 0, -1)
+    assert close(o1, o0, 5e-3, 1e-5) and close(l1, l0, 5e-3, 1e-5)
