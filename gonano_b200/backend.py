@@ -1,0 +1,205 @@
+"""``CudaBackend``: the host-side mirror of the reference's ``kernels.Backend``
+(kernels/backend.go:285-297) over the C-ABI's Tier A.  Method names are the Go
+method names in snake case; arguments keep the Go order and meaning, slices
+are numpy float32 / int32 arrays.  Like the Go contract the methods write into
+a destination the caller sized; for convenience they also return it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import GnAttentionParams, check, ptr
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _i32(a):
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+class CudaBackend:
+    """Selected the way ``tensors.UseKernelBackend(cuda.New())`` selects a backend in the reference."""
+
+    def __init__(self):
+        self.lib = _lib.load()
+
+    # ---------------------------------------------------------- Elementwise
+    def _binary(self, fn, left, right):
+        left, right = _f32(left), _f32(right)
+        dst = np.empty_like(left)
+        check(fn(ptr(dst), ptr(left), ptr(right), left.size))
+        return dst
+
+    def _unary(self, fn, src):
+        src = _f32(src)
+        dst = np.empty_like(src)
+        check(fn(ptr(dst), ptr(src), src.size))
+        return dst
+
+    def add(self, left, right): return self._binary(self.lib.gn_add, left, right)
+    def subtract(self, left, right): return self._binary(self.lib.gn_subtract, left, right)
+    def multiply(self, left, right): return self._binary(self.lib.gn_multiply, left, right)
+    def divide(self, left, right): return self._binary(self.lib.gn_divide, left, right)
+    def negate(self, src): return self._unary(self.lib.gn_negate, src)
+    def abs(self, src): return self._unary(self.lib.gn_abs, src)
+    def square(self, src): return self._unary(self.lib.gn_square, src)
+    def relu_squared(self, src): return self._unary(self.lib.gn_relu_squared, src)
+    def exp(self, src): return self._unary(self.lib.gn_exp, src)
+    def sigmoid(self, src): return self._unary(self.lib.gn_sigmoid, src)
+    def tanh(self, src): return self._unary(self.lib.gn_tanh, src)
+    def rsqrt(self, src): return self._unary(self.lib.gn_rsqrt, src)
+
+    def scale(self, src, factor):
+        src = _f32(src); dst = np.empty_like(src)
+        check(self.lib.gn_scale(ptr(dst), ptr(src), factor, src.size)); return dst
+
+    def add_scaled(self, base, scaled, factor):
+        base, scaled = _f32(base), _f32(scaled); dst = np.empty_like(base)
+        check(self.lib.gn_add_scaled(ptr(dst), ptr(base), ptr(scaled), factor, base.size)); return dst
+
+    def swiglu(self, gate, up, clamp):
+        gate, up = _f32(gate), _f32(up); dst = np.empty_like(gate)
+        check(self.lib.gn_swiglu(ptr(dst), ptr(gate), ptr(up), clamp, gate.size)); return dst
+
+    def swiglu_backward(self, gate, up, out_grad, clamp):
+        gate, up, out_grad = _f32(gate), _f32(up), _f32(out_grad)
+        gg, ug = np.empty_like(gate), np.empty_like(gate)
+        check(self.lib.gn_swiglu_backward(ptr(gg), ptr(ug), ptr(gate), ptr(up), ptr(out_grad), clamp, gate.size)); return gg, ug
+
+    # ----------------------------------------------------------- Reductions
+    def sum(self, values):
+        values = _f32(values); out = C.c_float()
+        check(self.lib.gn_sum(ptr(values), values.size, C.byref(out))); return out.value
+
+    def max(self, values):
+        values = _f32(values); out = C.c_float()
+        check(self.lib.gn_max(ptr(values), values.size, C.byref(out))); return out.value
+
+    def argmax(self, values):
+        values = _f32(values); out = C.c_int64()
+        check(self.lib.gn_argmax(ptr(values), values.size, C.byref(out))); return out.value
+
+    # -------------------------------------------------------- LinearAlgebra
+    def matmul(self, left, right, rows, cols, inner):
+        left, right = _f32(left), _f32(right); dst = np.empty(rows * cols, np.float32)
+        check(self.lib.gn_matmul(ptr(dst), ptr(left), ptr(right), rows, cols, inner)); return dst
+
+    def matmul_transposed(self, left, right, rows, cols, inner):
+        left, right = _f32(left), _f32(right); dst = np.empty(rows * cols, np.float32)
+        check(self.lib.gn_matmul_transposed(ptr(dst), ptr(left), ptr(right), rows, cols, inner)); return dst
+
+    def dot_product(self, left, right):
+        left, right = _f32(left), _f32(right); out = C.c_float()
+        check(self.lib.gn_dot_product(ptr(left), ptr(right), min(left.size, right.size), C.byref(out))); return out.value
+
+    # -------------------------------------------------------------- Indexer
+    def indexer_scores(self, query, key, weight, rows, blocks, heads, dim):
+        query, key, weight = _f32(query), _f32(key), _f32(weight); dst = np.empty(rows * blocks, np.float32)
+        check(self.lib.gn_indexer_scores(ptr(dst), ptr(query), ptr(key), ptr(weight), rows, blocks, heads, dim)); return dst
+
+    def indexer_block_max(self, scores, rows, blocks, group_size):
+        scores = _f32(scores); g = max(group_size, 1)
+        dst = np.empty(rows * ((blocks + g - 1) // g), np.float32)
+        check(self.lib.gn_indexer_block_max(ptr(dst), ptr(scores), rows, blocks, group_size)); return dst
+
+    # ------------------------------------------------------------------ MoE
+    def topk_indices(self, scores, rows, count, k):
+        scores = _f32(scores); dst = np.zeros(rows * k, np.int32)
+        check(self.lib.gn_topk_indices(ptr(dst), ptr(scores), rows, count, k)); return dst
+
+    def moe_gate_topk(self, logits, bias, rows, experts, k):
+        logits, bias = _f32(logits), _f32(bias)
+        probs = np.empty(rows * experts, np.float32); sel = np.zeros(rows * k, np.int32); w = np.zeros(rows * k, np.float32)
+        check(self.lib.gn_moe_gate_topk(ptr(logits), ptr(bias), ptr(probs), ptr(sel), ptr(w), rows, experts, k)); return probs, sel, w
+
+    def grouped_matmul_transposed(self, inp, weight, token_counts, experts, cols, inner):
+        inp, weight, token_counts = _f32(inp), _f32(weight), _i32(token_counts)
+        dst = np.zeros(int(token_counts.sum()) * cols, np.float32)
+        check(self.lib.gn_grouped_matmul_transposed(ptr(dst), ptr(inp), ptr(weight), ptr(token_counts), experts, cols, inner)); return dst
+
+    # ----------------------------------------------------------------- Rows
+    def softmax_last_dim(self, src, rows, cols):
+        src = _f32(src); dst = np.empty(rows * cols, np.float32)
+        check(self.lib.gn_softmax_last_dim(ptr(dst), ptr(src), rows, cols)); return dst
+
+    def rmsnorm_last_dim(self, src, rows, cols, epsilon):
+        src = _f32(src); dst = np.empty(rows * cols, np.float32)
+        check(self.lib.gn_rmsnorm_last_dim(ptr(dst), ptr(src), rows, cols, epsilon)); return dst
+
+    # ------------------------------------------------------------ Attention
+    @staticmethod
+    def _params(q, k, v, ql, kl, hd, offset, window, seg):
+        p = GnAttentionParams()
+        p.query, p.key, p.value = q.ctypes.data, k.ctypes.data, v.ctypes.data
+        p.query_len, p.key_len, p.head_dim, p.position_offset, p.window = ql, kl, hd, offset, window
+        p.segment_ids = seg.ctypes.data if seg is not None else None
+        return p
+
+    def attention_forward(self, q, k, v, ql, kl, hd, offset, window, segments=None):
+        q, k, v = _f32(q), _f32(k), _f32(v); seg = _i32(segments) if segments is not None else None
+        out = np.empty(ql * hd, np.float32); lse = np.empty(ql, np.float32)
+        p = self._params(q, k, v, ql, kl, hd, offset, window, seg)
+        check(self.lib.gn_attention_forward(C.byref(p), ptr(out), ptr(lse))); return out, lse
+
+    def attention_forward_split(self, q, k, v, ql, kl, hd, offset, window, key_start, key_end, segments=None):
+        q, k, v = _f32(q), _f32(k), _f32(v); seg = _i32(segments) if segments is not None else None
+        acc = np.empty(ql * hd, np.float32); mx = np.empty(ql, np.float32); sm = np.empty(ql, np.float32)
+        p = self._params(q, k, v, ql, kl, hd, offset, window, seg)
+        check(self.lib.gn_attention_forward_split(C.byref(p), key_start, key_end, ptr(acc), ptr(mx), ptr(sm))); return acc, mx, sm
+
+    def attention_combine(self, accs, maxima, sums, ql, hd):
+        acc = _f32(np.stack(accs)); mx = _f32(np.stack(maxima)); sm = _f32(np.stack(sums))
+        out = np.empty(ql * hd, np.float32); lse = np.empty(ql, np.float32)
+        check(self.lib.gn_attention_combine(ptr(acc), ptr(mx), ptr(sm), len(accs), ql, hd, ptr(out), ptr(lse))); return out, lse
+
+    def attention_backward(self, q, k, v, output, out_grad, lse, ql, kl, hd, offset, window, row_correction=None, segments=None,
+                           dq=None, dk=None, dv=None):
+        q, k, v, output, out_grad, lse = _f32(q), _f32(k), _f32(v), _f32(output), _f32(out_grad), _f32(lse)
+        seg = _i32(segments) if segments is not None else None
+        rc = _f32(row_correction) if row_correction is not None else None
+        dq = np.zeros(ql * hd, np.float32) if dq is None else _f32(dq).copy()
+        dk = np.zeros(kl * hd, np.float32) if dk is None else _f32(dk).copy()
+        dv = np.zeros(kl * hd, np.float32) if dv is None else _f32(dv).copy()
+        p = self._params(q, k, v, ql, kl, hd, offset, window, seg)
+        check(self.lib.gn_attention_backward(C.byref(p), ptr(output), ptr(out_grad), ptr(lse), ptr(rc), ptr(dq), ptr(dk), ptr(dv)))
+        return dq, dk, dv
+
+
+# -------------------------------------------------------------------------
+# Stand-alone kernels of the RL step
+# -------------------------------------------------------------------------
+def sample_next_token(logits, temperature, top_k, uniforms=None, seeds=None, group=1, step=0):
+    """inference.SampleNextToken (inference/sampler.go:16-25) for a [rows, vocab] logit matrix."""
+    lib = _lib.load()
+    logits = _f32(logits); rows, vocab = logits.shape
+    out = np.empty(rows, np.int32)
+    u = _f32(uniforms) if uniforms is not None else None
+    s = np.ascontiguousarray(seeds, dtype=np.uint64) if seeds is not None else None
+    check(lib.gn_sample_next_token(ptr(logits), rows, vocab, ptr(u), ptr(s), group, step, temperature, top_k, ptr(out)))
+    return out
+
+
+def group_advantage(rewards, group, mode=0):
+    """Group-relative advantages (cmd/chat_rl/main.go:137-154); mode 1 divides by the group std."""
+    lib = _lib.load()
+    rewards = _f32(rewards); adv = np.empty_like(rewards)
+    check(lib.gn_group_advantage(ptr(rewards), rewards.size // group, group, mode, ptr(adv)))
+    return adv
+
+
+def pg_loss_backward(logits, targets, advantages, seq_len, norm, softcap=0.0, want_grad=True, in_place=False):
+    """Per-token nll, policy-gradient loss and dlogits at given logits (trainer/rl.go:23-56)."""
+    lib = _lib.load()
+    logits = _f32(logits); targets = _i32(targets); advantages = _f32(advantages)
+    rows, vocab = logits.shape
+    nll = np.empty(rows, np.float32)
+    grad = logits if in_place else (np.empty((rows, vocab), np.float32) if want_grad else None)
+    loss = C.c_double()
+    check(lib.gn_pg_loss_backward(ptr(logits), ptr(targets), ptr(advantages), rows, vocab, seq_len, norm, softcap, ptr(nll), ptr(grad),
+                                  C.byref(loss)))
+    return loss.value, nll, grad

@@ -1,0 +1,687 @@
+// Attention kernels (kernels/backend.go:167-283; scalar statement
+// kernels/scalar/attention.go:16-245).
+//
+//   attention_forward   tiled online-softmax attention over token-major,
+//                       strided Q/K/V (all (batch, head) pairs in one launch);
+//                       used by prefill, by the training forward and by the
+//                       single-head conformance entry point.
+//   attention_backward  two deterministic kernels: one CTA per key tile for
+//                       dK/dV (it also walks the query heads that share the
+//                       kv head, so grouped-query gradients need no atomics),
+//                       one CTA per query tile for dQ.
+//   attention_decode    one query token per row over the KV cache: warp-level
+//                       online softmax, float4 coalesced K/V loads, optional
+//                       split over the key range with a combine pass.
+//   attention_split / attention_combine  the contract's split-K pair.
+//
+// Scores are raw q.k (the model applies no 1/sqrt(d)); a masked score is the
+// finite -1e30 of the reference (kernels/scalar/attention.go:11).
+#include "kernels.cuh"
+
+namespace gn {
+
+constexpr float kMaskedScore = -1e30f;
+constexpr int AT = 256;  // threads per CTA in the tiled kernels
+
+__device__ __forceinline__ bool attn_masked(int qpos, int kj, int window, const int32_t* seg, int seg_len, int32_t qseg) {
+  bool m = kj > qpos || (window >= 0 && qpos - kj > window);
+  if (!m && seg != nullptr && kj < seg_len && seg[kj] != qseg) m = true;
+  return m;
+}
+
+// acc[TM][TN] += sum_k A[k][m..m+TM) * B[k][n..n+TN), A and B shared-memory
+// tiles stored k-major with row pitches lda / ldb (multiples of 4 floats).
+template <int TM, int TN>
+__device__ __forceinline__ void mm_acc(float (&acc)[TM][TN], const float* A, int lda, const float* B, int ldb, int K, int m, int n) {
+#pragma unroll 4
+  for (int k = 0; k < K; ++k) {
+    float a[TM], b[TN];
+    if (TM == 4) { float4 v = *reinterpret_cast<const float4*>(A + k * lda + m); a[0] = v.x; a[1] = v.y; a[2] = v.z; a[3] = v.w; }
+    else if (TM == 2) { float2 v = *reinterpret_cast<const float2*>(A + k * lda + m); a[0] = v.x; a[1] = v.y; }
+    else { for (int i = 0; i < TM; ++i) a[i] = A[k * lda + m + i]; }
+    if (TN == 4) { float4 v = *reinterpret_cast<const float4*>(B + k * ldb + n); b[0] = v.x; b[1] = v.y; b[2] = v.z; b[3] = v.w; }
+    else if (TN == 2) { float2 v = *reinterpret_cast<const float2*>(B + k * ldb + n); b[0] = v.x; b[1] = v.y; }
+    else { for (int j = 0; j < TN; ++j) b[j] = B[k * ldb + n + j]; }
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+  }
+}
+
+// Copies `nrows` token rows of D floats (pitch `tstride` in global memory) into
+// shared memory, zero-filling rows >= valid and columns >= D up to DP.
+//   row-major:  S[r*ld + c]        transposed: S[c*ld + r]
+template <int DP, bool TRANSPOSED>
+__device__ __forceinline__ void load_tile(float* S, int ld, const float* g, int64_t tstride, int nrows, int valid, int D) {
+  for (int idx = threadIdx.x; idx < nrows * DP; idx += AT) {
+    int r = idx / DP, c = idx % DP;
+    float v = (r < valid && c < D) ? g[(int64_t)r * tstride + c] : 0.0f;
+    if (TRANSPOSED) S[c * ld + r] = v; else S[r * ld + c] = v;
+  }
+}
+
+// ============================================================== forward
+// CTA: 64 queries of one (batch, query head); loops over 64-key tiles.
+template <int DP>
+__global__ void __launch_bounds__(AT) attn_fwd_kernel(AttnShape sh, const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                                                      float* __restrict__ out, float* __restrict__ lse) {
+  constexpr int BQ = 64, BKV = 64, LQ = BQ + 4, LV = DP + 4;
+  constexpr int NG = (DP == 128) ? 2 : 1;      // column groups of the output tile per thread
+  constexpr int TN = (DP == 32) ? 2 : 4;       // output columns per group per thread
+  extern __shared__ __align__(16) float smem[];
+  float* Qt = smem;                  // [DP][LQ]
+  float* Kt = Qt + DP * LQ;          // [DP][LQ]
+  float* Vs = Kt + DP * LQ;          // [BKV][LV]
+  float* Pt = Vs + BKV * LV;         // [BKV][LQ]   P transposed: Pt[j][i]
+
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int bh = blockIdx.y, b = bh / sh.Hq, hq = bh % sh.Hq, hk = hq / (sh.Hq / sh.Hkv);
+  const int q0 = blockIdx.x * BQ;
+  const int qvalid = min(BQ, sh.Tq - q0);
+  const int offset = sh.offset0;
+
+  const float* qg = q + (int64_t)b * sh.q_bstride + (int64_t)q0 * sh.q_tstride + (int64_t)hq * sh.D;
+  const float* kg = k + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride;
+  const float* vg = v + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride;
+  load_tile<DP, true>(Qt, LQ, qg, sh.q_tstride, BQ, qvalid, sh.D);
+
+  float m_run[4], l_run[4], o[NG][4][TN];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    m_run[i] = -INFINITY; l_run[i] = 0.0f;
+#pragma unroll
+    for (int g = 0; g < NG; ++g)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) o[g][i][j] = 0.0f;
+  }
+  int32_t qseg[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int qpos = offset + q0 + ty * 4 + i;
+    qseg[i] = (sh.segment_ids && qpos < sh.seg_len) ? sh.segment_ids[qpos] : 0;
+  }
+  // The reference keeps the last seen query segment when the position runs past
+  // the segment array; positions here never do for valid rows.
+
+  // Key range that any query of this tile can see.
+  const int max_qpos = offset + q0 + qvalid - 1;
+  int k_end = min(sh.Tk, max_qpos + 1);
+  int k_begin = 0;
+  if (sh.window >= 0) k_begin = max(0, offset + q0 - sh.window);
+  k_begin = (k_begin / BKV) * BKV;
+
+  for (int kt = k_begin; kt < k_end; kt += BKV) {
+    const int kvalid = min(BKV, sh.Tk - kt);
+    __syncthreads();
+    load_tile<DP, true>(Kt, LQ, kg + (int64_t)kt * sh.kv_tstride, sh.kv_tstride, BKV, kvalid, sh.D);
+    load_tile<DP, false>(Vs, LV, vg + (int64_t)kt * sh.kv_tstride, sh.kv_tstride, BKV, kvalid, sh.D);
+    __syncthreads();
+    float s[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] = 0.0f;
+    mm_acc<4, 4>(s, Qt, LQ, Kt, LQ, DP, ty * 4, tx * 4);
+    // mask, row max over the 16 threads that share the rows
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int qpos = offset + q0 + ty * 4 + i;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        int kj = kt + tx * 4 + j;
+        if (kj >= sh.Tk) s[i][j] = -INFINITY;   // beyond the key array: contributes nothing
+        else if (attn_masked(qpos, kj, sh.window, sh.segment_ids, sh.seg_len, qseg[i])) s[i][j] = kMaskedScore;
+        mx = fmaxf(mx, s[i][j]);
+      }
+#pragma unroll
+      for (int o2 = 8; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o2));
+      float m_new = fmaxf(m_run[i], mx);
+      float alpha = (m_run[i] == -INFINITY) ? 0.0f : __expf(m_run[i] - m_new);
+      float rs = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float p = (s[i][j] == -INFINITY) ? 0.0f : __expf(s[i][j] - m_new);
+        s[i][j] = p; rs += p;
+      }
+#pragma unroll
+      for (int o2 = 8; o2 > 0; o2 >>= 1) rs += __shfl_xor_sync(0xffffffffu, rs, o2);
+      l_run[i] = l_run[i] * alpha + rs;
+      m_run[i] = m_new;
+#pragma unroll
+      for (int g = 0; g < NG; ++g)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) o[g][i][j] *= alpha;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) Pt[(tx * 4 + j) * LQ + ty * 4 + i] = s[i][j];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < NG; ++g) mm_acc<4, TN>(o[g], Pt, LQ, Vs, LV, BKV, ty * 4, g * 64 + tx * TN);
+  }
+  // write out
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int qi = q0 + ty * 4 + i;
+    if (qi >= sh.Tq) continue;
+    float inv = l_run[i] > 0.0f ? 1.0f / l_run[i] : 0.0f;
+    float* og = out + (int64_t)b * sh.o_bstride + (int64_t)qi * sh.o_tstride + (int64_t)hq * sh.D;
+#pragma unroll
+    for (int g = 0; g < NG; ++g)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) {
+        int c = g * 64 + tx * TN + j;
+        if (c < sh.D) og[c] = o[g][i][j] * inv;
+      }
+    if (lse && tx == 0) lse[((int64_t)b * sh.Hq + hq) * sh.Tq + qi] = m_run[i] + logf(l_run[i]);
+  }
+}
+
+template <int DP>
+static int attn_fwd_go(const AttnShape& sh, const float* q, const float* k, const float* v, float* out, float* lse, cudaStream_t s) {
+  constexpr int LQ = 68, LV = DP + 4;
+  size_t smem = sizeof(float) * (size_t)(2 * DP * LQ + 64 * LV + 64 * LQ);
+  static bool configured = false;
+  if (!configured) {
+    GN_CUDA(cudaFuncSetAttribute(attn_fwd_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  dim3 grid(ceil_div(sh.Tq, 64), sh.B * sh.Hq);
+  attn_fwd_kernel<DP><<<grid, AT, smem, s>>>(sh, q, k, v, out, lse);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+int attention_forward_launch(const AttnShape& sh, const float* q, const float* k, const float* v, float* out, float* lse, cudaStream_t s) {
+  if (sh.Tq <= 0 || sh.B <= 0) return GN_OK;
+  GN_REQUIRE(sh.D > 0 && sh.D <= 128, "attention: head_dim %d outside (0,128]", sh.D);
+  GN_REQUIRE(sh.Hkv > 0 && sh.Hq % sh.Hkv == 0, "attention: %d query heads not divisible by %d kv heads", sh.Hq, sh.Hkv);
+  if (sh.D <= 32) return attn_fwd_go<32>(sh, q, k, v, out, lse, s);
+  if (sh.D <= 64) return attn_fwd_go<64>(sh, q, k, v, out, lse, s);
+  return attn_fwd_go<128>(sh, q, k, v, out, lse, s);
+}
+
+// ============================================================== backward
+// delta[b,hq,i] = sum_c dO[i][c] * O[i][c]  (equals sum_j P_ij dP_ij).
+__global__ void __launch_bounds__(256) attn_delta_kernel(AttnShape sh, const float* out, const float* dout, float* delta) {
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int64_t idx = (int64_t)blockIdx.x * 8 + warp;
+  int64_t total = (int64_t)sh.B * sh.Hq * sh.Tq;
+  if (idx >= total) return;
+  int i = (int)(idx % sh.Tq); int bh = (int)(idx / sh.Tq); int b = bh / sh.Hq, hq = bh % sh.Hq;
+  const float* o = out + (int64_t)b * sh.o_bstride + (int64_t)i * sh.o_tstride + (int64_t)hq * sh.D;
+  const float* d = dout + (int64_t)b * sh.o_bstride + (int64_t)i * sh.o_tstride + (int64_t)hq * sh.D;
+  float acc = 0;
+  for (int c = lane; c < sh.D; c += 32) acc = fmaf(o[c], d[c], acc);
+  acc = warp_sum(acc);
+  if (lane == 0) delta[idx] = acc;
+}
+
+// dK/dV: CTA = 64 keys of one (batch, kv head).  Walks the query heads of the
+// group and 32-query tiles.  dOut/out use the o_* strides, dq the q strides.
+template <int DP>
+__global__ void __launch_bounds__(AT) attn_bwd_dkv_kernel(AttnShape sh, const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                                                          const float* __restrict__ dout, const float* __restrict__ lse, const float* __restrict__ delta,
+                                                          float* __restrict__ dk, float* __restrict__ dv, int accumulate) {
+  constexpr int BQ = 32, BKV = 64, LK = BKV + 4, LQ = BQ + 4, LD = DP + 4;
+  constexpr int NG = (DP == 128) ? 2 : 1;
+  constexpr int TN = (DP == 32) ? 2 : 4;
+  extern __shared__ __align__(16) float smem[];
+  float* Kt = smem;                   // [DP][LK]
+  float* Vt = Kt + DP * LK;           // [DP][LK]
+  float* Qt = Vt + DP * LK;           // [DP][LQ]
+  float* dOt = Qt + DP * LQ;          // [DP][LQ]
+  float* Qs = dOt + DP * LQ;          // [BQ][LD]
+  float* dOs = Qs + BQ * LD;          // [BQ][LD]
+  float* Ps = dOs + BQ * LD;          // [BQ][LK]   P[i][j]
+  float* dSs = Ps + BQ * LK;          // [BQ][LK]
+  __shared__ float lse_s[BQ], delta_s[BQ];
+
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int bh = blockIdx.y, b = bh / sh.Hkv, hk = bh % sh.Hkv;
+  const int ratio = sh.Hq / sh.Hkv;
+  const int k0 = blockIdx.x * BKV;
+  const int kvalid = min(BKV, sh.Tk - k0);
+  const int offset = sh.offset0;
+  const float* kg = k + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride + (int64_t)k0 * sh.kv_tstride;
+  const float* vg = v + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride + (int64_t)k0 * sh.kv_tstride;
+  load_tile<DP, true>(Kt, LK, kg, sh.kv_tstride, BKV, kvalid, sh.D);
+  load_tile<DP, true>(Vt, LK, vg, sh.kv_tstride, BKV, kvalid, sh.D);
+
+  // accumulators: keys ty*4..+3, columns g*64 + tx*TN ..
+  float adk[NG][4][TN], adv[NG][4][TN];
+#pragma unroll
+  for (int g = 0; g < NG; ++g)
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) { adk[g][i][j] = 0.0f; adv[g][i][j] = 0.0f; }
+
+  // queries that can see any key of this tile: qpos >= k0  and qpos - (k0+kvalid-1) <= window ... per-element masks decide.
+  int q_begin = max(0, k0 - offset);
+  q_begin = (q_begin / BQ) * BQ;
+  int q_end = sh.Tq;
+  if (sh.window >= 0) q_end = min(sh.Tq, k0 + kvalid - 1 + sh.window - offset + 1);
+
+  for (int h = 0; h < ratio; ++h) {
+    const int hq = hk * ratio + h;
+    for (int q0 = q_begin; q0 < q_end; q0 += BQ) {
+      const int qvalid = min(BQ, sh.Tq - q0);
+      const float* qg = q + (int64_t)b * sh.q_bstride + (int64_t)q0 * sh.q_tstride + (int64_t)hq * sh.D;
+      const float* dog = dout + (int64_t)b * sh.o_bstride + (int64_t)q0 * sh.o_tstride + (int64_t)hq * sh.D;
+      __syncthreads();
+      load_tile<DP, true>(Qt, LQ, qg, sh.q_tstride, BQ, qvalid, sh.D);
+      load_tile<DP, false>(Qs, LD, qg, sh.q_tstride, BQ, qvalid, sh.D);
+      load_tile<DP, true>(dOt, LQ, dog, sh.o_tstride, BQ, qvalid, sh.D);
+      load_tile<DP, false>(dOs, LD, dog, sh.o_tstride, BQ, qvalid, sh.D);
+      if (tid < BQ) {
+        int qi = q0 + tid;
+        lse_s[tid] = qi < sh.Tq ? lse[((int64_t)b * sh.Hq + hq) * sh.Tq + qi] : 0.0f;
+        delta_s[tid] = qi < sh.Tq ? delta[((int64_t)b * sh.Hq + hq) * sh.Tq + qi] : 0.0f;
+      }
+      __syncthreads();
+      // S and dP tiles: 32 x 64, thread = rows ty*2..+1, cols tx*4..+3
+      float s[2][4], dp[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { s[i][j] = 0.0f; dp[i][j] = 0.0f; }
+      mm_acc<2, 4>(s, Qt, LQ, Kt, LK, DP, ty * 2, tx * 4);
+      mm_acc<2, 4>(dp, dOt, LQ, Vt, LK, DP, ty * 2, tx * 4);
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        int il = ty * 2 + i, qi = q0 + il, qpos = offset + qi;
+        int32_t qseg = (sh.segment_ids && qpos < sh.seg_len) ? sh.segment_ids[qpos] : 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          int kj = k0 + tx * 4 + j;
+          float p = 0.0f;
+          if (qi < sh.Tq && kj < sh.Tk && !attn_masked(qpos, kj, sh.window, sh.segment_ids, sh.seg_len, qseg)) p = __expf(s[i][j] - lse_s[il]);
+          Ps[il * LK + tx * 4 + j] = p;
+          dSs[il * LK + tx * 4 + j] = p * (dp[i][j] - delta_s[il]);
+        }
+      }
+      __syncthreads();
+      // dV[j][c] += sum_i P[i][j] dO[i][c] ; dK[j][c] += sum_i dS[i][j] Q[i][c]
+#pragma unroll
+      for (int g = 0; g < NG; ++g) {
+        mm_acc<4, TN>(adv[g], Ps, LK, dOs, LD, BQ, ty * 4, g * 64 + tx * TN);
+        mm_acc<4, TN>(adk[g], dSs, LK, Qs, LD, BQ, ty * 4, g * 64 + tx * TN);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int kj = k0 + ty * 4 + i;
+    if (kj >= sh.Tk) continue;
+    float* dkg = dk + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride + (int64_t)kj * sh.kv_tstride;
+    float* dvg = dv + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride + (int64_t)kj * sh.kv_tstride;
+#pragma unroll
+    for (int g = 0; g < NG; ++g)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) {
+        int c = g * 64 + tx * TN + j;
+        if (c < sh.D) {
+          if (accumulate) { dkg[c] += adk[g][i][j]; dvg[c] += adv[g][i][j]; }
+          else { dkg[c] = adk[g][i][j]; dvg[c] = adv[g][i][j]; }
+        }
+      }
+  }
+}
+
+// dQ: CTA = 64 queries of one (batch, query head); walks 32-key tiles.
+template <int DP>
+__global__ void __launch_bounds__(AT) attn_bwd_dq_kernel(AttnShape sh, const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                                                         const float* __restrict__ dout, const float* __restrict__ lse, const float* __restrict__ delta,
+                                                         float* __restrict__ dq, int accumulate) {
+  constexpr int BQ = 64, BKV = 32, LQ = BQ + 4, LK = BKV + 4, LD = DP + 4;
+  constexpr int NG = (DP == 128) ? 2 : 1;
+  constexpr int TN = (DP == 32) ? 2 : 4;
+  extern __shared__ __align__(16) float smem[];
+  float* Qt = smem;                   // [DP][LQ]
+  float* dOt = Qt + DP * LQ;          // [DP][LQ]
+  float* Kt = dOt + DP * LQ;          // [DP][LK]
+  float* Vt = Kt + DP * LK;           // [DP][LK]
+  float* Ks = Vt + DP * LK;           // [BKV][LD]
+  float* dSt = Ks + BKV * LD;         // [BKV][LQ]  dS transposed: dSt[j][i]
+  __shared__ float lse_s[BQ], delta_s[BQ];
+
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int bh = blockIdx.y, b = bh / sh.Hq, hq = bh % sh.Hq, hk = hq / (sh.Hq / sh.Hkv);
+  const int q0 = blockIdx.x * BQ;
+  const int qvalid = min(BQ, sh.Tq - q0);
+  const int offset = sh.offset0;
+  const float* qg = q + (int64_t)b * sh.q_bstride + (int64_t)q0 * sh.q_tstride + (int64_t)hq * sh.D;
+  const float* dog = dout + (int64_t)b * sh.o_bstride + (int64_t)q0 * sh.o_tstride + (int64_t)hq * sh.D;
+  const float* kg = k + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride;
+  const float* vg = v + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride;
+  load_tile<DP, true>(Qt, LQ, qg, sh.q_tstride, BQ, qvalid, sh.D);
+  load_tile<DP, true>(dOt, LQ, dog, sh.o_tstride, BQ, qvalid, sh.D);
+  if (tid < BQ) {
+    int qi = q0 + tid;
+    lse_s[tid] = qi < sh.Tq ? lse[((int64_t)b * sh.Hq + hq) * sh.Tq + qi] : 0.0f;
+    delta_s[tid] = qi < sh.Tq ? delta[((int64_t)b * sh.Hq + hq) * sh.Tq + qi] : 0.0f;
+  }
+  float adq[NG][4][TN];
+#pragma unroll
+  for (int g = 0; g < NG; ++g)
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) adq[g][i][j] = 0.0f;
+
+  const int max_qpos = offset + q0 + qvalid - 1;
+  int k_end = min(sh.Tk, max_qpos + 1);
+  int k_begin = 0;
+  if (sh.window >= 0) k_begin = max(0, offset + q0 - sh.window);
+  k_begin = (k_begin / BKV) * BKV;
+  // S tile 64 x 32: thread = rows (tid>>3)*2..+1, cols (tid&7)*4..+3
+  const int sy = tid >> 3, sx = tid & 7;
+  for (int kt = k_begin; kt < k_end; kt += BKV) {
+    const int kvalid = min(BKV, sh.Tk - kt);
+    __syncthreads();
+    load_tile<DP, true>(Kt, LK, kg + (int64_t)kt * sh.kv_tstride, sh.kv_tstride, BKV, kvalid, sh.D);
+    load_tile<DP, true>(Vt, LK, vg + (int64_t)kt * sh.kv_tstride, sh.kv_tstride, BKV, kvalid, sh.D);
+    load_tile<DP, false>(Ks, LD, kg + (int64_t)kt * sh.kv_tstride, sh.kv_tstride, BKV, kvalid, sh.D);
+    __syncthreads();
+    float s[2][4], dp[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { s[i][j] = 0.0f; dp[i][j] = 0.0f; }
+    mm_acc<2, 4>(s, Qt, LQ, Kt, LK, DP, sy * 2, sx * 4);
+    mm_acc<2, 4>(dp, dOt, LQ, Vt, LK, DP, sy * 2, sx * 4);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      int il = sy * 2 + i, qi = q0 + il, qpos = offset + qi;
+      int32_t qseg = (sh.segment_ids && qpos < sh.seg_len) ? sh.segment_ids[qpos] : 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        int kj = kt + sx * 4 + j;
+        float p = 0.0f;
+        if (qi < sh.Tq && kj < sh.Tk && !attn_masked(qpos, kj, sh.window, sh.segment_ids, sh.seg_len, qseg)) p = __expf(s[i][j] - lse_s[il]);
+        dSt[(sx * 4 + j) * LQ + il] = p * (dp[i][j] - delta_s[il]);
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < NG; ++g) mm_acc<4, TN>(adq[g], dSt, LQ, Ks, LD, BKV, ty * 4, g * 64 + tx * TN);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int qi = q0 + ty * 4 + i;
+    if (qi >= sh.Tq) continue;
+    float* dqg = dq + (int64_t)b * sh.q_bstride + (int64_t)qi * sh.q_tstride + (int64_t)hq * sh.D;
+#pragma unroll
+    for (int g = 0; g < NG; ++g)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) {
+        int c = g * 64 + tx * TN + j;
+        if (c < sh.D) { if (accumulate) dqg[c] += adq[g][i][j]; else dqg[c] = adq[g][i][j]; }
+      }
+  }
+}
+
+template <int DP>
+static int attn_bwd_go(const AttnShape& sh, const float* q, const float* k, const float* v, const float* dout, const float* lse, const float* delta,
+                       float* dq, float* dk, float* dv, int accumulate, cudaStream_t s) {
+  constexpr int LD = DP + 4;
+  size_t smem_kv = sizeof(float) * (size_t)(2 * DP * 68 + 2 * DP * 36 + 2 * 32 * LD + 2 * 32 * 68);
+  size_t smem_q = sizeof(float) * (size_t)(2 * DP * 68 + 2 * DP * 36 + 32 * LD + 32 * 68);
+  static bool configured = false;
+  if (!configured) {
+    GN_CUDA(cudaFuncSetAttribute(attn_bwd_dkv_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv));
+    GN_CUDA(cudaFuncSetAttribute(attn_bwd_dq_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_q));
+    configured = true;
+  }
+  dim3 gkv(ceil_div(sh.Tk, 64), sh.B * sh.Hkv);
+  attn_bwd_dkv_kernel<DP><<<gkv, AT, smem_kv, s>>>(sh, q, k, v, dout, lse, delta, dk, dv, accumulate);
+  GN_LAUNCH_CHECK();
+  dim3 gq(ceil_div(sh.Tq, 64), sh.B * sh.Hq);
+  attn_bwd_dq_kernel<DP><<<gq, AT, smem_q, s>>>(sh, q, k, v, dout, lse, delta, dq, accumulate);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+int attention_backward_launch(const AttnShape& sh, const float* q, const float* k, const float* v, const float* out, const float* dout,
+                              const float* lse, const float* row_correction, float* dq, float* dk, float* dv, int accumulate,
+                              float* delta_scratch, cudaStream_t s) {
+  if (sh.Tq <= 0 || sh.B <= 0) return GN_OK;
+  GN_REQUIRE(sh.D > 0 && sh.D <= 128, "attention: head_dim %d outside (0,128]", sh.D);
+  const float* delta = row_correction;
+  if (!delta) {
+    int64_t total = (int64_t)sh.B * sh.Hq * sh.Tq;
+    attn_delta_kernel<<<ceil_div(total, 8), 256, 0, s>>>(sh, out, dout, delta_scratch);
+    GN_LAUNCH_CHECK();
+    delta = delta_scratch;
+  }
+  if (sh.D <= 32) return attn_bwd_go<32>(sh, q, k, v, dout, lse, delta, dq, dk, dv, accumulate, s);
+  if (sh.D <= 64) return attn_bwd_go<64>(sh, q, k, v, dout, lse, delta, dq, dk, dv, accumulate, s);
+  return attn_bwd_go<128>(sh, q, k, v, dout, lse, delta, dq, dk, dv, accumulate, s);
+}
+
+// ============================================================== split / combine (contract)
+// One warp per query row; the shard's keys are walked sequentially.
+__global__ void __launch_bounds__(128) attn_split_kernel(AttnShape sh, const float* q, const float* k, const float* v, int kstart, int kend,
+                                                         float* acc, float* mx, float* sm) {
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int i = blockIdx.x * 4 + warp;
+  if (i >= sh.Tq) return;
+  const int D = sh.D;
+  const float* qr = q + (int64_t)i * sh.q_tstride;
+  int qpos = sh.offset0 + i;
+  int32_t qseg = (sh.segment_ids && qpos < sh.seg_len) ? sh.segment_ids[qpos] : 0;
+  float qv[4], o[4] = {0, 0, 0, 0};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { int c = lane + 32 * e; qv[e] = c < D ? qr[c] : 0.0f; }
+  float m = -INFINITY, l = 0.0f;
+  for (int kj = kstart; kj < kend; ++kj) {
+    const float* kr = k + (int64_t)kj * sh.kv_tstride;
+    float d = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { int c = lane + 32 * e; if (c < D) d = fmaf(qv[e], kr[c], d); }
+    d = warp_sum(d);
+    bool msk = kj > qpos || (sh.window >= 0 && qpos - kj > sh.window);
+    if (!msk && sh.segment_ids && kj < sh.seg_len && qpos < sh.seg_len && sh.segment_ids[kj] != qseg) msk = true;
+    if (msk) d = kMaskedScore;
+    float mn = fmaxf(m, d);
+    float alpha = (m == -INFINITY) ? 0.0f : expf(m - mn);
+    float p = expf(d - mn);
+    l = l * alpha + p;
+    const float* vr = v + (int64_t)kj * sh.kv_tstride;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { int c = lane + 32 * e; if (c < D) o[e] = o[e] * alpha + p * vr[c]; }
+    m = mn;
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { int c = lane + 32 * e; if (c < D) acc[(int64_t)i * D + c] = o[e]; }
+  if (lane == 0) { mx[i] = m; sm[i] = l; }
+}
+int attention_split_launch(const AttnShape& sh, const float* q, const float* k, const float* v, int kstart, int kend, float* acc, float* mx,
+                           float* sm, cudaStream_t s) {
+  if (sh.Tq <= 0) return GN_OK;
+  GN_REQUIRE(sh.D > 0 && sh.D <= 128, "attention: head_dim %d outside (0,128]", sh.D);
+  if (kend > sh.Tk) kend = sh.Tk;
+  if (kstart < 0) kstart = 0;
+  attn_split_kernel<<<ceil_div(sh.Tq, 4), 128, 0, s>>>(sh, q, k, v, kstart, kend, acc, mx, sm);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+// kernels/scalar/attention.go:104-141
+__global__ void __launch_bounds__(128) attn_combine_kernel(const float* acc, const float* mx, const float* sm, int parts, int ql, int hd, float* out, float* lse) {
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int i = blockIdx.x * 4 + warp;
+  if (i >= ql) return;
+  float gm = -INFINITY;
+  for (int p = 0; p < parts; ++p) gm = fmaxf(gm, mx[(int64_t)p * ql + i]);
+  float total = 0;
+  for (int p = 0; p < parts; ++p) {
+    float m = mx[(int64_t)p * ql + i];
+    float sc = (m > -INFINITY) ? expf(m - gm) : 0.0f;
+    total += sm[(int64_t)p * ql + i] * sc;
+  }
+  float inv = total > 0 ? 1.0f / total : 1.0f;
+  for (int c = lane; c < hd; c += 32) {
+    float o = 0;
+    for (int p = 0; p < parts; ++p) {
+      float m = mx[(int64_t)p * ql + i];
+      float sc = (m > -INFINITY) ? expf(m - gm) : 0.0f;
+      o += acc[((int64_t)p * ql + i) * hd + c] * sc;
+    }
+    out[(int64_t)i * hd + c] = o * inv;
+  }
+  if (lse && lane == 0) lse[i] = gm + logf(total);
+}
+int attention_combine_launch(const float* acc, const float* mx, const float* sm, int parts, int ql, int hd, float* out, float* lse, cudaStream_t s) {
+  if (ql <= 0) return GN_OK;
+  attn_combine_kernel<<<ceil_div(ql, 4), 128, 0, s>>>(acc, mx, sm, parts, ql, hd, out, lse);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+// ============================================================== decode
+// CTA = one (row, kv head, key split); 4 warps stride over the keys of the
+// split; each lane owns D/32 consecutive channels (float4 for D = 128), so a
+// warp reads one K row and one V row as a single coalesced 512-byte request.
+// All query heads of the group are served from the same K/V registers.
+// Warp partials are merged through shared memory, splits through a second pass.
+template <int D, int RATIO>
+__global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restrict__ q, int64_t q_rstride, const float* __restrict__ kcache,
+                                                          const float* __restrict__ vcache, int64_t row_stride, int64_t head_stride,
+                                                          const int32_t* __restrict__ ctx_len, int Hq, int Hkv, int window, float* __restrict__ out,
+                                                          int64_t o_rstride, float* __restrict__ part_acc, float* __restrict__ part_ms, int splits) {
+  constexpr int E = D / 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x / Hkv, hk = blockIdx.x % Hkv, split = blockIdx.y;
+  const int ctx = ctx_len[row];
+  const int qpos = ctx - 1;
+  int kbeg = 0;
+  if (window >= 0) kbeg = max(0, qpos - window);
+  const int span = ctx - kbeg;
+  const int per = (span + splits - 1) / splits;
+  const int k0 = kbeg + split * per, k1 = min(ctx, k0 + per);
+
+  float qv[RATIO][E];
+#pragma unroll
+  for (int h = 0; h < RATIO; ++h)
+#pragma unroll
+    for (int e = 0; e < E; ++e) qv[h][e] = q[(int64_t)row * q_rstride + (int64_t)(hk * RATIO + h) * D + lane * E + e];
+  float m[RATIO], l[RATIO], o[RATIO][E];
+#pragma unroll
+  for (int h = 0; h < RATIO; ++h) {
+    m[h] = -INFINITY; l[h] = 0.0f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) o[h][e] = 0.0f;
+  }
+  const float* kb = kcache + (int64_t)row * row_stride + (int64_t)hk * head_stride;
+  const float* vb = vcache + (int64_t)row * row_stride + (int64_t)hk * head_stride;
+  for (int kj = k0 + warp; kj < k1; kj += 4) {
+    float kv[E], vv[E];
+    if (E == 4) {
+      float4 a = *reinterpret_cast<const float4*>(kb + (int64_t)kj * D + lane * 4);
+      float4 c = *reinterpret_cast<const float4*>(vb + (int64_t)kj * D + lane * 4);
+      kv[0] = a.x; kv[1] = a.y; kv[2] = a.z; kv[3] = a.w; vv[0] = c.x; vv[1] = c.y; vv[2] = c.z; vv[3] = c.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < E; ++e) { kv[e] = kb[(int64_t)kj * D + lane * E + e]; vv[e] = vb[(int64_t)kj * D + lane * E + e]; }
+    }
+#pragma unroll
+    for (int h = 0; h < RATIO; ++h) {
+      float d = 0;
+#pragma unroll
+      for (int e = 0; e < E; ++e) d = fmaf(qv[h][e], kv[e], d);
+      d = warp_sum(d);
+      float mn = fmaxf(m[h], d);
+      float alpha = (m[h] == -INFINITY) ? 0.0f : __expf(m[h] - mn);
+      float p = __expf(d - mn);
+      l[h] = l[h] * alpha + p;
+#pragma unroll
+      for (int e = 0; e < E; ++e) o[h][e] = o[h][e] * alpha + p * vv[e];
+      m[h] = mn;
+    }
+  }
+  // merge the 4 warps
+  __shared__ float sm_o[4][RATIO][D];
+  __shared__ float sm_m[4][RATIO], sm_l[4][RATIO];
+#pragma unroll
+  for (int h = 0; h < RATIO; ++h) {
+#pragma unroll
+    for (int e = 0; e < E; ++e) sm_o[warp][h][lane * E + e] = o[h][e];
+    if (lane == 0) { sm_m[warp][h] = m[h]; sm_l[warp][h] = l[h]; }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < RATIO * D; idx += 128) {
+    int h = idx / D, c = idx % D;
+    float gm = fmaxf(fmaxf(sm_m[0][h], sm_m[1][h]), fmaxf(sm_m[2][h], sm_m[3][h]));
+    float tot = 0, acc = 0;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      float sc = (sm_m[w][h] == -INFINITY) ? 0.0f : __expf(sm_m[w][h] - gm);
+      tot += sm_l[w][h] * sc;
+      acc += sm_o[w][h][c] * sc;
+    }
+    int hq = hk * RATIO + h;
+    if (splits == 1) {
+      out[(int64_t)row * o_rstride + (int64_t)hq * D + c] = tot > 0 ? acc / tot : 0.0f;
+    } else {
+      int64_t pi = ((int64_t)row * Hq + hq) * splits + split;
+      part_acc[pi * D + c] = acc;
+      if (c == 0) { part_ms[pi * 2] = gm; part_ms[pi * 2 + 1] = tot; }
+    }
+  }
+}
+template <int D>
+__global__ void __launch_bounds__(128) attn_decode_combine_kernel(const float* part_acc, const float* part_ms, int splits, int Hq, float* out, int64_t o_rstride) {
+  int row = blockIdx.x / Hq, hq = blockIdx.x % Hq;
+  int64_t base = ((int64_t)row * Hq + hq) * splits;
+  float gm = -INFINITY;
+  for (int s = 0; s < splits; ++s) gm = fmaxf(gm, part_ms[(base + s) * 2]);
+  float tot = 0;
+  for (int s = 0; s < splits; ++s) { float m = part_ms[(base + s) * 2]; tot += (m == -INFINITY) ? 0.0f : part_ms[(base + s) * 2 + 1] * __expf(m - gm); }
+  for (int c = threadIdx.x; c < D; c += 128) {
+    float acc = 0;
+    for (int s = 0; s < splits; ++s) { float m = part_ms[(base + s) * 2]; if (m != -INFINITY) acc += part_acc[(base + s) * D + c] * __expf(m - gm); }
+    out[(int64_t)row * o_rstride + (int64_t)hq * D + c] = tot > 0 ? acc / tot : 0.0f;
+  }
+}
+
+int attention_decode_splits(int rows, int Hkv, int max_ctx) {
+  // Fill the machine: aim at >= 4 CTAs per SM, at least 64 keys per split.
+  int base = rows * Hkv;
+  int splits = 1;
+  while (base * splits < kNumSM * 4 && max_ctx / (splits * 2) >= 64 && splits < 16) splits *= 2;
+  return splits;
+}
+
+template <int D, int RATIO>
+static int decode_go(const float* q, int64_t q_rstride, const float* kcache, const float* vcache, int64_t row_stride, int64_t head_stride,
+                     const int32_t* ctx_len, int rows, int Hq, int Hkv, int window, float* out, int64_t o_rstride, float* part_acc, float* part_ms,
+                     int splits, cudaStream_t s) {
+  dim3 grid(rows * Hkv, splits);
+  attn_decode_kernel<D, RATIO><<<grid, 128, 0, s>>>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, Hq, Hkv, window, out, o_rstride,
+                                                    part_acc, part_ms, splits);
+  GN_LAUNCH_CHECK();
+  if (splits > 1) {
+    attn_decode_combine_kernel<D><<<rows * Hq, 128, 0, s>>>(part_acc, part_ms, splits, Hq, out, o_rstride);
+    GN_LAUNCH_CHECK();
+  }
+  return GN_OK;
+}
+
+int attention_decode_launch(const float* q, int64_t q_rstride, const float* kcache, const float* vcache, int64_t row_stride, int64_t head_stride,
+                            const int32_t* ctx_len, int rows, int Hq, int Hkv, int D, int window, float* out, int64_t o_rstride,
+                            float* part_acc, float* part_ms, int splits, cudaStream_t s) {
+  if (rows <= 0) return GN_OK;
+  int ratio = Hq / Hkv;
+#define GN_DEC(DD, RR) if (D == DD && ratio == RR) return decode_go<DD, RR>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, rows, Hq, Hkv, window, out, o_rstride, part_acc, part_ms, splits, s)
+  GN_DEC(128, 1); GN_DEC(128, 2); GN_DEC(128, 3); GN_DEC(128, 4); GN_DEC(128, 8);
+  GN_DEC(64, 1); GN_DEC(64, 2); GN_DEC(64, 3); GN_DEC(64, 4); GN_DEC(64, 8);
+  GN_DEC(32, 1); GN_DEC(32, 2); GN_DEC(32, 4);
+#undef GN_DEC
+  set_error("decode attention: unsupported head_dim %d / group ratio %d", D, ratio);
+  return GN_ERR_INVALID;
+}
+
+}  // namespace gn

@@ -1,0 +1,379 @@
+// C entry points of Tier A (one per kernels.Backend method, kernels/backend.go:
+// 16-297) and of the stand-alone RL-step kernels.  Pointers may be host or
+// device memory: host buffers are staged through device memory and the call
+// returns once the results are back, which is what a cgo caller needs (Go
+// memory must not be retained after the call returns).  One process-wide lock
+// serialises these calls: the reference invokes its backend from many
+// goroutines at once (model/attention.go:311-320, tensors/loss.go:30-37).
+#include <atomic>
+#include <cstdarg>
+#include <mutex>
+#include <vector>
+
+#include "kernels.cuh"
+
+namespace gn {
+
+static thread_local char g_error[1024] = "";
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+const char* get_error() { return g_error; }
+
+static std::atomic<int64_t> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+int64_t launch_count() { return g_launches.load(std::memory_order_relaxed); }
+
+int gemm_tcgen05_supported(const GemmArgs& a);
+int gemm_tcgen05(const GemmArgs& a, cudaStream_t s);
+int gemm_default_kind() {
+#ifdef GN_HAVE_TCGEN05
+  return 1;
+#else
+  return 0;
+#endif
+}
+int gemm_dispatch(const GemmArgs& a, int kind, cudaStream_t s) {
+#ifdef GN_HAVE_TCGEN05
+  if (kind == 1 && gemm_tcgen05_supported(a)) return gemm_tcgen05(a, s);
+#endif
+  (void)kind;
+  return gemm_simt(a, s);
+}
+
+namespace {
+
+std::mutex g_lock;
+cudaStream_t g_stream = nullptr;
+
+int tier_a_stream(cudaStream_t* out) {
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0) { set_error("no CUDA device available: %s", cudaGetErrorString(e)); return GN_ERR_CUDA; }
+  if (!g_stream) GN_CUDA(cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking));
+  *out = g_stream;
+  return GN_OK;
+}
+
+bool on_device(const void* p) {
+  cudaPointerAttributes at;
+  cudaError_t e = cudaPointerGetAttributes(&at, p);
+  if (e != cudaSuccess) { cudaGetLastError(); return false; }
+  return at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged;
+}
+
+// Stages host buffers for the duration of one call.
+struct Stage {
+  cudaStream_t s;
+  struct Back { void* host; void* dev; size_t bytes; };
+  std::vector<void*> owned;
+  std::vector<Back> back;
+  int status = GN_OK;
+  explicit Stage(cudaStream_t st) : s(st) {}
+  ~Stage() { for (void* p : owned) cudaFree(p); }
+  template <typename T>
+  const T* in(const T* p, size_t n) {
+    if (!p || n == 0 || on_device(p) || status != GN_OK) return p;
+    void* dev = nullptr;
+    if (cudaMalloc(&dev, n * sizeof(T)) != cudaSuccess) { set_error("staging: cudaMalloc of %zu bytes failed", n * sizeof(T)); status = GN_ERR_NOMEM; return nullptr; }
+    owned.push_back(dev);
+    if (cudaMemcpyAsync(dev, p, n * sizeof(T), cudaMemcpyHostToDevice, s) != cudaSuccess) { set_error("staging: host to device copy failed"); status = GN_ERR_CUDA; }
+    return (const T*)dev;
+  }
+  template <typename T>
+  T* out(T* p, size_t n, bool read_too = false) {
+    if (!p || n == 0 || on_device(p) || status != GN_OK) return p;
+    void* dev = nullptr;
+    if (cudaMalloc(&dev, n * sizeof(T)) != cudaSuccess) { set_error("staging: cudaMalloc of %zu bytes failed", n * sizeof(T)); status = GN_ERR_NOMEM; return nullptr; }
+    owned.push_back(dev);
+    if (read_too && cudaMemcpyAsync(dev, p, n * sizeof(T), cudaMemcpyHostToDevice, s) != cudaSuccess) { set_error("staging: host to device copy failed"); status = GN_ERR_CUDA; }
+    back.push_back({p, dev, n * sizeof(T)});
+    return (T*)dev;
+  }
+  int finish() {
+    if (status != GN_OK) return status;
+    for (auto& b : back) GN_CUDA(cudaMemcpyAsync(b.host, b.dev, b.bytes, cudaMemcpyDeviceToHost, s));
+    GN_CUDA(cudaStreamSynchronize(s));
+    return GN_OK;
+  }
+};
+
+#define GN_BEGIN()                               \
+  std::lock_guard<std::mutex> guard__(g_lock);   \
+  cudaStream_t s = nullptr;                      \
+  GN_TRY(tier_a_stream(&s));                     \
+  Stage st(s)
+
+#define GN_END()                                 \
+  return st.finish()
+
+int ew2(int op, float* dst, const float* a, const float* b, float f, int64_t n) {
+  if (n <= 0) return GN_OK;
+  GN_REQUIRE(dst && a, "elementwise: null pointer");
+  GN_BEGIN();
+  const float* da = st.in(a, n); const float* db = b ? st.in(b, n) : nullptr; float* dd = st.out(dst, n);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(ew_launch(op, dd, da, db, f, n, s));
+  GN_END();
+}
+
+}  // namespace
+}  // namespace gn
+
+using namespace gn;
+
+extern "C" {
+
+const char* gn_last_error(void) { return get_error(); }
+const char* gn_version(void) { return "gonano-cuda 0.1 (sm_100a)"; }
+int gn_device_count(void) {
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess) { cudaGetLastError(); return 0; }
+  return count;
+}
+
+int gn_add(float* d, const float* a, const float* b, int64_t n) { return ew2(EW_ADD, d, a, b, 0, n); }
+int gn_subtract(float* d, const float* a, const float* b, int64_t n) { return ew2(EW_SUB, d, a, b, 0, n); }
+int gn_multiply(float* d, const float* a, const float* b, int64_t n) { return ew2(EW_MUL, d, a, b, 0, n); }
+int gn_divide(float* d, const float* a, const float* b, int64_t n) { return ew2(EW_DIV, d, a, b, 0, n); }
+int gn_scale(float* d, const float* a, float f, int64_t n) { return ew2(EW_SCALE, d, a, nullptr, f, n); }
+int gn_add_scaled(float* d, const float* base, const float* sc, float f, int64_t n) { return ew2(EW_ADD_SCALED, d, base, sc, f, n); }
+int gn_negate(float* d, const float* a, int64_t n) { return ew2(EW_NEG, d, a, nullptr, 0, n); }
+int gn_abs(float* d, const float* a, int64_t n) { return ew2(EW_ABS, d, a, nullptr, 0, n); }
+int gn_square(float* d, const float* a, int64_t n) { return ew2(EW_SQUARE, d, a, nullptr, 0, n); }
+int gn_relu_squared(float* d, const float* a, int64_t n) { return ew2(EW_RELU2, d, a, nullptr, 0, n); }
+int gn_swiglu(float* d, const float* gate, const float* up, float clamp, int64_t n) { return ew2(EW_SWIGLU, d, gate, up, clamp, n); }
+int gn_exp(float* d, const float* a, int64_t n) { return ew2(EW_EXP, d, a, nullptr, 0, n); }
+int gn_sigmoid(float* d, const float* a, int64_t n) { return ew2(EW_SIGMOID, d, a, nullptr, 0, n); }
+int gn_tanh(float* d, const float* a, int64_t n) { return ew2(EW_TANH, d, a, nullptr, 0, n); }
+int gn_rsqrt(float* d, const float* a, int64_t n) { return ew2(EW_RSQRT, d, a, nullptr, 0, n); }
+
+int gn_swiglu_backward(float* gg, float* ug, const float* gate, const float* up, const float* og, float clamp, int64_t n) {
+  if (n <= 0) return GN_OK;
+  GN_REQUIRE(gg && ug && gate && up && og, "swiglu_backward: null pointer");
+  GN_BEGIN();
+  const float* dg = st.in(gate, n); const float* du = st.in(up, n); const float* dog = st.in(og, n);
+  float* dgg = st.out(gg, n); float* dug = st.out(ug, n);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(swiglu_backward_launch(dgg, dug, dg, du, dog, clamp, n, s));
+  GN_END();
+}
+
+static int reduce_scalar(int which, const float* v, const float* w, int64_t n, float* out_f, int64_t* out_i) {
+  GN_BEGIN();
+  const float* dv = st.in(v, n > 0 ? n : 0); const float* dw = w ? st.in(w, n) : nullptr;
+  void* res = nullptr;
+  GN_CUDA(cudaMalloc(&res, 8));
+  st.owned.push_back(res);
+  if (st.status != GN_OK) return st.status;
+  if (which == 0) GN_TRY(reduce_sum_launch(dv, n, (float*)res, s));
+  else if (which == 1) GN_TRY(reduce_max_launch(dv, n, (float*)res, s));
+  else if (which == 2) GN_TRY(reduce_argmax_launch(dv, n, (int64_t*)res, s));
+  else GN_TRY(dot_launch(dv, dw, n, (float*)res, s));
+  if (which == 2) GN_CUDA(cudaMemcpyAsync(out_i, res, 8, cudaMemcpyDeviceToHost, s));
+  else GN_CUDA(cudaMemcpyAsync(out_f, res, 4, cudaMemcpyDeviceToHost, s));
+  GN_END();
+}
+int gn_sum(const float* v, int64_t n, float* out) { GN_REQUIRE(out, "sum: null out"); if (n <= 0) { *out = 0; return GN_OK; } return reduce_scalar(0, v, nullptr, n, out, nullptr); }
+int gn_max(const float* v, int64_t n, float* out) { GN_REQUIRE(out, "max: null out"); if (n <= 0) { *out = 0; return GN_OK; } return reduce_scalar(1, v, nullptr, n, out, nullptr); }
+int gn_argmax(const float* v, int64_t n, int64_t* out) { GN_REQUIRE(out, "argmax: null out"); if (n <= 0) { *out = 0; return GN_OK; } return reduce_scalar(2, v, nullptr, n, nullptr, out); }
+int gn_dot_product(const float* a, const float* b, int64_t n, float* out) { GN_REQUIRE(out, "dot: null out"); if (n <= 0) { *out = 0; return GN_OK; } return reduce_scalar(3, a, b, n, out, nullptr); }
+
+static int matmul_any(float* dst, const float* left, const float* right, int rows, int cols, int inner, int b_trans) {
+  if (rows <= 0 || cols <= 0) return GN_OK;
+  GN_REQUIRE(dst && left && right && inner >= 0, "matmul: bad argument");
+  GN_BEGIN();
+  GemmArgs g;
+  g.A = st.in(left, (size_t)rows * inner); g.B = st.in(right, (size_t)cols * inner); g.C = st.out(dst, (size_t)rows * cols);
+  if (st.status != GN_OK) return st.status;
+  g.M = rows; g.N = cols; g.K = inner; g.lda = inner; g.ldb = b_trans ? inner : cols; g.ldc = cols; g.b_trans = b_trans;
+  GN_TRY(gemm_dispatch(g, gemm_default_kind(), s));
+  GN_END();
+}
+int gn_matmul(float* dst, const float* l, const float* r, int rows, int cols, int inner) { return matmul_any(dst, l, r, rows, cols, inner, 0); }
+int gn_matmul_transposed(float* dst, const float* l, const float* r, int rows, int cols, int inner) { return matmul_any(dst, l, r, rows, cols, inner, 1); }
+
+int gn_indexer_scores(float* dst, const float* q, const float* k, const float* w, int rows, int blocks, int heads, int dim) {
+  if (rows <= 0 || blocks <= 0) return GN_OK;
+  GN_BEGIN();
+  const float* dq = st.in(q, (size_t)rows * heads * dim); const float* dk = st.in(k, (size_t)blocks * heads * dim); const float* dw = st.in(w, heads);
+  float* dd = st.out(dst, (size_t)rows * blocks);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(indexer_scores_launch(dd, dq, dk, dw, rows, blocks, heads, dim, s));
+  GN_END();
+}
+int gn_indexer_block_max(float* dst, const float* scores, int rows, int blocks, int group) {
+  if (rows <= 0 || blocks <= 0) return GN_OK;
+  if (group < 1) group = 1;
+  int groups = (blocks + group - 1) / group;
+  GN_BEGIN();
+  const float* ds = st.in(scores, (size_t)rows * blocks); float* dd = st.out(dst, (size_t)rows * groups);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(indexer_block_max_launch(dd, ds, rows, blocks, group, s));
+  GN_END();
+}
+
+int gn_topk_indices(int32_t* dst, const float* scores, int rows, int count, int k) {
+  if (rows <= 0 || count <= 0 || k <= 0) return GN_OK;
+  GN_BEGIN();
+  const float* ds = st.in(scores, (size_t)rows * count); int32_t* dd = st.out(dst, (size_t)rows * k, true);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(topk_indices_launch(dd, ds, rows, count, k, s));
+  GN_END();
+}
+int gn_moe_gate_topk(const float* logits, const float* bias, float* probs, int32_t* sel, float* w, int rows, int experts, int k) {
+  if (rows <= 0 || experts <= 0) return GN_OK;
+  GN_REQUIRE(logits && bias && probs && sel && w && k > 0, "moe_gate_topk: bad argument");
+  GN_BEGIN();
+  const float* dl = st.in(logits, (size_t)rows * experts); const float* db = st.in(bias, experts);
+  float* dp = st.out(probs, (size_t)rows * experts); int32_t* dsel = st.out(sel, (size_t)rows * k, true); float* dw = st.out(w, (size_t)rows * k, true);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(moe_gate_topk_launch(dl, db, dp, dsel, dw, rows, experts, k, s));
+  GN_END();
+}
+int gn_grouped_matmul_transposed(float* dst, const float* input, const float* weight, const int32_t* counts, int experts, int cols, int inner) {
+  GN_REQUIRE(counts && experts >= 0, "grouped_matmul: bad argument");
+  GN_BEGIN();
+  // The row total is needed on the host to size the launch.
+  std::vector<int32_t> hc(experts);
+  if (on_device(counts)) { GN_CUDA(cudaMemcpyAsync(hc.data(), counts, sizeof(int32_t) * experts, cudaMemcpyDeviceToHost, s)); GN_CUDA(cudaStreamSynchronize(s)); }
+  else std::memcpy(hc.data(), counts, sizeof(int32_t) * experts);
+  int64_t total = 0;
+  for (int e = 0; e < experts; ++e) { GN_REQUIRE(hc[e] >= 0, "grouped_matmul: negative token count"); total += hc[e]; }
+  if (total == 0 || cols <= 0) return GN_OK;
+  const float* din = st.in(input, (size_t)total * inner); const float* dw = st.in(weight, (size_t)experts * cols * inner);
+  const int32_t* dc = st.in(counts, experts); float* dd = st.out(dst, (size_t)total * cols);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(grouped_matmul_t_launch(dd, din, dw, dc, experts, cols, inner, total, s));
+  GN_END();
+}
+
+int gn_softmax_last_dim(float* dst, const float* src, int64_t rows, int cols) {
+  if (rows <= 0 || cols <= 0) return GN_OK;
+  GN_BEGIN();
+  const float* ds = st.in(src, (size_t)rows * cols); float* dd = st.out(dst, (size_t)rows * cols);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(softmax_rows_launch(dd, ds, rows, cols, s));
+  GN_END();
+}
+int gn_rmsnorm_last_dim(float* dst, const float* src, int64_t rows, int cols, float eps) {
+  if (rows <= 0 || cols <= 0) return GN_OK;
+  GN_BEGIN();
+  const float* ds = st.in(src, (size_t)rows * cols); float* dd = st.out(dst, (size_t)rows * cols);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(rmsnorm_rows_launch(dd, ds, rows, cols, eps, s));
+  GN_END();
+}
+
+static int attn_shape(const gn_attention_params* p, AttnShape& sh, Stage& st, const float** q, const float** k, const float** v) {
+  GN_REQUIRE(p && p->query && p->key && p->value, "attention: null argument");
+  GN_REQUIRE(p->head_dim > 0 && p->head_dim <= 128, "attention: head_dim %d outside (0,128]", p->head_dim);
+  GN_REQUIRE(p->query_len >= 0 && p->key_len >= 0, "attention: negative length");
+  sh.B = 1; sh.Hq = 1; sh.Hkv = 1; sh.D = p->head_dim; sh.Tq = p->query_len; sh.Tk = p->key_len;
+  sh.q_bstride = 0; sh.q_tstride = p->head_dim; sh.kv_bstride = 0; sh.kv_tstride = p->head_dim; sh.kv_hstride = 0;
+  sh.o_bstride = 0; sh.o_tstride = p->head_dim; sh.window = p->window; sh.offset0 = p->position_offset;
+  *q = st.in(p->query, (size_t)p->query_len * p->head_dim);
+  *k = st.in(p->key, (size_t)p->key_len * p->head_dim);
+  *v = st.in(p->value, (size_t)p->key_len * p->head_dim);
+  sh.segment_ids = p->segment_ids ? st.in(p->segment_ids, (size_t)p->key_len) : nullptr;
+  sh.seg_len = p->segment_ids ? p->key_len : 0;
+  return st.status;
+}
+int gn_attention_forward(const gn_attention_params* p, float* out, float* lse) {
+  GN_REQUIRE(p && out, "attention_forward: null argument");
+  if (p->query_len <= 0) return GN_OK;
+  GN_BEGIN();
+  AttnShape sh; const float *q, *k, *v;
+  GN_TRY(attn_shape(p, sh, st, &q, &k, &v));
+  float* dout = st.out(out, (size_t)p->query_len * p->head_dim); float* dlse = lse ? st.out(lse, p->query_len) : nullptr;
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(attention_forward_launch(sh, q, k, v, dout, dlse, s));
+  GN_END();
+}
+int gn_attention_forward_split(const gn_attention_params* p, int kstart, int kend, float* acc, float* mx, float* sm) {
+  GN_REQUIRE(p && acc && mx && sm, "attention_forward_split: null argument");
+  if (p->query_len <= 0) return GN_OK;
+  GN_BEGIN();
+  AttnShape sh; const float *q, *k, *v;
+  GN_TRY(attn_shape(p, sh, st, &q, &k, &v));
+  float* dacc = st.out(acc, (size_t)p->query_len * p->head_dim); float* dmx = st.out(mx, p->query_len); float* dsm = st.out(sm, p->query_len);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(attention_split_launch(sh, q, k, v, kstart, kend, dacc, dmx, dsm, s));
+  GN_END();
+}
+int gn_attention_combine(const float* acc, const float* mx, const float* sm, int parts, int ql, int hd, float* out, float* lse) {
+  GN_REQUIRE(acc && mx && sm && out && parts > 0, "attention_combine: bad argument");
+  if (ql <= 0) return GN_OK;
+  GN_BEGIN();
+  const float* da = st.in(acc, (size_t)parts * ql * hd); const float* dm = st.in(mx, (size_t)parts * ql); const float* ds = st.in(sm, (size_t)parts * ql);
+  float* dout = st.out(out, (size_t)ql * hd); float* dlse = lse ? st.out(lse, ql) : nullptr;
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(attention_combine_launch(da, dm, ds, parts, ql, hd, dout, dlse, s));
+  GN_END();
+}
+int gn_attention_backward(const gn_attention_params* p, const float* output, const float* out_grad, const float* lse, const float* rowcorr,
+                          float* dq, float* dk, float* dv) {
+  GN_REQUIRE(p && out_grad && lse && dq && dk && dv && (output || rowcorr), "attention_backward: null argument");
+  if (p->query_len <= 0) return GN_OK;
+  GN_BEGIN();
+  AttnShape sh; const float *q, *k, *v;
+  GN_TRY(attn_shape(p, sh, st, &q, &k, &v));
+  size_t nq = (size_t)p->query_len * p->head_dim, nk = (size_t)p->key_len * p->head_dim;
+  const float* dout = st.in(out_grad, nq); const float* dlse = st.in(lse, p->query_len);
+  const float* dO = output ? st.in(output, nq) : nullptr;
+  const float* drc = rowcorr ? st.in(rowcorr, p->query_len) : nullptr;
+  float* ddq = st.out(dq, nq, true); float* ddk = st.out(dk, nk, true); float* ddv = st.out(dv, nk, true);
+  float* delta = nullptr;
+  GN_CUDA(cudaMalloc((void**)&delta, sizeof(float) * (size_t)std::max(p->query_len, 1)));
+  st.owned.push_back(delta);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(attention_backward_launch(sh, q, k, v, dO, dout, dlse, drc, ddq, ddk, ddv, 1, delta, s));
+  GN_END();
+}
+
+int gn_sample_next_token(const float* logits, int rows, int vocab, const float* uniforms, const uint64_t* seeds, int group, uint32_t step,
+                         float temperature, int top_k, int32_t* out) {
+  GN_REQUIRE(logits && out, "sample_next_token: null argument");
+  if (rows <= 0) return GN_OK;
+  if (group < 1) group = 1;
+  GN_BEGIN();
+  const float* dl = st.in(logits, (size_t)rows * vocab); const float* du = uniforms ? st.in(uniforms, (size_t)rows * vocab) : nullptr;
+  const uint64_t* dsd = seeds ? st.in(seeds, (size_t)((rows + group - 1) / group)) : nullptr;
+  int32_t* dd = st.out(out, rows);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(sample_launch(dl, rows, vocab, 1, du, dsd, group, nullptr, step, temperature, top_k, dd, s));
+  GN_END();
+}
+int gn_group_advantage(const float* rewards, int groups, int group, int mode, float* adv) {
+  GN_REQUIRE(rewards && adv && group > 0, "group_advantage: bad argument");
+  if (groups <= 0) return GN_OK;
+  GN_BEGIN();
+  const float* dr = st.in(rewards, (size_t)groups * group); float* da = st.out(adv, (size_t)groups * group);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(advantage_launch(dr, groups, group, mode, da, s));
+  GN_END();
+}
+int gn_pg_loss_backward(const float* logits, const int32_t* targets, const float* adv, int64_t rows, int vocab, int seq_len, float norm, float softcap,
+                        float* nll, float* dlogits, double* loss) {
+  GN_REQUIRE(logits && targets && adv && loss && vocab > 0 && seq_len > 0 && rows >= 0, "pg_loss_backward: bad argument");
+  GN_BEGIN();
+  size_t n = (size_t)rows * vocab;
+  const bool in_place = dlogits == logits;
+  const float* dl; float* dd = nullptr;
+  if (in_place) { dd = st.out(dlogits, n, true); dl = dd; }
+  else { dl = st.in(logits, n); dd = dlogits ? st.out(dlogits, n) : nullptr; }
+  const int32_t* dt = st.in(targets, rows); const float* da = st.in(adv, (size_t)((rows + seq_len - 1) / seq_len));
+  float* dn = nll ? st.out(nll, rows) : nullptr;
+  double* scratch = nullptr;
+  GN_CUDA(cudaMalloc((void**)&scratch, sizeof(double) * (size_t)(rows + 1)));
+  st.owned.push_back(scratch);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(pg_loss_launch(dl, dt, da, rows, vocab, vocab, seq_len, norm, softcap, dn, dd, vocab, scratch + 1, scratch, 0, s));
+  GN_CUDA(cudaMemcpyAsync(loss, scratch, sizeof(double), cudaMemcpyDeviceToHost, s));
+  GN_END();
+}
+
+}  // extern "C"

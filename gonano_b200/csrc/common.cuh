@@ -1,0 +1,135 @@
+// Shared declarations for the gonano CUDA backend (sm_100a).
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "../../include/gonano_cuda.h"
+
+namespace gn {
+
+// Thread-local message behind gn_last_error().
+void set_error(const char* fmt, ...);
+const char* get_error();
+
+#define GN_CUDA(expr)                                                                      \
+  do {                                                                                     \
+    cudaError_t e__ = (expr);                                                              \
+    if (e__ != cudaSuccess) {                                                              \
+      gn::set_error("%s:%d: %s -> %s", __FILE__, __LINE__, #expr, cudaGetErrorString(e__)); \
+      return GN_ERR_CUDA;                                                                  \
+    }                                                                                      \
+  } while (0)
+
+#define GN_TRY(expr)                 \
+  do {                               \
+    int s__ = (expr);                \
+    if (s__ != GN_OK) return s__;    \
+  } while (0)
+
+#define GN_REQUIRE(cond, ...)        \
+  do {                               \
+    if (!(cond)) {                   \
+      gn::set_error(__VA_ARGS__);    \
+      return GN_ERR_INVALID;         \
+    }                                \
+  } while (0)
+
+// Check the launch that just happened and count it (gn_ctx_launch_count).
+void count_launch();
+#define GN_LAUNCH_CHECK()          \
+  do {                             \
+    gn::count_launch();            \
+    GN_CUDA(cudaGetLastError());   \
+  } while (0)
+
+constexpr int kNumSM = 148;  // B200
+
+static inline int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
+
+// ------------------------------------------------------------ device helpers
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ double warp_sum_d(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// Block-wide sum; `scratch` holds at least 32 floats; every thread gets the total.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (threadIdx.x < nw) ? scratch[threadIdx.x] : 0.0f;
+  if (warp == 0) { t = warp_sum(t); if (lane == 0) scratch[0] = t; }
+  __syncthreads();
+  return scratch[0];
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (threadIdx.x < nw) ? scratch[threadIdx.x] : -INFINITY;
+  if (warp == 0) { t = warp_max(t); if (lane == 0) scratch[0] = t; }
+  __syncthreads();
+  return scratch[0];
+}
+__device__ __forceinline__ double block_sum_d(double v, double* scratch) {
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum_d(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  double t = (threadIdx.x < nw) ? scratch[threadIdx.x] : 0.0;
+  if (warp == 0) { t = warp_sum_d(t); if (lane == 0) scratch[0] = t; }
+  __syncthreads();
+  return scratch[0];
+}
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
+// Sigmoid evaluated in double like the reference's scalar backend
+// (kernels/scalar/elementwise.go:146-150); used where a gate decides values.
+__device__ __forceinline__ float sigmoid_exact(float x) { return (float)(1.0 / (1.0 + exp((double)(-x)))); }
+
+// ---------------------------------------------------------------- GEMM API
+// C[M,N] (op)= A(M,K) * B(K,N), row-major storage with leading dimensions.
+//   a_trans = 0: A(m,k) = A[m*lda + k]      a_trans = 1: A(m,k) = A[k*lda + m]
+//   b_trans = 0: B(k,n) = B[k*ldb + n]      b_trans = 1: B(k,n) = B[n*ldb + k]   (weights stored [out,in])
+enum GemmEpilogue {
+  EPI_STORE = 0,     // C = acc
+  EPI_ACCUM = 1,     // C += acc
+  EPI_RESIDUAL = 2,  // C = R + acc        (R = aux, ld = ldaux; R may alias C)
+  EPI_RELU2 = 3,     // aux = acc (optional), C = max(acc,0)^2
+  EPI_SOFTCAP = 4,   // C = cap * tanh(acc / cap)   (cap = scalar)
+  EPI_RELU2_BWD = 5, // C = acc * 2*max(aux,0)      (aux = saved pre-activation)
+};
+struct GemmArgs {
+  const float* A = nullptr; const float* B = nullptr; float* C = nullptr;
+  int M = 0, N = 0, K = 0;
+  int64_t lda = 0, ldb = 0, ldc = 0;
+  int a_trans = 0, b_trans = 0;
+  int epilogue = EPI_STORE;
+  float* aux = nullptr; int64_t ldaux = 0;
+  float scalar = 0.0f;
+};
+int gemm_simt(const GemmArgs& args, cudaStream_t stream);
+// kind 0: SIMT float32.  kind 1: tcgen05 3xTF32 where the shape allows it, else SIMT.
+int gemm_dispatch(const GemmArgs& args, int kind, cudaStream_t stream);
+int gemm_default_kind();
+int64_t launch_count();
+
+}  // namespace gn

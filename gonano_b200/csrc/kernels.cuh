@@ -1,0 +1,72 @@
+// Internal launchers (device pointers, asynchronous on `stream`).  Each returns a
+// gn status after checking the launch.
+#pragma once
+#include "common.cuh"
+
+namespace gn {
+
+// ------------------------------------------------------------- elementwise.cu
+enum EwOp { EW_ADD, EW_SUB, EW_MUL, EW_DIV, EW_SCALE, EW_ADD_SCALED, EW_NEG, EW_ABS, EW_SQUARE, EW_RELU2, EW_EXP, EW_SIGMOID,
+            EW_TANH, EW_RSQRT, EW_SWIGLU };
+int ew_launch(int op, float* dst, const float* a, const float* b, float factor, int64_t n, cudaStream_t s);
+int swiglu_backward_launch(float* gg, float* ug, const float* gate, const float* up, const float* og, float clamp, int64_t n, cudaStream_t s);
+// out (device) receives the result.
+int reduce_sum_launch(const float* v, int64_t n, float* out, cudaStream_t s);
+int reduce_max_launch(const float* v, int64_t n, float* out, cudaStream_t s);
+int reduce_argmax_launch(const float* v, int64_t n, int64_t* out, cudaStream_t s);
+int dot_launch(const float* a, const float* b, int64_t n, float* out, cudaStream_t s);
+int softmax_rows_launch(float* dst, const float* src, int64_t rows, int cols, cudaStream_t s);
+int rmsnorm_rows_launch(float* dst, const float* src, int64_t rows, int cols, float eps, cudaStream_t s);
+// dx = dy/r - x*(dy.x)/(n r^3); when `add` != null: dx = add + that.
+int rmsnorm_backward_launch(float* dx, const float* x, const float* dy, const float* add, int64_t rows, int cols, float eps, cudaStream_t s);
+int fill_launch(float* dst, float value, int64_t n, cudaStream_t s);
+
+// --------------------------------------------------------------------- moe.cu
+int topk_indices_launch(int32_t* dst, const float* scores, int rows, int count, int k, cudaStream_t s);
+int moe_gate_topk_launch(const float* logits, const float* bias, float* probs, int32_t* sel, float* w, int rows, int experts, int k, cudaStream_t s);
+int grouped_matmul_t_launch(float* dst, const float* input, const float* weight, const int32_t* counts_dev, int experts, int cols, int inner,
+                            int64_t total_rows, cudaStream_t s);
+int indexer_scores_launch(float* dst, const float* q, const float* k, const float* w, int rows, int blocks, int heads, int dim, cudaStream_t s);
+int indexer_block_max_launch(float* dst, const float* scores, int rows, int blocks, int group, cudaStream_t s);
+
+// --------------------------------------------------------------- attention.cu
+// Strided multi-head attention over token-major tensors.
+//   q:  element (b, t, hq, d) at q[(b*q_bstride + t*q_tstride) + hq*D + d]
+//   k/v: element (b, j, hk, d) at k[b*kv_bstride + j*kv_tstride + hk*kv_hstride + d]
+//   out: like q with its own strides; lse [B, Hq, Tq] (nullable)
+//   query i of row b sits at absolute position offset[b] (or offset0 when offsets == null) + i.
+struct AttnShape {
+  int B = 1, Hq = 1, Hkv = 1, D = 0, Tq = 0, Tk = 0;
+  int64_t q_bstride = 0, q_tstride = 0;
+  int64_t kv_bstride = 0, kv_tstride = 0, kv_hstride = 0;
+  int64_t o_bstride = 0, o_tstride = 0;
+  int window = -1;
+  int offset0 = 0;
+  const int32_t* segment_ids = nullptr;  // [Tk] shared by all rows (Tier A only)
+  int seg_len = 0;
+};
+int attention_forward_launch(const AttnShape& sh, const float* q, const float* k, const float* v, float* out, float* lse, cudaStream_t s);
+// Gradients: dq like q (strides of q), dk/dv like k/v.  accumulate != 0 adds into them.
+int attention_backward_launch(const AttnShape& sh, const float* q, const float* k, const float* v, const float* out, const float* dout,
+                              const float* lse, const float* row_correction, float* dq, float* dk, float* dv, int accumulate,
+                              float* delta_scratch, cudaStream_t s);
+int attention_split_launch(const AttnShape& sh, const float* q, const float* k, const float* v, int kstart, int kend, float* acc, float* mx,
+                           float* sm, cudaStream_t s);
+int attention_combine_launch(const float* acc, const float* mx, const float* sm, int parts, int ql, int hd, float* out, float* lse, cudaStream_t s);
+// Decode: one query token per row over the KV cache [row][hk][max_seq][D]; ctx_len[row] keys (device array).
+int attention_decode_launch(const float* q, int64_t q_rstride, const float* kcache, const float* vcache, int64_t row_stride, int64_t head_stride,
+                            const int32_t* ctx_len, int rows, int Hq, int Hkv, int D, int window, float* out, int64_t o_rstride,
+                            float* part_acc, float* part_ms, int splits, cudaStream_t s);
+int attention_decode_splits(int rows, int Hkv, int max_ctx);
+
+// ----------------------------------------------------------------- sampler.cu
+int sample_launch(const float* logits, int rows, int vocab, int logits_row_div, const float* uniforms, const uint64_t* seeds_dev, int group,
+                  const uint32_t* step_dev, uint32_t step_host, float temperature, int top_k, int32_t* out, cudaStream_t s);
+
+// -------------------------------------------------------------------- loss.cu
+// row_loss: [rows] double scratch; loss_out: device double.
+int pg_loss_launch(const float* logits, const int32_t* targets, const float* adv, int64_t rows, int vocab, int64_t ld, int seq_len, float norm,
+                   float softcap, float* nll, float* dlogits, int64_t ldd, double* row_loss, double* loss_out, int accumulate_loss, cudaStream_t s);
+int advantage_launch(const float* rewards, int groups, int group, int mode, float* adv, cudaStream_t s);
+
+}  // namespace gn

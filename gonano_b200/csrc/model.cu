@@ -1,0 +1,711 @@
+// Resident session (Tier B): the dense transformer of the reference held in
+// device memory, with the three phases of the RL step driven from the host in
+// C++: batched rollout (inference/engine.go:112-369 over
+// model/transformer.go:243-342), the policy-gradient loss and the training
+// forward/backward (trainer/rl.go:14-60, model/train_transformer.go:63-320,
+// model/train.go:55-572).
+//
+// Memory layout in HBM
+//   parameters / gradients: one flat float32 buffer each, every tensor padded to
+//     a multiple of 64 floats; per layer c_q, c_k, c_v are adjacent so that the
+//     three projections are one GEMM.  The gradient buffer is what the
+//     data-parallel all-reduce sums.
+//   KV cache: [layer][k|v][row][kv head][max_seq][head_dim], contiguous per
+//     (row, head) like the reference's cache (model/kvcache.go:10-28), all rows
+//     of all prompts in one batch.
+//   activations: token-major [rows, width]; attention reads Q/K/V in place from
+//     the fused projection output through strides (no head-major transposes).
+#include <algorithm>
+#include <cmath>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "kernels.cuh"
+#include "model_kernels.cuh"
+
+using namespace gn;
+
+struct gn_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  bool own_stream = false;
+  int gemm_kind = 1;
+};
+
+namespace {
+
+struct DevBuf {
+  void* p = nullptr;
+  size_t bytes = 0;
+  int ensure(size_t n) {
+    if (n <= bytes) return GN_OK;
+    if (p) cudaFree(p);
+    p = nullptr; bytes = 0;
+    cudaError_t e = cudaMalloc(&p, n);
+    if (e != cudaSuccess) { set_error("cudaMalloc(%zu bytes) failed: %s", n, cudaGetErrorString(e)); return GN_ERR_NOMEM; }
+    bytes = n;
+    return GN_OK;
+  }
+  void release() { if (p) cudaFree(p); p = nullptr; bytes = 0; }
+  float* f() const { return (float*)p; }
+  int32_t* i() const { return (int32_t*)p; }
+};
+
+struct ParamInfo {
+  std::string name;
+  int rows = 0, cols = 0;
+  int64_t offset = 0;
+};
+
+// A bump allocator over one DevBuf: buffers of one pass are carved in order.
+struct Arena {
+  DevBuf buf;
+  size_t used = 0;
+  size_t planned = 0;
+  bool planning = false;
+  float* take(size_t floats) {
+    size_t bytes = ((floats * sizeof(float) + 255) / 256) * 256;
+    if (planning) { planned += bytes; return nullptr; }
+    float* r = (float*)((char*)buf.p + used);
+    used += bytes;
+    return r;
+  }
+};
+
+struct LayerOffsets { int64_t qkv, proj, ve_gate, fc, mproj, ve; bool has_ve; };
+
+struct LayerSaved {
+  float *Xin, *H, *QKV, *QKROT, *O, *LSE, *VESIG, *MID, *M, *U, *HID, *XOUT;
+};
+
+}  // namespace
+
+struct gn_model {
+  gn_ctx* ctx = nullptr;
+  gn_config cfg{};
+  int d = 0, L = 0, Hq = 0, Hkv = 0, D = 0, R = 0, V = 0, Vp = 0, W = 0, KV = 0;
+  std::vector<int> windows;
+  std::vector<ParamInfo> params;               // sorted by name
+  std::map<std::string, int> index;
+  int64_t total = 0;
+  DevBuf P, G;
+  std::vector<LayerOffsets> lo;
+  int64_t off_wte = 0, off_lm = 0, off_rho = 0, off_chi = 0, off_smear_gate = 0, off_smear_lambda = 0, off_backout = 0;
+  DevBuf cosb, sinb, sacc;
+  // inference state
+  DevBuf cache, prev, pos, ctxlen, ids_dev, sampled, seeds, out_tokens, out_lengths, done, n_done, sel;
+  DevBuf part_acc, part_ms;
+  Arena infer, train;
+  DevBuf tgt_dev, adv_dev, rowloss, loss_dev, in_dev;
+  std::map<std::string, float> phase_ms;
+  cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
+
+  float* p(int64_t off) const { return P.f() + off; }
+  float* g(int64_t off) const { return G.f() + off; }
+  cudaStream_t s() const { return ctx->stream; }
+};
+
+namespace {
+
+int gemm(gn_model* m, const GemmArgs& a) { return gemm_dispatch(a, m->ctx->gemm_kind, m->s()); }
+
+int64_t align64(int64_t n) { return (n + 63) / 64 * 64; }
+
+bool has_ve(int layer, int L) { return layer % 2 == (L - 1) % 2; }  // model/helpers.go:69-71
+
+int build_layout(gn_model* m) {
+  const int d = m->d, L = m->L, D = m->D, Hq = m->Hq, Hkv = m->Hkv, Vp = m->Vp, KV = m->KV;
+  int64_t off = 0;
+  auto add = [&](const std::string& name, int rows, int cols, bool align = true) {
+    ParamInfo pi; pi.name = name; pi.rows = rows; pi.cols = cols;
+    if (align) off = align64(off);
+    pi.offset = off; off += (int64_t)rows * cols;
+    m->params.push_back(pi);
+    return pi.offset;
+  };
+  m->off_wte = add("transformer.wte.weight", Vp, d);
+  m->off_lm = add("lm_head.weight", Vp, d);
+  m->lo.resize(L);
+  for (int l = 0; l < L; ++l) {
+    std::string p = "transformer.h." + std::to_string(l) + ".";
+    LayerOffsets& o = m->lo[l];
+    o.qkv = add(p + "attn.c_q.weight", Hq * D, d);
+    add(p + "attn.c_k.weight", KV, d, false);   // adjacent: [c_q; c_k; c_v] is one [W, d] matrix
+    add(p + "attn.c_v.weight", KV, d, false);
+    o.proj = add(p + "attn.c_proj.weight", d, d);
+    o.has_ve = has_ve(l, L);
+    o.ve_gate = o.ve = -1;
+    if (o.has_ve) {
+      o.ve_gate = add(p + "attn.ve_gate.weight", Hkv, kVeGateChannels);
+      o.ve = add("value_embeds." + std::to_string(l) + ".weight", Vp, KV);
+    }
+    o.fc = add(p + "mlp.c_fc.weight", 4 * d, d);
+    o.mproj = add(p + "mlp.c_proj.weight", d, 4 * d);
+  }
+  m->off_smear_gate = add("smear_gate.weight", 1, kSmearChannels);
+  // The four scalar parameter groups are adjacent (2L+2 floats) so that their
+  // float64 accumulators flush in one launch.
+  m->off_rho = add("resid_lambdas", 1, L);
+  m->off_chi = add("x0_lambdas", 1, L, false);
+  m->off_smear_lambda = add("smear_lambda", 1, 1, false);
+  m->off_backout = add("backout_lambda", 1, 1, false);
+  m->total = align64(off);
+  std::sort(m->params.begin(), m->params.end(), [](const ParamInfo& a, const ParamInfo& b) { return a.name < b.name; });
+  for (size_t i = 0; i < m->params.size(); ++i) m->index[m->params[i].name] = (int)i;
+  return GN_OK;
+}
+
+int enter(gn_model* m) {
+  GN_REQUIRE(m && m->ctx, "null model");
+  GN_CUDA(cudaSetDevice(m->ctx->device));
+  return GN_OK;
+}
+
+// ------------------------------------------------------------------ forward
+enum Mode { MODE_PLAIN, MODE_PREFILL, MODE_DECODE, MODE_TRAIN };
+
+struct FwdBufs {
+  float *E, *X0, *Xa, *Xb, *H, *QKV, *O, *M, *HID, *BO, *Y, *LOGITS;
+  // train only
+  float *SIG, *FP;
+  std::vector<LayerSaved> layers;
+};
+
+struct FwdArgs {
+  Mode mode;
+  const int32_t* ids;      // device [B*T]
+  int B, T;
+  int cache_rows = 0, cache_row_mul = 1, max_seq = 0;
+  int logits_rows = 0;     // rows that get logits (PLAIN/TRAIN: all; PREFILL: B; DECODE: B)
+};
+
+size_t plan_bufs(gn_model* m, Arena& a, FwdBufs& b, Mode mode, int64_t rows, int64_t logit_rows, int B, int T) {
+  const int d = m->d, W = m->W, Hq = m->Hq, Hkv = m->Hkv, D = m->D, V = m->V, L = m->L;
+  b.E = a.take(rows * d);
+  b.X0 = a.take(rows * d);
+  b.Y = a.take(std::max<int64_t>(rows, logit_rows) * d);
+  b.LOGITS = a.take(logit_rows * V);
+  if (mode == MODE_TRAIN) {
+    b.SIG = a.take((int64_t)B * std::max(T - 1, 1));
+    b.FP = a.take(rows * d);
+    b.layers.resize(L);
+    for (int l = 0; l < L; ++l) {
+      LayerSaved& s = b.layers[l];
+      s.Xin = a.take(rows * d); s.H = a.take(rows * d); s.QKV = a.take(rows * W); s.QKROT = a.take(rows * (int64_t)(Hq + Hkv) * D);
+      s.O = a.take(rows * (int64_t)Hq * D); s.LSE = a.take((int64_t)B * Hq * T); s.VESIG = a.take(rows * Hkv);
+      s.MID = a.take(rows * d); s.M = a.take(rows * d); s.U = a.take(rows * 4 * d); s.HID = a.take(rows * 4 * d); s.XOUT = a.take(rows * d);
+    }
+    b.Xa = b.Xb = b.H = b.QKV = b.O = b.M = b.HID = b.BO = nullptr;
+  } else {
+    b.Xa = a.take(rows * d); b.Xb = nullptr;
+    b.H = a.take(rows * d); b.QKV = a.take(rows * W); b.O = a.take(rows * (int64_t)Hq * D);
+    b.M = a.take(rows * d); b.HID = a.take(rows * 4 * d); b.BO = a.take(rows * d);
+    b.SIG = b.FP = nullptr;
+  }
+  return a.planned;
+}
+
+int make_bufs(gn_model* m, Arena& a, FwdBufs& b, Mode mode, int64_t rows, int64_t logit_rows, int B, int T, size_t extra_floats, float** extra) {
+  a.planning = true; a.planned = 0;
+  plan_bufs(m, a, b, mode, rows, logit_rows, B, T);
+  if (extra_floats) a.take(extra_floats);
+  size_t need = a.planned;
+  a.planning = false;
+  GN_TRY(a.buf.ensure(need));
+  a.used = 0;
+  plan_bufs(m, a, b, mode, rows, logit_rows, B, T);
+  if (extra_floats) *extra = a.take(extra_floats);
+  return GN_OK;
+}
+
+// Runs the trunk.  Returns with b.Y = final normalised hidden rows that feed lm_head
+// (PREFILL: one row per sequence, the last position) and b.LOGITS filled.
+int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
+  const int d = m->d, W = m->W, Hq = m->Hq, Hkv = m->Hkv, D = m->D, V = m->V, L = m->L;
+  const int B = a.B, T = a.T;
+  const int64_t rows = (int64_t)B * T;
+  cudaStream_t s = m->s();
+  const bool train = a.mode == MODE_TRAIN;
+  const bool cached = a.mode == MODE_PREFILL || a.mode == MODE_DECODE;
+
+  GN_TRY(embed_norm_launch(a.ids, m->p(m->off_wte), b.E, rows, d, s));
+  const float* prev_in = (a.mode == MODE_DECODE) ? m->prev.f() : nullptr;
+  float* prev_out = cached ? m->prev.f() : nullptr;
+  GN_TRY(smear_launch(b.E, b.X0, prev_in, prev_out, a.cache_row_mul, train ? b.SIG : nullptr, m->p(m->off_smear_gate), m->p(m->off_smear_lambda),
+                      B, T, d, s));
+  const int64_t layer_stride = (int64_t)a.cache_rows * Hkv * a.max_seq * D;
+  const float* x_prev = b.X0;
+  const float* backout = nullptr;
+  for (int l = 0; l < L; ++l) {
+    const LayerOffsets& o = m->lo[l];
+    float *Xin, *H, *QKV, *O, *MID, *Mn, *U, *HID, *XOUT;
+    if (train) {
+      LayerSaved& sv = b.layers[l];
+      Xin = sv.Xin; H = sv.H; QKV = sv.QKV; O = sv.O; MID = sv.MID; Mn = sv.M; U = sv.U; HID = sv.HID; XOUT = sv.XOUT;
+    } else {
+      Xin = b.Xa; H = b.H; QKV = b.QKV; O = b.O; MID = b.Xa; Mn = b.M; U = nullptr; HID = b.HID; XOUT = b.Xa;
+    }
+    GN_TRY(mix_norm_launch(x_prev, b.X0, m->p(m->off_rho), m->p(m->off_chi), l, Xin, H, rows, d, s));
+    // q, k, v projections as one GEMM against [c_q; c_k; c_v]
+    { GemmArgs g; g.A = H; g.lda = d; g.B = m->p(o.qkv); g.ldb = d; g.b_trans = 1; g.C = QKV; g.ldc = W; g.M = (int)rows; g.N = W; g.K = d; GN_TRY(gemm(m, g)); }
+    QkvPost qp;
+    qp.qkv = QKV; qp.H = H; qp.ids = a.ids;
+    qp.ve_table = o.has_ve ? m->p(o.ve) : nullptr; qp.ve_gate = o.has_ve ? m->p(o.ve_gate) : nullptr;
+    qp.cosv = m->cosb.f(); qp.sinv = m->sinb.f();
+    qp.qk_rot = train ? b.layers[l].QKROT : nullptr; qp.ve_sig = train ? b.layers[l].VESIG : nullptr;
+    if (cached) {
+      qp.kcache = m->cache.f() + (int64_t)(2 * l) * layer_stride; qp.vcache = m->cache.f() + (int64_t)(2 * l + 1) * layer_stride;
+      qp.pos = m->pos.i(); qp.cache_row_mul = a.cache_row_mul; qp.max_seq = a.max_seq;
+    }
+    qp.B = B; qp.T = T; qp.Hq = Hq; qp.Hkv = Hkv; qp.D = D; qp.R = m->R; qp.d = d;
+    GN_TRY(qkv_post_launch(qp, s));
+    if (a.mode == MODE_DECODE) {
+      int splits = attention_decode_splits(B, Hkv, a.max_seq);
+      GN_TRY(attention_decode_launch(QKV, W, m->cache.f() + (int64_t)(2 * l) * layer_stride, m->cache.f() + (int64_t)(2 * l + 1) * layer_stride,
+                                     (int64_t)Hkv * a.max_seq * D, (int64_t)a.max_seq * D, m->ctxlen.i(), B, Hq, Hkv, D, m->windows[l], O,
+                                     (int64_t)Hq * D, m->part_acc.f(), m->part_ms.f(), splits, s));
+    } else {
+      AttnShape sh;
+      sh.B = B; sh.Hq = Hq; sh.Hkv = Hkv; sh.D = D; sh.Tq = T; sh.Tk = T;
+      sh.q_bstride = (int64_t)T * W; sh.q_tstride = W; sh.kv_bstride = (int64_t)T * W; sh.kv_tstride = W; sh.kv_hstride = D;
+      sh.o_bstride = (int64_t)T * Hq * D; sh.o_tstride = (int64_t)Hq * D; sh.window = m->windows[l]; sh.offset0 = 0;
+      GN_TRY(attention_forward_launch(sh, QKV, QKV + (int64_t)Hq * D, QKV + (int64_t)(Hq + Hkv) * D, O, train ? b.layers[l].LSE : nullptr, s));
+    }
+    // MID = Xin + O Wo^T
+    { GemmArgs g; g.A = O; g.lda = (int64_t)Hq * D; g.B = m->p(o.proj); g.ldb = (int64_t)Hq * D; g.b_trans = 1; g.C = MID; g.ldc = d; g.M = (int)rows; g.N = d; g.K = Hq * D;
+      g.epilogue = EPI_RESIDUAL; g.aux = Xin; g.ldaux = d; GN_TRY(gemm(m, g)); }
+    GN_TRY(norm_launch(MID, Mn, rows, d, s));
+    // HID = relu(M Wfc^T)^2   (training also keeps the pre-activation)
+    { GemmArgs g; g.A = Mn; g.lda = d; g.B = m->p(o.fc); g.ldb = d; g.b_trans = 1; g.C = HID; g.ldc = 4 * d; g.M = (int)rows; g.N = 4 * d; g.K = d;
+      g.epilogue = EPI_RELU2; g.aux = U; g.ldaux = 4 * d; GN_TRY(gemm(m, g)); }
+    // XOUT = MID + HID Wp^T
+    { GemmArgs g; g.A = HID; g.lda = 4 * d; g.B = m->p(o.mproj); g.ldb = 4 * d; g.b_trans = 1; g.C = XOUT; g.ldc = d; g.M = (int)rows; g.N = d; g.K = 4 * d;
+      g.epilogue = EPI_RESIDUAL; g.aux = MID; g.ldaux = d; GN_TRY(gemm(m, g)); }
+    if (l == L / 2) {
+      if (train) backout = XOUT;
+      else { GN_CUDA(cudaMemcpyAsync(b.BO, XOUT, sizeof(float) * rows * d, cudaMemcpyDeviceToDevice, s)); backout = b.BO; }
+    }
+    x_prev = XOUT;
+  }
+  // final: y = norm(x - lambda_b * backout); logits = softcap(y W_lm^T)[:, :V]
+  int64_t lrows = rows;
+  const int32_t* sel = nullptr;
+  if (a.mode == MODE_PREFILL) { lrows = B; sel = m->sel.i(); }
+  GN_TRY(backout_norm_launch(x_prev, backout, m->p(m->off_backout), sel, train ? b.FP : nullptr, b.Y, lrows, d, s));
+  { GemmArgs g; g.A = b.Y; g.lda = d; g.B = m->p(m->off_lm); g.ldb = d; g.b_trans = 1; g.C = b.LOGITS; g.ldc = V; g.M = (int)lrows; g.N = V; g.K = d;
+    g.epilogue = EPI_SOFTCAP; g.scalar = kSoftcap; GN_TRY(gemm(m, g)); }
+  return GN_OK;
+}
+
+// ----------------------------------------------------------------- backward
+struct BwdBufs { float *DFP, *DY, *CUR, *DX0, *DOUT, *DU, *DM, *DMID, *DO, *DQKV, *DH, *DXIN, *DELTA, *DPRE, *DE; };
+
+size_t bwd_floats(gn_model* m, int64_t rows, int B, int T) {
+  const int64_t d = m->d, W = m->W, Hq = m->Hq, Hkv = m->Hkv, D = m->D;
+  auto r = [](int64_t n) { return (n + 63) / 64 * 64; };
+  return r(rows * d) * 9 + r(rows * 4 * d) + r(rows * Hq * D) + r(rows * W) + r((int64_t)B * Hq * T) + r(rows * Hkv);
+}
+void carve_bwd(gn_model* m, float* base, BwdBufs& w, int64_t rows, int B, int T) {
+  const int64_t d = m->d, W = m->W, Hq = m->Hq, Hkv = m->Hkv, D = m->D;
+  auto r = [](int64_t n) { return (n + 63) / 64 * 64; };
+  float* p = base;
+  auto take = [&](int64_t n) { float* q = p; p += r(n); return q; };
+  w.DFP = take(rows * d); w.DY = take(rows * d); w.CUR = take(rows * d); w.DX0 = take(rows * d); w.DOUT = take(rows * d);
+  w.DM = take(rows * d); w.DMID = take(rows * d); w.DH = take(rows * d); w.DXIN = take(rows * d);
+  w.DU = take(rows * 4 * d); w.DO = take(rows * Hq * D); w.DQKV = take(rows * W); w.DELTA = take((int64_t)B * Hq * T); w.DPRE = take(rows * Hkv);
+  w.DE = w.DY;  // free again by the time the embedding gradient is formed
+}
+
+int backward_core(gn_model* m, FwdBufs& b, BwdBufs& w, const int32_t* ids, int B, int T) {
+  const int d = m->d, W = m->W, Hq = m->Hq, Hkv = m->Hkv, D = m->D, V = m->V, L = m->L;
+  const int64_t rows = (int64_t)B * T;
+  const int64_t n = rows * d;
+  cudaStream_t s = m->s();
+  double* sacc = (double*)m->sacc.p;
+  float* DZ = b.LOGITS;  // the loss kernel turned the logits into dz in place
+  // lm_head: dW[:V] += dz^T y ; dy = dz W[:V]      (model/layers/linear.go:45-53)
+  { GemmArgs g; g.A = DZ; g.lda = V; g.a_trans = 1; g.B = b.Y; g.ldb = d; g.b_trans = 0; g.C = m->g(m->off_lm); g.ldc = d; g.M = V; g.N = d; g.K = (int)rows;
+    g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
+  { GemmArgs g; g.A = DZ; g.lda = V; g.B = m->p(m->off_lm); g.ldb = d; g.b_trans = 0; g.C = w.DY; g.ldc = d; g.M = (int)rows; g.N = d; g.K = V; GN_TRY(gemm(m, g)); }
+  GN_TRY(rmsnorm_backward_launch(w.DFP, b.FP, w.DY, nullptr, rows, d, kNormEps, s));
+  const float* backout = b.layers[L / 2].XOUT;
+  GN_TRY(dot_accumulate_launch(w.DFP, backout, n, -1.0, sacc + 2 * L + 1, s));   // d lambda_b (train_transformer.go:181-190)
+  const float* cur = w.DFP;
+  for (int l = L - 1; l >= 0; --l) {
+    const LayerOffsets& o = m->lo[l];
+    LayerSaved& sv = b.layers[l];
+    const float* dout = cur;
+    if (l == L / 2) {
+      // the backout branch joins here: dout = cur + (-lambda_b) * dFP
+      GN_CUDA(cudaMemcpyAsync(w.DOUT, cur, sizeof(float) * n, cudaMemcpyDeviceToDevice, s));
+      GN_TRY(axpy_launch(w.DOUT, w.DFP, 0.0f, m->p(m->off_backout), -1.0f, 1, n, s));
+      dout = w.DOUT;
+    }
+    // ---- MLP backward (model/train.go:505-514)
+    { GemmArgs g; g.A = dout; g.lda = d; g.a_trans = 1; g.B = sv.HID; g.ldb = 4 * d; g.C = m->g(o.mproj); g.ldc = 4 * d; g.M = d; g.N = 4 * d; g.K = (int)rows;
+      g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
+    { GemmArgs g; g.A = dout; g.lda = d; g.B = m->p(o.mproj); g.ldb = 4 * d; g.C = w.DU; g.ldc = 4 * d; g.M = (int)rows; g.N = 4 * d; g.K = d;
+      g.epilogue = EPI_RELU2_BWD; g.aux = sv.U; g.ldaux = 4 * d; GN_TRY(gemm(m, g)); }
+    { GemmArgs g; g.A = w.DU; g.lda = 4 * d; g.a_trans = 1; g.B = sv.M; g.ldb = d; g.C = m->g(o.fc); g.ldc = d; g.M = 4 * d; g.N = d; g.K = (int)rows;
+      g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
+    { GemmArgs g; g.A = w.DU; g.lda = 4 * d; g.B = m->p(o.fc); g.ldb = d; g.C = w.DM; g.ldc = d; g.M = (int)rows; g.N = d; g.K = 4 * d; GN_TRY(gemm(m, g)); }
+    GN_TRY(rmsnorm_backward_launch(w.DMID, sv.MID, w.DM, dout, rows, d, kNormEps, s));
+    // ---- attention backward (model/train.go:198-427)
+    { GemmArgs g; g.A = w.DMID; g.lda = d; g.a_trans = 1; g.B = sv.O; g.ldb = (int64_t)Hq * D; g.C = m->g(o.proj); g.ldc = (int64_t)Hq * D; g.M = d; g.N = Hq * D; g.K = (int)rows;
+      g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
+    { GemmArgs g; g.A = w.DMID; g.lda = d; g.B = m->p(o.proj); g.ldb = (int64_t)Hq * D; g.C = w.DO; g.ldc = (int64_t)Hq * D; g.M = (int)rows; g.N = Hq * D; g.K = d; GN_TRY(gemm(m, g)); }
+    AttnShape sh;
+    sh.B = B; sh.Hq = Hq; sh.Hkv = Hkv; sh.D = D; sh.Tq = T; sh.Tk = T;
+    sh.q_bstride = (int64_t)T * W; sh.q_tstride = W; sh.kv_bstride = (int64_t)T * W; sh.kv_tstride = W; sh.kv_hstride = D;
+    sh.o_bstride = (int64_t)T * Hq * D; sh.o_tstride = (int64_t)Hq * D; sh.window = m->windows[l]; sh.offset0 = 0;
+    GN_TRY(attention_backward_launch(sh, sv.QKV, sv.QKV + (int64_t)Hq * D, sv.QKV + (int64_t)(Hq + Hkv) * D, sv.O, w.DO, sv.LSE, nullptr, w.DQKV,
+                                     w.DQKV + (int64_t)Hq * D, w.DQKV + (int64_t)(Hq + Hkv) * D, 0, w.DELTA, s));
+    QkvPostBwd qb;
+    qb.dqkv = w.DQKV; qb.qk_rot = sv.QKROT; qb.ve_sig = sv.VESIG; qb.ve_table = o.has_ve ? m->p(o.ve) : nullptr; qb.ids = ids;
+    qb.ve_grad = o.has_ve ? m->g(o.ve) : nullptr; qb.dpre = w.DPRE; qb.cosv = m->cosb.f(); qb.sinv = m->sinb.f();
+    qb.B = B; qb.T = T; qb.Hq = Hq; qb.Hkv = Hkv; qb.D = D; qb.R = m->R;
+    GN_TRY(qkv_post_backward_launch(qb, s));
+    { GemmArgs g; g.A = w.DQKV; g.lda = W; g.a_trans = 1; g.B = sv.H; g.ldb = d; g.C = m->g(o.qkv); g.ldc = d; g.M = W; g.N = d; g.K = (int)rows;
+      g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
+    { GemmArgs g; g.A = w.DQKV; g.lda = W; g.B = m->p(o.qkv); g.ldb = d; g.C = w.DH; g.ldc = d; g.M = (int)rows; g.N = d; g.K = W; GN_TRY(gemm(m, g)); }
+    if (o.has_ve) GN_TRY(ve_gate_backward_launch(w.DPRE, sv.H, m->p(o.ve_gate), m->g(o.ve_gate), w.DH, rows, Hkv, d, s));
+    GN_TRY(rmsnorm_backward_launch(w.DXIN, sv.Xin, w.DH, w.DMID, rows, d, kNormEps, s));
+    // ---- residual mix (model/train_transformer.go:218-242)
+    const float* prevX = (l == 0) ? b.X0 : b.layers[l - 1].XOUT;
+    GN_TRY(mix_backward_launch(w.DXIN, prevX, b.X0, m->p(m->off_rho), m->p(m->off_chi), l, w.CUR, w.DX0, l == L - 1, sacc + l, sacc + L + l, n, s));
+    cur = w.CUR;
+  }
+  GN_TRY(ew_launch(EW_ADD, w.CUR, w.CUR, w.DX0, 0.0f, n, s));
+  GN_TRY(smear_backward_launch(w.CUR, b.X0, b.E, b.SIG, m->p(m->off_smear_gate), m->p(m->off_smear_lambda), w.DE, m->g(m->off_smear_gate), sacc + 2 * L,
+                               B, T, d, s));
+  GN_TRY(embed_backward_launch(ids, m->p(m->off_wte), w.DE, m->g(m->off_wte), rows, d, s));
+  return GN_OK;
+}
+
+}  // namespace
+
+// =========================================================================
+extern "C" {
+
+int gn_ctx_create(int device, void* stream, gn_ctx** out) {
+  GN_REQUIRE(out, "gn_ctx_create: null out");
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0) { set_error("no CUDA device: %s", cudaGetErrorString(e)); return GN_ERR_CUDA; }
+  GN_REQUIRE(device >= 0 && device < count, "device %d outside [0,%d)", device, count);
+  GN_CUDA(cudaSetDevice(device));
+  gn_ctx* c = new gn_ctx();
+  c->device = device;
+  if (stream) { c->stream = (cudaStream_t)stream; c->own_stream = false; }
+  else { GN_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking)); c->own_stream = true; }
+  c->gemm_kind = gemm_default_kind();
+  *out = c;
+  return GN_OK;
+}
+int gn_ctx_destroy(gn_ctx* c) {
+  if (!c) return GN_OK;
+  cudaSetDevice(c->device);
+  if (c->own_stream) cudaStreamDestroy(c->stream);
+  delete c;
+  return GN_OK;
+}
+int gn_ctx_sync(gn_ctx* c) { GN_REQUIRE(c, "null ctx"); GN_CUDA(cudaSetDevice(c->device)); GN_CUDA(cudaStreamSynchronize(c->stream)); return GN_OK; }
+int gn_ctx_launch_count(gn_ctx* c, int64_t* out) { GN_REQUIRE(out, "null out"); *out = launch_count(); return GN_OK; }
+int gn_ctx_set_gemm(gn_ctx* c, int kind) { GN_REQUIRE(c && (kind == 0 || kind == 1), "gemm kind must be 0 or 1"); c->gemm_kind = kind; return GN_OK; }
+
+int gn_model_create(gn_ctx* ctx, const gn_config* cfg, gn_model** out) {
+  GN_REQUIRE(ctx && cfg && out, "gn_model_create: null argument");
+  GN_REQUIRE(cfg->n_head > 0 && cfg->n_kv_head > 0 && cfg->embed_dim % cfg->n_head == 0, "embed_dim %d not divisible by n_head %d", cfg->embed_dim, cfg->n_head);
+  GN_REQUIRE(cfg->n_head % cfg->n_kv_head == 0, "n_head %d not divisible by n_kv_head %d", cfg->n_head, cfg->n_kv_head);
+  GN_REQUIRE(cfg->n_layer > 0 && cfg->vocab_size > 11 && cfg->sequence_len > 0, "bad layer/vocab/sequence configuration");
+  GN_CUDA(cudaSetDevice(ctx->device));
+  gn_model* m = new gn_model();
+  m->ctx = ctx; m->cfg = *cfg;
+  m->d = cfg->embed_dim; m->L = cfg->n_layer; m->Hq = cfg->n_head; m->Hkv = cfg->n_kv_head; m->D = m->d / m->Hq;
+  m->R = cfg->rotary_dims <= 0 ? m->D : cfg->rotary_dims;     // model/config.go:430-444
+  m->V = cfg->vocab_size; m->Vp = (m->V + 63) / 64 * 64;      // model/config.go:619-624
+  m->W = (m->Hq + 2 * m->Hkv) * m->D; m->KV = m->Hkv * m->D;
+  if (m->D > 128 || m->R > m->D || m->R % 2 != 0 || m->d < kSmearChannels) { set_error("unsupported head_dim %d / rotary %d / embed %d", m->D, m->R, m->d); delete m; return GN_ERR_INVALID; }
+  // model/config.go:629-645 (integer division truncating toward zero, as in Go)
+  std::string pattern = cfg->window_pattern[0] ? std::string(cfg->window_pattern, strnlen(cfg->window_pattern, 16)) : std::string("L");
+  int longw = cfg->sequence_len, shortw = -((-cfg->sequence_len / 4) / 128) * 128;
+  m->windows.assign(m->L, longw);
+  for (int l = 0; l < m->L; ++l) { char c = pattern[l % pattern.size()]; m->windows[l] = (c == 'S' || c == 's') ? shortw : longw; }
+  m->windows[m->L - 1] = longw;
+  build_layout(m);
+  int st = m->P.ensure(sizeof(float) * m->total);
+  if (st == GN_OK) st = m->G.ensure(sizeof(float) * m->total);
+  if (st == GN_OK) st = m->sacc.ensure(sizeof(double) * (2 * m->L + 2));
+  if (st != GN_OK) { delete m; return st; }
+  GN_CUDA(cudaMemsetAsync(m->P.p, 0, sizeof(float) * m->total, ctx->stream));
+  GN_CUDA(cudaMemsetAsync(m->G.p, 0, sizeof(float) * m->total, ctx->stream));
+  GN_CUDA(cudaMemsetAsync(m->sacc.p, 0, sizeof(double) * (2 * m->L + 2), ctx->stream));
+  // rotary tables in float64 -> float32 (model/rotary.go:16-30), sequence_len*10 positions
+  int half = m->R / 2; int64_t seq = (int64_t)cfg->sequence_len * 10;
+  std::vector<float> c((size_t)seq * half), sn((size_t)seq * half);
+  for (int64_t p = 0; p < seq; ++p)
+    for (int j = 0; j < half; ++j) {
+      double inv = std::pow(100000.0, -2.0 * (double)j / (double)m->R);
+      double f = (double)p * inv;
+      c[(size_t)p * half + j] = (float)std::cos(f); sn[(size_t)p * half + j] = (float)std::sin(f);
+    }
+  GN_TRY(m->cosb.ensure(sizeof(float) * c.size())); GN_TRY(m->sinb.ensure(sizeof(float) * sn.size()));
+  GN_CUDA(cudaMemcpyAsync(m->cosb.p, c.data(), sizeof(float) * c.size(), cudaMemcpyHostToDevice, ctx->stream));
+  GN_CUDA(cudaMemcpyAsync(m->sinb.p, sn.data(), sizeof(float) * sn.size(), cudaMemcpyHostToDevice, ctx->stream));
+  for (int i = 0; i < 4; ++i) GN_CUDA(cudaEventCreate(&m->ev[i]));
+  GN_CUDA(cudaStreamSynchronize(ctx->stream));
+  *out = m;
+  return GN_OK;
+}
+
+int gn_model_destroy(gn_model* m) {
+  if (!m) return GN_OK;
+  cudaSetDevice(m->ctx->device);
+  cudaStreamSynchronize(m->ctx->stream);
+  DevBuf* bufs[] = {&m->P, &m->G, &m->cosb, &m->sinb, &m->sacc, &m->cache, &m->prev, &m->pos, &m->ctxlen, &m->ids_dev, &m->sampled, &m->seeds,
+                    &m->out_tokens, &m->out_lengths, &m->done, &m->n_done, &m->sel, &m->part_acc, &m->part_ms, &m->infer.buf, &m->train.buf,
+                    &m->tgt_dev, &m->adv_dev, &m->rowloss, &m->loss_dev, &m->in_dev};
+  for (DevBuf* b : bufs) b->release();
+  for (int i = 0; i < 4; ++i) if (m->ev[i]) cudaEventDestroy(m->ev[i]);
+  delete m;
+  return GN_OK;
+}
+
+int gn_model_param_count(gn_model* m, int* out) { GN_REQUIRE(m && out, "null argument"); *out = (int)m->params.size(); return GN_OK; }
+int gn_model_param_info(gn_model* m, int i, const char** name, int* rows, int* cols) {
+  GN_REQUIRE(m && i >= 0 && i < (int)m->params.size(), "parameter index %d out of range", i);
+  if (name) *name = m->params[i].name.c_str();
+  if (rows) *rows = m->params[i].rows;
+  if (cols) *cols = m->params[i].cols;
+  return GN_OK;
+}
+static int find_param(gn_model* m, const char* name, int64_t n, const ParamInfo** out) {
+  GN_REQUIRE(m && name, "null argument");
+  auto it = m->index.find(name);
+  GN_REQUIRE(it != m->index.end(), "unknown parameter '%s'", name);
+  const ParamInfo& pi = m->params[it->second];
+  GN_REQUIRE(n == (int64_t)pi.rows * pi.cols, "parameter '%s' has %lld elements, got %lld", name, (long long)pi.rows * pi.cols, (long long)n);
+  *out = &pi;
+  return GN_OK;
+}
+int gn_model_upload(gn_model* m, const char* name, const float* host, int64_t n) {
+  const ParamInfo* pi; GN_TRY(find_param(m, name, n, &pi)); GN_TRY(enter(m));
+  GN_CUDA(cudaMemcpyAsync(m->p(pi->offset), host, sizeof(float) * n, cudaMemcpyHostToDevice, m->s()));
+  GN_CUDA(cudaStreamSynchronize(m->s()));
+  return GN_OK;
+}
+int gn_model_download(gn_model* m, const char* name, float* host, int64_t n) {
+  const ParamInfo* pi; GN_TRY(find_param(m, name, n, &pi)); GN_TRY(enter(m));
+  GN_CUDA(cudaMemcpyAsync(host, m->p(pi->offset), sizeof(float) * n, cudaMemcpyDeviceToHost, m->s()));
+  GN_CUDA(cudaStreamSynchronize(m->s()));
+  return GN_OK;
+}
+int gn_model_download_grad(gn_model* m, const char* name, float* host, int64_t n) {
+  const ParamInfo* pi; GN_TRY(find_param(m, name, n, &pi)); GN_TRY(enter(m));
+  GN_CUDA(cudaMemcpyAsync(host, m->g(pi->offset), sizeof(float) * n, cudaMemcpyDeviceToHost, m->s()));
+  GN_CUDA(cudaStreamSynchronize(m->s()));
+  return GN_OK;
+}
+int gn_model_zero_grad(gn_model* m) {
+  GN_TRY(enter(m));
+  GN_CUDA(cudaMemsetAsync(m->G.p, 0, sizeof(float) * m->total, m->s()));
+  GN_CUDA(cudaMemsetAsync(m->sacc.p, 0, sizeof(double) * (2 * m->L + 2), m->s()));
+  return GN_OK;
+}
+int gn_model_grad_buffer(gn_model* m, float** ptr, int64_t* n) { GN_REQUIRE(m && ptr && n, "null argument"); *ptr = m->G.f(); *n = m->total; return GN_OK; }
+int gn_model_param_buffer(gn_model* m, float** ptr, int64_t* n) { GN_REQUIRE(m && ptr && n, "null argument"); *ptr = m->P.f(); *n = m->total; return GN_OK; }
+int gn_model_checksum(gn_model* m, double* psum, double* gsum) {
+  GN_TRY(enter(m));
+  std::vector<float> h((size_t)m->total);
+  for (int which = 0; which < 2; ++which) {
+    GN_CUDA(cudaMemcpyAsync(h.data(), which ? m->G.p : m->P.p, sizeof(float) * m->total, cudaMemcpyDeviceToHost, m->s()));
+    GN_CUDA(cudaStreamSynchronize(m->s()));
+    double acc = 0; for (float v : h) acc += std::fabs((double)v);
+    if (which == 0 && psum) *psum = acc;
+    if (which == 1 && gsum) *gsum = acc;
+  }
+  return GN_OK;
+}
+
+int gn_model_forward(gn_model* m, const int32_t* ids, int B, int T, float* logits) {
+  GN_TRY(enter(m));
+  GN_REQUIRE(ids && logits && B > 0 && T > 1, "gn_model_forward needs ids, logits, batch > 0 and seq > 1");
+  GN_REQUIRE(T <= m->cfg.sequence_len, "sequence %d longer than the rotary cache (%d)", T, m->cfg.sequence_len);
+  const int64_t rows = (int64_t)B * T;
+  GN_TRY(m->ids_dev.ensure(sizeof(int32_t) * rows));
+  GN_CUDA(cudaMemcpyAsync(m->ids_dev.p, ids, sizeof(int32_t) * rows, cudaMemcpyHostToDevice, m->s()));
+  FwdBufs b;
+  GN_TRY(make_bufs(m, m->infer, b, MODE_PLAIN, rows, rows, B, T, 0, nullptr));
+  FwdArgs a; a.mode = MODE_PLAIN; a.ids = m->ids_dev.i(); a.B = B; a.T = T;
+  GN_TRY(forward_core(m, b, a));
+  GN_CUDA(cudaMemcpyAsync(logits, b.LOGITS, sizeof(float) * rows * m->V, cudaMemcpyDeviceToHost, m->s()));
+  GN_CUDA(cudaStreamSynchronize(m->s()));
+  return GN_OK;
+}
+
+int gn_generate_batch(gn_model* m, const int32_t* prompts, int P, int plen, int G, int max_tokens, float temperature, int top_k, const uint64_t* seeds,
+                      int32_t* out_tokens, int32_t* out_lengths, float* step_logits, int* steps_run) {
+  GN_TRY(enter(m));
+  GN_REQUIRE(prompts && seeds && out_tokens && out_lengths, "gn_generate_batch: null argument");
+  GN_REQUIRE(P > 0 && plen > 0 && G > 0 && max_tokens > 0, "gn_generate_batch: sizes must be positive");
+  GN_REQUIRE(plen <= m->cfg.sequence_len, "prompt of %d tokens longer than sequence_len %d", plen, m->cfg.sequence_len);
+  GN_REQUIRE((int64_t)plen + max_tokens <= (int64_t)m->cfg.sequence_len * 10, "context %d exceeds the rotary table", plen + max_tokens);
+  const int d = m->d, Hq = m->Hq, Hkv = m->Hkv, D = m->D, V = m->V, L = m->L;
+  const int rows = P * G, max_seq = plen + max_tokens;
+  const int bos = V - 11, aend = V - 7;   // tokenizer/special.go:19-31
+  cudaStream_t s = m->s();
+  // ---- state
+  GN_TRY(m->cache.ensure(sizeof(float) * (size_t)L * 2 * rows * Hkv * max_seq * D));
+  GN_TRY(m->prev.ensure(sizeof(float) * (size_t)rows * d));
+  GN_TRY(m->pos.ensure(sizeof(int32_t) * rows)); GN_TRY(m->ctxlen.ensure(sizeof(int32_t) * rows));
+  GN_TRY(m->ids_dev.ensure(sizeof(int32_t) * std::max<int64_t>((int64_t)P * plen, rows)));
+  GN_TRY(m->sampled.ensure(sizeof(int32_t) * rows)); GN_TRY(m->seeds.ensure(sizeof(uint64_t) * P));
+  GN_TRY(m->out_tokens.ensure(sizeof(int32_t) * (size_t)rows * max_tokens)); GN_TRY(m->out_lengths.ensure(sizeof(int32_t) * rows));
+  GN_TRY(m->done.ensure(sizeof(int32_t) * rows)); GN_TRY(m->n_done.ensure(sizeof(int32_t)));
+  GN_TRY(m->sel.ensure(sizeof(int32_t) * P));
+  int splits = attention_decode_splits(rows, Hkv, max_seq);
+  GN_TRY(m->part_acc.ensure(sizeof(float) * (size_t)rows * Hq * splits * D)); GN_TRY(m->part_ms.ensure(sizeof(float) * (size_t)rows * Hq * splits * 2));
+  GN_CUDA(cudaMemcpyAsync(m->ids_dev.p, prompts, sizeof(int32_t) * (size_t)P * plen, cudaMemcpyHostToDevice, s));
+  GN_CUDA(cudaMemcpyAsync(m->seeds.p, seeds, sizeof(uint64_t) * P, cudaMemcpyHostToDevice, s));
+  std::vector<int32_t> sel(P);
+  for (int p = 0; p < P; ++p) sel[p] = p * plen + plen - 1;
+  GN_CUDA(cudaMemcpyAsync(m->sel.p, sel.data(), sizeof(int32_t) * P, cudaMemcpyHostToDevice, s));
+  GN_CUDA(cudaMemsetAsync(m->pos.p, 0, sizeof(int32_t) * rows, s));
+  GN_CUDA(cudaMemsetAsync(m->out_lengths.p, 0, sizeof(int32_t) * rows, s));
+  GN_CUDA(cudaMemsetAsync(m->done.p, 0, sizeof(int32_t) * rows, s));
+  GN_CUDA(cudaMemsetAsync(m->n_done.p, 0, sizeof(int32_t), s));
+
+  // ---- prefill: all prompts in one batch; prompt p writes cache row p*G (engine.go:141-172)
+  GN_CUDA(cudaEventRecord(m->ev[0], s));
+  FwdBufs b;
+  {
+    const int64_t prow = (int64_t)P * plen;
+    GN_TRY(make_bufs(m, m->infer, b, MODE_PREFILL, std::max<int64_t>(prow, rows), std::max(P, rows), P, plen, 0, nullptr));
+    FwdArgs a; a.mode = MODE_PREFILL; a.ids = m->ids_dev.i(); a.B = P; a.T = plen; a.cache_rows = rows; a.cache_row_mul = G; a.max_seq = max_seq;
+    GN_TRY(forward_core(m, b, a));
+  }
+  // replicate each prompt's cache over its group (engine.go:194-209, kvcache.go:383-448)
+  GN_TRY(kv_replicate_launch(m->cache.f(), (int64_t)rows * Hkv * max_seq * D, 2 * L, (int64_t)Hkv * max_seq * D, (int64_t)max_seq * D, Hkv, D, P, G, plen,
+                             m->prev.f(), d, nullptr, s));
+  GN_TRY(fill_i32_launch(m->pos.i(), plen, rows, s));
+  GN_CUDA(cudaEventRecord(m->ev[1], s));
+
+  // ---- decode loop (engine.go:241-325)
+  std::vector<float> host_logits;
+  int generated = 0;
+  int logits_div = G;   // the first sampling step reads the prompt's last-position logits for all G rows
+  int32_t n_done_host = 0;
+  while (true) {
+    if (step_logits) {
+      int lr = rows / logits_div;
+      host_logits.resize((size_t)lr * V);
+      GN_CUDA(cudaMemcpyAsync(host_logits.data(), b.LOGITS, sizeof(float) * (size_t)lr * V, cudaMemcpyDeviceToHost, s));
+      GN_CUDA(cudaStreamSynchronize(s));
+      float* dst = step_logits + (size_t)generated * rows * V;
+      for (int r = 0; r < rows; ++r) std::memcpy(dst + (size_t)r * V, host_logits.data() + (size_t)(r / logits_div) * V, sizeof(float) * V);
+    }
+    GN_TRY(sample_launch(b.LOGITS, rows, V, logits_div, nullptr, (const uint64_t*)m->seeds.p, G, nullptr, (uint32_t)generated, temperature, top_k,
+                         m->sampled.i(), s));
+    GN_TRY(engine_step_launch(m->sampled.i(), m->out_tokens.i(), m->out_lengths.i(), m->done.i(), m->n_done.i(), rows, max_tokens, bos, aend, s));
+    ++generated;
+    if (generated >= max_tokens) break;
+    if (generated % 16 == 0 || step_logits) {  // every row finished: stop early (engine.go:245-254)
+      GN_CUDA(cudaMemcpyAsync(&n_done_host, m->n_done.p, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+      GN_CUDA(cudaStreamSynchronize(s));
+      if (n_done_host >= rows) break;
+    }
+    // forward the sampled column (engine.go:321-324)
+    GN_TRY(ctx_from_pos_launch(m->pos.i(), m->ctxlen.i(), rows, s));
+    FwdArgs a; a.mode = MODE_DECODE; a.ids = m->sampled.i(); a.B = rows; a.T = 1; a.cache_rows = rows; a.cache_row_mul = 1; a.max_seq = max_seq;
+    GN_TRY(forward_core(m, b, a));
+    GN_TRY(add_i32_launch(m->pos.i(), 1, rows, s));
+    logits_div = 1;
+  }
+  GN_CUDA(cudaEventRecord(m->ev[2], s));
+  GN_CUDA(cudaMemcpyAsync(out_tokens, m->out_tokens.p, sizeof(int32_t) * (size_t)rows * max_tokens, cudaMemcpyDeviceToHost, s));
+  GN_CUDA(cudaMemcpyAsync(out_lengths, m->out_lengths.p, sizeof(int32_t) * rows, cudaMemcpyDeviceToHost, s));
+  GN_CUDA(cudaStreamSynchronize(s));
+  float ms = 0;
+  GN_CUDA(cudaEventElapsedTime(&ms, m->ev[0], m->ev[1])); m->phase_ms["prefill"] = ms;
+  GN_CUDA(cudaEventElapsedTime(&ms, m->ev[1], m->ev[2])); m->phase_ms["decode"] = ms;
+  if (steps_run) *steps_run = generated;
+  return GN_OK;
+}
+
+int gn_policy_gradient_step(gn_model* m, const int32_t* inputs, const int32_t* targets, const float* adv, int B, int T, float norm, int rows_per_pass,
+                            float* loss, float* nll_tap, float* dlogits_tap, float* logits_tap) {
+  GN_TRY(enter(m));
+  GN_REQUIRE(inputs && targets && adv && loss, "gn_policy_gradient_step: null argument");
+  GN_REQUIRE(B > 0 && T > 1, "gn_policy_gradient_step: batch must be positive and seq > 1 (model/transformer.go:269-271)");
+  GN_REQUIRE(T <= m->cfg.sequence_len, "sequence %d longer than sequence_len %d", T, m->cfg.sequence_len);
+  const int V = m->V, L = m->L;
+  cudaStream_t s = m->s();
+  if (rows_per_pass <= 0) rows_per_pass = std::max(1, 16384 / T);
+  rows_per_pass = std::min(rows_per_pass, B);
+  const int64_t all = (int64_t)B * T;
+  GN_TRY(m->in_dev.ensure(sizeof(int32_t) * all)); GN_TRY(m->tgt_dev.ensure(sizeof(int32_t) * all)); GN_TRY(m->adv_dev.ensure(sizeof(float) * B));
+  GN_TRY(m->rowloss.ensure(sizeof(double) * (size_t)rows_per_pass * T)); GN_TRY(m->loss_dev.ensure(sizeof(double)));
+  GN_CUDA(cudaMemcpyAsync(m->in_dev.p, inputs, sizeof(int32_t) * all, cudaMemcpyHostToDevice, s));
+  GN_CUDA(cudaMemcpyAsync(m->tgt_dev.p, targets, sizeof(int32_t) * all, cudaMemcpyHostToDevice, s));
+  GN_CUDA(cudaMemcpyAsync(m->adv_dev.p, adv, sizeof(float) * B, cudaMemcpyHostToDevice, s));
+  GN_CUDA(cudaMemsetAsync(m->loss_dev.p, 0, sizeof(double), s));
+  FwdBufs b; BwdBufs w; float* extra = nullptr;
+  const int64_t prow = (int64_t)rows_per_pass * T;
+  GN_TRY(make_bufs(m, m->train, b, MODE_TRAIN, prow, prow, rows_per_pass, T, bwd_floats(m, prow, rows_per_pass, T), &extra));
+  carve_bwd(m, extra, w, prow, rows_per_pass, T);
+  float t_fwd = 0, t_loss = 0, t_bwd = 0;
+  std::vector<float> nll_host;
+  for (int b0 = 0; b0 < B; b0 += rows_per_pass) {
+    const int Bm = std::min(rows_per_pass, B - b0);
+    const int64_t rows = (int64_t)Bm * T;
+    const int32_t* ids = m->in_dev.i() + (int64_t)b0 * T;
+    GN_CUDA(cudaEventRecord(m->ev[0], s));
+    FwdArgs a; a.mode = MODE_TRAIN; a.ids = ids; a.B = Bm; a.T = T;
+    GN_TRY(forward_core(m, b, a));
+    GN_CUDA(cudaEventRecord(m->ev[1], s));
+    if (logits_tap) GN_CUDA(cudaMemcpyAsync(logits_tap + (size_t)b0 * T * V, b.LOGITS, sizeof(float) * rows * V, cudaMemcpyDeviceToHost, s));
+    // loss + dlogits with the softcap backward folded in; dz overwrites the logits.
+    // The taps want the gradient at the softcapped logits, so they take a separate pass.
+    if (dlogits_tap) {
+      // The tap is the gradient at the softcapped logits (what trainer/rl.go hands to
+      // TrainBackward), so it takes its own pass without the folded softcap backward.
+      DevBuf scratch;
+      GN_TRY(scratch.ensure(sizeof(float) * rows * V));
+      GN_TRY(pg_loss_launch(b.LOGITS, m->tgt_dev.i() + (int64_t)b0 * T, m->adv_dev.f() + b0, rows, V, V, T, norm, 0.0f, nullptr, scratch.f(), V,
+                            (double*)m->rowloss.p, nullptr, 2, s));
+      GN_CUDA(cudaMemcpyAsync(dlogits_tap + (size_t)b0 * T * V, scratch.p, sizeof(float) * rows * V, cudaMemcpyDeviceToHost, s));
+      GN_CUDA(cudaStreamSynchronize(s));
+      scratch.release();
+    }
+    float* nll_dev = w.DELTA;  // [Bm*Hq*T] >= rows floats; free until the attention backward
+    GN_TRY(pg_loss_launch(b.LOGITS, m->tgt_dev.i() + (int64_t)b0 * T, m->adv_dev.f() + b0, rows, V, V, T, norm, kSoftcap, nll_dev, b.LOGITS, V,
+                          (double*)m->rowloss.p, (double*)m->loss_dev.p, 1, s));
+    if (nll_tap) GN_CUDA(cudaMemcpyAsync(nll_tap + (size_t)b0 * T, nll_dev, sizeof(float) * rows, cudaMemcpyDeviceToHost, s));
+    GN_CUDA(cudaEventRecord(m->ev[2], s));
+    GN_TRY(backward_core(m, b, w, ids, Bm, T));
+    GN_CUDA(cudaEventRecord(m->ev[3], s));
+    GN_CUDA(cudaStreamSynchronize(s));
+    float ms = 0;
+    GN_CUDA(cudaEventElapsedTime(&ms, m->ev[0], m->ev[1])); t_fwd += ms;
+    GN_CUDA(cudaEventElapsedTime(&ms, m->ev[1], m->ev[2])); t_loss += ms;
+    GN_CUDA(cudaEventElapsedTime(&ms, m->ev[2], m->ev[3])); t_bwd += ms;
+  }
+  GN_TRY(scalar_flush_launch(m->g(m->off_rho), (double*)m->sacc.p, 2 * L + 2, s));
+  double loss_host = 0;
+  GN_CUDA(cudaMemcpyAsync(&loss_host, m->loss_dev.p, sizeof(double), cudaMemcpyDeviceToHost, s));
+  GN_CUDA(cudaStreamSynchronize(s));
+  *loss = (float)loss_host;
+  m->phase_ms["train_forward"] = t_fwd; m->phase_ms["loss"] = t_loss; m->phase_ms["train_backward"] = t_bwd;
+  return GN_OK;
+}
+
+int gn_model_phase_ms(gn_model* m, const char* phase, float* ms) {
+  GN_REQUIRE(m && phase && ms, "null argument");
+  auto it = m->phase_ms.find(phase);
+  GN_REQUIRE(it != m->phase_ms.end(), "no timing recorded for phase '%s'", phase);
+  *ms = it->second;
+  return GN_OK;
+}
+
+}  // extern "C"

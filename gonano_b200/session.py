@@ -1,0 +1,209 @@
+"""Resident session over the C-ABI's Tier B: the host-side mirror of the
+reference's ``model.Transformer``, ``inference.Engine`` and ``trainer`` calls
+that make up one RL step (cmd/chat_rl/main.go:87-184).
+
+The arithmetic all happens in the CUDA library; this module only moves ids and
+scalars across the boundary and assembles the padded batch the way
+``cmd/chat_rl`` does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import _lib
+from ._lib import GnConfig, check, ptr
+
+SPECIAL_TOKENS = 11  # tokenizer/special.go:19-31
+
+
+def _i32(a):
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+class Context:
+    """One CUDA device + stream.  ``stream`` may be a raw ``cudaStream_t`` (int), e.g. torch's current stream."""
+
+    def __init__(self, device: int = 0, stream: int | None = None):
+        self.lib = _lib.load()
+        self.h = C.c_void_p()
+        check(self.lib.gn_ctx_create(device, C.c_void_p(stream) if stream else None, C.byref(self.h)))
+        self.device = device
+
+    def sync(self):
+        check(self.lib.gn_ctx_sync(self.h))
+
+    def launch_count(self) -> int:
+        out = C.c_int64()
+        check(self.lib.gn_ctx_launch_count(self.h, C.byref(out)))
+        return out.value
+
+    def set_gemm(self, kind: int):
+        check(self.lib.gn_ctx_set_gemm(self.h, kind))
+
+    def close(self):
+        if self.h:
+            self.lib.gn_ctx_destroy(self.h)
+            self.h = C.c_void_p()
+
+
+class Model:
+    """``model.Transformer`` (dense preset) resident on the device."""
+
+    def __init__(self, ctx: Context, sequence_len, vocab_size, n_layer, n_head, n_kv_head, embed_dim, rotary_dims=0, window_pattern="L"):
+        self.ctx = ctx
+        self.lib = ctx.lib
+        self.cfg = GnConfig(sequence_len, vocab_size, n_layer, n_head, n_kv_head, embed_dim, rotary_dims, window_pattern.encode())
+        self.vocab = vocab_size
+        self.h = C.c_void_p()
+        check(self.lib.gn_model_create(ctx.h, C.byref(self.cfg), C.byref(self.h)))
+        n = C.c_int()
+        check(self.lib.gn_model_param_count(self.h, C.byref(n)))
+        self.names, self._shape = [], {}
+        for i in range(n.value):
+            name, rows, cols = C.c_char_p(), C.c_int(), C.c_int()
+            check(self.lib.gn_model_param_info(self.h, i, C.byref(name), C.byref(rows), C.byref(cols)))
+            self.names.append(name.value.decode())
+            self._shape[self.names[-1]] = (rows.value, cols.value)
+
+    def close(self):
+        if self.h:
+            self.lib.gn_model_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def shape(self, name):
+        return self._shape[name]
+
+    def upload(self, name, values):
+        values = _f32(values).reshape(-1)
+        check(self.lib.gn_model_upload(self.h, name.encode(), ptr(values), values.size))
+
+    def download(self, name) -> np.ndarray:
+        rows, cols = self._shape[name]
+        out = np.empty(rows * cols, np.float32)
+        check(self.lib.gn_model_download(self.h, name.encode(), ptr(out), out.size))
+        return out
+
+    def grad(self, name) -> np.ndarray:
+        rows, cols = self._shape[name]
+        out = np.empty(rows * cols, np.float32)
+        check(self.lib.gn_model_download_grad(self.h, name.encode(), ptr(out), out.size))
+        return out
+
+    def zero_grad(self):
+        check(self.lib.gn_model_zero_grad(self.h))
+
+    def grad_buffer(self):
+        """(device address, float count) of the flat gradient buffer that a data-parallel all-reduce sums."""
+        p, n = C.c_void_p(), C.c_int64()
+        check(self.lib.gn_model_grad_buffer(self.h, C.byref(p), C.byref(n)))
+        return p.value, n.value
+
+    def param_buffer(self):
+        p, n = C.c_void_p(), C.c_int64()
+        check(self.lib.gn_model_param_buffer(self.h, C.byref(p), C.byref(n)))
+        return p.value, n.value
+
+    def checksum(self):
+        ps, gs = C.c_double(), C.c_double()
+        check(self.lib.gn_model_checksum(self.h, C.byref(ps), C.byref(gs)))
+        return ps.value, gs.value
+
+    def phase_ms(self, phase: str) -> float:
+        out = C.c_float()
+        check(self.lib.gn_model_phase_ms(self.h, phase.encode(), C.byref(out)))
+        return out.value
+
+    # ---- Transformer.Forward without a cache (model/transformer.go:211-342)
+    def forward(self, ids) -> np.ndarray:
+        ids = _i32(ids); B, T = ids.shape
+        logits = np.empty((B, T, self.vocab), np.float32)
+        check(self.lib.gn_model_forward(self.h, ptr(ids), B, T, ptr(logits)))
+        return logits
+
+    # ---- Engine.GenerateBatchWith for many prompts (inference/engine.go:336-369)
+    def generate_batch(self, prompts, group, max_tokens, temperature, top_k, seeds, want_logits=False):
+        prompts = _i32(prompts); P, plen = prompts.shape
+        seeds = np.ascontiguousarray(seeds, dtype=np.uint64)
+        assert seeds.size == P
+        rows = P * group
+        tokens = np.zeros((rows, max_tokens), np.int32); lengths = np.zeros(rows, np.int32)
+        step_logits = np.zeros((max_tokens, rows, self.vocab), np.float32) if want_logits else None
+        steps = C.c_int()
+        check(self.lib.gn_generate_batch(self.h, ptr(prompts), P, plen, group, max_tokens, temperature, top_k, ptr(seeds), ptr(tokens),
+                                         ptr(lengths), ptr(step_logits), C.byref(steps)))
+        return tokens, lengths, steps.value, step_logits
+
+    # ---- trainer.PolicyGradientStep (trainer/rl.go:14-60)
+    def policy_gradient_step(self, inputs, targets, advantages, norm, rows_per_pass=0, taps=False):
+        inputs, targets, advantages = _i32(inputs), _i32(targets), _f32(advantages)
+        B, T = inputs.shape
+        loss = C.c_float()
+        nll = np.empty(B * T, np.float32) if taps else None
+        dl = np.empty((B * T, self.vocab), np.float32) if taps else None
+        lg = np.empty((B * T, self.vocab), np.float32) if taps else None
+        check(self.lib.gn_policy_gradient_step(self.h, ptr(inputs), ptr(targets), ptr(advantages), B, T, norm, rows_per_pass, C.byref(loss),
+                                               ptr(nll), ptr(dl), ptr(lg)))
+        return loss.value, nll, dl, lg
+
+
+# -------------------------------------------------------------------------
+# Batch assembly of cmd/chat_rl (host side, integer work)
+# -------------------------------------------------------------------------
+def build_batch(prompts, group, tokens, lengths, pad_token):
+    """Pads every rollout (prompt + kept tokens) to the longest one with ``pad_token``
+    (= <|assistant_end|>), shifts inputs/targets by one and masks targets whose index is
+    below the prompt length (cmd/chat_rl/main.go:156-182).  Returns inputs, targets
+    ([rows, max_len-1] int32) and max_len.  Pad positions are NOT masked, as in the reference.
+    """
+    prompts = _i32(prompts); tokens = _i32(tokens); lengths = _i32(lengths)
+    P, plen = prompts.shape
+    rows = P * group
+    max_len = plen + int(lengths.max())
+    padded = np.full((rows, max_len), pad_token, np.int32)
+    padded[:, :plen] = np.repeat(prompts, group, axis=0)
+    for r in range(rows):
+        padded[r, plen:plen + lengths[r]] = tokens[r, :lengths[r]]
+    inputs = np.ascontiguousarray(padded[:, :-1])
+    targets = np.ascontiguousarray(padded[:, 1:]).copy()
+    targets[:, :plen] = -1          # target index < prompt length (also hides the first sampled token)
+    return inputs, targets, max_len
+
+
+@dataclass
+class RLStepResult:
+    loss: float
+    rollout_tokens: int
+    rows: int
+    max_len: int
+    steps: int
+    tokens: np.ndarray
+    lengths: np.ndarray
+    advantages: np.ndarray
+
+
+def rl_step(model: Model, prompts, group, max_tokens, temperature, top_k, seeds, reward_fn, advantage_mode=0, rows_per_pass=0,
+            norm=None, all_reduce=None) -> RLStepResult:
+    """One RL step the way cmd/chat_rl runs it (main.go:87-184), minus the optimizer:
+    rollout -> rewards -> group-relative advantages -> padded batch -> PolicyGradientStep
+    -> gradient all-reduce (``all_reduce(model)``, when data parallel).  ``reward_fn(tokens,
+    lengths)`` returns one reward per rollout.  ``norm`` defaults to the padded length
+    (main.go:183)."""
+    from .backend import group_advantage
+    prompts = _i32(prompts)
+    tokens, lengths, steps, _ = model.generate_batch(prompts, group, max_tokens, temperature, top_k, seeds)
+    rewards = _f32(reward_fn(tokens, lengths))
+    adv = group_advantage(rewards, group, advantage_mode)
+    pad = model.vocab - 7  # <|assistant_end|>
+    inputs, targets, max_len = build_batch(prompts, group, tokens, lengths, pad)
+    model.zero_grad()
+    loss, _, _, _ = model.policy_gradient_step(inputs, targets, adv, float(max_len) if norm is None else norm, rows_per_pass)
+    if all_reduce is not None:
+        all_reduce(model)
+    return RLStepResult(loss, int(lengths.sum()), len(lengths), max_len, steps, tokens, lengths, adv)

@@ -1,0 +1,244 @@
+/*
+ * gonano_cuda.h - C ABI of the B200 (sm_100a) CUDA backend for gonano's RL step.
+ *
+ * The library replaces, for the reinforcement-learning step of gonano
+ * (trainer/rl.go driven by cmd/chat_rl), the work that the reference routes
+ * through its numeric backend interface `kernels.Backend`
+ * (kernels/backend.go:285-297) and through the Go loops around it.
+ *
+ * Two tiers:
+ *
+ *   Tier A  one entry point per `kernels.Backend` method, same argument order
+ *           and meaning.  Pointers may be host or device memory (detected per
+ *           call); host buffers are staged through device memory and the call
+ *           returns when the result is back.  This is what a cgo shim that
+ *           implements `kernels.Backend` binds.
+ *
+ *   Tier B  a resident session: the model's parameters, KV cache, activations
+ *           and gradients live in device memory, and whole phases of the RL
+ *           step run without crossing the host boundary.  This is what
+ *           model/, inference/engine.go and trainer/rl.go call when the
+ *           selected backend also offers the resident interface.
+ *
+ * Conventions
+ *   - every function returns a status (GN_OK == 0); gn_last_error() gives the
+ *     message of the calling thread's last failure.  Nothing aborts or traps.
+ *   - matrices are contiguous, row-major float32; token ids are int32
+ *     (tensors/tensor.go:10-17, tensors/ids.go:8-11).
+ *   - Tier A is safe to call from any number of OS threads (the reference
+ *     calls its backend from many goroutines, model/attention.go:311-320);
+ *     calls are serialised on one internal lock per process.
+ *   - Tier B objects are single-caller: one thread per gn_ctx at a time.
+ *   - there is no CPU fallback: without a CUDA device every compute call
+ *     fails with GN_ERR_CUDA.
+ */
+#ifndef GONANO_CUDA_H
+#define GONANO_CUDA_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GN_OK 0
+#define GN_ERR_INVALID 1 /* bad argument */
+#define GN_ERR_CUDA 2    /* CUDA runtime/driver error, or no device */
+#define GN_ERR_COMM 3    /* collective communication error */
+#define GN_ERR_TIMEOUT 4 /* a bounded device-side wait ran out */
+#define GN_ERR_NOMEM 5
+
+const char* gn_last_error(void);
+/* Library version string. */
+const char* gn_version(void);
+/* Number of visible CUDA devices (0 when none; never fails). */
+int gn_device_count(void);
+
+/* ===================================================================== *
+ * Tier A - kernels.Backend                                              *
+ * ===================================================================== */
+
+/* Elementwise (kernels/backend.go:21-67).  dst may alias a source. */
+int gn_add(float* dst, const float* left, const float* right, int64_t n);
+int gn_subtract(float* dst, const float* left, const float* right, int64_t n);
+int gn_multiply(float* dst, const float* left, const float* right, int64_t n);
+int gn_divide(float* dst, const float* left, const float* right, int64_t n);
+int gn_scale(float* dst, const float* src, float factor, int64_t n);
+int gn_add_scaled(float* dst, const float* base, const float* scaled, float factor, int64_t n);
+int gn_negate(float* dst, const float* src, int64_t n);
+int gn_abs(float* dst, const float* src, int64_t n);
+int gn_square(float* dst, const float* src, int64_t n);
+int gn_relu_squared(float* dst, const float* src, int64_t n);
+int gn_swiglu(float* dst, const float* gate, const float* up, float clamp, int64_t n);
+/* Overwrites gate_grad and up_grad (kernels/backend.go:54-57). */
+int gn_swiglu_backward(float* gate_grad, float* up_grad, const float* gate, const float* up, const float* out_grad,
+                       float clamp, int64_t n);
+int gn_exp(float* dst, const float* src, int64_t n);
+int gn_sigmoid(float* dst, const float* src, int64_t n);
+int gn_tanh(float* dst, const float* src, int64_t n);
+int gn_rsqrt(float* dst, const float* src, int64_t n);
+
+/* Reductions (kernels/backend.go:70-78); the Go methods return the value, here it
+ * comes back through `out` (host memory). Max of an empty slice is 0, ArgMax 0. */
+int gn_sum(const float* values, int64_t n, float* out);
+int gn_max(const float* values, int64_t n, float* out);
+int gn_argmax(const float* values, int64_t n, int64_t* out);
+
+/* Linear algebra (kernels/backend.go:82-93). */
+int gn_matmul(float* dst, const float* left, const float* right, int rows, int cols, int inner);
+int gn_matmul_transposed(float* dst, const float* left, const float* right, int rows, int cols, int inner);
+int gn_dot_product(const float* left, const float* right, int64_t n, float* out);
+
+/* Indexer (kernels/backend.go:103-116). */
+int gn_indexer_scores(float* dst, const float* query, const float* key, const float* weight, int rows, int blocks,
+                      int heads, int dim);
+int gn_indexer_block_max(float* dst, const float* scores, int rows, int blocks, int group_size);
+
+/* MoE (kernels/backend.go:119-141).  Indices are exact: descending score, ties
+ * toward the smaller index. */
+int gn_topk_indices(int32_t* dst, const float* scores, int rows, int count, int k);
+int gn_moe_gate_topk(const float* logits, const float* bias, float* probs, int32_t* selected, float* selected_weights,
+                     int rows, int experts, int k);
+int gn_grouped_matmul_transposed(float* dst, const float* input, const float* weight, const int32_t* token_counts,
+                                 int experts, int cols, int inner);
+
+/* Rows (kernels/backend.go:145-153). */
+int gn_softmax_last_dim(float* dst, const float* src, int64_t rows, int cols);
+int gn_rmsnorm_last_dim(float* dst, const float* src, int64_t rows, int cols, float epsilon);
+
+/* Attention for one (batch, head) (kernels/backend.go:167-283).
+ * window < 0: full causal context, else left sliding-window width.
+ * segment_ids: NULL or one id per key position (length key_len). */
+typedef struct gn_attention_params {
+  const float* query;  /* [query_len, head_dim] */
+  const float* key;    /* [key_len, head_dim] */
+  const float* value;  /* [key_len, head_dim] */
+  int32_t query_len, key_len, head_dim, position_offset, window;
+  const int32_t* segment_ids;
+} gn_attention_params;
+
+/* out [query_len, head_dim]; lse NULL or [query_len]. */
+int gn_attention_forward(const gn_attention_params* p, float* out, float* lse);
+/* One key shard [key_start, key_end): overwrites acc [query_len, head_dim], max and sum [query_len]. */
+int gn_attention_forward_split(const gn_attention_params* p, int key_start, int key_end, float* acc, float* maximum,
+                               float* sum);
+/* Partials packed shard-major: acc [parts, query_len, head_dim], maximum/sum [parts, query_len]. */
+int gn_attention_combine(const float* acc, const float* maximum, const float* sum, int parts, int query_len,
+                         int head_dim, float* out, float* lse);
+/* ACCUMULATES into dq [query_len, head_dim], dk, dv [key_len, head_dim] (kernels/backend.go:217-220).
+ * output is the forward output; row_correction NULL or [query_len] (kernels/backend.go:205-211). */
+int gn_attention_backward(const gn_attention_params* p, const float* output, const float* out_grad, const float* lse,
+                          const float* row_correction, float* dq, float* dk, float* dv);
+
+/* ===================================================================== *
+ * Stand-alone kernels of the RL step (host or device pointers)          *
+ * ===================================================================== */
+
+/* inference/sampler.go:16-77 with tensors/random.go:60-80: per row, keep the
+ * values >= the top_k-th largest (top_k <= 0 or >= vocab keeps all), add Gumbel
+ * noise -log(-log(u)) to value/temperature and take the first maximum;
+ * temperature <= 0 is a plain first-maximum argmax.  u comes from `uniforms`
+ * ([rows, vocab], one per vocabulary entry, values <= 0 read as 1e-12) or, when
+ * uniforms is NULL, from the counter generator Philox-4x32-10 keyed by
+ * seeds[row / group] with counter (column/4, row % group, step, 0).
+ * Indices are bit-exact against the CPU statement of the same rule. */
+int gn_sample_next_token(const float* logits, int rows, int vocab, const float* uniforms, const uint64_t* seeds,
+                         int group, uint32_t step, float temperature, int top_k, int32_t* out_ids);
+
+/* cmd/chat_rl/main.go:137-154: advantages of `groups` groups of `group` rewards.
+ * mode 0: reward - group mean (the reference).  mode 1: (reward - mean) /
+ * (population std + 1e-6). */
+int gn_group_advantage(const float* rewards, int groups, int group, int mode, float* advantages);
+
+/* trainer/rl.go:23-56 at given logits [rows, vocab]: per-row
+ * nll = logsumexp(row) - row[target] (0 where target == -1),
+ * loss = sum nll * adv[row / seq_len] / norm, and
+ * dlogits = (softmax - onehot) * adv / norm (0 on ignored rows).  When
+ * softcap > 0 the gradient is also multiplied by 1 - (logit / softcap)^2, the
+ * backward of the logit softcap (tensors/backward.go:108-116).  dlogits may
+ * alias logits (in place) or be NULL (loss only).  nll may be NULL. */
+int gn_pg_loss_backward(const float* logits, const int32_t* targets, const float* advantages, int64_t rows, int vocab,
+                        int seq_len, float norm, float softcap, float* nll, float* dlogits, double* loss);
+
+/* ===================================================================== *
+ * Tier B - resident session                                             *
+ * ===================================================================== */
+
+typedef struct gn_ctx gn_ctx;
+typedef struct gn_model gn_model;
+
+/* model.Config fields the dense preset uses (model/config.go:9-124). */
+typedef struct gn_config {
+  int32_t sequence_len;  /* SequenceLen: rotary table covers 10x this; window sizes derive from it */
+  int32_t vocab_size;    /* VocabSize (padded to a multiple of 64 internally, model/config.go:619-624) */
+  int32_t n_layer;       /* NumLayer */
+  int32_t n_head;        /* NumHead */
+  int32_t n_kv_head;     /* NumKVHead */
+  int32_t embed_dim;     /* EmbedDim */
+  int32_t rotary_dims;   /* RotaryDims (<= 0: whole head) */
+  char window_pattern[16]; /* WindowPattern, e.g. "SSSL" (model/config.go:629-645); empty = "L" */
+} gn_config;
+
+/* device: CUDA ordinal.  stream: a cudaStream_t to run on, or NULL for a
+ * stream the context creates. */
+int gn_ctx_create(int device, void* stream, gn_ctx** out);
+int gn_ctx_destroy(gn_ctx* ctx);
+int gn_ctx_sync(gn_ctx* ctx);
+/* Number of this library's kernels launched through the context so far. */
+int gn_ctx_launch_count(gn_ctx* ctx, int64_t* out);
+/* Select the GEMM path: 0 = SIMT float32, 1 = tcgen05 3xTF32 (default when built). */
+int gn_ctx_set_gemm(gn_ctx* ctx, int kind);
+
+/* model.NewTransformer (model/transformer.go:49-83): parameters start at zero. */
+int gn_model_create(gn_ctx* ctx, const gn_config* config, gn_model** out);
+int gn_model_destroy(gn_model* model);
+/* Parameter table, names as in Transformer.NamedParameters (model/params.go:14-74), sorted. */
+int gn_model_param_count(gn_model* model, int* out);
+int gn_model_param_info(gn_model* model, int index, const char** name, int* rows, int* cols);
+int gn_model_upload(gn_model* model, const char* name, const float* host, int64_t n);
+int gn_model_download(gn_model* model, const char* name, float* host, int64_t n);
+int gn_model_download_grad(gn_model* model, const char* name, float* host, int64_t n);
+/* Tensor.ZeroGrad over every parameter (model/params.go:100-104). */
+int gn_model_zero_grad(gn_model* model);
+/* The flat device buffer that holds every gradient (what the data-parallel
+ * all-reduce sums), and the matching parameter buffer. */
+int gn_model_grad_buffer(gn_model* model, float** device_ptr, int64_t* n);
+int gn_model_param_buffer(gn_model* model, float** device_ptr, int64_t* n);
+/* Sum of |gradient| and of |parameter| in float64 (replica checks). */
+int gn_model_checksum(gn_model* model, double* param_sum, double* grad_sum);
+
+/* Transformer.Forward without a cache (model/transformer.go:211-342): ids [B,T] (host) ->
+ * logits [B,T,vocab] (host).  T > 1. */
+int gn_model_forward(gn_model* model, const int32_t* ids, int batch, int seq, float* logits);
+
+/* Engine.GenerateBatchWith for many prompts at once (inference/engine.go:112-369):
+ * prefill each prompt, replicate its cache over `group` rows, then sample and
+ * decode up to max_tokens steps.  Prompts are [n_prompts, prompt_len] (host).
+ * Row p*group+g uses the generator keyed by seeds[p].  A row completes on
+ * <|bos|> (vocab-11) or <|assistant_end|> (vocab-7); out_tokens
+ * [n_prompts*group, max_tokens] receives the kept tokens (terminal stripped),
+ * out_lengths their counts.  step_logits: NULL or host [max_tokens, rows, vocab],
+ * the logits each sampling step saw.  steps_run: NULL or the number of sampling steps. */
+int gn_generate_batch(gn_model* model, const int32_t* prompts, int n_prompts, int prompt_len, int group,
+                      int max_tokens, float temperature, int top_k, const uint64_t* seeds, int32_t* out_tokens,
+                      int32_t* out_lengths, float* step_logits, int* steps_run);
+
+/* trainer.PolicyGradientStep (trainer/rl.go:14-60): inputs/targets [batch, seq]
+ * (host, target -1 = ignore), advantages [batch], norm.  Gradients ACCUMULATE
+ * into the model's gradient buffer (tensors/tensor.go:189-194).  Rows are
+ * processed in chunks of `rows_per_pass` sequences (0 = library default); the
+ * result does not depend on it beyond float32 summation order.
+ * Optional host taps: nll [batch*seq], dlogits and logits [batch*seq, vocab]. */
+int gn_policy_gradient_step(gn_model* model, const int32_t* inputs, const int32_t* targets, const float* advantages,
+                            int batch, int seq, float norm, int rows_per_pass, float* loss, float* nll_tap,
+                            float* dlogits_tap, float* logits_tap);
+
+/* Phase timings of the last gn_generate_batch / gn_policy_gradient_step in
+ * milliseconds (CUDA events on the context's stream): names are
+ * "prefill", "decode", "train_forward", "loss", "train_backward". */
+int gn_model_phase_ms(gn_model* model, const char* phase, float* ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GONANO_CUDA_H */

@@ -1,0 +1,175 @@
+"""The resident session (Tier B) through the C-ABI against the oracle: forward logits,
+rollouts compared by teacher forcing, and the policy-gradient step's loss and gradients.
+
+Tolerances are the RL step's: logits <= 1e-3 max relative error; log-probs, advantages,
+loss and gradients <= 1e-4 relative error (relative to the tensor's largest magnitude, with
+the reference's `Close`-style absolute floor near zero, kernels/kerneltest/compare.go:31-39).
+"""
+import numpy as np
+import pytest
+
+from gonano_b200 import synthetic
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_err(got, want):
+    got = np.asarray(got, np.float64); want = np.asarray(want, np.float64)
+    return float(np.max(np.abs(got - want)) / max(np.max(np.abs(want)), 1e-30))
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    from gonano_b200.session import Context
+    c = Context(0)
+    yield c
+    c.close()
+
+
+def make_pair(oracle, ctx, name, seed=1, std=0.02, **over):
+    from gonano_b200.session import Model
+    cfg = dict(synthetic.dense_config(name)); cfg.update(over)
+    om = oracle.Model(**cfg)
+    gm = Model(ctx, **cfg)
+    assert sorted(gm.names) == sorted(om.names)
+    for pname, value in synthetic.fill_weights(om.names, om.shape, seed, std=std):
+        assert gm.shape(pname) == om.shape(pname)
+        om.param(pname)[:] = value
+        gm.upload(pname, value)
+    return om, gm, cfg
+
+
+def test_param_round_trip(oracle, ctx):
+    om, gm, cfg = make_pair(oracle, ctx, "tiny")
+    for n in gm.names:
+        assert np.array_equal(gm.download(n), om.param(n))
+    gm.close()
+
+
+@pytest.mark.parametrize("name,std,B,T", [("tiny", 0.1, 2, 6), ("tiny", 0.1, 3, 16), ("c1", 0.02, 2, 33), ("c1", 0.1, 1, 70)])
+def test_forward_logits(oracle, ctx, name, std, B, T):
+    om, gm, cfg = make_pair(oracle, ctx, name, std=std)
+    rng = np.random.default_rng(0)
+    ids = rng.integers(0, cfg["vocab_size"] - 11, (B, T), dtype=np.int32)
+    want = om.forward(ids)
+    got = gm.forward(ids)
+    assert rel_err(got, want) <= 1e-3
+    gm.close()
+
+
+def test_forward_sliding_window(oracle, ctx):
+    """A short window that binds (model/config.go:629-645: sequence 512 gives S = 128)."""
+    om, gm, cfg = make_pair(oracle, ctx, "c1", std=0.1, sequence_len=512, window_pattern="SL", n_layer=2)
+    assert list(om.window_sizes()) == [128, 512]
+    rng = np.random.default_rng(2)
+    ids = rng.integers(0, cfg["vocab_size"] - 11, (1, 200), dtype=np.int32)
+    assert rel_err(gm.forward(ids), om.forward(ids)) <= 1e-3
+    gm.close()
+
+
+@pytest.mark.parametrize("name,std,P,plen,G,maxtok", [("tiny", 0.1, 2, 4, 3, 6), ("c1", 0.02, 3, 32, 4, 12), ("c1", 0.3, 2, 9, 2, 20)])
+def test_rollout_by_teacher_forcing(oracle, ctx, name, std, P, plen, G, maxtok):
+    """The GPU rollout is fed back through the oracle: the logits every sampling step saw agree
+    within 1e-3, and on the GPU's own logits the oracle's sampler draws the same token (bit-exact)."""
+    om, gm, cfg = make_pair(oracle, ctx, name, std=std)
+    V = cfg["vocab_size"]
+    prompts = synthetic.prompts(P, plen, V, seed=4)
+    seeds = np.arange(P, dtype=np.uint64) + 100
+    tokens, lengths, steps, slog = gm.generate_batch(prompts, G, maxtok, 1.0, 50, seeds, want_logits=True)
+    assert steps >= 1 and np.all(lengths <= maxtok)
+    for p in range(P):
+        cache0 = om.cache(1, plen)
+        last = om.forward_cached(cache0, prompts[p:p + 1])[:, -1]
+        cache = om.cache(G, plen + maxtok)
+        cache.replicate_from(cache0)
+        cur = np.repeat(last, G, axis=0)
+        done = np.zeros(G, bool)
+        kept = [[] for _ in range(G)]
+        for step in range(steps):
+            rows = slice(p * G, (p + 1) * G)
+            assert rel_err(slog[step, rows], cur) <= 1e-3, (p, step)
+            drawn = oracle.sample_next_token(slog[step, rows], 1.0, 50, seeds=seeds[p:p + 1], group=G, step=step)
+            for g in range(G):
+                if not done[g]:
+                    if drawn[g] in (V - 11, V - 7): done[g] = True
+                    else: kept[g].append(int(drawn[g]))
+            if step + 1 == steps: break
+            cur = om.forward_cached(cache, drawn.reshape(G, 1))[:, 0]
+        for g in range(G):
+            r = p * G + g
+            assert kept[g] == tokens[r, :lengths[r]].tolist(), (p, g)
+    gm.close()
+
+
+def test_rollout_greedy_matches_oracle_engine(oracle, ctx):
+    """Temperature 0 removes the generator: the whole engine must agree token for token."""
+    om, gm, cfg = make_pair(oracle, ctx, "tiny", std=0.3, sequence_len=32)
+    prompts = np.array([[1, 5, 2, 8], [3, 3, 7, 0]], np.int32)
+    tokens, lengths, steps, _ = gm.generate_batch(prompts, 2, 8, 0.0, 0, np.array([1, 2], np.uint64))
+    for p in range(2):
+        wt, wl, ws, _ = om.generate(prompts[p], 2, 8, 0.0, 0, seed=1)
+        for g in range(2):
+            assert lengths[p * 2 + g] == wl[g]
+            assert np.array_equal(tokens[p * 2 + g, :wl[g]], wt[g, :wl[g]])
+    gm.close()
+
+
+@pytest.mark.parametrize("name,std,B,T,rpp", [("tiny", 0.1, 2, 4, 0), ("tiny", 0.1, 5, 12, 2), ("c1", 0.05, 3, 40, 0), ("c1", 0.05, 4, 24, 3)])
+def test_policy_gradient_step(oracle, ctx, name, std, B, T, rpp):
+    om, gm, cfg = make_pair(oracle, ctx, name, std=std)
+    V = cfg["vocab_size"]
+    rng = np.random.default_rng(B * T)
+    ids = rng.integers(0, V - 11, (B, T), dtype=np.int32)
+    ids[:, 1] = ids[:, 0]                      # repeated ids: scatter-add paths see collisions
+    tg = rng.integers(0, V, (B, T)).astype(np.int32)
+    tg[:, : T // 3] = -1
+    adv = rng.standard_normal(B).astype(np.float32)
+    if B == 2 and T == 4:                      # trainer/sft_rl_test.go:53-75
+        adv = np.array([1.0, -0.5], np.float32); norm = 8.0
+    else:
+        norm = float(T + 1)
+    om.zero_grad()
+    want_loss, want_nll, want_dl, want_lg = om.policy_gradient_step(ids, tg, adv, norm, taps=True)
+    gm.zero_grad()
+    loss, nll, dl, lg = gm.policy_gradient_step(ids, tg, adv, norm, rows_per_pass=rpp, taps=True)
+    assert np.isfinite(loss)
+    assert rel_err(lg, want_lg) <= 1e-3
+    assert abs(loss - want_loss) <= 1e-4 * max(abs(want_loss), 1e-3)
+    assert rel_err(nll, want_nll) <= 1e-4
+    assert rel_err(dl, want_dl) <= 2e-4
+    nonzero = 0
+    for n in gm.names:
+        g, w = gm.grad(n), om.grad(n)
+        scale = max(float(np.max(np.abs(w))), 1e-12)
+        err = float(np.max(np.abs(g - w))) / scale
+        assert err <= 2e-4 or float(np.max(np.abs(g - w))) <= 1e-9, (n, err, scale)
+        nonzero += int(np.any(g != 0))
+    assert nonzero >= len(gm.names) - 1
+    # gradients accumulate across calls (tensors/tensor.go:189-194) and zero_grad clears them
+    before = gm.grad("lm_head.weight")
+    gm.policy_gradient_step(ids, tg, adv, norm, rows_per_pass=rpp)
+    assert rel_err(gm.grad("lm_head.weight"), 2 * before) <= 1e-5
+    gm.zero_grad()
+    assert not np.any(gm.grad("lm_head.weight"))
+    gm.close()
+
+
+def test_rl_step_end_to_end(oracle, ctx):
+    """One whole step on the plumbing configuration: rollout, rewards, advantages, batch, loss, gradients."""
+    from gonano_b200.session import rl_step, build_batch
+    om, gm, cfg = make_pair(oracle, ctx, "c1", std=0.02)
+    V = cfg["vocab_size"]
+    prompts = synthetic.prompts(4, 16, V, seed=9)
+    seeds = np.arange(4, dtype=np.uint64)
+    res = rl_step(gm, prompts, 4, 8, 1.0, 50, seeds, lambda t, l: synthetic.bernoulli_rewards(len(l), 3), advantage_mode=1)
+    assert res.rows == 16 and np.isfinite(res.loss)
+    inputs, targets, max_len = build_batch(prompts, 4, res.tokens, res.lengths, V - 7)
+    want_adv = oracle.advantage(synthetic.bernoulli_rewards(16, 3), 4, 1)
+    assert np.array_equal(res.advantages, want_adv)
+    om.zero_grad()
+    want_loss, _, _, _ = om.policy_gradient_step(inputs, targets, want_adv, float(max_len))
+    assert abs(res.loss - want_loss) <= 1e-4 * max(abs(want_loss), 1e-3)
+    for n in ["lm_head.weight", "transformer.h.0.attn.c_q.weight", "transformer.h.1.mlp.c_fc.weight", "resid_lambdas", "smear_lambda"]:
+        w = om.grad(n)
+        assert float(np.max(np.abs(gm.grad(n) - w))) <= 2e-4 * max(float(np.max(np.abs(w))), 1e-12), n
+    gm.close()
