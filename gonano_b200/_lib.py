@@ -76,6 +76,7 @@ SIGNATURES = {
     "gn_generate_batch": (I, [vp, vp, I, I, I, I, F, I, vp, vp, vp, vp, C.POINTER(I)]),
     "gn_policy_gradient_step": (I, [vp, vp, vp, vp, I, I, F, I, f32p, vp, vp, vp]),
     "gn_model_phase_ms": (I, [vp, C.c_char_p, f32p]),
+    "gn_profile_kernel": (I, [vp, C.c_char_p, C.POINTER(C.c_int64), I, I, f32p]),
 }
 
 _lib = None

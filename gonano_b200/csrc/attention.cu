@@ -547,12 +547,13 @@ int attention_combine_launch(const float* acc, const float* mx, const float* sm,
 // warp reads one K row and one V row as a single coalesced 512-byte request.
 // All query heads of the group are served from the same K/V registers.
 // Warp partials are merged through shared memory, splits through a second pass.
-template <int D, int RATIO>
+template <int DP, int RATIO>
 __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restrict__ q, int64_t q_rstride, const float* __restrict__ kcache,
                                                           const float* __restrict__ vcache, int64_t row_stride, int64_t head_stride,
-                                                          const int32_t* __restrict__ ctx_len, int Hq, int Hkv, int window, float* __restrict__ out,
+                                                          const int32_t* __restrict__ ctx_len, int Hq, int Hkv, int D, int window, float* __restrict__ out,
                                                           int64_t o_rstride, float* __restrict__ part_acc, float* __restrict__ part_ms, int splits) {
-  constexpr int E = D / 32;
+  // DP = head_dim rounded up to a multiple of 32; channels >= D are zero padding.
+  constexpr int E = DP / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x / Hkv, hk = blockIdx.x % Hkv, split = blockIdx.y;
   const int ctx = ctx_len[row];
@@ -567,7 +568,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restric
 #pragma unroll
   for (int h = 0; h < RATIO; ++h)
 #pragma unroll
-    for (int e = 0; e < E; ++e) qv[h][e] = q[(int64_t)row * q_rstride + (int64_t)(hk * RATIO + h) * D + lane * E + e];
+    for (int e = 0; e < E; ++e) qv[h][e] = (lane * E + e < D) ? q[(int64_t)row * q_rstride + (int64_t)(hk * RATIO + h) * D + lane * E + e] : 0.0f;
   float m[RATIO], l[RATIO], o[RATIO][E];
 #pragma unroll
   for (int h = 0; h < RATIO; ++h) {
@@ -579,13 +580,16 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restric
   const float* vb = vcache + (int64_t)row * row_stride + (int64_t)hk * head_stride;
   for (int kj = k0 + warp; kj < k1; kj += 4) {
     float kv[E], vv[E];
-    if (E == 4) {
+    if (E == 4 && DP == 128) {
       float4 a = *reinterpret_cast<const float4*>(kb + (int64_t)kj * D + lane * 4);
       float4 c = *reinterpret_cast<const float4*>(vb + (int64_t)kj * D + lane * 4);
       kv[0] = a.x; kv[1] = a.y; kv[2] = a.z; kv[3] = a.w; vv[0] = c.x; vv[1] = c.y; vv[2] = c.z; vv[3] = c.w;
     } else {
 #pragma unroll
-      for (int e = 0; e < E; ++e) { kv[e] = kb[(int64_t)kj * D + lane * E + e]; vv[e] = vb[(int64_t)kj * D + lane * E + e]; }
+      for (int e = 0; e < E; ++e) {
+        bool ok = lane * E + e < D;
+        kv[e] = ok ? kb[(int64_t)kj * D + lane * E + e] : 0.0f; vv[e] = ok ? vb[(int64_t)kj * D + lane * E + e] : 0.0f;
+      }
     }
 #pragma unroll
     for (int h = 0; h < RATIO; ++h) {
@@ -603,7 +607,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restric
     }
   }
   // merge the 4 warps
-  __shared__ float sm_o[4][RATIO][D];
+  __shared__ float sm_o[4][RATIO][DP];
   __shared__ float sm_m[4][RATIO], sm_l[4][RATIO];
 #pragma unroll
   for (int h = 0; h < RATIO; ++h) {
@@ -612,8 +616,9 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restric
     if (lane == 0) { sm_m[warp][h] = m[h]; sm_l[warp][h] = l[h]; }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < RATIO * D; idx += 128) {
-    int h = idx / D, c = idx % D;
+  for (int idx = threadIdx.x; idx < RATIO * DP; idx += 128) {
+    int h = idx / DP, c = idx % DP;
+    if (c >= D) continue;
     float gm = fmaxf(fmaxf(sm_m[0][h], sm_m[1][h]), fmaxf(sm_m[2][h], sm_m[3][h]));
     float tot = 0, acc = 0;
 #pragma unroll
@@ -632,8 +637,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restric
     }
   }
 }
-template <int D>
-__global__ void __launch_bounds__(128) attn_decode_combine_kernel(const float* part_acc, const float* part_ms, int splits, int Hq, float* out, int64_t o_rstride) {
+__global__ void __launch_bounds__(128) attn_decode_combine_kernel(const float* part_acc, const float* part_ms, int splits, int Hq, int D, float* out, int64_t o_rstride) {
   int row = blockIdx.x / Hq, hq = blockIdx.x % Hq;
   int64_t base = ((int64_t)row * Hq + hq) * splits;
   float gm = -INFINITY;
@@ -655,16 +659,16 @@ int attention_decode_splits(int rows, int Hkv, int max_ctx) {
   return splits;
 }
 
-template <int D, int RATIO>
+template <int DP, int RATIO>
 static int decode_go(const float* q, int64_t q_rstride, const float* kcache, const float* vcache, int64_t row_stride, int64_t head_stride,
-                     const int32_t* ctx_len, int rows, int Hq, int Hkv, int window, float* out, int64_t o_rstride, float* part_acc, float* part_ms,
+                     const int32_t* ctx_len, int rows, int Hq, int Hkv, int D, int window, float* out, int64_t o_rstride, float* part_acc, float* part_ms,
                      int splits, cudaStream_t s) {
   dim3 grid(rows * Hkv, splits);
-  attn_decode_kernel<D, RATIO><<<grid, 128, 0, s>>>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, Hq, Hkv, window, out, o_rstride,
-                                                    part_acc, part_ms, splits);
+  attn_decode_kernel<DP, RATIO><<<grid, 128, 0, s>>>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, Hq, Hkv, D, window, out, o_rstride,
+                                                     part_acc, part_ms, splits);
   GN_LAUNCH_CHECK();
   if (splits > 1) {
-    attn_decode_combine_kernel<D><<<rows * Hq, 128, 0, s>>>(part_acc, part_ms, splits, Hq, out, o_rstride);
+    attn_decode_combine_kernel<<<rows * Hq, 128, 0, s>>>(part_acc, part_ms, splits, Hq, D, out, o_rstride);
     GN_LAUNCH_CHECK();
   }
   return GN_OK;
@@ -675,10 +679,12 @@ int attention_decode_launch(const float* q, int64_t q_rstride, const float* kcac
                             float* part_acc, float* part_ms, int splits, cudaStream_t s) {
   if (rows <= 0) return GN_OK;
   int ratio = Hq / Hkv;
-#define GN_DEC(DD, RR) if (D == DD && ratio == RR) return decode_go<DD, RR>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, rows, Hq, Hkv, window, out, o_rstride, part_acc, part_ms, splits, s)
+  const int dp = (D + 31) / 32 * 32;
+#define GN_DEC(DD, RR) if (dp == DD && ratio == RR) return decode_go<DD, RR>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, rows, Hq, Hkv, D, window, out, o_rstride, part_acc, part_ms, splits, s)
   GN_DEC(128, 1); GN_DEC(128, 2); GN_DEC(128, 3); GN_DEC(128, 4); GN_DEC(128, 8);
+  GN_DEC(96, 1); GN_DEC(96, 2); GN_DEC(96, 4);
   GN_DEC(64, 1); GN_DEC(64, 2); GN_DEC(64, 3); GN_DEC(64, 4); GN_DEC(64, 8);
-  GN_DEC(32, 1); GN_DEC(32, 2); GN_DEC(32, 4);
+  GN_DEC(32, 1); GN_DEC(32, 2); GN_DEC(32, 3); GN_DEC(32, 4); GN_DEC(32, 8);
 #undef GN_DEC
   set_error("decode attention: unsupported head_dim %d / group ratio %d", D, ratio);
   return GN_ERR_INVALID;

@@ -1,0 +1,10 @@
+// The context behind gn_ctx: one device, one stream.
+#pragma once
+#include <cuda_runtime.h>
+
+struct gn_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  bool own_stream = false;
+  int gemm_kind = 1;
+};

@@ -23,15 +23,10 @@
 
 #include "kernels.cuh"
 #include "model_kernels.cuh"
+#include "ctx.cuh"
 
 using namespace gn;
 
-struct gn_ctx {
-  int device = 0;
-  cudaStream_t stream = nullptr;
-  bool own_stream = false;
-  int gemm_kind = 1;
-};
 
 namespace {
 

@@ -1,0 +1,135 @@
+// gn_profile_kernel: per-kernel timing on synthetic device data (CUDA events on the
+// context's stream).  The benchmark uses it to put each hot kernel beside its roofline.
+#include <string>
+#include <vector>
+
+#include "kernels.cuh"
+#include "ctx.cuh"
+
+using namespace gn;
+
+
+namespace {
+
+__global__ void synth_kernel(float* dst, int64_t n, float lo, float hi, uint32_t salt) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    uint32_t h = (uint32_t)i * 2654435761u + salt;
+    h ^= h >> 15; h *= 2246822519u; h ^= h >> 13;
+    dst[i] = lo + (hi - lo) * (float)(h >> 8) * (1.0f / 16777216.0f);
+  }
+}
+__global__ void synth_targets_kernel(int32_t* dst, int64_t n, int vocab, int valid_percent) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  uint32_t h = (uint32_t)i * 2654435761u + 12345u;
+  h ^= h >> 15; h *= 2246822519u; h ^= h >> 13;
+  dst[i] = ((int)(h % 100u) < valid_percent) ? (int32_t)((h >> 7) % (uint32_t)vocab) : -1;
+}
+
+struct Bufs {
+  std::vector<void*> p;
+  ~Bufs() { for (void* q : p) cudaFree(q); }
+  template <typename T>
+  int get(T** out, size_t n) {
+    void* q = nullptr;
+    cudaError_t e = cudaMalloc(&q, n * sizeof(T));
+    if (e != cudaSuccess) { set_error("profile: cudaMalloc of %zu bytes failed: %s", n * sizeof(T), cudaGetErrorString(e)); return GN_ERR_NOMEM; }
+    p.push_back(q);
+    *out = (T*)q;
+    return GN_OK;
+  }
+};
+
+int synth(float* dst, int64_t n, float lo, float hi, uint32_t salt, cudaStream_t s) {
+  synth_kernel<<<kNumSM * 8, 256, 0, s>>>(dst, n, lo, hi, salt);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+template <typename F>
+int time_it(cudaStream_t s, int iters, float* mean_ms, F&& launch) {
+  cudaEvent_t a, b;
+  GN_CUDA(cudaEventCreate(&a)); GN_CUDA(cudaEventCreate(&b));
+  for (int i = 0; i < 3; ++i) GN_TRY(launch());
+  GN_CUDA(cudaStreamSynchronize(s));
+  GN_CUDA(cudaEventRecord(a, s));
+  for (int i = 0; i < iters; ++i) GN_TRY(launch());
+  GN_CUDA(cudaEventRecord(b, s));
+  GN_CUDA(cudaEventSynchronize(b));
+  float ms = 0;
+  GN_CUDA(cudaEventElapsedTime(&ms, a, b));
+  cudaEventDestroy(a); cudaEventDestroy(b);
+  *mean_ms = ms / (float)iters;
+  return GN_OK;
+}
+
+}  // namespace
+
+extern "C" int gn_profile_kernel(gn_ctx* ctx, const char* kernel, const int64_t* dims, int n_dims, int iters, float* mean_ms) {
+  GN_REQUIRE(ctx && kernel && dims && mean_ms && iters > 0, "gn_profile_kernel: bad argument");
+  GN_CUDA(cudaSetDevice(ctx->device));
+  cudaStream_t s = ctx->stream;
+  std::string k(kernel);
+  Bufs bufs;
+  if (k == "gemm_nt" || k == "gemm_nn" || k == "gemm_tn") {
+    GN_REQUIRE(n_dims == 3, "%s wants {M, N, K}", kernel);
+    int M = (int)dims[0], N = (int)dims[1], K = (int)dims[2];
+    float *A, *B, *C;
+    GN_TRY(bufs.get(&A, (size_t)M * K)); GN_TRY(bufs.get(&B, (size_t)N * K)); GN_TRY(bufs.get(&C, (size_t)M * N));
+    GN_TRY(synth(A, (int64_t)M * K, -1, 1, 1, s)); GN_TRY(synth(B, (int64_t)N * K, -1, 1, 2, s));
+    GemmArgs g; g.A = A; g.B = B; g.C = C; g.M = M; g.N = N; g.K = K; g.ldc = N;
+    if (k == "gemm_nt") { g.lda = K; g.ldb = K; g.b_trans = 1; }
+    else if (k == "gemm_nn") { g.lda = K; g.ldb = N; g.b_trans = 0; }
+    else { g.lda = M; g.a_trans = 1; g.ldb = N; g.b_trans = 0; }
+    int kind = ctx->gemm_kind;
+    return time_it(s, iters, mean_ms, [&]() { return gemm_dispatch(g, kind, s); });
+  }
+  if (k == "loss") {
+    GN_REQUIRE(n_dims == 3, "loss wants {rows, vocab, valid_percent}");
+    int64_t rows = dims[0]; int vocab = (int)dims[1]; int pct = (int)dims[2];
+    float *logits, *grad, *adv, *nll; int32_t* tg; double* rl;
+    GN_TRY(bufs.get(&logits, (size_t)rows * vocab)); GN_TRY(bufs.get(&grad, (size_t)rows * vocab)); GN_TRY(bufs.get(&adv, (size_t)rows));
+    GN_TRY(bufs.get(&nll, (size_t)rows)); GN_TRY(bufs.get(&tg, (size_t)rows)); GN_TRY(bufs.get(&rl, (size_t)rows + 1));
+    GN_TRY(synth(logits, rows * vocab, -15, 15, 3, s)); GN_TRY(synth(adv, rows, -1, 1, 4, s));
+    synth_targets_kernel<<<ceil_div(rows, 256), 256, 0, s>>>(tg, rows, vocab, pct);
+    GN_LAUNCH_CHECK();
+    return time_it(s, iters, mean_ms, [&]() { return pg_loss_launch(logits, tg, adv, rows, vocab, vocab, 512, 8192.0f, 15.0f, nll, grad, vocab, rl + 1, rl, 0, s); });
+  }
+  if (k == "sampler") {
+    GN_REQUIRE(n_dims == 3, "sampler wants {rows, vocab, top_k}");
+    int rows = (int)dims[0], vocab = (int)dims[1], topk = (int)dims[2];
+    float* logits; int32_t* out; uint64_t* seeds;
+    GN_TRY(bufs.get(&logits, (size_t)rows * vocab)); GN_TRY(bufs.get(&out, (size_t)rows)); GN_TRY(bufs.get(&seeds, (size_t)rows));
+    GN_TRY(synth(logits, (int64_t)rows * vocab, -15, 15, 5, s));
+    GN_CUDA(cudaMemsetAsync(seeds, 1, sizeof(uint64_t) * rows, s));
+    uint32_t step = 0;
+    return time_it(s, iters, mean_ms, [&]() { return sample_launch(logits, rows, vocab, 1, nullptr, seeds, 8, nullptr, step++, 1.0f, topk, out, s); });
+  }
+  if (k == "decode_attention") {
+    GN_REQUIRE(n_dims == 5, "decode_attention wants {rows, n_head, n_kv_head, head_dim, context}");
+    int rows = (int)dims[0], Hq = (int)dims[1], Hkv = (int)dims[2], D = (int)dims[3], ctxl = (int)dims[4];
+    float *q, *kc, *vc, *out, *pa, *pm; int32_t* cl;
+    size_t cache = (size_t)rows * Hkv * ctxl * D;
+    int splits = attention_decode_splits(rows, Hkv, ctxl);
+    GN_TRY(bufs.get(&q, (size_t)rows * Hq * D)); GN_TRY(bufs.get(&kc, cache)); GN_TRY(bufs.get(&vc, cache)); GN_TRY(bufs.get(&out, (size_t)rows * Hq * D));
+    GN_TRY(bufs.get(&pa, (size_t)rows * Hq * splits * D)); GN_TRY(bufs.get(&pm, (size_t)rows * Hq * splits * 2)); GN_TRY(bufs.get(&cl, (size_t)rows));
+    GN_TRY(synth(q, (int64_t)rows * Hq * D, -1, 1, 6, s)); GN_TRY(synth(kc, (int64_t)cache, -1, 1, 7, s)); GN_TRY(synth(vc, (int64_t)cache, -1, 1, 8, s));
+    std::vector<int32_t> h(rows, ctxl);
+    GN_CUDA(cudaMemcpyAsync(cl, h.data(), sizeof(int32_t) * rows, cudaMemcpyHostToDevice, s));
+    GN_CUDA(cudaStreamSynchronize(s));
+    return time_it(s, iters, mean_ms, [&]() {
+      return attention_decode_launch(q, (int64_t)Hq * D, kc, vc, (int64_t)Hkv * ctxl * D, (int64_t)ctxl * D, cl, rows, Hq, Hkv, D, -1, out, (int64_t)Hq * D, pa, pm, splits, s);
+    });
+  }
+  if (k == "advantage") {
+    GN_REQUIRE(n_dims == 2, "advantage wants {groups, group}");
+    int groups = (int)dims[0], group = (int)dims[1];
+    float *r, *a;
+    GN_TRY(bufs.get(&r, (size_t)groups * group)); GN_TRY(bufs.get(&a, (size_t)groups * group));
+    GN_TRY(synth(r, (int64_t)groups * group, 0, 1, 9, s));
+    return time_it(s, iters, mean_ms, [&]() { return advantage_launch(r, groups, group, 0, a, s); });
+  }
+  set_error("gn_profile_kernel: unknown kernel '%s'", kernel);
+  return GN_ERR_INVALID;
+}

@@ -47,6 +47,13 @@ class Context:
     def set_gemm(self, kind: int):
         check(self.lib.gn_ctx_set_gemm(self.h, kind))
 
+    def profile_kernel(self, kernel: str, dims, iters: int = 10) -> float:
+        """Mean milliseconds per launch of one hot kernel on synthetic device data (CUDA events)."""
+        arr = (C.c_int64 * len(dims))(*[int(x) for x in dims])
+        out = C.c_float()
+        check(self.lib.gn_profile_kernel(self.h, kernel.encode(), arr, len(dims), iters, C.byref(out)))
+        return out.value
+
     def close(self):
         if self.h:
             self.lib.gn_ctx_destroy(self.h)
@@ -156,7 +163,7 @@ class Model:
 # -------------------------------------------------------------------------
 # Batch assembly of cmd/chat_rl (host side, integer work)
 # -------------------------------------------------------------------------
-def build_batch(prompts, group, tokens, lengths, pad_token):
+def build_batch(prompts, group, tokens, lengths, pad_token, max_len=None):
     """Pads every rollout (prompt + kept tokens) to the longest one with ``pad_token``
     (= <|assistant_end|>), shifts inputs/targets by one and masks targets whose index is
     below the prompt length (cmd/chat_rl/main.go:156-182).  Returns inputs, targets
@@ -165,7 +172,8 @@ def build_batch(prompts, group, tokens, lengths, pad_token):
     prompts = _i32(prompts); tokens = _i32(tokens); lengths = _i32(lengths)
     P, plen = prompts.shape
     rows = P * group
-    max_len = plen + int(lengths.max())
+    local = plen + int(lengths.max())
+    max_len = local if max_len is None else max(int(max_len), local)   # data parallel: every rank pads to the global length
     padded = np.full((rows, max_len), pad_token, np.int32)
     padded[:, :plen] = np.repeat(prompts, group, axis=0)
     for r in range(rows):
@@ -189,19 +197,20 @@ class RLStepResult:
 
 
 def rl_step(model: Model, prompts, group, max_tokens, temperature, top_k, seeds, reward_fn, advantage_mode=0, rows_per_pass=0,
-            norm=None, all_reduce=None) -> RLStepResult:
+            norm=None, all_reduce=None, max_len_fn=None) -> RLStepResult:
     """One RL step the way cmd/chat_rl runs it (main.go:87-184), minus the optimizer:
     rollout -> rewards -> group-relative advantages -> padded batch -> PolicyGradientStep
     -> gradient all-reduce (``all_reduce(model)``, when data parallel).  ``reward_fn(tokens,
     lengths)`` returns one reward per rollout.  ``norm`` defaults to the padded length
-    (main.go:183)."""
+    (main.go:183).  ``max_len_fn(local_max_len)`` returns the length every rank pads to."""
     from .backend import group_advantage
     prompts = _i32(prompts)
     tokens, lengths, steps, _ = model.generate_batch(prompts, group, max_tokens, temperature, top_k, seeds)
     rewards = _f32(reward_fn(tokens, lengths))
     adv = group_advantage(rewards, group, advantage_mode)
     pad = model.vocab - 7  # <|assistant_end|>
-    inputs, targets, max_len = build_batch(prompts, group, tokens, lengths, pad)
+    local_max = prompts.shape[1] + int(lengths.max())
+    inputs, targets, max_len = build_batch(prompts, group, tokens, lengths, pad, max_len_fn(local_max) if max_len_fn else None)
     model.zero_grad()
     loss, _, _, _ = model.policy_gradient_step(inputs, targets, adv, float(max_len) if norm is None else norm, rows_per_pass)
     if all_reduce is not None:

@@ -238,6 +238,17 @@ int gn_policy_gradient_step(gn_model* model, const int32_t* inputs, const int32_
  * "prefill", "decode", "train_forward", "loss", "train_backward". */
 int gn_model_phase_ms(gn_model* model, const char* phase, float* ms);
 
+/* Profiling aid (no counterpart in the reference): times `iters` launches of one kernel of
+ * the RL step on synthetic device data with CUDA events on the context's stream, after three
+ * warm-up launches, and returns the mean time of one launch in milliseconds.
+ *   "gemm_nt" / "gemm_nn" / "gemm_tn"  dims {M, N, K}        C = A B^T / A B / A^T B
+ *   "loss"              dims {rows, vocab, valid_percent}    fused loss + dlogits (+ softcap backward)
+ *   "sampler"           dims {rows, vocab, top_k}
+ *   "decode_attention"  dims {rows, n_head, n_kv_head, head_dim, context}
+ *   "advantage"         dims {groups, group}
+ * Buffers are larger than L2 for the workloads this is used on, so no cache flush is done. */
+int gn_profile_kernel(gn_ctx* ctx, const char* kernel, const int64_t* dims, int n_dims, int iters, float* mean_ms);
+
 #ifdef __cplusplus
 }
 #endif

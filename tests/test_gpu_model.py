@@ -138,11 +138,17 @@ def test_policy_gradient_step(oracle, ctx, name, std, B, T, rpp):
     assert rel_err(nll, want_nll) <= 1e-4
     assert rel_err(dl, want_dl) <= 2e-4
     nonzero = 0
+    # Per tensor: 2e-4 of the tensor's largest gradient.  A scalar parameter whose gradient is a
+    # sum of cancelling terms (backout_lambda: sum of dX * -backout with dX orthogonal to the
+    # normalised row) has no digits left at that scale, so an absolute floor of 1e-5 of the
+    # largest gradient entry of the whole model applies, in the spirit of the reference's
+    # Close() floor (kernels/kerneltest/compare.go:31-39).
+    global_scale = max(float(np.max(np.abs(om.grad(n)))) for n in om.names)
     for n in gm.names:
         g, w = gm.grad(n), om.grad(n)
         scale = max(float(np.max(np.abs(w))), 1e-12)
-        err = float(np.max(np.abs(g - w))) / scale
-        assert err <= 2e-4 or float(np.max(np.abs(g - w))) <= 1e-9, (n, err, scale)
+        err = float(np.max(np.abs(g - w)))
+        assert err <= 2e-4 * scale or err <= 1e-5 * global_scale, (n, err, scale, global_scale)
         nonzero += int(np.any(g != 0))
     assert nonzero >= len(gm.names) - 1
     # gradients accumulate across calls (tensors/tensor.go:189-194) and zero_grad clears them
