@@ -29,6 +29,21 @@ int64_t launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
 int gemm_tcgen05_supported(const GemmArgs& a);
 int gemm_tcgen05(const GemmArgs& a, cudaStream_t s);
+void gemm_tcgen05_invalidate();
+int gemm_tcgen05_check(cudaStream_t s);
+void gemm_invalidate_static() {
+#ifdef GN_HAVE_TCGEN05
+  gemm_tcgen05_invalidate();
+#endif
+}
+int gemm_check_error(cudaStream_t s) {
+#ifdef GN_HAVE_TCGEN05
+  return gemm_tcgen05_check(s);
+#else
+  (void)s;
+  return GN_OK;
+#endif
+}
 int gemm_default_kind() {
 #ifdef GN_HAVE_TCGEN05
   return 1;
@@ -191,7 +206,8 @@ static int matmul_any(float* dst, const float* left, const float* right, int row
   if (st.status != GN_OK) return st.status;
   g.M = rows; g.N = cols; g.K = inner; g.lda = inner; g.ldb = b_trans ? inner : cols; g.ldc = cols; g.b_trans = b_trans;
   GN_TRY(gemm_dispatch(g, gemm_default_kind(), s));
-  GN_END();
+  GN_TRY(st.finish());
+  return gemm_check_error(s);
 }
 int gn_matmul(float* dst, const float* l, const float* r, int rows, int cols, int inner) { return matmul_any(dst, l, r, rows, cols, inner, 0); }
 int gn_matmul_transposed(float* dst, const float* l, const float* r, int rows, int cols, int inner) { return matmul_any(dst, l, r, rows, cols, inner, 1); }

@@ -125,11 +125,15 @@ struct GemmArgs {
   int epilogue = EPI_STORE;
   float* aux = nullptr; int64_t ldaux = 0;
   float scalar = 0.0f;
+  int a_static = 0, b_static = 0;  // operand is a parameter tensor: its tensor-core split may be cached
 };
 int gemm_simt(const GemmArgs& args, cudaStream_t stream);
 // kind 0: SIMT float32.  kind 1: tcgen05 3xTF32 where the shape allows it, else SIMT.
 int gemm_dispatch(const GemmArgs& args, int kind, cudaStream_t stream);
 int gemm_default_kind();
 int64_t launch_count();
+// tcgen05 path housekeeping (no-ops when the library was built without it).
+void gemm_invalidate_static();        // parameters changed: drop cached operand splits
+int gemm_check_error(cudaStream_t s); // GN_ERR_TIMEOUT when a bounded device wait ran out
 
 }  // namespace gn

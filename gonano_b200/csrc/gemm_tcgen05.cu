@@ -1,0 +1,497 @@
+// 3xTF32 GEMM on the 5th-generation tensor cores (tcgen05), sm_100a only.
+//
+//   C[M,N] (epilogue)= A[M,K] * B[N,K]^T      float32 in, float32 out
+//
+// Every float32 operand x is split once into hi = tf32(x) and lo = tf32(x - hi);
+// the product is accumulated as  lo_a*hi_b + hi_a*lo_b + hi_a*hi_b  in float32
+// inside tensor memory (the lo*lo term, ~2^-22 relative, is dropped).  This keeps
+// the results float32-faithful against the reference, which is float32
+// throughout (guides/06-numeric-precision.md), while the multiplies run on the
+// TF32 tensor pipe.
+//
+// Kernel structure (one 128 x BN output tile per CTA, 192 threads):
+//   warp 0     TMA producer: four tiled bulk-tensor loads per k-block (A hi/lo,
+//              B hi/lo; 32 floats = one 128-byte swizzle row each) into a ring of
+//              shared-memory stages, completion on the stage's "full" mbarrier.
+//   warp 1     allocates tensor memory; one elected lane issues the
+//              tcgen05.mma.kind::tf32 instructions (M=128, N=BN, K=8; twelve per
+//              k-block) and commits each stage back to its "empty" mbarrier and the
+//              finished tile to the "accumulator full" mbarrier.
+//   warps 2-5  epilogue: tcgen05.ld the accumulator (each warp its own 32-lane
+//              quarter), apply the fused epilogue, store to global memory.
+// Every wait on an mbarrier is bounded; when a bound runs out the kernel raises a
+// flag in global memory, drains and returns, and the host reports GN_ERR_TIMEOUT.
+//
+// Operands must be K-major.  The forward products (x W^T) already are; for the
+// data gradient (dY W) a transposed split copy of the weight is kept, and for the
+// weight gradient (dY^T X) both operands are transposed while they are split.
+// Split copies of parameter tensors are cached until the parameters change.
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "kernels.cuh"
+
+namespace gn {
+
+namespace {
+
+constexpr int TBM = 128;       // tile rows = UMMA M
+constexpr int TBK = 32;        // floats per k-block = one 128-byte swizzle row
+constexpr int UMMA_K = 8;      // tf32 MMA depth
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the limit ran out (the flag is raised by the caller).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_test(bar, parity)) return true;
+    if (i > 64) __nanosleep(64);
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  uint32_t z = 0;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(z), "r"(z), "r"(z), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+        "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+        "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows of 128 bytes, 8-row
+// groups 1024 bytes apart.  Bits: [0,14) address>>4, [16,30) leading offset>>4 (1 for
+// swizzled K-major), [32,46) stride offset>>4, [46,48) version 1, [61,64) layout 2.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Instruction descriptor for kind::tf32, float32 accumulate, both operands K-major:
+// [4,6) D format 1 = F32, [7,10) A format 2 = TF32, [10,13) B format 2, [17,23) N>>3, [24,29) M>>4.
+__device__ __forceinline__ uint32_t instr_desc_tf32(int m, int n) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+struct TcEpilogue {
+  float* C; int64_t ldc;
+  float* aux; int64_t ldaux;
+  int epi; float scalar;
+};
+
+__device__ __forceinline__ float epi_value(const TcEpilogue& e, float acc, int64_t m, int n, float cold, bool& write_aux, float& auxv) {
+  write_aux = false;
+  switch (e.epi) {
+    case EPI_STORE: return acc;
+    case EPI_ACCUM: return cold + acc;
+    case EPI_RESIDUAL: return e.aux[m * e.ldaux + n] + acc;
+    case EPI_RELU2: { write_aux = e.aux != nullptr; auxv = acc; float r = acc < 0.0f ? 0.0f : acc; return r * r; }
+    case EPI_SOFTCAP: return e.scalar * tanhf(acc * (1.0f / e.scalar));
+    case EPI_RELU2_BWD: { float u = e.aux[m * e.ldaux + n]; return u > 0.0f ? acc * 2.0f * u : 0.0f; }
+  }
+  return acc;
+}
+
+// Two-level accumulation.  The tensor core adds into its float32 accumulator with
+// truncation, so the error of one long K loop grows linearly with K (measured: 2e-5 of
+// the largest output at K = 3072).  The K loop is therefore cut into chunks of
+// kChunkBlocks k-blocks; each chunk accumulates from zero in one of two tensor-memory
+// buffers and the epilogue warps add the finished chunk into float32 registers with
+// round-to-nearest while the next chunk is being multiplied.
+constexpr int kChunkBlocks = 4;   // 4 x 32 = 128 elements of K per chunk
+
+template <int BN, int STAGES>
+struct TcSmem {
+  static constexpr int A_BYTES = TBM * TBK * 4;   // 16 KB
+  static constexpr int B_BYTES = BN * TBK * 4;
+  static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + slack for the 1024-byte alignment
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
+                                                         const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
+                                                         TcEpilogue ep, int M, int N, int K, int* err) {
+  using S = TcSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  // swizzled tiles want 1024-byte alignment
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bars = base + S::BAR_OFFSET;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto acc_full = [&](int b) { return bars + 8u * (2 * STAGES + b); };
+  auto acc_empty = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
+  const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 4);
+  uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + S::BAR_OFFSET + 8 * (2 * STAGES + 4));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * TBM, n0 = blockIdx.x * BN;
+  const int nk = (K + TBK - 1) / TBK;
+  const int nchunks = (nk + kChunkBlocks - 1) / kChunkBlocks;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BN);   // two accumulator buffers of BN float32 columns (a power of two >= 32)
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+  bool failed = false;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      for (int kb = 0; kb < nk; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t round = (uint32_t)(kb / STAGES);
+        if (kb >= STAGES && !mbar_wait(empty_bar(s), (round - 1) & 1u)) { failed = true; break; }
+        const uint32_t st = base + (uint32_t)s * S::STAGE_BYTES;
+        mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
+        tma_load_2d(st, &tmAh, full_bar(s), kb * TBK, m0);
+        tma_load_2d(st + S::A_BYTES, &tmAl, full_bar(s), kb * TBK, m0);
+        tma_load_2d(st + 2 * S::A_BYTES, &tmBh, full_bar(s), kb * TBK, n0);
+        tma_load_2d(st + 2 * S::A_BYTES + S::B_BYTES, &tmBl, full_bar(s), kb * TBK, n0);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc_tf32(TBM, BN);
+      for (int c = 0; c < nchunks && !failed; ++c) {
+        const int buf = c & 1;
+        // the epilogue must have drained this buffer's previous chunk
+        if (c >= 2 && !mbar_wait(acc_empty(buf), (uint32_t)(c / 2 - 1) & 1u)) { failed = true; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+        const int kb_end = min(nk, (c + 1) * kChunkBlocks);
+        for (int kb = c * kChunkBlocks; kb < kb_end; ++kb) {
+          const int s = kb % STAGES;
+          if (!mbar_wait(full_bar(s), (uint32_t)(kb / STAGES) & 1u)) { failed = true; break; }
+          tc_fence_after();
+          const uint32_t st = base + (uint32_t)s * S::STAGE_BYTES;
+          const uint64_t ah = smem_desc_sw128(st), al = smem_desc_sw128(st + S::A_BYTES);
+          const uint64_t bh = smem_desc_sw128(st + 2 * S::A_BYTES), bl = smem_desc_sw128(st + 2 * S::A_BYTES + S::B_BYTES);
+#pragma unroll
+          for (int k = 0; k < TBK / UMMA_K; ++k) {
+            // advancing along K inside the 128-byte swizzle row: +32 bytes = +2 in the address field
+            const uint64_t adv = (uint64_t)((k * UMMA_K * 4) >> 4);
+            umma_tf32(d_tmem, al + adv, bh + adv, idesc, (kb > c * kChunkBlocks || k > 0) ? 1u : 0u);
+            umma_tf32(d_tmem, ah + adv, bl + adv, idesc, 1u);
+            umma_tf32(d_tmem, ah + adv, bh + adv, idesc, 1u);
+          }
+          umma_commit(empty_bar(s));   // the stage is free once these MMAs have read it
+        }
+        if (!failed) umma_commit(acc_full(buf));   // this chunk's partial sums are complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue (warps 2..5)
+    const int quarter = warp & 3;    // tcgen05.ld: a warp reads lanes [32*(warp%4), +32)
+    float acc[BN];
+#pragma unroll
+    for (int j = 0; j < BN; ++j) acc[j] = 0.0f;
+    for (int c = 0; c < nchunks; ++c) {
+      const int buf = c & 1;
+      if (!mbar_wait(acc_full(buf), (uint32_t)(c / 2) & 1u)) { failed = true; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[c0 + j] += __uint_as_float(r[j]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(buf)) : "memory");
+    }
+    if (!failed) {
+      const int64_t m = (int64_t)m0 + quarter * 32 + lane;
+      const bool vec_ok = (ep.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.C) & 15) == 0) &&
+                          (ep.aux == nullptr || ((ep.ldaux % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.aux) & 15) == 0)));
+      if (m < M) {
+        float* crow = ep.C + m * ep.ldc;
+#pragma unroll
+        for (int j = 0; j < BN; j += 4) {
+          const int n = n0 + j;
+          if (vec_ok && n + 4 <= N) {
+            float4 cold = make_float4(0, 0, 0, 0);
+            if (ep.epi == EPI_ACCUM) cold = *reinterpret_cast<const float4*>(crow + n);
+            float co[4] = {cold.x, cold.y, cold.z, cold.w}, out[4], av[4];
+            bool wa = false;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) out[e] = epi_value(ep, acc[j + e], m, n + e, co[e], wa, av[e]);
+            if (wa) *reinterpret_cast<float4*>(ep.aux + m * ep.ldaux + n) = make_float4(av[0], av[1], av[2], av[3]);
+            *reinterpret_cast<float4*>(crow + n) = make_float4(out[0], out[1], out[2], out[3]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              if (n + e < N) {
+                bool wa = false; float av = 0.0f;
+                float cold = (ep.epi == EPI_ACCUM) ? crow[n + e] : 0.0f;
+                float out = epi_value(ep, acc[j + e], m, n + e, cold, wa, av);
+                if (wa) ep.aux[m * ep.ldaux + n + e] = av;
+                crow[n + e] = out;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  if (failed) {
+    atomicExch(err, 1);
+    // give bulk copies that are still in flight time to land before the CTA goes away
+    for (int i = 0; i < 4096; ++i) __nanosleep(256);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
+}
+
+// ------------------------------------------------------------------ operand split
+__device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
+  uint32_t h, l;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+  hi = __uint_as_float(h);
+  float rest = x - hi;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(rest));
+  lo = __uint_as_float(l);
+}
+// src [rows, cols] (pitch ld) -> hi, lo [rows, cols] (pitch ldd)
+__global__ void __launch_bounds__(256) split_kernel(const float* __restrict__ src, int64_t ld, float* __restrict__ hi, float* __restrict__ lo, int64_t ldd,
+                                                    int64_t rows, int cols) {
+  const int cv = cols >> 2;  // cols is a multiple of 4
+  int64_t total = rows * cv;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t r = i / cv; int c = (int)(i % cv) * 4;
+    float4 v = *reinterpret_cast<const float4*>(src + r * ld + c);
+    float4 h, l;
+    split_tf32(v.x, h.x, l.x); split_tf32(v.y, h.y, l.y); split_tf32(v.z, h.z, l.z); split_tf32(v.w, h.w, l.w);
+    *reinterpret_cast<float4*>(hi + r * ldd + c) = h;
+    *reinterpret_cast<float4*>(lo + r * ldd + c) = l;
+  }
+}
+// src [rows, cols] (pitch ld) -> hi, lo [cols, rows_padded] (pitch ldd), zero-filled padding
+__global__ void __launch_bounds__(256) split_transpose_kernel(const float* __restrict__ src, int64_t ld, float* __restrict__ hi, float* __restrict__ lo,
+                                                              int64_t ldd, int64_t rows, int cols) {
+  __shared__ float th[32][33], tl[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  const int64_t r0 = (int64_t)blockIdx.y * 32; const int c0 = blockIdx.x * 32;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int64_t r = r0 + ty + 8 * i; int c = c0 + tx;
+    float h = 0.0f, l = 0.0f;
+    if (r < rows && c < cols) split_tf32(src[r * ld + c], h, l);
+    th[ty + 8 * i][tx] = h; tl[ty + 8 * i][tx] = l;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int c = c0 + ty + 8 * i; int64_t r = r0 + tx;
+    if (c < cols && r < ldd) { hi[(int64_t)c * ldd + r] = th[tx][ty + 8 * i]; lo[(int64_t)c * ldd + r] = tl[tx][ty + 8 * i]; }
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+int* g_err_flag = nullptr;
+std::mutex g_mu;
+
+struct SplitBuf { float* hi = nullptr; float* lo = nullptr; size_t floats = 0; int64_t ld = 0; };
+// Cached splits of parameter tensors: key = (pointer, rows, cols, transposed).
+std::map<std::tuple<const void*, int64_t, int64_t, int>, SplitBuf> g_static;
+SplitBuf g_dyn[2];  // scratch for the activation operands (A and B of the current product)
+
+int ensure_init() {
+  if (g_encode && g_err_flag) return GN_OK;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  GN_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+  GN_REQUIRE(fn != nullptr && q == cudaDriverEntryPointSuccess, "cuTensorMapEncodeTiled is not available from this driver");
+  g_encode = (EncodeTiledFn)fn;
+  GN_CUDA(cudaMalloc((void**)&g_err_flag, sizeof(int)));
+  GN_CUDA(cudaMemset(g_err_flag, 0, sizeof(int)));
+  return GN_OK;
+}
+
+int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t k, int64_t ld, int box_rows) {
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
+  cuuint32_t box[2] = {(cuuint32_t)TBK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with %d (rows %lld, k %lld, ld %lld)", (int)r, (long long)rows, (long long)k, (long long)ld); return GN_ERR_CUDA; }
+  return GN_OK;
+}
+
+int ensure_buf(SplitBuf& b, size_t floats) {
+  if (floats <= b.floats) return GN_OK;
+  if (b.hi) { cudaFree(b.hi); cudaFree(b.lo); b.hi = b.lo = nullptr; b.floats = 0; }
+  cudaError_t e1 = cudaMalloc((void**)&b.hi, floats * sizeof(float));
+  cudaError_t e2 = e1 == cudaSuccess ? cudaMalloc((void**)&b.lo, floats * sizeof(float)) : e1;
+  if (e1 != cudaSuccess || e2 != cudaSuccess) { set_error("tcgen05 gemm: cannot allocate %zu-byte operand split buffers", 2 * floats * sizeof(float)); return GN_ERR_NOMEM; }
+  b.floats = floats;
+  return GN_OK;
+}
+
+// Produces K-major hi/lo copies of an operand.  `rows` x `k` is the logical operand
+// (rows = M or N).  stored_transposed: the source is stored [k, rows] (pitch ld).
+int split_operand(const float* src, int64_t ld, int64_t rows, int64_t k, bool stored_transposed, bool is_static, int which, SplitBuf& out, cudaStream_t s) {
+  const int64_t kp = (k + 3) / 4 * 4;
+  auto key = std::make_tuple((const void*)src, rows, k, stored_transposed ? 1 : 0);
+  if (is_static) {
+    auto it = g_static.find(key);
+    if (it != g_static.end()) { out = it->second; return GN_OK; }
+  }
+  SplitBuf buf;
+  SplitBuf* target = is_static ? &buf : &g_dyn[which];
+  GN_TRY(ensure_buf(*target, (size_t)rows * kp));
+  target->ld = kp;
+  if (!stored_transposed) {
+    int64_t total = rows * (k / 4);
+    int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)kNumSM * 16);
+    split_kernel<<<std::max(blocks, 1), 256, 0, s>>>(src, ld, target->hi, target->lo, kp, rows, (int)k);
+  } else {
+    dim3 grid(ceil_div(rows, 32), ceil_div(kp, 32));   // source is [k, rows]: x over its columns (= rows), y over its rows (= k)
+    split_transpose_kernel<<<grid, 256, 0, s>>>(src, ld, target->hi, target->lo, kp, k, (int)rows);
+  }
+  GN_LAUNCH_CHECK();
+  if (is_static) g_static[key] = *target;
+  out = *target;
+  return GN_OK;
+}
+
+template <int BN, int STAGES>
+int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep, int M, int N, int K, cudaStream_t s) {
+  using S = TcSmem<BN, STAGES>;
+  static bool configured = false;
+  if (!configured) {
+    GN_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+    configured = true;
+  }
+  CUtensorMap mah, mal, mbh, mbl;
+  GN_TRY(make_map(&mah, a.hi, M, K, a.ld, TBM)); GN_TRY(make_map(&mal, a.lo, M, K, a.ld, TBM));
+  GN_TRY(make_map(&mbh, b.hi, N, K, b.ld, BN)); GN_TRY(make_map(&mbl, b.lo, N, K, b.ld, BN));
+  dim3 grid(ceil_div(N, BN), ceil_div(M, TBM));
+  gemm_tc_kernel<BN, STAGES><<<grid, 192, S::TOTAL, s>>>(mah, mal, mbh, mbl, ep, M, N, K, g_err_flag);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+}  // namespace
+
+int gemm_tcgen05_supported(const GemmArgs& g) {
+  if (g.M < 64 || g.N < 64 || g.K < 32) return 0;      // tiny products stay on the SIMT kernel
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (!al(g.A) || !al(g.B)) return 0;
+  // Sources read with float4 need a contiguous extent that is a multiple of 4; the
+  // transposing split reads scalars and pads.
+  if (!g.a_trans && (g.K % 4 != 0 || g.lda % 4 != 0)) return 0;
+  if (g.b_trans && (g.K % 4 != 0 || g.ldb % 4 != 0)) return 0;
+  return 1;
+}
+
+int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  GN_TRY(ensure_init());
+  SplitBuf a, b;
+  // A is logically [M, K]; stored transposed ([K, M]) when a_trans.
+  GN_TRY(split_operand(g.A, g.lda, g.M, g.K, g.a_trans != 0, g.a_static != 0, 0, a, s));
+  // B is logically [N, K]; stored that way when b_trans (weights [out, in]), else stored [K, N].
+  GN_TRY(split_operand(g.B, g.ldb, g.N, g.K, g.b_trans == 0, g.b_static != 0, 1, b, s));
+  TcEpilogue ep{g.C, g.ldc, g.aux, g.ldaux, g.epilogue, g.scalar};
+  return launch_tc<128, 3>(a, b, ep, g.M, g.N, g.K, s);
+}
+
+// Drops the cached splits of parameter tensors (call after the parameters change).
+void gemm_tcgen05_invalidate() {
+  std::lock_guard<std::mutex> lock(g_mu);
+  cudaDeviceSynchronize();
+  for (auto& kv : g_static) { cudaFree(kv.second.hi); cudaFree(kv.second.lo); }
+  g_static.clear();
+}
+
+// Reads and clears the device-side timeout flag.
+int gemm_tcgen05_check(cudaStream_t s) {
+  if (!g_err_flag) return GN_OK;
+  int flag = 0;
+  GN_CUDA(cudaMemcpyAsync(&flag, g_err_flag, sizeof(int), cudaMemcpyDeviceToHost, s));
+  GN_CUDA(cudaStreamSynchronize(s));
+  if (flag) {
+    cudaMemsetAsync(g_err_flag, 0, sizeof(int), s);
+    set_error("tcgen05 gemm: a bounded mbarrier wait ran out (pipeline stalled)");
+    return GN_ERR_TIMEOUT;
+  }
+  return GN_OK;
+}
+
+}  // namespace gn

@@ -95,6 +95,7 @@ struct gn_model {
   DevBuf tgt_dev, adv_dev, rowloss, loss_dev, in_dev;
   std::map<std::string, float> phase_ms;
   cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
+  bool weights_dirty = true;   // cached tensor-core operand splits of the parameters are stale
 
   float* p(int64_t off) const { return P.f() + off; }
   float* g(int64_t off) const { return G.f() + off; }
@@ -154,6 +155,12 @@ int build_layout(gn_model* m) {
 int enter(gn_model* m) {
   GN_REQUIRE(m && m->ctx, "null model");
   GN_CUDA(cudaSetDevice(m->ctx->device));
+  return GN_OK;
+}
+// Entry of a compute phase: stale operand splits are dropped before the first GEMM.
+int enter_compute(gn_model* m) {
+  GN_TRY(enter(m));
+  if (m->weights_dirty) { gemm_invalidate_static(); m->weights_dirty = false; }
   return GN_OK;
 }
 
@@ -243,7 +250,7 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
     }
     GN_TRY(mix_norm_launch(x_prev, b.X0, m->p(m->off_rho), m->p(m->off_chi), l, Xin, H, rows, d, s));
     // q, k, v projections as one GEMM against [c_q; c_k; c_v]
-    { GemmArgs g; g.A = H; g.lda = d; g.B = m->p(o.qkv); g.ldb = d; g.b_trans = 1; g.C = QKV; g.ldc = W; g.M = (int)rows; g.N = W; g.K = d; GN_TRY(gemm(m, g)); }
+    { GemmArgs g; g.A = H; g.lda = d; g.B = m->p(o.qkv); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = QKV; g.ldc = W; g.M = (int)rows; g.N = W; g.K = d; GN_TRY(gemm(m, g)); }
     QkvPost qp;
     qp.qkv = QKV; qp.H = H; qp.ids = a.ids;
     qp.ve_table = o.has_ve ? m->p(o.ve) : nullptr; qp.ve_gate = o.has_ve ? m->p(o.ve_gate) : nullptr;
@@ -268,14 +275,14 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
       GN_TRY(attention_forward_launch(sh, QKV, QKV + (int64_t)Hq * D, QKV + (int64_t)(Hq + Hkv) * D, O, train ? b.layers[l].LSE : nullptr, s));
     }
     // MID = Xin + O Wo^T
-    { GemmArgs g; g.A = O; g.lda = (int64_t)Hq * D; g.B = m->p(o.proj); g.ldb = (int64_t)Hq * D; g.b_trans = 1; g.C = MID; g.ldc = d; g.M = (int)rows; g.N = d; g.K = Hq * D;
+    { GemmArgs g; g.A = O; g.lda = (int64_t)Hq * D; g.B = m->p(o.proj); g.b_static = 1; g.ldb = (int64_t)Hq * D; g.b_trans = 1; g.C = MID; g.ldc = d; g.M = (int)rows; g.N = d; g.K = Hq * D;
       g.epilogue = EPI_RESIDUAL; g.aux = Xin; g.ldaux = d; GN_TRY(gemm(m, g)); }
     GN_TRY(norm_launch(MID, Mn, rows, d, s));
     // HID = relu(M Wfc^T)^2   (training also keeps the pre-activation)
-    { GemmArgs g; g.A = Mn; g.lda = d; g.B = m->p(o.fc); g.ldb = d; g.b_trans = 1; g.C = HID; g.ldc = 4 * d; g.M = (int)rows; g.N = 4 * d; g.K = d;
+    { GemmArgs g; g.A = Mn; g.lda = d; g.B = m->p(o.fc); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = HID; g.ldc = 4 * d; g.M = (int)rows; g.N = 4 * d; g.K = d;
       g.epilogue = EPI_RELU2; g.aux = U; g.ldaux = 4 * d; GN_TRY(gemm(m, g)); }
     // XOUT = MID + HID Wp^T
-    { GemmArgs g; g.A = HID; g.lda = 4 * d; g.B = m->p(o.mproj); g.ldb = 4 * d; g.b_trans = 1; g.C = XOUT; g.ldc = d; g.M = (int)rows; g.N = d; g.K = 4 * d;
+    { GemmArgs g; g.A = HID; g.lda = 4 * d; g.B = m->p(o.mproj); g.b_static = 1; g.ldb = 4 * d; g.b_trans = 1; g.C = XOUT; g.ldc = d; g.M = (int)rows; g.N = d; g.K = 4 * d;
       g.epilogue = EPI_RESIDUAL; g.aux = MID; g.ldaux = d; GN_TRY(gemm(m, g)); }
     if (l == L / 2) {
       if (train) backout = XOUT;
@@ -288,7 +295,7 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
   const int32_t* sel = nullptr;
   if (a.mode == MODE_PREFILL) { lrows = B; sel = m->sel.i(); }
   GN_TRY(backout_norm_launch(x_prev, backout, m->p(m->off_backout), sel, train ? b.FP : nullptr, b.Y, lrows, d, s));
-  { GemmArgs g; g.A = b.Y; g.lda = d; g.B = m->p(m->off_lm); g.ldb = d; g.b_trans = 1; g.C = b.LOGITS; g.ldc = V; g.M = (int)lrows; g.N = V; g.K = d;
+  { GemmArgs g; g.A = b.Y; g.lda = d; g.B = m->p(m->off_lm); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = b.LOGITS; g.ldc = V; g.M = (int)lrows; g.N = V; g.K = d;
     g.epilogue = EPI_SOFTCAP; g.scalar = kSoftcap; GN_TRY(gemm(m, g)); }
   return GN_OK;
 }
@@ -322,7 +329,7 @@ int backward_core(gn_model* m, FwdBufs& b, BwdBufs& w, const int32_t* ids, int B
   // lm_head: dW[:V] += dz^T y ; dy = dz W[:V]      (model/layers/linear.go:45-53)
   { GemmArgs g; g.A = DZ; g.lda = V; g.a_trans = 1; g.B = b.Y; g.ldb = d; g.b_trans = 0; g.C = m->g(m->off_lm); g.ldc = d; g.M = V; g.N = d; g.K = (int)rows;
     g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
-  { GemmArgs g; g.A = DZ; g.lda = V; g.B = m->p(m->off_lm); g.ldb = d; g.b_trans = 0; g.C = w.DY; g.ldc = d; g.M = (int)rows; g.N = d; g.K = V; GN_TRY(gemm(m, g)); }
+  { GemmArgs g; g.A = DZ; g.lda = V; g.B = m->p(m->off_lm); g.b_static = 1; g.ldb = d; g.b_trans = 0; g.C = w.DY; g.ldc = d; g.M = (int)rows; g.N = d; g.K = V; GN_TRY(gemm(m, g)); }
   GN_TRY(rmsnorm_backward_launch(w.DFP, b.FP, w.DY, nullptr, rows, d, kNormEps, s));
   const float* backout = b.layers[L / 2].XOUT;
   GN_TRY(dot_accumulate_launch(w.DFP, backout, n, -1.0, sacc + 2 * L + 1, s));   // d lambda_b (train_transformer.go:181-190)
@@ -340,16 +347,16 @@ int backward_core(gn_model* m, FwdBufs& b, BwdBufs& w, const int32_t* ids, int B
     // ---- MLP backward (model/train.go:505-514)
     { GemmArgs g; g.A = dout; g.lda = d; g.a_trans = 1; g.B = sv.HID; g.ldb = 4 * d; g.C = m->g(o.mproj); g.ldc = 4 * d; g.M = d; g.N = 4 * d; g.K = (int)rows;
       g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
-    { GemmArgs g; g.A = dout; g.lda = d; g.B = m->p(o.mproj); g.ldb = 4 * d; g.C = w.DU; g.ldc = 4 * d; g.M = (int)rows; g.N = 4 * d; g.K = d;
+    { GemmArgs g; g.A = dout; g.lda = d; g.B = m->p(o.mproj); g.b_static = 1; g.ldb = 4 * d; g.C = w.DU; g.ldc = 4 * d; g.M = (int)rows; g.N = 4 * d; g.K = d;
       g.epilogue = EPI_RELU2_BWD; g.aux = sv.U; g.ldaux = 4 * d; GN_TRY(gemm(m, g)); }
     { GemmArgs g; g.A = w.DU; g.lda = 4 * d; g.a_trans = 1; g.B = sv.M; g.ldb = d; g.C = m->g(o.fc); g.ldc = d; g.M = 4 * d; g.N = d; g.K = (int)rows;
       g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
-    { GemmArgs g; g.A = w.DU; g.lda = 4 * d; g.B = m->p(o.fc); g.ldb = d; g.C = w.DM; g.ldc = d; g.M = (int)rows; g.N = d; g.K = 4 * d; GN_TRY(gemm(m, g)); }
+    { GemmArgs g; g.A = w.DU; g.lda = 4 * d; g.B = m->p(o.fc); g.b_static = 1; g.ldb = d; g.C = w.DM; g.ldc = d; g.M = (int)rows; g.N = d; g.K = 4 * d; GN_TRY(gemm(m, g)); }
     GN_TRY(rmsnorm_backward_launch(w.DMID, sv.MID, w.DM, dout, rows, d, kNormEps, s));
     // ---- attention backward (model/train.go:198-427)
     { GemmArgs g; g.A = w.DMID; g.lda = d; g.a_trans = 1; g.B = sv.O; g.ldb = (int64_t)Hq * D; g.C = m->g(o.proj); g.ldc = (int64_t)Hq * D; g.M = d; g.N = Hq * D; g.K = (int)rows;
       g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
-    { GemmArgs g; g.A = w.DMID; g.lda = d; g.B = m->p(o.proj); g.ldb = (int64_t)Hq * D; g.C = w.DO; g.ldc = (int64_t)Hq * D; g.M = (int)rows; g.N = Hq * D; g.K = d; GN_TRY(gemm(m, g)); }
+    { GemmArgs g; g.A = w.DMID; g.lda = d; g.B = m->p(o.proj); g.b_static = 1; g.ldb = (int64_t)Hq * D; g.C = w.DO; g.ldc = (int64_t)Hq * D; g.M = (int)rows; g.N = Hq * D; g.K = d; GN_TRY(gemm(m, g)); }
     AttnShape sh;
     sh.B = B; sh.Hq = Hq; sh.Hkv = Hkv; sh.D = D; sh.Tq = T; sh.Tk = T;
     sh.q_bstride = (int64_t)T * W; sh.q_tstride = W; sh.kv_bstride = (int64_t)T * W; sh.kv_tstride = W; sh.kv_hstride = D;
@@ -363,7 +370,7 @@ int backward_core(gn_model* m, FwdBufs& b, BwdBufs& w, const int32_t* ids, int B
     GN_TRY(qkv_post_backward_launch(qb, s));
     { GemmArgs g; g.A = w.DQKV; g.lda = W; g.a_trans = 1; g.B = sv.H; g.ldb = d; g.C = m->g(o.qkv); g.ldc = d; g.M = W; g.N = d; g.K = (int)rows;
       g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
-    { GemmArgs g; g.A = w.DQKV; g.lda = W; g.B = m->p(o.qkv); g.ldb = d; g.C = w.DH; g.ldc = d; g.M = (int)rows; g.N = d; g.K = W; GN_TRY(gemm(m, g)); }
+    { GemmArgs g; g.A = w.DQKV; g.lda = W; g.B = m->p(o.qkv); g.b_static = 1; g.ldb = d; g.C = w.DH; g.ldc = d; g.M = (int)rows; g.N = d; g.K = W; GN_TRY(gemm(m, g)); }
     if (o.has_ve) GN_TRY(ve_gate_backward_launch(w.DPRE, sv.H, m->p(o.ve_gate), m->g(o.ve_gate), w.DH, rows, Hkv, d, s));
     GN_TRY(rmsnorm_backward_launch(w.DXIN, sv.Xin, w.DH, w.DMID, rows, d, kNormEps, s));
     // ---- residual mix (model/train_transformer.go:218-242)
@@ -458,6 +465,7 @@ int gn_model_destroy(gn_model* m) {
   if (!m) return GN_OK;
   cudaSetDevice(m->ctx->device);
   cudaStreamSynchronize(m->ctx->stream);
+  gemm_invalidate_static();   // cached splits are keyed by addresses that are about to be freed
   DevBuf* bufs[] = {&m->P, &m->G, &m->cosb, &m->sinb, &m->sacc, &m->cache, &m->prev, &m->pos, &m->ctxlen, &m->ids_dev, &m->sampled, &m->seeds,
                     &m->out_tokens, &m->out_lengths, &m->done, &m->n_done, &m->sel, &m->part_acc, &m->part_ms, &m->infer.buf, &m->train.buf,
                     &m->tgt_dev, &m->adv_dev, &m->rowloss, &m->loss_dev, &m->in_dev};
@@ -488,6 +496,7 @@ int gn_model_upload(gn_model* m, const char* name, const float* host, int64_t n)
   const ParamInfo* pi; GN_TRY(find_param(m, name, n, &pi)); GN_TRY(enter(m));
   GN_CUDA(cudaMemcpyAsync(m->p(pi->offset), host, sizeof(float) * n, cudaMemcpyHostToDevice, m->s()));
   GN_CUDA(cudaStreamSynchronize(m->s()));
+  m->weights_dirty = true;
   return GN_OK;
 }
 int gn_model_download(gn_model* m, const char* name, float* host, int64_t n) {
@@ -524,7 +533,7 @@ int gn_model_checksum(gn_model* m, double* psum, double* gsum) {
 }
 
 int gn_model_forward(gn_model* m, const int32_t* ids, int B, int T, float* logits) {
-  GN_TRY(enter(m));
+  GN_TRY(enter_compute(m));
   GN_REQUIRE(ids && logits && B > 0 && T > 1, "gn_model_forward needs ids, logits, batch > 0 and seq > 1");
   GN_REQUIRE(T <= m->cfg.sequence_len, "sequence %d longer than the rotary cache (%d)", T, m->cfg.sequence_len);
   const int64_t rows = (int64_t)B * T;
@@ -536,12 +545,12 @@ int gn_model_forward(gn_model* m, const int32_t* ids, int B, int T, float* logit
   GN_TRY(forward_core(m, b, a));
   GN_CUDA(cudaMemcpyAsync(logits, b.LOGITS, sizeof(float) * rows * m->V, cudaMemcpyDeviceToHost, m->s()));
   GN_CUDA(cudaStreamSynchronize(m->s()));
-  return GN_OK;
+  return gemm_check_error(m->s());
 }
 
 int gn_generate_batch(gn_model* m, const int32_t* prompts, int P, int plen, int G, int max_tokens, float temperature, int top_k, const uint64_t* seeds,
                       int32_t* out_tokens, int32_t* out_lengths, float* step_logits, int* steps_run) {
-  GN_TRY(enter(m));
+  GN_TRY(enter_compute(m));
   GN_REQUIRE(prompts && seeds && out_tokens && out_lengths, "gn_generate_batch: null argument");
   GN_REQUIRE(P > 0 && plen > 0 && G > 0 && max_tokens > 0, "gn_generate_batch: sizes must be positive");
   GN_REQUIRE(plen <= m->cfg.sequence_len, "prompt of %d tokens longer than sequence_len %d", plen, m->cfg.sequence_len);
@@ -625,12 +634,12 @@ int gn_generate_batch(gn_model* m, const int32_t* prompts, int P, int plen, int 
   GN_CUDA(cudaEventElapsedTime(&ms, m->ev[0], m->ev[1])); m->phase_ms["prefill"] = ms;
   GN_CUDA(cudaEventElapsedTime(&ms, m->ev[1], m->ev[2])); m->phase_ms["decode"] = ms;
   if (steps_run) *steps_run = generated;
-  return GN_OK;
+  return gemm_check_error(s);
 }
 
 int gn_policy_gradient_step(gn_model* m, const int32_t* inputs, const int32_t* targets, const float* adv, int B, int T, float norm, int rows_per_pass,
                             float* loss, float* nll_tap, float* dlogits_tap, float* logits_tap) {
-  GN_TRY(enter(m));
+  GN_TRY(enter_compute(m));
   GN_REQUIRE(inputs && targets && adv && loss, "gn_policy_gradient_step: null argument");
   GN_REQUIRE(B > 0 && T > 1, "gn_policy_gradient_step: batch must be positive and seq > 1 (model/transformer.go:269-271)");
   GN_REQUIRE(T <= m->cfg.sequence_len, "sequence %d longer than sequence_len %d", T, m->cfg.sequence_len);
@@ -692,7 +701,7 @@ int gn_policy_gradient_step(gn_model* m, const int32_t* inputs, const int32_t* t
   GN_CUDA(cudaStreamSynchronize(s));
   *loss = (float)loss_host;
   m->phase_ms["train_forward"] = t_fwd; m->phase_ms["loss"] = t_loss; m->phase_ms["train_backward"] = t_bwd;
-  return GN_OK;
+  return gemm_check_error(s);
 }
 
 int gn_model_phase_ms(gn_model* m, const char* phase, float* ms) {

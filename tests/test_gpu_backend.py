@@ -202,3 +202,20 @@ def test_grouped_matmul_parity(oracle, bk, ref):
     inp = oracle.kt_data(int(counts.sum()) * inner); w = oracle.kt_data_b(experts * cols * inner)
     close(oracle, bk.grouped_matmul_transposed(inp, w, counts, experts, cols, inner),
           ref.grouped_matmul_transposed(inp, w, counts, experts, cols, inner), 2e-3, 1e-4)
+
+
+# The tensor-core path (tcgen05, 3xTF32) serves the large aligned products; these shapes reach it
+# through the same entry points, tails included, and must stay float32-faithful.
+@pytest.mark.parametrize("rows,cols,inner", [(128, 128, 32), (128, 128, 256), (256, 384, 768), (200, 264, 768), (130, 70, 100), (1000, 3072, 768),
+                                             (512, 768, 3072)])
+def test_tensor_core_matmul_faithful(oracle, bk, ref, rows, cols, inner):
+    rng = np.random.default_rng(rows * 7 + cols)
+    left = rng.standard_normal(rows * inner).astype(np.float32)
+    rt = rng.standard_normal(cols * inner).astype(np.float32)
+    want = ref.matmul_transposed(left, rt, rows, cols, inner)
+    got = bk.matmul_transposed(left, rt, rows, cols, inner)
+    assert np.max(np.abs(got - want)) <= 2e-5 * np.max(np.abs(want))
+    right = rng.standard_normal(inner * cols).astype(np.float32)      # stored [inner, cols]: the transposing operand split
+    want = ref.matmul(left, right, rows, cols, inner)
+    got = bk.matmul(left, right, rows, cols, inner)
+    assert np.max(np.abs(got - want)) <= 2e-5 * np.max(np.abs(want))
