@@ -40,6 +40,7 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
     defines = []
     if (CSRC / "gemm_tcgen05.cu").exists():
         defines.append("-DGN_HAVE_TCGEN05")
+    defines += os.environ.get("GN_EXTRA_NVCC_FLAGS", "").split()   # e.g. -DGN_TC_TRACE for the pipeline timeline
 
     def compile_one(src: Path):
         obj = OBJ / (src.stem + ".o")

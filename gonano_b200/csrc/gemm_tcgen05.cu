@@ -67,7 +67,7 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_test(bar, parity)) return true;
-    if (i > 64) __nanosleep(64);
+    if (i > 4096) __nanosleep(64);
   }
   return false;
 }
@@ -133,17 +133,27 @@ struct TcEpilogue {
   float* C; int64_t ldc;
   float* aux; int64_t ldaux;
   int epi; float scalar;
+  long long* trace;   // timeline of CTA (0,0) in SM cycles when the library is built with GN_TC_TRACE, else unused
 };
 
-__device__ __forceinline__ float epi_value(const TcEpilogue& e, float acc, int64_t m, int n, float cold, bool& write_aux, float& auxv) {
+#ifdef GN_TC_TRACE
+#define TC_TRACE(slot) do { if (ep.trace && blockIdx.x == 0 && blockIdx.y == 0) ep.trace[(slot)] = clock64(); } while (0)
+#else
+#define TC_TRACE(slot) do { } while (0)
+#endif
+// trace slots: [0,256) producer issue per k-block, [256,512) MMA saw the stage full, [512,768) MMA issued,
+// [768,832) epilogue saw chunk full, [832,896) epilogue drained chunk, 896 start, 897 end
+
+// aux_in: the value of the aux operand at this element (residual / saved pre-activation).
+__device__ __forceinline__ float epi_value(const TcEpilogue& e, float acc, float aux_in, float cold, bool& write_aux, float& auxv) {
   write_aux = false;
   switch (e.epi) {
     case EPI_STORE: return acc;
     case EPI_ACCUM: return cold + acc;
-    case EPI_RESIDUAL: return e.aux[m * e.ldaux + n] + acc;
+    case EPI_RESIDUAL: return aux_in + acc;
     case EPI_RELU2: { write_aux = e.aux != nullptr; auxv = acc; float r = acc < 0.0f ? 0.0f : acc; return r * r; }
     case EPI_SOFTCAP: return e.scalar * tanhf(acc * (1.0f / e.scalar));
-    case EPI_RELU2_BWD: { float u = e.aux[m * e.ldaux + n]; return u > 0.0f ? acc * 2.0f * u : 0.0f; }
+    case EPI_RELU2_BWD: return aux_in > 0.0f ? acc * 2.0f * aux_in : 0.0f;
   }
   return acc;
 }
@@ -155,6 +165,7 @@ __device__ __forceinline__ float epi_value(const TcEpilogue& e, float acc, int64
 // buffers and the epilogue warps add the finished chunk into float32 registers with
 // round-to-nearest while the next chunk is being multiplied.
 constexpr int kChunkBlocks = 4;   // 4 x 32 = 128 elements of K per chunk
+constexpr int kStagePitch = 132;  // floats per staged output row (128 + 4: conflict-free float4 rows)
 
 template <int BN, int STAGES>
 struct TcSmem {
@@ -201,6 +212,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
   bool failed = false;
+  if (threadIdx.x == 0) TC_TRACE(896);
 
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer
@@ -210,6 +222,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
         const uint32_t round = (uint32_t)(kb / STAGES);
         if (kb >= STAGES && !mbar_wait(empty_bar(s), (round - 1) & 1u)) { failed = true; break; }
         const uint32_t st = base + (uint32_t)s * S::STAGE_BYTES;
+        if (kb < 256) TC_TRACE(kb);
         mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
         tma_load_2d(st, &tmAh, full_bar(s), kb * TBK, m0);
         tma_load_2d(st + S::A_BYTES, &tmAl, full_bar(s), kb * TBK, m0);
@@ -232,6 +245,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
           const int s = kb % STAGES;
           if (!mbar_wait(full_bar(s), (uint32_t)(kb / STAGES) & 1u)) { failed = true; break; }
           tc_fence_after();
+          if (kb < 256) TC_TRACE(256 + kb);
           const uint32_t st = base + (uint32_t)s * S::STAGE_BYTES;
           const uint64_t ah = smem_desc_sw128(st), al = smem_desc_sw128(st + S::A_BYTES);
           const uint64_t bh = smem_desc_sw128(st + 2 * S::A_BYTES), bl = smem_desc_sw128(st + 2 * S::A_BYTES + S::B_BYTES);
@@ -244,6 +258,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
             umma_tf32(d_tmem, ah + adv, bh + adv, idesc, 1u);
           }
           umma_commit(empty_bar(s));   // the stage is free once these MMAs have read it
+          if (kb < 256) TC_TRACE(512 + kb);
         }
         if (!failed) umma_commit(acc_full(buf));   // this chunk's partial sums are complete
       }
@@ -258,6 +273,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
       const int buf = c & 1;
       if (!mbar_wait(acc_full(buf), (uint32_t)(c / 2) & 1u)) { failed = true; break; }
       tc_fence_after();
+      if (warp == 2 && lane == 0 && c < 64) TC_TRACE(768 + c);
 #pragma unroll
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
@@ -269,23 +285,39 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
       tc_fence_before();
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(buf)) : "memory");
+      if (warp == 2 && lane == 0 && c < 64) TC_TRACE(832 + c);
     }
     if (!failed) {
-      const int64_t m = (int64_t)m0 + quarter * 32 + lane;
+      // The accumulator row of a thread is scattered (thread = row), so it goes through shared
+      // memory first: the pipeline stages are idle once the last chunk has been drained, and
+      // each warp then writes whole 512-byte row segments (a thread-per-row store pattern was
+      // measured at 3.5x the cost of the entire K loop).
+      float* stg = reinterpret_cast<float*>(gen_base) + (size_t)quarter * 32 * kStagePitch;
+#pragma unroll
+      for (int j = 0; j < BN; j += 4) *reinterpret_cast<float4*>(&stg[lane * kStagePitch + j]) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+      __syncwarp();
       const bool vec_ok = (ep.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.C) & 15) == 0) &&
                           (ep.aux == nullptr || ((ep.ldaux % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.aux) & 15) == 0)));
-      if (m < M) {
-        float* crow = ep.C + m * ep.ldc;
-#pragma unroll
-        for (int j = 0; j < BN; j += 4) {
-          const int n = n0 + j;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 128) {
+        const int n = n0 + c0 + lane * 4;
+#pragma unroll 4
+        for (int r = 0; r < 32; ++r) {
+          const int64_t m = (int64_t)m0 + quarter * 32 + r;
+          if (m >= M) break;
+          const float4 v4 = *reinterpret_cast<const float4*>(&stg[r * kStagePitch + c0 + lane * 4]);
+          const float v[4] = {v4.x, v4.y, v4.z, v4.w};
+          float* crow = ep.C + m * ep.ldc;
           if (vec_ok && n + 4 <= N) {
             float4 cold = make_float4(0, 0, 0, 0);
             if (ep.epi == EPI_ACCUM) cold = *reinterpret_cast<const float4*>(crow + n);
-            float co[4] = {cold.x, cold.y, cold.z, cold.w}, out[4], av[4];
+            float4 a4 = make_float4(0, 0, 0, 0);
+            if (ep.epi == EPI_RESIDUAL || ep.epi == EPI_RELU2_BWD) a4 = *reinterpret_cast<const float4*>(ep.aux + m * ep.ldaux + n);
+            const float co[4] = {cold.x, cold.y, cold.z, cold.w}, ax[4] = {a4.x, a4.y, a4.z, a4.w};
+            float out[4], av[4];
             bool wa = false;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) out[e] = epi_value(ep, acc[j + e], m, n + e, co[e], wa, av[e]);
+            for (int e = 0; e < 4; ++e) out[e] = epi_value(ep, v[e], ax[e], co[e], wa, av[e]);
             if (wa) *reinterpret_cast<float4*>(ep.aux + m * ep.ldaux + n) = make_float4(av[0], av[1], av[2], av[3]);
             *reinterpret_cast<float4*>(crow + n) = make_float4(out[0], out[1], out[2], out[3]);
           } else {
@@ -293,8 +325,9 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
             for (int e = 0; e < 4; ++e) {
               if (n + e < N) {
                 bool wa = false; float av = 0.0f;
-                float cold = (ep.epi == EPI_ACCUM) ? crow[n + e] : 0.0f;
-                float out = epi_value(ep, acc[j + e], m, n + e, cold, wa, av);
+                const float cold = (ep.epi == EPI_ACCUM) ? crow[n + e] : 0.0f;
+                const float ax = (ep.epi == EPI_RESIDUAL || ep.epi == EPI_RELU2_BWD) ? ep.aux[m * ep.ldaux + n + e] : 0.0f;
+                const float out = epi_value(ep, v[e], ax, cold, wa, av);
                 if (wa) ep.aux[m * ep.ldaux + n + e] = av;
                 crow[n + e] = out;
               }
@@ -311,6 +344,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
   }
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) TC_TRACE(897);
   if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
 }
 
@@ -363,6 +397,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
 int* g_err_flag = nullptr;
+long long* g_trace = nullptr;   // device buffer of 1024 slots (GN_TC_TRACE builds)
 std::mutex g_mu;
 
 struct SplitBuf { float* hi = nullptr; float* lo = nullptr; size_t floats = 0; int64_t ld = 0; };
@@ -468,7 +503,7 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
   GN_TRY(split_operand(g.A, g.lda, g.M, g.K, g.a_trans != 0, g.a_static != 0, 0, a, s));
   // B is logically [N, K]; stored that way when b_trans (weights [out, in]), else stored [K, N].
   GN_TRY(split_operand(g.B, g.ldb, g.N, g.K, g.b_trans == 0, g.b_static != 0, 1, b, s));
-  TcEpilogue ep{g.C, g.ldc, g.aux, g.ldaux, g.epilogue, g.scalar};
+  TcEpilogue ep{g.C, g.ldc, g.aux, g.ldaux, g.epilogue, g.scalar, g_trace};
   return launch_tc<128, 3>(a, b, ep, g.M, g.N, g.K, s);
 }
 
@@ -479,6 +514,20 @@ void gemm_tcgen05_invalidate() {
   for (auto& kv : g_static) { cudaFree(kv.second.hi); cudaFree(kv.second.lo); }
   g_static.clear();
 }
+
+#ifdef GN_TC_TRACE
+// Development aid: the next products record CTA (0,0)'s timeline; returns it (1024 slots).
+extern "C" int gn_debug_gemm_trace(long long* host_out, int arm) {
+  if (arm) {
+    if (!g_trace) GN_CUDA(cudaMalloc((void**)&g_trace, 1024 * sizeof(long long)));
+    GN_CUDA(cudaMemset(g_trace, 0, 1024 * sizeof(long long)));
+    return GN_OK;
+  }
+  GN_CUDA(cudaDeviceSynchronize());
+  if (g_trace && host_out) GN_CUDA(cudaMemcpy(host_out, g_trace, 1024 * sizeof(long long), cudaMemcpyDeviceToHost));
+  return GN_OK;
+}
+#endif
 
 // Reads and clears the device-side timeout flag.
 int gemm_tcgen05_check(cudaStream_t s) {
