@@ -160,6 +160,24 @@ int gn_group_advantage(const float* rewards, int groups, int group, int mode, fl
 int gn_pg_loss_backward(const float* logits, const int32_t* targets, const float* advantages, int64_t rows, int vocab,
                         int seq_len, float norm, float softcap, float* nll, float* dlogits, double* loss);
 
+/* gn_pg_loss_backward for callers that must not allocate.  No counterpart in the reference:
+ * it exists for hosts that own all device memory themselves (a process whose own arena spans
+ * the GPU, a loop that cannot afford cudaMalloc's device-wide synchronisation or a late
+ * out-of-memory failure).  The per-row scratch lives in a fixed array inside the library, so
+ * the call makes no allocation at all.  Consequences:
+ *   - at most GN_STATIC_LOSS_MAX_ROWS rows per call (more is refused with GN_ERR_INVALID);
+ *   - logits, targets, advantages, nll and dlogits must be device pointers (no host staging);
+ *     loss may be host or device; stream is a cudaStream_t (NULL = default stream); the call
+ *     returns after the loss has been written;
+ *   - the array is shared by every call on a GPU and keeps the last call's values: what must
+ *     start at zero is cleared per call, and calls that overlap on one GPU race - serialise them;
+ *   - the first call on each device looks up the array's device address; make that call at
+ *     start-up, before any stream capture. */
+#define GN_STATIC_LOSS_MAX_ROWS 65536
+int gn_pg_loss_backward_static(const float* logits, const int32_t* targets, const float* advantages, int64_t rows,
+                               int vocab, int seq_len, float norm, float softcap, float* nll, float* dlogits,
+                               double* loss, void* stream);
+
 /* ===================================================================== *
  * Tier B - resident session                                             *
  * ===================================================================== */
