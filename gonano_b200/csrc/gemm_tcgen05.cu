@@ -133,6 +133,7 @@ struct TcEpilogue {
   float* C; int64_t ldc;
   float* aux; int64_t ldaux;
   int epi; float scalar;
+  int64_t split_stride;   // split-K: floats between the partial tiles of consecutive splits
   long long* trace;   // timeline of CTA (0,0) in SM cycles when the library is built with GN_TC_TRACE, else unused
 };
 
@@ -165,7 +166,6 @@ __device__ __forceinline__ float epi_value(const TcEpilogue& e, float acc, float
 // buffers and the epilogue warps add the finished chunk into float32 registers with
 // round-to-nearest while the next chunk is being multiplied.
 constexpr int kChunkBlocks = 4;   // 4 x 32 = 128 elements of K per chunk
-constexpr int kStagePitch = 132;  // floats per staged output row (128 + 4: conflict-free float4 rows)
 
 template <int BN, int STAGES>
 struct TcSmem {
@@ -195,8 +195,13 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * TBM, n0 = blockIdx.x * BN;
-  const int nk = (K + TBK - 1) / TBK;
+  // split-K: CTA z works on k-blocks [kb0, kb0 + nk) and writes a partial tile
+  const int nk_total = (K + TBK - 1) / TBK;
+  const int per_split = (nk_total + (int)gridDim.z - 1) / (int)gridDim.z;
+  const int kb0 = (int)blockIdx.z * per_split;
+  const int nk = max(0, min(per_split, nk_total - kb0));
   const int nchunks = (nk + kChunkBlocks - 1) / kChunkBlocks;
+  if (gridDim.z > 1) ep.C += (int64_t)blockIdx.z * ep.split_stride;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -224,10 +229,10 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
         const uint32_t st = base + (uint32_t)s * S::STAGE_BYTES;
         if (kb < 256) TC_TRACE(kb);
         mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
-        tma_load_2d(st, &tmAh, full_bar(s), kb * TBK, m0);
-        tma_load_2d(st + S::A_BYTES, &tmAl, full_bar(s), kb * TBK, m0);
-        tma_load_2d(st + 2 * S::A_BYTES, &tmBh, full_bar(s), kb * TBK, n0);
-        tma_load_2d(st + 2 * S::A_BYTES + S::B_BYTES, &tmBl, full_bar(s), kb * TBK, n0);
+        tma_load_2d(st, &tmAh, full_bar(s), (kb0 + kb) * TBK, m0);
+        tma_load_2d(st + S::A_BYTES, &tmAl, full_bar(s), (kb0 + kb) * TBK, m0);
+        tma_load_2d(st + 2 * S::A_BYTES, &tmBh, full_bar(s), (kb0 + kb) * TBK, n0);
+        tma_load_2d(st + 2 * S::A_BYTES + S::B_BYTES, &tmBl, full_bar(s), (kb0 + kb) * TBK, n0);
       }
     }
   } else if (warp == 1) {
@@ -292,45 +297,47 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
       // memory first: the pipeline stages are idle once the last chunk has been drained, and
       // each warp then writes whole 512-byte row segments (a thread-per-row store pattern was
       // measured at 3.5x the cost of the entire K loop).
-      float* stg = reinterpret_cast<float*>(gen_base) + (size_t)quarter * 32 * kStagePitch;
+      constexpr int PITCH = BN + 4;            // floats per staged row: conflict-free float4 rows
+      constexpr int LPR = BN / 4;              // lanes that cover one row with float4
+      constexpr int RPI = 32 / LPR;            // rows a warp writes per iteration
+      float* stg = reinterpret_cast<float*>(gen_base) + (size_t)quarter * 32 * PITCH;
 #pragma unroll
-      for (int j = 0; j < BN; j += 4) *reinterpret_cast<float4*>(&stg[lane * kStagePitch + j]) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+      for (int j = 0; j < BN; j += 4) *reinterpret_cast<float4*>(&stg[lane * PITCH + j]) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
       __syncwarp();
       const bool vec_ok = (ep.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.C) & 15) == 0) &&
                           (ep.aux == nullptr || ((ep.ldaux % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.aux) & 15) == 0)));
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 128) {
-        const int n = n0 + c0 + lane * 4;
+      const int col = (lane % LPR) * 4;
+      const int n = n0 + col;
 #pragma unroll 4
-        for (int r = 0; r < 32; ++r) {
-          const int64_t m = (int64_t)m0 + quarter * 32 + r;
-          if (m >= M) break;
-          const float4 v4 = *reinterpret_cast<const float4*>(&stg[r * kStagePitch + c0 + lane * 4]);
-          const float v[4] = {v4.x, v4.y, v4.z, v4.w};
-          float* crow = ep.C + m * ep.ldc;
-          if (vec_ok && n + 4 <= N) {
-            float4 cold = make_float4(0, 0, 0, 0);
-            if (ep.epi == EPI_ACCUM) cold = *reinterpret_cast<const float4*>(crow + n);
-            float4 a4 = make_float4(0, 0, 0, 0);
-            if (ep.epi == EPI_RESIDUAL || ep.epi == EPI_RELU2_BWD) a4 = *reinterpret_cast<const float4*>(ep.aux + m * ep.ldaux + n);
-            const float co[4] = {cold.x, cold.y, cold.z, cold.w}, ax[4] = {a4.x, a4.y, a4.z, a4.w};
-            float out[4], av[4];
-            bool wa = false;
+      for (int r0 = 0; r0 < 32; r0 += RPI) {
+        const int r = r0 + lane / LPR;
+        const int64_t m = (int64_t)m0 + quarter * 32 + r;
+        if (m >= M) continue;
+        const float4 v4 = *reinterpret_cast<const float4*>(&stg[r * PITCH + col]);
+        const float v[4] = {v4.x, v4.y, v4.z, v4.w};
+        float* crow = ep.C + m * ep.ldc;
+        if (vec_ok && n + 4 <= N) {
+          float4 cold = make_float4(0, 0, 0, 0);
+          if (ep.epi == EPI_ACCUM) cold = *reinterpret_cast<const float4*>(crow + n);
+          float4 a4 = make_float4(0, 0, 0, 0);
+          if (ep.epi == EPI_RESIDUAL || ep.epi == EPI_RELU2_BWD) a4 = *reinterpret_cast<const float4*>(ep.aux + m * ep.ldaux + n);
+          const float co[4] = {cold.x, cold.y, cold.z, cold.w}, ax[4] = {a4.x, a4.y, a4.z, a4.w};
+          float out[4], av[4];
+          bool wa = false;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) out[e] = epi_value(ep, v[e], ax[e], co[e], wa, av[e]);
-            if (wa) *reinterpret_cast<float4*>(ep.aux + m * ep.ldaux + n) = make_float4(av[0], av[1], av[2], av[3]);
-            *reinterpret_cast<float4*>(crow + n) = make_float4(out[0], out[1], out[2], out[3]);
-          } else {
+          for (int e = 0; e < 4; ++e) out[e] = epi_value(ep, v[e], ax[e], co[e], wa, av[e]);
+          if (wa) *reinterpret_cast<float4*>(ep.aux + m * ep.ldaux + n) = make_float4(av[0], av[1], av[2], av[3]);
+          *reinterpret_cast<float4*>(crow + n) = make_float4(out[0], out[1], out[2], out[3]);
+        } else {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              if (n + e < N) {
-                bool wa = false; float av = 0.0f;
-                const float cold = (ep.epi == EPI_ACCUM) ? crow[n + e] : 0.0f;
-                const float ax = (ep.epi == EPI_RESIDUAL || ep.epi == EPI_RELU2_BWD) ? ep.aux[m * ep.ldaux + n + e] : 0.0f;
-                const float out = epi_value(ep, v[e], ax, cold, wa, av);
-                if (wa) ep.aux[m * ep.ldaux + n + e] = av;
-                crow[n + e] = out;
-              }
+          for (int e = 0; e < 4; ++e) {
+            if (n + e < N) {
+              bool wa = false; float av = 0.0f;
+              const float cold = (ep.epi == EPI_ACCUM) ? crow[n + e] : 0.0f;
+              const float ax = (ep.epi == EPI_RESIDUAL || ep.epi == EPI_RELU2_BWD) ? ep.aux[m * ep.ldaux + n + e] : 0.0f;
+              const float out = epi_value(ep, v[e], ax, cold, wa, av);
+              if (wa) ep.aux[m * ep.ldaux + n + e] = av;
+              crow[n + e] = out;
             }
           }
         }
@@ -465,8 +472,36 @@ int split_operand(const float* src, int64_t ld, int64_t rows, int64_t k, bool st
   return GN_OK;
 }
 
+// Split-K second pass: C = epilogue(sum over splits of the partial tiles), in a fixed order.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, int splits, int64_t split_stride, TcEpilogue ep, int M, int N) {
+  const int nv = N >> 2;   // N is a multiple of 4 on this path
+  const int64_t total = (int64_t)M * nv;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = i / nv; const int n = (int)(i % nv) * 4;
+    float4 acc = *reinterpret_cast<const float4*>(part + m * N + n);
+    for (int z = 1; z < splits; ++z) {
+      const float4 p = *reinterpret_cast<const float4*>(part + (int64_t)z * split_stride + m * N + n);
+      acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+    }
+    float* crow = ep.C + m * ep.ldc + n;
+    const float v[4] = {acc.x, acc.y, acc.z, acc.w};
+    float out[4], av[4]; bool wa = false;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float cold = (ep.epi == EPI_ACCUM) ? crow[e] : 0.0f;
+      const float ax = (ep.epi == EPI_RESIDUAL || ep.epi == EPI_RELU2_BWD) ? ep.aux[m * ep.ldaux + n + e] : 0.0f;
+      out[e] = epi_value(ep, v[e], ax, cold, wa, av[e]);
+    }
+    if (wa) { for (int e = 0; e < 4; ++e) ep.aux[m * ep.ldaux + n + e] = av[e]; }
+    for (int e = 0; e < 4; ++e) crow[e] = out[e];
+  }
+}
+
+float* g_splitk_ws = nullptr;
+size_t g_splitk_floats = 0;
+
 template <int BN, int STAGES>
-int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep, int M, int N, int K, cudaStream_t s) {
+int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int M, int N, int K, int splits, cudaStream_t s) {
   using S = TcSmem<BN, STAGES>;
   static bool configured = false;
   if (!configured) {
@@ -476,9 +511,25 @@ int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep, int M,
   CUtensorMap mah, mal, mbh, mbl;
   GN_TRY(make_map(&mah, a.hi, M, K, a.ld, TBM)); GN_TRY(make_map(&mal, a.lo, M, K, a.ld, TBM));
   GN_TRY(make_map(&mbh, b.hi, N, K, b.ld, BN)); GN_TRY(make_map(&mbl, b.lo, N, K, b.ld, BN));
-  dim3 grid(ceil_div(N, BN), ceil_div(M, TBM));
+  TcEpilogue ep = ep_in;
+  if (splits > 1) {
+    size_t need = (size_t)splits * M * N;
+    if (need > g_splitk_floats) {
+      if (g_splitk_ws) cudaFree(g_splitk_ws);
+      g_splitk_ws = nullptr; g_splitk_floats = 0;
+      if (cudaMalloc((void**)&g_splitk_ws, need * sizeof(float)) != cudaSuccess) { set_error("tcgen05 gemm: cannot allocate the split-K workspace"); return GN_ERR_NOMEM; }
+      g_splitk_floats = need;
+    }
+    ep.C = g_splitk_ws; ep.ldc = N; ep.aux = nullptr; ep.epi = EPI_STORE; ep.split_stride = (int64_t)M * N;
+  }
+  dim3 grid(ceil_div(N, BN), ceil_div(M, TBM), splits);
   gemm_tc_kernel<BN, STAGES><<<grid, 192, S::TOTAL, s>>>(mah, mal, mbh, mbl, ep, M, N, K, g_err_flag);
   GN_LAUNCH_CHECK();
+  if (splits > 1) {
+    int blocks = (int)std::min<int64_t>(((int64_t)M * (N / 4) + 255) / 256, (int64_t)kNumSM * 8);
+    splitk_reduce_kernel<<<blocks, 256, 0, s>>>(g_splitk_ws, splits, (int64_t)M * N, ep_in, M, N);
+    GN_LAUNCH_CHECK();
+  }
   return GN_OK;
 }
 
@@ -503,8 +554,20 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
   GN_TRY(split_operand(g.A, g.lda, g.M, g.K, g.a_trans != 0, g.a_static != 0, 0, a, s));
   // B is logically [N, K]; stored that way when b_trans (weights [out, in]), else stored [K, N].
   GN_TRY(split_operand(g.B, g.ldb, g.N, g.K, g.b_trans == 0, g.b_static != 0, 1, b, s));
-  TcEpilogue ep{g.C, g.ldc, g.aux, g.ldaux, g.epilogue, g.scalar, g_trace};
-  return launch_tc<128, 3>(a, b, ep, g.M, g.N, g.K, s);
+  TcEpilogue ep{g.C, g.ldc, g.aux, g.ldaux, g.epilogue, g.scalar, 0, g_trace};
+  // Filling the machine when the output has few tiles (the rollout's products have 512 rows):
+  // the K loop is split over gridDim.z so that about one CTA per SM runs, each writing a partial
+  // tile that a second pass sums in a fixed order (deterministic, unlike atomics).  Narrow tiles
+  // would also add CTAs but re-read the activation operand once per column tile, and the kernel
+  // is bound by the 64 B/clk/SM path from L2.
+  const int64_t tiles = (int64_t)ceil_div(g.M, TBM) * ceil_div(g.N, 128);
+  const int nk = ceil_div(g.K, TBK);
+  int splits = 1;
+  if (tiles < kNumSM / 2 && g.N % 4 == 0 && g.ldc % 4 == 0) {
+    splits = (int)std::min<int64_t>(kNumSM / tiles, nk / 4);   // at least 4 k-blocks per split
+    if (splits < 1) splits = 1;
+  }
+  return launch_tc<128, 3>(a, b, ep, g.M, g.N, g.K, splits, s);
 }
 
 // Drops the cached splits of parameter tensors (call after the parameters change).
