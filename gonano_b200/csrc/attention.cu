@@ -23,6 +23,12 @@ namespace gn {
 constexpr float kMaskedScore = -1e30f;
 constexpr int AT = 256;  // threads per CTA in the tiled kernels
 
+// head_dim 128 fast path (defined further down)
+static bool fast128_ok(const AttnShape& sh, const void* p0, const void* p1, const void* p2, const void* p3, const void* p4);
+static int attn_fwd128_go(const AttnShape& sh, const float* q, const float* k, const float* v, float* out, float* lse, cudaStream_t s);
+static int attn_bwd128_go(const AttnShape& sh, const float* q, const float* k, const float* v, const float* dout, const float* lse, const float* delta,
+                          float* dq, float* dk, float* dv, int accumulate, cudaStream_t s);
+
 __device__ __forceinline__ bool attn_masked(int qpos, int kj, int window, const int32_t* seg, int seg_len, int32_t qseg) {
   bool m = kj > qpos || (window >= 0 && qpos - kj > window);
   if (!m && seg != nullptr && kj < seg_len && seg[kj] != qseg) m = true;
@@ -36,7 +42,11 @@ __device__ __forceinline__ void mm_acc(float (&acc)[TM][TN], const float* A, int
 #pragma unroll 4
   for (int k = 0; k < K; ++k) {
     float a[TM], b[TN];
-    if (TM == 4) { float4 v = *reinterpret_cast<const float4*>(A + k * lda + m); a[0] = v.x; a[1] = v.y; a[2] = v.z; a[3] = v.w; }
+    if (TM == 8) {
+      float4 v = *reinterpret_cast<const float4*>(A + k * lda + m), w = *reinterpret_cast<const float4*>(A + k * lda + m + 4);
+      a[0] = v.x; a[1] = v.y; a[2] = v.z; a[3] = v.w; a[4 % TM] = w.x; a[5 % TM] = w.y; a[6 % TM] = w.z; a[7 % TM] = w.w;
+    }
+    else if (TM == 4) { float4 v = *reinterpret_cast<const float4*>(A + k * lda + m); a[0] = v.x; a[1] = v.y; a[2] = v.z; a[3] = v.w; }
     else if (TM == 2) { float2 v = *reinterpret_cast<const float2*>(A + k * lda + m); a[0] = v.x; a[1] = v.y; }
     else { for (int i = 0; i < TM; ++i) a[i] = A[k * lda + m + i]; }
     if (TN == 4) { float4 v = *reinterpret_cast<const float4*>(B + k * ldb + n); b[0] = v.x; b[1] = v.y; b[2] = v.z; b[3] = v.w; }
@@ -197,9 +207,353 @@ int attention_forward_launch(const AttnShape& sh, const float* q, const float* k
   if (sh.Tq <= 0 || sh.B <= 0) return GN_OK;
   GN_REQUIRE(sh.D > 0 && sh.D <= 128, "attention: head_dim %d outside (0,128]", sh.D);
   GN_REQUIRE(sh.Hkv > 0 && sh.Hq % sh.Hkv == 0, "attention: %d query heads not divisible by %d kv heads", sh.Hq, sh.Hkv);
+  if (fast128_ok(sh, q, k, v, out, nullptr)) return attn_fwd128_go(sh, q, k, v, out, lse, s);
   if (sh.D <= 32) return attn_fwd_go<32>(sh, q, k, v, out, lse, s);
   if (sh.D <= 64) return attn_fwd_go<64>(sh, q, k, v, out, lse, s);
   return attn_fwd_go<128>(sh, q, k, v, out, lse, s);
+}
+
+// ============================================================== head_dim 128 fast path
+// The model's head width.  Same algorithm as the generic kernels above, retiled so that the
+// inner products are FMA-bound instead of shared-memory-bound: 8x4 / 4x4 register tiles fed by
+// broadcast float4 reads, transposed tiles written with lane = row (conflict-free), and in the
+// backward kernels the probability tiles alias the transposed Q / dO (or V) tiles once those
+// have been consumed, which is what lets 64x64 tiles fit in shared memory.
+constexpr int FD = 128;
+
+// rows of FD floats -> transposed St[c][r]; consecutive lanes take consecutive rows.
+__device__ __forceinline__ void load_rows_T(float* St, int ld, const float* g, int64_t tstride, int nrows, int valid) {
+  for (int idx = threadIdx.x; idx < nrows * (FD / 4); idx += AT) {
+    const int r = idx % nrows, c = (idx / nrows) * 4;
+    float4 v = make_float4(0, 0, 0, 0);
+    if (r < valid) v = *reinterpret_cast<const float4*>(g + (int64_t)r * tstride + c);
+    St[(c + 0) * ld + r] = v.x; St[(c + 1) * ld + r] = v.y; St[(c + 2) * ld + r] = v.z; St[(c + 3) * ld + r] = v.w;
+  }
+}
+// rows of FD floats -> row-major S[r][c], float4 coalesced.
+__device__ __forceinline__ void load_rows(float* S, int ld, const float* g, int64_t tstride, int nrows, int valid) {
+  for (int idx = threadIdx.x; idx < nrows * (FD / 4); idx += AT) {
+    const int r = idx / (FD / 4), c = (idx % (FD / 4)) * 4;
+    float4 v = make_float4(0, 0, 0, 0);
+    if (r < valid) v = *reinterpret_cast<const float4*>(g + (int64_t)r * tstride + c);
+    *reinterpret_cast<float4*>(S + r * ld + c) = v;
+  }
+}
+
+// Forward: CTA = 128 queries of one (batch, head); 64-key tiles.
+__global__ void __launch_bounds__(AT, 1) attn_fwd128_kernel(AttnShape sh, const float* __restrict__ q, const float* __restrict__ k,
+                                                            const float* __restrict__ v, float* __restrict__ out, float* __restrict__ lse) {
+  constexpr int BQ = 128, BKV = 64, LQ = BQ + 4, LK = BKV + 4, LV = FD + 4;
+  extern __shared__ __align__(16) float smem[];
+  float* Qt = smem;               // [FD][LQ]
+  float* Kt = Qt + FD * LQ;       // [FD][LK]
+  float* Vs = Kt + FD * LK;       // [BKV][LV]
+  float* Pt = Vs + BKV * LV;      // [BKV][LQ]
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int bh = blockIdx.y, b = bh / sh.Hq, hq = bh % sh.Hq, hk = hq / (sh.Hq / sh.Hkv);
+  const int q0 = blockIdx.x * BQ, qvalid = min(BQ, sh.Tq - q0), offset = sh.offset0;
+  const float* qg = q + (int64_t)b * sh.q_bstride + (int64_t)q0 * sh.q_tstride + (int64_t)hq * FD;
+  const float* kg = k + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride;
+  const float* vg = v + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride;
+  load_rows_T(Qt, LQ, qg, sh.q_tstride, BQ, qvalid);
+  float m_run[8], l_run[8], o[2][8][4];
+  int32_t qseg[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    m_run[i] = -INFINITY; l_run[i] = 0.0f;
+    const int qpos = offset + q0 + ty * 8 + i;
+    qseg[i] = (sh.segment_ids && qpos < sh.seg_len) ? sh.segment_ids[qpos] : 0;
+#pragma unroll
+    for (int g = 0; g < 2; ++g)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[g][i][j] = 0.0f;
+  }
+  const int max_qpos = offset + q0 + qvalid - 1;
+  const int k_end = min(sh.Tk, max_qpos + 1);
+  int k_begin = 0;
+  if (sh.window >= 0) k_begin = max(0, offset + q0 - sh.window);
+  k_begin = (k_begin / BKV) * BKV;
+  for (int kt = k_begin; kt < k_end; kt += BKV) {
+    const int kvalid = min(BKV, sh.Tk - kt);
+    __syncthreads();
+    load_rows_T(Kt, LK, kg + (int64_t)kt * sh.kv_tstride, sh.kv_tstride, BKV, kvalid);
+    load_rows(Vs, LV, vg + (int64_t)kt * sh.kv_tstride, sh.kv_tstride, BKV, kvalid);
+    __syncthreads();
+    float s[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] = 0.0f;
+    mm_acc<8, 4>(s, Qt, LQ, Kt, LK, FD, ty * 8, tx * 4);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int qpos = offset + q0 + ty * 8 + i;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int kj = kt + tx * 4 + j;
+        if (kj >= sh.Tk) s[i][j] = -INFINITY;
+        else if (attn_masked(qpos, kj, sh.window, sh.segment_ids, sh.seg_len, qseg[i])) s[i][j] = kMaskedScore;
+        mx = fmaxf(mx, s[i][j]);
+      }
+#pragma unroll
+      for (int o2 = 8; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o2));
+      const float m_new = fmaxf(m_run[i], mx);
+      const float alpha = (m_run[i] == -INFINITY) ? 0.0f : __expf(m_run[i] - m_new);
+      float rs = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float p = (s[i][j] == -INFINITY) ? 0.0f : __expf(s[i][j] - m_new); s[i][j] = p; rs += p; }
+#pragma unroll
+      for (int o2 = 8; o2 > 0; o2 >>= 1) rs += __shfl_xor_sync(0xffffffffu, rs, o2);
+      l_run[i] = l_run[i] * alpha + rs;
+      m_run[i] = m_new;
+#pragma unroll
+      for (int g = 0; g < 2; ++g)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[g][i][j] *= alpha;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float* dst = Pt + (tx * 4 + j) * LQ + ty * 8;
+      *reinterpret_cast<float4*>(dst) = make_float4(s[0][j], s[1][j], s[2][j], s[3][j]);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(s[4][j], s[5][j], s[6][j], s[7][j]);
+    }
+    __syncthreads();
+    mm_acc<8, 4>(o[0], Pt, LQ, Vs, LV, BKV, ty * 8, tx * 4);
+    mm_acc<8, 4>(o[1], Pt, LQ, Vs, LV, BKV, ty * 8, 64 + tx * 4);
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int qi = q0 + ty * 8 + i;
+    if (qi >= sh.Tq) continue;
+    const float inv = l_run[i] > 0.0f ? 1.0f / l_run[i] : 0.0f;
+    float* og = out + (int64_t)b * sh.o_bstride + (int64_t)qi * sh.o_tstride + (int64_t)hq * FD;
+#pragma unroll
+    for (int g = 0; g < 2; ++g)
+      *reinterpret_cast<float4*>(og + g * 64 + tx * 4) = make_float4(o[g][i][0] * inv, o[g][i][1] * inv, o[g][i][2] * inv, o[g][i][3] * inv);
+    if (lse && tx == 0) lse[((int64_t)b * sh.Hq + hq) * sh.Tq + qi] = m_run[i] + logf(l_run[i]);
+  }
+}
+
+// dK/dV: CTA = 64 keys of one (batch, kv head); walks the group's query heads and 64-query tiles.
+__global__ void __launch_bounds__(AT, 1) attn_bwd128_dkv_kernel(AttnShape sh, const float* __restrict__ q, const float* __restrict__ k,
+                                                                const float* __restrict__ v, const float* __restrict__ dout,
+                                                                const float* __restrict__ lse, const float* __restrict__ delta,
+                                                                float* __restrict__ dk, float* __restrict__ dv, int accumulate) {
+  constexpr int BQ = 64, BKV = 64, LT = 68, LD = FD + 4;
+  extern __shared__ __align__(16) float smem[];
+  float* Kt = smem;               // [FD][LT]
+  float* Vt = Kt + FD * LT;       // [FD][LT]
+  float* Qt = Vt + FD * LT;       // [FD][LT]   reused as Ps [BQ][LT] once S is formed
+  float* dOt = Qt + FD * LT;      // [FD][LT]   reused as dSs [BQ][LT]
+  float* Qs = dOt + FD * LT;      // [BQ][LD]
+  float* dOs = Qs + BQ * LD;      // [BQ][LD]
+  float* Ps = Qt; float* dSs = dOt;
+  __shared__ float lse_s[BQ], delta_s[BQ];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int bh = blockIdx.y, b = bh / sh.Hkv, hk = bh % sh.Hkv, ratio = sh.Hq / sh.Hkv;
+  const int k0 = blockIdx.x * BKV, kvalid = min(BKV, sh.Tk - k0), offset = sh.offset0;
+  const float* kg = k + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride + (int64_t)k0 * sh.kv_tstride;
+  const float* vg = v + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride + (int64_t)k0 * sh.kv_tstride;
+  load_rows_T(Kt, LT, kg, sh.kv_tstride, BKV, kvalid);
+  load_rows_T(Vt, LT, vg, sh.kv_tstride, BKV, kvalid);
+  float adk[2][4][4], adv[2][4][4];
+#pragma unroll
+  for (int g = 0; g < 2; ++g)
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { adk[g][i][j] = 0.0f; adv[g][i][j] = 0.0f; }
+  int q_begin = max(0, k0 - offset);
+  q_begin = (q_begin / BQ) * BQ;
+  int q_end = sh.Tq;
+  if (sh.window >= 0) q_end = min(sh.Tq, k0 + kvalid - 1 + sh.window - offset + 1);
+  for (int h = 0; h < ratio; ++h) {
+    const int hq = hk * ratio + h;
+    for (int q0 = q_begin; q0 < q_end; q0 += BQ) {
+      const int qvalid = min(BQ, sh.Tq - q0);
+      const float* qg = q + (int64_t)b * sh.q_bstride + (int64_t)q0 * sh.q_tstride + (int64_t)hq * FD;
+      const float* dog = dout + (int64_t)b * sh.o_bstride + (int64_t)q0 * sh.o_tstride + (int64_t)hq * FD;
+      __syncthreads();
+      load_rows_T(Qt, LT, qg, sh.q_tstride, BQ, qvalid);
+      load_rows_T(dOt, LT, dog, sh.o_tstride, BQ, qvalid);
+      load_rows(Qs, LD, qg, sh.q_tstride, BQ, qvalid);
+      load_rows(dOs, LD, dog, sh.o_tstride, BQ, qvalid);
+      if (tid < BQ) {
+        const int qi = q0 + tid;
+        lse_s[tid] = qi < sh.Tq ? lse[((int64_t)b * sh.Hq + hq) * sh.Tq + qi] : 0.0f;
+        delta_s[tid] = qi < sh.Tq ? delta[((int64_t)b * sh.Hq + hq) * sh.Tq + qi] : 0.0f;
+      }
+      __syncthreads();
+      float s[4][4], dp[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { s[i][j] = 0.0f; dp[i][j] = 0.0f; }
+      mm_acc<4, 4>(s, Qt, LT, Kt, LT, FD, ty * 4, tx * 4);
+      mm_acc<4, 4>(dp, dOt, LT, Vt, LT, FD, ty * 4, tx * 4);
+      __syncthreads();   // Qt / dOt are consumed: their memory now holds P and dS
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int il = ty * 4 + i, qi = q0 + il, qpos = offset + qi;
+        const int32_t qseg = (sh.segment_ids && qpos < sh.seg_len) ? sh.segment_ids[qpos] : 0;
+        float pv[4], dsv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int kj = k0 + tx * 4 + j;
+          float p = 0.0f;
+          if (qi < sh.Tq && kj < sh.Tk && !attn_masked(qpos, kj, sh.window, sh.segment_ids, sh.seg_len, qseg)) p = __expf(s[i][j] - lse_s[il]);
+          pv[j] = p; dsv[j] = p * (dp[i][j] - delta_s[il]);
+        }
+        *reinterpret_cast<float4*>(Ps + il * LT + tx * 4) = make_float4(pv[0], pv[1], pv[2], pv[3]);
+        *reinterpret_cast<float4*>(dSs + il * LT + tx * 4) = make_float4(dsv[0], dsv[1], dsv[2], dsv[3]);
+      }
+      __syncthreads();
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        mm_acc<4, 4>(adv[g], Ps, LT, dOs, LD, BQ, ty * 4, g * 64 + tx * 4);
+        mm_acc<4, 4>(adk[g], dSs, LT, Qs, LD, BQ, ty * 4, g * 64 + tx * 4);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int kj = k0 + ty * 4 + i;
+    if (kj >= sh.Tk) continue;
+    float* dkg = dk + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride + (int64_t)kj * sh.kv_tstride;
+    float* dvg = dv + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride + (int64_t)kj * sh.kv_tstride;
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+      float4 a = make_float4(adk[g][i][0], adk[g][i][1], adk[g][i][2], adk[g][i][3]);
+      float4 c = make_float4(adv[g][i][0], adv[g][i][1], adv[g][i][2], adv[g][i][3]);
+      float4* pk = reinterpret_cast<float4*>(dkg + g * 64 + tx * 4); float4* pv = reinterpret_cast<float4*>(dvg + g * 64 + tx * 4);
+      if (accumulate) { float4 ok = *pk, ov = *pv; a.x += ok.x; a.y += ok.y; a.z += ok.z; a.w += ok.w; c.x += ov.x; c.y += ov.y; c.z += ov.z; c.w += ov.w; }
+      *pk = a; *pv = c;
+    }
+  }
+}
+
+// dQ: CTA = 64 queries of one (batch, query head); walks 64-key tiles.
+__global__ void __launch_bounds__(AT, 1) attn_bwd128_dq_kernel(AttnShape sh, const float* __restrict__ q, const float* __restrict__ k,
+                                                               const float* __restrict__ v, const float* __restrict__ dout,
+                                                               const float* __restrict__ lse, const float* __restrict__ delta,
+                                                               float* __restrict__ dq, int accumulate) {
+  constexpr int BQ = 64, BKV = 64, LT = 68, LD = FD + 4;
+  extern __shared__ __align__(16) float smem[];
+  float* Qt = smem;               // [FD][LT]
+  float* dOt = Qt + FD * LT;      // [FD][LT]
+  float* Kt = dOt + FD * LT;      // [FD][LT]
+  float* Vt = Kt + FD * LT;       // [FD][LT]   reused as dSt [BKV][LT] once dP is formed
+  float* Ks = Vt + FD * LT;       // [BKV][LD]
+  float* dSt = Vt;
+  __shared__ float lse_s[BQ], delta_s[BQ];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int bh = blockIdx.y, b = bh / sh.Hq, hq = bh % sh.Hq, hk = hq / (sh.Hq / sh.Hkv);
+  const int q0 = blockIdx.x * BQ, qvalid = min(BQ, sh.Tq - q0), offset = sh.offset0;
+  const float* qg = q + (int64_t)b * sh.q_bstride + (int64_t)q0 * sh.q_tstride + (int64_t)hq * FD;
+  const float* dog = dout + (int64_t)b * sh.o_bstride + (int64_t)q0 * sh.o_tstride + (int64_t)hq * FD;
+  const float* kg = k + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride;
+  const float* vg = v + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride;
+  load_rows_T(Qt, LT, qg, sh.q_tstride, BQ, qvalid);
+  load_rows_T(dOt, LT, dog, sh.o_tstride, BQ, qvalid);
+  if (tid < BQ) {
+    const int qi = q0 + tid;
+    lse_s[tid] = qi < sh.Tq ? lse[((int64_t)b * sh.Hq + hq) * sh.Tq + qi] : 0.0f;
+    delta_s[tid] = qi < sh.Tq ? delta[((int64_t)b * sh.Hq + hq) * sh.Tq + qi] : 0.0f;
+  }
+  float adq[2][4][4];
+#pragma unroll
+  for (int g = 0; g < 2; ++g)
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) adq[g][i][j] = 0.0f;
+  const int max_qpos = offset + q0 + qvalid - 1;
+  const int k_end = min(sh.Tk, max_qpos + 1);
+  int k_begin = 0;
+  if (sh.window >= 0) k_begin = max(0, offset + q0 - sh.window);
+  k_begin = (k_begin / BKV) * BKV;
+  for (int kt = k_begin; kt < k_end; kt += BKV) {
+    const int kvalid = min(BKV, sh.Tk - kt);
+    __syncthreads();
+    load_rows_T(Kt, LT, kg + (int64_t)kt * sh.kv_tstride, sh.kv_tstride, BKV, kvalid);
+    load_rows_T(Vt, LT, vg + (int64_t)kt * sh.kv_tstride, sh.kv_tstride, BKV, kvalid);
+    load_rows(Ks, LD, kg + (int64_t)kt * sh.kv_tstride, sh.kv_tstride, BKV, kvalid);
+    __syncthreads();
+    float s[4][4], dp[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { s[i][j] = 0.0f; dp[i][j] = 0.0f; }
+    mm_acc<4, 4>(s, Qt, LT, Kt, LT, FD, ty * 4, tx * 4);
+    mm_acc<4, 4>(dp, dOt, LT, Vt, LT, FD, ty * 4, tx * 4);
+    __syncthreads();   // Vt is consumed: its memory now holds dS transposed
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int kj = kt + tx * 4 + j;
+      float dsv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int il = ty * 4 + i, qi = q0 + il, qpos = offset + qi;
+        const int32_t qseg = (sh.segment_ids && qpos < sh.seg_len) ? sh.segment_ids[qpos] : 0;
+        float p = 0.0f;
+        if (qi < sh.Tq && kj < sh.Tk && !attn_masked(qpos, kj, sh.window, sh.segment_ids, sh.seg_len, qseg)) p = __expf(s[i][j] - lse_s[il]);
+        dsv[i] = p * (dp[i][j] - delta_s[il]);
+      }
+      *reinterpret_cast<float4*>(dSt + (tx * 4 + j) * LT + ty * 4) = make_float4(dsv[0], dsv[1], dsv[2], dsv[3]);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < 2; ++g) mm_acc<4, 4>(adq[g], dSt, LT, Ks, LD, BKV, ty * 4, g * 64 + tx * 4);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int qi = q0 + ty * 4 + i;
+    if (qi >= sh.Tq) continue;
+    float* dqg = dq + (int64_t)b * sh.q_bstride + (int64_t)qi * sh.q_tstride + (int64_t)hq * FD;
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+      float4 a = make_float4(adq[g][i][0], adq[g][i][1], adq[g][i][2], adq[g][i][3]);
+      float4* pq = reinterpret_cast<float4*>(dqg + g * 64 + tx * 4);
+      if (accumulate) { float4 o4 = *pq; a.x += o4.x; a.y += o4.y; a.z += o4.z; a.w += o4.w; }
+      *pq = a;
+    }
+  }
+}
+
+// float4 row access needs 16-byte aligned rows.
+static bool fast128_ok(const AttnShape& sh, const void* p0, const void* p1, const void* p2, const void* p3, const void* p4) {
+  auto al = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  return sh.D == FD && al(p0) && al(p1) && al(p2) && al(p3) && al(p4) && sh.q_tstride % 4 == 0 && sh.q_bstride % 4 == 0 && sh.kv_tstride % 4 == 0 &&
+         sh.kv_bstride % 4 == 0 && sh.kv_hstride % 4 == 0 && sh.o_tstride % 4 == 0 && sh.o_bstride % 4 == 0;
+}
+
+static int attn_fwd128_go(const AttnShape& sh, const float* q, const float* k, const float* v, float* out, float* lse, cudaStream_t s) {
+  const size_t smem = sizeof(float) * (size_t)(FD * 132 + FD * 68 + 64 * 132 + 64 * 132);
+  static bool configured = false;
+  if (!configured) { GN_CUDA(cudaFuncSetAttribute(attn_fwd128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); configured = true; }
+  dim3 grid(ceil_div(sh.Tq, 128), sh.B * sh.Hq);
+  attn_fwd128_kernel<<<grid, AT, smem, s>>>(sh, q, k, v, out, lse);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+static int attn_bwd128_go(const AttnShape& sh, const float* q, const float* k, const float* v, const float* dout, const float* lse, const float* delta,
+                          float* dq, float* dk, float* dv, int accumulate, cudaStream_t s) {
+  const size_t smem_kv = sizeof(float) * (size_t)(4 * FD * 68 + 2 * 64 * 132);
+  const size_t smem_q = sizeof(float) * (size_t)(4 * FD * 68 + 64 * 132);
+  static bool configured = false;
+  if (!configured) {
+    GN_CUDA(cudaFuncSetAttribute(attn_bwd128_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv));
+    GN_CUDA(cudaFuncSetAttribute(attn_bwd128_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_q));
+    configured = true;
+  }
+  dim3 gkv(ceil_div(sh.Tk, 64), sh.B * sh.Hkv);
+  attn_bwd128_dkv_kernel<<<gkv, AT, smem_kv, s>>>(sh, q, k, v, dout, lse, delta, dk, dv, accumulate);
+  GN_LAUNCH_CHECK();
+  dim3 gq(ceil_div(sh.Tq, 64), sh.B * sh.Hq);
+  attn_bwd128_dq_kernel<<<gq, AT, smem_q, s>>>(sh, q, k, v, dout, lse, delta, dq, accumulate);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
 }
 
 // ============================================================== backward
@@ -456,6 +810,8 @@ int attention_backward_launch(const AttnShape& sh, const float* q, const float* 
     GN_LAUNCH_CHECK();
     delta = delta_scratch;
   }
+  if (fast128_ok(sh, q, k, v, dout, dq) && fast128_ok(sh, dk, dv, nullptr, nullptr, nullptr))
+    return attn_bwd128_go(sh, q, k, v, dout, lse, delta, dq, dk, dv, accumulate, s);
   if (sh.D <= 32) return attn_bwd_go<32>(sh, q, k, v, dout, lse, delta, dq, dk, dv, accumulate, s);
   if (sh.D <= 64) return attn_bwd_go<64>(sh, q, k, v, dout, lse, delta, dq, dk, dv, accumulate, s);
   return attn_bwd_go<128>(sh, q, k, v, dout, lse, delta, dq, dk, dv, accumulate, s);

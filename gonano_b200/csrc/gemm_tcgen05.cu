@@ -177,7 +177,7 @@ struct TcSmem {
 };
 
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
+__global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
                                                          const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
                                                          TcEpilogue ep, int M, int N, int K, int* err) {
   using S = TcSmem<BN, STAGES>;
@@ -205,7 +205,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), BN > 128 ? 8 : 4); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -270,19 +270,23 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
     }
   } else {
     // ------------------------------------------------------------- epilogue (warps 2..5)
+    // Each epilogue thread owns one accumulator row and ACC of its columns: 4 warps cover a tile
+    // up to 128 columns wide, 8 warps (two column halves) a 256-column tile.
+    constexpr int ACC = BN > 128 ? 128 : BN;
     const int quarter = warp & 3;    // tcgen05.ld: a warp reads lanes [32*(warp%4), +32)
-    float acc[BN];
+    const int chalf = ((warp - 2) >> 2) * ACC;   // first column of this warp's share
+    float acc[ACC];
 #pragma unroll
-    for (int j = 0; j < BN; ++j) acc[j] = 0.0f;
+    for (int j = 0; j < ACC; ++j) acc[j] = 0.0f;
     for (int c = 0; c < nchunks; ++c) {
       const int buf = c & 1;
       if (!mbar_wait(acc_full(buf), (uint32_t)(c / 2) & 1u)) { failed = true; break; }
       tc_fence_after();
       if (warp == 2 && lane == 0 && c < 64) TC_TRACE(768 + c);
 #pragma unroll
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 0; c0 < ACC; c0 += 32) {
         uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), r);
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + chalf + c0), r);
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[c0 + j] += __uint_as_float(r[j]);
@@ -297,17 +301,17 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
       // memory first: the pipeline stages are idle once the last chunk has been drained, and
       // each warp then writes whole 512-byte row segments (a thread-per-row store pattern was
       // measured at 3.5x the cost of the entire K loop).
-      constexpr int PITCH = BN + 4;            // floats per staged row: conflict-free float4 rows
-      constexpr int LPR = BN / 4;              // lanes that cover one row with float4
+      constexpr int PITCH = ACC + 4;           // floats per staged row: conflict-free float4 rows
+      constexpr int LPR = ACC / 4;             // lanes that cover one row with float4
       constexpr int RPI = 32 / LPR;            // rows a warp writes per iteration
-      float* stg = reinterpret_cast<float*>(gen_base) + (size_t)quarter * 32 * PITCH;
+      float* stg = reinterpret_cast<float*>(gen_base) + (size_t)(warp - 2) * 32 * PITCH;
 #pragma unroll
-      for (int j = 0; j < BN; j += 4) *reinterpret_cast<float4*>(&stg[lane * PITCH + j]) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+      for (int j = 0; j < ACC; j += 4) *reinterpret_cast<float4*>(&stg[lane * PITCH + j]) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
       __syncwarp();
       const bool vec_ok = (ep.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.C) & 15) == 0) &&
                           (ep.aux == nullptr || ((ep.ldaux % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.aux) & 15) == 0)));
       const int col = (lane % LPR) * 4;
-      const int n = n0 + col;
+      const int n = n0 + chalf + col;
 #pragma unroll 4
       for (int r0 = 0; r0 < 32; r0 += RPI) {
         const int r = r0 + lane / LPR;
@@ -523,7 +527,7 @@ int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int
     ep.C = g_splitk_ws; ep.ldc = N; ep.aux = nullptr; ep.epi = EPI_STORE; ep.split_stride = (int64_t)M * N;
   }
   dim3 grid(ceil_div(N, BN), ceil_div(M, TBM), splits);
-  gemm_tc_kernel<BN, STAGES><<<grid, 192, S::TOTAL, s>>>(mah, mal, mbh, mbl, ep, M, N, K, g_err_flag);
+  gemm_tc_kernel<BN, STAGES><<<grid, 64 + 32 * (BN > 128 ? 8 : 4), S::TOTAL, s>>>(mah, mal, mbh, mbl, ep, M, N, K, g_err_flag);
   GN_LAUNCH_CHECK();
   if (splits > 1) {
     int blocks = (int)std::min<int64_t>(((int64_t)M * (N / 4) + 255) / 256, (int64_t)kNumSM * 8);
@@ -567,6 +571,11 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
     splits = (int)std::min<int64_t>(kNumSM / tiles, nk / 4);   // at least 4 k-blocks per split
     if (splits < 1) splits = 1;
   }
+  // Wide 128 x 256 tiles when the output is large: the K loop is bound by the 64 B/clk/SM path from
+  // L2, and a 256-column tile reads the A operand once for twice the work (96 KB per k-block for
+  // two 128 x 128 units instead of 128 KB).
+  if (splits == 1 && g.N >= 512 && (int64_t)ceil_div(g.M, TBM) * ceil_div(g.N, 256) >= kNumSM * 3 / 2)
+    return launch_tc<256, 2>(a, b, ep, g.M, g.N, g.K, 1, s);
   return launch_tc<128, 3>(a, b, ep, g.M, g.N, g.K, splits, s);
 }
 

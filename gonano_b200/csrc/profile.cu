@@ -122,6 +122,26 @@ extern "C" int gn_profile_kernel(gn_ctx* ctx, const char* kernel, const int64_t*
       return attention_decode_launch(q, (int64_t)Hq * D, kc, vc, (int64_t)Hkv * ctxl * D, (int64_t)ctxl * D, cl, rows, Hq, Hkv, D, -1, out, (int64_t)Hq * D, pa, pm, splits, s);
     });
   }
+  if (k == "attention_fwd" || k == "attention_bwd") {
+    GN_REQUIRE(n_dims == 5, "%s wants {batch, n_head, n_kv_head, head_dim, seq}", kernel);
+    int B = (int)dims[0], Hq = (int)dims[1], Hkv = (int)dims[2], D = (int)dims[3], T = (int)dims[4];
+    const int W = (Hq + 2 * Hkv) * D;
+    const int64_t rows = (int64_t)B * T;
+    float *qkv, *o, *lse, *dqkv, *dout, *delta;
+    GN_TRY(bufs.get(&qkv, (size_t)rows * W)); GN_TRY(bufs.get(&o, (size_t)rows * Hq * D)); GN_TRY(bufs.get(&lse, (size_t)B * Hq * T));
+    GN_TRY(bufs.get(&dqkv, (size_t)rows * W)); GN_TRY(bufs.get(&dout, (size_t)rows * Hq * D)); GN_TRY(bufs.get(&delta, (size_t)B * Hq * T));
+    GN_TRY(synth(qkv, rows * W, -1.2f, 1.2f, 11, s)); GN_TRY(synth(dout, rows * Hq * D, -1, 1, 12, s));
+    AttnShape sh;
+    sh.B = B; sh.Hq = Hq; sh.Hkv = Hkv; sh.D = D; sh.Tq = T; sh.Tk = T;
+    sh.q_bstride = (int64_t)T * W; sh.q_tstride = W; sh.kv_bstride = (int64_t)T * W; sh.kv_tstride = W; sh.kv_hstride = D;
+    sh.o_bstride = (int64_t)T * Hq * D; sh.o_tstride = (int64_t)Hq * D; sh.window = -1; sh.offset0 = 0;
+    const float* kp = qkv + (int64_t)Hq * D; const float* vp = qkv + (int64_t)(Hq + Hkv) * D;
+    GN_TRY(attention_forward_launch(sh, qkv, kp, vp, o, lse, s));
+    if (k == "attention_fwd") return time_it(s, iters, mean_ms, [&]() { return attention_forward_launch(sh, qkv, kp, vp, o, lse, s); });
+    return time_it(s, iters, mean_ms, [&]() {
+      return attention_backward_launch(sh, qkv, kp, vp, o, dout, lse, nullptr, dqkv, dqkv + (int64_t)Hq * D, dqkv + (int64_t)(Hq + Hkv) * D, 0, delta, s);
+    });
+  }
   if (k == "advantage") {
     GN_REQUIRE(n_dims == 2, "advantage wants {groups, group}");
     int groups = (int)dims[0], group = (int)dims[1];

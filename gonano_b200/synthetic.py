@@ -22,6 +22,9 @@ def dense_config(name: str) -> dict:
     if name == "d12":  # ConfigForDepthRatio(12, 32768, 64, 128, 2048, "SSSL", 3)
         return dict(sequence_len=2048, vocab_size=32768, n_layer=12, n_head=6, n_kv_head=2, embed_dim=768, rotary_dims=64,
                     window_pattern="SSSL")
+    if name == "h128":  # small model with the d12 head geometry (head_dim 128, 2:1 grouped queries, partial rotary, a binding window)
+        return dict(sequence_len=512, vocab_size=1024, n_layer=2, n_head=2, n_kv_head=1, embed_dim=256, rotary_dims=64,
+                    window_pattern="SL")
     if name == "tiny":  # model/gradcheck_test.go:14-31 tinyTrainModel shape, GQA 2:1
         return dict(sequence_len=16, vocab_size=16, n_layer=2, n_head=2, n_kv_head=1, embed_dim=32, rotary_dims=0,
                     window_pattern="L")

@@ -263,6 +263,7 @@ int gn_model_phase_ms(gn_model* model, const char* phase, float* ms);
  *   "loss"              dims {rows, vocab, valid_percent}    fused loss + dlogits (+ softcap backward)
  *   "sampler"           dims {rows, vocab, top_k}
  *   "decode_attention"  dims {rows, n_head, n_kv_head, head_dim, context}
+ *   "attention_fwd" / "attention_bwd"  dims {batch, n_head, n_kv_head, head_dim, seq}   causal training attention
  *   "advantage"         dims {groups, group}
  * Buffers are larger than L2 for the workloads this is used on, so no cache flush is done. */
 int gn_profile_kernel(gn_ctx* ctx, const char* kernel, const int64_t* dims, int n_dims, int iters, float* mean_ms);

@@ -97,7 +97,8 @@ def test_row_parity(oracle, bk, ref, cols):
 
 
 ATTN_CASES = [("causal", 6, 6, 8, 0, -1), ("decode", 1, 10, 8, 9, -1), ("sliding", 6, 6, 8, 0, 2), ("sliding-decode", 1, 10, 4, 9, 3),
-              ("wide-head", 5, 5, 16, 0, -1), ("d64", 70, 70, 64, 0, -1), ("d128-window", 150, 150, 128, 0, 40), ("offset", 40, 100, 32, 60, -1)]
+              ("wide-head", 5, 5, 16, 0, -1), ("d64", 70, 70, 64, 0, -1), ("d128-window", 150, 150, 128, 0, 40), ("offset", 40, 100, 32, 60, -1),
+              ("d128-train", 383, 383, 128, 0, -1), ("d128-offset", 70, 200, 128, 130, -1), ("d128-decode", 1, 300, 128, 299, 64)]
 
 
 # parity_test.go:350-431 (forward + backward), 203-223 (large)

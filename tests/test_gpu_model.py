@@ -46,7 +46,7 @@ def test_param_round_trip(oracle, ctx):
     gm.close()
 
 
-@pytest.mark.parametrize("name,std,B,T", [("tiny", 0.1, 2, 6), ("tiny", 0.1, 3, 16), ("c1", 0.02, 2, 33), ("c1", 0.1, 1, 70)])
+@pytest.mark.parametrize("name,std,B,T", [("tiny", 0.1, 2, 6), ("tiny", 0.1, 3, 16), ("c1", 0.02, 2, 33), ("c1", 0.1, 1, 70), ("h128", 0.05, 2, 200)])
 def test_forward_logits(oracle, ctx, name, std, B, T):
     om, gm, cfg = make_pair(oracle, ctx, name, std=std)
     rng = np.random.default_rng(0)
@@ -67,7 +67,8 @@ def test_forward_sliding_window(oracle, ctx):
     gm.close()
 
 
-@pytest.mark.parametrize("name,std,P,plen,G,maxtok", [("tiny", 0.1, 2, 4, 3, 6), ("c1", 0.02, 3, 32, 4, 12), ("c1", 0.3, 2, 9, 2, 20)])
+@pytest.mark.parametrize("name,std,P,plen,G,maxtok", [("tiny", 0.1, 2, 4, 3, 6), ("c1", 0.02, 3, 32, 4, 12), ("c1", 0.3, 2, 9, 2, 20),
+                                                       ("h128", 0.05, 2, 140, 3, 6)])
 def test_rollout_by_teacher_forcing(oracle, ctx, name, std, P, plen, G, maxtok):
     """The GPU rollout is fed back through the oracle: the logits every sampling step saw agree
     within 1e-3, and on the GPU's own logits the oracle's sampler draws the same token (bit-exact)."""
@@ -114,7 +115,8 @@ def test_rollout_greedy_matches_oracle_engine(oracle, ctx):
     gm.close()
 
 
-@pytest.mark.parametrize("name,std,B,T,rpp", [("tiny", 0.1, 2, 4, 0), ("tiny", 0.1, 5, 12, 2), ("c1", 0.05, 3, 40, 0), ("c1", 0.05, 4, 24, 3)])
+@pytest.mark.parametrize("name,std,B,T,rpp", [("tiny", 0.1, 2, 4, 0), ("tiny", 0.1, 5, 12, 2), ("c1", 0.05, 3, 40, 0), ("c1", 0.05, 4, 24, 3),
+                                              ("h128", 0.05, 2, 150, 0)])
 def test_policy_gradient_step(oracle, ctx, name, std, B, T, rpp):
     om, gm, cfg = make_pair(oracle, ctx, name, std=std)
     V = cfg["vocab_size"]
