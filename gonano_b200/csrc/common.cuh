@@ -39,6 +39,7 @@ const char* get_error();
 
 // Check the launch that just happened and count it (gn_ctx_launch_count).
 void count_launch();
+void count_launches(int64_t n);   // kernels replayed through a CUDA graph
 #define GN_LAUNCH_CHECK()          \
   do {                             \
     gn::count_launch();            \
@@ -105,6 +106,16 @@ __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __ex
 // (kernels/scalar/elementwise.go:146-150); used where a gate decides values.
 __device__ __forceinline__ float sigmoid_exact(float x) { return (float)(1.0 / (1.0 + exp((double)(-x)))); }
 
+// hi = tf32(x) (round to nearest), lo = tf32(x - hi): the operand form of the 3xTF32 products.
+__device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
+  uint32_t h, l;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+  hi = __uint_as_float(h);
+  float rest = x - hi;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(rest));
+  lo = __uint_as_float(l);
+}
+
 // ---------------------------------------------------------------- GEMM API
 // C[M,N] (op)= A(M,K) * B(K,N), row-major storage with leading dimensions.
 //   a_trans = 0: A(m,k) = A[m*lda + k]      a_trans = 1: A(m,k) = A[k*lda + m]
@@ -126,6 +137,10 @@ struct GemmArgs {
   float* aux = nullptr; int64_t ldaux = 0;
   float scalar = 0.0f;
   int a_static = 0, b_static = 0;  // operand is a parameter tensor: its tensor-core split may be cached
+  // Tensor-core path only: A already split by its producer (hi = tf32(x), lo = tf32(x - hi)), pitch lda.
+  const float* a_hi = nullptr; const float* a_lo = nullptr;
+  // Tensor-core path only: also write the split of the output (pitch ldc) for the next product.
+  float* c_hi = nullptr; float* c_lo = nullptr;
 };
 int gemm_simt(const GemmArgs& args, cudaStream_t stream);
 // kind 0: SIMT float32.  kind 1: tcgen05 3xTF32 where the shape allows it, else SIMT.

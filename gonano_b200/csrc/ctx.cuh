@@ -7,4 +7,5 @@ struct gn_ctx {
   cudaStream_t stream = nullptr;
   bool own_stream = false;
   int gemm_kind = 1;
+  bool use_graphs = true;   // replay the decode step as a CUDA graph
 };

@@ -134,6 +134,7 @@ struct TcEpilogue {
   float* aux; int64_t ldaux;
   int epi; float scalar;
   int64_t split_stride;   // split-K: floats between the partial tiles of consecutive splits
+  float* c_hi; float* c_lo; // optional: the output split for the next product (pitch ldc)
   long long* trace;   // timeline of CTA (0,0) in SM cycles when the library is built with GN_TC_TRACE, else unused
 };
 
@@ -332,6 +333,13 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
           for (int e = 0; e < 4; ++e) out[e] = epi_value(ep, v[e], ax[e], co[e], wa, av[e]);
           if (wa) *reinterpret_cast<float4*>(ep.aux + m * ep.ldaux + n) = make_float4(av[0], av[1], av[2], av[3]);
           *reinterpret_cast<float4*>(crow + n) = make_float4(out[0], out[1], out[2], out[3]);
+          if (ep.c_hi) {
+            float h[4], l[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) split_tf32(out[e], h[e], l[e]);
+            *reinterpret_cast<float4*>(ep.c_hi + m * ep.ldc + n) = make_float4(h[0], h[1], h[2], h[3]);
+            *reinterpret_cast<float4*>(ep.c_lo + m * ep.ldc + n) = make_float4(l[0], l[1], l[2], l[3]);
+          }
         } else {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -342,6 +350,7 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
               const float out = epi_value(ep, v[e], ax, cold, wa, av);
               if (wa) ep.aux[m * ep.ldaux + n + e] = av;
               crow[n + e] = out;
+              if (ep.c_hi) { float h, l; split_tf32(out, h, l); ep.c_hi[m * ep.ldc + n + e] = h; ep.c_lo[m * ep.ldc + n + e] = l; }
             }
           }
         }
@@ -360,14 +369,6 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
 }
 
 // ------------------------------------------------------------------ operand split
-__device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
-  uint32_t h, l;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
-  hi = __uint_as_float(h);
-  float rest = x - hi;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(rest));
-  lo = __uint_as_float(l);
-}
 // src [rows, cols] (pitch ld) -> hi, lo [rows, cols] (pitch ldd)
 __global__ void __launch_bounds__(256) split_kernel(const float* __restrict__ src, int64_t ld, float* __restrict__ hi, float* __restrict__ lo, int64_t ldd,
                                                     int64_t rows, int cols) {
@@ -498,6 +499,9 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
     }
     if (wa) { for (int e = 0; e < 4; ++e) ep.aux[m * ep.ldaux + n + e] = av[e]; }
     for (int e = 0; e < 4; ++e) crow[e] = out[e];
+    if (ep.c_hi) {
+      for (int e = 0; e < 4; ++e) { float h, l; split_tf32(out[e], h, l); ep.c_hi[m * ep.ldc + n + e] = h; ep.c_lo[m * ep.ldc + n + e] = l; }
+    }
   }
 }
 
@@ -524,7 +528,7 @@ int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int
       if (cudaMalloc((void**)&g_splitk_ws, need * sizeof(float)) != cudaSuccess) { set_error("tcgen05 gemm: cannot allocate the split-K workspace"); return GN_ERR_NOMEM; }
       g_splitk_floats = need;
     }
-    ep.C = g_splitk_ws; ep.ldc = N; ep.aux = nullptr; ep.epi = EPI_STORE; ep.split_stride = (int64_t)M * N;
+    ep.C = g_splitk_ws; ep.ldc = N; ep.aux = nullptr; ep.epi = EPI_STORE; ep.split_stride = (int64_t)M * N; ep.c_hi = ep.c_lo = nullptr;
   }
   dim3 grid(ceil_div(N, BN), ceil_div(M, TBM), splits);
   gemm_tc_kernel<BN, STAGES><<<grid, 64 + 32 * (BN > 128 ? 8 : 4), S::TOTAL, s>>>(mah, mal, mbh, mbl, ep, M, N, K, g_err_flag);
@@ -555,10 +559,11 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
   GN_TRY(ensure_init());
   SplitBuf a, b;
   // A is logically [M, K]; stored transposed ([K, M]) when a_trans.
-  GN_TRY(split_operand(g.A, g.lda, g.M, g.K, g.a_trans != 0, g.a_static != 0, 0, a, s));
+  if (g.a_hi && g.a_lo && !g.a_trans) { a.hi = const_cast<float*>(g.a_hi); a.lo = const_cast<float*>(g.a_lo); a.ld = g.lda; }   // split by the producer
+  else GN_TRY(split_operand(g.A, g.lda, g.M, g.K, g.a_trans != 0, g.a_static != 0, 0, a, s));
   // B is logically [N, K]; stored that way when b_trans (weights [out, in]), else stored [K, N].
   GN_TRY(split_operand(g.B, g.ldb, g.N, g.K, g.b_trans == 0, g.b_static != 0, 1, b, s));
-  TcEpilogue ep{g.C, g.ldc, g.aux, g.ldaux, g.epilogue, g.scalar, 0, g_trace};
+  TcEpilogue ep{g.C, g.ldc, g.aux, g.ldaux, g.epilogue, g.scalar, 0, g.c_hi, g.c_lo, g_trace};
   // Filling the machine when the output has few tiles (the rollout's products have 512 rows):
   // the K loop is split over gridDim.z so that about one CTA per SM runs, each writing a partial
   // tile that a second pass sums in a fixed order (deterministic, unlike atomics).  Narrow tiles

@@ -17,6 +17,7 @@
 //     the fused projection output through strides (no head-major transposes).
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <map>
 #include <string>
 #include <vector>
@@ -90,7 +91,7 @@ struct gn_model {
   DevBuf cosb, sinb, sacc;
   // inference state
   DevBuf cache, prev, pos, ctxlen, ids_dev, sampled, seeds, out_tokens, out_lengths, done, n_done, sel;
-  DevBuf part_acc, part_ms;
+  DevBuf part_acc, part_ms, step_dev;
   Arena infer, train;
   DevBuf tgt_dev, adv_dev, rowloss, loss_dev, in_dev;
   std::map<std::string, float> phase_ms;
@@ -169,6 +170,7 @@ enum Mode { MODE_PLAIN, MODE_PREFILL, MODE_DECODE, MODE_TRAIN };
 
 struct FwdBufs {
   float *E, *X0, *Xa, *Xb, *H, *QKV, *O, *M, *HID, *BO, *Y, *LOGITS;
+  float *S1h, *S1l, *S4h, *S4l;   // producer-written tf32 splits: one [rows, d] pair and one [rows, 4d] pair, reused by every layer
   // train only
   float *SIG, *FP;
   std::vector<LayerSaved> layers;
@@ -188,6 +190,8 @@ size_t plan_bufs(gn_model* m, Arena& a, FwdBufs& b, Mode mode, int64_t rows, int
   b.X0 = a.take(rows * d);
   b.Y = a.take(std::max<int64_t>(rows, logit_rows) * d);
   b.LOGITS = a.take(logit_rows * V);
+  b.S1h = a.take(std::max<int64_t>(rows, logit_rows) * d); b.S1l = a.take(std::max<int64_t>(rows, logit_rows) * d);
+  b.S4h = a.take(rows * 4 * d); b.S4l = a.take(rows * 4 * d);
   if (mode == MODE_TRAIN) {
     b.SIG = a.take((int64_t)B * std::max(T - 1, 1));
     b.FP = a.take(rows * d);
@@ -248,9 +252,11 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
     } else {
       Xin = b.Xa; H = b.H; QKV = b.QKV; O = b.O; MID = b.Xa; Mn = b.M; U = nullptr; HID = b.HID; XOUT = b.Xa;
     }
-    GN_TRY(mix_norm_launch(x_prev, b.X0, m->p(m->off_rho), m->p(m->off_chi), l, Xin, H, rows, d, s));
+    const bool tc = m->ctx->gemm_kind == 1;
+    GN_TRY(mix_norm_launch(x_prev, b.X0, m->p(m->off_rho), m->p(m->off_chi), l, Xin, H, tc ? b.S1h : nullptr, tc ? b.S1l : nullptr, rows, d, s));
     // q, k, v projections as one GEMM against [c_q; c_k; c_v]
-    { GemmArgs g; g.A = H; g.lda = d; g.B = m->p(o.qkv); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = QKV; g.ldc = W; g.M = (int)rows; g.N = W; g.K = d; GN_TRY(gemm(m, g)); }
+    { GemmArgs g; g.A = H; g.lda = d; g.B = m->p(o.qkv); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = QKV; g.ldc = W; g.M = (int)rows; g.N = W; g.K = d;
+      if (tc) { g.a_hi = b.S1h; g.a_lo = b.S1l; } GN_TRY(gemm(m, g)); }
     QkvPost qp;
     qp.qkv = QKV; qp.H = H; qp.ids = a.ids;
     qp.ve_table = o.has_ve ? m->p(o.ve) : nullptr; qp.ve_gate = o.has_ve ? m->p(o.ve_gate) : nullptr;
@@ -277,13 +283,15 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
     // MID = Xin + O Wo^T
     { GemmArgs g; g.A = O; g.lda = (int64_t)Hq * D; g.B = m->p(o.proj); g.b_static = 1; g.ldb = (int64_t)Hq * D; g.b_trans = 1; g.C = MID; g.ldc = d; g.M = (int)rows; g.N = d; g.K = Hq * D;
       g.epilogue = EPI_RESIDUAL; g.aux = Xin; g.ldaux = d; GN_TRY(gemm(m, g)); }
-    GN_TRY(norm_launch(MID, Mn, rows, d, s));
+    GN_TRY(norm_launch(MID, Mn, tc ? b.S1h : nullptr, tc ? b.S1l : nullptr, rows, d, s));
     // HID = relu(M Wfc^T)^2   (training also keeps the pre-activation)
     { GemmArgs g; g.A = Mn; g.lda = d; g.B = m->p(o.fc); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = HID; g.ldc = 4 * d; g.M = (int)rows; g.N = 4 * d; g.K = d;
-      g.epilogue = EPI_RELU2; g.aux = U; g.ldaux = 4 * d; GN_TRY(gemm(m, g)); }
+      g.epilogue = EPI_RELU2; g.aux = U; g.ldaux = 4 * d;
+      if (tc) { g.a_hi = b.S1h; g.a_lo = b.S1l; g.c_hi = b.S4h; g.c_lo = b.S4l; } GN_TRY(gemm(m, g)); }
     // XOUT = MID + HID Wp^T
     { GemmArgs g; g.A = HID; g.lda = 4 * d; g.B = m->p(o.mproj); g.b_static = 1; g.ldb = 4 * d; g.b_trans = 1; g.C = XOUT; g.ldc = d; g.M = (int)rows; g.N = d; g.K = 4 * d;
-      g.epilogue = EPI_RESIDUAL; g.aux = MID; g.ldaux = d; GN_TRY(gemm(m, g)); }
+      g.epilogue = EPI_RESIDUAL; g.aux = MID; g.ldaux = d;
+      if (tc) { g.a_hi = b.S4h; g.a_lo = b.S4l; } GN_TRY(gemm(m, g)); }
     if (l == L / 2) {
       if (train) backout = XOUT;
       else { GN_CUDA(cudaMemcpyAsync(b.BO, XOUT, sizeof(float) * rows * d, cudaMemcpyDeviceToDevice, s)); backout = b.BO; }
@@ -294,9 +302,11 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
   int64_t lrows = rows;
   const int32_t* sel = nullptr;
   if (a.mode == MODE_PREFILL) { lrows = B; sel = m->sel.i(); }
-  GN_TRY(backout_norm_launch(x_prev, backout, m->p(m->off_backout), sel, train ? b.FP : nullptr, b.Y, lrows, d, s));
+  const bool tc_head = m->ctx->gemm_kind == 1;
+  GN_TRY(backout_norm_launch(x_prev, backout, m->p(m->off_backout), sel, train ? b.FP : nullptr, b.Y, tc_head ? b.S1h : nullptr, tc_head ? b.S1l : nullptr, lrows, d, s));
   { GemmArgs g; g.A = b.Y; g.lda = d; g.B = m->p(m->off_lm); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = b.LOGITS; g.ldc = V; g.M = (int)lrows; g.N = V; g.K = d;
-    g.epilogue = EPI_SOFTCAP; g.scalar = kSoftcap; GN_TRY(gemm(m, g)); }
+    g.epilogue = EPI_SOFTCAP; g.scalar = kSoftcap;
+    if (tc_head) { g.a_hi = b.S1h; g.a_lo = b.S1l; } GN_TRY(gemm(m, g)); }
   return GN_OK;
 }
 
@@ -402,6 +412,7 @@ int gn_ctx_create(int device, void* stream, gn_ctx** out) {
   if (stream) { c->stream = (cudaStream_t)stream; c->own_stream = false; }
   else { GN_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking)); c->own_stream = true; }
   c->gemm_kind = gemm_default_kind();
+  c->use_graphs = std::getenv("GN_NO_GRAPH") == nullptr;   // debugging aid: GN_NO_GRAPH=1 keeps the decode loop eager
   *out = c;
   return GN_OK;
 }
@@ -467,7 +478,7 @@ int gn_model_destroy(gn_model* m) {
   cudaStreamSynchronize(m->ctx->stream);
   gemm_invalidate_static();   // cached splits are keyed by addresses that are about to be freed
   DevBuf* bufs[] = {&m->P, &m->G, &m->cosb, &m->sinb, &m->sacc, &m->cache, &m->prev, &m->pos, &m->ctxlen, &m->ids_dev, &m->sampled, &m->seeds,
-                    &m->out_tokens, &m->out_lengths, &m->done, &m->n_done, &m->sel, &m->part_acc, &m->part_ms, &m->infer.buf, &m->train.buf,
+                    &m->out_tokens, &m->out_lengths, &m->done, &m->n_done, &m->sel, &m->part_acc, &m->part_ms, &m->step_dev, &m->infer.buf, &m->train.buf,
                     &m->tgt_dev, &m->adv_dev, &m->rowloss, &m->loss_dev, &m->in_dev};
   for (DevBuf* b : bufs) b->release();
   for (int i = 0; i < 4; ++i) if (m->ev[i]) cudaEventDestroy(m->ev[i]);
@@ -596,36 +607,84 @@ int gn_generate_batch(gn_model* m, const int32_t* prompts, int P, int plen, int 
   GN_CUDA(cudaEventRecord(m->ev[1], s));
 
   // ---- decode loop (engine.go:241-325)
+  // One iteration = forward the sampled column, then sample the next one.  The sequence of
+  // launches is identical from step to step (positions, the step counter and the sampled ids
+  // live in device memory), so after two eager iterations it is captured once into a CUDA graph
+  // and replayed: a decode step is ~150 small launches, and at small batch the launch gaps
+  // otherwise rival the kernels.  With the per-step logits tap the loop stays eager.
   std::vector<float> host_logits;
   int generated = 0;
-  int logits_div = G;   // the first sampling step reads the prompt's last-position logits for all G rows
   int32_t n_done_host = 0;
-  while (true) {
-    if (step_logits) {
-      int lr = rows / logits_div;
-      host_logits.resize((size_t)lr * V);
-      GN_CUDA(cudaMemcpyAsync(host_logits.data(), b.LOGITS, sizeof(float) * (size_t)lr * V, cudaMemcpyDeviceToHost, s));
-      GN_CUDA(cudaStreamSynchronize(s));
-      float* dst = step_logits + (size_t)generated * rows * V;
-      for (int r = 0; r < rows; ++r) std::memcpy(dst + (size_t)r * V, host_logits.data() + (size_t)(r / logits_div) * V, sizeof(float) * V);
-    }
-    GN_TRY(sample_launch(b.LOGITS, rows, V, logits_div, nullptr, (const uint64_t*)m->seeds.p, G, nullptr, (uint32_t)generated, temperature, top_k,
-                         m->sampled.i(), s));
+  auto tap = [&](int div) -> int {
+    if (!step_logits) return GN_OK;
+    int lr = rows / div;
+    host_logits.resize((size_t)lr * V);
+    GN_CUDA(cudaMemcpyAsync(host_logits.data(), b.LOGITS, sizeof(float) * (size_t)lr * V, cudaMemcpyDeviceToHost, s));
+    GN_CUDA(cudaStreamSynchronize(s));
+    float* dst = step_logits + (size_t)generated * rows * V;
+    for (int r = 0; r < rows; ++r) std::memcpy(dst + (size_t)r * V, host_logits.data() + (size_t)(r / div) * V, sizeof(float) * V);
+    return GN_OK;
+  };
+  GN_TRY(m->step_dev.ensure(sizeof(uint32_t)));
+  GN_CUDA(cudaMemsetAsync(m->step_dev.p, 0, sizeof(uint32_t), s));
+  // first column: every row of a group samples from its prompt's last-position logits (engine.go:182-191)
+  GN_TRY(tap(G));
+  GN_TRY(sample_launch(b.LOGITS, rows, V, G, nullptr, (const uint64_t*)m->seeds.p, G, (const uint32_t*)m->step_dev.p, 0, temperature, top_k, m->sampled.i(), s));
+  GN_TRY(engine_step_launch(m->sampled.i(), m->out_tokens.i(), m->out_lengths.i(), m->done.i(), m->n_done.i(), rows, max_tokens, bos, aend, s));
+  GN_TRY(add_u32_launch((uint32_t*)m->step_dev.p, 1, s));
+  ++generated;
+  auto body = [&]() -> int {
+    GN_TRY(ctx_from_pos_launch(m->pos.i(), m->ctxlen.i(), rows, s));
+    FwdArgs a; a.mode = MODE_DECODE; a.ids = m->sampled.i(); a.B = rows; a.T = 1; a.cache_rows = rows; a.cache_row_mul = 1; a.max_seq = max_seq;
+    GN_TRY(forward_core(m, b, a));                       // forward the sampled column (engine.go:321-324)
+    GN_TRY(add_i32_launch(m->pos.i(), 1, rows, s));
+    GN_TRY(sample_launch(b.LOGITS, rows, V, 1, nullptr, (const uint64_t*)m->seeds.p, G, (const uint32_t*)m->step_dev.p, 0, temperature, top_k, m->sampled.i(), s));
     GN_TRY(engine_step_launch(m->sampled.i(), m->out_tokens.i(), m->out_lengths.i(), m->done.i(), m->n_done.i(), rows, max_tokens, bos, aend, s));
-    ++generated;
-    if (generated >= max_tokens) break;
+    GN_TRY(add_u32_launch((uint32_t*)m->step_dev.p, 1, s));
+    return GN_OK;
+  };
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  size_t graph_nodes = 0;
+  const bool use_graph = !step_logits && m->ctx->use_graphs;
+  int status = GN_OK;
+  int eager_done = 0;
+  while (generated < max_tokens) {
     if (generated % 16 == 0 || step_logits) {  // every row finished: stop early (engine.go:245-254)
       GN_CUDA(cudaMemcpyAsync(&n_done_host, m->n_done.p, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
       GN_CUDA(cudaStreamSynchronize(s));
       if (n_done_host >= rows) break;
     }
-    // forward the sampled column (engine.go:321-324)
-    GN_TRY(ctx_from_pos_launch(m->pos.i(), m->ctxlen.i(), rows, s));
-    FwdArgs a; a.mode = MODE_DECODE; a.ids = m->sampled.i(); a.B = rows; a.T = 1; a.cache_rows = rows; a.cache_row_mul = 1; a.max_seq = max_seq;
-    GN_TRY(forward_core(m, b, a));
-    GN_TRY(add_i32_launch(m->pos.i(), 1, rows, s));
-    logits_div = 1;
+    if (step_logits) {
+      // the tap wants the logits each sampling step saw: forward first, copy, then sample
+      GN_TRY(ctx_from_pos_launch(m->pos.i(), m->ctxlen.i(), rows, s));
+      FwdArgs a; a.mode = MODE_DECODE; a.ids = m->sampled.i(); a.B = rows; a.T = 1; a.cache_rows = rows; a.cache_row_mul = 1; a.max_seq = max_seq;
+      GN_TRY(forward_core(m, b, a));
+      GN_TRY(add_i32_launch(m->pos.i(), 1, rows, s));
+      GN_TRY(tap(1));
+      GN_TRY(sample_launch(b.LOGITS, rows, V, 1, nullptr, (const uint64_t*)m->seeds.p, G, (const uint32_t*)m->step_dev.p, 0, temperature, top_k, m->sampled.i(), s));
+      GN_TRY(engine_step_launch(m->sampled.i(), m->out_tokens.i(), m->out_lengths.i(), m->done.i(), m->n_done.i(), rows, max_tokens, bos, aend, s));
+      GN_TRY(add_u32_launch((uint32_t*)m->step_dev.p, 1, s));
+    } else if (!use_graph || eager_done < 2) {
+      GN_TRY(body());       // eager: also sizes every scratch buffer before the capture
+      ++eager_done;
+    } else {
+      if (!exec) {
+        GN_CUDA(cudaStreamSynchronize(s));
+        GN_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+        status = body();
+        cudaError_t ce = cudaStreamEndCapture(s, &graph);
+        if (status != GN_OK) { if (graph) cudaGraphDestroy(graph); return status; }
+        if (ce != cudaSuccess) { set_error("decode graph capture failed: %s", cudaGetErrorString(ce)); return GN_ERR_CUDA; }
+        GN_CUDA(cudaGraphGetNodes(graph, nullptr, &graph_nodes));
+        GN_CUDA(cudaGraphInstantiate(&exec, graph, 0));
+      }
+      GN_CUDA(cudaGraphLaunch(exec, s));
+      count_launches((int64_t)graph_nodes);
+    }
+    ++generated;
   }
+  if (exec) { GN_CUDA(cudaStreamSynchronize(s)); cudaGraphExecDestroy(exec); cudaGraphDestroy(graph); }
   GN_CUDA(cudaEventRecord(m->ev[2], s));
   GN_CUDA(cudaMemcpyAsync(out_tokens, m->out_tokens.p, sizeof(int32_t) * (size_t)rows * max_tokens, cudaMemcpyDeviceToHost, s));
   GN_CUDA(cudaMemcpyAsync(out_lengths, m->out_lengths.p, sizeof(int32_t) * rows, cudaMemcpyDeviceToHost, s));

@@ -70,7 +70,7 @@ int smear_launch(const float* E, float* X, const float* prev_in, float* prev_out
 
 // ---------------------------------------------------------- mix / norm / backout
 __global__ void __launch_bounds__(WPB * 32) mix_norm_kernel(const float* X, const float* X0, const float* rho, const float* chi, int layer, float* Xin,
-                                                            float* H, int64_t rows, int d) {
+                                                            float* H, float* Hh, float* Hl, int64_t rows, int d) {
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int64_t r = (int64_t)blockIdx.x * WPB + warp;
   if (r >= rows) return;
@@ -84,18 +84,22 @@ __global__ void __launch_bounds__(WPB * 32) mix_norm_kernel(const float* X, cons
   }
   ss = warp_sum(ss);
   float inv = row_inv_rms(ss, d);
-  for (int c = lane; c < d; c += 32) H[r * d + c] = Xin[r * d + c] * inv;
+  for (int c = lane; c < d; c += 32) {
+    float v = Xin[r * d + c] * inv;
+    H[r * d + c] = v;
+    if (Hh) { float h, l; split_tf32(v, h, l); Hh[r * d + c] = h; Hl[r * d + c] = l; }
+  }
 }
-int mix_norm_launch(const float* X, const float* X0, const float* rho, const float* chi, int layer, float* Xin, float* H, int64_t rows, int d,
-                    cudaStream_t s) {
+int mix_norm_launch(const float* X, const float* X0, const float* rho, const float* chi, int layer, float* Xin, float* H, float* Hh, float* Hl,
+                    int64_t rows, int d, cudaStream_t s) {
   if (rows <= 0) return GN_OK;
-  mix_norm_kernel<<<ceil_div(rows, WPB), WPB * 32, 0, s>>>(X, X0, rho, chi, layer, Xin, H, rows, d);
+  mix_norm_kernel<<<ceil_div(rows, WPB), WPB * 32, 0, s>>>(X, X0, rho, chi, layer, Xin, H, Hh, Hl, rows, d);
   GN_LAUNCH_CHECK();
   return GN_OK;
 }
 
 __global__ void __launch_bounds__(WPB * 32) backout_norm_kernel(const float* X, const float* BO, const float* lambda_b, const int32_t* sel, float* FP,
-                                                                float* Y, int64_t rows, int d) {
+                                                                float* Y, float* Yh, float* Yl, int64_t rows, int d) {
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int64_t r = (int64_t)blockIdx.x * WPB + warp;
   if (r >= rows) return;
@@ -114,18 +118,20 @@ __global__ void __launch_bounds__(WPB * 32) backout_norm_kernel(const float* X, 
   for (int c = lane; c < d; c += 32) {
     float v = X[src * d + c];
     if (BO) v = v + lam * BO[src * d + c];
-    Y[r * d + c] = v * inv;
+    v = v * inv;
+    Y[r * d + c] = v;
+    if (Yh) { float h, l; split_tf32(v, h, l); Yh[r * d + c] = h; Yl[r * d + c] = l; }
   }
 }
-int backout_norm_launch(const float* X, const float* BO, const float* lambda_b, const int32_t* sel, float* FP, float* Y, int64_t rows, int d,
-                        cudaStream_t s) {
+int backout_norm_launch(const float* X, const float* BO, const float* lambda_b, const int32_t* sel, float* FP, float* Y, float* Yh, float* Yl,
+                        int64_t rows, int d, cudaStream_t s) {
   if (rows <= 0) return GN_OK;
-  backout_norm_kernel<<<ceil_div(rows, WPB), WPB * 32, 0, s>>>(X, BO, lambda_b, sel, FP, Y, rows, d);
+  backout_norm_kernel<<<ceil_div(rows, WPB), WPB * 32, 0, s>>>(X, BO, lambda_b, sel, FP, Y, Yh, Yl, rows, d);
   GN_LAUNCH_CHECK();
   return GN_OK;
 }
-int norm_launch(const float* X, float* Y, int64_t rows, int d, cudaStream_t s) {
-  return backout_norm_launch(X, nullptr, nullptr, nullptr, nullptr, Y, rows, d, s);
+int norm_launch(const float* X, float* Y, float* Yh, float* Yl, int64_t rows, int d, cudaStream_t s) {
+  return backout_norm_launch(X, nullptr, nullptr, nullptr, nullptr, Y, Yh, Yl, rows, d, s);
 }
 
 // ----------------------------------------------------------------- qkv post
@@ -269,6 +275,8 @@ int add_i32_launch(int32_t* dst, int32_t delta, int64_t n, cudaStream_t s) {
   if (n <= 0) return GN_OK;
   add_i32_kernel<<<ceil_div(n, 256), 256, 0, s>>>(dst, delta, n); GN_LAUNCH_CHECK(); return GN_OK;
 }
+__global__ void add_u32_kernel(uint32_t* dst, uint32_t v) { *dst += v; }
+int add_u32_launch(uint32_t* dst, uint32_t delta, cudaStream_t s) { add_u32_kernel<<<1, 1, 0, s>>>(dst, delta); GN_LAUNCH_CHECK(); return GN_OK; }
 int ctx_from_pos_launch(const int32_t* pos, int32_t* ctx, int64_t n, cudaStream_t s) {
   if (n <= 0) return GN_OK;
   ctx_from_pos_kernel<<<ceil_div(n, 256), 256, 0, s>>>(pos, ctx, n); GN_LAUNCH_CHECK(); return GN_OK;

@@ -26,13 +26,14 @@ int smear_launch(const float* E, float* X, const float* prev_in, float* prev_out
                  const float* lambda, int B, int T, int d, cudaStream_t s);
 
 // Xin = rho[l]*X + chi[l]*X0 ; H = rmsnorm(Xin)   (model/transformer.go:312, model/block.go:39)
-int mix_norm_launch(const float* X, const float* X0, const float* rho, const float* chi, int layer, float* Xin, float* H, int64_t rows, int d,
-                    cudaStream_t s);
-// Y = rmsnorm(X)
-int norm_launch(const float* X, float* Y, int64_t rows, int d, cudaStream_t s);
+// Hh/Hl (nullable): the tf32 hi/lo split of H for the tensor-core product that consumes it.
+int mix_norm_launch(const float* X, const float* X0, const float* rho, const float* chi, int layer, float* Xin, float* H, float* Hh, float* Hl,
+                    int64_t rows, int d, cudaStream_t s);
+// Y = rmsnorm(X) (+ optional split)
+int norm_launch(const float* X, float* Y, float* Yh, float* Yl, int64_t rows, int d, cudaStream_t s);
 // FP = X - lambda_b*BO (BO nullable) ; Y = rmsnorm(FP).  When sel != null row i reads X/BO row sel[i].
-int backout_norm_launch(const float* X, const float* BO, const float* lambda_b, const int32_t* sel, float* FP, float* Y, int64_t rows, int d,
-                        cudaStream_t s);
+int backout_norm_launch(const float* X, const float* BO, const float* lambda_b, const int32_t* sel, float* FP, float* Y, float* Yh, float* Yl,
+                        int64_t rows, int d, cudaStream_t s);
 
 struct QkvPost {
   float* qkv = nullptr;        // [rows, (Hq+2Hkv)*D]  in: projections; out: q,k normalised, v final (in place)
@@ -57,6 +58,7 @@ int kv_replicate_launch(float* cache, int64_t layer_stride, int n_layer2, int64_
                         int group, int len, float* prev, int d, int32_t* pos, cudaStream_t s);
 int fill_i32_launch(int32_t* dst, int32_t value, int64_t n, cudaStream_t s);
 int add_i32_launch(int32_t* dst, int32_t delta, int64_t n, cudaStream_t s);
+int add_u32_launch(uint32_t* dst, uint32_t delta, cudaStream_t s);
 // ctx[i] = pos[i] + 1
 int ctx_from_pos_launch(const int32_t* pos, int32_t* ctx, int64_t n, cudaStream_t s);
 // Engine bookkeeping per decode step (inference/engine.go:256-319,349-367): append the
