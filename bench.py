@@ -30,6 +30,17 @@ if str(ROOT) not in sys.path:
 
 from gonano_b200 import synthetic  # noqa: E402
 
+_STDOUT_FD = None
+
+
+def emit(line: dict) -> None:
+    data = (json.dumps(line) + "\n").encode()
+    if _STDOUT_FD is None:
+        sys.stdout.write(data.decode()); sys.stdout.flush()
+    else:
+        os.write(_STDOUT_FD, data)
+
+
 WORKLOAD = dict(name="d12", n_prompts=64, prompt_len=128, group=8, max_tokens=256, temperature=1.0, top_k=50, seed=0)
 METRIC, UNIT = "rl_steps_per_s_d12", "steps/s"
 
@@ -146,7 +157,7 @@ def run_reference(args):
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": "dense d12 RL step: 64 prompts x G=8, 128 prompt tokens, 256 new tokens, vocab 32768 (bounded sample, extrapolated)"},
             "cpu_baseline": best, "e2e": {"value": best["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line))
+    emit(line)
     return 0
 
 
@@ -210,7 +221,7 @@ def run_ours(args):
         return rewards_all[lo * G:hi * G]
 
     all_reduce = gdist.GradAllReduce(model, local, stream) if world > 1 else None
-    phases = ["prefill", "decode", "train_forward", "loss", "train_backward"]
+    phases = ["prefill", "decode", "train_forward", "loss", "train_backward", "allreduce"]
     state = {"step": 0}
 
     def one_step():
@@ -218,7 +229,9 @@ def run_ours(args):
         state["step"] += 1
         res = rl_step(model, prompts, G, w["max_tokens"], w["temperature"], w["top_k"], seeds, reward_fn, advantage_mode=0,
                       all_reduce=all_reduce, max_len_fn=gdist.global_max_len if world > 1 else None)
-        return res, {p: model.phase_ms(p) for p in phases}
+        ph = {p: model.phase_ms(p) for p in phases if p != "allreduce"}
+        ph["allreduce"] = all_reduce.last_ms() if all_reduce is not None else 0.0
+        return res, ph
 
     for _ in range(args.warmup):
         one_step()
@@ -313,13 +326,19 @@ def run_ours(args):
         "cpu_baseline": cpu,
         "peaks": pk,
     }
-    print(json.dumps(line))
+    emit(line)
     if world > 1:
         dist.destroy_process_group()
     return 0
 
 
 def main():
+    # Libraries (NCCL prints its version) write to stdout; the contract is ONE JSON line there,
+    # so everything else goes to stderr and the line is written to the original descriptor.
+    global _STDOUT_FD
+    sys.stdout.flush()
+    _STDOUT_FD = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2)

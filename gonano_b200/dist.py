@@ -59,10 +59,23 @@ class GradAllReduce:
         self.tensor = device_tensor(address, count, device)
         self.stream = stream
         self.bytes = count * 4
+        self._start = torch.cuda.Event(enable_timing=True)
+        self._end = torch.cuda.Event(enable_timing=True)
+        self._timed = False
 
     def __call__(self, model=None):
         with self.torch.cuda.stream(self.stream):
+            self._start.record(self.stream)
             all_reduce_sum(self.tensor)
+            self._end.record(self.stream)
+        self._timed = True
+
+    def last_ms(self) -> float:
+        """Device time of the last all-reduce (includes waiting for the slowest rank)."""
+        if not self._timed:
+            return 0.0
+        self._end.synchronize()
+        return float(self._start.elapsed_time(self._end))
 
 
 def global_max_len(local_max_len: int) -> int:
