@@ -907,7 +907,8 @@ template <int DP, int RATIO>
 __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restrict__ q, int64_t q_rstride, const float* __restrict__ kcache,
                                                           const float* __restrict__ vcache, int64_t row_stride, int64_t head_stride,
                                                           const int32_t* __restrict__ ctx_len, int Hq, int Hkv, int D, int window, float* __restrict__ out,
-                                                          int64_t o_rstride, float* __restrict__ part_acc, float* __restrict__ part_ms, int splits) {
+                                                          int64_t o_rstride, float* __restrict__ part_acc, float* __restrict__ part_ms, int splits,
+                                                          float* __restrict__ out_hi, float* __restrict__ out_lo) {
   // DP = head_dim rounded up to a multiple of 32; channels >= D are zero padding.
   constexpr int E = DP / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -985,7 +986,10 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restric
     }
     int hq = hk * RATIO + h;
     if (splits == 1) {
-      out[(int64_t)row * o_rstride + (int64_t)hq * D + c] = tot > 0 ? acc / tot : 0.0f;
+      const float v = tot > 0 ? acc / tot : 0.0f;
+      const int64_t oi = (int64_t)row * o_rstride + (int64_t)hq * D + c;
+      out[oi] = v;
+      if (out_hi) { float h2, l2; split_tf32(v, h2, l2); out_hi[oi] = h2; out_lo[oi] = l2; }
     } else {
       int64_t pi = ((int64_t)row * Hq + hq) * splits + split;
       part_acc[pi * D + c] = acc;
@@ -993,7 +997,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restric
     }
   }
 }
-__global__ void __launch_bounds__(128) attn_decode_combine_kernel(const float* part_acc, const float* part_ms, int splits, int Hq, int D, float* out, int64_t o_rstride) {
+__global__ void __launch_bounds__(128) attn_decode_combine_kernel(const float* part_acc, const float* part_ms, int splits, int Hq, int D, float* out, int64_t o_rstride,
+                                                                  float* out_hi, float* out_lo) {
   int row = blockIdx.x / Hq, hq = blockIdx.x % Hq;
   int64_t base = ((int64_t)row * Hq + hq) * splits;
   float gm = -INFINITY;
@@ -1003,7 +1008,10 @@ __global__ void __launch_bounds__(128) attn_decode_combine_kernel(const float* p
   for (int c = threadIdx.x; c < D; c += 128) {
     float acc = 0;
     for (int s = 0; s < splits; ++s) { float m = part_ms[(base + s) * 2]; if (m != -INFINITY) acc += part_acc[(base + s) * D + c] * __expf(m - gm); }
-    out[(int64_t)row * o_rstride + (int64_t)hq * D + c] = tot > 0 ? acc / tot : 0.0f;
+    const float v = tot > 0 ? acc / tot : 0.0f;
+    const int64_t oi = (int64_t)row * o_rstride + (int64_t)hq * D + c;
+    out[oi] = v;
+    if (out_hi) { float h2, l2; split_tf32(v, h2, l2); out_hi[oi] = h2; out_lo[oi] = l2; }
   }
 }
 
@@ -1018,13 +1026,13 @@ int attention_decode_splits(int rows, int Hkv, int max_ctx) {
 template <int DP, int RATIO>
 static int decode_go(const float* q, int64_t q_rstride, const float* kcache, const float* vcache, int64_t row_stride, int64_t head_stride,
                      const int32_t* ctx_len, int rows, int Hq, int Hkv, int D, int window, float* out, int64_t o_rstride, float* part_acc, float* part_ms,
-                     int splits, cudaStream_t s) {
+                     int splits, cudaStream_t s, float* out_hi, float* out_lo) {
   dim3 grid(rows * Hkv, splits);
   attn_decode_kernel<DP, RATIO><<<grid, 128, 0, s>>>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, Hq, Hkv, D, window, out, o_rstride,
-                                                     part_acc, part_ms, splits);
+                                                     part_acc, part_ms, splits, out_hi, out_lo);
   GN_LAUNCH_CHECK();
   if (splits > 1) {
-    attn_decode_combine_kernel<<<rows * Hq, 128, 0, s>>>(part_acc, part_ms, splits, Hq, D, out, o_rstride);
+    attn_decode_combine_kernel<<<rows * Hq, 128, 0, s>>>(part_acc, part_ms, splits, Hq, D, out, o_rstride, out_hi, out_lo);
     GN_LAUNCH_CHECK();
   }
   return GN_OK;
@@ -1032,11 +1040,11 @@ static int decode_go(const float* q, int64_t q_rstride, const float* kcache, con
 
 int attention_decode_launch(const float* q, int64_t q_rstride, const float* kcache, const float* vcache, int64_t row_stride, int64_t head_stride,
                             const int32_t* ctx_len, int rows, int Hq, int Hkv, int D, int window, float* out, int64_t o_rstride,
-                            float* part_acc, float* part_ms, int splits, cudaStream_t s) {
+                            float* part_acc, float* part_ms, int splits, cudaStream_t s, float* out_hi, float* out_lo) {
   if (rows <= 0) return GN_OK;
   int ratio = Hq / Hkv;
   const int dp = (D + 31) / 32 * 32;
-#define GN_DEC(DD, RR) if (dp == DD && ratio == RR) return decode_go<DD, RR>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, rows, Hq, Hkv, D, window, out, o_rstride, part_acc, part_ms, splits, s)
+#define GN_DEC(DD, RR) if (dp == DD && ratio == RR) return decode_go<DD, RR>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, rows, Hq, Hkv, D, window, out, o_rstride, part_acc, part_ms, splits, s, out_hi, out_lo)
   GN_DEC(128, 1); GN_DEC(128, 2); GN_DEC(128, 3); GN_DEC(128, 4); GN_DEC(128, 8);
   GN_DEC(96, 1); GN_DEC(96, 2); GN_DEC(96, 4);
   GN_DEC(64, 1); GN_DEC(64, 2); GN_DEC(64, 3); GN_DEC(64, 4); GN_DEC(64, 8);

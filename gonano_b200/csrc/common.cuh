@@ -128,6 +128,37 @@ enum GemmEpilogue {
   EPI_SOFTCAP = 4,   // C = cap * tanh(acc / cap)   (cap = scalar)
   EPI_RELU2_BWD = 5, // C = acc * 2*max(aux,0)      (aux = saved pre-activation)
 };
+// A product left unreduced by gemm_dispatch: value(m, n) = sum over z < splits of ptr[z*stride + m*ld + n],
+// added in the order z = 0, 1, ... (the same order the stand-alone reduction uses).
+struct Partials {
+  const float* ptr = nullptr; int splits = 0; int64_t stride = 0; int64_t ld = 0;
+  __host__ __device__ bool on() const { return ptr != nullptr; }
+#ifdef __CUDACC__
+  __device__ __forceinline__ float at(int64_t m, int64_t n) const {
+    const float* q = ptr + m * ld + n;
+    float a = q[0];
+    for (int z = 1; z < splits; ++z) a += q[(int64_t)z * stride];
+    return a;
+  }
+  // Four consecutive columns (n, ld and stride multiples of 4, ptr 16-byte aligned).  The loads of
+  // eight splits are issued together; the additions keep the order z = 0, 1, ...
+  __device__ __forceinline__ float4 at4(int64_t m, int64_t n) const {
+    const float* q = ptr + m * ld + n;
+    float4 a = *reinterpret_cast<const float4*>(q);
+    for (int z0 = 1; z0 < splits; z0 += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (z0 + j < splits) v[j] = *reinterpret_cast<const float4*>(q + (int64_t)(z0 + j) * stride);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (z0 + j < splits) { a.x += v[j].x; a.y += v[j].y; a.z += v[j].z; a.w += v[j].w; }
+    }
+    return a;
+  }
+#endif
+};
+
 struct GemmArgs {
   const float* A = nullptr; const float* B = nullptr; float* C = nullptr;
   int M = 0, N = 0, K = 0;
@@ -141,6 +172,10 @@ struct GemmArgs {
   const float* a_hi = nullptr; const float* a_lo = nullptr;
   // Tensor-core path only: also write the split of the output (pitch ldc) for the next product.
   float* c_hi = nullptr; float* c_lo = nullptr;
+  // When set (epilogue must be EPI_STORE): the product may be left as split-K partial tiles for the
+  // consumer kernel to sum; *leave says where they are (splits == 1 and ptr == C when it was not split).
+  // The partial tiles live in a workspace that the next product on the stream reuses.
+  Partials* leave = nullptr;
 };
 int gemm_simt(const GemmArgs& args, cudaStream_t stream);
 // kind 0: SIMT float32.  kind 1: tcgen05 3xTF32 where the shape allows it, else SIMT.

@@ -509,7 +509,7 @@ float* g_splitk_ws = nullptr;
 size_t g_splitk_floats = 0;
 
 template <int BN, int STAGES>
-int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int M, int N, int K, int splits, cudaStream_t s) {
+int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int M, int N, int K, int splits, cudaStream_t s, Partials* leave = nullptr) {
   using S = TcSmem<BN, STAGES>;
   static bool configured = false;
   if (!configured) {
@@ -533,7 +533,10 @@ int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int
   dim3 grid(ceil_div(N, BN), ceil_div(M, TBM), splits);
   gemm_tc_kernel<BN, STAGES><<<grid, 64 + 32 * (BN > 128 ? 8 : 4), S::TOTAL, s>>>(mah, mal, mbh, mbl, ep, M, N, K, g_err_flag);
   GN_LAUNCH_CHECK();
-  if (splits > 1) {
+  if (leave) {
+    if (splits > 1) *leave = Partials{g_splitk_ws, splits, (int64_t)M * N, (int64_t)N};
+    else *leave = Partials{ep_in.C, 1, 0, ep_in.ldc};
+  } else if (splits > 1) {
     int blocks = (int)std::min<int64_t>(((int64_t)M * (N / 4) + 255) / 256, (int64_t)kNumSM * 8);
     splitk_reduce_kernel<<<blocks, 256, 0, s>>>(g_splitk_ws, splits, (int64_t)M * N, ep_in, M, N);
     GN_LAUNCH_CHECK();
@@ -580,8 +583,8 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
   // L2, and a 256-column tile reads the A operand once for twice the work (96 KB per k-block for
   // two 128 x 128 units instead of 128 KB).
   if (splits == 1 && g.N >= 512 && (int64_t)ceil_div(g.M, TBM) * ceil_div(g.N, 256) >= kNumSM * 3 / 2)
-    return launch_tc<256, 2>(a, b, ep, g.M, g.N, g.K, 1, s);
-  return launch_tc<128, 3>(a, b, ep, g.M, g.N, g.K, splits, s);
+    return launch_tc<256, 2>(a, b, ep, g.M, g.N, g.K, 1, s, g.leave);
+  return launch_tc<128, 3>(a, b, ep, g.M, g.N, g.K, splits, s, g.leave);
 }
 
 // Drops the cached splits of parameter tensors (call after the parameters change).

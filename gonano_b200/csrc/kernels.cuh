@@ -56,7 +56,8 @@ int attention_combine_launch(const float* acc, const float* mx, const float* sm,
 // Decode: one query token per row over the KV cache [row][hk][max_seq][D]; ctx_len[row] keys (device array).
 int attention_decode_launch(const float* q, int64_t q_rstride, const float* kcache, const float* vcache, int64_t row_stride, int64_t head_stride,
                             const int32_t* ctx_len, int rows, int Hq, int Hkv, int D, int window, float* out, int64_t o_rstride,
-                            float* part_acc, float* part_ms, int splits, cudaStream_t s);
+                            float* part_acc, float* part_ms, int splits, cudaStream_t s,
+                            float* out_hi = nullptr, float* out_lo = nullptr);   // optional tf32 hi/lo split of the output, same pitch
 int attention_decode_splits(int rows, int Hkv, int max_ctx);
 
 // ----------------------------------------------------------------- sampler.cu

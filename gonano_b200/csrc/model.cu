@@ -243,6 +243,7 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
   const int64_t layer_stride = (int64_t)a.cache_rows * Hkv * a.max_seq * D;
   const float* x_prev = b.X0;
   const float* backout = nullptr;
+  Partials pending;   // the previous layer's output projection, not yet added to its residual
   for (int l = 0; l < L; ++l) {
     const LayerOffsets& o = m->lo[l];
     float *Xin, *H, *QKV, *O, *MID, *Mn, *U, *HID, *XOUT;
@@ -253,12 +254,26 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
       Xin = b.Xa; H = b.H; QKV = b.QKV; O = b.O; MID = b.Xa; Mn = b.M; U = nullptr; HID = b.HID; XOUT = b.Xa;
     }
     const bool tc = m->ctx->gemm_kind == 1;
-    GN_TRY(mix_norm_launch(x_prev, b.X0, m->p(m->off_rho), m->p(m->off_chi), l, Xin, H, tc ? b.S1h : nullptr, tc ? b.S1l : nullptr, rows, d, s));
+    // Inference on the tensor-core path: products whose K loop was split over CTAs are left as partial
+    // tiles and summed by the kernel that consumes them (one launch less per product).
+    const bool fuse = tc && !train && sum_norm_supported(d) && D % 4 == 0;
+    if (pending.on()) {
+      SumNorm sn; sn.R = x_prev; sn.part = pending; sn.X0 = b.X0; sn.rho = m->p(m->off_rho); sn.chi = m->p(m->off_chi); sn.layer = l;
+      if (l - 1 == L / 2) { sn.Xsum = b.BO; backout = b.BO; }
+      sn.V = Xin; sn.Y = H; sn.Yh = b.S1h; sn.Yl = b.S1l; sn.rows = rows; sn.d = d;
+      GN_TRY(sum_norm_launch(sn, s));
+      pending = Partials();
+    } else {
+      GN_TRY(mix_norm_launch(x_prev, b.X0, m->p(m->off_rho), m->p(m->off_chi), l, Xin, H, tc ? b.S1h : nullptr, tc ? b.S1l : nullptr, rows, d, s));
+    }
     // q, k, v projections as one GEMM against [c_q; c_k; c_v]
+    Partials qkv_part;
     { GemmArgs g; g.A = H; g.lda = d; g.B = m->p(o.qkv); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = QKV; g.ldc = W; g.M = (int)rows; g.N = W; g.K = d;
+      if (fuse) g.leave = &qkv_part;
       if (tc) { g.a_hi = b.S1h; g.a_lo = b.S1l; } GN_TRY(gemm(m, g)); }
     QkvPost qp;
     qp.qkv = QKV; qp.H = H; qp.ids = a.ids;
+    if (qkv_part.on() && qkv_part.ptr != QKV) qp.part = qkv_part;
     qp.ve_table = o.has_ve ? m->p(o.ve) : nullptr; qp.ve_gate = o.has_ve ? m->p(o.ve_gate) : nullptr;
     qp.cosv = m->cosb.f(); qp.sinv = m->sinb.f();
     qp.qk_rot = train ? b.layers[l].QKROT : nullptr; qp.ve_sig = train ? b.layers[l].VESIG : nullptr;
@@ -268,11 +283,13 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
     }
     qp.B = B; qp.T = T; qp.Hq = Hq; qp.Hkv = Hkv; qp.D = D; qp.R = m->R; qp.d = d;
     GN_TRY(qkv_post_launch(qp, s));
+    bool o_split = false;   // the attention kernel also wrote the tf32 split of O
     if (a.mode == MODE_DECODE) {
       int splits = attention_decode_splits(B, Hkv, a.max_seq);
+      o_split = tc && Hq * D <= 4 * d;
       GN_TRY(attention_decode_launch(QKV, W, m->cache.f() + (int64_t)(2 * l) * layer_stride, m->cache.f() + (int64_t)(2 * l + 1) * layer_stride,
                                      (int64_t)Hkv * a.max_seq * D, (int64_t)a.max_seq * D, m->ctxlen.i(), B, Hq, Hkv, D, m->windows[l], O,
-                                     (int64_t)Hq * D, m->part_acc.f(), m->part_ms.f(), splits, s));
+                                     (int64_t)Hq * D, m->part_acc.f(), m->part_ms.f(), splits, s, o_split ? b.S4h : nullptr, o_split ? b.S4l : nullptr));
     } else {
       AttnShape sh;
       sh.B = B; sh.Hq = Hq; sh.Hkv = Hkv; sh.D = D; sh.Tq = T; sh.Tk = T;
@@ -280,30 +297,54 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
       sh.o_bstride = (int64_t)T * Hq * D; sh.o_tstride = (int64_t)Hq * D; sh.window = m->windows[l]; sh.offset0 = 0;
       GN_TRY(attention_forward_launch(sh, QKV, QKV + (int64_t)Hq * D, QKV + (int64_t)(Hq + Hkv) * D, O, train ? b.layers[l].LSE : nullptr, s));
     }
-    // MID = Xin + O Wo^T
-    { GemmArgs g; g.A = O; g.lda = (int64_t)Hq * D; g.B = m->p(o.proj); g.b_static = 1; g.ldb = (int64_t)Hq * D; g.b_trans = 1; g.C = MID; g.ldc = d; g.M = (int)rows; g.N = d; g.K = Hq * D;
-      g.epilogue = EPI_RESIDUAL; g.aux = Xin; g.ldaux = d; GN_TRY(gemm(m, g)); }
-    GN_TRY(norm_launch(MID, Mn, tc ? b.S1h : nullptr, tc ? b.S1l : nullptr, rows, d, s));
+    if (fuse) {
+      // MID = Xin + O Wo^T, summed and normalised in one kernel (H is free after qkv_post and takes an unsplit product)
+      Partials op;
+      { GemmArgs g; g.A = O; g.lda = (int64_t)Hq * D; g.B = m->p(o.proj); g.b_static = 1; g.ldb = (int64_t)Hq * D; g.b_trans = 1; g.C = H; g.ldc = d; g.M = (int)rows; g.N = d; g.K = Hq * D;
+        g.leave = &op; if (o_split) { g.a_hi = b.S4h; g.a_lo = b.S4l; } GN_TRY(gemm(m, g)); }
+      SumNorm sn; sn.R = Xin; sn.part = op; sn.V = MID; sn.Y = Mn; sn.Yh = b.S1h; sn.Yl = b.S1l; sn.rows = rows; sn.d = d;
+      GN_TRY(sum_norm_launch(sn, s));
+    } else {
+      // MID = Xin + O Wo^T
+      { GemmArgs g; g.A = O; g.lda = (int64_t)Hq * D; g.B = m->p(o.proj); g.b_static = 1; g.ldb = (int64_t)Hq * D; g.b_trans = 1; g.C = MID; g.ldc = d; g.M = (int)rows; g.N = d; g.K = Hq * D;
+        g.epilogue = EPI_RESIDUAL; g.aux = Xin; g.ldaux = d; if (o_split) { g.a_hi = b.S4h; g.a_lo = b.S4l; } GN_TRY(gemm(m, g)); }
+      GN_TRY(norm_launch(MID, Mn, tc ? b.S1h : nullptr, tc ? b.S1l : nullptr, rows, d, s));
+    }
     // HID = relu(M Wfc^T)^2   (training also keeps the pre-activation)
     { GemmArgs g; g.A = Mn; g.lda = d; g.B = m->p(o.fc); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = HID; g.ldc = 4 * d; g.M = (int)rows; g.N = 4 * d; g.K = d;
       g.epilogue = EPI_RELU2; g.aux = U; g.ldaux = 4 * d;
       if (tc) { g.a_hi = b.S1h; g.a_lo = b.S1l; g.c_hi = b.S4h; g.c_lo = b.S4l; } GN_TRY(gemm(m, g)); }
-    // XOUT = MID + HID Wp^T
-    { GemmArgs g; g.A = HID; g.lda = 4 * d; g.B = m->p(o.mproj); g.b_static = 1; g.ldb = 4 * d; g.b_trans = 1; g.C = XOUT; g.ldc = d; g.M = (int)rows; g.N = d; g.K = 4 * d;
-      g.epilogue = EPI_RESIDUAL; g.aux = MID; g.ldaux = d;
-      if (tc) { g.a_hi = b.S4h; g.a_lo = b.S4l; } GN_TRY(gemm(m, g)); }
-    if (l == L / 2) {
-      if (train) backout = XOUT;
-      else { GN_CUDA(cudaMemcpyAsync(b.BO, XOUT, sizeof(float) * rows * d, cudaMemcpyDeviceToDevice, s)); backout = b.BO; }
+    // XOUT = MID + HID Wp^T.  When fused the sum is taken by the next layer's mix (or the final norm);
+    // a layer whose output is also the backout tap of the last layer is materialised.
+    const bool fuse_out = fuse && !(l == L / 2 && l == L - 1);
+    if (fuse_out) {
+      // Mn was consumed by the product above and takes an unsplit product
+      GemmArgs g; g.A = HID; g.lda = 4 * d; g.B = m->p(o.mproj); g.b_static = 1; g.ldb = 4 * d; g.b_trans = 1; g.C = Mn; g.ldc = d; g.M = (int)rows; g.N = d; g.K = 4 * d;
+      g.leave = &pending; g.a_hi = b.S4h; g.a_lo = b.S4l; GN_TRY(gemm(m, g));
+      x_prev = MID;   // the residual the pending product is added to
+    } else {
+      { GemmArgs g; g.A = HID; g.lda = 4 * d; g.B = m->p(o.mproj); g.b_static = 1; g.ldb = 4 * d; g.b_trans = 1; g.C = XOUT; g.ldc = d; g.M = (int)rows; g.N = d; g.K = 4 * d;
+        g.epilogue = EPI_RESIDUAL; g.aux = MID; g.ldaux = d;
+        if (tc) { g.a_hi = b.S4h; g.a_lo = b.S4l; } GN_TRY(gemm(m, g)); }
+      if (l == L / 2) {
+        if (train) backout = XOUT;
+        else { GN_CUDA(cudaMemcpyAsync(b.BO, XOUT, sizeof(float) * rows * d, cudaMemcpyDeviceToDevice, s)); backout = b.BO; }
+      }
+      x_prev = XOUT;
     }
-    x_prev = XOUT;
   }
   // final: y = norm(x - lambda_b * backout); logits = softcap(y W_lm^T)[:, :V]
   int64_t lrows = rows;
   const int32_t* sel = nullptr;
   if (a.mode == MODE_PREFILL) { lrows = B; sel = m->sel.i(); }
   const bool tc_head = m->ctx->gemm_kind == 1;
-  GN_TRY(backout_norm_launch(x_prev, backout, m->p(m->off_backout), sel, train ? b.FP : nullptr, b.Y, tc_head ? b.S1h : nullptr, tc_head ? b.S1l : nullptr, lrows, d, s));
+  if (pending.on()) {
+    SumNorm sn; sn.R = x_prev; sn.part = pending; sn.sel = sel; sn.BO = backout; sn.lambda_b = m->p(m->off_backout);
+    sn.Y = b.Y; sn.Yh = b.S1h; sn.Yl = b.S1l; sn.rows = lrows; sn.d = d;
+    GN_TRY(sum_norm_launch(sn, s));
+  } else {
+    GN_TRY(backout_norm_launch(x_prev, backout, m->p(m->off_backout), sel, train ? b.FP : nullptr, b.Y, tc_head ? b.S1h : nullptr, tc_head ? b.S1l : nullptr, lrows, d, s));
+  }
   { GemmArgs g; g.A = b.Y; g.lda = d; g.B = m->p(m->off_lm); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = b.LOGITS; g.ldc = V; g.M = (int)lrows; g.N = V; g.K = d;
     g.epilogue = EPI_SOFTCAP; g.scalar = kSoftcap;
     if (tc_head) { g.a_hi = b.S1h; g.a_lo = b.S1l; } GN_TRY(gemm(m, g)); }

@@ -134,10 +134,59 @@ int norm_launch(const float* X, float* Y, float* Yh, float* Yl, int64_t rows, in
   return backout_norm_launch(X, nullptr, nullptr, nullptr, nullptr, Y, Yh, Yl, rows, d, s);
 }
 
+// One block per row, one float4 per thread.
+__global__ void __launch_bounds__(1024) sum_norm_kernel(SumNorm p) {
+  __shared__ float scratch[33];
+  const int64_t r = blockIdx.x;
+  const int64_t src = p.sel ? p.sel[r] : r;
+  const int c = threadIdx.x * 4;
+  const bool live = c < p.d;
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (live) {
+    v = *reinterpret_cast<const float4*>(p.R + src * p.d + c);
+    if (p.part.on()) { const float4 q = p.part.at4(src, c); v.x = __fadd_rn(q.x, v.x); v.y = __fadd_rn(q.y, v.y); v.z = __fadd_rn(q.z, v.z); v.w = __fadd_rn(q.w, v.w); }
+    if (p.Xsum) *reinterpret_cast<float4*>(p.Xsum + r * p.d + c) = v;
+    if (p.X0) {
+      // combineResidual: two rounded products, then the sum (model/transformer.go:544-551)
+      const float rw = p.rho[p.layer], xw = p.chi[p.layer];
+      const float4 x0 = *reinterpret_cast<const float4*>(p.X0 + r * p.d + c);
+      v.x = __fadd_rn(__fmul_rn(rw, v.x), __fmul_rn(xw, x0.x)); v.y = __fadd_rn(__fmul_rn(rw, v.y), __fmul_rn(xw, x0.y));
+      v.z = __fadd_rn(__fmul_rn(rw, v.z), __fmul_rn(xw, x0.z)); v.w = __fadd_rn(__fmul_rn(rw, v.w), __fmul_rn(xw, x0.w));
+    }
+    if (p.BO) {
+      const float lam = -p.lambda_b[0];
+      const float4 bo = *reinterpret_cast<const float4*>(p.BO + src * p.d + c);
+      v.x = v.x + lam * bo.x; v.y = v.y + lam * bo.y; v.z = v.z + lam * bo.z; v.w = v.w + lam * bo.w;
+    }
+    if (p.V) *reinterpret_cast<float4*>(p.V + r * p.d + c) = v;
+  }
+  float ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
+  ss = block_sum(ss, scratch);
+  const float inv = row_inv_rms(ss, p.d);
+  if (live) {
+    const float4 y = make_float4(v.x * inv, v.y * inv, v.z * inv, v.w * inv);
+    *reinterpret_cast<float4*>(p.Y + r * p.d + c) = y;
+    if (p.Yh) {
+      float4 h, l;
+      split_tf32(y.x, h.x, l.x); split_tf32(y.y, h.y, l.y); split_tf32(y.z, h.z, l.z); split_tf32(y.w, h.w, l.w);
+      *reinterpret_cast<float4*>(p.Yh + r * p.d + c) = h;
+      *reinterpret_cast<float4*>(p.Yl + r * p.d + c) = l;
+    }
+  }
+}
+int sum_norm_launch(const SumNorm& p, cudaStream_t s) {
+  if (p.rows <= 0) return GN_OK;
+  GN_REQUIRE(sum_norm_supported(p.d), "sum_norm: width %d unsupported", p.d);
+  const int threads = (p.d / 4 + 31) / 32 * 32;
+  sum_norm_kernel<<<(unsigned)p.rows, threads, 0, s>>>(p);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
 // ----------------------------------------------------------------- qkv post
 // One warp per (token row, head slot); slots = Hq query heads, Hkv key heads, Hkv value heads.
 __global__ void __launch_bounds__(WPB * 32) qkv_post_kernel(QkvPost p) {
-  __shared__ float sh[WPB][128];
+  __shared__ __align__(16) float sh[WPB][128];
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slots = p.Hq + 2 * p.Hkv;
   int64_t idx = (int64_t)blockIdx.x * WPB + warp;
@@ -153,7 +202,11 @@ __global__ void __launch_bounds__(WPB * 32) qkv_post_kernel(QkvPost p) {
 
   if (slot < p.Hq + p.Hkv) {
     // ---- rotary on the trailing R channels, pairs (first half, second half)  (model/rotary.go:43-75)
-    for (int c = lane; c < D; c += 32) buf[c] = x[c];
+    if (p.part.on()) {
+      for (int c = lane * 4; c < D; c += 128) *reinterpret_cast<float4*>(buf + c) = p.part.at4(r, (int64_t)slot * D + c);
+    } else {
+      for (int c = lane; c < D; c += 32) buf[c] = x[c];
+    }
     __syncwarp();
     const int half = p.R / 2, off = D - p.R;
     const float* cw = p.cosv + (int64_t)pos * half; const float* sw = p.sinv + (int64_t)pos * half;
@@ -203,8 +256,12 @@ __global__ void __launch_bounds__(WPB * 32) qkv_post_kernel(QkvPost p) {
       ve = p.ve_table + (int64_t)p.ids[r] * (p.Hkv * D) + (int64_t)hk * D;
     }
     float* vc = p.vcache ? p.vcache + (((int64_t)crow * p.Hkv + hk) * p.max_seq + pos) * D : nullptr;
+    if (p.part.on()) {
+      for (int c = lane * 4; c < D; c += 128) *reinterpret_cast<float4*>(buf + c) = p.part.at4(r, (int64_t)slot * D + c);
+      __syncwarp();
+    }
     for (int c = lane; c < D; c += 32) {
-      float v = x[c];
+      float v = p.part.on() ? buf[c] : x[c];
       if (ve) v += gate * ve[c];
       x[c] = v;
       if (vc) vc[c] = v;
@@ -215,6 +272,7 @@ int qkv_post_launch(const QkvPost& p, cudaStream_t s) {
   int64_t n = (int64_t)p.B * p.T * (p.Hq + 2 * p.Hkv);
   if (n <= 0) return GN_OK;
   GN_REQUIRE(p.D <= 128 && p.R <= p.D && p.R % 2 == 0 && p.R / 2 <= 64, "qkv_post: head_dim %d / rotary %d unsupported", p.D, p.R);
+  GN_REQUIRE(!p.part.on() || p.D % 4 == 0, "qkv_post: unreduced input needs head_dim %% 4 == 0 (got %d)", p.D);
   qkv_post_kernel<<<ceil_div(n, WPB), WPB * 32, 0, s>>>(p);
   GN_LAUNCH_CHECK();
   return GN_OK;

@@ -35,8 +35,27 @@ int norm_launch(const float* X, float* Y, float* Yh, float* Yl, int64_t rows, in
 int backout_norm_launch(const float* X, const float* BO, const float* lambda_b, const int32_t* sel, float* FP, float* Y, float* Yh, float* Yl,
                         int64_t rows, int d, cudaStream_t s);
 
+// Inference glue that also finishes a product left as split-K partial tiles, one block per row:
+//   x = R[src] + sum of the partial tiles at row src        (src = sel[r] when sel != null, else r)
+//   v = rho[layer]*x + chi[layer]*X0[r]   when X0 != null   (the residual mix of the next layer)
+//   v = v - lambda_b*BO[src]              when BO != null   (the backout before the final norm)
+//   y = rmsnorm(v), also written as its tf32 hi/lo split when Yh != null
+// Xsum and V (nullable) receive x and v; each may alias R when sel == null.  Needs d % 4 == 0, d <= 4096.
+struct SumNorm {
+  const float* R = nullptr; Partials part; const int32_t* sel = nullptr;
+  float* Xsum = nullptr;
+  const float* X0 = nullptr; const float* rho = nullptr; const float* chi = nullptr; int layer = 0;
+  const float* BO = nullptr; const float* lambda_b = nullptr;
+  float* V = nullptr;
+  float* Y = nullptr; float* Yh = nullptr; float* Yl = nullptr;
+  int64_t rows = 0; int d = 0;
+};
+int sum_norm_launch(const SumNorm& p, cudaStream_t s);
+inline bool sum_norm_supported(int d) { return d % 4 == 0 && d <= 4096; }
+
 struct QkvPost {
   float* qkv = nullptr;        // [rows, (Hq+2Hkv)*D]  in: projections; out: q,k normalised, v final (in place)
+  Partials part;               // when on: the projections are read from this unreduced product instead of qkv (needs D % 4 == 0)
   const float* H = nullptr;    // [rows, d] attention input (for the value-embedding gate)
   const int32_t* ids = nullptr;
   const float* ve_table = nullptr;  // [Vp, Hkv*D] or null
