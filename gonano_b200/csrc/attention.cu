@@ -207,6 +207,7 @@ int attention_forward_launch(const AttnShape& sh, const float* q, const float* k
   if (sh.Tq <= 0 || sh.B <= 0) return GN_OK;
   GN_REQUIRE(sh.D > 0 && sh.D <= 128, "attention: head_dim %d outside (0,128]", sh.D);
   GN_REQUIRE(sh.Hkv > 0 && sh.Hq % sh.Hkv == 0, "attention: %d query heads not divisible by %d kv heads", sh.Hq, sh.Hkv);
+  if (sh.tensor && attention_mma_ok(sh, q, k, v, out, nullptr)) return attention_mma_forward(sh, q, k, v, out, lse, s);
   if (fast128_ok(sh, q, k, v, out, nullptr)) return attn_fwd128_go(sh, q, k, v, out, lse, s);
   if (sh.D <= 32) return attn_fwd_go<32>(sh, q, k, v, out, lse, s);
   if (sh.D <= 64) return attn_fwd_go<64>(sh, q, k, v, out, lse, s);
@@ -810,6 +811,8 @@ int attention_backward_launch(const AttnShape& sh, const float* q, const float* 
     GN_LAUNCH_CHECK();
     delta = delta_scratch;
   }
+  if (sh.tensor && attention_mma_ok(sh, q, k, v, dout, dq) && attention_mma_ok(sh, dk, dv, nullptr, nullptr, nullptr))
+    return attention_mma_backward(sh, q, k, v, dout, lse, delta, dq, dk, dv, accumulate, s);
   if (fast128_ok(sh, q, k, v, dout, dq) && fast128_ok(sh, dk, dv, nullptr, nullptr, nullptr))
     return attn_bwd128_go(sh, q, k, v, dout, lse, delta, dq, dk, dv, accumulate, s);
   if (sh.D <= 32) return attn_bwd_go<32>(sh, q, k, v, dout, lse, delta, dq, dk, dv, accumulate, s);

@@ -1,0 +1,395 @@
+// head_dim 128 attention on the warp-level tensor-core instruction (mma.sync m16n8k8, tf32
+// operands, float32 accumulate), forward and backward, for the prefill and the training pass
+// (kernels/backend.go:167-283; scalar statement kernels/scalar/attention.go:16-245).
+//
+// Precision: every float32 operand x is used as hi = tf32(x) and lo = tf32(x - hi) and each
+// product is three instructions, a_lo*b_hi + a_hi*b_lo + a_hi*b_hi (the small terms first), which
+// keeps the products at float32 accuracy.  The split is done in registers right after the
+// shared-memory load.
+//
+// Tiling: a warp owns 16 rows of the output (queries in the forward and dQ kernels, keys in the
+// dK/dV kernel) and all 128 channels; all tiles sit row-major in shared memory with a pitch of
+// 132 floats, which makes both fragment access patterns (row g, channel t and row 2t, channel g
+// for lane = 4g + t) free of bank conflicts.
+//
+// The second product of each pair (P V, dS K, P^T dO, dS^T Q) contracts over the index that the
+// first product's accumulator fragment holds as columns 2t, 2t+1.  Instead of moving data
+// between lanes, the contraction index is permuted: slot t of the k-step stands for column 2t
+// and slot t+4 for column 2t+1, on both operands, so the accumulator registers are used
+// directly as the A fragment and the B fragment is read from rows 2t and 2t+1.
+//
+// Scores are raw q.k (the model applies no 1/sqrt(d)); a masked score is the finite -1e30 of
+// the reference (kernels/scalar/attention.go:11).
+#include "kernels.cuh"
+
+namespace gn {
+
+namespace {
+
+constexpr float kMasked = -1e30f;
+constexpr int HD = 128;       // head_dim
+constexpr int LD = HD + 4;    // shared-memory pitch in floats
+constexpr int NTH = 128;      // threads per CTA: 4 warps x 16 rows
+
+// hi = x rounded to tf32 (nearest, ties away: add half a unit of the kept mantissa to the magnitude
+// bits, clear the 13 dropped ones); lo = x - hi, exact in float32.  lo is handed to the tensor core as
+// it is: the instruction reads the tf32 part of the register, so lo is cut to its leading 11 bits,
+// an error of 2^-21 |x| at most.  Three integer/float instructions; the conversion instruction costs
+// several times that here, and these loops are bound by instruction issue.
+__device__ __forceinline__ void split(float x, uint32_t& hi, uint32_t& lo) {
+  hi = (__float_as_uint(x) + 0x1000u) & 0xffffe000u;
+  lo = __float_as_uint(x - __uint_as_float(hi));
+}
+__device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+// The three instructions of one product form a dependent chain on the accumulator, so they are issued
+// for GR independent accumulator tiles at a time, term by term.
+constexpr int GR = 4;
+__device__ __forceinline__ void mma3_group(float (*c)[4], const uint32_t (&ah)[4], const uint32_t (&al)[4], const uint32_t (&bh)[GR][2], const uint32_t (&bl)[GR][2]) {
+#pragma unroll
+  for (int i = 0; i < GR; ++i) mma(c[i], al, bh[i]);
+#pragma unroll
+  for (int i = 0; i < GR; ++i) mma(c[i], ah, bl[i]);
+#pragma unroll
+  for (int i = 0; i < GR; ++i) mma(c[i], ah, bh[i]);
+}
+
+// acc[nt] (16 x 8 tiles) += A[16 rows][128] . B[8*nt + n][128]^T ; A points at the warp's first row.
+template <int NT>
+__device__ __forceinline__ void mm_rows(float (&acc)[NT][4], const float* A, const float* B, int g, int t) {
+#pragma unroll 2
+  for (int ks = 0; ks < HD / 8; ++ks) {
+    uint32_t ah[4], al[4];
+    const float* ap = A + g * LD + ks * 8 + t;
+    split(ap[0], ah[0], al[0]); split(ap[8 * LD], ah[1], al[1]); split(ap[4], ah[2], al[2]); split(ap[8 * LD + 4], ah[3], al[3]);
+#pragma unroll
+    for (int n0 = 0; n0 < NT; n0 += GR) {
+      uint32_t bh[GR][2], bl[GR][2];
+#pragma unroll
+      for (int i = 0; i < GR; ++i) {
+        const float* bp = B + ((n0 + i) * 8 + g) * LD + ks * 8 + t;
+        split(bp[0], bh[i][0], bl[i][0]); split(bp[4], bh[i][1], bl[i][1]);
+      }
+      mma3_group(&acc[n0], ah, al, bh, bl);
+    }
+  }
+}
+
+// acc[nt] (16 x 8 tiles over the 128 channels) += P[16][8*NK] . B[8*NK rows][128], where P is held
+// as NK accumulator fragments (columns 2t, 2t+1 of each 8-wide tile) and B is row-major.
+template <int NK>
+__device__ __forceinline__ void mm_perm(float (&acc)[HD / 8][4], const float (&p)[NK][4], const float* B, int g, int t) {
+#pragma unroll
+  for (int ks = 0; ks < NK; ++ks) {
+    uint32_t ah[4], al[4];
+    split(p[ks][0], ah[0], al[0]); split(p[ks][2], ah[1], al[1]); split(p[ks][1], ah[2], al[2]); split(p[ks][3], ah[3], al[3]);
+    const float* brow = B + (ks * 8 + 2 * t) * LD + g;
+#pragma unroll
+    for (int n0 = 0; n0 < HD / 8; n0 += GR) {
+      uint32_t bh[GR][2], bl[GR][2];
+#pragma unroll
+      for (int i = 0; i < GR; ++i) { split(brow[(n0 + i) * 8], bh[i][0], bl[i][0]); split(brow[LD + (n0 + i) * 8], bh[i][1], bl[i][1]); }
+      mma3_group(&acc[n0], ah, al, bh, bl);
+    }
+  }
+}
+
+// rows of 128 floats -> row-major tile, float4 coalesced; rows >= valid are zero.
+__device__ __forceinline__ void load_tile(float* S, const float* gsrc, int64_t tstride, int nrows, int valid) {
+  for (int idx = threadIdx.x; idx < nrows * (HD / 4); idx += NTH) {
+    const int r = idx / (HD / 4), c = (idx % (HD / 4)) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < valid) v = *reinterpret_cast<const float4*>(gsrc + (int64_t)r * tstride + c);
+    *reinterpret_cast<float4*>(S + r * LD + c) = v;
+  }
+}
+
+__device__ __forceinline__ bool masked(int qpos, int kj, int window, const int32_t* seg, int seg_len, int32_t qseg) {
+  bool m = kj > qpos || (window >= 0 && qpos - kj > window);
+  if (!m && seg != nullptr && kj < seg_len && seg[kj] != qseg) m = true;
+  return m;
+}
+
+// ------------------------------------------------------------------ forward
+// CTA = 64 queries of one (batch, head); 64-key tiles; later (heavier) query tiles are scheduled first.
+__global__ void __launch_bounds__(NTH, 2) attn_mma_fwd_kernel(AttnShape sh, const float* __restrict__ q, const float* __restrict__ k,
+                                                              const float* __restrict__ v, float* __restrict__ out, float* __restrict__ lse) {
+  constexpr int BQ = 64, BKV = 64;
+  extern __shared__ __align__(16) float smem[];
+  float* Qs = smem; float* Ks = Qs + BQ * LD; float* Vs = Ks + BKV * LD;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int bh = blockIdx.y, b = bh / sh.Hq, hq = bh % sh.Hq, hk = hq / (sh.Hq / sh.Hkv);
+  const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BQ, qvalid = min(BQ, sh.Tq - q0), offset = sh.offset0;
+  const float* qg = q + (int64_t)b * sh.q_bstride + (int64_t)q0 * sh.q_tstride + (int64_t)hq * HD;
+  const float* kg = k + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride;
+  const float* vg = v + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride;
+  load_tile(Qs, qg, sh.q_tstride, BQ, qvalid);
+  float o[HD / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < HD / 8; ++nt) { o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f; }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+  int qpos2[2]; int32_t qseg[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    qpos2[h] = offset + q0 + warp * 16 + g + 8 * h;
+    qseg[h] = (sh.segment_ids && qpos2[h] < sh.seg_len) ? sh.segment_ids[qpos2[h]] : 0;
+  }
+  const int max_qpos = offset + q0 + qvalid - 1;
+  const int k_end = min(sh.Tk, max_qpos + 1);
+  int k_begin = 0;
+  if (sh.window >= 0) k_begin = max(0, offset + q0 - sh.window);
+  k_begin = (k_begin / BKV) * BKV;
+  for (int kt = k_begin; kt < k_end; kt += BKV) {
+    const int kvalid = min(BKV, sh.Tk - kt);
+    __syncthreads();
+    load_tile(Ks, kg + (int64_t)kt * sh.kv_tstride, sh.kv_tstride, BKV, kvalid);
+    load_tile(Vs, vg + (int64_t)kt * sh.kv_tstride, sh.kv_tstride, BKV, kvalid);
+    __syncthreads();
+    float s[BKV / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < BKV / 8; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f; }
+    mm_rows<BKV / 8>(s, Qs + warp * 16 * LD, Ks, g, t);
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < BKV / 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h = e >> 1, kj = kt + nt * 8 + 2 * t + (e & 1);
+        if (kj >= sh.Tk) s[nt][e] = -INFINITY;
+        else if (masked(qpos2[h], kj, sh.window, sh.segment_ids, sh.seg_len, qseg[h])) s[nt][e] = kMasked;
+        mx[h] = fmaxf(mx[h], s[nt][e]);
+      }
+    float alpha[2], rs[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      const float m_new = fmaxf(m_run[h], mx[h]);
+      alpha[h] = (m_run[h] == -INFINITY) ? 0.0f : __expf(m_run[h] - m_new);
+      m_run[h] = m_new;
+    }
+#pragma unroll
+    for (int nt = 0; nt < BKV / 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h = e >> 1;
+        const float p = (s[nt][e] == -INFINITY) ? 0.0f : __expf(s[nt][e] - m_run[h]);
+        s[nt][e] = p; rs[h] += p;
+      }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 1);
+      rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 2);
+      l_run[h] = l_run[h] * alpha[h] + rs[h];
+    }
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt) { o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0]; o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1]; }
+    mm_perm<BKV / 8>(o, s, Vs, g, t);
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int qi = q0 + warp * 16 + g + 8 * h;
+    if (qi >= sh.Tq) continue;
+    const float inv = l_run[h] > 0.0f ? 1.0f / l_run[h] : 0.0f;
+    float* og = out + (int64_t)b * sh.o_bstride + (int64_t)qi * sh.o_tstride + (int64_t)hq * HD;
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt)
+      *reinterpret_cast<float2*>(og + nt * 8 + 2 * t) = make_float2(o[nt][2 * h] * inv, o[nt][2 * h + 1] * inv);
+    if (lse && t == 0) lse[((int64_t)b * sh.Hq + hq) * sh.Tq + qi] = m_run[h] + logf(l_run[h]);
+  }
+}
+
+// ------------------------------------------------------------------ dK / dV
+// CTA = 64 keys of one (batch, kv head), 16 per warp; walks the group's query heads and 32-query
+// tiles.  The warp computes S^T and dP^T (keys x queries) so that both gradients accumulate in its
+// own registers: no atomics, a fixed summation order.
+__global__ void __launch_bounds__(NTH, 2) attn_mma_dkv_kernel(AttnShape sh, const float* __restrict__ q, const float* __restrict__ k,
+                                                              const float* __restrict__ v, const float* __restrict__ dout,
+                                                              const float* __restrict__ lse, const float* __restrict__ delta,
+                                                              float* __restrict__ dk, float* __restrict__ dv, int accumulate) {
+  constexpr int BQ = 32, BKV = 64;
+  extern __shared__ __align__(16) float smem[];
+  float* Ks = smem; float* Vs = Ks + BKV * LD; float* Qs = Vs + BKV * LD; float* dOs = Qs + BQ * LD;
+  __shared__ float lse_s[BQ], delta_s[BQ];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int bh = blockIdx.y, b = bh / sh.Hkv, hk = bh % sh.Hkv, ratio = sh.Hq / sh.Hkv;
+  const int k0 = blockIdx.x * BKV, kvalid = min(BKV, sh.Tk - k0), offset = sh.offset0;
+  const float* kg = k + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride + (int64_t)k0 * sh.kv_tstride;
+  const float* vg = v + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride + (int64_t)k0 * sh.kv_tstride;
+  load_tile(Ks, kg, sh.kv_tstride, BKV, kvalid);
+  load_tile(Vs, vg, sh.kv_tstride, BKV, kvalid);
+  float adk[HD / 8][4], adv[HD / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < HD / 8; ++nt) { adk[nt][0] = adk[nt][1] = adk[nt][2] = adk[nt][3] = 0.0f; adv[nt][0] = adv[nt][1] = adv[nt][2] = adv[nt][3] = 0.0f; }
+  int q_begin = max(0, k0 - offset);
+  q_begin = (q_begin / BQ) * BQ;
+  int q_end = sh.Tq;
+  if (sh.window >= 0) q_end = min(sh.Tq, k0 + kvalid - 1 + sh.window - offset + 1);
+  const int kj2[2] = {k0 + warp * 16 + g, k0 + warp * 16 + g + 8};
+  for (int h = 0; h < ratio; ++h) {
+    const int hq = hk * ratio + h;
+    for (int q0 = q_begin; q0 < q_end; q0 += BQ) {
+      const int qvalid = min(BQ, sh.Tq - q0);
+      const float* qg = q + (int64_t)b * sh.q_bstride + (int64_t)q0 * sh.q_tstride + (int64_t)hq * HD;
+      const float* dog = dout + (int64_t)b * sh.o_bstride + (int64_t)q0 * sh.o_tstride + (int64_t)hq * HD;
+      __syncthreads();
+      load_tile(Qs, qg, sh.q_tstride, BQ, qvalid);
+      load_tile(dOs, dog, sh.o_tstride, BQ, qvalid);
+      if (threadIdx.x < BQ) {
+        const int qi = q0 + threadIdx.x;
+        lse_s[threadIdx.x] = qi < sh.Tq ? lse[((int64_t)b * sh.Hq + hq) * sh.Tq + qi] : 0.0f;
+        delta_s[threadIdx.x] = qi < sh.Tq ? delta[((int64_t)b * sh.Hq + hq) * sh.Tq + qi] : 0.0f;
+      }
+      __syncthreads();
+      float st[BQ / 8][4], dpt[BQ / 8][4];
+#pragma unroll
+      for (int nt = 0; nt < BQ / 8; ++nt) { st[nt][0] = st[nt][1] = st[nt][2] = st[nt][3] = 0.0f; dpt[nt][0] = dpt[nt][1] = dpt[nt][2] = dpt[nt][3] = 0.0f; }
+      mm_rows<BQ / 8>(st, Ks + warp * 16 * LD, Qs, g, t);
+      mm_rows<BQ / 8>(dpt, Vs + warp * 16 * LD, dOs, g, t);
+#pragma unroll
+      for (int nt = 0; nt < BQ / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int il = nt * 8 + 2 * t + (e & 1), qi = q0 + il, qpos = offset + qi, kj = kj2[e >> 1];
+          const int32_t qseg = (sh.segment_ids && qpos < sh.seg_len) ? sh.segment_ids[qpos] : 0;
+          float p = 0.0f;
+          if (qi < sh.Tq && kj < sh.Tk && !masked(qpos, kj, sh.window, sh.segment_ids, sh.seg_len, qseg)) p = __expf(st[nt][e] - lse_s[il]);
+          st[nt][e] = p;
+          dpt[nt][e] = p * (dpt[nt][e] - delta_s[il]);
+        }
+      mm_perm<BQ / 8>(adv, st, dOs, g, t);
+      mm_perm<BQ / 8>(adk, dpt, Qs, g, t);
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int kj = kj2[h];
+    if (kj >= sh.Tk) continue;
+    float* dkg = dk + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride + (int64_t)kj * sh.kv_tstride;
+    float* dvg = dv + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride + (int64_t)kj * sh.kv_tstride;
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt) {
+      float2 a = make_float2(adk[nt][2 * h], adk[nt][2 * h + 1]);
+      float2 c = make_float2(adv[nt][2 * h], adv[nt][2 * h + 1]);
+      float2* pk = reinterpret_cast<float2*>(dkg + nt * 8 + 2 * t); float2* pv = reinterpret_cast<float2*>(dvg + nt * 8 + 2 * t);
+      if (accumulate) { const float2 ok = *pk, ov = *pv; a.x += ok.x; a.y += ok.y; c.x += ov.x; c.y += ov.y; }
+      *pk = a; *pv = c;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ dQ
+// CTA = 64 queries of one (batch, query head), 16 per warp; walks 32-key tiles.
+__global__ void __launch_bounds__(NTH, 2) attn_mma_dq_kernel(AttnShape sh, const float* __restrict__ q, const float* __restrict__ k,
+                                                             const float* __restrict__ v, const float* __restrict__ dout,
+                                                             const float* __restrict__ lse, const float* __restrict__ delta,
+                                                             float* __restrict__ dq, int accumulate) {
+  constexpr int BQ = 64, BKV = 32;
+  extern __shared__ __align__(16) float smem[];
+  float* Qs = smem; float* dOs = Qs + BQ * LD; float* Ks = dOs + BQ * LD; float* Vs = Ks + BKV * LD;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int bh = blockIdx.y, b = bh / sh.Hq, hq = bh % sh.Hq, hk = hq / (sh.Hq / sh.Hkv);
+  const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BQ, qvalid = min(BQ, sh.Tq - q0), offset = sh.offset0;
+  const float* qg = q + (int64_t)b * sh.q_bstride + (int64_t)q0 * sh.q_tstride + (int64_t)hq * HD;
+  const float* dog = dout + (int64_t)b * sh.o_bstride + (int64_t)q0 * sh.o_tstride + (int64_t)hq * HD;
+  const float* kg = k + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride;
+  const float* vg = v + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride;
+  load_tile(Qs, qg, sh.q_tstride, BQ, qvalid);
+  load_tile(dOs, dog, sh.o_tstride, BQ, qvalid);
+  float lse2[2], delta2[2]; int qi2[2]; int32_t qseg[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    qi2[h] = q0 + warp * 16 + g + 8 * h;
+    const bool ok = qi2[h] < sh.Tq;
+    lse2[h] = ok ? lse[((int64_t)b * sh.Hq + hq) * sh.Tq + qi2[h]] : 0.0f;
+    delta2[h] = ok ? delta[((int64_t)b * sh.Hq + hq) * sh.Tq + qi2[h]] : 0.0f;
+    const int qpos = offset + qi2[h];
+    qseg[h] = (sh.segment_ids && qpos < sh.seg_len) ? sh.segment_ids[qpos] : 0;
+  }
+  float adq[HD / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < HD / 8; ++nt) { adq[nt][0] = adq[nt][1] = adq[nt][2] = adq[nt][3] = 0.0f; }
+  const int max_qpos = offset + q0 + qvalid - 1;
+  const int k_end = min(sh.Tk, max_qpos + 1);
+  int k_begin = 0;
+  if (sh.window >= 0) k_begin = max(0, offset + q0 - sh.window);
+  k_begin = (k_begin / BKV) * BKV;
+  for (int kt = k_begin; kt < k_end; kt += BKV) {
+    const int kvalid = min(BKV, sh.Tk - kt);
+    __syncthreads();
+    load_tile(Ks, kg + (int64_t)kt * sh.kv_tstride, sh.kv_tstride, BKV, kvalid);
+    load_tile(Vs, vg + (int64_t)kt * sh.kv_tstride, sh.kv_tstride, BKV, kvalid);
+    __syncthreads();
+    float s[BKV / 8][4], dp[BKV / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < BKV / 8; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f; dp[nt][0] = dp[nt][1] = dp[nt][2] = dp[nt][3] = 0.0f; }
+    mm_rows<BKV / 8>(s, Qs + warp * 16 * LD, Ks, g, t);
+    mm_rows<BKV / 8>(dp, dOs + warp * 16 * LD, Vs, g, t);
+#pragma unroll
+    for (int nt = 0; nt < BKV / 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h = e >> 1, kj = kt + nt * 8 + 2 * t + (e & 1);
+        float p = 0.0f;
+        if (qi2[h] < sh.Tq && kj < sh.Tk && !masked(offset + qi2[h], kj, sh.window, sh.segment_ids, sh.seg_len, qseg[h])) p = __expf(s[nt][e] - lse2[h]);
+        dp[nt][e] = p * (dp[nt][e] - delta2[h]);
+      }
+    mm_perm<BKV / 8>(adq, dp, Ks, g, t);
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (qi2[h] >= sh.Tq) continue;
+    float* dqg = dq + (int64_t)b * sh.q_bstride + (int64_t)qi2[h] * sh.q_tstride + (int64_t)hq * HD;
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt) {
+      float2 a = make_float2(adq[nt][2 * h], adq[nt][2 * h + 1]);
+      float2* pq = reinterpret_cast<float2*>(dqg + nt * 8 + 2 * t);
+      if (accumulate) { const float2 o2 = *pq; a.x += o2.x; a.y += o2.y; }
+      *pq = a;
+    }
+  }
+}
+
+constexpr size_t kSmemFwd = sizeof(float) * (size_t)(3 * 64 * LD);
+constexpr size_t kSmemDkv = sizeof(float) * (size_t)((2 * 64 + 2 * 32) * LD);
+constexpr size_t kSmemDq = sizeof(float) * (size_t)((2 * 64 + 2 * 32) * LD);
+
+}  // namespace
+
+// Row access is by float4 / float2: 16-byte aligned rows, head_dim 128.
+bool attention_mma_ok(const AttnShape& sh, const void* p0, const void* p1, const void* p2, const void* p3, const void* p4) {
+  auto al = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  return sh.D == HD && al(p0) && al(p1) && al(p2) && al(p3) && al(p4) && sh.q_tstride % 4 == 0 && sh.q_bstride % 4 == 0 && sh.kv_tstride % 4 == 0 &&
+         sh.kv_bstride % 4 == 0 && sh.kv_hstride % 4 == 0 && sh.o_tstride % 4 == 0 && sh.o_bstride % 4 == 0;
+}
+
+int attention_mma_forward(const AttnShape& sh, const float* q, const float* k, const float* v, float* out, float* lse, cudaStream_t s) {
+  static bool configured = false;
+  if (!configured) { GN_CUDA(cudaFuncSetAttribute(attn_mma_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemFwd)); configured = true; }
+  dim3 grid(ceil_div(sh.Tq, 64), sh.B * sh.Hq);
+  attn_mma_fwd_kernel<<<grid, NTH, kSmemFwd, s>>>(sh, q, k, v, out, lse);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+int attention_mma_backward(const AttnShape& sh, const float* q, const float* k, const float* v, const float* dout, const float* lse, const float* delta,
+                           float* dq, float* dk, float* dv, int accumulate, cudaStream_t s) {
+  static bool configured = false;
+  if (!configured) {
+    GN_CUDA(cudaFuncSetAttribute(attn_mma_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemDkv));
+    GN_CUDA(cudaFuncSetAttribute(attn_mma_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemDq));
+    configured = true;
+  }
+  dim3 gkv(ceil_div(sh.Tk, 64), sh.B * sh.Hkv);
+  attn_mma_dkv_kernel<<<gkv, NTH, kSmemDkv, s>>>(sh, q, k, v, dout, lse, delta, dk, dv, accumulate);
+  GN_LAUNCH_CHECK();
+  dim3 gq(ceil_div(sh.Tq, 64), sh.B * sh.Hq);
+  attn_mma_dq_kernel<<<gq, NTH, kSmemDq, s>>>(sh, q, k, v, dout, lse, delta, dq, accumulate);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+}  // namespace gn

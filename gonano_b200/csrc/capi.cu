@@ -292,7 +292,7 @@ static int attn_shape(const gn_attention_params* p, AttnShape& sh, Stage& st, co
   GN_REQUIRE(p->query_len >= 0 && p->key_len >= 0, "attention: negative length");
   sh.B = 1; sh.Hq = 1; sh.Hkv = 1; sh.D = p->head_dim; sh.Tq = p->query_len; sh.Tk = p->key_len;
   sh.q_bstride = 0; sh.q_tstride = p->head_dim; sh.kv_bstride = 0; sh.kv_tstride = p->head_dim; sh.kv_hstride = 0;
-  sh.o_bstride = 0; sh.o_tstride = p->head_dim; sh.window = p->window; sh.offset0 = p->position_offset;
+  sh.o_bstride = 0; sh.o_tstride = p->head_dim; sh.window = p->window; sh.offset0 = p->position_offset; sh.tensor = gemm_default_kind();
   *q = st.in(p->query, (size_t)p->query_len * p->head_dim);
   *k = st.in(p->key, (size_t)p->key_len * p->head_dim);
   *v = st.in(p->value, (size_t)p->key_len * p->head_dim);

@@ -44,7 +44,13 @@ struct AttnShape {
   int offset0 = 0;
   const int32_t* segment_ids = nullptr;  // [Tk] shared by all rows (Tier A only)
   int seg_len = 0;
+  int tensor = 0;   // 1: head_dim 128 may run on the tensor cores in 3xTF32 (forward and backward)
 };
+// head_dim 128 tensor-core kernels (attention_mma.cu); reached through the two launches below when sh.tensor is set.
+bool attention_mma_ok(const AttnShape& sh, const void* p0, const void* p1, const void* p2, const void* p3, const void* p4);
+int attention_mma_forward(const AttnShape& sh, const float* q, const float* k, const float* v, float* out, float* lse, cudaStream_t s);
+int attention_mma_backward(const AttnShape& sh, const float* q, const float* k, const float* v, const float* dout, const float* lse, const float* delta,
+                           float* dq, float* dk, float* dv, int accumulate, cudaStream_t s);
 int attention_forward_launch(const AttnShape& sh, const float* q, const float* k, const float* v, float* out, float* lse, cudaStream_t s);
 // Gradients: dq like q (strides of q), dk/dv like k/v.  accumulate != 0 adds into them.
 int attention_backward_launch(const AttnShape& sh, const float* q, const float* k, const float* v, const float* out, const float* dout,

@@ -294,7 +294,7 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
       AttnShape sh;
       sh.B = B; sh.Hq = Hq; sh.Hkv = Hkv; sh.D = D; sh.Tq = T; sh.Tk = T;
       sh.q_bstride = (int64_t)T * W; sh.q_tstride = W; sh.kv_bstride = (int64_t)T * W; sh.kv_tstride = W; sh.kv_hstride = D;
-      sh.o_bstride = (int64_t)T * Hq * D; sh.o_tstride = (int64_t)Hq * D; sh.window = m->windows[l]; sh.offset0 = 0;
+      sh.o_bstride = (int64_t)T * Hq * D; sh.o_tstride = (int64_t)Hq * D; sh.window = m->windows[l]; sh.offset0 = 0; sh.tensor = m->ctx->gemm_kind == 1;
       GN_TRY(attention_forward_launch(sh, QKV, QKV + (int64_t)Hq * D, QKV + (int64_t)(Hq + Hkv) * D, O, train ? b.layers[l].LSE : nullptr, s));
     }
     if (fuse) {
@@ -411,7 +411,7 @@ int backward_core(gn_model* m, FwdBufs& b, BwdBufs& w, const int32_t* ids, int B
     AttnShape sh;
     sh.B = B; sh.Hq = Hq; sh.Hkv = Hkv; sh.D = D; sh.Tq = T; sh.Tk = T;
     sh.q_bstride = (int64_t)T * W; sh.q_tstride = W; sh.kv_bstride = (int64_t)T * W; sh.kv_tstride = W; sh.kv_hstride = D;
-    sh.o_bstride = (int64_t)T * Hq * D; sh.o_tstride = (int64_t)Hq * D; sh.window = m->windows[l]; sh.offset0 = 0;
+    sh.o_bstride = (int64_t)T * Hq * D; sh.o_tstride = (int64_t)Hq * D; sh.window = m->windows[l]; sh.offset0 = 0; sh.tensor = m->ctx->gemm_kind == 1;
     GN_TRY(attention_backward_launch(sh, sv.QKV, sv.QKV + (int64_t)Hq * D, sv.QKV + (int64_t)(Hq + Hkv) * D, sv.O, w.DO, sv.LSE, nullptr, w.DQKV,
                                      w.DQKV + (int64_t)Hq * D, w.DQKV + (int64_t)(Hq + Hkv) * D, 0, w.DELTA, s));
     QkvPostBwd qb;

@@ -134,7 +134,7 @@ extern "C" int gn_profile_kernel(gn_ctx* ctx, const char* kernel, const int64_t*
     AttnShape sh;
     sh.B = B; sh.Hq = Hq; sh.Hkv = Hkv; sh.D = D; sh.Tq = T; sh.Tk = T;
     sh.q_bstride = (int64_t)T * W; sh.q_tstride = W; sh.kv_bstride = (int64_t)T * W; sh.kv_tstride = W; sh.kv_hstride = D;
-    sh.o_bstride = (int64_t)T * Hq * D; sh.o_tstride = (int64_t)Hq * D; sh.window = -1; sh.offset0 = 0;
+    sh.o_bstride = (int64_t)T * Hq * D; sh.o_tstride = (int64_t)Hq * D; sh.window = -1; sh.offset0 = 0; sh.tensor = ctx->gemm_kind == 1;
     const float* kp = qkv + (int64_t)Hq * D; const float* vp = qkv + (int64_t)(Hq + Hkv) * D;
     GN_TRY(attention_forward_launch(sh, qkv, kp, vp, o, lse, s));
     if (k == "attention_fwd") return time_it(s, iters, mean_ms, [&]() { return attention_forward_launch(sh, qkv, kp, vp, o, lse, s); });
