@@ -26,6 +26,8 @@ class GnConfig(C.Structure):
     _fields_ = [
         ("sequence_len", C.c_int32), ("vocab_size", C.c_int32), ("n_layer", C.c_int32), ("n_head", C.c_int32),
         ("n_kv_head", C.c_int32), ("embed_dim", C.c_int32), ("rotary_dims", C.c_int32), ("window_pattern", C.c_char * 16),
+        ("n_experts", C.c_int32), ("experts_per_token", C.c_int32), ("expert_hidden", C.c_int32), ("shared_hidden", C.c_int32),
+        ("moe_clamp", C.c_float), ("moe_scale", C.c_float), ("mla_latent", C.c_int32), ("mla_rotary_dims", C.c_int32),
     ]
 
 

@@ -22,90 +22,13 @@
 #include <string>
 #include <vector>
 
-#include "kernels.cuh"
-#include "model_kernels.cuh"
-#include "ctx.cuh"
+#include "model_internal.cuh"
 
 using namespace gn;
 
 
-namespace {
-
-struct DevBuf {
-  void* p = nullptr;
-  size_t bytes = 0;
-  int ensure(size_t n) {
-    if (n <= bytes) return GN_OK;
-    if (p) cudaFree(p);
-    p = nullptr; bytes = 0;
-    cudaError_t e = cudaMalloc(&p, n);
-    if (e != cudaSuccess) { set_error("cudaMalloc(%zu bytes) failed: %s", n, cudaGetErrorString(e)); return GN_ERR_NOMEM; }
-    bytes = n;
-    return GN_OK;
-  }
-  void release() { if (p) cudaFree(p); p = nullptr; bytes = 0; }
-  float* f() const { return (float*)p; }
-  int32_t* i() const { return (int32_t*)p; }
-};
-
-struct ParamInfo {
-  std::string name;
-  int rows = 0, cols = 0;
-  int64_t offset = 0;
-};
-
-// A bump allocator over one DevBuf: buffers of one pass are carved in order.
-struct Arena {
-  DevBuf buf;
-  size_t used = 0;
-  size_t planned = 0;
-  bool planning = false;
-  float* take(size_t floats) {
-    size_t bytes = ((floats * sizeof(float) + 255) / 256) * 256;
-    if (planning) { planned += bytes; return nullptr; }
-    float* r = (float*)((char*)buf.p + used);
-    used += bytes;
-    return r;
-  }
-};
-
-struct LayerOffsets { int64_t qkv, proj, ve_gate, fc, mproj, ve; bool has_ve; };
-
-struct LayerSaved {
-  float *Xin, *H, *QKV, *QKROT, *O, *LSE, *VESIG, *MID, *M, *U, *HID, *XOUT;
-};
-
-}  // namespace
-
-struct gn_model {
-  gn_ctx* ctx = nullptr;
-  gn_config cfg{};
-  int d = 0, L = 0, Hq = 0, Hkv = 0, D = 0, R = 0, V = 0, Vp = 0, W = 0, KV = 0;
-  std::vector<int> windows;
-  std::vector<ParamInfo> params;               // sorted by name
-  std::map<std::string, int> index;
-  int64_t total = 0;
-  DevBuf P, G;
-  std::vector<LayerOffsets> lo;
-  int64_t off_wte = 0, off_lm = 0, off_rho = 0, off_chi = 0, off_smear_gate = 0, off_smear_lambda = 0, off_backout = 0;
-  DevBuf cosb, sinb, sacc;
-  // inference state
-  DevBuf cache, prev, pos, ctxlen, ids_dev, sampled, seeds, out_tokens, out_lengths, done, n_done, sel;
-  DevBuf part_acc, part_ms, step_dev;
-  Arena infer, train;
-  DevBuf tgt_dev, adv_dev, rowloss, loss_dev, in_dev;
-  std::map<std::string, float> phase_ms;
-  cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
-  bool weights_dirty = true;   // cached tensor-core operand splits of the parameters are stale
-
-  float* p(int64_t off) const { return P.f() + off; }
-  float* g(int64_t off) const { return G.f() + off; }
-  cudaStream_t s() const { return ctx->stream; }
-};
 
 namespace {
-
-int gemm(gn_model* m, const GemmArgs& a) { return gemm_dispatch(a, m->ctx->gemm_kind, m->s()); }
 
 int64_t align64(int64_t n) { return (n + 63) / 64 * 64; }
 
@@ -127,18 +50,42 @@ int build_layout(gn_model* m) {
   for (int l = 0; l < L; ++l) {
     std::string p = "transformer.h." + std::to_string(l) + ".";
     LayerOffsets& o = m->lo[l];
-    o.qkv = add(p + "attn.c_q.weight", Hq * D, d);
-    add(p + "attn.c_k.weight", KV, d, false);   // adjacent: [c_q; c_k; c_v] is one [W, d] matrix
-    add(p + "attn.c_v.weight", KV, d, false);
+    o.qkv = -1;
+    if (m->mla()) {
+      // model/mla.go:41-60.  The four projections of the block input are adjacent: one [2 lat + (Hq+Hkv) rope, d] matrix.
+      o.mla_cat = add(p + "attn.mla_q_down.weight", m->lat, d);
+      add(p + "attn.mla_kv_down.weight", m->lat, d, false);
+      add(p + "attn.mla_q_rope.weight", Hq * m->rope, d, false);
+      add(p + "attn.mla_k_rope.weight", Hkv * m->rope, d, false);
+      o.mla_q_up = add(p + "attn.mla_q_up.weight", Hq * m->content, m->lat);
+      o.mla_k_up = add(p + "attn.mla_k_up.weight", Hkv * m->content, m->lat);
+      o.mla_v_up = add(p + "attn.mla_v_up.weight", Hkv * D, m->lat);
+    } else {
+      o.qkv = add(p + "attn.c_q.weight", Hq * D, d);
+      add(p + "attn.c_k.weight", KV, d, false);   // adjacent: [c_q; c_k; c_v] is one [W, d] matrix
+      add(p + "attn.c_v.weight", KV, d, false);
+    }
     o.proj = add(p + "attn.c_proj.weight", d, d);
-    o.has_ve = has_ve(l, L);
+    o.has_ve = !m->mla() && has_ve(l, L);        // model/transformer.go:73
     o.ve_gate = o.ve = -1;
     if (o.has_ve) {
       o.ve_gate = add(p + "attn.ve_gate.weight", Hkv, kVeGateChannels);
       o.ve = add("value_embeds." + std::to_string(l) + ".weight", Vp, KV);
     }
-    o.fc = add(p + "mlp.c_fc.weight", 4 * d, d);
-    o.mproj = add(p + "mlp.c_proj.weight", d, 4 * d);
+    if (m->moe()) {
+      // shared SwiGLU expert (model/block.go:23-25): [c_fc; c_gate] adjacent; routed experts packed (model/moe.go:26-45)
+      o.fc = add(p + "mlp.c_fc.weight", m->sh, d);
+      add(p + "mlp.c_gate.weight", m->sh, d, false);
+      o.mproj = add(p + "mlp.c_proj.weight", d, m->sh);
+      o.router = add(p + "moe.router.weight", m->E, d);
+      o.router_bias = add(p + "moe.router_bias", 1, m->E);
+      o.exp_gate = add(p + "moe.experts.gate.weight", m->E * m->eh, d);
+      o.exp_up = add(p + "moe.experts.up.weight", m->E * m->eh, d);
+      o.exp_down = add(p + "moe.experts.down.weight", m->E * d, m->eh);
+    } else {
+      o.fc = add(p + "mlp.c_fc.weight", 4 * d, d);
+      o.mproj = add(p + "mlp.c_proj.weight", d, 4 * d);
+    }
   }
   m->off_smear_gate = add("smear_gate.weight", 1, kSmearChannels);
   // The four scalar parameter groups are adjacent (2L+2 floats) so that their
@@ -166,24 +113,6 @@ int enter_compute(gn_model* m) {
 }
 
 // ------------------------------------------------------------------ forward
-enum Mode { MODE_PLAIN, MODE_PREFILL, MODE_DECODE, MODE_TRAIN };
-
-struct FwdBufs {
-  float *E, *X0, *Xa, *Xb, *H, *QKV, *O, *M, *HID, *BO, *Y, *LOGITS;
-  float *S1h, *S1l, *S4h, *S4l;   // producer-written tf32 splits: one [rows, d] pair and one [rows, 4d] pair, reused by every layer
-  // train only
-  float *SIG, *FP;
-  std::vector<LayerSaved> layers;
-};
-
-struct FwdArgs {
-  Mode mode;
-  const int32_t* ids;      // device [B*T]
-  int B, T;
-  int cache_rows = 0, cache_row_mul = 1, max_seq = 0;
-  int logits_rows = 0;     // rows that get logits (PLAIN/TRAIN: all; PREFILL: B; DECODE: B)
-};
-
 size_t plan_bufs(gn_model* m, Arena& a, FwdBufs& b, Mode mode, int64_t rows, int64_t logit_rows, int B, int T) {
   const int d = m->d, W = m->W, Hq = m->Hq, Hkv = m->Hkv, D = m->D, V = m->V, L = m->L;
   b.E = a.take(rows * d);
@@ -208,6 +137,18 @@ size_t plan_bufs(gn_model* m, Arena& a, FwdBufs& b, Mode mode, int64_t rows, int
     b.H = a.take(rows * d); b.QKV = a.take(rows * W); b.O = a.take(rows * (int64_t)Hq * D);
     b.M = a.take(rows * d); b.HID = a.take(rows * 4 * d); b.BO = a.take(rows * d);
     b.SIG = b.FP = nullptr;
+    if (m->mla()) {
+      const int64_t n1 = 2 * m->lat + (int64_t)(Hq + Hkv) * m->rope;
+      b.P1 = a.take(rows * n1); b.QC = a.take(rows * (int64_t)Hq * m->content); b.QF = a.take(rows * (int64_t)Hq * (m->lat + m->rope));
+      b.AL = a.take(rows * (int64_t)Hq * m->lat);
+    }
+    if (m->moe()) {
+      const int64_t tot = rows * m->topk;
+      b.UG = a.take(rows * 2 * m->sh); b.SHH = a.take(rows * m->sh); b.SHO = a.take(rows * d);
+      b.RL = a.take(rows * m->E); b.PR = a.take(rows * m->E); b.SELW = a.take(tot);
+      b.GATH = a.take(tot * d); b.GG = a.take(tot * m->eh); b.GU = a.take(tot * m->eh); b.GO = a.take(tot * d);
+      b.SEL = (int32_t*)a.take(tot); b.CNT = (int32_t*)a.take(m->E + 1); b.POSI = (int32_t*)a.take(tot);
+    }
   }
   return a.planned;
 }
@@ -266,6 +207,11 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
     } else {
       GN_TRY(mix_norm_launch(x_prev, b.X0, m->p(m->off_rho), m->p(m->off_chi), l, Xin, H, tc ? b.S1h : nullptr, tc ? b.S1l : nullptr, rows, d, s));
     }
+    bool o_split = false;   // the attention kernel also wrote the tf32 split of O
+    if (m->mla()) {
+      GN_REQUIRE(!train, "latent attention is inference-only");
+      GN_TRY(latent_attention(m, b, a, l, H, O));
+    } else {
     // q, k, v projections as one GEMM against [c_q; c_k; c_v]
     Partials qkv_part;
     { GemmArgs g; g.A = H; g.lda = d; g.B = m->p(o.qkv); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = QKV; g.ldc = W; g.M = (int)rows; g.N = W; g.K = d;
@@ -283,7 +229,6 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
     }
     qp.B = B; qp.T = T; qp.Hq = Hq; qp.Hkv = Hkv; qp.D = D; qp.R = m->R; qp.d = d;
     GN_TRY(qkv_post_launch(qp, s));
-    bool o_split = false;   // the attention kernel also wrote the tf32 split of O
     if (a.mode == MODE_DECODE) {
       int splits = attention_decode_splits(B, Hkv, a.max_seq);
       o_split = tc && Hq * D <= 4 * d;
@@ -297,6 +242,7 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
       sh.o_bstride = (int64_t)T * Hq * D; sh.o_tstride = (int64_t)Hq * D; sh.window = m->windows[l]; sh.offset0 = 0; sh.tensor = m->ctx->gemm_kind == 1;
       GN_TRY(attention_forward_launch(sh, QKV, QKV + (int64_t)Hq * D, QKV + (int64_t)(Hq + Hkv) * D, O, train ? b.layers[l].LSE : nullptr, s));
     }
+    }
     if (fuse) {
       // MID = Xin + O Wo^T, summed and normalised in one kernel (H is free after qkv_post and takes an unsplit product)
       Partials op;
@@ -309,6 +255,13 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
       { GemmArgs g; g.A = O; g.lda = (int64_t)Hq * D; g.B = m->p(o.proj); g.b_static = 1; g.ldb = (int64_t)Hq * D; g.b_trans = 1; g.C = MID; g.ldc = d; g.M = (int)rows; g.N = d; g.K = Hq * D;
         g.epilogue = EPI_RESIDUAL; g.aux = Xin; g.ldaux = d; if (o_split) { g.a_hi = b.S4h; g.a_lo = b.S4l; } GN_TRY(gemm(m, g)); }
       GN_TRY(norm_launch(MID, Mn, tc ? b.S1h : nullptr, tc ? b.S1l : nullptr, rows, d, s));
+    }
+    if (m->moe()) {
+      GN_REQUIRE(!train, "routed experts are inference-only");
+      GN_TRY(moe_ffn(m, b, a, l, Mn, MID, XOUT));
+      if (l == L / 2) { GN_CUDA(cudaMemcpyAsync(b.BO, XOUT, sizeof(float) * rows * d, cudaMemcpyDeviceToDevice, s)); backout = b.BO; }
+      x_prev = XOUT;
+      continue;
     }
     // HID = relu(M Wfc^T)^2   (training also keeps the pre-activation)
     { GemmArgs g; g.A = Mn; g.lda = d; g.B = m->p(o.fc); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = HID; g.ldc = 4 * d; g.M = (int)rows; g.N = 4 * d; g.K = d;
@@ -480,6 +433,25 @@ int gn_model_create(gn_ctx* ctx, const gn_config* cfg, gn_model** out) {
   m->R = cfg->rotary_dims <= 0 ? m->D : cfg->rotary_dims;     // model/config.go:430-444
   m->V = cfg->vocab_size; m->Vp = (m->V + 63) / 64 * 64;      // model/config.go:619-624
   m->W = (m->Hq + 2 * m->Hkv) * m->D; m->KV = m->Hkv * m->D;
+  if (cfg->n_experts > 0) {   // model/config.go:137-229
+    m->E = cfg->n_experts;
+    m->topk = std::min(cfg->experts_per_token <= 0 ? 2 : cfg->experts_per_token, m->E);
+    m->eh = cfg->expert_hidden > 0 ? cfg->expert_hidden : m->d;
+    m->sh = cfg->shared_hidden > 0 ? cfg->shared_hidden : m->eh;
+    m->moe_clamp = cfg->moe_clamp == 0.0f ? 10.0f : cfg->moe_clamp;
+    m->moe_scale = cfg->moe_scale == 0.0f ? 1.0f : cfg->moe_scale;
+    if (m->E > 64 || m->topk > 8) { set_error("unsupported expert count %d / experts per token %d (limits 64 / 8)", m->E, m->topk); delete m; return GN_ERR_INVALID; }
+  }
+  if (cfg->mla_latent > 0) {  // model/config.go:249-280
+    m->lat = cfg->mla_latent;
+    if (cfg->mla_rotary_dims > 0) m->rope = cfg->mla_rotary_dims;
+    else { m->rope = std::min(m->D / 2, 64); if (m->rope % 2) --m->rope; }
+    m->content = m->D - m->rope;
+    if (m->rope % 2 != 0 || m->rope > 64 || m->content <= 0 || m->lat > 512) {
+      set_error("unsupported latent attention geometry: latent %d, rotary %d, head_dim %d", m->lat, m->rope, m->D); delete m; return GN_ERR_INVALID;
+    }
+    m->R = m->rope;           // model/config.go:430-433: the rotary table has the decoupled rotary width
+  }
   if (m->D > 128 || m->R > m->D || m->R % 2 != 0 || m->d < kSmearChannels) { set_error("unsupported head_dim %d / rotary %d / embed %d", m->D, m->R, m->d); delete m; return GN_ERR_INVALID; }
   // model/config.go:629-645 (integer division truncating toward zero, as in Go)
   std::string pattern = cfg->window_pattern[0] ? std::string(cfg->window_pattern, strnlen(cfg->window_pattern, 16)) : std::string("L");
@@ -520,7 +492,7 @@ int gn_model_destroy(gn_model* m) {
   gemm_invalidate_static();   // cached splits are keyed by addresses that are about to be freed
   DevBuf* bufs[] = {&m->P, &m->G, &m->cosb, &m->sinb, &m->sacc, &m->cache, &m->prev, &m->pos, &m->ctxlen, &m->ids_dev, &m->sampled, &m->seeds,
                     &m->out_tokens, &m->out_lengths, &m->done, &m->n_done, &m->sel, &m->part_acc, &m->part_ms, &m->step_dev, &m->infer.buf, &m->train.buf,
-                    &m->tgt_dev, &m->adv_dev, &m->rowloss, &m->loss_dev, &m->in_dev};
+                    &m->tgt_dev, &m->adv_dev, &m->rowloss, &m->loss_dev, &m->in_dev, &m->cache_lat, &m->cache_rope};
   for (DevBuf* b : bufs) b->release();
   for (int i = 0; i < 4; ++i) if (m->ev[i]) cudaEventDestroy(m->ev[i]);
   delete m;
@@ -594,6 +566,14 @@ int gn_model_forward(gn_model* m, const int32_t* ids, int B, int T, float* logit
   FwdBufs b;
   GN_TRY(make_bufs(m, m->infer, b, MODE_PLAIN, rows, rows, B, T, 0, nullptr));
   FwdArgs a; a.mode = MODE_PLAIN; a.ids = m->ids_dev.i(); a.B = B; a.T = T;
+  if (m->mla()) {
+    // model/transformer.go:248-253: a cache-less forward of a latent-attention model runs over a scratch latent cache
+    GN_TRY(m->cache_lat.ensure(sizeof(float) * (size_t)m->L * rows * m->lat));
+    GN_TRY(m->cache_rope.ensure(sizeof(float) * (size_t)m->L * rows * m->Hkv * m->rope));
+    GN_TRY(m->pos.ensure(sizeof(int32_t) * B));
+    GN_CUDA(cudaMemsetAsync(m->pos.p, 0, sizeof(int32_t) * B, m->s()));
+    a.cache_rows = B; a.cache_row_mul = 1; a.max_seq = T;
+  }
   GN_TRY(forward_core(m, b, a));
   GN_CUDA(cudaMemcpyAsync(logits, b.LOGITS, sizeof(float) * rows * m->V, cudaMemcpyDeviceToHost, m->s()));
   GN_CUDA(cudaStreamSynchronize(m->s()));
@@ -612,7 +592,12 @@ int gn_generate_batch(gn_model* m, const int32_t* prompts, int P, int plen, int 
   const int bos = V - 11, aend = V - 7;   // tokenizer/special.go:19-31
   cudaStream_t s = m->s();
   // ---- state
-  GN_TRY(m->cache.ensure(sizeof(float) * (size_t)L * 2 * rows * Hkv * max_seq * D));
+  if (m->mla()) {
+    GN_TRY(m->cache_lat.ensure(sizeof(float) * (size_t)L * rows * max_seq * m->lat));
+    GN_TRY(m->cache_rope.ensure(sizeof(float) * (size_t)L * rows * max_seq * Hkv * m->rope));
+  } else {
+    GN_TRY(m->cache.ensure(sizeof(float) * (size_t)L * 2 * rows * Hkv * max_seq * D));
+  }
   GN_TRY(m->prev.ensure(sizeof(float) * (size_t)rows * d));
   GN_TRY(m->pos.ensure(sizeof(int32_t) * rows)); GN_TRY(m->ctxlen.ensure(sizeof(int32_t) * rows));
   GN_TRY(m->ids_dev.ensure(sizeof(int32_t) * std::max<int64_t>((int64_t)P * plen, rows)));
@@ -642,8 +627,14 @@ int gn_generate_batch(gn_model* m, const int32_t* prompts, int P, int plen, int 
     GN_TRY(forward_core(m, b, a));
   }
   // replicate each prompt's cache over its group (engine.go:194-209, kvcache.go:383-448)
-  GN_TRY(kv_replicate_launch(m->cache.f(), (int64_t)rows * Hkv * max_seq * D, 2 * L, (int64_t)Hkv * max_seq * D, (int64_t)max_seq * D, Hkv, D, P, G, plen,
-                             m->prev.f(), d, nullptr, s));
+  if (m->mla()) {
+    const int rw = Hkv * m->rope;
+    GN_TRY(kv_replicate_launch(m->cache_lat.f(), (int64_t)rows * max_seq * m->lat, L, (int64_t)max_seq * m->lat, 0, 1, m->lat, P, G, plen, m->prev.f(), d, nullptr, s));
+    GN_TRY(kv_replicate_launch(m->cache_rope.f(), (int64_t)rows * max_seq * rw, L, (int64_t)max_seq * rw, 0, 1, rw, P, G, plen, nullptr, d, nullptr, s));
+  } else {
+    GN_TRY(kv_replicate_launch(m->cache.f(), (int64_t)rows * Hkv * max_seq * D, 2 * L, (int64_t)Hkv * max_seq * D, (int64_t)max_seq * D, Hkv, D, P, G, plen,
+                               m->prev.f(), d, nullptr, s));
+  }
   GN_TRY(fill_i32_launch(m->pos.i(), plen, rows, s));
   GN_CUDA(cudaEventRecord(m->ev[1], s));
 
@@ -741,6 +732,7 @@ int gn_policy_gradient_step(gn_model* m, const int32_t* inputs, const int32_t* t
                             float* loss, float* nll_tap, float* dlogits_tap, float* logits_tap) {
   GN_TRY(enter_compute(m));
   GN_REQUIRE(inputs && targets && adv && loss, "gn_policy_gradient_step: null argument");
+  if (m->moe() || m->mla()) { set_error("the training pass covers the dense preset only; latent attention and routed experts are inference-only here"); return GN_ERR_UNSUPPORTED; }
   GN_REQUIRE(B > 0 && T > 1, "gn_policy_gradient_step: batch must be positive and seq > 1 (model/transformer.go:269-271)");
   GN_REQUIRE(T <= m->cfg.sequence_len, "sequence %d longer than sequence_len %d", T, m->cfg.sequence_len);
   const int V = m->V, L = m->L;

@@ -1,0 +1,134 @@
+// Structures shared by the resident-session translation units (model.cu, model_latent.cu).
+#pragma once
+#include <map>
+#include <string>
+#include <vector>
+
+#include "kernels.cuh"
+#include "model_kernels.cuh"
+#include "ctx.cuh"
+
+namespace gnm {
+using namespace gn;
+
+struct DevBuf {
+  void* p = nullptr;
+  size_t bytes = 0;
+  int ensure(size_t n) {
+    if (n <= bytes) return GN_OK;
+    if (p) cudaFree(p);
+    p = nullptr; bytes = 0;
+    cudaError_t e = cudaMalloc(&p, n);
+    if (e != cudaSuccess) { set_error("cudaMalloc(%zu bytes) failed: %s", n, cudaGetErrorString(e)); return GN_ERR_NOMEM; }
+    bytes = n;
+    return GN_OK;
+  }
+  void release() { if (p) cudaFree(p); p = nullptr; bytes = 0; }
+  float* f() const { return (float*)p; }
+  int32_t* i() const { return (int32_t*)p; }
+};
+
+struct ParamInfo {
+  std::string name;
+  int rows = 0, cols = 0;
+  int64_t offset = 0;
+};
+
+// A bump allocator over one DevBuf: buffers of one pass are carved in order.
+struct Arena {
+  DevBuf buf;
+  size_t used = 0;
+  size_t planned = 0;
+  bool planning = false;
+  float* take(size_t floats) {
+    size_t bytes = ((floats * sizeof(float) + 255) / 256) * 256;
+    if (planning) { planned += bytes; return nullptr; }
+    float* r = (float*)((char*)buf.p + used);
+    used += bytes;
+    return r;
+  }
+};
+
+struct LayerOffsets {
+  int64_t qkv, proj, ve_gate, fc, mproj, ve; bool has_ve;
+  // latent attention (model/mla.go:15-37): mla_cat = [q_down; kv_down; q_rope; k_rope], adjacent, all with d columns
+  int64_t mla_cat = -1, mla_q_up = -1, mla_k_up = -1, mla_v_up = -1;
+  // routed experts (model/moe.go:26-45); with them fc = [c_fc; c_gate] adjacent and mproj = the shared expert's c_proj
+  int64_t router = -1, router_bias = -1, exp_gate = -1, exp_up = -1, exp_down = -1;
+};
+
+struct LayerSaved {
+  float *Xin, *H, *QKV, *QKROT, *O, *LSE, *VESIG, *MID, *M, *U, *HID, *XOUT;
+};
+
+}  // namespace gnm
+using namespace gnm;
+
+struct gn_model {
+  gn_ctx* ctx = nullptr;
+  gn_config cfg{};
+  int d = 0, L = 0, Hq = 0, Hkv = 0, D = 0, R = 0, V = 0, Vp = 0, W = 0, KV = 0;
+  // DeepSeekMoE / latent attention (zero when off)
+  int E = 0, topk = 0, eh = 0, sh = 0; float moe_clamp = 0.0f, moe_scale = 0.0f;
+  int lat = 0, rope = 0, content = 0;
+  bool moe() const { return E > 0; }
+  bool mla() const { return lat > 0; }
+  std::vector<int> windows;
+  std::vector<ParamInfo> params;               // sorted by name
+  std::map<std::string, int> index;
+  int64_t total = 0;
+  DevBuf P, G;
+  std::vector<LayerOffsets> lo;
+  int64_t off_wte = 0, off_lm = 0, off_rho = 0, off_chi = 0, off_smear_gate = 0, off_smear_lambda = 0, off_backout = 0;
+  DevBuf cosb, sinb, sacc;
+  // inference state
+  DevBuf cache, prev, pos, ctxlen, ids_dev, sampled, seeds, out_tokens, out_lengths, done, n_done, sel;
+  DevBuf part_acc, part_ms, step_dev;
+  DevBuf cache_lat, cache_rope;   // latent attention: [layer][row][max_seq][lat] and [layer][row][max_seq][Hkv*rope]
+  Arena infer, train;
+  DevBuf tgt_dev, adv_dev, rowloss, loss_dev, in_dev;
+  std::map<std::string, float> phase_ms;
+  cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
+  bool weights_dirty = true;   // cached tensor-core operand splits of the parameters are stale
+
+  float* p(int64_t off) const { return P.f() + off; }
+  float* g(int64_t off) const { return G.f() + off; }
+  cudaStream_t s() const { return ctx->stream; }
+};
+
+namespace gnm {
+using namespace gn;
+
+inline int gemm(gn_model* m, const gn::GemmArgs& a) { return gn::gemm_dispatch(a, m->ctx->gemm_kind, m->s()); }
+
+enum Mode { MODE_PLAIN, MODE_PREFILL, MODE_DECODE, MODE_TRAIN };
+
+struct FwdBufs {
+  float *E, *X0, *Xa, *Xb, *H, *QKV, *O, *M, *HID, *BO, *Y, *LOGITS;
+  float *S1h, *S1l, *S4h, *S4l;   // producer-written tf32 splits: one [rows, d] pair and one [rows, 4d] pair, reused by every layer
+  // train only
+  float *SIG, *FP;
+  std::vector<LayerSaved> layers;
+  // latent attention (inference): fused down/rope projections, content queries, absorbed queries, attended latents
+  float *P1 = nullptr, *QC = nullptr, *QF = nullptr, *AL = nullptr;
+  // routed experts (inference)
+  float *UG = nullptr, *SHH = nullptr, *SHO = nullptr, *RL = nullptr, *PR = nullptr, *SELW = nullptr, *GATH = nullptr, *GG = nullptr, *GU = nullptr, *GO = nullptr;
+  int32_t *SEL = nullptr, *CNT = nullptr, *POSI = nullptr;
+};
+
+struct FwdArgs {
+  Mode mode;
+  const int32_t* ids;      // device [B*T]
+  int B, T;
+  int cache_rows = 0, cache_row_mul = 1, max_seq = 0;
+  int logits_rows = 0;     // rows that get logits (PLAIN/TRAIN: all; PREFILL: B; DECODE: B)
+};
+
+// model_latent.cu: the two block variants of the latent preset, inference only.
+// Attention of layer l from H = norm(x) (with its tf32 split in b.S1h/b.S1l on the tensor-core path):
+// writes the head outputs [rows, Hq*D] to O (before c_proj) and appends to the latent cache.
+int latent_attention(gn_model* m, FwdBufs& b, const FwdArgs& a, int l, const float* H, float* O);
+// Feed-forward of layer l: XOUT = MID + shared_expert(Mn) + routed_experts(Mn).
+int moe_ffn(gn_model* m, FwdBufs& b, const FwdArgs& a, int l, const float* Mn, const float* MID, float* XOUT);
+
+}  // namespace gnm

@@ -308,8 +308,10 @@ int kv_replicate_launch(float* cache, int64_t layer_stride, int n_layer2, int64_
   dim3 grid(std::max(1, std::min(ceil_div(total, 256), 64)), n_prompts, n_layer2);
   kv_replicate_kernel<<<grid, 256, 0, s>>>(cache, layer_stride, row_stride, head_stride, Hkv, D, group, len);
   GN_LAUNCH_CHECK();
-  prev_replicate_kernel<<<n_prompts, 256, 0, s>>>(prev, d, pos, n_prompts, group);
-  GN_LAUNCH_CHECK();
+  if (prev) {
+    prev_replicate_kernel<<<n_prompts, 256, 0, s>>>(prev, d, pos, n_prompts, group);
+    GN_LAUNCH_CHECK();
+  }
   return GN_OK;
 }
 

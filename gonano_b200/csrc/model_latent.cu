@@ -1,0 +1,267 @@
+// The two block variants of the latent preset, inference only:
+//   latent_attention  absorbed multi-head latent attention (model/mla.go:185-279): the cache holds one
+//                     latent row and one rotary key row per token; the content-key up-projection is
+//                     folded into the query and the value up-projection is applied to the attended
+//                     latent, so no per-position key or value is ever materialised.
+//   moe_ffn           DeepSeekMoE feed-forward (model/block.go:39-46, model/moe.go:118-169): a shared
+//                     SwiGLU expert plus top-k routed experts; routing, the stable expert-major
+//                     permutation and the weighted un-permutation run on the device.
+//
+// Data layout
+//   latent cache  [layer][row][max_seq][latent]           (model/kvcache.go:224-237)
+//   rotary cache  [layer][row][max_seq][Hkv * rope]
+//   routed rows   expert-major [rows * k, width], position = offset[expert] + arrival order in
+//                 (row, slot) order, exactly the gather of model/moe.go:130-153.
+#include "model_internal.cuh"
+
+namespace gnm {
+
+namespace {
+
+constexpr int WPB = 8;   // warps per block in the row kernels
+
+// ------------------------------------------------------------------ latent attention glue
+// One warp per (token row, head slot); slots = Hq rotary queries, Hkv rotary keys, 1 latent copy.
+//   query slot: rotate P1's q_rope head (model/rotary.go:43-75, every channel rotates) into QF[r, hq, lat:]
+//   key slot:   rotate P1's k_rope head into the rotary cache at the token's position
+//   last slot:  copy the kv latent into the latent cache
+struct MlaPost {
+  const float* P1; int64_t n1;       // [rows, n1] = [q_lat | kv_lat | q_rope (Hq*rope) | k_rope (Hkv*rope)]
+  float* QF;                          // [rows, Hq, lat + rope]
+  float* lat_cache; float* rope_cache;  // this layer's slices
+  const float* cosv; const float* sinv;
+  const int32_t* pos; int cache_row_mul, max_seq;
+  int B, T, Hq, Hkv, lat, rope;
+};
+__global__ void __launch_bounds__(WPB * 32) mla_post_kernel(MlaPost p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slots = p.Hq + p.Hkv + 1;
+  const int64_t idx = (int64_t)blockIdx.x * WPB + warp;
+  const int64_t rows = (int64_t)p.B * p.T;
+  if (idx >= rows * slots) return;
+  const int64_t r = idx / slots; const int slot = (int)(idx % slots);
+  const int b = (int)(r / p.T), t = (int)(r % p.T);
+  const int crow = b * p.cache_row_mul;
+  const int pos = p.pos[crow] + t;
+  const float* row = p.P1 + r * p.n1;
+  const int half = p.rope / 2;
+  if (slot == p.Hq + p.Hkv) {
+    float* dst = p.lat_cache + ((int64_t)crow * p.max_seq + pos) * p.lat;
+    for (int c = lane; c < p.lat; c += 32) dst[c] = row[p.lat + c];
+    return;
+  }
+  const float* src; float* dst;
+  if (slot < p.Hq) { src = row + 2 * p.lat + (int64_t)slot * p.rope; dst = p.QF + (r * p.Hq + slot) * (int64_t)(p.lat + p.rope) + p.lat; }
+  else { const int hk = slot - p.Hq; src = row + 2 * p.lat + (int64_t)(p.Hq + hk) * p.rope; dst = p.rope_cache + (((int64_t)crow * p.max_seq + pos) * p.Hkv + hk) * p.rope; }
+  const float* cw = p.cosv + (int64_t)pos * half; const float* sw = p.sinv + (int64_t)pos * half;
+  for (int j = lane; j < half; j += 32) {
+    const float a = src[j], c = src[half + j];
+    dst[j] = __fadd_rn(__fmul_rn(a, cw[j]), __fmul_rn(c, sw[j]));
+    dst[half + j] = __fadd_rn(__fmul_rn(-a, sw[j]), __fmul_rn(c, cw[j]));
+  }
+}
+
+// One warp per (token row, query head): online softmax over the cached positions with
+// score = q_abs . latent[j] + q_rope . k_rope[j, hk]; the output is the attended latent.
+// Lane e-th element = channel 32 e + lane; latent <= 512, rope <= 64.
+struct MlaAttn {
+  const float* QF; const float* lat_cache; const float* rope_cache; float* AL;
+  const int32_t* pos; int cache_row_mul, max_seq;
+  int B, T, Hq, Hkv, lat, rope, window;
+};
+__global__ void __launch_bounds__(128) mla_attention_kernel(MlaAttn p) {
+  constexpr int ME = 16;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t idx = (int64_t)blockIdx.x * 4 + warp;
+  const int64_t rows = (int64_t)p.B * p.T;
+  if (idx >= rows * p.Hq) return;
+  const int64_t r = idx / p.Hq; const int hq = (int)(idx % p.Hq), hk = hq / (p.Hq / p.Hkv);
+  const int b = (int)(r / p.T), t = (int)(r % p.T);
+  const int crow = b * p.cache_row_mul;
+  const int qpos = p.pos[crow] + t;
+  const int hd = p.lat + p.rope;
+  const float* q = p.QF + (r * p.Hq + hq) * (int64_t)hd;
+  float qa[ME], acc[ME], qr[2];
+#pragma unroll
+  for (int e = 0; e < ME; ++e) { const int c = e * 32 + lane; qa[e] = c < p.lat ? q[c] : 0.0f; acc[e] = 0.0f; }
+#pragma unroll
+  for (int e = 0; e < 2; ++e) { const int c = e * 32 + lane; qr[e] = c < p.rope ? q[p.lat + c] : 0.0f; }
+  const float* lc = p.lat_cache + (int64_t)crow * p.max_seq * p.lat;
+  const float* rc = p.rope_cache + (int64_t)crow * p.max_seq * p.Hkv * p.rope + (int64_t)hk * p.rope;
+  int j0 = 0;
+  if (p.window >= 0) j0 = max(0, qpos - p.window);   // kernels/scalar/attention.go: masked when qpos - j > window
+  float mrun = -INFINITY, lrun = 0.0f;
+  for (int j = j0; j <= qpos; ++j) {
+    const float* lj = lc + (int64_t)j * p.lat;
+    const float* rj = rc + (int64_t)j * p.Hkv * p.rope;
+    float lv[ME];
+    float s = 0.0f;
+#pragma unroll
+    for (int e = 0; e < ME; ++e) { const int c = e * 32 + lane; lv[e] = (e * 32 < p.lat && c < p.lat) ? lj[c] : 0.0f; s = fmaf(qa[e], lv[e], s); }
+#pragma unroll
+    for (int e = 0; e < 2; ++e) { const int c = e * 32 + lane; if (c < p.rope) s = fmaf(qr[e], rj[c], s); }
+    s = warp_sum(s);
+    const float mn = fmaxf(mrun, s);
+    const float alpha = (mrun == -INFINITY) ? 0.0f : __expf(mrun - mn);
+    const float pj = __expf(s - mn);
+    lrun = lrun * alpha + pj;
+#pragma unroll
+    for (int e = 0; e < ME; ++e) acc[e] = acc[e] * alpha + pj * lv[e];
+    mrun = mn;
+  }
+  const float inv = lrun > 0.0f ? 1.0f / lrun : 0.0f;
+  float* out = p.AL + (r * p.Hq + hq) * (int64_t)p.lat;
+#pragma unroll
+  for (int e = 0; e < ME; ++e) { const int c = e * 32 + lane; if (c < p.lat) out[c] = acc[e] * inv; }
+}
+
+// ------------------------------------------------------------------ routed experts glue
+// hidden[r, c] = silu(clamp_above(gate)) * clamp(up) with UG = [up | gate] per row (kernels/scalar/elementwise.go:105-134).
+__global__ void __launch_bounds__(256) swiglu_rows_kernel(float* dst, const float* ug, int64_t rows, int width, float clampv) {
+  const int64_t total = rows * width;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / width; const int c = (int)(i % width);
+    float u = ug[r * 2 * width + c], g = ug[r * 2 * width + width + c];
+    if (clampv > 0.0f && g >= clampv) g = clampv;
+    if (clampv > 0.0f) { if (u > clampv) u = clampv; else if (u < -clampv) u = -clampv; }
+    const float sg = (float)(1.0 / (1.0 + exp((double)(-g))));
+    dst[i] = g * sg * u;
+  }
+}
+
+// One CTA: counts per expert, then the stable expert-major position of every (row, slot) entry in
+// entry order (model/moe.go:127-153).  Shared memory holds the per-expert counters and, per chunk of
+// blockDim entries, the per-warp tallies that turn warp-local ranks into global ones.
+constexpr int kMaxExperts = 64;
+__global__ void __launch_bounds__(1024) moe_route_kernel(const int32_t* __restrict__ sel, int64_t total, int E, int32_t* __restrict__ counts,
+                                                         int32_t* __restrict__ posi) {
+  __shared__ int cnt[kMaxExperts], offs[kMaxExperts], running[kMaxExperts];
+  __shared__ int warp_cnt[32][kMaxExperts];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
+  if (tid < kMaxExperts) { cnt[tid] = 0; running[tid] = 0; }
+  __syncthreads();
+  for (int64_t i = tid; i < total; i += blockDim.x) atomicAdd(&cnt[sel[i]], 1);
+  __syncthreads();
+  if (tid == 0) { int cur = 0; for (int e = 0; e < E; ++e) { offs[e] = cur; cur += cnt[e]; } }
+  if (tid < E) counts[tid] = cnt[tid];
+  for (int64_t base = 0; base < total; base += blockDim.x) {
+    for (int k = tid; k < 32 * kMaxExperts; k += blockDim.x) (&warp_cnt[0][0])[k] = 0;
+    __syncthreads();
+    const int64_t i = base + tid;
+    const bool live = i < total;
+    const int e = live ? sel[i] : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    if (live && rank == 0) warp_cnt[warp][e] = __popc(peers);
+    __syncthreads();
+    if (live) {
+      int before = running[e];
+      for (int w = 0; w < warp; ++w) before += warp_cnt[w][e];
+      posi[i] = offs[e] + before + rank;
+    }
+    __syncthreads();
+    if (tid < E) { int add = 0; for (int w = 0; w < nw; ++w) add += warp_cnt[w][tid]; running[tid] += add; }
+    __syncthreads();
+  }
+}
+
+// gathered[posi[i]] = x[i / k]   (one warp per entry)
+__global__ void __launch_bounds__(WPB * 32) moe_gather_kernel(float* gathered, const float* x, const int32_t* posi, int64_t total, int k, int d) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t i = (int64_t)blockIdx.x * WPB + warp;
+  if (i >= total) return;
+  const float* src = x + (i / k) * d; float* dst = gathered + (int64_t)posi[i] * d;
+  for (int c = lane; c < d; c += 32) dst[c] = src[c];
+}
+
+// XOUT[r] = MID[r] + (shared[r] + routed[r]),  routed[r] = sum over the row's entries in ascending
+// position of (weight * scale) * expert_out[position], each product and sum rounded (model/moe.go:160-169,
+// model/block.go:41-45).
+__global__ void __launch_bounds__(256) moe_combine_kernel(float* xout, const float* mid, const float* shared, const float* expert_out, const int32_t* posi,
+                                                          const float* selw, float scale, int64_t rows, int k, int d) {
+  const int64_t total = rows * d;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / d; const int c = (int)(i % d);
+    int ps[8]; float ws[8];
+    for (int s = 0; s < k; ++s) { ps[s] = posi[r * k + s]; ws[s] = __fmul_rn(selw[r * k + s], scale); }
+    for (int a = 1; a < k; ++a) {   // insertion sort by position (k <= 8)
+      const int pa = ps[a]; const float wa = ws[a]; int j = a - 1;
+      while (j >= 0 && ps[j] > pa) { ps[j + 1] = ps[j]; ws[j + 1] = ws[j]; --j; }
+      ps[j + 1] = pa; ws[j + 1] = wa;
+    }
+    float routed = 0.0f;
+    for (int s = 0; s < k; ++s) routed = __fadd_rn(routed, __fmul_rn(ws[s], expert_out[(int64_t)ps[s] * d + c]));
+    xout[i] = __fadd_rn(mid[i], __fadd_rn(shared[i], routed));
+  }
+}
+
+int grid_for(int64_t n) { return (int)std::max<int64_t>(1, std::min<int64_t>((n + 255) / 256, (int64_t)kNumSM * 16)); }
+
+}  // namespace
+
+int latent_attention(gn_model* m, FwdBufs& b, const FwdArgs& a, int l, const float* H, float* O) {
+  const int d = m->d, Hq = m->Hq, Hkv = m->Hkv, D = m->D, lat = m->lat, rope = m->rope, content = m->content;
+  const int ratio = Hq / Hkv, hd = lat + rope;
+  const int64_t rows = (int64_t)a.B * a.T;
+  const int n1 = 2 * lat + (Hq + Hkv) * rope;
+  const LayerOffsets& o = m->lo[l];
+  const bool tc = m->ctx->gemm_kind == 1;
+  cudaStream_t s = m->s();
+  GN_REQUIRE(a.cache_rows > 0 && a.max_seq > 0 && m->cache_lat.p && m->cache_rope.p, "latent attention needs its cache (model/mla.go:196-198)");
+  // [q_latent | kv_latent | q_rope | k_rope] = H [q_down; kv_down; q_rope; k_rope]^T
+  { GemmArgs g; g.A = H; g.lda = d; g.B = m->p(o.mla_cat); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = b.P1; g.ldc = n1; g.M = (int)rows; g.N = n1; g.K = d;
+    if (tc) { g.a_hi = b.S1h; g.a_lo = b.S1l; } GN_TRY(gemm(m, g)); }
+  // content queries [rows, Hq*content] = q_latent Wq_up^T
+  { GemmArgs g; g.A = b.P1; g.lda = n1; g.B = m->p(o.mla_q_up); g.b_static = 1; g.ldb = lat; g.b_trans = 1; g.C = b.QC; g.ldc = (int64_t)Hq * content;
+    g.M = (int)rows; g.N = Hq * content; g.K = lat; GN_TRY(gemm(m, g)); }
+  // absorbed queries: QF[:, hq, 0:lat] = QC[:, hq, :] Wk_up[hk]   (Wk_up[hk] is [content, lat]; model/mla.go:232-243)
+  for (int hq = 0; hq < Hq; ++hq) {
+    const int hk = hq / ratio;
+    GemmArgs g; g.A = b.QC + (int64_t)hq * content; g.lda = (int64_t)Hq * content; g.B = m->p(o.mla_k_up) + (int64_t)hk * content * lat; g.b_static = 1; g.ldb = lat;
+    g.b_trans = 0; g.C = b.QF + (int64_t)hq * hd; g.ldc = (int64_t)Hq * hd; g.M = (int)rows; g.N = lat; g.K = content; GN_TRY(gemm(m, g));
+  }
+  const int64_t lat_layer = (int64_t)a.cache_rows * a.max_seq * lat, rope_layer = (int64_t)a.cache_rows * a.max_seq * Hkv * rope;
+  float* lcache = m->cache_lat.f() + (int64_t)l * lat_layer; float* rcache = m->cache_rope.f() + (int64_t)l * rope_layer;
+  MlaPost pp; pp.P1 = b.P1; pp.n1 = n1; pp.QF = b.QF; pp.lat_cache = lcache; pp.rope_cache = rcache; pp.cosv = m->cosb.f(); pp.sinv = m->sinb.f();
+  pp.pos = m->pos.i(); pp.cache_row_mul = a.cache_row_mul; pp.max_seq = a.max_seq; pp.B = a.B; pp.T = a.T; pp.Hq = Hq; pp.Hkv = Hkv; pp.lat = lat; pp.rope = rope;
+  { const int64_t n = rows * (Hq + Hkv + 1); mla_post_kernel<<<ceil_div(n, WPB), WPB * 32, 0, s>>>(pp); GN_LAUNCH_CHECK(); }
+  MlaAttn pa; pa.QF = b.QF; pa.lat_cache = lcache; pa.rope_cache = rcache; pa.AL = b.AL; pa.pos = m->pos.i(); pa.cache_row_mul = a.cache_row_mul;
+  pa.max_seq = a.max_seq; pa.B = a.B; pa.T = a.T; pa.Hq = Hq; pa.Hkv = Hkv; pa.lat = lat; pa.rope = rope; pa.window = m->windows[l];
+  { const int64_t n = rows * Hq; mla_attention_kernel<<<ceil_div(n, 4), 128, 0, s>>>(pa); GN_LAUNCH_CHECK(); }
+  // head outputs: O[:, hq, :] = AL[:, hq, :] Wv_up[hk]^T   (Wv_up[hk] is [D, lat]; model/mla.go:264-274)
+  for (int hq = 0; hq < Hq; ++hq) {
+    const int hk = hq / ratio;
+    GemmArgs g; g.A = b.AL + (int64_t)hq * lat; g.lda = (int64_t)Hq * lat; g.B = m->p(o.mla_v_up) + (int64_t)hk * D * lat; g.b_static = 1; g.ldb = lat; g.b_trans = 1;
+    g.C = O + (int64_t)hq * D; g.ldc = (int64_t)Hq * D; g.M = (int)rows; g.N = D; g.K = lat; GN_TRY(gemm(m, g));
+  }
+  return GN_OK;
+}
+
+int moe_ffn(gn_model* m, FwdBufs& b, const FwdArgs& a, int l, const float* Mn, const float* MID, float* XOUT) {
+  const int d = m->d, E = m->E, K = m->topk, eh = m->eh, sh = m->sh;
+  const int64_t rows = (int64_t)a.B * a.T, total = rows * K;
+  const LayerOffsets& o = m->lo[l];
+  const bool tc = m->ctx->gemm_kind == 1;
+  cudaStream_t s = m->s();
+  // ---- shared expert (model/mlp.go:62-76 with the SwiGLU activation): [up | gate] in one product
+  { GemmArgs g; g.A = Mn; g.lda = d; g.B = m->p(o.fc); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = b.UG; g.ldc = 2 * sh; g.M = (int)rows; g.N = 2 * sh; g.K = d;
+    if (tc) { g.a_hi = b.S1h; g.a_lo = b.S1l; } GN_TRY(gemm(m, g)); }
+  swiglu_rows_kernel<<<grid_for(rows * sh), 256, 0, s>>>(b.SHH, b.UG, rows, sh, m->moe_clamp); GN_LAUNCH_CHECK();
+  { GemmArgs g; g.A = b.SHH; g.lda = sh; g.B = m->p(o.mproj); g.b_static = 1; g.ldb = sh; g.b_trans = 1; g.C = b.SHO; g.ldc = d; g.M = (int)rows; g.N = d; g.K = sh;
+    GN_TRY(gemm(m, g)); }
+  // ---- router (model/moe.go:123-124): selection on logits + bias, weights = softmax(logits) of the selected
+  { GemmArgs g; g.A = Mn; g.lda = d; g.B = m->p(o.router); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = b.RL; g.ldc = E; g.M = (int)rows; g.N = E; g.K = d;
+    GN_TRY(gemm_dispatch(g, 0, s)); }   // E columns: the float32 kernel (routing must not depend on a split's rounding)
+  GN_TRY(moe_gate_topk_launch(b.RL, m->p(o.router_bias), b.PR, b.SEL, b.SELW, (int)rows, E, K, s));
+  moe_route_kernel<<<1, 1024, 0, s>>>(b.SEL, total, E, b.CNT, b.POSI); GN_LAUNCH_CHECK();
+  moe_gather_kernel<<<ceil_div(total, WPB), WPB * 32, 0, s>>>(b.GATH, Mn, b.POSI, total, K, d); GN_LAUNCH_CHECK();
+  // ---- experts: grouped products over the expert-major rows (model/moe.go:155-158)
+  GN_TRY(grouped_matmul_t_launch(b.GG, b.GATH, m->p(o.exp_gate), b.CNT, E, eh, d, total, s));
+  GN_TRY(grouped_matmul_t_launch(b.GU, b.GATH, m->p(o.exp_up), b.CNT, E, eh, d, total, s));
+  GN_TRY(ew_launch(EW_SWIGLU, b.GG, b.GG, b.GU, m->moe_clamp, total * eh, s));
+  GN_TRY(grouped_matmul_t_launch(b.GO, b.GG, m->p(o.exp_down), b.CNT, E, d, eh, total, s));
+  moe_combine_kernel<<<grid_for(rows * d), 256, 0, s>>>(XOUT, MID, b.SHO, b.GO, b.POSI, b.SELW, m->moe_scale, rows, K, d); GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+}  // namespace gnm

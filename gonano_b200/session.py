@@ -61,12 +61,16 @@ class Context:
 
 
 class Model:
-    """``model.Transformer`` (dense preset) resident on the device."""
+    """``model.Transformer`` resident on the device: the dense preset (inference and training) and the latent preset
+    (absorbed MLA + DeepSeekMoE, inference)."""
 
-    def __init__(self, ctx: Context, sequence_len, vocab_size, n_layer, n_head, n_kv_head, embed_dim, rotary_dims=0, window_pattern="L"):
+    def __init__(self, ctx: Context, sequence_len, vocab_size, n_layer, n_head, n_kv_head, embed_dim, rotary_dims=0, window_pattern="L",
+                 n_experts=0, experts_per_token=0, expert_hidden=0, shared_hidden=0, moe_clamp=0.0, moe_scale=0.0, mla_latent=0,
+                 mla_rotary_dims=0):
         self.ctx = ctx
         self.lib = ctx.lib
-        self.cfg = GnConfig(sequence_len, vocab_size, n_layer, n_head, n_kv_head, embed_dim, rotary_dims, window_pattern.encode())
+        self.cfg = GnConfig(sequence_len, vocab_size, n_layer, n_head, n_kv_head, embed_dim, rotary_dims, window_pattern.encode(),
+                            n_experts, experts_per_token, expert_hidden, shared_hidden, moe_clamp, moe_scale, mla_latent, mla_rotary_dims)
         self.vocab = vocab_size
         self.h = C.c_void_p()
         check(self.lib.gn_model_create(ctx.h, C.byref(self.cfg), C.byref(self.h)))

@@ -31,6 +31,20 @@ def dense_config(name: str) -> dict:
     raise KeyError(name)
 
 
+def latent_config(name: str) -> dict:
+    """Latent-preset workloads (model/preset.go:120-128: absorbed MLA + DeepSeekMoE, grouped queries 2:1)."""
+    if name == "latent-tiny":  # the scale of the reference's own MLA / MoE unit-test models
+        return dict(sequence_len=32, vocab_size=96, n_layer=2, n_head=4, n_kv_head=2, embed_dim=64, window_pattern="L",
+                    n_experts=4, experts_per_token=2, expert_hidden=32, shared_hidden=32, mla_latent=24, mla_rotary_dims=8)
+    if name == "latent-small":  # head_dim 64, 8 experts: exercises the tensor-core products of the latent blocks
+        return dict(sequence_len=256, vocab_size=2048, n_layer=3, n_head=4, n_kv_head=2, embed_dim=256, window_pattern="L",
+                    n_experts=8, experts_per_token=2, expert_hidden=128, shared_hidden=128, mla_latent=128)
+    if name == "c3":  # d_model 1024, 8 heads, latent 256, 8 layers, 1 shared + 16 routed experts of hidden 512, top-2
+        return dict(sequence_len=1024, vocab_size=32768, n_layer=8, n_head=8, n_kv_head=4, embed_dim=1024, window_pattern="L",
+                    n_experts=16, experts_per_token=2, expert_hidden=512, shared_hidden=512, mla_latent=256)
+    raise KeyError(name)
+
+
 def fill_weights(names, shape_of, seed: int, std: float = 0.02, smear_lambda: float = 0.7):
     """Yield (name, float32 array) for every parameter name, deterministically."""
     n_layer = max((int(n.split(".")[2]) for n in names if n.startswith("transformer.h.")), default=-1) + 1

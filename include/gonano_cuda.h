@@ -47,6 +47,7 @@ extern "C" {
 #define GN_ERR_COMM 3    /* collective communication error */
 #define GN_ERR_TIMEOUT 4 /* a bounded device-side wait ran out */
 #define GN_ERR_NOMEM 5
+#define GN_ERR_UNSUPPORTED 6 /* valid request outside what this library implements (e.g. training a latent-preset model) */
 
 const char* gn_last_error(void);
 /* Library version string. */
@@ -185,7 +186,8 @@ int gn_pg_loss_backward_static(const float* logits, const int32_t* targets, cons
 typedef struct gn_ctx gn_ctx;
 typedef struct gn_model gn_model;
 
-/* model.Config fields the dense preset uses (model/config.go:9-124). */
+/* model.Config fields of the dense preset and of the latent preset (model/config.go:9-124).
+ * The last eight are zero for a dense model. */
 typedef struct gn_config {
   int32_t sequence_len;  /* SequenceLen: rotary table covers 10x this; window sizes derive from it */
   int32_t vocab_size;    /* VocabSize (padded to a multiple of 64 internally, model/config.go:619-624) */
@@ -195,6 +197,18 @@ typedef struct gn_config {
   int32_t embed_dim;     /* EmbedDim */
   int32_t rotary_dims;   /* RotaryDims (<= 0: whole head) */
   char window_pattern[16]; /* WindowPattern, e.g. "SSSL" (model/config.go:629-645); empty = "L" */
+  /* DeepSeekMoE feed-forward (model/config.go:92-123): n_experts > 0 replaces the dense MLP of every block by a
+   * shared SwiGLU expert plus routed experts (model/block.go:23-25).  Inference only in this library. */
+  int32_t n_experts;          /* NumExperts */
+  int32_t experts_per_token;  /* NumExpertsPerToken (<= 0: 2) */
+  int32_t expert_hidden;      /* ExpertHiddenDim (<= 0: embed_dim) */
+  int32_t shared_hidden;      /* SharedExpertHiddenDim (<= 0: expert_hidden) */
+  float moe_clamp;            /* MoEClamp (0: 10) */
+  float moe_scale;            /* MoEScale (0: 1) */
+  /* Absorbed multi-head latent attention (model/config.go:80-91): mla_latent > 0 enables it; value embeddings are
+   * then off (model/transformer.go:73).  Inference only in this library. */
+  int32_t mla_latent;         /* MLALatent */
+  int32_t mla_rotary_dims;    /* MLARotaryDims (<= 0: min(head_dim/2, 64), even) */
 } gn_config;
 
 /* device: CUDA ordinal.  stream: a cudaStream_t to run on, or NULL for a

@@ -237,6 +237,9 @@ void or_philox(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0, 
 struct or_config {
   int32_t sequence_len, vocab_size, n_layer, n_head, n_kv_head, embed_dim, rotary_dims;
   char window_pattern[16];
+  int32_t n_experts, experts_per_token, expert_hidden, shared_hidden;
+  float moe_clamp, moe_scale;
+  int32_t mla_latent, mla_rotary_dims;
 };
 
 void* or_model_create(const or_config* c, int mode) {
@@ -244,6 +247,8 @@ void* or_model_create(const or_config* c, int mode) {
   cfg.sequence_len = c->sequence_len; cfg.vocab = c->vocab_size; cfg.n_layer = c->n_layer; cfg.n_head = c->n_head;
   cfg.n_kv_head = c->n_kv_head; cfg.embed_dim = c->embed_dim; cfg.rotary_dims = c->rotary_dims;
   cfg.window_pattern = c->window_pattern[0] ? std::string(c->window_pattern) : std::string("L");
+  cfg.n_experts = c->n_experts; cfg.experts_per_token = c->experts_per_token; cfg.expert_hidden = c->expert_hidden; cfg.shared_hidden = c->shared_hidden;
+  cfg.moe_clamp = c->moe_clamp; cfg.moe_scale = c->moe_scale; cfg.mla_latent = c->mla_latent; cfg.mla_rotary_dims = c->mla_rotary_dims;
   return new Model(cfg, mode);
 }
 void or_model_destroy(void* m) { delete (Model*)m; }
@@ -275,6 +280,16 @@ void or_rotary_tables(float* x, const float* cosv, const float* sinv, int half, 
 // Forward without cache ([B,T] -> [B,T,V]); T must be > 1.
 void or_model_forward(void* m, const int32_t* ids, int B, int T, float* logits) {
   std::vector<float> out; ((Model*)m)->forward(out, ids, B, T, nullptr); std::copy(out.begin(), out.end(), logits);
+}
+
+// MLA models: the same function through the un-absorbed (training) construction (model/mla_test.go:279-293).
+void or_model_forward_unabsorbed(void* m, const int32_t* ids, int B, int T, float* logits) {
+  std::vector<float> out; ((Model*)m)->forward(out, ids, B, T, nullptr, true); std::copy(out.begin(), out.end(), logits);
+}
+// Routed-expert contribution of layer l for rows of normalised activations, with the selected expert ids.
+void or_model_moe_forward(void* m, int layer, const float* flat, int64_t rows, float* out, int32_t* selected) {
+  Model* mm = (Model*)m; std::vector<float> in(flat, flat + (size_t)rows * mm->cfg.embed_dim), o; std::vector<int32_t> sel;
+  mm->moe_forward(o, in, rows, layer, &sel); std::copy(o.begin(), o.end(), out); if (selected) std::copy(sel.begin(), sel.end(), selected);
 }
 
 void* or_cache_create(void* m, int batch, int max_seq) { KVCache* c = new KVCache(); ((Model*)m)->cache_init(*c, batch, max_seq); return c; }

@@ -28,8 +28,26 @@ static const double kRotaryBase = 100000; // model/rotary.go:10
 struct Config {
   int sequence_len = 0, vocab = 0, n_layer = 0, n_head = 0, n_kv_head = 0, embed_dim = 0, rotary_dims = 0;
   std::string window_pattern = "L";
+  // DeepSeekMoE feed-forward (model/config.go:92-123,137-229): n_experts > 0 enables it.
+  int n_experts = 0, experts_per_token = 0, expert_hidden = 0, shared_hidden = 0;
+  float moe_clamp = 0.0f, moe_scale = 0.0f;
+  // Absorbed multi-head latent attention (model/config.go:80-91,249-279): mla_latent > 0 enables it.
+  int mla_latent = 0, mla_rotary_dims = 0;
   int head_dim() const { return embed_dim / n_head; }
-  int rotary_dimension() const { return rotary_dims <= 0 ? head_dim() : rotary_dims; }  // model/config.go:430-444
+  bool moe() const { return n_experts > 0; }
+  bool mla() const { return mla_latent > 0; }
+  int moe_top_k() const { int k = experts_per_token <= 0 ? 2 : experts_per_token; return k > n_experts ? n_experts : k; }  // model/config.go:141-149,220-225
+  int moe_expert_hidden() const { return expert_hidden > 0 ? expert_hidden : embed_dim; }                                  // model/config.go:190-195
+  int moe_shared_hidden() const { return shared_hidden > 0 ? shared_hidden : moe_expert_hidden(); }                       // model/config.go:199-204
+  float moe_effective_clamp() const { return moe_clamp == 0.0f ? 10.0f : moe_clamp; }                                      // model/config.go:152-157
+  float moe_effective_scale() const { return moe_scale == 0.0f ? 1.0f : moe_scale; }                                       // model/config.go:160-165
+  int mla_rope() const {                                                                                                   // model/config.go:262-280
+    if (mla_rotary_dims > 0) return mla_rotary_dims;
+    int w = head_dim() / 2; if (w > 64) w = 64; if (w % 2) --w; return w;
+  }
+  int mla_content() const { return head_dim() - mla_rope(); }
+  // model/config.go:430-444 (with MLA the rotary width is the decoupled rotary width)
+  int rotary_dimension() const { return mla() ? mla_rope() : (rotary_dims <= 0 ? head_dim() : rotary_dims); }
   int padded_vocab() const { return ((vocab + 63) / 64) * 64; }                         // model/config.go:619-624
   // model/config.go:629-645 (integer division truncates toward zero, as in Go).
   std::vector<int> windows() const {
@@ -58,6 +76,8 @@ struct KVCache {
   std::vector<std::vector<std::vector<float>>> k, v;
   std::vector<float> prev;  // [batch, d] pre-smear embedding of the last token
   bool has_prev = false;
+  // MLA (model/kvcache.go:53-59,224-258): [layer][row] -> [max_seq, latent] and [max_seq, Hkv*rope]
+  std::vector<std::vector<std::vector<float>>> mla_latent, mla_rope;
 };
 
 struct LayerCtx {
@@ -112,16 +132,41 @@ struct Model {
     add("lm_head.weight", Vp, d);
     for (int l = 0; l < cfg.n_layer; ++l) {
       std::string p = "transformer.h." + std::to_string(l) + ".";
-      add(p + "attn.c_q.weight", cfg.n_head * D, d);
-      add(p + "attn.c_k.weight", KV, d);
-      add(p + "attn.c_v.weight", KV, d);
+      if (cfg.mla()) {
+        // model/mla.go:41-60, names model/params.go:19-27
+        int lat = cfg.mla_latent, rope = cfg.mla_rope(), content = cfg.mla_content();
+        add(p + "attn.mla_q_down.weight", lat, d);
+        add(p + "attn.mla_q_up.weight", cfg.n_head * content, lat);
+        add(p + "attn.mla_q_rope.weight", cfg.n_head * rope, d);
+        add(p + "attn.mla_kv_down.weight", lat, d);
+        add(p + "attn.mla_k_up.weight", cfg.n_kv_head * content, lat);
+        add(p + "attn.mla_v_up.weight", cfg.n_kv_head * D, lat);
+        add(p + "attn.mla_k_rope.weight", cfg.n_kv_head * rope, d);
+      } else {
+        add(p + "attn.c_q.weight", cfg.n_head * D, d);
+        add(p + "attn.c_k.weight", KV, d);
+        add(p + "attn.c_v.weight", KV, d);
+      }
       add(p + "attn.c_proj.weight", d, d);
-      if (has_value_embedding(l, cfg.n_layer)) {
+      if (!cfg.mla() && has_value_embedding(l, cfg.n_layer)) {   // model/transformer.go:73
         add(p + "attn.ve_gate.weight", cfg.n_kv_head, kVeGateChannels);
         add("value_embeds." + std::to_string(l) + ".weight", Vp, KV);
       }
-      add(p + "mlp.c_fc.weight", 4 * d, d);
-      add(p + "mlp.c_proj.weight", d, 4 * d);
+      if (cfg.moe()) {
+        // shared expert = SwiGLU MLP (model/block.go:23-25, model/mlp.go:51-60); routed experts model/moe.go:49-70
+        int sh = cfg.moe_shared_hidden(), eh = cfg.moe_expert_hidden(), E = cfg.n_experts;
+        add(p + "mlp.c_fc.weight", sh, d);
+        add(p + "mlp.c_gate.weight", sh, d);
+        add(p + "mlp.c_proj.weight", d, sh);
+        add(p + "moe.router.weight", E, d);
+        add(p + "moe.router_bias", 1, E);
+        add(p + "moe.experts.gate.weight", E * eh, d);
+        add(p + "moe.experts.up.weight", E * eh, d);
+        add(p + "moe.experts.down.weight", E * d, eh);
+      } else {
+        add(p + "mlp.c_fc.weight", 4 * d, d);
+        add(p + "mlp.c_proj.weight", d, 4 * d);
+      }
     }
     add("resid_lambdas", 1, cfg.n_layer);
     add("x0_lambdas", 1, cfg.n_layer);
@@ -199,6 +244,22 @@ struct Model {
       }
     }
   }
+  // The same rotation on heads of an explicit width (the MLA rotary heads are `R` wide: every channel rotates).
+  void rotary_w(std::vector<float>& x, int B, int T, int H, int width, int offset) const {
+    int half = R / 2, off = width - R;
+    for (int b = 0; b < B; ++b) for (int t = 0; t < T; ++t) {
+      int pos = offset + t;
+      const float* cw = cosv.data() + (size_t)pos * half; const float* sw = sinv.data() + (size_t)pos * half;
+      for (int h = 0; h < H; ++h) {
+        float* p = x.data() + (((size_t)b * T + t) * H + h) * width + off;
+        for (int j = 0; j < half; ++j) {
+          float a = p[j], c = p[half + j];
+          p[j] = a * cw[j] + c * sw[j];
+          p[half + j] = -a * sw[j] + c * cw[j];
+        }
+      }
+    }
+  }
   static void to_head_major(std::vector<float>& out, const std::vector<float>& in, int B, int T, int H, int D) {
     out.resize(in.size());
     for (int b = 0; b < B; ++b) for (int t = 0; t < T; ++t) for (int h = 0; h < H; ++h)
@@ -241,6 +302,13 @@ struct Model {
       c.k[l].assign((size_t)batch * cfg.n_kv_head, std::vector<float>((size_t)max_seq * D, 0.0f));
       c.v[l].assign((size_t)batch * cfg.n_kv_head, std::vector<float>((size_t)max_seq * D, 0.0f));
     }
+    if (cfg.mla()) {   // model/kvcache.go:224-237 (inference/engine.go:149-151,199-201)
+      c.mla_latent.assign(cfg.n_layer, {}); c.mla_rope.assign(cfg.n_layer, {});
+      for (int l = 0; l < cfg.n_layer; ++l) {
+        c.mla_latent[l].assign((size_t)batch, std::vector<float>((size_t)max_seq * cfg.mla_latent, 0.0f));
+        c.mla_rope[l].assign((size_t)batch, std::vector<float>((size_t)max_seq * cfg.n_kv_head * cfg.mla_rope(), 0.0f));
+      }
+    }
   }
   // model/kvcache.go:383-448 (dense part)
   void cache_replicate(KVCache& dst, const KVCache& src) const {
@@ -251,6 +319,14 @@ struct Model {
           std::copy(src.k[l][h].begin(), src.k[l][h].begin() + (size_t)pos * D, dst.k[l][(size_t)row * cfg.n_kv_head + h].begin());
           std::copy(src.v[l][h].begin(), src.v[l][h].begin() + (size_t)pos * D, dst.v[l][(size_t)row * cfg.n_kv_head + h].begin());
         }
+    if (cfg.mla()) {   // model/kvcache.go:427-436
+      size_t lw = (size_t)cfg.mla_latent, rw = (size_t)cfg.n_kv_head * cfg.mla_rope();
+      for (int l = 0; l < cfg.n_layer; ++l)
+        for (int row = 0; row < dst.batch; ++row) {
+          std::copy(src.mla_latent[l][0].begin(), src.mla_latent[l][0].begin() + (size_t)pos * lw, dst.mla_latent[l][row].begin());
+          std::copy(src.mla_rope[l][0].begin(), src.mla_rope[l][0].begin() + (size_t)pos * rw, dst.mla_rope[l][row].begin());
+        }
+    }
     dst.pos = pos;
     if (src.has_prev) {
       int d = cfg.embed_dim;
@@ -260,10 +336,136 @@ struct Model {
     }
   }
 
-  // Returns logits [B,T,V].  cache may be null (then T must be > 1).
-  void forward(std::vector<float>& logits, const int32_t* ids, int B, int T, KVCache* cache) const {
+  // Absorbed MLA attention of one layer (model/mla.go:185-279).  h = norm(x) [B,T,d]; returns the head
+  // outputs [B,T,Hq*D] before c_proj.  The absorption sums are float32, in the reference's loop order.
+  void mla_inference(std::vector<float>& out, const std::vector<float>& h, int B, int T, int offset, KVCache& cache, int l) const {
+    const int Hq = cfg.n_head, Hkv = cfg.n_kv_head, lat = cfg.mla_latent, rope = cfg.mla_rope(), content = cfg.mla_content();
+    const int ratio = Hq / Hkv, hd = lat + rope, vd = D;
+    const int64_t rows = (int64_t)B * T;
+    std::vector<float> ql, qc, qr, kvl, kr;
+    linear(ql, h, params.at(LP(l, "attn.mla_q_down.weight")), rows);
+    linear(qc, ql, params.at(LP(l, "attn.mla_q_up.weight")), rows);      // [B,T,Hq,content]
+    linear(qr, h, params.at(LP(l, "attn.mla_q_rope.weight")), rows);     // [B,T,Hq,rope]
+    rotary_w(qr, B, T, Hq, rope, offset);
+    linear(kvl, h, params.at(LP(l, "attn.mla_kv_down.weight")), rows);   // [B,T,lat]
+    linear(kr, h, params.at(LP(l, "attn.mla_k_rope.weight")), rows);     // [B,T,Hkv,rope]
+    rotary_w(kr, B, T, Hkv, rope, offset);
+    for (int b = 0; b < B; ++b) for (int t = 0; t < T; ++t) {
+      std::copy(kvl.begin() + ((size_t)b * T + t) * lat, kvl.begin() + ((size_t)b * T + t + 1) * lat, cache.mla_latent[l][b].begin() + (size_t)(offset + t) * lat);
+      std::copy(kr.begin() + ((size_t)b * T + t) * Hkv * rope, kr.begin() + ((size_t)b * T + t + 1) * Hkv * rope,
+                cache.mla_rope[l][b].begin() + (size_t)(offset + t) * Hkv * rope);
+    }
+    const int count = offset + T;
+    const float* key_up = params.at(LP(l, "attn.mla_k_up.weight")).w.data();
+    const float* value_up = params.at(LP(l, "attn.mla_v_up.weight")).w.data();
+    out.assign((size_t)rows * Hq * vd, 0.0f);
+#pragma omp parallel for schedule(static)
+    for (int idx = 0; idx < B * Hq; ++idx) {
+      const int b = idx / Hq, hq = idx % Hq, hk = hq / ratio;
+      std::vector<float> q((size_t)T * hd), key((size_t)count * hd), val((size_t)count * hd, 0.0f), ao((size_t)T * hd);
+      for (int t = 0; t < T; ++t) {
+        const float* qcp = qc.data() + (((size_t)b * T + t) * Hq + hq) * content;
+        for (int r = 0; r < lat; ++r) {
+          float sum = 0.0f;
+          for (int c = 0; c < content; ++c) sum += qcp[c] * key_up[((size_t)hk * content + c) * lat + r];
+          q[(size_t)t * hd + r] = sum;
+        }
+        std::copy(qr.begin() + (((size_t)b * T + t) * Hq + hq) * rope, qr.begin() + (((size_t)b * T + t) * Hq + hq + 1) * rope, q.begin() + (size_t)t * hd + lat);
+      }
+      const float* lc = cache.mla_latent[l][b].data(); const float* rc = cache.mla_rope[l][b].data();
+      for (int j = 0; j < count; ++j) {
+        std::copy(lc + (size_t)j * lat, lc + (size_t)(j + 1) * lat, key.begin() + (size_t)j * hd);
+        std::copy(rc + ((size_t)j * Hkv + hk) * rope, rc + ((size_t)j * Hkv + hk + 1) * rope, key.begin() + (size_t)j * hd + lat);
+        std::copy(lc + (size_t)j * lat, lc + (size_t)(j + 1) * lat, val.begin() + (size_t)j * hd);
+      }
+      bk.attention_forward(q.data(), key.data(), val.data(), T, count, hd, offset, windows[l], nullptr, 0, ao.data(), nullptr);
+      for (int t = 0; t < T; ++t) {
+        float* op = out.data() + (((size_t)b * T + t) * Hq + hq) * vd;
+        for (int dd = 0; dd < vd; ++dd) {
+          float sum = 0.0f;
+          for (int r = 0; r < lat; ++r) sum += ao[(size_t)t * hd + r] * value_up[((size_t)hk * vd + dd) * lat + r];
+          op[dd] = sum;
+        }
+      }
+    }
+  }
+  // The un-absorbed construction the training path uses (model/mla.go:106-124, model/train.go:59-86): per-head
+  // content|rotary queries and keys, values up-projected from the latent, no QK norm and no 1.2 scale.
+  void mla_unabsorbed(std::vector<float>& out, const std::vector<float>& h, int B, int T, int l) const {
+    const int Hq = cfg.n_head, Hkv = cfg.n_kv_head, rope = cfg.mla_rope(), content = cfg.mla_content(), ratio = Hq / Hkv;
+    const int64_t rows = (int64_t)B * T;
+    std::vector<float> ql, qc, qr, kvl, kc, kr, v;
+    linear(ql, h, params.at(LP(l, "attn.mla_q_down.weight")), rows);
+    linear(qc, ql, params.at(LP(l, "attn.mla_q_up.weight")), rows);
+    linear(qr, h, params.at(LP(l, "attn.mla_q_rope.weight")), rows);
+    linear(kvl, h, params.at(LP(l, "attn.mla_kv_down.weight")), rows);
+    linear(kc, kvl, params.at(LP(l, "attn.mla_k_up.weight")), rows);
+    linear(kr, h, params.at(LP(l, "attn.mla_k_rope.weight")), rows);
+    linear(v, kvl, params.at(LP(l, "attn.mla_v_up.weight")), rows);
+    auto concat = [&](std::vector<float>& dst, const std::vector<float>& c, const std::vector<float>& r, int H) {
+      dst.resize((size_t)rows * H * D);
+      for (int64_t i = 0; i < rows * H; ++i) {
+        std::copy(c.begin() + i * content, c.begin() + (i + 1) * content, dst.begin() + i * D);
+        std::copy(r.begin() + i * rope, r.begin() + (i + 1) * rope, dst.begin() + i * D + content);
+      }
+    };
+    std::vector<float> q, k;
+    concat(q, qc, qr, Hq); concat(k, kc, kr, Hkv);
+    rotary(q, B, T, Hq, 0, 1.0f); rotary(k, B, T, Hkv, 0, 1.0f);
+    std::vector<float> qh, kh, vh, oh((size_t)rows * Hq * D);
+    to_head_major(qh, q, B, T, Hq, D); to_head_major(kh, k, B, T, Hkv, D); to_head_major(vh, v, B, T, Hkv, D);
+#pragma omp parallel for schedule(static)
+    for (int idx = 0; idx < B * Hq; ++idx) {
+      int b = idx / Hq, hq = idx % Hq, hk = hq / ratio;
+      size_t slot = (size_t)b * Hkv + hk;
+      bk.attention_forward(qh.data() + (size_t)idx * T * D, kh.data() + slot * T * D, vh.data() + slot * T * D, T, T, D, 0, windows[l], nullptr, 0,
+                           oh.data() + (size_t)idx * T * D, nullptr);
+    }
+    to_seq_major(out, oh, B, T, Hq, D);
+  }
+  // Routed experts (model/moe.go:118-169): returns the routed contribution [rows, d]; `sel_out` (nullable)
+  // receives the selected expert ids [rows, k].
+  void moe_forward(std::vector<float>& out, const std::vector<float>& flat, int64_t rows, int l, std::vector<int32_t>* sel_out) const {
+    const int d = cfg.embed_dim, E = cfg.n_experts, K = cfg.moe_top_k(), eh = cfg.moe_expert_hidden();
+    std::vector<float> logits, probs((size_t)rows * E), selw((size_t)rows * K);
+    std::vector<int32_t> sel((size_t)rows * K);
+    linear(logits, flat, params.at(LP(l, "moe.router.weight")), rows);
+    bk.moe_gate_topk(logits.data(), params.at(LP(l, "moe.router_bias")).w.data(), probs.data(), sel.data(), selw.data(), (int)rows, E, K);
+    if (sel_out) *sel_out = sel;
+    const int64_t total = rows * K;
+    std::vector<int32_t> counts(E, 0);
+    for (int64_t i = 0; i < total; ++i) counts[sel[i]]++;
+    std::vector<int64_t> offsets(E, 0), fill(E, 0);
+    { int64_t cur = 0; for (int e = 0; e < E; ++e) { offsets[e] = cur; cur += counts[e]; } }
+    std::vector<float> gathered((size_t)total * d), gw((size_t)total);
+    std::vector<int64_t> grow((size_t)total);
+    for (int64_t r = 0; r < rows; ++r) for (int s = 0; s < K; ++s) {
+      int e = sel[r * K + s];
+      int64_t pos = offsets[e] + fill[e]++;
+      std::copy(flat.begin() + r * d, flat.begin() + (r + 1) * d, gathered.begin() + pos * d);
+      grow[pos] = r; gw[pos] = selw[r * K + s];
+    }
+    std::vector<float> gg((size_t)total * eh), gu((size_t)total * eh), gh((size_t)total * eh), go((size_t)total * d);
+    bk.grouped_matmul_t(gg.data(), gathered.data(), params.at(LP(l, "moe.experts.gate.weight")).w.data(), counts.data(), E, eh, d);
+    bk.grouped_matmul_t(gu.data(), gathered.data(), params.at(LP(l, "moe.experts.up.weight")).w.data(), counts.data(), E, eh, d);
+    bk.swiglu(gh.data(), gg.data(), gu.data(), cfg.moe_effective_clamp(), (int64_t)gh.size());
+    bk.grouped_matmul_t(go.data(), gh.data(), params.at(LP(l, "moe.experts.down.weight")).w.data(), counts.data(), E, d, eh);
+    out.assign((size_t)rows * d, 0.0f);
+    const float scale = cfg.moe_effective_scale();
+    for (int64_t i = 0; i < total; ++i) {
+      float w = gw[i] * scale;
+      float* o = out.data() + grow[i] * d; const float* g = go.data() + i * d;
+      for (int c = 0; c < d; ++c) o[c] += w * g[c];
+    }
+  }
+
+  // Returns logits [B,T,V].  cache may be null (then T must be > 1).  `unabsorbed` (MLA models, cache == null)
+  // evaluates attention in the training construction instead of the absorbed one.
+  void forward(std::vector<float>& logits, const int32_t* ids, int B, int T, KVCache* cache, bool unabsorbed = false) const {
     int d = cfg.embed_dim, Hq = cfg.n_head, Hkv = cfg.n_kv_head, L = cfg.n_layer;
     int64_t rows = (int64_t)B * T;
+    KVCache scratch;   // model/transformer.go:248-253: a cache-less MLA forward gets a scratch latent cache
+    if (!cache && cfg.mla() && !unabsorbed) { cache_init(scratch, B, T); cache = &scratch; }
     std::vector<float> raw, x;
     embedding(raw, params.at("transformer.wte.weight"), ids, rows);
     norm(x, raw, d);
@@ -308,6 +510,12 @@ struct Model {
       // ---- attention (model/attention.go:235-324)
       std::vector<float> h, q, k, v;
       norm(h, x, d);
+      if (cfg.mla()) {
+        std::vector<float> heads, ao;
+        if (unabsorbed) mla_unabsorbed(heads, h, B, T, l); else mla_inference(heads, h, B, T, offset, *cache, l);
+        linear(ao, heads, params.at(LP(l, "attn.c_proj.weight")), rows);
+        for (size_t i = 0; i < x.size(); ++i) x[i] = x[i] + ao[i];
+      } else {
       linear(q, h, params.at(LP(l, "attn.c_q.weight")), rows);
       linear(k, h, params.at(LP(l, "attn.c_k.weight")), rows);
       linear(v, h, params.at(LP(l, "attn.c_v.weight")), rows);
@@ -353,16 +561,26 @@ struct Model {
       to_seq_major(os, oh, B, T, Hq, D);
       linear(ao, os, params.at(LP(l, "attn.c_proj.weight")), rows);
       for (size_t i = 0; i < x.size(); ++i) x[i] = x[i] + ao[i];
-      // ---- MLP (model/mlp.go:62-76)
+      }
+      // ---- MLP (model/mlp.go:62-76); with MoE: shared SwiGLU expert + routed experts (model/block.go:39-46)
       std::vector<float> m, u, fo;
       norm(m, x, d);
       linear(u, m, params.at(LP(l, "mlp.c_fc.weight")), rows);
-      bk.relu_squared(u.data(), u.data(), (int64_t)u.size());
-      linear(fo, u, params.at(LP(l, "mlp.c_proj.weight")), rows);
+      if (cfg.moe()) {
+        std::vector<float> gate, hid(u.size()), routed;
+        linear(gate, m, params.at(LP(l, "mlp.c_gate.weight")), rows);
+        bk.swiglu(hid.data(), gate.data(), u.data(), cfg.moe_effective_clamp(), (int64_t)hid.size());
+        linear(fo, hid, params.at(LP(l, "mlp.c_proj.weight")), rows);
+        moe_forward(routed, m, rows, l, nullptr);
+        for (size_t i = 0; i < fo.size(); ++i) fo[i] = fo[i] + routed[i];
+      } else {
+        bk.relu_squared(u.data(), u.data(), (int64_t)u.size());
+        linear(fo, u, params.at(LP(l, "mlp.c_proj.weight")), rows);
+      }
       for (size_t i = 0; i < x.size(); ++i) x[i] = x[i] + fo[i];
       if (l == L / 2) backout = x;
     }
-    if (cache) cache->pos += T;
+    if (cache && cache != &scratch) cache->pos += T;
     if (!backout.empty()) {
       float lam = -params.at("backout_lambda").w[0];
       for (size_t i = 0; i < x.size(); ++i) x[i] = x[i] + lam * backout[i];

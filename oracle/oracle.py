@@ -68,6 +68,8 @@ class OrConfig(C.Structure):
     _fields_ = [
         ("sequence_len", C.c_int32), ("vocab_size", C.c_int32), ("n_layer", C.c_int32), ("n_head", C.c_int32),
         ("n_kv_head", C.c_int32), ("embed_dim", C.c_int32), ("rotary_dims", C.c_int32), ("window_pattern", C.c_char * 16),
+        ("n_experts", C.c_int32), ("experts_per_token", C.c_int32), ("expert_hidden", C.c_int32), ("shared_hidden", C.c_int32),
+        ("moe_clamp", C.c_float), ("moe_scale", C.c_float), ("mla_latent", C.c_int32), ("mla_rotary_dims", C.c_int32),
     ]
 
 
@@ -384,9 +386,12 @@ def pg_loss_backward(logits, targets, adv, seq_len, norm, mode=0, want_grad=True
 # Model
 # --------------------------------------------------------------------------
 class Model:
-    def __init__(self, sequence_len, vocab_size, n_layer, n_head, n_kv_head, embed_dim, rotary_dims=0, window_pattern="L", mode=0):
+    def __init__(self, sequence_len, vocab_size, n_layer, n_head, n_kv_head, embed_dim, rotary_dims=0, window_pattern="L", mode=0,
+                 n_experts=0, experts_per_token=0, expert_hidden=0, shared_hidden=0, moe_clamp=0.0, moe_scale=0.0, mla_latent=0,
+                 mla_rotary_dims=0):
         self.l = lib()
-        self.cfg = OrConfig(sequence_len, vocab_size, n_layer, n_head, n_kv_head, embed_dim, rotary_dims, window_pattern.encode())
+        self.cfg = OrConfig(sequence_len, vocab_size, n_layer, n_head, n_kv_head, embed_dim, rotary_dims, window_pattern.encode(),
+                            n_experts, experts_per_token, expert_hidden, shared_hidden, moe_clamp, moe_scale, mla_latent, mla_rotary_dims)
         self.h = C.c_void_p(self.l.or_model_create(C.byref(self.cfg), mode))
         self.vocab = vocab_size
         self.names = [self.l.or_model_param_name(self.h, i).decode() for i in range(self.l.or_model_param_count(self.h))]
@@ -423,6 +428,19 @@ class Model:
         ids = i32(ids); B, T = ids.shape
         logits = np.empty((B, T, self.vocab), np.float32)
         self.l.or_model_forward(self.h, _i(ids), B, T, _f(logits)); return logits
+
+    def forward_unabsorbed(self, ids):
+        """MLA models: logits through the un-absorbed (training) attention construction."""
+        ids = i32(ids); B, T = ids.shape
+        logits = np.empty((B, T, self.vocab), np.float32)
+        self.l.or_model_forward_unabsorbed(self.h, _i(ids), B, T, _f(logits)); return logits
+
+    def moe_forward(self, layer, flat):
+        """Routed-expert contribution of one layer for [rows, d] normalised activations -> (output, selected ids)."""
+        flat = f32(flat); rows, d = flat.shape
+        k = min(self.cfg.experts_per_token or 2, self.cfg.n_experts)
+        out = np.empty((rows, d), np.float32); sel = np.empty((rows, k), np.int32)
+        self.l.or_model_moe_forward(self.h, layer, _f(flat), C.c_int64(rows), _f(out), _i(sel)); return out, sel
 
     def train_forward(self, ids):
         ids = i32(ids); B, T = ids.shape
