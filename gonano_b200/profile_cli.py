@@ -19,7 +19,7 @@ from .session import Context, Model
 
 
 def make_model(ctx, name="d12", seed=0):
-    cfg = synthetic.dense_config(name)
+    cfg = synthetic.latent_config(name) if name in ("c3", "latent-tiny", "latent-small") else synthetic.dense_config(name)
     model = Model(ctx, **cfg)
     for pname, value in synthetic.fill_weights(model.names, model.shape, seed):
         model.upload(pname, value)
