@@ -16,6 +16,8 @@
 //
 // Scores are raw q.k (the model applies no 1/sqrt(d)); a masked score is the
 // finite -1e30 of the reference (kernels/scalar/attention.go:11).
+#include <cstdlib>
+
 #include "kernels.cuh"
 
 namespace gn {
@@ -911,15 +913,17 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restric
                                                           const float* __restrict__ vcache, int64_t row_stride, int64_t head_stride,
                                                           const int32_t* __restrict__ ctx_len, int Hq, int Hkv, int D, int window, float* __restrict__ out,
                                                           int64_t o_rstride, float* __restrict__ part_acc, float* __restrict__ part_ms, int splits,
-                                                          float* __restrict__ out_hi, float* __restrict__ out_lo) {
+                                                          float* __restrict__ out_hi, float* __restrict__ out_lo, int kmin, int slot0, int nslots) {
   // DP = head_dim rounded up to a multiple of 32; channels >= D are zero padding.
+  // Keys below kmin belong to the shared-prefix kernel; this kernel's partial results then go to
+  // slots slot0 .. slot0 + splits - 1 of nslots (nslots == splits and slot0 == 0 without a prefix pass).
   constexpr int E = DP / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x / Hkv, hk = blockIdx.x % Hkv, split = blockIdx.y;
   const int ctx = ctx_len[row];
   const int qpos = ctx - 1;
-  int kbeg = 0;
-  if (window >= 0) kbeg = max(0, qpos - window);
+  int kbeg = kmin;
+  if (window >= 0) kbeg = max(kmin, qpos - window);
   const int span = ctx - kbeg;
   const int per = (span + splits - 1) / splits;
   const int k0 = kbeg + split * per, k1 = min(ctx, k0 + per);
@@ -989,12 +993,24 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restric
     }
     int hq = hk * RATIO + h;
     if (splits == 1) {
+      // the only CTA of this (row, kv head): finish here, merging the slots an earlier shared-prefix
+      // launch left for this head (slot0 of them; stream order makes them visible)
+      const int64_t pi0 = ((int64_t)row * Hq + hq) * nslots;
+      for (int sl = 0; sl < slot0; ++sl) {
+        const float pm = part_ms[(pi0 + sl) * 2], pl = part_ms[(pi0 + sl) * 2 + 1];
+        if (pm == -INFINITY) continue;
+        const float mn = fmaxf(gm, pm);
+        const float a0 = (gm == -INFINITY) ? 0.0f : __expf(gm - mn), a1 = __expf(pm - mn);
+        tot = tot * a0 + pl * a1;
+        acc = acc * a0 + part_acc[(pi0 + sl) * D + c] * a1;
+        gm = mn;
+      }
       const float v = tot > 0 ? acc / tot : 0.0f;
       const int64_t oi = (int64_t)row * o_rstride + (int64_t)hq * D + c;
       out[oi] = v;
       if (out_hi) { float h2, l2; split_tf32(v, h2, l2); out_hi[oi] = h2; out_lo[oi] = l2; }
     } else {
-      int64_t pi = ((int64_t)row * Hq + hq) * splits + split;
+      int64_t pi = ((int64_t)row * Hq + hq) * nslots + slot0 + split;
       part_acc[pi * D + c] = acc;
       if (c == 0) { part_ms[pi * 2] = gm; part_ms[pi * 2 + 1] = tot; }
     }
@@ -1018,6 +1034,135 @@ __global__ void __launch_bounds__(128) attn_decode_combine_kernel(const float* p
   }
 }
 
+// Shared prefix (head_dim 128): the G rows of a group hold identical K/V for the prompt positions (the
+// prefill was replicated, model/kvcache.go:383-448), so one CTA serves a whole group from the first
+// row's copy and the prompt's K/V rows reach the SM once per group instead of once per row.
+// CTA = (prompt, kv head, tile of 32 prompt positions), 8 warps:
+//   1. the K and V tiles and the group's NH = G * RATIO query vectors are staged in shared memory;
+//   2. scores: a warp owns up to 4 query heads, lane = key; the K row is read once for them;
+//      softmax statistics of the tile by warp reductions; probabilities go to shared memory;
+//   3. P.V: thread = channel, half the heads each; V rows are read conflict-free, P by broadcast.
+// The tile's (max, sum, unnormalised output) is one partial-result slot of each (row, head); the
+// combine pass merges it with the slots of the per-row kernel.
+constexpr int kPrefixTile = 32, kPrefixMaxHeads = 32;
+template <int RATIO>
+__global__ void __launch_bounds__(256) attn_decode_prefix_kernel(const float* __restrict__ q, int64_t q_rstride, const float* __restrict__ kcache,
+                                                                 const float* __restrict__ vcache, int64_t row_stride, int64_t head_stride,
+                                                                 const int32_t* __restrict__ ctx_len, int Hq, int Hkv, int window, int group,
+                                                                 int prefix_len, float* __restrict__ part_acc, float* __restrict__ part_ms, int nslots) {
+  constexpr int D = 128, LDK = D + 4;
+  extern __shared__ __align__(16) float psm[];
+  float* Ks = psm;                          // [32][LDK]
+  float* Vs = Ks + kPrefixTile * LDK;       // [32][LDK]
+  float* Qs = Vs + kPrefixTile * LDK;       // [NH][D]
+  float* Ps = Qs + kPrefixMaxHeads * D;     // [NH][32]
+  __shared__ float Ms[kPrefixMaxHeads], Ls[kPrefixMaxHeads];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int p = blockIdx.x / Hkv, hk = blockIdx.x % Hkv, split = blockIdx.y;
+  const int NH = group * RATIO;
+  const int k0 = split * kPrefixTile, kvalid = min(kPrefixTile, prefix_len - k0);
+  const float* kb = kcache + (int64_t)p * group * row_stride + (int64_t)hk * head_stride + (int64_t)k0 * D;
+  const float* vb = vcache + (int64_t)p * group * row_stride + (int64_t)hk * head_stride + (int64_t)k0 * D;
+  for (int idx = tid; idx < kPrefixTile * (D / 4); idx += 256) {
+    const int r = idx >> 5, c = (idx & 31) * 4;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+    if (r < kvalid) { a = *reinterpret_cast<const float4*>(kb + (int64_t)r * D + c); b = *reinterpret_cast<const float4*>(vb + (int64_t)r * D + c); }
+    *reinterpret_cast<float4*>(Ks + r * LDK + c) = a; *reinterpret_cast<float4*>(Vs + r * LDK + c) = b;
+  }
+  for (int idx = tid; idx < NH * (D / 4); idx += 256) {
+    const int hh = idx >> 5, c = (idx & 31) * 4, g = hh / RATIO, h = hh % RATIO;
+    *reinterpret_cast<float4*>(Qs + hh * D + c) =
+        *reinterpret_cast<const float4*>(q + (int64_t)(p * group + g) * q_rstride + (int64_t)(hk * RATIO + h) * D + c);
+  }
+  __syncthreads();
+  // ---- scores: warp w owns heads w, w + 8, w + 16, w + 24
+  {
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+    const float* krow = Ks + lane * LDK;
+#pragma unroll 4
+    for (int c = 0; c < D; c += 4) {
+      const float4 kv = *reinterpret_cast<const float4*>(krow + c);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int hh = warp + 8 * i;
+        if (hh < NH) {
+          const float4 qv = *reinterpret_cast<const float4*>(Qs + hh * D + c);
+          d[i] = fmaf(qv.x, kv.x, d[i]); d[i] = fmaf(qv.y, kv.y, d[i]); d[i] = fmaf(qv.z, kv.z, d[i]); d[i] = fmaf(qv.w, kv.w, d[i]);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int hh = warp + 8 * i;
+      if (hh >= NH) continue;
+      const int qpos = ctx_len[p * group + hh / RATIO] - 1;
+      const int kj = k0 + lane;
+      const bool live = lane < kvalid && (window < 0 || qpos - kj <= window);
+      float sc = live ? d[i] : -INFINITY;
+      float mx = sc;
+#pragma unroll
+      for (int o2 = 16; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o2));
+      const float pj = live ? __expf(sc - mx) : 0.0f;
+      const float tot = warp_sum(pj);
+      Ps[hh * kPrefixTile + lane] = pj;
+      if (lane == 0) { Ms[hh] = mx; Ls[hh] = tot; }
+    }
+  }
+  __syncthreads();
+  // ---- P.V: thread = (channel pair, head group of 4): heads hg, hg + 4, ...; keys in blocks of 4 so that
+  //      one 128-bit read of P feeds 8 multiply-adds
+  {
+    const int cp = (tid & 63) * 2, hg = tid >> 6;
+    float acc[kPrefixMaxHeads / 4][2];
+#pragma unroll
+    for (int i = 0; i < kPrefixMaxHeads / 4; ++i) { acc[i][0] = 0.0f; acc[i][1] = 0.0f; }
+    for (int j = 0; j < kPrefixTile; j += 4) {      // rows >= kvalid are zero in Vs and P
+      float2 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const float2*>(Vs + (j + u) * LDK + cp);
+#pragma unroll
+      for (int i = 0; i < kPrefixMaxHeads / 4; ++i) {
+        const int hh = hg + 4 * i;
+        if (hh < NH) {
+          const float4 p4 = *reinterpret_cast<const float4*>(Ps + hh * kPrefixTile + j);
+          acc[i][0] = fmaf(p4.x, v[0].x, acc[i][0]); acc[i][1] = fmaf(p4.x, v[0].y, acc[i][1]);
+          acc[i][0] = fmaf(p4.y, v[1].x, acc[i][0]); acc[i][1] = fmaf(p4.y, v[1].y, acc[i][1]);
+          acc[i][0] = fmaf(p4.z, v[2].x, acc[i][0]); acc[i][1] = fmaf(p4.z, v[2].y, acc[i][1]);
+          acc[i][0] = fmaf(p4.w, v[3].x, acc[i][0]); acc[i][1] = fmaf(p4.w, v[3].y, acc[i][1]);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kPrefixMaxHeads / 4; ++i) {
+      const int hh = hg + 4 * i;
+      if (hh < NH) {
+        const int row = p * group + hh / RATIO, hq = hk * RATIO + hh % RATIO;
+        *reinterpret_cast<float2*>(part_acc + (((int64_t)row * Hq + hq) * nslots + split) * D + cp) = make_float2(acc[i][0], acc[i][1]);
+      }
+    }
+    if (tid < NH) {
+      const int row = p * group + tid / RATIO, hq = hk * RATIO + tid % RATIO;
+      const int64_t pi = ((int64_t)row * Hq + hq) * nslots + split;
+      part_ms[pi * 2] = Ms[tid]; part_ms[pi * 2 + 1] = Ls[tid];
+    }
+  }
+}
+constexpr size_t kPrefixSmem = sizeof(float) * (size_t)(2 * kPrefixTile * 132 + kPrefixMaxHeads * 128 + kPrefixMaxHeads * kPrefixTile);
+
+// Partial-result slots the shared-prefix pass writes: one per tile of 32 prompt positions
+// (0 when the pass does not apply: head_dim other than 128, or more than 32 query vectors per group and kv head).
+int attention_decode_prefix_splits(int rows, int group, int Hq, int Hkv, int D, int prefix_len) {
+  if (group <= 1 || prefix_len <= 0 || D != 128 || group * (Hq / Hkv) > kPrefixMaxHeads || rows % group != 0) return 0;
+  const int tiles = (prefix_len + kPrefixTile - 1) / kPrefixTile;
+  // Measured on d12: the pass pays off when it fills the machine (512 rows: 512 CTAs); with a few dozen
+  // CTAs its per-CTA latency exceeds what the shared reads save (64 rows), so small batches keep the per-row kernel.
+  // GN_PREFIX_SHARING=1 / 0 overrides the size rule (tests exercise the pass on small batches with it).
+  static const int forced = [] { const char* e = getenv("GN_PREFIX_SHARING"); return e ? (e[0] == '0' ? 0 : 1) : -1; }();
+  if (forced == 0) return 0;
+  if (forced < 0 && (int64_t)(rows / group) * Hkv * tiles < 2 * kNumSM) return 0;
+  return tiles;
+}
+
 int attention_decode_splits(int rows, int Hkv, int max_ctx) {
   // Fill the machine: aim at >= 4 CTAs per SM, at least 64 keys per split.
   int base = rows * Hkv;
@@ -1029,13 +1174,24 @@ int attention_decode_splits(int rows, int Hkv, int max_ctx) {
 template <int DP, int RATIO>
 static int decode_go(const float* q, int64_t q_rstride, const float* kcache, const float* vcache, int64_t row_stride, int64_t head_stride,
                      const int32_t* ctx_len, int rows, int Hq, int Hkv, int D, int window, float* out, int64_t o_rstride, float* part_acc, float* part_ms,
-                     int splits, cudaStream_t s, float* out_hi, float* out_lo) {
+                     int splits, cudaStream_t s, float* out_hi, float* out_lo, int group, int prefix_len) {
+  int psplits = 0;
+  psplits = attention_decode_prefix_splits(rows, group, Hq, Hkv, D, prefix_len);
+  if (psplits > 0) {
+    static bool configured = false;
+    if (!configured) { GN_CUDA(cudaFuncSetAttribute(attn_decode_prefix_kernel<RATIO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmem)); configured = true; }
+    dim3 pgrid((rows / group) * Hkv, psplits);
+    attn_decode_prefix_kernel<RATIO><<<pgrid, 256, kPrefixSmem, s>>>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, Hq, Hkv, window, group,
+                                                                     prefix_len, part_acc, part_ms, psplits + splits);
+    GN_LAUNCH_CHECK();
+  }
+  const int nslots = psplits + splits;
   dim3 grid(rows * Hkv, splits);
   attn_decode_kernel<DP, RATIO><<<grid, 128, 0, s>>>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, Hq, Hkv, D, window, out, o_rstride,
-                                                     part_acc, part_ms, splits, out_hi, out_lo);
+                                                     part_acc, part_ms, splits, out_hi, out_lo, psplits ? prefix_len : 0, psplits, nslots);
   GN_LAUNCH_CHECK();
   if (splits > 1) {
-    attn_decode_combine_kernel<<<rows * Hq, 128, 0, s>>>(part_acc, part_ms, splits, Hq, D, out, o_rstride, out_hi, out_lo);
+    attn_decode_combine_kernel<<<rows * Hq, 128, 0, s>>>(part_acc, part_ms, nslots, Hq, D, out, o_rstride, out_hi, out_lo);
     GN_LAUNCH_CHECK();
   }
   return GN_OK;
@@ -1043,11 +1199,11 @@ static int decode_go(const float* q, int64_t q_rstride, const float* kcache, con
 
 int attention_decode_launch(const float* q, int64_t q_rstride, const float* kcache, const float* vcache, int64_t row_stride, int64_t head_stride,
                             const int32_t* ctx_len, int rows, int Hq, int Hkv, int D, int window, float* out, int64_t o_rstride,
-                            float* part_acc, float* part_ms, int splits, cudaStream_t s, float* out_hi, float* out_lo) {
+                            float* part_acc, float* part_ms, int splits, cudaStream_t s, float* out_hi, float* out_lo, int group, int prefix_len) {
   if (rows <= 0) return GN_OK;
   int ratio = Hq / Hkv;
   const int dp = (D + 31) / 32 * 32;
-#define GN_DEC(DD, RR) if (dp == DD && ratio == RR) return decode_go<DD, RR>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, rows, Hq, Hkv, D, window, out, o_rstride, part_acc, part_ms, splits, s, out_hi, out_lo)
+#define GN_DEC(DD, RR) if (dp == DD && ratio == RR) return decode_go<DD, RR>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, rows, Hq, Hkv, D, window, out, o_rstride, part_acc, part_ms, splits, s, out_hi, out_lo, group, prefix_len)
   GN_DEC(128, 1); GN_DEC(128, 2); GN_DEC(128, 3); GN_DEC(128, 4); GN_DEC(128, 8);
   GN_DEC(96, 1); GN_DEC(96, 2); GN_DEC(96, 4);
   GN_DEC(64, 1); GN_DEC(64, 2); GN_DEC(64, 3); GN_DEC(64, 4); GN_DEC(64, 8);

@@ -63,8 +63,13 @@ int attention_combine_launch(const float* acc, const float* mx, const float* sm,
 int attention_decode_launch(const float* q, int64_t q_rstride, const float* kcache, const float* vcache, int64_t row_stride, int64_t head_stride,
                             const int32_t* ctx_len, int rows, int Hq, int Hkv, int D, int window, float* out, int64_t o_rstride,
                             float* part_acc, float* part_ms, int splits, cudaStream_t s,
-                            float* out_hi = nullptr, float* out_lo = nullptr);   // optional tf32 hi/lo split of the output, same pitch
+                            float* out_hi = nullptr, float* out_lo = nullptr,    // optional tf32 hi/lo split of the output, same pitch
+                            int group = 1, int prefix_len = 0);
+// group > 1 and prefix_len > 0: rows come in groups of `group` whose first prefix_len cached positions are identical
+// copies (a replicated prompt); those keys are read once per group.  The partial buffers then need
+// attention_decode_prefix_splits(...) + splits slots per (row, query head).
 int attention_decode_splits(int rows, int Hkv, int max_ctx);
+int attention_decode_prefix_splits(int rows, int group, int Hq, int Hkv, int D, int prefix_len);
 
 // ----------------------------------------------------------------- sampler.cu
 int sample_launch(const float* logits, int rows, int vocab, int logits_row_div, const float* uniforms, const uint64_t* seeds_dev, int group,

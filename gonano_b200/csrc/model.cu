@@ -234,7 +234,8 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
       o_split = tc && Hq * D <= 4 * d;
       GN_TRY(attention_decode_launch(QKV, W, m->cache.f() + (int64_t)(2 * l) * layer_stride, m->cache.f() + (int64_t)(2 * l + 1) * layer_stride,
                                      (int64_t)Hkv * a.max_seq * D, (int64_t)a.max_seq * D, m->ctxlen.i(), B, Hq, Hkv, D, m->windows[l], O,
-                                     (int64_t)Hq * D, m->part_acc.f(), m->part_ms.f(), splits, s, o_split ? b.S4h : nullptr, o_split ? b.S4l : nullptr));
+                                     (int64_t)Hq * D, m->part_acc.f(), m->part_ms.f(), splits, s, o_split ? b.S4h : nullptr, o_split ? b.S4l : nullptr,
+                                     a.group, a.prefix_len));
     } else {
       AttnShape sh;
       sh.B = B; sh.Hq = Hq; sh.Hkv = Hkv; sh.D = D; sh.Tq = T; sh.Tk = T;
@@ -605,7 +606,8 @@ int gn_generate_batch(gn_model* m, const int32_t* prompts, int P, int plen, int 
   GN_TRY(m->out_tokens.ensure(sizeof(int32_t) * (size_t)rows * max_tokens)); GN_TRY(m->out_lengths.ensure(sizeof(int32_t) * rows));
   GN_TRY(m->done.ensure(sizeof(int32_t) * rows)); GN_TRY(m->n_done.ensure(sizeof(int32_t)));
   GN_TRY(m->sel.ensure(sizeof(int32_t) * P));
-  int splits = attention_decode_splits(rows, Hkv, max_seq);
+  const bool share_prefix = G > 1;
+  int splits = attention_decode_splits(rows, Hkv, max_seq) + (share_prefix ? attention_decode_prefix_splits(rows, G, Hq, Hkv, D, plen) : 0);
   GN_TRY(m->part_acc.ensure(sizeof(float) * (size_t)rows * Hq * splits * D)); GN_TRY(m->part_ms.ensure(sizeof(float) * (size_t)rows * Hq * splits * 2));
   GN_CUDA(cudaMemcpyAsync(m->ids_dev.p, prompts, sizeof(int32_t) * (size_t)P * plen, cudaMemcpyHostToDevice, s));
   GN_CUDA(cudaMemcpyAsync(m->seeds.p, seeds, sizeof(uint64_t) * P, cudaMemcpyHostToDevice, s));
@@ -668,6 +670,7 @@ int gn_generate_batch(gn_model* m, const int32_t* prompts, int P, int plen, int 
   auto body = [&]() -> int {
     GN_TRY(ctx_from_pos_launch(m->pos.i(), m->ctxlen.i(), rows, s));
     FwdArgs a; a.mode = MODE_DECODE; a.ids = m->sampled.i(); a.B = rows; a.T = 1; a.cache_rows = rows; a.cache_row_mul = 1; a.max_seq = max_seq;
+    if (share_prefix) { a.group = G; a.prefix_len = plen; }
     GN_TRY(forward_core(m, b, a));                       // forward the sampled column (engine.go:321-324)
     GN_TRY(add_i32_launch(m->pos.i(), 1, rows, s));
     GN_TRY(sample_launch(b.LOGITS, rows, V, 1, nullptr, (const uint64_t*)m->seeds.p, G, (const uint32_t*)m->step_dev.p, 0, temperature, top_k, m->sampled.i(), s));
@@ -691,6 +694,7 @@ int gn_generate_batch(gn_model* m, const int32_t* prompts, int P, int plen, int 
       // the tap wants the logits each sampling step saw: forward first, copy, then sample
       GN_TRY(ctx_from_pos_launch(m->pos.i(), m->ctxlen.i(), rows, s));
       FwdArgs a; a.mode = MODE_DECODE; a.ids = m->sampled.i(); a.B = rows; a.T = 1; a.cache_rows = rows; a.cache_row_mul = 1; a.max_seq = max_seq;
+      if (share_prefix) { a.group = G; a.prefix_len = plen; }
       GN_TRY(forward_core(m, b, a));
       GN_TRY(add_i32_launch(m->pos.i(), 1, rows, s));
       GN_TRY(tap(1));

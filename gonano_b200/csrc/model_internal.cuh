@@ -122,6 +122,7 @@ struct FwdArgs {
   int B, T;
   int cache_rows = 0, cache_row_mul = 1, max_seq = 0;
   int logits_rows = 0;     // rows that get logits (PLAIN/TRAIN: all; PREFILL: B; DECODE: B)
+  int group = 1, prefix_len = 0;   // DECODE: rows come in groups sharing their first prefix_len cached positions
 };
 
 // model_latent.cu: the two block variants of the latent preset, inference only.

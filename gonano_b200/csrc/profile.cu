@@ -107,11 +107,13 @@ extern "C" int gn_profile_kernel(gn_ctx* ctx, const char* kernel, const int64_t*
     return time_it(s, iters, mean_ms, [&]() { return sample_launch(logits, rows, vocab, 1, nullptr, seeds, 8, nullptr, step++, 1.0f, topk, out, s); });
   }
   if (k == "decode_attention") {
-    GN_REQUIRE(n_dims == 5, "decode_attention wants {rows, n_head, n_kv_head, head_dim, context}");
+    GN_REQUIRE(n_dims == 5 || n_dims == 7, "decode_attention wants {rows, n_head, n_kv_head, head_dim, context[, group, shared prefix length]}");
     int rows = (int)dims[0], Hq = (int)dims[1], Hkv = (int)dims[2], D = (int)dims[3], ctxl = (int)dims[4];
+    const int group = n_dims == 7 ? (int)dims[5] : 1, prefix = n_dims == 7 ? (int)dims[6] : 0;
     float *q, *kc, *vc, *out, *pa, *pm; int32_t* cl;
     size_t cache = (size_t)rows * Hkv * ctxl * D;
-    int splits = attention_decode_splits(rows, Hkv, ctxl);
+    const int own = attention_decode_splits(rows, Hkv, ctxl);
+    int splits = own + attention_decode_prefix_splits(rows, group, Hq, Hkv, D, prefix);
     GN_TRY(bufs.get(&q, (size_t)rows * Hq * D)); GN_TRY(bufs.get(&kc, cache)); GN_TRY(bufs.get(&vc, cache)); GN_TRY(bufs.get(&out, (size_t)rows * Hq * D));
     GN_TRY(bufs.get(&pa, (size_t)rows * Hq * splits * D)); GN_TRY(bufs.get(&pm, (size_t)rows * Hq * splits * 2)); GN_TRY(bufs.get(&cl, (size_t)rows));
     GN_TRY(synth(q, (int64_t)rows * Hq * D, -1, 1, 6, s)); GN_TRY(synth(kc, (int64_t)cache, -1, 1, 7, s)); GN_TRY(synth(vc, (int64_t)cache, -1, 1, 8, s));
@@ -119,7 +121,8 @@ extern "C" int gn_profile_kernel(gn_ctx* ctx, const char* kernel, const int64_t*
     GN_CUDA(cudaMemcpyAsync(cl, h.data(), sizeof(int32_t) * rows, cudaMemcpyHostToDevice, s));
     GN_CUDA(cudaStreamSynchronize(s));
     return time_it(s, iters, mean_ms, [&]() {
-      return attention_decode_launch(q, (int64_t)Hq * D, kc, vc, (int64_t)Hkv * ctxl * D, (int64_t)ctxl * D, cl, rows, Hq, Hkv, D, -1, out, (int64_t)Hq * D, pa, pm, splits, s);
+      return attention_decode_launch(q, (int64_t)Hq * D, kc, vc, (int64_t)Hkv * ctxl * D, (int64_t)ctxl * D, cl, rows, Hq, Hkv, D, -1, out, (int64_t)Hq * D, pa, pm, own, s,
+                                     nullptr, nullptr, group, prefix);
     });
   }
   if (k == "attention_fwd" || k == "attention_bwd") {

@@ -196,3 +196,36 @@ def test_gemm_paths_agree(oracle, ctx):
     b = gm.forward(ids)
     assert rel_err(b, a) <= 2e-5
     gm.close()
+
+
+def test_shared_prefix_decode_attention(oracle):
+    """The shared-prefix attention pass (one CTA per group reads the replicated prompt once) is sized for large
+    batches; forced on in a child process it must reproduce the per-row kernel's rollout token for token and stay
+    within the logits tolerance of the oracle."""
+    import os, subprocess, sys, json
+    code = r'''
+import json, numpy as np
+from gonano_b200 import synthetic
+from gonano_b200.session import Context, Model
+ctx = Context(0)
+cfg = synthetic.dense_config("h128")
+m = Model(ctx, **cfg)
+for n, v in synthetic.fill_weights(m.names, m.shape, 1, std=0.05): m.upload(n, v)
+prompts = synthetic.prompts(3, 150, cfg["vocab_size"], seed=9)
+t, l, s, lg = m.generate_batch(prompts, 4, 10, 1.0, 50, np.array([5, 6, 7], np.uint64), want_logits=True)
+t2, l2, s2, _ = m.generate_batch(prompts, 4, 10, 1.0, 50, np.array([5, 6, 7], np.uint64))
+assert np.array_equal(l, l2) and all(np.array_equal(t[r, :l[r]], t2[r, :l2[r]]) for r in range(12))
+print(json.dumps({"tokens": t.tolist(), "lengths": l.tolist(), "steps": int(s), "logit_sum": float(np.abs(lg).sum()), "last": lg[s - 1].tolist()}))
+'''
+    outs = {}
+    for flag in ("0", "1"):
+        env = dict(os.environ, GN_PREFIX_SHARING=flag)
+        r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, cwd=os.path.dirname(os.path.dirname(__file__)))
+        assert r.returncode == 0, r.stderr[-2000:]
+        outs[flag] = json.loads(r.stdout.strip().splitlines()[-1])
+    a, b = outs["0"], outs["1"]
+    assert a["lengths"] == b["lengths"] and a["steps"] == b["steps"]
+    for r in range(12):
+        assert a["tokens"][r][:a["lengths"][r]] == b["tokens"][r][:b["lengths"][r]]
+    la, lb = np.array(a["last"]), np.array(b["last"])
+    assert rel_err(lb, la) <= 1e-4     # same arithmetic up to the order of the softmax merge
