@@ -61,6 +61,15 @@ int gemm_dispatch(const GemmArgs& a, int kind, cudaStream_t s) {
   return gemm_simt(a, s);
 }
 
+int gemm_grouped_dispatch(const GemmArgs& a, int kind, cudaStream_t s) {
+#ifdef GN_HAVE_TCGEN05
+  if (kind == 1 && a.groups > 0 && gemm_tcgen05_supported(a)) return gemm_tcgen05(a, s);
+#endif
+  (void)kind;
+  GN_REQUIRE(a.lda == a.K && a.ldb == a.K && a.ldc == a.N, "grouped product: the float32 kernel wants packed operands");
+  return grouped_matmul_t_launch(a.C, a.A, a.B, a.group_counts, a.groups, a.N, a.K, a.M, s);
+}
+
 namespace {
 
 std::mutex g_lock;
@@ -265,7 +274,9 @@ int gn_grouped_matmul_transposed(float* dst, const float* input, const float* we
   const float* din = st.in(input, (size_t)total * inner); const float* dw = st.in(weight, (size_t)experts * cols * inner);
   const int32_t* dc = st.in(counts, experts); float* dd = st.out(dst, (size_t)total * cols);
   if (st.status != GN_OK) return st.status;
-  GN_TRY(grouped_matmul_t_launch(dd, din, dw, dc, experts, cols, inner, total, s));
+  { GemmArgs g; g.A = din; g.lda = inner; g.B = dw; g.ldb = inner; g.b_trans = 1; g.C = dd; g.ldc = cols; g.M = (int)total; g.N = cols; g.K = inner;
+    g.group_counts = dc; g.groups = experts;
+    GN_TRY(gemm_grouped_dispatch(g, gemm_default_kind(), s)); }
   GN_END();
 }
 

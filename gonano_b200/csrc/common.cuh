@@ -176,10 +176,16 @@ struct GemmArgs {
   // consumer kernel to sum; *leave says where they are (splits == 1 and ptr == C when it was not split).
   // The partial tiles live in a workspace that the next product on the stream reuses.
   Partials* leave = nullptr;
+  // Grouped product over expert-major rows (kernels/backend.go:130-141): groups > 0 makes A [M, K] a stack of
+  // per-group row blocks with group_counts[g] rows each (device array, sum == M), B [groups * N, K] the packed
+  // per-group weights (b_trans = 1) and C [M, N] the stacked outputs.  EPI_STORE only.
+  const int32_t* group_counts = nullptr; int groups = 0;
 };
 int gemm_simt(const GemmArgs& args, cudaStream_t stream);
 // kind 0: SIMT float32.  kind 1: tcgen05 3xTF32 where the shape allows it, else SIMT.
 int gemm_dispatch(const GemmArgs& args, int kind, cudaStream_t stream);
+// Grouped product: tensor cores when kind == 1 and the shape allows it, else the float32 warp-per-row kernel.
+int gemm_grouped_dispatch(const GemmArgs& args, int kind, cudaStream_t stream);
 int gemm_default_kind();
 int64_t launch_count();
 // tcgen05 path housekeeping (no-ops when the library was built without it).

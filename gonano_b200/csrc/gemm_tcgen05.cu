@@ -136,6 +136,9 @@ struct TcEpilogue {
   int64_t split_stride;   // split-K: floats between the partial tiles of consecutive splits
   float* c_hi; float* c_lo; // optional: the output split for the next product (pitch ldc)
   long long* trace;   // timeline of CTA (0,0) in SM cycles when the library is built with GN_TC_TRACE, else unused
+  // Grouped product (expert-major rows): group g owns group_counts[g] consecutive rows of A and C and the
+  // weight rows [g * N, (g + 1) * N) of B; blockIdx.y enumerates (group, 128-row tile) pairs in group order.
+  const int32_t* group_counts; int groups;
 };
 
 #ifdef GN_TC_TRACE
@@ -195,7 +198,19 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + S::BAR_OFFSET + 8 * (2 * STAGES + 4));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * TBM, n0 = blockIdx.x * BN;
+  int m0 = blockIdx.y * TBM, b_row0 = blockIdx.x * BN;
+  const int n0 = blockIdx.x * BN;
+  if (ep.groups > 0) {
+    // find this CTA's (group, tile); surplus CTAs of the host's upper-bound grid leave before any barrier exists
+    int t = blockIdx.y, g = 0, off = 0;
+    for (; g < ep.groups; ++g) {
+      const int c = ep.group_counts[g], tiles = (c + TBM - 1) / TBM;
+      if (t < tiles) { M = off + c; break; }     // rows past the group's last one are computed but never stored
+      t -= tiles; off += c;
+    }
+    if (g == ep.groups) return;
+    m0 = off + t * TBM; b_row0 = g * N + n0;
+  }
   // split-K: CTA z works on k-blocks [kb0, kb0 + nk) and writes a partial tile
   const int nk_total = (K + TBK - 1) / TBK;
   const int per_split = (nk_total + (int)gridDim.z - 1) / (int)gridDim.z;
@@ -232,8 +247,8 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
         mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
         tma_load_2d(st, &tmAh, full_bar(s), (kb0 + kb) * TBK, m0);
         tma_load_2d(st + S::A_BYTES, &tmAl, full_bar(s), (kb0 + kb) * TBK, m0);
-        tma_load_2d(st + 2 * S::A_BYTES, &tmBh, full_bar(s), (kb0 + kb) * TBK, n0);
-        tma_load_2d(st + 2 * S::A_BYTES + S::B_BYTES, &tmBl, full_bar(s), (kb0 + kb) * TBK, n0);
+        tma_load_2d(st + 2 * S::A_BYTES, &tmBh, full_bar(s), (kb0 + kb) * TBK, b_row0);
+        tma_load_2d(st + 2 * S::A_BYTES + S::B_BYTES, &tmBl, full_bar(s), (kb0 + kb) * TBK, b_row0);
       }
     }
   } else if (warp == 1) {
@@ -518,7 +533,8 @@ int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int
   }
   CUtensorMap mah, mal, mbh, mbl;
   GN_TRY(make_map(&mah, a.hi, M, K, a.ld, TBM)); GN_TRY(make_map(&mal, a.lo, M, K, a.ld, TBM));
-  GN_TRY(make_map(&mbh, b.hi, N, K, b.ld, BN)); GN_TRY(make_map(&mbl, b.lo, N, K, b.ld, BN));
+  const int brows = ep_in.groups > 0 ? ep_in.groups * N : N;
+  GN_TRY(make_map(&mbh, b.hi, brows, K, b.ld, BN)); GN_TRY(make_map(&mbl, b.lo, brows, K, b.ld, BN));
   TcEpilogue ep = ep_in;
   if (splits > 1) {
     size_t need = (size_t)splits * M * N;
@@ -530,7 +546,7 @@ int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int
     }
     ep.C = g_splitk_ws; ep.ldc = N; ep.aux = nullptr; ep.epi = EPI_STORE; ep.split_stride = (int64_t)M * N; ep.c_hi = ep.c_lo = nullptr;
   }
-  dim3 grid(ceil_div(N, BN), ceil_div(M, TBM), splits);
+  dim3 grid(ceil_div(N, BN), ceil_div(M, TBM) + ep_in.groups, splits);   // grouped: an upper bound on the sum of per-group tiles
   gemm_tc_kernel<BN, STAGES><<<grid, 64 + 32 * (BN > 128 ? 8 : 4), S::TOTAL, s>>>(mah, mal, mbh, mbl, ep, M, N, K, g_err_flag);
   GN_LAUNCH_CHECK();
   if (leave) {
@@ -548,6 +564,7 @@ int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int
 
 int gemm_tcgen05_supported(const GemmArgs& g) {
   if (g.M < 64 || g.N < 64 || g.K < 32) return 0;      // tiny products stay on the SIMT kernel
+  if (g.groups > 0 && (!g.b_trans || g.a_trans || g.epilogue != EPI_STORE || g.N % 4 != 0)) return 0;
   auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   if (!al(g.A) || !al(g.B)) return 0;
   // Sources read with float4 need a contiguous extent that is a multiple of 4; the
@@ -565,8 +582,9 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
   if (g.a_hi && g.a_lo && !g.a_trans) { a.hi = const_cast<float*>(g.a_hi); a.lo = const_cast<float*>(g.a_lo); a.ld = g.lda; }   // split by the producer
   else GN_TRY(split_operand(g.A, g.lda, g.M, g.K, g.a_trans != 0, g.a_static != 0, 0, a, s));
   // B is logically [N, K]; stored that way when b_trans (weights [out, in]), else stored [K, N].
-  GN_TRY(split_operand(g.B, g.ldb, g.N, g.K, g.b_trans == 0, g.b_static != 0, 1, b, s));
-  TcEpilogue ep{g.C, g.ldc, g.aux, g.ldaux, g.epilogue, g.scalar, 0, g.c_hi, g.c_lo, g_trace};
+  GN_TRY(split_operand(g.B, g.ldb, g.groups > 0 ? (int64_t)g.groups * g.N : g.N, g.K, g.b_trans == 0, g.b_static != 0, 1, b, s));
+  TcEpilogue ep{g.C, g.ldc, g.aux, g.ldaux, g.epilogue, g.scalar, 0, g.c_hi, g.c_lo, g_trace, g.group_counts, g.groups};
+  if (g.groups > 0) return launch_tc<128, 3>(a, b, ep, g.M, g.N, g.K, 1, s, nullptr);
   // Filling the machine when the output has few tiles (the rollout's products have 512 rows):
   // the K loop is split over gridDim.z so that about one CTA per SM runs, each writing a partial
   // tile that a second pass sums in a fixed order (deterministic, unlike atomics).  Narrow tiles

@@ -148,6 +148,7 @@ size_t plan_bufs(gn_model* m, Arena& a, FwdBufs& b, Mode mode, int64_t rows, int
       b.RL = a.take(rows * m->E); b.PR = a.take(rows * m->E); b.SELW = a.take(tot);
       b.GATH = a.take(tot * d); b.GG = a.take(tot * m->eh); b.GU = a.take(tot * m->eh); b.GO = a.take(tot * d);
       b.SEL = (int32_t*)a.take(tot); b.CNT = (int32_t*)a.take(m->E + 1); b.POSI = (int32_t*)a.take(tot);
+      b.GATHh = a.take(tot * d); b.GATHl = a.take(tot * d); b.GHh = a.take(tot * m->eh); b.GHl = a.take(tot * m->eh);
     }
   }
   return a.planned;

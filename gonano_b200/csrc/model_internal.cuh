@@ -114,6 +114,7 @@ struct FwdBufs {
   // routed experts (inference)
   float *UG = nullptr, *SHH = nullptr, *SHO = nullptr, *RL = nullptr, *PR = nullptr, *SELW = nullptr, *GATH = nullptr, *GG = nullptr, *GU = nullptr, *GO = nullptr;
   int32_t *SEL = nullptr, *CNT = nullptr, *POSI = nullptr;
+  float *GATHh = nullptr, *GATHl = nullptr, *GHh = nullptr, *GHl = nullptr;   // tf32 splits of the gathered rows and of the experts' hidden rows
 };
 
 struct FwdArgs {

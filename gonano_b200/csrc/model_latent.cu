@@ -165,13 +165,30 @@ __global__ void __launch_bounds__(1024) moe_route_kernel(const int32_t* __restri
   }
 }
 
-// gathered[posi[i]] = x[i / k]   (one warp per entry)
-__global__ void __launch_bounds__(WPB * 32) moe_gather_kernel(float* gathered, const float* x, const int32_t* posi, int64_t total, int k, int d) {
+// gathered[posi[i]] = x[i / k]   (one warp per entry); hi/lo (nullable) receive the tf32 split of the row
+__global__ void __launch_bounds__(WPB * 32) moe_gather_kernel(float* gathered, float* hi, float* lo, const float* x, const int32_t* posi, int64_t total,
+                                                              int k, int d) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t i = (int64_t)blockIdx.x * WPB + warp;
   if (i >= total) return;
-  const float* src = x + (i / k) * d; float* dst = gathered + (int64_t)posi[i] * d;
-  for (int c = lane; c < d; c += 32) dst[c] = src[c];
+  const float* src = x + (i / k) * d; const int64_t o = (int64_t)posi[i] * d;
+  for (int c = lane; c < d; c += 32) {
+    const float v = src[c];
+    gathered[o + c] = v;
+    if (hi) { float h, l; split_tf32(v, h, l); hi[o + c] = h; lo[o + c] = l; }
+  }
+}
+// hidden = silu(clamp_above(gate)) * clamp(up) over the experts' rows, in place over gate, with the tf32 split
+__global__ void __launch_bounds__(256) swiglu_split_kernel(float* gate, const float* up, float* hi, float* lo, int64_t n, float clampv) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    float g = gate[i], u = up[i];
+    if (clampv > 0.0f && g >= clampv) g = clampv;
+    if (clampv > 0.0f) { if (u > clampv) u = clampv; else if (u < -clampv) u = -clampv; }
+    const float sg = (float)(1.0 / (1.0 + exp((double)(-g))));
+    const float v = g * sg * u;
+    gate[i] = v;
+    float h, l; split_tf32(v, h, l); hi[i] = h; lo[i] = l;
+  }
 }
 
 // XOUT[r] = MID[r] + (shared[r] + routed[r]),  routed[r] = sum over the row's entries in ascending
@@ -254,12 +271,19 @@ int moe_ffn(gn_model* m, FwdBufs& b, const FwdArgs& a, int l, const float* Mn, c
     GN_TRY(gemm_dispatch(g, 0, s)); }   // E columns: the float32 kernel (routing must not depend on a split's rounding)
   GN_TRY(moe_gate_topk_launch(b.RL, m->p(o.router_bias), b.PR, b.SEL, b.SELW, (int)rows, E, K, s));
   moe_route_kernel<<<1, 1024, 0, s>>>(b.SEL, total, E, b.CNT, b.POSI); GN_LAUNCH_CHECK();
-  moe_gather_kernel<<<ceil_div(total, WPB), WPB * 32, 0, s>>>(b.GATH, Mn, b.POSI, total, K, d); GN_LAUNCH_CHECK();
-  // ---- experts: grouped products over the expert-major rows (model/moe.go:155-158)
-  GN_TRY(grouped_matmul_t_launch(b.GG, b.GATH, m->p(o.exp_gate), b.CNT, E, eh, d, total, s));
-  GN_TRY(grouped_matmul_t_launch(b.GU, b.GATH, m->p(o.exp_up), b.CNT, E, eh, d, total, s));
-  GN_TRY(ew_launch(EW_SWIGLU, b.GG, b.GG, b.GU, m->moe_clamp, total * eh, s));
-  GN_TRY(grouped_matmul_t_launch(b.GO, b.GG, m->p(o.exp_down), b.CNT, E, d, eh, total, s));
+  moe_gather_kernel<<<ceil_div(total, WPB), WPB * 32, 0, s>>>(b.GATH, tc ? b.GATHh : nullptr, tc ? b.GATHl : nullptr, Mn, b.POSI, total, K, d); GN_LAUNCH_CHECK();
+  // ---- experts: grouped products over the expert-major rows (model/moe.go:155-158), on the tensor cores when the
+  //      expert shapes allow it (each 128-row tile of an expert is one CTA; rows past an expert's last are masked)
+  const int kind = m->ctx->gemm_kind;
+  auto grouped = [&](const float* A, const float* Ah, const float* Al, int64_t w_off, float* C, int n, int k) -> int {
+    GemmArgs g; g.A = A; g.lda = k; g.B = m->p(w_off); g.b_static = 1; g.ldb = k; g.b_trans = 1; g.C = C; g.ldc = n; g.M = (int)total; g.N = n; g.K = k;
+    g.group_counts = b.CNT; g.groups = E; if (tc) { g.a_hi = Ah; g.a_lo = Al; }
+    return gemm_grouped_dispatch(g, kind, s);
+  };
+  GN_TRY(grouped(b.GATH, b.GATHh, b.GATHl, o.exp_gate, b.GG, eh, d));
+  GN_TRY(grouped(b.GATH, b.GATHh, b.GATHl, o.exp_up, b.GU, eh, d));
+  swiglu_split_kernel<<<grid_for(total * eh), 256, 0, s>>>(b.GG, b.GU, b.GHh, b.GHl, total * eh, m->moe_clamp); GN_LAUNCH_CHECK();
+  GN_TRY(grouped(b.GG, b.GHh, b.GHl, o.exp_down, b.GO, d, eh));
   moe_combine_kernel<<<grid_for(rows * d), 256, 0, s>>>(XOUT, MID, b.SHO, b.GO, b.POSI, b.SELW, m->moe_scale, rows, K, d); GN_LAUNCH_CHECK();
   return GN_OK;
 }

@@ -205,6 +205,19 @@ def test_grouped_matmul_parity(oracle, bk, ref):
           ref.grouped_matmul_transposed(inp, w, counts, experts, cols, inner), 2e-3, 1e-4)
 
 
+# Expert shapes large enough for the grouped tensor-core product (each 128-row tile of an expert is one CTA):
+# empty experts, experts smaller and larger than a tile, a ragged last tile.
+@pytest.mark.parametrize("counts,cols,inner", [([130, 0, 5, 257, 0, 64, 1, 300], 128, 256), ([40, 90], 512, 128), ([0, 0, 700], 192, 64)])
+def test_grouped_matmul_tensor_core(oracle, bk, ref, counts, cols, inner):
+    counts = np.array(counts, np.int32); experts = len(counts)
+    rng = np.random.default_rng(3)
+    inp = rng.standard_normal(int(counts.sum()) * inner).astype(np.float32)
+    w = rng.standard_normal(experts * cols * inner).astype(np.float32)
+    got = bk.grouped_matmul_transposed(inp, w, counts, experts, cols, inner)
+    want = ref.grouped_matmul_transposed(inp, w, counts, experts, cols, inner)
+    assert np.max(np.abs(got - want)) <= 2e-5 * np.max(np.abs(want))
+
+
 # The tensor-core path (tcgen05, 3xTF32) serves the large aligned products; these shapes reach it
 # through the same entry points, tails included, and must stay float32-faithful.
 @pytest.mark.parametrize("rows,cols,inner", [(128, 128, 32), (128, 128, 256), (256, 384, 768), (200, 264, 768), (130, 70, 100), (1000, 3072, 768),
