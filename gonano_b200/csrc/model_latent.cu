@@ -115,6 +115,116 @@ __global__ void __launch_bounds__(128) mla_attention_kernel(MlaAttn p) {
   for (int e = 0; e < ME; ++e) { const int c = e * 32 + lane; if (c < p.lat) out[c] = acc[e] * inv; }
 }
 
+// Tiled form of the same attention: one CTA per query row serves ALL query heads, because they all read the
+// same latent rows (the latent is shared by every head; only the small rotary key differs per kv head).
+// Tiles of 32 cached positions are staged in shared memory; scores: a warp owns heads w, w + 8, ...,
+// lane = position; online softmax per head across tiles; P.V: thread = channel pair for every head.
+// Needs latent % 4 == 0, rope % 4 == 0, latent <= 512, Hq <= 16.
+constexpr int kMlaTile = 32, kMlaMaxHeads = 16;
+__global__ void __launch_bounds__(256) mla_attention_tiled_kernel(MlaAttn p) {
+  extern __shared__ __align__(16) float msm[];
+  const int lat = p.lat, rope = p.rope, hd = lat + rope, rw = p.Hkv * rope;
+  const int LDL = lat + 4, LDR = rw + 4;
+  float* Ls = msm;                       // [32][LDL]   latent tile
+  float* Rs = Ls + kMlaTile * LDL;       // [32][LDR]   rotary keys of every kv head
+  float* Qs = Rs + kMlaTile * LDR;       // [Hq][hd]
+  float* Ps = Qs + p.Hq * hd;            // [Hq][32]
+  __shared__ float m_run[kMlaMaxHeads], l_run[kMlaMaxHeads], alpha_s[kMlaMaxHeads];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int64_t r = blockIdx.x;
+  const int b = (int)(r / p.T), t = (int)(r % p.T);
+  const int crow = b * p.cache_row_mul;
+  const int qpos = p.pos[crow] + t;
+  const int ratio = p.Hq / p.Hkv;
+  for (int idx = tid; idx < p.Hq * hd / 4; idx += 256) *reinterpret_cast<float4*>(Qs + idx * 4) = *reinterpret_cast<const float4*>(p.QF + r * p.Hq * (int64_t)hd + idx * 4);
+  if (tid < kMlaMaxHeads) { m_run[tid] = -INFINITY; l_run[tid] = 0.0f; }
+  const float* lc = p.lat_cache + (int64_t)crow * p.max_seq * lat;
+  const float* rc = p.rope_cache + (int64_t)crow * p.max_seq * rw;
+  int jmin = 0;
+  if (p.window >= 0) jmin = max(0, qpos - p.window);
+  const int cp = tid * 2;                // this thread's channel pair in the P.V phase
+  float acc[kMlaMaxHeads][2];
+#pragma unroll
+  for (int h = 0; h < kMlaMaxHeads; ++h) { acc[h][0] = 0.0f; acc[h][1] = 0.0f; }
+  for (int j0 = (jmin / kMlaTile) * kMlaTile; j0 <= qpos; j0 += kMlaTile) {
+    __syncthreads();
+    for (int idx = tid; idx < kMlaTile * (lat / 4); idx += 256) {
+      const int jr = idx / (lat / 4), c = (idx % (lat / 4)) * 4;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (j0 + jr <= qpos) v = *reinterpret_cast<const float4*>(lc + (int64_t)(j0 + jr) * lat + c);
+      *reinterpret_cast<float4*>(Ls + jr * LDL + c) = v;
+    }
+    for (int idx = tid; idx < kMlaTile * (rw / 4); idx += 256) {
+      const int jr = idx / (rw / 4), c = (idx % (rw / 4)) * 4;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (j0 + jr <= qpos) v = *reinterpret_cast<const float4*>(rc + (int64_t)(j0 + jr) * rw + c);
+      *reinterpret_cast<float4*>(Rs + jr * LDR + c) = v;
+    }
+    __syncthreads();
+    for (int h = warp; h < p.Hq; h += 8) {
+      const int hk = h / ratio;
+      const float* q = Qs + h * hd;
+      const float* lrow = Ls + lane * LDL;
+      const float* rrow = Rs + lane * LDR + hk * rope;
+      float d0 = 0.0f, d1 = 0.0f;
+      for (int c = 0; c < lat; c += 8) {
+        const float4 k0 = *reinterpret_cast<const float4*>(lrow + c), k1 = *reinterpret_cast<const float4*>(lrow + c + 4);
+        const float4 q0 = *reinterpret_cast<const float4*>(q + c), q1 = *reinterpret_cast<const float4*>(q + c + 4);
+        d0 = fmaf(q0.x, k0.x, d0); d0 = fmaf(q0.y, k0.y, d0); d0 = fmaf(q0.z, k0.z, d0); d0 = fmaf(q0.w, k0.w, d0);
+        d1 = fmaf(q1.x, k1.x, d1); d1 = fmaf(q1.y, k1.y, d1); d1 = fmaf(q1.z, k1.z, d1); d1 = fmaf(q1.w, k1.w, d1);
+      }
+      for (int c = 0; c < rope; c += 4) {
+        const float4 k0 = *reinterpret_cast<const float4*>(rrow + c), q0 = *reinterpret_cast<const float4*>(q + lat + c);
+        d0 = fmaf(q0.x, k0.x, d0); d0 = fmaf(q0.y, k0.y, d0); d0 = fmaf(q0.z, k0.z, d0); d0 = fmaf(q0.w, k0.w, d0);
+      }
+      const int j = j0 + lane;
+      const bool live = j <= qpos && j >= jmin;
+      const float sc = live ? d0 + d1 : -INFINITY;
+      float mx = sc;
+#pragma unroll
+      for (int o2 = 16; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o2));
+      const float mo = m_run[h], mn = fmaxf(mo, mx);
+      const float pj = live ? __expf(sc - mn) : 0.0f;
+      const float tot = warp_sum(pj);
+      Ps[h * kMlaTile + lane] = pj;
+      __syncwarp();
+      if (lane == 0) {
+        const float al = (mo == -INFINITY) ? 0.0f : __expf(mo - mn);
+        alpha_s[h] = al; l_run[h] = l_run[h] * al + tot; m_run[h] = mn;
+      }
+    }
+    __syncthreads();
+    if (cp < lat) {
+#pragma unroll
+      for (int h = 0; h < kMlaMaxHeads; ++h) if (h < p.Hq) { const float al = alpha_s[h]; acc[h][0] *= al; acc[h][1] *= al; }
+      for (int jb = 0; jb < kMlaTile; jb += 4) {
+        float2 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const float2*>(Ls + (jb + u) * LDL + cp);
+#pragma unroll
+        for (int h = 0; h < kMlaMaxHeads; ++h) if (h < p.Hq) {
+          const float4 p4 = *reinterpret_cast<const float4*>(Ps + h * kMlaTile + jb);
+          acc[h][0] = fmaf(p4.x, v[0].x, acc[h][0]); acc[h][1] = fmaf(p4.x, v[0].y, acc[h][1]);
+          acc[h][0] = fmaf(p4.y, v[1].x, acc[h][0]); acc[h][1] = fmaf(p4.y, v[1].y, acc[h][1]);
+          acc[h][0] = fmaf(p4.z, v[2].x, acc[h][0]); acc[h][1] = fmaf(p4.z, v[2].y, acc[h][1]);
+          acc[h][0] = fmaf(p4.w, v[3].x, acc[h][0]); acc[h][1] = fmaf(p4.w, v[3].y, acc[h][1]);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (cp < lat) {
+#pragma unroll
+    for (int h = 0; h < kMlaMaxHeads; ++h) if (h < p.Hq) {
+      const float inv = l_run[h] > 0.0f ? 1.0f / l_run[h] : 0.0f;
+      *reinterpret_cast<float2*>(p.AL + (r * p.Hq + h) * (int64_t)lat + cp) = make_float2(acc[h][0] * inv, acc[h][1] * inv);
+    }
+  }
+}
+size_t mla_tiled_smem(int Hq, int Hkv, int lat, int rope) {
+  return sizeof(float) * ((size_t)kMlaTile * (lat + 4) + (size_t)kMlaTile * (Hkv * rope + 4) + (size_t)Hq * (lat + rope) + (size_t)Hq * kMlaTile);
+}
+
 // ------------------------------------------------------------------ routed experts glue
 // hidden[r, c] = silu(clamp_above(gate)) * clamp(up) with UG = [up | gate] per row (kernels/scalar/elementwise.go:105-134).
 __global__ void __launch_bounds__(256) swiglu_rows_kernel(float* dst, const float* ug, int64_t rows, int width, float clampv) {
@@ -126,6 +236,30 @@ __global__ void __launch_bounds__(256) swiglu_rows_kernel(float* dst, const floa
     if (clampv > 0.0f) { if (u > clampv) u = clampv; else if (u < -clampv) u = -clampv; }
     const float sg = (float)(1.0 / (1.0 + exp((double)(-g))));
     dst[i] = g * sg * u;
+  }
+}
+
+// Router affinities (model/moe.go:123): logits[r, e] = x[r] . W[e]; one warp per row, the row stays in registers
+// (d <= 4096) while the E weight rows stream from L1/L2.  float32 accumulation, fixed order.
+__global__ void __launch_bounds__(WPB * 32) router_logits_kernel(float* logits, const float* x, const float* w, int64_t rows, int d, int E) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t r = (int64_t)blockIdx.x * WPB + warp;
+  if (r >= rows) return;
+  constexpr int MAXV = 32;   // float4 per lane: d <= 4096
+  float4 xv[MAXV];
+  const int nv = d / 128;    // d % 128 == 0 on this path
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) if (i < nv) xv[i] = *reinterpret_cast<const float4*>(x + r * d + (i * 32 + lane) * 4);
+  for (int e = 0; e < E; ++e) {
+    const float* we = w + (int64_t)e * d;
+    float acc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) if (i < nv) {
+      const float4 wv = *reinterpret_cast<const float4*>(we + (i * 32 + lane) * 4);
+      acc = fmaf(xv[i].x, wv.x, acc); acc = fmaf(xv[i].y, wv.y, acc); acc = fmaf(xv[i].z, wv.z, acc); acc = fmaf(xv[i].w, wv.w, acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) logits[r * E + e] = acc;
   }
 }
 
@@ -244,7 +378,14 @@ int latent_attention(gn_model* m, FwdBufs& b, const FwdArgs& a, int l, const flo
   { const int64_t n = rows * (Hq + Hkv + 1); mla_post_kernel<<<ceil_div(n, WPB), WPB * 32, 0, s>>>(pp); GN_LAUNCH_CHECK(); }
   MlaAttn pa; pa.QF = b.QF; pa.lat_cache = lcache; pa.rope_cache = rcache; pa.AL = b.AL; pa.pos = m->pos.i(); pa.cache_row_mul = a.cache_row_mul;
   pa.max_seq = a.max_seq; pa.B = a.B; pa.T = a.T; pa.Hq = Hq; pa.Hkv = Hkv; pa.lat = lat; pa.rope = rope; pa.window = m->windows[l];
-  { const int64_t n = rows * Hq; mla_attention_kernel<<<ceil_div(n, 4), 128, 0, s>>>(pa); GN_LAUNCH_CHECK(); }
+  const size_t tiled_smem = mla_tiled_smem(Hq, Hkv, lat, rope);
+  if (lat % 8 == 0 && rope % 4 == 0 && lat <= 512 && Hq <= kMlaMaxHeads && tiled_smem <= 200 * 1024) {
+    static size_t configured = 0;
+    if (tiled_smem > configured) { GN_CUDA(cudaFuncSetAttribute(mla_attention_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tiled_smem)); configured = tiled_smem; }
+    mla_attention_tiled_kernel<<<(unsigned)rows, 256, tiled_smem, s>>>(pa); GN_LAUNCH_CHECK();
+  } else {
+    const int64_t n = rows * Hq; mla_attention_kernel<<<ceil_div(n, 4), 128, 0, s>>>(pa); GN_LAUNCH_CHECK();
+  }
   // head outputs: O[:, hq, :] = AL[:, hq, :] Wv_up[hk]^T   (Wv_up[hk] is [D, lat]; model/mla.go:264-274)
   for (int hq = 0; hq < Hq; ++hq) {
     const int hk = hq / ratio;
@@ -267,8 +408,12 @@ int moe_ffn(gn_model* m, FwdBufs& b, const FwdArgs& a, int l, const float* Mn, c
   { GemmArgs g; g.A = b.SHH; g.lda = sh; g.B = m->p(o.mproj); g.b_static = 1; g.ldb = sh; g.b_trans = 1; g.C = b.SHO; g.ldc = d; g.M = (int)rows; g.N = d; g.K = sh;
     GN_TRY(gemm(m, g)); }
   // ---- router (model/moe.go:123-124): selection on logits + bias, weights = softmax(logits) of the selected
-  { GemmArgs g; g.A = Mn; g.lda = d; g.B = m->p(o.router); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = b.RL; g.ldc = E; g.M = (int)rows; g.N = E; g.K = d;
-    GN_TRY(gemm_dispatch(g, 0, s)); }   // E columns: the float32 kernel (routing must not depend on a split's rounding)
+  if (d % 128 == 0 && d <= 4096) {
+    router_logits_kernel<<<ceil_div(rows, WPB), WPB * 32, 0, s>>>(b.RL, Mn, m->p(o.router), rows, d, E); GN_LAUNCH_CHECK();
+  } else {
+    GemmArgs g; g.A = Mn; g.lda = d; g.B = m->p(o.router); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = b.RL; g.ldc = E; g.M = (int)rows; g.N = E; g.K = d;
+    GN_TRY(gemm_dispatch(g, 0, s));   // E columns: the float32 kernel (routing must not depend on a split's rounding)
+  }
   GN_TRY(moe_gate_topk_launch(b.RL, m->p(o.router_bias), b.PR, b.SEL, b.SELW, (int)rows, E, K, s));
   moe_route_kernel<<<1, 1024, 0, s>>>(b.SEL, total, E, b.CNT, b.POSI); GN_LAUNCH_CHECK();
   moe_gather_kernel<<<ceil_div(total, WPB), WPB * 32, 0, s>>>(b.GATH, tc ? b.GATHh : nullptr, tc ? b.GATHl : nullptr, Mn, b.POSI, total, K, d); GN_LAUNCH_CHECK();
