@@ -24,6 +24,7 @@
 #endif
 #include "backend.h"
 #include "model.h"
+#include "optimizer.h"
 #include "philox.h"
 
 namespace gnor {
@@ -453,5 +454,20 @@ double or_pg_loss_backward(int mode, const float* logits, const int32_t* targets
 void or_train_forward(void* mp, const int32_t* ids, int B, int T, float* logits) {
   TrainCtx ctx; ((Model*)mp)->train_forward(ctx, ids, B, T); std::copy(ctx.logits.begin(), ctx.logits.end(), logits);
 }
+
+// ---------------------------------------------------------------- optimizer
+void or_adamw_step(float* param, const float* grad, float* exp_avg, float* exp_avg_sq, int64_t n, int step, float lr, float beta1, float beta2, float eps,
+                   float weight_decay) { gnopt::adamw_step(param, grad, exp_avg, exp_avg_sq, n, step, lr, beta1, beta2, eps, weight_decay); }
+void or_muon_step(int mode, float* param, const float* grad, float* mom, float* second_mom, int rows, int cols, float lr, float momentum, int ns_steps,
+                  float beta2, float weight_decay) {
+  BK(mode); gnopt::muon_step(bk, param, grad, mom, second_mom, rows, cols, lr, momentum, ns_steps, beta2, weight_decay);
+}
+void or_sinkhorn_step(float* param, const float* grad, float* mom, int rows, int cols, float lr, float momentum, float gamma, int steps, float tau,
+                      float eps) { gnopt::sinkhorn_step(param, grad, mom, rows, cols, lr, momentum, gamma, steps, tau, eps); }
+void* or_optimizer_create(void* model, float ulr, float elr, float mlr, float wd, float slr, float mult) {
+  return new gnopt::Optimizer((Model*)model, ulr, elr, mlr, wd, slr, mult);
+}
+void or_optimizer_destroy(void* o) { delete (gnopt::Optimizer*)o; }
+void or_optimizer_step(void* o) { ((gnopt::Optimizer*)o)->step(); }
 
 }  // extern "C"

@@ -383,6 +383,44 @@ def pg_loss_backward(logits, targets, adv, seq_len, norm, mode=0, want_grad=True
 
 
 # --------------------------------------------------------------------------
+# Optimizer (optimizer/optimizer.go, muon.go, sinkhorn.go): in-place updates of float32 arrays
+# --------------------------------------------------------------------------
+def adamw_step(param, grad, exp_avg, exp_avg_sq, step, lr, beta1, beta2, eps, weight_decay=0.0):
+    lib().or_adamw_step(_f(param), _f(f32(grad)), _f(exp_avg), _f(exp_avg_sq), C.c_int64(param.size), step, C.c_float(lr), C.c_float(beta1),
+                        C.c_float(beta2), C.c_float(eps), C.c_float(weight_decay))
+
+
+def muon_step(param, grad, mom, second_mom, rows, cols, lr, momentum=0.95, ns_steps=5, beta2=0.9, weight_decay=0.0, mode=0):
+    lib().or_muon_step(mode, _f(param), _f(f32(grad)), _f(mom), _f(second_mom), rows, cols, C.c_float(lr), C.c_float(momentum), ns_steps,
+                       C.c_float(beta2), C.c_float(weight_decay))
+
+
+def sinkhorn_step(param, grad, mom, rows, cols, lr, momentum=0.95, gamma=0.18, steps=11, tau=1e-3, eps=1e-20):
+    lib().or_sinkhorn_step(_f(param), _f(f32(grad)), _f(mom), rows, cols, C.c_float(lr), C.c_float(momentum), C.c_float(gamma), steps,
+                           C.c_float(tau), C.c_float(eps))
+
+
+class Optimizer:
+    """chat_rl's MuonAdamW over a dense-preset Model (model/optimizer.go:20-165, cmd/chat_rl/main.go:68-72)."""
+
+    def __init__(self, model, unembedding_lr=0.004, embedding_lr=0.2, matrix_lr=0.02, weight_decay=0.0, scalar_lr=0.5, lr_mult=0.05):
+        self.l = lib(); self.model = model
+        self.l.or_optimizer_create.restype = C.c_void_p
+        self.h = C.c_void_p(self.l.or_optimizer_create(model.h, C.c_float(unembedding_lr), C.c_float(embedding_lr), C.c_float(matrix_lr),
+                                                       C.c_float(weight_decay), C.c_float(scalar_lr), C.c_float(lr_mult)))
+
+    def step(self):
+        """optimizer.Step() followed by ZeroGrad() (trainer/rl.go:65-66)."""
+        self.l.or_optimizer_step(self.h)
+
+    def __del__(self):
+        try:
+            self.l.or_optimizer_destroy(self.h)
+        except Exception:
+            pass
+
+
+# --------------------------------------------------------------------------
 # Model
 # --------------------------------------------------------------------------
 class Model:
