@@ -5,8 +5,10 @@
 
 One "step" is one whole RL step on the dense d12 workload: rollout of 64 prompts x G=8 rows
 (128 prompt tokens, 256 new tokens, temperature 1.0, top-k 50), Bernoulli(0.5) rewards, group
-advantages, the teacher-forced policy-gradient loss with its backward, and the gradient
-all-reduce.  With N GPUs the 64 prompts are split into N contiguous shards (strong scaling: the
+advantages, the teacher-forced policy-gradient loss with its backward, the gradient
+all-reduce and the optimizer step with ZeroGrad (trainer/rl.go:62-67; chat_rl's MuonAdamW:
+Sinkhorn for lm_head / wte / value embeddings, Muon for the block matrices, AdamW for the
+scalars).  With N GPUs the 64 prompts are split into N contiguous shards (strong scaling: the
 total work is fixed), one process per GPU, a full policy replica each.
 
 Prints ONE JSON line (rank 0).
@@ -134,12 +136,30 @@ def cpu_baseline(sample_scale: int = 1):
     t0 = time.perf_counter()
     om.policy_gradient_step(inputs, targets, np.array([0.5], np.float32), float(T + 1))
     t_train_row = time.perf_counter() - t0
+    # optimizer step (optimizer/muon.go, sinkhorn.go): one update of each distinct matrix shape, scaled by how many the model has
+    d, L, V, KV = cfg["embed_dim"], cfg["n_layer"], om.padded_vocab(), cfg["n_kv_head"] * (cfg["embed_dim"] // cfg["n_head"])
+
+    def t_muon(rows, cols):
+        p = (rng.standard_normal(rows * cols) * 0.02).astype(np.float32); g = (rng.standard_normal(rows * cols) * 0.01).astype(np.float32)
+        t = time.perf_counter()
+        oracle.muon_step(p, g, np.zeros_like(p), np.zeros(max(rows, cols), np.float32), rows, cols, lr=0.001, mode=1)
+        return time.perf_counter() - t
+
+    def t_sink(rows, cols):
+        p = np.zeros(rows * cols, np.float32); g = (rng.standard_normal(rows * cols) * 0.01).astype(np.float32)
+        t = time.perf_counter()
+        oracle.sinkhorn_step(p, g, np.zeros_like(p), rows, cols, lr=0.001)
+        return time.perf_counter() - t
+
+    n_ve = sum(1 for n in om.names if n.startswith("value_embeds."))
+    t_opt = L * (2 * t_muon(d, d) + 2 * t_muon(KV, d) + t_muon(4 * d, d) + t_muon(d, 4 * d)) + t_sink(V, KV) * (2.0 * d / KV + n_ve)
     P = w["n_prompts"]
     # decode cost grows with the context; the sample sits at the start of the rollout, so this is a lower bound
-    step_s = P * (t_prefill + new * t_decode) + P * G * t_train_row
+    step_s = P * (t_prefill + new * t_decode) + P * G * t_train_row + t_opt
     return {"value": 1.0 / step_s, "unit": UNIT, "cores": threads, "kind": "port",
             "sample": (f"extrapolated: 1 prompt prefill ({t_prefill:.3f}s) + {n_dec} decode steps of {G} rows ({t_decode:.4f}s each) + "
                        f"train/loss/backward of 1 row x {T} tokens ({t_train_row:.2f}s), scaled to {P} prompts x {G} rows x {new} tokens; "
+                       f"optimizer: one Muon update per matrix shape and one Sinkhorn update of a value-embedding table, scaled by count ({t_opt:.1f}s); "
                        f"oracle mode 1 (kernels/simd structure), {oracle.isa()}, {threads} threads"),
             "step_seconds_extrapolated": step_s}
 
@@ -220,15 +240,16 @@ def run_ours(args):
     def reward_fn(tokens, lengths):
         return rewards_all[lo * G:hi * G]
 
+    model.optimizer_init()   # cmd/chat_rl/main.go:68-72
     all_reduce = gdist.GradAllReduce(model, local, stream) if world > 1 else None
-    phases = ["prefill", "decode", "train_forward", "loss", "train_backward", "allreduce"]
+    phases = ["prefill", "decode", "train_forward", "loss", "train_backward", "allreduce", "optimizer"]
     state = {"step": 0}
 
     def one_step():
         seeds = np.arange(lo, hi, dtype=np.uint64) + np.uint64(1000 * state["step"])   # cmd/chat_rl seeds rollouts by step
         state["step"] += 1
         res = rl_step(model, prompts, G, w["max_tokens"], w["temperature"], w["top_k"], seeds, reward_fn, advantage_mode=0,
-                      all_reduce=all_reduce, max_len_fn=gdist.global_max_len if world > 1 else None)
+                      all_reduce=all_reduce, max_len_fn=gdist.global_max_len if world > 1 else None, optimizer=True)
         ph = {p: model.phase_ms(p) for p in phases if p != "allreduce"}
         ph["allreduce"] = all_reduce.last_ms() if all_reduce is not None else 0.0
         return res, ph
@@ -311,8 +332,8 @@ def run_ours(args):
         "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
         "config": {"workload": "dense d12 RL step: 64 prompts x G=8 (512 rows), 128 prompt tokens, 256 new tokens, T=1.0, top-k 50, "
-                               "vocab 32768, d768 L12 Hq6 Hkv2; rollout + advantage + policy-gradient loss/backward + gradient all-reduce "
-                               "(optimizer step not included)",
+                               "vocab 32768, d768 L12 Hq6 Hkv2; rollout + advantage + policy-gradient loss/backward + gradient all-reduce + "
+                               "optimizer step (Sinkhorn / Muon / AdamW as cmd/chat_rl) + ZeroGrad",
                    "parallelism": f"dp{world}", "l2": "working set (705 MB weights, 4.8 GB KV cache, GBs of activations) is far larger than L2; no flush",
                    "gemm": "tcgen05 3xTF32" if os.environ.get("GN_GEMM", "") != "simt" else "simt"},
         "e2e": {"value": steps_per_s_e2e, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},

@@ -31,6 +31,11 @@ class GnConfig(C.Structure):
     ]
 
 
+class GnOptimizerConfig(C.Structure):
+    _fields_ = [("unembedding_lr", C.c_float), ("embedding_lr", C.c_float), ("matrix_lr", C.c_float), ("weight_decay", C.c_float),
+                ("scalar_lr", C.c_float), ("lr_mult", C.c_float)]
+
+
 class GnAttentionParams(C.Structure):
     _fields_ = [
         ("query", vp), ("key", vp), ("value", vp),
@@ -63,6 +68,10 @@ SIGNATURES = {
     "gn_attention_backward": (I, [C.POINTER(GnAttentionParams), vp, vp, vp, vp, vp, vp, vp]),
     "gn_sample_next_token": (I, [vp, I, I, vp, vp, I, U32, F, I, vp]),
     "gn_group_advantage": (I, [vp, I, I, I, vp]),
+    "gn_adamw_step": (I, [vp, vp, vp, vp, L, I, F, F, F, F, F]),
+    "gn_muon_step": (I, [vp, vp, vp, vp, I, I, F, F, I, F, F]),
+    "gn_sinkhorn_step": (I, [vp, vp, vp, I, I, F, F, F, I, F, F]),
+    "gn_model_optimizer_init": (I, [vp, C.POINTER(GnOptimizerConfig)]), "gn_model_optimizer_step": (I, [vp]),
     "gn_pg_loss_backward": (I, [vp, vp, vp, L, I, I, F, F, vp, vp, C.POINTER(C.c_double)]),
     "gn_pg_loss_backward_static": (I, [vp, vp, vp, L, I, I, F, F, vp, vp, vp, vp]),
     "gn_ctx_create": (I, [I, vp, C.POINTER(vp)]), "gn_ctx_destroy": (I, [vp]), "gn_ctx_sync": (I, [vp]),
@@ -71,7 +80,7 @@ SIGNATURES = {
     "gn_model_param_count": (I, [vp, C.POINTER(I)]),
     "gn_model_param_info": (I, [vp, I, C.POINTER(C.c_char_p), C.POINTER(I), C.POINTER(I)]),
     "gn_model_upload": (I, [vp, C.c_char_p, vp, L]), "gn_model_download": (I, [vp, C.c_char_p, vp, L]),
-    "gn_model_download_grad": (I, [vp, C.c_char_p, vp, L]), "gn_model_zero_grad": (I, [vp]),
+    "gn_model_download_grad": (I, [vp, C.c_char_p, vp, L]), "gn_model_upload_grad": (I, [vp, C.c_char_p, vp, L]), "gn_model_zero_grad": (I, [vp]),
     "gn_model_grad_buffer": (I, [vp, C.POINTER(vp), C.POINTER(C.c_int64)]),
     "gn_model_param_buffer": (I, [vp, C.POINTER(vp), C.POINTER(C.c_int64)]),
     "gn_model_checksum": (I, [vp, C.POINTER(C.c_double), C.POINTER(C.c_double)]),

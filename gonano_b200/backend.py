@@ -203,3 +203,24 @@ def pg_loss_backward(logits, targets, advantages, seq_len, norm, softcap=0.0, wa
     check(lib.gn_pg_loss_backward(ptr(logits), ptr(targets), ptr(advantages), rows, vocab, seq_len, norm, softcap, ptr(nll), ptr(grad),
                                   C.byref(loss)))
     return loss.value, nll, grad
+
+
+# -------------------------------------------------------------------------
+# Optimizer updates of one tensor (optimizer/optimizer.go, muon.go, sinkhorn.go); arrays are updated in place
+# -------------------------------------------------------------------------
+def adamw_step(param, grad, exp_avg, exp_avg_sq, step, lr, beta1, beta2, eps, weight_decay=0.0):
+    lib = _lib.load()
+    g = _f32(grad).copy()
+    check(lib.gn_adamw_step(ptr(param), ptr(g), ptr(exp_avg), ptr(exp_avg_sq), param.size, step, lr, beta1, beta2, eps, weight_decay))
+
+
+def muon_step(param, grad, mom, second_mom, rows, cols, lr, momentum=0.95, ns_steps=5, beta2=0.9, weight_decay=0.0):
+    lib = _lib.load()
+    g = _f32(grad).copy()
+    check(lib.gn_muon_step(ptr(param), ptr(g), ptr(mom), ptr(second_mom), rows, cols, lr, momentum, ns_steps, beta2, weight_decay))
+
+
+def sinkhorn_step(param, grad, mom, rows, cols, lr, momentum=0.95, gamma=0.18, steps=11, tau=1e-3, eps=1e-20):
+    lib = _lib.load()
+    g = _f32(grad).copy()
+    check(lib.gn_sinkhorn_step(ptr(param), ptr(g), ptr(mom), rows, cols, lr, momentum, gamma, steps, tau, eps))

@@ -31,10 +31,16 @@ int64_t launch_count() { return g_launches.load(std::memory_order_relaxed); }
 int gemm_tcgen05_supported(const GemmArgs& a);
 int gemm_tcgen05(const GemmArgs& a, cudaStream_t s);
 void gemm_tcgen05_invalidate();
+void gemm_tcgen05_mark_stale();
 int gemm_tcgen05_check(cudaStream_t s);
 void gemm_invalidate_static() {
 #ifdef GN_HAVE_TCGEN05
   gemm_tcgen05_invalidate();
+#endif
+}
+void gemm_mark_static_stale() {
+#ifdef GN_HAVE_TCGEN05
+  gemm_tcgen05_mark_stale();
 #endif
 }
 int gemm_check_error(cudaStream_t s) {
@@ -277,6 +283,53 @@ int gn_grouped_matmul_transposed(float* dst, const float* input, const float* we
   { GemmArgs g; g.A = din; g.lda = inner; g.B = dw; g.ldb = inner; g.b_trans = 1; g.C = dd; g.ldc = cols; g.M = (int)total; g.N = cols; g.K = inner;
     g.group_counts = dc; g.groups = experts;
     GN_TRY(gemm_grouped_dispatch(g, gemm_default_kind(), s)); }
+  GN_END();
+}
+
+int gn_adamw_step(float* param, float* grad, float* exp_avg, float* exp_avg_sq, int64_t n, int step, float lr, float beta1, float beta2, float eps,
+                  float weight_decay) {
+  GN_REQUIRE(param && grad && exp_avg && exp_avg_sq && n >= 0 && step >= 1, "adamw_step: bad argument");
+  if (n == 0) return GN_OK;
+  GN_BEGIN();
+  float* dp = st.out(param, (size_t)n, true); const float* dg = st.in(grad, (size_t)n);
+  float* dm = st.out(exp_avg, (size_t)n, true); float* dv = st.out(exp_avg_sq, (size_t)n, true);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(adamw_launch(dp, dg, dm, dv, n, step, lr, beta1, beta2, eps, weight_decay, s));
+  GN_END();
+}
+
+namespace {
+struct Scratch {   // device workspace freed on scope exit
+  void* p = nullptr;
+  ~Scratch() { if (p) cudaFree(p); }
+  int get(size_t bytes) { if (cudaMalloc(&p, bytes) != cudaSuccess) { set_error("optimizer: cannot allocate a %zu-byte workspace", bytes); return GN_ERR_NOMEM; } return GN_OK; }
+};
+}  // namespace
+
+int gn_muon_step(float* param, float* grad, float* momentum_state, float* second_mom, int rows, int cols, float lr, float momentum, int ns_steps,
+                 float beta2, float weight_decay) {
+  GN_REQUIRE(param && grad && momentum_state && second_mom && rows > 0 && cols > 0, "muon_step: bad argument");
+  GN_BEGIN();
+  const size_t n = (size_t)rows * cols, nv = (size_t)std::max(rows, cols);
+  float* dp = st.out(param, n, true); float* dg = st.out(grad, n, true);
+  float* dm = st.out(momentum_state, n, true); float* dv = st.out(second_mom, nv, true);
+  if (st.status != GN_OK) return st.status;
+  Scratch ws; GN_TRY(ws.get(muon_workspace_bytes(rows, cols)));
+  GN_TRY(muon_launch(dp, dg, dm, dv, rows, cols, lr, momentum, ns_steps, beta2, weight_decay, ws.p, gemm_default_kind(), s));
+  int rc = st.finish();
+  if (rc == GN_OK) rc = gemm_check_error(s);
+  return rc;
+}
+
+int gn_sinkhorn_step(float* param, float* grad, float* momentum_state, int rows, int cols, float lr, float momentum, float gamma, int steps, float tau,
+                     float eps) {
+  GN_REQUIRE(param && grad && momentum_state && rows > 0 && cols > 0, "sinkhorn_step: bad argument");
+  GN_BEGIN();
+  const size_t n = (size_t)rows * cols;
+  float* dp = st.out(param, n, true); float* dg = st.out(grad, n, true); float* dm = st.out(momentum_state, n, true);
+  if (st.status != GN_OK) return st.status;
+  Scratch ws; GN_TRY(ws.get(sinkhorn_workspace_bytes(rows, cols)));
+  GN_TRY(sinkhorn_launch(dp, dg, dm, rows, cols, lr, momentum, gamma, steps, tau, eps, ws.p, s));
   GN_END();
 }
 

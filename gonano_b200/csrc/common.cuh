@@ -189,7 +189,8 @@ int gemm_grouped_dispatch(const GemmArgs& args, int kind, cudaStream_t stream);
 int gemm_default_kind();
 int64_t launch_count();
 // tcgen05 path housekeeping (no-ops when the library was built without it).
-void gemm_invalidate_static();        // parameters changed: drop cached operand splits
+void gemm_invalidate_static();        // parameter storage is going away: free cached operand splits
+void gemm_mark_static_stale();        // parameters changed in place: cached splits are redone (in their buffers) on next use
 int gemm_check_error(cudaStream_t s); // GN_ERR_TIMEOUT when a bounded device wait ran out
 
 }  // namespace gn

@@ -427,7 +427,7 @@ int* g_err_flag = nullptr;
 long long* g_trace = nullptr;   // device buffer of 1024 slots (GN_TC_TRACE builds)
 std::mutex g_mu;
 
-struct SplitBuf { float* hi = nullptr; float* lo = nullptr; size_t floats = 0; int64_t ld = 0; };
+struct SplitBuf { float* hi = nullptr; float* lo = nullptr; size_t floats = 0; int64_t ld = 0; bool fresh = true; };
 // Cached splits of parameter tensors: key = (pointer, rows, cols, transposed).
 std::map<std::tuple<const void*, int64_t, int64_t, int>, SplitBuf> g_static;
 SplitBuf g_dyn[2];  // scratch for the activation operands (A and B of the current product)
@@ -470,11 +470,14 @@ int ensure_buf(SplitBuf& b, size_t floats) {
 int split_operand(const float* src, int64_t ld, int64_t rows, int64_t k, bool stored_transposed, bool is_static, int which, SplitBuf& out, cudaStream_t s) {
   const int64_t kp = (k + 3) / 4 * 4;
   auto key = std::make_tuple((const void*)src, rows, k, stored_transposed ? 1 : 0);
+  SplitBuf buf;
   if (is_static) {
     auto it = g_static.find(key);
-    if (it != g_static.end()) { out = it->second; return GN_OK; }
+    if (it != g_static.end()) {
+      if (it->second.fresh) { out = it->second; return GN_OK; }
+      buf = it->second;          // the parameters changed: split again into the buffers this entry already owns
+    }
   }
-  SplitBuf buf;
   SplitBuf* target = is_static ? &buf : &g_dyn[which];
   GN_TRY(ensure_buf(*target, (size_t)rows * kp));
   target->ld = kp;
@@ -487,6 +490,7 @@ int split_operand(const float* src, int64_t ld, int64_t rows, int64_t k, bool st
     split_transpose_kernel<<<grid, 256, 0, s>>>(src, ld, target->hi, target->lo, kp, k, (int)rows);
   }
   GN_LAUNCH_CHECK();
+  target->fresh = true;
   if (is_static) g_static[key] = *target;
   out = *target;
   return GN_OK;
@@ -606,6 +610,11 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
 }
 
 // Drops the cached splits of parameter tensors (call after the parameters change).
+// The parameters changed in place (an optimizer step, an upload): cached splits keep their buffers and are redone on next use.
+void gemm_tcgen05_mark_stale() {
+  std::lock_guard<std::mutex> lock(g_mu);
+  for (auto& kv : g_static) kv.second.fresh = false;
+}
 void gemm_tcgen05_invalidate() {
   std::lock_guard<std::mutex> lock(g_mu);
   cudaDeviceSynchronize();

@@ -21,6 +21,17 @@ int rmsnorm_rows_launch(float* dst, const float* src, int64_t rows, int cols, fl
 int rmsnorm_backward_launch(float* dx, const float* x, const float* dy, const float* add, int64_t rows, int cols, float eps, cudaStream_t s);
 int fill_launch(float* dst, float value, int64_t n, cudaStream_t s);
 
+// --------------------------------------------------------------- optimizer.cu
+// In-place updates (optimizer/optimizer.go:143-173, muon.go:23-173, sinkhorn.go:27-95).  `g` is overwritten (it holds the
+// update matrix while the step runs).  `step` is AdamW's 1-based count.  Workspaces: *_workspace_bytes.
+size_t muon_workspace_bytes(int rows, int cols);
+size_t sinkhorn_workspace_bytes(int rows, int cols);
+int adamw_launch(float* p, const float* g, float* m, float* v, int64_t n, int step, float lr, float beta1, float beta2, float eps, float wd, cudaStream_t s);
+int muon_launch(float* p, float* g, float* mom, float* second, int rows, int cols, float lr, float momentum, int ns_steps, float beta2, float wd,
+                void* workspace, int gemm_kind, cudaStream_t s);
+int sinkhorn_launch(float* p, float* g, float* mom, int rows, int cols, float lr, float momentum, float gamma, int steps, float tau, float eps,
+                    void* workspace, cudaStream_t s);
+
 // --------------------------------------------------------------------- moe.cu
 int topk_indices_launch(int32_t* dst, const float* scores, int rows, int count, int k, cudaStream_t s);
 int moe_gate_topk_launch(const float* logits, const float* bias, float* probs, int32_t* sel, float* w, int rows, int experts, int k, cudaStream_t s);

@@ -108,7 +108,7 @@ int enter(gn_model* m) {
 // Entry of a compute phase: stale operand splits are dropped before the first GEMM.
 int enter_compute(gn_model* m) {
   GN_TRY(enter(m));
-  if (m->weights_dirty) { gemm_invalidate_static(); m->weights_dirty = false; }
+  if (m->weights_dirty) { gemm_mark_static_stale(); m->weights_dirty = false; }
   return GN_OK;
 }
 
@@ -494,7 +494,8 @@ int gn_model_destroy(gn_model* m) {
   gemm_invalidate_static();   // cached splits are keyed by addresses that are about to be freed
   DevBuf* bufs[] = {&m->P, &m->G, &m->cosb, &m->sinb, &m->sacc, &m->cache, &m->prev, &m->pos, &m->ctxlen, &m->ids_dev, &m->sampled, &m->seeds,
                     &m->out_tokens, &m->out_lengths, &m->done, &m->n_done, &m->sel, &m->part_acc, &m->part_ms, &m->step_dev, &m->infer.buf, &m->train.buf,
-                    &m->tgt_dev, &m->adv_dev, &m->rowloss, &m->loss_dev, &m->in_dev, &m->cache_lat, &m->cache_rope};
+                    &m->tgt_dev, &m->adv_dev, &m->rowloss, &m->loss_dev, &m->in_dev, &m->cache_lat, &m->cache_rope, &m->opt_mom, &m->opt_second,
+                    &m->opt_ws};
   for (DevBuf* b : bufs) b->release();
   for (int i = 0; i < 4; ++i) if (m->ev[i]) cudaEventDestroy(m->ev[i]);
   delete m;
@@ -534,6 +535,12 @@ int gn_model_download(gn_model* m, const char* name, float* host, int64_t n) {
 int gn_model_download_grad(gn_model* m, const char* name, float* host, int64_t n) {
   const ParamInfo* pi; GN_TRY(find_param(m, name, n, &pi)); GN_TRY(enter(m));
   GN_CUDA(cudaMemcpyAsync(host, m->g(pi->offset), sizeof(float) * n, cudaMemcpyDeviceToHost, m->s()));
+  GN_CUDA(cudaStreamSynchronize(m->s()));
+  return GN_OK;
+}
+int gn_model_upload_grad(gn_model* m, const char* name, const float* host, int64_t n) {
+  const ParamInfo* pi; GN_TRY(find_param(m, name, n, &pi)); GN_TRY(enter(m));
+  GN_CUDA(cudaMemcpyAsync(m->g(pi->offset), host, sizeof(float) * n, cudaMemcpyHostToDevice, m->s()));
   GN_CUDA(cudaStreamSynchronize(m->s()));
   return GN_OK;
 }
@@ -580,6 +587,61 @@ int gn_model_forward(gn_model* m, const int32_t* ids, int B, int T, float* logit
   GN_CUDA(cudaMemcpyAsync(logits, b.LOGITS, sizeof(float) * rows * m->V, cudaMemcpyDeviceToHost, m->s()));
   GN_CUDA(cudaStreamSynchronize(m->s()));
   return gemm_check_error(m->s());
+}
+
+// ---------------------------------------------------------------- optimizer
+int gn_model_optimizer_init(gn_model* m, const gn_optimizer_config* cfg) {
+  GN_TRY(enter(m));
+  GN_REQUIRE(cfg, "gn_model_optimizer_init: null config");
+  if (m->moe() || m->mla()) { set_error("the optimizer step covers the dense preset only"); return GN_ERR_UNSUPPORTED; }
+  m->opt_cfg = *cfg; m->opt_steps = 0;
+  GN_TRY(m->opt_mom.ensure(sizeof(float) * m->total)); GN_TRY(m->opt_second.ensure(sizeof(float) * m->total));
+  GN_CUDA(cudaMemsetAsync(m->opt_mom.p, 0, sizeof(float) * m->total, m->s()));
+  GN_CUDA(cudaMemsetAsync(m->opt_second.p, 0, sizeof(float) * m->total, m->s()));
+  size_t ws = 0;
+  for (const ParamInfo& pi : m->params) {
+    const bool sink = pi.name == "lm_head.weight" || pi.name == "transformer.wte.weight" || pi.name.rfind("value_embeds.", 0) == 0;
+    const bool scalar = pi.name.rfind("transformer.h.", 0) != 0 && !sink;
+    if (sink) ws = std::max(ws, sinkhorn_workspace_bytes(pi.rows, pi.cols));
+    else if (!scalar) ws = std::max(ws, muon_workspace_bytes(pi.rows, pi.cols));
+  }
+  GN_TRY(m->opt_ws.ensure(ws));
+  m->opt_ready = true;
+  return GN_OK;
+}
+
+// Routing: model/optimizer.go:20-165 (sinkhorn = true).  Parameters are visited in name order; the updates are
+// independent of one another, so the order only fixes the launch sequence.
+int gn_model_optimizer_step(gn_model* m) {
+  GN_TRY(enter(m));
+  GN_REQUIRE(m->opt_ready, "gn_model_optimizer_step: call gn_model_optimizer_init first");
+  cudaStream_t s = m->s();
+  const gn_optimizer_config& c = m->opt_cfg;
+  GN_CUDA(cudaEventRecord(m->ev[0], s));
+  ++m->opt_steps;
+  const float dscale = (float)std::pow((double)m->d / 768.0, -0.5);   // model/optimizer.go:108
+  for (const ParamInfo& pi : m->params) {
+    float* p = m->p(pi.offset); float* g = m->g(pi.offset);
+    float* mo = m->opt_mom.f() + pi.offset; float* se = m->opt_second.f() + pi.offset;
+    const int64_t n = (int64_t)pi.rows * pi.cols;
+    auto sink = [&](float lr) { return sinkhorn_launch(p, g, mo, pi.rows, pi.cols, lr * c.lr_mult, 0.95f, 0.18f, 11, 1e-3f, 1e-20f, m->opt_ws.p, s); };
+    auto adam = [&](float lr, float b1, float b2, float wd) { return adamw_launch(p, g, mo, se, n, m->opt_steps, lr * c.lr_mult, b1, b2, 1e-10f, wd, s); };
+    if (pi.name == "lm_head.weight") GN_TRY(sink(c.unembedding_lr * dscale));
+    else if (pi.name == "transformer.wte.weight") GN_TRY(sink(c.embedding_lr * dscale));
+    else if (pi.name.rfind("value_embeds.", 0) == 0) GN_TRY(sink(c.embedding_lr * dscale * 0.5f));
+    else if (pi.name == "resid_lambdas") GN_TRY(adam(c.scalar_lr * 0.01f, 0.8f, 0.95f, 0.05f));
+    else if (pi.name == "x0_lambdas") GN_TRY(adam(c.scalar_lr, 0.96f, 0.95f, 0.0f));
+    else if (pi.name == "smear_gate.weight" || pi.name == "smear_lambda" || pi.name == "backout_lambda") GN_TRY(adam(0.2f, 0.8f, 0.95f, 0.0f));
+    else GN_TRY(muon_launch(p, g, mo, se, pi.rows, pi.cols, c.matrix_lr * c.lr_mult, 0.95f, 5, 0.9f, c.weight_decay, m->opt_ws.p, m->ctx->gemm_kind, s));
+  }
+  GN_CUDA(cudaMemsetAsync(m->G.p, 0, sizeof(float) * m->total, s));   // ZeroGrad (trainer/rl.go:66)
+  GN_CUDA(cudaMemsetAsync(m->sacc.p, 0, sizeof(double) * (2 * m->L + 2), s));
+  GN_CUDA(cudaEventRecord(m->ev[1], s));
+  m->weights_dirty = true;   // cached tensor-core splits of the parameters are stale
+  GN_CUDA(cudaStreamSynchronize(s));
+  float ms = 0;
+  GN_CUDA(cudaEventElapsedTime(&ms, m->ev[0], m->ev[1])); m->phase_ms["optimizer"] = ms;
+  return gemm_check_error(s);
 }
 
 int gn_generate_batch(gn_model* m, const int32_t* prompts, int P, int plen, int G, int max_tokens, float temperature, int top_k, const uint64_t* seeds,

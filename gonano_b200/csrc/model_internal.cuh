@@ -84,6 +84,11 @@ struct gn_model {
   // inference state
   DevBuf cache, prev, pos, ctxlen, ids_dev, sampled, seeds, out_tokens, out_lengths, done, n_done, sel;
   DevBuf part_acc, part_ms, step_dev;
+  // optimizer state (gn_model_optimizer_init): momentum / exp_avg and second moment / exp_avg_sq at the parameter's offset
+  DevBuf opt_mom, opt_second, opt_ws;
+  gn_optimizer_config opt_cfg{};
+  int opt_steps = 0;
+  bool opt_ready = false;
   DevBuf cache_lat, cache_rope;   // latent attention: [layer][row][max_seq][lat] and [layer][row][max_seq][Hkv*rope]
   Arena infer, train;
   DevBuf tgt_dev, adv_dev, rowloss, loss_dev, in_dev;

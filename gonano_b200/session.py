@@ -14,7 +14,7 @@ from dataclasses import dataclass
 import numpy as np
 
 from . import _lib
-from ._lib import GnConfig, check, ptr
+from ._lib import GnConfig, GnOptimizerConfig, check, ptr
 
 SPECIAL_TOKENS = 11  # tokenizer/special.go:19-31
 
@@ -110,6 +110,10 @@ class Model:
     def zero_grad(self):
         check(self.lib.gn_model_zero_grad(self.h))
 
+    def upload_grad(self, name, values):
+        values = _f32(values)
+        check(self.lib.gn_model_upload_grad(self.h, name.encode(), ptr(values), values.size))
+
     def grad_buffer(self):
         """(device address, float count) of the flat gradient buffer that a data-parallel all-reduce sums."""
         p, n = C.c_void_p(), C.c_int64()
@@ -152,6 +156,15 @@ class Model:
         return tokens, lengths, steps.value, step_logits
 
     # ---- trainer.PolicyGradientStep (trainer/rl.go:14-60)
+    def optimizer_init(self, unembedding_lr=0.004, embedding_lr=0.2, matrix_lr=0.02, weight_decay=0.0, scalar_lr=0.5, lr_mult=0.05):
+        """chat_rl's MuonAdamW (model.SetupOptimizer(0.004, 0.2, 0.02, 0.0, 0.5, true), every LR x 0.05; cmd/chat_rl/main.go:68-72)."""
+        cfg = GnOptimizerConfig(unembedding_lr, embedding_lr, matrix_lr, weight_decay, scalar_lr, lr_mult)
+        check(self.lib.gn_model_optimizer_init(self.h, C.byref(cfg)))
+
+    def optimizer_step(self):
+        """optimizer.Step() then ZeroGrad() (trainer/rl.go:65-66)."""
+        check(self.lib.gn_model_optimizer_step(self.h))
+
     def policy_gradient_step(self, inputs, targets, advantages, norm, rows_per_pass=0, taps=False):
         inputs, targets, advantages = _i32(inputs), _i32(targets), _f32(advantages)
         B, T = inputs.shape
@@ -201,10 +214,11 @@ class RLStepResult:
 
 
 def rl_step(model: Model, prompts, group, max_tokens, temperature, top_k, seeds, reward_fn, advantage_mode=0, rows_per_pass=0,
-            norm=None, all_reduce=None, max_len_fn=None) -> RLStepResult:
-    """One RL step the way cmd/chat_rl runs it (main.go:87-184), minus the optimizer:
+            norm=None, all_reduce=None, max_len_fn=None, optimizer=False) -> RLStepResult:
+    """One RL step the way cmd/chat_rl runs it (main.go:87-184):
     rollout -> rewards -> group-relative advantages -> padded batch -> PolicyGradientStep
-    -> gradient all-reduce (``all_reduce(model)``, when data parallel).  ``reward_fn(tokens,
+    -> gradient all-reduce (``all_reduce(model)``, when data parallel) -> optimizer step and
+    ZeroGrad when ``optimizer`` (trainer/rl.go:62-67; needs ``model.optimizer_init()``).  ``reward_fn(tokens,
     lengths)`` returns one reward per rollout.  ``norm`` defaults to the padded length
     (main.go:183).  ``max_len_fn(local_max_len)`` returns the length every rank pads to."""
     from .backend import group_advantage
@@ -219,4 +233,6 @@ def rl_step(model: Model, prompts, group, max_tokens, temperature, top_k, seeds,
     loss, _, _, _ = model.policy_gradient_step(inputs, targets, adv, float(max_len) if norm is None else norm, rows_per_pass)
     if all_reduce is not None:
         all_reduce(model)
+    if optimizer:
+        model.optimizer_step()
     return RLStepResult(loss, int(lengths.sum()), len(lengths), max_len, steps, tokens, lengths, adv)

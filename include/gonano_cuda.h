@@ -230,6 +230,8 @@ int gn_model_param_info(gn_model* model, int index, const char** name, int* rows
 int gn_model_upload(gn_model* model, const char* name, const float* host, int64_t n);
 int gn_model_download(gn_model* model, const char* name, float* host, int64_t n);
 int gn_model_download_grad(gn_model* model, const char* name, float* host, int64_t n);
+/* Overwrites one tensor's gradient (Tensor.Grad) from host memory, e.g. gradients reduced elsewhere. */
+int gn_model_upload_grad(gn_model* model, const char* name, const float* host, int64_t n);
 /* Tensor.ZeroGrad over every parameter (model/params.go:100-104). */
 int gn_model_zero_grad(gn_model* model);
 /* The flat device buffer that holds every gradient (what the data-parallel
@@ -281,6 +283,34 @@ int gn_model_phase_ms(gn_model* model, const char* phase, float* ms);
  *   "advantage"         dims {groups, group}
  * Buffers are larger than L2 for the workloads this is used on, so no cache flush is done. */
 int gn_profile_kernel(gn_ctx* ctx, const char* kernel, const int64_t* dims, int n_dims, int iters, float* mean_ms);
+
+/* ---------------------------------------------------------------------------
+ * Optimizer step (trainer/rl.go:62-67: RLStep = PolicyGradientStep, optimizer.Step, optimizer.ZeroGrad).
+ * Stand-alone updates of one tensor, in place; pointers may be host or device memory.  `grad` is
+ * overwritten (it serves as the update matrix while the step runs).
+ *   gn_adamw_step     optimizer/optimizer.go:143-173; `step` is the 1-based count of this tensor's updates
+ *   gn_muon_step      optimizer/muon.go:23-173; second_mom has max(rows, cols) floats
+ *   gn_sinkhorn_step  optimizer/sinkhorn.go:27-95; `steps` odd
+ */
+int gn_adamw_step(float* param, float* grad, float* exp_avg, float* exp_avg_sq, int64_t n, int step, float lr, float beta1, float beta2, float eps,
+                  float weight_decay);
+int gn_muon_step(float* param, float* grad, float* momentum_state, float* second_mom, int rows, int cols, float lr, float momentum, int ns_steps,
+                 float beta2, float weight_decay);
+int gn_sinkhorn_step(float* param, float* grad, float* momentum_state, int rows, int cols, float lr, float momentum, float gamma, int steps, float tau,
+                     float eps);
+
+/* The optimizer chat_rl builds for the model (model.SetupOptimizer with sinkhorn = true, model/optimizer.go:20-165):
+ * Sinkhorn for lm_head, wte and the value embeddings; AdamW for resid_lambdas, x0_lambdas and the smear / backout
+ * scalars; Muon for every block matrix.  cmd/chat_rl/main.go:68-72 passes (0.004, 0.2, 0.02, 0.0, 0.5) and multiplies
+ * every learning rate by 0.05.  Dense preset only. */
+typedef struct gn_optimizer_config {
+  float unembedding_lr, embedding_lr, matrix_lr, weight_decay, scalar_lr;
+  float lr_mult; /* applied to every group's learning rate */
+} gn_optimizer_config;
+/* Allocates (or resets) the optimizer state of the model: one momentum and one second-moment float per parameter. */
+int gn_model_optimizer_init(gn_model* model, const gn_optimizer_config* config);
+/* optimizer.Step() then ZeroGrad() on the model's gradient buffer (after the all-reduce in a data-parallel job). */
+int gn_model_optimizer_step(gn_model* model);
 
 #ifdef __cplusplus
 }
