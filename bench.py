@@ -249,7 +249,8 @@ def run_ours(args):
         seeds = np.arange(lo, hi, dtype=np.uint64) + np.uint64(1000 * state["step"])   # cmd/chat_rl seeds rollouts by step
         state["step"] += 1
         res = rl_step(model, prompts, G, w["max_tokens"], w["temperature"], w["top_k"], seeds, reward_fn, advantage_mode=0,
-                      all_reduce=all_reduce, max_len_fn=gdist.global_max_len if world > 1 else None, optimizer=True)
+                      all_reduce=all_reduce, max_len_fn=gdist.global_max_len if world > 1 else None, optimizer=True,
+                      shard=(rank, world))
         ph = {p: model.phase_ms(p) for p in phases if p != "allreduce"}
         ph["allreduce"] = all_reduce.last_ms() if all_reduce is not None else 0.0
         return res, ph

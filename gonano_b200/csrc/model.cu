@@ -611,16 +611,42 @@ int gn_model_optimizer_init(gn_model* m, const gn_optimizer_config* cfg) {
 }
 
 // Routing: model/optimizer.go:20-165 (sinkhorn = true).  Parameters are visited in name order; the updates are
-// independent of one another, so the order only fixes the launch sequence.
-int gn_model_optimizer_step(gn_model* m) {
-  GN_TRY(enter(m));
-  GN_REQUIRE(m->opt_ready, "gn_model_optimizer_step: call gn_model_optimizer_init first");
+// independent of one another, so the order only fixes the launch sequence.  With shard_count > 1 only the tensors
+// this shard owns are updated (ownership: greedy balance of an operation-count estimate, identical on every rank).
+namespace {
+std::vector<int> optimizer_owners(gn_model* m, int shard_count) {
+  const size_t n = m->params.size();
+  std::vector<int> owner(n, 0);
+  if (shard_count <= 1) return owner;
+  std::vector<std::pair<double, size_t>> cost(n);
+  for (size_t i = 0; i < n; ++i) {
+    const ParamInfo& pi = m->params[i];
+    const double elems = (double)pi.rows * pi.cols;
+    const bool sink = pi.name == "lm_head.weight" || pi.name == "transformer.wte.weight" || pi.name.rfind("value_embeds.", 0) == 0;
+    const bool matrix = pi.name.rfind("transformer.h.", 0) == 0;
+    // Muon: 5 iterations of three products + ~35 launches; Sinkhorn: 16 passes over the table; AdamW: nothing
+    const double c = sink ? 16.0 * elems : (matrix ? 30.0 * elems * std::min(pi.rows, pi.cols) / 400.0 + 4e6 : 1.0);
+    cost[i] = {c, i};
+  }
+  std::sort(cost.begin(), cost.end(), [](const std::pair<double, size_t>& a, const std::pair<double, size_t>& b) { return a.first != b.first ? a.first > b.first : a.second < b.second; });
+  std::vector<double> load(shard_count, 0.0);
+  for (auto& c : cost) {
+    int best = 0;
+    for (int r = 1; r < shard_count; ++r) if (load[r] < load[best]) best = r;
+    owner[c.second] = best; load[best] += c.first;
+  }
+  return owner;
+}
+
+int optimizer_run(gn_model* m, int shard, int shard_count) {
   cudaStream_t s = m->s();
   const gn_optimizer_config& c = m->opt_cfg;
-  GN_CUDA(cudaEventRecord(m->ev[0], s));
   ++m->opt_steps;
   const float dscale = (float)std::pow((double)m->d / 768.0, -0.5);   // model/optimizer.go:108
-  for (const ParamInfo& pi : m->params) {
+  const std::vector<int> owner = optimizer_owners(m, shard_count);
+  for (size_t i = 0; i < m->params.size(); ++i) {
+    if (owner[i] != shard) continue;
+    const ParamInfo& pi = m->params[i];
     float* p = m->p(pi.offset); float* g = m->g(pi.offset);
     float* mo = m->opt_mom.f() + pi.offset; float* se = m->opt_second.f() + pi.offset;
     const int64_t n = (int64_t)pi.rows * pi.cols;
@@ -634,6 +660,26 @@ int gn_model_optimizer_step(gn_model* m) {
     else if (pi.name == "smear_gate.weight" || pi.name == "smear_lambda" || pi.name == "backout_lambda") GN_TRY(adam(0.2f, 0.8f, 0.95f, 0.0f));
     else GN_TRY(muon_launch(p, g, mo, se, pi.rows, pi.cols, c.matrix_lr * c.lr_mult, 0.95f, 5, 0.9f, c.weight_decay, m->opt_ws.p, m->ctx->gemm_kind, s));
   }
+  if (shard_count > 1) {
+    // Exchange form: the gradient buffer becomes "my updated tensors, zero elsewhere"; a SUM all-reduce over it then
+    // yields every updated tensor on every rank exactly (x + 0 + ... + 0), and gn_model_optimizer_finish installs it.
+    for (size_t i = 0; i < m->params.size(); ++i) {
+      const ParamInfo& pi = m->params[i];
+      const size_t bytes = sizeof(float) * (size_t)pi.rows * pi.cols;
+      if (owner[i] == shard) GN_CUDA(cudaMemcpyAsync(m->g(pi.offset), m->p(pi.offset), bytes, cudaMemcpyDeviceToDevice, s));
+      else GN_CUDA(cudaMemsetAsync(m->g(pi.offset), 0, bytes, s));
+    }
+  }
+  return GN_OK;
+}
+}  // namespace
+
+int gn_model_optimizer_step(gn_model* m) {
+  GN_TRY(enter(m));
+  GN_REQUIRE(m->opt_ready, "gn_model_optimizer_step: call gn_model_optimizer_init first");
+  cudaStream_t s = m->s();
+  GN_CUDA(cudaEventRecord(m->ev[0], s));
+  GN_TRY(optimizer_run(m, 0, 1));
   GN_CUDA(cudaMemsetAsync(m->G.p, 0, sizeof(float) * m->total, s));   // ZeroGrad (trainer/rl.go:66)
   GN_CUDA(cudaMemsetAsync(m->sacc.p, 0, sizeof(double) * (2 * m->L + 2), s));
   GN_CUDA(cudaEventRecord(m->ev[1], s));
@@ -642,6 +688,36 @@ int gn_model_optimizer_step(gn_model* m) {
   float ms = 0;
   GN_CUDA(cudaEventElapsedTime(&ms, m->ev[0], m->ev[1])); m->phase_ms["optimizer"] = ms;
   return gemm_check_error(s);
+}
+
+int gn_model_optimizer_step_shard(gn_model* m, int shard, int shard_count) {
+  GN_TRY(enter(m));
+  GN_REQUIRE(m->opt_ready, "gn_model_optimizer_step_shard: call gn_model_optimizer_init first");
+  GN_REQUIRE(shard_count >= 1 && shard >= 0 && shard < shard_count, "gn_model_optimizer_step_shard: shard %d of %d", shard, shard_count);
+  cudaStream_t s = m->s();
+  GN_CUDA(cudaEventRecord(m->ev[0], s));
+  GN_TRY(optimizer_run(m, shard, shard_count));
+  GN_CUDA(cudaEventRecord(m->ev[1], s));
+  GN_CUDA(cudaStreamSynchronize(s));
+  float ms = 0;
+  GN_CUDA(cudaEventElapsedTime(&ms, m->ev[0], m->ev[1])); m->phase_ms["optimizer"] = ms;
+  return gemm_check_error(s);
+}
+
+int gn_model_optimizer_finish(gn_model* m) {
+  GN_TRY(enter(m));
+  cudaStream_t s = m->s();
+  GN_CUDA(cudaEventRecord(m->ev[0], s));
+  for (const ParamInfo& pi : m->params)
+    GN_CUDA(cudaMemcpyAsync(m->p(pi.offset), m->g(pi.offset), sizeof(float) * (size_t)pi.rows * pi.cols, cudaMemcpyDeviceToDevice, s));
+  GN_CUDA(cudaMemsetAsync(m->G.p, 0, sizeof(float) * m->total, s));   // ZeroGrad (trainer/rl.go:66)
+  GN_CUDA(cudaMemsetAsync(m->sacc.p, 0, sizeof(double) * (2 * m->L + 2), s));
+  GN_CUDA(cudaEventRecord(m->ev[1], s));
+  m->weights_dirty = true;
+  GN_CUDA(cudaStreamSynchronize(s));
+  float ms = 0;
+  GN_CUDA(cudaEventElapsedTime(&ms, m->ev[0], m->ev[1])); m->phase_ms["optimizer"] += ms;
+  return GN_OK;
 }
 
 int gn_generate_batch(gn_model* m, const int32_t* prompts, int P, int plen, int G, int max_tokens, float temperature, int top_k, const uint64_t* seeds,

@@ -59,23 +59,25 @@ class GradAllReduce:
         self.tensor = device_tensor(address, count, device)
         self.stream = stream
         self.bytes = count * 4
-        self._start = torch.cuda.Event(enable_timing=True)
-        self._end = torch.cuda.Event(enable_timing=True)
-        self._timed = False
+        self._pending = []   # (start, end) events of the calls since the last last_ms()
 
     def __call__(self, model=None):
+        start, end = self.torch.cuda.Event(enable_timing=True), self.torch.cuda.Event(enable_timing=True)
         with self.torch.cuda.stream(self.stream):
-            self._start.record(self.stream)
+            start.record(self.stream)
             all_reduce_sum(self.tensor)
-            self._end.record(self.stream)
-        self._timed = True
+            end.record(self.stream)
+        self._pending.append((start, end))
 
     def last_ms(self) -> float:
-        """Device time of the last all-reduce (includes waiting for the slowest rank)."""
-        if not self._timed:
-            return 0.0
-        self._end.synchronize()
-        return float(self._start.elapsed_time(self._end))
+        """Device time of the all-reduces issued since the previous call of this method (each includes waiting
+        for the slowest rank); a step with a sharded optimizer issues two."""
+        total = 0.0
+        for start, end in self._pending:
+            end.synchronize()
+            total += float(start.elapsed_time(end))
+        self._pending = []
+        return total
 
 
 def global_max_len(local_max_len: int) -> int:

@@ -165,6 +165,13 @@ class Model:
         """optimizer.Step() then ZeroGrad() (trainer/rl.go:65-66)."""
         check(self.lib.gn_model_optimizer_step(self.h))
 
+    def optimizer_step_shard(self, shard, shard_count):
+        """Data parallel: update only this shard's tensors and stage them in the gradient buffer for one more SUM all-reduce."""
+        check(self.lib.gn_model_optimizer_step_shard(self.h, shard, shard_count))
+
+    def optimizer_finish(self):
+        check(self.lib.gn_model_optimizer_finish(self.h))
+
     def policy_gradient_step(self, inputs, targets, advantages, norm, rows_per_pass=0, taps=False):
         inputs, targets, advantages = _i32(inputs), _i32(targets), _f32(advantages)
         B, T = inputs.shape
@@ -214,11 +221,12 @@ class RLStepResult:
 
 
 def rl_step(model: Model, prompts, group, max_tokens, temperature, top_k, seeds, reward_fn, advantage_mode=0, rows_per_pass=0,
-            norm=None, all_reduce=None, max_len_fn=None, optimizer=False) -> RLStepResult:
+            norm=None, all_reduce=None, max_len_fn=None, optimizer=False, shard=None) -> RLStepResult:
     """One RL step the way cmd/chat_rl runs it (main.go:87-184):
     rollout -> rewards -> group-relative advantages -> padded batch -> PolicyGradientStep
     -> gradient all-reduce (``all_reduce(model)``, when data parallel) -> optimizer step and
-    ZeroGrad when ``optimizer`` (trainer/rl.go:62-67; needs ``model.optimizer_init()``).  ``reward_fn(tokens,
+    ZeroGrad when ``optimizer`` (trainer/rl.go:62-67; needs ``model.optimizer_init()``; ``shard=(rank, world)``
+    splits the optimizer's tensors over the ranks).  ``reward_fn(tokens,
     lengths)`` returns one reward per rollout.  ``norm`` defaults to the padded length
     (main.go:183).  ``max_len_fn(local_max_len)`` returns the length every rank pads to."""
     from .backend import group_advantage
@@ -234,5 +242,11 @@ def rl_step(model: Model, prompts, group, max_tokens, temperature, top_k, seeds,
     if all_reduce is not None:
         all_reduce(model)
     if optimizer:
-        model.optimizer_step()
+        if shard is not None and all_reduce is not None and shard[1] > 1:
+            # each rank updates the tensors it owns; a second all-reduce of the same buffer distributes them (exactly)
+            model.optimizer_step_shard(shard[0], shard[1])
+            all_reduce(model)
+            model.optimizer_finish()
+        else:
+            model.optimizer_step()
     return RLStepResult(loss, int(lengths.sum()), len(lengths), max_len, steps, tokens, lengths, adv)

@@ -311,6 +311,14 @@ typedef struct gn_optimizer_config {
 int gn_model_optimizer_init(gn_model* model, const gn_optimizer_config* config);
 /* optimizer.Step() then ZeroGrad() on the model's gradient buffer (after the all-reduce in a data-parallel job). */
 int gn_model_optimizer_step(gn_model* model);
+/* Data-parallel form (the reference has no counterpart: it is single-process).  Every rank calls
+ * gn_model_optimizer_step_shard(model, rank, world) after the gradient all-reduce: it updates only the tensors the
+ * shard owns (the same deterministic assignment on every rank) and turns the gradient buffer into "my updated tensors,
+ * zero elsewhere".  The caller then SUM-all-reduces gn_model_grad_buffer once more and calls gn_model_optimizer_finish,
+ * which installs the reduced buffer as the parameters and zeroes the gradients.  The result equals
+ * gn_model_optimizer_step bit for bit. */
+int gn_model_optimizer_step_shard(gn_model* model, int shard, int shard_count);
+int gn_model_optimizer_finish(gn_model* model);
 
 #ifdef __cplusplus
 }

@@ -156,3 +156,43 @@ def test_rl_step_with_optimizer_end_to_end(oracle):
         else:
             assert upd_err(got, want, before[n]) <= 5e-3, n
     gm.close(); ctx.close()
+
+
+def test_sharded_optimizer_equals_whole_step():
+    """Two shards emulated on one GPU with two replicas: each updates the tensors it owns and stages them; the SUM of
+    the two staged buffers (what the second all-reduce produces) installed by optimizer_finish equals the un-sharded
+    step bit for bit, and between them the shards own every tensor exactly once."""
+    from gonano_b200.session import Context, Model
+    cfg = synthetic.dense_config("c1")
+    ctx = Context(0)
+    whole, a, b = Model(ctx, **cfg), Model(ctx, **cfg), Model(ctx, **cfg)
+    rng = np.random.default_rng(11)
+    grads = {}
+    for pname, value in synthetic.fill_weights(whole.names, whole.shape, 4, std=0.05):
+        grads[pname] = (rng.standard_normal(value.size) * 0.01).astype(np.float32)
+        for m in (whole, a, b):
+            m.upload(pname, value)
+    for m in (whole, a, b):
+        m.optimizer_init()
+    for step in range(2):
+        for pname in whole.names:
+            g = grads[pname] * np.float32(1 + step)
+            for m in (whole, a, b):
+                m.upload_grad(pname, g)
+        whole.optimizer_step()
+        a.optimizer_step_shard(0, 2); b.optimizer_step_shard(1, 2)
+        owned_once = True
+        for pname in whole.names:
+            ga, gb = a.grad(pname), b.grad(pname)
+            owned_once &= not (np.any(ga) and np.any(gb))
+            total = ga + gb
+            a.upload_grad(pname, total); b.upload_grad(pname, total)
+        assert owned_once
+        a.optimizer_finish(); b.optimizer_finish()
+        for pname in whole.names:
+            want = whole.download(pname)
+            assert np.array_equal(a.download(pname), want) and np.array_equal(b.download(pname), want), (step, pname)
+            assert not np.any(a.grad(pname))
+    for m in (whole, a, b):
+        m.close()
+    ctx.close()
