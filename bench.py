@@ -210,7 +210,21 @@ def kernel_rooflines(ctx, pk, tf32_tflops):
     hbm_entry("sampler", [512, 32768, 50], 4.0 * 512 * 32768, "d12 decode step, 512 rows")
     r, hq, hkv, d, c = 512, 6, 2, 128, 320
     hbm_entry("decode_attention", [r, hq, hkv, d, c], r * (2.0 * hkv * d * 4 * c + 2 * hq * d * 4), "d12 one layer, 512 rows, context 320")
+    # the same layer with the prompt's 128 positions read once per group of 8 rows: the algorithmic bytes drop
+    hbm_entry("decode_attention", [r, hq, hkv, d, c, 8, 128], (r / 8) * 2.0 * hkv * d * 4 * 128 + r * (2.0 * hkv * d * 4 * (c - 128) + 2 * hq * d * 4),
+              "d12 one layer, 512 rows, context 320, shared 128-token prefix per group of 8")
     hbm_entry("advantage", [64, 8], 8.0 * 512, "64 groups of 8 (latency-bound)")
+
+    # attention of one training pass (32 x 383 tokens, causal): 2 products forward, 7 backward (S and dP are recomputed
+    # in both backward kernels), each 2*T^2/2*D flop per (row, head), on the legacy mma.sync pipe in 3xTF32
+    B, T = 32, 383
+    unit = B * hq * (T * (T + 1) / 2.0) * d * 2.0
+    for name, products, label in (("attention_fwd", 2, "forward"), ("attention_bwd", 7, "backward (dK/dV + dQ)")):
+        ms = ctx.profile_kernel(name, [B, hq, hkv, d, T], 10)
+        tf = products * unit / (ms * 1e-3) / 1e12
+        out.append({"kernel": name, "workload": f"d12 one layer of a training pass, {B} x {T} tokens, {label}", "bound": "tensor", "ms": ms,
+                    "achieved": tf, "peak": gemm_peak, "unit": "TFLOP/s", "frac": tf / gemm_peak if gemm_peak else None,
+                    "note": "mma.sync m16n8k8 tf32; a dense loop of that instruction reaches 278/3 = 92 TFLOP/s useful on this GPU"})
     return out
 
 
