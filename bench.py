@@ -43,6 +43,7 @@ def emit(line: dict) -> None:
         os.write(_STDOUT_FD, data)
 
 
+GEMM_TRAFFIC_BYTES = 282038272   # 120.4 MB read + 161.7 MB written: ncu capture of `profile_cli kernel gemm_nt 16384 3072 768` (profiles/gemm_tc_timeline.md)
 WORKLOAD = dict(name="d12", n_prompts=64, prompt_len=128, group=8, max_tokens=256, temperature=1.0, top_k=50, seed=0)
 METRIC, UNIT = "rl_steps_per_s_d12", "steps/s"
 
@@ -315,6 +316,8 @@ def run_ours(args):
     # only as a roofline denominator): 8192^3, best of 10.
     tf32 = None
     try:
+        if args.lean:
+            raise RuntimeError("lean run")
         torch.backends.cuda.matmul.allow_tf32 = True
         a = torch.randn(8192, 8192, device=f"cuda:{local}"); b = torch.randn(8192, 8192, device=f"cuda:{local}")
         best = 1e9
@@ -326,12 +329,14 @@ def run_ours(args):
         del a, b
     except Exception:
         pass
-    kernels = kernel_rooflines(ctx, pk, tf32)
+    kernels = kernel_rooflines(ctx, pk, tf32) if not args.lean else [{"kernel": "gemm_nt", "workload": "not measured (--lean)"}]
     dominant = dict(kernels[0])
-    dominant["traffic"] = None
+    # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this product under ncu (profiles/gemm_tc_timeline.md);
+    # algorithmic: operands hi+lo 2 * 4 * (M*K + N*K) = 119.5 MB read, output 201.3 MB written
+    dominant["traffic"] = GEMM_TRAFFIC_BYTES
     dominant["peak_source"] = f"TF32 8192^3 torch.matmul measured in this run ({tf32:.1f} TFLOP/s) / 3 for the 3xTF32 split" if tf32 else "unavailable"
     cpu = None
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and not args.lean:
         try:
             cpu = cpu_baseline()
         except Exception as exc:  # the oracle is test infrastructure: its absence must not hide the GPU number
@@ -381,6 +386,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--lean", action="store_true", help="steps only: no per-kernel microbenchmarks, TF32 peak or CPU baseline (for ncu launch lists)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
