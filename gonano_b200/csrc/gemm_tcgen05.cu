@@ -123,10 +123,20 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
   d |= (uint64_t)2 << 61;
   return d;
 }
+// The same for an operand stored with its M (or N) index contiguous ("MN-major": the operand of a product A^T B or
+// A B whose source is row-major [K, MN]).  For 32-bit elements the tensor core wants the 128-byte swizzle with
+// 32-byte atoms (layout type 1; the TMA mode of the same name): rows of 128 bytes = 32 consecutive MN elements,
+// one row per k, a 128 (MN) x 32 (K) tile = four 2-D TMA boxes [32 MN x 32 K] of the row-major source, 4096 bytes
+// apart.  Leading offset = distance between the MN groups (4096 bytes), stride offset 512 bytes (the 4-row swizzle
+// period), and one instruction's K = 8 advances the start address by 8 rows = 1024 bytes.  This form was found by
+// comparing a 128 x 128 x 64 product against float64 over a handful of candidates; only this one agreed (7e-7).
+constexpr uint64_t kMnDesc = ((uint64_t)(4096 >> 4) << 16) | ((uint64_t)(512 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)1 << 61);
+constexpr uint32_t kMnKStep = 1024 >> 4;
 // Instruction descriptor for kind::tf32, float32 accumulate, both operands K-major:
 // [4,6) D format 1 = F32, [7,10) A format 2 = TF32, [10,13) B format 2, [17,23) N>>3, [24,29) M>>4.
-__device__ __forceinline__ uint32_t instr_desc_tf32(int m, int n) {
-  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+// Bits 15 / 16 select the MN-major form of A / B.
+__device__ __forceinline__ uint32_t instr_desc_tf32(int m, int n, int a_mn = 0, int b_mn = 0) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 struct TcEpilogue {
@@ -139,6 +149,7 @@ struct TcEpilogue {
   // Grouped product (expert-major rows): group g owns group_counts[g] consecutive rows of A and C and the
   // weight rows [g * N, (g + 1) * N) of B; blockIdx.y enumerates (group, 128-row tile) pairs in group order.
   const int32_t* group_counts; int groups;
+  int a_mn, b_mn;   // operand arrives MN-major (tensor map over a row-major [K, MN] source) instead of K-major
 };
 
 #ifdef GN_TC_TRACE
@@ -245,16 +256,32 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
         const uint32_t st = base + (uint32_t)s * S::STAGE_BYTES;
         if (kb < 256) TC_TRACE(kb);
         mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
-        tma_load_2d(st, &tmAh, full_bar(s), (kb0 + kb) * TBK, m0);
-        tma_load_2d(st + S::A_BYTES, &tmAl, full_bar(s), (kb0 + kb) * TBK, m0);
-        tma_load_2d(st + 2 * S::A_BYTES, &tmBh, full_bar(s), (kb0 + kb) * TBK, b_row0);
-        tma_load_2d(st + 2 * S::A_BYTES + S::B_BYTES, &tmBl, full_bar(s), (kb0 + kb) * TBK, b_row0);
+        if (ep.a_mn) {
+#pragma unroll
+          for (int j = 0; j < TBM / 32; ++j) {
+            tma_load_2d(st + j * 4096, &tmAh, full_bar(s), m0 + 32 * j, (kb0 + kb) * TBK);
+            tma_load_2d(st + S::A_BYTES + j * 4096, &tmAl, full_bar(s), m0 + 32 * j, (kb0 + kb) * TBK);
+          }
+        } else {
+          tma_load_2d(st, &tmAh, full_bar(s), (kb0 + kb) * TBK, m0);
+          tma_load_2d(st + S::A_BYTES, &tmAl, full_bar(s), (kb0 + kb) * TBK, m0);
+        }
+        if (ep.b_mn) {
+#pragma unroll
+          for (int j = 0; j < BN / 32; ++j) {
+            tma_load_2d(st + 2 * S::A_BYTES + j * 4096, &tmBh, full_bar(s), b_row0 + 32 * j, (kb0 + kb) * TBK);
+            tma_load_2d(st + 2 * S::A_BYTES + S::B_BYTES + j * 4096, &tmBl, full_bar(s), b_row0 + 32 * j, (kb0 + kb) * TBK);
+          }
+        } else {
+          tma_load_2d(st + 2 * S::A_BYTES, &tmBh, full_bar(s), (kb0 + kb) * TBK, b_row0);
+          tma_load_2d(st + 2 * S::A_BYTES + S::B_BYTES, &tmBl, full_bar(s), (kb0 + kb) * TBK, b_row0);
+        }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = instr_desc_tf32(TBM, BN);
+      const uint32_t idesc = instr_desc_tf32(TBM, BN, ep.a_mn, ep.b_mn);
       for (int c = 0; c < nchunks && !failed; ++c) {
         const int buf = c & 1;
         // the epilogue must have drained this buffer's previous chunk
@@ -268,15 +295,20 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
           tc_fence_after();
           if (kb < 256) TC_TRACE(256 + kb);
           const uint32_t st = base + (uint32_t)s * S::STAGE_BYTES;
-          const uint64_t ah = smem_desc_sw128(st), al = smem_desc_sw128(st + S::A_BYTES);
-          const uint64_t bh = smem_desc_sw128(st + 2 * S::A_BYTES), bl = smem_desc_sw128(st + 2 * S::A_BYTES + S::B_BYTES);
+          auto mn_desc = [&](uint32_t addr) { return kMnDesc | (uint64_t)((addr & 0x3FFFFu) >> 4); };
+          const uint64_t ah = ep.a_mn ? mn_desc(st) : smem_desc_sw128(st);
+          const uint64_t al = ep.a_mn ? mn_desc(st + S::A_BYTES) : smem_desc_sw128(st + S::A_BYTES);
+          const uint64_t bh = ep.b_mn ? mn_desc(st + 2 * S::A_BYTES) : smem_desc_sw128(st + 2 * S::A_BYTES);
+          const uint64_t bl = ep.b_mn ? mn_desc(st + 2 * S::A_BYTES + S::B_BYTES) : smem_desc_sw128(st + 2 * S::A_BYTES + S::B_BYTES);
+          // advancing by one instruction's K = 8: K-major +32 bytes inside the 128-byte swizzle row (+2 in the address
+          // field); MN-major the next k-group of 8, 1024 bytes on (+64)
+          const uint64_t a_step = ep.a_mn ? kMnKStep : (uint64_t)((UMMA_K * 4) >> 4), b_step = ep.b_mn ? kMnKStep : (uint64_t)((UMMA_K * 4) >> 4);
 #pragma unroll
           for (int k = 0; k < TBK / UMMA_K; ++k) {
-            // advancing along K inside the 128-byte swizzle row: +32 bytes = +2 in the address field
-            const uint64_t adv = (uint64_t)((k * UMMA_K * 4) >> 4);
-            umma_tf32(d_tmem, al + adv, bh + adv, idesc, (kb > c * kChunkBlocks || k > 0) ? 1u : 0u);
-            umma_tf32(d_tmem, ah + adv, bl + adv, idesc, 1u);
-            umma_tf32(d_tmem, ah + adv, bh + adv, idesc, 1u);
+            const uint64_t aa = a_step * (uint64_t)k, ba = b_step * (uint64_t)k;
+            umma_tf32(d_tmem, al + aa, bh + ba, idesc, (kb > c * kChunkBlocks || k > 0) ? 1u : 0u);
+            umma_tf32(d_tmem, ah + aa, bl + ba, idesc, 1u);
+            umma_tf32(d_tmem, ah + aa, bh + ba, idesc, 1u);
           }
           umma_commit(empty_bar(s));   // the stage is free once these MMAs have read it
           if (kb < 256) TC_TRACE(512 + kb);
@@ -426,8 +458,11 @@ EncodeTiledFn g_encode = nullptr;
 int* g_err_flag = nullptr;
 long long* g_trace = nullptr;   // device buffer of 1024 slots (GN_TC_TRACE builds)
 std::mutex g_mu;
+// GN_TC_MN=0 keeps the transposing operand split for products whose operands are stored [K, M] / [K, N].
+const bool g_allow_mn = [] { const char* e = getenv("GN_TC_MN"); return !(e && e[0] == '0'); }();
 
-struct SplitBuf { float* hi = nullptr; float* lo = nullptr; size_t floats = 0; int64_t ld = 0; bool fresh = true; };
+
+struct SplitBuf { float* hi = nullptr; float* lo = nullptr; size_t floats = 0; int64_t ld = 0; bool fresh = true; bool mn = false; };
 // Cached splits of parameter tensors: key = (pointer, rows, cols, transposed).
 std::map<std::tuple<const void*, int64_t, int64_t, int>, SplitBuf> g_static;
 SplitBuf g_dyn[2];  // scratch for the activation operands (A and B of the current product)
@@ -455,6 +490,18 @@ int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t k, int64
   return GN_OK;
 }
 
+// 2-D map over a row-major [k, mn] array (pitch ld floats): a box [32 mn x 32 k] is one MN group of the MN-major tile above.
+int make_map_mn(CUtensorMap* map, const float* base, int64_t mn, int64_t k, int64_t ld) {
+  cuuint64_t dims[2] = {(cuuint64_t)mn, (cuuint64_t)k};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
+  cuuint32_t box[2] = {32, (cuuint32_t)TBK};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (MN-major) failed with %d (mn %lld, k %lld, ld %lld)", (int)r, (long long)mn, (long long)k, (long long)ld); return GN_ERR_CUDA; }
+  return GN_OK;
+}
+
 int ensure_buf(SplitBuf& b, size_t floats) {
   if (floats <= b.floats) return GN_OK;
   if (b.hi) { cudaFree(b.hi); cudaFree(b.lo); b.hi = b.lo = nullptr; b.floats = 0; }
@@ -467,7 +514,20 @@ int ensure_buf(SplitBuf& b, size_t floats) {
 
 // Produces K-major hi/lo copies of an operand.  `rows` x `k` is the logical operand
 // (rows = M or N).  stored_transposed: the source is stored [k, rows] (pitch ld).
-int split_operand(const float* src, int64_t ld, int64_t rows, int64_t k, bool stored_transposed, bool is_static, int which, SplitBuf& out, cudaStream_t s) {
+int split_operand(const float* src, int64_t ld, int64_t rows, int64_t k, bool stored_transposed, bool is_static, int which, SplitBuf& out, cudaStream_t s,
+                  bool allow_mn = false) {
+  if (stored_transposed && allow_mn && !is_static && rows % 4 == 0 && ld % 4 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+    // The source is row-major [k, rows]: keep it that way (a plain split, no transpose) and let the tensor core read it MN-major.
+    SplitBuf* target = &g_dyn[which];
+    GN_TRY(ensure_buf(*target, (size_t)k * rows));
+    target->ld = rows; target->mn = true;
+    const int64_t total = k * (rows / 4);
+    const int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)kNumSM * 16);
+    split_kernel<<<std::max(blocks, 1), 256, 0, s>>>(src, ld, target->hi, target->lo, rows, k, (int)rows);
+    GN_LAUNCH_CHECK();
+    out = *target;
+    return GN_OK;
+  }
   const int64_t kp = (k + 3) / 4 * 4;
   auto key = std::make_tuple((const void*)src, rows, k, stored_transposed ? 1 : 0);
   SplitBuf buf;
@@ -480,7 +540,7 @@ int split_operand(const float* src, int64_t ld, int64_t rows, int64_t k, bool st
   }
   SplitBuf* target = is_static ? &buf : &g_dyn[which];
   GN_TRY(ensure_buf(*target, (size_t)rows * kp));
-  target->ld = kp;
+  target->ld = kp; target->mn = false;
   if (!stored_transposed) {
     int64_t total = rows * (k / 4);
     int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)kNumSM * 16);
@@ -536,10 +596,13 @@ int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int
     configured = true;
   }
   CUtensorMap mah, mal, mbh, mbl;
-  GN_TRY(make_map(&mah, a.hi, M, K, a.ld, TBM)); GN_TRY(make_map(&mal, a.lo, M, K, a.ld, TBM));
+  if (a.mn) { GN_TRY(make_map_mn(&mah, a.hi, M, K, a.ld)); GN_TRY(make_map_mn(&mal, a.lo, M, K, a.ld)); }
+  else { GN_TRY(make_map(&mah, a.hi, M, K, a.ld, TBM)); GN_TRY(make_map(&mal, a.lo, M, K, a.ld, TBM)); }
   const int brows = ep_in.groups > 0 ? ep_in.groups * N : N;
-  GN_TRY(make_map(&mbh, b.hi, brows, K, b.ld, BN)); GN_TRY(make_map(&mbl, b.lo, brows, K, b.ld, BN));
+  if (b.mn) { GN_TRY(make_map_mn(&mbh, b.hi, brows, K, b.ld)); GN_TRY(make_map_mn(&mbl, b.lo, brows, K, b.ld)); }
+  else { GN_TRY(make_map(&mbh, b.hi, brows, K, b.ld, BN)); GN_TRY(make_map(&mbl, b.lo, brows, K, b.ld, BN)); }
   TcEpilogue ep = ep_in;
+  ep.a_mn = a.mn ? 1 : 0; ep.b_mn = b.mn ? 1 : 0;
   if (splits > 1) {
     size_t need = (size_t)splits * M * N;
     if (need > g_splitk_floats) {
@@ -584,10 +647,10 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
   SplitBuf a, b;
   // A is logically [M, K]; stored transposed ([K, M]) when a_trans.
   if (g.a_hi && g.a_lo && !g.a_trans) { a.hi = const_cast<float*>(g.a_hi); a.lo = const_cast<float*>(g.a_lo); a.ld = g.lda; }   // split by the producer
-  else GN_TRY(split_operand(g.A, g.lda, g.M, g.K, g.a_trans != 0, g.a_static != 0, 0, a, s));
+  else GN_TRY(split_operand(g.A, g.lda, g.M, g.K, g.a_trans != 0, g.a_static != 0, 0, a, s, g_allow_mn));
   // B is logically [N, K]; stored that way when b_trans (weights [out, in]), else stored [K, N].
-  GN_TRY(split_operand(g.B, g.ldb, g.groups > 0 ? (int64_t)g.groups * g.N : g.N, g.K, g.b_trans == 0, g.b_static != 0, 1, b, s));
-  TcEpilogue ep{g.C, g.ldc, g.aux, g.ldaux, g.epilogue, g.scalar, 0, g.c_hi, g.c_lo, g_trace, g.group_counts, g.groups};
+  GN_TRY(split_operand(g.B, g.ldb, g.groups > 0 ? (int64_t)g.groups * g.N : g.N, g.K, g.b_trans == 0, g.b_static != 0, 1, b, s, g_allow_mn));
+  TcEpilogue ep{g.C, g.ldc, g.aux, g.ldaux, g.epilogue, g.scalar, 0, g.c_hi, g.c_lo, g_trace, g.group_counts, g.groups, 0, 0};
   if (g.groups > 0) return launch_tc<128, 3>(a, b, ep, g.M, g.N, g.K, 1, s, nullptr);
   // Filling the machine when the output has few tiles (the rollout's products have 512 rows):
   // the K loop is split over gridDim.z so that about one CTA per SM runs, each writing a partial
