@@ -170,6 +170,9 @@ struct GemmArgs {
   int a_static = 0, b_static = 0;  // operand is a parameter tensor: its tensor-core split may be cached
   // Tensor-core path only: A already split by its producer (hi = tf32(x), lo = tf32(x - hi)), pitch lda.
   const float* a_hi = nullptr; const float* a_lo = nullptr;
+  // Tensor-core path only: A (same pointer, pitch and shape, possibly through the other a_trans) is unchanged since the
+  // previous product issued on this stream, so its split may be reused (dY feeds the weight gradient, then the data gradient).
+  int a_reuse = 0;
   // Tensor-core path only: also write the split of the output (pitch ldc) for the next product.
   float* c_hi = nullptr; float* c_lo = nullptr;
   // When set (epilogue must be EPI_STORE): the product may be left as split-K partial tiles for the

@@ -466,6 +466,7 @@ struct SplitBuf { float* hi = nullptr; float* lo = nullptr; size_t floats = 0; i
 // Cached splits of parameter tensors: key = (pointer, rows, cols, transposed).
 std::map<std::tuple<const void*, int64_t, int64_t, int>, SplitBuf> g_static;
 SplitBuf g_dyn[2];  // scratch for the activation operands (A and B of the current product)
+struct { const void* src = nullptr; int64_t ld = 0, rows = 0, cols = 0; bool valid = false; } g_last_a;   // what g_dyn[0] holds
 
 int ensure_init() {
   if (g_encode && g_err_flag) return GN_OK;
@@ -646,8 +647,18 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
   GN_TRY(ensure_init());
   SplitBuf a, b;
   // A is logically [M, K]; stored transposed ([K, M]) when a_trans.
+  // the source of A as stored: [src_rows, src_cols]
+  const int64_t src_rows = g.a_trans ? g.K : g.M, src_cols = g.a_trans ? g.M : g.K;
   if (g.a_hi && g.a_lo && !g.a_trans) { a.hi = const_cast<float*>(g.a_hi); a.lo = const_cast<float*>(g.a_lo); a.ld = g.lda; }   // split by the producer
-  else GN_TRY(split_operand(g.A, g.lda, g.M, g.K, g.a_trans != 0, g.a_static != 0, 0, a, s, g_allow_mn));
+  else if (g.a_reuse && g_last_a.valid && g_last_a.src == g.A && g_last_a.ld == g.lda && g_last_a.rows == src_rows && g_last_a.cols == src_cols &&
+           (!g.a_trans || g_allow_mn)) {
+    a = g_dyn[0]; a.ld = src_cols; a.mn = g.a_trans != 0;   // the plain split of the previous product, read K-major or MN-major
+  } else {
+    GN_TRY(split_operand(g.A, g.lda, g.M, g.K, g.a_trans != 0, g.a_static != 0, 0, a, s, g_allow_mn));
+    // a plain (untransposed) split with an unpadded pitch can serve the next product too
+    const bool plain = !g.a_static && src_cols % 4 == 0 && (g.a_trans ? a.mn : true);
+    g_last_a.valid = plain; g_last_a.src = g.A; g_last_a.ld = g.lda; g_last_a.rows = src_rows; g_last_a.cols = src_cols;
+  }
   // B is logically [N, K]; stored that way when b_trans (weights [out, in]), else stored [K, N].
   GN_TRY(split_operand(g.B, g.ldb, g.groups > 0 ? (int64_t)g.groups * g.N : g.N, g.K, g.b_trans == 0, g.b_static != 0, 1, b, s, g_allow_mn));
   TcEpilogue ep{g.C, g.ldc, g.aux, g.ldaux, g.epilogue, g.scalar, 0, g.c_hi, g.c_lo, g_trace, g.group_counts, g.groups, 0, 0};

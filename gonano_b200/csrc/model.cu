@@ -335,7 +335,7 @@ int backward_core(gn_model* m, FwdBufs& b, BwdBufs& w, const int32_t* ids, int B
   // lm_head: dW[:V] += dz^T y ; dy = dz W[:V]      (model/layers/linear.go:45-53)
   { GemmArgs g; g.A = DZ; g.lda = V; g.a_trans = 1; g.B = b.Y; g.ldb = d; g.b_trans = 0; g.C = m->g(m->off_lm); g.ldc = d; g.M = V; g.N = d; g.K = (int)rows;
     g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
-  { GemmArgs g; g.A = DZ; g.lda = V; g.B = m->p(m->off_lm); g.b_static = 1; g.ldb = d; g.b_trans = 0; g.C = w.DY; g.ldc = d; g.M = (int)rows; g.N = d; g.K = V; GN_TRY(gemm(m, g)); }
+  { GemmArgs g; g.A = DZ; g.lda = V; g.a_reuse = 1; g.B = m->p(m->off_lm); g.b_static = 1; g.ldb = d; g.b_trans = 0; g.C = w.DY; g.ldc = d; g.M = (int)rows; g.N = d; g.K = V; GN_TRY(gemm(m, g)); }
   GN_TRY(rmsnorm_backward_launch(w.DFP, b.FP, w.DY, nullptr, rows, d, kNormEps, s));
   const float* backout = b.layers[L / 2].XOUT;
   GN_TRY(dot_accumulate_launch(w.DFP, backout, n, -1.0, sacc + 2 * L + 1, s));   // d lambda_b (train_transformer.go:181-190)
@@ -353,16 +353,16 @@ int backward_core(gn_model* m, FwdBufs& b, BwdBufs& w, const int32_t* ids, int B
     // ---- MLP backward (model/train.go:505-514)
     { GemmArgs g; g.A = dout; g.lda = d; g.a_trans = 1; g.B = sv.HID; g.ldb = 4 * d; g.C = m->g(o.mproj); g.ldc = 4 * d; g.M = d; g.N = 4 * d; g.K = (int)rows;
       g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
-    { GemmArgs g; g.A = dout; g.lda = d; g.B = m->p(o.mproj); g.b_static = 1; g.ldb = 4 * d; g.C = w.DU; g.ldc = 4 * d; g.M = (int)rows; g.N = 4 * d; g.K = d;
+    { GemmArgs g; g.A = dout; g.lda = d; g.a_reuse = 1; g.B = m->p(o.mproj); g.b_static = 1; g.ldb = 4 * d; g.C = w.DU; g.ldc = 4 * d; g.M = (int)rows; g.N = 4 * d; g.K = d;
       g.epilogue = EPI_RELU2_BWD; g.aux = sv.U; g.ldaux = 4 * d; GN_TRY(gemm(m, g)); }
     { GemmArgs g; g.A = w.DU; g.lda = 4 * d; g.a_trans = 1; g.B = sv.M; g.ldb = d; g.C = m->g(o.fc); g.ldc = d; g.M = 4 * d; g.N = d; g.K = (int)rows;
       g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
-    { GemmArgs g; g.A = w.DU; g.lda = 4 * d; g.B = m->p(o.fc); g.b_static = 1; g.ldb = d; g.C = w.DM; g.ldc = d; g.M = (int)rows; g.N = d; g.K = 4 * d; GN_TRY(gemm(m, g)); }
+    { GemmArgs g; g.A = w.DU; g.lda = 4 * d; g.a_reuse = 1; g.B = m->p(o.fc); g.b_static = 1; g.ldb = d; g.C = w.DM; g.ldc = d; g.M = (int)rows; g.N = d; g.K = 4 * d; GN_TRY(gemm(m, g)); }
     GN_TRY(rmsnorm_backward_launch(w.DMID, sv.MID, w.DM, dout, rows, d, kNormEps, s));
     // ---- attention backward (model/train.go:198-427)
     { GemmArgs g; g.A = w.DMID; g.lda = d; g.a_trans = 1; g.B = sv.O; g.ldb = (int64_t)Hq * D; g.C = m->g(o.proj); g.ldc = (int64_t)Hq * D; g.M = d; g.N = Hq * D; g.K = (int)rows;
       g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
-    { GemmArgs g; g.A = w.DMID; g.lda = d; g.B = m->p(o.proj); g.b_static = 1; g.ldb = (int64_t)Hq * D; g.C = w.DO; g.ldc = (int64_t)Hq * D; g.M = (int)rows; g.N = Hq * D; g.K = d; GN_TRY(gemm(m, g)); }
+    { GemmArgs g; g.A = w.DMID; g.lda = d; g.a_reuse = 1; g.B = m->p(o.proj); g.b_static = 1; g.ldb = (int64_t)Hq * D; g.C = w.DO; g.ldc = (int64_t)Hq * D; g.M = (int)rows; g.N = Hq * D; g.K = d; GN_TRY(gemm(m, g)); }
     AttnShape sh;
     sh.B = B; sh.Hq = Hq; sh.Hkv = Hkv; sh.D = D; sh.Tq = T; sh.Tk = T;
     sh.q_bstride = (int64_t)T * W; sh.q_tstride = W; sh.kv_bstride = (int64_t)T * W; sh.kv_tstride = W; sh.kv_hstride = D;
@@ -376,7 +376,7 @@ int backward_core(gn_model* m, FwdBufs& b, BwdBufs& w, const int32_t* ids, int B
     GN_TRY(qkv_post_backward_launch(qb, s));
     { GemmArgs g; g.A = w.DQKV; g.lda = W; g.a_trans = 1; g.B = sv.H; g.ldb = d; g.C = m->g(o.qkv); g.ldc = d; g.M = W; g.N = d; g.K = (int)rows;
       g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
-    { GemmArgs g; g.A = w.DQKV; g.lda = W; g.B = m->p(o.qkv); g.b_static = 1; g.ldb = d; g.C = w.DH; g.ldc = d; g.M = (int)rows; g.N = d; g.K = W; GN_TRY(gemm(m, g)); }
+    { GemmArgs g; g.A = w.DQKV; g.lda = W; g.a_reuse = 1; g.B = m->p(o.qkv); g.b_static = 1; g.ldb = d; g.C = w.DH; g.ldc = d; g.M = (int)rows; g.N = d; g.K = W; GN_TRY(gemm(m, g)); }
     if (o.has_ve) GN_TRY(ve_gate_backward_launch(w.DPRE, sv.H, m->p(o.ve_gate), m->g(o.ve_gate), w.DH, rows, Hkv, d, s));
     GN_TRY(rmsnorm_backward_launch(w.DXIN, sv.Xin, w.DH, w.DMID, rows, d, kNormEps, s));
     // ---- residual mix (model/train_transformer.go:218-242)
