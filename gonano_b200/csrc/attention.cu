@@ -914,6 +914,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restric
                                                           const int32_t* __restrict__ ctx_len, int Hq, int Hkv, int D, int window, float* __restrict__ out,
                                                           int64_t o_rstride, float* __restrict__ part_acc, float* __restrict__ part_ms, int splits,
                                                           float* __restrict__ out_hi, float* __restrict__ out_lo, int kmin, int slot0, int nslots) {
+  pdl_trigger();
   // DP = head_dim rounded up to a multiple of 32; channels >= D are zero padding.
   // Keys below kmin belong to the shared-prefix kernel; this kernel's partial results then go to
   // slots slot0 .. slot0 + splits - 1 of nslots (nslots == splits and slot0 == 0 without a prefix pass).
@@ -1018,6 +1019,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restric
 }
 __global__ void __launch_bounds__(128) attn_decode_combine_kernel(const float* part_acc, const float* part_ms, int splits, int Hq, int D, float* out, int64_t o_rstride,
                                                                   float* out_hi, float* out_lo) {
+  pdl_trigger();
   int row = blockIdx.x / Hq, hq = blockIdx.x % Hq;
   int64_t base = ((int64_t)row * Hq + hq) * splits;
   float gm = -INFINITY;

@@ -117,6 +117,7 @@ __device__ __forceinline__ bool masked(int qpos, int kj, int window, const int32
 // CTA = 64 queries of one (batch, head); 64-key tiles; later (heavier) query tiles are scheduled first.
 __global__ void __launch_bounds__(NTH, 2) attn_mma_fwd_kernel(AttnShape sh, const float* __restrict__ q, const float* __restrict__ k,
                                                               const float* __restrict__ v, float* __restrict__ out, float* __restrict__ lse) {
+  pdl_trigger();
   constexpr int BQ = 64, BKV = 64;
   extern __shared__ __align__(16) float smem[];
   float* Qs = smem; float* Ks = Qs + BQ * LD; float* Vs = Ks + BKV * LD;

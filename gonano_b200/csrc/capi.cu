@@ -64,7 +64,10 @@ int gemm_dispatch(const GemmArgs& a, int kind, cudaStream_t s) {
 #endif
   (void)kind;
   if (a.leave) *a.leave = Partials{a.C, 1, 0, a.ldc};
-  return gemm_simt(a, s);
+  GN_TRY(gemm_simt(a, s));
+  // the caller asked for the output's tf32 split (the tensor-core epilogue writes it; here it is a pass of its own)
+  if (a.c_hi && a.c_lo) GN_TRY(split_matrix_launch(a.C, a.c_hi, a.c_lo, a.M, a.N, a.ldc, s));
+  return GN_OK;
 }
 
 int gemm_grouped_dispatch(const GemmArgs& a, int kind, cudaStream_t s) {

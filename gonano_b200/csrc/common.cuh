@@ -106,6 +106,13 @@ __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __ex
 // (kernels/scalar/elementwise.go:146-150); used where a gate decides values.
 __device__ __forceinline__ float sigmoid_exact(float x) { return (float)(1.0 / (1.0 + exp((double)(-x)))); }
 
+// Programmatic dependent launch.  A kernel that feeds a product calls pdl_trigger() first thing: the product's grid
+// may then be scheduled while this one still runs, and sets up (barriers, tensor memory, descriptors) in its shadow.
+// The product calls pdl_wait() before it touches global memory: it returns once the triggering grid has completed
+// and its writes are visible.  Both are no-ops when the next / this launch does not carry the attribute.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // hi = tf32(x) (round to nearest), lo = tf32(x - hi): the operand form of the 3xTF32 products.
 __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
   uint32_t h, l;
@@ -173,6 +180,8 @@ struct GemmArgs {
   // Tensor-core path only: A (same pointer, pitch and shape, possibly through the other a_trans) is unchanged since the
   // previous product issued on this stream, so its split may be reused (dY feeds the weight gradient, then the data gradient).
   int a_reuse = 0;
+  // Tensor-core path only: B stored [K, N] (b_trans = 0) already split by its producer, pitch ldb (read MN-major).
+  const float* b_hi = nullptr; const float* b_lo = nullptr;
   // Tensor-core path only: also write the split of the output (pitch ldc) for the next product.
   float* c_hi = nullptr; float* c_lo = nullptr;
   // When set (epilogue must be EPI_STORE): the product may be left as split-K partial tiles for the

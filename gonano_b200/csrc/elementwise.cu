@@ -98,6 +98,23 @@ int swiglu_backward_launch(float* gg, float* ug, const float* gate, const float*
   return GN_OK;
 }
 
+// hi/lo tf32 split of a pitched matrix (the form the tensor-core products read), for producers that ran on the float32 path
+__global__ void __launch_bounds__(256) split_matrix_kernel(const float* src, float* hi, float* lo, int64_t rows, int cols, int64_t ld) {
+  const int64_t total = rows * cols;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / cols; const int c = (int)(i % cols);
+    float h, l; split_tf32(src[r * ld + c], h, l);
+    hi[r * ld + c] = h; lo[r * ld + c] = l;
+  }
+}
+int split_matrix_launch(const float* src, float* hi, float* lo, int64_t rows, int cols, int64_t ld, cudaStream_t s) {
+  if (rows <= 0 || cols <= 0) return GN_OK;
+  const int blocks = (int)std::min<int64_t>((rows * cols + 255) / 256, (int64_t)kNumSM * 16);
+  split_matrix_kernel<<<blocks, 256, 0, s>>>(src, hi, lo, rows, cols, ld);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
 __global__ void __launch_bounds__(256) fill_kernel(float* dst, float v, int64_t n) {
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) dst[i] = v;

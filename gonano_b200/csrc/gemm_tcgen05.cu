@@ -244,6 +244,7 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
   bool failed = false;
+  pdl_wait();   // everything above ran in the shadow of the kernel that produces this product's operands
   if (threadIdx.x == 0) TC_TRACE(896);
 
   if (warp == 0) {
@@ -459,6 +460,8 @@ int* g_err_flag = nullptr;
 long long* g_trace = nullptr;   // device buffer of 1024 slots (GN_TC_TRACE builds)
 std::mutex g_mu;
 // GN_TC_MN=0 keeps the transposing operand split for products whose operands are stored [K, M] / [K, N].
+// GN_TC_PDL=0 launches the products without programmatic stream serialization.
+const bool g_use_pdl = [] { const char* e = getenv("GN_TC_PDL"); return !(e && e[0] == '0'); }();
 const bool g_allow_mn = [] { const char* e = getenv("GN_TC_MN"); return !(e && e[0] == '0'); }();
 
 
@@ -559,6 +562,7 @@ int split_operand(const float* src, int64_t ld, int64_t rows, int64_t k, bool st
 
 // Split-K second pass: C = epilogue(sum over splits of the partial tiles), in a fixed order.
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, int splits, int64_t split_stride, TcEpilogue ep, int M, int N) {
+  pdl_trigger();
   const int nv = N >> 2;   // N is a multiple of 4 on this path
   const int64_t total = (int64_t)M * nv;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -615,7 +619,15 @@ int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int
     ep.C = g_splitk_ws; ep.ldc = N; ep.aux = nullptr; ep.epi = EPI_STORE; ep.split_stride = (int64_t)M * N; ep.c_hi = ep.c_lo = nullptr;
   }
   dim3 grid(ceil_div(N, BN), ceil_div(M, TBM) + ep_in.groups, splits);   // grouped: an upper bound on the sum of per-group tiles
-  gemm_tc_kernel<BN, STAGES><<<grid, 64 + 32 * (BN > 128 ? 8 : 4), S::TOTAL, s>>>(mah, mal, mbh, mbl, ep, M, N, K, g_err_flag);
+  {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = dim3(64 + 32 * (BN > 128 ? 8 : 4)); cfg.dynamicSmemBytes = S::TOTAL; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = g_use_pdl ? 1 : 0;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    GN_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES>, mah, mal, mbh, mbl, ep, M, N, K, g_err_flag));
+  }
   GN_LAUNCH_CHECK();
   if (leave) {
     if (splits > 1) *leave = Partials{g_splitk_ws, splits, (int64_t)M * N, (int64_t)N};
@@ -660,7 +672,11 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
     g_last_a.valid = plain; g_last_a.src = g.A; g_last_a.ld = g.lda; g_last_a.rows = src_rows; g_last_a.cols = src_cols;
   }
   // B is logically [N, K]; stored that way when b_trans (weights [out, in]), else stored [K, N].
-  GN_TRY(split_operand(g.B, g.ldb, g.groups > 0 ? (int64_t)g.groups * g.N : g.N, g.K, g.b_trans == 0, g.b_static != 0, 1, b, s, g_allow_mn));
+  if (g.b_hi && g.b_lo && !g.b_trans && g_allow_mn && g.groups == 0 && g.ldb % 4 == 0) {
+    b.hi = const_cast<float*>(g.b_hi); b.lo = const_cast<float*>(g.b_lo); b.ld = g.ldb; b.mn = true;   // split by the producer
+  } else {
+    GN_TRY(split_operand(g.B, g.ldb, g.groups > 0 ? (int64_t)g.groups * g.N : g.N, g.K, g.b_trans == 0, g.b_static != 0, 1, b, s, g_allow_mn));
+  }
   TcEpilogue ep{g.C, g.ldc, g.aux, g.ldaux, g.epilogue, g.scalar, 0, g.c_hi, g.c_lo, g_trace, g.group_counts, g.groups, 0, 0};
   if (g.groups > 0) return launch_tc<128, 3>(a, b, ep, g.M, g.N, g.K, 1, s, nullptr);
   // Filling the machine when the output has few tiles (the rollout's products have 512 rows):

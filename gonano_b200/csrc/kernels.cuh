@@ -20,6 +20,7 @@ int rmsnorm_rows_launch(float* dst, const float* src, int64_t rows, int cols, fl
 // dx = dy/r - x*(dy.x)/(n r^3); when `add` != null: dx = add + that.
 int rmsnorm_backward_launch(float* dx, const float* x, const float* dy, const float* add, int64_t rows, int cols, float eps, cudaStream_t s);
 int fill_launch(float* dst, float value, int64_t n, cudaStream_t s);
+int split_matrix_launch(const float* src, float* hi, float* lo, int64_t rows, int cols, int64_t ld, cudaStream_t s);
 
 // --------------------------------------------------------------- optimizer.cu
 // In-place updates (optimizer/optimizer.go:143-173, muon.go:23-173, sinkhorn.go:27-95).  `g` is overwritten (it holds the

@@ -130,6 +130,10 @@ size_t plan_bufs(gn_model* m, Arena& a, FwdBufs& b, Mode mode, int64_t rows, int
       s.Xin = a.take(rows * d); s.H = a.take(rows * d); s.QKV = a.take(rows * W); s.QKROT = a.take(rows * (int64_t)(Hq + Hkv) * D);
       s.O = a.take(rows * (int64_t)Hq * D); s.LSE = a.take((int64_t)B * Hq * T); s.VESIG = a.take(rows * Hkv);
       s.MID = a.take(rows * d); s.M = a.take(rows * d); s.U = a.take(rows * 4 * d); s.HID = a.take(rows * 4 * d); s.XOUT = a.take(rows * d);
+      if (m->ctx->gemm_kind == 1) {
+        s.Hh = a.take(rows * d); s.Hl = a.take(rows * d); s.Mh = a.take(rows * d); s.Ml = a.take(rows * d);
+        s.Ph = a.take(rows * 4 * d); s.Pl = a.take(rows * 4 * d);
+      }
     }
     b.Xa = b.Xb = b.H = b.QKV = b.O = b.M = b.HID = b.BO = nullptr;
   } else {
@@ -196,17 +200,21 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
       Xin = b.Xa; H = b.H; QKV = b.QKV; O = b.O; MID = b.Xa; Mn = b.M; U = nullptr; HID = b.HID; XOUT = b.Xa;
     }
     const bool tc = m->ctx->gemm_kind == 1;
+    // where the tf32 splits of H, M and HID go: kept per layer in training (the backward reads them), shared otherwise
+    float* Hh = (train && tc) ? b.layers[l].Hh : b.S1h; float* Hl = (train && tc) ? b.layers[l].Hl : b.S1l;
+    float* Mh = (train && tc) ? b.layers[l].Mh : b.S1h; float* Ml = (train && tc) ? b.layers[l].Ml : b.S1l;
+    float* Ph = (train && tc) ? b.layers[l].Ph : b.S4h; float* Pl = (train && tc) ? b.layers[l].Pl : b.S4l;
     // Inference on the tensor-core path: products whose K loop was split over CTAs are left as partial
     // tiles and summed by the kernel that consumes them (one launch less per product).
     const bool fuse = tc && !train && sum_norm_supported(d) && D % 4 == 0;
     if (pending.on()) {
       SumNorm sn; sn.R = x_prev; sn.part = pending; sn.X0 = b.X0; sn.rho = m->p(m->off_rho); sn.chi = m->p(m->off_chi); sn.layer = l;
       if (l - 1 == L / 2) { sn.Xsum = b.BO; backout = b.BO; }
-      sn.V = Xin; sn.Y = H; sn.Yh = b.S1h; sn.Yl = b.S1l; sn.rows = rows; sn.d = d;
+      sn.V = Xin; sn.Y = H; sn.Yh = Hh; sn.Yl = Hl; sn.rows = rows; sn.d = d;
       GN_TRY(sum_norm_launch(sn, s));
       pending = Partials();
     } else {
-      GN_TRY(mix_norm_launch(x_prev, b.X0, m->p(m->off_rho), m->p(m->off_chi), l, Xin, H, tc ? b.S1h : nullptr, tc ? b.S1l : nullptr, rows, d, s));
+      GN_TRY(mix_norm_launch(x_prev, b.X0, m->p(m->off_rho), m->p(m->off_chi), l, Xin, H, tc ? Hh : nullptr, tc ? Hl : nullptr, rows, d, s));
     }
     bool o_split = false;   // the attention kernel also wrote the tf32 split of O
     if (m->mla()) {
@@ -217,7 +225,7 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
     Partials qkv_part;
     { GemmArgs g; g.A = H; g.lda = d; g.B = m->p(o.qkv); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = QKV; g.ldc = W; g.M = (int)rows; g.N = W; g.K = d;
       if (fuse) g.leave = &qkv_part;
-      if (tc) { g.a_hi = b.S1h; g.a_lo = b.S1l; } GN_TRY(gemm(m, g)); }
+      if (tc) { g.a_hi = Hh; g.a_lo = Hl; } GN_TRY(gemm(m, g)); }
     QkvPost qp;
     qp.qkv = QKV; qp.H = H; qp.ids = a.ids;
     if (qkv_part.on() && qkv_part.ptr != QKV) qp.part = qkv_part;
@@ -250,13 +258,13 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
       Partials op;
       { GemmArgs g; g.A = O; g.lda = (int64_t)Hq * D; g.B = m->p(o.proj); g.b_static = 1; g.ldb = (int64_t)Hq * D; g.b_trans = 1; g.C = H; g.ldc = d; g.M = (int)rows; g.N = d; g.K = Hq * D;
         g.leave = &op; if (o_split) { g.a_hi = b.S4h; g.a_lo = b.S4l; } GN_TRY(gemm(m, g)); }
-      SumNorm sn; sn.R = Xin; sn.part = op; sn.V = MID; sn.Y = Mn; sn.Yh = b.S1h; sn.Yl = b.S1l; sn.rows = rows; sn.d = d;
+      SumNorm sn; sn.R = Xin; sn.part = op; sn.V = MID; sn.Y = Mn; sn.Yh = Mh; sn.Yl = Ml; sn.rows = rows; sn.d = d;
       GN_TRY(sum_norm_launch(sn, s));
     } else {
       // MID = Xin + O Wo^T
       { GemmArgs g; g.A = O; g.lda = (int64_t)Hq * D; g.B = m->p(o.proj); g.b_static = 1; g.ldb = (int64_t)Hq * D; g.b_trans = 1; g.C = MID; g.ldc = d; g.M = (int)rows; g.N = d; g.K = Hq * D;
         g.epilogue = EPI_RESIDUAL; g.aux = Xin; g.ldaux = d; if (o_split) { g.a_hi = b.S4h; g.a_lo = b.S4l; } GN_TRY(gemm(m, g)); }
-      GN_TRY(norm_launch(MID, Mn, tc ? b.S1h : nullptr, tc ? b.S1l : nullptr, rows, d, s));
+      GN_TRY(norm_launch(MID, Mn, tc ? Mh : nullptr, tc ? Ml : nullptr, rows, d, s));
     }
     if (m->moe()) {
       GN_REQUIRE(!train, "routed experts are inference-only");
@@ -268,19 +276,19 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
     // HID = relu(M Wfc^T)^2   (training also keeps the pre-activation)
     { GemmArgs g; g.A = Mn; g.lda = d; g.B = m->p(o.fc); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = HID; g.ldc = 4 * d; g.M = (int)rows; g.N = 4 * d; g.K = d;
       g.epilogue = EPI_RELU2; g.aux = U; g.ldaux = 4 * d;
-      if (tc) { g.a_hi = b.S1h; g.a_lo = b.S1l; g.c_hi = b.S4h; g.c_lo = b.S4l; } GN_TRY(gemm(m, g)); }
+      if (tc) { g.a_hi = Mh; g.a_lo = Ml; g.c_hi = Ph; g.c_lo = Pl; } GN_TRY(gemm(m, g)); }
     // XOUT = MID + HID Wp^T.  When fused the sum is taken by the next layer's mix (or the final norm);
     // a layer whose output is also the backout tap of the last layer is materialised.
     const bool fuse_out = fuse && !(l == L / 2 && l == L - 1);
     if (fuse_out) {
       // Mn was consumed by the product above and takes an unsplit product
       GemmArgs g; g.A = HID; g.lda = 4 * d; g.B = m->p(o.mproj); g.b_static = 1; g.ldb = 4 * d; g.b_trans = 1; g.C = Mn; g.ldc = d; g.M = (int)rows; g.N = d; g.K = 4 * d;
-      g.leave = &pending; g.a_hi = b.S4h; g.a_lo = b.S4l; GN_TRY(gemm(m, g));
+      g.leave = &pending; g.a_hi = Ph; g.a_lo = Pl; GN_TRY(gemm(m, g));
       x_prev = MID;   // the residual the pending product is added to
     } else {
       { GemmArgs g; g.A = HID; g.lda = 4 * d; g.B = m->p(o.mproj); g.b_static = 1; g.ldb = 4 * d; g.b_trans = 1; g.C = XOUT; g.ldc = d; g.M = (int)rows; g.N = d; g.K = 4 * d;
         g.epilogue = EPI_RESIDUAL; g.aux = MID; g.ldaux = d;
-        if (tc) { g.a_hi = b.S4h; g.a_lo = b.S4l; } GN_TRY(gemm(m, g)); }
+        if (tc) { g.a_hi = Ph; g.a_lo = Pl; } GN_TRY(gemm(m, g)); }
       if (l == L / 2) {
         if (train) backout = XOUT;
         else { GN_CUDA(cudaMemcpyAsync(b.BO, XOUT, sizeof(float) * rows * d, cudaMemcpyDeviceToDevice, s)); backout = b.BO; }
@@ -333,7 +341,7 @@ int backward_core(gn_model* m, FwdBufs& b, BwdBufs& w, const int32_t* ids, int B
   double* sacc = (double*)m->sacc.p;
   float* DZ = b.LOGITS;  // the loss kernel turned the logits into dz in place
   // lm_head: dW[:V] += dz^T y ; dy = dz W[:V]      (model/layers/linear.go:45-53)
-  { GemmArgs g; g.A = DZ; g.lda = V; g.a_trans = 1; g.B = b.Y; g.ldb = d; g.b_trans = 0; g.C = m->g(m->off_lm); g.ldc = d; g.M = V; g.N = d; g.K = (int)rows;
+  { GemmArgs g; g.A = DZ; g.lda = V; g.a_trans = 1; g.B = b.Y; g.ldb = d; g.b_trans = 0; g.b_hi = b.S1h; g.b_lo = b.S1l; g.C = m->g(m->off_lm); g.ldc = d; g.M = V; g.N = d; g.K = (int)rows;
     g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
   { GemmArgs g; g.A = DZ; g.lda = V; g.a_reuse = 1; g.B = m->p(m->off_lm); g.b_static = 1; g.ldb = d; g.b_trans = 0; g.C = w.DY; g.ldc = d; g.M = (int)rows; g.N = d; g.K = V; GN_TRY(gemm(m, g)); }
   GN_TRY(rmsnorm_backward_launch(w.DFP, b.FP, w.DY, nullptr, rows, d, kNormEps, s));
@@ -351,11 +359,11 @@ int backward_core(gn_model* m, FwdBufs& b, BwdBufs& w, const int32_t* ids, int B
       dout = w.DOUT;
     }
     // ---- MLP backward (model/train.go:505-514)
-    { GemmArgs g; g.A = dout; g.lda = d; g.a_trans = 1; g.B = sv.HID; g.ldb = 4 * d; g.C = m->g(o.mproj); g.ldc = 4 * d; g.M = d; g.N = 4 * d; g.K = (int)rows;
+    { GemmArgs g; g.A = dout; g.lda = d; g.a_trans = 1; g.B = sv.HID; g.ldb = 4 * d; g.b_hi = sv.Ph; g.b_lo = sv.Pl; g.C = m->g(o.mproj); g.ldc = 4 * d; g.M = d; g.N = 4 * d; g.K = (int)rows;
       g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
     { GemmArgs g; g.A = dout; g.lda = d; g.a_reuse = 1; g.B = m->p(o.mproj); g.b_static = 1; g.ldb = 4 * d; g.C = w.DU; g.ldc = 4 * d; g.M = (int)rows; g.N = 4 * d; g.K = d;
       g.epilogue = EPI_RELU2_BWD; g.aux = sv.U; g.ldaux = 4 * d; GN_TRY(gemm(m, g)); }
-    { GemmArgs g; g.A = w.DU; g.lda = 4 * d; g.a_trans = 1; g.B = sv.M; g.ldb = d; g.C = m->g(o.fc); g.ldc = d; g.M = 4 * d; g.N = d; g.K = (int)rows;
+    { GemmArgs g; g.A = w.DU; g.lda = 4 * d; g.a_trans = 1; g.B = sv.M; g.ldb = d; g.b_hi = sv.Mh; g.b_lo = sv.Ml; g.C = m->g(o.fc); g.ldc = d; g.M = 4 * d; g.N = d; g.K = (int)rows;
       g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
     { GemmArgs g; g.A = w.DU; g.lda = 4 * d; g.a_reuse = 1; g.B = m->p(o.fc); g.b_static = 1; g.ldb = d; g.C = w.DM; g.ldc = d; g.M = (int)rows; g.N = d; g.K = 4 * d; GN_TRY(gemm(m, g)); }
     GN_TRY(rmsnorm_backward_launch(w.DMID, sv.MID, w.DM, dout, rows, d, kNormEps, s));
@@ -374,7 +382,7 @@ int backward_core(gn_model* m, FwdBufs& b, BwdBufs& w, const int32_t* ids, int B
     qb.ve_grad = o.has_ve ? m->g(o.ve) : nullptr; qb.dpre = w.DPRE; qb.cosv = m->cosb.f(); qb.sinv = m->sinb.f();
     qb.B = B; qb.T = T; qb.Hq = Hq; qb.Hkv = Hkv; qb.D = D; qb.R = m->R;
     GN_TRY(qkv_post_backward_launch(qb, s));
-    { GemmArgs g; g.A = w.DQKV; g.lda = W; g.a_trans = 1; g.B = sv.H; g.ldb = d; g.C = m->g(o.qkv); g.ldc = d; g.M = W; g.N = d; g.K = (int)rows;
+    { GemmArgs g; g.A = w.DQKV; g.lda = W; g.a_trans = 1; g.B = sv.H; g.ldb = d; g.b_hi = sv.Hh; g.b_lo = sv.Hl; g.C = m->g(o.qkv); g.ldc = d; g.M = W; g.N = d; g.K = (int)rows;
       g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
     { GemmArgs g; g.A = w.DQKV; g.lda = W; g.a_reuse = 1; g.B = m->p(o.qkv); g.b_static = 1; g.ldb = d; g.C = w.DH; g.ldc = d; g.M = (int)rows; g.N = d; g.K = W; GN_TRY(gemm(m, g)); }
     if (o.has_ve) GN_TRY(ve_gate_backward_launch(w.DPRE, sv.H, m->p(o.ve_gate), m->g(o.ve_gate), w.DH, rows, Hkv, d, s));

@@ -59,6 +59,9 @@ struct LayerOffsets {
 
 struct LayerSaved {
   float *Xin, *H, *QKV, *QKROT, *O, *LSE, *VESIG, *MID, *M, *U, *HID, *XOUT;
+  // tf32 hi/lo splits of H, M and HID written by their producers in the forward pass and read again by the
+  // weight-gradient products (tensor-core path; null otherwise)
+  float *Hh = nullptr, *Hl = nullptr, *Mh = nullptr, *Ml = nullptr, *Ph = nullptr, *Pl = nullptr;
 };
 
 }  // namespace gnm

@@ -71,6 +71,7 @@ int smear_launch(const float* E, float* X, const float* prev_in, float* prev_out
 // ---------------------------------------------------------- mix / norm / backout
 __global__ void __launch_bounds__(WPB * 32) mix_norm_kernel(const float* X, const float* X0, const float* rho, const float* chi, int layer, float* Xin,
                                                             float* H, float* Hh, float* Hl, int64_t rows, int d) {
+  pdl_trigger();
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int64_t r = (int64_t)blockIdx.x * WPB + warp;
   if (r >= rows) return;
@@ -100,6 +101,7 @@ int mix_norm_launch(const float* X, const float* X0, const float* rho, const flo
 
 __global__ void __launch_bounds__(WPB * 32) backout_norm_kernel(const float* X, const float* BO, const float* lambda_b, const int32_t* sel, float* FP,
                                                                 float* Y, float* Yh, float* Yl, int64_t rows, int d) {
+  pdl_trigger();
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int64_t r = (int64_t)blockIdx.x * WPB + warp;
   if (r >= rows) return;
@@ -136,6 +138,7 @@ int norm_launch(const float* X, float* Y, float* Yh, float* Yl, int64_t rows, in
 
 // One block per row, one float4 per thread.
 __global__ void __launch_bounds__(1024) sum_norm_kernel(SumNorm p) {
+  pdl_trigger();
   __shared__ float scratch[33];
   const int64_t r = blockIdx.x;
   const int64_t src = p.sel ? p.sel[r] : r;

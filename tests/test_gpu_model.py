@@ -115,7 +115,7 @@ def test_rollout_greedy_matches_oracle_engine(oracle, ctx):
     gm.close()
 
 
-@pytest.mark.parametrize("name,std,B,T,rpp", [("tiny", 0.1, 2, 4, 0), ("tiny", 0.1, 5, 12, 2), ("c1", 0.05, 3, 40, 0), ("c1", 0.05, 4, 24, 3),
+@pytest.mark.parametrize("name,std,B,T,rpp", [("tiny", 0.1, 2, 4, 0), ("tiny", 0.1, 5, 12, 2), ("c1", 0.05, 3, 40, 0), ("c1", 0.05, 4, 24, 3), ("c1", 0.05, 3, 20, 0),
                                               ("h128", 0.05, 2, 150, 0)])
 def test_policy_gradient_step(oracle, ctx, name, std, B, T, rpp):
     om, gm, cfg = make_pair(oracle, ctx, name, std=std)
