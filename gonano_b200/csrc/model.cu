@@ -888,7 +888,9 @@ int gn_policy_gradient_step(gn_model* m, const int32_t* inputs, const int32_t* t
   GN_REQUIRE(T <= m->cfg.sequence_len, "sequence %d longer than sequence_len %d", T, m->cfg.sequence_len);
   const int V = m->V, L = m->L;
   cudaStream_t s = m->s();
-  if (rows_per_pass <= 0) rows_per_pass = std::max(1, 16384 / T);
+  // ~48 K tokens per pass: measured on d12, 128-row passes cost 1.86 ms per sequence against 2.00 ms for 32-row passes
+  // (fuller waves in the products); the pass's saved tensors are ~1.1 MB per token (54 GB at this size)
+  if (rows_per_pass <= 0) rows_per_pass = std::max(1, 49152 / T);
   rows_per_pass = std::min(rows_per_pass, B);
   const int64_t all = (int64_t)B * T;
   GN_TRY(m->in_dev.ensure(sizeof(int32_t) * all)); GN_TRY(m->tgt_dev.ensure(sizeof(int32_t) * all)); GN_TRY(m->adv_dev.ensure(sizeof(float) * B));
