@@ -211,9 +211,11 @@ def kernel_rooflines(ctx, pk, tf32_tflops):
     hbm_entry("sampler", [512, 32768, 50], 4.0 * 512 * 32768, "d12 decode step, 512 rows")
     r, hq, hkv, d, c = 512, 6, 2, 128, 320
     hbm_entry("decode_attention", [r, hq, hkv, d, c], r * (2.0 * hkv * d * 4 * c + 2 * hq * d * 4), "d12 one layer, 512 rows, context 320")
-    # the same layer with the prompt's 128 positions read once per group of 8 rows: the algorithmic bytes drop
-    hbm_entry("decode_attention", [r, hq, hkv, d, c, 8, 128], (r / 8) * 2.0 * hkv * d * 4 * 128 + r * (2.0 * hkv * d * 4 * (c - 128) + 2 * hq * d * 4),
-              "d12 one layer, 512 rows, context 320, shared 128-token prefix per group of 8")
+    # a long prompt (1024 positions) shared by each group of 8 rows: the prompt's keys are read once per group by the
+    # shared-prefix pass, so the algorithmic bytes drop (short prompts such as d12's 128 tokens keep the per-row kernel)
+    r2, c2, p2 = 256, 1088, 1024
+    hbm_entry("decode_attention", [r2, hq, hkv, d, c2, 8, p2], (r2 / 8) * 2.0 * hkv * d * 4 * p2 + r2 * (2.0 * hkv * d * 4 * (c2 - p2) + 2 * hq * d * 4),
+              "one layer, 256 rows, context 1088, shared 1024-token prefix per group of 8")
     hbm_entry("advantage", [64, 8], 8.0 * 512, "64 groups of 8 (latency-bound)")
 
     # attention of one training pass (32 x 383 tokens, causal): 2 products forward, 7 backward (S and dP are recomputed

@@ -908,7 +908,7 @@ int attention_combine_launch(const float* acc, const float* mx, const float* sm,
 // warp reads one K row and one V row as a single coalesced 512-byte request.
 // All query heads of the group are served from the same K/V registers.
 // Warp partials are merged through shared memory, splits through a second pass.
-template <int DP, int RATIO>
+template <int DP, int RATIO, int U>
 __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restrict__ q, int64_t q_rstride, const float* __restrict__ kcache,
                                                           const float* __restrict__ vcache, int64_t row_stride, int64_t head_stride,
                                                           const int32_t* __restrict__ ctx_len, int Hq, int Hkv, int D, int window, float* __restrict__ out,
@@ -943,31 +943,74 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restric
   }
   const float* kb = kcache + (int64_t)row * row_stride + (int64_t)hk * head_stride;
   const float* vb = vcache + (int64_t)row * row_stride + (int64_t)hk * head_stride;
-  for (int kj = k0 + warp; kj < k1; kj += 4) {
-    float kv[E], vv[E];
+  // One key per warp per iteration; the next key's K and V rows are requested before the current one is used, so
+  // that two rows per warp are in flight (with a single row the loop runs at the memory latency, not the bandwidth).
+  auto load_row = [&](int kj, float (&kr)[E], float (&vr)[E]) {
     if (E == 4 && DP == 128) {
-      float4 a = *reinterpret_cast<const float4*>(kb + (int64_t)kj * D + lane * 4);
-      float4 c = *reinterpret_cast<const float4*>(vb + (int64_t)kj * D + lane * 4);
-      kv[0] = a.x; kv[1] = a.y; kv[2] = a.z; kv[3] = a.w; vv[0] = c.x; vv[1] = c.y; vv[2] = c.z; vv[3] = c.w;
+      const float4 a = *reinterpret_cast<const float4*>(kb + (int64_t)kj * D + lane * 4);
+      const float4 c = *reinterpret_cast<const float4*>(vb + (int64_t)kj * D + lane * 4);
+      kr[0] = a.x; kr[1] = a.y; kr[2] = a.z; kr[3] = a.w; vr[0] = c.x; vr[1] = c.y; vr[2] = c.z; vr[3] = c.w;
     } else {
 #pragma unroll
       for (int e = 0; e < E; ++e) {
-        bool ok = lane * E + e < D;
-        kv[e] = ok ? kb[(int64_t)kj * D + lane * E + e] : 0.0f; vv[e] = ok ? vb[(int64_t)kj * D + lane * E + e] : 0.0f;
+        const bool ok = lane * E + e < D;
+        kr[e] = ok ? kb[(int64_t)kj * D + lane * E + e] : 0.0f; vr[e] = ok ? vb[(int64_t)kj * D + lane * E + e] : 0.0f;
       }
     }
+  };
+  // U keys per warp per iteration (kj, kj + 4, ...), and the next U are requested before these are used: 2U rows per
+  // warp in flight, one running-maximum update per U keys.  U = 1 keeps more warps resident (large batches); U = 2
+  // shortens the dependent chain when there are few warps per SM.
+  float nk[U][E], nv[U][E];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+#pragma unroll
+    for (int e = 0; e < E; ++e) { nk[u][e] = 0.0f; nv[u][e] = 0.0f; }
+    if (k0 + warp + 4 * u < k1) load_row(k0 + warp + 4 * u, nk[u], nv[u]);
+  }
+  for (int kj = k0 + warp; kj < k1; kj += 4 * U) {
+    float kv[U][E], vv[U][E];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int e = 0; e < E; ++e) { kv[u][e] = nk[u][e]; vv[u][e] = nv[u][e]; }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (kj + 4 * (U + u) < k1) load_row(kj + 4 * (U + u), nk[u], nv[u]);
 #pragma unroll
     for (int h = 0; h < RATIO; ++h) {
-      float d = 0;
+      float d[U];
 #pragma unroll
-      for (int e = 0; e < E; ++e) d = fmaf(qv[h][e], kv[e], d);
-      d = warp_sum(d);
-      float mn = fmaxf(m[h], d);
-      float alpha = (m[h] == -INFINITY) ? 0.0f : __expf(m[h] - mn);
-      float p = __expf(d - mn);
-      l[h] = l[h] * alpha + p;
+      for (int u = 0; u < U; ++u) {
+        d[u] = 0;
 #pragma unroll
-      for (int e = 0; e < E; ++e) o[h][e] = o[h][e] * alpha + p * vv[e];
+        for (int e = 0; e < E; ++e) d[u] = fmaf(qv[h][e], kv[u][e], d[u]);
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+        for (int u = 0; u < U; ++u) d[u] += __shfl_xor_sync(0xffffffffu, d[u], off);
+      float mn = m[h];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (u > 0 && kj + 4 * u >= k1) d[u] = -INFINITY;
+        mn = fmaxf(mn, d[u]);
+      }
+      const float alpha = (m[h] == -INFINITY) ? 0.0f : __expf(m[h] - mn);
+      float p[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) p[u] = (u > 0 && kj + 4 * u >= k1) ? 0.0f : __expf(d[u] - mn);
+      float ls = l[h] * alpha;
+#pragma unroll
+      for (int u = 0; u < U; ++u) ls += p[u];
+      l[h] = ls;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        float acc = o[h][e] * alpha;
+#pragma unroll
+        for (int u = 0; u < U; ++u) acc = fmaf(p[u], vv[u][e], acc);
+        o[h][e] = acc;
+      }
       m[h] = mn;
     }
   }
@@ -1156,12 +1199,13 @@ constexpr size_t kPrefixSmem = sizeof(float) * (size_t)(2 * kPrefixTile * 132 + 
 int attention_decode_prefix_splits(int rows, int group, int Hq, int Hkv, int D, int prefix_len) {
   if (group <= 1 || prefix_len <= 0 || D != 128 || group * (Hq / Hkv) > kPrefixMaxHeads || rows % group != 0) return 0;
   const int tiles = (prefix_len + kPrefixTile - 1) / kPrefixTile;
-  // Measured on d12: the pass pays off when it fills the machine (512 rows: 512 CTAs); with a few dozen
-  // CTAs its per-CTA latency exceeds what the shared reads save (64 rows), so small batches keep the per-row kernel.
-  // GN_PREFIX_SHARING=1 / 0 overrides the size rule (tests exercise the pass on small batches with it).
+  // Measured on d12 (128-token prompts, 512 rows): the group's rows read the prompt's keys from L2 anyway, so the pass
+  // only wins while the prompt is most of the context (35 vs 39 us per layer at 160 keys, 60 vs 57 at 256).  It is
+  // therefore used when the prompt is long (>= 512 positions) and the pass fills the machine; short prompts and small
+  // batches keep the per-row kernel.  GN_PREFIX_SHARING=1 / 0 overrides the rule (tests exercise the pass with it).
   static const int forced = [] { const char* e = getenv("GN_PREFIX_SHARING"); return e ? (e[0] == '0' ? 0 : 1) : -1; }();
   if (forced == 0) return 0;
-  if (forced < 0 && (int64_t)(rows / group) * Hkv * tiles < 2 * kNumSM) return 0;
+  if (forced < 0 && (prefix_len < 512 || (int64_t)(rows / group) * Hkv * tiles < 2 * kNumSM)) return 0;
   return tiles;
 }
 
@@ -1189,8 +1233,13 @@ static int decode_go(const float* q, int64_t q_rstride, const float* kcache, con
   }
   const int nslots = psplits + splits;
   dim3 grid(rows * Hkv, splits);
-  attn_decode_kernel<DP, RATIO><<<grid, 128, 0, s>>>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, Hq, Hkv, D, window, out, o_rstride,
-                                                     part_acc, part_ms, splits, out_hi, out_lo, psplits ? prefix_len : 0, psplits, nslots);
+  // fewer than ~5 CTAs per SM: two keys per iteration (shorter chain); otherwise one (more resident warps)
+  if ((int64_t)rows * Hkv * splits < (int64_t)kNumSM * 5)
+    attn_decode_kernel<DP, RATIO, 2><<<grid, 128, 0, s>>>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, Hq, Hkv, D, window, out, o_rstride,
+                                                          part_acc, part_ms, splits, out_hi, out_lo, psplits ? prefix_len : 0, psplits, nslots);
+  else
+    attn_decode_kernel<DP, RATIO, 1><<<grid, 128, 0, s>>>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, Hq, Hkv, D, window, out, o_rstride,
+                                                          part_acc, part_ms, splits, out_hi, out_lo, psplits ? prefix_len : 0, psplits, nslots);
   GN_LAUNCH_CHECK();
   if (splits > 1) {
     attn_decode_combine_kernel<<<rows * Hq, 128, 0, s>>>(part_acc, part_ms, nslots, Hq, D, out, o_rstride, out_hi, out_lo);

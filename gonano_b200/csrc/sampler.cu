@@ -7,7 +7,8 @@
 // one uniform per vocabulary entry, and keeps the first maximum of
 // value/temperature - log(-log(u)).  Here the row is read from HBM once into
 // registers, the k-th largest value is found exactly by an 8-bit radix select
-// on the order-preserving integer image of the floats, and only the survivors
+// on the order-preserving integer image of the floats (for small k a candidate
+// filter finds it without the histograms), and only the survivors
 // pay for the uniform and the float64 logarithms.  Uniforms are addressed by
 // counter, so skipping the masked entries changes nothing.
 #include "kernels.cuh"
@@ -63,7 +64,8 @@ __global__ void __launch_bounds__(ST) sample_kernel(const float* __restrict__ lo
                                                     float temperature, int top_k, int32_t* __restrict__ out) {
   __shared__ unsigned int hist[32][256];  // one histogram per warp
   __shared__ unsigned int total[256];
-  __shared__ unsigned int sel_prefix, sel_remaining;
+  __shared__ unsigned int sel_prefix, sel_remaining, warp_count[32];
+  __shared__ float sel_threshold;
   __shared__ float shs[32];
   __shared__ int shi[32];
 
@@ -87,7 +89,77 @@ __global__ void __launch_bounds__(ST) sample_kernel(const float* __restrict__ lo
 
   float threshold = -INFINITY;
   const bool mask = top_k > 0 && top_k < vocab;
-  if (mask) {
+  bool found = false;
+  unsigned n_cand = 0;
+  // Fast path for small k.  Take, per warp, the m = ceil(k/32) largest of its threads' maxima: these are 32m >= k
+  // distinct entries, so the k-th largest of the row is at least t0 = the smallest of them, and every entry >= t0 is
+  // a candidate (a few hundred for ordinary logits).  The exact k-th largest is then found among the candidates by
+  // counting ranks.  Rows with more candidates than fit (many equal values) take the radix select below.
+  constexpr unsigned kWarpCand = 64, kCand = 32 * kWarpCand;  // 4 * kCand words = the histogram storage
+  const int m_per_warp = (top_k + 31) / 32;
+  if (mask && m_per_warp <= 4) {
+    float* warp_val = reinterpret_cast<float*>(&hist[0][0]);            // [32 warps][kWarpCand]
+    int* warp_idx = reinterpret_cast<int*>(&hist[0][0]) + kCand;         // [32 warps][kWarpCand]
+    float* cand = reinterpret_cast<float*>(&hist[0][0]) + 2 * kCand;     // packed [kCand]
+    int* cand_index = reinterpret_cast<int*>(&hist[0][0]) + 3 * kCand;   // packed [kCand]
+    const int lane = tid & 31;
+    float tmax = -INFINITY;
+#pragma unroll
+    for (int it = 0; it < IPT; ++it) tmax = fmaxf(tmax, x[it]);
+    float v = tmax, tw = -INFINITY;
+    for (int r = 0; r < m_per_warp; ++r) {
+      float w = v;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) w = fmaxf(w, __shfl_xor_sync(0xffffffffu, w, o));
+      tw = w;
+      const unsigned holders = __ballot_sync(0xffffffffu, v == w);
+      if (lane == __ffs(holders) - 1) v = -INFINITY;  // one holder leaves; ties stay for the next round
+    }
+    if (lane == 0) shs[warp] = tw;
+    __syncthreads();
+    float t0 = shs[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t0 = fminf(t0, __shfl_xor_sync(0xffffffffu, t0, o));
+    // Each warp lists its own candidates (positions from ballots, no atomics), then the lists are packed.
+    unsigned mine_count = 0;
+    const unsigned below = (1u << lane) - 1u;
+#pragma unroll
+    for (int it = 0; it < IPT; ++it) {
+      const bool pred = it * ST + tid < vocab && x[it] >= t0;
+      const unsigned votes = __ballot_sync(0xffffffffu, pred);
+      if (votes) {
+        const unsigned pos = mine_count + __popc(votes & below);
+        if (pred && pos < kWarpCand) { warp_val[warp * kWarpCand + pos] = x[it]; warp_idx[warp * kWarpCand + pos] = it * ST + tid; }
+        mine_count += __popc(votes);
+      }
+    }
+    if (lane == 0) warp_count[warp] = mine_count;
+    __syncthreads();
+    const unsigned cnt_l = warp_count[lane];
+    const bool overflow = __any_sync(0xffffffffu, cnt_l > kWarpCand);
+    unsigned incl = cnt_l;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const unsigned t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
+    const unsigned C = __shfl_sync(0xffffffffu, incl, 31);
+    const unsigned offset = __shfl_sync(0xffffffffu, incl - cnt_l, warp);
+    if (!overflow)
+      for (unsigned j = lane; j < mine_count; j += 32) { cand[offset + j] = warp_val[warp * kWarpCand + j]; cand_index[offset + j] = warp_idx[warp * kWarpCand + j]; }
+    __syncthreads();
+    if (!overflow) {
+      for (unsigned i = tid; i < C; i += ST) {
+        const float mine = cand[i];
+        int greater = 0, not_less = 0;
+#pragma unroll 4
+        for (unsigned j = 0; j < C; ++j) { const float other = cand[j]; greater += other > mine; not_less += other >= mine; }
+        if (greater < top_k && not_less >= top_k) sel_threshold = mine;  // every writer holds the same value
+      }
+      found = true;
+    }
+    __syncthreads();
+    if (found) threshold = sel_threshold;
+    n_cand = found ? C : 0u;
+  }
+  if (mask && !found) {
     if (tid == 0) { sel_prefix = 0u; sel_remaining = (unsigned)top_k; }
     for (int pass = 0; pass < 4; ++pass) {
       const int shift = 24 - 8 * pass;
@@ -147,17 +219,29 @@ __global__ void __launch_bounds__(ST) sample_kernel(const float* __restrict__ lo
   const uint32_t grow = (uint32_t)(row % group);
   const uint32_t step = step_dev ? *step_dev : step_host;
   Best b{-INFINITY, 0x7fffffff};
-#pragma unroll
-  for (int it = 0; it < IPT; ++it) {
-    int c = it * ST + tid;
-    if (c >= vocab) continue;
-    float value = x[it];
-    if (mask && !(value >= threshold)) continue;  // masked to -inf: can never beat a survivor
+  auto consider = [&](float value, int c) {
     float u = uniforms ? uniforms[(int64_t)row * vocab + c] : sampler_uniform(seed, step, grow, (uint32_t)c);
     if (u <= 0.0f) u = 1e-12f;
     float gumbel = -(float)log(-log((double)u));
     float score = __fadd_rn(__fdiv_rn(value, temperature), gumbel);
     best_merge(b, score, c);
+  };
+  if (found) {
+    // The survivors are among the candidates: one thread per survivor, so the float64 logarithms of the whole row
+    // run side by side instead of once per warp that happens to hold a survivor.
+    const float* cand = reinterpret_cast<const float*>(&hist[0][0]) + 2 * kCand;
+    const int* cand_index = reinterpret_cast<const int*>(&hist[0][0]) + 3 * kCand;
+    for (unsigned i = tid; i < n_cand; i += ST)
+      if (cand[i] >= threshold) consider(cand[i], cand_index[i]);
+  } else {
+#pragma unroll
+    for (int it = 0; it < IPT; ++it) {
+      int c = it * ST + tid;
+      if (c >= vocab) continue;
+      float value = x[it];
+      if (mask && !(value >= threshold)) continue;  // masked to -inf: can never beat a survivor
+      consider(value, c);
+    }
   }
   b = block_best(b, shs, shi);
   if (tid == 0) out[row] = b.index == 0x7fffffff ? 0 : b.index;

@@ -23,7 +23,7 @@ def test_sampler_known_answers():
 
 
 @pytest.mark.parametrize("vocab", [8, 1000, 8192, 32768, 65536])
-@pytest.mark.parametrize("top_k", [0, 1, 50])
+@pytest.mark.parametrize("top_k", [0, 1, 50, 100, 200])
 def test_sampler_bit_exact_with_explicit_uniforms(oracle, vocab, top_k):
     """Indices are identical to the CPU rule given identical logits and uniforms."""
     from gonano_b200.backend import sample_next_token
@@ -62,6 +62,21 @@ def test_sampler_ties_take_first_maximum(oracle):
     uniforms = np.full((2, 4096), 0.5, np.float32)
     assert list(sample_next_token(logits, 1.0, 0, uniforms=uniforms)) == [0, 0]
     assert list(oracle.sample_next_token(logits, 1.0, 0, uniforms=uniforms)) == [0, 0]
+
+
+def test_sampler_top_k_on_rows_of_equal_values(oracle):
+    """Every entry ties with the k-th largest, so all survive (inference/sampler.go:59-64); on the device this is the row
+    whose candidate list overflows and falls back to the radix select."""
+    from gonano_b200.backend import sample_next_token
+    rng = np.random.default_rng(3)
+    logits = np.zeros((3, 32768), np.float32)
+    logits[1, 100:130] = 2.0          # 30 larger entries, then a plateau that holds the 50th largest
+    logits[2] = -np.inf
+    logits[2, :60] = 1.0
+    uniforms = rng.random(logits.shape, dtype=np.float32)
+    got = sample_next_token(logits, 1.0, 50, uniforms=uniforms)
+    want = oracle.sample_next_token(logits, 1.0, 50, uniforms=uniforms)
+    assert np.array_equal(got, want)
 
 
 def test_group_advantage(oracle):
