@@ -4,13 +4,16 @@
 //
 // Precision: every float32 operand x is used as hi = tf32(x) and lo = tf32(x - hi) and each
 // product is three instructions, a_lo*b_hi + a_hi*b_lo + a_hi*b_hi (the small terms first), which
-// keeps the products at float32 accuracy.  The split is done in registers right after the
-// shared-memory load.
+// keeps the products at float32 accuracy.  The tiles that serve as B operands (K and V in the forward
+// and dQ kernels, Q and dO in the dK/dV kernel) are split once, when they are written to shared
+// memory, into a hi tile and a lo tile; A operands are split in registers (the forward's Q tile is
+// pre-split too: there is room for it).
 //
-// Tiling: a warp owns 16 rows of the output (queries in the forward and dQ kernels, keys in the
-// dK/dV kernel) and all 128 channels; all tiles sit row-major in shared memory with a pitch of
-// 132 floats, which makes both fragment access patterns (row g, channel t and row 2t, channel g
-// for lane = 4g + t) free of bank conflicts.
+// Tiling: a CTA is 8 warps; a warp owns 16 rows of the output (queries in the forward and dQ kernels,
+// keys in the dK/dV kernel) and all 128 channels; the other operand streams through in tiles of 32
+// rows.  All tiles sit row-major in shared memory with a pitch of 132 floats, which makes both
+// fragment access patterns (row g, channel t — read with ldmatrix, four 8 x 16-byte matrices per
+// instruction — and row 2t, channel g for lane = 4g + t) free of bank conflicts.
 //
 // The second product of each pair (P V, dS K, P^T dO, dS^T Q) contracts over the index that the
 // first product's accumulator fragment holds as columns 2t, 2t+1.  Instead of moving data
@@ -29,7 +32,9 @@ namespace {
 constexpr float kMasked = -1e30f;
 constexpr int HD = 128;       // head_dim
 constexpr int LD = HD + 4;    // shared-memory pitch in floats
-constexpr int NTH = 128;      // threads per CTA: 4 warps x 16 rows
+constexpr int NTH = 256;      // threads per CTA: 8 warps x 16 rows
+constexpr int BM = 128;       // rows owned by a CTA
+constexpr int BT = 32;        // rows of a streamed tile
 
 // hi = x rounded to tf32 (nearest, ties away: add half a unit of the kept mantissa to the magnitude
 // bits, clear the 13 dropped ones); lo = x - hi, exact in float32.  lo is handed to the tensor core as
@@ -45,8 +50,16 @@ __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], const
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
+// Four 8-row x 16-byte matrices from shared memory; lane L supplies the address of row L%8 of matrix L/8 and
+// receives word L%4 of row L/4 of each matrix, which is the (g, t) element of a tf32 fragment.
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
+}
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
 // The three instructions of one product form a dependent chain on the accumulator, so they are issued
-// for GR independent accumulator tiles at a time, term by term.
+// for GR independent accumulator tiles at a time, term by term.  (A second accumulator set for the small terms,
+// which halves the chains, was measured: no change — the loops are not bound by these chains.)
 constexpr int GR = 4;
 __device__ __forceinline__ void mma3_group(float (*c)[4], const uint32_t (&ah)[4], const uint32_t (&al)[4], const uint32_t (&bh)[GR][2], const uint32_t (&bl)[GR][2]) {
 #pragma unroll
@@ -57,21 +70,35 @@ __device__ __forceinline__ void mma3_group(float (*c)[4], const uint32_t (&ah)[4
   for (int i = 0; i < GR; ++i) mma(c[i], ah, bh[i]);
 }
 
-// acc[nt] (16 x 8 tiles) += A[16 rows][128] . B[8*nt + n][128]^T ; A points at the warp's first row.
-template <int NT>
-__device__ __forceinline__ void mm_rows(float (&acc)[NT][4], const float* A, const float* B, int g, int t) {
+// acc[nt] (16 x 8 tiles) += A[16 rows][128] . B[8*nt + n][128]^T.  A points at the warp's first row: a raw float32
+// tile (Alo == nullptr, split here) or a pre-split pair; Bh / Bl are the pre-split tile.
+template <int NT, bool APRE>
+__device__ __forceinline__ void mm_rows(float (&acc)[NT][4], const float* A, const float* Alo, const float* Bh, const float* Bl, int lane) {
+  const int mat = lane >> 3, r = lane & 7;
+  const int a_off = ((mat & 1) * 8 + r) * LD + (mat >> 1) * 4;
+  const uint32_t a_addr = smem_addr(A + a_off);
+  const uint32_t al_addr = APRE ? smem_addr(Alo + a_off) : 0u;
+  const uint32_t b_addr = smem_addr((mat < 2 ? Bh : Bl) + r * LD + (mat & 1) * 4);
 #pragma unroll 2
   for (int ks = 0; ks < HD / 8; ++ks) {
     uint32_t ah[4], al[4];
-    const float* ap = A + g * LD + ks * 8 + t;
-    split(ap[0], ah[0], al[0]); split(ap[8 * LD], ah[1], al[1]); split(ap[4], ah[2], al[2]); split(ap[8 * LD + 4], ah[3], al[3]);
+    if (APRE) {
+      ldsm4(ah, a_addr + ks * 32);
+      ldsm4(al, al_addr + ks * 32);
+    } else {
+      uint32_t raw[4];
+      ldsm4(raw, a_addr + ks * 32);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) split(__uint_as_float(raw[e]), ah[e], al[e]);
+    }
 #pragma unroll
     for (int n0 = 0; n0 < NT; n0 += GR) {
       uint32_t bh[GR][2], bl[GR][2];
 #pragma unroll
       for (int i = 0; i < GR; ++i) {
-        const float* bp = B + ((n0 + i) * 8 + g) * LD + ks * 8 + t;
-        split(bp[0], bh[i][0], bl[i][0]); split(bp[4], bh[i][1], bl[i][1]);
+        uint32_t f[4];
+        ldsm4(f, b_addr + (uint32_t)(((n0 + i) * 8 * LD + ks * 8) * 4));
+        bh[i][0] = f[0]; bh[i][1] = f[1]; bl[i][0] = f[2]; bl[i][1] = f[3];
       }
       mma3_group(&acc[n0], ah, al, bh, bl);
     }
@@ -79,19 +106,24 @@ __device__ __forceinline__ void mm_rows(float (&acc)[NT][4], const float* A, con
 }
 
 // acc[nt] (16 x 8 tiles over the 128 channels) += P[16][8*NK] . B[8*NK rows][128], where P is held
-// as NK accumulator fragments (columns 2t, 2t+1 of each 8-wide tile) and B is row-major.
+// as NK accumulator fragments (columns 2t, 2t+1 of each 8-wide tile) and B (pre-split) is row-major.
 template <int NK>
-__device__ __forceinline__ void mm_perm(float (&acc)[HD / 8][4], const float (&p)[NK][4], const float* B, int g, int t) {
+__device__ __forceinline__ void mm_perm(float (&acc)[HD / 8][4], const float (&p)[NK][4], const float* Bh, const float* Bl, int g, int t) {
 #pragma unroll
   for (int ks = 0; ks < NK; ++ks) {
     uint32_t ah[4], al[4];
     split(p[ks][0], ah[0], al[0]); split(p[ks][2], ah[1], al[1]); split(p[ks][1], ah[2], al[2]); split(p[ks][3], ah[3], al[3]);
-    const float* brow = B + (ks * 8 + 2 * t) * LD + g;
+    const int off = (ks * 8 + 2 * t) * LD + g;
+    const uint32_t* hrow = reinterpret_cast<const uint32_t*>(Bh) + off;
+    const uint32_t* lrow = reinterpret_cast<const uint32_t*>(Bl) + off;
 #pragma unroll
     for (int n0 = 0; n0 < HD / 8; n0 += GR) {
       uint32_t bh[GR][2], bl[GR][2];
 #pragma unroll
-      for (int i = 0; i < GR; ++i) { split(brow[(n0 + i) * 8], bh[i][0], bl[i][0]); split(brow[LD + (n0 + i) * 8], bh[i][1], bl[i][1]); }
+      for (int i = 0; i < GR; ++i) {
+        bh[i][0] = hrow[(n0 + i) * 8]; bh[i][1] = hrow[LD + (n0 + i) * 8];
+        bl[i][0] = lrow[(n0 + i) * 8]; bl[i][1] = lrow[LD + (n0 + i) * 8];
+      }
       mma3_group(&acc[n0], ah, al, bh, bl);
     }
   }
@@ -106,6 +138,38 @@ __device__ __forceinline__ void load_tile(float* S, const float* gsrc, int64_t t
     *reinterpret_cast<float4*>(S + r * LD + c) = v;
   }
 }
+// A streamed tile (32 rows) is fetched into registers while the previous tile is being used (4 float4 per thread)
+// and split into its hi and lo tiles in shared memory between two barriers.
+struct TileRegs { float4 v[BT * (HD / 4) / NTH]; };
+__device__ __forceinline__ void fetch_tile(TileRegs& r, const float* gsrc, int64_t tstride, int valid) {
+#pragma unroll
+  for (int i = 0; i < BT * (HD / 4) / NTH; ++i) {
+    const int idx = threadIdx.x + i * NTH, row = idx / (HD / 4), c = (idx % (HD / 4)) * 4;
+    r.v[i] = row < valid ? *reinterpret_cast<const float4*>(gsrc + (int64_t)row * tstride + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+__device__ __forceinline__ void stash_tile(const TileRegs& r, float* Sh, float* Sl) {
+#pragma unroll
+  for (int i = 0; i < BT * (HD / 4) / NTH; ++i) {
+    const int idx = threadIdx.x + i * NTH, row = idx / (HD / 4), c = (idx % (HD / 4)) * 4;
+    uint4 h, l;
+    split(r.v[i].x, h.x, l.x); split(r.v[i].y, h.y, l.y); split(r.v[i].z, h.z, l.z); split(r.v[i].w, h.w, l.w);
+    *reinterpret_cast<uint4*>(Sh + row * LD + c) = h;
+    *reinterpret_cast<uint4*>(Sl + row * LD + c) = l;
+  }
+}
+// the same, written as a hi tile and a lo tile
+__device__ __forceinline__ void load_tile_split(float* Sh, float* Sl, const float* gsrc, int64_t tstride, int nrows, int valid) {
+  for (int idx = threadIdx.x; idx < nrows * (HD / 4); idx += NTH) {
+    const int r = idx / (HD / 4), c = (idx % (HD / 4)) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < valid) v = *reinterpret_cast<const float4*>(gsrc + (int64_t)r * tstride + c);
+    uint4 h, l;
+    split(v.x, h.x, l.x); split(v.y, h.y, l.y); split(v.z, h.z, l.z); split(v.w, h.w, l.w);
+    *reinterpret_cast<uint4*>(Sh + r * LD + c) = h;
+    *reinterpret_cast<uint4*>(Sl + r * LD + c) = l;
+  }
+}
 
 __device__ __forceinline__ bool masked(int qpos, int kj, int window, const int32_t* seg, int seg_len, int32_t qseg) {
   bool m = kj > qpos || (window >= 0 && qpos - kj > window);
@@ -114,20 +178,20 @@ __device__ __forceinline__ bool masked(int qpos, int kj, int window, const int32
 }
 
 // ------------------------------------------------------------------ forward
-// CTA = 64 queries of one (batch, head); 64-key tiles; later (heavier) query tiles are scheduled first.
-__global__ void __launch_bounds__(NTH, 2) attn_mma_fwd_kernel(AttnShape sh, const float* __restrict__ q, const float* __restrict__ k,
+// CTA = 128 queries of one (batch, head); 32-key tiles; later (heavier) query tiles are scheduled first.
+// A warp skips the key tiles that lie wholly after its own 16 queries.
+__global__ void __launch_bounds__(NTH, 1) attn_mma_fwd_kernel(AttnShape sh, const float* __restrict__ q, const float* __restrict__ k,
                                                               const float* __restrict__ v, float* __restrict__ out, float* __restrict__ lse) {
   pdl_trigger();
-  constexpr int BQ = 64, BKV = 64;
   extern __shared__ __align__(16) float smem[];
-  float* Qs = smem; float* Ks = Qs + BQ * LD; float* Vs = Ks + BKV * LD;
+  float* Qh = smem; float* Ql = Qh + BM * LD; float* Kh = Ql + BM * LD; float* Kl = Kh + BT * LD; float* Vh = Kl + BT * LD; float* Vl = Vh + BT * LD;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int bh = blockIdx.y, b = bh / sh.Hq, hq = bh % sh.Hq, hk = hq / (sh.Hq / sh.Hkv);
-  const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BQ, qvalid = min(BQ, sh.Tq - q0), offset = sh.offset0;
+  const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BM, qvalid = min(BM, sh.Tq - q0), offset = sh.offset0;
   const float* qg = q + (int64_t)b * sh.q_bstride + (int64_t)q0 * sh.q_tstride + (int64_t)hq * HD;
   const float* kg = k + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride;
   const float* vg = v + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride;
-  load_tile(Qs, qg, sh.q_tstride, BQ, qvalid);
+  load_tile_split(Qh, Ql, qg, sh.q_tstride, BM, qvalid);
   float o[HD / 8][4];
 #pragma unroll
   for (int nt = 0; nt < HD / 8; ++nt) { o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f; }
@@ -138,24 +202,34 @@ __global__ void __launch_bounds__(NTH, 2) attn_mma_fwd_kernel(AttnShape sh, cons
     qpos2[h] = offset + q0 + warp * 16 + g + 8 * h;
     qseg[h] = (sh.segment_ids && qpos2[h] < sh.seg_len) ? sh.segment_ids[qpos2[h]] : 0;
   }
+  const int warp_last = offset + q0 + warp * 16 + 15;   // last query position of this warp
   const int max_qpos = offset + q0 + qvalid - 1;
   const int k_end = min(sh.Tk, max_qpos + 1);
   int k_begin = 0;
   if (sh.window >= 0) k_begin = max(0, offset + q0 - sh.window);
-  k_begin = (k_begin / BKV) * BKV;
-  for (int kt = k_begin; kt < k_end; kt += BKV) {
-    const int kvalid = min(BKV, sh.Tk - kt);
+  k_begin = (k_begin / BT) * BT;
+  TileRegs kr, vr;
+  if (k_begin < k_end) {
+    fetch_tile(kr, kg + (int64_t)k_begin * sh.kv_tstride, sh.kv_tstride, min(BT, sh.Tk - k_begin));
+    fetch_tile(vr, vg + (int64_t)k_begin * sh.kv_tstride, sh.kv_tstride, min(BT, sh.Tk - k_begin));
+  }
+  for (int kt = k_begin; kt < k_end; kt += BT) {
     __syncthreads();
-    load_tile(Ks, kg + (int64_t)kt * sh.kv_tstride, sh.kv_tstride, BKV, kvalid);
-    load_tile(Vs, vg + (int64_t)kt * sh.kv_tstride, sh.kv_tstride, BKV, kvalid);
+    stash_tile(kr, Kh, Kl);
+    stash_tile(vr, Vh, Vl);
     __syncthreads();
-    float s[BKV / 8][4];
+    if (kt + BT < k_end) {   // the next tile travels while this one is used
+      fetch_tile(kr, kg + (int64_t)(kt + BT) * sh.kv_tstride, sh.kv_tstride, min(BT, sh.Tk - kt - BT));
+      fetch_tile(vr, vg + (int64_t)(kt + BT) * sh.kv_tstride, sh.kv_tstride, min(BT, sh.Tk - kt - BT));
+    }
+    if (kt > warp_last) continue;   // every key of the tile is in this warp's future
+    float s[BT / 8][4];
 #pragma unroll
-    for (int nt = 0; nt < BKV / 8; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f; }
-    mm_rows<BKV / 8>(s, Qs + warp * 16 * LD, Ks, g, t);
+    for (int nt = 0; nt < BT / 8; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f; }
+    mm_rows<BT / 8, true>(s, Qh + warp * 16 * LD, Ql + warp * 16 * LD, Kh, Kl, lane);
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int nt = 0; nt < BKV / 8; ++nt)
+    for (int nt = 0; nt < BT / 8; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int h = e >> 1, kj = kt + nt * 8 + 2 * t + (e & 1);
@@ -173,7 +247,7 @@ __global__ void __launch_bounds__(NTH, 2) attn_mma_fwd_kernel(AttnShape sh, cons
       m_run[h] = m_new;
     }
 #pragma unroll
-    for (int nt = 0; nt < BKV / 8; ++nt)
+    for (int nt = 0; nt < BT / 8; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int h = e >> 1;
@@ -188,7 +262,7 @@ __global__ void __launch_bounds__(NTH, 2) attn_mma_fwd_kernel(AttnShape sh, cons
     }
 #pragma unroll
     for (int nt = 0; nt < HD / 8; ++nt) { o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0]; o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1]; }
-    mm_perm<BKV / 8>(o, s, Vs, g, t);
+    mm_perm<BT / 8>(o, s, Vh, Vl, g, t);
   }
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -204,54 +278,63 @@ __global__ void __launch_bounds__(NTH, 2) attn_mma_fwd_kernel(AttnShape sh, cons
 }
 
 // ------------------------------------------------------------------ dK / dV
-// CTA = 64 keys of one (batch, kv head), 16 per warp; walks the group's query heads and 32-query
+// CTA = 128 keys of one (batch, kv head), 16 per warp; walks the group's query heads and 32-query
 // tiles.  The warp computes S^T and dP^T (keys x queries) so that both gradients accumulate in its
-// own registers: no atomics, a fixed summation order.
-__global__ void __launch_bounds__(NTH, 2) attn_mma_dkv_kernel(AttnShape sh, const float* __restrict__ q, const float* __restrict__ k,
+// own registers: no atomics, a fixed summation order.  A warp skips the query tiles that lie wholly
+// before its own 16 keys.
+__global__ void __launch_bounds__(NTH, 1) attn_mma_dkv_kernel(AttnShape sh, const float* __restrict__ q, const float* __restrict__ k,
                                                               const float* __restrict__ v, const float* __restrict__ dout,
                                                               const float* __restrict__ lse, const float* __restrict__ delta,
                                                               float* __restrict__ dk, float* __restrict__ dv, int accumulate) {
-  constexpr int BQ = 32, BKV = 64;
   extern __shared__ __align__(16) float smem[];
-  float* Ks = smem; float* Vs = Ks + BKV * LD; float* Qs = Vs + BKV * LD; float* dOs = Qs + BQ * LD;
-  __shared__ float lse_s[BQ], delta_s[BQ];
+  float* Ks = smem; float* Vs = Ks + BM * LD; float* Qh = Vs + BM * LD; float* Ql = Qh + BT * LD; float* dOh = Ql + BT * LD; float* dOl = dOh + BT * LD;
+  __shared__ float lse_s[BT], delta_s[BT];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int bh = blockIdx.y, b = bh / sh.Hkv, hk = bh % sh.Hkv, ratio = sh.Hq / sh.Hkv;
-  const int k0 = blockIdx.x * BKV, kvalid = min(BKV, sh.Tk - k0), offset = sh.offset0;
+  const int k0 = blockIdx.x * BM, kvalid = min(BM, sh.Tk - k0), offset = sh.offset0;
   const float* kg = k + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride + (int64_t)k0 * sh.kv_tstride;
   const float* vg = v + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride + (int64_t)k0 * sh.kv_tstride;
-  load_tile(Ks, kg, sh.kv_tstride, BKV, kvalid);
-  load_tile(Vs, vg, sh.kv_tstride, BKV, kvalid);
+  load_tile(Ks, kg, sh.kv_tstride, BM, kvalid);
+  load_tile(Vs, vg, sh.kv_tstride, BM, kvalid);
   float adk[HD / 8][4], adv[HD / 8][4];
 #pragma unroll
   for (int nt = 0; nt < HD / 8; ++nt) { adk[nt][0] = adk[nt][1] = adk[nt][2] = adk[nt][3] = 0.0f; adv[nt][0] = adv[nt][1] = adv[nt][2] = adv[nt][3] = 0.0f; }
   int q_begin = max(0, k0 - offset);
-  q_begin = (q_begin / BQ) * BQ;
+  q_begin = (q_begin / BT) * BT;
   int q_end = sh.Tq;
   if (sh.window >= 0) q_end = min(sh.Tq, k0 + kvalid - 1 + sh.window - offset + 1);
   const int kj2[2] = {k0 + warp * 16 + g, k0 + warp * 16 + g + 8};
-  for (int h = 0; h < ratio; ++h) {
-    const int hq = hk * ratio + h;
-    for (int q0 = q_begin; q0 < q_end; q0 += BQ) {
-      const int qvalid = min(BQ, sh.Tq - q0);
-      const float* qg = q + (int64_t)b * sh.q_bstride + (int64_t)q0 * sh.q_tstride + (int64_t)hq * HD;
-      const float* dog = dout + (int64_t)b * sh.o_bstride + (int64_t)q0 * sh.o_tstride + (int64_t)hq * HD;
+  const int warp_first = k0 + warp * 16;   // first key of this warp
+  // one flat sequence of (query head, query tile) steps, so that the next step's tiles can be fetched early
+  const int n_qt = q_end > q_begin ? (q_end - q_begin + BT - 1) / BT : 0, n_steps = ratio * n_qt;
+  TileRegs qr, dor;
+  auto fetch_step = [&](int step) {
+    const int hq = hk * ratio + step / n_qt, q0 = q_begin + (step % n_qt) * BT, qvalid = min(BT, sh.Tq - q0);
+    fetch_tile(qr, q + (int64_t)b * sh.q_bstride + (int64_t)q0 * sh.q_tstride + (int64_t)hq * HD, sh.q_tstride, qvalid);
+    fetch_tile(dor, dout + (int64_t)b * sh.o_bstride + (int64_t)q0 * sh.o_tstride + (int64_t)hq * HD, sh.o_tstride, qvalid);
+  };
+  if (n_steps > 0) fetch_step(0);
+  for (int step = 0; step < n_steps; ++step) {
+    {
+      const int hq = hk * ratio + step / n_qt, q0 = q_begin + (step % n_qt) * BT;
       __syncthreads();
-      load_tile(Qs, qg, sh.q_tstride, BQ, qvalid);
-      load_tile(dOs, dog, sh.o_tstride, BQ, qvalid);
-      if (threadIdx.x < BQ) {
+      stash_tile(qr, Qh, Ql);
+      stash_tile(dor, dOh, dOl);
+      if (threadIdx.x < BT) {
         const int qi = q0 + threadIdx.x;
         lse_s[threadIdx.x] = qi < sh.Tq ? lse[((int64_t)b * sh.Hq + hq) * sh.Tq + qi] : 0.0f;
         delta_s[threadIdx.x] = qi < sh.Tq ? delta[((int64_t)b * sh.Hq + hq) * sh.Tq + qi] : 0.0f;
       }
       __syncthreads();
-      float st[BQ / 8][4], dpt[BQ / 8][4];
+      if (step + 1 < n_steps) fetch_step(step + 1);
+      if (offset + q0 + BT - 1 < warp_first) continue;   // every query of the tile precedes this warp's keys
+      float st[BT / 8][4], dpt[BT / 8][4];
 #pragma unroll
-      for (int nt = 0; nt < BQ / 8; ++nt) { st[nt][0] = st[nt][1] = st[nt][2] = st[nt][3] = 0.0f; dpt[nt][0] = dpt[nt][1] = dpt[nt][2] = dpt[nt][3] = 0.0f; }
-      mm_rows<BQ / 8>(st, Ks + warp * 16 * LD, Qs, g, t);
-      mm_rows<BQ / 8>(dpt, Vs + warp * 16 * LD, dOs, g, t);
+      for (int nt = 0; nt < BT / 8; ++nt) { st[nt][0] = st[nt][1] = st[nt][2] = st[nt][3] = 0.0f; dpt[nt][0] = dpt[nt][1] = dpt[nt][2] = dpt[nt][3] = 0.0f; }
+      mm_rows<BT / 8, false>(st, Ks + warp * 16 * LD, nullptr, Qh, Ql, lane);
+      mm_rows<BT / 8, false>(dpt, Vs + warp * 16 * LD, nullptr, dOh, dOl, lane);
 #pragma unroll
-      for (int nt = 0; nt < BQ / 8; ++nt)
+      for (int nt = 0; nt < BT / 8; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int il = nt * 8 + 2 * t + (e & 1), qi = q0 + il, qpos = offset + qi, kj = kj2[e >> 1];
@@ -261,8 +344,8 @@ __global__ void __launch_bounds__(NTH, 2) attn_mma_dkv_kernel(AttnShape sh, cons
           st[nt][e] = p;
           dpt[nt][e] = p * (dpt[nt][e] - delta_s[il]);
         }
-      mm_perm<BQ / 8>(adv, st, dOs, g, t);
-      mm_perm<BQ / 8>(adk, dpt, Qs, g, t);
+      mm_perm<BT / 8>(adv, st, dOh, dOl, g, t);
+      mm_perm<BT / 8>(adk, dpt, Qh, Ql, g, t);
     }
   }
 #pragma unroll
@@ -283,23 +366,22 @@ __global__ void __launch_bounds__(NTH, 2) attn_mma_dkv_kernel(AttnShape sh, cons
 }
 
 // ------------------------------------------------------------------ dQ
-// CTA = 64 queries of one (batch, query head), 16 per warp; walks 32-key tiles.
-__global__ void __launch_bounds__(NTH, 2) attn_mma_dq_kernel(AttnShape sh, const float* __restrict__ q, const float* __restrict__ k,
+// CTA = 128 queries of one (batch, query head), 16 per warp; walks 32-key tiles.
+__global__ void __launch_bounds__(NTH, 1) attn_mma_dq_kernel(AttnShape sh, const float* __restrict__ q, const float* __restrict__ k,
                                                              const float* __restrict__ v, const float* __restrict__ dout,
                                                              const float* __restrict__ lse, const float* __restrict__ delta,
                                                              float* __restrict__ dq, int accumulate) {
-  constexpr int BQ = 64, BKV = 32;
   extern __shared__ __align__(16) float smem[];
-  float* Qs = smem; float* dOs = Qs + BQ * LD; float* Ks = dOs + BQ * LD; float* Vs = Ks + BKV * LD;
+  float* Qs = smem; float* dOs = Qs + BM * LD; float* Kh = dOs + BM * LD; float* Kl = Kh + BT * LD; float* Vh = Kl + BT * LD; float* Vl = Vh + BT * LD;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int bh = blockIdx.y, b = bh / sh.Hq, hq = bh % sh.Hq, hk = hq / (sh.Hq / sh.Hkv);
-  const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BQ, qvalid = min(BQ, sh.Tq - q0), offset = sh.offset0;
+  const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BM, qvalid = min(BM, sh.Tq - q0), offset = sh.offset0;
   const float* qg = q + (int64_t)b * sh.q_bstride + (int64_t)q0 * sh.q_tstride + (int64_t)hq * HD;
   const float* dog = dout + (int64_t)b * sh.o_bstride + (int64_t)q0 * sh.o_tstride + (int64_t)hq * HD;
   const float* kg = k + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride;
   const float* vg = v + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride;
-  load_tile(Qs, qg, sh.q_tstride, BQ, qvalid);
-  load_tile(dOs, dog, sh.o_tstride, BQ, qvalid);
+  load_tile(Qs, qg, sh.q_tstride, BM, qvalid);
+  load_tile(dOs, dog, sh.o_tstride, BM, qvalid);
   float lse2[2], delta2[2]; int qi2[2]; int32_t qseg[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -313,24 +395,34 @@ __global__ void __launch_bounds__(NTH, 2) attn_mma_dq_kernel(AttnShape sh, const
   float adq[HD / 8][4];
 #pragma unroll
   for (int nt = 0; nt < HD / 8; ++nt) { adq[nt][0] = adq[nt][1] = adq[nt][2] = adq[nt][3] = 0.0f; }
+  const int warp_last = offset + q0 + warp * 16 + 15;
   const int max_qpos = offset + q0 + qvalid - 1;
   const int k_end = min(sh.Tk, max_qpos + 1);
   int k_begin = 0;
   if (sh.window >= 0) k_begin = max(0, offset + q0 - sh.window);
-  k_begin = (k_begin / BKV) * BKV;
-  for (int kt = k_begin; kt < k_end; kt += BKV) {
-    const int kvalid = min(BKV, sh.Tk - kt);
+  k_begin = (k_begin / BT) * BT;
+  TileRegs kr, vr;
+  if (k_begin < k_end) {
+    fetch_tile(kr, kg + (int64_t)k_begin * sh.kv_tstride, sh.kv_tstride, min(BT, sh.Tk - k_begin));
+    fetch_tile(vr, vg + (int64_t)k_begin * sh.kv_tstride, sh.kv_tstride, min(BT, sh.Tk - k_begin));
+  }
+  for (int kt = k_begin; kt < k_end; kt += BT) {
     __syncthreads();
-    load_tile(Ks, kg + (int64_t)kt * sh.kv_tstride, sh.kv_tstride, BKV, kvalid);
-    load_tile(Vs, vg + (int64_t)kt * sh.kv_tstride, sh.kv_tstride, BKV, kvalid);
+    stash_tile(kr, Kh, Kl);
+    stash_tile(vr, Vh, Vl);
     __syncthreads();
-    float s[BKV / 8][4], dp[BKV / 8][4];
+    if (kt + BT < k_end) {   // the next tile travels while this one is used
+      fetch_tile(kr, kg + (int64_t)(kt + BT) * sh.kv_tstride, sh.kv_tstride, min(BT, sh.Tk - kt - BT));
+      fetch_tile(vr, vg + (int64_t)(kt + BT) * sh.kv_tstride, sh.kv_tstride, min(BT, sh.Tk - kt - BT));
+    }
+    if (kt > warp_last) continue;   // every key of the tile is in this warp's future: p = 0
+    float s[BT / 8][4], dp[BT / 8][4];
 #pragma unroll
-    for (int nt = 0; nt < BKV / 8; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f; dp[nt][0] = dp[nt][1] = dp[nt][2] = dp[nt][3] = 0.0f; }
-    mm_rows<BKV / 8>(s, Qs + warp * 16 * LD, Ks, g, t);
-    mm_rows<BKV / 8>(dp, dOs + warp * 16 * LD, Vs, g, t);
+    for (int nt = 0; nt < BT / 8; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f; dp[nt][0] = dp[nt][1] = dp[nt][2] = dp[nt][3] = 0.0f; }
+    mm_rows<BT / 8, false>(s, Qs + warp * 16 * LD, nullptr, Kh, Kl, lane);
+    mm_rows<BT / 8, false>(dp, dOs + warp * 16 * LD, nullptr, Vh, Vl, lane);
 #pragma unroll
-    for (int nt = 0; nt < BKV / 8; ++nt)
+    for (int nt = 0; nt < BT / 8; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int h = e >> 1, kj = kt + nt * 8 + 2 * t + (e & 1);
@@ -338,7 +430,7 @@ __global__ void __launch_bounds__(NTH, 2) attn_mma_dq_kernel(AttnShape sh, const
         if (qi2[h] < sh.Tq && kj < sh.Tk && !masked(offset + qi2[h], kj, sh.window, sh.segment_ids, sh.seg_len, qseg[h])) p = __expf(s[nt][e] - lse2[h]);
         dp[nt][e] = p * (dp[nt][e] - delta2[h]);
       }
-    mm_perm<BKV / 8>(adq, dp, Ks, g, t);
+    mm_perm<BT / 8>(adq, dp, Kh, Kl, g, t);
   }
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -354,9 +446,8 @@ __global__ void __launch_bounds__(NTH, 2) attn_mma_dq_kernel(AttnShape sh, const
   }
 }
 
-constexpr size_t kSmemFwd = sizeof(float) * (size_t)(3 * 64 * LD);
-constexpr size_t kSmemDkv = sizeof(float) * (size_t)((2 * 64 + 2 * 32) * LD);
-constexpr size_t kSmemDq = sizeof(float) * (size_t)((2 * 64 + 2 * 32) * LD);
+constexpr size_t kSmemAll = sizeof(float) * (size_t)((2 * BM + 4 * BT) * LD);   // the three kernels use the same amount
+constexpr size_t kSmemFwd = kSmemAll, kSmemDkv = kSmemAll, kSmemDq = kSmemAll;
 
 }  // namespace
 
@@ -370,7 +461,7 @@ bool attention_mma_ok(const AttnShape& sh, const void* p0, const void* p1, const
 int attention_mma_forward(const AttnShape& sh, const float* q, const float* k, const float* v, float* out, float* lse, cudaStream_t s) {
   static bool configured = false;
   if (!configured) { GN_CUDA(cudaFuncSetAttribute(attn_mma_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemFwd)); configured = true; }
-  dim3 grid(ceil_div(sh.Tq, 64), sh.B * sh.Hq);
+  dim3 grid(ceil_div(sh.Tq, BM), sh.B * sh.Hq);
   attn_mma_fwd_kernel<<<grid, NTH, kSmemFwd, s>>>(sh, q, k, v, out, lse);
   GN_LAUNCH_CHECK();
   return GN_OK;
@@ -384,10 +475,10 @@ int attention_mma_backward(const AttnShape& sh, const float* q, const float* k, 
     GN_CUDA(cudaFuncSetAttribute(attn_mma_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemDq));
     configured = true;
   }
-  dim3 gkv(ceil_div(sh.Tk, 64), sh.B * sh.Hkv);
+  dim3 gkv(ceil_div(sh.Tk, BM), sh.B * sh.Hkv);
   attn_mma_dkv_kernel<<<gkv, NTH, kSmemDkv, s>>>(sh, q, k, v, dout, lse, delta, dk, dv, accumulate);
   GN_LAUNCH_CHECK();
-  dim3 gq(ceil_div(sh.Tq, 64), sh.B * sh.Hq);
+  dim3 gq(ceil_div(sh.Tq, BM), sh.B * sh.Hq);
   attn_mma_dq_kernel<<<gq, NTH, kSmemDq, s>>>(sh, q, k, v, dout, lse, delta, dq, accumulate);
   GN_LAUNCH_CHECK();
   return GN_OK;
