@@ -150,6 +150,9 @@ struct TcEpilogue {
   // weight rows [g * N, (g + 1) * N) of B; blockIdx.y enumerates (group, 128-row tile) pairs in group order.
   const int32_t* group_counts; int groups;
   int a_mn, b_mn;   // operand arrives MN-major (tensor map over a row-major [K, MN] source) instead of K-major
+  // persistent form: the grid is one CTA per SM and CTA b works on output tiles b, b + gridDim.x, ... of tiles_total
+  // (tile t = column tile t % tiles_n of row tile t / tiles_n); 0 = one tile per CTA, taken from blockIdx
+  int tiles_total, tiles_n;
 };
 
 #ifdef GN_TC_TRACE
@@ -177,10 +180,12 @@ __device__ __forceinline__ float epi_value(const TcEpilogue& e, float acc, float
 // Two-level accumulation.  The tensor core adds into its float32 accumulator with
 // truncation, so the error of one long K loop grows linearly with K (measured: 2e-5 of
 // the largest output at K = 3072).  The K loop is therefore cut into chunks of
-// kChunkBlocks k-blocks; each chunk accumulates from zero in one of two tensor-memory
+// kChunkBlocks k-blocks (384 elements: 2.5e-6 by that measurement; two chunks in flight also let the MMA warp run a
+// whole K = 768 tile ahead of the epilogue warps in the persistent form); each chunk accumulates from zero in one of two tensor-memory
 // buffers and the epilogue warps add the finished chunk into float32 registers with
 // round-to-nearest while the next chunk is being multiplied.
-constexpr int kChunkBlocks = 4;   // 4 x 32 = 128 elements of K per chunk
+constexpr int kChunkBlocks = 4;          // one-tile CTAs: 4 x 32 = 128 elements of K per chunk
+constexpr int kChunkBlocksPersistent = 12;   // persistent form: 384
 
 template <int BN, int STAGES>
 struct TcSmem {
@@ -188,10 +193,15 @@ struct TcSmem {
   static constexpr int B_BYTES = BN * TBK * 4;
   static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + slack for the 1024-byte alignment
+  // output staging of the persistent form: 32 rows x 32 columns (pitch 33) per epilogue warp, outside the pipeline
+  // stages because the next tile's loads are already landing there while a tile is being stored
+  static constexpr int STG_OFFSET = BAR_OFFSET + 256;
+  static constexpr int STG_WARP_FLOATS = 32 * 33;
+  static constexpr int STG_BYTES = (BN > 128 ? 8 : 4) * STG_WARP_FLOATS * 4;
+  static constexpr int TOTAL = STG_OFFSET + STG_BYTES + 1024;  // + slack for the 1024-byte alignment
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool PERSIST>
 __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
                                                          const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
                                                          TcEpilogue ep, int M, int N, int K, int* err) {
@@ -222,12 +232,20 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
     if (g == ep.groups) return;
     m0 = off + t * TBM; b_row0 = g * N + n0;
   }
+  // persistent form: this CTA's tiles are tile0, tile0 + tile_step, ...; otherwise the single tile found above
+  constexpr bool persistent = PERSIST;   // a compile-time form: the one-tile kernel carries none of the tile loop
+  const int tile0 = persistent ? (int)blockIdx.x : 0, tile_step = persistent ? (int)gridDim.x : 1, tile_end = persistent ? ep.tiles_total : 1;
+  auto tile_origin = [&](int t, int& tm0, int& tn0, int& tb0) {
+    if (persistent) { tm0 = (t / ep.tiles_n) * TBM; tn0 = (t % ep.tiles_n) * BN; tb0 = tn0; }
+    else { tm0 = m0; tn0 = n0; tb0 = b_row0; }
+  };
   // split-K: CTA z works on k-blocks [kb0, kb0 + nk) and writes a partial tile
   const int nk_total = (K + TBK - 1) / TBK;
   const int per_split = (nk_total + (int)gridDim.z - 1) / (int)gridDim.z;
   const int kb0 = (int)blockIdx.z * per_split;
   const int nk = max(0, min(per_split, nk_total - kb0));
-  const int nchunks = (nk + kChunkBlocks - 1) / kChunkBlocks;
+  constexpr int chunk_blocks = PERSIST ? kChunkBlocksPersistent : kChunkBlocks;
+  const int nchunks = (nk + chunk_blocks - 1) / chunk_blocks;
   if (gridDim.z > 1) ep.C += (int64_t)blockIdx.z * ep.split_stride;
 
   if (threadIdx.x == 0) {
@@ -250,32 +268,37 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      for (int kb = 0; kb < nk; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t round = (uint32_t)(kb / STAGES);
-        if (kb >= STAGES && !mbar_wait(empty_bar(s), (round - 1) & 1u)) { failed = true; break; }
-        const uint32_t st = base + (uint32_t)s * S::STAGE_BYTES;
-        if (kb < 256) TC_TRACE(kb);
-        mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
-        if (ep.a_mn) {
+      int it = 0;   // k-blocks issued so far, over all of this CTA's tiles
+      for (int t = tile0; t < tile_end && !failed; t += tile_step) {
+        int tm0, tn0, tb0;
+        tile_origin(t, tm0, tn0, tb0);
+        for (int kb = 0; kb < nk; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t round = (uint32_t)(it / STAGES);
+          if (it >= STAGES && !mbar_wait(empty_bar(s), (round - 1) & 1u)) { failed = true; break; }
+          const uint32_t st = base + (uint32_t)s * S::STAGE_BYTES;
+          if (it < 256) TC_TRACE(it);
+          mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
+          if (ep.a_mn) {
 #pragma unroll
-          for (int j = 0; j < TBM / 32; ++j) {
-            tma_load_2d(st + j * 4096, &tmAh, full_bar(s), m0 + 32 * j, (kb0 + kb) * TBK);
-            tma_load_2d(st + S::A_BYTES + j * 4096, &tmAl, full_bar(s), m0 + 32 * j, (kb0 + kb) * TBK);
+            for (int j = 0; j < TBM / 32; ++j) {
+              tma_load_2d(st + j * 4096, &tmAh, full_bar(s), tm0 + 32 * j, (kb0 + kb) * TBK);
+              tma_load_2d(st + S::A_BYTES + j * 4096, &tmAl, full_bar(s), tm0 + 32 * j, (kb0 + kb) * TBK);
+            }
+          } else {
+            tma_load_2d(st, &tmAh, full_bar(s), (kb0 + kb) * TBK, tm0);
+            tma_load_2d(st + S::A_BYTES, &tmAl, full_bar(s), (kb0 + kb) * TBK, tm0);
           }
-        } else {
-          tma_load_2d(st, &tmAh, full_bar(s), (kb0 + kb) * TBK, m0);
-          tma_load_2d(st + S::A_BYTES, &tmAl, full_bar(s), (kb0 + kb) * TBK, m0);
-        }
-        if (ep.b_mn) {
+          if (ep.b_mn) {
 #pragma unroll
-          for (int j = 0; j < BN / 32; ++j) {
-            tma_load_2d(st + 2 * S::A_BYTES + j * 4096, &tmBh, full_bar(s), b_row0 + 32 * j, (kb0 + kb) * TBK);
-            tma_load_2d(st + 2 * S::A_BYTES + S::B_BYTES + j * 4096, &tmBl, full_bar(s), b_row0 + 32 * j, (kb0 + kb) * TBK);
+            for (int j = 0; j < BN / 32; ++j) {
+              tma_load_2d(st + 2 * S::A_BYTES + j * 4096, &tmBh, full_bar(s), tb0 + 32 * j, (kb0 + kb) * TBK);
+              tma_load_2d(st + 2 * S::A_BYTES + S::B_BYTES + j * 4096, &tmBl, full_bar(s), tb0 + 32 * j, (kb0 + kb) * TBK);
+            }
+          } else {
+            tma_load_2d(st + 2 * S::A_BYTES, &tmBh, full_bar(s), (kb0 + kb) * TBK, tb0);
+            tma_load_2d(st + 2 * S::A_BYTES + S::B_BYTES, &tmBl, full_bar(s), (kb0 + kb) * TBK, tb0);
           }
-        } else {
-          tma_load_2d(st + 2 * S::A_BYTES, &tmBh, full_bar(s), (kb0 + kb) * TBK, b_row0);
-          tma_load_2d(st + 2 * S::A_BYTES + S::B_BYTES, &tmBl, full_bar(s), (kb0 + kb) * TBK, b_row0);
         }
       }
     }
@@ -283,38 +306,41 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
     // ------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       const uint32_t idesc = instr_desc_tf32(TBM, BN, ep.a_mn, ep.b_mn);
-      for (int c = 0; c < nchunks && !failed; ++c) {
-        const int buf = c & 1;
-        // the epilogue must have drained this buffer's previous chunk
-        if (c >= 2 && !mbar_wait(acc_empty(buf), (uint32_t)(c / 2 - 1) & 1u)) { failed = true; break; }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-        const int kb_end = min(nk, (c + 1) * kChunkBlocks);
-        for (int kb = c * kChunkBlocks; kb < kb_end; ++kb) {
-          const int s = kb % STAGES;
-          if (!mbar_wait(full_bar(s), (uint32_t)(kb / STAGES) & 1u)) { failed = true; break; }
+      int it = 0, gc = 0;   // k-blocks and chunks consumed so far, over all of this CTA's tiles
+      for (int t = tile0; t < tile_end && !failed; t += tile_step) {
+        for (int c = 0; c < nchunks && !failed; ++c, ++gc) {
+          const int buf = gc & 1;
+          // the epilogue must have drained this buffer's previous chunk
+          if (gc >= 2 && !mbar_wait(acc_empty(buf), (uint32_t)(gc / 2 - 1) & 1u)) { failed = true; break; }
           tc_fence_after();
-          if (kb < 256) TC_TRACE(256 + kb);
-          const uint32_t st = base + (uint32_t)s * S::STAGE_BYTES;
-          auto mn_desc = [&](uint32_t addr) { return kMnDesc | (uint64_t)((addr & 0x3FFFFu) >> 4); };
-          const uint64_t ah = ep.a_mn ? mn_desc(st) : smem_desc_sw128(st);
-          const uint64_t al = ep.a_mn ? mn_desc(st + S::A_BYTES) : smem_desc_sw128(st + S::A_BYTES);
-          const uint64_t bh = ep.b_mn ? mn_desc(st + 2 * S::A_BYTES) : smem_desc_sw128(st + 2 * S::A_BYTES);
-          const uint64_t bl = ep.b_mn ? mn_desc(st + 2 * S::A_BYTES + S::B_BYTES) : smem_desc_sw128(st + 2 * S::A_BYTES + S::B_BYTES);
-          // advancing by one instruction's K = 8: K-major +32 bytes inside the 128-byte swizzle row (+2 in the address
-          // field); MN-major the next k-group of 8, 1024 bytes on (+64)
-          const uint64_t a_step = ep.a_mn ? kMnKStep : (uint64_t)((UMMA_K * 4) >> 4), b_step = ep.b_mn ? kMnKStep : (uint64_t)((UMMA_K * 4) >> 4);
+          const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+          const int kb_end = min(nk, (c + 1) * chunk_blocks);
+          for (int kb = c * chunk_blocks; kb < kb_end; ++kb, ++it) {
+            const int s = it % STAGES;
+            if (!mbar_wait(full_bar(s), (uint32_t)(it / STAGES) & 1u)) { failed = true; break; }
+            tc_fence_after();
+            if (it < 256) TC_TRACE(256 + it);
+            const uint32_t st = base + (uint32_t)s * S::STAGE_BYTES;
+            auto mn_desc = [&](uint32_t addr) { return kMnDesc | (uint64_t)((addr & 0x3FFFFu) >> 4); };
+            const uint64_t ah = ep.a_mn ? mn_desc(st) : smem_desc_sw128(st);
+            const uint64_t al = ep.a_mn ? mn_desc(st + S::A_BYTES) : smem_desc_sw128(st + S::A_BYTES);
+            const uint64_t bh = ep.b_mn ? mn_desc(st + 2 * S::A_BYTES) : smem_desc_sw128(st + 2 * S::A_BYTES);
+            const uint64_t bl = ep.b_mn ? mn_desc(st + 2 * S::A_BYTES + S::B_BYTES) : smem_desc_sw128(st + 2 * S::A_BYTES + S::B_BYTES);
+            // advancing by one instruction's K = 8: K-major +32 bytes inside the 128-byte swizzle row (+2 in the address
+            // field); MN-major the next k-group of 8, 1024 bytes on (+64)
+            const uint64_t a_step = ep.a_mn ? kMnKStep : (uint64_t)((UMMA_K * 4) >> 4), b_step = ep.b_mn ? kMnKStep : (uint64_t)((UMMA_K * 4) >> 4);
 #pragma unroll
-          for (int k = 0; k < TBK / UMMA_K; ++k) {
-            const uint64_t aa = a_step * (uint64_t)k, ba = b_step * (uint64_t)k;
-            umma_tf32(d_tmem, al + aa, bh + ba, idesc, (kb > c * kChunkBlocks || k > 0) ? 1u : 0u);
-            umma_tf32(d_tmem, ah + aa, bl + ba, idesc, 1u);
-            umma_tf32(d_tmem, ah + aa, bh + ba, idesc, 1u);
+            for (int k = 0; k < TBK / UMMA_K; ++k) {
+              const uint64_t aa = a_step * (uint64_t)k, ba = b_step * (uint64_t)k;
+              umma_tf32(d_tmem, al + aa, bh + ba, idesc, (kb > c * chunk_blocks || k > 0) ? 1u : 0u);
+              umma_tf32(d_tmem, ah + aa, bl + ba, idesc, 1u);
+              umma_tf32(d_tmem, ah + aa, bh + ba, idesc, 1u);
+            }
+            umma_commit(empty_bar(s));   // the stage is free once these MMAs have read it
+            if (it < 256) TC_TRACE(512 + it);
           }
-          umma_commit(empty_bar(s));   // the stage is free once these MMAs have read it
-          if (kb < 256) TC_TRACE(512 + kb);
+          if (!failed) umma_commit(acc_full(buf));   // this chunk's partial sums are complete
         }
-        if (!failed) umma_commit(acc_full(buf));   // this chunk's partial sums are complete
       }
     }
   } else {
@@ -325,13 +351,17 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
     const int quarter = warp & 3;    // tcgen05.ld: a warp reads lanes [32*(warp%4), +32)
     const int chalf = ((warp - 2) >> 2) * ACC;   // first column of this warp's share
     float acc[ACC];
+    int gc = 0;   // chunks drained so far, over all of this CTA's tiles
+    for (int t = tile0; t < tile_end && !failed; t += tile_step) {
+    int tm0, tn0, tb0;
+    tile_origin(t, tm0, tn0, tb0);
 #pragma unroll
     for (int j = 0; j < ACC; ++j) acc[j] = 0.0f;
-    for (int c = 0; c < nchunks; ++c) {
-      const int buf = c & 1;
-      if (!mbar_wait(acc_full(buf), (uint32_t)(c / 2) & 1u)) { failed = true; break; }
+    for (int c = 0; c < nchunks; ++c, ++gc) {
+      const int buf = gc & 1;
+      if (!mbar_wait(acc_full(buf), (uint32_t)(gc / 2) & 1u)) { failed = true; break; }
       tc_fence_after();
-      if (warp == 2 && lane == 0 && c < 64) TC_TRACE(768 + c);
+      if (warp == 2 && lane == 0 && gc < 64) TC_TRACE(768 + gc);
 #pragma unroll
       for (int c0 = 0; c0 < ACC; c0 += 32) {
         uint32_t r[32];
@@ -343,9 +373,41 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
       tc_fence_before();
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(buf)) : "memory");
-      if (warp == 2 && lane == 0 && c < 64) TC_TRACE(832 + c);
+      if (warp == 2 && lane == 0 && gc < 64) TC_TRACE(832 + gc);
     }
-    if (!failed) {
+    if (!failed && persistent) {
+      // The next tile's loads and MMAs are already running, so the tile leaves through a small staging area of its
+      // own, 32 columns at a time: a thread owns a row of the accumulator, a warp store wants a row segment.
+      float* stg = reinterpret_cast<float*>(gen_base + S::STG_OFFSET) + (size_t)(warp - 2) * S::STG_WARP_FLOATS;
+#pragma unroll
+      for (int c0 = 0; c0 < ACC; c0 += 32) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) stg[lane * 33 + j] = acc[c0 + j];
+        __syncwarp();
+        const int n = tn0 + chalf + c0 + lane;
+        const int64_t row0 = (int64_t)tm0 + quarter * 32;
+        const int rows_valid = (int)min((int64_t)32, (int64_t)M - row0);
+        if (n < N) {
+          float* cp = ep.C + row0 * ep.ldc + n;
+          float* ap = ep.aux ? ep.aux + row0 * ep.ldaux + n : nullptr;
+          float* hp = ep.c_hi ? ep.c_hi + row0 * ep.ldc + n : nullptr;
+          float* lp = ep.c_lo ? ep.c_lo + row0 * ep.ldc + n : nullptr;
+          const bool reads_aux = ep.epi == EPI_RESIDUAL || ep.epi == EPI_RELU2_BWD;
+#pragma unroll 4
+          for (int r = 0; r < rows_valid; ++r) {
+            bool wa = false; float av = 0.0f;
+            const float cold = (ep.epi == EPI_ACCUM) ? cp[(int64_t)r * ep.ldc] : 0.0f;
+            const float ax = reads_aux ? ap[(int64_t)r * ep.ldaux] : 0.0f;
+            const float out = epi_value(ep, stg[r * 33 + lane], ax, cold, wa, av);
+            if (wa) ap[(int64_t)r * ep.ldaux] = av;
+            cp[(int64_t)r * ep.ldc] = out;
+            if (hp) { float h, l; split_tf32(out, h, l); hp[(int64_t)r * ep.ldc] = h; lp[(int64_t)r * ep.ldc] = l; }
+          }
+        }
+        __syncwarp();
+      }
+    }
+    if (!failed && !persistent) {
       // The accumulator row of a thread is scattered (thread = row), so it goes through shared
       // memory first: the pipeline stages are idle once the last chunk has been drained, and
       // each warp then writes whole 512-byte row segments (a thread-per-row store pattern was
@@ -404,6 +466,7 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
         }
       }
     }
+    }   // tiles
   }
   if (failed) {
     atomicExch(err, 1);
@@ -462,6 +525,9 @@ std::mutex g_mu;
 // GN_TC_MN=0 keeps the transposing operand split for products whose operands are stored [K, M] / [K, N].
 // GN_TC_PDL=0 launches the products without programmatic stream serialization.
 const bool g_use_pdl = [] { const char* e = getenv("GN_TC_PDL"); return !(e && e[0] == '0'); }();
+// CTAs of the persistent form: one per SM; GN_TC_PERSISTENT=0 switches the form off, GN_TC_PERSISTENT=<n> runs it on n CTAs
+// (tests use a handful, so that small products walk several tiles per CTA too).
+const int g_persistent_ctas = [] { const char* e = getenv("GN_TC_PERSISTENT"); const int v = e ? atoi(e) : kNumSM; return v < 0 ? 0 : v; }();
 const bool g_allow_mn = [] { const char* e = getenv("GN_TC_MN"); return !(e && e[0] == '0'); }();
 
 
@@ -592,12 +658,23 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
 float* g_splitk_ws = nullptr;
 size_t g_splitk_floats = 0;
 
+// Epilogues that suit the persistent form: those that only write.  Its store goes out 32 columns at a time, one
+// element per lane, while the next tile's operand loads keep the path to L2 busy; epilogues that also read the output
+// or an aux operand (accumulate, residual, relu^2 backward) or write the operand split of a plain product take longer
+// than the K loop they hide behind (measured on d12's training pass: forward 75.8 -> 70.2 ms per 128 sequences with
+// this rule, backward unchanged; with every epilogue persistent the backward lost 6 ms).
+static bool persist_rule_ok(const TcEpilogue& e) {
+  if (e.epi == EPI_RELU2) return true;
+  return (e.epi == EPI_STORE || e.epi == EPI_SOFTCAP) && e.c_hi == nullptr;
+}
+
 template <int BN, int STAGES>
 int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int M, int N, int K, int splits, cudaStream_t s, Partials* leave = nullptr) {
   using S = TcSmem<BN, STAGES>;
   static bool configured = false;
   if (!configured) {
-    GN_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+    GN_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL - S::STG_BYTES));
+    GN_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
     configured = true;
   }
   CUtensorMap mah, mal, mbh, mbl;
@@ -619,14 +696,25 @@ int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int
     ep.C = g_splitk_ws; ep.ldc = N; ep.aux = nullptr; ep.epi = EPI_STORE; ep.split_stride = (int64_t)M * N; ep.c_hi = ep.c_lo = nullptr;
   }
   dim3 grid(ceil_div(N, BN), ceil_div(M, TBM) + ep_in.groups, splits);   // grouped: an upper bound on the sum of per-group tiles
+  // More tiles than SMs and a short K loop: one CTA per SM walks the tiles, so that a tile's store (a third of a
+  // one-tile CTA's life at K = 768: the stores share the path to L2 with the operand loads of every other SM)
+  // overlaps the next tile's K loop.  With long K loops the store is negligible and one-tile CTAs, which the hardware
+  // hands out as SMs free up, balance better than a fixed round-robin (measured on the 16384-deep weight gradient).
+  const int64_t tiles_total = (int64_t)ceil_div(N, BN) * ceil_div(M, TBM);
+  if (g_persistent_ctas > 0 && splits == 1 && ep_in.groups == 0 && tiles_total > g_persistent_ctas && tiles_total < (int64_t)1 << 30 &&
+      K <= 4096 && persist_rule_ok(ep_in)) {
+    ep.tiles_total = (int)tiles_total; ep.tiles_n = ceil_div(N, BN);
+    grid = dim3(g_persistent_ctas, 1, 1);
+  }
   {
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = grid; cfg.blockDim = dim3(64 + 32 * (BN > 128 ? 8 : 4)); cfg.dynamicSmemBytes = S::TOTAL; cfg.stream = s;
+    cfg.gridDim = grid; cfg.blockDim = dim3(64 + 32 * (BN > 128 ? 8 : 4)); cfg.dynamicSmemBytes = ep.tiles_total > 0 ? S::TOTAL : S::TOTAL - S::STG_BYTES; cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = g_use_pdl ? 1 : 0;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    GN_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES>, mah, mal, mbh, mbl, ep, M, N, K, g_err_flag));
+    if (ep.tiles_total > 0) GN_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, true>, mah, mal, mbh, mbl, ep, M, N, K, g_err_flag));
+    else GN_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, false>, mah, mal, mbh, mbl, ep, M, N, K, g_err_flag));
   }
   GN_LAUNCH_CHECK();
   if (leave) {
@@ -677,7 +765,7 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
   } else {
     GN_TRY(split_operand(g.B, g.ldb, g.groups > 0 ? (int64_t)g.groups * g.N : g.N, g.K, g.b_trans == 0, g.b_static != 0, 1, b, s, g_allow_mn));
   }
-  TcEpilogue ep{g.C, g.ldc, g.aux, g.ldaux, g.epilogue, g.scalar, 0, g.c_hi, g.c_lo, g_trace, g.group_counts, g.groups, 0, 0};
+  TcEpilogue ep{g.C, g.ldc, g.aux, g.ldaux, g.epilogue, g.scalar, 0, g.c_hi, g.c_lo, g_trace, g.group_counts, g.groups, 0, 0, 0, 0};
   if (g.groups > 0) return launch_tc<128, 3>(a, b, ep, g.M, g.N, g.K, 1, s, nullptr);
   // Filling the machine when the output has few tiles (the rollout's products have 512 rows):
   // the K loop is split over gridDim.z so that about one CTA per SM runs, each writing a partial

@@ -229,3 +229,18 @@ print(json.dumps({"tokens": t.tolist(), "lengths": l.tolist(), "steps": int(s), 
         assert a["tokens"][r][:a["lengths"][r]] == b["tokens"][r][:b["lengths"][r]]
     la, lb = np.array(a["last"]), np.array(b["last"])
     assert rel_err(lb, la) <= 1e-4     # same arithmetic up to the order of the softmax merge
+
+
+def test_persistent_gemm_form_passes_the_parity_tests():
+    """The tensor-core product walks several output tiles per CTA when there are more tiles than CTAs; on the test
+    shapes that needs a small grid.  The product and gradient parity tests are run again with three persistent CTAs,
+    which sends every epilogue (plain, accumulate, residual, relu^2 and its backward, softcap, operand split) and both
+    tile widths through that form."""
+    import os, subprocess, sys
+    root = os.path.dirname(os.path.dirname(__file__))
+    env = dict(os.environ, GN_TC_PERSISTENT="3")
+    r = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu", "tests/test_gpu_backend.py", "tests/test_gpu_model.py",
+                        "-k", "tensor_core_matmul_faithful or policy_gradient_step or forward_logits or gemm_paths_agree"],
+                       capture_output=True, text=True, env=env, cwd=root)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+    assert " passed" in r.stdout
