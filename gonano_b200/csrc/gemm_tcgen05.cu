@@ -161,7 +161,8 @@ struct TcEpilogue {
 #define TC_TRACE(slot) do { } while (0)
 #endif
 // trace slots: [0,256) producer issue per k-block, [256,512) MMA saw the stage full, [512,768) MMA issued,
-// [768,832) epilogue saw chunk full, [832,896) epilogue drained chunk, 896 start, 897 end
+// [768,832) epilogue saw chunk full, [832,896) epilogue drained chunk, 896 start, 897 end,
+// 898 / 899 / 900 one-tile store: before staging, staged, stored (first epilogue warp)
 
 // aux_in: the value of the aux operand at this element (residual / saved pre-activation).
 __device__ __forceinline__ float epi_value(const TcEpilogue& e, float acc, float aux_in, float cold, bool& write_aux, float& auxv) {
@@ -393,15 +394,37 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
           float* hp = ep.c_hi ? ep.c_hi + row0 * ep.ldc + n : nullptr;
           float* lp = ep.c_lo ? ep.c_lo + row0 * ep.ldc + n : nullptr;
           const bool reads_aux = ep.epi == EPI_RESIDUAL || ep.epi == EPI_RELU2_BWD;
+          if (ep.epi == EPI_ACCUM || reads_aux) {
+            // four rows at a time: first the reads of the block (the output for accumulate, the aux operand), then the
+            // arithmetic and the stores, so that four loads per warp are in flight instead of one
+            for (int r0 = 0; r0 < rows_valid; r0 += 4) {
+              float cold[4], ax[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const bool ok = r0 + i < rows_valid;
+                cold[i] = (ep.epi == EPI_ACCUM && ok) ? cp[(int64_t)(r0 + i) * ep.ldc] : 0.0f;
+                ax[i] = (reads_aux && ok) ? ap[(int64_t)(r0 + i) * ep.ldaux] : 0.0f;
+              }
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int r = r0 + i;
+                if (r < rows_valid) {
+                  bool wa = false; float av = 0.0f;
+                  const float out = epi_value(ep, stg[r * 33 + lane], ax[i], cold[i], wa, av);
+                  cp[(int64_t)r * ep.ldc] = out;
+                  if (hp) { float h, l; split_tf32(out, h, l); hp[(int64_t)r * ep.ldc] = h; lp[(int64_t)r * ep.ldc] = l; }
+                }
+              }
+            }
+          } else {
 #pragma unroll 4
-          for (int r = 0; r < rows_valid; ++r) {
-            bool wa = false; float av = 0.0f;
-            const float cold = (ep.epi == EPI_ACCUM) ? cp[(int64_t)r * ep.ldc] : 0.0f;
-            const float ax = reads_aux ? ap[(int64_t)r * ep.ldaux] : 0.0f;
-            const float out = epi_value(ep, stg[r * 33 + lane], ax, cold, wa, av);
-            if (wa) ap[(int64_t)r * ep.ldaux] = av;
-            cp[(int64_t)r * ep.ldc] = out;
-            if (hp) { float h, l; split_tf32(out, h, l); hp[(int64_t)r * ep.ldc] = h; lp[(int64_t)r * ep.ldc] = l; }
+            for (int r = 0; r < rows_valid; ++r) {
+              bool wa = false; float av = 0.0f;
+              const float out = epi_value(ep, stg[r * 33 + lane], 0.0f, 0.0f, wa, av);
+              if (wa) ap[(int64_t)r * ep.ldaux] = av;
+              cp[(int64_t)r * ep.ldc] = out;
+              if (hp) { float h, l; split_tf32(out, h, l); hp[(int64_t)r * ep.ldc] = h; lp[(int64_t)r * ep.ldc] = l; }
+            }
           }
         }
         __syncwarp();
@@ -416,9 +439,11 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
       constexpr int LPR = ACC / 4;             // lanes that cover one row with float4
       constexpr int RPI = 32 / LPR;            // rows a warp writes per iteration
       float* stg = reinterpret_cast<float*>(gen_base) + (size_t)(warp - 2) * 32 * PITCH;
+      if (warp == 2 && lane == 0) TC_TRACE(898);
 #pragma unroll
       for (int j = 0; j < ACC; j += 4) *reinterpret_cast<float4*>(&stg[lane * PITCH + j]) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
       __syncwarp();
+      if (warp == 2 && lane == 0) TC_TRACE(899);
       const bool vec_ok = (ep.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.C) & 15) == 0) &&
                           (ep.aux == nullptr || ((ep.ldaux % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.aux) & 15) == 0)));
       const int col = (lane % LPR) * 4;
@@ -466,6 +491,7 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
         }
       }
     }
+    if (warp == 2 && lane == 0) TC_TRACE(900);
     }   // tiles
   }
   if (failed) {
@@ -658,16 +684,6 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
 float* g_splitk_ws = nullptr;
 size_t g_splitk_floats = 0;
 
-// Epilogues that suit the persistent form: those that only write.  Its store goes out 32 columns at a time, one
-// element per lane, while the next tile's operand loads keep the path to L2 busy; epilogues that also read the output
-// or an aux operand (accumulate, residual, relu^2 backward) or write the operand split of a plain product take longer
-// than the K loop they hide behind (measured on d12's training pass: forward 75.8 -> 70.2 ms per 128 sequences with
-// this rule, backward unchanged; with every epilogue persistent the backward lost 6 ms).
-static bool persist_rule_ok(const TcEpilogue& e) {
-  if (e.epi == EPI_RELU2) return true;
-  return (e.epi == EPI_STORE || e.epi == EPI_SOFTCAP) && e.c_hi == nullptr;
-}
-
 template <int BN, int STAGES>
 int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int M, int N, int K, int splits, cudaStream_t s, Partials* leave = nullptr) {
   using S = TcSmem<BN, STAGES>;
@@ -696,13 +712,15 @@ int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int
     ep.C = g_splitk_ws; ep.ldc = N; ep.aux = nullptr; ep.epi = EPI_STORE; ep.split_stride = (int64_t)M * N; ep.c_hi = ep.c_lo = nullptr;
   }
   dim3 grid(ceil_div(N, BN), ceil_div(M, TBM) + ep_in.groups, splits);   // grouped: an upper bound on the sum of per-group tiles
-  // More tiles than SMs and a short K loop: one CTA per SM walks the tiles, so that a tile's store (a third of a
-  // one-tile CTA's life at K = 768: the stores share the path to L2 with the operand loads of every other SM)
+  // More tiles than SMs and a short K loop: one CTA per SM walks the tiles, so that a tile's store (a fifth of a
+  // one-tile CTA's life at K = 768: an SM stores about 16 bytes per clock, 128 KB take 8-11 thousand cycles)
   // overlaps the next tile's K loop.  With long K loops the store is negligible and one-tile CTAs, which the hardware
   // hands out as SMs free up, balance better than a fixed round-robin (measured on the 16384-deep weight gradient).
+  // Epilogues that read (accumulate, residual, relu^2 backward) gain nothing from the form but lose nothing either
+  // once their reads are issued four rows at a time.
   const int64_t tiles_total = (int64_t)ceil_div(N, BN) * ceil_div(M, TBM);
   if (g_persistent_ctas > 0 && splits == 1 && ep_in.groups == 0 && tiles_total > g_persistent_ctas && tiles_total < (int64_t)1 << 30 &&
-      K <= 4096 && persist_rule_ok(ep_in)) {
+      K <= 4096) {
     ep.tiles_total = (int)tiles_total; ep.tiles_n = ceil_div(N, BN);
     grid = dim3(g_persistent_ctas, 1, 1);
   }

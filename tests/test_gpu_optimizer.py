@@ -158,41 +158,46 @@ def test_rl_step_with_optimizer_end_to_end(oracle):
     gm.close(); ctx.close()
 
 
-def test_sharded_optimizer_equals_whole_step():
-    """Two shards emulated on one GPU with two replicas: each updates the tensors it owns and stages them; the SUM of
-    the two staged buffers (what the second all-reduce produces) installed by optimizer_finish equals the un-sharded
-    step bit for bit, and between them the shards own every tensor exactly once."""
+@pytest.mark.parametrize("world", [2, 8])
+def test_sharded_optimizer_equals_whole_step(world):
+    """The shards of a `world`-rank step emulated on one GPU with one replica each: every replica updates the tensors it
+    owns and stages them; the SUM of the staged buffers (what the second all-reduce produces) installed by
+    optimizer_finish equals the un-sharded step bit for bit, and between them the shards own every tensor exactly once."""
     from gonano_b200.session import Context, Model
     cfg = synthetic.dense_config("c1")
     ctx = Context(0)
-    whole, a, b = Model(ctx, **cfg), Model(ctx, **cfg), Model(ctx, **cfg)
+    whole = Model(ctx, **cfg)
+    shards = [Model(ctx, **cfg) for _ in range(world)]
+    everyone = [whole] + shards
     rng = np.random.default_rng(11)
     grads = {}
     for pname, value in synthetic.fill_weights(whole.names, whole.shape, 4, std=0.05):
         grads[pname] = (rng.standard_normal(value.size) * 0.01).astype(np.float32)
-        for m in (whole, a, b):
+        for m in everyone:
             m.upload(pname, value)
-    for m in (whole, a, b):
+    for m in everyone:
         m.optimizer_init()
     for step in range(2):
         for pname in whole.names:
             g = grads[pname] * np.float32(1 + step)
-            for m in (whole, a, b):
+            for m in everyone:
                 m.upload_grad(pname, g)
         whole.optimizer_step()
-        a.optimizer_step_shard(0, 2); b.optimizer_step_shard(1, 2)
-        owned_once = True
+        for rank, m in enumerate(shards):
+            m.optimizer_step_shard(rank, world)
         for pname in whole.names:
-            ga, gb = a.grad(pname), b.grad(pname)
-            owned_once &= not (np.any(ga) and np.any(gb))
-            total = ga + gb
-            a.upload_grad(pname, total); b.upload_grad(pname, total)
-        assert owned_once
-        a.optimizer_finish(); b.optimizer_finish()
+            staged = [m.grad(pname) for m in shards]
+            assert sum(1 for g in staged if np.any(g)) <= 1, pname          # owned once (an all-zero update has no owner to see)
+            total = np.sum(staged, axis=0, dtype=np.float32)
+            for m in shards:
+                m.upload_grad(pname, total)
+        for m in shards:
+            m.optimizer_finish()
         for pname in whole.names:
             want = whole.download(pname)
-            assert np.array_equal(a.download(pname), want) and np.array_equal(b.download(pname), want), (step, pname)
-            assert not np.any(a.grad(pname))
-    for m in (whole, a, b):
+            for m in shards:
+                assert np.array_equal(m.download(pname), want), (step, pname)
+            assert not np.any(shards[0].grad(pname))
+    for m in everyone:
         m.close()
     ctx.close()
