@@ -244,3 +244,60 @@ def test_persistent_gemm_form_passes_the_parity_tests():
                        capture_output=True, text=True, env=env, cwd=root)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
     assert " passed" in r.stdout
+
+
+def test_full_size_d12_rollout_and_step_properties(ctx):
+    """The d12 workload at its full size (64 prompts x 8 rollouts = 512 rows, 128 prompt tokens, 256 new tokens), where
+    the oracle cannot follow, through properties that do not depend on the size:
+    the rollout is a deterministic function of the seeds; the greedy rollout of the cached decode path is the argmax of
+    the training-style forward over the same sequences (the engine == naive recompute invariant of
+    inference/inference_test.go:110-123, here across two different kernel paths); advantages are centred per group;
+    the loss is linear in the advantages and the gradients are finite."""
+    from gonano_b200.session import Model, build_batch
+    from gonano_b200.backend import group_advantage
+    cfg = synthetic.dense_config("d12")
+    gm = Model(ctx, **cfg)
+    for pname, value in synthetic.fill_weights(gm.names, gm.shape, 0):
+        gm.upload(pname, value)
+    V, P, G, NEW = cfg["vocab_size"], 64, 8, 256
+    prompts = synthetic.prompts(P, 128, V, seed=1)
+    seeds = np.arange(P, dtype=np.uint64)
+
+    t1, l1, s1, _ = gm.generate_batch(prompts, G, NEW, 1.0, 50, seeds)
+    t2, l2, s2, _ = gm.generate_batch(prompts, G, NEW, 1.0, 50, seeds)
+    assert s1 == s2 and np.array_equal(l1, l2) and np.array_equal(t1, t2)
+    assert len({tuple(t1[r, :16]) for r in range(G)}) > 1          # rollouts of one prompt differ
+
+    # greedy decode against the training-style forward on 4 of the rows (logits of 4 x 383 x 32768 floats)
+    tg, lg, _, _ = gm.generate_batch(prompts, G, NEW, 0.0, 0, seeds)
+    rows = [0, 137, 300, 511]
+    seqs = np.stack([np.concatenate([prompts[r // G], tg[r, :NEW - 1]]) for r in rows]).astype(np.int32)
+    logits = gm.forward(seqs)                                        # [4, 383, V]; position 127 + j predicts new token j
+    agree, total = 0, 0
+    for i, r in enumerate(rows):
+        n = int(lg[r])
+        pred = logits[i, 127:127 + n]
+        top = np.argmax(pred, axis=1)
+        for j in range(n):
+            total += 1
+            if top[j] == tg[r, j]:
+                agree += 1
+            else:   # a disagreement must be a near tie between the two candidates
+                gap = abs(float(pred[j, top[j]]) - float(pred[j, tg[r, j]]))
+                assert gap <= 1e-3 * max(1.0, float(np.max(np.abs(pred[j])))), (r, j, gap)
+    assert total > 0 and agree >= 0.99 * total
+
+    rewards = synthetic.bernoulli_rewards(P * G, 5)
+    adv = group_advantage(rewards, G, 0)
+    assert np.max(np.abs(adv.reshape(P, G).astype(np.float64).sum(axis=1))) <= 1e-5
+    inputs, targets, max_len = build_batch(prompts, G, t1, l1, V - 7)
+    gm.zero_grad()
+    loss1, _, _, _ = gm.policy_gradient_step(inputs, targets, adv, float(max_len), 0)
+    g1 = gm.grad("transformer.h.5.mlp.c_proj.weight").copy()
+    gm.zero_grad()
+    loss2, _, _, _ = gm.policy_gradient_step(inputs, targets, adv * np.float32(2), float(max_len), 0)
+    g2 = gm.grad("transformer.h.5.mlp.c_proj.weight")
+    assert np.isfinite(loss1) and np.all(np.isfinite(g1)) and np.any(g1)
+    assert abs(loss2 - 2 * loss1) <= 1e-4 * abs(loss1) + 1e-9
+    assert rel_err(g2, 2 * g1) <= 1e-4
+    gm.close()
