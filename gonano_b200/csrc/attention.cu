@@ -908,8 +908,8 @@ int attention_combine_launch(const float* acc, const float* mx, const float* sm,
 // warp reads one K row and one V row as a single coalesced 512-byte request.
 // All query heads of the group are served from the same K/V registers.
 // Warp partials are merged through shared memory, splits through a second pass.
-template <int DP, int RATIO, int U>
-__global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restrict__ q, int64_t q_rstride, const float* __restrict__ kcache,
+template <int DP, int RATIO, int U, int NW>
+__global__ void __launch_bounds__(32 * NW) attn_decode_kernel(const float* __restrict__ q, int64_t q_rstride, const float* __restrict__ kcache,
                                                           const float* __restrict__ vcache, int64_t row_stride, int64_t head_stride,
                                                           const int32_t* __restrict__ ctx_len, int Hq, int Hkv, int D, int window, float* __restrict__ out,
                                                           int64_t o_rstride, float* __restrict__ part_acc, float* __restrict__ part_ms, int splits,
@@ -958,7 +958,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restric
       }
     }
   };
-  // U keys per warp per iteration (kj, kj + 4, ...), and the next U are requested before these are used: 2U rows per
+  // NW warps share the keys of the CTA round-robin (small grids use more warps per CTA instead of more splits, which
+  // would need a combine pass).  U keys per warp per iteration (kj, kj + NW, ...), and the next U are requested before these are used: 2U rows per
   // warp in flight, one running-maximum update per U keys.  U = 1 keeps more warps resident (large batches); U = 2
   // shortens the dependent chain when there are few warps per SM.
   float nk[U][E], nv[U][E];
@@ -966,9 +967,9 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restric
   for (int u = 0; u < U; ++u) {
 #pragma unroll
     for (int e = 0; e < E; ++e) { nk[u][e] = 0.0f; nv[u][e] = 0.0f; }
-    if (k0 + warp + 4 * u < k1) load_row(k0 + warp + 4 * u, nk[u], nv[u]);
+    if (k0 + warp + NW * u < k1) load_row(k0 + warp + NW * u, nk[u], nv[u]);
   }
-  for (int kj = k0 + warp; kj < k1; kj += 4 * U) {
+  for (int kj = k0 + warp; kj < k1; kj += NW * U) {
     float kv[U][E], vv[U][E];
 #pragma unroll
     for (int u = 0; u < U; ++u)
@@ -976,7 +977,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restric
       for (int e = 0; e < E; ++e) { kv[u][e] = nk[u][e]; vv[u][e] = nv[u][e]; }
 #pragma unroll
     for (int u = 0; u < U; ++u)
-      if (kj + 4 * (U + u) < k1) load_row(kj + 4 * (U + u), nk[u], nv[u]);
+      if (kj + NW * (U + u) < k1) load_row(kj + NW * (U + u), nk[u], nv[u]);
 #pragma unroll
     for (int h = 0; h < RATIO; ++h) {
       float d[U];
@@ -993,13 +994,13 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restric
       float mn = m[h];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        if (u > 0 && kj + 4 * u >= k1) d[u] = -INFINITY;
+        if (u > 0 && kj + NW * u >= k1) d[u] = -INFINITY;
         mn = fmaxf(mn, d[u]);
       }
       const float alpha = (m[h] == -INFINITY) ? 0.0f : __expf(m[h] - mn);
       float p[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) p[u] = (u > 0 && kj + 4 * u >= k1) ? 0.0f : __expf(d[u] - mn);
+      for (int u = 0; u < U; ++u) p[u] = (u > 0 && kj + NW * u >= k1) ? 0.0f : __expf(d[u] - mn);
       float ls = l[h] * alpha;
 #pragma unroll
       for (int u = 0; u < U; ++u) ls += p[u];
@@ -1014,9 +1015,9 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restric
       m[h] = mn;
     }
   }
-  // merge the 4 warps
-  __shared__ float sm_o[4][RATIO][DP];
-  __shared__ float sm_m[4][RATIO], sm_l[4][RATIO];
+  // merge the warps
+  __shared__ float sm_o[NW][RATIO][DP];
+  __shared__ float sm_m[NW][RATIO], sm_l[NW][RATIO];
 #pragma unroll
   for (int h = 0; h < RATIO; ++h) {
 #pragma unroll
@@ -1024,13 +1025,15 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restric
     if (lane == 0) { sm_m[warp][h] = m[h]; sm_l[warp][h] = l[h]; }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < RATIO * DP; idx += 128) {
+  for (int idx = threadIdx.x; idx < RATIO * DP; idx += 32 * NW) {
     int h = idx / DP, c = idx % DP;
     if (c >= D) continue;
-    float gm = fmaxf(fmaxf(sm_m[0][h], sm_m[1][h]), fmaxf(sm_m[2][h], sm_m[3][h]));
+    float gm = sm_m[0][h];
+#pragma unroll
+    for (int w = 1; w < NW; ++w) gm = fmaxf(gm, sm_m[w][h]);
     float tot = 0, acc = 0;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
+    for (int w = 0; w < NW; ++w) {
       float sc = (sm_m[w][h] == -INFINITY) ? 0.0f : __expf(sm_m[w][h] - gm);
       tot += sm_l[w][h] * sc;
       acc += sm_o[w][h][c] * sc;
@@ -1209,11 +1212,19 @@ int attention_decode_prefix_splits(int rows, int group, int Hq, int Hkv, int D, 
   return tiles;
 }
 
+// Warps per CTA of the per-row kernel: 4 on grids that fill the machine, 8 or 16 on smaller ones.
+int attention_decode_warps(int rows, int Hkv) {
+  const int base = rows * Hkv;
+  return base >= kNumSM * 4 ? 4 : (base >= kNumSM * 2 ? 8 : 16);
+}
+
 int attention_decode_splits(int rows, int Hkv, int max_ctx) {
-  // Fill the machine: aim at >= 4 CTAs per SM, at least 64 keys per split.
-  int base = rows * Hkv;
+  // Fill the machine: aim at the equivalent of >= 4 four-warp CTAs per SM, at least 64 keys per four warps.  The
+  // warps of a CTA come first (no second pass); only very small batches also split the context over CTAs.
+  const int wf = attention_decode_warps(rows, Hkv) / 4;
+  int base = rows * Hkv * wf;
   int splits = 1;
-  while (base * splits < kNumSM * 4 && max_ctx / (splits * 2) >= 64 && splits < 16) splits *= 2;
+  while (base * splits < kNumSM * 4 && max_ctx / (splits * wf * 2) >= 64 && splits < 16) splits *= 2;
   return splits;
 }
 
@@ -1233,13 +1244,18 @@ static int decode_go(const float* q, int64_t q_rstride, const float* kcache, con
   }
   const int nslots = psplits + splits;
   dim3 grid(rows * Hkv, splits);
-  // fewer than ~5 CTAs per SM: two keys per iteration (shorter chain); otherwise one (more resident warps)
-  if ((int64_t)rows * Hkv * splits < (int64_t)kNumSM * 5)
-    attn_decode_kernel<DP, RATIO, 2><<<grid, 128, 0, s>>>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, Hq, Hkv, D, window, out, o_rstride,
-                                                          part_acc, part_ms, splits, out_hi, out_lo, psplits ? prefix_len : 0, psplits, nslots);
-  else
-    attn_decode_kernel<DP, RATIO, 1><<<grid, 128, 0, s>>>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, Hq, Hkv, D, window, out, o_rstride,
-                                                          part_acc, part_ms, splits, out_hi, out_lo, psplits ? prefix_len : 0, psplits, nslots);
+  // fewer than the equivalent of ~5 four-warp CTAs per SM: two keys per iteration (shorter chain); otherwise one
+  // (more resident warps)
+  const int nw = attention_decode_warps(rows, Hkv);
+#define GN_DEC_LAUNCH(UU, WW) attn_decode_kernel<DP, RATIO, UU, WW><<<grid, 32 * WW, 0, s>>>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, Hq, Hkv, D, window, out, o_rstride, \
+                                                                              part_acc, part_ms, splits, out_hi, out_lo, psplits ? prefix_len : 0, psplits, nslots)
+  // the warps' partial results meet in static shared memory (NW x RATIO x DP floats): wide groups get fewer warps
+  constexpr int kMaxW = RATIO * DP * 16 <= 10240 ? 16 : (RATIO * DP * 8 <= 10240 ? 8 : 4);
+  if (nw == 16 && kMaxW >= 16) { if constexpr (kMaxW >= 16) GN_DEC_LAUNCH(2, 16); }
+  else if (nw >= 8 && kMaxW >= 8) { if constexpr (kMaxW >= 8) GN_DEC_LAUNCH(2, 8); }
+  else if ((int64_t)rows * Hkv * splits < (int64_t)kNumSM * 5) GN_DEC_LAUNCH(2, 4);
+  else GN_DEC_LAUNCH(1, 4);
+#undef GN_DEC_LAUNCH
   GN_LAUNCH_CHECK();
   if (splits > 1) {
     attn_decode_combine_kernel<<<rows * Hq, 128, 0, s>>>(part_acc, part_ms, nslots, Hq, D, out, o_rstride, out_hi, out_lo);
