@@ -43,7 +43,7 @@ def emit(line: dict) -> None:
         os.write(_STDOUT_FD, data)
 
 
-GEMM_TRAFFIC_BYTES = 282038272   # 120.4 MB read + 161.7 MB written: ncu capture of `profile_cli kernel gemm_nt 16384 3072 768` (profiles/gemm_tc_timeline.md)
+GEMM_TRAFFIC_BYTES = 277851136   # 120.4 MB read + 157.5 MB written: ncu capture of `profile_cli kernel gemm_nt 16384 3072 768` (profiles/gemm_tc_timeline.md)
 WORKLOAD = dict(name="d12", n_prompts=64, prompt_len=128, group=8, max_tokens=256, temperature=1.0, top_k=50, seed=0)
 METRIC, UNIT = "rl_steps_per_s_d12", "steps/s"
 
