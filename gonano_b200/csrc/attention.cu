@@ -1043,14 +1043,22 @@ __global__ void __launch_bounds__(32 * NW) attn_decode_kernel(const float* __res
       // the only CTA of this (row, kv head): finish here, merging the slots an earlier shared-prefix
       // launch left for this head (slot0 of them; stream order makes them visible)
       const int64_t pi0 = ((int64_t)row * Hq + hq) * nslots;
-      for (int sl = 0; sl < slot0; ++sl) {
-        const float pm = part_ms[(pi0 + sl) * 2], pl = part_ms[(pi0 + sl) * 2 + 1];
-        if (pm == -INFINITY) continue;
-        const float mn = fmaxf(gm, pm);
-        const float a0 = (gm == -INFINITY) ? 0.0f : __expf(gm - mn), a1 = __expf(pm - mn);
-        tot = tot * a0 + pl * a1;
-        acc = acc * a0 + part_acc[(pi0 + sl) * D + c] * a1;
-        gm = mn;
+      if (slot0 > 0) {
+        // two passes, so that the loads of a pass do not wait on one another: the maximum over the slots first,
+        // then the sums against it (a long prompt leaves dozens of slots)
+        float gmax = gm;
+#pragma unroll 4
+        for (int sl = 0; sl < slot0; ++sl) gmax = fmaxf(gmax, part_ms[(pi0 + sl) * 2]);
+        const float a0 = (gm == -INFINITY) ? 0.0f : __expf(gm - gmax);
+        tot *= a0; acc *= a0;
+#pragma unroll 4
+        for (int sl = 0; sl < slot0; ++sl) {
+          const float pm = part_ms[(pi0 + sl) * 2], pl = part_ms[(pi0 + sl) * 2 + 1];
+          const float a1 = (pm == -INFINITY) ? 0.0f : __expf(pm - gmax);
+          tot += pl * a1;
+          acc += part_acc[(pi0 + sl) * D + c] * a1;
+        }
+        gm = gmax;
       }
       const float v = tot > 0 ? acc / tot : 0.0f;
       const int64_t oi = (int64_t)row * o_rstride + (int64_t)hq * D + c;

@@ -76,6 +76,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
                ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
                : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(cols) : "memory");
 }
@@ -280,7 +285,10 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
           const uint32_t st = base + (uint32_t)s * S::STAGE_BYTES;
           if (it < 256) TC_TRACE(it);
           mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
-          if (ep.a_mn) {
+          if (ep.a_mn == 2) {   // the whole MN-major tile as one 3-D box (MN a multiple of 32)
+            tma_load_3d(st, &tmAh, full_bar(s), 0, (kb0 + kb) * TBK, tm0 / 32);
+            tma_load_3d(st + S::A_BYTES, &tmAl, full_bar(s), 0, (kb0 + kb) * TBK, tm0 / 32);
+          } else if (ep.a_mn) {
 #pragma unroll
             for (int j = 0; j < TBM / 32; ++j) {
               tma_load_2d(st + j * 4096, &tmAh, full_bar(s), tm0 + 32 * j, (kb0 + kb) * TBK);
@@ -290,7 +298,10 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
             tma_load_2d(st, &tmAh, full_bar(s), (kb0 + kb) * TBK, tm0);
             tma_load_2d(st + S::A_BYTES, &tmAl, full_bar(s), (kb0 + kb) * TBK, tm0);
           }
-          if (ep.b_mn) {
+          if (ep.b_mn == 2) {
+            tma_load_3d(st + 2 * S::A_BYTES, &tmBh, full_bar(s), 0, (kb0 + kb) * TBK, tb0 / 32);
+            tma_load_3d(st + 2 * S::A_BYTES + S::B_BYTES, &tmBl, full_bar(s), 0, (kb0 + kb) * TBK, tb0 / 32);
+          } else if (ep.b_mn) {
 #pragma unroll
             for (int j = 0; j < BN / 32; ++j) {
               tma_load_2d(st + 2 * S::A_BYTES + j * 4096, &tmBh, full_bar(s), tb0 + 32 * j, (kb0 + kb) * TBK);
@@ -306,7 +317,7 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = instr_desc_tf32(TBM, BN, ep.a_mn, ep.b_mn);
+      const uint32_t idesc = instr_desc_tf32(TBM, BN, ep.a_mn != 0, ep.b_mn != 0);
       int it = 0, gc = 0;   // k-blocks and chunks consumed so far, over all of this CTA's tiles
       for (int t = tile0; t < tile_end && !failed; t += tile_step) {
         for (int c = 0; c < nchunks && !failed; ++c, ++gc) {
@@ -550,6 +561,7 @@ long long* g_trace = nullptr;   // device buffer of 1024 slots (GN_TC_TRACE buil
 std::mutex g_mu;
 // GN_TC_MN=0 keeps the transposing operand split for products whose operands are stored [K, M] / [K, N].
 // GN_TC_PDL=0 launches the products without programmatic stream serialization.
+const bool g_mn_3d = [] { const char* e = getenv("GN_TC_MN3D"); return !(e && e[0] == '0'); }();
 const bool g_use_pdl = [] { const char* e = getenv("GN_TC_PDL"); return !(e && e[0] == '0'); }();
 // CTAs of the persistent form: one per SM; GN_TC_PERSISTENT=0 switches the form off, GN_TC_PERSISTENT=<n> runs it on n CTAs
 // (tests use a handful, so that small products walk several tiles per CTA too).
@@ -583,6 +595,20 @@ int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t k, int64
   CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with %d (rows %lld, k %lld, ld %lld)", (int)r, (long long)rows, (long long)k, (long long)ld); return GN_ERR_CUDA; }
+  return GN_OK;
+}
+
+// 3-D map over the same array, for mn a multiple of 32: dimensions {32 consecutive mn, k, mn / 32}; a box
+// {32, 32, groups} is a whole MN-major tile (its MN groups land 4096 bytes apart, as the four or eight 2-D boxes do),
+// so a k-block costs one copy per operand half instead of up to twelve.
+int make_map_mn3(CUtensorMap* map, const float* base, int64_t mn, int64_t k, int64_t ld, int groups) {
+  cuuint64_t dims[3] = {32, (cuuint64_t)k, (cuuint64_t)(mn / 32)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * sizeof(float), 32 * sizeof(float)};
+  cuuint32_t box[3] = {32, (cuuint32_t)TBK, (cuuint32_t)groups};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (MN-major, 3-D) failed with %d (mn %lld, k %lld, ld %lld)", (int)r, (long long)mn, (long long)k, (long long)ld); return GN_ERR_CUDA; }
   return GN_OK;
 }
 
@@ -694,13 +720,17 @@ int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int
     configured = true;
   }
   CUtensorMap mah, mal, mbh, mbl;
-  if (a.mn) { GN_TRY(make_map_mn(&mah, a.hi, M, K, a.ld)); GN_TRY(make_map_mn(&mal, a.lo, M, K, a.ld)); }
+  const bool a3 = a.mn && g_mn_3d && M % 32 == 0;
+  if (a3) { GN_TRY(make_map_mn3(&mah, a.hi, M, K, a.ld, TBM / 32)); GN_TRY(make_map_mn3(&mal, a.lo, M, K, a.ld, TBM / 32)); }
+  else if (a.mn) { GN_TRY(make_map_mn(&mah, a.hi, M, K, a.ld)); GN_TRY(make_map_mn(&mal, a.lo, M, K, a.ld)); }
   else { GN_TRY(make_map(&mah, a.hi, M, K, a.ld, TBM)); GN_TRY(make_map(&mal, a.lo, M, K, a.ld, TBM)); }
   const int brows = ep_in.groups > 0 ? ep_in.groups * N : N;
-  if (b.mn) { GN_TRY(make_map_mn(&mbh, b.hi, brows, K, b.ld)); GN_TRY(make_map_mn(&mbl, b.lo, brows, K, b.ld)); }
+  const bool b3 = b.mn && g_mn_3d && brows % 32 == 0;
+  if (b3) { GN_TRY(make_map_mn3(&mbh, b.hi, brows, K, b.ld, BN / 32)); GN_TRY(make_map_mn3(&mbl, b.lo, brows, K, b.ld, BN / 32)); }
+  else if (b.mn) { GN_TRY(make_map_mn(&mbh, b.hi, brows, K, b.ld)); GN_TRY(make_map_mn(&mbl, b.lo, brows, K, b.ld)); }
   else { GN_TRY(make_map(&mbh, b.hi, brows, K, b.ld, BN)); GN_TRY(make_map(&mbl, b.lo, brows, K, b.ld, BN)); }
   TcEpilogue ep = ep_in;
-  ep.a_mn = a.mn ? 1 : 0; ep.b_mn = b.mn ? 1 : 0;
+  ep.a_mn = a3 ? 2 : (a.mn ? 1 : 0); ep.b_mn = b3 ? 2 : (b.mn ? 1 : 0);
   if (splits > 1) {
     size_t need = (size_t)splits * M * N;
     if (need > g_splitk_floats) {
