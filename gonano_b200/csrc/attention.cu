@@ -903,7 +903,7 @@ int attention_combine_launch(const float* acc, const float* mx, const float* sm,
 }
 
 // ============================================================== decode
-// CTA = one (row, kv head, key split); 4 warps stride over the keys of the
+// CTA = one (row, kv head, key split); NW warps (4, 8 or 16) stride over the keys of the
 // split; each lane owns D/32 consecutive channels (float4 for D = 128), so a
 // warp reads one K row and one V row as a single coalesced 512-byte request.
 // All query heads of the group are served from the same K/V registers.
