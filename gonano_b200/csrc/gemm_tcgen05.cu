@@ -157,7 +157,10 @@ struct TcEpilogue {
   int a_mn, b_mn;   // operand arrives MN-major (tensor map over a row-major [K, MN] source) instead of K-major
   // persistent form: the grid is one CTA per SM and CTA b works on output tiles b, b + gridDim.x, ... of tiles_total
   // (tile t = column tile t % tiles_n of row tile t / tiles_n); 0 = one tile per CTA, taken from blockIdx
-  int tiles_total, tiles_n;
+  // The tiles are walked in bands of tiles_gn column tiles: inside a band the column tile runs fastest, so the CTAs
+  // that are in flight together cover tiles_gn column tiles x a few row tiles and both operands are re-read from L2,
+  // not from HBM (with plain row-major order a 49 k x 32768 product re-reads its 201 MB of weights for every row tile).
+  int tiles_total, tiles_n, tiles_gn;
 };
 
 #ifdef GN_TC_TRACE
@@ -242,7 +245,12 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
   constexpr bool persistent = PERSIST;   // a compile-time form: the one-tile kernel carries none of the tile loop
   const int tile0 = persistent ? (int)blockIdx.x : 0, tile_step = persistent ? (int)gridDim.x : 1, tile_end = persistent ? ep.tiles_total : 1;
   auto tile_origin = [&](int t, int& tm0, int& tn0, int& tb0) {
-    if (persistent) { tm0 = (t / ep.tiles_n) * TBM; tn0 = (t % ep.tiles_n) * BN; tb0 = tn0; }
+    if (persistent) {
+      const int tiles_m = ep.tiles_total / ep.tiles_n, band_tiles = ep.tiles_gn * tiles_m;
+      const int band = t / band_tiles, within = t - band * band_tiles;
+      const int width = min(ep.tiles_gn, ep.tiles_n - band * ep.tiles_gn);   // the last band may be narrower
+      tm0 = (within / width) * TBM; tn0 = (band * ep.tiles_gn + within % width) * BN; tb0 = tn0;
+    }
     else { tm0 = m0; tn0 = n0; tb0 = b_row0; }
   };
   // split-K: CTA z works on k-blocks [kb0, kb0 + nk) and writes a partial tile
@@ -752,6 +760,10 @@ int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int
   if (g_persistent_ctas > 0 && splits == 1 && ep_in.groups == 0 && tiles_total > g_persistent_ctas && tiles_total < (int64_t)1 << 30 &&
       K <= 4096) {
     ep.tiles_total = (int)tiles_total; ep.tiles_n = ceil_div(N, BN);
+    const int tiles_m = ceil_div(M, TBM);
+    // few row tiles (the rollout's lm_head): all of them next to each other; otherwise bands of 16 column tiles
+    ep.tiles_gn = tiles_m < 10 ? std::max(1, g_persistent_ctas / tiles_m) : 16;   // measured: lm_head at 512 rows 0.217 -> 0.193 ms, 16384 x 32768 x 768 4.10 -> 3.42 ms
+    if (ep.tiles_gn > ep.tiles_n) ep.tiles_gn = ep.tiles_n;
     grid = dim3(g_persistent_ctas, 1, 1);
   }
   {
@@ -813,7 +825,7 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
   } else {
     GN_TRY(split_operand(g.B, g.ldb, g.groups > 0 ? (int64_t)g.groups * g.N : g.N, g.K, g.b_trans == 0, g.b_static != 0, 1, b, s, g_allow_mn));
   }
-  TcEpilogue ep{g.C, g.ldc, g.aux, g.ldaux, g.epilogue, g.scalar, 0, g.c_hi, g.c_lo, g_trace, g.group_counts, g.groups, 0, 0, 0, 0};
+  TcEpilogue ep{g.C, g.ldc, g.aux, g.ldaux, g.epilogue, g.scalar, 0, g.c_hi, g.c_lo, g_trace, g.group_counts, g.groups, 0, 0, 0, 0, 1};
   if (g.groups > 0) return launch_tc<128, 3>(a, b, ep, g.M, g.N, g.K, 1, s, nullptr);
   // Filling the machine when the output has few tiles (the rollout's products have 512 rows):
   // the K loop is split over gridDim.z so that about one CTA per SM runs, each writing a partial
