@@ -111,6 +111,13 @@ def cpu_baseline(sample_scale: int = 1):
     from oracle import oracle
     w = WORKLOAD
     cfg = synthetic.dense_config(w["name"])
+    # every host thread this process may use: a launcher such as torchrun sets OMP_NUM_THREADS=1, which would
+    # otherwise time the CPU path on one core
+    try:
+        avail = len(os.sched_getaffinity(0))
+    except AttributeError:
+        avail = os.cpu_count() or 1
+    oracle.set_threads(max(1, avail))
     threads = oracle.num_threads()
     om = oracle.Model(mode=1, **cfg)
     for name, value in synthetic.fill_weights(om.names, om.shape, w["seed"]):
