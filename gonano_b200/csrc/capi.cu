@@ -452,12 +452,18 @@ int gn_pg_loss_backward(const float* logits, const int32_t* targets, const float
   else { dl = st.in(logits, n); dd = dlogits ? st.out(dlogits, n) : nullptr; }
   const int32_t* dt = st.in(targets, rows); const float* da = st.in(adv, (size_t)((rows + seq_len - 1) / seq_len));
   float* dn = nll ? st.out(nll, rows) : nullptr;
+  // scratch: cell 0 the loss total, cell 1 the count of out-of-range targets, cells 2.. one term per row
   double* scratch = nullptr;
-  GN_CUDA(cudaMalloc((void**)&scratch, sizeof(double) * (size_t)(rows + 1)));
+  GN_CUDA(cudaMalloc((void**)&scratch, sizeof(double) * (size_t)(rows + 2)));
   st.owned.push_back(scratch);
   if (st.status != GN_OK) return st.status;
-  GN_TRY(pg_loss_launch(dl, dt, da, rows, vocab, vocab, seq_len, norm, softcap, dn, dd, vocab, scratch + 1, scratch, 0, s));
-  GN_CUDA(cudaMemcpyAsync(loss, scratch, sizeof(double), cudaMemcpyDeviceToHost, s));
+  GN_CUDA(cudaMemsetAsync(scratch, 0, 2 * sizeof(double), s));
+  GN_TRY(pg_loss_launch(dl, dt, da, rows, vocab, vocab, seq_len, norm, softcap, dn, dd, vocab, scratch + 2, scratch, 0, s, reinterpret_cast<int*>(scratch + 1)));
+  int bad = 0;
+  GN_CUDA(cudaMemcpyAsync(&bad, scratch + 1, sizeof(int), cudaMemcpyDeviceToHost, s));
+  GN_CUDA(cudaMemcpyAsync(loss, scratch, sizeof(double), cudaMemcpyDefault, s));   // loss may be host or device memory
+  GN_CUDA(cudaStreamSynchronize(s));
+  if (bad) { set_error("pg_loss_backward: %d targets outside {-1} and [0, %d)", bad, vocab); return GN_ERR_INVALID; }
   GN_END();
 }
 

@@ -88,9 +88,11 @@ int sample_launch(const float* logits, int rows, int vocab, int logits_row_div, 
                   const uint32_t* step_dev, uint32_t step_host, float temperature, int top_k, int32_t* out, cudaStream_t s);
 
 // -------------------------------------------------------------------- loss.cu
-// row_loss: [rows] double scratch; loss_out: device double.
+// row_loss: [rows] double scratch; loss_out: device double.  bad_targets: null or a device counter that receives the
+// number of targets outside {-1} and [0, vocab) (such rows are treated as ignored, never dereferenced).
 int pg_loss_launch(const float* logits, const int32_t* targets, const float* adv, int64_t rows, int vocab, int64_t ld, int seq_len, float norm,
-                   float softcap, float* nll, float* dlogits, int64_t ldd, double* row_loss, double* loss_out, int accumulate_loss, cudaStream_t s);
+                   float softcap, float* nll, float* dlogits, int64_t ldd, double* row_loss, double* loss_out, int accumulate_loss, cudaStream_t s,
+                   int* bad_targets = nullptr);
 int advantage_launch(const float* rewards, int groups, int group, int mode, float* adv, cudaStream_t s);
 
 }  // namespace gn

@@ -28,13 +28,16 @@ __device__ __forceinline__ void ms_merge(float& m, float& s, float om, float os)
 template <bool VEC>
 __global__ void __launch_bounds__(LT) pg_loss_kernel(const float* __restrict__ logits, const int32_t* __restrict__ targets, const float* __restrict__ adv,
                                                      int64_t rows, int vocab, int64_t ld, int seq_len, float norm, float softcap, float* __restrict__ nll,
-                                                     float* dlogits, int64_t ldd, double* __restrict__ row_loss) {
+                                                     float* dlogits, int64_t ldd, double* __restrict__ row_loss, int* __restrict__ bad_targets) {
   __shared__ float sh_m[32], sh_s[32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const int32_t target = targets[row];
     float* drow = dlogits ? dlogits + row * ldd : nullptr;
-    if (target < 0) {
+    // A target outside {-1} and [0, vocab) would index outside the row: the row is treated as ignored and counted,
+    // and the host turns a non-zero count into GN_ERR_INVALID (the reference panics on Go's bounds check instead).
+    if (target < -1 || target >= vocab) { if (tid == 0 && bad_targets) atomicAdd(bad_targets, 1); }
+    if (target < 0 || target >= vocab) {
       if (drow) {
         if (VEC) { float4 z = make_float4(0, 0, 0, 0); for (int c = tid * 4; c < vocab; c += LT * 4) *reinterpret_cast<float4*>(drow + c) = z; }
         else { for (int c = tid; c < vocab; c += LT) drow[c] = 0.0f; }
@@ -153,15 +156,16 @@ __global__ void __launch_bounds__(1024) loss_sum_kernel(const double* row_loss, 
 }
 
 int pg_loss_launch(const float* logits, const int32_t* targets, const float* adv, int64_t rows, int vocab, int64_t ld, int seq_len, float norm,
-                   float softcap, float* nll, float* dlogits, int64_t ldd, double* row_loss, double* loss_out, int accumulate_loss, cudaStream_t s) {
+                   float softcap, float* nll, float* dlogits, int64_t ldd, double* row_loss, double* loss_out, int accumulate_loss, cudaStream_t s,
+                   int* bad_targets) {
   GN_REQUIRE(vocab > 0 && seq_len > 0, "loss: vocab %d / seq_len %d must be positive", vocab, seq_len);
   if (rows > 0) {
     auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     bool vec = al(logits) && (!dlogits || al(dlogits)) && vocab % 4 == 0 && ld % 4 == 0 && ldd % 4 == 0;
     // In the vector path the register window covers LIPT*LT columns as float4 groups.
     int grid = (int)std::min<int64_t>(rows, (int64_t)kNumSM * 8);
-    if (vec) pg_loss_kernel<true><<<grid, LT, 0, s>>>(logits, targets, adv, rows, vocab, ld, seq_len, norm, softcap, nll, dlogits, ldd, row_loss);
-    else pg_loss_kernel<false><<<grid, LT, 0, s>>>(logits, targets, adv, rows, vocab, ld, seq_len, norm, softcap, nll, dlogits, ldd, row_loss);
+    if (vec) pg_loss_kernel<true><<<grid, LT, 0, s>>>(logits, targets, adv, rows, vocab, ld, seq_len, norm, softcap, nll, dlogits, ldd, row_loss, bad_targets);
+    else pg_loss_kernel<false><<<grid, LT, 0, s>>>(logits, targets, adv, rows, vocab, ld, seq_len, norm, softcap, nll, dlogits, ldd, row_loss, bad_targets);
     GN_LAUNCH_CHECK();
   }
   if (accumulate_loss != 2 && loss_out) {  // 0: overwrite, 1: add, 2: leave the total alone

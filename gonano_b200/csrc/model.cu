@@ -105,6 +105,19 @@ int enter(gn_model* m) {
   GN_CUDA(cudaSetDevice(m->ctx->device));
   return GN_OK;
 }
+// Token ids arrive from the host and index the embedding tables, the value-embedding tables and the logits row:
+// an id outside the vocabulary is refused before anything is launched (the reference panics on the slice bound,
+// model/layers/linear.go:71-85).  allow_ignore admits -1 (the ignored-target marker of tensors/loss.go:16-46).
+int check_ids(const int32_t* ids, int64_t n, int vocab, bool allow_ignore, const char* what) {
+  for (int64_t i = 0; i < n; ++i) {
+    const int32_t v = ids[i];
+    if ((v >= 0 && v < vocab) || (allow_ignore && v == -1)) continue;
+    set_error("%s[%lld] = %d is outside [0, %d)%s", what, (long long)i, (int)v, vocab, allow_ignore ? " and is not -1" : "");
+    return GN_ERR_INVALID;
+  }
+  return GN_OK;
+}
+
 // Entry of a compute phase: stale operand splits are dropped before the first GEMM.
 int enter_compute(gn_model* m) {
   GN_TRY(enter(m));
@@ -578,6 +591,7 @@ int gn_model_forward(gn_model* m, const int32_t* ids, int B, int T, float* logit
   GN_REQUIRE(ids && logits && B > 0 && T > 1, "gn_model_forward needs ids, logits, batch > 0 and seq > 1");
   GN_REQUIRE(T <= m->cfg.sequence_len, "sequence %d longer than the rotary cache (%d)", T, m->cfg.sequence_len);
   const int64_t rows = (int64_t)B * T;
+  GN_TRY(check_ids(ids, rows, m->V, false, "gn_model_forward: ids"));
   GN_TRY(m->ids_dev.ensure(sizeof(int32_t) * rows));
   GN_CUDA(cudaMemcpyAsync(m->ids_dev.p, ids, sizeof(int32_t) * rows, cudaMemcpyHostToDevice, m->s()));
   FwdBufs b;
@@ -735,6 +749,7 @@ int gn_generate_batch(gn_model* m, const int32_t* prompts, int P, int plen, int 
   GN_REQUIRE(P > 0 && plen > 0 && G > 0 && max_tokens > 0, "gn_generate_batch: sizes must be positive");
   GN_REQUIRE(plen <= m->cfg.sequence_len, "prompt of %d tokens longer than sequence_len %d", plen, m->cfg.sequence_len);
   GN_REQUIRE((int64_t)plen + max_tokens <= (int64_t)m->cfg.sequence_len * 10, "context %d exceeds the rotary table", plen + max_tokens);
+  GN_TRY(check_ids(prompts, (int64_t)P * plen, m->V, false, "gn_generate_batch: prompts"));
   const int d = m->d, Hq = m->Hq, Hkv = m->Hkv, D = m->D, V = m->V, L = m->L;
   const int rows = P * G, max_seq = plen + max_tokens;
   const int bos = V - 11, aend = V - 7;   // tokenizer/special.go:19-31
@@ -886,6 +901,8 @@ int gn_policy_gradient_step(gn_model* m, const int32_t* inputs, const int32_t* t
   if (m->moe() || m->mla()) { set_error("the training pass covers the dense preset only; latent attention and routed experts are inference-only here"); return GN_ERR_UNSUPPORTED; }
   GN_REQUIRE(B > 0 && T > 1, "gn_policy_gradient_step: batch must be positive and seq > 1 (model/transformer.go:269-271)");
   GN_REQUIRE(T <= m->cfg.sequence_len, "sequence %d longer than sequence_len %d", T, m->cfg.sequence_len);
+  GN_TRY(check_ids(inputs, (int64_t)B * T, m->V, false, "gn_policy_gradient_step: inputs"));
+  GN_TRY(check_ids(targets, (int64_t)B * T, m->V, true, "gn_policy_gradient_step: targets"));
   const int V = m->V, L = m->L;
   cudaStream_t s = m->s();
   // ~48 K tokens per pass: measured on d12, 128-row passes cost 1.86 ms per sequence against 2.00 ms for 32-row passes

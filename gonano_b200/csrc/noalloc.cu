@@ -20,18 +20,22 @@
 //     need an allocation.
 //
 // The array's device address is looked up once per device, on the first call that runs with
-// that device current.  Make that first call during start-up, before any stream capture.
+// that device current; make that first call during start-up.  The call cannot run inside a stream
+// capture: it synchronises the stream before it returns.  First calls on one device from several
+// threads at once may each do the look-up; they store the same address, so the race is harmless.
+#include <atomic>
+
 #include "kernels.cuh"
 
 namespace gn {
 namespace {
 
-// cell 0: the loss total; cells 32..: one term per row (offset keeps the rows 256-byte aligned)
+// cell 0: the loss total; cell 1: count of out-of-range targets; cells 32..: one term per row (offset keeps the rows 256-byte aligned)
 constexpr int64_t kStaticRowOffset = 32;
 static __device__ __align__(256) double g_static_loss_scratch[GN_STATIC_LOSS_MAX_ROWS + kStaticRowOffset];
 
 constexpr int kMaxDevices = 64;
-double* g_scratch_addr[kMaxDevices] = {nullptr};
+std::atomic<double*> g_scratch_addr[kMaxDevices];
 
 // The symbol name above is only a handle on the host side, not an address a kernel can use:
 // the real per-device address comes from the runtime.
@@ -39,12 +43,14 @@ int static_scratch(double** out) {
   int device = 0;
   GN_CUDA(cudaGetDevice(&device));
   GN_REQUIRE(device >= 0 && device < kMaxDevices, "device ordinal %d outside [0,%d)", device, kMaxDevices);
-  if (!g_scratch_addr[device]) {
+  double* addr = g_scratch_addr[device].load(std::memory_order_acquire);
+  if (!addr) {
     void* p = nullptr;
     GN_CUDA(cudaGetSymbolAddress(&p, g_static_loss_scratch));
-    g_scratch_addr[device] = static_cast<double*>(p);
+    addr = static_cast<double*>(p);
+    g_scratch_addr[device].store(addr, std::memory_order_release);
   }
-  *out = g_scratch_addr[device];
+  *out = addr;
   return GN_OK;
 }
 
@@ -70,11 +76,17 @@ extern "C" int gn_pg_loss_backward_static(const float* logits, const int32_t* ta
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   double* scratch = nullptr;
   GN_TRY(static_scratch(&scratch));
-  // The total must start from zero; the row cells are rewritten by the kernel before the sum reads them.
-  GN_CUDA(cudaMemsetAsync(scratch, 0, sizeof(double), s));
-  GN_TRY(pg_loss_launch(logits, targets, advantages, rows, vocab, vocab, seq_len, norm, softcap, nll, dlogits, vocab, scratch + kStaticRowOffset, scratch, 1, s));
+  // The total and the bad-target count must start from zero; the row cells are rewritten by the kernel before the sum reads them.
+  GN_CUDA(cudaMemsetAsync(scratch, 0, 2 * sizeof(double), s));
+  GN_TRY(pg_loss_launch(logits, targets, advantages, rows, vocab, vocab, seq_len, norm, softcap, nll, dlogits, vocab, scratch + kStaticRowOffset, scratch, 1, s,
+                        reinterpret_cast<int*>(scratch + 1)));
+  int bad = 0;
+  GN_CUDA(cudaMemcpyAsync(&bad, scratch + 1, sizeof(int), cudaMemcpyDeviceToHost, s));
   if (is_device_pointer(loss)) GN_CUDA(cudaMemcpyAsync(loss, scratch, sizeof(double), cudaMemcpyDeviceToDevice, s));
   else GN_CUDA(cudaMemcpyAsync(loss, scratch, sizeof(double), cudaMemcpyDeviceToHost, s));
   GN_CUDA(cudaStreamSynchronize(s));
+  if (bad) { set_error("pg_loss_backward_static: %d targets outside {-1} and [0, %d)", bad, vocab); return GN_ERR_INVALID; }
   return GN_OK;
 }
+
+extern "C" int gn_static_loss_max_rows(void) { return GN_STATIC_LOSS_MAX_ROWS; }

@@ -12,7 +12,7 @@
  *           and meaning.  Pointers may be host or device memory (detected per
  *           call); host buffers are staged through device memory and the call
  *           returns when the result is back.  This is what a cgo shim that
- *           implements `kernels.Backend` binds (see INTEGRATION.md).
+ *           implements `kernels.Backend` binds.
  *
  *   Tier B  a resident session: the model's parameters, KV cache, activations
  *           and gradients live in device memory, and whole phases of the RL
@@ -157,7 +157,9 @@ int gn_group_advantage(const float* rewards, int groups, int group, int mode, fl
  * dlogits = (softmax - onehot) * adv / norm (0 on ignored rows).  When
  * softcap > 0 the gradient is also multiplied by 1 - (logit / softcap)^2, the
  * backward of the logit softcap (tensors/backward.go:108-116).  dlogits may
- * alias logits (in place) or be NULL (loss only).  nll may be NULL. */
+ * alias logits (in place) or be NULL (loss only).  nll may be NULL.  loss may be host or
+ * device memory.  A target outside {-1} and [0, vocab) is never dereferenced: the call
+ * fails with GN_ERR_INVALID (the reference panics on the slice bound). */
 int gn_pg_loss_backward(const float* logits, const int32_t* targets, const float* advantages, int64_t rows, int vocab,
                         int seq_len, float norm, float softcap, float* nll, float* dlogits, double* loss);
 
@@ -173,8 +175,11 @@ int gn_pg_loss_backward(const float* logits, const int32_t* targets, const float
  *   - the array is shared by every call on a GPU and keeps the last call's values: what must
  *     start at zero is cleared per call, and calls that overlap on one GPU race - serialise them;
  *   - the first call on each device looks up the array's device address; make that call at
- *     start-up, before any stream capture. */
+ *     start-up.  The call synchronises the stream before it returns, so it cannot run inside a
+ *     stream capture.
+ * gn_static_loss_max_rows() returns the row limit the loaded library was built with. */
 #define GN_STATIC_LOSS_MAX_ROWS 65536
+int gn_static_loss_max_rows(void);
 int gn_pg_loss_backward_static(const float* logits, const int32_t* targets, const float* advantages, int64_t rows,
                                int vocab, int seq_len, float norm, float softcap, float* nll, float* dlogits,
                                double* loss, void* stream);

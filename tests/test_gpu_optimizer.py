@@ -133,7 +133,7 @@ def test_model_optimizer_step(oracle, name):
 def test_rl_step_with_optimizer_end_to_end(oracle):
     """PolicyGradientStep + optimizer step from the same batch on both sides.  The block matrices and the tables move
     as the oracle's do (the optimizers normalise the gradient, so 1e-4 gradient agreement carries over at ~1e-3 of the
-    update); the scalar AdamW groups are sign-like in the gradient and only their direction is compared."""
+    update); the scalar AdamW groups are compared by value too."""
     from gonano_b200.session import Context, Model
     cfg = synthetic.dense_config("c1")
     ctx = Context(0)
@@ -151,10 +151,8 @@ def test_rl_step_with_optimizer_end_to_end(oracle):
     scalars = ("resid_lambdas", "x0_lambdas", "smear_gate.weight", "smear_lambda", "backout_lambda")
     for n in om.names:
         got, want = gm.download(n), om.param(n)
-        if n in scalars:
-            assert np.all(np.sign(got - before[n]) == np.sign(want - before[n])), n
-        else:
-            assert upd_err(got, want, before[n]) <= 5e-3, n
+        # AdamW (optimizer/optimizer.go:148-174): the first step moves a scalar by lr * g / (|g| + eps), compared by value
+        assert upd_err(got, want, before[n]) <= (2e-3 if n in scalars else 5e-3), n
     gm.close(); ctx.close()
 
 

@@ -132,6 +132,20 @@ def test_loss_parity(oracle, rows, vocab, seq):
     assert abs(loss2 - want_loss) <= 1e-4 * max(abs(want_loss), 1e-3)
 
 
+def test_loss_refuses_targets_outside_the_vocabulary():
+    """A target >= vocab (or below -1) is never used as an index: the row is skipped on the device and the call
+    reports GN_ERR_INVALID, where the reference would panic on the slice bound (tensors/loss.go:39)."""
+    from gonano_b200._lib import GonanoError
+    logits = np.zeros((4, 8), np.float32)
+    adv = np.ones(4, np.float32)
+    for bad in (8, 1000, -2):
+        targets = np.array([1, bad, -1, 2], np.int32)
+        with pytest.raises(GonanoError, match="targets outside"):
+            B.pg_loss_backward(logits, targets, adv, 1, 1.0)
+    loss, nll, grad = B.pg_loss_backward(logits, np.array([1, 7, -1, 2], np.int32), adv, 1, 1.0)
+    assert np.isfinite(loss) and nll[2] == 0 and not np.any(grad[2])
+
+
 def test_loss_properties_at_scale():
     """Size-independent checks at the microbenchmark's row width: each valid gradient row sums to 0
     and the loss is linear in the advantages."""

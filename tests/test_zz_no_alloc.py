@@ -14,8 +14,6 @@ import pytest
 
 pytestmark = pytest.mark.gpu
 
-MAX_ROWS = 65536
-
 
 def _case(rng, rows, vocab, seq):
     z = rng.standard_normal((rows, vocab)).astype(np.float32) * np.float32(3)
@@ -61,10 +59,19 @@ def test_static_loss_limits_are_enforced():
     t = torch.zeros(16, device=dev)
     ti = torch.zeros(16, dtype=torch.int32, device=dev)
     loss = C.c_double()
-    status = lib.gn_pg_loss_backward_static(t.data_ptr(), ti.data_ptr(), t.data_ptr(), MAX_ROWS + 1, 4, 1, 1.0, 0.0, None, None,
+    max_rows = lib.gn_static_loss_max_rows()      # the limit of the library that is loaded, not a copy of it
+    assert max_rows >= 1024
+    status = lib.gn_pg_loss_backward_static(t.data_ptr(), ti.data_ptr(), t.data_ptr(), max_rows + 1, 4, 1, 1.0, 0.0, None, None,
                                             C.cast(C.byref(loss), C.c_void_p), None)
     assert status != 0 and b"exceed" in lib.gn_last_error()
     host = np.zeros(16, np.float32)
     status = lib.gn_pg_loss_backward_static(host.ctypes.data, ti.data_ptr(), t.data_ptr(), 4, 4, 1, 1.0, 0.0, None, None,
                                             C.cast(C.byref(loss), C.c_void_p), None)
     assert status != 0 and b"device memory" in lib.gn_last_error()
+    # a target beyond the vocabulary is never dereferenced: the call reports it instead
+    logits = torch.zeros(4, 8, device=dev)
+    bad = torch.tensor([1, 8, -1, 2], dtype=torch.int32, device=dev)
+    adv = torch.ones(4, device=dev)
+    status = lib.gn_pg_loss_backward_static(logits.data_ptr(), bad.data_ptr(), adv.data_ptr(), 4, 8, 1, 1.0, 0.0, None, None,
+                                            C.cast(C.byref(loss), C.c_void_p), None)
+    assert status == 1 and b"targets outside" in lib.gn_last_error()
