@@ -78,6 +78,7 @@ SIGNATURES = {
     "gn_static_loss_max_rows": (I, []),
     "gn_ctx_create": (I, [I, vp, C.POINTER(vp)]), "gn_ctx_destroy": (I, [vp]), "gn_ctx_sync": (I, [vp]),
     "gn_ctx_launch_count": (I, [vp, C.POINTER(C.c_int64)]), "gn_ctx_set_gemm": (I, [vp, I]),
+    "gn_ctx_set_option": (I, [vp, C.c_char_p, I]),
     "gn_model_create": (I, [vp, C.POINTER(GnConfig), C.POINTER(vp)]), "gn_model_destroy": (I, [vp]),
     "gn_model_param_count": (I, [vp, C.POINTER(I)]),
     "gn_model_param_info": (I, [vp, I, C.POINTER(C.c_char_p), C.POINTER(I), C.POINTER(I)]),

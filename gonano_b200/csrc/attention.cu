@@ -18,6 +18,8 @@
 // finite -1e30 of the reference (kernels/scalar/attention.go:11).
 #include <cstdlib>
 
+#include <atomic>
+
 #include "kernels.cuh"
 
 namespace gn {
@@ -1203,6 +1205,10 @@ __global__ void __launch_bounds__(256) attn_decode_prefix_kernel(const float* __
     }
   }
 }
+// -1: the rule below decides; 0 / 1: the shared-prefix pass is off / on wherever it applies (process-wide policy).
+std::atomic<int> g_prefix_sharing{-1};
+void attention_decode_prefix_mode(int mode) { g_prefix_sharing.store(mode < 0 ? -1 : (mode ? 1 : 0), std::memory_order_relaxed); }
+
 constexpr size_t kPrefixSmem = sizeof(float) * (size_t)(2 * kPrefixTile * 132 + kPrefixMaxHeads * 128 + kPrefixMaxHeads * kPrefixTile);
 
 // Partial-result slots the shared-prefix pass writes: one per tile of 32 prompt positions
@@ -1213,17 +1219,18 @@ int attention_decode_prefix_splits(int rows, int group, int Hq, int Hkv, int D, 
   // Measured on d12 (128-token prompts, 512 rows): the group's rows read the prompt's keys from L2 anyway, so the pass
   // only wins while the prompt is most of the context (35 vs 39 us per layer at 160 keys, 60 vs 57 at 256).  It is
   // therefore used when the prompt is long (>= 512 positions) and the pass fills the machine; short prompts and small
-  // batches keep the per-row kernel.  GN_PREFIX_SHARING=1 / 0 overrides the rule (tests exercise the pass with it).
-  static const int forced = [] { const char* e = getenv("GN_PREFIX_SHARING"); return e ? (e[0] == '0' ? 0 : 1) : -1; }();
+  // batches keep the per-row kernel.  The option "decode_prefix_sharing" (1 / 0) overrides the rule; tests exercise
+  // the pass with it.
+  const int forced = g_prefix_sharing.load(std::memory_order_relaxed);
   if (forced == 0) return 0;
-  if (forced < 0 && (prefix_len < 512 || (int64_t)(rows / group) * Hkv * tiles < 2 * kNumSM)) return 0;
+  if (forced < 0 && (prefix_len < 512 || (int64_t)(rows / group) * Hkv * tiles < 2 * num_sms())) return 0;
   return tiles;
 }
 
 // Warps per CTA of the per-row kernel: 4 on grids that fill the machine, 8 or 16 on smaller ones.
 int attention_decode_warps(int rows, int Hkv) {
   const int base = rows * Hkv;
-  return base >= kNumSM * 4 ? 4 : (base >= kNumSM * 2 ? 8 : 16);
+  return base >= num_sms() * 4 ? 4 : (base >= num_sms() * 2 ? 8 : 16);
 }
 
 int attention_decode_splits(int rows, int Hkv, int max_ctx) {
@@ -1232,7 +1239,7 @@ int attention_decode_splits(int rows, int Hkv, int max_ctx) {
   const int wf = attention_decode_warps(rows, Hkv) / 4;
   int base = rows * Hkv * wf;
   int splits = 1;
-  while (base * splits < kNumSM * 4 && max_ctx / (splits * wf * 2) >= 64 && splits < 16) splits *= 2;
+  while (base * splits < num_sms() * 4 && max_ctx / (splits * wf * 2) >= 64 && splits < 16) splits *= 2;
   return splits;
 }
 
@@ -1261,7 +1268,7 @@ static int decode_go(const float* q, int64_t q_rstride, const float* kcache, con
   constexpr int kMaxW = RATIO * DP * 16 <= 10240 ? 16 : (RATIO * DP * 8 <= 10240 ? 8 : 4);
   if (nw == 16 && kMaxW >= 16) { if constexpr (kMaxW >= 16) GN_DEC_LAUNCH(2, 16); }
   else if (nw >= 8 && kMaxW >= 8) { if constexpr (kMaxW >= 8) GN_DEC_LAUNCH(2, 8); }
-  else if ((int64_t)rows * Hkv * splits < (int64_t)kNumSM * 5) GN_DEC_LAUNCH(2, 4);
+  else if ((int64_t)rows * Hkv * splits < (int64_t)num_sms() * 5) GN_DEC_LAUNCH(2, 4);
   else GN_DEC_LAUNCH(1, 4);
 #undef GN_DEC_LAUNCH
   GN_LAUNCH_CHECK();

@@ -33,6 +33,35 @@ int gemm_tcgen05(const GemmArgs& a, cudaStream_t s);
 void gemm_tcgen05_invalidate();
 void gemm_tcgen05_mark_stale();
 int gemm_tcgen05_check(cudaStream_t s);
+void gemm_tcgen05_release(cudaStream_t s);
+int gemm_tcgen05_option(cudaStream_t s, const char* name, int value);
+void gemm_release_stream(cudaStream_t s) {
+#ifdef GN_HAVE_TCGEN05
+  gemm_tcgen05_release(s);
+#else
+  (void)s;
+#endif
+}
+int gemm_set_option(cudaStream_t s, const char* name, int value) {
+#ifdef GN_HAVE_TCGEN05
+  return gemm_tcgen05_option(s, name, value);
+#else
+  (void)s; (void)value;
+  set_error("unknown option '%s'", name);
+  return GN_ERR_INVALID;
+#endif
+}
+int num_sms() {
+  static std::atomic<int> cache[64];
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 148;
+  int v = cache[device].load(std::memory_order_relaxed);
+  if (v <= 0) {
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || v <= 0) { cudaGetLastError(); v = 148; }
+    cache[device].store(v, std::memory_order_relaxed);
+  }
+  return v;
+}
 void gemm_invalidate_static() {
 #ifdef GN_HAVE_TCGEN05
   gemm_tcgen05_invalidate();
@@ -83,15 +112,27 @@ namespace {
 
 std::mutex g_lock;
 cudaStream_t g_stream = nullptr;
+int g_stream_device = -1;   // the stand-alone calls run on the device that was current at the first of them
 
 int tier_a_stream(cudaStream_t* out) {
   int count = 0;
   cudaError_t e = cudaGetDeviceCount(&count);
   if (e != cudaSuccess || count == 0) { set_error("no CUDA device available: %s", cudaGetErrorString(e)); return GN_ERR_CUDA; }
-  if (!g_stream) GN_CUDA(cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking));
+  int device = 0;
+  GN_CUDA(cudaGetDevice(&device));
+  if (!g_stream) { GN_CUDA(cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking)); g_stream_device = device; }
+  if (device != g_stream_device) {
+    set_error("the stand-alone calls of this process run on device %d (current at their first use); device %d is current now - use a gn_ctx for other devices",
+              g_stream_device, device);
+    return GN_ERR_UNSUPPORTED;
+  }
   *out = g_stream;
   return GN_OK;
 }
+
+}  // namespace
+cudaStream_t tier_a_stream_or_null() { return g_stream; }
+namespace {
 
 bool on_device(const void* p) {
   cudaPointerAttributes at;

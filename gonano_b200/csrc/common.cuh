@@ -46,7 +46,8 @@ void count_launches(int64_t n);   // kernels replayed through a CUDA graph
     GN_CUDA(cudaGetLastError());   \
   } while (0)
 
-constexpr int kNumSM = 148;  // B200
+// Streaming multiprocessors of the current device (148 on B200), queried once per device.
+int num_sms();
 
 static inline int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
 
@@ -204,5 +205,8 @@ int64_t launch_count();
 void gemm_invalidate_static();        // parameter storage is going away: free cached operand splits
 void gemm_mark_static_stale();        // parameters changed in place: cached splits are redone (in their buffers) on next use
 int gemm_check_error(cudaStream_t s); // GN_ERR_TIMEOUT when a bounded device wait ran out
+void gemm_release_stream(cudaStream_t s);   // the stream is going away: free the scratch held for its products
+int gemm_set_option(cudaStream_t s, const char* name, int value);
+cudaStream_t tier_a_stream_or_null();       // the stream Tier A runs on (null before its first call)
 
 }  // namespace gn

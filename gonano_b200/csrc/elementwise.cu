@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(256) ew_kernel(float* __restrict__ dst, const 
 template <int OP>
 static int ew_go(float* dst, const float* a, const float* b, float f, int64_t n, cudaStream_t s) {
   if (n <= 0) return GN_OK;
-  int blocks = (int)std::min<int64_t>((n + 255) / 256, (int64_t)kNumSM * 16);
+  int blocks = (int)std::min<int64_t>((n + 255) / 256, (int64_t)num_sms() * 16);
   ew_kernel<OP><<<blocks, 256, 0, s>>>(dst, a, b, f, n);
   GN_LAUNCH_CHECK();
   return GN_OK;
@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(float* gg, float* ug, c
 }
 int swiglu_backward_launch(float* gg, float* ug, const float* gate, const float* up, const float* og, float clamp, int64_t n, cudaStream_t s) {
   if (n <= 0) return GN_OK;
-  int blocks = (int)std::min<int64_t>((n + 255) / 256, (int64_t)kNumSM * 16);
+  int blocks = (int)std::min<int64_t>((n + 255) / 256, (int64_t)num_sms() * 16);
   swiglu_bwd_kernel<<<blocks, 256, 0, s>>>(gg, ug, gate, up, og, clamp, n);
   GN_LAUNCH_CHECK();
   return GN_OK;
@@ -109,7 +109,7 @@ __global__ void __launch_bounds__(256) split_matrix_kernel(const float* src, flo
 }
 int split_matrix_launch(const float* src, float* hi, float* lo, int64_t rows, int cols, int64_t ld, cudaStream_t s) {
   if (rows <= 0 || cols <= 0) return GN_OK;
-  const int blocks = (int)std::min<int64_t>((rows * cols + 255) / 256, (int64_t)kNumSM * 16);
+  const int blocks = (int)std::min<int64_t>((rows * cols + 255) / 256, (int64_t)num_sms() * 16);
   split_matrix_kernel<<<blocks, 256, 0, s>>>(src, hi, lo, rows, cols, ld);
   GN_LAUNCH_CHECK();
   return GN_OK;
@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(256) fill_kernel(float* dst, float v, int64_t 
 }
 int fill_launch(float* dst, float value, int64_t n, cudaStream_t s) {
   if (n <= 0) return GN_OK;
-  int blocks = (int)std::min<int64_t>((n + 255) / 256, (int64_t)kNumSM * 16);
+  int blocks = (int)std::min<int64_t>((n + 255) / 256, (int64_t)num_sms() * 16);
   fill_kernel<<<blocks, 256, 0, s>>>(dst, value, n);
   GN_LAUNCH_CHECK();
   return GN_OK;

@@ -22,10 +22,10 @@
 // Every wait on an mbarrier is bounded; when a bound runs out the kernel raises a
 // flag in global memory, drains and returns, and the host reports GN_ERR_TIMEOUT.
 //
-// Operands must be K-major.  The forward products (x W^T) already are; for the
-// data gradient (dY W) a transposed split copy of the weight is kept, and for the
-// weight gradient (dY^T X) both operands are transposed while they are split.
-// Split copies of parameter tensors are cached until the parameters change.
+// Operands are read K-major (x W^T: both as stored) or MN-major (an operand stored [K, M] or
+// [K, N], as in the weight gradient dY^T X and the data gradient dY W: read in place through the
+// 128-byte swizzle with 32-byte atoms, no transposed copy).  Split copies of parameter tensors
+// are cached per stream until the parameters change.
 #include <cuda.h>
 
 #include <map>
@@ -564,34 +564,56 @@ __global__ void __launch_bounds__(256) split_transpose_kernel(const float* __res
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
-int* g_err_flag = nullptr;
 long long* g_trace = nullptr;   // device buffer of 1024 slots (GN_TC_TRACE builds)
 std::mutex g_mu;
-// GN_TC_MN=0 keeps the transposing operand split for products whose operands are stored [K, M] / [K, N].
-// GN_TC_PDL=0 launches the products without programmatic stream serialization.
-const bool g_mn_3d = [] { const char* e = getenv("GN_TC_MN3D"); return !(e && e[0] == '0'); }();
-const bool g_use_pdl = [] { const char* e = getenv("GN_TC_PDL"); return !(e && e[0] == '0'); }();
-// CTAs of the persistent form: one per SM; GN_TC_PERSISTENT=0 switches the form off, GN_TC_PERSISTENT=<n> runs it on n CTAs
-// (tests use a handful, so that small products walk several tiles per CTA too).
-const int g_persistent_ctas = [] { const char* e = getenv("GN_TC_PERSISTENT"); const int v = e ? atoi(e) : kNumSM; return v < 0 ? 0 : v; }();
-const bool g_allow_mn = [] { const char* e = getenv("GN_TC_MN"); return !(e && e[0] == '0'); }();
-
 
 struct SplitBuf { float* hi = nullptr; float* lo = nullptr; size_t floats = 0; int64_t ld = 0; bool fresh = true; bool mn = false; };
-// Cached splits of parameter tensors: key = (pointer, rows, cols, transposed).
-std::map<std::tuple<const void*, int64_t, int64_t, int>, SplitBuf> g_static;
-SplitBuf g_dyn[2];  // scratch for the activation operands (A and B of the current product)
-struct { const void* src = nullptr; int64_t ld = 0, rows = 0, cols = 0; bool valid = false; } g_last_a;   // what g_dyn[0] holds
+
+// Everything a product needs beyond its operands lives here, one instance per (device, stream): products issued on
+// different streams or devices never share scratch, and the bounded-wait flag is read on the stream that raised it.
+struct GemmState {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  int* err_flag = nullptr;
+  // Cached splits of parameter tensors: key = (pointer, rows, cols, transposed).
+  std::map<std::tuple<const void*, int64_t, int64_t, int>, SplitBuf> statics;
+  SplitBuf dyn[2];  // scratch for the activation operands (A and B of the current product)
+  struct { const void* src = nullptr; int64_t ld = 0, rows = 0, cols = 0; bool valid = false; } last_a;   // what dyn[0] holds
+  float* splitk_ws = nullptr;
+  size_t splitk_floats = 0;
+  // options (gn_ctx_set_option)
+  int persistent_ctas = -1;   // CTAs of the persistent form: -1 = one per SM, 0 = form off, n = run it on n CTAs
+  bool pdl = true;            // programmatic dependent launch of the products
+  bool mn = true;             // read [K, M] / [K, N] operands MN-major instead of transposing them while splitting
+  bool mn3d = true;           // one 3-D TMA box per MN-major tile instead of one 2-D box per 32 columns
+};
+std::map<std::pair<int, cudaStream_t>, GemmState*> g_states;
+
+// g_mu held by the caller.
+int state_for(cudaStream_t s, GemmState** out) {
+  int device = 0;
+  GN_CUDA(cudaGetDevice(&device));
+  auto key = std::make_pair(device, s);
+  auto it = g_states.find(key);
+  if (it == g_states.end()) {
+    GemmState* st = new GemmState();
+    st->device = device; st->stream = s;
+    GN_CUDA(cudaMalloc((void**)&st->err_flag, sizeof(int)));
+    GN_CUDA(cudaMemsetAsync(st->err_flag, 0, sizeof(int), s));
+    it = g_states.emplace(key, st).first;
+  }
+  *out = it->second;
+  return GN_OK;
+}
+int persistent_ctas(const GemmState& st) { return st.persistent_ctas < 0 ? num_sms() : st.persistent_ctas; }
 
 int ensure_init() {
-  if (g_encode && g_err_flag) return GN_OK;
+  if (g_encode) return GN_OK;
   void* fn = nullptr;
   cudaDriverEntryPointQueryResult q;
   GN_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
   GN_REQUIRE(fn != nullptr && q == cudaDriverEntryPointSuccess, "cuTensorMapEncodeTiled is not available from this driver");
   g_encode = (EncodeTiledFn)fn;
-  GN_CUDA(cudaMalloc((void**)&g_err_flag, sizeof(int)));
-  GN_CUDA(cudaMemset(g_err_flag, 0, sizeof(int)));
   return GN_OK;
 }
 
@@ -644,15 +666,15 @@ int ensure_buf(SplitBuf& b, size_t floats) {
 
 // Produces K-major hi/lo copies of an operand.  `rows` x `k` is the logical operand
 // (rows = M or N).  stored_transposed: the source is stored [k, rows] (pitch ld).
-int split_operand(const float* src, int64_t ld, int64_t rows, int64_t k, bool stored_transposed, bool is_static, int which, SplitBuf& out, cudaStream_t s,
-                  bool allow_mn = false) {
+int split_operand(GemmState& gs, const float* src, int64_t ld, int64_t rows, int64_t k, bool stored_transposed, bool is_static, int which, SplitBuf& out,
+                  cudaStream_t s, bool allow_mn = false) {
   if (stored_transposed && allow_mn && !is_static && rows % 4 == 0 && ld % 4 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
     // The source is row-major [k, rows]: keep it that way (a plain split, no transpose) and let the tensor core read it MN-major.
-    SplitBuf* target = &g_dyn[which];
+    SplitBuf* target = &gs.dyn[which];
     GN_TRY(ensure_buf(*target, (size_t)k * rows));
     target->ld = rows; target->mn = true;
     const int64_t total = k * (rows / 4);
-    const int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)kNumSM * 16);
+    const int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)num_sms() * 16);
     split_kernel<<<std::max(blocks, 1), 256, 0, s>>>(src, ld, target->hi, target->lo, rows, k, (int)rows);
     GN_LAUNCH_CHECK();
     out = *target;
@@ -662,18 +684,18 @@ int split_operand(const float* src, int64_t ld, int64_t rows, int64_t k, bool st
   auto key = std::make_tuple((const void*)src, rows, k, stored_transposed ? 1 : 0);
   SplitBuf buf;
   if (is_static) {
-    auto it = g_static.find(key);
-    if (it != g_static.end()) {
+    auto it = gs.statics.find(key);
+    if (it != gs.statics.end()) {
       if (it->second.fresh) { out = it->second; return GN_OK; }
       buf = it->second;          // the parameters changed: split again into the buffers this entry already owns
     }
   }
-  SplitBuf* target = is_static ? &buf : &g_dyn[which];
+  SplitBuf* target = is_static ? &buf : &gs.dyn[which];
   GN_TRY(ensure_buf(*target, (size_t)rows * kp));
   target->ld = kp; target->mn = false;
   if (!stored_transposed) {
     int64_t total = rows * (k / 4);
-    int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)kNumSM * 16);
+    int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)num_sms() * 16);
     split_kernel<<<std::max(blocks, 1), 256, 0, s>>>(src, ld, target->hi, target->lo, kp, rows, (int)k);
   } else {
     dim3 grid(ceil_div(rows, 32), ceil_div(kp, 32));   // source is [k, rows]: x over its columns (= rows), y over its rows (= k)
@@ -681,7 +703,7 @@ int split_operand(const float* src, int64_t ld, int64_t rows, int64_t k, bool st
   }
   GN_LAUNCH_CHECK();
   target->fresh = true;
-  if (is_static) g_static[key] = *target;
+  if (is_static) gs.statics[key] = *target;
   out = *target;
   return GN_OK;
 }
@@ -715,11 +737,9 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
   }
 }
 
-float* g_splitk_ws = nullptr;
-size_t g_splitk_floats = 0;
 
 template <int BN, int STAGES>
-int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int M, int N, int K, int splits, cudaStream_t s, Partials* leave = nullptr) {
+int launch_tc(GemmState& gs, const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int M, int N, int K, int splits, cudaStream_t s, Partials* leave = nullptr) {
   using S = TcSmem<BN, STAGES>;
   static bool configured = false;
   if (!configured) {
@@ -728,12 +748,12 @@ int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int
     configured = true;
   }
   CUtensorMap mah, mal, mbh, mbl;
-  const bool a3 = a.mn && g_mn_3d && M % 32 == 0;
+  const bool a3 = a.mn && gs.mn3d && M % 32 == 0;
   if (a3) { GN_TRY(make_map_mn3(&mah, a.hi, M, K, a.ld, TBM / 32)); GN_TRY(make_map_mn3(&mal, a.lo, M, K, a.ld, TBM / 32)); }
   else if (a.mn) { GN_TRY(make_map_mn(&mah, a.hi, M, K, a.ld)); GN_TRY(make_map_mn(&mal, a.lo, M, K, a.ld)); }
   else { GN_TRY(make_map(&mah, a.hi, M, K, a.ld, TBM)); GN_TRY(make_map(&mal, a.lo, M, K, a.ld, TBM)); }
   const int brows = ep_in.groups > 0 ? ep_in.groups * N : N;
-  const bool b3 = b.mn && g_mn_3d && brows % 32 == 0;
+  const bool b3 = b.mn && gs.mn3d && brows % 32 == 0;
   if (b3) { GN_TRY(make_map_mn3(&mbh, b.hi, brows, K, b.ld, BN / 32)); GN_TRY(make_map_mn3(&mbl, b.lo, brows, K, b.ld, BN / 32)); }
   else if (b.mn) { GN_TRY(make_map_mn(&mbh, b.hi, brows, K, b.ld)); GN_TRY(make_map_mn(&mbl, b.lo, brows, K, b.ld)); }
   else { GN_TRY(make_map(&mbh, b.hi, brows, K, b.ld, BN)); GN_TRY(make_map(&mbl, b.lo, brows, K, b.ld, BN)); }
@@ -741,13 +761,13 @@ int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int
   ep.a_mn = a3 ? 2 : (a.mn ? 1 : 0); ep.b_mn = b3 ? 2 : (b.mn ? 1 : 0);
   if (splits > 1) {
     size_t need = (size_t)splits * M * N;
-    if (need > g_splitk_floats) {
-      if (g_splitk_ws) cudaFree(g_splitk_ws);
-      g_splitk_ws = nullptr; g_splitk_floats = 0;
-      if (cudaMalloc((void**)&g_splitk_ws, need * sizeof(float)) != cudaSuccess) { set_error("tcgen05 gemm: cannot allocate the split-K workspace"); return GN_ERR_NOMEM; }
-      g_splitk_floats = need;
+    if (need > gs.splitk_floats) {
+      if (gs.splitk_ws) cudaFree(gs.splitk_ws);
+      gs.splitk_ws = nullptr; gs.splitk_floats = 0;
+      if (cudaMalloc((void**)&gs.splitk_ws, need * sizeof(float)) != cudaSuccess) { set_error("tcgen05 gemm: cannot allocate the split-K workspace"); return GN_ERR_NOMEM; }
+      gs.splitk_floats = need;
     }
-    ep.C = g_splitk_ws; ep.ldc = N; ep.aux = nullptr; ep.epi = EPI_STORE; ep.split_stride = (int64_t)M * N; ep.c_hi = ep.c_lo = nullptr;
+    ep.C = gs.splitk_ws; ep.ldc = N; ep.aux = nullptr; ep.epi = EPI_STORE; ep.split_stride = (int64_t)M * N; ep.c_hi = ep.c_lo = nullptr;
   }
   dim3 grid(ceil_div(N, BN), ceil_div(M, TBM) + ep_in.groups, splits);   // grouped: an upper bound on the sum of per-group tiles
   // More tiles than SMs and a short K loop: one CTA per SM walks the tiles, so that a tile's store (a fifth of a
@@ -757,32 +777,33 @@ int launch_tc(const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int
   // Epilogues that read (accumulate, residual, relu^2 backward) gain nothing from the form but lose nothing either
   // once their reads are issued four rows at a time.
   const int64_t tiles_total = (int64_t)ceil_div(N, BN) * ceil_div(M, TBM);
-  if (g_persistent_ctas > 0 && splits == 1 && ep_in.groups == 0 && tiles_total > g_persistent_ctas && tiles_total < (int64_t)1 << 30 &&
+  const int pctas = persistent_ctas(gs);
+  if (pctas > 0 && splits == 1 && ep_in.groups == 0 && tiles_total > pctas && tiles_total < (int64_t)1 << 30 &&
       K <= 4096) {
     ep.tiles_total = (int)tiles_total; ep.tiles_n = ceil_div(N, BN);
     const int tiles_m = ceil_div(M, TBM);
     // few row tiles (the rollout's lm_head): all of them next to each other; otherwise bands of 16 column tiles
-    ep.tiles_gn = tiles_m < 10 ? std::max(1, g_persistent_ctas / tiles_m) : 16;   // measured: lm_head at 512 rows 0.217 -> 0.193 ms, 16384 x 32768 x 768 4.10 -> 3.42 ms
+    ep.tiles_gn = tiles_m < 10 ? std::max(1, pctas / tiles_m) : 16;   // measured: lm_head at 512 rows 0.217 -> 0.193 ms, 16384 x 32768 x 768 4.10 -> 3.42 ms
     if (ep.tiles_gn > ep.tiles_n) ep.tiles_gn = ep.tiles_n;
-    grid = dim3(g_persistent_ctas, 1, 1);
+    grid = dim3(pctas, 1, 1);
   }
   {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid; cfg.blockDim = dim3(64 + 32 * (BN > 128 ? 8 : 4)); cfg.dynamicSmemBytes = ep.tiles_total > 0 ? S::TOTAL : S::TOTAL - S::STG_BYTES; cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = g_use_pdl ? 1 : 0;
+    attr[0].val.programmaticStreamSerializationAllowed = gs.pdl ? 1 : 0;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    if (ep.tiles_total > 0) GN_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, true>, mah, mal, mbh, mbl, ep, M, N, K, g_err_flag));
-    else GN_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, false>, mah, mal, mbh, mbl, ep, M, N, K, g_err_flag));
+    if (ep.tiles_total > 0) GN_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, true>, mah, mal, mbh, mbl, ep, M, N, K, gs.err_flag));
+    else GN_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, false>, mah, mal, mbh, mbl, ep, M, N, K, gs.err_flag));
   }
   GN_LAUNCH_CHECK();
   if (leave) {
-    if (splits > 1) *leave = Partials{g_splitk_ws, splits, (int64_t)M * N, (int64_t)N};
+    if (splits > 1) *leave = Partials{gs.splitk_ws, splits, (int64_t)M * N, (int64_t)N};
     else *leave = Partials{ep_in.C, 1, 0, ep_in.ldc};
   } else if (splits > 1) {
-    int blocks = (int)std::min<int64_t>(((int64_t)M * (N / 4) + 255) / 256, (int64_t)kNumSM * 8);
-    splitk_reduce_kernel<<<blocks, 256, 0, s>>>(g_splitk_ws, splits, (int64_t)M * N, ep_in, M, N);
+    int blocks = (int)std::min<int64_t>(((int64_t)M * (N / 4) + 255) / 256, (int64_t)num_sms() * 8);
+    splitk_reduce_kernel<<<blocks, 256, 0, s>>>(gs.splitk_ws, splits, (int64_t)M * N, ep_in, M, N);
     GN_LAUNCH_CHECK();
   }
   return GN_OK;
@@ -805,28 +826,31 @@ int gemm_tcgen05_supported(const GemmArgs& g) {
 int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
   std::lock_guard<std::mutex> lock(g_mu);
   GN_TRY(ensure_init());
+  GemmState* gsp = nullptr;
+  GN_TRY(state_for(s, &gsp));
+  GemmState& gs = *gsp;
   SplitBuf a, b;
   // A is logically [M, K]; stored transposed ([K, M]) when a_trans.
   // the source of A as stored: [src_rows, src_cols]
   const int64_t src_rows = g.a_trans ? g.K : g.M, src_cols = g.a_trans ? g.M : g.K;
   if (g.a_hi && g.a_lo && !g.a_trans) { a.hi = const_cast<float*>(g.a_hi); a.lo = const_cast<float*>(g.a_lo); a.ld = g.lda; }   // split by the producer
-  else if (g.a_reuse && g_last_a.valid && g_last_a.src == g.A && g_last_a.ld == g.lda && g_last_a.rows == src_rows && g_last_a.cols == src_cols &&
-           (!g.a_trans || g_allow_mn)) {
-    a = g_dyn[0]; a.ld = src_cols; a.mn = g.a_trans != 0;   // the plain split of the previous product, read K-major or MN-major
+  else if (g.a_reuse && gs.last_a.valid && gs.last_a.src == g.A && gs.last_a.ld == g.lda && gs.last_a.rows == src_rows && gs.last_a.cols == src_cols &&
+           (!g.a_trans || gs.mn)) {
+    a = gs.dyn[0]; a.ld = src_cols; a.mn = g.a_trans != 0;   // the plain split of the previous product, read K-major or MN-major
   } else {
-    GN_TRY(split_operand(g.A, g.lda, g.M, g.K, g.a_trans != 0, g.a_static != 0, 0, a, s, g_allow_mn));
+    GN_TRY(split_operand(gs, g.A, g.lda, g.M, g.K, g.a_trans != 0, g.a_static != 0, 0, a, s, gs.mn));
     // a plain (untransposed) split with an unpadded pitch can serve the next product too
     const bool plain = !g.a_static && src_cols % 4 == 0 && (g.a_trans ? a.mn : true);
-    g_last_a.valid = plain; g_last_a.src = g.A; g_last_a.ld = g.lda; g_last_a.rows = src_rows; g_last_a.cols = src_cols;
+    gs.last_a.valid = plain; gs.last_a.src = g.A; gs.last_a.ld = g.lda; gs.last_a.rows = src_rows; gs.last_a.cols = src_cols;
   }
   // B is logically [N, K]; stored that way when b_trans (weights [out, in]), else stored [K, N].
-  if (g.b_hi && g.b_lo && !g.b_trans && g_allow_mn && g.groups == 0 && g.ldb % 4 == 0) {
+  if (g.b_hi && g.b_lo && !g.b_trans && gs.mn && g.groups == 0 && g.ldb % 4 == 0) {
     b.hi = const_cast<float*>(g.b_hi); b.lo = const_cast<float*>(g.b_lo); b.ld = g.ldb; b.mn = true;   // split by the producer
   } else {
-    GN_TRY(split_operand(g.B, g.ldb, g.groups > 0 ? (int64_t)g.groups * g.N : g.N, g.K, g.b_trans == 0, g.b_static != 0, 1, b, s, g_allow_mn));
+    GN_TRY(split_operand(gs, g.B, g.ldb, g.groups > 0 ? (int64_t)g.groups * g.N : g.N, g.K, g.b_trans == 0, g.b_static != 0, 1, b, s, gs.mn));
   }
   TcEpilogue ep{g.C, g.ldc, g.aux, g.ldaux, g.epilogue, g.scalar, 0, g.c_hi, g.c_lo, g_trace, g.group_counts, g.groups, 0, 0, 0, 0, 1};
-  if (g.groups > 0) return launch_tc<128, 3>(a, b, ep, g.M, g.N, g.K, 1, s, nullptr);
+  if (g.groups > 0) return launch_tc<128, 3>(gs, a, b, ep, g.M, g.N, g.K, 1, s, nullptr);
   // Filling the machine when the output has few tiles (the rollout's products have 512 rows):
   // the K loop is split over gridDim.z so that about one CTA per SM runs, each writing a partial
   // tile that a second pass sums in a fixed order (deterministic, unlike atomics).  Narrow tiles
@@ -835,29 +859,68 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
   const int64_t tiles = (int64_t)ceil_div(g.M, TBM) * ceil_div(g.N, 128);
   const int nk = ceil_div(g.K, TBK);
   int splits = 1;
-  if (tiles < kNumSM / 2 && g.N % 4 == 0 && g.ldc % 4 == 0) {
-    splits = (int)std::min<int64_t>(kNumSM / tiles, nk / 4);   // at least 4 k-blocks per split
+  if (tiles < num_sms() / 2 && g.N % 4 == 0 && g.ldc % 4 == 0) {
+    splits = (int)std::min<int64_t>(num_sms() / tiles, nk / 4);   // at least 4 k-blocks per split
     if (splits < 1) splits = 1;
   }
   // Wide 128 x 256 tiles when the output is large: the K loop is bound by the 64 B/clk/SM path from
   // L2, and a 256-column tile reads the A operand once for twice the work (96 KB per k-block for
   // two 128 x 128 units instead of 128 KB).
-  if (splits == 1 && g.N >= 512 && (int64_t)ceil_div(g.M, TBM) * ceil_div(g.N, 256) >= kNumSM * 3 / 2)
-    return launch_tc<256, 2>(a, b, ep, g.M, g.N, g.K, 1, s, g.leave);
-  return launch_tc<128, 3>(a, b, ep, g.M, g.N, g.K, splits, s, g.leave);
+  if (splits == 1 && g.N >= 512 && (int64_t)ceil_div(g.M, TBM) * ceil_div(g.N, 256) >= num_sms() * 3 / 2)
+    return launch_tc<256, 2>(gs, a, b, ep, g.M, g.N, g.K, 1, s, g.leave);
+  return launch_tc<128, 3>(gs, a, b, ep, g.M, g.N, g.K, splits, s, g.leave);
 }
 
-// Drops the cached splits of parameter tensors (call after the parameters change).
-// The parameters changed in place (an optimizer step, an upload): cached splits keep their buffers and are redone on next use.
+// The parameters changed in place (an optimizer step, an upload): cached splits on this device keep their buffers and
+// are redone on next use.
 void gemm_tcgen05_mark_stale() {
   std::lock_guard<std::mutex> lock(g_mu);
-  for (auto& kv : g_static) kv.second.fresh = false;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return;
+  for (auto& st : g_states)
+    if (st.first.first == device)
+      for (auto& kv : st.second->statics) kv.second.fresh = false;
 }
+// Parameter storage on this device is going away: free the cached splits that are keyed by its addresses.
 void gemm_tcgen05_invalidate() {
   std::lock_guard<std::mutex> lock(g_mu);
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return;
   cudaDeviceSynchronize();
-  for (auto& kv : g_static) { cudaFree(kv.second.hi); cudaFree(kv.second.lo); }
-  g_static.clear();
+  for (auto& st : g_states) {
+    if (st.first.first != device) continue;
+    for (auto& kv : st.second->statics) { cudaFree(kv.second.hi); cudaFree(kv.second.lo); }
+    st.second->statics.clear();
+  }
+}
+// The stream is going away (its context is destroyed): free everything held for it.
+void gemm_tcgen05_release(cudaStream_t s) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return;
+  auto it = g_states.find(std::make_pair(device, s));
+  if (it == g_states.end()) return;
+  cudaStreamSynchronize(s);
+  GemmState* st = it->second;
+  for (auto& kv : st->statics) { cudaFree(kv.second.hi); cudaFree(kv.second.lo); }
+  for (SplitBuf& b : st->dyn) { if (b.hi) { cudaFree(b.hi); cudaFree(b.lo); } }
+  if (st->splitk_ws) cudaFree(st->splitk_ws);
+  if (st->err_flag) cudaFree(st->err_flag);
+  delete st;
+  g_states.erase(it);
+}
+// Options of the products issued on stream s.  Unknown names return GN_ERR_INVALID.
+int gemm_tcgen05_option(cudaStream_t s, const char* name, int value) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  GemmState* st = nullptr;
+  GN_TRY(state_for(s, &st));
+  const std::string n = name;
+  if (n == "gemm_persistent_ctas") st->persistent_ctas = value;
+  else if (n == "gemm_pdl") st->pdl = value != 0;
+  else if (n == "gemm_mn_major") st->mn = value != 0;
+  else if (n == "gemm_mn_3d") st->mn3d = value != 0;
+  else { set_error("unknown option '%s'", name); return GN_ERR_INVALID; }
+  return GN_OK;
 }
 
 #ifdef GN_TC_TRACE
@@ -874,14 +937,22 @@ extern "C" int gn_debug_gemm_trace(long long* host_out, int arm) {
 }
 #endif
 
-// Reads and clears the device-side timeout flag.
+// Reads and clears the device-side timeout flag of the stream's products.
 int gemm_tcgen05_check(cudaStream_t s) {
-  if (!g_err_flag) return GN_OK;
+  int* flag_dev = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    int device = 0;
+    GN_CUDA(cudaGetDevice(&device));
+    auto it = g_states.find(std::make_pair(device, s));
+    if (it == g_states.end()) return GN_OK;
+    flag_dev = it->second->err_flag;
+  }
   int flag = 0;
-  GN_CUDA(cudaMemcpyAsync(&flag, g_err_flag, sizeof(int), cudaMemcpyDeviceToHost, s));
+  GN_CUDA(cudaMemcpyAsync(&flag, flag_dev, sizeof(int), cudaMemcpyDeviceToHost, s));
   GN_CUDA(cudaStreamSynchronize(s));
   if (flag) {
-    cudaMemsetAsync(g_err_flag, 0, sizeof(int), s);
+    cudaMemsetAsync(flag_dev, 0, sizeof(int), s);
     set_error("tcgen05 gemm: a bounded mbarrier wait ran out (pipeline stalled)");
     return GN_ERR_TIMEOUT;
   }

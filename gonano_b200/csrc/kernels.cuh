@@ -81,6 +81,7 @@ int attention_decode_launch(const float* q, int64_t q_rstride, const float* kcac
 // copies (a replicated prompt); those keys are read once per group.  The partial buffers then need
 // attention_decode_prefix_splits(...) + splits slots per (row, query head).
 int attention_decode_splits(int rows, int Hkv, int max_ctx);
+void attention_decode_prefix_mode(int mode);   // -1 automatic, 0 off, 1 on wherever the pass applies
 int attention_decode_prefix_splits(int rows, int group, int Hq, int Hkv, int D, int prefix_len);
 
 // ----------------------------------------------------------------- sampler.cu

@@ -163,7 +163,7 @@ int pg_loss_launch(const float* logits, const int32_t* targets, const float* adv
     auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     bool vec = al(logits) && (!dlogits || al(dlogits)) && vocab % 4 == 0 && ld % 4 == 0 && ldd % 4 == 0;
     // In the vector path the register window covers LIPT*LT columns as float4 groups.
-    int grid = (int)std::min<int64_t>(rows, (int64_t)kNumSM * 8);
+    int grid = (int)std::min<int64_t>(rows, (int64_t)num_sms() * 8);
     if (vec) pg_loss_kernel<true><<<grid, LT, 0, s>>>(logits, targets, adv, rows, vocab, ld, seq_len, norm, softcap, nll, dlogits, ldd, row_loss, bad_targets);
     else pg_loss_kernel<false><<<grid, LT, 0, s>>>(logits, targets, adv, rows, vocab, ld, seq_len, norm, softcap, nll, dlogits, ldd, row_loss, bad_targets);
     GN_LAUNCH_CHECK();

@@ -429,19 +429,30 @@ int gn_ctx_create(int device, void* stream, gn_ctx** out) {
   if (stream) { c->stream = (cudaStream_t)stream; c->own_stream = false; }
   else { GN_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking)); c->own_stream = true; }
   c->gemm_kind = gemm_default_kind();
-  c->use_graphs = std::getenv("GN_NO_GRAPH") == nullptr;   // debugging aid: GN_NO_GRAPH=1 keeps the decode loop eager
+  c->use_graphs = true;
   *out = c;
   return GN_OK;
 }
 int gn_ctx_destroy(gn_ctx* c) {
   if (!c) return GN_OK;
   cudaSetDevice(c->device);
+  gemm_release_stream(c->stream);
   if (c->own_stream) cudaStreamDestroy(c->stream);
   delete c;
   return GN_OK;
 }
 int gn_ctx_sync(gn_ctx* c) { GN_REQUIRE(c, "null ctx"); GN_CUDA(cudaSetDevice(c->device)); GN_CUDA(cudaStreamSynchronize(c->stream)); return GN_OK; }
 int gn_ctx_launch_count(gn_ctx* c, int64_t* out) { GN_REQUIRE(out, "null out"); *out = launch_count(); return GN_OK; }
+int gn_ctx_set_option(gn_ctx* c, const char* name, int value) {
+  GN_REQUIRE(name, "gn_ctx_set_option: null name");
+  const std::string n = name;
+  if (n == "decode_prefix_sharing") { attention_decode_prefix_mode(value); return GN_OK; }
+  if (c && n == "decode_graph") { c->use_graphs = value != 0; return GN_OK; }
+  cudaStream_t s = nullptr;
+  if (c) { GN_CUDA(cudaSetDevice(c->device)); s = c->stream; }
+  else { s = tier_a_stream_or_null(); GN_REQUIRE(s != nullptr, "gn_ctx_set_option(NULL, ...): no stand-alone call has run yet"); }
+  return gemm_set_option(s, name, value);
+}
 int gn_ctx_set_gemm(gn_ctx* c, int kind) { GN_REQUIRE(c && (kind == 0 || kind == 1), "gemm kind must be 0 or 1"); c->gemm_kind = kind; return GN_OK; }
 
 int gn_model_create(gn_ctx* ctx, const gn_config* cfg, gn_model** out) {

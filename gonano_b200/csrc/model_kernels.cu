@@ -476,7 +476,7 @@ __global__ void __launch_bounds__(256) mix_bwd_kernel(const float* dXin, const f
 int mix_backward_launch(const float* dXin, const float* prevX, const float* X0, const float* rho, const float* chi, int layer, float* dX, float* dX0,
                         int first, double* acc_rho, double* acc_chi, int64_t n, cudaStream_t s) {
   if (n <= 0) return GN_OK;
-  int blocks = (int)std::min<int64_t>((n + 255) / 256, (int64_t)kNumSM * 8);
+  int blocks = (int)std::min<int64_t>((n + 255) / 256, (int64_t)num_sms() * 8);
   mix_bwd_kernel<<<blocks, 256, 0, s>>>(dXin, prevX, X0, rho, chi, layer, dX, dX0, first, acc_rho, acc_chi, n);
   GN_LAUNCH_CHECK();
   return GN_OK;
@@ -491,7 +491,7 @@ __global__ void __launch_bounds__(256) dot_acc_kernel(const float* a, const floa
 }
 int dot_accumulate_launch(const float* a, const float* b, int64_t n, double sign, double* acc, cudaStream_t s) {
   if (n <= 0) return GN_OK;
-  int blocks = (int)std::min<int64_t>((n + 255) / 256, (int64_t)kNumSM * 8);
+  int blocks = (int)std::min<int64_t>((n + 255) / 256, (int64_t)num_sms() * 8);
   dot_acc_kernel<<<blocks, 256, 0, s>>>(a, b, n, sign, acc);
   GN_LAUNCH_CHECK();
   return GN_OK;
@@ -504,7 +504,7 @@ __global__ void __launch_bounds__(256) axpy_kernel(float* dst, const float* src,
 }
 int axpy_launch(float* dst, const float* src, float alpha, const float* alpha_dev, float alpha_sign, int accumulate, int64_t n, cudaStream_t s) {
   if (n <= 0) return GN_OK;
-  int blocks = (int)std::min<int64_t>((n + 255) / 256, (int64_t)kNumSM * 8);
+  int blocks = (int)std::min<int64_t>((n + 255) / 256, (int64_t)num_sms() * 8);
   axpy_kernel<<<blocks, 256, 0, s>>>(dst, src, alpha, alpha_dev, alpha_sign, accumulate, n);
   GN_LAUNCH_CHECK();
   return GN_OK;

@@ -346,7 +346,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(float* xout, const flo
   }
 }
 
-int grid_for(int64_t n) { return (int)std::max<int64_t>(1, std::min<int64_t>((n + 255) / 256, (int64_t)kNumSM * 16)); }
+int grid_for(int64_t n) { return (int)std::max<int64_t>(1, std::min<int64_t>((n + 255) / 256, (int64_t)num_sms() * 16)); }
 
 }  // namespace
 

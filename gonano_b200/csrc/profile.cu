@@ -42,7 +42,7 @@ struct Bufs {
 };
 
 int synth(float* dst, int64_t n, float lo, float hi, uint32_t salt, cudaStream_t s) {
-  synth_kernel<<<kNumSM * 8, 256, 0, s>>>(dst, n, lo, hi, salt);
+  synth_kernel<<<num_sms() * 8, 256, 0, s>>>(dst, n, lo, hi, salt);
   GN_LAUNCH_CHECK();
   return GN_OK;
 }

@@ -47,6 +47,10 @@ class Context:
     def set_gemm(self, kind: int):
         check(self.lib.gn_ctx_set_gemm(self.h, kind))
 
+    def set_option(self, name: str, value: int):
+        """Tuning / test switches of include/gonano_cuda.h (gn_ctx_set_option)."""
+        check(self.lib.gn_ctx_set_option(self.h, name.encode(), int(value)))
+
     def profile_kernel(self, kernel: str, dims, iters: int = 10) -> float:
         """Mean milliseconds per launch of one hot kernel on synthetic device data (CUDA events)."""
         arr = (C.c_int64 * len(dims))(*[int(x) for x in dims])

@@ -27,8 +27,12 @@
  *     (tensors/tensor.go:10-17, tensors/ids.go:8-11).
  *   - Tier A is safe to call from any number of OS threads (the reference
  *     calls its backend from many goroutines, model/attention.go:311-320);
- *     calls are serialised on one internal lock per process.
- *   - Tier B objects are single-caller: one thread per gn_ctx at a time.
+ *     calls are serialised on one internal lock per process and run on the CUDA device that was
+ *     current at the first of them (another current device is refused with GN_ERR_UNSUPPORTED;
+ *     other devices are reached through a gn_ctx).
+ *   - Tier B objects are single-caller: one thread per gn_ctx at a time.  Every gn_ctx (and
+ *     Tier A) owns its scratch memory per (device, stream): contexts on different streams or
+ *     devices of one process do not share buffers, so they may run concurrently.
  *   - there is no CPU fallback: without a CUDA device every compute call
  *     fails with GN_ERR_CUDA.
  */
@@ -225,6 +229,16 @@ int gn_ctx_sync(gn_ctx* ctx);
 int gn_ctx_launch_count(gn_ctx* ctx, int64_t* out);
 /* Select the GEMM path: 0 = SIMT float32, 1 = tcgen05 3xTF32 (default when built). */
 int gn_ctx_set_gemm(gn_ctx* ctx, int kind);
+
+/* Tuning and test switches (no counterpart in the reference).  ctx == NULL addresses the stand-alone
+ * (Tier A) calls, after the first of them has run.  Names:
+ *   "decode_graph"           1 (default) replays the decode step from a CUDA graph, 0 keeps it eager
+ *   "decode_prefix_sharing"  -1 (default) automatic, 0 / 1 shared-prompt attention pass off / on (process-wide)
+ *   "gemm_persistent_ctas"   -1 (default) one CTA per SM for the tile-walking form, 0 form off, n = n CTAs
+ *   "gemm_pdl"               1 (default) products launch with programmatic stream serialization
+ *   "gemm_mn_major"          1 (default) operands stored [K, M] / [K, N] are read in place, 0 transposes them
+ *   "gemm_mn_3d"             1 (default) one 3-D bulk-tensor copy per such tile instead of one per 32 columns */
+int gn_ctx_set_option(gn_ctx* ctx, const char* name, int value);
 
 /* model.NewTransformer (model/transformer.go:49-83): parameters start at zero. */
 int gn_model_create(gn_ctx* ctx, const gn_config* config, gn_model** out);

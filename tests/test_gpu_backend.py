@@ -11,8 +11,15 @@ AWKWARD = [1, 7, 31, 64, 513, 1031]
 
 @pytest.fixture(scope="module")
 def bk():
+    import os
+    from gonano_b200 import _lib
     from gonano_b200.backend import CudaBackend
-    return CudaBackend()
+    b = CudaBackend()
+    if os.environ.get("GN_TEST_GEMM_PERSISTENT_CTAS"):   # set by the test that re-runs the product tests on a small persistent grid
+        one = np.ones(4, np.float32)
+        b.add(one, one)                                   # the stand-alone calls' stream exists after their first call
+        _lib.check(_lib.load().gn_ctx_set_option(None, b"gemm_persistent_ctas", int(os.environ["GN_TEST_GEMM_PERSISTENT_CTAS"])))
+    return b
 
 
 @pytest.fixture(scope="module")

@@ -18,8 +18,11 @@ from parity import GRAD_REL, assert_gradients_close, close_elementwise, rel_err 
 
 @pytest.fixture(scope="module")
 def ctx():
+    import os
     from gonano_b200.session import Context
     c = Context(0)
+    if os.environ.get("GN_TEST_GEMM_PERSISTENT_CTAS"):   # set by the test that re-runs the parity tests on a small persistent grid
+        c.set_option("gemm_persistent_ctas", int(os.environ["GN_TEST_GEMM_PERSISTENT_CTAS"]))
     yield c
     c.close()
 
@@ -148,6 +151,37 @@ def test_policy_gradient_step(oracle, ctx, name, std, B, T, rpp):
     gm.close()
 
 
+def test_two_contexts_in_one_process_do_not_share_scratch():
+    """Two contexts (two streams) with different models, driven from two threads at once: each gets the logits it gets
+    alone.  The products' operand-split scratch, split-K workspace and error flag belong to the (device, stream)."""
+    import threading
+    from gonano_b200.session import Context, Model
+    cfg = synthetic.dense_config("h128")
+    ids = np.random.default_rng(3).integers(0, cfg["vocab_size"] - 11, (2, 160), dtype=np.int32)
+    ctxs = [Context(0), Context(0)]
+    models = []
+    for i, c in enumerate(ctxs):
+        m = Model(c, **cfg)
+        for n, v in synthetic.fill_weights(m.names, m.shape, 10 + i, std=0.05):
+            m.upload(n, v)
+        models.append(m)
+    alone = [m.forward(ids) for m in models]
+    assert not np.array_equal(alone[0], alone[1])
+    results = [[None] * 6, [None] * 6]
+
+    def work(i):
+        for k in range(6):
+            results[i][k] = models[i].forward(ids)
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(2)]
+    for t in threads: t.start()
+    for t in threads: t.join()
+    for i in range(2):
+        for k in range(6):
+            assert np.array_equal(results[i][k], alone[i]), (i, k)
+    for m in models: m.close()
+    for c in ctxs: c.close()
+
+
 def test_out_of_range_ids_are_refused(ctx):
     """An id outside the vocabulary would index outside the embedding table or the logits row; every session entry
     point refuses it with GN_ERR_INVALID before anything is launched (the reference panics on the slice bound)."""
@@ -210,37 +244,35 @@ def test_gemm_paths_agree(oracle, ctx):
     gm.close()
 
 
-def test_shared_prefix_decode_attention(oracle):
+def test_shared_prefix_decode_attention(ctx):
     """The shared-prefix attention pass (one CTA per group reads the replicated prompt once) is sized for large
-    batches; forced on in a child process it must reproduce the per-row kernel's rollout token for token and stay
-    within the logits tolerance of the oracle."""
-    import os, subprocess, sys, json
-    code = r'''
-import json, numpy as np
-from gonano_b200 import synthetic
-from gonano_b200.session import Context, Model
-ctx = Context(0)
-cfg = synthetic.dense_config("h128")
-m = Model(ctx, **cfg)
-for n, v in synthetic.fill_weights(m.names, m.shape, 1, std=0.05): m.upload(n, v)
-prompts = synthetic.prompts(3, 150, cfg["vocab_size"], seed=9)
-t, l, s, lg = m.generate_batch(prompts, 4, 10, 1.0, 50, np.array([5, 6, 7], np.uint64), want_logits=True)
-t2, l2, s2, _ = m.generate_batch(prompts, 4, 10, 1.0, 50, np.array([5, 6, 7], np.uint64))
-assert np.array_equal(l, l2) and all(np.array_equal(t[r, :l[r]], t2[r, :l2[r]]) for r in range(12))
-print(json.dumps({"tokens": t.tolist(), "lengths": l.tolist(), "steps": int(s), "logit_sum": float(np.abs(lg).sum()), "last": lg[s - 1].tolist()}))
-'''
+    batches; forced on it must reproduce the per-row kernel's rollout token for token and stay within float32
+    rounding of its logits (same arithmetic up to the order of the softmax merge)."""
+    from gonano_b200.session import Model
+    cfg = synthetic.dense_config("h128")
+    m = Model(ctx, **cfg)
+    for n, v in synthetic.fill_weights(m.names, m.shape, 1, std=0.05):
+        m.upload(n, v)
+    seeds = np.array([5, 6, 7, 8, 9, 10, 11, 12], np.uint64)
     outs = {}
-    for flag in ("0", "1"):
-        env = dict(os.environ, GN_PREFIX_SHARING=flag)
-        r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, cwd=os.path.dirname(os.path.dirname(__file__)))
-        assert r.returncode == 0, r.stderr[-2000:]
-        outs[flag] = json.loads(r.stdout.strip().splitlines()[-1])
-    a, b = outs["0"], outs["1"]
-    assert a["lengths"] == b["lengths"] and a["steps"] == b["steps"]
-    for r in range(12):
-        assert a["tokens"][r][:a["lengths"][r]] == b["tokens"][r][:b["lengths"][r]]
-    la, lb = np.array(a["last"]), np.array(b["last"])
-    assert rel_err(lb, la) <= 1e-4     # same arithmetic up to the order of the softmax merge
+    try:
+        for flag in (0, 1):
+            ctx.set_option("decode_prefix_sharing", flag)
+            for P, plen, G in [(3, 150, 4), (8, 128, 8)]:       # the second: groups of 8 over 128-token prompts
+                prompts = synthetic.prompts(P, plen, cfg["vocab_size"], seed=9)
+                t, l, s, lg = m.generate_batch(prompts, G, 10, 1.0, 50, seeds[:P], want_logits=True)
+                t2, l2, s2, _ = m.generate_batch(prompts, G, 10, 1.0, 50, seeds[:P])     # graph-replayed loop
+                assert np.array_equal(l, l2) and all(np.array_equal(t[r, :l[r]], t2[r, :l2[r]]) for r in range(P * G))
+                outs[(flag, P)] = (t, l, s, lg[s - 1].copy())
+    finally:
+        ctx.set_option("decode_prefix_sharing", -1)
+    for P in (3, 8):
+        (ta, la, sa, lga), (tb, lb, sb, lgb) = outs[(0, P)], outs[(1, P)]
+        assert sa == sb and np.array_equal(la, lb)
+        for r in range(len(la)):
+            assert np.array_equal(ta[r, :la[r]], tb[r, :lb[r]])
+        assert rel_err(lgb, lga) <= 1e-4
+    m.close()
 
 
 def test_persistent_gemm_form_passes_the_parity_tests():
@@ -250,7 +282,7 @@ def test_persistent_gemm_form_passes_the_parity_tests():
     tile widths through that form."""
     import os, subprocess, sys
     root = os.path.dirname(os.path.dirname(__file__))
-    env = dict(os.environ, GN_TC_PERSISTENT="3")
+    env = dict(os.environ, GN_TEST_GEMM_PERSISTENT_CTAS="3")
     r = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu", "tests/test_gpu_backend.py", "tests/test_gpu_model.py",
                         "-k", "tensor_core_matmul_faithful or policy_gradient_step or forward_logits or gemm_paths_agree"],
                        capture_output=True, text=True, env=env, cwd=root)

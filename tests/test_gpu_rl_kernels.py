@@ -136,6 +136,7 @@ def test_loss_refuses_targets_outside_the_vocabulary():
     """A target >= vocab (or below -1) is never used as an index: the row is skipped on the device and the call
     reports GN_ERR_INVALID, where the reference would panic on the slice bound (tensors/loss.go:39)."""
     from gonano_b200._lib import GonanoError
+    from gonano_b200 import backend as B
     logits = np.zeros((4, 8), np.float32)
     adv = np.ones(4, np.float32)
     for bad in (8, 1000, -2):
