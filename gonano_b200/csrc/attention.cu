@@ -917,6 +917,7 @@ __global__ void __launch_bounds__(32 * NW) attn_decode_kernel(const float* __res
                                                           int64_t o_rstride, float* __restrict__ part_acc, float* __restrict__ part_ms, int splits,
                                                           float* __restrict__ out_hi, float* __restrict__ out_lo, int kmin, int slot0, int nslots) {
   pdl_trigger();
+  pdl_wait();
   // DP = head_dim rounded up to a multiple of 32; channels >= D are zero padding.
   // Keys below kmin belong to the shared-prefix kernel; this kernel's partial results then go to
   // slots slot0 .. slot0 + splits - 1 of nslots (nslots == splits and slot0 == 0 without a prefix pass).
@@ -1076,6 +1077,7 @@ __global__ void __launch_bounds__(32 * NW) attn_decode_kernel(const float* __res
 __global__ void __launch_bounds__(128) attn_decode_combine_kernel(const float* part_acc, const float* part_ms, int splits, int Hq, int D, float* out, int64_t o_rstride,
                                                                   float* out_hi, float* out_lo) {
   pdl_trigger();
+  pdl_wait();
   int row = blockIdx.x / Hq, hq = blockIdx.x % Hq;
   int64_t base = ((int64_t)row * Hq + hq) * splits;
   float gm = -INFINITY;
@@ -1262,18 +1264,18 @@ static int decode_go(const float* q, int64_t q_rstride, const float* kcache, con
   // fewer than the equivalent of ~5 four-warp CTAs per SM: two keys per iteration (shorter chain); otherwise one
   // (more resident warps)
   const int nw = attention_decode_warps(rows, Hkv);
-#define GN_DEC_LAUNCH(UU, WW) attn_decode_kernel<DP, RATIO, UU, WW><<<grid, 32 * WW, 0, s>>>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, Hq, Hkv, D, window, out, o_rstride, \
-                                                                              part_acc, part_ms, splits, out_hi, out_lo, psplits ? prefix_len : 0, psplits, nslots)
+#define GN_DEC_LAUNCH(UU, WW) GN_CUDA(launch_pdl(attn_decode_kernel<DP, RATIO, UU, WW>, grid, dim3(32 * WW), 0, s, q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, Hq, Hkv, D, window, out, o_rstride, \
+                                                                              part_acc, part_ms, splits, out_hi, out_lo, psplits ? prefix_len : 0, psplits, nslots))
   // the warps' partial results meet in static shared memory (NW x RATIO x DP floats): wide groups get fewer warps
   constexpr int kMaxW = RATIO * DP * 16 <= 10240 ? 16 : (RATIO * DP * 8 <= 10240 ? 8 : 4);
-  if (nw == 16 && kMaxW >= 16) { if constexpr (kMaxW >= 16) GN_DEC_LAUNCH(2, 16); }
-  else if (nw >= 8 && kMaxW >= 8) { if constexpr (kMaxW >= 8) GN_DEC_LAUNCH(2, 8); }
-  else if ((int64_t)rows * Hkv * splits < (int64_t)num_sms() * 5) GN_DEC_LAUNCH(2, 4);
-  else GN_DEC_LAUNCH(1, 4);
+  if (nw == 16 && kMaxW >= 16) { if constexpr (kMaxW >= 16) { GN_DEC_LAUNCH(2, 16); } }
+  else if (nw >= 8 && kMaxW >= 8) { if constexpr (kMaxW >= 8) { GN_DEC_LAUNCH(2, 8); } }
+  else if ((int64_t)rows * Hkv * splits < (int64_t)num_sms() * 5) { GN_DEC_LAUNCH(2, 4); }
+  else { GN_DEC_LAUNCH(1, 4); }
 #undef GN_DEC_LAUNCH
   GN_LAUNCH_CHECK();
   if (splits > 1) {
-    attn_decode_combine_kernel<<<rows * Hq, 128, 0, s>>>(part_acc, part_ms, nslots, Hq, D, out, o_rstride, out_hi, out_lo);
+    GN_CUDA(launch_pdl(attn_decode_combine_kernel, dim3(rows * Hq), dim3(128), 0, s, part_acc, part_ms, nslots, Hq, D, out, o_rstride, out_hi, out_lo));
     GN_LAUNCH_CHECK();
   }
   return GN_OK;

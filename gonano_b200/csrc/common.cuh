@@ -114,6 +114,19 @@ __device__ __forceinline__ float sigmoid_exact(float x) { return (float)(1.0 / (
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// Launch with programmatic stream serialization: the grid may be scheduled while the kernel in front of it on the stream
+// still runs.  ONLY for kernels that call pdl_wait() before their first access to global memory.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // hi = tf32(x) (round to nearest), lo = tf32(x - hi): the operand form of the 3xTF32 products.
 __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
   uint32_t h, l;
@@ -176,6 +189,9 @@ struct GemmArgs {
   float* aux = nullptr; int64_t ldaux = 0;
   float scalar = 0.0f;
   int a_static = 0, b_static = 0;  // operand is a parameter tensor: its tensor-core split may be cached
+  // Tensor-core path only: B holds parameters that no kernel in flight writes, so a product may request them before the
+  // kernel in front of it on the stream has finished (programmatic dependent launch).
+  int b_prefetch = 0;
   // Tensor-core path only: A already split by its producer (hi = tf32(x), lo = tf32(x - hi)), pitch lda.
   const float* a_hi = nullptr; const float* a_lo = nullptr;
   // Tensor-core path only: A (same pointer, pitch and shape, possibly through the other a_trans) is unchanged since the

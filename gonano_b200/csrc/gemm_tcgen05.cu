@@ -28,6 +28,7 @@
 // are cached per stream until the parameters change.
 #include <cuda.h>
 
+#include <atomic>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -164,7 +165,7 @@ struct TcEpilogue {
 };
 
 #ifdef GN_TC_TRACE
-#define TC_TRACE(slot) do { if (ep.trace && blockIdx.x == 0 && blockIdx.y == 0) ep.trace[(slot)] = clock64(); } while (0)
+#define TC_TRACE(slot) do { if (ep.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ep.trace[(slot)] = clock64(); } while (0)
 #else
 #define TC_TRACE(slot) do { } while (0)
 #endif
@@ -524,6 +525,244 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
   if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
 }
 
+// ------------------------------------------------------------------ few-row products (the rollout's decode step)
+//
+//   C[rows, N] = X[rows, K] * W[N, K]^T   rows in blocks of at most 256 per CTA
+//
+// With a few hundred rows or fewer a product of the decode step is bound by streaming its weights, not by the
+// multiplies.  This form therefore swaps the operands of the tensor-core instruction: a slab of 128 WEIGHT rows is the
+// 128-row A operand and the activation rows are the (narrow) B operand, so that every CTA streams a different 16 KB of
+// weights per k-block and the whole grid pulls on HBM at once, the K dimension being split over CTAs as well.  The
+// weights are read as raw float32, once: the producer warp fetches each 128 x 32 tile with one bulk-tensor copy, four
+// converter warps rewrite it in place as hi = tf32(w) and write lo = tf32(w - hi) beside it (the same split the
+// cached-copy path stores in HBM, so 4 bytes per weight cross HBM instead of 8 and no split copy is kept), and the
+// issuing thread multiplies lo*hi + hi*lo + hi*hi into tensor memory.  The activations arrive already split.
+// The accumulator holds C^T: lane = weight row n, column = activation row m; each thread of the four epilogue warps
+// (the converter warps, once the K loop is done) owns one n and stores along m, 32 consecutive n per warp store.
+//
+// With programmatic dependent launch the weight tiles of the first stages are requested BEFORE the wait on the
+// preceding kernel (weights do not depend on it), so they stream in while the small kernel in front of the product
+// still runs; the activation tiles follow after the wait.
+//
+// grid = (row blocks, weight slabs, K splits): the row blocks of one weight tile are neighbours in launch order, so
+// the tile is fetched from HBM once and found in L2 by the others.  splits > 1 leaves partial planes [split][rows][N] that the
+// consumer (or splitk_reduce_kernel) sums in a fixed order.
+constexpr int SK_W_BYTES = TBM * TBK * 4;        // 16 KB: one raw weight tile, and as much again for its lo part
+constexpr int SK_MAX_STAGES = 6;
+struct SkinnyArgs {
+  TcEpilogue ep;
+  int M, N, K;          // activation rows, weight rows, inner dimension
+  int block_rows;       // activation rows per CTA (a multiple of 16, at most 256)
+  int rowsN;            // UMMA N of a full row block: min(M, block_rows) rounded up to 16
+  int nk_per_split;     // k-blocks per K split
+  int stages;
+  int tmem_cols;        // power of two >= max(32, rowsN)
+  int prefetch;         // 1: the weights may be requested before the wait on the preceding kernel
+};
+
+// split_tf32 with integer arithmetic: adding half a tf32 unit to the magnitude bits and clearing the low 13 bits rounds to
+// nearest with ties away from zero, which is what cvt.rna.tf32.f32 does, at the full rate of the integer pipe (the
+// conversion instruction runs at a fraction of it, and the converter warps sit on the K loop's critical path).
+__device__ __forceinline__ void split_tf32_int(float x, float& hi, float& lo) {
+  hi = __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
+  const float rest = x - hi;
+  lo = __uint_as_float((__float_as_uint(rest) + 0x1000u) & 0xFFFFE000u);
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+        "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+// Epilogue of the few-row form for one thread (= one weight row n): 16 accumulator columns (= activation rows) at a
+// time out of tensor memory, the fused epilogue, one 4-byte store per row; the 32 lanes of a warp write 32
+// consecutive n of the same row.  SPLIT also writes the tf32 split of the result (c_hi / c_lo may still be null).
+template <int EPI, bool SPLIT>
+__device__ __forceinline__ void skinny_store(const TcEpilogue& e, float* Cb, uint32_t tmem_base, int quarter, int n, int m0, int un, int M, int N, bool have) {
+  for (int c0 = 0; c0 < un; c0 += 16) {
+    uint32_t r[16];
+    if (have) { tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r); tmem_ld_wait(); }
+    else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) r[j] = 0u;
+    }
+    if (n >= N) continue;
+    const int64_t mfirst = (int64_t)m0 + c0;
+    const int valid = (int)min((int64_t)16, (int64_t)M - mfirst);
+    float* cp = Cb + mfirst * e.ldc + n;
+    const float* ap = (EPI == EPI_RESIDUAL || EPI == EPI_RELU2_BWD) ? e.aux + mfirst * e.ldaux + n : nullptr;
+    float cold[16];
+    if (EPI == EPI_ACCUM || EPI == EPI_RESIDUAL || EPI == EPI_RELU2_BWD) {   // the reads of the block first, so that they are in flight together
+#pragma unroll
+      for (int j = 0; j < 16; ++j) cold[j] = (j < valid) ? (EPI == EPI_ACCUM ? cp[(int64_t)j * e.ldc] : ap[(int64_t)j * e.ldaux]) : 0.0f;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if (j < valid) {
+        const float acc = __uint_as_float(r[j]);
+        float out;
+        if (EPI == EPI_STORE) out = acc;
+        else if (EPI == EPI_ACCUM || EPI == EPI_RESIDUAL) out = cold[j] + acc;
+        else if (EPI == EPI_RELU2) { if (e.aux) e.aux[(mfirst + j) * e.ldaux + n] = acc; const float t = acc < 0.0f ? 0.0f : acc; out = t * t; }
+        else if (EPI == EPI_SOFTCAP) out = e.scalar * tanhf(acc * (1.0f / e.scalar));
+        else out = cold[j] > 0.0f ? acc * 2.0f * cold[j] : 0.0f;
+        cp[(int64_t)j * e.ldc] = out;
+        if (SPLIT && e.c_hi) { float h, l; split_tf32(out, h, l); e.c_hi[(mfirst + j) * e.ldc + n] = h; e.c_lo[(mfirst + j) * e.ldc + n] = l; }
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(192, 2) gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmXh,
+                                                             const __grid_constant__ CUtensorMap tmXl, SkinnyArgs p, int* err) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  const int XB = p.rowsN * TBK * 4;                       // bytes of one activation tile (hi or lo)
+  const int stage_bytes = 2 * SK_W_BYTES + 2 * XB;
+  const uint32_t bars = base + (uint32_t)p.stages * stage_bytes;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto conv_bar = [&](int s) { return bars + 8u * (SK_MAX_STAGES + s); };
+  auto empty_bar = [&](int s) { return bars + 8u * (2 * SK_MAX_STAGES + s); };
+  const uint32_t acc_bar = bars + 8u * (3 * SK_MAX_STAGES);
+  const uint32_t tmem_slot = bars + 8u * (3 * SK_MAX_STAGES + 1);
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + (size_t)p.stages * stage_bytes + 8 * (3 * SK_MAX_STAGES + 1));
+
+  const TcEpilogue& ep = p.ep;
+  if (threadIdx.x == 0) TC_TRACE(0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.y * TBM;
+  const int nk_total = (p.K + TBK - 1) / TBK;
+  const int kb0 = (int)blockIdx.z * p.nk_per_split;
+  const int nk = max(0, min(p.nk_per_split, nk_total - kb0));
+  const int m0 = (int)blockIdx.x * p.block_rows;
+  const int rows_here = min(p.block_rows, p.M - m0);
+  const int un = (rows_here + 15) & ~15;                  // UMMA N of this row block
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) { mbar_init(full_bar(s), 1); mbar_init(conv_bar(s), 4); mbar_init(empty_bar(s), 1); }
+    mbar_init(acc_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, (uint32_t)p.tmem_cols); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+  bool failed = false;
+  if (threadIdx.x == 0) TC_TRACE(1);
+  pdl_trigger();   // the next kernel may set up (and request its own weights) while this one runs
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- producer
+    if (lane == 0) {
+      const uint32_t tx = (uint32_t)(SK_W_BYTES + 2 * XB);
+      const int pre = p.prefetch ? min(nk, p.stages) : 0;
+      for (int kb = 0; kb < pre; ++kb) {          // weights of the first stages: independent of the preceding kernel
+        const uint32_t st = base + (uint32_t)kb * stage_bytes;
+        mbar_expect_tx(full_bar(kb), tx);
+        tma_load_2d(st, &tmW, full_bar(kb), (kb0 + kb) * TBK, n0);
+      }
+      TC_TRACE(2);
+      pdl_wait();
+      TC_TRACE(3);
+      for (int kb = 0; kb < nk; ++kb) {
+        const int s = kb % p.stages;
+        const uint32_t st = base + (uint32_t)s * stage_bytes;
+        if (kb >= pre) {
+          if (kb >= p.stages && !mbar_wait(empty_bar(s), (uint32_t)(kb / p.stages - 1) & 1u)) { failed = true; break; }
+          mbar_expect_tx(full_bar(s), tx);
+          tma_load_2d(st, &tmW, full_bar(s), (kb0 + kb) * TBK, n0);
+        }
+        tma_load_2d(st + 2 * SK_W_BYTES, &tmXh, full_bar(s), (kb0 + kb) * TBK, m0);
+        tma_load_2d(st + 2 * SK_W_BYTES + XB, &tmXl, full_bar(s), (kb0 + kb) * TBK, m0);
+        if (kb < 32) TC_TRACE(16 + kb);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc_tf32(TBM, un);
+      for (int kb = 0; kb < nk; ++kb) {
+        const int s = kb % p.stages;
+        if (!mbar_wait(conv_bar(s), (uint32_t)(kb / p.stages) & 1u)) { failed = true; break; }
+        tc_fence_after();
+        if (kb < 32) TC_TRACE(48 + kb);
+        const uint32_t st = base + (uint32_t)s * stage_bytes;
+        const uint64_t wh = smem_desc_sw128(st), wl = smem_desc_sw128(st + SK_W_BYTES);
+        const uint64_t xh = smem_desc_sw128(st + 2 * SK_W_BYTES), xl = smem_desc_sw128(st + 2 * SK_W_BYTES + XB);
+#pragma unroll
+        for (int k = 0; k < TBK / UMMA_K; ++k) {
+          const uint64_t adv = (uint64_t)((UMMA_K * 4) >> 4) * (uint64_t)k;
+          umma_tf32(tmem_base, wl + adv, xh + adv, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_tf32(tmem_base, wh + adv, xl + adv, idesc, 1u);
+          umma_tf32(tmem_base, wh + adv, xh + adv, idesc, 1u);
+        }
+        umma_commit(empty_bar(s));
+        if (kb < 32) TC_TRACE(80 + kb);
+      }
+      if (!failed) umma_commit(acc_bar);
+    }
+  } else {
+    // ------------------------------------------------------------- converters, then epilogue (warps 2..5)
+    const int ct = threadIdx.x - 64;   // 0..127
+    for (int kb = 0; kb < nk && !failed; ++kb) {
+      const int s = kb % p.stages;
+      if (!mbar_wait(full_bar(s), (uint32_t)(kb / p.stages) & 1u)) { failed = true; break; }
+      if (ct == 0 && kb < 32) TC_TRACE(112 + kb);
+      float4* wt = reinterpret_cast<float4*>(gen_base + (size_t)s * stage_bytes);
+      float4* wlo = reinterpret_cast<float4*>(gen_base + (size_t)s * stage_bytes + SK_W_BYTES);
+#pragma unroll
+      for (int i = 0; i < SK_W_BYTES / 16 / 128; ++i) {
+        const int c = i * 128 + ct;
+        const float4 v = wt[c];
+        float4 h, l;
+        split_tf32_int(v.x, h.x, l.x); split_tf32_int(v.y, h.y, l.y); split_tf32_int(v.z, h.z, l.z); split_tf32_int(v.w, h.w, l.w);
+        wt[c] = h; wlo[c] = l;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor core reads these tiles through the async proxy
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(conv_bar(s)) : "memory");
+      if (ct == 0 && kb < 32) TC_TRACE(144 + kb);
+    }
+    if (!failed && nk > 0 && !mbar_wait(acc_bar, 0u)) failed = true;
+    if (ct == 0) TC_TRACE(4);
+    if (!failed) {
+      tc_fence_after();
+      const int quarter = warp & 3;
+      const int n = n0 + quarter * 32 + lane;
+      const TcEpilogue& e = ep;
+      float* Cb = e.C + (gridDim.z > 1 ? (int64_t)blockIdx.z * e.split_stride : 0);
+      // One specialised store loop per epilogue kind, selected once per CTA: the loop bodies stay small and straight.
+      switch (e.epi) {
+        case EPI_STORE: if (e.c_hi) skinny_store<EPI_STORE, true>(e, Cb, tmem_base, quarter, n, m0, un, p.M, p.N, nk > 0);
+                        else skinny_store<EPI_STORE, false>(e, Cb, tmem_base, quarter, n, m0, un, p.M, p.N, nk > 0);
+                        break;
+        case EPI_ACCUM: skinny_store<EPI_ACCUM, false>(e, Cb, tmem_base, quarter, n, m0, un, p.M, p.N, nk > 0); break;
+        case EPI_RESIDUAL: if (e.c_hi) skinny_store<EPI_RESIDUAL, true>(e, Cb, tmem_base, quarter, n, m0, un, p.M, p.N, nk > 0);
+                           else skinny_store<EPI_RESIDUAL, false>(e, Cb, tmem_base, quarter, n, m0, un, p.M, p.N, nk > 0);
+                           break;
+        case EPI_RELU2: skinny_store<EPI_RELU2, true>(e, Cb, tmem_base, quarter, n, m0, un, p.M, p.N, nk > 0); break;
+        case EPI_SOFTCAP: skinny_store<EPI_SOFTCAP, false>(e, Cb, tmem_base, quarter, n, m0, un, p.M, p.N, nk > 0); break;
+        default: skinny_store<EPI_RELU2_BWD, false>(e, Cb, tmem_base, quarter, n, m0, un, p.M, p.N, nk > 0); break;
+      }
+    }
+  }
+  if (threadIdx.x == 64) TC_TRACE(5);
+  if (failed) {
+    atomicExch(err, 1);
+    for (int i = 0; i < 4096; ++i) __nanosleep(256);   // let bulk copies that are still in flight land
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0) TC_TRACE(6);
+  if (warp == 1) tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+}
+
 // ------------------------------------------------------------------ operand split
 // src [rows, cols] (pitch ld) -> hi, lo [rows, cols] (pitch ldd)
 __global__ void __launch_bounds__(256) split_kernel(const float* __restrict__ src, int64_t ld, float* __restrict__ hi, float* __restrict__ lo, int64_t ldd,
@@ -711,6 +950,7 @@ int split_operand(GemmState& gs, const float* src, int64_t ld, int64_t rows, int
 // Split-K second pass: C = epilogue(sum over splits of the partial tiles), in a fixed order.
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, int splits, int64_t split_stride, TcEpilogue ep, int M, int N) {
   pdl_trigger();
+  pdl_wait();
   const int nv = N >> 2;   // N is a multiple of 4 on this path
   const int64_t total = (int64_t)M * nv;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -803,7 +1043,90 @@ int launch_tc(GemmState& gs, const SplitBuf& a, const SplitBuf& b, const TcEpilo
     else *leave = Partials{ep_in.C, 1, 0, ep_in.ldc};
   } else if (splits > 1) {
     int blocks = (int)std::min<int64_t>(((int64_t)M * (N / 4) + 255) / 256, (int64_t)num_sms() * 8);
-    splitk_reduce_kernel<<<blocks, 256, 0, s>>>(gs.splitk_ws, splits, (int64_t)M * N, ep_in, M, N);
+    GN_CUDA(launch_pdl(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, s, (const float*)gs.splitk_ws, splits, (int64_t)M * N, ep_in, M, N));
+    GN_LAUNCH_CHECK();
+  }
+  return GN_OK;
+}
+
+
+// Rows up to which x W^T products take the few-row form (0 = never).  Process-wide policy, like the tile shapes.
+std::atomic<int> g_skinny_max_rows{256};
+// Smallest number of k-blocks a K split of the few-row form may get.
+std::atomic<int> g_skinny_min_kblocks{2};
+// Activation rows one CTA of the few-row form takes (more rows: row blocks side by side on the same weight tile).
+std::atomic<int> g_skinny_block_rows{128};
+
+bool skinny_applies(const GemmArgs& g) {
+  const int max_rows = g_skinny_max_rows.load(std::memory_order_relaxed);
+  if (max_rows <= 0 || g.M < 1 || g.M > max_rows || g.groups > 0 || g.a_trans || !g.b_trans) return false;
+  if (g.N < 64 || g.K < 32 || g.K % 4 != 0 || g.ldb % 4 != 0 || g.lda % 4 != 0) return false;
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  return al(g.A) && al(g.B);
+}
+
+int launch_skinny(GemmState& gs, const SplitBuf& a, const GemmArgs& g, const TcEpilogue& ep_in, cudaStream_t s) {
+  const int M = g.M, N = g.N, K = g.K;
+  SkinnyArgs p{};
+  p.M = M; p.N = N; p.K = K;
+  p.block_rows = std::max(16, std::min(256, g_skinny_block_rows.load(std::memory_order_relaxed) / 16 * 16));
+  p.rowsN = (std::min(M, p.block_rows) + 15) / 16 * 16;
+  p.tmem_cols = 32; while (p.tmem_cols < p.rowsN) p.tmem_cols *= 2;
+  p.prefetch = g.b_prefetch ? 1 : 0;
+  const int stage_bytes = 2 * SK_W_BYTES + 2 * p.rowsN * TBK * 4;
+  const int slabs = ceil_div(N, TBM), rblocks = ceil_div(M, p.block_rows), nk_total = ceil_div(K, TBK);
+  // K splits: about one CTA per SM, every split at least min_kblocks k-blocks and at most 24 (768 elements of K are
+  // accumulated in tensor memory in one go; longer sums are cut so that the accumulator's truncating adds stay
+  // below 5e-6 of the result, as measured for the one-level K loop)
+  const bool can_split = g.leave != nullptr || (N % 4 == 0 && g.ldc % 4 == 0);
+  const int min_kb = std::max(1, g_skinny_min_kblocks.load(std::memory_order_relaxed));
+  int splits = 1;
+  if (can_split) splits = std::max(1, std::min(num_sms() / std::max(1, slabs * rblocks), nk_total / min_kb));
+  int nkps = ceil_div(nk_total, splits);
+  if (nkps > 24 && can_split) nkps = 24;
+  splits = ceil_div(nk_total, nkps);
+  p.nk_per_split = nkps;
+  const int64_t ctas = (int64_t)slabs * rblocks * splits;
+  // stages: as many as fit (more weight bytes in flight per SM); when there are more CTAs than SMs, two CTAs per SM
+  const int bar_bytes = (3 * SK_MAX_STAGES + 2) * 8 + 1024;
+  const int smem_one = 227 * 1024 - bar_bytes, smem_two = (227 * 1024) / 2 - 1024 - bar_bytes;
+  int stages = std::min(SK_MAX_STAGES, smem_one / stage_bytes);
+  if (ctas > num_sms() && smem_two / stage_bytes >= 2) stages = std::min(SK_MAX_STAGES, smem_two / stage_bytes);
+  stages = std::max(1, std::min(stages, std::max(nkps, 1)));
+  GN_REQUIRE(stages >= 1 && stage_bytes * stages + bar_bytes <= 227 * 1024, "few-row product: a stage of %d bytes does not fit shared memory", stage_bytes);
+  p.stages = stages;
+  const size_t smem = (size_t)stages * stage_bytes + bar_bytes;
+  static bool configured = false;
+  if (!configured) { GN_CUDA(cudaFuncSetAttribute(gemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)); configured = true; }
+  CUtensorMap mw, mxh, mxl;
+  GN_TRY(make_map(&mw, g.B, N, K, g.ldb, TBM));
+  GN_TRY(make_map(&mxh, a.hi, M, K, a.ld, p.rowsN));
+  GN_TRY(make_map(&mxl, a.lo, M, K, a.ld, p.rowsN));
+  p.ep = ep_in;
+  if (splits > 1) {
+    const size_t need = (size_t)splits * M * N;
+    if (need > gs.splitk_floats) {
+      if (gs.splitk_ws) cudaFree(gs.splitk_ws);
+      gs.splitk_ws = nullptr; gs.splitk_floats = 0;
+      if (cudaMalloc((void**)&gs.splitk_ws, need * sizeof(float)) != cudaSuccess) { set_error("tcgen05 gemm: cannot allocate the split-K workspace"); return GN_ERR_NOMEM; }
+      gs.splitk_floats = need;
+    }
+    p.ep.C = gs.splitk_ws; p.ep.ldc = N; p.ep.aux = nullptr; p.ep.epi = EPI_STORE; p.ep.split_stride = (int64_t)M * N; p.ep.c_hi = p.ep.c_lo = nullptr;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(rblocks, slabs, splits); cfg.blockDim = dim3(192); cfg.dynamicSmemBytes = smem; cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = gs.pdl ? 1 : 0;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  GN_CUDA(cudaLaunchKernelEx(&cfg, gemm_skinny_kernel, mw, mxh, mxl, p, gs.err_flag));
+  GN_LAUNCH_CHECK();
+  if (g.leave) {
+    if (splits > 1) *g.leave = Partials{gs.splitk_ws, splits, (int64_t)M * N, (int64_t)N};
+    else *g.leave = Partials{ep_in.C, 1, 0, ep_in.ldc};
+  } else if (splits > 1) {
+    int blocks = (int)std::min<int64_t>(((int64_t)M * (N / 4) + 255) / 256, (int64_t)num_sms() * 8);
+    GN_CUDA(launch_pdl(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, s, (const float*)gs.splitk_ws, splits, (int64_t)M * N, ep_in, M, N));
     GN_LAUNCH_CHECK();
   }
   return GN_OK;
@@ -812,6 +1135,7 @@ int launch_tc(GemmState& gs, const SplitBuf& a, const SplitBuf& b, const TcEpilo
 }  // namespace
 
 int gemm_tcgen05_supported(const GemmArgs& g) {
+  if (skinny_applies(g)) return 1;                      // x W^T with few rows: the weight-streaming form
   if (g.M < 64 || g.N < 64 || g.K < 32) return 0;      // tiny products stay on the SIMT kernel
   if (g.groups > 0 && (!g.b_trans || g.a_trans || g.epilogue != EPI_STORE || g.N % 4 != 0)) return 0;
   auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
@@ -842,6 +1166,11 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
     // a plain (untransposed) split with an unpadded pitch can serve the next product too
     const bool plain = !g.a_static && src_cols % 4 == 0 && (g.a_trans ? a.mn : true);
     gs.last_a.valid = plain; gs.last_a.src = g.A; gs.last_a.ld = g.lda; gs.last_a.rows = src_rows; gs.last_a.cols = src_cols;
+  }
+  if (skinny_applies(g)) {
+    // few rows against a weight matrix: the weights are streamed raw and split on chip
+    TcEpilogue ep{g.C, g.ldc, g.aux, g.ldaux, g.epilogue, g.scalar, 0, g.c_hi, g.c_lo, g_trace, nullptr, 0, 0, 0, 0, 0, 1};
+    return launch_skinny(gs, a, g, ep, s);
   }
   // B is logically [N, K]; stored that way when b_trans (weights [out, in]), else stored [K, N].
   if (g.b_hi && g.b_lo && !g.b_trans && gs.mn && g.groups == 0 && g.ldb % 4 == 0) {
@@ -919,6 +1248,9 @@ int gemm_tcgen05_option(cudaStream_t s, const char* name, int value) {
   else if (n == "gemm_pdl") st->pdl = value != 0;
   else if (n == "gemm_mn_major") st->mn = value != 0;
   else if (n == "gemm_mn_3d") st->mn3d = value != 0;
+  else if (n == "gemm_few_rows_max") g_skinny_max_rows.store(value, std::memory_order_relaxed);
+  else if (n == "gemm_few_rows_min_kblocks") g_skinny_min_kblocks.store(value, std::memory_order_relaxed);
+  else if (n == "gemm_few_rows_block") g_skinny_block_rows.store(value, std::memory_order_relaxed);
   else { set_error("unknown option '%s'", name); return GN_ERR_INVALID; }
   return GN_OK;
 }

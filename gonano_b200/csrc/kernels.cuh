@@ -85,8 +85,17 @@ void attention_decode_prefix_mode(int mode);   // -1 automatic, 0 off, 1 on wher
 int attention_decode_prefix_splits(int rows, int group, int Hq, int Hkv, int D, int prefix_len);
 
 // ----------------------------------------------------------------- sampler.cu
+// Optional bookkeeping of the rollout engine folded into the sampler (one thread per row; all pointers device memory).
+// pos != null: the Philox step of row r is pos[r] - pos_base + advance, and afterwards pos[r] += advance,
+// ctxlen[r] = pos[r] + 1.  done != null: the engine step (keep the token or finish the row on bos / aend).
+struct SampleTail {
+  int32_t* pos = nullptr; int32_t* ctxlen = nullptr; int pos_base = 0; int advance = 0;
+  int32_t* out_tokens = nullptr; int32_t* out_lengths = nullptr; int32_t* done = nullptr; int32_t* n_done = nullptr;
+  int max_tokens = 0, bos = -1, aend = -1;
+};
 int sample_launch(const float* logits, int rows, int vocab, int logits_row_div, const float* uniforms, const uint64_t* seeds_dev, int group,
-                  const uint32_t* step_dev, uint32_t step_host, float temperature, int top_k, int32_t* out, cudaStream_t s);
+                  const uint32_t* step_dev, uint32_t step_host, float temperature, int top_k, int32_t* out, cudaStream_t s,
+                  const SampleTail* tail = nullptr);
 
 // -------------------------------------------------------------------- loss.cu
 // row_loss: [rows] double scratch; loss_out: device double.  bad_targets: null or a device counter that receives the

@@ -193,12 +193,21 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
   cudaStream_t s = m->s();
   const bool train = a.mode == MODE_TRAIN;
   const bool cached = a.mode == MODE_PREFILL || a.mode == MODE_DECODE;
+  const int prefetch = train ? 0 : 1;   // inference: no kernel in flight writes the parameters, products may request them early
 
-  GN_TRY(embed_norm_launch(a.ids, m->p(m->off_wte), b.E, rows, d, s));
-  const float* prev_in = (a.mode == MODE_DECODE) ? m->prev.f() : nullptr;
-  float* prev_out = cached ? m->prev.f() : nullptr;
-  GN_TRY(smear_launch(b.E, b.X0, prev_in, prev_out, a.cache_row_mul, train ? b.SIG : nullptr, m->p(m->off_smear_gate), m->p(m->off_smear_lambda),
-                      B, T, d, s));
+  // Decode (one token per row): embedding, smear and layer 0's mix + norm in one launch.
+  const bool front = a.mode == MODE_DECODE && T == 1 && a.cache_row_mul == 1 && sum_norm_supported(d) && d >= 128;
+  if (front) {
+    const bool tc0 = m->ctx->gemm_kind == 1;
+    GN_TRY(decode_front_launch(a.ids, m->p(m->off_wte), m->prev.f(), m->p(m->off_smear_gate), m->p(m->off_smear_lambda), m->p(m->off_rho), m->p(m->off_chi),
+                               b.X0, b.Xa, b.H, tc0 ? b.S1h : nullptr, tc0 ? b.S1l : nullptr, rows, d, s));
+  } else {
+    GN_TRY(embed_norm_launch(a.ids, m->p(m->off_wte), b.E, rows, d, s));
+    const float* prev_in = (a.mode == MODE_DECODE) ? m->prev.f() : nullptr;
+    float* prev_out = cached ? m->prev.f() : nullptr;
+    GN_TRY(smear_launch(b.E, b.X0, prev_in, prev_out, a.cache_row_mul, train ? b.SIG : nullptr, m->p(m->off_smear_gate), m->p(m->off_smear_lambda),
+                        B, T, d, s));
+  }
   const int64_t layer_stride = (int64_t)a.cache_rows * Hkv * a.max_seq * D;
   const float* x_prev = b.X0;
   const float* backout = nullptr;
@@ -226,7 +235,7 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
       sn.V = Xin; sn.Y = H; sn.Yh = Hh; sn.Yl = Hl; sn.rows = rows; sn.d = d;
       GN_TRY(sum_norm_launch(sn, s));
       pending = Partials();
-    } else {
+    } else if (!(front && l == 0)) {   // the decode front already produced layer 0's Xin and H
       GN_TRY(mix_norm_launch(x_prev, b.X0, m->p(m->off_rho), m->p(m->off_chi), l, Xin, H, tc ? Hh : nullptr, tc ? Hl : nullptr, rows, d, s));
     }
     bool o_split = false;   // the attention kernel also wrote the tf32 split of O
@@ -236,7 +245,7 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
     } else {
     // q, k, v projections as one GEMM against [c_q; c_k; c_v]
     Partials qkv_part;
-    { GemmArgs g; g.A = H; g.lda = d; g.B = m->p(o.qkv); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = QKV; g.ldc = W; g.M = (int)rows; g.N = W; g.K = d;
+    { GemmArgs g; g.A = H; g.lda = d; g.B = m->p(o.qkv); g.b_static = 1; g.b_prefetch = prefetch; g.ldb = d; g.b_trans = 1; g.C = QKV; g.ldc = W; g.M = (int)rows; g.N = W; g.K = d;
       if (fuse) g.leave = &qkv_part;
       if (tc) { g.a_hi = Hh; g.a_lo = Hl; } GN_TRY(gemm(m, g)); }
     QkvPost qp;
@@ -269,13 +278,13 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
     if (fuse) {
       // MID = Xin + O Wo^T, summed and normalised in one kernel (H is free after qkv_post and takes an unsplit product)
       Partials op;
-      { GemmArgs g; g.A = O; g.lda = (int64_t)Hq * D; g.B = m->p(o.proj); g.b_static = 1; g.ldb = (int64_t)Hq * D; g.b_trans = 1; g.C = H; g.ldc = d; g.M = (int)rows; g.N = d; g.K = Hq * D;
+      { GemmArgs g; g.A = O; g.lda = (int64_t)Hq * D; g.B = m->p(o.proj); g.b_static = 1; g.b_prefetch = prefetch; g.ldb = (int64_t)Hq * D; g.b_trans = 1; g.C = H; g.ldc = d; g.M = (int)rows; g.N = d; g.K = Hq * D;
         g.leave = &op; if (o_split) { g.a_hi = b.S4h; g.a_lo = b.S4l; } GN_TRY(gemm(m, g)); }
       SumNorm sn; sn.R = Xin; sn.part = op; sn.V = MID; sn.Y = Mn; sn.Yh = Mh; sn.Yl = Ml; sn.rows = rows; sn.d = d;
       GN_TRY(sum_norm_launch(sn, s));
     } else {
       // MID = Xin + O Wo^T
-      { GemmArgs g; g.A = O; g.lda = (int64_t)Hq * D; g.B = m->p(o.proj); g.b_static = 1; g.ldb = (int64_t)Hq * D; g.b_trans = 1; g.C = MID; g.ldc = d; g.M = (int)rows; g.N = d; g.K = Hq * D;
+      { GemmArgs g; g.A = O; g.lda = (int64_t)Hq * D; g.B = m->p(o.proj); g.b_static = 1; g.b_prefetch = prefetch; g.ldb = (int64_t)Hq * D; g.b_trans = 1; g.C = MID; g.ldc = d; g.M = (int)rows; g.N = d; g.K = Hq * D;
         g.epilogue = EPI_RESIDUAL; g.aux = Xin; g.ldaux = d; if (o_split) { g.a_hi = b.S4h; g.a_lo = b.S4l; } GN_TRY(gemm(m, g)); }
       GN_TRY(norm_launch(MID, Mn, tc ? Mh : nullptr, tc ? Ml : nullptr, rows, d, s));
     }
@@ -287,7 +296,7 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
       continue;
     }
     // HID = relu(M Wfc^T)^2   (training also keeps the pre-activation)
-    { GemmArgs g; g.A = Mn; g.lda = d; g.B = m->p(o.fc); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = HID; g.ldc = 4 * d; g.M = (int)rows; g.N = 4 * d; g.K = d;
+    { GemmArgs g; g.A = Mn; g.lda = d; g.B = m->p(o.fc); g.b_static = 1; g.b_prefetch = prefetch; g.ldb = d; g.b_trans = 1; g.C = HID; g.ldc = 4 * d; g.M = (int)rows; g.N = 4 * d; g.K = d;
       g.epilogue = EPI_RELU2; g.aux = U; g.ldaux = 4 * d;
       if (tc) { g.a_hi = Mh; g.a_lo = Ml; g.c_hi = Ph; g.c_lo = Pl; } GN_TRY(gemm(m, g)); }
     // XOUT = MID + HID Wp^T.  When fused the sum is taken by the next layer's mix (or the final norm);
@@ -295,11 +304,11 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
     const bool fuse_out = fuse && !(l == L / 2 && l == L - 1);
     if (fuse_out) {
       // Mn was consumed by the product above and takes an unsplit product
-      GemmArgs g; g.A = HID; g.lda = 4 * d; g.B = m->p(o.mproj); g.b_static = 1; g.ldb = 4 * d; g.b_trans = 1; g.C = Mn; g.ldc = d; g.M = (int)rows; g.N = d; g.K = 4 * d;
+      GemmArgs g; g.A = HID; g.lda = 4 * d; g.B = m->p(o.mproj); g.b_static = 1; g.b_prefetch = prefetch; g.ldb = 4 * d; g.b_trans = 1; g.C = Mn; g.ldc = d; g.M = (int)rows; g.N = d; g.K = 4 * d;
       g.leave = &pending; g.a_hi = Ph; g.a_lo = Pl; GN_TRY(gemm(m, g));
       x_prev = MID;   // the residual the pending product is added to
     } else {
-      { GemmArgs g; g.A = HID; g.lda = 4 * d; g.B = m->p(o.mproj); g.b_static = 1; g.ldb = 4 * d; g.b_trans = 1; g.C = XOUT; g.ldc = d; g.M = (int)rows; g.N = d; g.K = 4 * d;
+      { GemmArgs g; g.A = HID; g.lda = 4 * d; g.B = m->p(o.mproj); g.b_static = 1; g.b_prefetch = prefetch; g.ldb = 4 * d; g.b_trans = 1; g.C = XOUT; g.ldc = d; g.M = (int)rows; g.N = d; g.K = 4 * d;
         g.epilogue = EPI_RESIDUAL; g.aux = MID; g.ldaux = d;
         if (tc) { g.a_hi = Ph; g.a_lo = Pl; } GN_TRY(gemm(m, g)); }
       if (l == L / 2) {
@@ -321,7 +330,7 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
   } else {
     GN_TRY(backout_norm_launch(x_prev, backout, m->p(m->off_backout), sel, train ? b.FP : nullptr, b.Y, tc_head ? b.S1h : nullptr, tc_head ? b.S1l : nullptr, lrows, d, s));
   }
-  { GemmArgs g; g.A = b.Y; g.lda = d; g.B = m->p(m->off_lm); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = b.LOGITS; g.ldc = V; g.M = (int)lrows; g.N = V; g.K = d;
+  { GemmArgs g; g.A = b.Y; g.lda = d; g.B = m->p(m->off_lm); g.b_static = 1; g.b_prefetch = prefetch; g.ldb = d; g.b_trans = 1; g.C = b.LOGITS; g.ldc = V; g.M = (int)lrows; g.N = V; g.K = d;
     g.epilogue = EPI_SOFTCAP; g.scalar = kSoftcap;
     if (tc_head) { g.a_hi = b.S1h; g.a_lo = b.S1l; } GN_TRY(gemm(m, g)); }
   return GN_OK;
@@ -832,23 +841,24 @@ int gn_generate_batch(gn_model* m, const int32_t* prompts, int P, int plen, int 
     for (int r = 0; r < rows; ++r) std::memcpy(dst + (size_t)r * V, host_logits.data() + (size_t)(r / div) * V, sizeof(float) * V);
     return GN_OK;
   };
-  GN_TRY(m->step_dev.ensure(sizeof(uint32_t)));
-  GN_CUDA(cudaMemsetAsync(m->step_dev.p, 0, sizeof(uint32_t), s));
+  // The sampler's row CTAs also do the engine's bookkeeping (position, context length, keep-or-finish): see SampleTail.
+  SampleTail tail;
+  tail.pos = m->pos.i(); tail.ctxlen = m->ctxlen.i(); tail.pos_base = plen; tail.advance = 0;
+  tail.out_tokens = m->out_tokens.i(); tail.out_lengths = m->out_lengths.i(); tail.done = m->done.i(); tail.n_done = m->n_done.i();
+  tail.max_tokens = max_tokens; tail.bos = bos; tail.aend = aend;
   // first column: every row of a group samples from its prompt's last-position logits (engine.go:182-191)
   GN_TRY(tap(G));
-  GN_TRY(sample_launch(b.LOGITS, rows, V, G, nullptr, (const uint64_t*)m->seeds.p, G, (const uint32_t*)m->step_dev.p, 0, temperature, top_k, m->sampled.i(), s));
-  GN_TRY(engine_step_launch(m->sampled.i(), m->out_tokens.i(), m->out_lengths.i(), m->done.i(), m->n_done.i(), rows, max_tokens, bos, aend, s));
-  GN_TRY(add_u32_launch((uint32_t*)m->step_dev.p, 1, s));
+  GN_TRY(sample_launch(b.LOGITS, rows, V, G, nullptr, (const uint64_t*)m->seeds.p, G, nullptr, 0, temperature, top_k, m->sampled.i(), s, &tail));
   ++generated;
-  auto body = [&]() -> int {
-    GN_TRY(ctx_from_pos_launch(m->pos.i(), m->ctxlen.i(), rows, s));
+  tail.advance = 1;   // from here on a sampling step follows a forward of the previous token
+  auto forward_step = [&]() -> int {
     FwdArgs a; a.mode = MODE_DECODE; a.ids = m->sampled.i(); a.B = rows; a.T = 1; a.cache_rows = rows; a.cache_row_mul = 1; a.max_seq = max_seq;
     if (share_prefix) { a.group = G; a.prefix_len = plen; }
-    GN_TRY(forward_core(m, b, a));                       // forward the sampled column (engine.go:321-324)
-    GN_TRY(add_i32_launch(m->pos.i(), 1, rows, s));
-    GN_TRY(sample_launch(b.LOGITS, rows, V, 1, nullptr, (const uint64_t*)m->seeds.p, G, (const uint32_t*)m->step_dev.p, 0, temperature, top_k, m->sampled.i(), s));
-    GN_TRY(engine_step_launch(m->sampled.i(), m->out_tokens.i(), m->out_lengths.i(), m->done.i(), m->n_done.i(), rows, max_tokens, bos, aend, s));
-    GN_TRY(add_u32_launch((uint32_t*)m->step_dev.p, 1, s));
+    return forward_core(m, b, a);                       // forward the sampled column (engine.go:321-324)
+  };
+  auto body = [&]() -> int {
+    GN_TRY(forward_step());
+    GN_TRY(sample_launch(b.LOGITS, rows, V, 1, nullptr, (const uint64_t*)m->seeds.p, G, nullptr, 0, temperature, top_k, m->sampled.i(), s, &tail));
     return GN_OK;
   };
   cudaGraph_t graph = nullptr;
@@ -865,15 +875,9 @@ int gn_generate_batch(gn_model* m, const int32_t* prompts, int P, int plen, int 
     }
     if (step_logits) {
       // the tap wants the logits each sampling step saw: forward first, copy, then sample
-      GN_TRY(ctx_from_pos_launch(m->pos.i(), m->ctxlen.i(), rows, s));
-      FwdArgs a; a.mode = MODE_DECODE; a.ids = m->sampled.i(); a.B = rows; a.T = 1; a.cache_rows = rows; a.cache_row_mul = 1; a.max_seq = max_seq;
-      if (share_prefix) { a.group = G; a.prefix_len = plen; }
-      GN_TRY(forward_core(m, b, a));
-      GN_TRY(add_i32_launch(m->pos.i(), 1, rows, s));
+      GN_TRY(forward_step());
       GN_TRY(tap(1));
-      GN_TRY(sample_launch(b.LOGITS, rows, V, 1, nullptr, (const uint64_t*)m->seeds.p, G, (const uint32_t*)m->step_dev.p, 0, temperature, top_k, m->sampled.i(), s));
-      GN_TRY(engine_step_launch(m->sampled.i(), m->out_tokens.i(), m->out_lengths.i(), m->done.i(), m->n_done.i(), rows, max_tokens, bos, aend, s));
-      GN_TRY(add_u32_launch((uint32_t*)m->step_dev.p, 1, s));
+      GN_TRY(sample_launch(b.LOGITS, rows, V, 1, nullptr, (const uint64_t*)m->seeds.p, G, nullptr, 0, temperature, top_k, m->sampled.i(), s, &tail));
     } else if (!use_graph || eager_done < 2) {
       GN_TRY(body());       // eager: also sizes every scratch buffer before the capture
       ++eager_done;

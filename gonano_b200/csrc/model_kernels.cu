@@ -139,6 +139,7 @@ int norm_launch(const float* X, float* Y, float* Yh, float* Yl, int64_t rows, in
 // One block per row, one float4 per thread.
 __global__ void __launch_bounds__(1024) sum_norm_kernel(SumNorm p) {
   pdl_trigger();
+  pdl_wait();
   __shared__ float scratch[33];
   const int64_t r = blockIdx.x;
   const int64_t src = p.sel ? p.sel[r] : r;
@@ -181,7 +182,74 @@ int sum_norm_launch(const SumNorm& p, cudaStream_t s) {
   if (p.rows <= 0) return GN_OK;
   GN_REQUIRE(sum_norm_supported(p.d), "sum_norm: width %d unsupported", p.d);
   const int threads = (p.d / 4 + 31) / 32 * 32;
-  sum_norm_kernel<<<(unsigned)p.rows, threads, 0, s>>>(p);
+  GN_CUDA(launch_pdl(sum_norm_kernel, dim3((unsigned)p.rows), dim3(threads), 0, s, p));
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+// ------------------------------------------------------------ decode front
+// The first three kernels of a decode step in one: e = norm(wte[id]); x0 = e + lambda * sigmoid(Ws . e[0:24]) * prev;
+// prev <- e (model/transformer.go:255-301,520-530); then layer 0's residual mix and norm (model/transformer.go:312,
+// model/block.go:39) with the tf32 split of the result.  One block per row, one float4 per thread.
+__global__ void __launch_bounds__(1024) decode_front_kernel(const int32_t* __restrict__ ids, const float* __restrict__ wte, float* __restrict__ prev,
+                                                            const float* __restrict__ Ws, const float* __restrict__ lambda, const float* __restrict__ rho,
+                                                            const float* __restrict__ chi, float* __restrict__ X0, float* __restrict__ Xin,
+                                                            float* __restrict__ H, float* __restrict__ Hh, float* __restrict__ Hl, int d) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float scratch[33];
+  __shared__ float gate_sh;
+  const int64_t r = blockIdx.x;
+  const int c = threadIdx.x * 4;
+  const bool live = c < d;
+  float4 e = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (live) e = *reinterpret_cast<const float4*>(wte + (int64_t)ids[r] * d + c);
+  float ss = fmaf(e.x, e.x, fmaf(e.y, e.y, fmaf(e.z, e.z, e.w * e.w)));
+  ss = block_sum(ss, scratch);
+  float inv = row_inv_rms(ss, d);
+  e.x *= inv; e.y *= inv; e.z *= inv; e.w *= inv;
+  // gate from the first kSmearChannels channels of the normalised embedding (they sit in the first warp)
+  if (threadIdx.x < 32) {
+    float pre = 0.0f;
+    const float ev[4] = {e.x, e.y, e.z, e.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) if (c + j < kSmearChannels) pre = fmaf(ev[j], Ws[c + j], pre);
+    pre = warp_sum(pre);
+    if (threadIdx.x == 0) gate_sh = sigmoid_exact(pre) * lambda[0];
+  }
+  __syncthreads();
+  const float gate = gate_sh;
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (live) {
+    const float4 pv = *reinterpret_cast<const float4*>(prev + r * d + c);
+    *reinterpret_cast<float4*>(prev + r * d + c) = e;
+    float4 x0 = make_float4(e.x + gate * pv.x, e.y + gate * pv.y, e.z + gate * pv.z, e.w + gate * pv.w);
+    *reinterpret_cast<float4*>(X0 + r * d + c) = x0;
+    const float rw = rho[0], xw = chi[0];
+    v.x = __fadd_rn(__fmul_rn(rw, x0.x), __fmul_rn(xw, x0.x)); v.y = __fadd_rn(__fmul_rn(rw, x0.y), __fmul_rn(xw, x0.y));
+    v.z = __fadd_rn(__fmul_rn(rw, x0.z), __fmul_rn(xw, x0.z)); v.w = __fadd_rn(__fmul_rn(rw, x0.w), __fmul_rn(xw, x0.w));
+    *reinterpret_cast<float4*>(Xin + r * d + c) = v;
+  }
+  float s2 = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
+  s2 = block_sum(s2, scratch);
+  const float inv2 = row_inv_rms(s2, d);
+  if (live) {
+    const float4 y = make_float4(v.x * inv2, v.y * inv2, v.z * inv2, v.w * inv2);
+    *reinterpret_cast<float4*>(H + r * d + c) = y;
+    if (Hh) {
+      float4 h, l;
+      split_tf32(y.x, h.x, l.x); split_tf32(y.y, h.y, l.y); split_tf32(y.z, h.z, l.z); split_tf32(y.w, h.w, l.w);
+      *reinterpret_cast<float4*>(Hh + r * d + c) = h;
+      *reinterpret_cast<float4*>(Hl + r * d + c) = l;
+    }
+  }
+}
+int decode_front_launch(const int32_t* ids, const float* wte, float* prev, const float* Ws, const float* lambda, const float* rho, const float* chi,
+                        float* X0, float* Xin, float* H, float* Hh, float* Hl, int64_t rows, int d, cudaStream_t s) {
+  if (rows <= 0) return GN_OK;
+  GN_REQUIRE(sum_norm_supported(d) && d >= 4 * 32 && kSmearChannels <= 128, "decode_front: width %d unsupported", d);
+  const int threads = (d / 4 + 31) / 32 * 32;
+  GN_CUDA(launch_pdl(decode_front_kernel, dim3((unsigned)rows), dim3(threads), 0, s, ids, wte, prev, Ws, lambda, rho, chi, X0, Xin, H, Hh, Hl, d));
   GN_LAUNCH_CHECK();
   return GN_OK;
 }
@@ -190,6 +258,8 @@ int sum_norm_launch(const SumNorm& p, cudaStream_t s) {
 // One warp per (token row, head slot); slots = Hq query heads, Hkv key heads, Hkv value heads.
 __global__ void __launch_bounds__(WPB * 32) qkv_post_kernel(QkvPost p) {
   __shared__ __align__(16) float sh[WPB][128];
+  pdl_trigger();
+  pdl_wait();
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slots = p.Hq + 2 * p.Hkv;
   int64_t idx = (int64_t)blockIdx.x * WPB + warp;
@@ -276,7 +346,7 @@ int qkv_post_launch(const QkvPost& p, cudaStream_t s) {
   if (n <= 0) return GN_OK;
   GN_REQUIRE(p.D <= 128 && p.R <= p.D && p.R % 2 == 0 && p.R / 2 <= 64, "qkv_post: head_dim %d / rotary %d unsupported", p.D, p.R);
   GN_REQUIRE(!p.part.on() || p.D % 4 == 0, "qkv_post: unreduced input needs head_dim %% 4 == 0 (got %d)", p.D);
-  qkv_post_kernel<<<ceil_div(n, WPB), WPB * 32, 0, s>>>(p);
+  GN_CUDA(launch_pdl(qkv_post_kernel, dim3(ceil_div(n, WPB)), dim3(WPB * 32), 0, s, p));
   GN_LAUNCH_CHECK();
   return GN_OK;
 }

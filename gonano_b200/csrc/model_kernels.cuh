@@ -51,6 +51,10 @@ struct SumNorm {
   int64_t rows = 0; int d = 0;
 };
 int sum_norm_launch(const SumNorm& p, cudaStream_t s);
+// Decode step, T = 1: embedding + norm, smear against the cached previous embedding (updated in place), layer 0's mix
+// and norm with the tf32 split of H.  prev [rows, d] is read and rewritten.
+int decode_front_launch(const int32_t* ids, const float* wte, float* prev, const float* Ws, const float* lambda, const float* rho, const float* chi,
+                        float* X0, float* Xin, float* H, float* Hh, float* Hl, int64_t rows, int d, cudaStream_t s);
 inline bool sum_norm_supported(int d) { return d % 4 == 0 && d <= 4096; }
 
 struct QkvPost {

@@ -85,6 +85,25 @@ extern "C" int gn_profile_kernel(gn_ctx* ctx, const char* kernel, const int64_t*
     int kind = ctx->gemm_kind;
     return time_it(s, iters, mean_ms, [&]() { return gemm_dispatch(g, kind, s); });
   }
+  if (k == "gemm_decode") {
+    // A product of the decode step: few activation rows (already split by their producer) against one of `copies`
+    // distinct weight matrices in turn, so that the weights come from HBM as they do in a 12-layer step, the result
+    // left as K-split partial tiles for the consumer when the path splits K.
+    GN_REQUIRE(n_dims == 4 && dims[3] >= 1, "gemm_decode wants {rows, N, K, weight copies}");
+    int M = (int)dims[0], N = (int)dims[1], K = (int)dims[2], copies = (int)dims[3];
+    float *A, *Ah, *Al, *B, *C;
+    GN_TRY(bufs.get(&A, (size_t)M * K)); GN_TRY(bufs.get(&Ah, (size_t)M * K)); GN_TRY(bufs.get(&Al, (size_t)M * K));
+    GN_TRY(bufs.get(&B, (size_t)copies * N * K)); GN_TRY(bufs.get(&C, (size_t)M * N));
+    GN_TRY(synth(A, (int64_t)M * K, -1, 1, 1, s)); GN_TRY(synth(B, (int64_t)copies * N * K, -1, 1, 2, s));
+    GN_TRY(split_matrix_launch(A, Ah, Al, M, K, K, s));
+    int kind = ctx->gemm_kind, turn = 0;
+    return time_it(s, iters, mean_ms, [&]() {
+      Partials left;
+      GemmArgs g; g.A = A; g.a_hi = Ah; g.a_lo = Al; g.lda = K; g.B = B + (size_t)(turn++ % copies) * N * K; g.ldb = K; g.b_trans = 1; g.b_static = 1; g.b_prefetch = 1;
+      g.C = C; g.ldc = N; g.M = M; g.N = N; g.K = K; g.leave = &left;
+      return gemm_dispatch(g, kind, s);
+    });
+  }
   if (k == "loss") {
     GN_REQUIRE(n_dims == 3, "loss wants {rows, vocab, valid_percent}");
     int64_t rows = dims[0]; int vocab = (int)dims[1]; int pct = (int)dims[2];

@@ -58,10 +58,21 @@ __device__ __forceinline__ Best block_best(Best b, float* shs, int* shi) {
 }
 
 // IPT = vocabulary entries held per thread (vocab <= IPT * 1024).
+// The rollout engine's per-row bookkeeping after a sampling step (inference/engine.go:260-319, 349-367), done by the
+// row's own CTA: the row's position advances past the token that was just forwarded, its context length for the next
+// step follows, and the sampled token is either kept or ends the row (<|bos|>, <|assistant_end|>).
+__device__ __forceinline__ void sample_tail(const SampleTail& t, int row, int32_t token) {
+  if (t.pos) { const int32_t pn = t.pos[row] + t.advance; t.pos[row] = pn; if (t.ctxlen) t.ctxlen[row] = pn + 1; }
+  if (t.done && !t.done[row]) {
+    if (token == t.aend || token == t.bos) { t.done[row] = 1; atomicAdd(t.n_done, 1); }
+    else { const int n = t.out_lengths[row]; if (n < t.max_tokens) { t.out_tokens[(int64_t)row * t.max_tokens + n] = token; t.out_lengths[row] = n + 1; } }
+  }
+}
+
 template <int IPT>
 __global__ void __launch_bounds__(ST) sample_kernel(const float* __restrict__ logits, int vocab, int row_div, const float* __restrict__ uniforms,
                                                     const uint64_t* __restrict__ seeds, int group, const uint32_t* step_dev, uint32_t step_host,
-                                                    float temperature, int top_k, int32_t* __restrict__ out) {
+                                                    float temperature, int top_k, int32_t* __restrict__ out, SampleTail tail) {
   __shared__ unsigned int hist[32][256];  // one histogram per warp
   __shared__ unsigned int total[256];
   __shared__ unsigned int sel_prefix, sel_remaining, warp_count[32];
@@ -69,6 +80,8 @@ __global__ void __launch_bounds__(ST) sample_kernel(const float* __restrict__ lo
   __shared__ float shs[32];
   __shared__ int shi[32];
 
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x, tid = threadIdx.x, warp = tid >> 5;
   const float* src = logits + (int64_t)(row / row_div) * vocab;
   float x[IPT];
@@ -83,7 +96,7 @@ __global__ void __launch_bounds__(ST) sample_kernel(const float* __restrict__ lo
 #pragma unroll
     for (int it = 0; it < IPT; ++it) { int c = it * ST + tid; if (c < vocab) best_merge(b, x[it], c); }
     b = block_best(b, shs, shi);
-    if (tid == 0) out[row] = b.index == 0x7fffffff ? 0 : b.index;
+    if (tid == 0) { const int32_t t = b.index == 0x7fffffff ? 0 : b.index; out[row] = t; sample_tail(tail, row, t); }
     return;
   }
 
@@ -217,7 +230,8 @@ __global__ void __launch_bounds__(ST) sample_kernel(const float* __restrict__ lo
 
   const uint64_t seed = seeds ? seeds[row / group] : 0ull;
   const uint32_t grow = (uint32_t)(row % group);
-  const uint32_t step = step_dev ? *step_dev : step_host;
+  // with the engine tail the step is the number of tokens this row has sampled so far: its position past the prompt
+  const uint32_t step = tail.pos ? (uint32_t)(tail.pos[row] - tail.pos_base + tail.advance) : (step_dev ? *step_dev : step_host);
   Best b{-INFINITY, 0x7fffffff};
   auto consider = [&](float value, int c) {
     float u = uniforms ? uniforms[(int64_t)row * vocab + c] : sampler_uniform(seed, step, grow, (uint32_t)c);
@@ -244,20 +258,22 @@ __global__ void __launch_bounds__(ST) sample_kernel(const float* __restrict__ lo
     }
   }
   b = block_best(b, shs, shi);
-  if (tid == 0) out[row] = b.index == 0x7fffffff ? 0 : b.index;
+  if (tid == 0) { const int32_t t = b.index == 0x7fffffff ? 0 : b.index; out[row] = t; sample_tail(tail, row, t); }
 }
 
 int sample_launch(const float* logits, int rows, int vocab, int logits_row_div, const float* uniforms, const uint64_t* seeds_dev, int group,
-                  const uint32_t* step_dev, uint32_t step_host, float temperature, int top_k, int32_t* out, cudaStream_t s) {
+                  const uint32_t* step_dev, uint32_t step_host, float temperature, int top_k, int32_t* out, cudaStream_t s, const SampleTail* tail_in) {
+  SampleTail tail{};
+  if (tail_in) tail = *tail_in;
   if (rows <= 0) return GN_OK;
   GN_REQUIRE(vocab > 0 && vocab <= 64 * ST, "sampler: vocabulary %d outside (0, %d]", vocab, 64 * ST);
   if (logits_row_div < 1) logits_row_div = 1;
   if (group < 1) group = 1;
-#define GN_SAMPLE(IPT) sample_kernel<IPT><<<rows, ST, 0, s>>>(logits, vocab, logits_row_div, uniforms, seeds_dev, group, step_dev, step_host, temperature, top_k, out)
-  if (vocab <= 8 * ST) GN_SAMPLE(8);
-  else if (vocab <= 16 * ST) GN_SAMPLE(16);
-  else if (vocab <= 32 * ST) GN_SAMPLE(32);
-  else GN_SAMPLE(64);
+#define GN_SAMPLE(IPT) GN_CUDA(launch_pdl(sample_kernel<IPT>, dim3(rows), dim3(ST), 0, s, logits, vocab, logits_row_div, uniforms, seeds_dev, group, step_dev, step_host, temperature, top_k, out, tail))
+  if (vocab <= 8 * ST) { GN_SAMPLE(8); }
+  else if (vocab <= 16 * ST) { GN_SAMPLE(16); }
+  else if (vocab <= 32 * ST) { GN_SAMPLE(32); }
+  else { GN_SAMPLE(64); }
 #undef GN_SAMPLE
   GN_LAUNCH_CHECK();
   return GN_OK;

@@ -237,7 +237,11 @@ int gn_ctx_set_gemm(gn_ctx* ctx, int kind);
  *   "gemm_persistent_ctas"   -1 (default) one CTA per SM for the tile-walking form, 0 form off, n = n CTAs
  *   "gemm_pdl"               1 (default) products launch with programmatic stream serialization
  *   "gemm_mn_major"          1 (default) operands stored [K, M] / [K, N] are read in place, 0 transposes them
- *   "gemm_mn_3d"             1 (default) one 3-D bulk-tensor copy per such tile instead of one per 32 columns */
+ *   "gemm_mn_3d"             1 (default) one 3-D bulk-tensor copy per such tile instead of one per 32 columns
+ *   "gemm_few_rows_max"      256 (default): x W^T products with at most this many rows stream the float32 weights
+ *                            once and split them on chip (the decode step's form); 0 = off (process-wide)
+ *   "gemm_few_rows_min_kblocks"  2 (default): smallest K share (in 32-element blocks) of one CTA of that form
+ *   "gemm_few_rows_block"    128 (default): activation rows per CTA of that form (16..256) */
 int gn_ctx_set_option(gn_ctx* ctx, const char* name, int value);
 
 /* model.NewTransformer (model/transformer.go:49-83): parameters start at zero. */
@@ -295,6 +299,7 @@ int gn_model_phase_ms(gn_model* model, const char* phase, float* ms);
  * the RL step on synthetic device data with CUDA events on the context's stream, after three
  * warm-up launches, and returns the mean time of one launch in milliseconds.
  *   "gemm_nt" / "gemm_nn" / "gemm_tn"  dims {M, N, K}        C = A B^T / A B / A^T B
+ *   "gemm_decode"       dims {rows, N, K, weight copies}      x W^T of the decode step, weights cycled so they come from HBM
  *   "loss"              dims {rows, vocab, valid_percent}    fused loss + dlogits (+ softcap backward)
  *   "sampler"           dims {rows, vocab, top_k}
  *   "decode_attention"  dims {rows, n_head, n_kv_head, head_dim, context}

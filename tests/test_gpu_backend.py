@@ -240,3 +240,19 @@ def test_tensor_core_matmul_faithful(oracle, bk, ref, rows, cols, inner):
     want = ref.matmul(left, right, rows, cols, inner)
     got = bk.matmul(left, right, rows, cols, inner)
     assert np.max(np.abs(got - want)) <= 2e-5 * np.max(np.abs(want))
+
+
+# The decode step's products have few rows (the rollout batch) against a weight matrix; they take the weight-streaming
+# form of the tensor-core kernel (weights read raw and split on chip, K split over CTAs).  Every row count class, slab
+# tails, K tails, K splits with and without remainder, one and two row blocks.
+@pytest.mark.parametrize("rows,cols,inner", [(1, 128, 32), (7, 64, 128), (16, 256, 768), (64, 1280, 768), (64, 768, 3072), (100, 200, 100),
+                                             (128, 3072, 768), (256, 768, 768), (12, 8192, 128), (40, 1000, 2052)])
+def test_few_row_products(oracle, bk, ref, rows, cols, inner):
+    rng = np.random.default_rng(rows * 13 + cols)
+    left = rng.standard_normal(rows * inner).astype(np.float32)
+    rt = rng.standard_normal(cols * inner).astype(np.float32)
+    want = ref.matmul_transposed(left, rt, rows, cols, inner)
+    got = bk.matmul_transposed(left, rt, rows, cols, inner)
+    assert np.max(np.abs(got - want)) <= 2e-5 * np.max(np.abs(want))
+    again = bk.matmul_transposed(left, rt, rows, cols, inner)
+    assert np.array_equal(got, again)          # fixed summation order: bit-reproducible
