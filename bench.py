@@ -12,6 +12,12 @@ scalars).  With N GPUs the 64 prompts are split into N contiguous shards (strong
 total work is fixed), one process per GPU, a full policy replica each.
 
 Prints ONE JSON line (rank 0).
+
+Sub-workloads for profiling (each prints one small JSON line; `ncu` wraps these, never the whole benchmark):
+
+    python bench.py --only decode --prompts 8 --tokens 4 [--eager]     # prefill + a few decode steps of the d12 model
+    python bench.py --only train --rows 32                             # one training pass (forward, loss, backward)
+    python bench.py --only kernel --kernel gemm_nt --dims 16384 3072 768   # one kernel on synthetic device data
 """
 from __future__ import annotations
 
@@ -43,7 +49,9 @@ def emit(line: dict) -> None:
         os.write(_STDOUT_FD, data)
 
 
-GEMM_TRAFFIC_BYTES = 277851136   # 120.4 MB read + 157.5 MB written: ncu capture of `profile_cli kernel gemm_nt 16384 3072 768` (profiles/gemm_tc_timeline.md)
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the 16384 x 3072 x 768 product under ncu
+# (`bench.py --only kernel --kernel gemm_nt --dims 16384 3072 768`): 120.4 MB read + 157.5 MB written
+GEMM_TRAFFIC_BYTES = 277851136
 WORKLOAD = dict(name="d12", n_prompts=64, prompt_len=128, group=8, max_tokens=256, temperature=1.0, top_k=50, seed=0)
 METRIC, UNIT = "rl_steps_per_s_d12", "steps/s"
 
@@ -105,47 +113,64 @@ class ClockSampler:
 
 # ---------------------------------------------------------------------------------------------
 # CPU baseline: the oracle's SIMD-structured flavour (restatement of kernels/simd), all host
-# threads, on a bounded sample of the same workload, extrapolated linearly to one full step.
+# threads.  The d12 step is far too long to run on the host (about an hour), so it is timed on a
+# bounded sample and extrapolated linearly, labelled so; the plumbing step and the loss
+# microbenchmark are small enough to run IN FULL on both arms and are reported as measured pairs.
 # ---------------------------------------------------------------------------------------------
-def cpu_baseline(sample_scale: int = 1):
-    from oracle import oracle
-    w = WORKLOAD
-    cfg = synthetic.dense_config(w["name"])
+def _host_threads():
     # every host thread this process may use: a launcher such as torchrun sets OMP_NUM_THREADS=1, which would
     # otherwise time the CPU path on one core
+    from oracle import oracle
     try:
         avail = len(os.sched_getaffinity(0))
     except AttributeError:
         avail = os.cpu_count() or 1
     oracle.set_threads(max(1, avail))
-    threads = oracle.num_threads()
+    return oracle.num_threads()
+
+
+def cpu_baseline():
+    from oracle import oracle
+    w = WORKLOAD
+    cfg = synthetic.dense_config(w["name"])
+    threads = _host_threads()
     om = oracle.Model(mode=1, **cfg)
     for name, value in synthetic.fill_weights(om.names, om.shape, w["seed"]):
         om.param(name)[:] = value
     G, plen, new = w["group"], w["prompt_len"], w["max_tokens"]
-    prompt = synthetic.prompts(1, plen, cfg["vocab_size"], w["seed"])
+    V = cfg["vocab_size"]
+    prompt = synthetic.prompts(1, plen, V, w["seed"])
     t0 = time.perf_counter()
     cache0 = om.cache(1, plen)
     logits = om.forward_cached(cache0, prompt)
     t_prefill = time.perf_counter() - t0
-    cache = om.cache(G, plen + new)
-    cache.replicate_from(cache0)
-    ids = oracle.sample_next_token(np.repeat(logits[:, -1], G, axis=0), w["temperature"], w["top_k"], seeds=[0], group=G, step=0)
-    n_dec = 4 * sample_scale
-    t0 = time.perf_counter()
-    for step in range(n_dec):
-        logits = om.forward_cached(cache, ids.reshape(G, 1))
-        ids = oracle.sample_next_token(logits[:, 0], w["temperature"], w["top_k"], seeds=[0], group=G, step=step + 1)
-    t_decode = (time.perf_counter() - t0) / n_dec
-    T = plen + new - 1
+    # decode at three context lengths (start, middle, end of the rollout), two steps each, median per length
     rng = np.random.default_rng(0)
-    inputs = rng.integers(0, cfg["vocab_size"] - 11, (1, T), dtype=np.int32)
+    t_ctx = []
+    for ctx_len in (plen, plen + new // 2, plen + new - 2):
+        cache = om.cache(G, plen + new)
+        cache.replicate_from(cache0)
+        if ctx_len > plen:      # grow the cache to the wanted context with one batched forward (untimed)
+            filler = rng.integers(0, V - 11, (G, ctx_len - plen), dtype=np.int32)
+            om.forward_cached(cache, filler)
+        ids = rng.integers(0, V - 11, (G, 1), dtype=np.int32)
+        samples = []
+        for step in range(2):
+            t0 = time.perf_counter()
+            lg = om.forward_cached(cache, ids)
+            ids = oracle.sample_next_token(lg[:, 0], w["temperature"], w["top_k"], seeds=[0], group=G, step=step + 1).reshape(G, 1)
+            samples.append(time.perf_counter() - t0)
+        t_ctx.append(float(np.median(samples)))
+    t_decode = float(np.mean(t_ctx))       # the context grows linearly over the rollout: mean of start / middle / end
+    T = plen + new - 1
+    n_train = 2
+    inputs = rng.integers(0, V - 11, (n_train, T), dtype=np.int32)
     targets = np.roll(inputs, -1, axis=1).copy(); targets[:, :plen] = -1
     t0 = time.perf_counter()
-    om.policy_gradient_step(inputs, targets, np.array([0.5], np.float32), float(T + 1))
-    t_train_row = time.perf_counter() - t0
+    om.policy_gradient_step(inputs, targets, np.array([0.5, -0.5], np.float32), float(T + 1))
+    t_train_row = (time.perf_counter() - t0) / n_train
     # optimizer step (optimizer/muon.go, sinkhorn.go): one update of each distinct matrix shape, scaled by how many the model has
-    d, L, V, KV = cfg["embed_dim"], cfg["n_layer"], om.padded_vocab(), cfg["n_kv_head"] * (cfg["embed_dim"] // cfg["n_head"])
+    d, L, Vp, KV = cfg["embed_dim"], cfg["n_layer"], om.padded_vocab(), cfg["n_kv_head"] * (cfg["embed_dim"] // cfg["n_head"])
 
     def t_muon(rows, cols):
         p = (rng.standard_normal(rows * cols) * 0.02).astype(np.float32); g = (rng.standard_normal(rows * cols) * 0.01).astype(np.float32)
@@ -160,31 +185,108 @@ def cpu_baseline(sample_scale: int = 1):
         return time.perf_counter() - t
 
     n_ve = sum(1 for n in om.names if n.startswith("value_embeds."))
-    t_opt = L * (2 * t_muon(d, d) + 2 * t_muon(KV, d) + t_muon(4 * d, d) + t_muon(d, 4 * d)) + t_sink(V, KV) * (2.0 * d / KV + n_ve)
+    t_opt = L * (2 * t_muon(d, d) + 2 * t_muon(KV, d) + t_muon(4 * d, d) + t_muon(d, 4 * d)) + t_sink(Vp, KV) * (2.0 * d / KV + n_ve)
     P = w["n_prompts"]
-    # decode cost grows with the context; the sample sits at the start of the rollout, so this is a lower bound
     step_s = P * (t_prefill + new * t_decode) + P * G * t_train_row + t_opt
     return {"value": 1.0 / step_s, "unit": UNIT, "cores": threads, "kind": "port",
-            "sample": (f"extrapolated: 1 prompt prefill ({t_prefill:.3f}s) + {n_dec} decode steps of {G} rows ({t_decode:.4f}s each) + "
-                       f"train/loss/backward of 1 row x {T} tokens ({t_train_row:.2f}s), scaled to {P} prompts x {G} rows x {new} tokens; "
-                       f"optimizer: one Muon update per matrix shape and one Sinkhorn update of a value-embedding table, scaled by count ({t_opt:.1f}s); "
-                       f"oracle mode 1 (kernels/simd structure), {oracle.isa()}, {threads} threads"),
+            "sample": (f"extrapolated, not measured whole: 1 prompt prefill ({t_prefill:.3f}s) + decode steps of {G} rows at contexts {plen}, "
+                       f"{plen + new // 2}, {plen + new - 2} (medians {t_ctx[0]:.4f} / {t_ctx[1]:.4f} / {t_ctx[2]:.4f}s, mean used) + "
+                       f"train/loss/backward of {n_train} rows x {T} tokens ({t_train_row:.2f}s per row), scaled linearly to {P} prompts x {G} rows x "
+                       f"{new} tokens; optimizer: one Muon update per matrix shape and one Sinkhorn update of a value-embedding table, scaled by "
+                       f"count ({t_opt:.1f}s); oracle mode 1 (a C++ restatement of the structure of kernels/simd, not the reference's own "
+                       f"binary), {oracle.isa()}, {threads} threads"),
             "step_seconds_extrapolated": step_s}
+
+
+def plumbing_step_cpu():
+    """The plumbing RL step (depth 2, d128, vocab 8192; 8 prompts x 32, G = 4, 32 new tokens, reward = contains id 7,
+    std advantage, one optimizer step) IN FULL on the host: seconds for one step."""
+    from oracle import oracle
+    _host_threads()
+    cfg = synthetic.dense_config("c1")
+    om = oracle.Model(mode=1, **cfg)
+    for name, value in synthetic.fill_weights(om.names, om.shape, 0):
+        om.param(name)[:] = value
+    V, P, PLEN, G, NEW = cfg["vocab_size"], 8, 32, 4, 32
+    prompts = synthetic.prompts(P, PLEN, V, 1)
+    opt = oracle.Optimizer(om)
+    from gonano_b200.session import build_batch
+    t0 = time.perf_counter()
+    toks, lens = [], []
+    for p in range(P):
+        t, l, _, _ = om.generate(prompts[p], G, NEW, 1.0, 50, seed=40 + p)
+        toks.append(t); lens.append(l)
+    tokens, lengths = np.concatenate(toks), np.concatenate(lens)
+    adv = oracle.advantage(synthetic.contains_token_rewards(tokens, lengths, 7), G, 1)
+    inputs, targets, max_len = build_batch(prompts, G, tokens, lengths, V - 7)
+    om.zero_grad()
+    om.policy_gradient_step(inputs, targets, adv, float(max_len))
+    opt.step()
+    return time.perf_counter() - t0
+
+
+def loss_microbench_cpu(rows=16384, vocab=65536, block=2048):
+    """The loss microbenchmark (16384 x 65536 logits, 50% of the positions valid) IN FULL on the host, as passes over one
+    `block`-row buffer of logits (every row is processed; the buffer is far larger than the caches): seconds."""
+    from oracle import oracle
+    _host_threads()
+    rng = np.random.default_rng(0)
+    z = rng.standard_normal((block, vocab), dtype=np.float32) * np.float32(3)
+    logits = (np.float32(15) * np.tanh(z / np.float32(15))).astype(np.float32)
+    del z
+    total = 0.0
+    for b0 in range(0, rows, block):
+        targets = rng.integers(0, vocab, block).astype(np.int32)
+        targets[rng.random(block) < 0.5] = -1
+        adv = rng.standard_normal(block // 512).astype(np.float32)
+        t0 = time.perf_counter()
+        oracle.pg_loss_backward(logits, targets, adv, 512, float(rows // 2), mode=1)
+        total += time.perf_counter() - t0
+    return total
+
+
+def measured_pairs(ctx):
+    """Workloads small enough to run whole on both arms: (config, cpu seconds, gpu seconds)."""
+    from gonano_b200.session import Model, rl_step
+    pairs = []
+    # plumbing step on the GPU through the public call
+    cfg = synthetic.dense_config("c1")
+    gm = Model(ctx, **cfg)
+    for name, value in synthetic.fill_weights(gm.names, gm.shape, 0):
+        gm.upload(name, value)
+    gm.optimizer_init()
+    prompts = synthetic.prompts(8, 32, cfg["vocab_size"], 1)
+    seeds = np.arange(8, dtype=np.uint64) + 40
+    reward_fn = lambda t, l: synthetic.contains_token_rewards(t, l, 7)
+    times = []
+    for _ in range(4):
+        t0 = time.perf_counter()
+        rl_step(gm, prompts, 4, 32, 1.0, 50, seeds, reward_fn, advantage_mode=1, optimizer=True)
+        ctx.sync()
+        times.append(time.perf_counter() - t0)
+    gm.close()
+    pairs.append({"config": "plumbing RL step (depth 2, d128, vocab 8192; 8 prompts x 32, G=4, 32 new tokens, one optimizer step), whole step, host buffers",
+                  "cpu_s": plumbing_step_cpu(), "gpu_s": float(np.median(times[1:]))})
+    ms = ctx.profile_kernel("loss", [16384, 65536, 50], 5)
+    pairs.append({"config": "loss microbenchmark 16384 x 65536, 50% valid: log-probs, loss and dlogits (device-resident on the GPU arm)",
+                  "cpu_s": loss_microbench_cpu(), "gpu_s": ms * 1e-3})
+    for p in pairs:
+        p["ratio"] = p["cpu_s"] / p["gpu_s"] if p["gpu_s"] else None
+    return pairs
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    steps = []
-    for i in range(max(1, min(args.steps, 2))):
-        steps.append(cpu_baseline())
-    best = max(steps, key=lambda s: s["value"])
-    line = {"impl": "reference", "metric": METRIC, "value": best["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": 1000.0 / best["value"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+    steps = [cpu_baseline() for _ in range(max(1, min(args.steps, 3)))]
+    steps.sort(key=lambda s: s["value"])
+    mid = steps[len(steps) // 2]     # the median sample
+    line = {"impl": "reference", "metric": METRIC, "value": mid["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1000.0 / mid["value"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": "dense d12 RL step: 64 prompts x G=8, 128 prompt tokens, 256 new tokens, vocab 32768 (bounded sample, extrapolated)"},
-            "cpu_baseline": best, "e2e": {"value": best["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+            "cpu_baseline": mid, "e2e": {"value": mid["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     emit(line)
     return 0
 
@@ -238,20 +340,80 @@ def kernel_rooflines(ctx, pk, tf32_tflops):
     return out
 
 
+def step_flop(cfg, w):
+    """Useful floating-point work of one RL step: 2*M*N*K per product (the 3xTF32 split issues three times as many
+    tensor-core flop), attention by the reference's own accounting (model/flops.go:107-117: 4*T_q*T_k*d per layer)."""
+    d, L, Vp = cfg["embed_dim"], cfg["n_layer"], (cfg["vocab_size"] + 63) // 64 * 64
+    D = d // cfg["n_head"]
+    kv = cfg["n_kv_head"] * D
+    per_layer = d * (d + 2 * kv) + d * d + 8 * d * d          # q,k,v, c_proj, c_fc + mlp c_proj
+    p_mm = L * per_layer + Vp * d
+    rows, plen, new = w["n_prompts"] * w["group"], w["prompt_len"], w["max_tokens"]
+    T = plen + new - 1
+    decode = 2.0 * p_mm * rows * new
+    prefill = 2.0 * p_mm * w["n_prompts"] * plen
+    train = 6.0 * p_mm * rows * T
+    attn_train = 3.0 * L * rows * 4.0 * (T * (T + 1) / 2.0) * d      # forward + backward (2x)
+    attn_decode = L * rows * 4.0 * d * sum(range(plen + 1, plen + new + 1))
+    return decode + prefill + train + attn_train + attn_decode
+
+
+def run_only(args):
+    """Sub-workloads for profiling: one small JSON line each."""
+    from gonano_b200.session import Context, Model
+    ctx = Context(0)
+    if args.only == "kernel":
+        ms = ctx.profile_kernel(args.kernel, args.dims, args.iters)
+        emit({"only": "kernel", "kernel": args.kernel, "dims": args.dims, "ms": ms})
+        return 0
+    cfg = synthetic.latent_config(args.model) if args.model in ("c3", "latent-small", "latent-tiny") else synthetic.dense_config(args.model)
+    model = Model(ctx, **cfg)
+    for name, value in synthetic.fill_weights(model.names, model.shape, 0):
+        model.upload(name, value)
+    V = cfg["vocab_size"]
+    if args.only == "decode":
+        if args.eager:
+            ctx.set_option("decode_graph", 0)
+        prompts = synthetic.prompts(args.prompts, 128, V, 1)
+        seeds = np.arange(args.prompts, dtype=np.uint64)
+        for _ in range(2):
+            tokens, lengths, steps, _ = model.generate_batch(prompts, 8, args.tokens, 1.0, 50, seeds)
+        emit({"only": "decode", "rows": args.prompts * 8, "steps": steps, "prefill_ms": model.phase_ms("prefill"), "decode_ms": model.phase_ms("decode"),
+              "ms_per_decode_step": model.phase_ms("decode") / max(steps - 1, 1)})
+    else:
+        rng = np.random.default_rng(0)
+        T = 383
+        ids = rng.integers(0, V - 11, (args.rows, T), dtype=np.int32)
+        tg = np.roll(ids, -1, axis=1).copy(); tg[:, : T // 3] = -1
+        adv = rng.standard_normal(args.rows).astype(np.float32)
+        for _ in range(2):
+            model.zero_grad()
+            loss, _, _, _ = model.policy_gradient_step(ids, tg, adv, float(T + 1), rows_per_pass=args.rows)
+        emit({"only": "train", "rows": args.rows, "seq": T, "loss": loss, "ms": {p: model.phase_ms(p) for p in ["train_forward", "loss", "train_backward"]}})
+    model.close(); ctx.close()
+    return 0
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
     from gonano_b200 import dist as gdist
-    from gonano_b200.session import Context, Model, rl_step
+    from gonano_b200.session import Context, Model, rl_step, build_batch
+    from gonano_b200.backend import group_advantage
 
     rank, world, local = gdist.env_rank_world()
     torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
     w = WORKLOAD
     cfg = synthetic.dense_config(w["name"])
     stream = torch.cuda.Stream(device=local)
     ctx = Context(local, stream.cuda_stream)
+    if world > 1:
+        # torch.distributed is the rendezvous (it hands rank 0's communicator id to the others) and the clock's
+        # barrier; the gradient exchange itself runs inside the library (gn_model_grad_allreduce, NCCL)
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+        box = [Context.comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        ctx.comm_init(box[0], rank, world)
     model = Model(ctx, **cfg)
     for name, value in synthetic.fill_weights(model.names, model.shape, w["seed"]):
         model.upload(name, value)
@@ -265,7 +427,6 @@ def run_ours(args):
         return rewards_all[lo * G:hi * G]
 
     model.optimizer_init()   # cmd/chat_rl/main.go:68-72
-    all_reduce = gdist.GradAllReduce(model, local, stream) if world > 1 else None
     phases = ["prefill", "decode", "train_forward", "loss", "train_backward", "allreduce", "optimizer"]
     state = {"step": 0}
 
@@ -273,10 +434,9 @@ def run_ours(args):
         seeds = np.arange(lo, hi, dtype=np.uint64) + np.uint64(1000 * state["step"])   # cmd/chat_rl seeds rollouts by step
         state["step"] += 1
         res = rl_step(model, prompts, G, w["max_tokens"], w["temperature"], w["top_k"], seeds, reward_fn, advantage_mode=0,
-                      all_reduce=all_reduce, max_len_fn=gdist.global_max_len if world > 1 else None, optimizer=True,
-                      shard=(rank, world))
+                      optimizer=True, data_parallel=world > 1)
         ph = {p: model.phase_ms(p) for p in phases if p != "allreduce"}
-        ph["allreduce"] = all_reduce.last_ms() if all_reduce is not None else 0.0
+        ph["allreduce"] = model.phase_ms("allreduce") if world > 1 else 0.0
         return res, ph
 
     for _ in range(args.warmup):
@@ -315,6 +475,40 @@ def run_ours(args):
         dist.all_reduce(tok, op=dist.ReduceOp.SUM)
     ms_total, ms_resident = float(t[0]), float(t[1])
     tokens_total = int(tok[0])
+
+    # ---- untimed verification of the data-parallel run: replicas and the reduced gradient
+    verify = {}
+    if world > 1 and not args.lean:
+        psum, _ = model.checksum()
+        sums = [None] * world
+        dist.all_gather_object(sums, psum)
+        verify["replicas_identical"] = bool(all(v == sums[0] for v in sums))
+        verify["replica_param_checksums"] = sums
+        # one more rollout + policy-gradient step without the optimizer: the all-reduced gradient of the N shards against
+        # the gradient rank 0 computes alone over all rows (same parameters, same rollouts, same padded length)
+        seeds = np.arange(lo, hi, dtype=np.uint64) + np.uint64(777)
+        tk, ln, _, _ = model.generate_batch(prompts, G, w["max_tokens"], w["temperature"], w["top_k"], seeds)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (tk, ln))
+        tk_all = np.concatenate([g[0] for g in gathered]); ln_all = np.concatenate([g[1] for g in gathered])
+        adv_all = group_advantage(rewards_all, G, 0)
+        pad = cfg["vocab_size"] - 7
+        max_len = w["prompt_len"] + int(ln_all.max())
+        inputs, targets, _ = build_batch(prompts, G, tk, ln, pad, max_len)
+        model.zero_grad()
+        model.policy_gradient_step(inputs, targets, adv_all[lo * G:hi * G], float(max_len))
+        model.grad_allreduce()
+        address, count = model.grad_buffer()
+        g_n = gdist.device_tensor(address, count, local).clone()
+        dist.barrier()
+        if rank == 0:
+            inputs, targets, _ = build_batch(prompts_all, G, tk_all, ln_all, pad, max_len)
+            model.zero_grad()
+            model.policy_gradient_step(inputs, targets, adv_all, float(max_len))
+            g_1 = gdist.device_tensor(address, count, local)
+            verify["grad_vs_single_rank"] = float((g_n - g_1).abs().max() / g_1.abs().max())
+        model.zero_grad()
+        dist.barrier()
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -340,14 +534,15 @@ def run_ours(args):
         pass
     kernels = kernel_rooflines(ctx, pk, tf32) if not args.lean else [{"kernel": "gemm_nt", "workload": "not measured (--lean)"}]
     dominant = dict(kernels[0])
-    # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this product under ncu (profiles/gemm_tc_timeline.md);
-    # algorithmic: operands hi+lo 2 * 4 * (M*K + N*K) = 119.5 MB read, output 201.3 MB written
+    # algorithmic bytes of that product: operands hi+lo 2 * 4 * (M*K + N*K) = 119.5 MB read, output 201.3 MB written
     dominant["traffic"] = GEMM_TRAFFIC_BYTES
     dominant["peak_source"] = f"TF32 8192^3 torch.matmul measured in this run ({tf32:.1f} TFLOP/s) / 3 for the 3xTF32 split" if tf32 else "unavailable"
-    cpu = None
+    cpu, pairs = None, None
     if world == 1 and not args.no_cpu_baseline and not args.lean:
         try:
             cpu = cpu_baseline()
+            pairs = measured_pairs(ctx)
+            cpu["measured"] = pairs
         except Exception as exc:  # the oracle is test infrastructure: its absence must not hide the GPU number
             cpu = {"value": None, "unit": UNIT, "cores": None, "kind": "port", "sample": f"unavailable: {exc}"}
     steps_per_s_e2e = args.steps / (ms_total * 1e-3)
@@ -356,6 +551,8 @@ def run_ours(args):
     T = w["prompt_len"] + w["max_tokens"] - 1
     h2d = P * w["prompt_len"] * 4 + P * 8 + 2 * rows * T * 4 + rows * 4 + rows * 4
     d2h = rows * w["max_tokens"] * 4 + rows * 4 + 8 + rows * 4
+    flop = step_flop(cfg, w)
+    step_tflops = flop / (ms_total / args.steps * 1e-3) / 1e12
     line = {
         "metric": METRIC, "value": steps_per_s_resident, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
@@ -364,7 +561,7 @@ def run_ours(args):
                                "vocab 32768, d768 L12 Hq6 Hkv2; rollout + advantage + policy-gradient loss/backward + gradient all-reduce + "
                                "optimizer step (Sinkhorn / Muon / AdamW as cmd/chat_rl) + ZeroGrad",
                    "parallelism": f"dp{world}", "l2": "working set (705 MB weights, 4.8 GB KV cache, GBs of activations) is far larger than L2; no flush",
-                   "gemm": "tcgen05 3xTF32" if os.environ.get("GN_GEMM", "") != "simt" else "simt"},
+                   "gemm": "tcgen05 3xTF32"},
         "e2e": {"value": steps_per_s_e2e, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "rollout_tokens_per_s": tokens_total / (ms_total * 1e-3),
         "phase_ms_per_step": {p: phase_sum[p] / args.steps for p in phases},
@@ -372,10 +569,15 @@ def run_ours(args):
         "gpu_launches": launches,
         "clocks": clocks,
         "roofline": dominant,
+        # the whole step against the same tensor roof: useful flop of one step / step time (all N GPUs) / (N x peak)
+        "step_roofline": {"flop": flop, "tflops": step_tflops, "peak": (tf32 / 3.0 * world) if tf32 else None,
+                          "frac": step_tflops / (tf32 / 3.0 * world) if tf32 else None,
+                          "note": "useful flop of one whole step (products 2*M*N*K, attention 4*Tq*Tk*d per layer) / step time; the `roofline` object is one kernel"},
         "kernels": kernels,
         "cpu_baseline": cpu,
         "peaks": pk,
     }
+    line.update(verify)
     emit(line)
     if world > 1:
         dist.destroy_process_group()
@@ -395,10 +597,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--lean", action="store_true", help="steps only: no per-kernel microbenchmarks, TF32 peak or CPU baseline (for ncu launch lists)")
+    ap.add_argument("--lean", action="store_true", help="steps only: no per-kernel microbenchmarks, TF32 peak, CPU baseline or replica checks")
+    ap.add_argument("--only", choices=["decode", "train", "kernel"], help="run one sub-workload for profiling instead of the benchmark")
+    ap.add_argument("--model", default="d12"); ap.add_argument("--prompts", type=int, default=64); ap.add_argument("--tokens", type=int, default=4)
+    ap.add_argument("--rows", type=int, default=32); ap.add_argument("--eager", action="store_true", help="--only decode: no CUDA-graph replay, so that a profiler sees every launch")
+    ap.add_argument("--kernel", default="gemm_nt"); ap.add_argument("--dims", type=int, nargs="+", default=[16384, 3072, 768]); ap.add_argument("--iters", type=int, default=5)
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.only:
+        return run_only(args)
     return run_ours(args)
 
 

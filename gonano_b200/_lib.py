@@ -91,6 +91,9 @@ SIGNATURES = {
     "gn_generate_batch": (I, [vp, vp, I, I, I, I, F, I, vp, vp, vp, vp, C.POINTER(I)]),
     "gn_policy_gradient_step": (I, [vp, vp, vp, vp, I, I, F, I, f32p, vp, vp, vp]),
     "gn_model_phase_ms": (I, [vp, C.c_char_p, f32p]),
+    "gn_comm_unique_id": (I, [vp]), "gn_ctx_comm_init": (I, [vp, vp, I, I]), "gn_ctx_comm_destroy": (I, [vp]),
+    "gn_model_grad_allreduce": (I, [vp]), "gn_ctx_allreduce_max_i64": (I, [vp, C.POINTER(C.c_int64)]),
+    "gn_model_optimizer_exchange": (I, [vp]),
     "gn_profile_kernel": (I, [vp, C.c_char_p, C.POINTER(C.c_int64), I, I, f32p]),
 }
 

@@ -1264,8 +1264,14 @@ static int decode_go(const float* q, int64_t q_rstride, const float* kcache, con
   // fewer than the equivalent of ~5 four-warp CTAs per SM: two keys per iteration (shorter chain); otherwise one
   // (more resident warps)
   const int nw = attention_decode_warps(rows, Hkv);
-#define GN_DEC_LAUNCH(UU, WW) GN_CUDA(launch_pdl(attn_decode_kernel<DP, RATIO, UU, WW>, grid, dim3(32 * WW), 0, s, q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, Hq, Hkv, D, window, out, o_rstride, \
-                                                                              part_acc, part_ms, splits, out_hi, out_lo, psplits ? prefix_len : 0, psplits, nslots))
+  // Small grids launch as programmatic dependents (their CTAs are resident and waiting when the kernel in front
+  // finishes); a grid of several waves gains nothing from that and would only take residency from the tail of its
+  // predecessor, so it launches normally (the kernel's wait is then a no-op).
+  const bool dependent = (int64_t)rows * Hkv * splits <= 2 * (int64_t)num_sms();
+#define GN_DEC_LAUNCH(UU, WW) do { if (dependent) GN_CUDA(launch_pdl(attn_decode_kernel<DP, RATIO, UU, WW>, grid, dim3(32 * WW), 0, s, q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, Hq, Hkv, D, window, out, o_rstride, \
+                                                                              part_acc, part_ms, splits, out_hi, out_lo, psplits ? prefix_len : 0, psplits, nslots)); \
+    else attn_decode_kernel<DP, RATIO, UU, WW><<<grid, 32 * WW, 0, s>>>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, Hq, Hkv, D, window, out, o_rstride, \
+                                                                              part_acc, part_ms, splits, out_hi, out_lo, psplits ? prefix_len : 0, psplits, nslots); } while (0)
   // the warps' partial results meet in static shared memory (NW x RATIO x DP floats): wide groups get fewer warps
   constexpr int kMaxW = RATIO * DP * 16 <= 10240 ? 16 : (RATIO * DP * 8 <= 10240 ? 8 : 4);
   if (nw == 16 && kMaxW >= 16) { if constexpr (kMaxW >= 16) { GN_DEC_LAUNCH(2, 16); } }

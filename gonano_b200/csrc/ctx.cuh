@@ -8,4 +8,6 @@ struct gn_ctx {
   bool own_stream = false;
   int gemm_kind = 1;
   bool use_graphs = true;   // replay the decode step as a CUDA graph
+  void* comm = nullptr;     // ncclComm_t of the data-parallel job (gn_ctx_comm_init), null in a single-process run
+  int comm_rank = 0, comm_world = 1;
 };

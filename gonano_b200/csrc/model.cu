@@ -445,6 +445,7 @@ int gn_ctx_create(int device, void* stream, gn_ctx** out) {
 int gn_ctx_destroy(gn_ctx* c) {
   if (!c) return GN_OK;
   cudaSetDevice(c->device);
+  gn_ctx_comm_destroy(c);
   gemm_release_stream(c->stream);
   if (c->own_stream) cudaStreamDestroy(c->stream);
   delete c;
@@ -655,7 +656,8 @@ int gn_model_optimizer_init(gn_model* m, const gn_optimizer_config* cfg) {
 // Routing: model/optimizer.go:20-165 (sinkhorn = true).  Parameters are visited in name order; the updates are
 // independent of one another, so the order only fixes the launch sequence.  With shard_count > 1 only the tensors
 // this shard owns are updated (ownership: greedy balance of an operation-count estimate, identical on every rank).
-namespace {
+}  // extern "C"
+namespace gnm {
 std::vector<int> optimizer_owners(gn_model* m, int shard_count) {
   const size_t n = m->params.size();
   std::vector<int> owner(n, 0);
@@ -679,6 +681,9 @@ std::vector<int> optimizer_owners(gn_model* m, int shard_count) {
   }
   return owner;
 }
+}  // namespace gnm
+extern "C" {
+namespace {
 
 int optimizer_run(gn_model* m, int shard, int shard_count) {
   cudaStream_t s = m->s();

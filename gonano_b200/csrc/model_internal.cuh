@@ -111,6 +111,10 @@ inline int gemm(gn_model* m, const gn::GemmArgs& a) { return gn::gemm_dispatch(a
 
 enum Mode { MODE_PLAIN, MODE_PREFILL, MODE_DECODE, MODE_TRAIN };
 
+// Which shard updates which tensor in a sharded optimizer step: a greedy balance of an operation-count estimate,
+// identical on every rank (index = position in gn_model::params).
+std::vector<int> optimizer_owners(gn_model* m, int shard_count);
+
 struct FwdBufs {
   float *E, *X0, *Xa, *Xb, *H, *QKV, *O, *M, *HID, *BO, *Y, *LOGITS;
   float *S1h, *S1l, *S4h, *S4l;   // producer-written tf32 splits: one [rows, d] pair and one [rows, 4d] pair, reused by every layer

@@ -58,6 +58,25 @@ class Context:
         check(self.lib.gn_profile_kernel(self.h, kernel.encode(), arr, len(dims), iters, C.byref(out)))
         return out.value
 
+    # ---- data-parallel exchange inside the library (NCCL; one process per GPU)
+    @staticmethod
+    def comm_unique_id() -> bytes:
+        """Rank 0 creates the id and hands these bytes to the other ranks (by any transport)."""
+        lib = _lib.load()
+        buf = C.create_string_buffer(128)
+        check(lib.gn_comm_unique_id(buf))
+        return buf.raw
+
+    def comm_init(self, unique_id: bytes, rank: int, world: int):
+        """Collective: returns when every rank has joined."""
+        check(self.lib.gn_ctx_comm_init(self.h, C.c_char_p(unique_id), rank, world))
+        self.rank, self.world = rank, world
+
+    def allreduce_max(self, value: int) -> int:
+        v = C.c_int64(int(value))
+        check(self.lib.gn_ctx_allreduce_max_i64(self.h, C.byref(v)))
+        return int(v.value)
+
     def close(self):
         if self.h:
             self.lib.gn_ctx_destroy(self.h)
@@ -176,6 +195,14 @@ class Model:
     def optimizer_finish(self):
         check(self.lib.gn_model_optimizer_finish(self.h))
 
+    def grad_allreduce(self):
+        """SUM of the flat gradient buffer over the ranks of the context's communicator."""
+        check(self.lib.gn_model_grad_allreduce(self.h))
+
+    def optimizer_exchange(self):
+        """After optimizer_step_shard on every rank: broadcast each tensor from its owner, then ZeroGrad."""
+        check(self.lib.gn_model_optimizer_exchange(self.h))
+
     def policy_gradient_step(self, inputs, targets, advantages, norm, rows_per_pass=0, taps=False):
         inputs, targets, advantages = _i32(inputs), _i32(targets), _f32(advantages)
         B, T = inputs.shape
@@ -225,15 +252,22 @@ class RLStepResult:
 
 
 def rl_step(model: Model, prompts, group, max_tokens, temperature, top_k, seeds, reward_fn, advantage_mode=0, rows_per_pass=0,
-            norm=None, all_reduce=None, max_len_fn=None, optimizer=False, shard=None) -> RLStepResult:
+            norm=None, all_reduce=None, max_len_fn=None, optimizer=False, shard=None, data_parallel=False) -> RLStepResult:
     """One RL step the way cmd/chat_rl runs it (main.go:87-184):
     rollout -> rewards -> group-relative advantages -> padded batch -> PolicyGradientStep
     -> gradient all-reduce (``all_reduce(model)``, when data parallel) -> optimizer step and
     ZeroGrad when ``optimizer`` (trainer/rl.go:62-67; needs ``model.optimizer_init()``; ``shard=(rank, world)``
     splits the optimizer's tensors over the ranks).  ``reward_fn(tokens,
     lengths)`` returns one reward per rollout.  ``norm`` defaults to the padded length
-    (main.go:183).  ``max_len_fn(local_max_len)`` returns the length every rank pads to."""
+    (main.go:183).  ``max_len_fn(local_max_len)`` returns the length every rank pads to.
+    ``data_parallel=True`` uses the communicator of the model's context (``Context.comm_init``) for all three
+    exchanges: the padded length, the gradient all-reduce and the sharded optimizer's broadcasts."""
     from .backend import group_advantage
+    if data_parallel:
+        ctx = model.ctx
+        max_len_fn = ctx.allreduce_max
+        all_reduce = lambda m: m.grad_allreduce()
+        shard = (getattr(ctx, "rank", 0), getattr(ctx, "world", 1))
     prompts = _i32(prompts)
     tokens, lengths, steps, _ = model.generate_batch(prompts, group, max_tokens, temperature, top_k, seeds)
     rewards = _f32(reward_fn(tokens, lengths))
@@ -246,7 +280,11 @@ def rl_step(model: Model, prompts, group, max_tokens, temperature, top_k, seeds,
     if all_reduce is not None:
         all_reduce(model)
     if optimizer:
-        if shard is not None and all_reduce is not None and shard[1] > 1:
+        if data_parallel and shard[1] > 1:
+            # each rank updates the tensors it owns; every tensor is then broadcast from its owner
+            model.optimizer_step_shard(shard[0], shard[1])
+            model.optimizer_exchange()
+        elif shard is not None and all_reduce is not None and shard[1] > 1:
             # each rank updates the tensors it owns; a second all-reduce of the same buffer distributes them (exactly)
             model.optimizer_step_shard(shard[0], shard[1])
             all_reduce(model)

@@ -344,6 +344,27 @@ int gn_model_optimizer_step(gn_model* model);
 int gn_model_optimizer_step_shard(gn_model* model, int shard, int shard_count);
 int gn_model_optimizer_finish(gn_model* model);
 
+/* ---------------------------------------------------------------------------
+ * Data-parallel exchange (no counterpart in the reference, which is single-process, optimizer/optimizer.go:5-7;
+ * its nearest analogue is the accumulation into Tensor.Grad, tensors/tensor.go:189-194).  One process per GPU, a
+ * full replica each; rollout prompts are sharded by the host.  Rank 0 calls gn_comm_unique_id and hands the
+ * GN_COMM_ID_BYTES bytes to the other ranks by its own means; every rank then calls gn_ctx_comm_init (collective:
+ * it returns when all ranks have joined).  NCCL (libnccl.so.2) is loaded at the first of these calls.
+ *   gn_model_grad_allreduce      SUM of the flat gradient buffer over the ranks, on the context's stream (the
+ *                                1/norm factor is already in the gradients, trainer/rl.go:41); phase "allreduce"
+ *   gn_ctx_allreduce_max_i64     MAX of one host integer over the ranks (the padded length every rank must use)
+ *   gn_model_optimizer_exchange  after gn_model_optimizer_step_shard(model, rank, world) on every rank: each tensor
+ *                                is broadcast from the rank that updated it, then the gradients are zeroed
+ *                                (optimizer.ZeroGrad); replaces the all-reduce + gn_model_optimizer_finish pair
+ * Without a communicator (or with world == 1) the three calls are local no-ops apart from the ZeroGrad. */
+#define GN_COMM_ID_BYTES 128
+int gn_comm_unique_id(void* id_out);
+int gn_ctx_comm_init(gn_ctx* ctx, const void* id, int rank, int world);
+int gn_ctx_comm_destroy(gn_ctx* ctx);
+int gn_model_grad_allreduce(gn_model* model);
+int gn_ctx_allreduce_max_i64(gn_ctx* ctx, int64_t* value);
+int gn_model_optimizer_exchange(gn_model* model);
+
 #ifdef __cplusplus
 }
 #endif
