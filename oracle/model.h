@@ -93,7 +93,15 @@ struct LayerCtx {
   std::vector<float> mid;         // x_in + attention output
   std::vector<float> m;           // norm(mid)
   std::vector<float> u;           // c_fc output (pre activation)
-  std::vector<float> hid;         // relu(u)^2
+  std::vector<float> hid;         // relu(u)^2, or the shared expert's SwiGLU output when the block has routed experts
+  // latent attention, training construction (model/train.go:43-45): the two shared latents
+  std::vector<float> mla_ql, mla_kvl;   // [rows, latent]
+  // shared SwiGLU expert (model/train.go:486-503): c_gate projection (u holds the c_fc = "up" projection)
+  std::vector<float> gate;
+  // routed experts (model/moe.go:83-97,171-198): router softmax, routing and the expert-major activations
+  std::vector<float> probs, gw, gathered, gg, gu, gh, go;   // gw: selected weight per gathered row
+  std::vector<int32_t> counts;                             // rows per expert
+  std::vector<int64_t> offsets, grow;                      // first gathered row per expert; source row per gathered row
 };
 
 struct TrainCtx {
@@ -202,6 +210,16 @@ struct Model {
     for (size_t i = 0; i < gw.size(); ++i) w.g[i] += gw[i];
     dx.resize((size_t)rows * in);
     bk.matmul(dx.data(), dy.data(), w.w.data(), (int)rows, in, out);
+  }
+  // The same for one expert's [out, in] view of a packed [E*out, in] parameter (model/moe.go:60-81): x and dy are
+  // the expert's `rows` gathered rows; the weight gradient accumulates into the view's slice.
+  void expert_linear_backward(float* dx, const float* x, const float* dy, Param& w, int expert, int out, int in, int64_t rows) const {
+    std::vector<float> dyT((size_t)out * rows), gwt((size_t)out * in);
+    for (int64_t r = 0; r < rows; ++r) for (int o = 0; o < out; ++o) dyT[(size_t)o * rows + r] = dy[(size_t)r * out + o];
+    bk.matmul(gwt.data(), dyT.data(), x, out, in, (int)rows);
+    float* g = w.g.data() + (size_t)expert * out * in;
+    for (size_t i = 0; i < gwt.size(); ++i) g[i] += gwt[i];
+    bk.matmul(dx, dy, w.w.data() + (size_t)expert * out * in, (int)rows, in, out);
   }
   void norm(std::vector<float>& out, const std::vector<float>& in, int cols) const {
     out.resize(in.size());
@@ -590,6 +608,97 @@ struct Model {
     lm_head(logits, y, rows);
   }
 
+  // Routed experts of the training pass (model/moe.go:118-198): like moe_forward, keeping the routing and every
+  // expert-major activation for the backward.
+  void moe_train_forward(LayerCtx& c, std::vector<float>& out, int64_t rows, int l) const {
+    const int d = cfg.embed_dim, E = cfg.n_experts, K = cfg.moe_top_k(), eh = cfg.moe_expert_hidden();
+    std::vector<float> logits, selw((size_t)rows * K);
+    std::vector<int32_t> sel((size_t)rows * K);
+    c.probs.assign((size_t)rows * E, 0.0f);
+    linear(logits, c.m, params.at(LP(l, "moe.router.weight")), rows);
+    bk.moe_gate_topk(logits.data(), params.at(LP(l, "moe.router_bias")).w.data(), c.probs.data(), sel.data(), selw.data(), (int)rows, E, K);
+    const int64_t total = rows * K;
+    c.counts.assign(E, 0);
+    for (int64_t i = 0; i < total; ++i) c.counts[sel[i]]++;
+    c.offsets.assign(E, 0);
+    std::vector<int64_t> fill(E, 0);
+    { int64_t cur = 0; for (int e = 0; e < E; ++e) { c.offsets[e] = cur; cur += c.counts[e]; } }
+    c.gathered.assign((size_t)total * d, 0.0f); c.gw.assign((size_t)total, 0.0f); c.grow.assign((size_t)total, 0);
+    for (int64_t r = 0; r < rows; ++r) for (int s = 0; s < K; ++s) {
+      int e = sel[r * K + s];
+      int64_t pos = c.offsets[e] + fill[e]++;
+      std::copy(c.m.begin() + r * d, c.m.begin() + (r + 1) * d, c.gathered.begin() + pos * d);
+      c.grow[pos] = r; c.gw[pos] = selw[r * K + s];
+    }
+    c.gg.assign((size_t)total * eh, 0.0f); c.gu.assign((size_t)total * eh, 0.0f); c.gh.assign((size_t)total * eh, 0.0f); c.go.assign((size_t)total * d, 0.0f);
+    bk.grouped_matmul_t(c.gg.data(), c.gathered.data(), params.at(LP(l, "moe.experts.gate.weight")).w.data(), c.counts.data(), E, eh, d);
+    bk.grouped_matmul_t(c.gu.data(), c.gathered.data(), params.at(LP(l, "moe.experts.up.weight")).w.data(), c.counts.data(), E, eh, d);
+    bk.swiglu(c.gh.data(), c.gg.data(), c.gu.data(), cfg.moe_effective_clamp(), (int64_t)c.gh.size());
+    bk.grouped_matmul_t(c.go.data(), c.gh.data(), params.at(LP(l, "moe.experts.down.weight")).w.data(), c.counts.data(), E, d, eh);
+    out.assign((size_t)rows * d, 0.0f);
+    const float scale = cfg.moe_effective_scale();
+    for (int64_t i = 0; i < total; ++i) {
+      float w = c.gw[i] * scale;
+      float* o = out.data() + c.grow[i] * d; const float* g = c.go.data() + i * d;
+      for (int cc = 0; cc < d; ++cc) o[cc] += w * g[cc];
+    }
+  }
+  // model/moe.go:203-267 with the sequence-level balance loss of :276-326 (weight 1e-4, model/moe.go:47-58; its
+  // gradient enters through the router softmax).  dout: gradient of the block output; returns the gradient at m.
+  void moe_train_backward(LayerCtx& c, std::vector<float>& dm, const std::vector<float>& dout, int64_t rows, int seq_len, int l) {
+    const int d = cfg.embed_dim, E = cfg.n_experts, K = cfg.moe_top_k(), eh = cfg.moe_expert_hidden();
+    const float scale = cfg.moe_effective_scale(), clampv = cfg.moe_effective_clamp();
+    dm.assign((size_t)rows * d, 0.0f);
+    std::vector<double> gprobs((size_t)rows * E, 0.0);
+    Param& wg = P(LP(l, "moe.experts.gate.weight")); Param& wu = P(LP(l, "moe.experts.up.weight")); Param& wd = P(LP(l, "moe.experts.down.weight"));
+    for (int e = 0; e < E; ++e) {
+      const int64_t cnt = c.counts[e], off = c.offsets[e];
+      if (cnt == 0) continue;
+      std::vector<float> dgo((size_t)cnt * d);
+      for (int64_t i = 0; i < cnt; ++i) {
+        const int64_t row = c.grow[off + i];
+        const float w = c.gw[off + i] * scale;
+        double dot = 0;
+        for (int cc = 0; cc < d; ++cc) {
+          const float g = dout[(size_t)row * d + cc];
+          dgo[(size_t)i * d + cc] = g * w;
+          dot += (double)g * (double)c.go[(size_t)(off + i) * d + cc];
+        }
+        gprobs[(size_t)row * E + e] += dot * (double)scale;
+      }
+      std::vector<float> dgh((size_t)cnt * eh), dgg((size_t)cnt * eh), dgu((size_t)cnt * eh), dfg((size_t)cnt * d), dfu((size_t)cnt * d);
+      expert_linear_backward(dgh.data(), c.gh.data() + (size_t)off * eh, dgo.data(), wd, e, d, eh, cnt);
+      bk.swiglu_backward(dgg.data(), dgu.data(), c.gg.data() + (size_t)off * eh, c.gu.data() + (size_t)off * eh, dgh.data(), clampv, (int64_t)cnt * eh);
+      expert_linear_backward(dfg.data(), c.gathered.data() + (size_t)off * d, dgg.data(), wg, e, eh, d, cnt);
+      expert_linear_backward(dfu.data(), c.gathered.data() + (size_t)off * d, dgu.data(), wu, e, eh, d, cnt);
+      for (int64_t i = 0; i < cnt; ++i) {
+        float* o = dm.data() + (size_t)c.grow[off + i] * d;
+        for (int cc = 0; cc < d; ++cc) o[cc] += dfg[(size_t)i * d + cc] + dfu[(size_t)i * d + cc];
+      }
+    }
+    // sequence-level balance loss (model/moe.go:276-326): dL/dp[t,e] = weight / (S*T) * E/(K*T) * count[s(t), e]
+    const float balance_weight = 1e-4f;   // defaultMoEBalanceWeight (model/config.go:133-135,176-186)
+    if (balance_weight > 0 && seq_len > 0 && rows > 0 && rows % seq_len == 0) {
+      const int64_t sequences = rows / seq_len;
+      std::vector<double> cnts((size_t)sequences * E, 0.0);
+      for (int e = 0; e < E; ++e) for (int64_t i = 0; i < c.counts[e]; ++i) cnts[(size_t)(c.grow[c.offsets[e] + i] / seq_len) * E + e] += 1.0;
+      const double selection_scale = (double)E / ((double)K * (double)seq_len);
+      const double coefficient = (double)balance_weight / ((double)sequences * (double)seq_len);
+      for (int64_t r = 0; r < rows; ++r) for (int e = 0; e < E; ++e)
+        gprobs[(size_t)r * E + e] += coefficient * selection_scale * cnts[(size_t)(r / seq_len) * E + e];
+    }
+    // router softmax backward and the router's own Linear
+    std::vector<float> glog((size_t)rows * E);
+    for (int64_t r = 0; r < rows; ++r) {
+      double dot = 0;
+      for (int e = 0; e < E; ++e) dot += (double)c.probs[(size_t)r * E + e] * gprobs[(size_t)r * E + e];
+      for (int e = 0; e < E; ++e) glog[(size_t)r * E + e] = (float)((double)c.probs[(size_t)r * E + e] * (gprobs[(size_t)r * E + e] - dot));
+    }
+    std::vector<float> gri;
+    linear_backward(gri, c.m, glog, P(LP(l, "moe.router.weight")), rows);
+    for (size_t i = 0; i < dm.size(); ++i) dm[i] = dm[i] + gri[i];
+  }
+
   // ------------------------------------------------- training forward
   void train_forward(TrainCtx& ctx, const int32_t* ids, int B, int T) const {
     int d = cfg.embed_dim, Hq = cfg.n_head, Hkv = cfg.n_kv_head, L = cfg.n_layer;
@@ -629,6 +738,30 @@ struct Model {
       c.x_in = x;
       norm(c.h, x, d);
       std::vector<float> q, k, v;
+      if (cfg.mla()) {
+        // model/mla.go:106-124: per-head [content | rotary] queries and keys, values up-projected from the latent;
+        // no QK norm and no 1.2 scale (model/train.go:82-85); value embeddings are off (model/transformer.go:73)
+        const int rope = cfg.mla_rope(), content = cfg.mla_content();
+        std::vector<float> qc, qr, kc, kr;
+        linear(c.mla_ql, c.h, params.at(LP(l, "attn.mla_q_down.weight")), rows);
+        linear(qc, c.mla_ql, params.at(LP(l, "attn.mla_q_up.weight")), rows);
+        linear(qr, c.h, params.at(LP(l, "attn.mla_q_rope.weight")), rows);
+        linear(c.mla_kvl, c.h, params.at(LP(l, "attn.mla_kv_down.weight")), rows);
+        linear(kc, c.mla_kvl, params.at(LP(l, "attn.mla_k_up.weight")), rows);
+        linear(kr, c.h, params.at(LP(l, "attn.mla_k_rope.weight")), rows);
+        linear(v, c.mla_kvl, params.at(LP(l, "attn.mla_v_up.weight")), rows);
+        auto concat = [&](std::vector<float>& dst, const std::vector<float>& cc, const std::vector<float>& rr, int H) {
+          dst.resize((size_t)rows * H * D);
+          for (int64_t i = 0; i < rows * H; ++i) {
+            std::copy(cc.begin() + i * content, cc.begin() + (i + 1) * content, dst.begin() + i * D);
+            std::copy(rr.begin() + i * rope, rr.begin() + (i + 1) * rope, dst.begin() + i * D + content);
+          }
+        };
+        concat(q, qc, qr, Hq); concat(k, kc, kr, Hkv);
+        rotary(q, B, T, Hq, 0, 1.0f);
+        rotary(k, B, T, Hkv, 0, 1.0f);
+        to_head_major(c.q_hm, q, B, T, Hq, D); to_head_major(c.k_hm, k, B, T, Hkv, D); to_head_major(c.v_hm, v, B, T, Hkv, D);
+      } else {
       linear(q, c.h, params.at(LP(l, "attn.c_q.weight")), rows);
       linear(k, c.h, params.at(LP(l, "attn.c_k.weight")), rows);
       linear(v, c.h, params.at(LP(l, "attn.c_v.weight")), rows);
@@ -653,6 +786,7 @@ struct Model {
       for (auto& e : qn) e *= kQKScale;
       for (auto& e : kn) e *= kQKScale;
       to_head_major(c.q_hm, qn, B, T, Hq, D); to_head_major(c.k_hm, kn, B, T, Hkv, D); to_head_major(c.v_hm, v, B, T, Hkv, D);
+      }
       c.o_hm.assign((size_t)rows * Hq * D, 0.0f);
       c.lse.assign((size_t)B * Hq * T, 0.0f);
 #pragma omp parallel for schedule(static)
@@ -670,10 +804,20 @@ struct Model {
       norm(c.m, c.mid, d);
       linear(c.u, c.m, params.at(LP(l, "mlp.c_fc.weight")), rows);
       c.hid.resize(c.u.size());
-      bk.relu_squared(c.hid.data(), c.u.data(), (int64_t)c.u.size());
       std::vector<float> fo;
-      linear(fo, c.hid, params.at(LP(l, "mlp.c_proj.weight")), rows);
-      for (size_t i = 0; i < x.size(); ++i) x[i] = c.mid[i] + fo[i];
+      if (cfg.moe()) {
+        // shared SwiGLU expert (model/train.go:490-503) plus the routed experts (model/train.go:538-552)
+        linear(c.gate, c.m, params.at(LP(l, "mlp.c_gate.weight")), rows);
+        bk.swiglu(c.hid.data(), c.gate.data(), c.u.data(), cfg.moe_effective_clamp(), (int64_t)c.hid.size());
+        linear(fo, c.hid, params.at(LP(l, "mlp.c_proj.weight")), rows);
+        std::vector<float> mo;
+        moe_train_forward(c, mo, rows, l);
+        for (size_t i = 0; i < x.size(); ++i) x[i] = c.mid[i] + (fo[i] + mo[i]);
+      } else {
+        bk.relu_squared(c.hid.data(), c.u.data(), (int64_t)c.u.size());
+        linear(fo, c.hid, params.at(LP(l, "mlp.c_proj.weight")), rows);
+        for (size_t i = 0; i < x.size(); ++i) x[i] = c.mid[i] + fo[i];
+      }
       if (l == L / 2) ctx.backout = x;
     }
     if (!ctx.backout.empty()) {
@@ -719,8 +863,19 @@ struct Model {
       std::vector<float> dhid, dm, dmid;
       linear_backward(dhid, c.hid, dout, P(LP(l, "mlp.c_proj.weight")), rows);
       std::vector<float> du(dhid.size(), 0.0f);
+      if (cfg.moe()) {
+        // shared SwiGLU expert (model/train.go:505-514), then the routed experts (model/train.go:563-566)
+        std::vector<float> dgate(dhid.size()), t2, dmoe;
+        bk.swiglu_backward(dgate.data(), du.data(), c.gate.data(), c.u.data(), dhid.data(), cfg.moe_effective_clamp(), (int64_t)dhid.size());
+        linear_backward(dm, c.m, dgate, P(LP(l, "mlp.c_gate.weight")), rows);
+        linear_backward(t2, c.m, du, P(LP(l, "mlp.c_fc.weight")), rows);
+        for (size_t i = 0; i < dm.size(); ++i) dm[i] = dm[i] + t2[i];
+        moe_train_backward(c, dmoe, dout, rows, T, l);
+        for (size_t i = 0; i < dm.size(); ++i) dm[i] = dm[i] + dmoe[i];
+      } else {
       for (size_t i = 0; i < du.size(); ++i) if (c.u[i] > 0) du[i] = dhid[i] * 2 * c.u[i];   // tensors/backward.go:57-65
       linear_backward(dm, c.m, du, P(LP(l, "mlp.c_fc.weight")), rows);
+      }
       std::vector<float> nb;
       norm_backward(nb, c.mid, dm, d);
       dmid.resize(dout.size());
@@ -739,20 +894,50 @@ struct Model {
                               doh.data() + idx * T * D, c.lse.data() + idx * T, nullptr, T, T, D, 0, windows[l], nullptr, 0,
                               dq.data() + idx * T * D, dk.data() + slot * T * D, dv.data() + slot * T * D);
       }
+      std::vector<float> dqs, dks, dvs, dqp, dkp;
+      std::vector<float> dh, t1;
+      if (cfg.mla()) {
+        // model/train.go:414-419 and model/mla.go:126-146: inverse rotation, split into content / rotary parts, the two
+        // up-projections into the shared latents, then the down-projections and the rotary projections into h
+        const int rope = cfg.mla_rope(), content = cfg.mla_content(), lat = cfg.mla_latent;
+        to_seq_major(dqs, dq, B, T, Hq, D); to_seq_major(dks, dk, B, T, Hkv, D); to_seq_major(dvs, dv, B, T, Hkv, D);
+        rotary(dqs, B, T, Hq, 0, -1.0f);
+        rotary(dks, B, T, Hkv, 0, -1.0f);
+        auto split = [&](const std::vector<float>& src, std::vector<float>& cc, std::vector<float>& rr, int H) {
+          cc.resize((size_t)rows * H * content); rr.resize((size_t)rows * H * rope);
+          for (int64_t i = 0; i < rows * H; ++i) {
+            std::copy(src.begin() + i * D, src.begin() + i * D + content, cc.begin() + i * content);
+            std::copy(src.begin() + i * D + content, src.begin() + (i + 1) * D, rr.begin() + i * rope);
+          }
+        };
+        std::vector<float> dqc, dqr, dkc, dkr, dql, dkvl, t3;
+        split(dqs, dqc, dqr, Hq); split(dks, dkc, dkr, Hkv);
+        linear_backward(dql, c.mla_ql, dqc, P(LP(l, "attn.mla_q_up.weight")), rows);
+        linear_backward(dh, c.h, dql, P(LP(l, "attn.mla_q_down.weight")), rows);
+        linear_backward(t1, c.h, dqr, P(LP(l, "attn.mla_q_rope.weight")), rows);
+        for (size_t i = 0; i < dh.size(); ++i) dh[i] = dh[i] + t1[i];
+        linear_backward(dkvl, c.mla_kvl, dkc, P(LP(l, "attn.mla_k_up.weight")), rows);
+        linear_backward(t3, c.mla_kvl, dvs, P(LP(l, "attn.mla_v_up.weight")), rows);
+        for (size_t i = 0; i < dkvl.size(); ++i) dkvl[i] = dkvl[i] + t3[i];
+        linear_backward(t1, c.h, dkvl, P(LP(l, "attn.mla_kv_down.weight")), rows);
+        for (size_t i = 0; i < dh.size(); ++i) dh[i] = dh[i] + t1[i];
+        linear_backward(t1, c.h, dkr, P(LP(l, "attn.mla_k_rope.weight")), rows);
+        for (size_t i = 0; i < dh.size(); ++i) dh[i] = dh[i] + t1[i];
+        (void)lat;
+      } else {
       for (auto& e : dq) e *= kQKScale;
       for (auto& e : dk) e *= kQKScale;
-      std::vector<float> dqs, dks, dvs, dqp, dkp;
       to_seq_major(dqs, dq, B, T, Hq, D); to_seq_major(dks, dk, B, T, Hkv, D); to_seq_major(dvs, dv, B, T, Hkv, D);
       norm_backward(dqp, c.q_rot, dqs, D);
       norm_backward(dkp, c.k_rot, dks, D);
       rotary(dqp, B, T, Hq, 0, -1.0f);
       rotary(dkp, B, T, Hkv, 0, -1.0f);
-      std::vector<float> dh, t1;
       linear_backward(dh, c.h, dqp, P(LP(l, "attn.c_q.weight")), rows);
       linear_backward(t1, c.h, dkp, P(LP(l, "attn.c_k.weight")), rows);
       for (size_t i = 0; i < dh.size(); ++i) dh[i] = dh[i] + t1[i];
       linear_backward(t1, c.h, dvs, P(LP(l, "attn.c_v.weight")), rows);
       for (size_t i = 0; i < dh.size(); ++i) dh[i] = dh[i] + t1[i];
+      }
       if (!c.ve.empty()) {
         // model/train.go:375-409
         Param& wg = P(LP(l, "attn.ve_gate.weight"));

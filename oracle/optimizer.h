@@ -148,7 +148,7 @@ inline void sinkhorn_step(float* param, const float* grad, float* mom, int rows,
   for (int64_t i = 0; i < n; ++i) param[i] -= (float)(l * (double)u[i]);
 }
 
-// The optimizer chat_rl builds for a dense-preset model: SetupOptimizer(0.004, 0.2, 0.02, 0.0, 0.5, true) with every
+// The optimizer chat_rl builds for a model (dense or latent preset): SetupOptimizer(0.004, 0.2, 0.02, 0.0, 0.5, true) with every
 // learning rate multiplied by 0.05 (cmd/chat_rl/main.go:68-72), i.e. Sinkhorn for lm_head / wte / value embeddings,
 // AdamW for the scalar groups, Muon for every block matrix (model/optimizer.go:20-165).
 struct Optimizer {
@@ -179,6 +179,15 @@ struct Optimizer {
       else if (name == "resid_lambdas") adam(scalar_lr * 0.01f, 0.8f, 0.95f, 0.05f);
       else if (name == "x0_lambdas") adam(scalar_lr, 0.96f, 0.95f, 0.0f);
       else if (name == "smear_gate.weight" || name == "smear_lambda" || name == "backout_lambda") adam(0.2f, 0.8f, 0.95f, 0.0f);
+      else if (ends_with(name, "moe.router_bias")) continue;   // updated by load, never optimised (model/optimizer.go:83-86)
+      else if (name.find(".moe.experts.") != std::string::npos) {
+        // packed expert weights: one Muon matrix per expert view (model/optimizer.go:87-93, model/moe.go:60-81)
+        const int E = m->cfg.n_experts, er = p.rows / E;
+        for (int e = 0; e < E; ++e) {
+          const int64_t off = (int64_t)e * er * p.cols;
+          muon_step(m->bk, p.w.data() + off, p.g.data() + off, mo + off, se + off, er, p.cols, matrix_lr * lr_mult, 0.95f, 5, 0.9f, weight_decay);
+        }
+      }
       else muon_step(m->bk, p.w.data(), p.g.data(), mo, se, p.rows, p.cols, matrix_lr * lr_mult, 0.95f, 5, 0.9f, weight_decay);
     }
     m->zero_grad();   // trainer/rl.go:65-66
