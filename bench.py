@@ -53,6 +53,8 @@ def emit(line: dict) -> None:
 # (`bench.py --only kernel --kernel gemm_nt --dims 16384 3072 768`): 120.4 MB read + 157.5 MB written
 GEMM_TRAFFIC_BYTES = 277851136
 WORKLOAD = dict(name="d12", n_prompts=64, prompt_len=128, group=8, max_tokens=256, temperature=1.0, top_k=50, seed=0)
+# the latent preset's workload (absorbed MLA rollout, un-absorbed MLA + DeepSeekMoE training): `--workload c3`, one GPU line
+WORKLOAD_C3 = dict(name="c3", n_prompts=32, prompt_len=256, group=8, max_tokens=256, temperature=1.0, top_k=50, seed=0)
 METRIC, UNIT = "rl_steps_per_s_d12", "steps/s"
 
 
@@ -403,8 +405,11 @@ def run_ours(args):
 
     rank, world, local = gdist.env_rank_world()
     torch.cuda.set_device(local)
-    w = WORKLOAD
-    cfg = synthetic.dense_config(w["name"])
+    latent = args.workload == "c3"
+    w = WORKLOAD_C3 if latent else WORKLOAD
+    cfg = synthetic.latent_config(w["name"]) if latent else synthetic.dense_config(w["name"])
+    if latent:
+        args.lean = True      # the per-kernel rooflines, the CPU sample and the flop model below describe the dense d12 step
     stream = torch.cuda.Stream(device=local)
     ctx = Context(local, stream.cuda_stream)
     if world > 1:
@@ -551,13 +556,16 @@ def run_ours(args):
     T = w["prompt_len"] + w["max_tokens"] - 1
     h2d = P * w["prompt_len"] * 4 + P * 8 + 2 * rows * T * 4 + rows * 4 + rows * 4
     d2h = rows * w["max_tokens"] * 4 + rows * 4 + 8 + rows * 4
-    flop = step_flop(cfg, w)
-    step_tflops = flop / (ms_total / args.steps * 1e-3) / 1e12
+    flop = step_flop(cfg, w) if not latent else None
+    step_tflops = flop / (ms_total / args.steps * 1e-3) / 1e12 if flop else None
     line = {
-        "metric": METRIC, "value": steps_per_s_resident, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "metric": METRIC if not latent else "rl_steps_per_s_c3", "value": steps_per_s_resident, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "dense d12 RL step: 64 prompts x G=8 (512 rows), 128 prompt tokens, 256 new tokens, T=1.0, top-k 50, "
+        "config": {"workload": ("latent preset RL step: 32 prompts x G=8 (256 rows), 256 prompt tokens, 256 new tokens, T=1.0, top-k 50, vocab 32768, "
+                                "d1024 L8 Hq8, latent 256, 1 shared + 16 routed experts of hidden 512, top-2; absorbed-MLA rollout, un-absorbed MLA + MoE "
+                                "training pass with the balance loss, optimizer step (per-expert Muon views)") if latent else
+                               "dense d12 RL step: 64 prompts x G=8 (512 rows), 128 prompt tokens, 256 new tokens, T=1.0, top-k 50, "
                                "vocab 32768, d768 L12 Hq6 Hkv2; rollout + advantage + policy-gradient loss/backward + gradient all-reduce + "
                                "optimizer step (Sinkhorn / Muon / AdamW as cmd/chat_rl) + ZeroGrad",
                    "parallelism": f"dp{world}", "l2": "working set (705 MB weights, 4.8 GB KV cache, GBs of activations) is far larger than L2; no flush",
@@ -571,7 +579,7 @@ def run_ours(args):
         "roofline": dominant,
         # the whole step against the same tensor roof: useful flop of one step / step time (all N GPUs) / (N x peak)
         "step_roofline": {"flop": flop, "tflops": step_tflops, "peak": (tf32 / 3.0 * world) if tf32 else None,
-                          "frac": step_tflops / (tf32 / 3.0 * world) if tf32 else None,
+                          "frac": step_tflops / (tf32 / 3.0 * world) if (tf32 and step_tflops) else None,
                           "note": "useful flop of one whole step (products 2*M*N*K, attention 4*Tq*Tk*d per layer) / step time; the `roofline` object is one kernel"},
         "kernels": kernels,
         "cpu_baseline": cpu,
@@ -598,6 +606,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--lean", action="store_true", help="steps only: no per-kernel microbenchmarks, TF32 peak, CPU baseline or replica checks")
+    ap.add_argument("--workload", default="d12", choices=["d12", "c3"], help="d12: the dense step the metric is quoted on; c3: the latent preset's step")
     ap.add_argument("--only", choices=["decode", "train", "kernel"], help="run one sub-workload for profiling instead of the benchmark")
     ap.add_argument("--model", default="d12"); ap.add_argument("--prompts", type=int, default=64); ap.add_argument("--tokens", type=int, default=4)
     ap.add_argument("--rows", type=int, default=32); ap.add_argument("--eager", action="store_true", help="--only decode: no CUDA-graph replay, so that a profiler sees every launch")

@@ -140,12 +140,18 @@ size_t plan_bufs(gn_model* m, Arena& a, FwdBufs& b, Mode mode, int64_t rows, int
     b.layers.resize(L);
     for (int l = 0; l < L; ++l) {
       LayerSaved& s = b.layers[l];
-      s.Xin = a.take(rows * d); s.H = a.take(rows * d); s.QKV = a.take(rows * W); s.QKROT = a.take(rows * (int64_t)(Hq + Hkv) * D);
-      s.O = a.take(rows * (int64_t)Hq * D); s.LSE = a.take((int64_t)B * Hq * T); s.VESIG = a.take(rows * Hkv);
-      s.MID = a.take(rows * d); s.M = a.take(rows * d); s.U = a.take(rows * 4 * d); s.HID = a.take(rows * 4 * d); s.XOUT = a.take(rows * d);
+      s.Xin = a.take(rows * d); s.H = a.take(rows * d); s.QKV = a.take(rows * W);
+      s.QKROT = m->mla() ? nullptr : a.take(rows * (int64_t)(Hq + Hkv) * D);
+      s.O = a.take(rows * (int64_t)Hq * D); s.LSE = a.take((int64_t)B * Hq * T); s.VESIG = m->mla() ? nullptr : a.take(rows * Hkv);
+      s.MID = a.take(rows * d); s.M = a.take(rows * d); s.XOUT = a.take(rows * d);
+      if (m->moe()) s.U = s.HID = nullptr; else { s.U = a.take(rows * 4 * d); s.HID = a.take(rows * 4 * d); }
       if (m->ctx->gemm_kind == 1) {
         s.Hh = a.take(rows * d); s.Hl = a.take(rows * d); s.Mh = a.take(rows * d); s.Ml = a.take(rows * d);
-        s.Ph = a.take(rows * 4 * d); s.Pl = a.take(rows * 4 * d);
+        if (!m->moe()) { s.Ph = a.take(rows * 4 * d); s.Pl = a.take(rows * 4 * d); }
+      }
+      if (m->mla() || m->moe()) {   // what the latent preset's layers keep for their backward (model_latent_train.cu)
+        float* base = a.take(latent_saved_layout(m, nullptr, nullptr, rows));
+        if (base) latent_saved_layout(m, base, &s, rows);
       }
     }
     b.Xa = b.Xb = b.H = b.QKV = b.O = b.M = b.HID = b.BO = nullptr;
@@ -240,8 +246,8 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
     }
     bool o_split = false;   // the attention kernel also wrote the tf32 split of O
     if (m->mla()) {
-      GN_REQUIRE(!train, "latent attention is inference-only");
-      GN_TRY(latent_attention(m, b, a, l, H, O));
+      if (train) GN_TRY(latent_attention_train(m, b.layers[l], *b.lws, l, H, tc ? Hh : nullptr, tc ? Hl : nullptr, B, T));
+      else GN_TRY(latent_attention(m, b, a, l, H, O));
     } else {
     // q, k, v projections as one GEMM against [c_q; c_k; c_v]
     Partials qkv_part;
@@ -289,9 +295,13 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
       GN_TRY(norm_launch(MID, Mn, tc ? Mh : nullptr, tc ? Ml : nullptr, rows, d, s));
     }
     if (m->moe()) {
-      GN_REQUIRE(!train, "routed experts are inference-only");
-      GN_TRY(moe_ffn(m, b, a, l, Mn, MID, XOUT));
-      if (l == L / 2) { GN_CUDA(cudaMemcpyAsync(b.BO, XOUT, sizeof(float) * rows * d, cudaMemcpyDeviceToDevice, s)); backout = b.BO; }
+      if (train) {
+        GN_TRY(moe_ffn_train(m, b.layers[l], *b.lws, l, Mn, tc ? Mh : nullptr, tc ? Ml : nullptr, MID, XOUT, rows));
+        if (l == L / 2) backout = XOUT;
+      } else {
+        GN_TRY(moe_ffn(m, b, a, l, Mn, MID, XOUT));
+        if (l == L / 2) { GN_CUDA(cudaMemcpyAsync(b.BO, XOUT, sizeof(float) * rows * d, cudaMemcpyDeviceToDevice, s)); backout = b.BO; }
+      }
       x_prev = XOUT;
       continue;
     }
@@ -380,6 +390,10 @@ int backward_core(gn_model* m, FwdBufs& b, BwdBufs& w, const int32_t* ids, int B
       GN_TRY(axpy_launch(w.DOUT, w.DFP, 0.0f, m->p(m->off_backout), -1.0f, 1, n, s));
       dout = w.DOUT;
     }
+    if (m->moe()) {
+      // ---- shared SwiGLU expert + routed experts (model/train.go:505-514,560-566, model/moe.go:203-267)
+      GN_TRY(moe_ffn_backward(m, sv, *b.lws, l, sv.M, dout, w.DM, rows, T));
+    } else {
     // ---- MLP backward (model/train.go:505-514)
     { GemmArgs g; g.A = dout; g.lda = d; g.a_trans = 1; g.B = sv.HID; g.ldb = 4 * d; g.b_hi = sv.Ph; g.b_lo = sv.Pl; g.C = m->g(o.mproj); g.ldc = 4 * d; g.M = d; g.N = 4 * d; g.K = (int)rows;
       g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
@@ -388,6 +402,7 @@ int backward_core(gn_model* m, FwdBufs& b, BwdBufs& w, const int32_t* ids, int B
     { GemmArgs g; g.A = w.DU; g.lda = 4 * d; g.a_trans = 1; g.B = sv.M; g.ldb = d; g.b_hi = sv.Mh; g.b_lo = sv.Ml; g.C = m->g(o.fc); g.ldc = d; g.M = 4 * d; g.N = d; g.K = (int)rows;
       g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
     { GemmArgs g; g.A = w.DU; g.lda = 4 * d; g.a_reuse = 1; g.B = m->p(o.fc); g.b_static = 1; g.ldb = d; g.C = w.DM; g.ldc = d; g.M = (int)rows; g.N = d; g.K = 4 * d; GN_TRY(gemm(m, g)); }
+    }
     GN_TRY(rmsnorm_backward_launch(w.DMID, sv.MID, w.DM, dout, rows, d, kNormEps, s));
     // ---- attention backward (model/train.go:198-427)
     { GemmArgs g; g.A = w.DMID; g.lda = d; g.a_trans = 1; g.B = sv.O; g.ldb = (int64_t)Hq * D; g.C = m->g(o.proj); g.ldc = (int64_t)Hq * D; g.M = d; g.N = Hq * D; g.K = (int)rows;
@@ -399,6 +414,10 @@ int backward_core(gn_model* m, FwdBufs& b, BwdBufs& w, const int32_t* ids, int B
     sh.o_bstride = (int64_t)T * Hq * D; sh.o_tstride = (int64_t)Hq * D; sh.window = m->windows[l]; sh.offset0 = 0; sh.tensor = m->ctx->gemm_kind == 1;
     GN_TRY(attention_backward_launch(sh, sv.QKV, sv.QKV + (int64_t)Hq * D, sv.QKV + (int64_t)(Hq + Hkv) * D, sv.O, w.DO, sv.LSE, nullptr, w.DQKV,
                                      w.DQKV + (int64_t)Hq * D, w.DQKV + (int64_t)(Hq + Hkv) * D, 0, w.DELTA, s));
+    if (m->mla()) {
+      // inverse rotation, the up-projections into the two latents and the four projections of H (model/mla.go:126-146)
+      GN_TRY(latent_attention_backward(m, sv, *b.lws, l, sv.H, w.DQKV, w.DH, B, T));
+    } else {
     QkvPostBwd qb;
     qb.dqkv = w.DQKV; qb.qk_rot = sv.QKROT; qb.ve_sig = sv.VESIG; qb.ve_table = o.has_ve ? m->p(o.ve) : nullptr; qb.ids = ids;
     qb.ve_grad = o.has_ve ? m->g(o.ve) : nullptr; qb.dpre = w.DPRE; qb.cosv = m->cosb.f(); qb.sinv = m->sinb.f();
@@ -408,6 +427,7 @@ int backward_core(gn_model* m, FwdBufs& b, BwdBufs& w, const int32_t* ids, int B
       g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
     { GemmArgs g; g.A = w.DQKV; g.lda = W; g.a_reuse = 1; g.B = m->p(o.qkv); g.b_static = 1; g.ldb = d; g.C = w.DH; g.ldc = d; g.M = (int)rows; g.N = d; g.K = W; GN_TRY(gemm(m, g)); }
     if (o.has_ve) GN_TRY(ve_gate_backward_launch(w.DPRE, sv.H, m->p(o.ve_gate), m->g(o.ve_gate), w.DH, rows, Hkv, d, s));
+    }
     GN_TRY(rmsnorm_backward_launch(w.DXIN, sv.Xin, w.DH, w.DMID, rows, d, kNormEps, s));
     // ---- residual mix (model/train_transformer.go:218-242)
     const float* prevX = (l == 0) ? b.X0 : b.layers[l - 1].XOUT;
@@ -536,7 +556,7 @@ int gn_model_destroy(gn_model* m) {
   gemm_invalidate_static();   // cached splits are keyed by addresses that are about to be freed
   DevBuf* bufs[] = {&m->P, &m->G, &m->cosb, &m->sinb, &m->sacc, &m->cache, &m->prev, &m->pos, &m->ctxlen, &m->ids_dev, &m->sampled, &m->seeds,
                     &m->out_tokens, &m->out_lengths, &m->done, &m->n_done, &m->sel, &m->part_acc, &m->part_ms, &m->step_dev, &m->infer.buf, &m->train.buf,
-                    &m->tgt_dev, &m->adv_dev, &m->rowloss, &m->loss_dev, &m->in_dev, &m->cache_lat, &m->cache_rope, &m->opt_mom, &m->opt_second,
+                    &m->tgt_dev, &m->adv_dev, &m->rowloss, &m->loss_dev, &m->in_dev, &m->lat_ws, &m->cache_lat, &m->cache_rope, &m->opt_mom, &m->opt_second,
                     &m->opt_ws};
   for (DevBuf* b : bufs) b->release();
   for (int i = 0; i < 4; ++i) if (m->ev[i]) cudaEventDestroy(m->ev[i]);
@@ -636,7 +656,6 @@ int gn_model_forward(gn_model* m, const int32_t* ids, int B, int T, float* logit
 int gn_model_optimizer_init(gn_model* m, const gn_optimizer_config* cfg) {
   GN_TRY(enter(m));
   GN_REQUIRE(cfg, "gn_model_optimizer_init: null config");
-  if (m->moe() || m->mla()) { set_error("the optimizer step covers the dense preset only"); return GN_ERR_UNSUPPORTED; }
   m->opt_cfg = *cfg; m->opt_steps = 0;
   GN_TRY(m->opt_mom.ensure(sizeof(float) * m->total)); GN_TRY(m->opt_second.ensure(sizeof(float) * m->total));
   GN_CUDA(cudaMemsetAsync(m->opt_mom.p, 0, sizeof(float) * m->total, m->s()));
@@ -645,8 +664,9 @@ int gn_model_optimizer_init(gn_model* m, const gn_optimizer_config* cfg) {
   for (const ParamInfo& pi : m->params) {
     const bool sink = pi.name == "lm_head.weight" || pi.name == "transformer.wte.weight" || pi.name.rfind("value_embeds.", 0) == 0;
     const bool scalar = pi.name.rfind("transformer.h.", 0) != 0 && !sink;
+    const bool experts = pi.name.find(".moe.experts.") != std::string::npos;   // per-expert views (model/optimizer.go:87-93)
     if (sink) ws = std::max(ws, sinkhorn_workspace_bytes(pi.rows, pi.cols));
-    else if (!scalar) ws = std::max(ws, muon_workspace_bytes(pi.rows, pi.cols));
+    else if (!scalar) ws = std::max(ws, muon_workspace_bytes(experts ? pi.rows / m->E : pi.rows, pi.cols));
   }
   GN_TRY(m->opt_ws.ensure(ws));
   m->opt_ready = true;
@@ -705,6 +725,15 @@ int optimizer_run(gn_model* m, int shard, int shard_count) {
     else if (pi.name == "resid_lambdas") GN_TRY(adam(c.scalar_lr * 0.01f, 0.8f, 0.95f, 0.05f));
     else if (pi.name == "x0_lambdas") GN_TRY(adam(c.scalar_lr, 0.96f, 0.95f, 0.0f));
     else if (pi.name == "smear_gate.weight" || pi.name == "smear_lambda" || pi.name == "backout_lambda") GN_TRY(adam(0.2f, 0.8f, 0.95f, 0.0f));
+    else if (pi.name.size() > 11 && pi.name.compare(pi.name.size() - 11, 11, "router_bias") == 0) continue;   // updated by load, never optimised (model/optimizer.go:83-86)
+    else if (pi.name.find(".moe.experts.") != std::string::npos) {
+      // packed expert weights: one Muon matrix per expert view (model/optimizer.go:87-93, model/moe.go:60-81)
+      const int er = pi.rows / m->E;
+      for (int e = 0; e < m->E; ++e) {
+        const int64_t off = (int64_t)e * er * pi.cols;
+        GN_TRY(muon_launch(p + off, g + off, mo + off, se + off, er, pi.cols, c.matrix_lr * c.lr_mult, 0.95f, 5, 0.9f, c.weight_decay, m->opt_ws.p, m->ctx->gemm_kind, s));
+      }
+    }
     else GN_TRY(muon_launch(p, g, mo, se, pi.rows, pi.cols, c.matrix_lr * c.lr_mult, 0.95f, 5, 0.9f, c.weight_decay, m->opt_ws.p, m->ctx->gemm_kind, s));
   }
   if (shard_count > 1) {
@@ -918,7 +947,6 @@ int gn_policy_gradient_step(gn_model* m, const int32_t* inputs, const int32_t* t
                             float* loss, float* nll_tap, float* dlogits_tap, float* logits_tap) {
   GN_TRY(enter_compute(m));
   GN_REQUIRE(inputs && targets && adv && loss, "gn_policy_gradient_step: null argument");
-  if (m->moe() || m->mla()) { set_error("the training pass covers the dense preset only; latent attention and routed experts are inference-only here"); return GN_ERR_UNSUPPORTED; }
   GN_REQUIRE(B > 0 && T > 1, "gn_policy_gradient_step: batch must be positive and seq > 1 (model/transformer.go:269-271)");
   GN_REQUIRE(T <= m->cfg.sequence_len, "sequence %d longer than sequence_len %d", T, m->cfg.sequence_len);
   GN_TRY(check_ids(inputs, (int64_t)B * T, m->V, false, "gn_policy_gradient_step: inputs"));
@@ -940,6 +968,13 @@ int gn_policy_gradient_step(gn_model* m, const int32_t* inputs, const int32_t* t
   const int64_t prow = (int64_t)rows_per_pass * T;
   GN_TRY(make_bufs(m, m->train, b, MODE_TRAIN, prow, prow, rows_per_pass, T, bwd_floats(m, prow, rows_per_pass, T), &extra));
   carve_bwd(m, extra, w, prow, rows_per_pass, T);
+  LatentWs lws;
+  if (m->mla() || m->moe()) {
+    GN_TRY(m->lat_ws.ensure(sizeof(float) * latent_ws_layout(m, nullptr, nullptr, prow, rows_per_pass)));
+    latent_ws_layout(m, m->lat_ws.f(), &lws, prow, rows_per_pass);
+    lws.total_sequences = B;
+    b.lws = &lws;
+  }
   float t_fwd = 0, t_loss = 0, t_bwd = 0;
   std::vector<float> nll_host;
   for (int b0 = 0; b0 < B; b0 += rows_per_pass) {

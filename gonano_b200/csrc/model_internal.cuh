@@ -62,10 +62,40 @@ struct LayerSaved {
   // tf32 hi/lo splits of H, M and HID written by their producers in the forward pass and read again by the
   // weight-gradient products (tensor-core path; null otherwise)
   float *Hh = nullptr, *Hl = nullptr, *Mh = nullptr, *Ml = nullptr, *Ph = nullptr, *Pl = nullptr;
+  // latent preset (model_latent_train.cu): the fused down / rotary projections of latent attention; the shared
+  // expert's [up | gate] and hidden rows; the router's softmax, selection, weights, expert-major positions and counts;
+  // the experts' gate / up / hidden / output rows
+  float *P1 = nullptr, *UG = nullptr, *SHH = nullptr, *SHHh = nullptr, *SHHl = nullptr, *PR = nullptr, *SELW = nullptr;
+  int32_t *SEL = nullptr, *POSI = nullptr, *CNT = nullptr;
+  float *GG = nullptr, *GU = nullptr, *GH = nullptr, *GHh = nullptr, *GHl = nullptr, *GO = nullptr;
+  std::vector<int32_t> host_counts;   // rows per expert, read back once in the forward pass
 };
+
+// Scratch of one training pass of the latent preset, shared by all layers.
+struct LatentWs {
+  float *QC = nullptr, *KC = nullptr, *DQC = nullptr, *DKC = nullptr, *DP1 = nullptr;
+  float *SHO = nullptr, *RL = nullptr, *GATH = nullptr, *GATHh = nullptr, *GATHl = nullptr;
+  float *DSHH = nullptr, *DUG = nullptr, *DMS = nullptr, *DMR = nullptr, *DGO = nullptr, *DGH = nullptr, *DGG = nullptr, *DGU = nullptr, *DGATH = nullptr;
+  double* GPROB = nullptr; float* GLOG = nullptr; int32_t* SEQCNT = nullptr;
+  int total_sequences = 0;   // sequences of the whole policy-gradient call (the balance loss is a mean over them)
+};
+constexpr float kMoEBalanceWeight = 1e-4f;   // defaultMoEBalanceWeight (model/config.go:133-135,176-186)
 
 }  // namespace gnm
 using namespace gnm;
+
+struct gn_model;
+namespace gnm {
+// model_latent.cu / model_latent_train.cu
+int moe_router_logits(gn_model* m, int l, const float* Mn, float* RL, int64_t rows);
+int moe_route_launch(const int32_t* sel, int64_t total, int E, int32_t* counts, int32_t* posi, cudaStream_t s);
+size_t latent_saved_layout(const gn_model* m, float* base, LayerSaved* s, int64_t rows);
+size_t latent_ws_layout(const gn_model* m, float* base, LatentWs* w, int64_t rows, int B);
+int latent_attention_train(gn_model* m, LayerSaved& sv, LatentWs& w, int l, const float* H, const float* Hh, const float* Hl, int B, int T);
+int latent_attention_backward(gn_model* m, LayerSaved& sv, LatentWs& w, int l, const float* H, const float* DQKV, float* DH, int B, int T);
+int moe_ffn_train(gn_model* m, LayerSaved& sv, LatentWs& w, int l, const float* Mn, const float* Mh, const float* Ml, const float* MID, float* XOUT, int64_t rows);
+int moe_ffn_backward(gn_model* m, LayerSaved& sv, LatentWs& w, int l, const float* Mn, const float* DOUT, float* DM, int64_t rows, int seq_len);
+}  // namespace gnm
 
 struct gn_model {
   gn_ctx* ctx = nullptr;
@@ -94,7 +124,7 @@ struct gn_model {
   bool opt_ready = false;
   DevBuf cache_lat, cache_rope;   // latent attention: [layer][row][max_seq][lat] and [layer][row][max_seq][Hkv*rope]
   Arena infer, train;
-  DevBuf tgt_dev, adv_dev, rowloss, loss_dev, in_dev;
+  DevBuf tgt_dev, adv_dev, rowloss, loss_dev, in_dev, lat_ws;
   std::map<std::string, float> phase_ms;
   cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
   bool weights_dirty = true;   // cached tensor-core operand splits of the parameters are stale
@@ -121,6 +151,7 @@ struct FwdBufs {
   // train only
   float *SIG, *FP;
   std::vector<LayerSaved> layers;
+  LatentWs* lws = nullptr;   // train, latent preset: the pass's scratch
   // latent attention (inference): fused down/rope projections, content queries, absorbed queries, attended latents
   float *P1 = nullptr, *QC = nullptr, *QF = nullptr, *AL = nullptr;
   // routed experts (inference)

@@ -350,6 +350,24 @@ int grid_for(int64_t n) { return (int)std::max<int64_t>(1, std::min<int64_t>((n 
 
 }  // namespace
 
+// Router affinities logits[r, e] = x[r] . W[e] in plain float32 (model/moe.go:123): the same kernel in inference and in
+// training, so that both route alike.
+int moe_router_logits(gn_model* m, int l, const float* Mn, float* RL, int64_t rows) {
+  const int d = m->d, E = m->E;
+  const LayerOffsets& o = m->lo[l];
+  cudaStream_t s = m->s();
+  if (d % 128 == 0 && d <= 4096) {
+    router_logits_kernel<<<ceil_div(rows, WPB), WPB * 32, 0, s>>>(RL, Mn, m->p(o.router), rows, d, E); GN_LAUNCH_CHECK();
+    return GN_OK;
+  }
+  GemmArgs g; g.A = Mn; g.lda = d; g.B = m->p(o.router); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = RL; g.ldc = E; g.M = (int)rows; g.N = E; g.K = d;
+  return gemm_dispatch(g, 0, s);   // E columns: the float32 kernel (routing must not depend on a split's rounding)
+}
+int moe_route_launch(const int32_t* sel, int64_t total, int E, int32_t* counts, int32_t* posi, cudaStream_t s) {
+  moe_route_kernel<<<1, 1024, 0, s>>>(sel, total, E, counts, posi); GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
 int latent_attention(gn_model* m, FwdBufs& b, const FwdArgs& a, int l, const float* H, float* O) {
   const int d = m->d, Hq = m->Hq, Hkv = m->Hkv, D = m->D, lat = m->lat, rope = m->rope, content = m->content;
   const int ratio = Hq / Hkv, hd = lat + rope;
@@ -408,14 +426,9 @@ int moe_ffn(gn_model* m, FwdBufs& b, const FwdArgs& a, int l, const float* Mn, c
   { GemmArgs g; g.A = b.SHH; g.lda = sh; g.B = m->p(o.mproj); g.b_static = 1; g.ldb = sh; g.b_trans = 1; g.C = b.SHO; g.ldc = d; g.M = (int)rows; g.N = d; g.K = sh;
     GN_TRY(gemm(m, g)); }
   // ---- router (model/moe.go:123-124): selection on logits + bias, weights = softmax(logits) of the selected
-  if (d % 128 == 0 && d <= 4096) {
-    router_logits_kernel<<<ceil_div(rows, WPB), WPB * 32, 0, s>>>(b.RL, Mn, m->p(o.router), rows, d, E); GN_LAUNCH_CHECK();
-  } else {
-    GemmArgs g; g.A = Mn; g.lda = d; g.B = m->p(o.router); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = b.RL; g.ldc = E; g.M = (int)rows; g.N = E; g.K = d;
-    GN_TRY(gemm_dispatch(g, 0, s));   // E columns: the float32 kernel (routing must not depend on a split's rounding)
-  }
+  GN_TRY(moe_router_logits(m, l, Mn, b.RL, rows));
   GN_TRY(moe_gate_topk_launch(b.RL, m->p(o.router_bias), b.PR, b.SEL, b.SELW, (int)rows, E, K, s));
-  moe_route_kernel<<<1, 1024, 0, s>>>(b.SEL, total, E, b.CNT, b.POSI); GN_LAUNCH_CHECK();
+  GN_TRY(moe_route_launch(b.SEL, total, E, b.CNT, b.POSI, s));
   moe_gather_kernel<<<ceil_div(total, WPB), WPB * 32, 0, s>>>(b.GATH, tc ? b.GATHh : nullptr, tc ? b.GATHl : nullptr, Mn, b.POSI, total, K, d); GN_LAUNCH_CHECK();
   // ---- experts: grouped products over the expert-major rows (model/moe.go:155-158), on the tensor cores when the
   //      expert shapes allow it (each 128-row tile of an expert is one CTA; rows past an expert's last are masked)

@@ -99,9 +99,57 @@ def test_graph_replayed_rollout_matches_eager(oracle, ctx):
     gm.close()
 
 
-def test_training_is_refused(oracle, ctx):
-    om, gm, cfg = make_pair(oracle, ctx, "latent-tiny")
-    ids = np.zeros((2, 6), np.int32)
-    with pytest.raises(Exception, match="inference-only"):
-        gm.policy_gradient_step(ids, ids, np.ones(2, np.float32), 6.0)
+@pytest.mark.parametrize("name,variant,std,B,T,rpp", [("latent-tiny", "latent", 0.15, 2, 8, 0), ("latent-tiny", "moe-only", 0.15, 3, 12, 2),
+                                                       ("latent-tiny", "mla-only", 0.15, 2, 16, 0), ("latent-small", "latent", 0.05, 2, 70, 0),
+                                                       ("latent-small", "latent", 0.05, 3, 40, 2)])
+def test_policy_gradient_step(oracle, ctx, name, variant, std, B, T, rpp):
+    """trainer.PolicyGradientStep through latent attention (un-absorbed training construction) and the routed experts
+    (with the sequence-level balance loss): logits, log-probs, loss, the gradient at the logits and every parameter
+    gradient against the oracle; the router correction bias gets no gradient."""
+    from parity import GRAD_REL, assert_gradients_close, close_elementwise
+    om, gm, cfg = make_pair(oracle, ctx, name, std=std, **VARIANTS[variant])
+    V = cfg["vocab_size"]
+    rng = np.random.default_rng(B * T + 1)
+    ids = rng.integers(0, V - 11, (B, T), dtype=np.int32)
+    ids[:, 1] = ids[:, 0]
+    tg = rng.integers(0, V, (B, T)).astype(np.int32)
+    tg[:, : T // 3] = -1
+    adv = rng.standard_normal(B).astype(np.float32)
+    om.zero_grad()
+    want_loss, want_nll, want_dl, want_lg = om.policy_gradient_step(ids, tg, adv, float(T + 1), taps=True)
+    gm.zero_grad()
+    loss, nll, dl, lg = gm.policy_gradient_step(ids, tg, adv, float(T + 1), rows_per_pass=rpp, taps=True)
+    assert rel_err(lg, want_lg) <= 1e-3
+    terms = np.abs(want_nll.reshape(B, T) * adv[:, None]) / float(T + 1)
+    assert abs(loss - want_loss) <= 1e-4 * float(terms.sum())
+    assert close_elementwise(nll, want_nll, 1e-4, 1e-5)
+    assert close_elementwise(dl, want_dl, GRAD_REL, 1e-6)
+    assert_gradients_close(gm, om)
+    for n in gm.names:
+        if n.endswith("router_bias"):
+            assert not np.any(gm.grad(n))
+    gm.close()
+
+
+def test_optimizer_step_of_a_latent_model(oracle, ctx):
+    """chat_rl's optimizer on a latent-preset model from identical gradients: Muon on every latent-attention matrix,
+    on the router and on each expert's view of the packed weights; the router correction bias stays put
+    (model/optimizer.go:25-36,83-93)."""
+    om, gm, cfg = make_pair(oracle, ctx, "latent-tiny", std=0.1)
+    oopt = oracle.Optimizer(om); gm.optimizer_init()
+    rng = np.random.default_rng(3)
+    before = {n: om.param(n).copy() for n in om.names}
+    for n in om.names:
+        g = (rng.standard_normal(om.param(n).size) * 0.01).astype(np.float32)
+        om.grad(n)[:] = g; gm.upload_grad(n, g)
+    oopt.step(); gm.optimizer_step()
+    for n in om.names:
+        got, want = gm.download(n), om.param(n)
+        if n.endswith("router_bias"):
+            assert np.array_equal(got, before[n]) and np.array_equal(want, before[n])
+            continue
+        upd = float(np.max(np.abs(want.astype(np.float64) - before[n])))
+        assert upd > 0, n
+        assert float(np.max(np.abs(got.astype(np.float64) - want))) <= 1e-4 * upd + float(np.max(np.abs(want))) * 2.0 ** -23, n
+        assert not np.any(gm.grad(n)), n
     gm.close()

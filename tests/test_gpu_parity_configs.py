@@ -8,7 +8,7 @@
   tokens, T = 1.0, top-k 50, reward 1 when the generated part contains id 7, advantage (r - mean) / (std + 1e-6),
   one optimizer step -- loss, every gradient and every updated parameter;
 * the latent preset at its own dimensions (d_model 1024, 8 heads, latent 256, 8 layers, 1 shared + 16 routed
-  experts of hidden 512, top-2, vocab 32768): forward logits and a short rollout.
+  experts of hidden 512, top-2, vocab 32768): forward logits, a short rollout and a policy-gradient step.
 
 Tolerances are the RL step's: logits 1e-3 of the largest logit; log-probs, loss, advantages and gradients 1e-4,
 element-wise in the reference's ``Close`` form (``tests/parity.py``) with the floor stated beside each check.
@@ -179,4 +179,20 @@ def test_latent_preset_at_its_own_dimensions(oracle, ctx):
     assert rel_err(gm.forward(ids), om.forward(ids)) <= 1e-3
     prompts = synthetic.prompts(1, 64, V, seed=6)
     teacher_forced_rollout_check(oracle, om, gm, V, prompts, 2, 4, np.array([5], np.uint64))
+    # the training pass (un-absorbed latent attention, routed experts with the balance loss): 2 rows x 40 tokens
+    rng = np.random.default_rng(9)
+    B, T = 2, 40
+    ids = rng.integers(0, V - 11, (B, T), dtype=np.int32)
+    tg = rng.integers(0, V, (B, T)).astype(np.int32)
+    tg[:, :12] = -1
+    adv = np.array([0.8, -1.1], np.float32)
+    om.zero_grad()
+    want_loss, want_nll, _, want_lg = om.policy_gradient_step(ids, tg, adv, float(T + 1), taps=True)
+    gm.zero_grad()
+    loss, nll, _, lg = gm.policy_gradient_step(ids, tg, adv, float(T + 1), taps=True)
+    assert rel_err(lg, want_lg) <= 1e-3
+    assert close_elementwise(nll, want_nll, 1e-4, 1e-5)
+    terms = np.abs(want_nll.reshape(B, T) * adv[:, None]) / float(T + 1)
+    assert abs(loss - want_loss) <= 1e-4 * float(terms.sum())
+    assert_gradients_close(gm, om)
     gm.close()
