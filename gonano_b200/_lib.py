@@ -36,6 +36,11 @@ class GnOptimizerConfig(C.Structure):
                 ("scalar_lr", C.c_float), ("lr_mult", C.c_float)]
 
 
+class GnGenerateOptions(C.Structure):
+    _fields_ = [("thinking", C.c_int32), ("thinking_budget", C.c_int32), ("forced", C.c_void_p), ("forced_stride", C.c_int32),
+                ("forced_counts", C.c_void_p)]
+
+
 class GnAttentionParams(C.Structure):
     _fields_ = [
         ("query", vp), ("key", vp), ("value", vp),
@@ -89,7 +94,14 @@ SIGNATURES = {
     "gn_model_checksum": (I, [vp, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "gn_model_forward": (I, [vp, vp, I, I, vp]),
     "gn_generate_batch": (I, [vp, vp, I, I, I, I, F, I, vp, vp, vp, vp, C.POINTER(I)]),
+    "gn_generate_batch_ex": (I, [vp, vp, I, I, I, I, F, I, vp, C.POINTER(GnGenerateOptions), vp, vp, vp, vp, C.POINTER(I)]),
+    "gn_rollout_begin": (I, [vp, vp, I, I, I, I, vp, C.POINTER(GnGenerateOptions)]),
+    "gn_rollout_logits": (I, [vp, C.POINTER(vp), C.POINTER(I), C.POINTER(I)]),
+    "gn_rollout_sample": (I, [vp, vp, F, I, vp, vp, C.POINTER(I)]),
+    "gn_rollout_force": (I, [vp, I, vp, I]), "gn_rollout_forward": (I, [vp, vp]), "gn_rollout_end": (I, [vp, vp, vp, vp]),
     "gn_policy_gradient_step": (I, [vp, vp, vp, vp, I, I, F, I, f32p, vp, vp, vp]),
+    "gn_model_kv_info": (I, [vp, C.POINTER(I), C.POINTER(I), C.POINTER(I)]), "gn_model_kv_alloc": (I, [vp, I, I, I]),
+    "gn_model_kv_read": (I, [vp, I, I, I, I, I, vp, L]), "gn_model_kv_write": (I, [vp, I, I, I, I, I, vp, L]),
     "gn_model_phase_ms": (I, [vp, C.c_char_p, f32p]),
     "gn_comm_unique_id": (I, [vp]), "gn_ctx_comm_init": (I, [vp, vp, I, I]), "gn_ctx_comm_destroy": (I, [vp]),
     "gn_model_grad_allreduce": (I, [vp]), "gn_ctx_allreduce_max_i64": (I, [vp, C.POINTER(C.c_int64)]),

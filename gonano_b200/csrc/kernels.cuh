@@ -90,8 +90,14 @@ int attention_decode_prefix_splits(int rows, int group, int Hq, int Hkv, int D, 
 // ctxlen[r] = pos[r] + 1.  done != null: the engine step (keep the token or finish the row on bos / aend).
 struct SampleTail {
   int32_t* pos = nullptr; int32_t* ctxlen = nullptr; int pos_base = 0; int advance = 0;
-  int32_t* out_tokens = nullptr; int32_t* out_lengths = nullptr; int32_t* done = nullptr; int32_t* n_done = nullptr;
+  int32_t* out_tokens = nullptr; int32_t* out_lengths = nullptr; int32_t* out_masks = nullptr; int32_t* done = nullptr; int32_t* n_done = nullptr;
   int max_tokens = 0, bos = -1, aend = -1;
+  // forced-token ring per row (inference/engine.go:262-273): a queued token overrides the sampled one (mask 0)
+  int32_t* forced_head = nullptr; int32_t* forced_len = nullptr; int32_t* forced_buf = nullptr; int forced_cap = 0;
+  // thinking trace (inference/engine.go:301-314): inside <|think_start|> ... <|think_end|> reasoning tokens are counted
+  // and, once `thinking_budget` of them have been emitted, <|think_end|> is queued
+  int32_t* in_think = nullptr; int32_t* think_count = nullptr; int thinking = 0, thinking_budget = 0, think_start = -1, think_end = -1;
+  int32_t* step_mask = nullptr;   // this step's mask per row (1 sampled, 0 forced)
 };
 int sample_launch(const float* logits, int rows, int vocab, int logits_row_div, const float* uniforms, const uint64_t* seeds_dev, int group,
                   const uint32_t* step_dev, uint32_t step_host, float temperature, int top_k, int32_t* out, cudaStream_t s,

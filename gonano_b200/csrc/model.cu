@@ -555,7 +555,7 @@ int gn_model_destroy(gn_model* m) {
   cudaStreamSynchronize(m->ctx->stream);
   gemm_invalidate_static();   // cached splits are keyed by addresses that are about to be freed
   DevBuf* bufs[] = {&m->P, &m->G, &m->cosb, &m->sinb, &m->sacc, &m->cache, &m->prev, &m->pos, &m->ctxlen, &m->ids_dev, &m->sampled, &m->seeds,
-                    &m->out_tokens, &m->out_lengths, &m->done, &m->n_done, &m->sel, &m->part_acc, &m->part_ms, &m->step_dev, &m->infer.buf, &m->train.buf,
+                    &m->out_tokens, &m->out_lengths, &m->out_masks, &m->engine_state, &m->done, &m->n_done, &m->sel, &m->part_acc, &m->part_ms, &m->step_dev, &m->infer.buf, &m->train.buf,
                     &m->tgt_dev, &m->adv_dev, &m->rowloss, &m->loss_dev, &m->in_dev, &m->lat_ws, &m->cache_lat, &m->cache_rope, &m->opt_mom, &m->opt_second,
                     &m->opt_ws};
   for (DevBuf* b : bufs) b->release();
@@ -796,32 +796,44 @@ int gn_model_optimizer_finish(gn_model* m) {
   return GN_OK;
 }
 
-int gn_generate_batch(gn_model* m, const int32_t* prompts, int P, int plen, int G, int max_tokens, float temperature, int top_k, const uint64_t* seeds,
-                      int32_t* out_tokens, int32_t* out_lengths, float* step_logits, int* steps_run) {
-  GN_TRY(enter_compute(m));
-  GN_REQUIRE(prompts && seeds && out_tokens && out_lengths, "gn_generate_batch: null argument");
-  GN_REQUIRE(P > 0 && plen > 0 && G > 0 && max_tokens > 0, "gn_generate_batch: sizes must be positive");
+// ---------------------------------------------------------------- rollout (inference/engine.go:112-369)
+namespace {
+
+constexpr int kForcedQueue = 64;   // forced tokens a row can hold at once (a tool result plus the closing tokens)
+
+// Prefill every prompt, replicate its cache over the group, and reset the engine's per-row state
+// (inference/engine.go:141-238).  Afterwards m->ro.logits holds the prompts' last-position logits [P, V].
+int rollout_begin(gn_model* m, const int32_t* prompts, int P, int plen, int G, int max_tokens, const uint64_t* seeds, const gn_generate_options* opt) {
+  GN_REQUIRE(prompts && seeds, "rollout: null argument");
+  GN_REQUIRE(P > 0 && plen > 0 && G > 0 && max_tokens > 0, "rollout: sizes must be positive");
   GN_REQUIRE(plen <= m->cfg.sequence_len, "prompt of %d tokens longer than sequence_len %d", plen, m->cfg.sequence_len);
   GN_REQUIRE((int64_t)plen + max_tokens <= (int64_t)m->cfg.sequence_len * 10, "context %d exceeds the rotary table", plen + max_tokens);
-  GN_TRY(check_ids(prompts, (int64_t)P * plen, m->V, false, "gn_generate_batch: prompts"));
+  GN_TRY(check_ids(prompts, (int64_t)P * plen, m->V, false, "rollout: prompts"));
   const int d = m->d, Hq = m->Hq, Hkv = m->Hkv, D = m->D, V = m->V, L = m->L;
   const int rows = P * G, max_seq = plen + max_tokens;
-  const int bos = V - 11, aend = V - 7;   // tokenizer/special.go:19-31
   cudaStream_t s = m->s();
-  // ---- state
+  Rollout& ro = m->ro;
+  ro = Rollout();
+  ro.P = P; ro.plen = plen; ro.G = G; ro.max_tokens = max_tokens; ro.rows = rows; ro.max_seq = max_seq;
+  if (opt) { ro.thinking = opt->thinking != 0 || opt->thinking_budget > 0; ro.thinking_budget = opt->thinking_budget; }
   if (m->mla()) {
     GN_TRY(m->cache_lat.ensure(sizeof(float) * (size_t)L * rows * max_seq * m->lat));
     GN_TRY(m->cache_rope.ensure(sizeof(float) * (size_t)L * rows * max_seq * Hkv * m->rope));
   } else {
     GN_TRY(m->cache.ensure(sizeof(float) * (size_t)L * 2 * rows * Hkv * max_seq * D));
   }
+  m->kv_rows = rows; m->kv_max_seq = max_seq;
   GN_TRY(m->prev.ensure(sizeof(float) * (size_t)rows * d));
   GN_TRY(m->pos.ensure(sizeof(int32_t) * rows)); GN_TRY(m->ctxlen.ensure(sizeof(int32_t) * rows));
   GN_TRY(m->ids_dev.ensure(sizeof(int32_t) * std::max<int64_t>((int64_t)P * plen, rows)));
   GN_TRY(m->sampled.ensure(sizeof(int32_t) * rows)); GN_TRY(m->seeds.ensure(sizeof(uint64_t) * P));
   GN_TRY(m->out_tokens.ensure(sizeof(int32_t) * (size_t)rows * max_tokens)); GN_TRY(m->out_lengths.ensure(sizeof(int32_t) * rows));
+  GN_TRY(m->out_masks.ensure(sizeof(int32_t) * (size_t)rows * max_tokens));
   GN_TRY(m->done.ensure(sizeof(int32_t) * rows)); GN_TRY(m->n_done.ensure(sizeof(int32_t)));
   GN_TRY(m->sel.ensure(sizeof(int32_t) * P));
+  // engine state per row: forced-token ring (head, length, tokens), thinking flag and count, this step's mask
+  GN_TRY(m->engine_state.ensure(sizeof(int32_t) * (size_t)rows * (5 + kForcedQueue)));
+  GN_CUDA(cudaMemsetAsync(m->engine_state.p, 0, sizeof(int32_t) * (size_t)rows * (5 + kForcedQueue), s));
   const bool share_prefix = G > 1;
   int splits = attention_decode_splits(rows, Hkv, max_seq) + (share_prefix ? attention_decode_prefix_splits(rows, G, Hq, Hkv, D, plen) : 0);
   GN_TRY(m->part_acc.ensure(sizeof(float) * (size_t)rows * Hq * splits * D)); GN_TRY(m->part_ms.ensure(sizeof(float) * (size_t)rows * Hq * splits * 2));
@@ -834,15 +846,30 @@ int gn_generate_batch(gn_model* m, const int32_t* prompts, int P, int plen, int 
   GN_CUDA(cudaMemsetAsync(m->out_lengths.p, 0, sizeof(int32_t) * rows, s));
   GN_CUDA(cudaMemsetAsync(m->done.p, 0, sizeof(int32_t) * rows, s));
   GN_CUDA(cudaMemsetAsync(m->n_done.p, 0, sizeof(int32_t), s));
-
+  // A prompt that already ends in <|think_start|> starts inside the trace (inference/engine.go:229-236)
+  bool primed = false;
+  if (ro.thinking) for (int p = 0; p < P; ++p) primed = primed || prompts[(size_t)p * plen + plen - 1] == V - 2;
+  if ((opt && opt->forced && opt->forced_counts) || primed) {   // tokens queued before the first step / primed traces
+    std::vector<int32_t> st((size_t)rows * (5 + kForcedQueue), 0);
+    if (ro.thinking) for (int r = 0; r < rows; ++r) st[(size_t)rows * 2 + r] = prompts[(size_t)(r / G) * plen + plen - 1] == V - 2 ? 1 : 0;
+    if (opt && opt->forced && opt->forced_counts)
+    for (int r = 0; r < rows; ++r) {
+      const int n = opt->forced_counts[r];
+      GN_REQUIRE(n >= 0 && n <= kForcedQueue && n <= opt->forced_stride, "rollout: %d forced tokens for row %d (at most %d)", n, r, kForcedQueue);
+      st[(size_t)rows * 1 + r] = n;
+      for (int i = 0; i < n; ++i) st[(size_t)rows * 5 + (size_t)r * kForcedQueue + i] = opt->forced[(size_t)r * opt->forced_stride + i];
+    }
+    GN_TRY(check_ids(st.data() + (size_t)rows * 5, (int64_t)rows * kForcedQueue, V, false, "rollout: forced tokens"));
+    GN_CUDA(cudaMemcpyAsync(m->engine_state.p, st.data(), sizeof(int32_t) * st.size(), cudaMemcpyHostToDevice, s));
+    GN_CUDA(cudaStreamSynchronize(s));
+  }
   // ---- prefill: all prompts in one batch; prompt p writes cache row p*G (engine.go:141-172)
   GN_CUDA(cudaEventRecord(m->ev[0], s));
-  FwdBufs b;
   {
     const int64_t prow = (int64_t)P * plen;
-    GN_TRY(make_bufs(m, m->infer, b, MODE_PREFILL, std::max<int64_t>(prow, rows), std::max(P, rows), P, plen, 0, nullptr));
+    GN_TRY(make_bufs(m, m->infer, ro.b, MODE_PREFILL, std::max<int64_t>(prow, rows), std::max(P, rows), P, plen, 0, nullptr));
     FwdArgs a; a.mode = MODE_PREFILL; a.ids = m->ids_dev.i(); a.B = P; a.T = plen; a.cache_rows = rows; a.cache_row_mul = G; a.max_seq = max_seq;
-    GN_TRY(forward_core(m, b, a));
+    GN_TRY(forward_core(m, ro.b, a));
   }
   // replicate each prompt's cache over its group (engine.go:194-209, kvcache.go:383-448)
   if (m->mla()) {
@@ -855,44 +882,73 @@ int gn_generate_batch(gn_model* m, const int32_t* prompts, int P, int plen, int 
   }
   GN_TRY(fill_i32_launch(m->pos.i(), plen, rows, s));
   GN_CUDA(cudaEventRecord(m->ev[1], s));
+  ro.logits_row_div = G;   // every row of a group samples from its prompt's last-position logits (engine.go:182-191)
+  ro.active = true;
+  return GN_OK;
+}
 
+// The sampler's row CTAs also do the engine's bookkeeping: see SampleTail.
+SampleTail rollout_tail(gn_model* m) {
+  const Rollout& ro = m->ro;
+  const int V = m->V;
+  int32_t* st = m->engine_state.i();
+  SampleTail t;
+  t.pos = m->pos.i(); t.ctxlen = m->ctxlen.i(); t.pos_base = ro.plen; t.advance = ro.generated > 0 ? 1 : 0;
+  t.out_tokens = m->out_tokens.i(); t.out_lengths = m->out_lengths.i(); t.out_masks = m->out_masks.i(); t.done = m->done.i(); t.n_done = m->n_done.i();
+  t.max_tokens = ro.max_tokens; t.bos = V - 11; t.aend = V - 7;   // tokenizer/special.go:19-31
+  t.forced_head = st; t.forced_len = st + ro.rows; t.in_think = st + 2 * (size_t)ro.rows; t.think_count = st + 3 * (size_t)ro.rows; t.step_mask = st + 4 * (size_t)ro.rows;
+  t.forced_buf = st + 5 * (size_t)ro.rows; t.forced_cap = kForcedQueue;
+  t.thinking = ro.thinking ? 1 : 0; t.thinking_budget = ro.thinking_budget; t.think_start = V - 2; t.think_end = V - 1;
+  return t;
+}
+// One sampling step from `logits` (null: the model's own) with the engine's state machine (engine.go:256-314).
+int rollout_sample(gn_model* m, const float* logits, float temperature, int top_k) {
+  Rollout& ro = m->ro;
+  SampleTail tail = rollout_tail(m);
+  GN_TRY(sample_launch(logits ? logits : ro.b.LOGITS, ro.rows, m->V, ro.logits_row_div, nullptr, (const uint64_t*)m->seeds.p, ro.G, nullptr, 0, temperature, top_k,
+                       m->sampled.i(), m->s(), &tail));
+  return GN_OK;
+}
+// Forward the current token column through the decode cache (engine.go:321-324).
+int rollout_forward(gn_model* m) {
+  Rollout& ro = m->ro;
+  FwdArgs a; a.mode = MODE_DECODE; a.ids = m->sampled.i(); a.B = ro.rows; a.T = 1; a.cache_rows = ro.rows; a.cache_row_mul = 1; a.max_seq = ro.max_seq;
+  if (ro.G > 1) { a.group = ro.G; a.prefix_len = ro.plen; }
+  return forward_core(m, ro.b, a);
+}
+
+}  // namespace
+
+int gn_generate_batch_ex(gn_model* m, const int32_t* prompts, int P, int plen, int G, int max_tokens, float temperature, int top_k, const uint64_t* seeds,
+                         const gn_generate_options* opt, int32_t* out_tokens, int32_t* out_lengths, int32_t* out_masks, float* step_logits, int* steps_run) {
+  GN_TRY(enter_compute(m));
+  GN_REQUIRE(out_tokens && out_lengths, "gn_generate_batch: null argument");
+  GN_TRY(rollout_begin(m, prompts, P, plen, G, max_tokens, seeds, opt));
+  Rollout& ro = m->ro;
+  const int rows = ro.rows, V = m->V;
+  cudaStream_t s = m->s();
   // ---- decode loop (engine.go:241-325)
-  // One iteration = forward the sampled column, then sample the next one.  The sequence of
-  // launches is identical from step to step (positions, the step counter and the sampled ids
-  // live in device memory), so after two eager iterations it is captured once into a CUDA graph
-  // and replayed: a decode step is ~150 small launches, and at small batch the launch gaps
-  // otherwise rival the kernels.  With the per-step logits tap the loop stays eager.
+  // One iteration = forward the sampled column, then sample the next one.  The sequence of launches is identical from
+  // step to step (positions and the engine state live in device memory), so after two eager iterations it is captured
+  // once into a CUDA graph and replayed.  With the per-step logits tap the loop stays eager.
   std::vector<float> host_logits;
-  int generated = 0;
   int32_t n_done_host = 0;
   auto tap = [&](int div) -> int {
     if (!step_logits) return GN_OK;
     int lr = rows / div;
     host_logits.resize((size_t)lr * V);
-    GN_CUDA(cudaMemcpyAsync(host_logits.data(), b.LOGITS, sizeof(float) * (size_t)lr * V, cudaMemcpyDeviceToHost, s));
+    GN_CUDA(cudaMemcpyAsync(host_logits.data(), ro.b.LOGITS, sizeof(float) * (size_t)lr * V, cudaMemcpyDeviceToHost, s));
     GN_CUDA(cudaStreamSynchronize(s));
-    float* dst = step_logits + (size_t)generated * rows * V;
+    float* dst = step_logits + (size_t)ro.generated * rows * V;
     for (int r = 0; r < rows; ++r) std::memcpy(dst + (size_t)r * V, host_logits.data() + (size_t)(r / div) * V, sizeof(float) * V);
     return GN_OK;
   };
-  // The sampler's row CTAs also do the engine's bookkeeping (position, context length, keep-or-finish): see SampleTail.
-  SampleTail tail;
-  tail.pos = m->pos.i(); tail.ctxlen = m->ctxlen.i(); tail.pos_base = plen; tail.advance = 0;
-  tail.out_tokens = m->out_tokens.i(); tail.out_lengths = m->out_lengths.i(); tail.done = m->done.i(); tail.n_done = m->n_done.i();
-  tail.max_tokens = max_tokens; tail.bos = bos; tail.aend = aend;
-  // first column: every row of a group samples from its prompt's last-position logits (engine.go:182-191)
   GN_TRY(tap(G));
-  GN_TRY(sample_launch(b.LOGITS, rows, V, G, nullptr, (const uint64_t*)m->seeds.p, G, nullptr, 0, temperature, top_k, m->sampled.i(), s, &tail));
-  ++generated;
-  tail.advance = 1;   // from here on a sampling step follows a forward of the previous token
-  auto forward_step = [&]() -> int {
-    FwdArgs a; a.mode = MODE_DECODE; a.ids = m->sampled.i(); a.B = rows; a.T = 1; a.cache_rows = rows; a.cache_row_mul = 1; a.max_seq = max_seq;
-    if (share_prefix) { a.group = G; a.prefix_len = plen; }
-    return forward_core(m, b, a);                       // forward the sampled column (engine.go:321-324)
-  };
+  GN_TRY(rollout_sample(m, nullptr, temperature, top_k));
+  ++ro.generated; ro.logits_row_div = 1;
   auto body = [&]() -> int {
-    GN_TRY(forward_step());
-    GN_TRY(sample_launch(b.LOGITS, rows, V, 1, nullptr, (const uint64_t*)m->seeds.p, G, nullptr, 0, temperature, top_k, m->sampled.i(), s, &tail));
+    GN_TRY(rollout_forward(m));
+    GN_TRY(rollout_sample(m, nullptr, temperature, top_k));
     return GN_OK;
   };
   cudaGraph_t graph = nullptr;
@@ -901,46 +957,138 @@ int gn_generate_batch(gn_model* m, const int32_t* prompts, int P, int plen, int 
   const bool use_graph = !step_logits && m->ctx->use_graphs;
   int status = GN_OK;
   int eager_done = 0;
-  while (generated < max_tokens) {
-    if (generated % 16 == 0 || step_logits) {  // every row finished: stop early (engine.go:245-254)
-      GN_CUDA(cudaMemcpyAsync(&n_done_host, m->n_done.p, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
-      GN_CUDA(cudaStreamSynchronize(s));
+  auto drop_graph = [&]() { if (exec) cudaGraphExecDestroy(exec); if (graph) cudaGraphDestroy(graph); exec = nullptr; graph = nullptr; };
+  while (ro.generated < max_tokens) {
+    if (ro.generated % 16 == 0 || step_logits) {  // every row finished: stop early (engine.go:245-254)
+      if ((status = cudaMemcpyAsync(&n_done_host, m->n_done.p, sizeof(int32_t), cudaMemcpyDeviceToHost, s) != cudaSuccess ? GN_ERR_CUDA : GN_OK) != GN_OK) break;
+      if (cudaStreamSynchronize(s) != cudaSuccess) { status = GN_ERR_CUDA; break; }
       if (n_done_host >= rows) break;
     }
     if (step_logits) {
       // the tap wants the logits each sampling step saw: forward first, copy, then sample
-      GN_TRY(forward_step());
-      GN_TRY(tap(1));
-      GN_TRY(sample_launch(b.LOGITS, rows, V, 1, nullptr, (const uint64_t*)m->seeds.p, G, nullptr, 0, temperature, top_k, m->sampled.i(), s, &tail));
+      if ((status = rollout_forward(m)) != GN_OK) break;
+      if ((status = tap(1)) != GN_OK) break;
+      if ((status = rollout_sample(m, nullptr, temperature, top_k)) != GN_OK) break;
     } else if (!use_graph || eager_done < 2) {
-      GN_TRY(body());       // eager: also sizes every scratch buffer before the capture
+      if ((status = body()) != GN_OK) break;       // eager: also sizes every scratch buffer before the capture
       ++eager_done;
     } else {
       if (!exec) {
-        GN_CUDA(cudaStreamSynchronize(s));
-        GN_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+        if (cudaStreamSynchronize(s) != cudaSuccess || cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) != cudaSuccess) { status = GN_ERR_CUDA; break; }
         status = body();
         cudaError_t ce = cudaStreamEndCapture(s, &graph);
-        if (status != GN_OK) { if (graph) cudaGraphDestroy(graph); return status; }
-        if (ce != cudaSuccess) { set_error("decode graph capture failed: %s", cudaGetErrorString(ce)); return GN_ERR_CUDA; }
-        GN_CUDA(cudaGraphGetNodes(graph, nullptr, &graph_nodes));
-        GN_CUDA(cudaGraphInstantiate(&exec, graph, 0));
+        if (status != GN_OK) break;
+        if (ce != cudaSuccess) { set_error("decode graph capture failed: %s", cudaGetErrorString(ce)); status = GN_ERR_CUDA; break; }
+        if (cudaGraphGetNodes(graph, nullptr, &graph_nodes) != cudaSuccess || cudaGraphInstantiate(&exec, graph, 0) != cudaSuccess) {
+          set_error("decode graph instantiation failed"); status = GN_ERR_CUDA; break;
+        }
       }
-      GN_CUDA(cudaGraphLaunch(exec, s));
+      if (cudaGraphLaunch(exec, s) != cudaSuccess) { set_error("decode graph launch failed"); status = GN_ERR_CUDA; break; }
       count_launches((int64_t)graph_nodes);
     }
-    ++generated;
+    ++ro.generated;
   }
-  if (exec) { GN_CUDA(cudaStreamSynchronize(s)); cudaGraphExecDestroy(exec); cudaGraphDestroy(graph); }
+  if (exec || graph) { cudaStreamSynchronize(s); drop_graph(); }   // also on the error paths
+  if (status != GN_OK) { ro.active = false; if (status == GN_ERR_CUDA && !*get_error()) set_error("CUDA error in the decode loop"); return status; }
   GN_CUDA(cudaEventRecord(m->ev[2], s));
   GN_CUDA(cudaMemcpyAsync(out_tokens, m->out_tokens.p, sizeof(int32_t) * (size_t)rows * max_tokens, cudaMemcpyDeviceToHost, s));
   GN_CUDA(cudaMemcpyAsync(out_lengths, m->out_lengths.p, sizeof(int32_t) * rows, cudaMemcpyDeviceToHost, s));
+  if (out_masks) GN_CUDA(cudaMemcpyAsync(out_masks, m->out_masks.p, sizeof(int32_t) * (size_t)rows * max_tokens, cudaMemcpyDeviceToHost, s));
   GN_CUDA(cudaStreamSynchronize(s));
   float ms = 0;
   GN_CUDA(cudaEventElapsedTime(&ms, m->ev[0], m->ev[1])); m->phase_ms["prefill"] = ms;
   GN_CUDA(cudaEventElapsedTime(&ms, m->ev[1], m->ev[2])); m->phase_ms["decode"] = ms;
-  if (steps_run) *steps_run = generated;
+  if (steps_run) *steps_run = ro.generated;
+  ro.active = false;
   return gemm_check_error(s);
+}
+
+int gn_generate_batch(gn_model* m, const int32_t* prompts, int P, int plen, int G, int max_tokens, float temperature, int top_k, const uint64_t* seeds,
+                      int32_t* out_tokens, int32_t* out_lengths, float* step_logits, int* steps_run) {
+  return gn_generate_batch_ex(m, prompts, P, plen, G, max_tokens, temperature, top_k, seeds, nullptr, out_tokens, out_lengths, nullptr, step_logits, steps_run);
+}
+
+// ---- the same engine one step at a time, for hosts that interleave their own logic between steps: tool calls that
+//      need the tokenizer (inference/engine.go:284-300), ensembles that blend several models' logits before sampling
+//      (inference/ensemble.go:104-243).  Every call returns with the stream idle.
+int gn_rollout_begin(gn_model* m, const int32_t* prompts, int P, int plen, int G, int max_tokens, const uint64_t* seeds, const gn_generate_options* opt) {
+  GN_TRY(enter_compute(m));
+  GN_TRY(rollout_begin(m, prompts, P, plen, G, max_tokens, seeds, opt));
+  GN_CUDA(cudaStreamSynchronize(m->s()));
+  return gemm_check_error(m->s());
+}
+int gn_rollout_logits(gn_model* m, float** device_ptr, int* logit_rows, int* row_div) {
+  GN_REQUIRE(m && m->ro.active && device_ptr, "gn_rollout_logits: no rollout in progress");
+  *device_ptr = m->ro.b.LOGITS;
+  if (logit_rows) *logit_rows = m->ro.rows / m->ro.logits_row_div;
+  if (row_div) *row_div = m->ro.logits_row_div;
+  return GN_OK;
+}
+int gn_rollout_sample(gn_model* m, const float* logits_device, float temperature, int top_k, int32_t* column, int32_t* mask, int* all_done) {
+  GN_TRY(enter(m));
+  GN_REQUIRE(m->ro.active, "gn_rollout_sample: no rollout in progress");
+  Rollout& ro = m->ro;
+  cudaStream_t s = m->s();
+  GN_REQUIRE(ro.generated < ro.max_tokens, "gn_rollout_sample: the rollout already has its %d tokens", ro.max_tokens);
+  GN_TRY(rollout_sample(m, logits_device, temperature, top_k));
+  ++ro.generated; ro.logits_row_div = 1;
+  if (column) GN_CUDA(cudaMemcpyAsync(column, m->sampled.p, sizeof(int32_t) * ro.rows, cudaMemcpyDeviceToHost, s));
+  if (mask) GN_CUDA(cudaMemcpyAsync(mask, m->engine_state.i() + 4 * (size_t)ro.rows, sizeof(int32_t) * ro.rows, cudaMemcpyDeviceToHost, s));
+  int32_t n_done = 0;
+  GN_CUDA(cudaMemcpyAsync(&n_done, m->n_done.p, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+  GN_CUDA(cudaStreamSynchronize(s));
+  if (all_done) *all_done = n_done >= ro.rows ? 1 : 0;
+  return GN_OK;
+}
+int gn_rollout_force(gn_model* m, int row, const int32_t* tokens, int n) {
+  GN_TRY(enter(m));
+  GN_REQUIRE(m->ro.active && tokens && n >= 0, "gn_rollout_force: no rollout in progress or null tokens");
+  Rollout& ro = m->ro;
+  GN_REQUIRE(row >= 0 && row < ro.rows, "gn_rollout_force: row %d out of range", row);
+  GN_TRY(check_ids(tokens, n, m->V, false, "gn_rollout_force: tokens"));
+  cudaStream_t s = m->s();
+  int32_t* st = m->engine_state.i();
+  int32_t head = 0, len = 0;
+  GN_CUDA(cudaMemcpyAsync(&head, st + row, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+  GN_CUDA(cudaMemcpyAsync(&len, st + ro.rows + row, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+  GN_CUDA(cudaStreamSynchronize(s));
+  GN_REQUIRE(len + n <= kForcedQueue, "gn_rollout_force: row %d would hold %d forced tokens (at most %d)", row, len + n, kForcedQueue);
+  for (int i = 0; i < n; ++i) {
+    const int slot = (head + len + i) % kForcedQueue;
+    GN_CUDA(cudaMemcpyAsync(st + 5 * (size_t)ro.rows + (size_t)row * kForcedQueue + slot, tokens + i, sizeof(int32_t), cudaMemcpyHostToDevice, s));
+  }
+  len += n;
+  GN_CUDA(cudaMemcpyAsync(st + ro.rows + row, &len, sizeof(int32_t), cudaMemcpyHostToDevice, s));
+  GN_CUDA(cudaStreamSynchronize(s));
+  return GN_OK;
+}
+int gn_rollout_forward(gn_model* m, const int32_t* column) {
+  GN_TRY(enter_compute(m));
+  GN_REQUIRE(m->ro.active, "gn_rollout_forward: no rollout in progress");
+  Rollout& ro = m->ro;
+  cudaStream_t s = m->s();
+  if (column) {   // a column sampled elsewhere (an ensemble member follows the member that sampled)
+    GN_TRY(check_ids(column, ro.rows, m->V, false, "gn_rollout_forward: column"));
+    GN_CUDA(cudaMemcpyAsync(m->sampled.p, column, sizeof(int32_t) * ro.rows, cudaMemcpyHostToDevice, s));
+    if (ro.follower_steps++ > 0) GN_TRY(add_i32_launch(m->pos.i(), 1, ro.rows, s));   // a follower advances its own positions
+    GN_TRY(ctx_from_pos_launch(m->pos.i(), m->ctxlen.i(), ro.rows, s));
+  }
+  GN_TRY(rollout_forward(m));
+  GN_CUDA(cudaStreamSynchronize(s));
+  ro.logits_row_div = 1;
+  return gemm_check_error(s);
+}
+int gn_rollout_end(gn_model* m, int32_t* out_tokens, int32_t* out_lengths, int32_t* out_masks) {
+  GN_TRY(enter(m));
+  GN_REQUIRE(m->ro.active, "gn_rollout_end: no rollout in progress");
+  Rollout& ro = m->ro;
+  cudaStream_t s = m->s();
+  if (out_tokens) GN_CUDA(cudaMemcpyAsync(out_tokens, m->out_tokens.p, sizeof(int32_t) * (size_t)ro.rows * ro.max_tokens, cudaMemcpyDeviceToHost, s));
+  if (out_lengths) GN_CUDA(cudaMemcpyAsync(out_lengths, m->out_lengths.p, sizeof(int32_t) * ro.rows, cudaMemcpyDeviceToHost, s));
+  if (out_masks) GN_CUDA(cudaMemcpyAsync(out_masks, m->out_masks.p, sizeof(int32_t) * (size_t)ro.rows * ro.max_tokens, cudaMemcpyDeviceToHost, s));
+  GN_CUDA(cudaStreamSynchronize(s));
+  ro.active = false;
+  return GN_OK;
 }
 
 int gn_policy_gradient_step(gn_model* m, const int32_t* inputs, const int32_t* targets, const float* adv, int B, int T, float norm, int rows_per_pass,
@@ -1019,6 +1167,78 @@ int gn_policy_gradient_step(gn_model* m, const int32_t* inputs, const int32_t* t
   *loss = (float)loss_host;
   m->phase_ms["train_forward"] = t_fwd; m->phase_ms["loss"] = t_loss; m->phase_ms["train_backward"] = t_bwd;
   return gemm_check_error(s);
+}
+
+// ---------------------------------------------------------------- KV cache access (wire format support)
+namespace {
+// Address and float count of one slice of the cache: kind 0 / 1 = key / value of (layer, row, head), 2 = latent of
+// (layer, row), 3 = rotary keys of (layer, row), 4 = previous embedding of row.  `positions` cached positions.
+int kv_slice(gn_model* m, int layer, int kind, int row, int head, int positions, float** ptr, int64_t* n) {
+  GN_REQUIRE(m->kv_rows > 0, "no KV cache: run gn_generate_batch or gn_model_kv_alloc first");
+  GN_REQUIRE(row >= 0 && row < m->kv_rows && positions >= 0 && positions <= m->kv_max_seq, "KV slice: row %d / positions %d out of range", row, positions);
+  const int64_t S = m->kv_max_seq;
+  if (kind == 4) { *ptr = m->prev.f() + (int64_t)row * m->d; *n = m->d; return GN_OK; }
+  GN_REQUIRE(layer >= 0 && layer < m->L, "KV slice: layer %d out of range", layer);
+  if (kind == 0 || kind == 1) {
+    GN_REQUIRE(!m->mla(), "a latent-attention cache holds no per-head keys or values");
+    GN_REQUIRE(head >= 0 && head < m->Hkv, "KV slice: head %d out of range", head);
+    const int64_t layer_stride = (int64_t)m->kv_rows * m->Hkv * S * m->D;
+    *ptr = m->cache.f() + (int64_t)(2 * layer + kind) * layer_stride + ((int64_t)row * m->Hkv + head) * S * m->D;
+    *n = (int64_t)positions * m->D;
+    return GN_OK;
+  }
+  GN_REQUIRE(m->mla() && (kind == 2 || kind == 3), "KV slice: kind %d not available for this model", kind);
+  if (kind == 2) { *ptr = m->cache_lat.f() + ((int64_t)layer * m->kv_rows + row) * S * m->lat; *n = (int64_t)positions * m->lat; }
+  else { const int rw = m->Hkv * m->rope; *ptr = m->cache_rope.f() + ((int64_t)layer * m->kv_rows + row) * S * rw; *n = (int64_t)positions * rw; }
+  return GN_OK;
+}
+}  // namespace
+
+int gn_model_kv_info(gn_model* m, int* rows, int* max_seq, int* position) {
+  GN_TRY(enter(m));
+  if (rows) *rows = m->kv_rows;
+  if (max_seq) *max_seq = m->kv_max_seq;
+  if (position) {
+    int32_t p = 0;
+    if (m->kv_rows > 0) { GN_CUDA(cudaMemcpyAsync(&p, m->pos.p, sizeof(int32_t), cudaMemcpyDeviceToHost, m->s())); GN_CUDA(cudaStreamSynchronize(m->s())); }
+    *position = p;
+  }
+  return GN_OK;
+}
+int gn_model_kv_alloc(gn_model* m, int rows, int max_seq, int position) {
+  GN_TRY(enter(m));
+  GN_REQUIRE(rows > 0 && max_seq > 0 && position >= 0 && position <= max_seq, "gn_model_kv_alloc: bad geometry");
+  if (m->mla()) {
+    GN_TRY(m->cache_lat.ensure(sizeof(float) * (size_t)m->L * rows * max_seq * m->lat));
+    GN_TRY(m->cache_rope.ensure(sizeof(float) * (size_t)m->L * rows * max_seq * m->Hkv * m->rope));
+  } else {
+    GN_TRY(m->cache.ensure(sizeof(float) * (size_t)m->L * 2 * rows * m->Hkv * max_seq * m->D));
+  }
+  GN_TRY(m->prev.ensure(sizeof(float) * (size_t)rows * m->d));
+  GN_TRY(m->pos.ensure(sizeof(int32_t) * rows)); GN_TRY(m->ctxlen.ensure(sizeof(int32_t) * rows));
+  m->kv_rows = rows; m->kv_max_seq = max_seq;
+  GN_TRY(fill_i32_launch(m->pos.i(), position, rows, m->s()));
+  GN_TRY(fill_i32_launch(m->ctxlen.i(), position + 1, rows, m->s()));
+  GN_CUDA(cudaStreamSynchronize(m->s()));
+  return GN_OK;
+}
+int gn_model_kv_read(gn_model* m, int layer, int kind, int row, int head, int positions, float* host, int64_t n) {
+  GN_TRY(enter(m));
+  GN_REQUIRE(host, "gn_model_kv_read: null buffer");
+  float* p = nullptr; int64_t want = 0;
+  GN_TRY(kv_slice(m, layer, kind, row, head, positions, &p, &want));
+  GN_REQUIRE(n == want, "gn_model_kv_read: the slice has %lld floats, got room for %lld", (long long)want, (long long)n);
+  if (n > 0) { GN_CUDA(cudaMemcpyAsync(host, p, sizeof(float) * n, cudaMemcpyDeviceToHost, m->s())); GN_CUDA(cudaStreamSynchronize(m->s())); }
+  return GN_OK;
+}
+int gn_model_kv_write(gn_model* m, int layer, int kind, int row, int head, int positions, const float* host, int64_t n) {
+  GN_TRY(enter(m));
+  GN_REQUIRE(host, "gn_model_kv_write: null buffer");
+  float* p = nullptr; int64_t want = 0;
+  GN_TRY(kv_slice(m, layer, kind, row, head, positions, &p, &want));
+  GN_REQUIRE(n == want, "gn_model_kv_write: the slice has %lld floats, got %lld", (long long)want, (long long)n);
+  if (n > 0) { GN_CUDA(cudaMemcpyAsync(p, host, sizeof(float) * n, cudaMemcpyHostToDevice, m->s())); GN_CUDA(cudaStreamSynchronize(m->s())); }
+  return GN_OK;
 }
 
 int gn_model_phase_ms(gn_model* m, const char* phase, float* ms) {

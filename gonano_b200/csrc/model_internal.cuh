@@ -84,6 +84,46 @@ constexpr float kMoEBalanceWeight = 1e-4f;   // defaultMoEBalanceWeight (model/c
 }  // namespace gnm
 using namespace gnm;
 
+namespace gnm {
+enum Mode { MODE_PLAIN, MODE_PREFILL, MODE_DECODE, MODE_TRAIN };
+
+struct FwdBufs {
+  float *E, *X0, *Xa, *Xb, *H, *QKV, *O, *M, *HID, *BO, *Y, *LOGITS;
+  float *S1h, *S1l, *S4h, *S4l;   // producer-written tf32 splits: one [rows, d] pair and one [rows, 4d] pair, reused by every layer
+  // train only
+  float *SIG, *FP;
+  std::vector<LayerSaved> layers;
+  LatentWs* lws = nullptr;   // train, latent preset: the pass's scratch
+  // latent attention (inference): fused down/rope projections, content queries, absorbed queries, attended latents
+  float *P1 = nullptr, *QC = nullptr, *QF = nullptr, *AL = nullptr;
+  // routed experts (inference)
+  float *UG = nullptr, *SHH = nullptr, *SHO = nullptr, *RL = nullptr, *PR = nullptr, *SELW = nullptr, *GATH = nullptr, *GG = nullptr, *GU = nullptr, *GO = nullptr;
+  int32_t *SEL = nullptr, *CNT = nullptr, *POSI = nullptr;
+  float *GATHh = nullptr, *GATHl = nullptr, *GHh = nullptr, *GHl = nullptr;   // tf32 splits of the gathered rows and of the experts' hidden rows
+};
+
+struct FwdArgs {
+  Mode mode;
+  const int32_t* ids;      // device [B*T]
+  int B, T;
+  int cache_rows = 0, cache_row_mul = 1, max_seq = 0;
+  int logits_rows = 0;     // rows that get logits (PLAIN/TRAIN: all; PREFILL: B; DECODE: B)
+  int group = 1, prefix_len = 0;   // DECODE: rows come in groups sharing their first prefix_len cached positions
+};
+
+}  // namespace gnm
+namespace gnm {
+// A rollout in progress (inference/engine.go:112-327): geometry, options and the buffers of its decode steps.
+struct Rollout {
+  bool active = false;
+  int P = 0, plen = 0, G = 0, max_tokens = 0, rows = 0, max_seq = 0;
+  int generated = 0;          // sampling steps taken
+  int logits_row_div = 1;     // rows that share one row of the current logits (G right after the prefill, then 1)
+  bool thinking = false; int thinking_budget = 0;
+  int follower_steps = 0;     // forwards of columns sampled elsewhere (ensemble members)
+  FwdBufs b;
+};
+}  // namespace gnm
 struct gn_model;
 namespace gnm {
 // model_latent.cu / model_latent_train.cu
@@ -115,7 +155,8 @@ struct gn_model {
   int64_t off_wte = 0, off_lm = 0, off_rho = 0, off_chi = 0, off_smear_gate = 0, off_smear_lambda = 0, off_backout = 0;
   DevBuf cosb, sinb, sacc;
   // inference state
-  DevBuf cache, prev, pos, ctxlen, ids_dev, sampled, seeds, out_tokens, out_lengths, done, n_done, sel;
+  DevBuf cache, prev, pos, ctxlen, ids_dev, sampled, seeds, out_tokens, out_lengths, out_masks, engine_state, done, n_done, sel;
+  Rollout ro;   // the rollout in progress (gn_generate_batch, gn_rollout_*)
   DevBuf part_acc, part_ms, step_dev;
   // optimizer state (gn_model_optimizer_init): momentum / exp_avg and second moment / exp_avg_sq at the parameter's offset
   DevBuf opt_mom, opt_second, opt_ws;
@@ -128,6 +169,7 @@ struct gn_model {
   std::map<std::string, float> phase_ms;
   cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
   bool weights_dirty = true;   // cached tensor-core operand splits of the parameters are stale
+  int kv_rows = 0, kv_max_seq = 0;   // geometry of the KV cache currently held
 
   float* p(int64_t off) const { return P.f() + off; }
   float* g(int64_t off) const { return G.f() + off; }
@@ -139,35 +181,9 @@ using namespace gn;
 
 inline int gemm(gn_model* m, const gn::GemmArgs& a) { return gn::gemm_dispatch(a, m->ctx->gemm_kind, m->s()); }
 
-enum Mode { MODE_PLAIN, MODE_PREFILL, MODE_DECODE, MODE_TRAIN };
-
 // Which shard updates which tensor in a sharded optimizer step: a greedy balance of an operation-count estimate,
 // identical on every rank (index = position in gn_model::params).
 std::vector<int> optimizer_owners(gn_model* m, int shard_count);
-
-struct FwdBufs {
-  float *E, *X0, *Xa, *Xb, *H, *QKV, *O, *M, *HID, *BO, *Y, *LOGITS;
-  float *S1h, *S1l, *S4h, *S4l;   // producer-written tf32 splits: one [rows, d] pair and one [rows, 4d] pair, reused by every layer
-  // train only
-  float *SIG, *FP;
-  std::vector<LayerSaved> layers;
-  LatentWs* lws = nullptr;   // train, latent preset: the pass's scratch
-  // latent attention (inference): fused down/rope projections, content queries, absorbed queries, attended latents
-  float *P1 = nullptr, *QC = nullptr, *QF = nullptr, *AL = nullptr;
-  // routed experts (inference)
-  float *UG = nullptr, *SHH = nullptr, *SHO = nullptr, *RL = nullptr, *PR = nullptr, *SELW = nullptr, *GATH = nullptr, *GG = nullptr, *GU = nullptr, *GO = nullptr;
-  int32_t *SEL = nullptr, *CNT = nullptr, *POSI = nullptr;
-  float *GATHh = nullptr, *GATHl = nullptr, *GHh = nullptr, *GHl = nullptr;   // tf32 splits of the gathered rows and of the experts' hidden rows
-};
-
-struct FwdArgs {
-  Mode mode;
-  const int32_t* ids;      // device [B*T]
-  int B, T;
-  int cache_rows = 0, cache_row_mul = 1, max_seq = 0;
-  int logits_rows = 0;     // rows that get logits (PLAIN/TRAIN: all; PREFILL: B; DECODE: B)
-  int group = 1, prefix_len = 0;   // DECODE: rows come in groups sharing their first prefix_len cached positions
-};
 
 // model_latent.cu: the two block variants of the latent preset, inference only.
 // Attention of layer l from H = norm(x) (with its tf32 split in b.S1h/b.S1l on the tensor-core path):

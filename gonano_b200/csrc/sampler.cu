@@ -60,13 +60,42 @@ __device__ __forceinline__ Best block_best(Best b, float* shs, int* shi) {
 // IPT = vocabulary entries held per thread (vocab <= IPT * 1024).
 // The rollout engine's per-row bookkeeping after a sampling step (inference/engine.go:260-319, 349-367), done by the
 // row's own CTA: the row's position advances past the token that was just forwarded, its context length for the next
-// step follows, and the sampled token is either kept or ends the row (<|bos|>, <|assistant_end|>).
-__device__ __forceinline__ void sample_tail(const SampleTail& t, int row, int32_t token) {
+// step follows, a queued forced token replaces the sampled one, the thinking budget is enforced, and the token is
+// either kept or ends the row (<|bos|>, <|assistant_end|>).  Returns the token the row forwards next.
+__device__ __forceinline__ int32_t sample_tail(const SampleTail& t, int row, int32_t token) {
+  int32_t mask = 1;
+  if (t.forced_len && t.forced_len[row] > 0) {   // a queued token overrides the sampled one (the draw is still consumed)
+    const int head = t.forced_head[row];
+    token = t.forced_buf[(int64_t)row * t.forced_cap + head];
+    t.forced_head[row] = (head + 1) % t.forced_cap; t.forced_len[row] -= 1;
+    mask = 0;
+  }
+  if (t.step_mask) t.step_mask[row] = mask;
   if (t.pos) { const int32_t pn = t.pos[row] + t.advance; t.pos[row] = pn; if (t.ctxlen) t.ctxlen[row] = pn + 1; }
+  if (t.thinking && t.in_think) {
+    if (token == t.think_start) { t.in_think[row] = 1; t.think_count[row] = 0; }
+    else if (token == t.think_end && t.in_think[row]) t.in_think[row] = 0;
+    else if (t.in_think[row]) {
+      const int n = t.think_count[row] + 1;
+      t.think_count[row] = n;
+      if (t.thinking_budget > 0 && n >= t.thinking_budget && t.forced_len && t.forced_len[row] < t.forced_cap) {
+        t.forced_buf[(int64_t)row * t.forced_cap + (t.forced_head[row] + t.forced_len[row]) % t.forced_cap] = t.think_end;
+        t.forced_len[row] += 1;
+      }
+    }
+  }
   if (t.done && !t.done[row]) {
     if (token == t.aend || token == t.bos) { t.done[row] = 1; atomicAdd(t.n_done, 1); }
-    else { const int n = t.out_lengths[row]; if (n < t.max_tokens) { t.out_tokens[(int64_t)row * t.max_tokens + n] = token; t.out_lengths[row] = n + 1; } }
+    else {
+      const int n = t.out_lengths[row];
+      if (n < t.max_tokens) {
+        t.out_tokens[(int64_t)row * t.max_tokens + n] = token;
+        if (t.out_masks) t.out_masks[(int64_t)row * t.max_tokens + n] = mask;
+        t.out_lengths[row] = n + 1;
+      }
+    }
   }
+  return token;
 }
 
 template <int IPT>
@@ -96,7 +125,7 @@ __global__ void __launch_bounds__(ST) sample_kernel(const float* __restrict__ lo
 #pragma unroll
     for (int it = 0; it < IPT; ++it) { int c = it * ST + tid; if (c < vocab) best_merge(b, x[it], c); }
     b = block_best(b, shs, shi);
-    if (tid == 0) { const int32_t t = b.index == 0x7fffffff ? 0 : b.index; out[row] = t; sample_tail(tail, row, t); }
+    if (tid == 0) { const int32_t t = b.index == 0x7fffffff ? 0 : b.index; out[row] = sample_tail(tail, row, t); }
     return;
   }
 
@@ -258,7 +287,7 @@ __global__ void __launch_bounds__(ST) sample_kernel(const float* __restrict__ lo
     }
   }
   b = block_best(b, shs, shi);
-  if (tid == 0) { const int32_t t = b.index == 0x7fffffff ? 0 : b.index; out[row] = t; sample_tail(tail, row, t); }
+  if (tid == 0) { const int32_t t = b.index == 0x7fffffff ? 0 : b.index; out[row] = sample_tail(tail, row, t); }
 }
 
 int sample_launch(const float* logits, int rows, int vocab, int logits_row_div, const float* uniforms, const uint64_t* seeds_dev, int group,

@@ -14,7 +14,7 @@ from dataclasses import dataclass
 import numpy as np
 
 from . import _lib
-from ._lib import GnConfig, GnOptimizerConfig, check, ptr
+from ._lib import GnConfig, GnGenerateOptions, GnOptimizerConfig, check, ptr
 
 SPECIAL_TOKENS = 11  # tokenizer/special.go:19-31
 
@@ -166,17 +166,75 @@ class Model:
         return logits
 
     # ---- Engine.GenerateBatchWith for many prompts (inference/engine.go:336-369)
-    def generate_batch(self, prompts, group, max_tokens, temperature, top_k, seeds, want_logits=False):
+    def _options(self, rows, thinking, thinking_budget, forced):
+        """inference.GenerateOptions plus tokens queued per row before the first step (what a handled tool call queues)."""
+        if not thinking and not thinking_budget and not forced:
+            return None, ()
+        opt = GnGenerateOptions(int(bool(thinking)), int(thinking_budget), None, 0, None)
+        keep = ()
+        if forced:
+            assert len(forced) == rows
+            stride = max(max(len(f) for f in forced), 1)
+            buf = np.zeros((rows, stride), np.int32); counts = np.zeros(rows, np.int32)
+            for r, f in enumerate(forced):
+                buf[r, :len(f)] = f; counts[r] = len(f)
+            opt.forced = buf.ctypes.data; opt.forced_stride = stride; opt.forced_counts = counts.ctypes.data
+            keep = (buf, counts)
+        return opt, keep
+
+    def generate_batch(self, prompts, group, max_tokens, temperature, top_k, seeds, want_logits=False, thinking=False, thinking_budget=0,
+                       forced=None, want_masks=False):
         prompts = _i32(prompts); P, plen = prompts.shape
         seeds = np.ascontiguousarray(seeds, dtype=np.uint64)
         assert seeds.size == P
         rows = P * group
         tokens = np.zeros((rows, max_tokens), np.int32); lengths = np.zeros(rows, np.int32)
+        masks = np.zeros((rows, max_tokens), np.int32) if want_masks else None
         step_logits = np.zeros((max_tokens, rows, self.vocab), np.float32) if want_logits else None
         steps = C.c_int()
-        check(self.lib.gn_generate_batch(self.h, ptr(prompts), P, plen, group, max_tokens, temperature, top_k, ptr(seeds), ptr(tokens),
-                                         ptr(lengths), ptr(step_logits), C.byref(steps)))
+        opt, keep = self._options(rows, thinking, thinking_budget, forced)
+        check(self.lib.gn_generate_batch_ex(self.h, ptr(prompts), P, plen, group, max_tokens, temperature, top_k, ptr(seeds),
+                                            C.byref(opt) if opt is not None else None, ptr(tokens), ptr(lengths), ptr(masks), ptr(step_logits),
+                                            C.byref(steps)))
+        del keep
+        if want_masks:
+            return tokens, lengths, steps.value, step_logits, masks
         return tokens, lengths, steps.value, step_logits
+
+    # ---- the same engine one step at a time (tool calls on the host, ensembles)
+    def rollout_begin(self, prompts, group, max_tokens, seeds, thinking=False, thinking_budget=0, forced=None):
+        prompts = _i32(prompts); P, plen = prompts.shape
+        seeds = np.ascontiguousarray(seeds, dtype=np.uint64)
+        self._ro = (P * group, max_tokens)
+        opt, keep = self._options(P * group, thinking, thinking_budget, forced)
+        check(self.lib.gn_rollout_begin(self.h, ptr(prompts), P, plen, group, max_tokens, ptr(seeds), C.byref(opt) if opt is not None else None))
+        del keep
+
+    def rollout_logits(self):
+        """(device address, logit rows, row divisor) of the current logits [logit_rows, vocab]."""
+        p, n, div = C.c_void_p(), C.c_int(), C.c_int()
+        check(self.lib.gn_rollout_logits(self.h, C.byref(p), C.byref(n), C.byref(div)))
+        return p.value, n.value, div.value
+
+    def rollout_sample(self, temperature, top_k, logits_device=None):
+        rows = self._ro[0]
+        column = np.zeros(rows, np.int32); mask = np.zeros(rows, np.int32); done = C.c_int()
+        check(self.lib.gn_rollout_sample(self.h, C.c_void_p(logits_device) if logits_device else None, temperature, top_k, ptr(column), ptr(mask),
+                                         C.byref(done)))
+        return column, mask, bool(done.value)
+
+    def rollout_force(self, row, tokens):
+        tokens = _i32(tokens)
+        check(self.lib.gn_rollout_force(self.h, int(row), ptr(tokens), tokens.size))
+
+    def rollout_forward(self, column=None):
+        check(self.lib.gn_rollout_forward(self.h, ptr(_i32(column)) if column is not None else None))
+
+    def rollout_end(self):
+        rows, max_tokens = self._ro
+        tokens = np.zeros((rows, max_tokens), np.int32); lengths = np.zeros(rows, np.int32); masks = np.zeros((rows, max_tokens), np.int32)
+        check(self.lib.gn_rollout_end(self.h, ptr(tokens), ptr(lengths), ptr(masks)))
+        return tokens, lengths, masks
 
     # ---- trainer.PolicyGradientStep (trainer/rl.go:14-60)
     def optimizer_init(self, unembedding_lr=0.004, embedding_lr=0.2, matrix_lr=0.02, weight_decay=0.0, scalar_lr=0.5, lr_mult=0.05):

@@ -280,6 +280,47 @@ int gn_generate_batch(gn_model* model, const int32_t* prompts, int n_prompts, in
                       int max_tokens, float temperature, int top_k, const uint64_t* seeds, int32_t* out_tokens,
                       int32_t* out_lengths, float* step_logits, int* steps_run);
 
+/* inference.GenerateOptions (inference/engine.go:24-35) plus tokens queued before the first step.
+ * thinking / thinking_budget: the engine tracks <|think_start|> (vocab-2) ... <|think_end|> (vocab-1) and, once
+ * thinking_budget reasoning tokens have been emitted, forces <|think_end|> (inference/engine.go:301-314).
+ * forced [rows, forced_stride] with forced_counts[row] tokens: what a handled tool call would queue for that row
+ * (inference/engine.go:284-300); a queued token overrides the sampled one and gets mask 0.  At most 64 per row. */
+typedef struct gn_generate_options {
+  int32_t thinking;
+  int32_t thinking_budget;
+  const int32_t* forced;
+  int32_t forced_stride;
+  const int32_t* forced_counts;
+} gn_generate_options;
+/* gn_generate_batch with options (NULL = none) and the masks of Engine.GenerateBatchWith: out_masks NULL or
+ * [n_prompts*group, max_tokens], 1 = sampled, 0 = forced, parallel to out_tokens. */
+int gn_generate_batch_ex(gn_model* model, const int32_t* prompts, int n_prompts, int prompt_len, int group, int max_tokens,
+                         float temperature, int top_k, const uint64_t* seeds, const gn_generate_options* options,
+                         int32_t* out_tokens, int32_t* out_lengths, int32_t* out_masks, float* step_logits, int* steps_run);
+
+/* The same engine one step at a time, for hosts that put their own logic between steps: tool calls, which need the
+ * tokenizer and a tool registry (inference/engine.go:284-300, inference/tooluse.go), and ensembles, which blend the
+ * logits of several models before one token is sampled (inference/ensemble.go:104-243).  Every call returns with
+ * the stream idle.
+ *   gn_rollout_begin    prefill, replicate the caches over the groups, reset the per-row engine state
+ *   gn_rollout_logits   device address of the current logits [logit_rows, vocab]; row r reads row r / row_div
+ *                       (row_div = group right after the prefill, then 1)
+ *   gn_rollout_sample   one sampling step from logits_device (NULL: the model's own; same shape) through the engine's
+ *                       state machine; column / mask (host, [rows], nullable) receive the tokens that are forwarded
+ *                       next and their masks; all_done is set when every row has finished
+ *   gn_rollout_force    queue tokens for one row (they override the next samples of that row)
+ *   gn_rollout_forward  forward the current column (column NULL) or one sampled by another model (an ensemble member
+ *                       following the member that sampled)
+ *   gn_rollout_end      kept tokens, lengths and masks, as gn_generate_batch_ex returns them */
+int gn_rollout_begin(gn_model* model, const int32_t* prompts, int n_prompts, int prompt_len, int group, int max_tokens,
+                     const uint64_t* seeds, const gn_generate_options* options);
+int gn_rollout_logits(gn_model* model, float** device_ptr, int* logit_rows, int* row_div);
+int gn_rollout_sample(gn_model* model, const float* logits_device, float temperature, int top_k, int32_t* column, int32_t* mask,
+                      int* all_done);
+int gn_rollout_force(gn_model* model, int row, const int32_t* tokens, int n);
+int gn_rollout_forward(gn_model* model, const int32_t* column);
+int gn_rollout_end(gn_model* model, int32_t* out_tokens, int32_t* out_lengths, int32_t* out_masks);
+
 /* trainer.PolicyGradientStep (trainer/rl.go:14-60): inputs/targets [batch, seq]
  * (host, target -1 = ignore), advantages [batch], norm.  Gradients ACCUMULATE
  * into the model's gradient buffer (tensors/tensor.go:189-194).  Rows are
@@ -289,6 +330,18 @@ int gn_generate_batch(gn_model* model, const int32_t* prompts, int n_prompts, in
 int gn_policy_gradient_step(gn_model* model, const int32_t* inputs, const int32_t* targets, const float* advantages,
                             int batch, int seq, float norm, int rows_per_pass, float* loss, float* nll_tap,
                             float* dlogits_tap, float* logits_tap);
+
+/* The session's KV cache, slice by slice, for the cache wire format of model/kvcache_codec.go (a host routine
+ * serialises what these calls return).  All rows share one position, as in the reference (model/kvcache.go:91-94).
+ *   kind 0 / 1  keys / values of (layer, row, kv head): positions * head_dim floats (model/kvcache.go:10-28)
+ *   kind 2      latent rows of (layer, row): positions * latent floats        (latent attention, model/kvcache.go:224-237)
+ *   kind 3      rotary keys of (layer, row): positions * n_kv_head * rope floats
+ *   kind 4      the row's previous pre-smear embedding: embed_dim floats (layer, head, positions ignored)
+ * gn_model_kv_alloc sizes an empty cache (for writing a deserialised one); gn_generate_batch sizes its own. */
+int gn_model_kv_info(gn_model* model, int* rows, int* max_seq, int* position);
+int gn_model_kv_alloc(gn_model* model, int rows, int max_seq, int position);
+int gn_model_kv_read(gn_model* model, int layer, int kind, int row, int head, int positions, float* host, int64_t n);
+int gn_model_kv_write(gn_model* model, int layer, int kind, int row, int head, int positions, const float* host, int64_t n);
 
 /* Phase timings of the last gn_generate_batch / gn_policy_gradient_step in
  * milliseconds (CUDA events on the context's stream): names are

@@ -349,6 +349,69 @@ int or_generate(void* mp, const int32_t* prompt, int prompt_len, int group, int 
   return generated;
 }
 
+// Engine.GenerateWith + GenerateBatchWith with the forced-token queue and the thinking-trace state machine
+// (inference/engine.go:256-314,349-367).  `forced` [group, forced_stride] with forced_counts[g] tokens queued for row
+// g before the first step (what a handled tool call would queue; tool execution itself needs the tokenizer and is
+// stubbed to "not handled", so the tool-call flags have no effect).  thinking / thinking_budget as GenerateOptions.
+// out_masks parallels out_tokens: 1 = sampled, 0 = forced.
+int or_generate_ex(void* mp, const int32_t* prompt, int prompt_len, int group, int max_tokens, float temperature, int top_k, uint64_t seed,
+                   int thinking, int thinking_budget, const int32_t* forced, int forced_stride, const int32_t* forced_counts,
+                   int32_t* out_tokens, int32_t* out_lengths, int32_t* out_masks) {
+  Model* m = (Model*)mp;
+  int V = m->cfg.vocab;
+  const int bos = V - 11, aend = V - 7, think_start = V - 2, think_end = V - 1;   // tokenizer/special.go:19-31
+  KVCache pre; m->cache_init(pre, 1, prompt_len);
+  std::vector<float> logits;
+  m->forward(logits, prompt, 1, prompt_len, &pre);
+  std::vector<float> cur((size_t)group * V);
+  for (int g = 0; g < group; ++g) std::copy(logits.begin() + (size_t)(prompt_len - 1) * V, logits.begin() + (size_t)prompt_len * V, cur.begin() + (size_t)g * V);
+  KVCache dec; m->cache_init(dec, group, prompt_len + max_tokens);
+  m->cache_replicate(dec, pre);
+  struct Row { std::vector<int32_t> forced; bool in_thinking = false; int thinking_tokens = 0; bool completed = false, kept_done = false; };
+  std::vector<Row> rows(group);
+  for (int g = 0; g < group; ++g) {
+    out_lengths[g] = 0;
+    if ((thinking || thinking_budget > 0) && prompt_len > 0 && prompt[prompt_len - 1] == think_start) rows[g].in_thinking = true;   // engine.go:229-236
+    if (forced && forced_counts) rows[g].forced.assign(forced + (size_t)g * forced_stride, forced + (size_t)g * forced_stride + forced_counts[g]);
+  }
+  int generated = 0;
+  std::vector<int32_t> sampled(group), col(group), mask(group);
+  while (true) {
+    if (max_tokens > 0 && generated >= max_tokens) break;
+    bool all = true;
+    for (int g = 0; g < group; ++g) if (!rows[g].completed) { all = false; break; }
+    if (all) break;
+    or_sample_next_token(cur.data(), group, V, nullptr, &seed, group, (uint32_t)generated, temperature, top_k, sampled.data());
+    for (int g = 0; g < group; ++g) {
+      Row& st = rows[g];
+      const bool is_forced = !st.forced.empty();
+      mask[g] = is_forced ? 0 : 1;
+      int t;
+      if (is_forced) { t = st.forced.front(); st.forced.erase(st.forced.begin()); } else t = sampled[g];
+      col[g] = t;
+      if (t == aend || t == bos) st.completed = true;
+      if (thinking || thinking_budget > 0) {
+        if (t == think_start) { st.in_thinking = true; st.thinking_tokens = 0; }
+        else if (t == think_end && st.in_thinking) st.in_thinking = false;
+        else if (st.in_thinking) {
+          st.thinking_tokens++;
+          if (thinking_budget > 0 && st.thinking_tokens >= thinking_budget) st.forced.push_back(think_end);
+        }
+      }
+      if (!st.kept_done) {
+        if (t == aend || t == bos) st.kept_done = true;
+        else { out_tokens[(size_t)g * max_tokens + out_lengths[g]] = t; if (out_masks) out_masks[(size_t)g * max_tokens + out_lengths[g]] = mask[g]; out_lengths[g]++; }
+      }
+    }
+    ++generated;
+    bool alldone = true;
+    for (int g = 0; g < group; ++g) if (!rows[g].kept_done) { alldone = false; break; }
+    if (alldone) break;
+    m->forward(cur, col.data(), group, 1, &dec);
+  }
+  return generated;
+}
+
 // ----------------------------------------------------------------------- RL
 // cmd/chat_rl/main.go:137-154.  mode 0: reward - group mean (the reference).
 // mode 1: (reward - mean) / (population std + 1e-6), float32, a build-side

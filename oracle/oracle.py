@@ -501,6 +501,20 @@ class Model:
                                    C.c_uint64(seed), _i(toks), _i(lens), _f(sl) if want_logits else None)
         return toks, lens, int(steps), sl
 
+    def generate_ex(self, prompt, group, max_tokens, temperature, top_k, seed, thinking=False, thinking_budget=0, forced=None):
+        """The engine with its forced-token queue and thinking budget (inference/engine.go:256-314): ``forced`` is a list of
+        token lists, one per row, queued before the first step.  Returns tokens, lengths, masks, steps."""
+        prompt = i32(prompt)
+        toks = np.zeros((group, max_tokens), np.int32); lens = np.zeros(group, np.int32); masks = np.zeros((group, max_tokens), np.int32)
+        stride = max([len(f) for f in forced] + [1]) if forced else 1
+        fb = np.zeros((group, stride), np.int32); fc = np.zeros(group, np.int32)
+        if forced:
+            for g, f in enumerate(forced):
+                fb[g, :len(f)] = f; fc[g] = len(f)
+        steps = self.l.or_generate_ex(self.h, _i(prompt), prompt.size, group, max_tokens, C.c_float(temperature), top_k, C.c_uint64(seed),
+                                      int(bool(thinking)), int(thinking_budget), _i(fb), stride, _i(fc), _i(toks), _i(lens), _i(masks))
+        return toks, lens, masks, int(steps)
+
     def policy_gradient_step(self, inputs, targets, adv, norm, taps=False):
         inputs, targets, adv = i32(inputs), i32(targets), f32(adv)
         B, T = inputs.shape
