@@ -364,6 +364,9 @@ def run_only(args):
     """Sub-workloads for profiling: one small JSON line each."""
     from gonano_b200.session import Context, Model
     ctx = Context(0)
+    for item in args.option:
+        name, value = item.split("=")
+        ctx.set_option(name, int(value))
     if args.only == "kernel":
         ms = ctx.profile_kernel(args.kernel, args.dims, args.iters)
         emit({"only": "kernel", "kernel": args.kernel, "dims": args.dims, "ms": ms})
@@ -412,6 +415,9 @@ def run_ours(args):
         args.lean = True      # the per-kernel rooflines, the CPU sample and the flop model below describe the dense d12 step
     stream = torch.cuda.Stream(device=local)
     ctx = Context(local, stream.cuda_stream)
+    for item in args.option:
+        name, value = item.split("=")
+        ctx.set_option(name, int(value))
     if world > 1:
         # torch.distributed is the rendezvous (it hands rank 0's communicator id to the others) and the clock's
         # barrier; the gradient exchange itself runs inside the library (gn_model_grad_allreduce, NCCL)
@@ -607,6 +613,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--lean", action="store_true", help="steps only: no per-kernel microbenchmarks, TF32 peak, CPU baseline or replica checks")
     ap.add_argument("--workload", default="d12", choices=["d12", "c3"], help="d12: the dense step the metric is quoted on; c3: the latent preset's step")
+    ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE", help="a gn_ctx_set_option switch, e.g. head_chunk_rows=8192 (repeatable)")
     ap.add_argument("--only", choices=["decode", "train", "kernel"], help="run one sub-workload for profiling instead of the benchmark")
     ap.add_argument("--model", default="d12"); ap.add_argument("--prompts", type=int, default=64); ap.add_argument("--tokens", type=int, default=4)
     ap.add_argument("--rows", type=int, default=32); ap.add_argument("--eager", action="store_true", help="--only decode: no CUDA-graph replay, so that a profiler sees every launch")

@@ -79,6 +79,7 @@ SIGNATURES = {
     "gn_model_optimizer_init": (I, [vp, C.POINTER(GnOptimizerConfig)]), "gn_model_optimizer_step": (I, [vp]),
     "gn_model_optimizer_step_shard": (I, [vp, I, I]), "gn_model_optimizer_finish": (I, [vp]),
     "gn_pg_loss_backward": (I, [vp, vp, vp, L, I, I, F, F, vp, vp, C.POINTER(C.c_double)]),
+    "gn_distillation_loss_backward": (I, [vp, vp, vp, L, I, F, F, vp, vp, C.POINTER(C.c_double), C.POINTER(C.c_int64)]),
     "gn_pg_loss_backward_static": (I, [vp, vp, vp, L, I, I, F, F, vp, vp, vp, vp]),
     "gn_static_loss_max_rows": (I, []),
     "gn_ctx_create": (I, [I, vp, C.POINTER(vp)]), "gn_ctx_destroy": (I, [vp]), "gn_ctx_sync": (I, [vp]),

@@ -205,6 +205,22 @@ def pg_loss_backward(logits, targets, advantages, seq_len, norm, softcap=0.0, wa
     return loss.value, nll, grad
 
 
+def distillation_loss_backward(student, teacher, temperature=1.0, mask=None, scale=1.0, want_grad=True):
+    """tensors.DistillationLossPerPosition / DistillationGrad / DistillationLoss (tensors/loss.go:84-213):
+    per-position losses, the valid count, the mean loss over the valid positions and the gradient at the student."""
+    lib = _lib.load()
+    student, teacher = _f32(student), _f32(teacher)
+    rows, vocab = student.shape
+    mk = _i32(mask) if mask is not None else None
+    losses = np.zeros(rows, np.float32)
+    grad = np.zeros((rows, vocab), np.float32) if want_grad else None
+    total, valid = C.c_double(), C.c_int64()
+    check(lib.gn_distillation_loss_backward(ptr(student), ptr(teacher), ptr(mk), rows, vocab, temperature, scale, ptr(losses), ptr(grad),
+                                            C.byref(total), C.byref(valid)))
+    mean = total.value / valid.value if valid.value else 0.0
+    return losses, valid.value, mean, grad
+
+
 # -------------------------------------------------------------------------
 # Optimizer updates of one tensor (optimizer/optimizer.go, muon.go, sinkhorn.go); arrays are updated in place
 # -------------------------------------------------------------------------

@@ -508,4 +508,32 @@ int gn_pg_loss_backward(const float* logits, const int32_t* targets, const float
   GN_END();
 }
 
+// tensors.DistillationLossPerPosition + DistillationGrad (tensors/loss.go:84-213)
+int gn_distillation_loss_backward(const float* student, const float* teacher, const int32_t* mask, int64_t rows, int vocab, float temperature, float scale,
+                                  float* losses, float* dstudent, double* loss_sum, int64_t* valid) {
+  GN_REQUIRE(student && teacher && vocab > 0 && rows >= 0, "distillation_loss_backward: bad argument");
+  GN_BEGIN();
+  const size_t n = (size_t)rows * vocab;
+  const float* ds = st.in(student, n); const float* dt = st.in(teacher, n);
+  const int32_t* dm = mask ? st.in(mask, rows) : nullptr;
+  float* dl = losses ? st.out(losses, rows) : nullptr; float* dg = dstudent ? st.out(dstudent, n) : nullptr;
+  double* scratch = nullptr;
+  GN_CUDA(cudaMalloc((void**)&scratch, sizeof(double) * (size_t)(rows + 1)));
+  st.owned.push_back(scratch);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(distillation_launch(ds, dt, dm, rows, vocab, temperature, scale, dl, dg, scratch + 1, scratch, s));
+  if (loss_sum) GN_CUDA(cudaMemcpyAsync(loss_sum, scratch, sizeof(double), cudaMemcpyDefault, s));
+  if (valid) {   // the mask is small: count it on the host side of the call
+    int64_t count = rows;
+    if (mask) {
+      std::vector<int32_t> hm((size_t)rows);
+      GN_CUDA(cudaMemcpyAsync(hm.data(), dm, sizeof(int32_t) * rows, cudaMemcpyDeviceToHost, s));
+      GN_CUDA(cudaStreamSynchronize(s));
+      count = 0; for (int32_t v : hm) count += v != 0;
+    }
+    *valid = count;
+  }
+  GN_END();
+}
+
 }  // extern "C"

@@ -108,7 +108,9 @@ int sample_launch(const float* logits, int rows, int vocab, int logits_row_div, 
 // number of targets outside {-1} and [0, vocab) (such rows are treated as ignored, never dereferenced).
 int pg_loss_launch(const float* logits, const int32_t* targets, const float* adv, int64_t rows, int vocab, int64_t ld, int seq_len, float norm,
                    float softcap, float* nll, float* dlogits, int64_t ldd, double* row_loss, double* loss_out, int accumulate_loss, cudaStream_t s,
-                   int* bad_targets = nullptr);
+                   int* bad_targets = nullptr, int64_t row_offset = 0);   // row r's advantage is adv[(row_offset + r) / seq_len]
 int advantage_launch(const float* rewards, int groups, int group, int mode, float* adv, cudaStream_t s);
+int distillation_launch(const float* student, const float* teacher, const int32_t* mask, int64_t rows, int vocab, float temperature, float scale,
+                        float* losses, float* grad, double* row_loss, double* loss_sum, cudaStream_t s);
 
 }  // namespace gn

@@ -28,7 +28,8 @@ __device__ __forceinline__ void ms_merge(float& m, float& s, float om, float os)
 template <bool VEC>
 __global__ void __launch_bounds__(LT) pg_loss_kernel(const float* __restrict__ logits, const int32_t* __restrict__ targets, const float* __restrict__ adv,
                                                      int64_t rows, int vocab, int64_t ld, int seq_len, float norm, float softcap, float* __restrict__ nll,
-                                                     float* dlogits, int64_t ldd, double* __restrict__ row_loss, int* __restrict__ bad_targets) {
+                                                     float* dlogits, int64_t ldd, double* __restrict__ row_loss, int* __restrict__ bad_targets,
+                                                     int64_t row_offset) {
   __shared__ float sh_m[32], sh_s[32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -93,11 +94,11 @@ __global__ void __launch_bounds__(LT) pg_loss_kernel(const float* __restrict__ l
       float om = __shfl_xor_sync(0xffffffffu, m, o), os = __shfl_xor_sync(0xffffffffu, s, o);
       ms_merge(m, s, om, os);
     }
-    const float a_over_n = adv[row / seq_len] / norm;
+    const float a_over_n = adv[(row_offset + row) / seq_len] / norm;   // rows may be a slice of the batch: row_offset is its first row
     if (tid == 0) {
       float l = m + logf(s) - x_target;
       if (nll) nll[row] = l;
-      row_loss[row] = (double)l * (double)adv[row / seq_len] / (double)norm;
+      row_loss[row] = (double)l * (double)adv[(row_offset + row) / seq_len] / (double)norm;
     }
     if (!drow) continue;
     // ---- pass 2: gradient
@@ -157,21 +158,76 @@ __global__ void __launch_bounds__(1024) loss_sum_kernel(const double* row_loss, 
 
 int pg_loss_launch(const float* logits, const int32_t* targets, const float* adv, int64_t rows, int vocab, int64_t ld, int seq_len, float norm,
                    float softcap, float* nll, float* dlogits, int64_t ldd, double* row_loss, double* loss_out, int accumulate_loss, cudaStream_t s,
-                   int* bad_targets) {
+                   int* bad_targets, int64_t row_offset) {
   GN_REQUIRE(vocab > 0 && seq_len > 0, "loss: vocab %d / seq_len %d must be positive", vocab, seq_len);
   if (rows > 0) {
     auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     bool vec = al(logits) && (!dlogits || al(dlogits)) && vocab % 4 == 0 && ld % 4 == 0 && ldd % 4 == 0;
     // In the vector path the register window covers LIPT*LT columns as float4 groups.
     int grid = (int)std::min<int64_t>(rows, (int64_t)num_sms() * 8);
-    if (vec) pg_loss_kernel<true><<<grid, LT, 0, s>>>(logits, targets, adv, rows, vocab, ld, seq_len, norm, softcap, nll, dlogits, ldd, row_loss, bad_targets);
-    else pg_loss_kernel<false><<<grid, LT, 0, s>>>(logits, targets, adv, rows, vocab, ld, seq_len, norm, softcap, nll, dlogits, ldd, row_loss, bad_targets);
+    if (vec) pg_loss_kernel<true><<<grid, LT, 0, s>>>(logits, targets, adv, rows, vocab, ld, seq_len, norm, softcap, nll, dlogits, ldd, row_loss, bad_targets, row_offset);
+    else pg_loss_kernel<false><<<grid, LT, 0, s>>>(logits, targets, adv, rows, vocab, ld, seq_len, norm, softcap, nll, dlogits, ldd, row_loss, bad_targets, row_offset);
     GN_LAUNCH_CHECK();
   }
   if (accumulate_loss != 2 && loss_out) {  // 0: overwrite, 1: add, 2: leave the total alone
     loss_sum_kernel<<<1, 1024, 0, s>>>(row_loss, rows, loss_out, accumulate_loss);
     GN_LAUNCH_CHECK();
   }
+  return GN_OK;
+}
+
+// On-policy distillation loss (tensors/loss.go:84-213): per position the cross-entropy of softmax(teacher / tau)
+// under softmax(student / tau), and its gradient (softmax(student/tau) - softmax(teacher/tau)) * scale / tau.
+// One CTA per row: a first pass over both rows finds the two maxima, a second the two sums and the teacher-weighted
+// student logits, a third writes the gradient; the second and third passes re-read the rows from L2 (a row pair is
+// at most 512 KB).  HBM traffic per valid row: 2 rows read + 1 written.  Masked rows are never read.
+__global__ void __launch_bounds__(LT) distill_kernel(const float* __restrict__ student, const float* __restrict__ teacher, const int32_t* __restrict__ mask,
+                                                     int64_t rows, int vocab, float inv_tau, float grad_scale, float* __restrict__ losses,
+                                                     float* __restrict__ grad, double* __restrict__ row_loss) {
+  __shared__ float sh[33];
+  __shared__ double shd[33];
+  const int tid = threadIdx.x;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    float* grow = grad ? grad + row * vocab : nullptr;
+    if (mask && mask[row] == 0) {
+      if (grow) for (int c = tid; c < vocab; c += LT) grow[c] = 0.0f;
+      if (tid == 0) { if (losses) losses[row] = 0.0f; row_loss[row] = 0.0; }
+      continue;
+    }
+    const float* s = student + row * vocab; const float* t = teacher + row * vocab;
+    float smax = -INFINITY, tmax = -INFINITY;
+    for (int c = tid; c < vocab; c += LT) { smax = fmaxf(smax, s[c] * inv_tau); tmax = fmaxf(tmax, t[c] * inv_tau); }
+    smax = block_max(smax, sh); tmax = block_max(tmax, sh);
+    double ssum = 0.0, tsum = 0.0, weighted = 0.0;
+    for (int c = tid; c < vocab; c += LT) {
+      const float sv = s[c] * inv_tau;
+      const float sw = __expf(sv - smax), tw = __expf(t[c] * inv_tau - tmax);
+      ssum += (double)sw; tsum += (double)tw; weighted += (double)tw * (double)sv;
+    }
+    ssum = block_sum_d(ssum, shd); tsum = block_sum_d(tsum, shd); weighted = block_sum_d(weighted, shd);
+    if (tid == 0) {
+      const double l = (double)smax + log(ssum) - weighted / tsum;
+      if (losses) losses[row] = (float)l;
+      row_loss[row] = l;
+    }
+    if (!grow) continue;
+    const float is = (float)(1.0 / ssum), it = (float)(1.0 / tsum);
+    for (int c = tid; c < vocab; c += LT)
+      grow[c] = (__expf(s[c] * inv_tau - smax) * is - __expf(t[c] * inv_tau - tmax) * it) * grad_scale;
+  }
+}
+// losses / grad nullable; row_loss: [rows] double scratch; loss_sum: device double receiving the sum of the valid rows' losses.
+int distillation_launch(const float* student, const float* teacher, const int32_t* mask, int64_t rows, int vocab, float temperature, float scale,
+                        float* losses, float* grad, double* row_loss, double* loss_sum, cudaStream_t s) {
+  GN_REQUIRE(vocab > 0, "distillation: vocab must be positive");
+  const float tau = temperature <= 0.0f ? 1.0f : temperature;   // tensors/loss.go:151-157
+  if (rows > 0) {
+    const int grid = (int)std::min<int64_t>(rows, (int64_t)num_sms() * 8);
+    distill_kernel<<<grid, LT, 0, s>>>(student, teacher, mask, rows, vocab, 1.0f / tau, scale / tau, losses, grad, row_loss);
+    GN_LAUNCH_CHECK();
+  }
+  loss_sum_kernel<<<1, 1024, 0, s>>>(row_loss, rows, loss_sum, 0);
+  GN_LAUNCH_CHECK();
   return GN_OK;
 }
 

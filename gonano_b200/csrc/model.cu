@@ -340,6 +340,7 @@ int forward_core(gn_model* m, FwdBufs& b, const FwdArgs& a) {
   } else {
     GN_TRY(backout_norm_launch(x_prev, backout, m->p(m->off_backout), sel, train ? b.FP : nullptr, b.Y, tc_head ? b.S1h : nullptr, tc_head ? b.S1l : nullptr, lrows, d, s));
   }
+  if (a.skip_head) return GN_OK;
   { GemmArgs g; g.A = b.Y; g.lda = d; g.B = m->p(m->off_lm); g.b_static = 1; g.b_prefetch = prefetch; g.ldb = d; g.b_trans = 1; g.C = b.LOGITS; g.ldc = V; g.M = (int)lrows; g.N = V; g.K = d;
     g.epilogue = EPI_SOFTCAP; g.scalar = kSoftcap;
     if (tc_head) { g.a_hi = b.S1h; g.a_lo = b.S1l; } GN_TRY(gemm(m, g)); }
@@ -365,17 +366,19 @@ void carve_bwd(gn_model* m, float* base, BwdBufs& w, int64_t rows, int B, int T)
   w.DE = w.DY;  // free again by the time the embedding gradient is formed
 }
 
-int backward_core(gn_model* m, FwdBufs& b, BwdBufs& w, const int32_t* ids, int B, int T) {
+int backward_core(gn_model* m, FwdBufs& b, BwdBufs& w, const int32_t* ids, int B, int T, bool head_done) {
   const int d = m->d, W = m->W, Hq = m->Hq, Hkv = m->Hkv, D = m->D, V = m->V, L = m->L;
   const int64_t rows = (int64_t)B * T;
   const int64_t n = rows * d;
   cudaStream_t s = m->s();
   double* sacc = (double*)m->sacc.p;
   float* DZ = b.LOGITS;  // the loss kernel turned the logits into dz in place
-  // lm_head: dW[:V] += dz^T y ; dy = dz W[:V]      (model/layers/linear.go:45-53)
+  // lm_head: dW[:V] += dz^T y ; dy = dz W[:V]      (model/layers/linear.go:45-53); already done in row chunks when head_done
+  if (!head_done) {
   { GemmArgs g; g.A = DZ; g.lda = V; g.a_trans = 1; g.B = b.Y; g.ldb = d; g.b_trans = 0; g.b_hi = b.S1h; g.b_lo = b.S1l; g.C = m->g(m->off_lm); g.ldc = d; g.M = V; g.N = d; g.K = (int)rows;
     g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
   { GemmArgs g; g.A = DZ; g.lda = V; g.a_reuse = 1; g.B = m->p(m->off_lm); g.b_static = 1; g.ldb = d; g.b_trans = 0; g.C = w.DY; g.ldc = d; g.M = (int)rows; g.N = d; g.K = V; GN_TRY(gemm(m, g)); }
+  }
   GN_TRY(rmsnorm_backward_launch(w.DFP, b.FP, w.DY, nullptr, rows, d, kNormEps, s));
   const float* backout = b.layers[L / 2].XOUT;
   GN_TRY(dot_accumulate_launch(w.DFP, backout, n, -1.0, sacc + 2 * L + 1, s));   // d lambda_b (train_transformer.go:181-190)
@@ -478,6 +481,7 @@ int gn_ctx_set_option(gn_ctx* c, const char* name, int value) {
   const std::string n = name;
   if (n == "decode_prefix_sharing") { attention_decode_prefix_mode(value); return GN_OK; }
   if (c && n == "decode_graph") { c->use_graphs = value != 0; return GN_OK; }
+  if (c && n == "head_chunk_rows") { GN_REQUIRE(value >= 1, "head_chunk_rows must be positive"); c->head_chunk_rows = value; return GN_OK; }
   cudaStream_t s = nullptr;
   if (c) { GN_CUDA(cudaSetDevice(c->device)); s = c->stream; }
   else { s = tier_a_stream_or_null(); GN_REQUIRE(s != nullptr, "gn_ctx_set_option(NULL, ...): no stand-alone call has run yet"); }
@@ -1107,14 +1111,19 @@ int gn_policy_gradient_step(gn_model* m, const int32_t* inputs, const int32_t* t
   rows_per_pass = std::min(rows_per_pass, B);
   const int64_t all = (int64_t)B * T;
   GN_TRY(m->in_dev.ensure(sizeof(int32_t) * all)); GN_TRY(m->tgt_dev.ensure(sizeof(int32_t) * all)); GN_TRY(m->adv_dev.ensure(sizeof(float) * B));
-  GN_TRY(m->rowloss.ensure(sizeof(double) * (size_t)rows_per_pass * T)); GN_TRY(m->loss_dev.ensure(sizeof(double)));
+  GN_TRY(m->loss_dev.ensure(sizeof(double)));
   GN_CUDA(cudaMemcpyAsync(m->in_dev.p, inputs, sizeof(int32_t) * all, cudaMemcpyHostToDevice, s));
   GN_CUDA(cudaMemcpyAsync(m->tgt_dev.p, targets, sizeof(int32_t) * all, cudaMemcpyHostToDevice, s));
   GN_CUDA(cudaMemcpyAsync(m->adv_dev.p, adv, sizeof(float) * B, cudaMemcpyHostToDevice, s));
   GN_CUDA(cudaMemsetAsync(m->loss_dev.p, 0, sizeof(double), s));
   FwdBufs b; BwdBufs w; float* extra = nullptr;
   const int64_t prow = (int64_t)rows_per_pass * T;
-  GN_TRY(make_bufs(m, m->train, b, MODE_TRAIN, prow, prow, rows_per_pass, T, bwd_floats(m, prow, rows_per_pass, T), &extra));
+  // lm_head, the loss and lm_head's backward run in chunks of rows, so that the [tokens, vocab] logits of a pass never
+  // exist as a whole: a chunk is produced, turned into dz in place and consumed by the two gradient products
+  // (model/train_transformer.go:137-156 materialises logits, softmax and gradient for the whole batch).
+  const int64_t head_chunk = std::min<int64_t>(prow, std::max(1, m->ctx->head_chunk_rows));
+  GN_TRY(m->rowloss.ensure(sizeof(double) * (size_t)head_chunk));
+  GN_TRY(make_bufs(m, m->train, b, MODE_TRAIN, prow, head_chunk, rows_per_pass, T, bwd_floats(m, prow, rows_per_pass, T), &extra));
   carve_bwd(m, extra, w, prow, rows_per_pass, T);
   LatentWs lws;
   if (m->mla() || m->moe()) {
@@ -1123,36 +1132,48 @@ int gn_policy_gradient_step(gn_model* m, const int32_t* inputs, const int32_t* t
     lws.total_sequences = B;
     b.lws = &lws;
   }
+  const bool tc = m->ctx->gemm_kind == 1;
+  const int d = m->d;
   float t_fwd = 0, t_loss = 0, t_bwd = 0;
-  std::vector<float> nll_host;
+  DevBuf tap_scratch;
   for (int b0 = 0; b0 < B; b0 += rows_per_pass) {
     const int Bm = std::min(rows_per_pass, B - b0);
     const int64_t rows = (int64_t)Bm * T;
     const int32_t* ids = m->in_dev.i() + (int64_t)b0 * T;
     GN_CUDA(cudaEventRecord(m->ev[0], s));
-    FwdArgs a; a.mode = MODE_TRAIN; a.ids = ids; a.B = Bm; a.T = T;
+    FwdArgs a; a.mode = MODE_TRAIN; a.ids = ids; a.B = Bm; a.T = T; a.skip_head = true;
     GN_TRY(forward_core(m, b, a));
     GN_CUDA(cudaEventRecord(m->ev[1], s));
-    if (logits_tap) GN_CUDA(cudaMemcpyAsync(logits_tap + (size_t)b0 * T * V, b.LOGITS, sizeof(float) * rows * V, cudaMemcpyDeviceToHost, s));
-    // loss + dlogits with the softcap backward folded in; dz overwrites the logits.
-    // The taps want the gradient at the softcapped logits, so they take a separate pass.
-    if (dlogits_tap) {
-      // The tap is the gradient at the softcapped logits (what trainer/rl.go hands to
-      // TrainBackward), so it takes its own pass without the folded softcap backward.
-      DevBuf scratch;
-      GN_TRY(scratch.ensure(sizeof(float) * rows * V));
-      GN_TRY(pg_loss_launch(b.LOGITS, m->tgt_dev.i() + (int64_t)b0 * T, m->adv_dev.f() + b0, rows, V, V, T, norm, 0.0f, nullptr, scratch.f(), V,
-                            (double*)m->rowloss.p, nullptr, 2, s));
-      GN_CUDA(cudaMemcpyAsync(dlogits_tap + (size_t)b0 * T * V, scratch.p, sizeof(float) * rows * V, cudaMemcpyDeviceToHost, s));
-      GN_CUDA(cudaStreamSynchronize(s));
-      scratch.release();
-    }
     float* nll_dev = w.DELTA;  // [Bm*Hq*T] >= rows floats; free until the attention backward
-    GN_TRY(pg_loss_launch(b.LOGITS, m->tgt_dev.i() + (int64_t)b0 * T, m->adv_dev.f() + b0, rows, V, V, T, norm, kSoftcap, nll_dev, b.LOGITS, V,
-                          (double*)m->rowloss.p, (double*)m->loss_dev.p, 1, s));
+    for (int64_t r0 = 0; r0 < rows; r0 += head_chunk) {
+      const int64_t rc = std::min(head_chunk, rows - r0);
+      const int32_t* tg = m->tgt_dev.i() + (int64_t)b0 * T + r0;
+      // logits of the chunk: softcap(y W_lm^T)[:, :V]
+      { GemmArgs g; g.A = b.Y + r0 * d; g.lda = d; g.B = m->p(m->off_lm); g.b_static = 1; g.ldb = d; g.b_trans = 1; g.C = b.LOGITS; g.ldc = V; g.M = (int)rc; g.N = V; g.K = d;
+        g.epilogue = EPI_SOFTCAP; g.scalar = kSoftcap;
+        if (tc) { g.a_hi = b.S1h + r0 * d; g.a_lo = b.S1l + r0 * d; } GN_TRY(gemm(m, g)); }
+      if (logits_tap) GN_CUDA(cudaMemcpyAsync(logits_tap + ((size_t)b0 * T + r0) * V, b.LOGITS, sizeof(float) * rc * V, cudaMemcpyDeviceToHost, s));
+      if (dlogits_tap) {
+        // The tap is the gradient at the softcapped logits (what trainer/rl.go hands to TrainBackward), so it takes
+        // its own pass without the folded softcap backward.
+        GN_TRY(tap_scratch.ensure(sizeof(float) * head_chunk * V));
+        GN_TRY(pg_loss_launch(b.LOGITS, tg, m->adv_dev.f() + b0, rc, V, V, T, norm, 0.0f, nullptr, tap_scratch.f(), V, (double*)m->rowloss.p, nullptr, 2, s,
+                              nullptr, r0));
+        GN_CUDA(cudaMemcpyAsync(dlogits_tap + ((size_t)b0 * T + r0) * V, tap_scratch.p, sizeof(float) * rc * V, cudaMemcpyDeviceToHost, s));
+        GN_CUDA(cudaStreamSynchronize(s));
+      }
+      // loss + dlogits with the softcap backward folded in; dz overwrites the chunk's logits
+      GN_TRY(pg_loss_launch(b.LOGITS, tg, m->adv_dev.f() + b0, rc, V, V, T, norm, kSoftcap, nll_dev + r0, b.LOGITS, V, (double*)m->rowloss.p,
+                            (double*)m->loss_dev.p, 1, s, nullptr, r0));
+      // lm_head: dW[:V] += dz^T y ; dy = dz W[:V]      (model/layers/linear.go:45-53)
+      { GemmArgs g; g.A = b.LOGITS; g.lda = V; g.a_trans = 1; g.B = b.Y + r0 * d; g.ldb = d; g.b_trans = 0; if (tc) { g.b_hi = b.S1h + r0 * d; g.b_lo = b.S1l + r0 * d; }
+        g.C = m->g(m->off_lm); g.ldc = d; g.M = V; g.N = d; g.K = (int)rc; g.epilogue = EPI_ACCUM; GN_TRY(gemm(m, g)); }
+      { GemmArgs g; g.A = b.LOGITS; g.lda = V; g.a_reuse = 1; g.B = m->p(m->off_lm); g.b_static = 1; g.ldb = d; g.b_trans = 0; g.C = w.DY + r0 * d; g.ldc = d; g.M = (int)rc; g.N = d; g.K = V;
+        GN_TRY(gemm(m, g)); }
+    }
     if (nll_tap) GN_CUDA(cudaMemcpyAsync(nll_tap + (size_t)b0 * T, nll_dev, sizeof(float) * rows, cudaMemcpyDeviceToHost, s));
     GN_CUDA(cudaEventRecord(m->ev[2], s));
-    GN_TRY(backward_core(m, b, w, ids, Bm, T));
+    GN_TRY(backward_core(m, b, w, ids, Bm, T, true));
     GN_CUDA(cudaEventRecord(m->ev[3], s));
     GN_CUDA(cudaStreamSynchronize(s));
     float ms = 0;
@@ -1160,6 +1181,7 @@ int gn_policy_gradient_step(gn_model* m, const int32_t* inputs, const int32_t* t
     GN_CUDA(cudaEventElapsedTime(&ms, m->ev[1], m->ev[2])); t_loss += ms;
     GN_CUDA(cudaEventElapsedTime(&ms, m->ev[2], m->ev[3])); t_bwd += ms;
   }
+  tap_scratch.release();
   GN_TRY(scalar_flush_launch(m->g(m->off_rho), (double*)m->sacc.p, 2 * L + 2, s));
   double loss_host = 0;
   GN_CUDA(cudaMemcpyAsync(&loss_host, m->loss_dev.p, sizeof(double), cudaMemcpyDeviceToHost, s));

@@ -109,6 +109,7 @@ struct FwdArgs {
   int cache_rows = 0, cache_row_mul = 1, max_seq = 0;
   int logits_rows = 0;     // rows that get logits (PLAIN/TRAIN: all; PREFILL: B; DECODE: B)
   int group = 1, prefix_len = 0;   // DECODE: rows come in groups sharing their first prefix_len cached positions
+  bool skip_head = false;          // TRAIN: stop after the final norm (b.Y); the caller runs lm_head, loss and their backward in row chunks
 };
 
 }  // namespace gnm

@@ -167,6 +167,14 @@ int gn_group_advantage(const float* rewards, int groups, int group, int mode, fl
 int gn_pg_loss_backward(const float* logits, const int32_t* targets, const float* advantages, int64_t rows, int vocab,
                         int seq_len, float norm, float softcap, float* nll, float* dlogits, double* loss);
 
+/* tensors.DistillationLossPerPosition and DistillationGrad (tensors/loss.go:84-213) in one pass: per position the
+ * cross-entropy of softmax(teacher / temperature) under softmax(student / temperature) (the teacher's entropy is
+ * constant and dropped), and d loss / d student = (softmax(student/T) - softmax(teacher/T)) * scale / T.
+ * mask: NULL or one int32 per row, 0 = masked (loss 0, zero gradient).  temperature <= 0 reads as 1.
+ * losses [rows], dstudent [rows, vocab], loss_sum (sum over the valid rows) and valid (their count) are optional. */
+int gn_distillation_loss_backward(const float* student, const float* teacher, const int32_t* mask, int64_t rows, int vocab,
+                                  float temperature, float scale, float* losses, float* dstudent, double* loss_sum, int64_t* valid);
+
 /* gn_pg_loss_backward for callers that must not allocate.  No counterpart in the reference:
  * it exists for hosts that own all device memory themselves (a process whose own arena spans
  * the GPU, a loop that cannot afford cudaMalloc's device-wide synchronisation or a late
@@ -233,6 +241,7 @@ int gn_ctx_set_gemm(gn_ctx* ctx, int kind);
 /* Tuning and test switches (no counterpart in the reference).  ctx == NULL addresses the stand-alone
  * (Tier A) calls, after the first of them has run.  Names:
  *   "decode_graph"           1 (default) replays the decode step from a CUDA graph, 0 keeps it eager
+ *   "head_chunk_rows"        16384 (default): token rows whose logits exist at once in the training pass
  *   "decode_prefix_sharing"  -1 (default) automatic, 0 / 1 shared-prompt attention pass off / on (process-wide)
  *   "gemm_persistent_ctas"   -1 (default) one CTA per SM for the tile-walking form, 0 form off, n = n CTAs
  *   "gemm_pdl"               1 (default) products launch with programmatic stream serialization

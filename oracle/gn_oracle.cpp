@@ -412,6 +412,38 @@ int or_generate_ex(void* mp, const int32_t* prompt, int prompt_len, int group, i
   return generated;
 }
 
+// tensors/loss.go:84-213: forward KL from the student to the teacher's soft distribution per position (float64 inside),
+// and its gradient (softmax(student/tau) - softmax(teacher/tau)) / tau * scale.  mask: null or one int per row (0 =
+// masked: loss 0, zero gradient).  losses / grad nullable.  Returns the number of valid positions.
+int64_t or_distillation(const float* student, const float* teacher, int64_t rows, int vocab, float temperature, const int32_t* mask, float scale,
+                        float* losses, float* grad) {
+  const double tau = temperature <= 0 ? 1.0 : (double)temperature;
+  int64_t valid = 0;
+  for (int64_t r = 0; r < rows; ++r) {
+    const float* s = student + (size_t)r * vocab; const float* t = teacher + (size_t)r * vocab;
+    if (mask && mask[r] == 0) {
+      if (losses) losses[r] = 0.0f;
+      if (grad) std::fill(grad + (size_t)r * vocab, grad + (size_t)(r + 1) * vocab, 0.0f);
+      continue;
+    }
+    ++valid;
+    double smax = -INFINITY, tmax = -INFINITY;
+    for (int v = 0; v < vocab; ++v) { smax = std::max(smax, (double)s[v] / tau); tmax = std::max(tmax, (double)t[v] / tau); }
+    double ssum = 0, tsum = 0, weighted = 0;
+    for (int v = 0; v < vocab; ++v) {
+      const double sw = std::exp((double)s[v] / tau - smax), tw = std::exp((double)t[v] / tau - tmax);
+      ssum += sw; tsum += tw; weighted += tw * ((double)s[v] / tau);
+    }
+    if (losses) losses[r] = (float)(smax + std::log(ssum) - weighted / tsum);
+    if (grad) {
+      const double is = 1.0 / ssum, it = 1.0 / tsum, gs = (double)scale / tau;
+      for (int v = 0; v < vocab; ++v)
+        grad[(size_t)r * vocab + v] = (float)((std::exp((double)s[v] / tau - smax) * is - std::exp((double)t[v] / tau - tmax) * it) * gs);
+    }
+  }
+  return valid;
+}
+
 // ----------------------------------------------------------------------- RL
 // cmd/chat_rl/main.go:137-154.  mode 0: reward - group mean (the reference).
 // mode 1: (reward - mean) / (population std + 1e-6), float32, a build-side

@@ -294,6 +294,19 @@ def cross_entropy_grad(logits, targets, ignore=-1, scale=1.0, mode=0):
     return grad
 
 
+def distillation(student, teacher, temperature=1.0, mask=None, scale=1.0, want_grad=True):
+    """tensors.DistillationLossPerPosition / DistillationGrad (tensors/loss.go:84-213): losses [rows], valid count, gradient."""
+    student, teacher = f32(student), f32(teacher)
+    rows, vocab = student.shape
+    losses = np.zeros(rows, np.float32)
+    grad = np.zeros((rows, vocab), np.float32) if want_grad else None
+    mk = i32(mask) if mask is not None else None
+    l = lib(); l.or_distillation.restype = C.c_int64
+    valid = l.or_distillation(_f(student), _f(teacher), C.c_int64(rows), vocab, C.c_float(temperature), _i(mk) if mk is not None else None,
+                              C.c_float(scale), _f(losses), _f(grad) if want_grad else None)
+    return losses, int(valid), grad
+
+
 def softcap(x, cap=15.0):
     x = f32(x); d = np.empty_like(x); lib().or_softcap(_f(d), _f(x), C.c_float(cap), C.c_int64(x.size)); return d
 

@@ -151,6 +151,33 @@ def test_policy_gradient_step(oracle, ctx, name, std, B, T, rpp):
     gm.close()
 
 
+@pytest.mark.parametrize("chunk", [7, 32])
+def test_policy_gradient_step_in_small_head_chunks(oracle, ctx, chunk):
+    """lm_head, the loss and lm_head's backward run over chunks of token rows; a chunk that cuts through sequences (7 rows
+    against 40-token sequences) must give the same loss, log-probs and gradients as the oracle's whole-batch pass."""
+    om, gm, cfg = make_pair(oracle, ctx, "c1", std=0.05)
+    V = cfg["vocab_size"]
+    rng = np.random.default_rng(11)
+    B, T = 3, 40
+    ids = rng.integers(0, V - 11, (B, T), dtype=np.int32)
+    tg = rng.integers(0, V, (B, T)).astype(np.int32); tg[:, :13] = -1
+    adv = rng.standard_normal(B).astype(np.float32)
+    om.zero_grad()
+    want_loss, want_nll, want_dl, want_lg = om.policy_gradient_step(ids, tg, adv, float(T + 1), taps=True)
+    ctx.set_option("head_chunk_rows", chunk)
+    try:
+        gm.zero_grad()
+        loss, nll, dl, lg = gm.policy_gradient_step(ids, tg, adv, float(T + 1), rows_per_pass=2, taps=True)
+    finally:
+        ctx.set_option("head_chunk_rows", 16384)
+    assert rel_err(lg, want_lg) <= 1e-3
+    assert abs(loss - want_loss) <= 1e-4 * max(abs(want_loss), 1e-3)
+    assert close_elementwise(nll, want_nll, 1e-4, 1e-5)
+    assert close_elementwise(dl, want_dl, GRAD_REL, 1e-6)
+    assert_gradients_close(gm, om)
+    gm.close()
+
+
 def test_two_contexts_in_one_process_do_not_share_scratch():
     """Two contexts (two streams) with different models, driven from two threads at once: each gets the logits it gets
     alone.  The products' operand-split scratch, split-K workspace and error flag belong to the (device, stream)."""

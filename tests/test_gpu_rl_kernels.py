@@ -163,3 +163,29 @@ def test_loss_properties_at_scale():
     assert np.max(np.abs(g1[1::2].astype(np.float64).sum(axis=1))) <= 1e-6
     assert np.all(g1[::2] == 0) and np.all(nll[::2] == 0)
     assert np.allclose(g2, 2 * g1, rtol=1e-6, atol=1e-12)
+
+
+# tensors/loss_test.go:66-140 on the device, then parity with the oracle at vocabulary scale
+def test_distillation_loss(oracle):
+    from gonano_b200.backend import distillation_loss_backward
+    logits = np.array([[0.5, -1, 2, 0.3], [-0.2, 1.5, -0.5, 0.9]], np.float32)
+    teacher = np.array([[0, 0, 100, 0], [0, 100, 0, 0]], np.float32)
+    losses, valid, mean, grad = distillation_loss_backward(logits, teacher, 1.0)
+    ce, _ = oracle.cross_entropy_per_position(logits, np.array([2, 1], np.int32))
+    assert valid == 2 and abs(mean - float(ce.mean())) <= 1e-3
+    assert np.max(np.abs(grad - oracle.cross_entropy_grad(logits, np.array([2, 1], np.int32), scale=1.0))) <= 1e-3
+    x = oracle.kt_data(8).reshape(2, 4)
+    assert np.max(np.abs(distillation_loss_backward(x, x.copy(), 1.0)[3])) <= 1e-6
+    s2 = np.array([[0.1, 0.2, 0.3], [1, 2, 3]], np.float32); t2 = np.array([[3, 2, 1], [-1, -2, -3]], np.float32)
+    losses, valid, mean, grad = distillation_loss_backward(s2, t2, 1.0, mask=[0, 1])
+    assert valid == 1 and losses[0] == 0 and losses[1] != 0 and not np.any(grad[0]) and np.any(grad[1])
+    rng = np.random.default_rng(5)
+    for rows, vocab, tau in [(24, 32768, 1.0), (9, 1000, 2.0), (6, 65536, 0.7)]:
+        student = softcapped_logits(rng, rows, vocab); teach = softcapped_logits(rng, rows, vocab)
+        mask = (rng.random(rows) < 0.7).astype(np.int32)
+        want_l, want_valid, want_g = oracle.distillation(student, teach, tau, mask=mask, scale=0.5)
+        losses, valid, mean, grad = distillation_loss_backward(student, teach, tau, mask=mask, scale=0.5)
+        assert valid == want_valid
+        assert np.max(np.abs(losses - want_l)) <= 1e-4 * max(1.0, float(np.max(np.abs(want_l))))
+        assert np.max(np.abs(grad - want_g)) <= 1e-4 * float(np.max(np.abs(want_g))) + 1e-9
+        assert abs(mean - float(want_l.sum(dtype=np.float64)) / max(want_valid, 1)) <= 1e-4

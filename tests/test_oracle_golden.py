@@ -212,3 +212,24 @@ def test_simd_port_within_reference_tolerances(oracle):
     o1, l1 = sp.attention_forward(q, k, v, ql, kl, hd, 0, -1)
     o0, l0 = sc.attention_forward(q, k, v, ql, kl, hd, 0, -1)
     assert close(o1, o0, 5e-3, 1e-5) and close(l1, l0, 5e-3, 1e-5)
+
+
+# tensors/loss_test.go:66-140: the distillation loss's own known answers
+def test_distillation_known_answers(oracle):
+    logits = np.array([[0.5, -1, 2, 0.3], [-0.2, 1.5, -0.5, 0.9]], np.float32)
+    teacher = np.array([[0, 0, 100, 0], [0, 100, 0, 0]], np.float32)             # effectively one-hot
+    losses, valid, grad = oracle.distillation(logits, teacher, 1.0)
+    ce, _ = oracle.cross_entropy_per_position(logits, np.array([2, 1], np.int32))
+    assert valid == 2 and abs(float(losses.mean()) - float(ce.mean())) <= 1e-3
+    assert np.max(np.abs(grad - oracle.cross_entropy_grad(logits, np.array([2, 1], np.int32), scale=1.0))) <= 1e-3
+    student = np.array([[0.3, -0.7, 1.1]], np.float32); teach = np.array([[0.8, 0.2, -0.4]], np.float32)
+    _, _, g = oracle.distillation(student, teach, 1.0)
+    for i in range(3):                                                            # numeric gradient, eps 1e-3
+        p = student.copy(); p[0, i] += 1e-3; q = student.copy(); q[0, i] -= 1e-3
+        numeric = (oracle.distillation(p, teach, 1.0)[0][0] - oracle.distillation(q, teach, 1.0)[0][0]) / 2e-3
+        assert abs(numeric - g[0, i]) <= 1e-3
+    x = oracle.kt_data(8).reshape(2, 4)
+    assert np.max(np.abs(oracle.distillation(x, x.copy(), 1.0)[2])) <= 1e-6          # self-distillation: zero gradient
+    s2 = np.array([[0.1, 0.2, 0.3], [1, 2, 3]], np.float32); t2 = np.array([[3, 2, 1], [-1, -2, -3]], np.float32)
+    losses, valid, grad = oracle.distillation(s2, t2, 1.0, mask=[0, 1])
+    assert valid == 1 and losses[0] == 0 and losses[1] != 0 and not np.any(grad[0]) and np.any(grad[1])
