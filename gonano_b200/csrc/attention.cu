@@ -211,6 +211,9 @@ int attention_forward_launch(const AttnShape& sh, const float* q, const float* k
   if (sh.Tq <= 0 || sh.B <= 0) return GN_OK;
   GN_REQUIRE(sh.D > 0 && sh.D <= 128, "attention: head_dim %d outside (0,128]", sh.D);
   GN_REQUIRE(sh.Hkv > 0 && sh.Hq % sh.Hkv == 0, "attention: %d query heads not divisible by %d kv heads", sh.Hq, sh.Hkv);
+#ifdef GN_HAVE_TCGEN05
+  if (sh.tensor && attention_tc_ok(sh, q, k, v, out)) return attention_tc_forward(sh, q, k, v, out, lse, s);
+#endif
   if (sh.tensor && attention_mma_ok(sh, q, k, v, out, nullptr)) return attention_mma_forward(sh, q, k, v, out, lse, s);
   if (fast128_ok(sh, q, k, v, out, nullptr)) return attn_fwd128_go(sh, q, k, v, out, lse, s);
   if (sh.D <= 32) return attn_fwd_go<32>(sh, q, k, v, out, lse, s);

@@ -480,6 +480,9 @@ int gn_ctx_set_option(gn_ctx* c, const char* name, int value) {
   GN_REQUIRE(name, "gn_ctx_set_option: null name");
   const std::string n = name;
   if (n == "decode_prefix_sharing") { attention_decode_prefix_mode(value); return GN_OK; }
+#ifdef GN_HAVE_TCGEN05
+  if (n == "attention_tcgen05") { attention_tc_enable(value); return GN_OK; }
+#endif
   if (c && n == "decode_graph") { c->use_graphs = value != 0; return GN_OK; }
   if (c && n == "head_chunk_rows") { GN_REQUIRE(value >= 1, "head_chunk_rows must be positive"); c->head_chunk_rows = value; return GN_OK; }
   cudaStream_t s = nullptr;
