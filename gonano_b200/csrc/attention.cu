@@ -818,6 +818,10 @@ int attention_backward_launch(const AttnShape& sh, const float* q, const float* 
     GN_LAUNCH_CHECK();
     delta = delta_scratch;
   }
+#ifdef GN_HAVE_TCGEN05
+  if (sh.tensor && attention_tc_backward_ok(sh, q, k, v, dout, dq) && attention_mma_ok(sh, dk, dv, nullptr, nullptr, nullptr))
+    return attention_tc_backward(sh, q, k, v, dout, lse, delta, dq, dk, dv, accumulate, s);
+#endif
   if (sh.tensor && attention_mma_ok(sh, q, k, v, dout, dq) && attention_mma_ok(sh, dk, dv, nullptr, nullptr, nullptr))
     return attention_mma_backward(sh, q, k, v, dout, lse, delta, dq, dk, dv, accumulate, s);
   if (fast128_ok(sh, q, k, v, dout, dq) && fast128_ok(sh, dk, dv, nullptr, nullptr, nullptr))

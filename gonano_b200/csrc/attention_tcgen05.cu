@@ -368,6 +368,244 @@ __global__ void __launch_bounds__(352, 1) attn_tc_fwd_kernel(const __grid_consta
   if (threadIdx.x == 0) AT_TRACE(10);
 }
 
+// ================================================================================================ backward
+// The backward pass materialises the probabilities: with both Q and dO wanted as resident 128-row operands, a
+// flash-style kernel in 3xTF32 (every operand as a hi and a lo copy) does not fit tensor plus shared memory.  Per call:
+//   pack    Q, dO -> [B, Hq, Tp, 128], K, V -> [B, Hkv, Tp, 128] as hi/lo tf32 copies, Tp = T rounded up to 128, the
+//           padding rows zero (so that no tile crosses a sequence and padded rows add nothing to a contraction);
+//   scores  (this file, tcgen05) P = exp(Q K^T - lse) under the causal mask, as hi/lo, [B, Hq, Tp, Tp];
+//   scores  dS = P o (dO V^T - delta), as hi/lo;
+//   dV = P^T dO and dK = dS^T Q summed over the query heads of a kv head (one contraction over (head, query)), and
+//   dQ = dS K: batched products on the tensor-core GEMM, their K loops cut to the causal range.
+// The score kernel is the forward kernel without its second product: the stationary operand (Q or dO) sits in tensor
+// memory as the A operand, K or V streams through a ring of k-block stages (128 keys x 32 channels, hi and lo), the
+// score tile is 128 x 128 in one of two tensor-memory buffers, and 256 threads (two per row) turn it into P or dS and
+// store it.  Used when the sequence is causal from position 0 without an effective window (the training pass);
+// other shapes keep the mma.sync kernels.
+constexpr int SC_STAGES = 6;
+constexpr uint32_t SC_STAGE_BYTES = 32768, SC_BARS = SC_STAGES * SC_STAGE_BYTES;
+constexpr int kSmemScore = SC_BARS + 256 + 1024;
+
+struct ScoreArgs {
+  int mode;                 // 0: P from (Q, K, lse); 1: dS from (dO, V, P, delta)
+  int Hq, Hkv, T, Tp;
+  const float* rowv;        // lse (mode 0) or delta (mode 1), [B, Hq, T]
+  float* out_hi; float* out_lo;   // P or dS
+  const float* p_hi; const float* p_lo;   // mode 1: P
+};
+
+__global__ void __launch_bounds__(256) attn_tc_pack_kernel(AttnShape sh, const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                                                           const float* __restrict__ dout, float* __restrict__ hi, float* __restrict__ lo, int Tp,
+                                                           int64_t off_do, int64_t off_k, int64_t off_v) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t nq = (int64_t)sh.B * sh.Hq * Tp, nk = (int64_t)sh.B * sh.Hkv * Tp;
+  const int64_t idx = (int64_t)blockIdx.x * 8 + warp;
+  if (idx >= 2 * nq + 2 * nk) return;
+  const float* src = nullptr; int64_t dst;
+  if (idx < 2 * nq) {
+    const bool isdo = idx >= nq; const int64_t e = isdo ? idx - nq : idx;
+    const int t = (int)(e % Tp); const int64_t bh = e / Tp; const int h = (int)(bh % sh.Hq); const int64_t b = bh / sh.Hq;
+    if (t < sh.Tq) src = isdo ? dout + b * sh.o_bstride + (int64_t)t * sh.o_tstride + (int64_t)h * AD : q + b * sh.q_bstride + (int64_t)t * sh.q_tstride + (int64_t)h * AD;
+    dst = (isdo ? off_do : 0) + e * AD;
+  } else {
+    const int64_t i = idx - 2 * nq; const bool isv = i >= nk; const int64_t e = isv ? i - nk : i;
+    const int t = (int)(e % Tp); const int64_t bh = e / Tp; const int h = (int)(bh % sh.Hkv); const int64_t b = bh / sh.Hkv;
+    if (t < sh.Tk) src = (isv ? v : k) + b * sh.kv_bstride + (int64_t)t * sh.kv_tstride + (int64_t)h * sh.kv_hstride;
+    dst = (isv ? off_v : off_k) + e * AD;
+  }
+  float4 h4 = make_float4(0, 0, 0, 0), l4 = h4;
+  if (src) {
+    const float4 x = reinterpret_cast<const float4*>(src)[lane];
+    split_tf32_int(x.x, h4.x, l4.x); split_tf32_int(x.y, h4.y, l4.y); split_tf32_int(x.z, h4.z, l4.z); split_tf32_int(x.w, h4.w, l4.w);
+  }
+  reinterpret_cast<float4*>(hi + dst)[lane] = h4;
+  reinterpret_cast<float4*>(lo + dst)[lane] = l4;
+}
+
+// Batch tables of the three products: by (sequence, query head) for dQ, by (sequence, kv head) for dK / dV.
+__global__ void attn_tc_batches_kernel(TcBatch* by_q, TcBatch* by_kv, int B, int Hq, int Hkv, int Tp, int64_t q_bstride, int64_t kv_bstride, int64_t kv_hstride) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int gq = Hq / Hkv;
+  if (i < B * Hq) {
+    const int b = i / Hq, h = i % Hq, hk = h / gq;
+    TcBatch t; t.a_m = i * Tp; t.a_k = 0; t.b_n = 0; t.b_k = (b * Hkv + hk) * Tp; t.c_off = (long long)b * q_bstride + (long long)h * AD;
+    by_q[i] = t;
+  }
+  if (i < B * Hkv) {
+    const int b = i / Hkv, hk = i % Hkv;
+    TcBatch t; t.a_m = 0; t.a_k = (b * Hq + hk * gq) * Tp; t.b_n = 0; t.b_k = t.a_k; t.c_off = (long long)b * kv_bstride + (long long)hk * kv_hstride;
+    by_kv[i] = t;
+  }
+}
+
+__global__ void __launch_bounds__(320, 1) attn_tc_score_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
+                                                               const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
+                                                               ScoreArgs p, int* err) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bars = base + SC_BARS;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (SC_STAGES + s); };
+  auto s_full = [&](int b) { return bars + 8u * (2 * SC_STAGES + b); };
+  auto s_empty = [&](int b) { return bars + 8u * (2 * SC_STAGES + 2 + b); };
+  const uint32_t q_done = bars + 8u * (2 * SC_STAGES + 4);
+  const uint32_t tmem_slot = bars + 8u * (2 * SC_STAGES + 5);
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen + SC_BARS + 8 * (2 * SC_STAGES + 5));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * AQ;   // the long tiles first
+  const int h = blockIdx.y, b = blockIdx.z, hk = h / (p.Hq / p.Hkv);
+  const int n = q0 / 128 + 1;                                     // key steps of 128: keys [0, q0 + 128)
+  const int a_row0 = (b * p.Hq + h) * p.Tp + q0, b_row0 = (b * p.Hkv + hk) * p.Tp;
+  const int total = 4 + 4 * n;                                    // ring iterations: 4 k-blocks of A, then 4 per key step
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < SC_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(s_full(i), 1); mbar_init(s_empty(i), 256); }
+    mbar_init(q_done, 256);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+  bool failed = false;
+  pdl_wait();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- TMA producer: the ring of k-block stages
+    if (lane == 0) {
+      for (int it = 0; it < total; ++it) {
+        const int s = it % SC_STAGES;
+        if (it >= SC_STAGES && !mbar_wait(empty_bar(s), (uint32_t)(it / SC_STAGES - 1) & 1u)) { failed = true; break; }
+        const uint32_t st = base + (uint32_t)s * SC_STAGE_BYTES;
+        mbar_expect_tx(full_bar(s), SC_STAGE_BYTES);
+        if (it < 4) {
+          tma_load_2d(st, &tmAh, full_bar(s), it * 32, a_row0);
+          tma_load_2d(st + 16384, &tmAl, full_bar(s), it * 32, a_row0);
+        } else {
+          const int j = (it - 4) >> 2, kb = (it - 4) & 3;
+          tma_load_2d(st, &tmBh, full_bar(s), kb * 32, b_row0 + j * 128);
+          tma_load_2d(st + 16384, &tmBl, full_bar(s), kb * 32, b_row0 + j * 128);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idS = instr_desc_tf32(AQ, 128);
+      if (!mbar_wait(q_done, 0u)) failed = true;
+      tc_fence_after();
+      for (int j = 0; j < n && !failed; ++j) {
+        if (j >= 2 && !mbar_wait(s_empty(j & 1), (uint32_t)((j >> 1) - 1) & 1u)) { failed = true; break; }
+        const uint32_t d = tmem_base + 256u + (uint32_t)(j & 1) * 128u;
+        for (int kb = 0; kb < 4; ++kb) {
+          const int it = 4 + 4 * j + kb, s = it % SC_STAGES;
+          if (!mbar_wait(full_bar(s), (uint32_t)(it / SC_STAGES) & 1u)) { failed = true; break; }
+          tc_fence_after();
+          const uint32_t st = base + (uint32_t)s * SC_STAGE_BYTES;
+          const uint64_t bh = smem_desc_sw128(st), bl = smem_desc_sw128(st + 16384);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint32_t ah = tmem_base + kb * 32 + ks * 8, al = tmem_base + 128 + kb * 32 + ks * 8;
+            umma_tf32_ts(d, al, bh + 2u * ks, idS, (kb > 0 || ks > 0) ? 1u : 0u);
+            umma_tf32_ts(d, ah, bl + 2u * ks, idS, 1u);
+            umma_tf32_ts(d, ah, bh + 2u * ks, idS, 1u);
+          }
+          umma_commit(empty_bar(s));
+        }
+        if (!failed) umma_commit(s_full(j & 1));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- 256 threads, two per query row
+    const int quarter = warp & 3, half = ((warp - 2) >> 2) & 1;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t sw = (uint32_t)(row & 7);
+    // the stationary operand: ring stages 0..3 -> tensor memory (half 0 moves hi to columns [0,128), half 1 lo to [128,256))
+    for (int kb = 0; kb < 4 && !failed; ++kb) {
+      if (!mbar_wait(full_bar(kb), 0u)) { failed = true; break; }
+      const uint8_t* src = gen + kb * SC_STAGE_BYTES + half * 16384 + row * 128;
+      uint32_t r[32];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint4 x = *reinterpret_cast<const uint4*>(src + ((c ^ sw) << 4));
+        r[4 * c] = x.x; r[4 * c + 1] = x.y; r[4 * c + 2] = x.z; r[4 * c + 3] = x.w;
+      }
+      tmem_st32(lane_addr + half * 128 + kb * 32, r);
+      asm volatile("bar.sync 1, 256;" ::: "memory");          // every thread has read the stage
+      if (threadIdx.x == 64) mbar_arrive(empty_bar(kb));
+    }
+    tmem_st_wait();
+    tc_fence_before();
+    mbar_arrive(q_done);
+    const int q = q0 + row;
+    const float rv = q < p.T ? p.rowv[((int64_t)b * p.Hq + h) * p.T + q] : 0.0f;
+    const int64_t orow = ((int64_t)(b * p.Hq + h) * p.Tp + q) * p.Tp;
+    constexpr float kLog2e = 1.4426950408889634f;
+    for (int j = 0; j < n && !failed; ++j) {
+      if (!mbar_wait(s_full(j & 1), (uint32_t)(j >> 1) & 1u)) { failed = true; break; }
+      tc_fence_after();
+      const int key0 = j * 128 + half * 64;
+#pragma unroll
+      for (int c0 = 0; c0 < 64; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(lane_addr + 256u + (uint32_t)(j & 1) * 128u + half * 64 + c0, r);
+        tmem_ld_wait();
+        if (c0 == 32) { tc_fence_before(); mbar_arrive(s_empty(j & 1)); }   // both halves of the row are in registers
+        float* oh = p.out_hi + orow + key0 + c0;
+        float* ol = p.out_lo + orow + key0 + c0;
+        const int lim = min(q, p.T - 1) - (key0 + c0);   // columns [0, lim] are valid keys of this row
+        const bool live = q < p.T;
+        if (p.mode == 0) {
+          const float mneg = -rv * kLog2e;
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            float hv[4], lv[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              float e = exp2f(fmaf(__uint_as_float(r[i + t]), kLog2e, mneg));
+              e = (live && i + t <= lim) ? e : 0.0f;
+              hv[t] = __uint_as_float(__float_as_uint(e) & 0xFFFFE000u);
+              lv[t] = e - hv[t];
+            }
+            *reinterpret_cast<float4*>(oh + i) = make_float4(hv[0], hv[1], hv[2], hv[3]);
+            *reinterpret_cast<float4*>(ol + i) = make_float4(lv[0], lv[1], lv[2], lv[3]);
+          }
+        } else {
+          const float* ph = p.p_hi + orow + key0 + c0;
+          const float* pl = p.p_lo + orow + key0 + c0;
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float4 a = *reinterpret_cast<const float4*>(ph + i), c = *reinterpret_cast<const float4*>(pl + i);
+            const float pv[4] = {a.x + c.x, a.y + c.y, a.z + c.z, a.w + c.w};
+            float hv[4], lv[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              float e = pv[t] * (__uint_as_float(r[i + t]) - rv);
+              e = (live && i + t <= lim) ? e : 0.0f;
+              hv[t] = __uint_as_float(__float_as_uint(e) & 0xFFFFE000u);
+              lv[t] = e - hv[t];
+            }
+            *reinterpret_cast<float4*>(oh + i) = make_float4(hv[0], hv[1], hv[2], hv[3]);
+            *reinterpret_cast<float4*>(ol + i) = make_float4(lv[0], lv[1], lv[2], lv[3]);
+          }
+        }
+      }
+    }
+  }
+  if (failed) {
+    atomicExch(err, 1);
+    for (int i = 0; i < 4096; ++i) __nanosleep(256);   // let bulk copies that are still in flight land
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
 }  // namespace
 
 #ifdef GN_TC_TRACE
@@ -414,6 +652,76 @@ int attention_tc_forward(const AttnShape& sh, const float* q, const float* k, co
   GN_REQUIRE(sh.B <= 65535 && sh.Hq <= 65535, "attention: %d sequences x %d heads exceed the grid", sh.B, sh.Hq);
   attn_tc_fwd_kernel<<<grid, 352, kSmemFwd, s>>>(mqh, mql, mkh, mkl, mvh, mvl, p, err);
   GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+// Whether the backward pass of this shape runs on the tensor-core path: causal from position 0, no effective
+// window, no segment mask; its scratch (P and dS as hi/lo, 16 bytes per score) below 8 GiB.
+bool attention_tc_backward_ok(const AttnShape& sh, const void* p0, const void* p1, const void* p2, const void* p3, const void* p4) {
+  if (!attention_tc_ok(sh, p0, p1, p2, p3) || (reinterpret_cast<uintptr_t>(p4) & 15) != 0) return false;
+  if (sh.Tq != sh.Tk || sh.offset0 != 0 || (sh.window >= 0 && sh.window < sh.Tk - 1)) return false;
+  const int64_t Tp = (int64_t)(sh.Tq + 127) / 128 * 128;
+  if ((int64_t)sh.B * sh.Hq * Tp >= (1ll << 31) / 2) return false;
+  return (int64_t)sh.B * sh.Hq * Tp * Tp * 16 <= (8ll << 30);
+}
+
+int attention_tc_backward(const AttnShape& sh, const float* q, const float* k, const float* v, const float* dout, const float* lse, const float* delta,
+                          float* dq, float* dk, float* dv, int accumulate, cudaStream_t s) {
+  const int Tp = (sh.Tq + 127) / 128 * 128;
+  const int64_t nQ = (int64_t)sh.B * sh.Hq * Tp * AD, nK = (int64_t)sh.B * sh.Hkv * Tp * AD, nP = (int64_t)sh.B * sh.Hq * Tp * Tp;
+  const int64_t off_do = nQ, off_k = 2 * nQ, off_v = 2 * nQ + nK, off_p = 2 * nQ + 2 * nK, off_ds = off_p + nP;
+  const int nbq = sh.B * sh.Hq, nbk = sh.B * sh.Hkv;
+  const int64_t tab_floats = ((int64_t)(nbq + nbk) * (int64_t)sizeof(TcBatch) + 3) / 4 + 64;
+  float *hi = nullptr, *lo = nullptr; int* err = nullptr;
+  GN_TRY(tc_attention_scratch(s, (size_t)(off_ds + nP + tab_floats), &hi, &lo, &err));
+  TcBatch* by_q = reinterpret_cast<TcBatch*>(hi + (off_ds + nP + 63) / 64 * 64);
+  TcBatch* by_kv = by_q + nbq;
+  {
+    const int64_t warps = 2 * (int64_t)sh.B * sh.Hq * Tp + 2 * (int64_t)sh.B * sh.Hkv * Tp;
+    attn_tc_pack_kernel<<<(unsigned)ceil_div(warps, 8), 256, 0, s>>>(sh, q, k, v, dout, hi, lo, Tp, off_do, off_k, off_v);
+    GN_LAUNCH_CHECK();
+    attn_tc_batches_kernel<<<ceil_div(nbq, 256), 256, 0, s>>>(by_q, by_kv, sh.B, sh.Hq, sh.Hkv, Tp, sh.q_bstride, sh.kv_bstride, sh.kv_hstride);
+    GN_LAUNCH_CHECK();
+  }
+  static bool configured = false;
+  if (!configured) { GN_CUDA(cudaFuncSetAttribute(attn_tc_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemScore)); configured = true; }
+  GN_REQUIRE(sh.B <= 65535 && sh.Hq <= 65535, "attention: %d sequences x %d heads exceed the grid", sh.B, sh.Hq);
+  const dim3 grid(Tp / AQ, sh.Hq, sh.B);
+  for (int mode = 0; mode < 2; ++mode) {
+    CUtensorMap mah, mal, mbh, mbl;
+    const int64_t ao = mode ? off_do : 0, bo = mode ? off_v : off_k;
+    GN_TRY(tc_make_map(&mah, hi + ao, (int64_t)nbq * Tp, AD, AD, AQ));
+    GN_TRY(tc_make_map(&mal, lo + ao, (int64_t)nbq * Tp, AD, AD, AQ));
+    GN_TRY(tc_make_map(&mbh, hi + bo, (int64_t)nbk * Tp, AD, AD, 128));
+    GN_TRY(tc_make_map(&mbl, lo + bo, (int64_t)nbk * Tp, AD, AD, 128));
+    ScoreArgs a{};
+    a.mode = mode; a.Hq = sh.Hq; a.Hkv = sh.Hkv; a.T = sh.Tq; a.Tp = Tp; a.rowv = mode ? delta : lse;
+    a.out_hi = hi + (mode ? off_ds : off_p); a.out_lo = lo + (mode ? off_ds : off_p); a.p_hi = hi + off_p; a.p_lo = lo + off_p;
+    attn_tc_score_kernel<<<grid, 320, kSmemScore, s>>>(mah, mal, mbh, mbl, a, err);
+    GN_LAUNCH_CHECK();
+  }
+  const int gq = sh.Hq / sh.Hkv;
+  // dV = P^T dO, dK = dS^T Q: rows = keys, contraction over (query head of the group, query >= key tile)
+  for (int which = 0; which < 2; ++which) {
+    TcBatched g{};
+    const int64_t po = which ? off_ds : off_p, xo = which ? 0 : off_do;
+    g.a = TcOperand{hi + po, lo + po, (int64_t)nbq * Tp, Tp, Tp, 1};
+    g.b = TcOperand{hi + xo, lo + xo, (int64_t)nbq * Tp, AD, AD, 1};
+    g.M = sh.Tk; g.N = AD; g.K = gq * Tp;
+    g.C = which ? dk : dv; g.ldc = sh.kv_tstride; g.accumulate = accumulate;
+    g.batch = by_kv; g.batches = nbk; g.k_segments = gq; g.k_seg_stride = Tp / 32; g.k_causal = 2;
+    GN_TRY(gemm_tc_batched(g, s));
+  }
+  // dQ = dS K: rows = queries, contraction over the keys up to the tile's last query
+  {
+    TcBatched g{};
+    g.a = TcOperand{hi + off_ds, lo + off_ds, (int64_t)nbq * Tp, Tp, Tp, 0};
+    g.b = TcOperand{hi + off_k, lo + off_k, (int64_t)nbk * Tp, AD, AD, 1};
+    g.M = sh.Tq; g.N = AD; g.K = Tp;
+    g.C = dq; g.ldc = sh.q_tstride; g.accumulate = accumulate;
+    g.batch = by_q; g.batches = nbq; g.k_segments = 0; g.k_seg_stride = 0; g.k_causal = 1;
+    GN_TRY(gemm_tc_batched(g, s));
+  }
   return GN_OK;
 }
 

@@ -58,6 +58,11 @@ struct TcEpilogue {
   // that are in flight together cover tiles_gn column tiles x a few row tiles and both operands are re-read from L2,
   // not from HBM (with plain row-major order a 49 k x 32768 product re-reads its 201 MB of weights for every row tile).
   int tiles_total, tiles_n, tiles_gn;
+  // Batched product (one-tile form only): blockIdx.z selects an entry of `batch`.  The K loop of a tile walks
+  // k_segments segments of the contraction index, k_seg_stride k-blocks apart (0 segments = the plain loop); k_causal
+  // cuts each segment to the k-blocks in which a causal operand is non-zero: 1 = k < m0 + 128 (the contraction runs over
+  // keys, the rows are queries), 2 = k >= m0 (the contraction runs over queries, the rows are keys).
+  const TcBatch* batch; int k_segments, k_seg_stride, k_causal;
 };
 
 #ifdef GN_TC_TRACE
@@ -151,13 +156,30 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
     else { tm0 = m0; tn0 = n0; tb0 = b_row0; }
   };
   // split-K: CTA z works on k-blocks [kb0, kb0 + nk) and writes a partial tile
+  const bool batched = !PERSIST && ep.batch != nullptr;
+  const int zsplits = batched ? 1 : (int)gridDim.z, zi = batched ? 0 : (int)blockIdx.z;
   const int nk_total = (K + TBK - 1) / TBK;
-  const int per_split = (nk_total + (int)gridDim.z - 1) / (int)gridDim.z;
-  const int kb0 = (int)blockIdx.z * per_split;
-  const int nk = max(0, min(per_split, nk_total - kb0));
+  const int per_split = (nk_total + zsplits - 1) / zsplits;
+  const int kb0 = zi * per_split;
+  int nk = max(0, min(per_split, nk_total - kb0));
+  int a_m_off = 0, a_k_off = 0, b_n_off = 0, b_k_off = 0, seg_nk = 1, seg_kb0 = 0, seg_stride = 0;
+  if (batched) {
+    const TcBatch bt = ep.batch[blockIdx.z];
+    a_m_off = bt.a_m; a_k_off = bt.a_k; b_n_off = bt.b_n; b_k_off = bt.b_k;
+    ep.C += bt.c_off;
+    const int segs = max(1, ep.k_segments);
+    seg_stride = ep.k_segments > 0 ? ep.k_seg_stride : 0;
+    const int seg_total = ep.k_segments > 0 ? ep.k_seg_stride : nk_total;
+    seg_kb0 = ep.k_causal == 2 ? min(seg_total, m0 / TBK) : 0;
+    seg_nk = ep.k_causal == 1 ? min(seg_total, (m0 + TBM) / TBK) : seg_total - seg_kb0;
+    nk = segs * seg_nk;
+    if (seg_nk <= 0) { seg_nk = 1; nk = 0; }
+  }
+  // first element of the contraction index of this CTA's k-block number kb
+  auto kcoord = [&](int kb) { return batched ? ((kb / seg_nk) * seg_stride + seg_kb0 + kb % seg_nk) * TBK : (kb0 + kb) * TBK; };
   constexpr int chunk_blocks = PERSIST ? kChunkBlocksPersistent : kChunkBlocks;
   const int nchunks = (nk + chunk_blocks - 1) / chunk_blocks;
-  if (gridDim.z > 1) ep.C += (int64_t)blockIdx.z * ep.split_stride;
+  if (zsplits > 1) ep.C += (int64_t)blockIdx.z * ep.split_stride;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -190,31 +212,32 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
           const uint32_t st = base + (uint32_t)s * S::STAGE_BYTES;
           if (it < 256) TC_TRACE(it);
           mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
+          const int kc = kcoord(kb);
           if (ep.a_mn == 2) {   // the whole MN-major tile as one 3-D box (MN a multiple of 32)
-            tma_load_3d(st, &tmAh, full_bar(s), 0, (kb0 + kb) * TBK, tm0 / 32);
-            tma_load_3d(st + S::A_BYTES, &tmAl, full_bar(s), 0, (kb0 + kb) * TBK, tm0 / 32);
+            tma_load_3d(st, &tmAh, full_bar(s), 0, kc, tm0 / 32);
+            tma_load_3d(st + S::A_BYTES, &tmAl, full_bar(s), 0, kc, tm0 / 32);
           } else if (ep.a_mn) {
 #pragma unroll
             for (int j = 0; j < TBM / 32; ++j) {
-              tma_load_2d(st + j * 4096, &tmAh, full_bar(s), tm0 + 32 * j, (kb0 + kb) * TBK);
-              tma_load_2d(st + S::A_BYTES + j * 4096, &tmAl, full_bar(s), tm0 + 32 * j, (kb0 + kb) * TBK);
+              tma_load_2d(st + j * 4096, &tmAh, full_bar(s), tm0 + 32 * j + a_m_off, kc + a_k_off);
+              tma_load_2d(st + S::A_BYTES + j * 4096, &tmAl, full_bar(s), tm0 + 32 * j + a_m_off, kc + a_k_off);
             }
           } else {
-            tma_load_2d(st, &tmAh, full_bar(s), (kb0 + kb) * TBK, tm0);
-            tma_load_2d(st + S::A_BYTES, &tmAl, full_bar(s), (kb0 + kb) * TBK, tm0);
+            tma_load_2d(st, &tmAh, full_bar(s), kc + a_k_off, tm0 + a_m_off);
+            tma_load_2d(st + S::A_BYTES, &tmAl, full_bar(s), kc + a_k_off, tm0 + a_m_off);
           }
           if (ep.b_mn == 2) {
-            tma_load_3d(st + 2 * S::A_BYTES, &tmBh, full_bar(s), 0, (kb0 + kb) * TBK, tb0 / 32);
-            tma_load_3d(st + 2 * S::A_BYTES + S::B_BYTES, &tmBl, full_bar(s), 0, (kb0 + kb) * TBK, tb0 / 32);
+            tma_load_3d(st + 2 * S::A_BYTES, &tmBh, full_bar(s), 0, kc, tb0 / 32);
+            tma_load_3d(st + 2 * S::A_BYTES + S::B_BYTES, &tmBl, full_bar(s), 0, kc, tb0 / 32);
           } else if (ep.b_mn) {
 #pragma unroll
             for (int j = 0; j < BN / 32; ++j) {
-              tma_load_2d(st + 2 * S::A_BYTES + j * 4096, &tmBh, full_bar(s), tb0 + 32 * j, (kb0 + kb) * TBK);
-              tma_load_2d(st + 2 * S::A_BYTES + S::B_BYTES + j * 4096, &tmBl, full_bar(s), tb0 + 32 * j, (kb0 + kb) * TBK);
+              tma_load_2d(st + 2 * S::A_BYTES + j * 4096, &tmBh, full_bar(s), tb0 + 32 * j + b_n_off, kc + b_k_off);
+              tma_load_2d(st + 2 * S::A_BYTES + S::B_BYTES + j * 4096, &tmBl, full_bar(s), tb0 + 32 * j + b_n_off, kc + b_k_off);
             }
           } else {
-            tma_load_2d(st + 2 * S::A_BYTES, &tmBh, full_bar(s), (kb0 + kb) * TBK, tb0);
-            tma_load_2d(st + 2 * S::A_BYTES + S::B_BYTES, &tmBl, full_bar(s), (kb0 + kb) * TBK, tb0);
+            tma_load_2d(st + 2 * S::A_BYTES, &tmBh, full_bar(s), kc + b_k_off, tb0 + b_n_off);
+            tma_load_2d(st + 2 * S::A_BYTES + S::B_BYTES, &tmBl, full_bar(s), kc + b_k_off, tb0 + b_n_off);
           }
         }
       }
@@ -1187,6 +1210,35 @@ int tc_attention_scratch(cudaStream_t s, size_t floats, float** hi, float** lo, 
   GN_TRY(state_for(s, &st));
   GN_TRY(ensure_buf(st->attn, floats));
   *hi = st->attn.hi; *lo = st->attn.lo; *err_flag = st->err_flag;
+  return GN_OK;
+}
+
+int gemm_tc_batched(const TcBatched& g, cudaStream_t s) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  GemmState* st = nullptr;
+  GN_TRY(state_for(s, &st));
+  GN_TRY(ensure_init());
+  using S = TcSmem<128, 3>;
+  static bool configured = false;
+  if (!configured) { GN_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<128, 3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL - S::STG_BYTES)); configured = true; }
+  GN_REQUIRE(g.batches >= 1 && g.batches <= 65535 && g.batch != nullptr, "batched product: %d batches", g.batches);
+  CUtensorMap mah, mal, mbh, mbl;
+  if (g.a.mn) { GN_TRY(make_map_mn(&mah, g.a.hi, g.a.cols, g.a.rows, g.a.ld)); GN_TRY(make_map_mn(&mal, g.a.lo, g.a.cols, g.a.rows, g.a.ld)); }
+  else { GN_TRY(make_map(&mah, g.a.hi, g.a.rows, g.a.cols, g.a.ld, TBM)); GN_TRY(make_map(&mal, g.a.lo, g.a.rows, g.a.cols, g.a.ld, TBM)); }
+  if (g.b.mn) { GN_TRY(make_map_mn(&mbh, g.b.hi, g.b.cols, g.b.rows, g.b.ld)); GN_TRY(make_map_mn(&mbl, g.b.lo, g.b.cols, g.b.rows, g.b.ld)); }
+  else { GN_TRY(make_map(&mbh, g.b.hi, g.b.rows, g.b.cols, g.b.ld, 128)); GN_TRY(make_map(&mbl, g.b.lo, g.b.rows, g.b.cols, g.b.ld, 128)); }
+  TcEpilogue ep{};
+  ep.C = g.C; ep.ldc = g.ldc; ep.epi = g.accumulate ? EPI_ACCUM : EPI_STORE; ep.scalar = 1.0f;
+  ep.a_mn = g.a.mn ? 1 : 0; ep.b_mn = g.b.mn ? 1 : 0;
+  ep.batch = g.batch; ep.k_segments = g.k_segments; ep.k_seg_stride = g.k_seg_stride; ep.k_causal = g.k_causal;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(ceil_div(g.N, 128), ceil_div(g.M, TBM), g.batches); cfg.blockDim = dim3(64 + 32 * 4); cfg.dynamicSmemBytes = S::TOTAL - S::STG_BYTES; cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 0;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  GN_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<128, 3, false>, mah, mal, mbh, mbl, ep, g.M, g.N, g.K, st->err_flag));
+  GN_LAUNCH_CHECK();
   return GN_OK;
 }
 

@@ -64,6 +64,9 @@ int attention_mma_forward(const AttnShape& sh, const float* q, const float* k, c
 // head_dim 128 forward on tcgen05 (attention_tcgen05.cu); preferred over the mma.sync kernel when sh.tensor is set.
 bool attention_tc_ok(const AttnShape& sh, const void* p0, const void* p1, const void* p2, const void* p3);
 int attention_tc_forward(const AttnShape& sh, const float* q, const float* k, const float* v, float* out, float* lse, cudaStream_t s);
+bool attention_tc_backward_ok(const AttnShape& sh, const void* p0, const void* p1, const void* p2, const void* p3, const void* p4);
+int attention_tc_backward(const AttnShape& sh, const float* q, const float* k, const float* v, const float* dout, const float* lse, const float* delta,
+                          float* dq, float* dk, float* dv, int accumulate, cudaStream_t s);
 void attention_tc_enable(int on);   // 0: keep head_dim 128 attention on the mma.sync kernels
 int attention_mma_backward(const AttnShape& sh, const float* q, const float* k, const float* v, const float* dout, const float* lse, const float* delta,
                            float* dq, float* dk, float* dv, int accumulate, cudaStream_t s);

@@ -149,6 +149,24 @@ __device__ __forceinline__ void split_tf32_int(float x, float& hi, float& lo) {
 
 }  // namespace
 
+// Batched product on the one-tile form of the tensor-core GEMM (gemm_tcgen05.cu):
+//   C_z[M, N] (+)= A_z[M, K] * B_z[N, K]^T   for z in [0, batches)
+// A and B are 2-D float32 arrays given as hi/lo tf32 splits; K-major (mn = 0): rows = the m (or n) index, cols = k;
+// MN-major (mn = 1): rows = k, cols = the m (or n) index.  A batch is a window of the arrays: its offsets (device
+// array, one TcBatch per batch) are added to the tile coordinates in the operand's (m or n, k) index space, c_off
+// (floats) to C.  The contraction may walk k_segments segments k_seg_stride 32-element blocks apart, each cut to the
+// causal range: k_causal 1 = k < m0 + 128, 2 = k >= m0 (m0 the tile's first row); 0 segments = the plain K loop.
+struct TcBatch { int a_m, a_k, b_n, b_k; long long c_off; };
+struct TcOperand { const float* hi; const float* lo; int64_t rows, cols, ld; int mn; };
+struct TcBatched {
+  TcOperand a, b;
+  int M, N, K;
+  float* C; int64_t ldc; int accumulate;
+  const TcBatch* batch; int batches;
+  int k_segments, k_seg_stride, k_causal;
+};
+int gemm_tc_batched(const TcBatched& g, cudaStream_t s);
+
 // Host side (gemm_tcgen05.cu): tensor maps over float32 arrays and the per-(device, stream) scratch of the attention kernels.
 // K-major: a box is [32 floats x box_rows rows] of a row-major [rows, k] array (pitch ld floats), 128-byte swizzle.
 int tc_make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t k, int64_t ld, int box_rows);
