@@ -382,9 +382,9 @@ __global__ void __launch_bounds__(352, 1) attn_tc_fwd_kernel(const __grid_consta
 // score tile is 128 x 128 in one of two tensor-memory buffers, and 256 threads (two per row) turn it into P or dS and
 // store it.  Used when the sequence is causal from position 0 without an effective window (the training pass);
 // other shapes keep the mma.sync kernels.
-constexpr int SC_STAGES = 6;
-constexpr uint32_t SC_STAGE_BYTES = 32768, SC_BARS = SC_STAGES * SC_STAGE_BYTES;
-constexpr int kSmemScore = SC_BARS + 256 + 1024;
+constexpr int SC_STAGES = 5;
+constexpr uint32_t SC_STAGE_BYTES = 32768, SC_BARS = SC_STAGES * SC_STAGE_BYTES, SC_STG = SC_BARS + 256;
+constexpr int kSmemScore = SC_STG + 8 * 32 * 36 * 4 + 1024;   // stages, barriers, one staging tile per warp, alignment slack
 
 struct ScoreArgs {
   int mode;                 // 0: P from (Q, K, lse); 1: dS from (dO, V, P, delta)
@@ -544,7 +544,9 @@ __global__ void __launch_bounds__(320, 1) attn_tc_score_kernel(const __grid_cons
     mbar_arrive(q_done);
     const int q = q0 + row;
     const float rv = q < p.T ? p.rowv[((int64_t)b * p.Hq + h) * p.T + q] : 0.0f;
-    const int64_t orow = ((int64_t)(b * p.Hq + h) * p.Tp + q) * p.Tp;
+    const int64_t wbase = ((int64_t)(b * p.Hq + h) * p.Tp + q0 + quarter * 32) * p.Tp;   // row 0 of this warp's 32 rows
+    float* stg = reinterpret_cast<float*>(gen + SC_STG) + (warp - 2) * (32 * 36);
+    const int rr0 = lane >> 3, cc = (lane & 7) * 4;
     constexpr float kLog2e = 1.4426950408889634f;
     for (int j = 0; j < n && !failed; ++j) {
       if (!mbar_wait(s_full(j & 1), (uint32_t)(j >> 1) & 1u)) { failed = true; break; }
@@ -556,43 +558,61 @@ __global__ void __launch_bounds__(320, 1) attn_tc_score_kernel(const __grid_cons
         tmem_ld32(lane_addr + 256u + (uint32_t)(j & 1) * 128u + half * 64 + c0, r);
         tmem_ld_wait();
         if (c0 == 32) { tc_fence_before(); mbar_arrive(s_empty(j & 1)); }   // both halves of the row are in registers
-        float* oh = p.out_hi + orow + key0 + c0;
-        float* ol = p.out_lo + orow + key0 + c0;
+        // The thread owns a row, a store wants a row segment: values pass through a 32 x 32 staging tile of the warp
+        // (pitch 36 floats: conflict-free float4 rows), eight lanes then write the 128 contiguous bytes of a row.
         const int lim = min(q, p.T - 1) - (key0 + c0);   // columns [0, lim] are valid keys of this row
         const bool live = q < p.T;
+        const int64_t gbase = wbase + key0 + c0;
+        float e[32];
         if (p.mode == 0) {
           const float mneg = -rv * kLog2e;
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            float hv[4], lv[4];
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-              float e = exp2f(fmaf(__uint_as_float(r[i + t]), kLog2e, mneg));
-              e = (live && i + t <= lim) ? e : 0.0f;
-              hv[t] = __uint_as_float(__float_as_uint(e) & 0xFFFFE000u);
-              lv[t] = e - hv[t];
-            }
-            *reinterpret_cast<float4*>(oh + i) = make_float4(hv[0], hv[1], hv[2], hv[3]);
-            *reinterpret_cast<float4*>(ol + i) = make_float4(lv[0], lv[1], lv[2], lv[3]);
+          for (int i = 0; i < 32; ++i) {
+            const float x = exp2f(fmaf(__uint_as_float(r[i]), kLog2e, mneg));
+            e[i] = (live && i <= lim) ? x : 0.0f;
           }
         } else {
-          const float* ph = p.p_hi + orow + key0 + c0;
-          const float* pl = p.p_lo + orow + key0 + c0;
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int rr = it * 4 + rr0;
+            const float4 a = *reinterpret_cast<const float4*>(p.p_hi + gbase + (int64_t)rr * p.Tp + cc);
+            const float4 c = *reinterpret_cast<const float4*>(p.p_lo + gbase + (int64_t)rr * p.Tp + cc);
+            *reinterpret_cast<float4*>(stg + rr * 36 + cc) = make_float4(a.x + c.x, a.y + c.y, a.z + c.z, a.w + c.w);
+          }
+          __syncwarp();
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
-            const float4 a = *reinterpret_cast<const float4*>(ph + i), c = *reinterpret_cast<const float4*>(pl + i);
-            const float pv[4] = {a.x + c.x, a.y + c.y, a.z + c.z, a.w + c.w};
-            float hv[4], lv[4];
+            const float4 pv = *reinterpret_cast<const float4*>(stg + lane * 36 + i);
+            const float pa[4] = {pv.x, pv.y, pv.z, pv.w};
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
-              float e = pv[t] * (__uint_as_float(r[i + t]) - rv);
-              e = (live && i + t <= lim) ? e : 0.0f;
-              hv[t] = __uint_as_float(__float_as_uint(e) & 0xFFFFE000u);
-              lv[t] = e - hv[t];
+              const float x = pa[t] * (__uint_as_float(r[i + t]) - rv);
+              e[i + t] = (live && i + t <= lim) ? x : 0.0f;
             }
-            *reinterpret_cast<float4*>(oh + i) = make_float4(hv[0], hv[1], hv[2], hv[3]);
-            *reinterpret_cast<float4*>(ol + i) = make_float4(lv[0], lv[1], lv[2], lv[3]);
           }
+          __syncwarp();
+        }
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {
+          // part 0: hi = the value cut to tf32; part 1: lo = value - hi (exact; the tensor core reads its leading bits)
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            float o[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const float hv = __uint_as_float(__float_as_uint(e[i + t]) & 0xFFFFE000u);
+              o[t] = part == 0 ? hv : e[i + t] - hv;
+            }
+            *reinterpret_cast<float4*>(stg + lane * 36 + i) = make_float4(o[0], o[1], o[2], o[3]);
+          }
+          __syncwarp();
+          float* out = part == 0 ? p.out_hi : p.out_lo;
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int rr = it * 4 + rr0;
+            *reinterpret_cast<float4*>(out + gbase + (int64_t)rr * p.Tp + cc) = *reinterpret_cast<const float4*>(stg + rr * 36 + cc);
+          }
+          __syncwarp();
         }
       }
     }

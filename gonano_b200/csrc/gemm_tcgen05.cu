@@ -214,8 +214,8 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
           mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
           const int kc = kcoord(kb);
           if (ep.a_mn == 2) {   // the whole MN-major tile as one 3-D box (MN a multiple of 32)
-            tma_load_3d(st, &tmAh, full_bar(s), 0, kc, tm0 / 32);
-            tma_load_3d(st + S::A_BYTES, &tmAl, full_bar(s), 0, kc, tm0 / 32);
+            tma_load_3d(st, &tmAh, full_bar(s), 0, kc + a_k_off, (tm0 + a_m_off) / 32);
+            tma_load_3d(st + S::A_BYTES, &tmAl, full_bar(s), 0, kc + a_k_off, (tm0 + a_m_off) / 32);
           } else if (ep.a_mn) {
 #pragma unroll
             for (int j = 0; j < TBM / 32; ++j) {
@@ -227,8 +227,8 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
             tma_load_2d(st + S::A_BYTES, &tmAl, full_bar(s), kc + a_k_off, tm0 + a_m_off);
           }
           if (ep.b_mn == 2) {
-            tma_load_3d(st + 2 * S::A_BYTES, &tmBh, full_bar(s), 0, kc, tb0 / 32);
-            tma_load_3d(st + 2 * S::A_BYTES + S::B_BYTES, &tmBl, full_bar(s), 0, kc, tb0 / 32);
+            tma_load_3d(st + 2 * S::A_BYTES, &tmBh, full_bar(s), 0, kc + b_k_off, (tb0 + b_n_off) / 32);
+            tma_load_3d(st + 2 * S::A_BYTES + S::B_BYTES, &tmBl, full_bar(s), 0, kc + b_k_off, (tb0 + b_n_off) / 32);
           } else if (ep.b_mn) {
 #pragma unroll
             for (int j = 0; j < BN / 32; ++j) {
@@ -1223,13 +1223,17 @@ int gemm_tc_batched(const TcBatched& g, cudaStream_t s) {
   if (!configured) { GN_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<128, 3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL - S::STG_BYTES)); configured = true; }
   GN_REQUIRE(g.batches >= 1 && g.batches <= 65535 && g.batch != nullptr, "batched product: %d batches", g.batches);
   CUtensorMap mah, mal, mbh, mbl;
-  if (g.a.mn) { GN_TRY(make_map_mn(&mah, g.a.hi, g.a.cols, g.a.rows, g.a.ld)); GN_TRY(make_map_mn(&mal, g.a.lo, g.a.cols, g.a.rows, g.a.ld)); }
+  // MN-major operands whose MN extent is a multiple of 32 come as one 3-D box per tile (the batch offsets in MN must then be multiples of 32)
+  const bool a3 = g.a.mn && g.a.cols % 32 == 0, b3 = g.b.mn && g.b.cols % 32 == 0;
+  if (a3) { GN_TRY(make_map_mn3(&mah, g.a.hi, g.a.cols, g.a.rows, g.a.ld, TBM / 32)); GN_TRY(make_map_mn3(&mal, g.a.lo, g.a.cols, g.a.rows, g.a.ld, TBM / 32)); }
+  else if (g.a.mn) { GN_TRY(make_map_mn(&mah, g.a.hi, g.a.cols, g.a.rows, g.a.ld)); GN_TRY(make_map_mn(&mal, g.a.lo, g.a.cols, g.a.rows, g.a.ld)); }
   else { GN_TRY(make_map(&mah, g.a.hi, g.a.rows, g.a.cols, g.a.ld, TBM)); GN_TRY(make_map(&mal, g.a.lo, g.a.rows, g.a.cols, g.a.ld, TBM)); }
-  if (g.b.mn) { GN_TRY(make_map_mn(&mbh, g.b.hi, g.b.cols, g.b.rows, g.b.ld)); GN_TRY(make_map_mn(&mbl, g.b.lo, g.b.cols, g.b.rows, g.b.ld)); }
+  if (b3) { GN_TRY(make_map_mn3(&mbh, g.b.hi, g.b.cols, g.b.rows, g.b.ld, 128 / 32)); GN_TRY(make_map_mn3(&mbl, g.b.lo, g.b.cols, g.b.rows, g.b.ld, 128 / 32)); }
+  else if (g.b.mn) { GN_TRY(make_map_mn(&mbh, g.b.hi, g.b.cols, g.b.rows, g.b.ld)); GN_TRY(make_map_mn(&mbl, g.b.lo, g.b.cols, g.b.rows, g.b.ld)); }
   else { GN_TRY(make_map(&mbh, g.b.hi, g.b.rows, g.b.cols, g.b.ld, 128)); GN_TRY(make_map(&mbl, g.b.lo, g.b.rows, g.b.cols, g.b.ld, 128)); }
   TcEpilogue ep{};
   ep.C = g.C; ep.ldc = g.ldc; ep.epi = g.accumulate ? EPI_ACCUM : EPI_STORE; ep.scalar = 1.0f;
-  ep.a_mn = g.a.mn ? 1 : 0; ep.b_mn = g.b.mn ? 1 : 0;
+  ep.a_mn = a3 ? 2 : (g.a.mn ? 1 : 0); ep.b_mn = b3 ? 2 : (g.b.mn ? 1 : 0);
   ep.batch = g.batch; ep.k_segments = g.k_segments; ep.k_seg_stride = g.k_seg_stride; ep.k_causal = g.k_causal;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(ceil_div(g.N, 128), ceil_div(g.M, TBM), g.batches); cfg.blockDim = dim3(64 + 32 * 4); cfg.dynamicSmemBytes = S::TOTAL - S::STG_BYTES; cfg.stream = s;
