@@ -107,6 +107,37 @@ class CudaBackend:
         dst = np.empty(rows * ((blocks + g - 1) // g), np.float32)
         check(self.lib.gn_indexer_block_max(ptr(dst), ptr(scores), rows, blocks, group_size)); return dst
 
+    # ------------------------------------------------------------------ compressed attention blocks
+    def compressor_forward(self, hidden, value, weight, bias, ratio):
+        """ChannelCompressor.Forward (model/compress.go:93-177) -> compressed [B, blocks, C], probabilities [B, blocks, ratio, C]."""
+        hidden, value, weight, bias = _f32(hidden), _f32(value), _f32(weight), _f32(bias)
+        B, T, d = hidden.shape; ch = value.shape[2]; blocks = (T + ratio - 1) // ratio
+        out = np.zeros((B, blocks, ch), np.float32); prob = np.zeros((B, blocks, ratio, ch), np.float32)
+        check(self.lib.gn_compressor_forward(ptr(hidden), ptr(value), ptr(weight), ptr(bias), B, T, d, ch, ratio, ptr(out), ptr(prob)))
+        return out, prob
+
+    def compressed_attention_forward(self, q, kc, vc, ratio):
+        """compressedAttentionForward (model/compress_attention.go:624-673): q [B,Hq,T,D], kc / vc [B,Hkv,blocks,D]."""
+        q, kc, vc = _f32(q), _f32(kc), _f32(vc)
+        B, Hq, T, D = q.shape; Hkv, blocks = kc.shape[1], kc.shape[2]
+        out = np.zeros_like(q); lse = np.zeros((B, Hq, T), np.float32)
+        check(self.lib.gn_compressed_attention_forward(ptr(q), ptr(kc), ptr(vc), B, Hq, Hkv, T, D, blocks, ratio, ptr(out), ptr(lse)))
+        return out, lse
+
+    def attention_merge(self, oa, la, ob, lb):
+        """mergeAttentionBranches (model/compress_attention.go:440-466)."""
+        oa, la, ob, lb = _f32(oa), _f32(la), _f32(ob), _f32(lb)
+        out = np.zeros_like(oa); lse = np.zeros_like(la)
+        check(self.lib.gn_attention_merge(ptr(oa), ptr(la), ptr(ob), ptr(lb), la.size, oa.shape[-1], ptr(out), ptr(lse)))
+        return out, lse
+
+    def select_blocks(self, scores, offset, ratio, topk):
+        """SelectBlocks (model/indexer.go:186-206): selection [tokens, topk] (-1 padded), counts [tokens]."""
+        scores = _f32(scores); tokens, blocks = scores.shape
+        sel = np.full((tokens, max(topk, 0)), -1, np.int32); cnt = np.zeros(tokens, np.int32)
+        check(self.lib.gn_select_blocks(ptr(scores), tokens, blocks, offset, ratio, topk, ptr(sel) if topk > 0 else None, ptr(cnt)))
+        return sel, cnt
+
     # ------------------------------------------------------------------ MoE
     def topk_indices(self, scores, rows, count, k):
         scores = _f32(scores); dst = np.zeros(rows * k, np.int32)

@@ -169,6 +169,15 @@ struct Stage {
     back.push_back({p, dev, n * sizeof(T)});
     return (T*)dev;
   }
+  // device scratch that lives until the call returns
+  template <typename T>
+  T* temp(size_t n) {
+    if (status != GN_OK) return nullptr;
+    void* dev = nullptr;
+    if (cudaMalloc(&dev, std::max<size_t>(n, 1) * sizeof(T)) != cudaSuccess) { set_error("staging: cudaMalloc of %zu bytes failed", n * sizeof(T)); status = GN_ERR_NOMEM; return nullptr; }
+    owned.push_back(dev);
+    return (T*)dev;
+  }
   int finish() {
     if (status != GN_OK) return status;
     for (auto& b : back) GN_CUDA(cudaMemcpyAsync(b.host, b.dev, b.bytes, cudaMemcpyDeviceToHost, s));
@@ -290,6 +299,64 @@ int gn_indexer_block_max(float* dst, const float* scores, int rows, int blocks, 
   const float* ds = st.in(scores, (size_t)rows * blocks); float* dd = st.out(dst, (size_t)rows * groups);
   if (st.status != GN_OK) return st.status;
   GN_TRY(indexer_block_max_launch(dd, ds, rows, blocks, group, s));
+  GN_END();
+}
+
+// ChannelCompressor.Forward (model/compress.go:93-177)
+int gn_compressor_forward(const float* hidden, const float* value, const float* logit_weight, const float* bias, int batch, int seq, int embed, int channels,
+                          int ratio, float* compressed, float* probabilities) {
+  if (batch <= 0 || seq <= 0 || channels <= 0) return GN_OK;
+  GN_REQUIRE(hidden && value && logit_weight && bias && compressed && ratio >= 1 && embed > 0, "compressor_forward: bad argument");
+  const int blocks = (seq + ratio - 1) / ratio;
+  GN_BEGIN();
+  const size_t rows = (size_t)batch * seq;
+  const float* dh = st.in(hidden, rows * embed); const float* dv = st.in(value, rows * channels);
+  const float* dw = st.in(logit_weight, (size_t)channels * embed); const float* db = st.in(bias, (size_t)ratio * channels);
+  float* dc = st.out(compressed, (size_t)batch * blocks * channels);
+  float* dp = probabilities ? st.out(probabilities, (size_t)batch * blocks * ratio * channels) : nullptr;
+  float* logits = st.temp<float>(rows * channels);
+  if (st.status != GN_OK) return st.status;
+  GemmArgs g;
+  g.A = dh; g.B = dw; g.C = logits; g.M = (int)rows; g.N = channels; g.K = embed; g.lda = embed; g.ldb = embed; g.ldc = channels; g.b_trans = 1;
+  GN_TRY(gemm_dispatch(g, gemm_default_kind(), s));
+  GN_TRY(compressor_pool_launch(logits, db, dv, batch, seq, channels, ratio, dc, dp, s));
+  GN_TRY(st.finish());
+  return gemm_check_error(s);
+}
+// compressedAttentionForward (model/compress_attention.go:624-673), no segment mask
+int gn_compressed_attention_forward(const float* query, const float* key_c, const float* value_c, int batch, int n_head, int n_kv_head, int seq, int head_dim,
+                                    int blocks, int ratio, float* out, float* lse) {
+  if (batch <= 0 || seq <= 0) return GN_OK;
+  GN_REQUIRE(query && key_c && value_c && out && blocks >= 0, "compressed_attention_forward: bad argument");
+  GN_BEGIN();
+  const size_t nq = (size_t)batch * n_head * seq * head_dim, nk = (size_t)batch * n_kv_head * blocks * head_dim;
+  const float* dq = st.in(query, nq); const float* dk = st.in(key_c, nk); const float* dv = st.in(value_c, nk);
+  float* dout = st.out(out, nq); float* dl = lse ? st.out(lse, (size_t)batch * n_head * seq) : nullptr;
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(compressed_attention_launch(dq, dk, dv, batch, n_head, n_kv_head, seq, head_dim, blocks, ratio, dout, dl, s));
+  GN_END();
+}
+// mergeAttentionBranches (model/compress_attention.go:440-466)
+int gn_attention_merge(const float* out_a, const float* lse_a, const float* out_b, const float* lse_b, int64_t rows, int head_dim, float* out, float* lse) {
+  if (rows <= 0) return GN_OK;
+  GN_REQUIRE(out_a && lse_a && out_b && lse_b && out && head_dim > 0, "attention_merge: bad argument");
+  GN_BEGIN();
+  const float* da = st.in(out_a, (size_t)rows * head_dim); const float* dla = st.in(lse_a, (size_t)rows);
+  const float* db = st.in(out_b, (size_t)rows * head_dim); const float* dlb = st.in(lse_b, (size_t)rows);
+  float* dout = st.out(out, (size_t)rows * head_dim); float* dl = lse ? st.out(lse, (size_t)rows) : nullptr;
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(attention_merge_launch(da, dla, db, dlb, rows, head_dim, dout, dl, s));
+  GN_END();
+}
+// SelectBlocks (model/indexer.go:186-206)
+int gn_select_blocks(const float* scores, int tokens, int blocks, int position_offset, int ratio, int topk, int32_t* selection, int32_t* counts) {
+  if (tokens <= 0) return GN_OK;
+  GN_REQUIRE(scores && counts && blocks > 0 && ratio >= 1 && topk >= 0 && (selection || topk == 0), "select_blocks: bad argument");
+  GN_BEGIN();
+  const float* ds = st.in(scores, (size_t)tokens * blocks);
+  int32_t* dsel = topk > 0 ? st.out(selection, (size_t)tokens * topk) : nullptr; int32_t* dc = st.out(counts, (size_t)tokens);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(select_blocks_launch(ds, tokens, blocks, position_offset, ratio, topk, dsel, dc, s));
   GN_END();
 }
 

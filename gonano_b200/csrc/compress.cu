@@ -1,0 +1,163 @@
+// Building blocks of the reference's compressed attention layers (the "flash" preset), inference forward:
+//   channel compressor            model/compress.go:93-177 (logits = hidden W^T + positional bias, softmax over the rows
+//                                 of a block per channel, weighted sum of the block's value rows)
+//   attention over the compressed blocks that strictly precede the query's block
+//                                 model/compress_attention.go:624-673
+//   merge of two softmax branches that share one normalisation (compressed + sliding window)
+//                                 model/compress_attention.go:440-484
+//   block selection of the sparse indexer: the top-k allowed blocks per token, descending score, ties toward the
+//   smaller index                 model/indexer.go:160-262
+// All HBM-bound row kernels; the compressor's logits come from the ordinary product.
+#include "kernels.cuh"
+
+namespace gn {
+
+namespace {
+
+// one thread per (batch, block, channel); logits [B*T, C] already hold hidden W^T
+__global__ void __launch_bounds__(256) compressor_pool_kernel(const float* __restrict__ logits, const float* __restrict__ bias, const float* __restrict__ value,
+                                                              int B, int T, int C, int ratio, int blocks, float* __restrict__ compressed,
+                                                              float* __restrict__ probabilities) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)B * blocks * C) return;
+  const int c = (int)(idx % C); const int64_t bb = idx / C; const int blk = (int)(bb % blocks); const int b = (int)(bb / blocks);
+  const int t0 = blk * ratio, rows = min(ratio, T - t0);
+  const float* lg = logits + ((int64_t)b * T + t0) * C + c;
+  float mx = -INFINITY;
+  for (int r = 0; r < rows; ++r) mx = fmaxf(mx, lg[(int64_t)r * C] + bias[(int64_t)r * C + c]);
+  double total = 0.0;
+  for (int r = 0; r < rows; ++r) total += (double)(float)exp((double)(lg[(int64_t)r * C] + bias[(int64_t)r * C + c] - mx));
+  float acc = 0.0f;
+  const float inv = total > 0.0 ? (float)(1.0 / total) : 0.0f;
+  const float* vp = value + ((int64_t)b * T + t0) * C + c;
+  float* pp = probabilities ? probabilities + (((int64_t)b * blocks + blk) * ratio) * C + c : nullptr;
+  for (int r = 0; r < ratio; ++r) {
+    float p = 0.0f;
+    if (r < rows && total > 0.0) {
+      p = (float)exp((double)(lg[(int64_t)r * C] + bias[(int64_t)r * C + c] - mx)) * inv;
+      acc = __fadd_rn(acc, __fmul_rn(p, vp[(int64_t)r * C]));
+    }
+    if (pp) pp[(int64_t)r * C] = p;
+  }
+  compressed[idx] = acc;
+}
+
+// one warp per (batch, query head, token): keys = compressed blocks 0 .. t / ratio - 1
+template <int DP>
+__global__ void __launch_bounds__(256) compressed_attention_kernel(const float* __restrict__ q, const float* __restrict__ kc, const float* __restrict__ vc, int B,
+                                                                   int Hq, int Hkv, int T, int D, int blocks, int ratio, float* __restrict__ out,
+                                                                   float* __restrict__ lse) {
+  constexpr int PER = DP / 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t idx = (int64_t)blockIdx.x * 8 + warp;
+  if (idx >= (int64_t)B * Hq * T) return;
+  const int t = (int)(idx % T); const int64_t bh = idx / T; const int h = (int)(bh % Hq); const int b = (int)(bh / Hq);
+  const int nk = min(t / ratio, blocks);
+  const float* qr = q + idx * D;
+  const int64_t kbase = ((int64_t)b * Hkv + h / (Hq / Hkv)) * blocks * D;
+  float qv[PER], acc[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; qv[i] = c < D ? qr[c] : 0.0f; acc[i] = 0.0f; }
+  float m = -INFINITY, l = 0.0f;
+  for (int j = 0; j < nk; ++j) {
+    const float* kr = kc + kbase + (int64_t)j * D; const float* vr = vc + kbase + (int64_t)j * D;
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; if (c < D) s = fmaf(qv[i], kr[c], s); }
+    s = warp_sum(s);
+    const float mn = fmaxf(m, s);
+    const float f = __expf(m - mn), p = __expf(s - mn);
+    l = l * f + p;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; if (c < D) acc[i] = acc[i] * f + p * vr[c]; }
+    m = mn;
+  }
+  const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; if (c < D) out[idx * D + c] = acc[i] * inv; }
+  if (lse && lane == 0) lse[idx] = nk > 0 ? m + logf(l) : -INFINITY;
+}
+
+// one warp per row
+__global__ void __launch_bounds__(256) attention_merge_kernel(const float* __restrict__ oa, const float* __restrict__ la, const float* __restrict__ ob,
+                                                              const float* __restrict__ lb, int64_t rows, int D, float* __restrict__ out, float* __restrict__ lse) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t r = (int64_t)blockIdx.x * 8 + warp;
+  if (r >= rows) return;
+  const float a = la[r], b = lb[r];
+  const float mx = fmaxf(a, b);
+  if (mx == -INFINITY) {
+    for (int c = lane; c < D; c += 32) out[r * D + c] = 0.0f;
+    if (lse && lane == 0) lse[r] = mx;
+    return;
+  }
+  const float wa = (float)exp((double)(a - mx)), wb = (float)exp((double)(b - mx));
+  const float total = wa + wb;
+  const float inv = (float)(1.0 / (double)total);
+  for (int c = lane; c < D; c += 32) out[r * D + c] = (wa * oa[r * D + c] + wb * ob[r * D + c]) * inv;
+  if (lse && lane == 0) lse[r] = mx + (float)log((double)total);
+}
+
+// one warp per token: the rank of an allowed block is the number of blocks that beat it (larger score, or equal score and
+// smaller index); blocks of rank < count are the selection, in rank order.  Exact, no sort.
+__global__ void __launch_bounds__(256) select_blocks_kernel(const float* __restrict__ scores, int tokens, int blocks, int offset, int ratio, int topk,
+                                                            int32_t* __restrict__ selection, int32_t* __restrict__ counts) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 8 + warp;
+  if (t >= tokens) return;
+  const int allowed = min((offset + t) / ratio, blocks);
+  const int count = allowed > 0 ? min(topk, allowed) : 0;
+  int32_t* sel = selection + (int64_t)t * topk;
+  for (int i = lane; i < topk; i += 32) sel[i] = -1;
+  if (lane == 0) counts[t] = count;
+  __syncwarp();
+  const float* v = scores + (int64_t)t * blocks;
+  for (int i = lane; i < allowed; i += 32) {
+    const float vi = v[i];
+    int rank = 0;
+    for (int j = 0; j < allowed; ++j) { const float vj = v[j]; rank += (vj > vi || (vj == vi && j < i)) ? 1 : 0; }
+    if (rank < count) sel[rank] = i;
+  }
+}
+
+}  // namespace
+
+int compressor_pool_launch(const float* logits, const float* bias, const float* value, int B, int T, int C, int ratio, float* compressed, float* probabilities,
+                           cudaStream_t s) {
+  const int blocks = (T + ratio - 1) / ratio;
+  const int64_t n = (int64_t)B * blocks * C;
+  if (n <= 0) return GN_OK;
+  compressor_pool_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, s>>>(logits, bias, value, B, T, C, ratio, blocks, compressed, probabilities);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+int compressed_attention_launch(const float* q, const float* kc, const float* vc, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* out, float* lse,
+                                cudaStream_t s) {
+  GN_REQUIRE(D > 0 && D <= 128, "compressed attention: head_dim %d outside (0,128]", D);
+  GN_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && ratio >= 1, "compressed attention: %d query heads, %d kv heads, ratio %d", Hq, Hkv, ratio);
+  const int64_t n = (int64_t)B * Hq * T;
+  if (n <= 0) return GN_OK;
+  const unsigned grid = (unsigned)ceil_div(n, 8);
+  if (D <= 32) compressed_attention_kernel<32><<<grid, 256, 0, s>>>(q, kc, vc, B, Hq, Hkv, T, D, blocks, ratio, out, lse);
+  else if (D <= 64) compressed_attention_kernel<64><<<grid, 256, 0, s>>>(q, kc, vc, B, Hq, Hkv, T, D, blocks, ratio, out, lse);
+  else compressed_attention_kernel<128><<<grid, 256, 0, s>>>(q, kc, vc, B, Hq, Hkv, T, D, blocks, ratio, out, lse);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+int attention_merge_launch(const float* oa, const float* la, const float* ob, const float* lb, int64_t rows, int D, float* out, float* lse, cudaStream_t s) {
+  if (rows <= 0) return GN_OK;
+  attention_merge_kernel<<<(unsigned)ceil_div(rows, 8), 256, 0, s>>>(oa, la, ob, lb, rows, D, out, lse);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+int select_blocks_launch(const float* scores, int tokens, int blocks, int offset, int ratio, int topk, int32_t* selection, int32_t* counts, cudaStream_t s) {
+  if (tokens <= 0) return GN_OK;
+  select_blocks_kernel<<<(unsigned)ceil_div(tokens, 8), 256, 0, s>>>(scores, tokens, blocks, offset, ratio, topk, selection, counts);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+}  // namespace gn

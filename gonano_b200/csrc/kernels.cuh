@@ -61,6 +61,13 @@ struct AttnShape {
 // head_dim 128 tensor-core kernels (attention_mma.cu); reached through the two launches below when sh.tensor is set.
 bool attention_mma_ok(const AttnShape& sh, const void* p0, const void* p1, const void* p2, const void* p3, const void* p4);
 int attention_mma_forward(const AttnShape& sh, const float* q, const float* k, const float* v, float* out, float* lse, cudaStream_t s);
+// compressed attention building blocks (compress.cu)
+int compressor_pool_launch(const float* logits, const float* bias, const float* value, int B, int T, int C, int ratio, float* compressed, float* probabilities,
+                           cudaStream_t s);
+int compressed_attention_launch(const float* q, const float* kc, const float* vc, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* out, float* lse,
+                                cudaStream_t s);
+int attention_merge_launch(const float* oa, const float* la, const float* ob, const float* lb, int64_t rows, int D, float* out, float* lse, cudaStream_t s);
+int select_blocks_launch(const float* scores, int tokens, int blocks, int offset, int ratio, int topk, int32_t* selection, int32_t* counts, cudaStream_t s);
 // head_dim 128 forward on tcgen05 (attention_tcgen05.cu); preferred over the mma.sync kernel when sh.tensor is set.
 bool attention_tc_ok(const AttnShape& sh, const void* p0, const void* p1, const void* p2, const void* p3);
 int attention_tc_forward(const AttnShape& sh, const float* q, const float* k, const float* v, float* out, float* lse, cudaStream_t s);

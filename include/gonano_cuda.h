@@ -99,6 +99,22 @@ int gn_indexer_scores(float* dst, const float* query, const float* key, const fl
                       int heads, int dim);
 int gn_indexer_block_max(float* dst, const float* scores, int rows, int blocks, int group_size);
 
+/* Building blocks of the compressed ("flash") attention layers, inference forward.  These bypass kernels.Backend in the
+ * reference (plain Go loops in model/): ChannelCompressor.Forward (model/compress.go:93-177; hidden [batch, seq, embed],
+ * value [batch, seq, channels], logit_weight [channels, embed], bias [ratio, channels] -> compressed [batch,
+ * ceil(seq / ratio), channels], probabilities nullable [batch, blocks, ratio, channels]); compressedAttentionForward
+ * without a segment mask (model/compress_attention.go:624-673; query [batch, n_head, seq, head_dim], key_c / value_c
+ * [batch, n_kv_head, blocks, head_dim]; the queries of block b attend blocks 0 .. b-1, block 0 yields zeros and
+ * lse = -inf); mergeAttentionBranches (:440-466); SelectBlocks (model/indexer.go:186-206; selection [tokens, topk]
+ * padded with -1, counts [tokens]; descending score, ties toward the smaller block index). */
+int gn_compressor_forward(const float* hidden, const float* value, const float* logit_weight, const float* bias, int batch, int seq, int embed,
+                          int channels, int ratio, float* compressed, float* probabilities);
+int gn_compressed_attention_forward(const float* query, const float* key_c, const float* value_c, int batch, int n_head, int n_kv_head, int seq,
+                                    int head_dim, int blocks, int ratio, float* out, float* lse);
+int gn_attention_merge(const float* out_a, const float* lse_a, const float* out_b, const float* lse_b, int64_t rows, int head_dim, float* out,
+                       float* lse);
+int gn_select_blocks(const float* scores, int tokens, int blocks, int position_offset, int ratio, int topk, int32_t* selection, int32_t* counts);
+
 /* MoE (kernels/backend.go:119-141).  Indices are exact: descending score, ties
  * toward the smaller index. */
 int gn_topk_indices(int32_t* dst, const float* scores, int rows, int count, int k);

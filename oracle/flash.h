@@ -1,0 +1,132 @@
+// TEST INFRASTRUCTURE, NOT PRODUCT: CPU restatement of the building blocks of the reference's compressed
+// ("flash") attention layers, used only to check the CUDA kernels.
+//
+//   channel compressor forward        model/compress.go:93-177
+//   compression of K and V per head    model/compress_attention.go:562-621 (compressForward, no segment mask)
+//   attention over preceding blocks    model/compress_attention.go:624-673 (compressedAttentionForward)
+//   local sliding-window branch        model/compress_attention.go:487-536 (attentionForwardWindowed = the ordinary
+//                                      attention with a window, kernels/scalar/attention.go:16-205)
+//   merge of two softmax branches      model/compress_attention.go:440-466 (mergeAttentionBranches)
+//   block selection                    model/indexer.go:160-262 (TopK, SelectBlocks, topKIndices = stable argsort[:k])
+//
+// Pinned to the reference's known answers in tests/test_oracle_golden.py: model/compress_test.go:10-26,
+// model/indexer_test.go:318-325,437-470.
+#pragma once
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <numeric>
+#include <vector>
+
+#include "backend.h"
+
+namespace gnor {
+
+// hidden [B, T, d], value [B, T, C], weight [C, d] (logits = hidden weight^T), bias [ratio, C]
+// -> compressed [B, ceil(T / ratio), C]; probabilities (nullable) [B, blocks, ratio, C].
+inline void compressor_forward(const Backend& bk, const float* hidden, const float* value, const float* weight, const float* bias, int B, int T, int d, int C,
+                               int ratio, float* compressed, float* probabilities) {
+  const int blocks = (T + ratio - 1) / ratio;
+  std::vector<float> logits((size_t)B * T * C);
+  bk.matmul_t(logits.data(), hidden, weight, B * T, C, d);
+  for (int b = 0; b < B; ++b)
+    for (int t = 0; t < T; ++t)
+      for (int c = 0; c < C; ++c) logits[((size_t)b * T + t) * C + c] += bias[(size_t)(t % ratio) * C + c];
+  std::fill(compressed, compressed + (size_t)B * blocks * C, 0.0f);
+  std::vector<float> prob(ratio);
+  for (int b = 0; b < B; ++b)
+    for (int blk = 0; blk < blocks; ++blk)
+      for (int c = 0; c < C; ++c) {
+        float mx = -INFINITY;
+        for (int r = 0; r < ratio; ++r) {
+          const int t = blk * ratio + r;
+          if (t >= T) continue;
+          mx = std::max(mx, logits[((size_t)b * T + t) * C + c]);
+        }
+        double total = 0;
+        for (int r = 0; r < ratio; ++r) {
+          const int t = blk * ratio + r;
+          float p = 0.0f;
+          if (t < T && mx > -INFINITY) p = (float)std::exp((double)(logits[((size_t)b * T + t) * C + c] - mx));
+          prob[r] = p; total += (double)p;
+        }
+        float acc = 0.0f;
+        if (total > 0) {
+          const float inv = (float)(1.0 / total);
+          for (int r = 0; r < ratio; ++r) {
+            prob[r] *= inv;
+            const int t = blk * ratio + r;
+            if (t < T) acc += prob[r] * value[((size_t)b * T + t) * C + c];
+          }
+          compressed[((size_t)b * blocks + blk) * C + c] = acc;
+        }
+        if (probabilities)
+          for (int r = 0; r < ratio; ++r) probabilities[(((size_t)b * blocks + blk) * ratio + r) * C + c] = prob[r];
+      }
+}
+
+// q [B, Hq, T, D], kc / vc [B, Hkv, blocks, D] -> out [B, Hq, T, D], lse [B, Hq, T]: the queries of block b attend the
+// compressed blocks 0 .. b-1 (none for block 0: zero output, lse = -inf).
+inline void compressed_attention_forward(const Backend& bk, const float* q, const float* kc, const float* vc, int B, int Hq, int Hkv, int T, int D, int blocks,
+                                         int ratio, float* out, float* lse) {
+  const int hr = Hq / Hkv;
+  for (int b = 0; b < B; ++b)
+    for (int h = 0; h < Hq; ++h) {
+      const size_t qi = (size_t)b * Hq + h;
+      const size_t kbase = ((size_t)b * Hkv + h / hr) * blocks * D;
+      for (int blk = 0; blk < blocks; ++blk) {
+        const int start = blk * ratio, end = std::min(start + ratio, T);
+        if (end <= start) continue;
+        float* o = out + (qi * T + start) * D;
+        float* l = lse ? lse + qi * T + start : nullptr;
+        if (blk == 0) {
+          std::fill(o, o + (size_t)(end - start) * D, 0.0f);
+          if (l) std::fill(l, l + (end - start), -INFINITY);
+          continue;
+        }
+        // position offset = blk: every compressed key index is below every query position (no causal cut inside)
+        bk.attention_forward(q + (qi * T + start) * D, kc + kbase, vc + kbase, end - start, blk, D, blk, -1, nullptr, 0, o, l);
+      }
+    }
+}
+
+// Two normalised branches that share one softmax over the union of their keys: rows x D outputs and rows log-sum-exps.
+inline void merge_branches(const float* oa, const float* la, const float* ob, const float* lb, int64_t rows, int D, float* out, float* lse) {
+  for (int64_t r = 0; r < rows; ++r) {
+    const float a = la[r], b = lb[r];
+    const float mx = std::max(a, b);
+    float* o = out + r * D;
+    if (mx == -INFINITY) { std::fill(o, o + D, 0.0f); if (lse) lse[r] = mx; continue; }
+    const float wa = (float)std::exp((double)(a - mx)), wb = (float)std::exp((double)(b - mx));
+    const float total = wa + wb;
+    const float inv = (float)(1.0 / (double)total);
+    for (int c = 0; c < D; ++c) o[c] = (wa * oa[r * D + c] + wb * ob[r * D + c]) * inv;
+    if (lse) lse[r] = mx + (float)std::log((double)total);
+  }
+}
+
+// The k largest of values[0, n) in descending order, ties toward the smaller index (= stable argsort descending, cut).
+inline std::vector<int> topk_indices(const float* values, int n, int k) {
+  if (k <= 0) return {};
+  std::vector<int> order(n);
+  std::iota(order.begin(), order.end(), 0);
+  std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return values[a] > values[b]; });
+  if (k < n) order.resize(k);
+  return order;
+}
+
+// scores [tokens, blocks] -> selection [tokens, topk] (-1 padded) and counts [tokens]: token t (absolute position
+// offset + t) may take the blocks [0, min((offset + t) / ratio, blocks)).
+inline void select_blocks(const float* scores, int tokens, int blocks, int offset, int ratio, int topk, int32_t* selection, int32_t* counts) {
+  for (int t = 0; t < tokens; ++t) {
+    int allowed = std::min((offset + t) / ratio, blocks);
+    int32_t* sel = selection + (size_t)t * std::max(topk, 0);
+    for (int i = 0; i < topk; ++i) sel[i] = -1;
+    if (allowed <= 0 || topk <= 0) { counts[t] = 0; continue; }
+    const std::vector<int> idx = topk_indices(scores + (size_t)t * blocks, allowed, std::min(topk, allowed));
+    counts[t] = (int32_t)idx.size();
+    for (size_t i = 0; i < idx.size(); ++i) sel[i] = idx[i];
+  }
+}
+
+}  // namespace gnor

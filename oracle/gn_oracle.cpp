@@ -23,6 +23,7 @@
 #include <omp.h>
 #endif
 #include "backend.h"
+#include "flash.h"
 #include "model.h"
 #include "optimizer.h"
 #include "philox.h"
@@ -564,5 +565,21 @@ void* or_optimizer_create(void* model, float ulr, float elr, float mlr, float wd
 }
 void or_optimizer_destroy(void* o) { delete (gnopt::Optimizer*)o; }
 void or_optimizer_step(void* o) { ((gnopt::Optimizer*)o)->step(); }
+
+// ---- building blocks of the compressed attention layers (flash.h)
+void or_compressor_forward(int m, const float* hidden, const float* value, const float* weight, const float* bias, int B, int T, int d, int C, int ratio,
+                           float* compressed, float* probabilities) {
+  BK(m); gnor::compressor_forward(bk, hidden, value, weight, bias, B, T, d, C, ratio, compressed, probabilities);
+}
+void or_compressed_attention_forward(int m, const float* q, const float* kc, const float* vc, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio,
+                                     float* out, float* lse) {
+  BK(m); gnor::compressed_attention_forward(bk, q, kc, vc, B, Hq, Hkv, T, D, blocks, ratio, out, lse);
+}
+void or_merge_branches(const float* oa, const float* la, const float* ob, const float* lb, int64_t rows, int D, float* out, float* lse) {
+  gnor::merge_branches(oa, la, ob, lb, rows, D, out, lse);
+}
+void or_select_blocks(const float* scores, int tokens, int blocks, int offset, int ratio, int topk, int32_t* selection, int32_t* counts) {
+  gnor::select_blocks(scores, tokens, blocks, offset, ratio, topk, selection, counts);
+}
 
 }  // extern "C"

@@ -555,3 +555,39 @@ class Cache:
 
     def replicate_from(self, src: "Cache"):
         self.model.l.or_cache_replicate(self.model.h, self.h, src.h)
+
+# ---------------------------------------------------------------------------------------------- compressed attention blocks
+def compressor_forward(hidden, value, weight, bias, ratio, mode=0):
+    """ChannelCompressor.Forward (model/compress.go:93-177): hidden [B,T,d], value [B,T,C], weight [C,d], bias [ratio,C]
+    -> compressed [B, blocks, C], probabilities [B, blocks, ratio, C]."""
+    hidden, value, weight, bias = f32(hidden), f32(value), f32(weight), f32(bias)
+    B, T, d = hidden.shape; C_ = value.shape[2]; blocks = (T + ratio - 1) // ratio
+    out = np.zeros((B, blocks, C_), np.float32); prob = np.zeros((B, blocks, ratio, C_), np.float32)
+    lib().or_compressor_forward(mode, _f(hidden), _f(value), _f(weight), _f(bias), B, T, d, C_, ratio, _f(out), _f(prob))
+    return out, prob
+
+
+def compressed_attention_forward(q, kc, vc, ratio, mode=0):
+    """compressedAttentionForward (model/compress_attention.go:624-673): q [B,Hq,T,D], kc/vc [B,Hkv,blocks,D]."""
+    q, kc, vc = f32(q), f32(kc), f32(vc)
+    B, Hq, T, D = q.shape; Hkv, blocks = kc.shape[1], kc.shape[2]
+    out = np.zeros_like(q); lse = np.zeros((B, Hq, T), np.float32)
+    lib().or_compressed_attention_forward(mode, _f(q), _f(kc), _f(vc), B, Hq, Hkv, T, D, blocks, ratio, _f(out), _f(lse))
+    return out, lse
+
+
+def merge_branches(oa, la, ob, lb):
+    """mergeAttentionBranches (model/compress_attention.go:440-466)."""
+    oa, la, ob, lb = f32(oa), f32(la), f32(ob), f32(lb)
+    D = oa.shape[-1]; rows = la.size
+    out = np.zeros_like(oa); lse = np.zeros_like(la)
+    lib().or_merge_branches(_f(oa), _f(la), _f(ob), _f(lb), C.c_int64(rows), D, _f(out), _f(lse))
+    return out, lse
+
+
+def select_blocks(scores, offset, ratio, topk):
+    """SelectBlocks (model/indexer.go:186-206): selection [tokens, topk] (-1 padded) and counts."""
+    scores = f32(scores); tokens, blocks = scores.shape
+    sel = np.full((tokens, max(topk, 0)), -1, np.int32); cnt = np.zeros(tokens, np.int32)
+    lib().or_select_blocks(_f(scores), tokens, blocks, offset, ratio, topk, _i(sel), _i(cnt))
+    return sel, cnt

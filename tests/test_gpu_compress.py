@@ -1,0 +1,104 @@
+"""Building blocks of the compressed attention layers on the device against the oracle (oracle/flash.h): the channel
+compressor, attention over the preceding compressed blocks, the merge of two softmax branches, block selection, and the
+three composed into the forward of one heavily-compressed attention layer (compressed global branch + sliding-window
+local branch, model/compress_attention.go:440-484,562-673)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def bk():
+    from gonano_b200.backend import CudaBackend
+    return CudaBackend()
+
+
+def close(got, want, rel, floor):
+    got = np.asarray(got, np.float64); want = np.asarray(want, np.float64)
+    fin = np.isfinite(want)
+    assert np.array_equal(np.isfinite(got), fin) and np.array_equal(got[~fin], want[~fin])
+    assert np.all(np.abs(got[fin] - want[fin]) <= floor + rel * np.maximum(np.abs(want[fin]), 1.0))
+
+
+@pytest.mark.parametrize("B,T,d,C,ratio", [(1, 3, 1, 1, 2), (2, 17, 24, 16, 4), (1, 130, 96, 128, 8), (3, 64, 128, 64, 64), (1, 5, 8, 4, 1)])
+def test_compressor_forward(oracle, bk, B, T, d, C, ratio):
+    rng = np.random.default_rng(B * 100 + T)
+    hidden = rng.standard_normal((B, T, d)).astype(np.float32); value = rng.standard_normal((B, T, C)).astype(np.float32)
+    weight = (rng.standard_normal((C, d)) * 0.3).astype(np.float32); bias = (rng.standard_normal((ratio, C)) * 0.5).astype(np.float32)
+    want, want_p = oracle.compressor_forward(hidden, value, weight, bias, ratio)
+    got, got_p = bk.compressor_forward(hidden, value, weight, bias, ratio)
+    close(got_p, want_p, 1e-5, 1e-6); close(got, want, 1e-5, 1e-6)
+    blocks = (T + ratio - 1) // ratio
+    full = (T // ratio)
+    assert np.allclose(got_p[:, :full].sum(axis=2), 1.0, atol=1e-5) and got.shape == (B, blocks, C)
+
+
+def test_compressor_known_answer(bk):
+    out, _ = bk.compressor_forward(np.zeros((1, 3, 1)), np.array([2, 4, 6], np.float32).reshape(1, 3, 1), np.zeros((1, 1)), np.zeros((2, 1)), 2)
+    assert out.ravel().tolist() == [3.0, 6.0]                     # model/compress_test.go:10-26
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,T,D,ratio", [(1, 1, 1, 9, 8, 2), (2, 6, 2, 70, 128, 4), (1, 4, 4, 33, 64, 8), (1, 2, 1, 40, 32, 64)])
+def test_compressed_attention_forward(oracle, bk, B, Hq, Hkv, T, D, ratio):
+    rng = np.random.default_rng(T + D)
+    blocks = (T + ratio - 1) // ratio
+    q = (rng.standard_normal((B, Hq, T, D)) * 0.4).astype(np.float32)
+    kc = (rng.standard_normal((B, Hkv, blocks, D)) * 0.4).astype(np.float32); vc = rng.standard_normal((B, Hkv, blocks, D)).astype(np.float32)
+    want, want_l = oracle.compressed_attention_forward(q, kc, vc, ratio)
+    got, got_l = bk.compressed_attention_forward(q, kc, vc, ratio)
+    close(got, want, 1e-4, 1e-5); close(got_l, want_l, 1e-4, 1e-5)
+    assert np.all(got[:, :, :min(ratio, T)] == 0)                 # block 0 has no preceding block
+
+
+def test_attention_merge(oracle, bk):
+    rng = np.random.default_rng(3)
+    rows, D = 257, 128
+    oa = rng.standard_normal((rows, D)).astype(np.float32); ob = rng.standard_normal((rows, D)).astype(np.float32)
+    la = (rng.standard_normal(rows) * 3).astype(np.float32); lb = (rng.standard_normal(rows) * 3).astype(np.float32)
+    la[:5] = -np.inf; lb[3:8] = -np.inf
+    want, want_l = oracle.merge_branches(oa, la, ob, lb)
+    got, got_l = bk.attention_merge(oa, la, ob, lb)
+    close(got, want, 1e-6, 1e-7); close(got_l, want_l, 1e-6, 1e-7)
+
+
+@pytest.mark.parametrize("tokens,blocks,offset,ratio,topk", [(8, 6, 0, 2, 2), (50, 40, 7, 4, 8), (33, 300, 1000, 4, 16), (5, 3, 0, 1, 10), (4, 4, 0, 2, 0)])
+def test_select_blocks(oracle, bk, tokens, blocks, offset, ratio, topk):
+    rng = np.random.default_rng(tokens + blocks)
+    scores = np.round(rng.standard_normal((tokens, blocks)) * 4).astype(np.float32)      # quantised: many ties (model/indexer_test.go:295-316)
+    want, want_c = oracle.select_blocks(scores, offset, ratio, topk)
+    got, got_c = bk.select_blocks(scores, offset, ratio, topk)
+    assert np.array_equal(got_c, want_c) and np.array_equal(got, want)
+    sel, cnt = bk.select_blocks(np.array([[5, 5, 5, 1, 2]], np.float32), 10, 1, 2)       # model/indexer_test.go:318-325
+    assert sel[0].tolist() == [0, 1]
+
+
+def test_heavily_compressed_layer_forward(oracle, bk):
+    """One HCA attention forward: K and V compressed per kv head from the layer input, the global branch over the
+    preceding compressed blocks, the local sliding-window branch over the raw keys, merged by their log-sum-exps."""
+    rng = np.random.default_rng(11)
+    B, Hq, Hkv, T, D, d, ratio, window = 2, 4, 2, 45, 64, 96, 4, 6
+    x = rng.standard_normal((B, T, d)).astype(np.float32)
+    q = (rng.standard_normal((B, Hq, T, D)) * 0.4).astype(np.float32)
+    k = (rng.standard_normal((B, Hkv, T, D)) * 0.4).astype(np.float32); v = rng.standard_normal((B, Hkv, T, D)).astype(np.float32)
+    wk = (rng.standard_normal((D, d)) * 0.2).astype(np.float32); bias = (rng.standard_normal((ratio, D)) * 0.3).astype(np.float32)
+    ref = oracle.Backend(0)
+
+    def layer(comp, catt, merge, attn):
+        blocks = (T + ratio - 1) // ratio
+        kc = np.zeros((B, Hkv, blocks, D), np.float32); vc = np.zeros_like(kc)
+        for b in range(B):
+            for h in range(Hkv):      # compressForward: the same compressor serves keys and values of every kv head
+                kc[b, h] = comp(x[b:b + 1], k[b, h][None], wk, bias, ratio)[0][0]
+                vc[b, h] = comp(x[b:b + 1], v[b, h][None], wk, bias, ratio)[0][0]
+        og, lg = catt(q, kc, vc, ratio)
+        ol = np.zeros_like(q); ll = np.zeros((B, Hq, T), np.float32)
+        for b in range(B):
+            for h in range(Hq):
+                o, l = attn(q[b, h], k[b, h // (Hq // Hkv)], v[b, h // (Hq // Hkv)], T, T, D, 0, window)
+                ol[b, h] = np.asarray(o).reshape(T, D); ll[b, h] = np.asarray(l).reshape(T)
+        return merge(og.reshape(-1, D), lg.reshape(-1), ol.reshape(-1, D), ll.reshape(-1))
+
+    want, want_l = layer(oracle.compressor_forward, oracle.compressed_attention_forward, oracle.merge_branches, ref.attention_forward)
+    got, got_l = layer(bk.compressor_forward, bk.compressed_attention_forward, bk.attention_merge, bk.attention_forward)
+    close(got, want, 1e-4, 1e-5); close(got_l, want_l, 1e-4, 1e-5)

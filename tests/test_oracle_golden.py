@@ -233,3 +233,45 @@ def test_distillation_known_answers(oracle):
     s2 = np.array([[0.1, 0.2, 0.3], [1, 2, 3]], np.float32); t2 = np.array([[3, 2, 1], [-1, -2, -3]], np.float32)
     losses, valid, grad = oracle.distillation(s2, t2, 1.0, mask=[0, 1])
     assert valid == 1 and losses[0] == 0 and losses[1] != 0 and not np.any(grad[0]) and np.any(grad[1])
+
+
+# model/compress_test.go:10-26: zero logits give a uniform softmax, so a complete block is the mean of its rows and a
+# trailing partial block keeps its single row
+def test_compressor_means_blocks(oracle):
+    out, prob = oracle.compressor_forward(np.zeros((1, 3, 1)), np.array([2, 4, 6], np.float32).reshape(1, 3, 1), np.zeros((1, 1)), np.zeros((2, 1)), 2)
+    assert out.shape == (1, 2, 1) and out[0, 0, 0] == 3.0 and out[0, 1, 0] == 6.0
+    assert prob[0, 0, :, 0].tolist() == [0.5, 0.5] and prob[0, 1, :, 0].tolist() == [1.0, 0.0]
+
+
+# model/indexer_test.go:318-325 (three equal maxima: the smallest indices win, in order), 437-470 (TopK orders and
+# breaks ties; k clamps to the block count), 413-435 (causality: a token takes only blocks before its own)
+def test_select_blocks_known_answers(oracle):
+    sel, cnt = oracle.select_blocks(np.array([[5, 5, 5, 1, 2]], np.float32), 10, 1, 2)
+    assert sel[0].tolist() == [0, 1] and cnt[0] == 2
+    scores = np.array([[1, 9, 3, 9, 2], [4, 5, 6, 7, 8]], np.float32)
+    sel, cnt = oracle.select_blocks(scores, 100, 1, 2)          # every block allowed: TopK
+    assert sel[0].tolist() == [1, 3] and sel[1].tolist() == [4, 3]
+    sel, cnt = oracle.select_blocks(np.array([[1, 2, 3]], np.float32), 100, 1, 10)
+    assert cnt[0] == 3 and sel[0, :3].tolist() == [2, 1, 0] and np.all(sel[0, 3:] == -1)
+    sel, cnt = oracle.select_blocks(np.tile(np.arange(6, dtype=np.float32), (8, 1)), 0, 2, 2)   # token t: blocks [0, t // 2)
+    assert cnt.tolist() == [0, 0, 1, 1, 2, 2, 2, 2]
+    assert sel[2].tolist() == [0, -1] and sel[4].tolist() == [1, 0] and sel[7].tolist() == [2, 1]
+
+
+# the merge of two branches equals attention over the union of their keys (the purpose stated at
+# model/compress_attention.go:434-439)
+def test_merge_branches_equals_joint_softmax(oracle):
+    rng = np.random.default_rng(0)
+    bk = oracle.Backend(0)
+    hd, na, nb = 8, 5, 7
+    q = rng.standard_normal(hd).astype(np.float32); k = rng.standard_normal((na + nb, hd)).astype(np.float32); v = rng.standard_normal((na + nb, hd)).astype(np.float32)
+    oa, la = bk.attention_forward(q, k[:na], v[:na], 1, na, hd, na, -1)
+    ob, lb = bk.attention_forward(q, k[na:], v[na:], 1, nb, hd, nb, -1)
+    want_o, want_l = bk.attention_forward(q, k, v, 1, na + nb, hd, na + nb, -1)
+    got_o, got_l = oracle.merge_branches(oa.reshape(1, hd), la.reshape(1), ob.reshape(1, hd), lb.reshape(1))
+    assert np.allclose(got_o.ravel(), want_o.ravel(), rtol=1e-5, atol=1e-6) and np.allclose(got_l.ravel(), want_l.ravel(), rtol=1e-5)
+    empty = np.full(1, -np.inf, np.float32)
+    o2, l2 = oracle.merge_branches(np.zeros((1, hd)), empty, ob.reshape(1, hd), lb.reshape(1))
+    assert np.array_equal(o2.ravel(), ob.ravel()) and l2[0] == lb.ravel()[0]
+    o3, l3 = oracle.merge_branches(np.zeros((1, hd)), empty, np.zeros((1, hd)), empty)
+    assert np.all(o3 == 0) and l3[0] == -np.inf
