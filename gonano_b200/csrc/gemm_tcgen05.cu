@@ -63,6 +63,7 @@ struct TcEpilogue {
   // cuts each segment to the k-blocks in which a causal operand is non-zero: 1 = k < m0 + 128 (the contraction runs over
   // keys, the rows are queries), 2 = k >= m0 (the contraction runs over queries, the rows are keys).
   const TcBatch* batch; int k_segments, k_seg_stride, k_causal;
+  int tma_store;   // 1: a one-tile CTA writes its tile with bulk-tensor stores through the map of C (plain stores only)
 };
 
 #ifdef GN_TC_TRACE
@@ -115,7 +116,7 @@ struct TcSmem {
 template <int BN, int STAGES, bool PERSIST>
 __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
                                                          const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
-                                                         TcEpilogue ep, int M, int N, int K, int* err) {
+                                                         const __grid_constant__ CUtensorMap tmC, TcEpilogue ep, int M, int N, int K, int* err) {
   using S = TcSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   // swizzled tiles want 1024-byte alignment
@@ -369,7 +370,29 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
         __syncwarp();
       }
     }
-    if (!failed && !persistent) {
+    if (!failed && !persistent && ep.tma_store) {
+      // Plain stores (a product's result or its K-split partial plane) leave through the bulk-tensor path: each warp
+      // stages its 32 rows as 32-column blocks in the 128-byte-swizzled layout (lane = row, chunk c at c ^ (row % 8):
+      // conflict-free) and one lane issues a store per block; rows and columns outside the matrix are clipped by the map.
+      const uint32_t sb = base + (uint32_t)(warp - 2) * (uint32_t)(ACC * 128);
+      uint8_t* sg = gen_base + (size_t)(warp - 2) * (ACC * 128);
+      if (warp == 2 && lane == 0) TC_TRACE(898);
+#pragma unroll
+      for (int cb = 0; cb < ACC / 32; ++cb)
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<float4*>(sg + cb * 4096 + lane * 128 + ((c ^ (lane & 7)) << 4)) =
+              make_float4(acc[cb * 32 + 4 * c], acc[cb * 32 + 4 * c + 1], acc[cb * 32 + 4 * c + 2], acc[cb * 32 + 4 * c + 3]);
+      fence_async_smem();
+      __syncwarp();
+      if (warp == 2 && lane == 0) TC_TRACE(899);
+      if (lane == 0) {
+#pragma unroll
+        for (int cb = 0; cb < ACC / 32; ++cb) tma_store_3d(&tmC, sb + cb * 4096, n0 + chalf + cb * 32, m0 + quarter * 32, zsplits > 1 ? (int)blockIdx.z : 0);
+        tma_store_commit_wait();
+      }
+      __syncwarp();
+    } else if (!failed && !persistent) {
       // The accumulator row of a thread is scattered (thread = row), so it goes through shared
       // memory first: the pipeline stages are idle once the last chunk has been drained, and
       // each warp then writes whole 512-byte row segments (a thread-per-row store pattern was
@@ -736,6 +759,7 @@ struct GemmState {
   bool pdl = true;            // programmatic dependent launch of the products
   bool mn = true;             // read [K, M] / [K, N] operands MN-major instead of transposing them while splitting
   bool mn3d = true;           // one 3-D TMA box per MN-major tile instead of one 2-D box per 32 columns
+  bool tma_store = true;      // one-tile CTAs store plain results through a tensor map of C
 };
 std::map<std::pair<int, cudaStream_t>, GemmState*> g_states;
 
@@ -938,6 +962,18 @@ int launch_tc(GemmState& gs, const SplitBuf& a, const SplitBuf& b, const TcEpilo
     if (ep.tiles_gn > ep.tiles_n) ep.tiles_gn = ep.tiles_n;
     grid = dim3(pctas, 1, 1);
   }
+  // One-tile CTAs with a plain store (results and K-split partial planes) write through a tensor map of C.
+  CUtensorMap mc = mah;
+  if (gs.tma_store && ep.tiles_total == 0 && ep.groups == 0 && ep.epi == EPI_STORE && ep.aux == nullptr && ep.c_hi == nullptr && ep.ldc % 4 == 0 &&
+      (reinterpret_cast<uintptr_t>(ep.C) & 15) == 0 && (splits == 1 || ((int64_t)M * N) % 4 == 0)) {
+    cuuint64_t dims[3] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)splits};
+    cuuint64_t strides[2] = {(cuuint64_t)ep.ldc * sizeof(float), (cuuint64_t)(splits > 1 ? ep.split_stride : (int64_t)M * ep.ldc) * sizeof(float)};
+    cuuint32_t box[3] = {32, 32, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = g_encode(&mc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)ep.C, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) ep.tma_store = 1;
+  }
   {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid; cfg.blockDim = dim3(64 + 32 * (BN > 128 ? 8 : 4)); cfg.dynamicSmemBytes = ep.tiles_total > 0 ? S::TOTAL : S::TOTAL - S::STG_BYTES; cfg.stream = s;
@@ -945,8 +981,8 @@ int launch_tc(GemmState& gs, const SplitBuf& a, const SplitBuf& b, const TcEpilo
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = gs.pdl ? 1 : 0;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    if (ep.tiles_total > 0) GN_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, true>, mah, mal, mbh, mbl, ep, M, N, K, gs.err_flag));
-    else GN_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, false>, mah, mal, mbh, mbl, ep, M, N, K, gs.err_flag));
+    if (ep.tiles_total > 0) GN_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, true>, mah, mal, mbh, mbl, mc, ep, M, N, K, gs.err_flag));
+    else GN_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, false>, mah, mal, mbh, mbl, mc, ep, M, N, K, gs.err_flag));
   }
   GN_LAUNCH_CHECK();
   if (leave) {
@@ -1160,6 +1196,7 @@ int gemm_tcgen05_option(cudaStream_t s, const char* name, int value) {
   else if (n == "gemm_pdl") st->pdl = value != 0;
   else if (n == "gemm_mn_major") st->mn = value != 0;
   else if (n == "gemm_mn_3d") st->mn3d = value != 0;
+  else if (n == "gemm_tma_store") st->tma_store = value != 0;
   else if (n == "gemm_few_rows_max") g_skinny_max_rows.store(value, std::memory_order_relaxed);
   else if (n == "gemm_few_rows_min_kblocks") g_skinny_min_kblocks.store(value, std::memory_order_relaxed);
   else if (n == "gemm_few_rows_block") g_skinny_block_rows.store(value, std::memory_order_relaxed);
@@ -1241,7 +1278,7 @@ int gemm_tc_batched(const TcBatched& g, cudaStream_t s) {
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 0;
   cfg.attrs = attr; cfg.numAttrs = 1;
-  GN_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<128, 3, false>, mah, mal, mbh, mbl, ep, g.M, g.N, g.K, st->err_flag));
+  GN_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<128, 3, false>, mah, mal, mbh, mbl, mah, ep, g.M, g.N, g.K, st->err_flag));
   GN_LAUNCH_CHECK();
   return GN_OK;
 }
