@@ -329,16 +329,18 @@ def kernel_rooflines(ctx, pk, tf32_tflops):
               "one layer, 256 rows, context 1088, shared 1024-token prefix per group of 8")
     hbm_entry("advantage", [64, 8], 8.0 * 512, "64 groups of 8 (latency-bound)")
 
-    # attention of one training pass (32 x 383 tokens, causal): 2 products forward, 7 backward (S and dP are recomputed
-    # in both backward kernels), each 2*T^2/2*D flop per (row, head), on the legacy mma.sync pipe in 3xTF32
-    B, T = 32, 383
+    # attention of one layer of a training pass (128 x 383 tokens, causal): 2 products forward; backward 5 products over
+    # the causal half (S and dP in the score kernel, dV, dK, dQ as batched products), each 2*T^2/2*D flop per (row, head),
+    # on tcgen05 in 3xTF32.  The backward is bound by the HBM traffic of the materialised P and dS, not by the tensor pipe.
+    B, T = 128, 383
     unit = B * hq * (T * (T + 1) / 2.0) * d * 2.0
-    for name, products, label in (("attention_fwd", 2, "forward"), ("attention_bwd", 7, "backward (dK/dV + dQ)")):
+    for name, products, label, note in (
+            ("attention_fwd", 2, "forward", "tcgen05: Q as the A operand in tensor memory, K/V by TMA, P through shared memory"),
+            ("attention_bwd", 5, "backward (pack, P, dS, dV, dK, dQ)", "tcgen05 score kernel + batched products; 3.6 GB of P / dS traffic per call")):
         ms = ctx.profile_kernel(name, [B, hq, hkv, d, T], 10)
         tf = products * unit / (ms * 1e-3) / 1e12
         out.append({"kernel": name, "workload": f"d12 one layer of a training pass, {B} x {T} tokens, {label}", "bound": "tensor", "ms": ms,
-                    "achieved": tf, "peak": gemm_peak, "unit": "TFLOP/s", "frac": tf / gemm_peak if gemm_peak else None,
-                    "note": "mma.sync m16n8k8 tf32; a dense loop of that instruction reaches 278/3 = 92 TFLOP/s useful on this GPU"})
+                    "achieved": tf, "peak": gemm_peak, "unit": "TFLOP/s", "frac": tf / gemm_peak if gemm_peak else None, "note": note})
     return out
 
 

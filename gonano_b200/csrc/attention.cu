@@ -196,10 +196,9 @@ template <int DP>
 static int attn_fwd_go(const AttnShape& sh, const float* q, const float* k, const float* v, float* out, float* lse, cudaStream_t s) {
   constexpr int LQ = 68, LV = DP + 4;
   size_t smem = sizeof(float) * (size_t)(2 * DP * LQ + 64 * LV + 64 * LQ);
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     GN_CUDA(cudaFuncSetAttribute(attn_fwd_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
   }
   dim3 grid(ceil_div(sh.Tq, 64), sh.B * sh.Hq);
   attn_fwd_kernel<DP><<<grid, AT, smem, s>>>(sh, q, k, v, out, lse);
@@ -538,8 +537,8 @@ static bool fast128_ok(const AttnShape& sh, const void* p0, const void* p1, cons
 
 static int attn_fwd128_go(const AttnShape& sh, const float* q, const float* k, const float* v, float* out, float* lse, cudaStream_t s) {
   const size_t smem = sizeof(float) * (size_t)(FD * 132 + FD * 68 + 64 * 132 + 64 * 132);
-  static bool configured = false;
-  if (!configured) { GN_CUDA(cudaFuncSetAttribute(attn_fwd128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); configured = true; }
+  static PerDeviceOnce configured;
+  if (configured.first()) { GN_CUDA(cudaFuncSetAttribute(attn_fwd128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); }
   dim3 grid(ceil_div(sh.Tq, 128), sh.B * sh.Hq);
   attn_fwd128_kernel<<<grid, AT, smem, s>>>(sh, q, k, v, out, lse);
   GN_LAUNCH_CHECK();
@@ -549,11 +548,10 @@ static int attn_bwd128_go(const AttnShape& sh, const float* q, const float* k, c
                           float* dq, float* dk, float* dv, int accumulate, cudaStream_t s) {
   const size_t smem_kv = sizeof(float) * (size_t)(4 * FD * 68 + 2 * 64 * 132);
   const size_t smem_q = sizeof(float) * (size_t)(4 * FD * 68 + 64 * 132);
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     GN_CUDA(cudaFuncSetAttribute(attn_bwd128_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv));
     GN_CUDA(cudaFuncSetAttribute(attn_bwd128_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_q));
-    configured = true;
   }
   dim3 gkv(ceil_div(sh.Tk, 64), sh.B * sh.Hkv);
   attn_bwd128_dkv_kernel<<<gkv, AT, smem_kv, s>>>(sh, q, k, v, dout, lse, delta, dk, dv, accumulate);
@@ -791,11 +789,10 @@ static int attn_bwd_go(const AttnShape& sh, const float* q, const float* k, cons
   constexpr int LD = DP + 4;
   size_t smem_kv = sizeof(float) * (size_t)(2 * DP * 68 + 2 * DP * 36 + 2 * 32 * LD + 2 * 32 * 68);
   size_t smem_q = sizeof(float) * (size_t)(2 * DP * 68 + 2 * DP * 36 + 32 * LD + 32 * 68);
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     GN_CUDA(cudaFuncSetAttribute(attn_bwd_dkv_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv));
     GN_CUDA(cudaFuncSetAttribute(attn_bwd_dq_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_q));
-    configured = true;
   }
   dim3 gkv(ceil_div(sh.Tk, 64), sh.B * sh.Hkv);
   attn_bwd_dkv_kernel<DP><<<gkv, AT, smem_kv, s>>>(sh, q, k, v, dout, lse, delta, dk, dv, accumulate);
@@ -1259,8 +1256,8 @@ static int decode_go(const float* q, int64_t q_rstride, const float* kcache, con
   int psplits = 0;
   psplits = attention_decode_prefix_splits(rows, group, Hq, Hkv, D, prefix_len);
   if (psplits > 0) {
-    static bool configured = false;
-    if (!configured) { GN_CUDA(cudaFuncSetAttribute(attn_decode_prefix_kernel<RATIO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmem)); configured = true; }
+    static PerDeviceOnce configured;
+    if (configured.first()) { GN_CUDA(cudaFuncSetAttribute(attn_decode_prefix_kernel<RATIO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmem)); }
     dim3 pgrid((rows / group) * Hkv, psplits);
     attn_decode_prefix_kernel<RATIO><<<pgrid, 256, kPrefixSmem, s>>>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, Hq, Hkv, window, group,
                                                                      prefix_len, part_acc, part_ms, psplits + splits);

@@ -459,8 +459,8 @@ bool attention_mma_ok(const AttnShape& sh, const void* p0, const void* p1, const
 }
 
 int attention_mma_forward(const AttnShape& sh, const float* q, const float* k, const float* v, float* out, float* lse, cudaStream_t s) {
-  static bool configured = false;
-  if (!configured) { GN_CUDA(cudaFuncSetAttribute(attn_mma_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemFwd)); configured = true; }
+  static PerDeviceOnce configured;
+  if (configured.first()) { GN_CUDA(cudaFuncSetAttribute(attn_mma_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemFwd)); }
   dim3 grid(ceil_div(sh.Tq, BM), sh.B * sh.Hq);
   attn_mma_fwd_kernel<<<grid, NTH, kSmemFwd, s>>>(sh, q, k, v, out, lse);
   GN_LAUNCH_CHECK();
@@ -469,11 +469,10 @@ int attention_mma_forward(const AttnShape& sh, const float* q, const float* k, c
 
 int attention_mma_backward(const AttnShape& sh, const float* q, const float* k, const float* v, const float* dout, const float* lse, const float* delta,
                            float* dq, float* dk, float* dv, int accumulate, cudaStream_t s) {
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     GN_CUDA(cudaFuncSetAttribute(attn_mma_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemDkv));
     GN_CUDA(cudaFuncSetAttribute(attn_mma_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemDq));
-    configured = true;
   }
   dim3 gkv(ceil_div(sh.Tk, BM), sh.B * sh.Hkv);
   attn_mma_dkv_kernel<<<gkv, NTH, kSmemDkv, s>>>(sh, q, k, v, dout, lse, delta, dk, dv, accumulate);

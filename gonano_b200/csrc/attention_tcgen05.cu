@@ -663,8 +663,8 @@ int attention_tc_forward(const AttnShape& sh, const float* q, const float* k, co
   GN_TRY(tc_make_map3(&mkl, lo + nq, (int64_t)sh.B * sh.Tk, (int64_t)sh.Hkv * AD, (int64_t)sh.Hkv * AD, AKV, AD / 32));
   GN_TRY(tc_make_map_mn3(&mvh, hi + nq + nk, (int64_t)sh.Hkv * AD, (int64_t)sh.B * sh.Tk, (int64_t)sh.Hkv * AD, AD / 32));
   GN_TRY(tc_make_map_mn3(&mvl, lo + nq + nk, (int64_t)sh.Hkv * AD, (int64_t)sh.B * sh.Tk, (int64_t)sh.Hkv * AD, AD / 32));
-  static bool configured = false;
-  if (!configured) { GN_CUDA(cudaFuncSetAttribute(attn_tc_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFwd)); configured = true; }
+  static PerDeviceOnce configured;
+  if (configured.first()) { GN_CUDA(cudaFuncSetAttribute(attn_tc_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFwd)); }
   AttnTc p{};
   p.B = sh.B; p.Hq = sh.Hq; p.Hkv = sh.Hkv; p.Tq = sh.Tq; p.Tk = sh.Tk; p.window = sh.window; p.offset = sh.offset0;
   p.out = out; p.o_bstride = sh.o_bstride; p.o_tstride = sh.o_tstride; p.lse = lse;
@@ -703,8 +703,8 @@ int attention_tc_backward(const AttnShape& sh, const float* q, const float* k, c
     attn_tc_batches_kernel<<<ceil_div(nbq, 256), 256, 0, s>>>(by_q, by_kv, sh.B, sh.Hq, sh.Hkv, Tp, sh.q_bstride, sh.kv_bstride, sh.kv_hstride);
     GN_LAUNCH_CHECK();
   }
-  static bool configured = false;
-  if (!configured) { GN_CUDA(cudaFuncSetAttribute(attn_tc_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemScore)); configured = true; }
+  static PerDeviceOnce configured;
+  if (configured.first()) { GN_CUDA(cudaFuncSetAttribute(attn_tc_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemScore)); }
   GN_REQUIRE(sh.B <= 65535 && sh.Hq <= 65535, "attention: %d sequences x %d heads exceed the grid", sh.B, sh.Hq);
   const dim3 grid(Tp / AQ, sh.Hq, sh.B);
   for (int mode = 0; mode < 2; ++mode) {

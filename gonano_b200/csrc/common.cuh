@@ -1,5 +1,6 @@
 // Shared declarations for the gonano CUDA backend (sm_100a).
 #pragma once
+#include <atomic>
 #include <cuda_runtime.h>
 #include <cstdint>
 #include <cstdio>
@@ -48,6 +49,18 @@ void count_launches(int64_t n);   // kernels replayed through a CUDA graph
 
 // Streaming multiprocessors of the current device (148 on B200), queried once per device.
 int num_sms();
+
+// Function attributes (cudaFuncSetAttribute) are per device: first() is true the first time a call site runs on the
+// current device, from whichever thread.
+struct PerDeviceOnce {
+  std::atomic<unsigned long long> done{0};
+  bool first() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+    const unsigned long long bit = 1ull << dev;
+    return (done.fetch_or(bit) & bit) == 0;
+  }
+};
 
 static inline int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
 

@@ -916,11 +916,10 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
 template <int BN, int STAGES>
 int launch_tc(GemmState& gs, const SplitBuf& a, const SplitBuf& b, const TcEpilogue& ep_in, int M, int N, int K, int splits, cudaStream_t s, Partials* leave = nullptr) {
   using S = TcSmem<BN, STAGES>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     GN_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL - S::STG_BYTES));
     GN_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
-    configured = true;
   }
   CUtensorMap mah, mal, mbh, mbl;
   const bool a3 = a.mn && gs.mn3d && M % 32 == 0;
@@ -1043,8 +1042,8 @@ int launch_skinny(GemmState& gs, const SplitBuf& a, const GemmArgs& g, const TcE
   GN_REQUIRE(stages >= 1 && stage_bytes * stages + bar_bytes <= 227 * 1024, "few-row product: a stage of %d bytes does not fit shared memory", stage_bytes);
   p.stages = stages;
   const size_t smem = (size_t)stages * stage_bytes + bar_bytes;
-  static bool configured = false;
-  if (!configured) { GN_CUDA(cudaFuncSetAttribute(gemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)); configured = true; }
+  static PerDeviceOnce configured;
+  if (configured.first()) { GN_CUDA(cudaFuncSetAttribute(gemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)); }
   CUtensorMap mw, mxh, mxl;
   GN_TRY(make_map(&mw, g.B, N, K, g.ldb, TBM));
   GN_TRY(make_map(&mxh, a.hi, M, K, a.ld, p.rowsN));
@@ -1256,8 +1255,8 @@ int gemm_tc_batched(const TcBatched& g, cudaStream_t s) {
   GN_TRY(state_for(s, &st));
   GN_TRY(ensure_init());
   using S = TcSmem<128, 3>;
-  static bool configured = false;
-  if (!configured) { GN_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<128, 3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL - S::STG_BYTES)); configured = true; }
+  static PerDeviceOnce configured;
+  if (configured.first()) { GN_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<128, 3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL - S::STG_BYTES)); }
   GN_REQUIRE(g.batches >= 1 && g.batches <= 65535 && g.batch != nullptr, "batched product: %d batches", g.batches);
   CUtensorMap mah, mal, mbh, mbl;
   // MN-major operands whose MN extent is a multiple of 32 come as one 3-D box per tile (the batch offsets in MN must then be multiples of 32)
