@@ -236,9 +236,10 @@ __global__ void __launch_bounds__(352, 1) attn_tc_fwd_kernel(const __grid_consta
       mbar_arrive(q_done);
       if (threadIdx.x == 64) AT_TRACE(3);
     }
-    for (int j = 0; j < n && !failed; ++j) {
+    for (int j = 0; j < n; ++j) {
       const int kv0 = k_begin + j * AKV;
-      if (!mbar_wait(s_full(j & 1), (uint32_t)(j >> 1) & 1u)) { failed = true; break; }
+      if (!failed && !mbar_wait(s_full(j & 1), (uint32_t)(j >> 1) & 1u)) failed = true;
+      if (failed) { asm volatile("bar.sync 1, 256;" ::: "memory"); continue; }   // a thread that gave up still meets the others at every barrier
       tc_fence_after();
       if (threadIdx.x == 64 && j < 8) AT_TRACE(16 + 8 * j);
       float s[32];
@@ -277,7 +278,7 @@ __global__ void __launch_bounds__(352, 1) attn_tc_fwd_kernel(const __grid_consta
       const bool need = mx > m_used + kRescaleStep;
       if (j > 0) {
         // the previous P V has finished: P may be overwritten and O is at rest
-        if (!mbar_wait(pv_done, (uint32_t)(j - 1) & 1u)) { failed = true; break; }
+        if (!mbar_wait(pv_done, (uint32_t)(j - 1) & 1u)) { failed = true; continue; }
         tc_fence_after();
         if (threadIdx.x == 64 && j < 8) AT_TRACE(18 + 8 * j);
         if (__any_sync(0xffffffffu, need)) {
@@ -338,7 +339,12 @@ __global__ void __launch_bounds__(352, 1) attn_tc_fwd_kernel(const __grid_consta
     }
     if (!failed) {
       const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-      float* dst = p.out + (int64_t)b * p.o_bstride + (int64_t)(q0 + row) * p.o_tstride + (int64_t)hq * AD + half * 64;
+      // The thread owns a row, a store wants a row segment: 32 x 32 staging tile per warp (the P area is idle now),
+      // then eight lanes write the 128 contiguous bytes of a row.
+      float* stg = reinterpret_cast<float*>(gen + P_HI) + (warp - 2) * (32 * 36);
+      const int rr0 = lane >> 3, cc = (lane & 7) * 4;
+      float* dst0 = p.out + (int64_t)b * p.o_bstride + (int64_t)(q0 + quarter * 32) * p.o_tstride + (int64_t)hq * AD + half * 64;
+      const int rows_valid = qvalid - quarter * 32;   // rows of this warp inside the sequence
 #pragma unroll
       for (int c0 = 0; c0 < 64; c0 += 32) {
         uint32_t r[32];
@@ -347,12 +353,17 @@ __global__ void __launch_bounds__(352, 1) attn_tc_fwd_kernel(const __grid_consta
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = 0u;
         }
-        if (row < qvalid) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            *reinterpret_cast<float4*>(dst + c0 + i) = make_float4(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv,
-                                                                   __uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+        for (int i = 0; i < 32; i += 4)
+          *reinterpret_cast<float4*>(stg + lane * 36 + i) = make_float4(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv,
+                                                                        __uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+        __syncwarp();
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int rr = it * 4 + rr0;
+          if (rr < rows_valid) *reinterpret_cast<float4*>(dst0 + (int64_t)rr * p.o_tstride + c0 + cc) = *reinterpret_cast<const float4*>(stg + rr * 36 + cc);
         }
+        __syncwarp();
       }
       if (p.lse && half == 0 && row < qvalid) p.lse[((int64_t)b * p.Hq + hq) * p.Tq + q0 + row] = l_run > 0.0f ? m_used + logf(l_run) : -1e30f;
       if (threadIdx.x == 64) AT_TRACE(9);
@@ -526,17 +537,19 @@ __global__ void __launch_bounds__(320, 1) attn_tc_score_kernel(const __grid_cons
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const uint32_t sw = (uint32_t)(row & 7);
     // the stationary operand: ring stages 0..3 -> tensor memory (half 0 moves hi to columns [0,128), half 1 lo to [128,256))
-    for (int kb = 0; kb < 4 && !failed; ++kb) {
-      if (!mbar_wait(full_bar(kb), 0u)) { failed = true; break; }
-      const uint8_t* src = gen + kb * SC_STAGE_BYTES + half * 16384 + row * 128;
-      uint32_t r[32];
+    for (int kb = 0; kb < 4; ++kb) {
+      if (!failed && !mbar_wait(full_bar(kb), 0u)) failed = true;
+      if (!failed) {
+        const uint8_t* src = gen + kb * SC_STAGE_BYTES + half * 16384 + row * 128;
+        uint32_t r[32];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const uint4 x = *reinterpret_cast<const uint4*>(src + ((c ^ sw) << 4));
-        r[4 * c] = x.x; r[4 * c + 1] = x.y; r[4 * c + 2] = x.z; r[4 * c + 3] = x.w;
+        for (int c = 0; c < 8; ++c) {
+          const uint4 x = *reinterpret_cast<const uint4*>(src + ((c ^ sw) << 4));
+          r[4 * c] = x.x; r[4 * c + 1] = x.y; r[4 * c + 2] = x.z; r[4 * c + 3] = x.w;
+        }
+        tmem_st32(lane_addr + half * 128 + kb * 32, r);
       }
-      tmem_st32(lane_addr + half * 128 + kb * 32, r);
-      asm volatile("bar.sync 1, 256;" ::: "memory");          // every thread has read the stage
+      asm volatile("bar.sync 1, 256;" ::: "memory");          // every thread has read the stage (also met by a thread that gave up)
       if (threadIdx.x == 64) mbar_arrive(empty_bar(kb));
     }
     tmem_st_wait();

@@ -484,6 +484,7 @@ int gn_ctx_set_option(gn_ctx* c, const char* name, int value) {
   if (n == "attention_tcgen05") { attention_tc_enable(value); return GN_OK; }
 #endif
   if (c && n == "decode_graph") { c->use_graphs = value != 0; return GN_OK; }
+  if (c && n == "optimizer_lanes") { GN_REQUIRE(value >= 1 && value <= 4, "optimizer_lanes must be 1..4"); c->optimizer_lanes = value; return GN_OK; }
   if (c && n == "head_chunk_rows") { GN_REQUIRE(value >= 1, "head_chunk_rows must be positive"); c->head_chunk_rows = value; return GN_OK; }
   cudaStream_t s = nullptr;
   if (c) { GN_CUDA(cudaSetDevice(c->device)); s = c->stream; }
@@ -566,6 +567,11 @@ int gn_model_destroy(gn_model* m) {
                     &m->tgt_dev, &m->adv_dev, &m->rowloss, &m->loss_dev, &m->in_dev, &m->lat_ws, &m->cache_lat, &m->cache_rope, &m->opt_mom, &m->opt_second,
                     &m->opt_ws};
   for (DevBuf* b : bufs) b->release();
+  for (int l = 1; l < gn_model::kOptLanes; ++l) {
+    m->opt_ws_lane[l].release();
+    if (m->opt_stream[l]) { cudaStreamSynchronize(m->opt_stream[l]); gemm_release_stream(m->opt_stream[l]); cudaStreamDestroy(m->opt_stream[l]); }
+  }
+  for (int l = 0; l <= gn_model::kOptLanes; ++l) if (m->opt_event[l]) cudaEventDestroy(m->opt_event[l]);
   for (int i = 0; i < 4; ++i) if (m->ev[i]) cudaEventDestroy(m->ev[i]);
   delete m;
   return GN_OK;
@@ -676,6 +682,11 @@ int gn_model_optimizer_init(gn_model* m, const gn_optimizer_config* cfg) {
     else if (!scalar) ws = std::max(ws, muon_workspace_bytes(experts ? pi.rows / m->E : pi.rows, pi.cols));
   }
   GN_TRY(m->opt_ws.ensure(ws));
+  for (int l = 1; l < gn_model::kOptLanes; ++l) {
+    GN_TRY(m->opt_ws_lane[l].ensure(ws));
+    if (!m->opt_stream[l]) GN_CUDA(cudaStreamCreateWithFlags(&m->opt_stream[l], cudaStreamNonBlocking));
+  }
+  for (int l = 0; l <= gn_model::kOptLanes; ++l) if (!m->opt_event[l]) GN_CUDA(cudaEventCreateWithFlags(&m->opt_event[l], cudaEventDisableTiming));
   m->opt_ready = true;
   return GN_OK;
 }
@@ -685,7 +696,7 @@ int gn_model_optimizer_init(gn_model* m, const gn_optimizer_config* cfg) {
 // this shard owns are updated (ownership: greedy balance of an operation-count estimate, identical on every rank).
 }  // extern "C"
 namespace gnm {
-std::vector<int> optimizer_owners(gn_model* m, int shard_count) {
+std::vector<int> optimizer_owners(gn_model* m, int shard_count, const std::vector<int>* within, int within_value) {
   const size_t n = m->params.size();
   std::vector<int> owner(n, 0);
   if (shard_count <= 1) return owner;
@@ -702,6 +713,7 @@ std::vector<int> optimizer_owners(gn_model* m, int shard_count) {
   std::sort(cost.begin(), cost.end(), [](const std::pair<double, size_t>& a, const std::pair<double, size_t>& b) { return a.first != b.first ? a.first > b.first : a.second < b.second; });
   std::vector<double> load(shard_count, 0.0);
   for (auto& c : cost) {
+    if (within && (*within)[c.second] != within_value) continue;
     int best = 0;
     for (int r = 1; r < shard_count; ++r) if (load[r] < load[best]) best = r;
     owner[c.second] = best; load[best] += c.first;
@@ -718,13 +730,25 @@ int optimizer_run(gn_model* m, int shard, int shard_count) {
   ++m->opt_steps;
   const float dscale = (float)std::pow((double)m->d / 768.0, -0.5);   // model/optimizer.go:108
   const std::vector<int> owner = optimizer_owners(m, shard_count);
+  // lanes: the owned tensors in cost order, each to the least loaded lane (the same cost model as the owners)
+  const int lanes = std::max(1, std::min(m->ctx->optimizer_lanes, (int)gn_model::kOptLanes));
+  std::vector<int> lane_of(m->params.size(), 0);
+  if (lanes > 1) {
+    const std::vector<int> by_lane = optimizer_owners(m, lanes, &owner, shard);
+    lane_of = by_lane;
+    GN_CUDA(cudaEventRecord(m->opt_event[0], m->s()));
+    for (int l = 1; l < lanes; ++l) GN_CUDA(cudaStreamWaitEvent(m->opt_stream[l], m->opt_event[0], 0));
+  }
   for (size_t i = 0; i < m->params.size(); ++i) {
     if (owner[i] != shard) continue;
+    const int lane = lane_of[i];
+    cudaStream_t s = lane == 0 ? m->s() : m->opt_stream[lane];
+    void* lane_ws = lane == 0 ? m->opt_ws.p : m->opt_ws_lane[lane].p;
     const ParamInfo& pi = m->params[i];
     float* p = m->p(pi.offset); float* g = m->g(pi.offset);
     float* mo = m->opt_mom.f() + pi.offset; float* se = m->opt_second.f() + pi.offset;
     const int64_t n = (int64_t)pi.rows * pi.cols;
-    auto sink = [&](float lr) { return sinkhorn_launch(p, g, mo, pi.rows, pi.cols, lr * c.lr_mult, 0.95f, 0.18f, 11, 1e-3f, 1e-20f, m->opt_ws.p, s); };
+    auto sink = [&](float lr) { return sinkhorn_launch(p, g, mo, pi.rows, pi.cols, lr * c.lr_mult, 0.95f, 0.18f, 11, 1e-3f, 1e-20f, lane_ws, s); };
     auto adam = [&](float lr, float b1, float b2, float wd) { return adamw_launch(p, g, mo, se, n, m->opt_steps, lr * c.lr_mult, b1, b2, 1e-10f, wd, s); };
     if (pi.name == "lm_head.weight") GN_TRY(sink(c.unembedding_lr * dscale));
     else if (pi.name == "transformer.wte.weight") GN_TRY(sink(c.embedding_lr * dscale));
@@ -738,10 +762,16 @@ int optimizer_run(gn_model* m, int shard, int shard_count) {
       const int er = pi.rows / m->E;
       for (int e = 0; e < m->E; ++e) {
         const int64_t off = (int64_t)e * er * pi.cols;
-        GN_TRY(muon_launch(p + off, g + off, mo + off, se + off, er, pi.cols, c.matrix_lr * c.lr_mult, 0.95f, 5, 0.9f, c.weight_decay, m->opt_ws.p, m->ctx->gemm_kind, s));
+        GN_TRY(muon_launch(p + off, g + off, mo + off, se + off, er, pi.cols, c.matrix_lr * c.lr_mult, 0.95f, 5, 0.9f, c.weight_decay, lane_ws, m->ctx->gemm_kind, s));
       }
     }
-    else GN_TRY(muon_launch(p, g, mo, se, pi.rows, pi.cols, c.matrix_lr * c.lr_mult, 0.95f, 5, 0.9f, c.weight_decay, m->opt_ws.p, m->ctx->gemm_kind, s));
+    else GN_TRY(muon_launch(p, g, mo, se, pi.rows, pi.cols, c.matrix_lr * c.lr_mult, 0.95f, 5, 0.9f, c.weight_decay, lane_ws, m->ctx->gemm_kind, s));
+  }
+  if (lanes > 1) {
+    for (int l = 1; l < lanes; ++l) {
+      GN_CUDA(cudaEventRecord(m->opt_event[l], m->opt_stream[l]));
+      GN_CUDA(cudaStreamWaitEvent(m->s(), m->opt_event[l], 0));
+    }
   }
   if (shard_count > 1) {
     // Exchange form: the gradient buffer becomes "my updated tensors, zero elsewhere"; a SUM all-reduce over it then
@@ -770,6 +800,7 @@ int gn_model_optimizer_step(gn_model* m) {
   GN_CUDA(cudaStreamSynchronize(s));
   float ms = 0;
   GN_CUDA(cudaEventElapsedTime(&ms, m->ev[0], m->ev[1])); m->phase_ms["optimizer"] = ms;
+  for (int l = 1; l < gn_model::kOptLanes; ++l) if (m->opt_stream[l]) GN_TRY(gemm_check_error(m->opt_stream[l]));
   return gemm_check_error(s);
 }
 
@@ -784,6 +815,7 @@ int gn_model_optimizer_step_shard(gn_model* m, int shard, int shard_count) {
   GN_CUDA(cudaStreamSynchronize(s));
   float ms = 0;
   GN_CUDA(cudaEventElapsedTime(&ms, m->ev[0], m->ev[1])); m->phase_ms["optimizer"] = ms;
+  for (int l = 1; l < gn_model::kOptLanes; ++l) if (m->opt_stream[l]) GN_TRY(gemm_check_error(m->opt_stream[l]));
   return gemm_check_error(s);
 }
 

@@ -161,6 +161,12 @@ struct gn_model {
   DevBuf part_acc, part_ms, step_dev;
   // optimizer state (gn_model_optimizer_init): momentum / exp_avg and second moment / exp_avg_sq at the parameter's offset
   DevBuf opt_mom, opt_second, opt_ws;
+  // The tensors of an optimizer step are independent: they are updated on kOptLanes streams side by side (lane 0 is the
+  // context's stream), each with its own workspace.
+  static constexpr int kOptLanes = 4;
+  cudaStream_t opt_stream[kOptLanes] = {nullptr, nullptr, nullptr, nullptr};
+  cudaEvent_t opt_event[kOptLanes + 1] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+  DevBuf opt_ws_lane[kOptLanes];
   gn_optimizer_config opt_cfg{};
   int opt_steps = 0;
   bool opt_ready = false;
@@ -184,7 +190,9 @@ inline int gemm(gn_model* m, const gn::GemmArgs& a) { return gn::gemm_dispatch(a
 
 // Which shard updates which tensor in a sharded optimizer step: a greedy balance of an operation-count estimate,
 // identical on every rank (index = position in gn_model::params).
-std::vector<int> optimizer_owners(gn_model* m, int shard_count);
+// Cost-balanced assignment of the parameters to `shard_count` bins; with `within`, only the parameters whose entry equals
+// `within_value` are assigned (the others stay in bin 0).
+std::vector<int> optimizer_owners(gn_model* m, int shard_count, const std::vector<int>* within = nullptr, int within_value = 0);
 
 // model_latent.cu: the two block variants of the latent preset, inference only.
 // Attention of layer l from H = norm(x) (with its tf32 split in b.S1h/b.S1l on the tensor-core path):
