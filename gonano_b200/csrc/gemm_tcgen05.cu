@@ -32,6 +32,7 @@
 #include <map>
 #include <mutex>
 #include <tuple>
+#include <type_traits>
 
 #include "kernels.cuh"
 #include "tcgen05.cuh"
@@ -116,7 +117,8 @@ struct TcSmem {
 template <int BN, int STAGES, bool PERSIST>
 __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
                                                          const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
-                                                         const __grid_constant__ CUtensorMap tmC, TcEpilogue ep, int M, int N, int K, int* err) {
+                                                         const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmCh, const __grid_constant__ CUtensorMap tmCl,
+                                                         TcEpilogue ep, int M, int N, int K, int* err) {
   using S = TcSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   // swizzled tiles want 1024-byte alignment
@@ -371,27 +373,52 @@ __global__ void __launch_bounds__(64 + 32 * (BN > 128 ? 8 : 4), 1) gemm_tc_kerne
       }
     }
     if (!failed && !persistent && ep.tma_store) {
-      // Plain stores (a product's result or its K-split partial plane) leave through the bulk-tensor path: each warp
-      // stages its 32 rows as 32-column blocks in the 128-byte-swizzled layout (lane = row, chunk c at c ^ (row % 8):
-      // conflict-free) and one lane issues a store per block; rows and columns outside the matrix are clipped by the map.
+      // Results without a read-modify-write (plain, relu^2, softcap; K-split partial planes) leave through the
+      // bulk-tensor path: each warp stages its 32 rows as 32-column blocks in the 128-byte-swizzled layout (lane = row,
+      // chunk c at c ^ (row % 8): conflict-free) and one lane issues a store per block; rows and columns outside the
+      // matrix are clipped by the map.  The tf32 split of the result, when asked for, follows through maps of its own.
       const uint32_t sb = base + (uint32_t)(warp - 2) * (uint32_t)(ACC * 128);
       uint8_t* sg = gen_base + (size_t)(warp - 2) * (ACC * 128);
       if (warp == 2 && lane == 0) TC_TRACE(898);
+      if (ep.epi == EPI_RELU2) {
 #pragma unroll
-      for (int cb = 0; cb < ACC / 32; ++cb)
+        for (int j = 0; j < ACC; ++j) { const float t = acc[j] < 0.0f ? 0.0f : acc[j]; acc[j] = t * t; }
+      } else if (ep.epi == EPI_SOFTCAP) {
+        const float invs = 1.0f / ep.scalar;
 #pragma unroll
-        for (int c = 0; c < 8; ++c)
-          *reinterpret_cast<float4*>(sg + cb * 4096 + lane * 128 + ((c ^ (lane & 7)) << 4)) =
-              make_float4(acc[cb * 32 + 4 * c], acc[cb * 32 + 4 * c + 1], acc[cb * 32 + 4 * c + 2], acc[cb * 32 + 4 * c + 3]);
-      fence_async_smem();
-      __syncwarp();
-      if (warp == 2 && lane == 0) TC_TRACE(899);
-      if (lane == 0) {
-#pragma unroll
-        for (int cb = 0; cb < ACC / 32; ++cb) tma_store_3d(&tmC, sb + cb * 4096, n0 + chalf + cb * 32, m0 + quarter * 32, zsplits > 1 ? (int)blockIdx.z : 0);
-        tma_store_commit_wait();
+        for (int j = 0; j < ACC; ++j) acc[j] = ep.scalar * tanhf(acc[j] * invs);
       }
-      __syncwarp();
+      // part 0: the value; parts 1 and 2: its tf32 hi and lo (compile-time, so that the accumulator stays in registers)
+      auto store_part = [&](auto part_c, const CUtensorMap* mp) {
+        constexpr int part = decltype(part_c)::value;
+#pragma unroll
+        for (int cb = 0; cb < ACC / 32; ++cb)
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            float o[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const float v = acc[cb * 32 + 4 * c + t];
+              if (part == 0) o[t] = v;
+              else { float h, l; split_tf32(v, h, l); o[t] = part == 1 ? h : l; }
+            }
+            *reinterpret_cast<float4*>(sg + cb * 4096 + lane * 128 + ((c ^ (lane & 7)) << 4)) = make_float4(o[0], o[1], o[2], o[3]);
+          }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+#pragma unroll
+          for (int cb = 0; cb < ACC / 32; ++cb) tma_store_3d(mp, sb + cb * 4096, n0 + chalf + cb * 32, m0 + quarter * 32, zsplits > 1 ? (int)blockIdx.z : 0);
+          tma_store_commit_wait();
+        }
+        __syncwarp();
+      };
+      store_part(std::integral_constant<int, 0>{}, &tmC);
+      if (warp == 2 && lane == 0) TC_TRACE(899);
+      if (ep.c_hi) {
+        store_part(std::integral_constant<int, 1>{}, &tmCh);
+        store_part(std::integral_constant<int, 2>{}, &tmCl);
+      }
     } else if (!failed && !persistent) {
       // The accumulator row of a thread is scattered (thread = row), so it goes through shared
       // memory first: the pipeline stages are idle once the last chunk has been drained, and
@@ -961,17 +988,24 @@ int launch_tc(GemmState& gs, const SplitBuf& a, const SplitBuf& b, const TcEpilo
     if (ep.tiles_gn > ep.tiles_n) ep.tiles_gn = ep.tiles_n;
     grid = dim3(pctas, 1, 1);
   }
-  // One-tile CTAs with a plain store (results and K-split partial planes) write through a tensor map of C.
-  CUtensorMap mc = mah;
-  if (gs.tma_store && ep.tiles_total == 0 && ep.groups == 0 && ep.epi == EPI_STORE && ep.aux == nullptr && ep.c_hi == nullptr && ep.ldc % 4 == 0 &&
-      (reinterpret_cast<uintptr_t>(ep.C) & 15) == 0 && (splits == 1 || ((int64_t)M * N) % 4 == 0)) {
+  // One-tile CTAs whose epilogue reads nothing (plain, relu^2 without the saved pre-activation, softcap; K-split partial
+  // planes) write through tensor maps of C and of the result's tf32 split.
+  CUtensorMap mc = mah, mch = mah, mcl = mah;
+  const bool tma_epi = ep.epi == EPI_STORE || (ep.epi == EPI_RELU2 && ep.aux == nullptr) || ep.epi == EPI_SOFTCAP;
+  if (gs.tma_store && ep.tiles_total == 0 && ep.groups == 0 && tma_epi && ep.aux == nullptr && ep.ldc % 4 == 0 &&
+      (reinterpret_cast<uintptr_t>(ep.C) & 15) == 0 && (splits == 1 || ((int64_t)M * N) % 4 == 0) &&
+      (ep.c_hi == nullptr || (((reinterpret_cast<uintptr_t>(ep.c_hi) | reinterpret_cast<uintptr_t>(ep.c_lo)) & 15) == 0))) {
     cuuint64_t dims[3] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)splits};
     cuuint64_t strides[2] = {(cuuint64_t)ep.ldc * sizeof(float), (cuuint64_t)(splits > 1 ? ep.split_stride : (int64_t)M * ep.ldc) * sizeof(float)};
     cuuint32_t box[3] = {32, 32, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = g_encode(&mc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)ep.C, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r == CUDA_SUCCESS) ep.tma_store = 1;
+    auto enc = [&](CUtensorMap* mp, float* ptr) {
+      return g_encode(mp, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    };
+    bool ok = enc(&mc, ep.C);
+    if (ok && ep.c_hi) ok = enc(&mch, ep.c_hi) && enc(&mcl, ep.c_lo);
+    if (ok) ep.tma_store = 1;
   }
   {
     cudaLaunchConfig_t cfg{};
@@ -980,8 +1014,8 @@ int launch_tc(GemmState& gs, const SplitBuf& a, const SplitBuf& b, const TcEpilo
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = gs.pdl ? 1 : 0;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    if (ep.tiles_total > 0) GN_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, true>, mah, mal, mbh, mbl, mc, ep, M, N, K, gs.err_flag));
-    else GN_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, false>, mah, mal, mbh, mbl, mc, ep, M, N, K, gs.err_flag));
+    if (ep.tiles_total > 0) GN_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, true>, mah, mal, mbh, mbl, mc, mch, mcl, ep, M, N, K, gs.err_flag));
+    else GN_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, false>, mah, mal, mbh, mbl, mc, mch, mcl, ep, M, N, K, gs.err_flag));
   }
   GN_LAUNCH_CHECK();
   if (leave) {
@@ -1277,7 +1311,7 @@ int gemm_tc_batched(const TcBatched& g, cudaStream_t s) {
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 0;
   cfg.attrs = attr; cfg.numAttrs = 1;
-  GN_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<128, 3, false>, mah, mal, mbh, mbl, mah, ep, g.M, g.N, g.K, st->err_flag));
+  GN_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<128, 3, false>, mah, mal, mbh, mbl, mah, mah, mah, ep, g.M, g.N, g.K, st->err_flag));
   GN_LAUNCH_CHECK();
   return GN_OK;
 }
