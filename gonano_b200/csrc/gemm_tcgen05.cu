@@ -787,6 +787,7 @@ struct GemmState {
   bool mn = true;             // read [K, M] / [K, N] operands MN-major instead of transposing them while splitting
   bool mn3d = true;           // one 3-D TMA box per MN-major tile instead of one 2-D box per 32 columns
   bool tma_store = true;      // one-tile CTAs store plain results through a tensor map of C
+  bool wide_split = true;     // 128 x 256 tiles with a K split for outputs of half a wave to a wave of 128-wide tiles
 };
 std::map<std::pair<int, cudaStream_t>, GemmState*> g_states;
 
@@ -1177,6 +1178,13 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
   // two 128 x 128 units instead of 128 KB).
   if (splits == 1 && g.N >= 512 && (int64_t)ceil_div(g.M, TBM) * ceil_div(g.N, 256) >= num_sms() * 3 / 2)
     return launch_tc<256, 2>(gs, a, b, ep, g.M, g.N, g.K, 1, s, g.leave);
+  // Between half a wave and a wave of 128-wide tiles (c_fc of a 512-row decode step: 96): wide tiles with the K loop
+  // split fill the machine in one wave, each CTA moving 96 KB per k-block for twice the work.
+  if (splits == 1 && gs.wide_split && tiles < num_sms() && g.N % 256 == 0 && g.ldc % 4 == 0 && nk >= 8) {
+    const int64_t wide = (int64_t)ceil_div(g.M, TBM) * (g.N / 256);
+    const int ws = (int)std::min<int64_t>(num_sms() / wide, nk / 4);
+    if (ws >= 2) return launch_tc<256, 2>(gs, a, b, ep, g.M, g.N, g.K, ws, s, g.leave);
+  }
   return launch_tc<128, 3>(gs, a, b, ep, g.M, g.N, g.K, splits, s, g.leave);
 }
 
@@ -1230,6 +1238,7 @@ int gemm_tcgen05_option(cudaStream_t s, const char* name, int value) {
   else if (n == "gemm_mn_major") st->mn = value != 0;
   else if (n == "gemm_mn_3d") st->mn3d = value != 0;
   else if (n == "gemm_tma_store") st->tma_store = value != 0;
+  else if (n == "gemm_wide_split") st->wide_split = value != 0;
   else if (n == "gemm_few_rows_max") g_skinny_max_rows.store(value, std::memory_order_relaxed);
   else if (n == "gemm_few_rows_min_kblocks") g_skinny_min_kblocks.store(value, std::memory_order_relaxed);
   else if (n == "gemm_few_rows_block") g_skinny_block_rows.store(value, std::memory_order_relaxed);

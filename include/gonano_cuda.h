@@ -266,6 +266,7 @@ int gn_ctx_set_gemm(gn_ctx* ctx, int kind);
  *   "gemm_mn_major"          1 (default) operands stored [K, M] / [K, N] are read in place, 0 transposes them
  *   "gemm_mn_3d"             1 (default) one 3-D bulk-tensor copy per such tile instead of one per 32 columns
  *   "gemm_tma_store"         1 (default) one-tile products write plain results with bulk-tensor stores
+ *   "gemm_wide_split"        1 (default) 128 x 256 tiles with a K split when 128-wide tiles fill half a wave to a wave
  *   "gemm_few_rows_max"      256 (default): x W^T products with at most this many rows stream the float32 weights
  *                            once and split them on chip (the decode step's form); 0 = off (process-wide)
  *   "gemm_few_rows_min_kblocks"  2 (default): smallest K share (in 32-element blocks) of one CTA of that form
