@@ -1168,23 +1168,39 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
   // is bound by the 64 B/clk/SM path from L2.
   const int64_t tiles = (int64_t)ceil_div(g.M, TBM) * ceil_div(g.N, 128);
   const int nk = ceil_div(g.K, TBK);
-  int splits = 1;
-  if (tiles < num_sms() / 2 && g.N % 4 == 0 && g.ldc % 4 == 0) {
-    splits = (int)std::min<int64_t>(num_sms() / tiles, nk / 4);   // at least 4 k-blocks per split
-    if (splits < 1) splits = 1;
-  }
+  const int sms = num_sms();
   // Wide 128 x 256 tiles when the output is large: the K loop is bound by the 64 B/clk/SM path from
   // L2, and a 256-column tile reads the A operand once for twice the work (96 KB per k-block for
   // two 128 x 128 units instead of 128 KB).
-  if (splits == 1 && g.N >= 512 && (int64_t)ceil_div(g.M, TBM) * ceil_div(g.N, 256) >= num_sms() * 3 / 2)
+  if (g.N >= 512 && (int64_t)ceil_div(g.M, TBM) * ceil_div(g.N, 256) >= sms * 3 / 2)
     return launch_tc<256, 2>(gs, a, b, ep, g.M, g.N, g.K, 1, s, g.leave);
-  // Between half a wave and a wave of 128-wide tiles (c_fc of a 512-row decode step: 96): wide tiles with the K loop
-  // split fill the machine in one wave, each CTA moving 96 KB per k-block for twice the work.
-  if (splits == 1 && gs.wide_split && tiles < num_sms() && g.N % 256 == 0 && g.ldc % 4 == 0 && nk >= 8) {
+  // Up to about a wave of tiles: the tile width and the K split with the smallest estimated time.  A k-block costs a
+  // CTA ~1080 cycles with 128-wide tiles and ~1600 with 256-wide ones (both bound by the L2 -> SM path: 64 and 96 KB),
+  // a CTA ~12 000 cycles of set-up and store, a K split a reduction pass over its planes.
+  const bool can_split = g.N % 4 == 0 && g.ldc % 4 == 0;
+  auto estimate = [&](int bn, int sp) {
+    const int64_t t = (int64_t)ceil_div(g.M, TBM) * ceil_div(g.N, bn);
+    const double waves = (double)ceil_div(t * sp, sms);
+    double c = waves * (ceil_div(nk, sp) * (bn == 256 ? 1600.0 : 1080.0) + 12000.0);
+    if (sp > 1) c += 6000.0 + (double)g.M * g.N * 4.0 * (sp + 1) / 1600.0;
+    return c;
+  };
+  // 128-wide tiles: the K loop split over gridDim.z until about one CTA per SM runs (at least 4 k-blocks per split)
+  int best_bn = 128, best_sp = 1;
+  if (tiles < sms / 2 && can_split) best_sp = (int)std::max<int64_t>(1, std::min<int64_t>(sms / tiles, nk / 4));
+  double best = estimate(128, best_sp);
+  auto consider = [&](int bn, int sp) {
+    if (sp < 1 || (sp > 1 && !can_split)) return;
+    const double c = estimate(bn, sp);
+    if (c < best) { best = c; best_bn = bn; best_sp = sp; }
+  };
+  if (gs.wide_split && g.N % 256 == 0 && nk >= 8) {
     const int64_t wide = (int64_t)ceil_div(g.M, TBM) * (g.N / 256);
-    const int ws = (int)std::min<int64_t>(num_sms() / wide, nk / 4);
-    if (ws >= 2) return launch_tc<256, 2>(gs, a, b, ep, g.M, g.N, g.K, ws, s, g.leave);
+    consider(256, 1);
+    if (wide < sms) consider(256, (int)std::min<int64_t>(sms / wide, nk / 4));
   }
+  if (best_bn == 256) return launch_tc<256, 2>(gs, a, b, ep, g.M, g.N, g.K, best_sp, s, g.leave);
+  const int splits = best_sp;
   return launch_tc<128, 3>(gs, a, b, ep, g.M, g.N, g.K, splits, s, g.leave);
 }
 
