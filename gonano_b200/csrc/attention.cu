@@ -1098,138 +1098,23 @@ __global__ void __launch_bounds__(128) attn_decode_combine_kernel(const float* p
   }
 }
 
-// Shared prefix (head_dim 128): the G rows of a group hold identical K/V for the prompt positions (the
-// prefill was replicated, model/kvcache.go:383-448), so one CTA serves a whole group from the first
-// row's copy and the prompt's K/V rows reach the SM once per group instead of once per row.
-// CTA = (prompt, kv head, tile of 32 prompt positions), 8 warps:
-//   1. the K and V tiles and the group's NH = G * RATIO query vectors are staged in shared memory;
-//   2. scores: a warp owns up to 4 query heads, lane = key; the K row is read once for them;
-//      softmax statistics of the tile by warp reductions; probabilities go to shared memory;
-//   3. P.V: thread = channel, half the heads each; V rows are read conflict-free, P by broadcast.
-// The tile's (max, sum, unnormalised output) is one partial-result slot of each (row, head); the
-// combine pass merges it with the slots of the per-row kernel.
-constexpr int kPrefixTile = 32, kPrefixMaxHeads = 32;
-template <int RATIO>
-__global__ void __launch_bounds__(256) attn_decode_prefix_kernel(const float* __restrict__ q, int64_t q_rstride, const float* __restrict__ kcache,
-                                                                 const float* __restrict__ vcache, int64_t row_stride, int64_t head_stride,
-                                                                 const int32_t* __restrict__ ctx_len, int Hq, int Hkv, int window, int group,
-                                                                 int prefix_len, float* __restrict__ part_acc, float* __restrict__ part_ms, int nslots) {
-  constexpr int D = 128, LDK = D + 4;
-  extern __shared__ __align__(16) float psm[];
-  float* Ks = psm;                          // [32][LDK]
-  float* Vs = Ks + kPrefixTile * LDK;       // [32][LDK]
-  float* Qs = Vs + kPrefixTile * LDK;       // [NH][D]
-  float* Ps = Qs + kPrefixMaxHeads * D;     // [NH][32]
-  __shared__ float Ms[kPrefixMaxHeads], Ls[kPrefixMaxHeads];
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int p = blockIdx.x / Hkv, hk = blockIdx.x % Hkv, split = blockIdx.y;
-  const int NH = group * RATIO;
-  const int k0 = split * kPrefixTile, kvalid = min(kPrefixTile, prefix_len - k0);
-  const float* kb = kcache + (int64_t)p * group * row_stride + (int64_t)hk * head_stride + (int64_t)k0 * D;
-  const float* vb = vcache + (int64_t)p * group * row_stride + (int64_t)hk * head_stride + (int64_t)k0 * D;
-  for (int idx = tid; idx < kPrefixTile * (D / 4); idx += 256) {
-    const int r = idx >> 5, c = (idx & 31) * 4;
-    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-    if (r < kvalid) { a = *reinterpret_cast<const float4*>(kb + (int64_t)r * D + c); b = *reinterpret_cast<const float4*>(vb + (int64_t)r * D + c); }
-    *reinterpret_cast<float4*>(Ks + r * LDK + c) = a; *reinterpret_cast<float4*>(Vs + r * LDK + c) = b;
-  }
-  for (int idx = tid; idx < NH * (D / 4); idx += 256) {
-    const int hh = idx >> 5, c = (idx & 31) * 4, g = hh / RATIO, h = hh % RATIO;
-    *reinterpret_cast<float4*>(Qs + hh * D + c) =
-        *reinterpret_cast<const float4*>(q + (int64_t)(p * group + g) * q_rstride + (int64_t)(hk * RATIO + h) * D + c);
-  }
-  __syncthreads();
-  // ---- scores: warp w owns heads w, w + 8, w + 16, w + 24
-  {
-    float d[4] = {0.f, 0.f, 0.f, 0.f};
-    const float* krow = Ks + lane * LDK;
-#pragma unroll 4
-    for (int c = 0; c < D; c += 4) {
-      const float4 kv = *reinterpret_cast<const float4*>(krow + c);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int hh = warp + 8 * i;
-        if (hh < NH) {
-          const float4 qv = *reinterpret_cast<const float4*>(Qs + hh * D + c);
-          d[i] = fmaf(qv.x, kv.x, d[i]); d[i] = fmaf(qv.y, kv.y, d[i]); d[i] = fmaf(qv.z, kv.z, d[i]); d[i] = fmaf(qv.w, kv.w, d[i]);
-        }
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int hh = warp + 8 * i;
-      if (hh >= NH) continue;
-      const int qpos = ctx_len[p * group + hh / RATIO] - 1;
-      const int kj = k0 + lane;
-      const bool live = lane < kvalid && (window < 0 || qpos - kj <= window);
-      float sc = live ? d[i] : -INFINITY;
-      float mx = sc;
-#pragma unroll
-      for (int o2 = 16; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o2));
-      const float pj = live ? __expf(sc - mx) : 0.0f;
-      const float tot = warp_sum(pj);
-      Ps[hh * kPrefixTile + lane] = pj;
-      if (lane == 0) { Ms[hh] = mx; Ls[hh] = tot; }
-    }
-  }
-  __syncthreads();
-  // ---- P.V: thread = (channel pair, head group of 4): heads hg, hg + 4, ...; keys in blocks of 4 so that
-  //      one 128-bit read of P feeds 8 multiply-adds
-  {
-    const int cp = (tid & 63) * 2, hg = tid >> 6;
-    float acc[kPrefixMaxHeads / 4][2];
-#pragma unroll
-    for (int i = 0; i < kPrefixMaxHeads / 4; ++i) { acc[i][0] = 0.0f; acc[i][1] = 0.0f; }
-    for (int j = 0; j < kPrefixTile; j += 4) {      // rows >= kvalid are zero in Vs and P
-      float2 v[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const float2*>(Vs + (j + u) * LDK + cp);
-#pragma unroll
-      for (int i = 0; i < kPrefixMaxHeads / 4; ++i) {
-        const int hh = hg + 4 * i;
-        if (hh < NH) {
-          const float4 p4 = *reinterpret_cast<const float4*>(Ps + hh * kPrefixTile + j);
-          acc[i][0] = fmaf(p4.x, v[0].x, acc[i][0]); acc[i][1] = fmaf(p4.x, v[0].y, acc[i][1]);
-          acc[i][0] = fmaf(p4.y, v[1].x, acc[i][0]); acc[i][1] = fmaf(p4.y, v[1].y, acc[i][1]);
-          acc[i][0] = fmaf(p4.z, v[2].x, acc[i][0]); acc[i][1] = fmaf(p4.z, v[2].y, acc[i][1]);
-          acc[i][0] = fmaf(p4.w, v[3].x, acc[i][0]); acc[i][1] = fmaf(p4.w, v[3].y, acc[i][1]);
-        }
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < kPrefixMaxHeads / 4; ++i) {
-      const int hh = hg + 4 * i;
-      if (hh < NH) {
-        const int row = p * group + hh / RATIO, hq = hk * RATIO + hh % RATIO;
-        *reinterpret_cast<float2*>(part_acc + (((int64_t)row * Hq + hq) * nslots + split) * D + cp) = make_float2(acc[i][0], acc[i][1]);
-      }
-    }
-    if (tid < NH) {
-      const int row = p * group + tid / RATIO, hq = hk * RATIO + tid % RATIO;
-      const int64_t pi = ((int64_t)row * Hq + hq) * nslots + split;
-      part_ms[pi * 2] = Ms[tid]; part_ms[pi * 2 + 1] = Ls[tid];
-    }
-  }
-}
+constexpr int kPrefixTile = 32, kPrefixMaxHeads = 32;   // the shared-prefix pass (attention_mma.cu): keys per tile, query vectors per group and kv head
 // -1: the rule below decides; 0 / 1: the shared-prefix pass is off / on wherever it applies (process-wide policy).
 std::atomic<int> g_prefix_sharing{-1};
 void attention_decode_prefix_mode(int mode) { g_prefix_sharing.store(mode < 0 ? -1 : (mode ? 1 : 0), std::memory_order_relaxed); }
-
-constexpr size_t kPrefixSmem = sizeof(float) * (size_t)(2 * kPrefixTile * 132 + kPrefixMaxHeads * 128 + kPrefixMaxHeads * kPrefixTile);
 
 // Partial-result slots the shared-prefix pass writes: one per tile of 32 prompt positions
 // (0 when the pass does not apply: head_dim other than 128, or more than 32 query vectors per group and kv head).
 int attention_decode_prefix_splits(int rows, int group, int Hq, int Hkv, int D, int prefix_len) {
   if (group <= 1 || prefix_len <= 0 || D != 128 || group * (Hq / Hkv) > kPrefixMaxHeads || rows % group != 0) return 0;
   const int tiles = (prefix_len + kPrefixTile - 1) / kPrefixTile;
-  // Measured on d12 (128-token prompts, 512 rows): the group's rows read the prompt's keys from L2 anyway, so the pass
-  // only wins while the prompt is most of the context (35 vs 39 us per layer at 160 keys, 60 vs 57 at 256).  It is
-  // therefore used when the prompt is long (>= 512 positions) and the pass fills the machine; short prompts and small
-  // batches keep the per-row kernel.  The option "decode_prefix_sharing" (1 / 0) overrides the rule; tests exercise
-  // the pass with it.
+  // Measured on d12 (128-token prompts, groups of 8): with the pass on the tensor pipe (13.6 us for the 512-row batch) the
+  // per-row kernel only walks the generated keys: 23 vs 33 us per layer at context 133, 51 vs 58 at 256, 74 vs 81 at 384
+  // with 512 rows, 31 vs 39 at 256 rows; at 128 rows and below the extra launch costs more than it saves (25 vs 18 us).
+  // The option "decode_prefix_sharing" (1 / 0) overrides the rule; tests exercise the pass with it.
   const int forced = g_prefix_sharing.load(std::memory_order_relaxed);
   if (forced == 0) return 0;
-  if (forced < 0 && (prefix_len < 512 || (int64_t)(rows / group) * Hkv * tiles < 2 * num_sms())) return 0;
+  if (forced < 0 && (prefix_len < 64 || group < 4 || (int64_t)rows * Hkv < 3 * (int64_t)num_sms())) return 0;
   return tiles;
 }
 
@@ -1256,12 +1141,8 @@ static int decode_go(const float* q, int64_t q_rstride, const float* kcache, con
   int psplits = 0;
   psplits = attention_decode_prefix_splits(rows, group, Hq, Hkv, D, prefix_len);
   if (psplits > 0) {
-    static PerDeviceOnce configured;
-    if (configured.first()) { GN_CUDA(cudaFuncSetAttribute(attn_decode_prefix_kernel<RATIO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefixSmem)); }
-    dim3 pgrid((rows / group) * Hkv, psplits);
-    attn_decode_prefix_kernel<RATIO><<<pgrid, 256, kPrefixSmem, s>>>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, Hq, Hkv, window, group,
-                                                                     prefix_len, part_acc, part_ms, psplits + splits);
-    GN_LAUNCH_CHECK();
+    GN_TRY(attention_mma_decode_prefix(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, rows, Hq, Hkv, window, group, prefix_len, part_acc, part_ms,
+                                       psplits + splits, s));
   }
   const int nslots = psplits + splits;
   dim3 grid(rows * Hkv, splits);

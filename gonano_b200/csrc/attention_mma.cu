@@ -72,13 +72,14 @@ __device__ __forceinline__ void mma3_group(float (*c)[4], const uint32_t (&ah)[4
 
 // acc[nt] (16 x 8 tiles) += A[16 rows][128] . B[8*nt + n][128]^T.  A points at the warp's first row: a raw float32
 // tile (Alo == nullptr, split here) or a pre-split pair; Bh / Bl are the pre-split tile.
-template <int NT, bool APRE>
+// BRAW: Bh is a raw float32 tile (Bl unused) and the B fragments are split in registers, two 8-row tiles per load.
+template <int NT, bool APRE, bool BRAW = false>
 __device__ __forceinline__ void mm_rows(float (&acc)[NT][4], const float* A, const float* Alo, const float* Bh, const float* Bl, int lane) {
   const int mat = lane >> 3, r = lane & 7;
   const int a_off = ((mat & 1) * 8 + r) * LD + (mat >> 1) * 4;
   const uint32_t a_addr = smem_addr(A + a_off);
   const uint32_t al_addr = APRE ? smem_addr(Alo + a_off) : 0u;
-  const uint32_t b_addr = smem_addr((mat < 2 ? Bh : Bl) + r * LD + (mat & 1) * 4);
+  const uint32_t b_addr = BRAW ? smem_addr(Bh + ((mat >> 1) * 8 + r) * LD + (mat & 1) * 4) : smem_addr((mat < 2 ? Bh : Bl) + r * LD + (mat & 1) * 4);
 #pragma unroll 2
   for (int ks = 0; ks < HD / 8; ++ks) {
     uint32_t ah[4], al[4];
@@ -94,11 +95,21 @@ __device__ __forceinline__ void mm_rows(float (&acc)[NT][4], const float* A, con
 #pragma unroll
     for (int n0 = 0; n0 < NT; n0 += GR) {
       uint32_t bh[GR][2], bl[GR][2];
+      if (BRAW) {
 #pragma unroll
-      for (int i = 0; i < GR; ++i) {
-        uint32_t f[4];
-        ldsm4(f, b_addr + (uint32_t)(((n0 + i) * 8 * LD + ks * 8) * 4));
-        bh[i][0] = f[0]; bh[i][1] = f[1]; bl[i][0] = f[2]; bl[i][1] = f[3];
+        for (int i = 0; i < GR; i += 2) {
+          uint32_t f[4];
+          ldsm4(f, b_addr + (uint32_t)(((n0 + i) * 8 * LD + ks * 8) * 4));
+          split(__uint_as_float(f[0]), bh[i][0], bl[i][0]); split(__uint_as_float(f[1]), bh[i][1], bl[i][1]);
+          split(__uint_as_float(f[2]), bh[i + 1][0], bl[i + 1][0]); split(__uint_as_float(f[3]), bh[i + 1][1], bl[i + 1][1]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < GR; ++i) {
+          uint32_t f[4];
+          ldsm4(f, b_addr + (uint32_t)(((n0 + i) * 8 * LD + ks * 8) * 4));
+          bh[i][0] = f[0]; bh[i][1] = f[1]; bl[i][0] = f[2]; bl[i][1] = f[3];
+        }
       }
       mma3_group(&acc[n0], ah, al, bh, bl);
     }
@@ -107,7 +118,7 @@ __device__ __forceinline__ void mm_rows(float (&acc)[NT][4], const float* A, con
 
 // acc[nt] (16 x 8 tiles over the 128 channels) += P[16][8*NK] . B[8*NK rows][128], where P is held
 // as NK accumulator fragments (columns 2t, 2t+1 of each 8-wide tile) and B (pre-split) is row-major.
-template <int NK>
+template <int NK, bool BRAW = false>
 __device__ __forceinline__ void mm_perm(float (&acc)[HD / 8][4], const float (&p)[NK][4], const float* Bh, const float* Bl, int g, int t) {
 #pragma unroll
   for (int ks = 0; ks < NK; ++ks) {
@@ -121,8 +132,12 @@ __device__ __forceinline__ void mm_perm(float (&acc)[HD / 8][4], const float (&p
       uint32_t bh[GR][2], bl[GR][2];
 #pragma unroll
       for (int i = 0; i < GR; ++i) {
-        bh[i][0] = hrow[(n0 + i) * 8]; bh[i][1] = hrow[LD + (n0 + i) * 8];
-        bl[i][0] = lrow[(n0 + i) * 8]; bl[i][1] = lrow[LD + (n0 + i) * 8];
+        if (BRAW) {
+          split(__uint_as_float(hrow[(n0 + i) * 8]), bh[i][0], bl[i][0]); split(__uint_as_float(hrow[LD + (n0 + i) * 8]), bh[i][1], bl[i][1]);
+        } else {
+          bh[i][0] = hrow[(n0 + i) * 8]; bh[i][1] = hrow[LD + (n0 + i) * 8];
+          bl[i][0] = lrow[(n0 + i) * 8]; bl[i][1] = lrow[LD + (n0 + i) * 8];
+        }
       }
       mma3_group(&acc[n0], ah, al, bh, bl);
     }
@@ -449,6 +464,106 @@ __global__ void __launch_bounds__(NTH, 1) attn_mma_dq_kernel(AttnShape sh, const
 constexpr size_t kSmemAll = sizeof(float) * (size_t)((2 * BM + 4 * BT) * LD);   // the three kernels use the same amount
 constexpr size_t kSmemFwd = kSmemAll, kSmemDkv = kSmemAll, kSmemDq = kSmemAll;
 
+// ------------------------------------------------------------------ decode: the prompt shared by a group
+// The G rows of a group hold identical K/V for the prompt positions (the prefill was replicated,
+// model/kvcache.go:383-448), so their G x RATIO query vectors of one kv head are treated as the rows of one small
+// attention problem against the first row's copy: CTA = (prompt, kv head, tile of 32 keys), two warps of 16 query rows
+// each (rows >= G x RATIO are zero padding).  The tile yields one partial-result slot per (row, head): (max, sum,
+// unnormalised output), merged with the per-row kernel's slots by its combine step.  The same arithmetic as the forward
+// kernel above (3xTF32 products on mma.sync, softmax on the accumulator fragments); Q, K and V reach shared memory as
+// raw float32 through cp.async (no registers in between, every request of the CTA in flight at once) and are split
+// into their tf32 parts as fragments are formed.
+constexpr int PFX_THREADS = 64;
+constexpr size_t kSmemPrefix = sizeof(float) * (size_t)(32 * LD + 2 * BT * LD);
+__device__ __forceinline__ void cp_async16(float* dst, const float* src, bool valid) {
+  const uint32_t d = smem_addr(dst);
+  const int bytes = valid ? 16 : 0;   // 0: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__global__ void __launch_bounds__(PFX_THREADS, 4) attn_decode_prefix_mma_kernel(const float* __restrict__ q, int64_t q_rstride, const float* __restrict__ kcache,
+                                                                              const float* __restrict__ vcache, int64_t row_stride, int64_t head_stride,
+                                                                              const int32_t* __restrict__ ctx_len, int Hq, int Hkv, int ratio, int window,
+                                                                              int group, int prefix_len, float* __restrict__ part_acc,
+                                                                              float* __restrict__ part_ms, int nslots) {
+  extern __shared__ __align__(16) float smem[];
+  float* Qs = smem; float* Ks = Qs + 32 * LD; float* Vs = Ks + BT * LD;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int p = blockIdx.x / Hkv, hk = blockIdx.x % Hkv, tile = blockIdx.y;
+  const int NH = group * ratio;
+  const int k0 = tile * BT, kvalid = min(BT, prefix_len - k0);
+  const float* kb = kcache + (int64_t)p * group * row_stride + (int64_t)hk * head_stride + (int64_t)k0 * HD;
+  const float* vb = vcache + (int64_t)p * group * row_stride + (int64_t)hk * head_stride + (int64_t)k0 * HD;
+  // the group's query vectors: row hh = (row of the group hh / ratio, head hh % ratio of this kv head)
+  for (int idx = threadIdx.x; idx < 32 * (HD / 4); idx += PFX_THREADS) {
+    const int hh = idx / (HD / 4), c = (idx % (HD / 4)) * 4;
+    const bool ok = hh < NH;
+    cp_async16(Qs + hh * LD + c, ok ? q + (int64_t)(p * group + hh / ratio) * q_rstride + (int64_t)(hk * ratio + hh % ratio) * HD + c : q, ok);
+  }
+  for (int idx = threadIdx.x; idx < BT * (HD / 4); idx += PFX_THREADS) {
+    const int r = idx / (HD / 4), c = (idx % (HD / 4)) * 4;
+    const bool ok = r < kvalid;
+    cp_async16(Ks + r * LD + c, ok ? kb + (int64_t)r * HD + c : kb, ok);
+    cp_async16(Vs + r * LD + c, ok ? vb + (int64_t)r * HD + c : vb, ok);
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  int qpos2[2]; bool live[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int hh = warp * 16 + g + 8 * h;
+    live[h] = hh < NH;
+    qpos2[h] = live[h] ? ctx_len[p * group + hh / ratio] - 1 : 0;
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
+  float s[BT / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < BT / 8; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f; }
+  mm_rows<BT / 8, false, true>(s, Qs + warp * 16 * LD, nullptr, Ks, Ks, lane);
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int nt = 0; nt < BT / 8; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int h = e >> 1, kj = k0 + nt * 8 + 2 * t + (e & 1);
+      if (kj >= prefix_len || (window >= 0 && qpos2[h] - kj > window)) s[nt][e] = -INFINITY;
+      mx[h] = fmaxf(mx[h], s[nt][e]);
+    }
+  float rs[2] = {0.0f, 0.0f};
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+  }
+#pragma unroll
+  for (int nt = 0; nt < BT / 8; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int h = e >> 1;
+      const float pj = (s[nt][e] == -INFINITY) ? 0.0f : __expf(s[nt][e] - mx[h]);
+      s[nt][e] = pj; rs[h] += pj;
+    }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 1);
+    rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 2);
+  }
+  float o[HD / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < HD / 8; ++nt) { o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f; }
+  mm_perm<BT / 8, true>(o, s, Vs, Vs, g, t);
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (!live[h]) continue;
+    const int hh = warp * 16 + g + 8 * h;
+    const int row = p * group + hh / ratio, hq = hk * ratio + hh % ratio;
+    const int64_t pi = ((int64_t)row * Hq + hq) * nslots + tile;
+    float* og = part_acc + pi * HD;
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt) *reinterpret_cast<float2*>(og + nt * 8 + 2 * t) = make_float2(o[nt][2 * h], o[nt][2 * h + 1]);
+    if (t == 0) { part_ms[pi * 2] = mx[h]; part_ms[pi * 2 + 1] = rs[h]; }
+  }
+}
+
 }  // namespace
 
 // Row access is by float4 / float2: 16-byte aligned rows, head_dim 128.
@@ -463,6 +578,19 @@ int attention_mma_forward(const AttnShape& sh, const float* q, const float* k, c
   if (configured.first()) { GN_CUDA(cudaFuncSetAttribute(attn_mma_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemFwd)); }
   dim3 grid(ceil_div(sh.Tq, BM), sh.B * sh.Hq);
   attn_mma_fwd_kernel<<<grid, NTH, kSmemFwd, s>>>(sh, q, k, v, out, lse);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+int attention_mma_decode_prefix(const float* q, int64_t q_rstride, const float* kcache, const float* vcache, int64_t row_stride, int64_t head_stride,
+                                const int32_t* ctx_len, int rows, int Hq, int Hkv, int window, int group, int prefix_len, float* part_acc, float* part_ms,
+                                int nslots, cudaStream_t s) {
+  static PerDeviceOnce configured;
+  if (configured.first()) { GN_CUDA(cudaFuncSetAttribute(attn_decode_prefix_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemPrefix)); }
+  const int tiles = (prefix_len + BT - 1) / BT;
+  dim3 grid((rows / group) * Hkv, tiles);
+  attn_decode_prefix_mma_kernel<<<grid, PFX_THREADS, kSmemPrefix, s>>>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, Hq, Hkv, Hq / Hkv, window,
+                                                                       group, prefix_len, part_acc, part_ms, nslots);
   GN_LAUNCH_CHECK();
   return GN_OK;
 }

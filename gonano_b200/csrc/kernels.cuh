@@ -68,6 +68,11 @@ int compressed_attention_launch(const float* q, const float* kc, const float* vc
                                 cudaStream_t s);
 int attention_merge_launch(const float* oa, const float* la, const float* ob, const float* lb, int64_t rows, int D, float* out, float* lse, cudaStream_t s);
 int select_blocks_launch(const float* scores, int tokens, int blocks, int offset, int ratio, int topk, int32_t* selection, int32_t* counts, cudaStream_t s);
+// decode attention over the prompt shared by the rows of a group, head_dim 128, on mma.sync (attention_mma.cu): one
+// partial-result slot per 32-key tile and (row, head), as attn_decode_prefix_kernel writes them
+int attention_mma_decode_prefix(const float* q, int64_t q_rstride, const float* kcache, const float* vcache, int64_t row_stride, int64_t head_stride,
+                                const int32_t* ctx_len, int rows, int Hq, int Hkv, int window, int group, int prefix_len, float* part_acc, float* part_ms,
+                                int nslots, cudaStream_t s);
 // head_dim 128 forward on tcgen05 (attention_tcgen05.cu); preferred over the mma.sync kernel when sh.tensor is set.
 bool attention_tc_ok(const AttnShape& sh, const void* p0, const void* p1, const void* p2, const void* p3);
 int attention_tc_forward(const AttnShape& sh, const float* q, const float* k, const float* v, float* out, float* lse, cudaStream_t s);
