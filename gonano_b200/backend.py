@@ -124,6 +124,14 @@ class CudaBackend:
         check(self.lib.gn_compressed_attention_forward(ptr(q), ptr(kc), ptr(vc), B, Hq, Hkv, T, D, blocks, ratio, ptr(out), ptr(lse)))
         return out, lse
 
+    def compressed_attention_sparse_forward(self, q, kc, vc, selection, counts):
+        """compressedAttentionForwardSparse (model/compress_attention.go:321-374): selection [B*Hkv, T, topk], counts [B*Hkv, T]."""
+        q, kc, vc = _f32(q), _f32(kc), _f32(vc); selection, counts = _i32(selection), _i32(counts)
+        B, Hq, T, D = q.shape; Hkv, blocks = kc.shape[1], kc.shape[2]; topk = selection.shape[-1]
+        out = np.zeros_like(q); lse = np.zeros((B, Hq, T), np.float32)
+        check(self.lib.gn_compressed_attention_sparse_forward(ptr(q), ptr(kc), ptr(vc), ptr(selection), ptr(counts), B, Hq, Hkv, T, D, blocks, topk, ptr(out), ptr(lse)))
+        return out, lse
+
     def attention_merge(self, oa, la, ob, lb):
         """mergeAttentionBranches (model/compress_attention.go:440-466)."""
         oa, la, ob, lb = _f32(oa), _f32(la), _f32(ob), _f32(lb)

@@ -333,7 +333,21 @@ int gn_compressed_attention_forward(const float* query, const float* key_c, cons
   const float* dq = st.in(query, nq); const float* dk = st.in(key_c, nk); const float* dv = st.in(value_c, nk);
   float* dout = st.out(out, nq); float* dl = lse ? st.out(lse, (size_t)batch * n_head * seq) : nullptr;
   if (st.status != GN_OK) return st.status;
-  GN_TRY(compressed_attention_launch(dq, dk, dv, batch, n_head, n_kv_head, seq, head_dim, blocks, ratio, dout, dl, s));
+  GN_TRY(compressed_attention_launch(dq, dk, dv, batch, n_head, n_kv_head, seq, head_dim, blocks, ratio, dout, dl, nullptr, nullptr, 0, s));
+  GN_END();
+}
+// compressedAttentionForwardSparse (model/compress_attention.go:321-374), no segment mask
+int gn_compressed_attention_sparse_forward(const float* query, const float* key_c, const float* value_c, const int32_t* selection, const int32_t* counts, int batch,
+                                           int n_head, int n_kv_head, int seq, int head_dim, int blocks, int topk, float* out, float* lse) {
+  if (batch <= 0 || seq <= 0) return GN_OK;
+  GN_REQUIRE(query && key_c && value_c && selection && counts && out && blocks >= 0 && topk >= 1, "compressed_attention_sparse_forward: bad argument");
+  GN_BEGIN();
+  const size_t nq = (size_t)batch * n_head * seq * head_dim, nk = (size_t)batch * n_kv_head * blocks * head_dim, nt = (size_t)batch * n_kv_head * seq;
+  const float* dq = st.in(query, nq); const float* dk = st.in(key_c, nk); const float* dv = st.in(value_c, nk);
+  const int32_t* ds = st.in(selection, nt * topk); const int32_t* dc = st.in(counts, nt);
+  float* dout = st.out(out, nq); float* dl = lse ? st.out(lse, (size_t)batch * n_head * seq) : nullptr;
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(compressed_attention_launch(dq, dk, dv, batch, n_head, n_kv_head, seq, head_dim, blocks, 1, dout, dl, ds, dc, topk, s));
   GN_END();
 }
 // mergeAttentionBranches (model/compress_attention.go:440-466)

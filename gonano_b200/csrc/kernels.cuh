@@ -64,8 +64,9 @@ int attention_mma_forward(const AttnShape& sh, const float* q, const float* k, c
 // compressed attention building blocks (compress.cu)
 int compressor_pool_launch(const float* logits, const float* bias, const float* value, int B, int T, int C, int ratio, float* compressed, float* probabilities,
                            cudaStream_t s);
+// selection == nullptr: every block before the query's own; else the token's selected blocks ([B * Hkv, T, topk] with counts [B * Hkv, T])
 int compressed_attention_launch(const float* q, const float* kc, const float* vc, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* out, float* lse,
-                                cudaStream_t s);
+                                const int32_t* selection, const int32_t* counts, int topk, cudaStream_t s);
 int attention_merge_launch(const float* oa, const float* la, const float* ob, const float* lb, int64_t rows, int D, float* out, float* lse, cudaStream_t s);
 int select_blocks_launch(const float* scores, int tokens, int blocks, int offset, int ratio, int topk, int32_t* selection, int32_t* counts, cudaStream_t s);
 // decode attention over the prompt shared by the rows of a group, head_dim 128, on mma.sync (attention_mma.cu): one

@@ -111,6 +111,10 @@ int gn_compressor_forward(const float* hidden, const float* value, const float* 
                           int channels, int ratio, float* compressed, float* probabilities);
 int gn_compressed_attention_forward(const float* query, const float* key_c, const float* value_c, int batch, int n_head, int n_kv_head, int seq,
                                     int head_dim, int blocks, int ratio, float* out, float* lse);
+/* compressedAttentionForwardSparse (model/compress_attention.go:321-374): selection [batch * n_kv_head, seq, topk] block
+ * indices, counts [batch * n_kv_head, seq]; block indices must lie in [0, blocks). */
+int gn_compressed_attention_sparse_forward(const float* query, const float* key_c, const float* value_c, const int32_t* selection, const int32_t* counts,
+                                           int batch, int n_head, int n_kv_head, int seq, int head_dim, int blocks, int topk, float* out, float* lse);
 int gn_attention_merge(const float* out_a, const float* lse_a, const float* out_b, const float* lse_b, int64_t rows, int head_dim, float* out,
                        float* lse);
 int gn_select_blocks(const float* scores, int tokens, int blocks, int position_offset, int ratio, int topk, int32_t* selection, int32_t* counts);

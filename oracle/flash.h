@@ -4,6 +4,7 @@
 //   channel compressor forward        model/compress.go:93-177
 //   compression of K and V per head    model/compress_attention.go:562-621 (compressForward, no segment mask)
 //   attention over preceding blocks    model/compress_attention.go:624-673 (compressedAttentionForward)
+//   attention over selected blocks     model/compress_attention.go:321-374 (compressedAttentionForwardSparse)
 //   local sliding-window branch        model/compress_attention.go:487-536 (attentionForwardWindowed = the ordinary
 //                                      attention with a window, kernels/scalar/attention.go:16-205)
 //   merge of two softmax branches      model/compress_attention.go:440-466 (mergeAttentionBranches)
@@ -86,6 +87,30 @@ inline void compressed_attention_forward(const Backend& bk, const float* q, cons
         }
         // position offset = blk: every compressed key index is below every query position (no causal cut inside)
         bk.attention_forward(q + (qi * T + start) * D, kc + kbase, vc + kbase, end - start, blk, D, blk, -1, nullptr, 0, o, l);
+      }
+    }
+}
+
+// The same over selected blocks only (model/compress_attention.go:321-374, no segment mask): selection
+// [B * Hkv, T, topk] block indices and counts [B * Hkv, T]; a token without a selected block yields zeros, lse = -inf.
+inline void compressed_attention_sparse_forward(const Backend& bk, const float* q, const float* kc, const float* vc, const int32_t* selection,
+                                                const int32_t* counts, int B, int Hq, int Hkv, int T, int D, int blocks, int topk, float* out, float* lse) {
+  const int hr = Hq / Hkv;
+  std::vector<float> ks((size_t)std::max(topk, 1) * D), vs((size_t)std::max(topk, 1) * D);
+  for (int b = 0; b < B; ++b)
+    for (int h = 0; h < Hq; ++h) {
+      const size_t qi = (size_t)b * Hq + h, kvh = (size_t)b * Hkv + h / hr;
+      const size_t kbase = kvh * blocks * D;
+      for (int t = 0; t < T; ++t) {
+        float* o = out + (qi * T + t) * D;
+        const int n = counts[kvh * T + t];
+        if (n <= 0) { std::fill(o, o + D, 0.0f); if (lse) lse[qi * T + t] = -INFINITY; continue; }
+        const int32_t* sel = selection + (kvh * T + t) * topk;
+        for (int i = 0; i < n; ++i) {
+          std::copy(kc + kbase + (size_t)sel[i] * D, kc + kbase + (size_t)(sel[i] + 1) * D, ks.begin() + (size_t)i * D);
+          std::copy(vc + kbase + (size_t)sel[i] * D, vc + kbase + (size_t)(sel[i] + 1) * D, vs.begin() + (size_t)i * D);
+        }
+        bk.attention_forward(q + (qi * T + t) * D, ks.data(), vs.data(), 1, n, D, n, -1, nullptr, 0, o, lse ? lse + qi * T + t : nullptr);
       }
     }
 }

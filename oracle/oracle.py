@@ -576,6 +576,15 @@ def compressed_attention_forward(q, kc, vc, ratio, mode=0):
     return out, lse
 
 
+def compressed_attention_sparse_forward(q, kc, vc, selection, counts, mode=0):
+    """compressedAttentionForwardSparse (model/compress_attention.go:321-374): selection [B*Hkv, T, topk], counts [B*Hkv, T]."""
+    q, kc, vc = f32(q), f32(kc), f32(vc); selection, counts = i32(selection), i32(counts)
+    B, Hq, T, D = q.shape; Hkv, blocks = kc.shape[1], kc.shape[2]; topk = selection.shape[-1]
+    out = np.zeros_like(q); lse = np.zeros((B, Hq, T), np.float32)
+    lib().or_compressed_attention_sparse_forward(mode, _f(q), _f(kc), _f(vc), _i(selection), _i(counts), B, Hq, Hkv, T, D, blocks, topk, _f(out), _f(lse))
+    return out, lse
+
+
 def merge_branches(oa, la, ob, lb):
     """mergeAttentionBranches (model/compress_attention.go:440-466)."""
     oa, la, ob, lb = f32(oa), f32(la), f32(ob), f32(lb)

@@ -102,3 +102,31 @@ def test_heavily_compressed_layer_forward(oracle, bk):
     want, want_l = layer(oracle.compressor_forward, oracle.compressed_attention_forward, oracle.merge_branches, ref.attention_forward)
     got, got_l = layer(bk.compressor_forward, bk.compressed_attention_forward, bk.attention_merge, bk.attention_forward)
     close(got, want, 1e-4, 1e-5); close(got_l, want_l, 1e-4, 1e-5)
+
+
+def test_compressed_attention_sparse_forward(oracle, bk):
+    """Attention over the selected blocks only (model/compress_attention.go:321-374), with the selection the block
+    selector made from quantised scores (ties) for every (sequence, kv head)."""
+    rng = np.random.default_rng(21)
+    B, Hq, Hkv, T, D, ratio, topk = 2, 4, 2, 37, 64, 4, 3
+    blocks = (T + ratio - 1) // ratio
+    q = (rng.standard_normal((B, Hq, T, D)) * 0.4).astype(np.float32)
+    kc = (rng.standard_normal((B, Hkv, blocks, D)) * 0.4).astype(np.float32); vc = rng.standard_normal((B, Hkv, blocks, D)).astype(np.float32)
+    sel = np.zeros((B * Hkv, T, topk), np.int32); cnt = np.zeros((B * Hkv, T), np.int32)
+    for i in range(B * Hkv):
+        scores = np.round(rng.standard_normal((T, blocks)) * 3).astype(np.float32)
+        sel[i], cnt[i] = bk.select_blocks(scores, 0, ratio, topk)
+        want_s, want_c = oracle.select_blocks(scores, 0, ratio, topk)
+        assert np.array_equal(sel[i], want_s) and np.array_equal(cnt[i], want_c)
+    want, want_l = oracle.compressed_attention_sparse_forward(q, kc, vc, np.maximum(sel, 0), cnt)
+    got, got_l = bk.compressed_attention_sparse_forward(q, kc, vc, np.maximum(sel, 0), cnt)
+    close(got, want, 1e-4, 1e-5); close(got_l, want_l, 1e-4, 1e-5)
+    assert np.all(got[:, :, :ratio] == 0) and np.all(np.isneginf(got_l[:, :, :ratio]))       # no block precedes block 0
+    # with every allowed block selected the sparse form equals the dense one (model/indexer_test.go:327-349, the
+    # unbounded selection)
+    full = np.zeros((B * Hkv, T, blocks), np.int32); fc = np.zeros((B * Hkv, T), np.int32)
+    for t in range(T):
+        fc[:, t] = min(t // ratio, blocks); full[:, t, :fc[0, t]] = np.arange(fc[0, t])
+    dense, dense_l = bk.compressed_attention_forward(q, kc, vc, ratio)
+    sparse, sparse_l = bk.compressed_attention_sparse_forward(q, kc, vc, full, fc)
+    close(sparse, dense, 1e-6, 1e-7); close(sparse_l, dense_l, 1e-6, 1e-7)
