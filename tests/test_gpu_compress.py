@@ -130,3 +130,49 @@ def test_compressed_attention_sparse_forward(oracle, bk):
     dense, dense_l = bk.compressed_attention_forward(q, kc, vc, ratio)
     sparse, sparse_l = bk.compressed_attention_sparse_forward(q, kc, vc, full, fc)
     close(sparse, dense, 1e-6, 1e-7); close(sparse_l, dense_l, 1e-6, 1e-7)
+
+
+def test_sparse_compressed_layer_forward(oracle, bk):
+    """One sparse compressed attention layer, inference forward, composed from the entry points the way
+    model/compress_attention.go does it: K and V compressed per kv head (compressForward), index scores
+    I[t, s] = sum_h w_h relu(q_t,h . k_s,h) from the hidden state and the compressed keys (SparseIndexer.Scores,
+    model/indexer.go:58-99: two Linear forwards + Backend.IndexerScores per sequence), the top-k preceding blocks per
+    token (SelectBlocks), attention over them, the sliding-window branch over the raw keys, merged by log-sum-exp.
+    Selection must agree exactly; the outputs within float32 rounding."""
+    rng = np.random.default_rng(31)
+    B, Hq, Hkv, T, D, d, ratio, window, topk, ih, idim = 2, 4, 2, 53, 64, 96, 4, 5, 3, 2, 16
+    blocks = (T + ratio - 1) // ratio
+    x = rng.standard_normal((B, T, d)).astype(np.float32)
+    q = (rng.standard_normal((B, Hq, T, D)) * 0.4).astype(np.float32)
+    k = (rng.standard_normal((B, Hkv, T, D)) * 0.4).astype(np.float32); v = rng.standard_normal((B, Hkv, T, D)).astype(np.float32)
+    wc = (rng.standard_normal((D, d)) * 0.2).astype(np.float32); bias = (rng.standard_normal((ratio, D)) * 0.3).astype(np.float32)
+    wq = (rng.standard_normal((ih * idim, d)) * 0.2).astype(np.float32); wk = (rng.standard_normal((ih * idim, D)) * 0.3).astype(np.float32)
+    hw = np.array([0.7, 1.3], np.float32)
+    ref = oracle.Backend(0)
+
+    def layer(be, comp, sparse, merge, select):
+        kc = np.zeros((B, Hkv, blocks, D), np.float32); vc = np.zeros_like(kc)
+        sel = np.zeros((B * Hkv, T, topk), np.int32); cnt = np.zeros((B * Hkv, T), np.int32)
+        for b in range(B):
+            iq = be.matmul_transposed(x[b], wq, T, ih * idim, d)                       # indexer queries [T, heads * dim]
+            for h in range(Hkv):
+                kc[b, h] = comp(x[b:b + 1], k[b, h][None], wc, bias, ratio)[0][0]
+                vc[b, h] = comp(x[b:b + 1], v[b, h][None], wc, bias, ratio)[0][0]
+                ik = be.matmul_transposed(kc[b, h], wk, blocks, ih * idim, D)          # indexer keys [blocks, heads * dim]
+                scores = np.asarray(be.indexer_scores(iq, ik, hw, T, blocks, ih, idim)).reshape(T, blocks)
+                sel[b * Hkv + h], cnt[b * Hkv + h] = select(scores, 0, ratio, topk)
+        og, lg = sparse(q, kc, vc, np.maximum(sel, 0), cnt)
+        ol = np.zeros_like(q); ll = np.zeros((B, Hq, T), np.float32)
+        for b in range(B):
+            for h in range(Hq):
+                o, l = be.attention_forward(q[b, h], k[b, h // (Hq // Hkv)], v[b, h // (Hq // Hkv)], T, T, D, 0, window)
+                ol[b, h] = np.asarray(o).reshape(T, D); ll[b, h] = np.asarray(l).reshape(T)
+        out, lse = merge(og.reshape(-1, D), lg.reshape(-1), ol.reshape(-1, D), ll.reshape(-1))
+        return out, lse, sel, cnt
+
+    want, want_l, want_sel, want_cnt = layer(ref, oracle.compressor_forward, oracle.compressed_attention_sparse_forward, oracle.merge_branches, oracle.select_blocks)
+    got, got_l, got_sel, got_cnt = layer(bk, bk.compressor_forward, bk.compressed_attention_sparse_forward, bk.attention_merge, bk.select_blocks)
+    assert np.array_equal(got_cnt, want_cnt)
+    same = np.all(got_sel == want_sel, axis=(1, 2))
+    assert same.all(), "block selection differs"       # scores agree to rounding; a flipped near-tie would show here
+    close(got, want, 1e-4, 1e-5); close(got_l, want_l, 1e-4, 1e-5)
