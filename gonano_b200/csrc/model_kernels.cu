@@ -341,12 +341,84 @@ __global__ void __launch_bounds__(WPB * 32) qkv_post_kernel(QkvPost p) {
     }
   }
 }
+// head_dim 128 form: a lane holds four consecutive channels (one 16-byte access per tensor), the rotary partner of a
+// channel sits half / 4 lanes away, nothing passes through shared memory.  Same arithmetic as the kernel above except
+// for the order in which the 128 squares of the norm are added.
+__global__ void __launch_bounds__(WPB * 32) qkv_post_vec_kernel(QkvPost p) {
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slots = p.Hq + 2 * p.Hkv;
+  const int64_t idx = (int64_t)blockIdx.x * WPB + warp;
+  const int64_t rows = (int64_t)p.B * p.T;
+  if (idx >= rows * slots) return;
+  const int64_t r = idx / slots; const int slot = (int)(idx % slots);
+  const int b = (int)(r / p.T), t = (int)(r % p.T);
+  constexpr int D = 128;
+  const int W = slots * D, c = lane * 4;
+  float* x = p.qkv + r * W + (int64_t)slot * D;
+  const int crow = b * p.cache_row_mul;
+  const int pos = (p.pos ? p.pos[crow] : 0) + t;
+  float4 v = p.part.on() ? p.part.at4(r, (int64_t)slot * D + c) : *reinterpret_cast<const float4*>(x + c);
+  if (slot < p.Hq + p.Hkv) {
+    // ---- rotary on the trailing R channels, pairs (first half, second half)  (model/rotary.go:43-75)
+    const int half = p.R / 2, off = D - p.R, hl = half / 4;
+    float4 o4;
+    o4.x = __shfl_xor_sync(0xffffffffu, v.x, hl); o4.y = __shfl_xor_sync(0xffffffffu, v.y, hl);
+    o4.z = __shfl_xor_sync(0xffffffffu, v.z, hl); o4.w = __shfl_xor_sync(0xffffffffu, v.w, hl);
+    if (c >= off) {
+      const bool first = c < off + half;
+      const int j = first ? c - off : c - off - half;
+      const float4 cw = *reinterpret_cast<const float4*>(p.cosv + (int64_t)pos * half + j);
+      const float4 sw = *reinterpret_cast<const float4*>(p.sinv + (int64_t)pos * half + j);
+      if (first) {   // a = this channel, b = its partner in the second half
+        v.x = __fadd_rn(__fmul_rn(v.x, cw.x), __fmul_rn(o4.x, sw.x)); v.y = __fadd_rn(__fmul_rn(v.y, cw.y), __fmul_rn(o4.y, sw.y));
+        v.z = __fadd_rn(__fmul_rn(v.z, cw.z), __fmul_rn(o4.z, sw.z)); v.w = __fadd_rn(__fmul_rn(v.w, cw.w), __fmul_rn(o4.w, sw.w));
+      } else {       // a = the partner in the first half, b = this channel
+        v.x = __fadd_rn(__fmul_rn(-o4.x, sw.x), __fmul_rn(v.x, cw.x)); v.y = __fadd_rn(__fmul_rn(-o4.y, sw.y), __fmul_rn(v.y, cw.y));
+        v.z = __fadd_rn(__fmul_rn(-o4.z, sw.z), __fmul_rn(v.z, cw.z)); v.w = __fadd_rn(__fmul_rn(-o4.w, sw.w), __fmul_rn(v.w, cw.w));
+      }
+    }
+    if (p.qk_rot) *reinterpret_cast<float4*>(p.qk_rot + r * (int64_t)((p.Hq + p.Hkv) * D) + (int64_t)slot * D + c) = v;
+    // ---- QK norm and the 1.2 scale (model/attention.go:255-256)
+    float ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
+    ss = warp_sum(ss);
+    const float inv = row_inv_rms(ss, D);
+    const float4 y = make_float4((v.x * inv) * kQKScale, (v.y * inv) * kQKScale, (v.z * inv) * kQKScale, (v.w * inv) * kQKScale);
+    *reinterpret_cast<float4*>(x + c) = y;
+    if (slot >= p.Hq && p.kcache) {
+      const int hk = slot - p.Hq;
+      *reinterpret_cast<float4*>(p.kcache + (((int64_t)crow * p.Hkv + hk) * p.max_seq + pos) * D + c) = y;
+    }
+  } else {
+    // ---- value (+ gated value embedding, model/attention.go:245-250,392-405)
+    const int hk = slot - p.Hq - p.Hkv;
+    if (p.ve_table) {
+      const float* h = p.H + r * p.d;
+      float pre = (lane < kVeGateChannels) ? h[lane] * p.ve_gate[hk * kVeGateChannels + lane] : 0.0f;
+      pre = warp_sum(pre);
+      const float sg = sigmoid_exact(pre);
+      if (p.ve_sig && lane == 0) p.ve_sig[r * p.Hkv + hk] = sg;
+      const float gate = sg * kVeGateScale;
+      const float4 ve = *reinterpret_cast<const float4*>(p.ve_table + (int64_t)p.ids[r] * (p.Hkv * D) + (int64_t)hk * D + c);
+      v.x += gate * ve.x; v.y += gate * ve.y; v.z += gate * ve.z; v.w += gate * ve.w;
+    }
+    *reinterpret_cast<float4*>(x + c) = v;
+    if (p.vcache) *reinterpret_cast<float4*>(p.vcache + (((int64_t)crow * p.Hkv + hk) * p.max_seq + pos) * D + c) = v;
+  }
+}
+
 int qkv_post_launch(const QkvPost& p, cudaStream_t s) {
   int64_t n = (int64_t)p.B * p.T * (p.Hq + 2 * p.Hkv);
   if (n <= 0) return GN_OK;
   GN_REQUIRE(p.D <= 128 && p.R <= p.D && p.R % 2 == 0 && p.R / 2 <= 64, "qkv_post: head_dim %d / rotary %d unsupported", p.D, p.R);
   GN_REQUIRE(!p.part.on() || p.D % 4 == 0, "qkv_post: unreduced input needs head_dim %% 4 == 0 (got %d)", p.D);
-  GN_CUDA(launch_pdl(qkv_post_kernel, dim3(ceil_div(n, WPB)), dim3(WPB * 32), 0, s, p));
+  const int half = p.R / 2;
+  auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  const bool vec = p.D == 128 && half >= 4 && half % 4 == 0 && ((half / 4) & (half / 4 - 1)) == 0 && (128 - p.R) % 4 == 0 && al16(p.qkv) && al16(p.cosv) && al16(p.sinv) &&
+                   al16(p.qk_rot) && al16(p.kcache) && al16(p.vcache) && al16(p.ve_table);
+  if (vec) { GN_CUDA(launch_pdl(qkv_post_vec_kernel, dim3(ceil_div(n, WPB)), dim3(WPB * 32), 0, s, p)); }
+  else GN_CUDA(launch_pdl(qkv_post_kernel, dim3(ceil_div(n, WPB)), dim3(WPB * 32), 0, s, p));
   GN_LAUNCH_CHECK();
   return GN_OK;
 }
