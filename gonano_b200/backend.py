@@ -116,6 +116,19 @@ class CudaBackend:
         check(self.lib.gn_compressor_forward(ptr(hidden), ptr(value), ptr(weight), ptr(bias), B, T, d, ch, ratio, ptr(out), ptr(prob)))
         return out, prob
 
+    def compressor_backward(self, hidden, value, weight, bias, ratio, grad_compressed, grad_weight=None, grad_bias=None):
+        """ChannelCompressor.Backward (model/compress.go:182-237): returns grad_hidden, grad_value, grad_weight, grad_bias
+        (the last two accumulate into the arrays given, zeros otherwise)."""
+        hidden, value, weight, bias, grad_compressed = _f32(hidden), _f32(value), _f32(weight), _f32(bias), _f32(grad_compressed)
+        B, T, d = hidden.shape; ch = value.shape[2]
+        comp, prob = self.compressor_forward(hidden, value, weight, bias, ratio)
+        gh = np.zeros_like(hidden); gv = np.zeros_like(value)
+        gw = np.zeros_like(weight) if grad_weight is None else _f32(grad_weight).copy()
+        gb = np.zeros_like(bias) if grad_bias is None else _f32(grad_bias).copy()
+        check(self.lib.gn_compressor_backward(ptr(hidden), ptr(value), ptr(weight), ptr(prob), ptr(comp), ptr(grad_compressed), B, T, d, ch, ratio,
+                                              ptr(gh), ptr(gv), ptr(gw), ptr(gb)))
+        return gh, gv, gw, gb
+
     def compressed_attention_forward(self, q, kc, vc, ratio):
         """compressedAttentionForward (model/compress_attention.go:624-673): q [B,Hq,T,D], kc / vc [B,Hkv,blocks,D]."""
         q, kc, vc = _f32(q), _f32(kc), _f32(vc)

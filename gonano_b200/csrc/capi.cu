@@ -323,6 +323,34 @@ int gn_compressor_forward(const float* hidden, const float* value, const float* 
   GN_TRY(st.finish());
   return gemm_check_error(s);
 }
+// ChannelCompressor.Backward (model/compress.go:182-237), no segment mask: grad_hidden and grad_value are overwritten,
+// grad_weight and grad_bias accumulated (Tensor.AddGrad)
+int gn_compressor_backward(const float* hidden, const float* value, const float* logit_weight, const float* probabilities, const float* compressed,
+                           const float* grad_compressed, int batch, int seq, int embed, int channels, int ratio, float* grad_hidden, float* grad_value,
+                           float* grad_weight, float* grad_bias) {
+  if (batch <= 0 || seq <= 0 || channels <= 0) return GN_OK;
+  GN_REQUIRE(hidden && value && logit_weight && probabilities && compressed && grad_compressed && grad_hidden && grad_value && grad_weight && grad_bias &&
+             ratio >= 1 && embed > 0, "compressor_backward: bad argument");
+  const int blocks = (seq + ratio - 1) / ratio;
+  GN_BEGIN();
+  const size_t rows = (size_t)batch * seq;
+  const float* dh = st.in(hidden, rows * embed); const float* dv = st.in(value, rows * channels);
+  const float* dw = st.in(logit_weight, (size_t)channels * embed);
+  const float* dp = st.in(probabilities, (size_t)batch * blocks * ratio * channels); const float* dc = st.in(compressed, (size_t)batch * blocks * channels);
+  const float* dg = st.in(grad_compressed, (size_t)batch * blocks * channels);
+  float* gh = st.out(grad_hidden, rows * embed); float* gv = st.out(grad_value, rows * channels);
+  float* gw = st.out(grad_weight, (size_t)channels * embed, true); float* gb = st.out(grad_bias, (size_t)ratio * channels, true);
+  float* gl = st.temp<float>(rows * channels);
+  if (st.status != GN_OK) return st.status;
+  // rows of a trailing partial block that do not exist are not written by the kernel: none are left out, every (b, t) belongs to a block
+  GN_TRY(compressor_pool_backward_launch(dv, dp, dc, dg, batch, seq, channels, ratio, gl, gv, gb, s));
+  { GemmArgs g; g.A = gl; g.lda = channels; g.B = dw; g.ldb = embed; g.b_trans = 0; g.C = gh; g.ldc = embed; g.M = (int)rows; g.N = embed; g.K = channels;
+    GN_TRY(gemm_dispatch(g, gemm_default_kind(), s)); }                       // dhidden = dlogits W
+  { GemmArgs g; g.A = gl; g.lda = channels; g.a_trans = 1; g.B = dh; g.ldb = embed; g.b_trans = 0; g.C = gw; g.ldc = embed; g.M = channels; g.N = embed; g.K = (int)rows;
+    g.epilogue = EPI_ACCUM; GN_TRY(gemm_dispatch(g, gemm_default_kind(), s)); }   // dW += dlogits^T hidden
+  GN_TRY(st.finish());
+  return gemm_check_error(s);
+}
 // compressedAttentionForward (model/compress_attention.go:624-673), no segment mask
 int gn_compressed_attention_forward(const float* query, const float* key_c, const float* value_c, int batch, int n_head, int n_kv_head, int seq, int head_dim,
                                     int blocks, int ratio, float* out, float* lse) {

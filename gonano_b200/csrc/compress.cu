@@ -42,6 +42,33 @@ __global__ void __launch_bounds__(256) compressor_pool_kernel(const float* __res
   compressed[idx] = acc;
 }
 
+// backward of the block softmax: one thread per (batch, block, channel) writes dlogits and dvalue of its rows
+__global__ void __launch_bounds__(256) compressor_pool_bwd_kernel(const float* __restrict__ value, const float* __restrict__ probabilities,
+                                                                  const float* __restrict__ compressed, const float* __restrict__ grad_compressed, int B, int T, int C,
+                                                                  int ratio, int blocks, float* __restrict__ grad_logits, float* __restrict__ grad_value) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)B * blocks * C) return;
+  const int c = (int)(idx % C); const int64_t bb = idx / C; const int blk = (int)(bb % blocks); const int b = (int)(bb / blocks);
+  const int t0 = blk * ratio, rows = min(ratio, T - t0);
+  const float g = grad_compressed[idx], cv = compressed[idx];
+  for (int r = 0; r < rows; ++r) {
+    const float p = probabilities[(((int64_t)b * blocks + blk) * ratio + r) * C + c];
+    const int64_t o = ((int64_t)b * T + t0 + r) * C + c;
+    grad_logits[o] = __fmul_rn(__fmul_rn(p, g), __fsub_rn(value[o], cv));
+    grad_value[o] = __fmul_rn(p, g);
+  }
+}
+// bias gradient: one thread per (block position, channel), the rows added in (batch, position) order
+__global__ void __launch_bounds__(256) compressor_bias_bwd_kernel(const float* __restrict__ grad_logits, int B, int T, int C, int ratio, float* __restrict__ grad_bias) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= ratio * C) return;
+  const int c = idx % C, r = idx / C;
+  float acc = grad_bias[idx];
+  for (int b = 0; b < B; ++b)
+    for (int t = r; t < T; t += ratio) acc = __fadd_rn(acc, grad_logits[((int64_t)b * T + t) * C + c]);
+  grad_bias[idx] = acc;
+}
+
 // one warp per (batch, query head, token): keys = compressed blocks 0 .. t / ratio - 1
 template <int DP>
 __global__ void __launch_bounds__(256) compressed_attention_kernel(const float* __restrict__ q, const float* __restrict__ kc, const float* __restrict__ vc, int B,
@@ -133,6 +160,18 @@ int compressor_pool_launch(const float* logits, const float* bias, const float* 
   const int64_t n = (int64_t)B * blocks * C;
   if (n <= 0) return GN_OK;
   compressor_pool_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, s>>>(logits, bias, value, B, T, C, ratio, blocks, compressed, probabilities);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+int compressor_pool_backward_launch(const float* value, const float* probabilities, const float* compressed, const float* grad_compressed, int B, int T, int C,
+                                    int ratio, float* grad_logits, float* grad_value, float* grad_bias, cudaStream_t s) {
+  const int blocks = (T + ratio - 1) / ratio;
+  const int64_t n = (int64_t)B * blocks * C;
+  if (n <= 0) return GN_OK;
+  compressor_pool_bwd_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, s>>>(value, probabilities, compressed, grad_compressed, B, T, C, ratio, blocks, grad_logits, grad_value);
+  GN_LAUNCH_CHECK();
+  compressor_bias_bwd_kernel<<<ceil_div((int64_t)ratio * C, 256), 256, 0, s>>>(grad_logits, B, T, C, ratio, grad_bias);
   GN_LAUNCH_CHECK();
   return GN_OK;
 }

@@ -64,6 +64,9 @@ int attention_mma_forward(const AttnShape& sh, const float* q, const float* k, c
 // compressed attention building blocks (compress.cu)
 int compressor_pool_launch(const float* logits, const float* bias, const float* value, int B, int T, int C, int ratio, float* compressed, float* probabilities,
                            cudaStream_t s);
+// dlogits and dvalue ([B, T, C], every element written) and the bias gradient (accumulated) from the gradient of the compressed output
+int compressor_pool_backward_launch(const float* value, const float* probabilities, const float* compressed, const float* grad_compressed, int B, int T, int C,
+                                    int ratio, float* grad_logits, float* grad_value, float* grad_bias, cudaStream_t s);
 // selection == nullptr: every block before the query's own; else the token's selected blocks ([B * Hkv, T, topk] with counts [B * Hkv, T])
 int compressed_attention_launch(const float* q, const float* kc, const float* vc, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* out, float* lse,
                                 const int32_t* selection, const int32_t* counts, int topk, cudaStream_t s);

@@ -109,6 +109,12 @@ int gn_indexer_block_max(float* dst, const float* scores, int rows, int blocks, 
  * padded with -1, counts [tokens]; descending score, ties toward the smaller block index). */
 int gn_compressor_forward(const float* hidden, const float* value, const float* logit_weight, const float* bias, int batch, int seq, int embed,
                           int channels, int ratio, float* compressed, float* probabilities);
+/* ChannelCompressor.Backward (model/compress.go:182-237): probabilities and compressed are gn_compressor_forward's
+ * outputs; grad_hidden [batch, seq, embed] and grad_value [batch, seq, channels] are overwritten, grad_weight
+ * [channels, embed] and grad_bias [ratio, channels] accumulated. */
+int gn_compressor_backward(const float* hidden, const float* value, const float* logit_weight, const float* probabilities, const float* compressed,
+                           const float* grad_compressed, int batch, int seq, int embed, int channels, int ratio, float* grad_hidden, float* grad_value,
+                           float* grad_weight, float* grad_bias);
 int gn_compressed_attention_forward(const float* query, const float* key_c, const float* value_c, int batch, int n_head, int n_kv_head, int seq,
                                     int head_dim, int blocks, int ratio, float* out, float* lse);
 /* compressedAttentionForwardSparse (model/compress_attention.go:321-374): selection [batch * n_kv_head, seq, topk] block

@@ -1,7 +1,7 @@
 // TEST INFRASTRUCTURE, NOT PRODUCT: CPU restatement of the building blocks of the reference's compressed
 // ("flash") attention layers, used only to check the CUDA kernels.
 //
-//   channel compressor forward        model/compress.go:93-177
+//   channel compressor forward        model/compress.go:93-177, backward :182-237
 //   compression of K and V per head    model/compress_attention.go:562-621 (compressForward, no segment mask)
 //   attention over preceding blocks    model/compress_attention.go:624-673 (compressedAttentionForward)
 //   attention over selected blocks     model/compress_attention.go:321-374 (compressedAttentionForwardSparse)
@@ -64,6 +64,39 @@ inline void compressor_forward(const Backend& bk, const float* hidden, const flo
         if (probabilities)
           for (int r = 0; r < ratio; ++r) probabilities[(((size_t)b * blocks + blk) * ratio + r) * C + c] = prob[r];
       }
+}
+
+// ChannelCompressor.Backward (model/compress.go:182-237, no segment mask): from the gradient of the compressed output to
+// grad_hidden [B, T, d] and grad_value [B, T, C] (overwritten) and grad_weight [C, d], grad_bias [ratio, C] (accumulated).
+// dlogit_j = p_j g (value_j - compressed); dvalue_j = p_j g; Linear.Backward: dW += dlogits^T hidden, dhidden = dlogits W.
+inline void compressor_backward(const Backend& bk, const float* hidden, const float* value, const float* weight, const float* probabilities,
+                                const float* compressed, const float* grad_compressed, int B, int T, int d, int C, int ratio, float* grad_hidden,
+                                float* grad_value, float* grad_weight, float* grad_bias) {
+  const int blocks = (T + ratio - 1) / ratio;
+  std::vector<float> gl((size_t)B * T * C, 0.0f);
+  std::fill(grad_value, grad_value + (size_t)B * T * C, 0.0f);
+  for (int b = 0; b < B; ++b)
+    for (int blk = 0; blk < blocks; ++blk)
+      for (int c = 0; c < C; ++c) {
+        const float g = grad_compressed[((size_t)b * blocks + blk) * C + c], cv = compressed[((size_t)b * blocks + blk) * C + c];
+        for (int r = 0; r < ratio; ++r) {
+          const int t = blk * ratio + r;
+          if (t >= T) continue;
+          const float p = probabilities[(((size_t)b * blocks + blk) * ratio + r) * C + c];
+          const float v = value[((size_t)b * T + t) * C + c];
+          gl[((size_t)b * T + t) * C + c] += p * g * (v - cv);
+          grad_value[((size_t)b * T + t) * C + c] += p * g;
+        }
+      }
+  // dhidden = dlogits [BT, C] . W [C, d];  dW += dlogits^T . hidden
+  bk.matmul(grad_hidden, gl.data(), weight, B * T, d, C);
+  std::vector<float> glt((size_t)C * B * T), dw((size_t)C * d);
+  for (int i = 0; i < B * T; ++i) for (int c = 0; c < C; ++c) glt[(size_t)c * B * T + i] = gl[(size_t)i * C + c];
+  bk.matmul(dw.data(), glt.data(), hidden, C, d, B * T);
+  for (size_t i = 0; i < dw.size(); ++i) grad_weight[i] += dw[i];
+  for (int b = 0; b < B; ++b)
+    for (int t = 0; t < T; ++t)
+      for (int c = 0; c < C; ++c) grad_bias[(size_t)(t % ratio) * C + c] += gl[((size_t)b * T + t) * C + c];
 }
 
 // q [B, Hq, T, D], kc / vc [B, Hkv, blocks, D] -> out [B, Hq, T, D], lse [B, Hq, T]: the queries of block b attend the

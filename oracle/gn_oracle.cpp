@@ -571,6 +571,11 @@ void or_compressor_forward(int m, const float* hidden, const float* value, const
                            float* compressed, float* probabilities) {
   BK(m); gnor::compressor_forward(bk, hidden, value, weight, bias, B, T, d, C, ratio, compressed, probabilities);
 }
+void or_compressor_backward(int m, const float* hidden, const float* value, const float* weight, const float* prob, const float* compressed,
+                            const float* grad_compressed, int B, int T, int d, int C, int ratio, float* grad_hidden, float* grad_value, float* grad_weight,
+                            float* grad_bias) {
+  BK(m); gnor::compressor_backward(bk, hidden, value, weight, prob, compressed, grad_compressed, B, T, d, C, ratio, grad_hidden, grad_value, grad_weight, grad_bias);
+}
 void or_compressed_attention_forward(int m, const float* q, const float* kc, const float* vc, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio,
                                      float* out, float* lse) {
   BK(m); gnor::compressed_attention_forward(bk, q, kc, vc, B, Hq, Hkv, T, D, blocks, ratio, out, lse);

@@ -567,6 +567,17 @@ def compressor_forward(hidden, value, weight, bias, ratio, mode=0):
     return out, prob
 
 
+def compressor_backward(hidden, value, weight, bias, ratio, grad_compressed, mode=0):
+    """ChannelCompressor.Backward (model/compress.go:182-237): gradients of hidden, value, logit weight and bias."""
+    hidden, value, weight, bias, grad_compressed = f32(hidden), f32(value), f32(weight), f32(bias), f32(grad_compressed)
+    B, T, d = hidden.shape; C_ = value.shape[2]
+    comp, prob = compressor_forward(hidden, value, weight, bias, ratio, mode)
+    gh = np.zeros_like(hidden); gv = np.zeros_like(value); gw = np.zeros_like(weight); gb = np.zeros_like(bias)
+    lib().or_compressor_backward(mode, _f(hidden), _f(value), _f(weight), _f(prob), _f(comp), _f(grad_compressed), B, T, d, C_, ratio,
+                                 _f(gh), _f(gv), _f(gw), _f(gb))
+    return gh, gv, gw, gb
+
+
 def compressed_attention_forward(q, kc, vc, ratio, mode=0):
     """compressedAttentionForward (model/compress_attention.go:624-673): q [B,Hq,T,D], kc/vc [B,Hkv,blocks,D]."""
     q, kc, vc = f32(q), f32(kc), f32(vc)

@@ -176,3 +176,21 @@ def test_sparse_compressed_layer_forward(oracle, bk):
     same = np.all(got_sel == want_sel, axis=(1, 2))
     assert same.all(), "block selection differs"       # scores agree to rounding; a flipped near-tie would show here
     close(got, want, 1e-4, 1e-5); close(got_l, want_l, 1e-4, 1e-5)
+
+
+@pytest.mark.parametrize("B,T,d,C,ratio", [(2, 5, 4, 3, 2), (2, 37, 48, 32, 4), (1, 130, 96, 128, 8)])
+def test_compressor_backward(oracle, bk, B, T, d, C, ratio):
+    """ChannelCompressor.Backward (model/compress.go:182-237) against the oracle, whose own backward is held to the
+    reference's finite-difference check (tests/test_oracle_golden.py); parameter gradients accumulate."""
+    rng = np.random.default_rng(B * 10 + T)
+    hidden = rng.standard_normal((B, T, d)).astype(np.float32); value = rng.standard_normal((B, T, C)).astype(np.float32)
+    weight = (rng.standard_normal((C, d)) * 0.4).astype(np.float32); bias = (rng.standard_normal((ratio, C)) * 0.5).astype(np.float32)
+    blocks = (T + ratio - 1) // ratio
+    gc = rng.standard_normal((B, blocks, C)).astype(np.float32)
+    want = oracle.compressor_backward(hidden, value, weight, bias, ratio, gc)
+    got = bk.compressor_backward(hidden, value, weight, bias, ratio, gc)
+    for g, w in zip(got, want):
+        close(g, w, 1e-4, 1e-5 * max(1.0, float(np.max(np.abs(w)))))
+    gw0 = rng.standard_normal(weight.shape).astype(np.float32); gb0 = rng.standard_normal(bias.shape).astype(np.float32)
+    acc = bk.compressor_backward(hidden, value, weight, bias, ratio, gc, grad_weight=gw0, grad_bias=gb0)
+    close(acc[2], got[2] + gw0, 1e-5, 1e-5); close(acc[3], got[3] + gb0, 1e-5, 1e-5)

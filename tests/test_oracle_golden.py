@@ -275,3 +275,22 @@ def test_merge_branches_equals_joint_softmax(oracle):
     assert np.array_equal(o2.ravel(), ob.ravel()) and l2[0] == lb.ravel()[0]
     o3, l3 = oracle.merge_branches(np.zeros((1, hd)), empty, np.zeros((1, hd)), empty)
     assert np.all(o3 == 0) and l3[0] == -np.inf
+
+
+# model/compress_test.go:28-110: the compressor's backward against a central finite difference along random directions of
+# every input and parameter (the reference's own check, same shapes: d 4, C 3, ratio 2, B 2, T 5)
+def test_compressor_gradient_matches_finite_difference(oracle):
+    rng = np.random.default_rng(7)
+    B, T, d, C_, ratio = 2, 5, 4, 3, 2
+    w = (rng.standard_normal((C_, d)) * 0.5).astype(np.float32); bias = (rng.standard_normal((ratio, C_)) * 0.5).astype(np.float32)
+    hidden = rng.standard_normal((B, T, d)).astype(np.float32); value = rng.standard_normal((B, T, C_)).astype(np.float32)
+    gc = rng.standard_normal((B, 3, C_)).astype(np.float32)
+    gh, gv, gw, gb = oracle.compressor_backward(hidden, value, w, bias, ratio, gc)
+    dirs = [rng.standard_normal(x.shape).astype(np.float32) for x in (hidden, value, w, bias)]
+    analytic = sum(float(np.sum(g.astype(np.float64) * dr)) for g, dr in zip((gh, gv, gw, gb), dirs))
+    def loss(eps):
+        out, _ = oracle.compressor_forward(hidden + eps * dirs[0], value + eps * dirs[1], w + eps * dirs[2], bias + eps * dirs[3], ratio)
+        return float(np.sum(out.astype(np.float64) * gc))
+    eps = 1e-3
+    numeric = (loss(eps) - loss(-eps)) / (2 * eps)
+    assert abs(analytic - numeric) <= 2e-3 * max(1.0, abs(numeric)), (analytic, numeric)
