@@ -546,6 +546,21 @@ def run_ours(args):
     except Exception:
         pass
     kernels = kernel_rooflines(ctx, pk, tf32) if not args.lean else [{"kernel": "gemm_nt", "workload": "not measured (--lean)"}]
+    if not args.lean and not latent:
+        # the decode step itself, event-timed over a rollout of 64 tokens replayed from the CUDA graph: the full batch and the
+        # shard an 8-GPU run gives each rank; bytes = the float32 weights once per step (what a step must at least stream)
+        weight_bytes = 4.0 * sum(int(np.prod(model.shape(n))) for n in model.names if n.startswith("transformer.h.") and model.shape(n)[-1] > 1 and "ve" not in n) \
+            + 4.0 * int(np.prod(model.shape("lm_head.weight")))
+        for prompts_n in (64, 8):
+            pp = synthetic.prompts(prompts_n, w["prompt_len"], cfg["vocab_size"], seed=77)
+            sd = np.arange(prompts_n, dtype=np.uint64) + 900
+            for _ in range(2):
+                _, _, nsteps, _ = model.generate_batch(pp, w["group"], 64, w["temperature"], w["top_k"], sd)
+            ms = model.phase_ms("decode") / max(nsteps - 1, 1)
+            gbs = weight_bytes / (ms * 1e-3) / 1e9
+            kernels.append({"kernel": "decode_step", "workload": f"d12, {prompts_n * w['group']} rows, 64 new tokens after a {w['prompt_len']}-token prompt (whole step, graph replay)",
+                            "bound": "hbm", "ms": ms, "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
+                            "note": "latency-bound chain of ~100 dependent launches; bytes counted = the float32 matmul weights once"})
     dominant = dict(kernels[0])
     # algorithmic bytes of that product: operands hi+lo 2 * 4 * (M*K + N*K) = 119.5 MB read, output 201.3 MB written
     dominant["traffic"] = GEMM_TRAFFIC_BYTES
