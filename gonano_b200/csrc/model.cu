@@ -952,7 +952,7 @@ int rollout_sample(gn_model* m, const float* logits, float temperature, int top_
 int rollout_forward(gn_model* m) {
   Rollout& ro = m->ro;
   FwdArgs a; a.mode = MODE_DECODE; a.ids = m->sampled.i(); a.B = ro.rows; a.T = 1; a.cache_rows = ro.rows; a.cache_row_mul = 1; a.max_seq = ro.max_seq;
-  if (ro.G > 1) { a.group = ro.G; a.prefix_len = ro.plen; }
+  if (ro.G > 1 && ro.prompt_shared) { a.group = ro.G; a.prefix_len = ro.plen; }
   return forward_core(m, ro.b, a);
 }
 
@@ -1295,6 +1295,7 @@ int gn_model_kv_write(gn_model* m, int layer, int kind, int row, int head, int p
   GN_TRY(kv_slice(m, layer, kind, row, head, positions, &p, &want));
   GN_REQUIRE(n == want, "gn_model_kv_write: the slice has %lld floats, got %lld", (long long)want, (long long)n);
   if (n > 0) { GN_CUDA(cudaMemcpyAsync(p, host, sizeof(float) * n, cudaMemcpyHostToDevice, m->s())); GN_CUDA(cudaStreamSynchronize(m->s())); }
+  m->ro.prompt_shared = false;   // the decode attention may no longer take the prompt's keys from the group's first row
   return GN_OK;
 }
 

@@ -122,6 +122,7 @@ struct Rollout {
   int logits_row_div = 1;     // rows that share one row of the current logits (G right after the prefill, then 1)
   bool thinking = false; int thinking_budget = 0;
   int follower_steps = 0;     // forwards of columns sampled elsewhere (ensemble members)
+  bool prompt_shared = true;  // the rows of a group still hold identical K/V for the prompt positions (false once the cache was written from outside)
   FwdBufs b;
 };
 }  // namespace gnm

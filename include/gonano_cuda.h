@@ -376,7 +376,9 @@ int gn_policy_gradient_step(gn_model* model, const int32_t* inputs, const int32_
  *   kind 2      latent rows of (layer, row): positions * latent floats        (latent attention, model/kvcache.go:224-237)
  *   kind 3      rotary keys of (layer, row): positions * n_kv_head * rope floats
  *   kind 4      the row's previous pre-smear embedding: embed_dim floats (layer, head, positions ignored)
- * gn_model_kv_alloc sizes an empty cache (for writing a deserialised one); gn_generate_batch sizes its own. */
+ * gn_model_kv_alloc sizes an empty cache (for writing a deserialised one); gn_generate_batch sizes its own.  After a
+ * gn_model_kv_write the rows of a group are no longer assumed to share their prompt's keys and values (the decode
+ * attention then reads every row's own copy until the next gn_rollout_begin / gn_generate_batch). */
 int gn_model_kv_info(gn_model* model, int* rows, int* max_seq, int* position);
 int gn_model_kv_alloc(gn_model* model, int rows, int max_seq, int position);
 int gn_model_kv_read(gn_model* model, int layer, int kind, int row, int head, int positions, float* host, int64_t n);
