@@ -117,6 +117,11 @@ int gn_compressor_backward(const float* hidden, const float* value, const float*
                            float* grad_weight, float* grad_bias);
 int gn_compressed_attention_forward(const float* query, const float* key_c, const float* value_c, int batch, int n_head, int n_kv_head, int seq,
                                     int head_dim, int blocks, int ratio, float* out, float* lse);
+/* compressedAttentionBackward (model/compress_attention.go:735-781): dq, dkc, dvc are accumulated into; row_correction
+ * (nullable, [batch, n_head, seq]) is the reference's rowCorrection for a branch whose output was merged with another. */
+int gn_compressed_attention_backward(const float* query, const float* key_c, const float* value_c, const float* out_grad, const float* lse,
+                                     const float* row_correction, int batch, int n_head, int n_kv_head, int seq, int head_dim, int blocks, int ratio,
+                                     float* dq, float* dkc, float* dvc);
 /* compressedAttentionForwardSparse (model/compress_attention.go:321-374): selection [batch * n_kv_head, seq, topk] block
  * indices, counts [batch * n_kv_head, seq]; block indices must lie in [0, blocks). */
 int gn_compressed_attention_sparse_forward(const float* query, const float* key_c, const float* value_c, const int32_t* selection, const int32_t* counts,

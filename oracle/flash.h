@@ -5,6 +5,7 @@
 //   compression of K and V per head    model/compress_attention.go:562-621 (compressForward, no segment mask)
 //   attention over preceding blocks    model/compress_attention.go:624-673 (compressedAttentionForward)
 //   attention over selected blocks     model/compress_attention.go:321-374 (compressedAttentionForwardSparse)
+//   backward over preceding blocks     model/compress_attention.go:735-781 (compressedAttentionBackward)
 //   local sliding-window branch        model/compress_attention.go:487-536 (attentionForwardWindowed = the ordinary
 //                                      attention with a window, kernels/scalar/attention.go:16-205)
 //   merge of two softmax branches      model/compress_attention.go:440-466 (mergeAttentionBranches)
@@ -120,6 +121,27 @@ inline void compressed_attention_forward(const Backend& bk, const float* q, cons
         }
         // position offset = blk: every compressed key index is below every query position (no causal cut inside)
         bk.attention_forward(q + (qi * T + start) * D, kc + kbase, vc + kbase, end - start, blk, D, blk, -1, nullptr, 0, o, l);
+      }
+    }
+}
+
+// compressedAttentionBackward (model/compress_attention.go:735-781, no segment mask): per block the ordinary attention
+// backward of its queries against the blocks before it; dq [B, Hq, T, D], dkc / dvc [B, Hkv, blocks, D] are accumulated into.
+// row_correction (nullable, [B, Hq, T]) replaces sum_j p_j dp_j when the branch's output was merged with another branch.
+inline void compressed_attention_backward(const Backend& bk, const float* q, const float* kc, const float* vc, const float* dout, const float* lse,
+                                          const float* row_correction, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* dq, float* dkc,
+                                          float* dvc) {
+  const int hr = Hq / Hkv;
+  for (int b = 0; b < B; ++b)
+    for (int h = 0; h < Hq; ++h) {
+      const size_t qi = (size_t)b * Hq + h;
+      const size_t kbase = ((size_t)b * Hkv + h / hr) * blocks * D;
+      for (int blk = 1; blk < blocks; ++blk) {
+        const int start = blk * ratio, end = std::min(start + ratio, T);
+        if (end <= start) continue;
+        bk.attention_backward(q + (qi * T + start) * D, kc + kbase, vc + kbase, dout + (qi * T + start) * D, lse + qi * T + start,
+                              row_correction ? row_correction + qi * T + start : nullptr, end - start, blk, D, blk, -1, nullptr, 0,
+                              dq + (qi * T + start) * D, dkc + kbase, dvc + kbase);
       }
     }
 }

@@ -596,6 +596,17 @@ def compressed_attention_sparse_forward(q, kc, vc, selection, counts, mode=0):
     return out, lse
 
 
+def compressed_attention_backward(q, kc, vc, dout, lse, ratio, row_correction=None, mode=0):
+    """compressedAttentionBackward (model/compress_attention.go:735-781): returns dq, dkc, dvc (from zero)."""
+    q, kc, vc, dout, lse = f32(q), f32(kc), f32(vc), f32(dout), f32(lse)
+    B, Hq, T, D = q.shape; Hkv, blocks = kc.shape[1], kc.shape[2]
+    rc = f32(row_correction) if row_correction is not None else None
+    dq = np.zeros_like(q); dk = np.zeros_like(kc); dv = np.zeros_like(vc)
+    lib().or_compressed_attention_backward(mode, _f(q), _f(kc), _f(vc), _f(dout), _f(lse), _f(rc) if rc is not None else None, B, Hq, Hkv, T, D, blocks, ratio,
+                                           _f(dq), _f(dk), _f(dv))
+    return dq, dk, dv
+
+
 def merge_branches(oa, la, ob, lb):
     """mergeAttentionBranches (model/compress_attention.go:440-466)."""
     oa, la, ob, lb = f32(oa), f32(la), f32(ob), f32(lb)

@@ -194,3 +194,28 @@ def test_compressor_backward(oracle, bk, B, T, d, C, ratio):
     gw0 = rng.standard_normal(weight.shape).astype(np.float32); gb0 = rng.standard_normal(bias.shape).astype(np.float32)
     acc = bk.compressor_backward(hidden, value, weight, bias, ratio, gc, grad_weight=gw0, grad_bias=gb0)
     close(acc[2], got[2] + gw0, 1e-5, 1e-5); close(acc[3], got[3] + gb0, 1e-5, 1e-5)
+
+
+# compressedAttentionBackward (model/compress_attention.go:735-781): with and without a row correction, grouped heads,
+# a ragged last block, and accumulation into gradients that already hold values
+@pytest.mark.parametrize("B,Hq,Hkv,T,D,ratio,corr", [(1, 1, 1, 9, 8, 2, False), (2, 6, 2, 70, 128, 4, False), (1, 4, 4, 33, 64, 8, True),
+                                                    (1, 2, 1, 40, 32, 64, False), (2, 6, 2, 130, 128, 4, True)])
+def test_compressed_attention_backward(oracle, bk, B, Hq, Hkv, T, D, ratio, corr):
+    rng = np.random.default_rng(T * 3 + D)
+    blocks = (T + ratio - 1) // ratio
+    q = (rng.standard_normal((B, Hq, T, D)) * 0.4).astype(np.float32)
+    kc = (rng.standard_normal((B, Hkv, blocks, D)) * 0.4).astype(np.float32); vc = rng.standard_normal((B, Hkv, blocks, D)).astype(np.float32)
+    dout = rng.standard_normal((B, Hq, T, D)).astype(np.float32)
+    _, lse = oracle.compressed_attention_forward(q, kc, vc, ratio)
+    rc = rng.standard_normal((B, Hq, T)).astype(np.float32) if corr else None
+    if corr:
+        lse = (lse + np.abs(rng.standard_normal(lse.shape)).astype(np.float32)).astype(np.float32)     # a merged row's lse exceeds the branch's own
+    want = oracle.compressed_attention_backward(q, kc, vc, dout, lse, ratio, rc)
+    got = bk.compressed_attention_backward(q, kc, vc, dout, lse, ratio, rc)
+    for g, w in zip(got, want):
+        close(g, w, 2e-4, 2e-5)
+    assert np.all(got[0][:, :, :min(ratio, T)] == 0) and np.all(got[1][:, :, (T - 1) // ratio:] == 0)   # no preceding block / no later token
+    seed = [rng.standard_normal(x.shape).astype(np.float32) for x in (q, kc, vc)]
+    acc = bk.compressed_attention_backward(q, kc, vc, dout, lse, ratio, rc, *seed)
+    for a, s0, w in zip(acc, seed, want):
+        close(a, s0 + w, 2e-4, 2e-5)

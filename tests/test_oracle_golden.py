@@ -294,3 +294,24 @@ def test_compressor_gradient_matches_finite_difference(oracle):
     eps = 1e-3
     numeric = (loss(eps) - loss(-eps)) / (2 * eps)
     assert abs(analytic - numeric) <= 2e-3 * max(1.0, abs(numeric)), (analytic, numeric)
+
+
+# compressedAttentionBackward (model/compress_attention.go:735-781) against a central difference of its forward
+def test_compressed_attention_gradient_matches_finite_difference(oracle):
+    rng = np.random.default_rng(11)
+    B, Hq, Hkv, T, D, ratio = 1, 4, 2, 11, 6, 3
+    blocks = (T + ratio - 1) // ratio
+    q = (rng.standard_normal((B, Hq, T, D)) * 0.5).astype(np.float32)
+    kc = (rng.standard_normal((B, Hkv, blocks, D)) * 0.5).astype(np.float32); vc = rng.standard_normal((B, Hkv, blocks, D)).astype(np.float32)
+    dout = rng.standard_normal((B, Hq, T, D)).astype(np.float32)
+    _, lse = oracle.compressed_attention_forward(q, kc, vc, ratio)
+    gq, gk, gv = oracle.compressed_attention_backward(q, kc, vc, dout, lse, ratio)
+    assert np.all(gq[:, :, :ratio] == 0) and np.all(gk[:, :, (T - 1) // ratio:] == 0)
+    dirs = [rng.standard_normal(x.shape).astype(np.float32) for x in (q, kc, vc)]
+    analytic = sum(float(np.sum(g.astype(np.float64) * dr)) for g, dr in zip((gq, gk, gv), dirs))
+    def loss(eps):
+        out, _ = oracle.compressed_attention_forward(q + eps * dirs[0], kc + eps * dirs[1], vc + eps * dirs[2], ratio)
+        return float(np.sum(out.astype(np.float64) * dout))
+    eps = 1e-3
+    numeric = (loss(eps) - loss(-eps)) / (2 * eps)
+    assert abs(analytic - numeric) <= 2e-3 * max(1.0, abs(numeric)), (analytic, numeric)
