@@ -148,6 +148,17 @@ class CudaBackend:
                                                         blocks, ratio, ptr(gq), ptr(gk), ptr(gv)))
         return gq, gk, gv
 
+    def compressed_attention_sparse_backward(self, q, kc, vc, dout, lse, selection, counts, row_correction=None, dq=None, dkc=None, dvc=None):
+        """compressedAttentionBackwardSparse (model/compress_attention.go:376-433): dq, dkc, dvc (accumulated into the arrays given)."""
+        q, kc, vc, dout, lse = _f32(q), _f32(kc), _f32(vc), _f32(dout), _f32(lse); selection, counts = _i32(selection), _i32(counts)
+        B, Hq, T, D = q.shape; Hkv, blocks = kc.shape[1], kc.shape[2]; topk = selection.shape[-1]
+        rc = _f32(row_correction) if row_correction is not None else None
+        gq = np.zeros_like(q) if dq is None else _f32(dq).copy(); gk = np.zeros_like(kc) if dkc is None else _f32(dkc).copy()
+        gv = np.zeros_like(vc) if dvc is None else _f32(dvc).copy()
+        check(self.lib.gn_compressed_attention_sparse_backward(ptr(q), ptr(kc), ptr(vc), ptr(dout), ptr(lse), ptr(rc) if rc is not None else None, ptr(selection),
+                                                               ptr(counts), B, Hq, Hkv, T, D, blocks, topk, ptr(gq), ptr(gk), ptr(gv)))
+        return gq, gk, gv
+
     def compressed_attention_sparse_forward(self, q, kc, vc, selection, counts):
         """compressedAttentionForwardSparse (model/compress_attention.go:321-374): selection [B*Hkv, T, topk], counts [B*Hkv, T]."""
         q, kc, vc = _f32(q), _f32(kc), _f32(vc); selection, counts = _i32(selection), _i32(counts)

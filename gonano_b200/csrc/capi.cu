@@ -377,7 +377,7 @@ int gn_compressed_attention_backward(const float* query, const float* key_c, con
   float* gq = st.out(dq, nq, true); float* gk = st.out(dkc, nk, true); float* gv = st.out(dvc, nk, true);
   float* scratch = st.temp<float>(nt);
   if (st.status != GN_OK) return st.status;
-  GN_TRY(compressed_attention_backward_launch(pq, pk, pv, pg, pl, pr, scratch, batch, n_head, n_kv_head, seq, head_dim, blocks, ratio, gq, gk, gv, s));
+  GN_TRY(compressed_attention_backward_launch(pq, pk, pv, pg, pl, pr, scratch, batch, n_head, n_kv_head, seq, head_dim, blocks, ratio, gq, gk, gv, nullptr, nullptr, 0, s));
   GN_END();
 }
 // compressedAttentionForwardSparse (model/compress_attention.go:321-374), no segment mask
@@ -392,6 +392,24 @@ int gn_compressed_attention_sparse_forward(const float* query, const float* key_
   float* dout = st.out(out, nq); float* dl = lse ? st.out(lse, (size_t)batch * n_head * seq) : nullptr;
   if (st.status != GN_OK) return st.status;
   GN_TRY(compressed_attention_launch(dq, dk, dv, batch, n_head, n_kv_head, seq, head_dim, blocks, 1, dout, dl, ds, dc, topk, s));
+  GN_END();
+}
+// compressedAttentionBackwardSparse (model/compress_attention.go:376-433), no segment mask; the three gradients accumulate
+int gn_compressed_attention_sparse_backward(const float* query, const float* key_c, const float* value_c, const float* out_grad, const float* lse,
+                                            const float* row_correction, const int32_t* selection, const int32_t* counts, int batch, int n_head, int n_kv_head,
+                                            int seq, int head_dim, int blocks, int topk, float* dq, float* dkc, float* dvc) {
+  if (batch <= 0 || seq <= 0 || blocks <= 0) return GN_OK;
+  GN_REQUIRE(query && key_c && value_c && out_grad && lse && selection && counts && topk >= 1 && dq && dkc && dvc, "compressed_attention_sparse_backward: bad argument");
+  GN_BEGIN();
+  const size_t nq = (size_t)batch * n_head * seq * head_dim, nk = (size_t)batch * n_kv_head * blocks * head_dim, nt = (size_t)batch * n_head * seq;
+  const size_t ns = (size_t)batch * n_kv_head * seq;
+  const float* pq = st.in(query, nq); const float* pk = st.in(key_c, nk); const float* pv = st.in(value_c, nk);
+  const float* pg = st.in(out_grad, nq); const float* pl = st.in(lse, nt); const float* pr = row_correction ? st.in(row_correction, nt) : nullptr;
+  const int32_t* ps = st.in(selection, ns * topk); const int32_t* pc = st.in(counts, ns);
+  float* gq = st.out(dq, nq, true); float* gk = st.out(dkc, nk, true); float* gv = st.out(dvc, nk, true);
+  float* scratch = st.temp<float>(nt);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(compressed_attention_backward_launch(pq, pk, pv, pg, pl, pr, scratch, batch, n_head, n_kv_head, seq, head_dim, blocks, 1, gq, gk, gv, ps, pc, topk, s));
   GN_END();
 }
 // mergeAttentionBranches (model/compress_attention.go:440-466)

@@ -92,6 +92,7 @@ __global__ void __launch_bounds__(256) compressed_attention_kernel(const float* 
   float m = -INFINITY, l = 0.0f;
   for (int j = 0; j < nk; ++j) {
     const int blk = sel ? sel[j] : j;
+    if ((unsigned)blk >= (unsigned)blocks) continue;      // an index outside the blocks is ignored, never dereferenced
     const float* kr = kc + kbase + (int64_t)blk * D; const float* vr = vc + kbase + (int64_t)blk * D;
     float s = 0.0f;
 #pragma unroll
@@ -112,73 +113,78 @@ __global__ void __launch_bounds__(256) compressed_attention_kernel(const float* 
 
 // Backward over the preceding blocks (model/compress_attention.go:735-781), deterministic, no atomics.
 // dq: one warp per (batch, query head, token): p_j = exp(q.k_j - lse), dp_j = dO.v_j, ds_j = p_j (dp_j - delta), dq += sum_j ds_j k_j,
-// delta = row_correction[t] when given, else sum_j p_j dp_j.
+// delta = row_correction[t] when given, else sum_j p_j dp_j (its own pass).  With a selection the keys are the token's selected blocks.
 template <int DP>
 __global__ void __launch_bounds__(256) compressed_attention_dq_kernel(const float* __restrict__ q, const float* __restrict__ kc, const float* __restrict__ vc,
                                                                       const float* __restrict__ dout, const float* __restrict__ lse,
-                                                                      const float* __restrict__ rowcorr, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio,
-                                                                      float* __restrict__ dq) {
+                                                                      const float* __restrict__ delta, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio,
+                                                                      float* __restrict__ dq, const int32_t* __restrict__ selection,
+                                                                      const int32_t* __restrict__ counts, int topk) {
   constexpr int PER = DP / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t idx = (int64_t)blockIdx.x * 8 + warp;
   if (idx >= (int64_t)B * Hq * T) return;
   const int t = (int)(idx % T); const int64_t bh = idx / T; const int h = (int)(bh % Hq); const int b = (int)(bh / Hq);
-  const int nk = min(t / ratio, blocks);
+  const int64_t kvh = (int64_t)b * Hkv + h / (Hq / Hkv);
+  const int32_t* sel = selection ? selection + (kvh * T + t) * topk : nullptr;
+  const int nk = selection ? max(0, min(counts[kvh * T + t], topk)) : min(t / ratio, blocks);
   if (nk <= 0) return;
-  const int64_t kbase = ((int64_t)b * Hkv + h / (Hq / Hkv)) * blocks * D;
+  const int64_t kbase = kvh * blocks * D;
   float qv[PER], gv[PER], acc[PER];
 #pragma unroll
   for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; qv[i] = c < D ? q[idx * D + c] : 0.0f; gv[i] = c < D ? dout[idx * D + c] : 0.0f; acc[i] = 0.0f; }
-  const float L = lse[idx];
-  float delta = 0.0f;
-  if (rowcorr) delta = rowcorr[idx];
-  else {
-    for (int j = 0; j < nk; ++j) {
-      float s = 0.0f, dp = 0.0f;
-#pragma unroll
-      for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; if (c < D) { s = fmaf(qv[i], kc[kbase + (int64_t)j * D + c], s); dp = fmaf(gv[i], vc[kbase + (int64_t)j * D + c], dp); } }
-      s = warp_sum(s); dp = warp_sum(dp);
-      delta = fmaf(__expf(s - L), dp, delta);
-    }
-  }
+  const float L = lse[idx], dl = delta[idx];
   for (int j = 0; j < nk; ++j) {
+    const int blk = sel ? sel[j] : j;
+    if ((unsigned)blk >= (unsigned)blocks) continue;
+    const int64_t kr = kbase + (int64_t)blk * D;
     float s = 0.0f, dp = 0.0f;
 #pragma unroll
-    for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; if (c < D) { s = fmaf(qv[i], kc[kbase + (int64_t)j * D + c], s); dp = fmaf(gv[i], vc[kbase + (int64_t)j * D + c], dp); } }
+    for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; if (c < D) { s = fmaf(qv[i], kc[kr + c], s); dp = fmaf(gv[i], vc[kr + c], dp); } }
     s = warp_sum(s); dp = warp_sum(dp);
-    const float ds = __expf(s - L) * (dp - delta);
+    const float ds = __expf(s - L) * (dp - dl);
 #pragma unroll
-    for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; if (c < D) acc[i] = fmaf(ds, kc[kbase + (int64_t)j * D + c], acc[i]); }
+    for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; if (c < D) acc[i] = fmaf(ds, kc[kr + c], acc[i]); }
   }
 #pragma unroll
   for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; if (c < D) dq[idx * D + c] += acc[i]; }
 }
-// dkc / dvc: one warp per (batch, kv head, block j): the query heads of the group and the tokens of the later blocks in order
+// dkc / dvc: one warp per (batch, kv head, block j) walks the tokens that attend to block j (dense: those of the later blocks;
+// selected blocks: a scan of each token's selection list) and, per token, the query heads of the group.
 template <int DP>
 __global__ void __launch_bounds__(256) compressed_attention_dkv_kernel(const float* __restrict__ q, const float* __restrict__ kc, const float* __restrict__ vc,
                                                                        const float* __restrict__ dout, const float* __restrict__ lse,
                                                                        const float* __restrict__ delta, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio,
-                                                                       float* __restrict__ dkc, float* __restrict__ dvc) {
+                                                                       float* __restrict__ dkc, float* __restrict__ dvc, const int32_t* __restrict__ selection,
+                                                                       const int32_t* __restrict__ counts, int topk) {
   constexpr int PER = DP / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t idx = (int64_t)blockIdx.x * 8 + warp;
   if (idx >= (int64_t)B * Hkv * blocks) return;
-  const int j = (int)(idx % blocks); const int64_t bk = idx / blocks; const int hk = (int)(bk % Hkv); const int b = (int)(bk / Hkv);
+  const int j = (int)(idx % blocks); const int64_t kvh = idx / blocks; const int hk = (int)(kvh % Hkv); const int b = (int)(kvh / Hkv);
   const int hr = Hq / Hkv;
   float kv[PER], vv[PER], ak[PER], av[PER];
 #pragma unroll
   for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; kv[i] = c < D ? kc[idx * D + c] : 0.0f; vv[i] = c < D ? vc[idx * D + c] : 0.0f; ak[i] = av[i] = 0.0f; }
-  for (int hh = 0; hh < hr; ++hh) {
-    const int64_t qi = (int64_t)b * Hq + hk * hr + hh;
-    for (int t = (j + 1) * ratio; t < T; ++t) {      // tokens whose block comes after block j
-      const float* qr = q + (qi * T + t) * D; const float* gr = dout + (qi * T + t) * D;
+  const int t0 = selection ? 0 : min((int64_t)(j + 1) * ratio, (int64_t)T);
+  for (int t = t0; t < T; ++t) {
+    if (selection) {
+      const int n = max(0, min(counts[kvh * T + t], topk));
+      const int32_t* sel = selection + (kvh * T + t) * topk;
+      bool mine = false;
+      for (int i = lane; i < n; i += 32) mine |= sel[i] == j;
+      if (!__any_sync(0xffffffffu, mine)) continue;
+    }
+    for (int hh = 0; hh < hr; ++hh) {
+      const int64_t row = ((int64_t)b * Hq + hk * hr + hh) * T + t;
+      const float* qr = q + row * D; const float* gr = dout + row * D;
       float qx[PER], gx[PER];
       float s = 0.0f, dp = 0.0f;
 #pragma unroll
       for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; qx[i] = c < D ? qr[c] : 0.0f; gx[i] = c < D ? gr[c] : 0.0f; s = fmaf(qx[i], kv[i], s); dp = fmaf(gx[i], vv[i], dp); }
       s = warp_sum(s); dp = warp_sum(dp);
-      const float p = __expf(s - lse[qi * T + t]);
-      const float ds = p * (dp - delta[qi * T + t]);
+      const float p = __expf(s - lse[row]);
+      const float ds = p * (dp - delta[row]);
 #pragma unroll
       for (int i = 0; i < PER; ++i) { av[i] = fmaf(p, gx[i], av[i]); ak[i] = fmaf(ds, qx[i], ak[i]); }
     }
@@ -186,27 +192,33 @@ __global__ void __launch_bounds__(256) compressed_attention_dkv_kernel(const flo
 #pragma unroll
   for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; if (c < D) { dkc[idx * D + c] += ak[i]; dvc[idx * D + c] += av[i]; } }
 }
-// delta[t] = sum_j p_j dp_j over the preceding blocks, for the rows that have no row correction
+// delta[t] = sum_j p_j dp_j over the keys of the row, for the rows that have no row correction
 template <int DP>
 __global__ void __launch_bounds__(256) compressed_attention_delta_kernel(const float* __restrict__ q, const float* __restrict__ kc, const float* __restrict__ vc,
                                                                          const float* __restrict__ dout, const float* __restrict__ lse, int B, int Hq, int Hkv, int T,
-                                                                         int D, int blocks, int ratio, float* __restrict__ delta) {
+                                                                         int D, int blocks, int ratio, float* __restrict__ delta,
+                                                                         const int32_t* __restrict__ selection, const int32_t* __restrict__ counts, int topk) {
   constexpr int PER = DP / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t idx = (int64_t)blockIdx.x * 8 + warp;
   if (idx >= (int64_t)B * Hq * T) return;
   const int t = (int)(idx % T); const int64_t bh = idx / T; const int h = (int)(bh % Hq); const int b = (int)(bh / Hq);
-  const int nk = min(t / ratio, blocks);
-  const int64_t kbase = ((int64_t)b * Hkv + h / (Hq / Hkv)) * blocks * D;
+  const int64_t kvh = (int64_t)b * Hkv + h / (Hq / Hkv);
+  const int32_t* sel = selection ? selection + (kvh * T + t) * topk : nullptr;
+  const int nk = selection ? max(0, min(counts[kvh * T + t], topk)) : min(t / ratio, blocks);
+  const int64_t kbase = kvh * blocks * D;
   float qv[PER], gv[PER];
 #pragma unroll
   for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; qv[i] = c < D ? q[idx * D + c] : 0.0f; gv[i] = c < D ? dout[idx * D + c] : 0.0f; }
   const float L = nk > 0 ? lse[idx] : 0.0f;
   float d = 0.0f;
   for (int j = 0; j < nk; ++j) {
+    const int blk = sel ? sel[j] : j;
+    if ((unsigned)blk >= (unsigned)blocks) continue;
+    const int64_t kr = kbase + (int64_t)blk * D;
     float s = 0.0f, dp = 0.0f;
 #pragma unroll
-    for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; if (c < D) { s = fmaf(qv[i], kc[kbase + (int64_t)j * D + c], s); dp = fmaf(gv[i], vc[kbase + (int64_t)j * D + c], dp); } }
+    for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; if (c < D) { s = fmaf(qv[i], kc[kr + c], s); dp = fmaf(gv[i], vc[kr + c], dp); } }
     s = warp_sum(s); dp = warp_sum(dp);
     d = fmaf(__expf(s - L), dp, d);
   }
@@ -294,17 +306,20 @@ int compressed_attention_launch(const float* q, const float* kc, const float* vc
 }
 
 int compressed_attention_backward_launch(const float* q, const float* kc, const float* vc, const float* dout, const float* lse, const float* rowcorr,
-                                         float* delta_scratch, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* dq, float* dkc, float* dvc, cudaStream_t s) {
+                                         float* delta_scratch, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* dq, float* dkc, float* dvc,
+                                         const int32_t* selection, const int32_t* counts, int topk, cudaStream_t s) {
   GN_REQUIRE(D > 0 && D <= 128, "compressed attention: head_dim %d outside (0,128]", D);
   GN_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && ratio >= 1, "compressed attention: %d query heads, %d kv heads, ratio %d", Hq, Hkv, ratio);
+  GN_REQUIRE(!selection || (counts && topk > 0), "compressed attention: a selection needs its counts and topk > 0");
   const int64_t nq = (int64_t)B * Hq * T, nkv = (int64_t)B * Hkv * blocks;
   if (nq <= 0 || nkv <= 0) return GN_OK;
   const unsigned gq = (unsigned)ceil_div(nq, 8), gk = (unsigned)ceil_div(nkv, 8);
   const float* delta = rowcorr;
 #define GN_CA_BWD(DPV) do { \
-    if (!delta) { compressed_attention_delta_kernel<DPV><<<gq, 256, 0, s>>>(q, kc, vc, dout, lse, B, Hq, Hkv, T, D, blocks, ratio, delta_scratch); delta = delta_scratch; } \
-    compressed_attention_dq_kernel<DPV><<<gq, 256, 0, s>>>(q, kc, vc, dout, lse, delta, B, Hq, Hkv, T, D, blocks, ratio, dq); \
-    compressed_attention_dkv_kernel<DPV><<<gk, 256, 0, s>>>(q, kc, vc, dout, lse, delta, B, Hq, Hkv, T, D, blocks, ratio, dkc, dvc); } while (0)
+    if (!delta) { compressed_attention_delta_kernel<DPV><<<gq, 256, 0, s>>>(q, kc, vc, dout, lse, B, Hq, Hkv, T, D, blocks, ratio, delta_scratch, selection, counts, topk); \
+                  delta = delta_scratch; } \
+    compressed_attention_dq_kernel<DPV><<<gq, 256, 0, s>>>(q, kc, vc, dout, lse, delta, B, Hq, Hkv, T, D, blocks, ratio, dq, selection, counts, topk); \
+    compressed_attention_dkv_kernel<DPV><<<gk, 256, 0, s>>>(q, kc, vc, dout, lse, delta, B, Hq, Hkv, T, D, blocks, ratio, dkc, dvc, selection, counts, topk); } while (0)
   if (D <= 32) GN_CA_BWD(32); else if (D <= 64) GN_CA_BWD(64); else GN_CA_BWD(128);
 #undef GN_CA_BWD
   GN_LAUNCH_CHECK();

@@ -70,9 +70,10 @@ int compressor_pool_backward_launch(const float* value, const float* probabiliti
 // selection == nullptr: every block before the query's own; else the token's selected blocks ([B * Hkv, T, topk] with counts [B * Hkv, T])
 int compressed_attention_launch(const float* q, const float* kc, const float* vc, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* out, float* lse,
                                 const int32_t* selection, const int32_t* counts, int topk, cudaStream_t s);
-// backward of the dense form: dq, dkc, dvc are accumulated into; rowcorr nullable (then delta_scratch [B * Hq * T] is used)
+// backward, dense (selection null) or over selected blocks: dq, dkc, dvc are accumulated into; rowcorr nullable (then delta_scratch [B * Hq * T] is used)
 int compressed_attention_backward_launch(const float* q, const float* kc, const float* vc, const float* dout, const float* lse, const float* rowcorr,
-                                         float* delta_scratch, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* dq, float* dkc, float* dvc, cudaStream_t s);
+                                         float* delta_scratch, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* dq, float* dkc, float* dvc,
+                                         const int32_t* selection, const int32_t* counts, int topk, cudaStream_t s);
 int attention_merge_launch(const float* oa, const float* la, const float* ob, const float* lb, int64_t rows, int D, float* out, float* lse, cudaStream_t s);
 int select_blocks_launch(const float* scores, int tokens, int blocks, int offset, int ratio, int topk, int32_t* selection, int32_t* counts, cudaStream_t s);
 // decode attention over the prompt shared by the rows of a group, head_dim 128, on mma.sync (attention_mma.cu): one

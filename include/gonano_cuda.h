@@ -123,9 +123,13 @@ int gn_compressed_attention_backward(const float* query, const float* key_c, con
                                      const float* row_correction, int batch, int n_head, int n_kv_head, int seq, int head_dim, int blocks, int ratio,
                                      float* dq, float* dkc, float* dvc);
 /* compressedAttentionForwardSparse (model/compress_attention.go:321-374): selection [batch * n_kv_head, seq, topk] block
- * indices, counts [batch * n_kv_head, seq]; block indices must lie in [0, blocks). */
+ * indices, counts [batch * n_kv_head, seq]; block indices lie in [0, blocks) (an entry outside is ignored). */
 int gn_compressed_attention_sparse_forward(const float* query, const float* key_c, const float* value_c, const int32_t* selection, const int32_t* counts,
                                            int batch, int n_head, int n_kv_head, int seq, int head_dim, int blocks, int topk, float* out, float* lse);
+/* compressedAttentionBackwardSparse (model/compress_attention.go:376-433): the same over each token's selected blocks. */
+int gn_compressed_attention_sparse_backward(const float* query, const float* key_c, const float* value_c, const float* out_grad, const float* lse,
+                                            const float* row_correction, const int32_t* selection, const int32_t* counts, int batch, int n_head, int n_kv_head,
+                                            int seq, int head_dim, int blocks, int topk, float* dq, float* dkc, float* dvc);
 int gn_attention_merge(const float* out_a, const float* lse_a, const float* out_b, const float* lse_b, int64_t rows, int head_dim, float* out,
                        float* lse);
 int gn_select_blocks(const float* scores, int tokens, int blocks, int position_offset, int ratio, int topk, int32_t* selection, int32_t* counts);

@@ -170,6 +170,35 @@ inline void compressed_attention_sparse_forward(const Backend& bk, const float* 
     }
 }
 
+// Backward of the selected-block form (model/compress_attention.go:376-433, no segment mask): per token the selected blocks are
+// gathered, the one-row backward runs on them, and the key / value gradients are scattered back; all three accumulate.
+inline void compressed_attention_sparse_backward(const Backend& bk, const float* q, const float* kc, const float* vc, const float* dout, const float* lse,
+                                                 const float* row_correction, const int32_t* selection, const int32_t* counts, int B, int Hq, int Hkv, int T,
+                                                 int D, int blocks, int topk, float* dq, float* dkc, float* dvc) {
+  const int hr = Hq / Hkv;
+  const size_t cap = (size_t)std::max(topk, 1) * D;
+  std::vector<float> ks(cap), vs(cap), gk(cap), gv(cap);
+  for (int b = 0; b < B; ++b)
+    for (int h = 0; h < Hq; ++h) {
+      const size_t qi = (size_t)b * Hq + h, kvh = (size_t)b * Hkv + h / hr;
+      const size_t kbase = kvh * blocks * D;
+      for (int t = 0; t < T; ++t) {
+        const int n = counts[kvh * T + t];
+        if (n <= 0) continue;
+        const int32_t* sel = selection + (kvh * T + t) * topk;
+        for (int i = 0; i < n; ++i) {
+          std::copy(kc + kbase + (size_t)sel[i] * D, kc + kbase + (size_t)(sel[i] + 1) * D, ks.begin() + (size_t)i * D);
+          std::copy(vc + kbase + (size_t)sel[i] * D, vc + kbase + (size_t)(sel[i] + 1) * D, vs.begin() + (size_t)i * D);
+        }
+        std::fill(gk.begin(), gk.begin() + (size_t)n * D, 0.0f); std::fill(gv.begin(), gv.begin() + (size_t)n * D, 0.0f);
+        bk.attention_backward(q + (qi * T + t) * D, ks.data(), vs.data(), dout + (qi * T + t) * D, lse + qi * T + t,
+                              row_correction ? row_correction + qi * T + t : nullptr, 1, n, D, n, -1, nullptr, 0, dq + (qi * T + t) * D, gk.data(), gv.data());
+        for (int i = 0; i < n; ++i)
+          for (int c = 0; c < D; ++c) { dkc[kbase + (size_t)sel[i] * D + c] += gk[(size_t)i * D + c]; dvc[kbase + (size_t)sel[i] * D + c] += gv[(size_t)i * D + c]; }
+      }
+    }
+}
+
 // Two normalised branches that share one softmax over the union of their keys: rows x D outputs and rows log-sum-exps.
 inline void merge_branches(const float* oa, const float* la, const float* ob, const float* lb, int64_t rows, int D, float* out, float* lse) {
   for (int64_t r = 0; r < rows; ++r) {

@@ -584,6 +584,11 @@ void or_compressed_attention_sparse_forward(int m, const float* q, const float* 
                                             int Hq, int Hkv, int T, int D, int blocks, int topk, float* out, float* lse) {
   BK(m); gnor::compressed_attention_sparse_forward(bk, q, kc, vc, selection, counts, B, Hq, Hkv, T, D, blocks, topk, out, lse);
 }
+void or_compressed_attention_sparse_backward(int m, const float* q, const float* kc, const float* vc, const float* dout, const float* lse, const float* rowcorr,
+                                             const int32_t* selection, const int32_t* counts, int B, int Hq, int Hkv, int T, int D, int blocks, int topk, float* dq,
+                                             float* dkc, float* dvc) {
+  BK(m); gnor::compressed_attention_sparse_backward(bk, q, kc, vc, dout, lse, rowcorr, selection, counts, B, Hq, Hkv, T, D, blocks, topk, dq, dkc, dvc);
+}
 void or_compressed_attention_backward(int m, const float* q, const float* kc, const float* vc, const float* dout, const float* lse, const float* rowcorr, int B,
                                       int Hq, int Hkv, int T, int D, int blocks, int ratio, float* dq, float* dkc, float* dvc) {
   BK(m); gnor::compressed_attention_backward(bk, q, kc, vc, dout, lse, rowcorr, B, Hq, Hkv, T, D, blocks, ratio, dq, dkc, dvc);

@@ -596,6 +596,17 @@ def compressed_attention_sparse_forward(q, kc, vc, selection, counts, mode=0):
     return out, lse
 
 
+def compressed_attention_sparse_backward(q, kc, vc, dout, lse, selection, counts, row_correction=None, mode=0):
+    """compressedAttentionBackwardSparse (model/compress_attention.go:376-433): returns dq, dkc, dvc (from zero)."""
+    q, kc, vc, dout, lse = f32(q), f32(kc), f32(vc), f32(dout), f32(lse); selection, counts = i32(selection), i32(counts)
+    B, Hq, T, D = q.shape; Hkv, blocks = kc.shape[1], kc.shape[2]; topk = selection.shape[-1]
+    rc = f32(row_correction) if row_correction is not None else None
+    dq = np.zeros_like(q); dk = np.zeros_like(kc); dv = np.zeros_like(vc)
+    lib().or_compressed_attention_sparse_backward(mode, _f(q), _f(kc), _f(vc), _f(dout), _f(lse), _f(rc) if rc is not None else None, _i(selection), _i(counts),
+                                                  B, Hq, Hkv, T, D, blocks, topk, _f(dq), _f(dk), _f(dv))
+    return dq, dk, dv
+
+
 def compressed_attention_backward(q, kc, vc, dout, lse, ratio, row_correction=None, mode=0):
     """compressedAttentionBackward (model/compress_attention.go:735-781): returns dq, dkc, dvc (from zero)."""
     q, kc, vc, dout, lse = f32(q), f32(kc), f32(vc), f32(dout), f32(lse)

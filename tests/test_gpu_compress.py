@@ -219,3 +219,95 @@ def test_compressed_attention_backward(oracle, bk, B, Hq, Hkv, T, D, ratio, corr
     acc = bk.compressed_attention_backward(q, kc, vc, dout, lse, ratio, rc, *seed)
     for a, s0, w in zip(acc, seed, want):
         close(a, s0 + w, 2e-4, 2e-5)
+
+
+# compressedAttentionBackwardSparse (model/compress_attention.go:376-433)
+@pytest.mark.parametrize("B,Hq,Hkv,T,D,ratio,topk,corr", [(2, 4, 2, 37, 64, 4, 3, False), (1, 6, 2, 130, 128, 4, 8, True), (1, 2, 2, 21, 32, 2, 40, False)])
+def test_compressed_attention_sparse_backward(oracle, bk, B, Hq, Hkv, T, D, ratio, topk, corr):
+    rng = np.random.default_rng(T + topk)
+    blocks = (T + ratio - 1) // ratio
+    q = (rng.standard_normal((B, Hq, T, D)) * 0.4).astype(np.float32)
+    kc = (rng.standard_normal((B, Hkv, blocks, D)) * 0.4).astype(np.float32); vc = rng.standard_normal((B, Hkv, blocks, D)).astype(np.float32)
+    dout = rng.standard_normal((B, Hq, T, D)).astype(np.float32)
+    sel = np.zeros((B * Hkv, T, topk), np.int32); cnt = np.zeros((B * Hkv, T), np.int32)
+    for i in range(B * Hkv):
+        sel[i], cnt[i] = oracle.select_blocks(np.round(rng.standard_normal((T, blocks)) * 3).astype(np.float32), 0, ratio, topk)
+    sel = np.maximum(sel, 0)
+    _, lse = oracle.compressed_attention_sparse_forward(q, kc, vc, sel, cnt)
+    rc = rng.standard_normal((B, Hq, T)).astype(np.float32) if corr else None
+    if corr:
+        lse = (lse + np.abs(rng.standard_normal(lse.shape)).astype(np.float32)).astype(np.float32)
+    want = oracle.compressed_attention_sparse_backward(q, kc, vc, dout, lse, sel, cnt, rc)
+    got = bk.compressed_attention_sparse_backward(q, kc, vc, dout, lse, sel, cnt, rc)
+    for g, w in zip(got, want):
+        close(g, w, 2e-4, 2e-5)
+    # every allowed block selected: the dense backward
+    full = np.zeros((B * Hkv, T, blocks), np.int32); fc = np.zeros((B * Hkv, T), np.int32)
+    for t in range(T):
+        fc[:, t] = min(t // ratio, blocks); full[:, t, :fc[0, t]] = np.arange(fc[0, t])
+    _, dl = oracle.compressed_attention_forward(q, kc, vc, ratio)
+    dense = bk.compressed_attention_backward(q, kc, vc, dout, dl, ratio)
+    sparse = bk.compressed_attention_sparse_backward(q, kc, vc, dout, dl, full, fc)
+    for a, b_ in zip(sparse, dense):
+        close(a, b_, 1e-5, 1e-6)
+
+
+def _hca_layer(ops, x, q, k, v, wk, bias, ratio, window, dout=None):
+    """Forward (and, with dout, backward) of one heavily-compressed attention layer from the blocks: compressor per kv head,
+    compressed global branch, sliding-window local branch, merge; the backward hands both branches the merged log-sum-exp
+    and the merged row correction dO . O (model/train.go:211-226, 289-301)."""
+    comp, comp_bwd, catt, catt_bwd, merge, attn, attn_bwd = ops
+    B, Hq, T, D = q.shape; Hkv = k.shape[1]; hr = Hq // Hkv
+    blocks = (T + ratio - 1) // ratio
+    kc = np.zeros((B, Hkv, blocks, D), np.float32); vc = np.zeros_like(kc)
+    for b in range(B):
+        for h in range(Hkv):
+            kc[b, h] = comp(x[b:b + 1], k[b, h][None], wk, bias, ratio)[0][0]
+            vc[b, h] = comp(x[b:b + 1], v[b, h][None], wk, bias, ratio)[0][0]
+    og, lg = catt(q, kc, vc, ratio)
+    ol = np.zeros_like(q); ll = np.zeros((B, Hq, T), np.float32)
+    for b in range(B):
+        for h in range(Hq):
+            o, l = attn(q[b, h], k[b, h // hr], v[b, h // hr], T, T, D, 0, window)
+            ol[b, h] = np.asarray(o).reshape(T, D); ll[b, h] = np.asarray(l).reshape(T)
+    out, lse = merge(og.reshape(-1, D), lg.reshape(-1), ol.reshape(-1, D), ll.reshape(-1))
+    out = np.asarray(out).reshape(B, Hq, T, D); lse = np.asarray(lse).reshape(B, Hq, T)
+    if dout is None:
+        return out, lse
+    rc = np.sum(dout.astype(np.float64) * out.astype(np.float64), axis=-1).astype(np.float32)
+    dq, dkc, dvc = catt_bwd(q, kc, vc, dout, lse, ratio, rc)
+    dk = np.zeros_like(k); dv = np.zeros_like(v)
+    for b in range(B):
+        for h in range(Hq):
+            g = attn_bwd(q[b, h], k[b, h // hr], v[b, h // hr], out[b, h], dout[b, h], lse[b, h], T, T, D, 0, window, row_correction=rc[b, h],
+                         dq=dq[b, h].ravel(), dk=dk[b, h // hr].ravel(), dv=dv[b, h // hr].ravel())
+            dq[b, h] = g[0].reshape(T, D); dk[b, h // hr] = g[1].reshape(T, D); dv[b, h // hr] = g[2].reshape(T, D)
+    dx = np.zeros_like(x); dw = np.zeros_like(wk); db = np.zeros_like(bias)
+    for b in range(B):
+        for h in range(Hkv):
+            for val, gc, gval in ((k, dkc, dk), (v, dvc, dv)):
+                gh, gv_, gw, gb = comp_bwd(x[b:b + 1], val[b, h][None], wk, bias, ratio, gc[b, h][None])
+                dx[b] += gh[0]; gval[b, h] += gv_[0]; dw += gw; db += gb
+    return out, (dq, dk, dv, dx, dw, db)
+
+
+def test_heavily_compressed_layer_backward(oracle, bk):
+    rng = np.random.default_rng(12)
+    B, Hq, Hkv, T, D, d, ratio, window = 2, 4, 2, 45, 64, 48, 4, 6
+    x = rng.standard_normal((B, T, d)).astype(np.float32)
+    q = (rng.standard_normal((B, Hq, T, D)) * 0.4).astype(np.float32)
+    k = (rng.standard_normal((B, Hkv, T, D)) * 0.4).astype(np.float32); v = rng.standard_normal((B, Hkv, T, D)).astype(np.float32)
+    wk = (rng.standard_normal((D, d)) * 0.2).astype(np.float32); bias = (rng.standard_normal((ratio, D)) * 0.3).astype(np.float32)
+    dout = rng.standard_normal((B, Hq, T, D)).astype(np.float32)
+    ref = oracle.Backend(0)
+
+    def ref_attn_bwd(q_, k_, v_, out_, dout_, lse_, ql, kl, hd, off, win, row_correction=None, dq=None, dk=None, dv=None):
+        return ref.attention_backward(q_, k_, v_, dout_, lse_, ql, kl, hd, off, win, row_correction=row_correction, dq=dq, dk=dk, dv=dv)
+
+    want_o, want = _hca_layer((oracle.compressor_forward, oracle.compressor_backward, oracle.compressed_attention_forward, oracle.compressed_attention_backward,
+                               oracle.merge_branches, ref.attention_forward, ref_attn_bwd), x, q, k, v, wk, bias, ratio, window, dout)
+    got_o, got = _hca_layer((bk.compressor_forward, bk.compressor_backward, bk.compressed_attention_forward, bk.compressed_attention_backward,
+                             bk.attention_merge, bk.attention_forward, bk.attention_backward), x, q, k, v, wk, bias, ratio, window, dout)
+    close(got_o, want_o, 1e-4, 1e-5)
+    for g, w in zip(got, want):
+        close(g, w, 3e-4, 3e-5)

@@ -315,3 +315,59 @@ def test_compressed_attention_gradient_matches_finite_difference(oracle):
     eps = 1e-3
     numeric = (loss(eps) - loss(-eps)) / (2 * eps)
     assert abs(analytic - numeric) <= 2e-3 * max(1.0, abs(numeric)), (analytic, numeric)
+
+
+# compressedAttentionBackwardSparse (model/compress_attention.go:376-433) against a central difference of its forward
+def test_sparse_attention_gradient_matches_finite_difference(oracle):
+    rng = np.random.default_rng(13)
+    B, Hq, Hkv, T, D, ratio, topk = 1, 4, 2, 13, 6, 2, 3
+    blocks = (T + ratio - 1) // ratio
+    q = (rng.standard_normal((B, Hq, T, D)) * 0.5).astype(np.float32)
+    kc = (rng.standard_normal((B, Hkv, blocks, D)) * 0.5).astype(np.float32); vc = rng.standard_normal((B, Hkv, blocks, D)).astype(np.float32)
+    dout = rng.standard_normal((B, Hq, T, D)).astype(np.float32)
+    sel = np.zeros((B * Hkv, T, topk), np.int32); cnt = np.zeros((B * Hkv, T), np.int32)
+    for i in range(B * Hkv):
+        sel[i], cnt[i] = oracle.select_blocks(rng.standard_normal((T, blocks)).astype(np.float32), 0, ratio, topk)
+    sel = np.maximum(sel, 0)
+    _, lse = oracle.compressed_attention_sparse_forward(q, kc, vc, sel, cnt)
+    grads = oracle.compressed_attention_sparse_backward(q, kc, vc, dout, lse, sel, cnt)
+    dirs = [rng.standard_normal(x.shape).astype(np.float32) for x in (q, kc, vc)]
+    analytic = sum(float(np.sum(g.astype(np.float64) * dr)) for g, dr in zip(grads, dirs))
+    def loss(eps):
+        out, _ = oracle.compressed_attention_sparse_forward(q + eps * dirs[0], kc + eps * dirs[1], vc + eps * dirs[2], sel, cnt)
+        return float(np.sum(out.astype(np.float64) * dout))
+    eps = 1e-3
+    numeric = (loss(eps) - loss(-eps)) / (2 * eps)
+    assert abs(analytic - numeric) <= 2e-3 * max(1.0, abs(numeric)), (analytic, numeric)
+
+
+# One heavily-compressed attention layer assembled from the blocks: both branches are differentiated with the merged
+# log-sum-exp and the merged row correction dO . O (model/train.go:211-226, 289-301); the assembled gradient must be the
+# gradient of the assembled forward.
+def test_heavily_compressed_layer_gradient_matches_finite_difference(oracle):
+    from test_gpu_compress import _hca_layer
+    rng = np.random.default_rng(17)
+    B, Hq, Hkv, T, D, d, ratio, window = 1, 2, 1, 11, 4, 5, 3, 4
+    x = rng.standard_normal((B, T, d)).astype(np.float32)
+    q = (rng.standard_normal((B, Hq, T, D)) * 0.5).astype(np.float32)
+    k = (rng.standard_normal((B, Hkv, T, D)) * 0.5).astype(np.float32); v = rng.standard_normal((B, Hkv, T, D)).astype(np.float32)
+    wk = (rng.standard_normal((D, d)) * 0.3).astype(np.float32); bias = (rng.standard_normal((ratio, D)) * 0.3).astype(np.float32)
+    dout = rng.standard_normal((B, Hq, T, D)).astype(np.float32)
+    ref = oracle.Backend(0)
+
+    def attn_bwd(q_, k_, v_, out_, dout_, lse_, ql, kl, hd, off, win, row_correction=None, dq=None, dk=None, dv=None):
+        return ref.attention_backward(q_, k_, v_, dout_, lse_, ql, kl, hd, off, win, row_correction=row_correction, dq=dq, dk=dk, dv=dv)
+
+    ops = (oracle.compressor_forward, oracle.compressor_backward, oracle.compressed_attention_forward, oracle.compressed_attention_backward,
+           oracle.merge_branches, ref.attention_forward, attn_bwd)
+    _, grads = _hca_layer(ops, x, q, k, v, wk, bias, ratio, window, dout)
+    args = (q, k, v, x, wk, bias)
+    dirs = [rng.standard_normal(a.shape).astype(np.float32) for a in args]
+    analytic = sum(float(np.sum(g.astype(np.float64) * dr)) for g, dr in zip(grads, dirs))
+    def loss(eps):
+        q2, k2, v2, x2, w2, b2 = [a + np.float32(eps) * dr for a, dr in zip(args, dirs)]
+        out, _ = _hca_layer(ops, x2, q2, k2, v2, w2, b2, ratio, window)
+        return float(np.sum(out.astype(np.float64) * dout))
+    eps = 1e-3
+    numeric = (loss(eps) - loss(-eps)) / (2 * eps)
+    assert abs(analytic - numeric) <= 3e-3 * max(1.0, abs(numeric)), (analytic, numeric)
