@@ -68,6 +68,10 @@ SIGNATURES = {
     "gn_compressor_backward": (I, [vp, vp, vp, vp, vp, vp, I, I, I, I, I, vp, vp, vp, vp]),
     "gn_compressed_attention_forward": (I, [vp, vp, vp, I, I, I, I, I, I, I, vp, vp]),
     "gn_compressed_attention_backward": (I, [vp, vp, vp, vp, vp, vp, I, I, I, I, I, I, I, vp, vp, vp]),
+    "gn_indexer_scores_backward": (I, [vp, vp, vp, vp, I, I, I, I, vp, vp, vp]),
+    "gn_hierarchical_cap": (I, [I, I]),
+    "gn_select_blocks_hierarchical": (I, [vp, I, I, I, I, I, I, I, vp, vp, vp, vp]),
+    "gn_select_blocks_within_pool": (I, [vp, I, I, I, I, I, vp, vp, I, vp, vp]),
     "gn_compressed_attention_sparse_backward": (I, [vp, vp, vp, vp, vp, vp, vp, vp, I, I, I, I, I, I, I, vp, vp, vp]),
     "gn_compressed_attention_sparse_forward": (I, [vp, vp, vp, vp, vp, I, I, I, I, I, I, I, vp, vp]),
     "gn_attention_merge": (I, [vp, vp, vp, vp, C.c_int64, I, vp, vp]), "gn_select_blocks": (I, [vp, I, I, I, I, I, vp, vp]),

@@ -102,6 +102,14 @@ class CudaBackend:
         query, key, weight = _f32(query), _f32(key), _f32(weight); dst = np.empty(rows * blocks, np.float32)
         check(self.lib.gn_indexer_scores(ptr(dst), ptr(query), ptr(key), ptr(weight), rows, blocks, heads, dim)); return dst
 
+    def indexer_scores_backward(self, grad_scores, query, key, weight, grad_weight=None):
+        """Score part of SparseIndexer.Backward (model/indexer.go:107-151): grad_query, grad_key (fresh), grad_weight (accumulated)."""
+        gs, q, k, w = _f32(grad_scores), _f32(query), _f32(key), _f32(weight)
+        rows, heads, dim = q.shape; blocks = k.shape[0]
+        gq = np.zeros_like(q); gk = np.zeros_like(k); gw = np.zeros(heads, np.float32) if grad_weight is None else _f32(grad_weight).copy()
+        check(self.lib.gn_indexer_scores_backward(ptr(gs), ptr(q), ptr(k), ptr(w), rows, blocks, heads, dim, ptr(gq), ptr(gk), ptr(gw)))
+        return gq, gk, gw
+
     def indexer_block_max(self, scores, rows, blocks, group_size):
         scores = _f32(scores); g = max(group_size, 1)
         dst = np.empty(rows * ((blocks + g - 1) // g), np.float32)
@@ -179,6 +187,24 @@ class CudaBackend:
         scores = _f32(scores); tokens, blocks = scores.shape
         sel = np.full((tokens, max(topk, 0)), -1, np.int32); cnt = np.zeros(tokens, np.int32)
         check(self.lib.gn_select_blocks(ptr(scores), tokens, blocks, offset, ratio, topk, ptr(sel) if topk > 0 else None, ptr(cnt)))
+        return sel, cnt
+
+    def select_blocks_hierarchical(self, scores, offset, ratio, topk, pool, budget):
+        """selectRowBlockMax per token (model/indexer.go:442-513): selection, counts, candidates [tokens, cap] (-1 padded), candidate counts."""
+        scores = _f32(scores); tokens, blocks = scores.shape
+        cap = self.lib.gn_hierarchical_cap(pool, budget)
+        sel = np.full((tokens, topk), -1, np.int32); cnt = np.zeros(tokens, np.int32)
+        cand = np.full((tokens, cap), -1, np.int32); ccnt = np.zeros(tokens, np.int32)
+        check(self.lib.gn_select_blocks_hierarchical(ptr(scores), tokens, blocks, offset, ratio, topk, pool, budget, ptr(sel), ptr(cnt), ptr(cand), ptr(ccnt)))
+        return sel, cnt, cand, ccnt
+
+    def select_blocks_within_pool(self, scores, offset, ratio, topk, candidates, candidate_counts):
+        """selectWithinPool over a score matrix (model/indexer.go:547-613)."""
+        scores = _f32(scores); tokens, blocks = scores.shape
+        candidates, candidate_counts = _i32(candidates), _i32(candidate_counts)
+        sel = np.full((tokens, topk), -1, np.int32); cnt = np.zeros(tokens, np.int32)
+        check(self.lib.gn_select_blocks_within_pool(ptr(scores), tokens, blocks, offset, ratio, topk, ptr(candidates), ptr(candidate_counts), candidates.shape[1],
+                                                    ptr(sel), ptr(cnt)))
         return sel, cnt
 
     # ------------------------------------------------------------------ MoE

@@ -435,6 +435,53 @@ int gn_select_blocks(const float* scores, int tokens, int blocks, int position_o
   GN_TRY(select_blocks_launch(ds, tokens, blocks, position_offset, ratio, topk, dsel, dc, s));
   GN_END();
 }
+// the score part of SparseIndexer.Backward (model/indexer.go:107-151) for one key set
+int gn_indexer_scores_backward(const float* grad_scores, const float* query, const float* key, const float* weight, int rows, int blocks, int heads, int dim,
+                               float* grad_query, float* grad_key, float* grad_weight) {
+  if (rows <= 0 || blocks <= 0 || heads <= 0) return GN_OK;
+  GN_REQUIRE(grad_scores && query && key && weight && grad_query && grad_key && grad_weight && dim >= 1, "indexer_scores_backward: bad argument");
+  GN_BEGIN();
+  const float* pg = st.in(grad_scores, (size_t)rows * blocks); const float* pq = st.in(query, (size_t)rows * heads * dim);
+  const float* pk = st.in(key, (size_t)blocks * heads * dim); const float* pw = st.in(weight, (size_t)heads);
+  float* gq = st.out(grad_query, (size_t)rows * heads * dim); float* gk = st.out(grad_key, (size_t)blocks * heads * dim);
+  float* gw = st.out(grad_weight, (size_t)heads, true);
+  float* wpart = st.temp<float>((size_t)rows * heads);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(indexer_scores_backward_launch(pg, pq, pk, pw, rows, blocks, heads, dim, gq, gk, gw, wpart, s));
+  GN_END();
+}
+// selectFromScoreMatrix / selectRowBlockMax (model/indexer.go:358-381, 442-513)
+int gn_hierarchical_cap(int pool, int candidate_budget) { pool = pool < 1 ? 1 : pool; const int g = (candidate_budget + pool - 1) / pool; return (g < 1 ? 1 : g) * pool; }
+int gn_select_blocks_hierarchical(const float* scores, int tokens, int blocks, int position_offset, int ratio, int topk, int pool, int candidate_budget,
+                                  int32_t* selection, int32_t* counts, int32_t* candidates, int32_t* candidate_counts) {
+  if (tokens <= 0) return GN_OK;
+  GN_REQUIRE(scores && counts && blocks > 0 && ratio >= 1 && topk >= 1 && selection && (!candidates || candidate_counts), "select_blocks_hierarchical: bad argument");
+  pool = pool < 1 ? 1 : pool;
+  const int cap = gn_hierarchical_cap(pool, candidate_budget);
+  GN_BEGIN();
+  const float* ds = st.in(scores, (size_t)tokens * blocks);
+  int32_t* dsel = st.out(selection, (size_t)tokens * topk); int32_t* dc = st.out(counts, (size_t)tokens);
+  int32_t* dcand = candidates ? st.out(candidates, (size_t)tokens * cap) : st.temp<int32_t>((size_t)tokens * cap);
+  int32_t* dcc = candidates ? st.out(candidate_counts, (size_t)tokens) : st.temp<int32_t>((size_t)tokens);
+  float* gmax = st.temp<float>((size_t)tokens * ((blocks + pool - 1) / pool));
+  int32_t* chosen = st.temp<int32_t>((size_t)tokens * (cap / pool));
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(select_hierarchical_launch(ds, tokens, blocks, position_offset, ratio, topk, pool, candidate_budget, gmax, chosen, dsel, dc, dcand, dcc, s));
+  GN_END();
+}
+// selectWithinPool over a score matrix (model/indexer.go:547-613)
+int gn_select_blocks_within_pool(const float* scores, int tokens, int blocks, int position_offset, int ratio, int topk, const int32_t* candidates,
+                                 const int32_t* candidate_counts, int cap, int32_t* selection, int32_t* counts) {
+  if (tokens <= 0) return GN_OK;
+  GN_REQUIRE(scores && counts && blocks > 0 && ratio >= 1 && topk >= 1 && selection && candidates && candidate_counts && cap >= 1, "select_blocks_within_pool: bad argument");
+  GN_BEGIN();
+  const float* ds = st.in(scores, (size_t)tokens * blocks);
+  const int32_t* dcand = st.in(candidates, (size_t)tokens * cap); const int32_t* dcc = st.in(candidate_counts, (size_t)tokens);
+  int32_t* dsel = st.out(selection, (size_t)tokens * topk); int32_t* dc = st.out(counts, (size_t)tokens);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(select_within_pool_launch(ds, tokens, blocks, position_offset, ratio, topk, dcand, dcc, cap, dsel, dc, s));
+  GN_END();
+}
 
 int gn_topk_indices(int32_t* dst, const float* scores, int rows, int count, int k) {
   if (rows <= 0 || count <= 0 || k <= 0) return GN_OK;

@@ -267,6 +267,165 @@ __global__ void __launch_bounds__(256) select_blocks_kernel(const float* __restr
   }
 }
 
+// Score part of SparseIndexer.Backward (model/indexer.go:107-151), no atomics.  gate = dot(q[row, h], k[block, h]) > 0.
+// grad_query: one warp per (row, head) over the blocks; it also leaves sum_b g * dot in wpart [rows, heads].
+__global__ void __launch_bounds__(256) indexer_bwd_query_kernel(const float* __restrict__ gs, const float* __restrict__ q, const float* __restrict__ key,
+                                                                const float* __restrict__ w, int rows, int blocks, int heads, int dim,
+                                                                float* __restrict__ gq, float* __restrict__ wpart) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t idx = (int64_t)blockIdx.x * 8 + warp;
+  if (idx >= (int64_t)rows * heads) return;
+  const int h = (int)(idx % heads); const int64_t row = idx / heads;
+  float qv[4], acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const int c = lane + 32 * i; qv[i] = c < dim ? q[idx * dim + c] : 0.0f; }
+  const float wh = w[h];
+  float wsum = 0.0f;
+  for (int b = 0; b < blocks; ++b) {
+    const float* kr = key + ((int64_t)b * heads + h) * dim;
+    float kv[4], d = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const int c = lane + 32 * i; kv[i] = c < dim ? kr[c] : 0.0f; d = fmaf(qv[i], kv[i], d); }
+    d = warp_sum(d);
+    if (d <= 0.0f) continue;
+    const float g = gs[row * blocks + b];
+    wsum = fmaf(g, d, wsum);
+    const float wg = g * wh;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] = fmaf(wg, kv[i], acc[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const int c = lane + 32 * i; if (c < dim) gq[idx * dim + c] = acc[i]; }
+  if (lane == 0) wpart[idx] = wsum;
+}
+// grad_key: one warp per (block, head) over the rows
+__global__ void __launch_bounds__(256) indexer_bwd_key_kernel(const float* __restrict__ gs, const float* __restrict__ q, const float* __restrict__ key,
+                                                              const float* __restrict__ w, int rows, int blocks, int heads, int dim, float* __restrict__ gk) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t idx = (int64_t)blockIdx.x * 8 + warp;
+  if (idx >= (int64_t)blocks * heads) return;
+  const int h = (int)(idx % heads); const int64_t b = idx / heads;
+  float kv[4], acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const int c = lane + 32 * i; kv[i] = c < dim ? key[idx * dim + c] : 0.0f; }
+  const float wh = w[h];
+  for (int r = 0; r < rows; ++r) {
+    const float* qr = q + ((int64_t)r * heads + h) * dim;
+    float qv[4], d = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const int c = lane + 32 * i; qv[i] = c < dim ? qr[c] : 0.0f; d = fmaf(qv[i], kv[i], d); }
+    d = warp_sum(d);
+    if (d <= 0.0f) continue;
+    const float wg = gs[(int64_t)r * blocks + b] * wh;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] = fmaf(wg, qv[i], acc[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const int c = lane + 32 * i; if (c < dim) gk[idx * dim + c] = acc[i]; }
+}
+// grad_weight[h] += sum over rows of wpart[row, h]: one CTA per head, fixed order
+__global__ void __launch_bounds__(256) indexer_bwd_weight_kernel(const float* __restrict__ wpart, int rows, int heads, float* __restrict__ gw) {
+  __shared__ double part[256];
+  const int h = blockIdx.x;
+  double a = 0.0;
+  for (int r = threadIdx.x; r < rows; r += 256) a += (double)wpart[(int64_t)r * heads + h];
+  part[threadIdx.x] = a;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) { if ((int)threadIdx.x < o) part[threadIdx.x] += part[threadIdx.x + o]; __syncthreads(); }
+  if (threadIdx.x == 0) gw[h] += (float)part[0];
+}
+
+// One warp per token, the two-level selection (model/indexer.go:442-513).  gmax [tokens, ceil(blocks / pool)] and chosen
+// [tokens, per_token] are scratch.  Ranks are counted exactly as in select_blocks_kernel: super-blocks by their maximum over
+// the allowed entries, then the candidate entries (super-blocks in rank order, entries ascending inside) by score with ties
+// toward the earlier candidate.
+__global__ void __launch_bounds__(256) select_hierarchical_kernel(const float* __restrict__ scores, int tokens, int blocks, int offset, int ratio, int topk,
+                                                                  int pool, int per_token, float* __restrict__ gmax, int32_t* __restrict__ chosen,
+                                                                  int32_t* __restrict__ selection, int32_t* __restrict__ counts,
+                                                                  int32_t* __restrict__ candidates, int32_t* __restrict__ candidate_counts) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 8 + warp;
+  if (t >= tokens) return;
+  const int cap = per_token * pool, all_groups = (blocks + pool - 1) / pool;
+  const int allowed = topk > 0 ? min((offset + t) / ratio, blocks) : 0;
+  int32_t* sel = selection + (int64_t)t * topk;
+  int32_t* cand = candidates + (int64_t)t * cap;
+  for (int i = lane; i < topk; i += 32) sel[i] = -1;
+  for (int i = lane; i < cap; i += 32) cand[i] = -1;
+  if (allowed <= 0) { if (lane == 0) { counts[t] = 0; candidate_counts[t] = 0; } return; }
+  const float* v = scores + (int64_t)t * blocks;
+  float* gm = gmax + (int64_t)t * all_groups;
+  int32_t* ch = chosen + (int64_t)t * per_token;
+  const int groups = (allowed + pool - 1) / pool, nch = min(per_token, groups);
+  for (int g = lane; g < groups; g += 32) {
+    float m = -INFINITY;
+    for (int e = g * pool; e < min((g + 1) * pool, allowed); ++e) m = fmaxf(m, v[e]);
+    gm[g] = m;
+  }
+  __syncwarp();
+  for (int g = lane; g < groups; g += 32) {
+    const float vi = gm[g];
+    int rank = 0;
+    for (int j = 0; j < groups; ++j) { const float vj = gm[j]; rank += (vj > vi || (vj == vi && j < g)) ? 1 : 0; }
+    if (rank < nch) ch[rank] = g;
+  }
+  __syncwarp();
+  // only the last allowed super-block can be short: find its rank among the chosen, if it is one of them
+  const int tail = allowed - (groups - 1) * pool;          // entries of the last allowed super-block, 1..pool
+  int short_rank = nch;
+  if (tail < pool) { for (int r = 0; r < nch; ++r) if (ch[r] == groups - 1) short_rank = r; }
+  const int ncand = nch * pool - (short_rank < nch ? pool - tail : 0);
+  for (int c = lane; c < ncand; c += 32) {
+    int r, e;
+    if (c < short_rank * pool) { r = c / pool; e = c % pool; }
+    else if (short_rank < nch && c < short_rank * pool + tail) { r = short_rank; e = c - short_rank * pool; }
+    else { const int c2 = c - short_rank * pool - tail; r = short_rank + 1 + c2 / pool; e = c2 % pool; }
+    cand[c] = ch[r] * pool + e;
+  }
+  __syncwarp();
+  const int count = min(topk, ncand);
+  if (lane == 0) { counts[t] = count; candidate_counts[t] = ncand; }
+  for (int c = lane; c < ncand; c += 32) {
+    const float vi = v[cand[c]];
+    int rank = 0;
+    for (int j = 0; j < ncand; ++j) { const float vj = v[cand[j]]; rank += (vj > vi || (vj == vi && j < c)) ? 1 : 0; }
+    if (rank < count) sel[rank] = cand[c];
+  }
+}
+// One warp per token: the top-k of a given candidate list (model/indexer.go:547-613); candidates outside [0, allowed) are dropped
+__global__ void __launch_bounds__(256) select_within_pool_kernel(const float* __restrict__ scores, int tokens, int blocks, int offset, int ratio, int topk,
+                                                                 const int32_t* __restrict__ candidates, const int32_t* __restrict__ candidate_counts, int cap,
+                                                                 int32_t* __restrict__ selection, int32_t* __restrict__ counts) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 8 + warp;
+  if (t >= tokens) return;
+  const int allowed = min((offset + t) / ratio, blocks);
+  int32_t* sel = selection + (int64_t)t * topk;
+  const int32_t* cand = candidates + (int64_t)t * cap;
+  for (int i = lane; i < topk; i += 32) sel[i] = -1;
+  const int n = topk > 0 ? max(0, min(candidate_counts[t], cap)) : 0;
+  int kept = 0;
+  for (int i = lane; i < n; i += 32) kept += (cand[i] >= 0 && cand[i] < allowed) ? 1 : 0;
+  kept = (int)warp_sum((float)kept);                       // at most cap entries: exact in float below 2^24
+  const int count = min(topk, kept);
+  if (lane == 0) counts[t] = count;
+  __syncwarp();
+  const float* v = scores + (int64_t)t * blocks;
+  for (int c = lane; c < n; c += 32) {
+    const int e = cand[c];
+    if (e < 0 || e >= allowed) continue;
+    const float vi = v[e];
+    int rank = 0;
+    for (int j = 0; j < n; ++j) {
+      const int ej = cand[j];
+      if (ej < 0 || ej >= allowed) continue;
+      const float vj = v[ej];
+      rank += (vj > vi || (vj == vi && j < c)) ? 1 : 0;
+    }
+    if (rank < count) sel[rank] = e;
+  }
+}
+
 }  // namespace
 
 int compressor_pool_launch(const float* logits, const float* bias, const float* value, int B, int T, int C, int ratio, float* compressed, float* probabilities,
@@ -336,6 +495,37 @@ int attention_merge_launch(const float* oa, const float* la, const float* ob, co
 int select_blocks_launch(const float* scores, int tokens, int blocks, int offset, int ratio, int topk, int32_t* selection, int32_t* counts, cudaStream_t s) {
   if (tokens <= 0) return GN_OK;
   select_blocks_kernel<<<(unsigned)ceil_div(tokens, 8), 256, 0, s>>>(scores, tokens, blocks, offset, ratio, topk, selection, counts);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+int indexer_scores_backward_launch(const float* gs, const float* q, const float* key, const float* w, int rows, int blocks, int heads, int dim, float* gq, float* gk,
+                                   float* gw, float* wpart, cudaStream_t s) {
+  if (rows <= 0 || blocks <= 0 || heads <= 0) return GN_OK;
+  GN_REQUIRE(dim >= 1 && dim <= 128, "indexer backward: dim %d outside [1,128]", dim);
+  indexer_bwd_query_kernel<<<(unsigned)ceil_div((int64_t)rows * heads, 8), 256, 0, s>>>(gs, q, key, w, rows, blocks, heads, dim, gq, wpart);
+  indexer_bwd_key_kernel<<<(unsigned)ceil_div((int64_t)blocks * heads, 8), 256, 0, s>>>(gs, q, key, w, rows, blocks, heads, dim, gk);
+  indexer_bwd_weight_kernel<<<heads, 256, 0, s>>>(wpart, rows, heads, gw);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+int select_hierarchical_launch(const float* scores, int tokens, int blocks, int offset, int ratio, int topk, int pool, int budget, float* gmax, int32_t* chosen,
+                               int32_t* selection, int32_t* counts, int32_t* candidates, int32_t* candidate_counts, cudaStream_t s) {
+  if (tokens <= 0) return GN_OK;
+  GN_REQUIRE(ratio >= 1 && pool >= 1 && blocks >= 0 && topk >= 0, "select_blocks_hierarchical: ratio %d, pool %d, blocks %d, topk %d", ratio, pool, blocks, topk);
+  const int per_token = max(1, (budget + pool - 1) / pool);
+  select_hierarchical_kernel<<<(unsigned)ceil_div(tokens, 8), 256, 0, s>>>(scores, tokens, blocks, offset, ratio, topk, pool, per_token, gmax, chosen, selection, counts,
+                                                                           candidates, candidate_counts);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+int select_within_pool_launch(const float* scores, int tokens, int blocks, int offset, int ratio, int topk, const int32_t* candidates,
+                              const int32_t* candidate_counts, int cap, int32_t* selection, int32_t* counts, cudaStream_t s) {
+  if (tokens <= 0) return GN_OK;
+  GN_REQUIRE(ratio >= 1 && cap >= 1 && topk >= 0, "select_blocks_within_pool: ratio %d, cap %d, topk %d", ratio, cap, topk);
+  select_within_pool_kernel<<<(unsigned)ceil_div(tokens, 8), 256, 0, s>>>(scores, tokens, blocks, offset, ratio, topk, candidates, candidate_counts, cap, selection, counts);
   GN_LAUNCH_CHECK();
   return GN_OK;
 }

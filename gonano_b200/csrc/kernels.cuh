@@ -75,6 +75,14 @@ int compressed_attention_backward_launch(const float* q, const float* kc, const 
                                          float* delta_scratch, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* dq, float* dkc, float* dvc,
                                          const int32_t* selection, const int32_t* counts, int topk, cudaStream_t s);
 int attention_merge_launch(const float* oa, const float* la, const float* ob, const float* lb, int64_t rows, int D, float* out, float* lse, cudaStream_t s);
+// score part of the indexer's backward: gq [rows, heads, dim], gk [blocks, heads, dim] overwritten, gw [heads] accumulated; wpart [rows, heads] scratch
+int indexer_scores_backward_launch(const float* gs, const float* q, const float* key, const float* w, int rows, int blocks, int heads, int dim, float* gq, float* gk,
+                                   float* gw, float* wpart, cudaStream_t s);
+// two-level selection: gmax [tokens, ceil(blocks / pool)] and chosen [tokens, max(1, ceil(budget / pool))] are scratch; candidates [tokens, that * pool]
+int select_hierarchical_launch(const float* scores, int tokens, int blocks, int offset, int ratio, int topk, int pool, int budget, float* gmax, int32_t* chosen,
+                               int32_t* selection, int32_t* counts, int32_t* candidates, int32_t* candidate_counts, cudaStream_t s);
+int select_within_pool_launch(const float* scores, int tokens, int blocks, int offset, int ratio, int topk, const int32_t* candidates,
+                              const int32_t* candidate_counts, int cap, int32_t* selection, int32_t* counts, cudaStream_t s);
 int select_blocks_launch(const float* scores, int tokens, int blocks, int offset, int ratio, int topk, int32_t* selection, int32_t* counts, cudaStream_t s);
 // decode attention over the prompt shared by the rows of a group, head_dim 128, on mma.sync (attention_mma.cu): one
 // partial-result slot per 32-key tile and (row, head), as attn_decode_prefix_kernel writes them

@@ -98,6 +98,10 @@ int gn_dot_product(const float* left, const float* right, int64_t n, float* out)
 int gn_indexer_scores(float* dst, const float* query, const float* key, const float* weight, int rows, int blocks,
                       int heads, int dim);
 int gn_indexer_block_max(float* dst, const float* scores, int rows, int blocks, int group_size);
+/* The score part of SparseIndexer.Backward (model/indexer.go:107-151) for one key set: grad_query [rows, heads, dim] and
+ * grad_key [blocks, heads, dim] are overwritten, grad_weight [heads] is accumulated into.  dim <= 128. */
+int gn_indexer_scores_backward(const float* grad_scores, const float* query, const float* key, const float* weight, int rows, int blocks, int heads, int dim,
+                               float* grad_query, float* grad_key, float* grad_weight);
 
 /* Building blocks of the compressed ("flash") attention layers, inference forward.  These bypass kernels.Backend in the
  * reference (plain Go loops in model/): ChannelCompressor.Forward (model/compress.go:93-177; hidden [batch, seq, embed],
@@ -133,6 +137,17 @@ int gn_compressed_attention_sparse_backward(const float* query, const float* key
 int gn_attention_merge(const float* out_a, const float* lse_a, const float* out_b, const float* lse_b, int64_t rows, int head_dim, float* out,
                        float* lse);
 int gn_select_blocks(const float* scores, int tokens, int blocks, int position_offset, int ratio, int topk, int32_t* selection, int32_t* counts);
+/* The two-level selection over a score matrix (SparseIndexer.selectFromScoreMatrix / selectRowBlockMax, model/indexer.go:358-381,
+ * 442-513): super-blocks of `pool` entries ranked by their maximum over the allowed entries, the best
+ * max(1, ceil(candidate_budget / pool)) of them give the candidates [tokens, gn_hierarchical_cap(pool, candidate_budget)]
+ * (-1 padded; nullable together with candidate_counts), the selection is the top-k of the candidates.  gn_select_blocks_within_pool
+ * is selectWithinPool (model/indexer.go:547-613) over the same score matrix: top-k of a given candidate list, entries outside
+ * [0, allowed) dropped. */
+int gn_hierarchical_cap(int pool, int candidate_budget);
+int gn_select_blocks_hierarchical(const float* scores, int tokens, int blocks, int position_offset, int ratio, int topk, int pool, int candidate_budget,
+                                  int32_t* selection, int32_t* counts, int32_t* candidates, int32_t* candidate_counts);
+int gn_select_blocks_within_pool(const float* scores, int tokens, int blocks, int position_offset, int ratio, int topk, const int32_t* candidates,
+                                 const int32_t* candidate_counts, int cap, int32_t* selection, int32_t* counts);
 
 /* MoE (kernels/backend.go:119-141).  Indices are exact: descending score, ties
  * toward the smaller index. */

@@ -238,4 +238,82 @@ inline void select_blocks(const float* scores, int tokens, int blocks, int offse
   }
 }
 
+// The score part of SparseIndexer.Backward (model/indexer.go:107-151) for one key set: grad_scores [rows, blocks], query
+// [rows, heads, dim], key [blocks, heads, dim]; grad_query and grad_key are overwritten, grad_weight [heads] accumulates.
+// float32 accumulation in the reference's loop order (row, block, head).
+inline void indexer_scores_backward(const float* grad_scores, const float* query, const float* key, const float* weight, int rows, int blocks, int heads, int dim,
+                                    float* grad_query, float* grad_key, float* grad_weight) {
+  std::fill(grad_query, grad_query + (size_t)rows * heads * dim, 0.0f);
+  std::fill(grad_key, grad_key + (size_t)blocks * heads * dim, 0.0f);
+  for (int r = 0; r < rows; ++r)
+    for (int b = 0; b < blocks; ++b) {
+      const float g = grad_scores[(size_t)r * blocks + b];
+      for (int h = 0; h < heads; ++h) {
+        const size_t qb = ((size_t)r * heads + h) * dim, kb = ((size_t)b * heads + h) * dim;
+        float dot = 0.0f;
+        for (int i = 0; i < dim; ++i) dot += query[qb + i] * key[kb + i];
+        if (dot <= 0) continue;
+        grad_weight[h] += g * dot;
+        const float wg = g * weight[h];
+        for (int i = 0; i < dim; ++i) { grad_query[qb + i] += wg * key[kb + i]; grad_key[kb + i] += wg * query[qb + i]; }
+      }
+    }
+}
+
+// selectRowBlockMax over a score matrix (model/indexer.go:442-513): super-blocks of `pool` entries are ranked by the maximum
+// score among their causally allowed entries, the best ceil(budget / pool) super-blocks (at least one) give the candidate
+// entries -- super-blocks in rank order, entries ascending inside --, and the selection is the top-k of the candidates by
+// score, ties toward the earlier candidate.  candidates [tokens, cap], cap = max(1, ceil(budget / pool)) * pool, -1 padded.
+inline int hierarchical_cap(int pool, int budget) { pool = std::max(pool, 1); return std::max(1, (budget + pool - 1) / pool) * pool; }
+inline void select_blocks_hierarchical(const float* scores, int tokens, int blocks, int offset, int ratio, int topk, int pool, int budget, int32_t* selection,
+                                       int32_t* counts, int32_t* candidates, int32_t* candidate_counts) {
+  pool = std::max(pool, 1);
+  const int per_token = std::max(1, (budget + pool - 1) / pool), cap = per_token * pool;
+  for (int t = 0; t < tokens; ++t) {
+    const int allowed = std::min((offset + t) / ratio, blocks);
+    int32_t* sel = selection + (size_t)t * std::max(topk, 0);
+    int32_t* cand = candidates + (size_t)t * cap;
+    for (int i = 0; i < topk; ++i) sel[i] = -1;
+    for (int i = 0; i < cap; ++i) cand[i] = -1;
+    counts[t] = 0; candidate_counts[t] = 0;
+    if (allowed <= 0 || topk <= 0) continue;
+    const float* row = scores + (size_t)t * blocks;
+    const int groups = (allowed + pool - 1) / pool;
+    std::vector<float> gmax(groups, -INFINITY);
+    for (int e = 0; e < allowed; ++e) gmax[e / pool] = std::max(gmax[e / pool], row[e]);
+    const std::vector<int> chosen = topk_indices(gmax.data(), groups, std::min(per_token, groups));
+    std::vector<int> list; std::vector<float> fine;
+    for (int g : chosen)
+      for (int e = g * pool; e < std::min((g + 1) * pool, allowed); ++e) { list.push_back(e); fine.push_back(row[e]); }
+    candidate_counts[t] = (int32_t)list.size();
+    std::copy(list.begin(), list.end(), cand);
+    const std::vector<int> order = topk_indices(fine.data(), (int)fine.size(), std::min<int>(topk, (int)fine.size()));
+    counts[t] = (int32_t)order.size();
+    for (size_t i = 0; i < order.size(); ++i) sel[i] = list[order[i]];
+  }
+}
+
+// selectWithinPool over a score matrix (model/indexer.go:547-613): the candidates of a token that lie in [0, allowed) are
+// kept in their order and the top-k of them by score is the selection, ties toward the earlier kept candidate.
+inline void select_blocks_within_pool(const float* scores, int tokens, int blocks, int offset, int ratio, int topk, const int32_t* candidates,
+                                      const int32_t* candidate_counts, int cap, int32_t* selection, int32_t* counts) {
+  for (int t = 0; t < tokens; ++t) {
+    const int allowed = std::min((offset + t) / ratio, blocks);
+    int32_t* sel = selection + (size_t)t * std::max(topk, 0);
+    for (int i = 0; i < topk; ++i) sel[i] = -1;
+    counts[t] = 0;
+    if (topk <= 0) continue;
+    const float* row = scores + (size_t)t * blocks;
+    std::vector<int> kept; std::vector<float> fine;
+    for (int i = 0; i < std::min(candidate_counts[t], cap); ++i) {
+      const int e = candidates[(size_t)t * cap + i];
+      if (e < 0 || e >= allowed) continue;
+      kept.push_back(e); fine.push_back(row[e]);
+    }
+    const std::vector<int> order = topk_indices(fine.data(), (int)fine.size(), std::min<int>(topk, (int)fine.size()));
+    counts[t] = (int32_t)order.size();
+    for (size_t i = 0; i < order.size(); ++i) sel[i] = kept[order[i]];
+  }
+}
+
 }  // namespace gnor

@@ -584,6 +584,19 @@ void or_compressed_attention_sparse_forward(int m, const float* q, const float* 
                                             int Hq, int Hkv, int T, int D, int blocks, int topk, float* out, float* lse) {
   BK(m); gnor::compressed_attention_sparse_forward(bk, q, kc, vc, selection, counts, B, Hq, Hkv, T, D, blocks, topk, out, lse);
 }
+void or_indexer_scores_backward(const float* gs, const float* q, const float* k, const float* w, int rows, int blocks, int heads, int dim, float* gq, float* gk,
+                                float* gw) {
+  gnor::indexer_scores_backward(gs, q, k, w, rows, blocks, heads, dim, gq, gk, gw);
+}
+int or_hierarchical_cap(int pool, int budget) { return gnor::hierarchical_cap(pool, budget); }
+void or_select_blocks_hierarchical(const float* scores, int tokens, int blocks, int offset, int ratio, int topk, int pool, int budget, int32_t* selection,
+                                   int32_t* counts, int32_t* candidates, int32_t* candidate_counts) {
+  gnor::select_blocks_hierarchical(scores, tokens, blocks, offset, ratio, topk, pool, budget, selection, counts, candidates, candidate_counts);
+}
+void or_select_blocks_within_pool(const float* scores, int tokens, int blocks, int offset, int ratio, int topk, const int32_t* candidates,
+                                  const int32_t* candidate_counts, int cap, int32_t* selection, int32_t* counts) {
+  gnor::select_blocks_within_pool(scores, tokens, blocks, offset, ratio, topk, candidates, candidate_counts, cap, selection, counts);
+}
 void or_compressed_attention_sparse_backward(int m, const float* q, const float* kc, const float* vc, const float* dout, const float* lse, const float* rowcorr,
                                              const int32_t* selection, const int32_t* counts, int B, int Hq, int Hkv, int T, int D, int blocks, int topk, float* dq,
                                              float* dkc, float* dvc) {

@@ -633,3 +633,31 @@ def select_blocks(scores, offset, ratio, topk):
     sel = np.full((tokens, max(topk, 0)), -1, np.int32); cnt = np.zeros(tokens, np.int32)
     lib().or_select_blocks(_f(scores), tokens, blocks, offset, ratio, topk, _i(sel), _i(cnt))
     return sel, cnt
+
+
+def select_blocks_hierarchical(scores, offset, ratio, topk, pool, budget):
+    """selectRowBlockMax per token (model/indexer.go:442-513): selection [tokens, topk], counts, candidates [tokens, cap], candidate counts."""
+    scores = f32(scores); tokens, blocks = scores.shape
+    cap = lib().or_hierarchical_cap(pool, budget)
+    sel = np.full((tokens, max(topk, 0)), -1, np.int32); cnt = np.zeros(tokens, np.int32)
+    cand = np.full((tokens, cap), -1, np.int32); ccnt = np.zeros(tokens, np.int32)
+    lib().or_select_blocks_hierarchical(_f(scores), tokens, blocks, offset, ratio, topk, pool, budget, _i(sel), _i(cnt), _i(cand), _i(ccnt))
+    return sel, cnt, cand, ccnt
+
+
+def select_blocks_within_pool(scores, offset, ratio, topk, candidates, candidate_counts):
+    """selectWithinPool over a score matrix (model/indexer.go:547-613)."""
+    scores = f32(scores); tokens, blocks = scores.shape
+    candidates, candidate_counts = i32(candidates), i32(candidate_counts)
+    sel = np.full((tokens, max(topk, 0)), -1, np.int32); cnt = np.zeros(tokens, np.int32)
+    lib().or_select_blocks_within_pool(_f(scores), tokens, blocks, offset, ratio, topk, _i(candidates), _i(candidate_counts), candidates.shape[1], _i(sel), _i(cnt))
+    return sel, cnt
+
+
+def indexer_scores_backward(grad_scores, query, key, weight, grad_weight=None):
+    """Score part of SparseIndexer.Backward (model/indexer.go:107-151): grad_query, grad_key (fresh), grad_weight (accumulated)."""
+    gs, q, k, w = f32(grad_scores), f32(query), f32(key), f32(weight)
+    rows, heads, dim = q.shape; blocks = k.shape[0]
+    gq = np.zeros_like(q); gk = np.zeros_like(k); gw = np.zeros(heads, np.float32) if grad_weight is None else f32(grad_weight).copy()
+    lib().or_indexer_scores_backward(_f(gs), _f(q), _f(k), _f(w), rows, blocks, heads, dim, _f(gq), _f(gk), _f(gw))
+    return gq, gk, gw

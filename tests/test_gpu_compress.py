@@ -311,3 +311,56 @@ def test_heavily_compressed_layer_backward(oracle, bk):
     close(got_o, want_o, 1e-4, 1e-5)
     for g, w in zip(got, want):
         close(g, w, 3e-4, 3e-5)
+
+
+# the two-level selection (model/indexer.go:442-513) and the selection inside a published candidate list (:547-613)
+@pytest.mark.parametrize("tokens,blocks,offset,ratio,topk,pool,budget", [(1, 4, 4, 1, 1, 2, 2), (40, 30, 0, 2, 4, 4, 8), (50, 300, 900, 4, 16, 8, 64),
+                                                                         (33, 70, 5, 1, 8, 3, 10), (20, 20, 0, 2, 2, 1, 1000), (9, 16, 64, 4, 64, 8, 0)])
+def test_select_blocks_hierarchical(oracle, bk, tokens, blocks, offset, ratio, topk, pool, budget):
+    rng = np.random.default_rng(tokens * 7 + blocks)
+    scores = np.round(rng.standard_normal((tokens, blocks)) * 4).astype(np.float32)      # quantised: ties in both stages
+    if tokens == 1:
+        scores = np.array([[4, 0, 3, 3]], np.float32)                                    # model/indexer_test.go:351-365
+    want = oracle.select_blocks_hierarchical(scores, offset, ratio, topk, pool, budget)
+    got = bk.select_blocks_hierarchical(scores, offset, ratio, topk, pool, budget)
+    for g, w in zip(got, want):
+        assert np.array_equal(g, w)
+    if tokens == 1:
+        assert got[2][0].tolist() == [0, 1] and got[0][0].tolist() == [0]
+    groups = max(1, -(-budget // pool))
+    assert got[2].shape[1] == groups * pool and np.all(got[3] <= groups * pool)          # model/indexer_test.go:212-244
+    allowed = np.minimum((offset + np.arange(tokens)) // ratio, blocks)
+    assert np.all((got[2] < allowed[:, None]) | (got[2] == -1))
+    # a later layer that re-selects inside the published candidates finds the same blocks (model/indexer_test.go:183-210)
+    want_p = oracle.select_blocks_within_pool(scores, offset, ratio, topk, got[2], got[3])
+    got_p = bk.select_blocks_within_pool(scores, offset, ratio, topk, got[2], got[3])
+    assert np.array_equal(got_p[0], want_p[0]) and np.array_equal(got_p[1], want_p[1])
+    assert np.array_equal(got_p[0], got[0]) and np.array_equal(got_p[1], got[1])
+    # candidates published for an earlier position: entries at or beyond the allowed range are dropped
+    late = np.roll(got[2], 3, axis=0); late_c = np.roll(got[3], 3)
+    want_l = oracle.select_blocks_within_pool(scores, offset, ratio, topk, late, late_c)
+    got_l = bk.select_blocks_within_pool(scores, offset, ratio, topk, late, late_c)
+    assert np.array_equal(got_l[0], want_l[0]) and np.array_equal(got_l[1], want_l[1])
+
+
+def test_hierarchical_selection_unbounded_equals_flat(bk):
+    rng = np.random.default_rng(5)
+    scores = rng.standard_normal((64, 40)).astype(np.float32)                            # no ties (model/indexer_test.go:327-349)
+    flat, flat_c = bk.select_blocks(scores, 0, 2, 2)
+    for pool in (1, 2, 3):
+        sel, cnt, _, _ = bk.select_blocks_hierarchical(scores, 0, 2, 2, pool, 1000)
+        assert np.array_equal(sel, flat) and np.array_equal(cnt, flat_c)
+
+
+# the score part of SparseIndexer.Backward (model/indexer.go:107-151)
+@pytest.mark.parametrize("rows,blocks,heads,dim", [(5, 3, 2, 2), (70, 33, 4, 32), (130, 64, 3, 100), (16, 300, 8, 64)])
+def test_indexer_scores_backward(oracle, bk, rows, blocks, heads, dim):
+    rng = np.random.default_rng(rows + dim)
+    q = rng.standard_normal((rows, heads, dim)).astype(np.float32); k = rng.standard_normal((blocks, heads, dim)).astype(np.float32)
+    w = rng.standard_normal(heads).astype(np.float32); gs = rng.standard_normal((rows, blocks)).astype(np.float32)
+    seed = rng.standard_normal(heads).astype(np.float32)
+    want = oracle.indexer_scores_backward(gs, q, k, w, seed)
+    got = bk.indexer_scores_backward(gs, q, k, w, seed)
+    scale = np.sqrt(dim)
+    for g, x in zip(got, want):
+        close(g, x, 1e-4, 1e-5 * scale * np.sqrt(max(rows, blocks)))

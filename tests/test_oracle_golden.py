@@ -371,3 +371,40 @@ def test_heavily_compressed_layer_gradient_matches_finite_difference(oracle):
     eps = 1e-3
     numeric = (loss(eps) - loss(-eps)) / (2 * eps)
     assert abs(analytic - numeric) <= 3e-3 * max(1.0, abs(numeric)), (analytic, numeric)
+
+
+# model/indexer_test.go:351-365 (super-blocks are ranked by their maximum, not their mean), :327-349 (an unbounded budget gives the
+# flat selection), :212-244 (candidates bounded by the budget and causal), :183-210 (re-selecting inside the candidates)
+def test_hierarchical_selection_known_answers(oracle):
+    sel, cnt, cand, cc = oracle.select_blocks_hierarchical(np.array([[4, 0, 3, 3]], np.float32), 4, 1, 1, 2, 2)
+    assert cand[0].tolist() == [0, 1] and cc[0] == 2 and sel[0].tolist() == [0] and cnt[0] == 1
+    rng = np.random.default_rng(3)
+    scores = rng.standard_normal((48, 32)).astype(np.float32)
+    flat, flat_c = oracle.select_blocks(scores, 0, 2, 2)
+    for pool in (1, 2, 3):
+        sel, cnt, _, _ = oracle.select_blocks_hierarchical(scores, 0, 2, 2, pool, 1000)
+        assert np.array_equal(sel, flat) and np.array_equal(cnt, flat_c)
+    sel, cnt, cand, cc = oracle.select_blocks_hierarchical(scores, 0, 2, 4, 4, 8)
+    assert cand.shape[1] == 8 and cc.max() <= 8
+    allowed = np.minimum(np.arange(48) // 2, 32)
+    assert np.all((cand < allowed[:, None]) | (cand == -1)) and cnt[0] == 0 and cnt[1] == 0
+    again, again_c = oracle.select_blocks_within_pool(scores, 0, 2, 4, cand, cc)
+    assert np.array_equal(again, sel) and np.array_equal(again_c, cnt)
+
+
+# SparseIndexer.Backward's score part against a central difference of the scores (model/indexer_test.go:86-181 checks the same way)
+def test_indexer_scores_gradient_matches_finite_difference(oracle):
+    rng = np.random.default_rng(23)
+    rows, blocks, heads, dim = 6, 5, 3, 4
+    bk = oracle.Backend(0)
+    q = rng.standard_normal((rows, heads, dim)).astype(np.float32); k = rng.standard_normal((blocks, heads, dim)).astype(np.float32)
+    w = rng.standard_normal(heads).astype(np.float32); gs = rng.standard_normal((rows, blocks)).astype(np.float32)
+    gq, gk, gw = oracle.indexer_scores_backward(gs, q, k, w)
+    dirs = [rng.standard_normal(x.shape).astype(np.float32) for x in (q, k, w)]
+    analytic = sum(float(np.sum(g.astype(np.float64) * d)) for g, d in zip((gq, gk, gw), dirs))
+    def loss(eps):
+        s = bk.indexer_scores(q + eps * dirs[0], k + eps * dirs[1], w + eps * dirs[2], rows, blocks, heads, dim)
+        return float(np.sum(np.asarray(s, np.float64).reshape(rows, blocks) * gs))
+    eps = 1e-3
+    numeric = (loss(eps) - loss(-eps)) / (2 * eps)
+    assert abs(analytic - numeric) <= 5e-3 * max(1.0, abs(numeric)), (analytic, numeric)
