@@ -110,6 +110,24 @@ class CudaBackend:
         check(self.lib.gn_indexer_scores_backward(ptr(gs), ptr(q), ptr(k), ptr(w), rows, blocks, heads, dim, ptr(gq), ptr(gk), ptr(gw)))
         return gq, gk, gw
 
+    def indexer_distillation_target(self, q, kc, ratio):
+        """distillationTarget (model/compress_attention.go:155-196): [B * Hkv, T, blocks]."""
+        q, kc = _f32(q), _f32(kc)
+        B, Hq, T, D = q.shape; Hkv, blocks = kc.shape[1], kc.shape[2]
+        target = np.zeros((B * Hkv, T, blocks), np.float32)
+        check(self.lib.gn_indexer_distillation_target(ptr(q), ptr(kc), B, Hq, Hkv, T, D, blocks, ratio, ptr(target)))
+        return target
+
+    def indexer_distillation_grad(self, scores, target, ratio, weight, candidates=None, candidate_counts=None):
+        """(masked softmax of the scores - target) * weight (model/compress_attention.go:120-151, 203-231, 266-303); scores [n, T, blocks]."""
+        scores, target = _f32(scores), _f32(target)
+        n, T, blocks = scores.shape
+        grad = np.zeros_like(scores)
+        cand = _i32(candidates) if candidates is not None else None; cc = _i32(candidate_counts) if candidates is not None else None
+        check(self.lib.gn_indexer_distillation_grad(ptr(scores), ptr(target), ptr(cand) if cand is not None else None, ptr(cc) if cand is not None else None,
+                                                    0 if cand is None else cand.shape[-1], n * T, blocks, T, ratio, weight, ptr(grad)))
+        return grad
+
     def indexer_block_max(self, scores, rows, blocks, group_size):
         scores = _f32(scores); g = max(group_size, 1)
         dst = np.empty(rows * ((blocks + g - 1) // g), np.float32)

@@ -450,6 +450,31 @@ int gn_indexer_scores_backward(const float* grad_scores, const float* query, con
   GN_TRY(indexer_scores_backward_launch(pg, pq, pk, pw, rows, blocks, heads, dim, gq, gk, gw, wpart, s));
   GN_END();
 }
+// distillationTarget (model/compress_attention.go:155-196) for every (batch, kv head)
+int gn_indexer_distillation_target(const float* query, const float* key_c, int batch, int n_head, int n_kv_head, int seq, int head_dim, int blocks, int ratio,
+                                   float* target) {
+  if (batch <= 0 || seq <= 0 || blocks <= 0) return GN_OK;
+  GN_REQUIRE(query && key_c && target && n_kv_head > 0, "indexer_distillation_target: bad argument");
+  GN_BEGIN();
+  const float* pq = st.in(query, (size_t)batch * n_head * seq * head_dim); const float* pk = st.in(key_c, (size_t)batch * n_kv_head * blocks * head_dim);
+  float* pt = st.out(target, (size_t)batch * n_kv_head * seq * blocks);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(distillation_target_launch(pq, pk, batch, n_head, n_kv_head, seq, head_dim, blocks, ratio, pt, s));
+  GN_END();
+}
+// the score gradient of indexerDistillationGradient (model/compress_attention.go:120-151) with restrictIndexerToPool (:203-231)
+int gn_indexer_distillation_grad(const float* scores, const float* target, const int32_t* candidates, const int32_t* candidate_counts, int cap, int64_t rows,
+                                 int blocks, int seq, int ratio, float weight, float* grad_scores) {
+  if (rows <= 0 || blocks <= 0) return GN_OK;
+  GN_REQUIRE(scores && target && grad_scores && (!candidates || candidate_counts), "indexer_distillation_grad: bad argument");
+  GN_BEGIN();
+  const float* ps = st.in(scores, (size_t)rows * blocks); const float* pt = st.in(target, (size_t)rows * blocks);
+  const int32_t* pc = candidates ? st.in(candidates, (size_t)rows * cap) : nullptr; const int32_t* pn = candidates ? st.in(candidate_counts, (size_t)rows) : nullptr;
+  float* pg = st.out(grad_scores, (size_t)rows * blocks);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(distillation_grad_launch(ps, pt, pc, pn, cap, rows, blocks, seq, ratio, weight, pg, s));
+  GN_END();
+}
 // selectFromScoreMatrix / selectRowBlockMax (model/indexer.go:358-381, 442-513)
 int gn_hierarchical_cap(int pool, int candidate_budget) { pool = pool < 1 ? 1 : pool; const int g = (candidate_budget + pool - 1) / pool; return (g < 1 ? 1 : g) * pool; }
 int gn_select_blocks_hierarchical(const float* scores, int tokens, int blocks, int position_offset, int ratio, int topk, int pool, int candidate_budget,

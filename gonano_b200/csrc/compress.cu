@@ -335,6 +335,80 @@ __global__ void __launch_bounds__(256) indexer_bwd_weight_kernel(const float* __
   if (threadIdx.x == 0) gw[h] += (float)part[0];
 }
 
+// distillationTarget (model/compress_attention.go:155-196): one warp per (batch, kv head, token).  The averaged logits are left in
+// the target row, then turned into the softmax over the allowed blocks; the rest of the row is zero.
+__global__ void __launch_bounds__(256) distillation_target_kernel(const float* __restrict__ q, const float* __restrict__ kc, int B, int Hq, int Hkv, int T, int D,
+                                                                  int blocks, int ratio, float* __restrict__ target) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t idx = (int64_t)blockIdx.x * 8 + warp;
+  if (idx >= (int64_t)B * Hkv * T) return;
+  const int t = (int)(idx % T); const int64_t kvh = idx / T; const int hk = (int)(kvh % Hkv); const int b = (int)(kvh / Hkv);
+  const int hr = Hq / Hkv, allowed = min(t / ratio, blocks);
+  float* row = target + idx * blocks;
+  for (int j = allowed + lane; j < blocks; j += 32) row[j] = 0.0f;
+  if (allowed == 0) return;
+  float mx = -INFINITY;
+  for (int j = 0; j < allowed; ++j) {
+    const float* kr = kc + (kvh * blocks + j) * D;
+    float sum = 0.0f;
+    for (int hh = 0; hh < hr; ++hh) {
+      const float* qr = q + (((int64_t)b * Hq + hk * hr + hh) * T + t) * D;
+      float d = 0.0f;
+      for (int c = lane; c < D; c += 32) d = fmaf(qr[c], kr[c], d);
+      sum += warp_sum(d);
+    }
+    const float logit = sum / (float)hr;
+    mx = fmaxf(mx, logit);
+    if (lane == 0) row[j] = logit;
+  }
+  __syncwarp();
+  double total = 0.0;
+  for (int j = lane; j < allowed; j += 32) { const double v = exp((double)(row[j] - mx)); row[j] = (float)v; total += v; }
+  total = warp_sum_d(total);
+  const float ft = (float)total;
+  for (int j = lane; j < allowed; j += 32) row[j] /= ft;
+}
+// (softmax over the allowed blocks - target) * weight, optionally restricted to the row's candidate list
+// (model/compress_attention.go:120-151, 203-231, 266-303): one warp per row; the gradient row doubles as the membership marker.
+__global__ void __launch_bounds__(256) distillation_grad_kernel(const float* __restrict__ scores, const float* __restrict__ target,
+                                                                const int32_t* __restrict__ candidates, const int32_t* __restrict__ candidate_counts, int cap,
+                                                                int64_t rows, int blocks, int seq, int ratio, float weight, float* __restrict__ grad) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t r = (int64_t)blockIdx.x * 8 + warp;
+  if (r >= rows) return;
+  const float* sc = scores + r * blocks; const float* tg = target + r * blocks;
+  float* g = grad + r * blocks;
+  const int allowed = min((int)(r % seq) / ratio, blocks);
+  const bool pooled = candidates != nullptr;
+  double ttotal = 0.0;
+  if (pooled) {
+    for (int e = lane; e < blocks; e += 32) g[e] = 0.0f;
+    __syncwarp();
+    const int n = max(0, min(candidate_counts[r], cap));
+    for (int i = lane; i < n; i += 32) { const int e = candidates[r * cap + i]; if (e >= 0 && e < blocks) g[e] = 1.0f; }
+    __syncwarp();
+    for (int e = lane; e < blocks; e += 32) if (g[e] != 0.0f) ttotal += (double)tg[e];
+    ttotal = warp_sum_d(ttotal);
+  }
+  float mx = -INFINITY;
+  for (int e = lane; e < allowed; e += 32) if (!pooled || g[e] != 0.0f) mx = fmaxf(mx, sc[e]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  double total = 0.0;
+  if (mx != -INFINITY)
+    for (int e = lane; e < allowed; e += 32) if (!pooled || g[e] != 0.0f) total += exp((double)(sc[e] - mx));
+  total = warp_sum_d(total);
+  const float ft = (float)total;
+  for (int e = lane; e < blocks; e += 32) {
+    const bool in = !pooled || g[e] != 0.0f;
+    float t = in ? tg[e] : 0.0f;
+    if (pooled && in && ttotal > 0.0) t = (float)((double)t / ttotal);
+    float p = 0.0f;
+    if (in && e < allowed && mx != -INFINITY) p = (float)exp((double)(sc[e] - mx)) / ft;
+    g[e] = (p - t) * weight;
+  }
+}
+
 // One warp per token, the two-level selection (model/indexer.go:442-513).  gmax [tokens, ceil(blocks / pool)] and chosen
 // [tokens, per_token] are scratch.  Ranks are counted exactly as in select_blocks_kernel: super-blocks by their maximum over
 // the allowed entries, then the candidate entries (super-blocks in rank order, entries ascending inside) by score with ties
@@ -506,6 +580,24 @@ int indexer_scores_backward_launch(const float* gs, const float* q, const float*
   indexer_bwd_query_kernel<<<(unsigned)ceil_div((int64_t)rows * heads, 8), 256, 0, s>>>(gs, q, key, w, rows, blocks, heads, dim, gq, wpart);
   indexer_bwd_key_kernel<<<(unsigned)ceil_div((int64_t)blocks * heads, 8), 256, 0, s>>>(gs, q, key, w, rows, blocks, heads, dim, gk);
   indexer_bwd_weight_kernel<<<heads, 256, 0, s>>>(wpart, rows, heads, gw);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+int distillation_target_launch(const float* q, const float* kc, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* target, cudaStream_t s) {
+  const int64_t n = (int64_t)B * Hkv * T;
+  if (n <= 0 || blocks <= 0) return GN_OK;
+  GN_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && ratio >= 1 && D >= 1, "distillation target: %d query heads, %d kv heads, ratio %d", Hq, Hkv, ratio);
+  distillation_target_kernel<<<(unsigned)ceil_div(n, 8), 256, 0, s>>>(q, kc, B, Hq, Hkv, T, D, blocks, ratio, target);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+int distillation_grad_launch(const float* scores, const float* target, const int32_t* candidates, const int32_t* candidate_counts, int cap, int64_t rows, int blocks,
+                             int seq, int ratio, float weight, float* grad, cudaStream_t s) {
+  if (rows <= 0 || blocks <= 0) return GN_OK;
+  GN_REQUIRE(seq >= 1 && ratio >= 1 && (!candidates || (candidate_counts && cap >= 1)), "distillation gradient: seq %d, ratio %d, cap %d", seq, ratio, cap);
+  distillation_grad_kernel<<<(unsigned)ceil_div(rows, 8), 256, 0, s>>>(scores, target, candidates, candidate_counts, cap, rows, blocks, seq, ratio, weight, grad);
   GN_LAUNCH_CHECK();
   return GN_OK;
 }

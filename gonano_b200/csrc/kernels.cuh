@@ -78,6 +78,10 @@ int attention_merge_launch(const float* oa, const float* la, const float* ob, co
 // score part of the indexer's backward: gq [rows, heads, dim], gk [blocks, heads, dim] overwritten, gw [heads] accumulated; wpart [rows, heads] scratch
 int indexer_scores_backward_launch(const float* gs, const float* q, const float* key, const float* w, int rows, int blocks, int heads, int dim, float* gq, float* gk,
                                    float* gw, float* wpart, cudaStream_t s);
+// the indexer's distillation: target [B * Hkv, T, blocks] from the main attention logits; grad = (masked softmax(scores) - target) * weight, row r = token r % seq
+int distillation_target_launch(const float* q, const float* kc, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* target, cudaStream_t s);
+int distillation_grad_launch(const float* scores, const float* target, const int32_t* candidates, const int32_t* candidate_counts, int cap, int64_t rows, int blocks,
+                             int seq, int ratio, float weight, float* grad, cudaStream_t s);
 // two-level selection: gmax [tokens, ceil(blocks / pool)] and chosen [tokens, max(1, ceil(budget / pool))] are scratch; candidates [tokens, that * pool]
 int select_hierarchical_launch(const float* scores, int tokens, int blocks, int offset, int ratio, int topk, int pool, int budget, float* gmax, int32_t* chosen,
                                int32_t* selection, int32_t* counts, int32_t* candidates, int32_t* candidate_counts, cudaStream_t s);

@@ -143,6 +143,15 @@ int gn_select_blocks(const float* scores, int tokens, int blocks, int position_o
  * (-1 padded; nullable together with candidate_counts), the selection is the top-k of the candidates.  gn_select_blocks_within_pool
  * is selectWithinPool (model/indexer.go:547-613) over the same score matrix: top-k of a given candidate list, entries outside
  * [0, allowed) dropped. */
+/* The indexer's distillation (model/compress_attention.go:120-196, 203-231, 266-303).  Target [batch * n_kv_head, seq, blocks]: per
+ * token the softmax over its allowed blocks of the main attention logits averaged over the query heads of the group.  Gradient
+ * with respect to the index scores [rows, blocks] (row r is token r % seq): (softmax over the allowed blocks - target) * weight;
+ * with candidates [rows, cap] (nullable) scores and target are first restricted to each row's candidate list, the target
+ * renormalised inside it. */
+int gn_indexer_distillation_target(const float* query, const float* key_c, int batch, int n_head, int n_kv_head, int seq, int head_dim, int blocks, int ratio,
+                                   float* target);
+int gn_indexer_distillation_grad(const float* scores, const float* target, const int32_t* candidates, const int32_t* candidate_counts, int cap, int64_t rows,
+                                 int blocks, int seq, int ratio, float weight, float* grad_scores);
 int gn_hierarchical_cap(int pool, int candidate_budget);
 int gn_select_blocks_hierarchical(const float* scores, int tokens, int blocks, int position_offset, int ratio, int topk, int pool, int candidate_budget,
                                   int32_t* selection, int32_t* counts, int32_t* candidates, int32_t* candidate_counts);

@@ -260,6 +260,69 @@ inline void indexer_scores_backward(const float* grad_scores, const float* query
     }
 }
 
+// distillationTarget (model/compress_attention.go:155-196) for every (batch, kv head): per token the softmax, over the allowed
+// blocks, of the main attention logits averaged over the query heads of the group.  target [B * Hkv, T, blocks], zero elsewhere.
+inline void indexer_distillation_target(const float* q, const float* kc, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* target) {
+  const int hr = Hq / Hkv;
+  std::fill(target, target + (size_t)B * Hkv * T * blocks, 0.0f);
+  std::vector<float> logits(std::max(blocks, 1));
+  for (int b = 0; b < B; ++b)
+    for (int hk = 0; hk < Hkv; ++hk)
+      for (int t = 0; t < T; ++t) {
+        const int allowed = std::min(t / ratio, blocks);
+        if (allowed == 0) continue;
+        float* row = target + (((size_t)b * Hkv + hk) * T + t) * blocks;
+        float mx = -INFINITY;
+        for (int j = 0; j < allowed; ++j) {
+          float sum = 0.0f;
+          for (int hh = 0; hh < hr; ++hh) {
+            const float* qr = q + (((size_t)b * Hq + hk * hr + hh) * T + t) * D;
+            const float* kr = kc + (((size_t)b * Hkv + hk) * blocks + j) * D;
+            float dot = 0.0f;
+            for (int c = 0; c < D; ++c) dot += qr[c] * kr[c];
+            sum += dot;
+          }
+          logits[j] = sum / (float)hr;
+          mx = std::max(mx, logits[j]);
+        }
+        double total = 0.0;
+        for (int j = 0; j < allowed; ++j) { const double v = std::exp((double)(logits[j] - mx)); row[j] = (float)v; total += v; }
+        for (int j = 0; j < allowed; ++j) row[j] /= (float)total;
+      }
+}
+
+// The gradient of the indexer's distillation loss with respect to its scores (model/compress_attention.go:120-151):
+// (softmax over the allowed blocks - target) * weight, row r being token r % seq.  With candidates [rows, cap] the scores and
+// the target are first restricted to each row's candidate list (restrictIndexerToPool, :203-231): -inf and 0 outside, the target
+// renormalised inside; a row without a finite score gets probabilities 0 (maskedIndexerSoftmax, :266-303).
+inline void indexer_distillation_grad(const float* scores, const float* target, const int32_t* candidates, const int32_t* candidate_counts, int cap, int64_t rows,
+                                      int blocks, int seq, int ratio, float weight, float* grad) {
+  std::vector<float> sc(std::max(blocks, 1)), tg(std::max(blocks, 1));
+  std::vector<char> in(std::max(blocks, 1));
+  for (int64_t r = 0; r < rows; ++r) {
+    std::copy(scores + r * blocks, scores + (r + 1) * blocks, sc.begin());
+    std::copy(target + r * blocks, target + (r + 1) * blocks, tg.begin());
+    if (candidates) {
+      std::fill(in.begin(), in.end(), 0);
+      for (int i = 0; i < std::min(candidate_counts[r], cap); ++i) { const int e = candidates[r * cap + i]; if (e >= 0 && e < blocks) in[e] = 1; }
+      double total = 0.0;
+      for (int e = 0; e < blocks; ++e) { if (!in[e]) { sc[e] = -INFINITY; tg[e] = 0.0f; } else total += (double)tg[e]; }
+      if (total > 0) for (int e = 0; e < blocks; ++e) if (in[e]) tg[e] = (float)((double)tg[e] / total);
+    }
+    float* g = grad + r * blocks;
+    const int allowed = std::min((int)(r % seq) / ratio, blocks);
+    for (int e = 0; e < blocks; ++e) g[e] = (0.0f - tg[e]) * weight;
+    if (allowed == 0) continue;
+    float mx = sc[0];
+    for (int e = 1; e < allowed; ++e) mx = std::max(mx, sc[e]);
+    if (mx == -INFINITY) continue;
+    double total = 0.0;
+    std::vector<float> p(allowed);
+    for (int e = 0; e < allowed; ++e) { const double v = std::exp((double)(sc[e] - mx)); p[e] = (float)v; total += v; }
+    for (int e = 0; e < allowed; ++e) g[e] = (p[e] / (float)total - tg[e]) * weight;
+  }
+}
+
 // selectRowBlockMax over a score matrix (model/indexer.go:442-513): super-blocks of `pool` entries are ranked by the maximum
 // score among their causally allowed entries, the best ceil(budget / pool) super-blocks (at least one) give the candidate
 // entries -- super-blocks in rank order, entries ascending inside --, and the selection is the top-k of the candidates by

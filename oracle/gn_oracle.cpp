@@ -588,6 +588,13 @@ void or_indexer_scores_backward(const float* gs, const float* q, const float* k,
                                 float* gw) {
   gnor::indexer_scores_backward(gs, q, k, w, rows, blocks, heads, dim, gq, gk, gw);
 }
+void or_indexer_distillation_target(const float* q, const float* kc, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* target) {
+  gnor::indexer_distillation_target(q, kc, B, Hq, Hkv, T, D, blocks, ratio, target);
+}
+void or_indexer_distillation_grad(const float* scores, const float* target, const int32_t* candidates, const int32_t* candidate_counts, int cap, int64_t rows,
+                                  int blocks, int seq, int ratio, float weight, float* grad) {
+  gnor::indexer_distillation_grad(scores, target, candidates, candidate_counts, cap, rows, blocks, seq, ratio, weight, grad);
+}
 int or_hierarchical_cap(int pool, int budget) { return gnor::hierarchical_cap(pool, budget); }
 void or_select_blocks_hierarchical(const float* scores, int tokens, int blocks, int offset, int ratio, int topk, int pool, int budget, int32_t* selection,
                                    int32_t* counts, int32_t* candidates, int32_t* candidate_counts) {

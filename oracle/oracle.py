@@ -661,3 +661,23 @@ def indexer_scores_backward(grad_scores, query, key, weight, grad_weight=None):
     gq = np.zeros_like(q); gk = np.zeros_like(k); gw = np.zeros(heads, np.float32) if grad_weight is None else f32(grad_weight).copy()
     lib().or_indexer_scores_backward(_f(gs), _f(q), _f(k), _f(w), rows, blocks, heads, dim, _f(gq), _f(gk), _f(gw))
     return gq, gk, gw
+
+
+def indexer_distillation_target(q, kc, ratio):
+    """distillationTarget (model/compress_attention.go:155-196): [B * Hkv, T, blocks]."""
+    q, kc = f32(q), f32(kc)
+    B, Hq, T, D = q.shape; Hkv, blocks = kc.shape[1], kc.shape[2]
+    target = np.zeros((B * Hkv, T, blocks), np.float32)
+    lib().or_indexer_distillation_target(_f(q), _f(kc), B, Hq, Hkv, T, D, blocks, ratio, _f(target))
+    return target
+
+
+def indexer_distillation_grad(scores, target, ratio, weight, candidates=None, candidate_counts=None):
+    """(masked softmax of the scores - target) * weight (model/compress_attention.go:120-151, 203-231, 266-303); scores [n, T, blocks]."""
+    scores, target = f32(scores), f32(target)
+    n, T, blocks = scores.shape
+    grad = np.zeros_like(scores)
+    cand = i32(candidates) if candidates is not None else None; cc = i32(candidate_counts) if candidates is not None else None
+    lib().or_indexer_distillation_grad(_f(scores), _f(target), _i(cand) if cand is not None else None, _i(cc) if cand is not None else None,
+                                       0 if cand is None else cand.shape[-1], C.c_int64(n * T), blocks, T, ratio, C.c_float(weight), _f(grad))
+    return grad

@@ -364,3 +364,31 @@ def test_indexer_scores_backward(oracle, bk, rows, blocks, heads, dim):
     scale = np.sqrt(dim)
     for g, x in zip(got, want):
         close(g, x, 1e-4, 1e-5 * scale * np.sqrt(max(rows, blocks)))
+
+
+# the indexer's distillation: target from the main attention logits and the score gradient, free and restricted to a
+# published candidate list (model/compress_attention.go:120-196, 203-231, 266-303)
+@pytest.mark.parametrize("B,Hq,Hkv,T,D,ratio", [(1, 2, 1, 9, 8, 2), (2, 6, 2, 70, 128, 4), (1, 8, 1, 130, 64, 4)])
+def test_indexer_distillation(oracle, bk, B, Hq, Hkv, T, D, ratio):
+    rng = np.random.default_rng(T + Hq)
+    blocks = (T + ratio - 1) // ratio
+    q = (rng.standard_normal((B, Hq, T, D)) * 0.4).astype(np.float32); kc = (rng.standard_normal((B, Hkv, blocks, D)) * 0.4).astype(np.float32)
+    want_t = oracle.indexer_distillation_target(q, kc, ratio)
+    got_t = bk.indexer_distillation_target(q, kc, ratio)
+    close(got_t, want_t, 1e-5, 1e-6)
+    full = np.minimum(np.arange(T) // ratio, blocks) > 0
+    assert np.allclose(got_t[:, full].sum(axis=-1), 1.0, atol=1e-5) and np.all(got_t[:, ~full] == 0)
+    scores = (rng.standard_normal((B * Hkv, T, blocks)) * 2).astype(np.float32)
+    want_g = oracle.indexer_distillation_grad(scores, want_t, ratio, 0.25)
+    got_g = bk.indexer_distillation_grad(scores, want_t, ratio, 0.25)
+    close(got_g, want_g, 1e-5, 1e-6)
+    assert np.allclose(got_g.sum(axis=-1), 0.0, atol=1e-5)                               # softmax and target both sum to one
+    # restricted to the candidates a two-level selection published; some rows get an empty list
+    cand = np.zeros((B * Hkv, T, 8), np.int32); cc = np.zeros((B * Hkv, T), np.int32)
+    for i in range(B * Hkv):
+        _, _, cand[i], cc[i] = oracle.select_blocks_hierarchical(scores[i], 0, ratio, 2, 4, 8)
+    cc[:, T // 2] = 0
+    want_r = oracle.indexer_distillation_grad(scores, want_t, ratio, 0.25, cand.reshape(-1, 8), cc.reshape(-1))
+    got_r = bk.indexer_distillation_grad(scores, want_t, ratio, 0.25, cand.reshape(-1, 8), cc.reshape(-1))
+    close(got_r, want_r, 1e-5, 1e-6)
+    assert np.all(got_r[:, T // 2] == 0)

@@ -408,3 +408,37 @@ def test_indexer_scores_gradient_matches_finite_difference(oracle):
     eps = 1e-3
     numeric = (loss(eps) - loss(-eps)) / (2 * eps)
     assert abs(analytic - numeric) <= 5e-3 * max(1.0, abs(numeric)), (analytic, numeric)
+
+
+# model/indexer_test.go:367-396: restricting to a candidate list masks the scores outside it and renormalises the target inside.
+# With weight 1 the gradient is softmax(masked scores) - restricted target, which exposes both.
+def test_distillation_restricted_to_candidates_known_answer(oracle):
+    scores = np.array([[[1, 2, 3, 4], [5, 6, 7, 8]]], np.float32)
+    target = np.array([[[0.1, 0.2, 0.3, 0.4], [0.25, 0.25, 0.25, 0.25]]], np.float32)
+    cand = np.array([[1, 3], [0, 2]], np.int32); cc = np.array([2, 2], np.int32)
+    # ratio 1 and a sequence of 2 would allow 0 / 1 blocks; rows here stand for late tokens, so place them at positions >= 4
+    big_s = np.zeros((1, 6, 4), np.float32); big_t = np.zeros((1, 6, 4), np.float32)
+    big_s[0, 4:] = scores[0]; big_t[0, 4:] = target[0]
+    big_c = np.full((6, 2), -1, np.int32); big_n = np.zeros(6, np.int32); big_c[4:] = cand; big_n[4:] = cc
+    g = oracle.indexer_distillation_grad(big_s, big_t, 1, 1.0, big_c, big_n)[0, 4:]
+    p0 = np.exp(np.array([2.0, 4.0]) - 4.0); p0 /= p0.sum()
+    assert np.allclose(g[0], [0, p0[0] - 1 / 3, 0, p0[1] - 2 / 3], atol=1e-6)
+    p1 = np.exp(np.array([5.0, 7.0]) - 7.0); p1 /= p1.sum()
+    assert np.allclose(g[1], [p1[0] - 0.5, 0, p1[1] - 0.5, 0], atol=1e-6)
+    # the free form: the gradient of KL(target || softmax(scores)) with respect to the scores
+    rng = np.random.default_rng(2)
+    s = rng.standard_normal((1, 9, 4)).astype(np.float32)
+    t = oracle.indexer_distillation_target(rng.standard_normal((1, 2, 9, 4)).astype(np.float32), rng.standard_normal((1, 1, 4, 4)).astype(np.float32), 2)
+    g = oracle.indexer_distillation_grad(s, t, 2, 1.0)
+    d = rng.standard_normal(s.shape).astype(np.float32)
+    def loss(eps):
+        total = 0.0
+        for tok in range(9):
+            a = min(tok // 2, 4)
+            if a == 0: continue
+            z = (s[0, tok, :a] + eps * d[0, tok, :a]).astype(np.float64)
+            logp = z - z.max() - np.log(np.exp(z - z.max()).sum())
+            total -= float(np.sum(t[0, tok, :a] * logp))
+        return total
+    numeric = (loss(1e-3) - loss(-1e-3)) / 2e-3
+    assert abs(float(np.sum(g.astype(np.float64) * d)) - numeric) <= 1e-3 * max(1.0, abs(numeric))
