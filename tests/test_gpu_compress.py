@@ -392,3 +392,106 @@ def test_indexer_distillation(oracle, bk, B, Hq, Hkv, T, D, ratio):
     got_r = bk.indexer_distillation_grad(scores, want_t, ratio, 0.25, cand.reshape(-1, 8), cc.reshape(-1))
     close(got_r, want_r, 1e-5, 1e-6)
     assert np.all(got_r[:, T // 2] == 0)
+
+
+def _csa_layer_step(ops, x, q, k, v, wc, bias, wq, wk, hw, sel, cnt, cand, ccnt, ratio, window, loss_weight, dout):
+    """Training forward and backward of one sparse compressed attention layer that owns its compressor and indexer
+    (model/train.go:99-169, 227-262, 289-301), from the blocks: the selection is an input (both arms get the same one);
+    the indexer is trained by distillation toward the main attention logits, its key gradient joins the compressed keys'
+    gradient before the compressor's backward, its hidden-state gradient joins the layer input's."""
+    be = ops["be"]
+    B, Hq, T, D = q.shape; Hkv = k.shape[1]; hr = Hq // Hkv; d = x.shape[-1]
+    blocks = (T + ratio - 1) // ratio
+    heads = hw.shape[0]; hd = wq.shape[0]; idim = hd // heads
+    kc = np.zeros((B, Hkv, blocks, D), np.float32); vc = np.zeros_like(kc)
+    for b in range(B):
+        for h in range(Hkv):
+            kc[b, h] = ops["comp"](x[b:b + 1], k[b, h][None], wc, bias, ratio)[0][0]
+            vc[b, h] = ops["comp"](x[b:b + 1], v[b, h][None], wc, bias, ratio)[0][0]
+    og, lg = ops["sparse"](q, kc, vc, sel, cnt)
+    ol = np.zeros_like(q); ll = np.zeros((B, Hq, T), np.float32)
+    for b in range(B):
+        for h in range(Hq):
+            o, l = be.attention_forward(q[b, h], k[b, h // hr], v[b, h // hr], T, T, D, 0, window)
+            ol[b, h] = np.asarray(o).reshape(T, D); ll[b, h] = np.asarray(l).reshape(T)
+    out, lse = ops["merge"](og.reshape(-1, D), lg.reshape(-1), ol.reshape(-1, D), ll.reshape(-1))
+    out = np.asarray(out).reshape(B, Hq, T, D); lse = np.asarray(lse).reshape(B, Hq, T)
+    rc = np.sum(dout.astype(np.float64) * out.astype(np.float64), axis=-1).astype(np.float32)
+    dq, dkc, dvc = ops["sparse_bwd"](q, kc, vc, dout, lse, sel, cnt, rc)
+    # the indexer: scores per (sequence, kv head), distillation gradient, backward through the scores and the two projections
+    target = ops["target"](q, kc, ratio)
+    dx = np.zeros_like(x); dwq = np.zeros_like(wq); dwk = np.zeros_like(wk); dhw = np.zeros_like(hw)
+    for b in range(B):
+        iq = np.asarray(be.matmul_transposed(x[b], wq, T, hd, d)).reshape(T, hd)
+        for h in range(Hkv):
+            i = b * Hkv + h
+            ik = np.asarray(be.matmul_transposed(kc[b, h], wk, blocks, hd, D)).reshape(blocks, hd)
+            scores = np.asarray(be.indexer_scores(iq, ik, hw, T, blocks, heads, idim)).reshape(1, T, blocks)
+            gs = ops["dgrad"](scores, target[i:i + 1], ratio, loss_weight, cand[i], ccnt[i])[0]
+            giq, gik, dhw = ops["idx_bwd"](gs, iq.reshape(T, heads, idim), ik.reshape(blocks, heads, idim), hw, dhw)
+            giq = giq.reshape(T, hd); gik = gik.reshape(blocks, hd)
+            dx[b] += np.asarray(be.matmul(giq, wq, T, d, hd)).reshape(T, d)
+            dwq += np.asarray(be.matmul(np.ascontiguousarray(giq.T), x[b], hd, d, T)).reshape(hd, d)
+            dkc[b, h] += np.asarray(be.matmul(gik, wk, blocks, D, hd)).reshape(blocks, D)
+            dwk += np.asarray(be.matmul(np.ascontiguousarray(gik.T), kc[b, h], hd, D, blocks)).reshape(hd, D)
+    dk = np.zeros_like(k); dv = np.zeros_like(v)
+    for b in range(B):
+        for h in range(Hq):
+            g = ops["attn_bwd"](q[b, h], k[b, h // hr], v[b, h // hr], out[b, h], dout[b, h], lse[b, h], T, T, D, 0, window, rc[b, h],
+                                dq[b, h].ravel(), dk[b, h // hr].ravel(), dv[b, h // hr].ravel())
+            dq[b, h] = g[0].reshape(T, D); dk[b, h // hr] = g[1].reshape(T, D); dv[b, h // hr] = g[2].reshape(T, D)
+    dwc = np.zeros_like(wc); db = np.zeros_like(bias)
+    for b in range(B):
+        for h in range(Hkv):
+            for val, gc, gval in ((k, dkc, dk), (v, dvc, dv)):
+                gh, gv_, gw, gb = ops["comp_bwd"](x[b:b + 1], val[b, h][None], wc, bias, ratio, gc[b, h][None])
+                dx[b] += gh[0]; gval[b, h] += gv_[0]; dwc += gw; db += gb
+    return out, (dq, dk, dv, dx, dwc, db, dwq, dwk, dhw)
+
+
+def test_sparse_compressed_layer_training_step(oracle, bk):
+    rng = np.random.default_rng(41)
+    B, Hq, Hkv, T, D, d, ratio, window, topk, heads, idim, pool, budget = 2, 4, 2, 53, 64, 48, 4, 5, 3, 2, 16, 2, 6
+    blocks = (T + ratio - 1) // ratio
+    x = rng.standard_normal((B, T, d)).astype(np.float32)
+    q = (rng.standard_normal((B, Hq, T, D)) * 0.4).astype(np.float32)
+    k = (rng.standard_normal((B, Hkv, T, D)) * 0.4).astype(np.float32); v = rng.standard_normal((B, Hkv, T, D)).astype(np.float32)
+    wc = (rng.standard_normal((D, d)) * 0.2).astype(np.float32); bias = (rng.standard_normal((ratio, D)) * 0.3).astype(np.float32)
+    wq = (rng.standard_normal((heads * idim, d)) * 0.2).astype(np.float32); wk = (rng.standard_normal((heads * idim, D)) * 0.3).astype(np.float32)
+    hw = np.array([0.7, 1.3], np.float32)
+    dout = rng.standard_normal((B, Hq, T, D)).astype(np.float32)
+    ref = oracle.Backend(0)
+    # the selection and the candidates of the two-level selector, from the oracle's own index scores, for both arms
+    cap = 6
+    sel = np.zeros((B * Hkv, T, topk), np.int32); cnt = np.zeros((B * Hkv, T), np.int32)
+    cand = np.zeros((B * Hkv, T, cap), np.int32); ccnt = np.zeros((B * Hkv, T), np.int32)
+    for b in range(B):
+        iq = ref.matmul_transposed(x[b], wq, T, heads * idim, d)
+        for h in range(Hkv):
+            kc = oracle.compressor_forward(x[b:b + 1], k[b, h][None], wc, bias, ratio)[0][0]
+            ik = ref.matmul_transposed(kc, wk, blocks, heads * idim, D)
+            scores = np.asarray(ref.indexer_scores(iq, ik, hw, T, blocks, heads, idim)).reshape(T, blocks)
+            i = b * Hkv + h
+            sel[i], cnt[i], cand[i], ccnt[i] = oracle.select_blocks_hierarchical(scores, 0, ratio, topk, pool, budget)
+    sel = np.maximum(sel, 0)
+
+    def ref_attn_bwd(q_, k_, v_, out_, dout_, lse_, ql, kl, hdim, off, win, rc_, dq_, dk_, dv_):
+        return ref.attention_backward(q_, k_, v_, dout_, lse_, ql, kl, hdim, off, win, row_correction=rc_, dq=dq_, dk=dk_, dv=dv_)
+
+    def dev_attn_bwd(q_, k_, v_, out_, dout_, lse_, ql, kl, hdim, off, win, rc_, dq_, dk_, dv_):
+        return bk.attention_backward(q_, k_, v_, out_, dout_, lse_, ql, kl, hdim, off, win, row_correction=rc_, dq=dq_, dk=dk_, dv=dv_)
+
+    want_o, want = _csa_layer_step(dict(be=ref, comp=oracle.compressor_forward, comp_bwd=oracle.compressor_backward, sparse=oracle.compressed_attention_sparse_forward,
+                                        sparse_bwd=oracle.compressed_attention_sparse_backward, merge=oracle.merge_branches, target=oracle.indexer_distillation_target,
+                                        dgrad=oracle.indexer_distillation_grad, idx_bwd=oracle.indexer_scores_backward, attn_bwd=ref_attn_bwd),
+                                   x, q, k, v, wc, bias, wq, wk, hw, sel, cnt, cand, ccnt, ratio, window, 0.1, dout)
+    got_o, got = _csa_layer_step(dict(be=bk, comp=bk.compressor_forward, comp_bwd=bk.compressor_backward, sparse=bk.compressed_attention_sparse_forward,
+                                      sparse_bwd=bk.compressed_attention_sparse_backward, merge=bk.attention_merge, target=bk.indexer_distillation_target,
+                                      dgrad=bk.indexer_distillation_grad, idx_bwd=bk.indexer_scores_backward, attn_bwd=dev_attn_bwd),
+                                 x, q, k, v, wc, bias, wq, wk, hw, sel, cnt, cand, ccnt, ratio, window, 0.1, dout)
+    close(got_o, want_o, 1e-4, 1e-5)
+    names = ("dq", "dk", "dv", "dx", "dwc", "dbias", "dwq", "dwk", "dhw")
+    for name, g, w in zip(names, got, want):
+        scale = float(np.max(np.abs(w))) if w.size else 1.0
+        err = float(np.max(np.abs(np.asarray(g, np.float64) - np.asarray(w, np.float64))))
+        assert err <= 3e-4 * max(scale, 1.0) + 3e-5, (name, err, scale)
