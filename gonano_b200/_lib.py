@@ -67,6 +67,7 @@ SIGNATURES = {
     "gn_compressor_forward": (I, [vp, vp, vp, vp, I, I, I, I, I, vp, vp]),
     "gn_compressor_backward": (I, [vp, vp, vp, vp, vp, vp, I, I, I, I, I, vp, vp, vp, vp]),
     "gn_compressed_attention_forward": (I, [vp, vp, vp, I, I, I, I, I, I, I, vp, vp]),
+    "gn_compressed_attention_forward_at": (I, [vp, vp, vp, I, I, I, I, I, I, I, I, vp, vp]),
     "gn_compressed_attention_backward": (I, [vp, vp, vp, vp, vp, vp, I, I, I, I, I, I, I, vp, vp, vp]),
     "gn_indexer_scores_backward": (I, [vp, vp, vp, vp, I, I, I, I, vp, vp, vp]),
     "gn_indexer_distillation_target": (I, [vp, vp, I, I, I, I, I, I, I, vp]),

@@ -155,12 +155,13 @@ class CudaBackend:
                                               ptr(gh), ptr(gv), ptr(gw), ptr(gb)))
         return gh, gv, gw, gb
 
-    def compressed_attention_forward(self, q, kc, vc, ratio):
-        """compressedAttentionForward (model/compress_attention.go:624-673): q [B,Hq,T,D], kc / vc [B,Hkv,blocks,D]."""
+    def compressed_attention_forward(self, q, kc, vc, ratio, offset=0):
+        """compressedAttentionForward (model/compress_attention.go:624-673): q [B,Hq,T,D], kc / vc [B,Hkv,blocks,D]; with offset > 0 the
+        T tokens stand at positions offset .. over the cached blocks (forwardCompressed, :962-1003)."""
         q, kc, vc = _f32(q), _f32(kc), _f32(vc)
         B, Hq, T, D = q.shape; Hkv, blocks = kc.shape[1], kc.shape[2]
         out = np.zeros_like(q); lse = np.zeros((B, Hq, T), np.float32)
-        check(self.lib.gn_compressed_attention_forward(ptr(q), ptr(kc), ptr(vc), B, Hq, Hkv, T, D, blocks, ratio, ptr(out), ptr(lse)))
+        check(self.lib.gn_compressed_attention_forward_at(ptr(q), ptr(kc), ptr(vc), B, Hq, Hkv, T, D, blocks, ratio, offset, ptr(out), ptr(lse)))
         return out, lse
 
     def compressed_attention_backward(self, q, kc, vc, dout, lse, ratio, row_correction=None, dq=None, dkc=None, dvc=None):

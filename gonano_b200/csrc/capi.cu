@@ -354,14 +354,19 @@ int gn_compressor_backward(const float* hidden, const float* value, const float*
 // compressedAttentionForward (model/compress_attention.go:624-673), no segment mask
 int gn_compressed_attention_forward(const float* query, const float* key_c, const float* value_c, int batch, int n_head, int n_kv_head, int seq, int head_dim,
                                     int blocks, int ratio, float* out, float* lse) {
+  return gn_compressed_attention_forward_at(query, key_c, value_c, batch, n_head, n_kv_head, seq, head_dim, blocks, ratio, 0, out, lse);
+}
+// the dense loop of forwardCompressed (model/compress_attention.go:962-1003): `seq` new tokens at positions position_offset .. over `blocks` cached blocks
+int gn_compressed_attention_forward_at(const float* query, const float* key_c, const float* value_c, int batch, int n_head, int n_kv_head, int seq, int head_dim,
+                                       int blocks, int ratio, int position_offset, float* out, float* lse) {
   if (batch <= 0 || seq <= 0) return GN_OK;
-  GN_REQUIRE(query && key_c && value_c && out && blocks >= 0, "compressed_attention_forward: bad argument");
+  GN_REQUIRE(query && (blocks == 0 || (key_c && value_c)) && out && blocks >= 0 && position_offset >= 0, "compressed_attention_forward: bad argument");
   GN_BEGIN();
   const size_t nq = (size_t)batch * n_head * seq * head_dim, nk = (size_t)batch * n_kv_head * blocks * head_dim;
   const float* dq = st.in(query, nq); const float* dk = st.in(key_c, nk); const float* dv = st.in(value_c, nk);
   float* dout = st.out(out, nq); float* dl = lse ? st.out(lse, (size_t)batch * n_head * seq) : nullptr;
   if (st.status != GN_OK) return st.status;
-  GN_TRY(compressed_attention_launch(dq, dk, dv, batch, n_head, n_kv_head, seq, head_dim, blocks, ratio, dout, dl, nullptr, nullptr, 0, s));
+  GN_TRY(compressed_attention_launch(dq, dk, dv, batch, n_head, n_kv_head, seq, head_dim, blocks, ratio, dout, dl, nullptr, nullptr, 0, position_offset, s));
   GN_END();
 }
 // compressedAttentionBackward (model/compress_attention.go:735-781), no segment mask; the three gradients accumulate
@@ -391,7 +396,7 @@ int gn_compressed_attention_sparse_forward(const float* query, const float* key_
   const int32_t* ds = st.in(selection, nt * topk); const int32_t* dc = st.in(counts, nt);
   float* dout = st.out(out, nq); float* dl = lse ? st.out(lse, (size_t)batch * n_head * seq) : nullptr;
   if (st.status != GN_OK) return st.status;
-  GN_TRY(compressed_attention_launch(dq, dk, dv, batch, n_head, n_kv_head, seq, head_dim, blocks, 1, dout, dl, ds, dc, topk, s));
+  GN_TRY(compressed_attention_launch(dq, dk, dv, batch, n_head, n_kv_head, seq, head_dim, blocks, 1, dout, dl, ds, dc, topk, 0, s));
   GN_END();
 }
 // compressedAttentionBackwardSparse (model/compress_attention.go:376-433), no segment mask; the three gradients accumulate

@@ -69,21 +69,21 @@ __global__ void __launch_bounds__(256) compressor_bias_bwd_kernel(const float* _
   grad_bias[idx] = acc;
 }
 
-// one warp per (batch, query head, token): keys = compressed blocks 0 .. t / ratio - 1
+// one warp per (batch, query head, token): keys = compressed blocks 0 .. (offset + t) / ratio - 1
 template <int DP>
 __global__ void __launch_bounds__(256) compressed_attention_kernel(const float* __restrict__ q, const float* __restrict__ kc, const float* __restrict__ vc, int B,
                                                                    int Hq, int Hkv, int T, int D, int blocks, int ratio, float* __restrict__ out,
                                                                    float* __restrict__ lse, const int32_t* __restrict__ selection,
-                                                                   const int32_t* __restrict__ counts, int topk) {
+                                                                   const int32_t* __restrict__ counts, int topk, int offset) {
   constexpr int PER = DP / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t idx = (int64_t)blockIdx.x * 8 + warp;
   if (idx >= (int64_t)B * Hq * T) return;
   const int t = (int)(idx % T); const int64_t bh = idx / T; const int h = (int)(bh % Hq); const int b = (int)(bh / Hq);
   const int64_t kvh = (int64_t)b * Hkv + h / (Hq / Hkv);
-  // dense: the blocks before the query's own; sparse: the token's selected blocks, in selection order
+  // dense: the blocks before the query's own (token t stands at position offset + t); sparse: the token's selected blocks, in selection order
   const int32_t* sel = selection ? selection + (kvh * T + t) * topk : nullptr;
-  const int nk = selection ? max(0, min(counts[kvh * T + t], topk)) : min(t / ratio, blocks);
+  const int nk = selection ? max(0, min(counts[kvh * T + t], topk)) : min((offset + t) / ratio, blocks);
   const float* qr = q + idx * D;
   const int64_t kbase = kvh * blocks * D;
   float qv[PER], acc[PER];
@@ -525,15 +525,15 @@ int compressor_pool_backward_launch(const float* value, const float* probabiliti
 }
 
 int compressed_attention_launch(const float* q, const float* kc, const float* vc, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* out, float* lse,
-                                const int32_t* selection, const int32_t* counts, int topk, cudaStream_t s) {
+                                const int32_t* selection, const int32_t* counts, int topk, int offset, cudaStream_t s) {
   GN_REQUIRE(D > 0 && D <= 128, "compressed attention: head_dim %d outside (0,128]", D);
-  GN_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && ratio >= 1, "compressed attention: %d query heads, %d kv heads, ratio %d", Hq, Hkv, ratio);
+  GN_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && ratio >= 1 && offset >= 0, "compressed attention: %d query heads, %d kv heads, ratio %d, offset %d", Hq, Hkv, ratio, offset);
   const int64_t n = (int64_t)B * Hq * T;
   if (n <= 0) return GN_OK;
   const unsigned grid = (unsigned)ceil_div(n, 8);
-  if (D <= 32) compressed_attention_kernel<32><<<grid, 256, 0, s>>>(q, kc, vc, B, Hq, Hkv, T, D, blocks, ratio, out, lse, selection, counts, topk);
-  else if (D <= 64) compressed_attention_kernel<64><<<grid, 256, 0, s>>>(q, kc, vc, B, Hq, Hkv, T, D, blocks, ratio, out, lse, selection, counts, topk);
-  else compressed_attention_kernel<128><<<grid, 256, 0, s>>>(q, kc, vc, B, Hq, Hkv, T, D, blocks, ratio, out, lse, selection, counts, topk);
+  if (D <= 32) compressed_attention_kernel<32><<<grid, 256, 0, s>>>(q, kc, vc, B, Hq, Hkv, T, D, blocks, ratio, out, lse, selection, counts, topk, offset);
+  else if (D <= 64) compressed_attention_kernel<64><<<grid, 256, 0, s>>>(q, kc, vc, B, Hq, Hkv, T, D, blocks, ratio, out, lse, selection, counts, topk, offset);
+  else compressed_attention_kernel<128><<<grid, 256, 0, s>>>(q, kc, vc, B, Hq, Hkv, T, D, blocks, ratio, out, lse, selection, counts, topk, offset);
   GN_LAUNCH_CHECK();
   return GN_OK;
 }

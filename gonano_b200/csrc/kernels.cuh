@@ -68,8 +68,9 @@ int compressor_pool_launch(const float* logits, const float* bias, const float* 
 int compressor_pool_backward_launch(const float* value, const float* probabilities, const float* compressed, const float* grad_compressed, int B, int T, int C,
                                     int ratio, float* grad_logits, float* grad_value, float* grad_bias, cudaStream_t s);
 // selection == nullptr: every block before the query's own; else the token's selected blocks ([B * Hkv, T, topk] with counts [B * Hkv, T])
+// (token t stands at position offset + t: offset > 0 is the cached inference form)
 int compressed_attention_launch(const float* q, const float* kc, const float* vc, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* out, float* lse,
-                                const int32_t* selection, const int32_t* counts, int topk, cudaStream_t s);
+                                const int32_t* selection, const int32_t* counts, int topk, int offset, cudaStream_t s);
 // backward, dense (selection null) or over selected blocks: dq, dkc, dvc are accumulated into; rowcorr nullable (then delta_scratch [B * Hq * T] is used)
 int compressed_attention_backward_launch(const float* q, const float* kc, const float* vc, const float* dout, const float* lse, const float* rowcorr,
                                          float* delta_scratch, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* dq, float* dkc, float* dvc,

@@ -121,6 +121,11 @@ int gn_compressor_backward(const float* hidden, const float* value, const float*
                            float* grad_weight, float* grad_bias);
 int gn_compressed_attention_forward(const float* query, const float* key_c, const float* value_c, int batch, int n_head, int n_kv_head, int seq,
                                     int head_dim, int blocks, int ratio, float* out, float* lse);
+/* The same for `seq` new tokens at positions position_offset .. position_offset + seq - 1 over `blocks` cached compressed
+ * blocks: the dense global branch of the cached inference path (forwardCompressed, model/compress_attention.go:962-1003);
+ * token t takes min((position_offset + t) / ratio, blocks) blocks.  One decode step is seq = 1. */
+int gn_compressed_attention_forward_at(const float* query, const float* key_c, const float* value_c, int batch, int n_head, int n_kv_head, int seq, int head_dim,
+                                       int blocks, int ratio, int position_offset, float* out, float* lse);
 /* compressedAttentionBackward (model/compress_attention.go:735-781): dq, dkc, dvc are accumulated into; row_correction
  * (nullable, [batch, n_head, seq]) is the reference's rowCorrection for a branch whose output was merged with another. */
 int gn_compressed_attention_backward(const float* query, const float* key_c, const float* value_c, const float* out_grad, const float* lse,

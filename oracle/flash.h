@@ -125,6 +125,24 @@ inline void compressed_attention_forward(const Backend& bk, const float* q, cons
     }
 }
 
+// The cached inference form (forwardCompressed, model/compress_attention.go:962-1003): T new tokens at positions offset .. over
+// `blocks` cached compressed blocks; token t attends to the first min((offset + t) / ratio, blocks) of them, one row at a time.
+inline void compressed_attention_forward_at(const Backend& bk, const float* q, const float* kc, const float* vc, int B, int Hq, int Hkv, int T, int D, int blocks,
+                                            int ratio, int offset, float* out, float* lse) {
+  const int hr = Hq / Hkv;
+  for (int b = 0; b < B; ++b)
+    for (int h = 0; h < Hq; ++h) {
+      const size_t qi = (size_t)b * Hq + h;
+      const size_t kbase = ((size_t)b * Hkv + h / hr) * blocks * D;
+      for (int t = 0; t < T; ++t) {
+        const int count = std::min((offset + t) / ratio, blocks);
+        float* o = out + (qi * T + t) * D;
+        if (count == 0) { std::fill(o, o + D, 0.0f); if (lse) lse[qi * T + t] = -INFINITY; continue; }
+        bk.attention_forward(q + (qi * T + t) * D, kc + kbase, vc + kbase, 1, count, D, count, -1, nullptr, 0, o, lse ? lse + qi * T + t : nullptr);
+      }
+    }
+}
+
 // compressedAttentionBackward (model/compress_attention.go:735-781, no segment mask): per block the ordinary attention
 // backward of its queries against the blocks before it; dq [B, Hq, T, D], dkc / dvc [B, Hkv, blocks, D] are accumulated into.
 // row_correction (nullable, [B, Hq, T]) replaces sum_j p_j dp_j when the branch's output was merged with another branch.

@@ -609,6 +609,10 @@ void or_compressed_attention_sparse_backward(int m, const float* q, const float*
                                              float* dkc, float* dvc) {
   BK(m); gnor::compressed_attention_sparse_backward(bk, q, kc, vc, dout, lse, rowcorr, selection, counts, B, Hq, Hkv, T, D, blocks, topk, dq, dkc, dvc);
 }
+void or_compressed_attention_forward_at(int m, const float* q, const float* kc, const float* vc, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, int offset,
+                                        float* out, float* lse) {
+  BK(m); gnor::compressed_attention_forward_at(bk, q, kc, vc, B, Hq, Hkv, T, D, blocks, ratio, offset, out, lse);
+}
 void or_compressed_attention_backward(int m, const float* q, const float* kc, const float* vc, const float* dout, const float* lse, const float* rowcorr, int B,
                                       int Hq, int Hkv, int T, int D, int blocks, int ratio, float* dq, float* dkc, float* dvc) {
   BK(m); gnor::compressed_attention_backward(bk, q, kc, vc, dout, lse, rowcorr, B, Hq, Hkv, T, D, blocks, ratio, dq, dkc, dvc);

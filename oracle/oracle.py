@@ -681,3 +681,12 @@ def indexer_distillation_grad(scores, target, ratio, weight, candidates=None, ca
     lib().or_indexer_distillation_grad(_f(scores), _f(target), _i(cand) if cand is not None else None, _i(cc) if cand is not None else None,
                                        0 if cand is None else cand.shape[-1], C.c_int64(n * T), blocks, T, ratio, C.c_float(weight), _f(grad))
     return grad
+
+
+def compressed_attention_forward_at(q, kc, vc, ratio, offset, mode=0):
+    """The dense global branch of the cached inference path (model/compress_attention.go:962-1003): T tokens at positions offset .. ."""
+    q, kc, vc = f32(q), f32(kc), f32(vc)
+    B, Hq, T, D = q.shape; Hkv, blocks = kc.shape[1], kc.shape[2]
+    out = np.zeros_like(q); lse = np.zeros((B, Hq, T), np.float32)
+    lib().or_compressed_attention_forward_at(mode, _f(q), _f(kc), _f(vc), B, Hq, Hkv, T, D, blocks, ratio, offset, _f(out), _f(lse))
+    return out, lse

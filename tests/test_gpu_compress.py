@@ -495,3 +495,28 @@ def test_sparse_compressed_layer_training_step(oracle, bk):
         scale = float(np.max(np.abs(w))) if w.size else 1.0
         err = float(np.max(np.abs(np.asarray(g, np.float64) - np.asarray(w, np.float64))))
         assert err <= 3e-4 * max(scale, 1.0) + 3e-5, (name, err, scale)
+
+
+# the dense global branch of the cached inference path (model/compress_attention.go:962-1003): one decode step and a
+# continuation of several tokens over cached blocks; at offset 0 it is the training form
+@pytest.mark.parametrize("B,Hq,Hkv,T,D,ratio,blocks,offset", [(4, 8, 1, 1, 128, 4, 51, 203), (2, 6, 2, 7, 64, 4, 10, 30), (1, 2, 2, 5, 32, 8, 3, 100),
+                                                              (2, 4, 2, 1, 128, 4, 10, 3)])
+def test_compressed_attention_forward_cached(oracle, bk, B, Hq, Hkv, T, D, ratio, blocks, offset):
+    rng = np.random.default_rng(offset + T)
+    q = (rng.standard_normal((B, Hq, T, D)) * 0.4).astype(np.float32)
+    kc = (rng.standard_normal((B, Hkv, blocks, D)) * 0.4).astype(np.float32); vc = rng.standard_normal((B, Hkv, blocks, D)).astype(np.float32)
+    want, want_l = oracle.compressed_attention_forward_at(q, kc, vc, ratio, offset)
+    got, got_l = bk.compressed_attention_forward(q, kc, vc, ratio, offset)
+    close(got, want, 1e-4, 1e-5); close(got_l, want_l, 1e-4, 1e-5)
+    if offset < ratio:
+        assert np.all(got[:, :, :ratio - offset] == 0)
+    # engine == recompute (inference/inference_test.go:306-440 checks the cached path against a full forward): the last
+    # rows of a full-sequence pass equal the cached continuation when the cache holds every block those rows may see
+    if (offset + T + ratio - 1) // ratio <= blocks:
+        full_T = offset + T
+        fq = (rng.standard_normal((B, Hq, full_T, D)) * 0.4).astype(np.float32); fq[:, :, offset:] = q
+        nb = (full_T + ratio - 1) // ratio
+        fk = np.zeros((B, Hkv, nb, D), np.float32); fv = np.zeros_like(fk)
+        m = min(nb, blocks); fk[:, :, :m] = kc[:, :, :m]; fv[:, :, :m] = vc[:, :, :m]
+        whole, whole_l = bk.compressed_attention_forward(fq, fk, fv, ratio)
+        close(whole[:, :, offset:], got, 1e-5, 1e-6); close(whole_l[:, :, offset:], got_l, 1e-5, 1e-6)
