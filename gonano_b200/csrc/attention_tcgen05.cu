@@ -50,8 +50,10 @@ __device__ long long g_attn_trace[256];
 
 struct AttnTc {
   int B, Hq, Hkv, Tq, Tk, window, offset;
-  float* out; int64_t o_bstride, o_tstride;
+  int ratio, shift;   // the last key a query at position p sees is p / ratio - shift: (1, 0) causal over positions, (r, 1) over blocks of r positions
+  float* out; int64_t o_bstride, o_tstride, o_hstride;
   float* lse;
+  __device__ __forceinline__ int last_key(int pos) const { return ratio == 1 ? pos : pos / ratio - shift; }
 };
 
 // Packed tf32 splits of the operands: Q as [B * Tq, Hq * 128], K and V as [B * Tk, Hkv * 128], hi and lo.
@@ -65,7 +67,7 @@ __global__ void __launch_bounds__(256) attn_tc_split_kernel(AttnShape sh, const 
   const float* src; int64_t dst;
   if (idx < nq) {
     const int h = (int)(idx % sh.Hq); const int64_t r = idx / sh.Hq; const int64_t b = r / sh.Tq, t = r % sh.Tq;
-    src = q + b * sh.q_bstride + t * sh.q_tstride + (int64_t)h * AD; dst = idx * AD;
+    src = q + b * sh.q_bstride + t * sh.q_tstride + (int64_t)h * (sh.q_hstride ? sh.q_hstride : AD); dst = idx * AD;
   } else {
     const int64_t i = idx - nq; const bool isv = i >= nk; const int64_t e = isv ? i - nk : i;
     const int h = (int)(e % sh.Hkv); const int64_t r = e / sh.Hkv; const int64_t b = r / sh.Tk, t = r % sh.Tk;
@@ -97,7 +99,7 @@ __global__ void __launch_bounds__(352, 1) attn_tc_fwd_kernel(const __grid_consta
   const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * AQ;   // the long tiles first
   const int hq = blockIdx.y, b = blockIdx.z, hk = hq / (p.Hq / p.Hkv);
   const int qvalid = min(AQ, p.Tq - q0);
-  const int k_end = min(p.Tk, p.offset + q0 + qvalid);
+  const int k_end = min(p.Tk, p.last_key(p.offset + q0 + qvalid - 1) + 1);
   int k_begin = p.window >= 0 ? max(0, p.offset + q0 - p.window) : 0;
   k_begin = (k_begin / AKV) * AKV;
   const int n = k_end > k_begin ? (k_end - k_begin + AKV - 1) / AKV : 0;   // key steps of this CTA
@@ -210,7 +212,7 @@ __global__ void __launch_bounds__(352, 1) attn_tc_fwd_kernel(const __grid_consta
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const uint32_t sw = (uint32_t)(row & 7);      // 128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r % 8)
-    const int qpos = p.offset + q0 + row;
+    const int qpos = p.last_key(p.offset + q0 + row);   // the last key this row sees
     float* xch = reinterpret_cast<float*>(gen + XCH);   // [2 steps][2 halves][128 rows]
     constexpr float kLog2e = 1.4426950408889634f;
     float m_used = -1e30f, l_run = 0.0f;
@@ -256,7 +258,7 @@ __global__ void __launch_bounds__(352, 1) attn_tc_fwd_kernel(const __grid_consta
       // mask (only in steps that touch the diagonal, the window's edge or the end of the sequence): key after the
       // query, key further back than the window, key past the sequence
       const int c0k = kv0 + half * 32;   // first key of this thread's columns
-      const bool clean = kv0 + AKV - 1 <= p.offset + q0 && kv0 + AKV - 1 < p.Tk && (p.window < 0 || p.offset + q0 + AQ - 1 - kv0 <= p.window);
+      const bool clean = kv0 + AKV - 1 <= p.last_key(p.offset + q0) && kv0 + AKV - 1 < p.Tk && (p.window < 0 || p.offset + q0 + AQ - 1 - kv0 <= p.window);
       float mx = -1e30f;
       if (clean) {
 #pragma unroll
@@ -343,7 +345,7 @@ __global__ void __launch_bounds__(352, 1) attn_tc_fwd_kernel(const __grid_consta
       // then eight lanes write the 128 contiguous bytes of a row.
       float* stg = reinterpret_cast<float*>(gen + P_HI) + (warp - 2) * (32 * 36);
       const int rr0 = lane >> 3, cc = (lane & 7) * 4;
-      float* dst0 = p.out + (int64_t)b * p.o_bstride + (int64_t)(q0 + quarter * 32) * p.o_tstride + (int64_t)hq * AD + half * 64;
+      float* dst0 = p.out + (int64_t)b * p.o_bstride + (int64_t)(q0 + quarter * 32) * p.o_tstride + (int64_t)hq * p.o_hstride + half * 64;
       const int rows_valid = qvalid - quarter * 32;   // rows of this warp inside the sequence
 #pragma unroll
       for (int c0 = 0; c0 < 64; c0 += 32) {
@@ -365,7 +367,7 @@ __global__ void __launch_bounds__(352, 1) attn_tc_fwd_kernel(const __grid_consta
         }
         __syncwarp();
       }
-      if (p.lse && half == 0 && row < qvalid) p.lse[((int64_t)b * p.Hq + hq) * p.Tq + q0 + row] = l_run > 0.0f ? m_used + logf(l_run) : -1e30f;
+      if (p.lse && half == 0 && row < qvalid) p.lse[((int64_t)b * p.Hq + hq) * p.Tq + q0 + row] = l_run > 0.0f ? m_used + logf(l_run) : (p.shift ? -INFINITY : -1e30f);
       if (threadIdx.x == 64) AT_TRACE(9);
     }
   }
@@ -655,6 +657,7 @@ void attention_tc_enable(int on) { g_attn_tc.store(on, std::memory_order_relaxed
 bool attention_tc_ok(const AttnShape& sh, const void* p0, const void* p1, const void* p2, const void* p3) {
   auto al = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   if (g_attn_tc.load(std::memory_order_relaxed) == 0) return false;
+  if (sh.key_ratio < 1 || (sh.key_ratio > 1 && sh.window >= 0) || sh.q_hstride % 4 != 0 || sh.o_hstride % 4 != 0 || sh.Tk < 1) return false;
   return sh.D == AD && sh.segment_ids == nullptr && sh.Hkv > 0 && sh.Hq % sh.Hkv == 0 && sh.offset0 >= 0 && al(p0) && al(p1) && al(p2) && al(p3) &&
          sh.q_tstride % 4 == 0 && sh.q_bstride % 4 == 0 && sh.kv_tstride % 4 == 0 && sh.kv_bstride % 4 == 0 && sh.kv_hstride % 4 == 0 &&
          sh.o_tstride % 4 == 0 && sh.o_bstride % 4 == 0 && (int64_t)sh.B * std::max(sh.Tq, sh.Tk) < (1ll << 30);
@@ -680,7 +683,8 @@ int attention_tc_forward(const AttnShape& sh, const float* q, const float* k, co
   if (configured.first()) { GN_CUDA(cudaFuncSetAttribute(attn_tc_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFwd)); }
   AttnTc p{};
   p.B = sh.B; p.Hq = sh.Hq; p.Hkv = sh.Hkv; p.Tq = sh.Tq; p.Tk = sh.Tk; p.window = sh.window; p.offset = sh.offset0;
-  p.out = out; p.o_bstride = sh.o_bstride; p.o_tstride = sh.o_tstride; p.lse = lse;
+  p.ratio = sh.key_ratio; p.shift = sh.key_ratio > 1 ? 1 : 0;
+  p.out = out; p.o_bstride = sh.o_bstride; p.o_tstride = sh.o_tstride; p.o_hstride = sh.o_hstride ? sh.o_hstride : AD; p.lse = lse;
   dim3 grid(ceil_div(sh.Tq, AQ), sh.Hq, sh.B);
   GN_REQUIRE(sh.B <= 65535 && sh.Hq <= 65535, "attention: %d sequences x %d heads exceed the grid", sh.B, sh.Hq);
   attn_tc_fwd_kernel<<<grid, 352, kSmemFwd, s>>>(mqh, mql, mkh, mkl, mvh, mvl, p, err);
@@ -692,7 +696,7 @@ int attention_tc_forward(const AttnShape& sh, const float* q, const float* k, co
 // window, no segment mask; its scratch (P and dS as hi/lo, 16 bytes per score) below 8 GiB.
 bool attention_tc_backward_ok(const AttnShape& sh, const void* p0, const void* p1, const void* p2, const void* p3, const void* p4) {
   if (!attention_tc_ok(sh, p0, p1, p2, p3) || (reinterpret_cast<uintptr_t>(p4) & 15) != 0) return false;
-  if (sh.Tq != sh.Tk || sh.offset0 != 0 || (sh.window >= 0 && sh.window < sh.Tk - 1)) return false;
+  if (sh.Tq != sh.Tk || sh.offset0 != 0 || (sh.window >= 0 && sh.window < sh.Tk - 1) || sh.key_ratio != 1 || sh.q_hstride != 0 || sh.o_hstride != 0) return false;
   const int64_t Tp = (int64_t)(sh.Tq + 127) / 128 * 128;
   if ((int64_t)sh.B * sh.Hq * Tp >= (1ll << 31) / 2) return false;
   return (int64_t)sh.B * sh.Hq * Tp * Tp * 16 <= (8ll << 30);

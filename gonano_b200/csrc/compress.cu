@@ -530,6 +530,19 @@ int compressed_attention_launch(const float* q, const float* kc, const float* vc
   GN_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && ratio >= 1 && offset >= 0, "compressed attention: %d query heads, %d kv heads, ratio %d, offset %d", Hq, Hkv, ratio, offset);
   const int64_t n = (int64_t)B * Hq * T;
   if (n <= 0) return GN_OK;
+#ifdef GN_HAVE_TCGEN05
+  // head_dim 128, every block before the query's own: the tensor-core attention forward with keys counted in blocks.
+  // Worth its fixed cost (operand split, 128-row query tiles) from a few thousand scores per head on.
+  if (!selection && D == 128 && blocks >= 1 && (int64_t)T * blocks >= 4096) {
+    AttnShape sh;
+    sh.B = B; sh.Hq = Hq; sh.Hkv = Hkv; sh.D = D; sh.Tq = T; sh.Tk = blocks;
+    sh.q_bstride = (int64_t)Hq * T * D; sh.q_tstride = D; sh.q_hstride = (int64_t)T * D;
+    sh.kv_bstride = (int64_t)Hkv * blocks * D; sh.kv_tstride = D; sh.kv_hstride = (int64_t)blocks * D;
+    sh.o_bstride = sh.q_bstride; sh.o_tstride = D; sh.o_hstride = sh.q_hstride;
+    sh.window = -1; sh.offset0 = offset; sh.key_ratio = ratio; sh.tensor = 1;
+    if (ratio > 1 && attention_tc_ok(sh, q, kc, vc, out)) return attention_tc_forward(sh, q, kc, vc, out, lse, s);
+  }
+#endif
   const unsigned grid = (unsigned)ceil_div(n, 8);
   if (D <= 32) compressed_attention_kernel<32><<<grid, 256, 0, s>>>(q, kc, vc, B, Hq, Hkv, T, D, blocks, ratio, out, lse, selection, counts, topk, offset);
   else if (D <= 64) compressed_attention_kernel<64><<<grid, 256, 0, s>>>(q, kc, vc, B, Hq, Hkv, T, D, blocks, ratio, out, lse, selection, counts, topk, offset);

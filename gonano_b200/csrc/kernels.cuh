@@ -50,10 +50,12 @@ int indexer_block_max_launch(float* dst, const float* scores, int rows, int bloc
 struct AttnShape {
   int B = 1, Hq = 1, Hkv = 1, D = 0, Tq = 0, Tk = 0;
   int64_t q_bstride = 0, q_tstride = 0;
+  int64_t q_hstride = 0, o_hstride = 0;   // 0: heads are D apart inside a token (the usual [token, head, D] layout)
   int64_t kv_bstride = 0, kv_tstride = 0, kv_hstride = 0;
   int64_t o_bstride = 0, o_tstride = 0;
   int window = -1;
   int offset0 = 0;
+  int key_ratio = 1;   // > 1: keys are blocks of key_ratio positions; the query at position p sees the blocks before its own, j < p / key_ratio (tensor-core forward only)
   const int32_t* segment_ids = nullptr;  // [Tk] shared by all rows (Tier A only)
   int seg_len = 0;
   int tensor = 0;   // 1: head_dim 128 may run on the tensor cores in 3xTF32 (forward and backward)

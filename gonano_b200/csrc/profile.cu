@@ -164,6 +164,38 @@ extern "C" int gn_profile_kernel(gn_ctx* ctx, const char* kernel, const int64_t*
       return attention_backward_launch(sh, qkv, kp, vp, o, dout, lse, nullptr, dqkv, dqkv + (int64_t)Hq * D, dqkv + (int64_t)(Hq + Hkv) * D, 0, delta, s);
     });
   }
+  if (k == "compressed_attention_fwd" || k == "compressed_attention_bwd" || k == "compressed_attention_sparse_fwd" || k == "compressed_attention_sparse_bwd") {
+    // the global branch of a compressed attention layer: {batch, n_head, n_kv_head, head_dim, seq, ratio[, topk]}
+    GN_REQUIRE(n_dims >= 6, "%s wants {batch, n_head, n_kv_head, head_dim, seq, ratio[, topk]}", kernel);
+    const int B = (int)dims[0], Hq = (int)dims[1], Hkv = (int)dims[2], D = (int)dims[3], T = (int)dims[4], ratio = (int)dims[5];
+    const int topk = n_dims > 6 ? (int)dims[6] : 0;
+    const bool sparse = k.find("sparse") != std::string::npos;
+    GN_REQUIRE(ratio >= 1 && T >= 1 && (!sparse || topk >= 1), "%s: ratio %d, seq %d, topk %d", kernel, ratio, T, topk);
+    const int blocks = (T + ratio - 1) / ratio;
+    const int64_t nq = (int64_t)B * Hq * T * D, nk = (int64_t)B * Hkv * blocks * D, nt = (int64_t)B * Hq * T;
+    float *q, *kc, *vc, *o, *lse, *dout, *dq, *dk, *dv, *delta, *scores = nullptr;
+    int32_t *sel = nullptr, *cnt = nullptr;
+    GN_TRY(bufs.get(&q, (size_t)nq)); GN_TRY(bufs.get(&kc, (size_t)nk)); GN_TRY(bufs.get(&vc, (size_t)nk)); GN_TRY(bufs.get(&o, (size_t)nq));
+    GN_TRY(bufs.get(&lse, (size_t)nt)); GN_TRY(bufs.get(&dout, (size_t)nq)); GN_TRY(bufs.get(&dq, (size_t)nq)); GN_TRY(bufs.get(&dk, (size_t)nk));
+    GN_TRY(bufs.get(&dv, (size_t)nk)); GN_TRY(bufs.get(&delta, (size_t)nt));
+    GN_TRY(synth(q, nq, -0.6f, 0.6f, 21, s)); GN_TRY(synth(kc, nk, -0.6f, 0.6f, 22, s)); GN_TRY(synth(vc, nk, -1, 1, 23, s)); GN_TRY(synth(dout, nq, -1, 1, 24, s));
+    if (sparse) {
+      // a selection per (sequence, kv head) from synthetic index scores
+      GN_TRY(bufs.get(&scores, (size_t)T * blocks));
+      GN_TRY(bufs.get(&sel, (size_t)B * Hkv * T * topk)); GN_TRY(bufs.get(&cnt, (size_t)B * Hkv * T));
+      for (int i = 0; i < B * Hkv; ++i) {
+        GN_TRY(synth(scores, (int64_t)T * blocks, -1, 1, 30 + i, s));
+        GN_TRY(select_blocks_launch(scores, T, blocks, 0, ratio, topk, sel + (int64_t)i * T * topk, cnt + (int64_t)i * T, s));
+      }
+    }
+    GN_TRY(compressed_attention_launch(q, kc, vc, B, Hq, Hkv, T, D, blocks, ratio, o, lse, sel, cnt, topk, 0, s));
+    if (k == "compressed_attention_fwd" || k == "compressed_attention_sparse_fwd")
+      return time_it(s, iters, mean_ms, [&]() { return compressed_attention_launch(q, kc, vc, B, Hq, Hkv, T, D, blocks, ratio, o, lse, sel, cnt, topk, 0, s); });
+    GN_CUDA(cudaMemsetAsync(dq, 0, sizeof(float) * nq, s)); GN_CUDA(cudaMemsetAsync(dk, 0, sizeof(float) * nk, s)); GN_CUDA(cudaMemsetAsync(dv, 0, sizeof(float) * nk, s));
+    return time_it(s, iters, mean_ms, [&]() {
+      return compressed_attention_backward_launch(q, kc, vc, dout, lse, nullptr, delta, B, Hq, Hkv, T, D, blocks, ratio, dq, dk, dv, sel, cnt, topk, s);
+    });
+  }
   if (k == "advantage") {
     GN_REQUIRE(n_dims == 2, "advantage wants {groups, group}");
     int groups = (int)dims[0], group = (int)dims[1];

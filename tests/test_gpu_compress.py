@@ -39,7 +39,8 @@ def test_compressor_known_answer(bk):
     assert out.ravel().tolist() == [3.0, 6.0]                     # model/compress_test.go:10-26
 
 
-@pytest.mark.parametrize("B,Hq,Hkv,T,D,ratio", [(1, 1, 1, 9, 8, 2), (2, 6, 2, 70, 128, 4), (1, 4, 4, 33, 64, 8), (1, 2, 1, 40, 32, 64)])
+@pytest.mark.parametrize("B,Hq,Hkv,T,D,ratio", [(1, 1, 1, 9, 8, 2), (2, 6, 2, 70, 128, 4), (1, 4, 4, 33, 64, 8), (1, 2, 1, 40, 32, 64),
+                                                (2, 8, 1, 300, 128, 4), (1, 4, 2, 1030, 128, 8), (1, 2, 2, 257, 128, 2)])   # the last three: tensor-core path
 def test_compressed_attention_forward(oracle, bk, B, Hq, Hkv, T, D, ratio):
     rng = np.random.default_rng(T + D)
     blocks = (T + ratio - 1) // ratio
@@ -500,7 +501,7 @@ def test_sparse_compressed_layer_training_step(oracle, bk):
 # the dense global branch of the cached inference path (model/compress_attention.go:962-1003): one decode step and a
 # continuation of several tokens over cached blocks; at offset 0 it is the training form
 @pytest.mark.parametrize("B,Hq,Hkv,T,D,ratio,blocks,offset", [(4, 8, 1, 1, 128, 4, 51, 203), (2, 6, 2, 7, 64, 4, 10, 30), (1, 2, 2, 5, 32, 8, 3, 100),
-                                                              (2, 4, 2, 1, 128, 4, 10, 3)])
+                                                              (2, 4, 2, 1, 128, 4, 10, 3), (2, 8, 1, 140, 128, 4, 200, 700), (1, 4, 2, 130, 128, 4, 70, 150)])   # the last two: tensor-core path
 def test_compressed_attention_forward_cached(oracle, bk, B, Hq, Hkv, T, D, ratio, blocks, offset):
     rng = np.random.default_rng(offset + T)
     q = (rng.standard_normal((B, Hq, T, D)) * 0.4).astype(np.float32)
