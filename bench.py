@@ -341,6 +341,14 @@ def kernel_rooflines(ctx, pk, tf32_tflops):
         tf = products * unit / (ms * 1e-3) / 1e12
         out.append({"kernel": name, "workload": f"d12 one layer of a training pass, {B} x {T} tokens, {label}", "bound": "tensor", "ms": ms,
                     "achieved": tf, "peak": gemm_peak, "unit": "TFLOP/s", "frac": tf / gemm_peak if gemm_peak else None, "note": note})
+    # the global branch of a compressed attention layer at the flash preset's shape (8 192-token prompt + 512 new tokens, 8 query heads
+    # on one kv head of 128, ratio 4): every query sees the blocks before its own, (T / ratio) / 2 on average; two products
+    Bc, Hc, Tc, ratio = 4, 8, 8704, 4
+    ms = ctx.profile_kernel("compressed_attention_fwd", [Bc, Hc, 1, d, Tc, ratio], 3)
+    tf = 2 * Bc * Hc * Tc * ((Tc // ratio) / 2.0) * d * 2.0 / (ms * 1e-3) / 1e12
+    out.append({"kernel": "compressed_attention_fwd", "workload": f"flash preset, one layer, {Bc} x {Tc} tokens over {Tc // ratio} compressed blocks, forward",
+                "bound": "tensor", "ms": ms, "achieved": tf, "peak": gemm_peak, "unit": "TFLOP/s", "frac": tf / gemm_peak if gemm_peak else None,
+                "note": "tcgen05 attention forward with the keys counted in blocks of `ratio` positions"})
     return out
 
 

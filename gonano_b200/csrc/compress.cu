@@ -69,46 +69,109 @@ __global__ void __launch_bounds__(256) compressor_bias_bwd_kernel(const float* _
   grad_bias[idx] = acc;
 }
 
-// one warp per (batch, query head, token): keys = compressed blocks 0 .. (offset + t) / ratio - 1
-template <int DP>
+// One warp per (batch, kv head, token) and HR query heads of the group: keys = compressed blocks 0 .. (offset + t) / ratio - 1, or
+// the token's selected blocks.  The K and V rows are read once for the HR heads (the heads of a group see the same keys; with one
+// row read per head the kernel sat on the L2 -> SM bandwidth).  32 keys at a time: lane j keeps the scores of key j of the chunk,
+// a chunk shares one rescale per head, rows are requested four at a time so that their latencies overlap.  An index outside the
+// blocks is ignored, never dereferenced.
+template <int DP, int HR>
 __global__ void __launch_bounds__(256) compressed_attention_kernel(const float* __restrict__ q, const float* __restrict__ kc, const float* __restrict__ vc, int B,
                                                                    int Hq, int Hkv, int T, int D, int blocks, int ratio, float* __restrict__ out,
                                                                    float* __restrict__ lse, const int32_t* __restrict__ selection,
                                                                    const int32_t* __restrict__ counts, int topk, int offset) {
   constexpr int PER = DP / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hr = Hq / Hkv, parts = hr / HR;
   const int64_t idx = (int64_t)blockIdx.x * 8 + warp;
-  if (idx >= (int64_t)B * Hq * T) return;
-  const int t = (int)(idx % T); const int64_t bh = idx / T; const int h = (int)(bh % Hq); const int b = (int)(bh / Hq);
-  const int64_t kvh = (int64_t)b * Hkv + h / (Hq / Hkv);
-  // dense: the blocks before the query's own (token t stands at position offset + t); sparse: the token's selected blocks, in selection order
+  if (idx >= (int64_t)B * Hkv * parts * T) return;
+  const int t = (int)(idx % T); const int64_t rest = idx / T; const int part = (int)(rest % parts); const int64_t kvh = rest / parts;
+  const int hk = (int)(kvh % Hkv); const int b = (int)(kvh / Hkv);
+  const int64_t row0 = ((int64_t)b * Hq + hk * hr + part * HR) * T + t;     // head g of this warp: row0 + g * T
   const int32_t* sel = selection ? selection + (kvh * T + t) * topk : nullptr;
   const int nk = selection ? max(0, min(counts[kvh * T + t], topk)) : min((offset + t) / ratio, blocks);
-  const float* qr = q + idx * D;
   const int64_t kbase = kvh * blocks * D;
-  float qv[PER], acc[PER];
+  float qv[HR][PER], acc[HR][PER], m[HR], l[HR];
 #pragma unroll
-  for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; qv[i] = c < D ? qr[c] : 0.0f; acc[i] = 0.0f; }
-  float m = -INFINITY, l = 0.0f;
-  for (int j = 0; j < nk; ++j) {
-    const int blk = sel ? sel[j] : j;
-    if ((unsigned)blk >= (unsigned)blocks) continue;      // an index outside the blocks is ignored, never dereferenced
-    const float* kr = kc + kbase + (int64_t)blk * D; const float* vr = vc + kbase + (int64_t)blk * D;
-    float s = 0.0f;
+  for (int g = 0; g < HR; ++g) {
+    m[g] = -INFINITY; l[g] = 0.0f;
 #pragma unroll
-    for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; if (c < D) s = fmaf(qv[i], kr[c], s); }
-    s = warp_sum(s);
-    const float mn = fmaxf(m, s);
-    const float f = __expf(m - mn), p = __expf(s - mn);
-    l = l * f + p;
-#pragma unroll
-    for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; if (c < D) acc[i] = acc[i] * f + p * vr[c]; }
-    m = mn;
+    for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; qv[g][i] = c < D ? q[(row0 + (int64_t)g * T) * D + c] : 0.0f; acc[g][i] = 0.0f; }
   }
-  const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+  for (int j0 = 0; j0 < nk; j0 += 32) {
+    const int cn = min(32, nk - j0);
+    int myblk = -1;
+    if (lane < cn) { myblk = sel ? sel[j0 + lane] : j0 + lane; if ((unsigned)myblk >= (unsigned)blocks) myblk = -1; }
+    float mys[HR];
 #pragma unroll
-  for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; if (c < D) out[idx * D + c] = acc[i] * inv; }
-  if (lse && lane == 0) lse[idx] = nk > 0 ? m + logf(l) : -INFINITY;
+    for (int g = 0; g < HR; ++g) mys[g] = -INFINITY;
+    for (int u0 = 0; u0 < cn; u0 += 4) {
+      float kv[4][PER]; int bl[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) { bl[u] = __shfl_sync(0xffffffffu, myblk, (u0 + u) & 31); if (u0 + u >= cn) bl[u] = -1; }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float* kr = kc + kbase + (int64_t)max(bl[u], 0) * D;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; kv[u][i] = (bl[u] >= 0 && c < D) ? kr[c] : 0.0f; }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (bl[u] < 0) continue;
+#pragma unroll
+        for (int g = 0; g < HR; ++g) {
+          float sc = 0.0f;
+#pragma unroll
+          for (int i = 0; i < PER; ++i) sc = fmaf(qv[g][i], kv[u][i], sc);
+          sc = warp_sum(sc);
+          if (lane == u0 + u) mys[g] = sc;
+        }
+      }
+    }
+    float e[HR];
+#pragma unroll
+    for (int g = 0; g < HR; ++g) {
+      float cm = mys[g];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, o));
+      e[g] = 0.0f;
+      if (cm == -INFINITY) continue;                       // no usable key in this chunk (the same for every lane)
+      const float mn = fmaxf(m[g], cm);
+      const float f = __expf(m[g] - mn);
+      e[g] = mys[g] == -INFINITY ? 0.0f : __expf(mys[g] - mn);
+      l[g] = l[g] * f + warp_sum(e[g]);
+#pragma unroll
+      for (int i = 0; i < PER; ++i) acc[g][i] *= f;
+      m[g] = mn;
+    }
+    for (int u0 = 0; u0 < cn; u0 += 4) {
+      float vv[4][PER]; int bl[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) { bl[u] = __shfl_sync(0xffffffffu, myblk, (u0 + u) & 31); if (u0 + u >= cn) bl[u] = -1; }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float* vr = vc + kbase + (int64_t)max(bl[u], 0) * D;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; vv[u][i] = (bl[u] >= 0 && c < D) ? vr[c] : 0.0f; }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+#pragma unroll
+        for (int g = 0; g < HR; ++g) {
+          const float pw = __shfl_sync(0xffffffffu, e[g], (u0 + u) & 31);     // 0 for a key that is not there
+#pragma unroll
+          for (int i = 0; i < PER; ++i) acc[g][i] = fmaf(pw, vv[u][i], acc[g][i]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < HR; ++g) {
+    const float inv = l[g] > 0.0f ? 1.0f / l[g] : 0.0f;
+    const int64_t row = row0 + (int64_t)g * T;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; if (c < D) out[row * D + c] = acc[g][i] * inv; }
+    if (lse && lane == 0) lse[row] = l[g] > 0.0f ? m[g] + logf(l[g]) : -INFINITY;
+  }
 }
 
 // Backward over the preceding blocks (model/compress_attention.go:735-781), deterministic, no atomics.
@@ -543,10 +606,21 @@ int compressed_attention_launch(const float* q, const float* kc, const float* vc
     if (ratio > 1 && attention_tc_ok(sh, q, kc, vc, out)) return attention_tc_forward(sh, q, kc, vc, out, lse, s);
   }
 #endif
-  const unsigned grid = (unsigned)ceil_div(n, 8);
-  if (D <= 32) compressed_attention_kernel<32><<<grid, 256, 0, s>>>(q, kc, vc, B, Hq, Hkv, T, D, blocks, ratio, out, lse, selection, counts, topk, offset);
-  else if (D <= 64) compressed_attention_kernel<64><<<grid, 256, 0, s>>>(q, kc, vc, B, Hq, Hkv, T, D, blocks, ratio, out, lse, selection, counts, topk, offset);
-  else compressed_attention_kernel<128><<<grid, 256, 0, s>>>(q, kc, vc, B, Hq, Hkv, T, D, blocks, ratio, out, lse, selection, counts, topk, offset);
+  // the largest supported head count per warp that divides the group
+  const int hr = Hq / Hkv;
+  const int HR = hr % 8 == 0 ? 8 : hr % 4 == 0 ? 4 : hr % 3 == 0 ? 3 : hr % 2 == 0 ? 2 : 1;
+  const unsigned grid = (unsigned)ceil_div(n / HR, 8);
+#define GN_CA_FWD(DPV, HRV) compressed_attention_kernel<DPV, HRV><<<grid, 256, 0, s>>>(q, kc, vc, B, Hq, Hkv, T, D, blocks, ratio, out, lse, selection, counts, topk, offset)
+#define GN_CA_FWD_D(HRV) do { if (D <= 32) GN_CA_FWD(32, HRV); else if (D <= 64) GN_CA_FWD(64, HRV); else GN_CA_FWD(128, HRV); } while (0)
+  switch (HR) {
+    case 8: GN_CA_FWD_D(8); break;
+    case 4: GN_CA_FWD_D(4); break;
+    case 3: GN_CA_FWD_D(3); break;
+    case 2: GN_CA_FWD_D(2); break;
+    default: GN_CA_FWD_D(1); break;
+  }
+#undef GN_CA_FWD_D
+#undef GN_CA_FWD
   GN_LAUNCH_CHECK();
   return GN_OK;
 }
