@@ -521,3 +521,55 @@ def test_compressed_attention_forward_cached(oracle, bk, B, Hq, Hkv, T, D, ratio
         m = min(nb, blocks); fk[:, :, :m] = kc[:, :, :m]; fv[:, :, :m] = vc[:, :, :m]
         whole, whole_l = bk.compressed_attention_forward(fq, fk, fv, ratio)
         close(whole[:, :, offset:], got, 1e-5, 1e-6); close(whole_l[:, :, offset:], got_l, 1e-5, 1e-6)
+
+
+def test_heavily_compressed_layer_incremental_equals_full(oracle, bk):
+    """The cached inference path of one heavily-compressed layer, from the blocks: after a prefill every new token compresses
+    the block it completes (compressTail, model/compress_attention.go:848-873: the compressor over that block's rows alone),
+    attends to the cached compressed blocks at its position and to the raw keys inside the window, and merges the two.  Each
+    row must equal the row of a full-sequence pass (the reference holds its engine to a naive recompute the same way,
+    inference/inference_test.go:306-440)."""
+    rng = np.random.default_rng(51)
+    B, Hq, Hkv, T, D, d, ratio, window, T0 = 2, 4, 2, 41, 128, 64, 4, 6, 18
+    hr = Hq // Hkv
+    x = rng.standard_normal((B, T, d)).astype(np.float32)
+    q = (rng.standard_normal((B, Hq, T, D)) * 0.4).astype(np.float32)
+    k = (rng.standard_normal((B, Hkv, T, D)) * 0.4).astype(np.float32); v = rng.standard_normal((B, Hkv, T, D)).astype(np.float32)
+    wc = (rng.standard_normal((D, d)) * 0.2).astype(np.float32); bias = (rng.standard_normal((ratio, D)) * 0.3).astype(np.float32)
+    ref = oracle.Backend(0)
+
+    def attn_fwd(q_, k_, v_, out_, dout_, lse_, *a, **kw):
+        raise AssertionError("forward only")
+
+    want, want_l = _hca_layer((oracle.compressor_forward, None, oracle.compressed_attention_forward, None, oracle.merge_branches, ref.attention_forward, attn_fwd),
+                              x, q, k, v, wc, bias, ratio, window)
+    full, full_l = _hca_layer((bk.compressor_forward, None, bk.compressed_attention_forward, None, bk.attention_merge, bk.attention_forward, attn_fwd),
+                              x, q, k, v, wc, bias, ratio, window)
+    close(full, want, 1e-4, 1e-5); close(full_l, want_l, 1e-4, 1e-5)
+
+    cap = T // ratio
+    kc = np.zeros((B, Hkv, cap, D), np.float32); vc = np.zeros_like(kc)
+    have = 0
+
+    def compress_completed(tokens):
+        nonlocal have
+        while (have + 1) * ratio <= tokens:
+            rows = slice(have * ratio, (have + 1) * ratio)
+            for b in range(B):
+                for h in range(Hkv):
+                    kc[b, h, have] = bk.compressor_forward(x[b:b + 1, rows], k[b, h, rows][None], wc, bias, ratio)[0][0, 0]
+                    vc[b, h, have] = bk.compressor_forward(x[b:b + 1, rows], v[b, h, rows][None], wc, bias, ratio)[0][0, 0]
+            have += 1
+
+    compress_completed(T0)                                     # the prefill's completed blocks
+    for p in range(T0, T):
+        compress_completed(p + 1)                              # token p may complete a block; it never attends to it
+        og, lg = bk.compressed_attention_forward(q[:, :, p:p + 1], kc[:, :, :have], vc[:, :, :have], ratio, offset=p)
+        ol = np.zeros((B, Hq, 1, D), np.float32); ll = np.zeros((B, Hq, 1), np.float32)
+        for b in range(B):
+            for h in range(Hq):
+                o, l = bk.attention_forward(q[b, h, p:p + 1], k[b, h // hr, :p + 1], v[b, h // hr, :p + 1], 1, p + 1, D, p, window)
+                ol[b, h, 0] = np.asarray(o).reshape(D); ll[b, h, 0] = np.asarray(l).reshape(())
+        out, lse = bk.attention_merge(og.reshape(-1, D), lg.reshape(-1), ol.reshape(-1, D), ll.reshape(-1))
+        close(np.asarray(out).reshape(B, Hq, D), full[:, :, p], 2e-5, 2e-6)
+        close(np.asarray(lse).reshape(B, Hq), full_l[:, :, p], 2e-5, 2e-6)
