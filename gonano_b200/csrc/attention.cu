@@ -1079,7 +1079,7 @@ __global__ void __launch_bounds__(32 * NW) attn_decode_kernel(const float* __res
   }
 }
 __global__ void __launch_bounds__(128) attn_decode_combine_kernel(const float* part_acc, const float* part_ms, int splits, int Hq, int D, float* out, int64_t o_rstride,
-                                                                  float* out_hi, float* out_lo) {
+                                                                  float* out_hi, float* out_lo, float* lse_out) {
   pdl_trigger();
   pdl_wait();
   int row = blockIdx.x / Hq, hq = blockIdx.x % Hq;
@@ -1088,6 +1088,7 @@ __global__ void __launch_bounds__(128) attn_decode_combine_kernel(const float* p
   for (int s = 0; s < splits; ++s) gm = fmaxf(gm, part_ms[(base + s) * 2]);
   float tot = 0;
   for (int s = 0; s < splits; ++s) { float m = part_ms[(base + s) * 2]; tot += (m == -INFINITY) ? 0.0f : part_ms[(base + s) * 2 + 1] * __expf(m - gm); }
+  if (lse_out && threadIdx.x == 0) lse_out[(int64_t)row * Hq + hq] = tot > 0 ? gm + logf(tot) : -INFINITY;   // [rows, Hq]
   for (int c = threadIdx.x; c < D; c += 128) {
     float acc = 0;
     for (int s = 0; s < splits; ++s) { float m = part_ms[(base + s) * 2]; if (m != -INFINITY) acc += part_acc[(base + s) * D + c] * __expf(m - gm); }
@@ -1137,7 +1138,8 @@ int attention_decode_splits(int rows, int Hkv, int max_ctx) {
 template <int DP, int RATIO>
 static int decode_go(const float* q, int64_t q_rstride, const float* kcache, const float* vcache, int64_t row_stride, int64_t head_stride,
                      const int32_t* ctx_len, int rows, int Hq, int Hkv, int D, int window, float* out, int64_t o_rstride, float* part_acc, float* part_ms,
-                     int splits, cudaStream_t s, float* out_hi, float* out_lo, int group, int prefix_len) {
+                     int splits, cudaStream_t s, float* out_hi, float* out_lo, int group, int prefix_len, float* lse_out) {
+  GN_REQUIRE(!lse_out || splits > 1, "decode attention: the log-sum-exp comes from the combine pass (splits %d)", splits);
   int psplits = 0;
   psplits = attention_decode_prefix_splits(rows, group, Hq, Hkv, D, prefix_len);
   if (psplits > 0) {
@@ -1166,7 +1168,7 @@ static int decode_go(const float* q, int64_t q_rstride, const float* kcache, con
 #undef GN_DEC_LAUNCH
   GN_LAUNCH_CHECK();
   if (splits > 1) {
-    GN_CUDA(launch_pdl(attn_decode_combine_kernel, dim3(rows * Hq), dim3(128), 0, s, part_acc, part_ms, nslots, Hq, D, out, o_rstride, out_hi, out_lo));
+    GN_CUDA(launch_pdl(attn_decode_combine_kernel, dim3(rows * Hq), dim3(128), 0, s, part_acc, part_ms, nslots, Hq, D, out, o_rstride, out_hi, out_lo, lse_out));
     GN_LAUNCH_CHECK();
   }
   return GN_OK;
@@ -1174,11 +1176,11 @@ static int decode_go(const float* q, int64_t q_rstride, const float* kcache, con
 
 int attention_decode_launch(const float* q, int64_t q_rstride, const float* kcache, const float* vcache, int64_t row_stride, int64_t head_stride,
                             const int32_t* ctx_len, int rows, int Hq, int Hkv, int D, int window, float* out, int64_t o_rstride,
-                            float* part_acc, float* part_ms, int splits, cudaStream_t s, float* out_hi, float* out_lo, int group, int prefix_len) {
+                            float* part_acc, float* part_ms, int splits, cudaStream_t s, float* out_hi, float* out_lo, int group, int prefix_len, float* lse_out) {
   if (rows <= 0) return GN_OK;
   int ratio = Hq / Hkv;
   const int dp = (D + 31) / 32 * 32;
-#define GN_DEC(DD, RR) if (dp == DD && ratio == RR) return decode_go<DD, RR>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, rows, Hq, Hkv, D, window, out, o_rstride, part_acc, part_ms, splits, s, out_hi, out_lo, group, prefix_len)
+#define GN_DEC(DD, RR) if (dp == DD && ratio == RR) return decode_go<DD, RR>(q, q_rstride, kcache, vcache, row_stride, head_stride, ctx_len, rows, Hq, Hkv, D, window, out, o_rstride, part_acc, part_ms, splits, s, out_hi, out_lo, group, prefix_len, lse_out)
   GN_DEC(128, 1); GN_DEC(128, 2); GN_DEC(128, 3); GN_DEC(128, 4); GN_DEC(128, 8);
   GN_DEC(96, 1); GN_DEC(96, 2); GN_DEC(96, 4);
   GN_DEC(64, 1); GN_DEC(64, 2); GN_DEC(64, 3); GN_DEC(64, 4); GN_DEC(64, 8);

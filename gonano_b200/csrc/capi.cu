@@ -365,6 +365,23 @@ int gn_compressed_attention_forward_at(const float* query, const float* key_c, c
   const size_t nq = (size_t)batch * n_head * seq * head_dim, nk = (size_t)batch * n_kv_head * blocks * head_dim;
   const float* dq = st.in(query, nq); const float* dk = st.in(key_c, nk); const float* dv = st.in(value_c, nk);
   float* dout = st.out(out, nq); float* dl = lse ? st.out(lse, (size_t)batch * n_head * seq) : nullptr;
+  // One decode step over a long compressed cache: the rows' blocks are a key / value cache of `count` positions, so the
+  // split-context decode attention kernel (a CTA per row and kv head and context share, the group's heads served from
+  // one read of each row) takes it; the warp-per-token form would walk the blocks one warp per group.
+  const int hr = n_kv_head > 0 ? n_head / n_kv_head : 0;
+  if (seq == 1 && head_dim == 128 && blocks >= 64 && n_kv_head > 0 && n_head % n_kv_head == 0 && ratio >= 1 &&
+      (hr == 1 || hr == 2 || hr == 3 || hr == 4 || hr == 8)) {
+    const int count = std::min(position_offset / ratio, blocks);
+    const int splits = std::max(2, attention_decode_splits(batch, n_kv_head, blocks));
+    std::vector<int32_t> ctx_host((size_t)batch, count);
+    const int32_t* ctx_len = st.in(ctx_host.data(), (size_t)batch);
+    float* pa = st.temp<float>((size_t)batch * n_head * splits * head_dim); float* pm = st.temp<float>((size_t)batch * n_head * splits * 2);
+    float* dl2 = dl ? dl : st.temp<float>((size_t)batch * n_head);
+    if (st.status != GN_OK) return st.status;
+    GN_TRY(attention_decode_launch(dq, (int64_t)n_head * head_dim, dk, dv, (int64_t)n_kv_head * blocks * head_dim, (int64_t)blocks * head_dim, ctx_len, batch, n_head,
+                                   n_kv_head, head_dim, -1, dout, (int64_t)n_head * head_dim, pa, pm, splits, s, nullptr, nullptr, 1, 0, dl2));
+    GN_END();
+  }
   if (st.status != GN_OK) return st.status;
   GN_TRY(compressed_attention_launch(dq, dk, dv, batch, n_head, n_kv_head, seq, head_dim, blocks, ratio, dout, dl, nullptr, nullptr, 0, position_offset, s));
   GN_END();

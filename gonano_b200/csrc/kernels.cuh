@@ -118,7 +118,8 @@ int attention_decode_launch(const float* q, int64_t q_rstride, const float* kcac
                             const int32_t* ctx_len, int rows, int Hq, int Hkv, int D, int window, float* out, int64_t o_rstride,
                             float* part_acc, float* part_ms, int splits, cudaStream_t s,
                             float* out_hi = nullptr, float* out_lo = nullptr,    // optional tf32 hi/lo split of the output, same pitch
-                            int group = 1, int prefix_len = 0);
+                            int group = 1, int prefix_len = 0,
+                            float* lse_out = nullptr);   // optional [rows, Hq] log-sum-exp; written by the combine pass, so splits must be > 1
 // group > 1 and prefix_len > 0: rows come in groups of `group` whose first prefix_len cached positions are identical
 // copies (a replicated prompt); those keys are read once per group.  The partial buffers then need
 // attention_decode_prefix_splits(...) + splits slots per (row, query head).

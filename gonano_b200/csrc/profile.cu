@@ -1,5 +1,6 @@
 // gn_profile_kernel: per-kernel timing on synthetic device data (CUDA events on the
 // context's stream).  The benchmark uses it to put each hot kernel beside its roofline.
+#include <algorithm>
 #include <string>
 #include <vector>
 
@@ -194,6 +195,27 @@ extern "C" int gn_profile_kernel(gn_ctx* ctx, const char* kernel, const int64_t*
     GN_CUDA(cudaMemsetAsync(dq, 0, sizeof(float) * nq, s)); GN_CUDA(cudaMemsetAsync(dk, 0, sizeof(float) * nk, s)); GN_CUDA(cudaMemsetAsync(dv, 0, sizeof(float) * nk, s));
     return time_it(s, iters, mean_ms, [&]() {
       return compressed_attention_backward_launch(q, kc, vc, dout, lse, nullptr, delta, B, Hq, Hkv, T, D, blocks, ratio, dq, dk, dv, sel, cnt, topk, s);
+    });
+  }
+  if (k == "compressed_attention_decode") {
+    // one decode step of the global branch over a cached compressed sequence: {rows, n_head, n_kv_head, head_dim, blocks}
+    GN_REQUIRE(n_dims == 5, "%s wants {rows, n_head, n_kv_head, head_dim, blocks}", kernel);
+    const int B = (int)dims[0], Hq = (int)dims[1], Hkv = (int)dims[2], D = (int)dims[3], blocks = (int)dims[4];
+    float *q, *kc, *vc, *o, *lse;
+    GN_TRY(bufs.get(&q, (size_t)B * Hq * D)); GN_TRY(bufs.get(&kc, (size_t)B * Hkv * blocks * D)); GN_TRY(bufs.get(&vc, (size_t)B * Hkv * blocks * D));
+    GN_TRY(bufs.get(&o, (size_t)B * Hq * D)); GN_TRY(bufs.get(&lse, (size_t)B * Hq));
+    GN_TRY(synth(q, (int64_t)B * Hq * D, -0.6f, 0.6f, 41, s)); GN_TRY(synth(kc, (int64_t)B * Hkv * blocks * D, -0.6f, 0.6f, 42, s));
+    GN_TRY(synth(vc, (int64_t)B * Hkv * blocks * D, -1, 1, 43, s));
+    // the launch gn_compressed_attention_forward_at makes for one token: the split-context decode kernel over the blocks
+    const int splits = std::max(2, attention_decode_splits(B, Hkv, blocks));
+    int32_t* cl; float *pa, *pm;
+    GN_TRY(bufs.get(&cl, (size_t)B)); GN_TRY(bufs.get(&pa, (size_t)B * Hq * splits * D)); GN_TRY(bufs.get(&pm, (size_t)B * Hq * splits * 2));
+    std::vector<int32_t> host((size_t)B, blocks);
+    GN_CUDA(cudaMemcpyAsync(cl, host.data(), sizeof(int32_t) * B, cudaMemcpyHostToDevice, s));
+    GN_CUDA(cudaStreamSynchronize(s));
+    return time_it(s, iters, mean_ms, [&]() {
+      return attention_decode_launch(q, (int64_t)Hq * D, kc, vc, (int64_t)Hkv * blocks * D, (int64_t)blocks * D, cl, B, Hq, Hkv, D, -1, o, (int64_t)Hq * D, pa, pm, splits, s,
+                                     nullptr, nullptr, 1, 0, lse);
     });
   }
   if (k == "advantage") {

@@ -501,7 +501,9 @@ def test_sparse_compressed_layer_training_step(oracle, bk):
 # the dense global branch of the cached inference path (model/compress_attention.go:962-1003): one decode step and a
 # continuation of several tokens over cached blocks; at offset 0 it is the training form
 @pytest.mark.parametrize("B,Hq,Hkv,T,D,ratio,blocks,offset", [(4, 8, 1, 1, 128, 4, 51, 203), (2, 6, 2, 7, 64, 4, 10, 30), (1, 2, 2, 5, 32, 8, 3, 100),
-                                                              (2, 4, 2, 1, 128, 4, 10, 3), (2, 8, 1, 140, 128, 4, 200, 700), (1, 4, 2, 130, 128, 4, 70, 150)])   # the last two: tensor-core path
+                                                              (2, 4, 2, 1, 128, 4, 10, 3), (2, 8, 1, 140, 128, 4, 200, 700), (1, 4, 2, 130, 128, 4, 70, 150),   # these two: tensor-core path
+                                                              (4, 8, 1, 1, 128, 4, 300, 1000), (3, 6, 2, 1, 128, 4, 100, 37), (2, 4, 4, 1, 128, 2, 80, 1),
+                                                              (8, 8, 1, 1, 128, 4, 2176, 8700)])   # one token over a long cache: the split-context decode kernel
 def test_compressed_attention_forward_cached(oracle, bk, B, Hq, Hkv, T, D, ratio, blocks, offset):
     rng = np.random.default_rng(offset + T)
     q = (rng.standard_normal((B, Hq, T, D)) * 0.4).astype(np.float32)
@@ -520,7 +522,7 @@ def test_compressed_attention_forward_cached(oracle, bk, B, Hq, Hkv, T, D, ratio
         fk = np.zeros((B, Hkv, nb, D), np.float32); fv = np.zeros_like(fk)
         m = min(nb, blocks); fk[:, :, :m] = kc[:, :, :m]; fv[:, :, :m] = vc[:, :, :m]
         whole, whole_l = bk.compressed_attention_forward(fq, fk, fv, ratio)
-        close(whole[:, :, offset:], got, 1e-5, 1e-6); close(whole_l[:, :, offset:], got_l, 1e-5, 1e-6)
+        close(whole[:, :, offset:], got, 1e-4, 1e-5); close(whole_l[:, :, offset:], got_l, 1e-4, 1e-5)   # the two passes may run on different kernels
 
 
 def test_heavily_compressed_layer_incremental_equals_full(oracle, bk):
