@@ -314,7 +314,7 @@ __global__ void __launch_bounds__(NTH, 1) attn_mma_dkv_kernel(AttnShape sh, cons
   float adk[HD / 8][4], adv[HD / 8][4];
 #pragma unroll
   for (int nt = 0; nt < HD / 8; ++nt) { adk[nt][0] = adk[nt][1] = adk[nt][2] = adk[nt][3] = 0.0f; adv[nt][0] = adv[nt][1] = adv[nt][2] = adv[nt][3] = 0.0f; }
-  int q_begin = max(0, k0 - offset);
+  int q_begin = max(0, sh.first_position(k0) - offset);
   q_begin = (q_begin / BT) * BT;
   int q_end = sh.Tq;
   if (sh.window >= 0) q_end = min(sh.Tq, k0 + kvalid - 1 + sh.window - offset + 1);
@@ -325,8 +325,8 @@ __global__ void __launch_bounds__(NTH, 1) attn_mma_dkv_kernel(AttnShape sh, cons
   TileRegs qr, dor;
   auto fetch_step = [&](int step) {
     const int hq = hk * ratio + step / n_qt, q0 = q_begin + (step % n_qt) * BT, qvalid = min(BT, sh.Tq - q0);
-    fetch_tile(qr, q + (int64_t)b * sh.q_bstride + (int64_t)q0 * sh.q_tstride + (int64_t)hq * HD, sh.q_tstride, qvalid);
-    fetch_tile(dor, dout + (int64_t)b * sh.o_bstride + (int64_t)q0 * sh.o_tstride + (int64_t)hq * HD, sh.o_tstride, qvalid);
+    fetch_tile(qr, q + (int64_t)b * sh.q_bstride + (int64_t)q0 * sh.q_tstride + sh.q_head(hq), sh.q_tstride, qvalid);
+    fetch_tile(dor, dout + (int64_t)b * sh.o_bstride + (int64_t)q0 * sh.o_tstride + sh.o_head(hq), sh.o_tstride, qvalid);
   };
   if (n_steps > 0) fetch_step(0);
   for (int step = 0; step < n_steps; ++step) {
@@ -342,7 +342,7 @@ __global__ void __launch_bounds__(NTH, 1) attn_mma_dkv_kernel(AttnShape sh, cons
       }
       __syncthreads();
       if (step + 1 < n_steps) fetch_step(step + 1);
-      if (offset + q0 + BT - 1 < warp_first) continue;   // every query of the tile precedes this warp's keys
+      if (sh.last_key(offset + q0 + BT - 1) < warp_first) continue;   // no query of the tile sees this warp's keys
       float st[BT / 8][4], dpt[BT / 8][4];
 #pragma unroll
       for (int nt = 0; nt < BT / 8; ++nt) { st[nt][0] = st[nt][1] = st[nt][2] = st[nt][3] = 0.0f; dpt[nt][0] = dpt[nt][1] = dpt[nt][2] = dpt[nt][3] = 0.0f; }
@@ -355,7 +355,7 @@ __global__ void __launch_bounds__(NTH, 1) attn_mma_dkv_kernel(AttnShape sh, cons
           const int il = nt * 8 + 2 * t + (e & 1), qi = q0 + il, qpos = offset + qi, kj = kj2[e >> 1];
           const int32_t qseg = (sh.segment_ids && qpos < sh.seg_len) ? sh.segment_ids[qpos] : 0;
           float p = 0.0f;
-          if (qi < sh.Tq && kj < sh.Tk && !masked(qpos, kj, sh.window, sh.segment_ids, sh.seg_len, qseg)) p = __expf(st[nt][e] - lse_s[il]);
+          if (qi < sh.Tq && kj < sh.Tk && !masked(sh.last_key(qpos), kj, sh.window, sh.segment_ids, sh.seg_len, qseg)) p = __expf(st[nt][e] - lse_s[il]);
           st[nt][e] = p;
           dpt[nt][e] = p * (dpt[nt][e] - delta_s[il]);
         }
@@ -391,8 +391,8 @@ __global__ void __launch_bounds__(NTH, 1) attn_mma_dq_kernel(AttnShape sh, const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int bh = blockIdx.y, b = bh / sh.Hq, hq = bh % sh.Hq, hk = hq / (sh.Hq / sh.Hkv);
   const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BM, qvalid = min(BM, sh.Tq - q0), offset = sh.offset0;
-  const float* qg = q + (int64_t)b * sh.q_bstride + (int64_t)q0 * sh.q_tstride + (int64_t)hq * HD;
-  const float* dog = dout + (int64_t)b * sh.o_bstride + (int64_t)q0 * sh.o_tstride + (int64_t)hq * HD;
+  const float* qg = q + (int64_t)b * sh.q_bstride + (int64_t)q0 * sh.q_tstride + sh.q_head(hq);
+  const float* dog = dout + (int64_t)b * sh.o_bstride + (int64_t)q0 * sh.o_tstride + sh.o_head(hq);
   const float* kg = k + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride;
   const float* vg = v + (int64_t)b * sh.kv_bstride + (int64_t)hk * sh.kv_hstride;
   load_tile(Qs, qg, sh.q_tstride, BM, qvalid);
@@ -410,9 +410,9 @@ __global__ void __launch_bounds__(NTH, 1) attn_mma_dq_kernel(AttnShape sh, const
   float adq[HD / 8][4];
 #pragma unroll
   for (int nt = 0; nt < HD / 8; ++nt) { adq[nt][0] = adq[nt][1] = adq[nt][2] = adq[nt][3] = 0.0f; }
-  const int warp_last = offset + q0 + warp * 16 + 15;
+  const int warp_last = sh.last_key(offset + q0 + warp * 16 + 15);   // the last key any query of this warp sees
   const int max_qpos = offset + q0 + qvalid - 1;
-  const int k_end = min(sh.Tk, max_qpos + 1);
+  const int k_end = min(sh.Tk, sh.last_key(max_qpos) + 1);
   int k_begin = 0;
   if (sh.window >= 0) k_begin = max(0, offset + q0 - sh.window);
   k_begin = (k_begin / BT) * BT;
@@ -442,7 +442,7 @@ __global__ void __launch_bounds__(NTH, 1) attn_mma_dq_kernel(AttnShape sh, const
       for (int e = 0; e < 4; ++e) {
         const int h = e >> 1, kj = kt + nt * 8 + 2 * t + (e & 1);
         float p = 0.0f;
-        if (qi2[h] < sh.Tq && kj < sh.Tk && !masked(offset + qi2[h], kj, sh.window, sh.segment_ids, sh.seg_len, qseg[h])) p = __expf(s[nt][e] - lse2[h]);
+        if (qi2[h] < sh.Tq && kj < sh.Tk && !masked(sh.last_key(offset + qi2[h]), kj, sh.window, sh.segment_ids, sh.seg_len, qseg[h])) p = __expf(s[nt][e] - lse2[h]);
         dp[nt][e] = p * (dp[nt][e] - delta2[h]);
       }
     mm_perm<BT / 8>(adq, dp, Kh, Kl, g, t);
@@ -450,7 +450,7 @@ __global__ void __launch_bounds__(NTH, 1) attn_mma_dq_kernel(AttnShape sh, const
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     if (qi2[h] >= sh.Tq) continue;
-    float* dqg = dq + (int64_t)b * sh.q_bstride + (int64_t)qi2[h] * sh.q_tstride + (int64_t)hq * HD;
+    float* dqg = dq + (int64_t)b * sh.q_bstride + (int64_t)qi2[h] * sh.q_tstride + sh.q_head(hq);
 #pragma unroll
     for (int nt = 0; nt < HD / 8; ++nt) {
       float2 a = make_float2(adq[nt][2 * h], adq[nt][2 * h + 1]);
@@ -574,6 +574,7 @@ bool attention_mma_ok(const AttnShape& sh, const void* p0, const void* p1, const
 }
 
 int attention_mma_forward(const AttnShape& sh, const float* q, const float* k, const float* v, float* out, float* lse, cudaStream_t s) {
+  GN_REQUIRE(sh.key_ratio == 1 && sh.q_hstride == 0 && sh.o_hstride == 0, "attention (mma.sync forward): keys counted in blocks and head-major queries are not served here");
   static PerDeviceOnce configured;
   if (configured.first()) { GN_CUDA(cudaFuncSetAttribute(attn_mma_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemFwd)); }
   dim3 grid(ceil_div(sh.Tq, BM), sh.B * sh.Hq);
@@ -597,6 +598,7 @@ int attention_mma_decode_prefix(const float* q, int64_t q_rstride, const float* 
 
 int attention_mma_backward(const AttnShape& sh, const float* q, const float* k, const float* v, const float* dout, const float* lse, const float* delta,
                            float* dq, float* dk, float* dv, int accumulate, cudaStream_t s) {
+  GN_REQUIRE(sh.key_ratio == 1 || sh.window < 0, "attention (mma.sync backward): keys counted in blocks take no window");
   static PerDeviceOnce configured;
   if (configured.first()) {
     GN_CUDA(cudaFuncSetAttribute(attn_mma_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemDkv));

@@ -635,6 +635,25 @@ int compressed_attention_backward_launch(const float* q, const float* kc, const 
   if (nq <= 0 || nkv <= 0) return GN_OK;
   const unsigned gq = (unsigned)ceil_div(nq, 8), gk = (unsigned)ceil_div(nkv, 8);
   const float* delta = rowcorr;
+  // head_dim 128, every block before the query's own: the mma.sync attention backward with keys counted in blocks (its dk / dv
+  // kernel owns 128 blocks per CTA and walks the group's heads and the query tiles that see them; no atomics there either)
+  if (!selection && D == 128 && ratio > 1 && (int64_t)T * blocks >= 4096) {
+    AttnShape sh;
+    sh.B = B; sh.Hq = Hq; sh.Hkv = Hkv; sh.D = D; sh.Tq = T; sh.Tk = blocks;
+    sh.q_bstride = (int64_t)Hq * T * D; sh.q_tstride = D; sh.q_hstride = (int64_t)T * D;
+    sh.kv_bstride = (int64_t)Hkv * blocks * D; sh.kv_tstride = D; sh.kv_hstride = (int64_t)blocks * D;
+    sh.o_bstride = sh.q_bstride; sh.o_tstride = D; sh.o_hstride = sh.q_hstride;
+    sh.window = -1; sh.offset0 = 0; sh.key_ratio = ratio; sh.tensor = 1;
+    auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (attention_mma_ok(sh, q, kc, vc, dout, dq) && al(dkc) && al(dvc)) {
+      if (!delta) {
+        compressed_attention_delta_kernel<128><<<gq, 256, 0, s>>>(q, kc, vc, dout, lse, B, Hq, Hkv, T, D, blocks, ratio, delta_scratch, nullptr, nullptr, 0);
+        GN_LAUNCH_CHECK();
+        delta = delta_scratch;
+      }
+      return attention_mma_backward(sh, q, kc, vc, dout, lse, delta, dq, dkc, dvc, 1, s);
+    }
+  }
 #define GN_CA_BWD(DPV) do { \
     if (!delta) { compressed_attention_delta_kernel<DPV><<<gq, 256, 0, s>>>(q, kc, vc, dout, lse, B, Hq, Hkv, T, D, blocks, ratio, delta_scratch, selection, counts, topk); \
                   delta = delta_scratch; } \

@@ -59,6 +59,11 @@ struct AttnShape {
   const int32_t* segment_ids = nullptr;  // [Tk] shared by all rows (Tier A only)
   int seg_len = 0;
   int tensor = 0;   // 1: head_dim 128 may run on the tensor cores in 3xTF32 (forward and backward)
+  // the last key a query at position pos sees / the first position that sees key j (before the window and the segment mask)
+  __host__ __device__ int last_key(int pos) const { return key_ratio == 1 ? pos : pos / key_ratio - 1; }
+  __host__ __device__ int first_position(int key) const { return key_ratio == 1 ? key : (key + 1) * key_ratio; }
+  __host__ __device__ int64_t q_head(int h) const { return (int64_t)h * (q_hstride ? q_hstride : D); }
+  __host__ __device__ int64_t o_head(int h) const { return (int64_t)h * (o_hstride ? o_hstride : D); }
 };
 // head_dim 128 tensor-core kernels (attention_mma.cu); reached through the two launches below when sh.tensor is set.
 bool attention_mma_ok(const AttnShape& sh, const void* p0, const void* p1, const void* p2, const void* p3, const void* p4);

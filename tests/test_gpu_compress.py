@@ -200,7 +200,8 @@ def test_compressor_backward(oracle, bk, B, T, d, C, ratio):
 # compressedAttentionBackward (model/compress_attention.go:735-781): with and without a row correction, grouped heads,
 # a ragged last block, and accumulation into gradients that already hold values
 @pytest.mark.parametrize("B,Hq,Hkv,T,D,ratio,corr", [(1, 1, 1, 9, 8, 2, False), (2, 6, 2, 70, 128, 4, False), (1, 4, 4, 33, 64, 8, True),
-                                                    (1, 2, 1, 40, 32, 64, False), (2, 6, 2, 130, 128, 4, True)])
+                                                    (1, 2, 1, 40, 32, 64, False), (2, 6, 2, 130, 128, 4, True),
+                                                    (2, 8, 1, 300, 128, 4, True), (1, 4, 2, 530, 128, 8, False), (1, 3, 3, 257, 128, 2, True)])   # the last three: mma.sync path
 def test_compressed_attention_backward(oracle, bk, B, Hq, Hkv, T, D, ratio, corr):
     rng = np.random.default_rng(T * 3 + D)
     blocks = (T + ratio - 1) // ratio
@@ -213,13 +214,15 @@ def test_compressed_attention_backward(oracle, bk, B, Hq, Hkv, T, D, ratio, corr
         lse = (lse + np.abs(rng.standard_normal(lse.shape)).astype(np.float32)).astype(np.float32)     # a merged row's lse exceeds the branch's own
     want = oracle.compressed_attention_backward(q, kc, vc, dout, lse, ratio, rc)
     got = bk.compressed_attention_backward(q, kc, vc, dout, lse, ratio, rc)
+    # an entry of dkc / dvc sums thousands of terms of the size of the tensor's largest entries (with an arbitrary row correction
+    # they do not cancel), so the floor scales with that size; the relative part stays element-wise
     for g, w in zip(got, want):
-        close(g, w, 2e-4, 2e-5)
+        close(g, w, 2e-4, 2e-5 * max(1.0, float(np.max(np.abs(w)))))
     assert np.all(got[0][:, :, :min(ratio, T)] == 0) and np.all(got[1][:, :, (T - 1) // ratio:] == 0)   # no preceding block / no later token
     seed = [rng.standard_normal(x.shape).astype(np.float32) for x in (q, kc, vc)]
     acc = bk.compressed_attention_backward(q, kc, vc, dout, lse, ratio, rc, *seed)
     for a, s0, w in zip(acc, seed, want):
-        close(a, s0 + w, 2e-4, 2e-5)
+        close(a, s0 + w, 2e-4, 2e-5 * max(1.0, float(np.max(np.abs(w)))))
 
 
 # compressedAttentionBackwardSparse (model/compress_attention.go:376-433)
@@ -249,8 +252,8 @@ def test_compressed_attention_sparse_backward(oracle, bk, B, Hq, Hkv, T, D, rati
     _, dl = oracle.compressed_attention_forward(q, kc, vc, ratio)
     dense = bk.compressed_attention_backward(q, kc, vc, dout, dl, ratio)
     sparse = bk.compressed_attention_sparse_backward(q, kc, vc, dout, dl, full, fc)
-    for a, b_ in zip(sparse, dense):
-        close(a, b_, 1e-5, 1e-6)
+    for a, b_ in zip(sparse, dense):      # the dense form may run on the tensor cores (3xTF32), the selected-block form does not
+        close(a, b_, 2e-4, 2e-5 * max(1.0, float(np.max(np.abs(b_)))))
 
 
 def _hca_layer(ops, x, q, k, v, wk, bias, ratio, window, dout=None):
