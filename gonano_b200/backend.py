@@ -265,6 +265,25 @@ class CudaBackend:
         p = self._params(q, k, v, ql, kl, hd, offset, window, seg)
         check(self.lib.gn_attention_forward(C.byref(p), ptr(out), ptr(lse))); return out, lse
 
+    def attention_windowed_forward(self, q, k, v, offset, window):
+        """attentionForwardWindowed (model/compress_attention.go:488-507): q [B,Hq,T,D], k / v [B,Hkv,T,D] -> out, lse [B,Hq,T]."""
+        q, k, v = _f32(q), _f32(k), _f32(v)
+        B, Hq, T, D = q.shape; Hkv = k.shape[1]
+        out = np.zeros_like(q); lse = np.zeros((B, Hq, T), np.float32)
+        check(self.lib.gn_attention_windowed_forward(ptr(q), ptr(k), ptr(v), B, Hq, Hkv, T, D, offset, window, ptr(out), ptr(lse)))
+        return out, lse
+
+    def attention_windowed_backward(self, q, k, v, out, dout, lse, offset, window, row_correction=None, dq=None, dk=None, dv=None):
+        """attentionBackwardWindowed (model/compress_attention.go:509-541): dq, dk, dv (accumulated into the arrays given)."""
+        q, k, v, dout, lse = _f32(q), _f32(k), _f32(v), _f32(dout), _f32(lse)
+        B, Hq, T, D = q.shape; Hkv = k.shape[1]
+        o = _f32(out) if out is not None else None; rc = _f32(row_correction) if row_correction is not None else None
+        gq = np.zeros_like(q) if dq is None else _f32(dq).copy(); gk = np.zeros_like(k) if dk is None else _f32(dk).copy()
+        gv = np.zeros_like(v) if dv is None else _f32(dv).copy()
+        check(self.lib.gn_attention_windowed_backward(ptr(q), ptr(k), ptr(v), ptr(o) if o is not None else None, ptr(dout), ptr(lse),
+                                                      ptr(rc) if rc is not None else None, B, Hq, Hkv, T, D, offset, window, ptr(gq), ptr(gk), ptr(gv)))
+        return gq, gk, gv
+
     def attention_forward_split(self, q, k, v, ql, kl, hd, offset, window, key_start, key_end, segments=None):
         q, k, v = _f32(q), _f32(k), _f32(v); seg = _i32(segments) if segments is not None else None
         acc = np.empty(ql * hd, np.float32); mx = np.empty(ql, np.float32); sm = np.empty(ql, np.float32)

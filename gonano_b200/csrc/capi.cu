@@ -697,6 +697,85 @@ int gn_attention_backward(const gn_attention_params* p, const float* output, con
   GN_END();
 }
 
+// attentionForwardWindowed / attentionBackwardWindowed (model/compress_attention.go:488-541), no segment mask: the local
+// sliding-window branch for every (batch, query head) over head-major tensors.  head_dim 128 runs as one batched launch on the
+// tensor cores (forward tcgen05, backward mma.sync); other head dims go head by head through the float32 kernels.
+static void windowed_shape(AttnShape& sh, int batch, int n_head, int n_kv_head, int seq, int head_dim, int position_offset, int window) {
+  sh.B = batch; sh.Hq = n_head; sh.Hkv = n_kv_head; sh.D = head_dim; sh.Tq = seq; sh.Tk = seq;
+  sh.q_bstride = (int64_t)n_head * seq * head_dim; sh.q_tstride = head_dim; sh.q_hstride = (int64_t)seq * head_dim;
+  sh.kv_bstride = (int64_t)n_kv_head * seq * head_dim; sh.kv_tstride = head_dim; sh.kv_hstride = (int64_t)seq * head_dim;
+  sh.o_bstride = sh.q_bstride; sh.o_tstride = head_dim; sh.o_hstride = sh.q_hstride;
+  sh.window = window; sh.offset0 = position_offset; sh.tensor = gemm_default_kind();
+}
+static void one_head_shape(AttnShape& sh, int seq, int head_dim, int position_offset, int window) {
+  sh = AttnShape();
+  sh.D = head_dim; sh.Tq = seq; sh.Tk = seq; sh.q_tstride = head_dim; sh.kv_tstride = head_dim; sh.o_tstride = head_dim;
+  sh.window = window; sh.offset0 = position_offset; sh.tensor = gemm_default_kind();
+}
+int gn_attention_windowed_forward(const float* query, const float* key, const float* value, int batch, int n_head, int n_kv_head, int seq, int head_dim,
+                                  int position_offset, int window, float* out, float* lse) {
+  if (batch <= 0 || seq <= 0) return GN_OK;
+  GN_REQUIRE(query && key && value && out && n_kv_head > 0 && n_head % n_kv_head == 0 && head_dim > 0 && head_dim <= 128 && position_offset >= 0,
+             "attention_windowed_forward: bad argument");
+  GN_BEGIN();
+  const size_t hd = (size_t)seq * head_dim, nq = (size_t)batch * n_head * hd, nk = (size_t)batch * n_kv_head * hd;
+  const float* pq = st.in(query, nq); const float* pk = st.in(key, nk); const float* pv = st.in(value, nk);
+  float* po = st.out(out, nq); float* pl = lse ? st.out(lse, (size_t)batch * n_head * seq) : nullptr;
+  if (st.status != GN_OK) return st.status;
+  AttnShape sh; windowed_shape(sh, batch, n_head, n_kv_head, seq, head_dim, position_offset, window);
+#ifdef GN_HAVE_TCGEN05
+  if (sh.tensor && attention_tc_ok(sh, pq, pk, pv, po)) { GN_TRY(attention_tc_forward(sh, pq, pk, pv, po, pl, s)); GN_END(); }
+#endif
+  AttnShape one; one_head_shape(one, seq, head_dim, position_offset, window);
+  const int hr = n_head / n_kv_head;
+  for (int b = 0; b < batch; ++b)
+    for (int h = 0; h < n_head; ++h) {
+      const size_t qi = (size_t)b * n_head + h, ki = (size_t)b * n_kv_head + h / hr;
+      GN_TRY(attention_forward_launch(one, pq + qi * hd, pk + ki * hd, pv + ki * hd, po + qi * hd, pl ? pl + qi * seq : nullptr, s));
+    }
+  GN_END();
+}
+__global__ void __launch_bounds__(256) row_dot_kernel(const float* __restrict__ a, const float* __restrict__ b, int64_t rows, int width, float* __restrict__ dst) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t r = (int64_t)blockIdx.x * 8 + warp;
+  if (r >= rows) return;
+  float acc = 0.0f;
+  for (int c = lane; c < width; c += 32) acc = fmaf(a[r * width + c], b[r * width + c], acc);
+  acc = warp_sum(acc);
+  if (lane == 0) dst[r] = acc;
+}
+int gn_attention_windowed_backward(const float* query, const float* key, const float* value, const float* output, const float* out_grad, const float* lse,
+                                   const float* row_correction, int batch, int n_head, int n_kv_head, int seq, int head_dim, int position_offset, int window,
+                                   float* dq, float* dk, float* dv) {
+  if (batch <= 0 || seq <= 0) return GN_OK;
+  GN_REQUIRE(query && key && value && out_grad && lse && dq && dk && dv && (output || row_correction) && n_kv_head > 0 && n_head % n_kv_head == 0 &&
+             head_dim > 0 && head_dim <= 128 && position_offset >= 0, "attention_windowed_backward: bad argument");
+  GN_BEGIN();
+  const size_t hd = (size_t)seq * head_dim, nq = (size_t)batch * n_head * hd, nk = (size_t)batch * n_kv_head * hd, nt = (size_t)batch * n_head * seq;
+  const float* pq = st.in(query, nq); const float* pk = st.in(key, nk); const float* pv = st.in(value, nk);
+  const float* po = output ? st.in(output, nq) : nullptr; const float* pg = st.in(out_grad, nq); const float* pl = st.in(lse, nt);
+  const float* pr = row_correction ? st.in(row_correction, nt) : nullptr;
+  float* gq = st.out(dq, nq, true); float* gk = st.out(dk, nk, true); float* gv = st.out(dv, nk, true);
+  float* delta = st.temp<float>(nt);
+  if (st.status != GN_OK) return st.status;
+  AttnShape sh; windowed_shape(sh, batch, n_head, n_kv_head, seq, head_dim, position_offset, window);
+  if (sh.tensor && attention_mma_ok(sh, pq, pk, pv, pg, gq) && (reinterpret_cast<uintptr_t>(gk) & 15) == 0 && (reinterpret_cast<uintptr_t>(gv) & 15) == 0) {
+    const float* dl = pr;
+    if (!dl) { row_dot_kernel<<<(unsigned)ceil_div((int64_t)nt, 8), 256, 0, s>>>(pg, po, (int64_t)nt, head_dim, delta); GN_LAUNCH_CHECK(); dl = delta; }
+    GN_TRY(attention_mma_backward(sh, pq, pk, pv, pg, pl, dl, gq, gk, gv, 1, s));
+    GN_END();
+  }
+  AttnShape one; one_head_shape(one, seq, head_dim, position_offset, window);
+  const int hr = n_head / n_kv_head;
+  for (int b = 0; b < batch; ++b)
+    for (int h = 0; h < n_head; ++h) {
+      const size_t qi = (size_t)b * n_head + h, ki = (size_t)b * n_kv_head + h / hr;
+      GN_TRY(attention_backward_launch(one, pq + qi * hd, pk + ki * hd, pv + ki * hd, po ? po + qi * hd : nullptr, pg + qi * hd, pl + qi * seq,
+                                       pr ? pr + qi * seq : nullptr, gq + qi * hd, gk + ki * hd, gv + ki * hd, 1, delta + qi * seq, s));
+    }
+  GN_END();
+}
+
 int gn_sample_next_token(const float* logits, int rows, int vocab, const float* uniforms, const uint64_t* seeds, int group, uint32_t step,
                          float temperature, int top_k, int32_t* out) {
   GN_REQUIRE(logits && out, "sample_next_token: null argument");

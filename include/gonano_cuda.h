@@ -199,6 +199,17 @@ int gn_attention_combine(const float* acc, const float* maximum, const float* su
 int gn_attention_backward(const gn_attention_params* p, const float* output, const float* out_grad, const float* lse,
                           const float* row_correction, float* dq, float* dk, float* dv);
 
+/* attentionForwardWindowed / attentionBackwardWindowed (model/compress_attention.go:488-541), no segment mask: the local
+ * sliding-window branch of a compressed attention layer for every (batch, query head).  query / out / out_grad / dq
+ * [batch, n_head, seq, head_dim], key / value / dk / dv [batch, n_kv_head, seq, head_dim], lse / row_correction
+ * [batch, n_head, seq].  The backward accumulates into dq, dk, dv; it takes the (merged) log-sum-exp and either the row
+ * correction dO . O of the merged output or, when that is NULL, the forward output. */
+int gn_attention_windowed_forward(const float* query, const float* key, const float* value, int batch, int n_head, int n_kv_head, int seq, int head_dim,
+                                  int position_offset, int window, float* out, float* lse);
+int gn_attention_windowed_backward(const float* query, const float* key, const float* value, const float* output, const float* out_grad, const float* lse,
+                                   const float* row_correction, int batch, int n_head, int n_kv_head, int seq, int head_dim, int position_offset, int window,
+                                   float* dq, float* dk, float* dv);
+
 /* ===================================================================== *
  * Stand-alone kernels of the RL step (host or device pointers)          *
  * ===================================================================== */

@@ -578,3 +578,37 @@ def test_heavily_compressed_layer_incremental_equals_full(oracle, bk):
         out, lse = bk.attention_merge(og.reshape(-1, D), lg.reshape(-1), ol.reshape(-1, D), ll.reshape(-1))
         close(np.asarray(out).reshape(B, Hq, D), full[:, :, p], 2e-5, 2e-6)
         close(np.asarray(lse).reshape(B, Hq), full_l[:, :, p], 2e-5, 2e-6)
+
+
+# the local sliding-window branch for every (batch, query head), head-major (model/compress_attention.go:488-541)
+@pytest.mark.parametrize("B,Hq,Hkv,T,D,window,corr", [(2, 4, 2, 45, 64, 6, True), (2, 8, 1, 300, 128, 64, True), (1, 6, 2, 200, 128, 512, False),
+                                                      (1, 2, 2, 37, 128, 5, False), (1, 3, 1, 20, 16, -1, True)])
+def test_attention_windowed(oracle, bk, B, Hq, Hkv, T, D, window, corr):
+    rng = np.random.default_rng(T + D + window)
+    hr = Hq // Hkv
+    q = (rng.standard_normal((B, Hq, T, D)) * 0.4).astype(np.float32)
+    k = (rng.standard_normal((B, Hkv, T, D)) * 0.4).astype(np.float32); v = rng.standard_normal((B, Hkv, T, D)).astype(np.float32)
+    dout = rng.standard_normal((B, Hq, T, D)).astype(np.float32)
+    ref = oracle.Backend(0)
+    want = np.zeros_like(q); want_l = np.zeros((B, Hq, T), np.float32)
+    for b in range(B):
+        for h in range(Hq):
+            o, l = ref.attention_forward(q[b, h], k[b, h // hr], v[b, h // hr], T, T, D, 0, window)
+            want[b, h] = np.asarray(o).reshape(T, D); want_l[b, h] = np.asarray(l).reshape(T)
+    got, got_l = bk.attention_windowed_forward(q, k, v, 0, window)
+    close(got, want, 1e-4, 1e-5); close(got_l, want_l, 1e-4, 1e-5)
+    # backward with the forward's own statistics, or as one branch of a merged softmax: a larger log-sum-exp and a given row correction
+    lse = want_l; rc = None
+    if corr:
+        lse = (want_l + np.abs(rng.standard_normal(want_l.shape)).astype(np.float32)).astype(np.float32)
+        rc = rng.standard_normal((B, Hq, T)).astype(np.float32)
+    wq = np.zeros_like(q); wk = np.zeros_like(k); wv = np.zeros_like(v)
+    for b in range(B):
+        for h in range(Hq):
+            g = ref.attention_backward(q[b, h], k[b, h // hr], v[b, h // hr], dout[b, h], lse[b, h], T, T, D, 0, window,
+                                       row_correction=None if rc is None else rc[b, h], dq=wq[b, h].ravel(), dk=wk[b, h // hr].ravel(), dv=wv[b, h // hr].ravel())
+            wq[b, h] = g[0].reshape(T, D); wk[b, h // hr] = g[1].reshape(T, D); wv[b, h // hr] = g[2].reshape(T, D)
+    seed = [rng.standard_normal(x.shape).astype(np.float32) for x in (q, k, v)]
+    gq, gk, gv = bk.attention_windowed_backward(q, k, v, want, dout, lse, 0, window, rc, *seed)
+    for g, s0, w in zip((gq, gk, gv), seed, (wq, wk, wv)):
+        close(g, s0 + w, 2e-4, 2e-5 * max(1.0, float(np.max(np.abs(w)))))
