@@ -74,6 +74,8 @@ SIGNATURES = {
     "gn_indexer_distillation_grad": (I, [vp, vp, vp, vp, I, C.c_int64, I, I, I, C.c_float, vp]),
     "gn_attention_windowed_forward": (I, [vp, vp, vp, I, I, I, I, I, I, I, vp, vp]),
     "gn_attention_windowed_backward": (I, [vp, vp, vp, vp, vp, vp, vp, I, I, I, I, I, I, I, vp, vp, vp]),
+    "gn_compress_forward": (I, [vp, vp, vp, vp, vp, I, I, I, I, I, I, vp, vp, vp]),
+    "gn_compress_backward": (I, [vp, vp, vp, vp, vp, vp, vp, vp, vp, I, I, I, I, I, I, vp, vp, vp, vp, vp]),
     "gn_hierarchical_cap": (I, [I, I]),
     "gn_select_blocks_hierarchical": (I, [vp, I, I, I, I, I, I, I, vp, vp, vp, vp]),
     "gn_select_blocks_within_pool": (I, [vp, I, I, I, I, I, vp, vp, I, vp, vp]),

@@ -155,6 +155,26 @@ class CudaBackend:
                                               ptr(gh), ptr(gv), ptr(gw), ptr(gb)))
         return gh, gv, gw, gb
 
+    def compress_forward(self, hidden, key, value, weight, bias, ratio):
+        """compressForward (model/compress_attention.go:562-622): key / value [B,Hkv,T,D] -> key_c, value_c [B,Hkv,blocks,D], probabilities [B,blocks,ratio,D]."""
+        hidden, key, value, weight, bias = _f32(hidden), _f32(key), _f32(value), _f32(weight), _f32(bias)
+        B, T, d = hidden.shape; H, D = key.shape[1], key.shape[3]
+        blocks = (T + ratio - 1) // ratio
+        kc = np.zeros((B, H, blocks, D), np.float32); vc = np.zeros_like(kc); prob = np.zeros((B, blocks, ratio, D), np.float32)
+        check(self.lib.gn_compress_forward(ptr(hidden), ptr(key), ptr(value), ptr(weight), ptr(bias), B, H, T, d, D, ratio, ptr(kc), ptr(vc), ptr(prob)))
+        return kc, vc, prob
+
+    def compress_backward(self, hidden, key, value, weight, prob, kc, vc, gkc, gvc, ratio, grad_weight=None, grad_bias=None):
+        """compressBackward (model/compress_attention.go:1182-1209): grad_hidden, grad_key, grad_value, grad_weight, grad_bias."""
+        hidden, key, value, weight, prob, kc, vc, gkc, gvc = (_f32(x) for x in (hidden, key, value, weight, prob, kc, vc, gkc, gvc))
+        B, T, d = hidden.shape; H, D = key.shape[1], key.shape[3]
+        gh = np.zeros_like(hidden); gk = np.zeros_like(key); gv = np.zeros_like(value)
+        gw = np.zeros_like(weight) if grad_weight is None else _f32(grad_weight).copy()
+        gb = np.zeros((ratio, D), np.float32) if grad_bias is None else _f32(grad_bias).copy()
+        check(self.lib.gn_compress_backward(ptr(hidden), ptr(key), ptr(value), ptr(weight), ptr(prob), ptr(kc), ptr(vc), ptr(gkc), ptr(gvc), B, H, T, d, D, ratio,
+                                            ptr(gh), ptr(gk), ptr(gv), ptr(gw), ptr(gb)))
+        return gh, gk, gv, gw, gb
+
     def compressed_attention_forward(self, q, kc, vc, ratio, offset=0):
         """compressedAttentionForward (model/compress_attention.go:624-673): q [B,Hq,T,D], kc / vc [B,Hkv,blocks,D]; with offset > 0 the
         T tokens stand at positions offset .. over the cached blocks (forwardCompressed, :962-1003)."""

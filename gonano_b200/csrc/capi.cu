@@ -351,6 +351,54 @@ int gn_compressor_backward(const float* hidden, const float* value, const float*
   GN_TRY(st.finish());
   return gemm_check_error(s);
 }
+// compressForward (model/compress_attention.go:562-622), no segment mask: one logit product, then the block softmax applied to the keys and values of every kv head
+int gn_compress_forward(const float* hidden, const float* key, const float* value, const float* logit_weight, const float* bias, int batch, int n_kv_head, int seq,
+                        int embed, int head_dim, int ratio, float* key_c, float* value_c, float* probabilities) {
+  if (batch <= 0 || seq <= 0 || head_dim <= 0 || n_kv_head <= 0) return GN_OK;
+  GN_REQUIRE(hidden && key && value && logit_weight && bias && key_c && value_c && ratio >= 1 && embed > 0, "compress_forward: bad argument");
+  const int blocks = (seq + ratio - 1) / ratio;
+  GN_BEGIN();
+  const size_t rows = (size_t)batch * seq, nkv = (size_t)batch * n_kv_head * seq * head_dim, nc = (size_t)batch * n_kv_head * blocks * head_dim;
+  const float* dh = st.in(hidden, rows * embed); const float* dk = st.in(key, nkv); const float* dv = st.in(value, nkv);
+  const float* dw = st.in(logit_weight, (size_t)head_dim * embed); const float* db = st.in(bias, (size_t)ratio * head_dim);
+  float* kc = st.out(key_c, nc); float* vc = st.out(value_c, nc);
+  const size_t np = (size_t)batch * blocks * ratio * head_dim;
+  float* dp = probabilities ? st.out(probabilities, np) : st.temp<float>(np);
+  float* logits = st.temp<float>(rows * head_dim);
+  if (st.status != GN_OK) return st.status;
+  GemmArgs g;
+  g.A = dh; g.B = dw; g.C = logits; g.M = (int)rows; g.N = head_dim; g.K = embed; g.lda = embed; g.ldb = embed; g.ldc = head_dim; g.b_trans = 1;
+  GN_TRY(gemm_dispatch(g, gemm_default_kind(), s));
+  GN_TRY(compress_heads_launch(logits, db, dk, dv, batch, n_kv_head, seq, head_dim, ratio, kc, vc, dp, s));
+  GN_TRY(st.finish());
+  return gemm_check_error(s);
+}
+// compressBackward (model/compress_attention.go:1182-1209): grad_hidden, grad_key, grad_value are overwritten, grad_weight and grad_bias accumulated
+int gn_compress_backward(const float* hidden, const float* key, const float* value, const float* logit_weight, const float* probabilities, const float* key_c,
+                         const float* value_c, const float* grad_key_c, const float* grad_value_c, int batch, int n_kv_head, int seq, int embed, int head_dim,
+                         int ratio, float* grad_hidden, float* grad_key, float* grad_value, float* grad_weight, float* grad_bias) {
+  if (batch <= 0 || seq <= 0 || head_dim <= 0 || n_kv_head <= 0) return GN_OK;
+  GN_REQUIRE(hidden && key && value && logit_weight && probabilities && key_c && value_c && grad_key_c && grad_value_c && grad_hidden && grad_key && grad_value &&
+             grad_weight && grad_bias && ratio >= 1 && embed > 0, "compress_backward: bad argument");
+  const int blocks = (seq + ratio - 1) / ratio;
+  GN_BEGIN();
+  const size_t rows = (size_t)batch * seq, nkv = (size_t)batch * n_kv_head * seq * head_dim, nc = (size_t)batch * n_kv_head * blocks * head_dim;
+  const float* dh = st.in(hidden, rows * embed); const float* dk = st.in(key, nkv); const float* dv = st.in(value, nkv);
+  const float* dw = st.in(logit_weight, (size_t)head_dim * embed);
+  const float* dp = st.in(probabilities, (size_t)batch * blocks * ratio * head_dim);
+  const float* kc = st.in(key_c, nc); const float* vc = st.in(value_c, nc); const float* gkc = st.in(grad_key_c, nc); const float* gvc = st.in(grad_value_c, nc);
+  float* gh = st.out(grad_hidden, rows * embed); float* gk = st.out(grad_key, nkv); float* gv = st.out(grad_value, nkv);
+  float* gw = st.out(grad_weight, (size_t)head_dim * embed, true); float* gb = st.out(grad_bias, (size_t)ratio * head_dim, true);
+  float* gl = st.temp<float>(rows * head_dim);
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(compress_heads_backward_launch(dk, dv, dp, kc, vc, gkc, gvc, batch, n_kv_head, seq, head_dim, ratio, gl, gk, gv, gb, s));
+  { GemmArgs g; g.A = gl; g.lda = head_dim; g.B = dw; g.ldb = embed; g.b_trans = 0; g.C = gh; g.ldc = embed; g.M = (int)rows; g.N = embed; g.K = head_dim;
+    GN_TRY(gemm_dispatch(g, gemm_default_kind(), s)); }                       // dhidden = dlogits W
+  { GemmArgs g; g.A = gl; g.lda = head_dim; g.a_trans = 1; g.B = dh; g.ldb = embed; g.b_trans = 0; g.C = gw; g.ldc = embed; g.M = head_dim; g.N = embed; g.K = (int)rows;
+    g.epilogue = EPI_ACCUM; GN_TRY(gemm_dispatch(g, gemm_default_kind(), s)); }   // dW += dlogits^T hidden
+  GN_TRY(st.finish());
+  return gemm_check_error(s);
+}
 // compressedAttentionForward (model/compress_attention.go:624-673), no segment mask
 int gn_compressed_attention_forward(const float* query, const float* key_c, const float* value_c, int batch, int n_head, int n_kv_head, int seq, int head_dim,
                                     int blocks, int ratio, float* out, float* lse) {

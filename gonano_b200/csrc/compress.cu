@@ -42,6 +42,62 @@ __global__ void __launch_bounds__(256) compressor_pool_kernel(const float* __res
   compressed[idx] = acc;
 }
 
+// compressForward for every kv head at once (model/compress_attention.go:562-622): the block softmax depends on the hidden state
+// alone, so a thread computes the weights of its (batch, block, channel) once -- the same arithmetic as compressor_pool_kernel --
+// and applies them to the keys and the values of every kv head.  probabilities [B, blocks, ratio, C] is written (it is also the
+// scratch between the two steps).
+__global__ void __launch_bounds__(256) compress_heads_kernel(const float* __restrict__ logits, const float* __restrict__ bias, const float* __restrict__ key,
+                                                             const float* __restrict__ value, int B, int H, int T, int C, int ratio, int blocks,
+                                                             float* __restrict__ key_c, float* __restrict__ value_c, float* __restrict__ probabilities) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)B * blocks * C) return;
+  const int c = (int)(idx % C); const int64_t bb = idx / C; const int blk = (int)(bb % blocks); const int b = (int)(bb / blocks);
+  const int t0 = blk * ratio, rows = min(ratio, T - t0);
+  const float* lg = logits + ((int64_t)b * T + t0) * C + c;
+  float mx = -INFINITY;
+  for (int r = 0; r < rows; ++r) mx = fmaxf(mx, lg[(int64_t)r * C] + bias[(int64_t)r * C + c]);
+  double total = 0.0;
+  for (int r = 0; r < rows; ++r) total += (double)(float)exp((double)(lg[(int64_t)r * C] + bias[(int64_t)r * C + c] - mx));
+  const float inv = total > 0.0 ? (float)(1.0 / total) : 0.0f;
+  float* pp = probabilities + (((int64_t)b * blocks + blk) * ratio) * C + c;
+  for (int r = 0; r < ratio; ++r) pp[(int64_t)r * C] = (r < rows && total > 0.0) ? (float)exp((double)(lg[(int64_t)r * C] + bias[(int64_t)r * C + c] - mx)) * inv : 0.0f;
+  for (int h = 0; h < H; ++h) {
+    const int64_t head = (int64_t)b * H + h;
+    const float* kp = key + (head * T + t0) * C + c; const float* vp = value + (head * T + t0) * C + c;
+    float ak = 0.0f, av = 0.0f;
+    for (int r = 0; r < rows; ++r) {
+      const float p = pp[(int64_t)r * C];
+      ak = __fadd_rn(ak, __fmul_rn(p, kp[(int64_t)r * C])); av = __fadd_rn(av, __fmul_rn(p, vp[(int64_t)r * C]));
+    }
+    key_c[(head * blocks + blk) * C + c] = ak; value_c[(head * blocks + blk) * C + c] = av;
+  }
+}
+// compressBackward for every kv head at once (model/compress_attention.go:1182-1209): grad_key / grad_value [B, H, T, C] of the rows,
+// and the logit gradient summed over the heads and over keys and values (the hidden-state and weight gradients follow from it).
+__global__ void __launch_bounds__(256) compress_heads_bwd_kernel(const float* __restrict__ key, const float* __restrict__ value,
+                                                                 const float* __restrict__ probabilities, const float* __restrict__ key_c,
+                                                                 const float* __restrict__ value_c, const float* __restrict__ grad_key_c,
+                                                                 const float* __restrict__ grad_value_c, int B, int H, int T, int C, int ratio, int blocks,
+                                                                 float* __restrict__ grad_logits, float* __restrict__ grad_key, float* __restrict__ grad_value) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)B * blocks * C) return;
+  const int c = (int)(idx % C); const int64_t bb = idx / C; const int blk = (int)(bb % blocks); const int b = (int)(bb / blocks);
+  const int t0 = blk * ratio, rows = min(ratio, T - t0);
+  const float* pp = probabilities + (((int64_t)b * blocks + blk) * ratio) * C + c;
+  for (int r = 0; r < rows; ++r) {
+    const float p = pp[(int64_t)r * C];
+    float gl = 0.0f;
+    for (int h = 0; h < H; ++h) {
+      const int64_t head = (int64_t)b * H + h, ci = (head * blocks + blk) * C + c, o = (head * T + t0 + r) * C + c;
+      const float pk = __fmul_rn(p, grad_key_c[ci]), pv = __fmul_rn(p, grad_value_c[ci]);
+      grad_key[o] = pk; grad_value[o] = pv;
+      gl = __fadd_rn(gl, __fmul_rn(pk, __fsub_rn(key[o], key_c[ci])));
+      gl = __fadd_rn(gl, __fmul_rn(pv, __fsub_rn(value[o], value_c[ci])));
+    }
+    grad_logits[((int64_t)b * T + t0 + r) * C + c] = gl;
+  }
+}
+
 // backward of the block softmax: one thread per (batch, block, channel) writes dlogits and dvalue of its rows
 __global__ void __launch_bounds__(256) compressor_pool_bwd_kernel(const float* __restrict__ value, const float* __restrict__ probabilities,
                                                                   const float* __restrict__ compressed, const float* __restrict__ grad_compressed, int B, int T, int C,
@@ -581,6 +637,30 @@ int compressor_pool_backward_launch(const float* value, const float* probabiliti
   const int64_t n = (int64_t)B * blocks * C;
   if (n <= 0) return GN_OK;
   compressor_pool_bwd_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, s>>>(value, probabilities, compressed, grad_compressed, B, T, C, ratio, blocks, grad_logits, grad_value);
+  GN_LAUNCH_CHECK();
+  compressor_bias_bwd_kernel<<<ceil_div((int64_t)ratio * C, 256), 256, 0, s>>>(grad_logits, B, T, C, ratio, grad_bias);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+int compress_heads_launch(const float* logits, const float* bias, const float* key, const float* value, int B, int H, int T, int C, int ratio, float* key_c,
+                          float* value_c, float* probabilities, cudaStream_t s) {
+  const int blocks = (T + ratio - 1) / ratio;
+  const int64_t n = (int64_t)B * blocks * C;
+  if (n <= 0 || H <= 0) return GN_OK;
+  compress_heads_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, s>>>(logits, bias, key, value, B, H, T, C, ratio, blocks, key_c, value_c, probabilities);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+
+int compress_heads_backward_launch(const float* key, const float* value, const float* probabilities, const float* key_c, const float* value_c,
+                                   const float* grad_key_c, const float* grad_value_c, int B, int H, int T, int C, int ratio, float* grad_logits, float* grad_key,
+                                   float* grad_value, float* grad_bias, cudaStream_t s) {
+  const int blocks = (T + ratio - 1) / ratio;
+  const int64_t n = (int64_t)B * blocks * C;
+  if (n <= 0 || H <= 0) return GN_OK;
+  compress_heads_bwd_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, s>>>(key, value, probabilities, key_c, value_c, grad_key_c, grad_value_c, B, H, T, C, ratio, blocks,
+                                                                       grad_logits, grad_key, grad_value);
   GN_LAUNCH_CHECK();
   compressor_bias_bwd_kernel<<<ceil_div((int64_t)ratio * C, 256), 256, 0, s>>>(grad_logits, B, T, C, ratio, grad_bias);
   GN_LAUNCH_CHECK();

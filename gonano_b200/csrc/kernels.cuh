@@ -74,6 +74,12 @@ int compressor_pool_launch(const float* logits, const float* bias, const float* 
 // dlogits and dvalue ([B, T, C], every element written) and the bias gradient (accumulated) from the gradient of the compressed output
 int compressor_pool_backward_launch(const float* value, const float* probabilities, const float* compressed, const float* grad_compressed, int B, int T, int C,
                                     int ratio, float* grad_logits, float* grad_value, float* grad_bias, cudaStream_t s);
+// compressForward / compressBackward over every kv head: logits [B * T, C] = hidden W^T; key / value [B, H, T, C]; probabilities [B, blocks, ratio, C]
+int compress_heads_launch(const float* logits, const float* bias, const float* key, const float* value, int B, int H, int T, int C, int ratio, float* key_c,
+                          float* value_c, float* probabilities, cudaStream_t s);
+int compress_heads_backward_launch(const float* key, const float* value, const float* probabilities, const float* key_c, const float* value_c,
+                                   const float* grad_key_c, const float* grad_value_c, int B, int H, int T, int C, int ratio, float* grad_logits, float* grad_key,
+                                   float* grad_value, float* grad_bias, cudaStream_t s);
 // selection == nullptr: every block before the query's own; else the token's selected blocks ([B * Hkv, T, topk] with counts [B * Hkv, T])
 // (token t stands at position offset + t: offset > 0 is the cached inference form)
 int compressed_attention_launch(const float* q, const float* kc, const float* vc, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* out, float* lse,

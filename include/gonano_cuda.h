@@ -113,6 +113,16 @@ int gn_indexer_scores_backward(const float* grad_scores, const float* query, con
  * padded with -1, counts [tokens]; descending score, ties toward the smaller block index). */
 int gn_compressor_forward(const float* hidden, const float* value, const float* logit_weight, const float* bias, int batch, int seq, int embed,
                           int channels, int ratio, float* compressed, float* probabilities);
+/* compressForward / compressBackward (model/compress_attention.go:562-622, 1182-1209), no segment mask: the compressor over the
+ * keys and the values of every kv head.  hidden [batch, seq, embed], key / value [batch, n_kv_head, seq, head_dim] ->
+ * key_c / value_c [batch, n_kv_head, blocks, head_dim]; the block softmax depends on the hidden state alone, so one logit
+ * product and one set of probabilities [batch, blocks, ratio, head_dim] (nullable in the forward) serve every head.  The
+ * backward overwrites grad_hidden, grad_key, grad_value and accumulates into grad_weight, grad_bias. */
+int gn_compress_forward(const float* hidden, const float* key, const float* value, const float* logit_weight, const float* bias, int batch, int n_kv_head, int seq,
+                        int embed, int head_dim, int ratio, float* key_c, float* value_c, float* probabilities);
+int gn_compress_backward(const float* hidden, const float* key, const float* value, const float* logit_weight, const float* probabilities, const float* key_c,
+                         const float* value_c, const float* grad_key_c, const float* grad_value_c, int batch, int n_kv_head, int seq, int embed, int head_dim,
+                         int ratio, float* grad_hidden, float* grad_key, float* grad_value, float* grad_weight, float* grad_bias);
 /* ChannelCompressor.Backward (model/compress.go:182-237): probabilities and compressed are gn_compressor_forward's
  * outputs; grad_hidden [batch, seq, embed] and grad_value [batch, seq, channels] are overwritten, grad_weight
  * [channels, embed] and grad_bias [ratio, channels] accumulated. */

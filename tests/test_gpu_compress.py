@@ -612,3 +612,28 @@ def test_attention_windowed(oracle, bk, B, Hq, Hkv, T, D, window, corr):
     gq, gk, gv = bk.attention_windowed_backward(q, k, v, want, dout, lse, 0, window, rc, *seed)
     for g, s0, w in zip((gq, gk, gv), seed, (wq, wk, wv)):
         close(g, s0 + w, 2e-4, 2e-5 * max(1.0, float(np.max(np.abs(w)))))
+
+
+# compressForward / compressBackward over every kv head at once (model/compress_attention.go:562-622, 1182-1209) against the
+# oracle's compressor applied head by head to keys and values, as the reference does
+@pytest.mark.parametrize("B,Hkv,T,d,D,ratio", [(2, 2, 37, 48, 32, 4), (1, 1, 130, 96, 128, 8), (3, 4, 16, 24, 16, 1)])
+def test_compress_heads(oracle, bk, B, Hkv, T, d, D, ratio):
+    rng = np.random.default_rng(B * 10 + T)
+    blocks = (T + ratio - 1) // ratio
+    x = rng.standard_normal((B, T, d)).astype(np.float32)
+    k = rng.standard_normal((B, Hkv, T, D)).astype(np.float32); v = rng.standard_normal((B, Hkv, T, D)).astype(np.float32)
+    w = (rng.standard_normal((D, d)) * 0.3).astype(np.float32); bias = (rng.standard_normal((ratio, D)) * 0.5).astype(np.float32)
+    gkc = rng.standard_normal((B, Hkv, blocks, D)).astype(np.float32); gvc = rng.standard_normal((B, Hkv, blocks, D)).astype(np.float32)
+    want_kc = np.zeros((B, Hkv, blocks, D), np.float32); want_vc = np.zeros_like(want_kc)
+    want = [np.zeros_like(x), np.zeros_like(k), np.zeros_like(v), np.zeros_like(w), np.zeros_like(bias)]
+    for b in range(B):
+        for h in range(Hkv):
+            for val, comp, gc, gval in ((k, want_kc, gkc, want[1]), (v, want_vc, gvc, want[2])):
+                comp[b, h], prob = (a[0] for a in oracle.compressor_forward(x[b:b + 1], val[b, h][None], w, bias, ratio))
+                gh, gv_, gw, gb = oracle.compressor_backward(x[b:b + 1], val[b, h][None], w, bias, ratio, gc[b, h][None])
+                want[0][b] += gh[0]; gval[b, h] = gv_[0]; want[3] += gw; want[4] += gb
+    kc, vc, prob = bk.compress_forward(x, k, v, w, bias, ratio)
+    close(kc, want_kc, 1e-5, 1e-6); close(vc, want_vc, 1e-5, 1e-6)
+    got = bk.compress_backward(x, k, v, w, prob, kc, vc, gkc, gvc, ratio)
+    for g, t_ in zip(got, want):
+        close(g, t_, 2e-4, 2e-5 * max(1.0, float(np.max(np.abs(t_)))))
