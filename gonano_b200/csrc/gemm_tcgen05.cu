@@ -35,6 +35,7 @@
 #include <type_traits>
 
 #include "kernels.cuh"
+#include <unordered_map>
 #include "tcgen05.cuh"
 
 namespace gn {
@@ -819,7 +820,34 @@ int ensure_init() {
   return GN_OK;
 }
 
+// A tensor map depends on the address, the extents, the pitch and the box alone, never on the data, and the same few thousand
+// (array, shape) pairs come back every step: encoded maps are kept per host thread and copied out (128 bytes) instead of being
+// encoded again (several per product, which shows where launches are the bound: the optimizer step, the eager decode loop).
+struct MapKey {
+  const void* base; int64_t a, b, c; int d, e, kind;
+  bool operator==(const MapKey& o) const { return base == o.base && a == o.a && b == o.b && c == o.c && d == o.d && e == o.e && kind == o.kind; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+    auto mix = [&](uint64_t v) { h ^= v + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2); };
+    mix((uint64_t)k.a); mix((uint64_t)k.b); mix((uint64_t)k.c); mix(((uint64_t)(uint32_t)k.d << 32) | (uint32_t)k.e); mix((uint64_t)k.kind);
+    return (size_t)h;
+  }
+};
+template <typename F>
+int cached_map(CUtensorMap* map, const MapKey& key, F&& encode) {
+  thread_local std::unordered_map<MapKey, CUtensorMap, MapKeyHash> maps;
+  auto it = maps.find(key);
+  if (it != maps.end()) { *map = it->second; return GN_OK; }
+  GN_TRY(encode());
+  if (maps.size() >= (1u << 16)) maps.clear();
+  maps.emplace(key, *map);
+  return GN_OK;
+}
+
 int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t k, int64_t ld, int box_rows) {
+  return cached_map(map, MapKey{base, rows, k, ld, box_rows, 0, 0}, [&]() -> int {
   cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
   cuuint32_t box[2] = {(cuuint32_t)TBK, (cuuint32_t)box_rows};
@@ -828,12 +856,14 @@ int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t k, int64
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with %d (rows %lld, k %lld, ld %lld)", (int)r, (long long)rows, (long long)k, (long long)ld); return GN_ERR_CUDA; }
   return GN_OK;
+  });
 }
 
 // 3-D map over the same array, for mn a multiple of 32: dimensions {32 consecutive mn, k, mn / 32}; a box
 // {32, 32, groups} is a whole MN-major tile (its MN groups land 4096 bytes apart, as the four or eight 2-D boxes do),
 // so a k-block costs one copy per operand half instead of up to twelve.
 int make_map_mn3(CUtensorMap* map, const float* base, int64_t mn, int64_t k, int64_t ld, int groups) {
+  return cached_map(map, MapKey{base, mn, k, ld, groups, 0, 1}, [&]() -> int {
   cuuint64_t dims[3] = {32, (cuuint64_t)k, (cuuint64_t)(mn / 32)};
   cuuint64_t strides[2] = {(cuuint64_t)ld * sizeof(float), 32 * sizeof(float)};
   cuuint32_t box[3] = {32, (cuuint32_t)TBK, (cuuint32_t)groups};
@@ -842,10 +872,12 @@ int make_map_mn3(CUtensorMap* map, const float* base, int64_t mn, int64_t k, int
                         CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (MN-major, 3-D) failed with %d (mn %lld, k %lld, ld %lld)", (int)r, (long long)mn, (long long)k, (long long)ld); return GN_ERR_CUDA; }
   return GN_OK;
+  });
 }
 
 // 2-D map over a row-major [k, mn] array (pitch ld floats): a box [32 mn x 32 k] is one MN group of the MN-major tile above.
 int make_map_mn(CUtensorMap* map, const float* base, int64_t mn, int64_t k, int64_t ld) {
+  return cached_map(map, MapKey{base, mn, k, ld, 0, 0, 2}, [&]() -> int {
   cuuint64_t dims[2] = {(cuuint64_t)mn, (cuuint64_t)k};
   cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
   cuuint32_t box[2] = {32, (cuuint32_t)TBK};
@@ -854,6 +886,7 @@ int make_map_mn(CUtensorMap* map, const float* base, int64_t mn, int64_t k, int6
                         CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (MN-major) failed with %d (mn %lld, k %lld, ld %lld)", (int)r, (long long)mn, (long long)k, (long long)ld); return GN_ERR_CUDA; }
   return GN_OK;
+  });
 }
 
 int ensure_buf(SplitBuf& b, size_t floats) {
@@ -1001,8 +1034,11 @@ int launch_tc(GemmState& gs, const SplitBuf& a, const SplitBuf& b, const TcEpilo
     cuuint32_t box[3] = {32, 32, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     auto enc = [&](CUtensorMap* mp, float* ptr) {
-      return g_encode(mp, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+      const MapKey key{ptr, ((int64_t)M << 32) | (int64_t)(uint32_t)N, (int64_t)strides[0], (int64_t)strides[1], splits, 0, 4};
+      return cached_map(mp, key, [&]() -> int {
+        return g_encode(mp, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? GN_OK : GN_ERR_CUDA;
+      }) == GN_OK;
     };
     bool ok = enc(&mc, ep.C);
     if (ok && ep.c_hi) ok = enc(&mch, ep.c_hi) && enc(&mcl, ep.c_lo);
@@ -1290,6 +1326,7 @@ int tc_make_map_mn3(CUtensorMap* map, const float* base, int64_t mn, int64_t k, 
 }
 int tc_make_map3(CUtensorMap* map, const float* base, int64_t rows, int64_t k, int64_t ld, int box_rows, int kblocks) {
   GN_TRY(ensure_init());
+  return cached_map(map, MapKey{base, rows, k, ld, box_rows, kblocks, 3}, [&]() -> int {
   cuuint64_t dims[3] = {32, (cuuint64_t)rows, (cuuint64_t)(k / 32)};
   cuuint64_t strides[2] = {(cuuint64_t)ld * sizeof(float), 32 * sizeof(float)};
   cuuint32_t box[3] = {32, (cuuint32_t)box_rows, (cuuint32_t)kblocks};
@@ -1298,6 +1335,7 @@ int tc_make_map3(CUtensorMap* map, const float* base, int64_t rows, int64_t k, i
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (K-major, 3-D) failed with %d (rows %lld, k %lld, ld %lld)", (int)r, (long long)rows, (long long)k, (long long)ld); return GN_ERR_CUDA; }
   return GN_OK;
+  });
 }
 int tc_attention_scratch(cudaStream_t s, size_t floats, float** hi, float** lo, int** err_flag) {
   std::lock_guard<std::mutex> lock(g_mu);
