@@ -22,6 +22,7 @@
 #include <string>
 #include <vector>
 
+#include <cstring>
 #include "model_internal.cuh"
 
 using namespace gn;
@@ -483,7 +484,9 @@ int gn_ctx_set_option(gn_ctx* c, const char* name, int value) {
 #ifdef GN_HAVE_TCGEN05
   if (n == "attention_tcgen05") { attention_tc_enable(value); return GN_OK; }
 #endif
+  if (c) ++c->option_generation;
   if (c && n == "decode_graph") { c->use_graphs = value != 0; return GN_OK; }
+  if (c && n == "optimizer_graph") { c->optimizer_graph = value != 0; return GN_OK; }
   if (c && n == "optimizer_lanes") { GN_REQUIRE(value >= 1 && value <= 4, "optimizer_lanes must be 1..4"); c->optimizer_lanes = value; return GN_OK; }
   if (c && n == "head_chunk_rows") { GN_REQUIRE(value >= 1, "head_chunk_rows must be positive"); c->head_chunk_rows = value; return GN_OK; }
   cudaStream_t s = nullptr;
@@ -491,7 +494,7 @@ int gn_ctx_set_option(gn_ctx* c, const char* name, int value) {
   else { s = tier_a_stream_or_null(); GN_REQUIRE(s != nullptr, "gn_ctx_set_option(NULL, ...): no stand-alone call has run yet"); }
   return gemm_set_option(s, name, value);
 }
-int gn_ctx_set_gemm(gn_ctx* c, int kind) { GN_REQUIRE(c && (kind == 0 || kind == 1), "gemm kind must be 0 or 1"); c->gemm_kind = kind; return GN_OK; }
+int gn_ctx_set_gemm(gn_ctx* c, int kind) { GN_REQUIRE(c && (kind == 0 || kind == 1), "gemm kind must be 0 or 1"); c->gemm_kind = kind; ++c->option_generation; return GN_OK; }
 
 int gn_model_create(gn_ctx* ctx, const gn_config* cfg, gn_model** out) {
   GN_REQUIRE(ctx && cfg && out, "gn_model_create: null argument");
@@ -571,6 +574,8 @@ int gn_model_destroy(gn_model* m) {
     m->opt_ws_lane[l].release();
     if (m->opt_stream[l]) { cudaStreamSynchronize(m->opt_stream[l]); gemm_release_stream(m->opt_stream[l]); cudaStreamDestroy(m->opt_stream[l]); }
   }
+  if (m->opt_graph_exec) cudaGraphExecDestroy(m->opt_graph_exec);
+  if (m->opt_graph) cudaGraphDestroy(m->opt_graph);
   for (int l = 0; l <= gn_model::kOptLanes; ++l) if (m->opt_event[l]) cudaEventDestroy(m->opt_event[l]);
   for (int i = 0; i < 4; ++i) if (m->ev[i]) cudaEventDestroy(m->ev[i]);
   delete m;
@@ -724,16 +729,17 @@ std::vector<int> optimizer_owners(gn_model* m, int shard_count, const std::vecto
 extern "C" {
 namespace {
 
-int optimizer_run(gn_model* m, int shard, int shard_count) {
+// part: 0 everything, 1 all but the AdamW tensors (the part a graph can hold), 2 the AdamW tensors alone
+int optimizer_body(gn_model* m, int shard, int shard_count, int part) {
   cudaStream_t s = m->s();
   const gn_optimizer_config& c = m->opt_cfg;
-  ++m->opt_steps;
   const float dscale = (float)std::pow((double)m->d / 768.0, -0.5);   // model/optimizer.go:108
   const std::vector<int> owner = optimizer_owners(m, shard_count);
   // lanes: the owned tensors in cost order, each to the least loaded lane (the same cost model as the owners)
   const int lanes = std::max(1, std::min(m->ctx->optimizer_lanes, (int)gn_model::kOptLanes));
   std::vector<int> lane_of(m->params.size(), 0);
-  if (lanes > 1) {
+  const bool fork = lanes > 1 && part != 2;   // the few AdamW updates stay on the main stream
+  if (fork) {
     const std::vector<int> by_lane = optimizer_owners(m, lanes, &owner, shard);
     lane_of = by_lane;
     GN_CUDA(cudaEventRecord(m->opt_event[0], m->s()));
@@ -750,6 +756,9 @@ int optimizer_run(gn_model* m, int shard, int shard_count) {
     const int64_t n = (int64_t)pi.rows * pi.cols;
     auto sink = [&](float lr) { return sinkhorn_launch(p, g, mo, pi.rows, pi.cols, lr * c.lr_mult, 0.95f, 0.18f, 11, 1e-3f, 1e-20f, lane_ws, s); };
     auto adam = [&](float lr, float b1, float b2, float wd) { return adamw_launch(p, g, mo, se, n, m->opt_steps, lr * c.lr_mult, b1, b2, 1e-10f, wd, s); };
+    const bool is_adam = pi.name == "resid_lambdas" || pi.name == "x0_lambdas" || pi.name == "smear_gate.weight" || pi.name == "smear_lambda" ||
+                         pi.name == "backout_lambda";
+    if ((part == 1 && is_adam) || (part == 2 && !is_adam)) continue;
     if (pi.name == "lm_head.weight") GN_TRY(sink(c.unembedding_lr * dscale));
     else if (pi.name == "transformer.wte.weight") GN_TRY(sink(c.embedding_lr * dscale));
     else if (pi.name.rfind("value_embeds.", 0) == 0) GN_TRY(sink(c.embedding_lr * dscale * 0.5f));
@@ -767,13 +776,13 @@ int optimizer_run(gn_model* m, int shard, int shard_count) {
     }
     else GN_TRY(muon_launch(p, g, mo, se, pi.rows, pi.cols, c.matrix_lr * c.lr_mult, 0.95f, 5, 0.9f, c.weight_decay, lane_ws, m->ctx->gemm_kind, s));
   }
-  if (lanes > 1) {
+  if (fork) {
     for (int l = 1; l < lanes; ++l) {
       GN_CUDA(cudaEventRecord(m->opt_event[l], m->opt_stream[l]));
       GN_CUDA(cudaStreamWaitEvent(m->s(), m->opt_event[l], 0));
     }
   }
-  if (shard_count > 1) {
+  if (shard_count > 1 && part != 1) {   // after every update of this rank, the AdamW ones included
     // Exchange form: the gradient buffer becomes "my updated tensors, zero elsewhere"; a SUM all-reduce over it then
     // yields every updated tensor on every rank exactly (x + 0 + ... + 0), and gn_model_optimizer_finish installs it.
     for (size_t i = 0; i < m->params.size(); ++i) {
@@ -784,6 +793,47 @@ int optimizer_run(gn_model* m, int shard, int shard_count) {
     }
   }
   return GN_OK;
+}
+
+// One optimizer step.  The launch sequence is the same every step (about 2 900 launches for d12, paced by the host), except
+// for the bias correction of the few AdamW tensors: the rest is captured once, after an eager step has sized every scratch
+// buffer, and replayed; the AdamW tensors and the exchange copies of a sharded step follow on the main stream.
+int optimizer_run(gn_model* m, int shard, int shard_count) {
+  cudaStream_t s = m->s();
+  ++m->opt_steps;
+  const int lanes = std::max(1, std::min(m->ctx->optimizer_lanes, (int)gn_model::kOptLanes));
+  const int key[5] = {shard, shard_count, lanes, m->ctx->gemm_kind, m->ctx->option_generation};
+  const bool want_graph = m->ctx->optimizer_graph && !m->opt_graph_failed && m->opt_eager_runs >= 1;
+  if (!want_graph) { ++m->opt_eager_runs; return optimizer_body(m, shard, shard_count, 0); }
+  if (m->opt_graph_exec && std::memcmp(key, m->opt_graph_key, sizeof(key)) != 0) {
+    cudaGraphExecDestroy(m->opt_graph_exec); cudaGraphDestroy(m->opt_graph); m->opt_graph_exec = nullptr; m->opt_graph = nullptr;
+    ++m->opt_eager_runs;
+    return optimizer_body(m, shard, shard_count, 0);   // the changed options may want other buffers: one eager step first
+  }
+  if (!m->opt_graph_exec) {
+    GN_CUDA(cudaStreamSynchronize(s));
+    for (int l = 1; l < lanes; ++l) GN_CUDA(cudaStreamSynchronize(m->opt_stream[l]));
+    bool ok = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+    int status = GN_OK;
+    if (ok) {
+      status = optimizer_body(m, shard, shard_count, 1);
+      cudaGraph_t graph = nullptr;
+      const cudaError_t ce = cudaStreamEndCapture(s, &graph);
+      ok = status == GN_OK && ce == cudaSuccess && graph != nullptr;
+      if (ok) ok = cudaGraphGetNodes(graph, nullptr, &m->opt_graph_nodes) == cudaSuccess && cudaGraphInstantiate(&m->opt_graph_exec, graph, 0) == cudaSuccess;
+      if (ok) { m->opt_graph = graph; std::memcpy(m->opt_graph_key, key, sizeof(key)); }
+      else if (graph) cudaGraphDestroy(graph);
+    }
+    if (!ok) {
+      // nothing of the captured part has run: clear the error state and do this step, and every later one, eagerly
+      cudaGetLastError();
+      m->opt_graph_exec = nullptr; m->opt_graph_failed = true;
+      return optimizer_body(m, shard, shard_count, 0);
+    }
+  }
+  GN_CUDA(cudaGraphLaunch(m->opt_graph_exec, s));
+  count_launches((int64_t)m->opt_graph_nodes);
+  return optimizer_body(m, shard, shard_count, 2);
 }
 }  // namespace
 

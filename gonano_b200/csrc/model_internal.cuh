@@ -170,6 +170,13 @@ struct gn_model {
   DevBuf opt_ws_lane[kOptLanes];
   gn_optimizer_config opt_cfg{};
   int opt_steps = 0;
+  // the captured optimizer step: valid for one (shard, shard_count, lanes, product kind, option generation)
+  cudaGraph_t opt_graph = nullptr;
+  cudaGraphExec_t opt_graph_exec = nullptr;
+  size_t opt_graph_nodes = 0;
+  int opt_graph_key[5] = {-1, -1, -1, -1, -1};
+  int opt_eager_runs = 0;          // eager steps so far: the first one sizes every scratch buffer
+  bool opt_graph_failed = false;   // a capture failed once: stay eager
   bool opt_ready = false;
   DevBuf cache_lat, cache_rope;   // latent attention: [layer][row][max_seq][lat] and [layer][row][max_seq][Hkv*rope]
   Arena infer, train;

@@ -328,6 +328,8 @@ int gn_ctx_set_gemm(gn_ctx* ctx, int kind);
  *   "decode_graph"           1 (default) replays the decode step from a CUDA graph, 0 keeps it eager
  *   "head_chunk_rows"        16384 (default): token rows whose logits exist at once in the training pass
  *   "optimizer_lanes"        4 (default): streams the independent tensors of an optimizer step are spread over (1..4)
+ *   "optimizer_graph"        1 (default): from the second step on the optimizer step is replayed from a CUDA graph (all but the
+ *                            AdamW scalars, whose bias correction changes every step); 0: launched eagerly every step
  *   "decode_prefix_sharing"  -1 (default) automatic, 0 / 1 shared-prompt attention pass off / on (process-wide)
  *   "attention_tcgen05"      1 (default) head_dim 128 attention forward on tcgen05, 0 on mma.sync (process-wide)
  *   "gemm_persistent_ctas"   -1 (default) one CTA per SM for the tile-walking form, 0 form off, n = n CTAs
