@@ -675,6 +675,9 @@ int gn_model_optimizer_init(gn_model* m, const gn_optimizer_config* cfg) {
   GN_TRY(enter(m));
   GN_REQUIRE(cfg, "gn_model_optimizer_init: null config");
   m->opt_cfg = *cfg; m->opt_steps = 0;
+  // the learning rates are arguments of the captured launches: a new configuration starts from an eager step again
+  if (m->opt_graph_exec) { GN_CUDA(cudaStreamSynchronize(m->s())); cudaGraphExecDestroy(m->opt_graph_exec); cudaGraphDestroy(m->opt_graph); m->opt_graph_exec = nullptr; m->opt_graph = nullptr; }
+  m->opt_eager_runs = 0; m->opt_graph_failed = false;
   GN_TRY(m->opt_mom.ensure(sizeof(float) * m->total)); GN_TRY(m->opt_second.ensure(sizeof(float) * m->total));
   GN_CUDA(cudaMemsetAsync(m->opt_mom.p, 0, sizeof(float) * m->total, m->s()));
   GN_CUDA(cudaMemsetAsync(m->opt_second.p, 0, sizeof(float) * m->total, m->s()));
