@@ -479,7 +479,9 @@ int gn_compressed_attention_sparse_backward(const float* query, const float* key
   float* gq = st.out(dq, nq, true); float* gk = st.out(dkc, nk, true); float* gv = st.out(dvc, nk, true);
   float* scratch = st.temp<float>(nt);
   if (st.status != GN_OK) return st.status;
-  GN_TRY(compressed_attention_backward_launch(pq, pk, pv, pg, pl, pr, scratch, batch, n_head, n_kv_head, seq, head_dim, blocks, 1, gq, gk, gv, ps, pc, topk, s));
+  uint32_t* bits = st.temp<uint32_t>((size_t)batch * n_kv_head * seq * ((blocks + 31) / 32));
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(compressed_attention_backward_launch(pq, pk, pv, pg, pl, pr, scratch, batch, n_head, n_kv_head, seq, head_dim, blocks, 1, gq, gk, gv, ps, pc, topk, s, bits));
   GN_END();
 }
 // mergeAttentionBranches (model/compress_attention.go:440-466)

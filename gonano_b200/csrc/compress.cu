@@ -268,32 +268,58 @@ __global__ void __launch_bounds__(256) compressed_attention_dq_kernel(const floa
 #pragma unroll
   for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; if (c < D) dq[idx * D + c] += acc[i]; }
 }
-// dkc / dvc: one warp per (batch, kv head, block j) walks the tokens that attend to block j (dense: those of the later blocks;
-// selected blocks: a scan of each token's selection list) and, per token, the query heads of the group.
+// bits[(kvh * words + j / 32) * T + t] bit j % 32 = token t of (batch, kv head) kvh selected block j (zeroed before; an OR of bits
+// gives the same word in any order)
+__global__ void __launch_bounds__(256) select_bits_kernel(const int32_t* __restrict__ selection, const int32_t* __restrict__ counts, int64_t tokens, int T, int topk,
+                                                          int blocks, uint32_t* __restrict__ bits) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= tokens * topk) return;
+  const int slot = (int)(idx % topk); const int64_t tr = idx / topk;      // tr = kvh * T + t
+  if (slot >= min(counts[tr], topk)) return;
+  const int j = selection[idx];
+  if ((unsigned)j >= (unsigned)blocks) return;
+  const int64_t kvh = tr / T; const int t = (int)(tr % T);
+  atomicOr(bits + (kvh * ((blocks + 31) / 32) + (j >> 5)) * T + t, 1u << (j & 31));
+}
+// dkc / dvc: one CTA per (batch, kv head, block j) walks the tokens that attend to block j (dense: those of the later blocks;
+// selected blocks: a scan of each token's selection list) and, per token, the query heads of the group.  Warp w takes the tokens
+// t0 + w, t0 + w + 8, ... in ascending order (a block early in a long sequence is attended by thousands of (token, head) rows,
+// and one warp's chain of dependent row reads set the kernel's time); the eight partial sums are added in warp order.
 template <int DP>
 __global__ void __launch_bounds__(256) compressed_attention_dkv_kernel(const float* __restrict__ q, const float* __restrict__ kc, const float* __restrict__ vc,
                                                                        const float* __restrict__ dout, const float* __restrict__ lse,
                                                                        const float* __restrict__ delta, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio,
                                                                        float* __restrict__ dkc, float* __restrict__ dvc, const int32_t* __restrict__ selection,
-                                                                       const int32_t* __restrict__ counts, int topk) {
+                                                                       const int32_t* __restrict__ counts, int topk, const uint32_t* __restrict__ bits) {
   constexpr int PER = DP / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t idx = (int64_t)blockIdx.x * 8 + warp;
-  if (idx >= (int64_t)B * Hkv * blocks) return;
+  __shared__ float part[8][2][DP];
+  const int64_t idx = blockIdx.x;   // grid = B * Hkv * blocks
   const int j = (int)(idx % blocks); const int64_t kvh = idx / blocks; const int hk = (int)(kvh % Hkv); const int b = (int)(kvh / Hkv);
   const int hr = Hq / Hkv;
   float kv[PER], vv[PER], ak[PER], av[PER];
 #pragma unroll
   for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; kv[i] = c < D ? kc[idx * D + c] : 0.0f; vv[i] = c < D ? vc[idx * D + c] : 0.0f; ak[i] = av[i] = 0.0f; }
-  const int t0 = selection ? 0 : min((int64_t)(j + 1) * ratio, (int64_t)T);
-  for (int t = t0; t < T; ++t) {
-    if (selection) {
-      const int n = max(0, min(counts[kvh * T + t], topk));
-      const int32_t* sel = selection + (kvh * T + t) * topk;
+  const int t0 = selection ? 0 : (int)min((int64_t)(j + 1) * ratio, (int64_t)T);
+  // With the selection turned into bits[(kvh, j / 32), t] (select_bits_kernel) a warp learns with one coalesced read which of
+  // 32 tokens attend to block j; warp w takes the token groups w, w + 8, ...  Without the bits it reads every token's list.
+  const int words = (blocks + 31) / 32;
+  const int step = bits ? 256 : 8;
+  for (int tb = t0 + (bits ? warp * 32 : warp); tb < T; tb += step) {
+    unsigned pending = 1u;                        // one token per iteration unless the bits name up to 32
+    if (bits) {
+      const uint32_t wd = tb + lane < T ? bits[(kvh * words + (j >> 5)) * T + tb + lane] : 0u;
+      pending = __ballot_sync(0xffffffffu, (wd >> (j & 31)) & 1u);
+    } else if (selection) {
+      const int n = max(0, min(counts[kvh * T + tb], topk));
+      const int32_t* sel = selection + (kvh * T + tb) * topk;
       bool mine = false;
       for (int i = lane; i < n; i += 32) mine |= sel[i] == j;
       if (!__any_sync(0xffffffffu, mine)) continue;
     }
+    while (pending) {
+    const int t = tb + __ffs(pending) - 1;
+    pending &= pending - 1;
     for (int hh = 0; hh < hr; ++hh) {
       const int64_t row = ((int64_t)b * Hq + hk * hr + hh) * T + t;
       const float* qr = q + row * D; const float* gr = dout + row * D;
@@ -307,9 +333,19 @@ __global__ void __launch_bounds__(256) compressed_attention_dkv_kernel(const flo
 #pragma unroll
       for (int i = 0; i < PER; ++i) { av[i] = fmaf(p, gx[i], av[i]); ak[i] = fmaf(ds, qx[i], ak[i]); }
     }
+    }
   }
 #pragma unroll
-  for (int i = 0; i < PER; ++i) { const int c = lane + 32 * i; if (c < D) { dkc[idx * D + c] += ak[i]; dvc[idx * D + c] += av[i]; } }
+  for (int i = 0; i < PER; ++i) { part[warp][0][lane + 32 * i] = ak[i]; part[warp][1][lane + 32 * i] = av[i]; }
+  __syncthreads();
+  for (int c = threadIdx.x; c < 2 * D; c += 256) {
+    const int which = c / D, cc = c % D;
+    float acc = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) acc += part[w][which][cc];
+    float* dst = which == 0 ? dkc : dvc;
+    dst[idx * D + cc] += acc;
+  }
 }
 // delta[t] = sum_j p_j dp_j over the keys of the row, for the rows that have no row correction
 template <int DP>
@@ -707,13 +743,21 @@ int compressed_attention_launch(const float* q, const float* kc, const float* vc
 
 int compressed_attention_backward_launch(const float* q, const float* kc, const float* vc, const float* dout, const float* lse, const float* rowcorr,
                                          float* delta_scratch, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* dq, float* dkc, float* dvc,
-                                         const int32_t* selection, const int32_t* counts, int topk, cudaStream_t s) {
+                                         const int32_t* selection, const int32_t* counts, int topk, cudaStream_t s, uint32_t* select_bits) {
   GN_REQUIRE(D > 0 && D <= 128, "compressed attention: head_dim %d outside (0,128]", D);
   GN_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && ratio >= 1, "compressed attention: %d query heads, %d kv heads, ratio %d", Hq, Hkv, ratio);
   GN_REQUIRE(!selection || (counts && topk > 0), "compressed attention: a selection needs its counts and topk > 0");
+  const uint32_t* bits = nullptr;
+  if (selection && select_bits && (int64_t)B * Hq * T > 0 && blocks > 0) {
+    const int64_t tokens = (int64_t)B * Hkv * T;
+    GN_CUDA(cudaMemsetAsync(select_bits, 0, sizeof(uint32_t) * (size_t)tokens * ((blocks + 31) / 32), s));
+    select_bits_kernel<<<(unsigned)ceil_div(tokens * topk, 256), 256, 0, s>>>(selection, counts, tokens, T, topk, blocks, select_bits);
+    GN_LAUNCH_CHECK();
+    bits = select_bits;
+  }
   const int64_t nq = (int64_t)B * Hq * T, nkv = (int64_t)B * Hkv * blocks;
   if (nq <= 0 || nkv <= 0) return GN_OK;
-  const unsigned gq = (unsigned)ceil_div(nq, 8), gk = (unsigned)ceil_div(nkv, 8);
+  const unsigned gq = (unsigned)ceil_div(nq, 8);
   const float* delta = rowcorr;
   // head_dim 128, every block before the query's own: the mma.sync attention backward with keys counted in blocks (its dk / dv
   // kernel owns 128 blocks per CTA and walks the group's heads and the query tiles that see them; no atomics there either)
@@ -738,7 +782,7 @@ int compressed_attention_backward_launch(const float* q, const float* kc, const 
     if (!delta) { compressed_attention_delta_kernel<DPV><<<gq, 256, 0, s>>>(q, kc, vc, dout, lse, B, Hq, Hkv, T, D, blocks, ratio, delta_scratch, selection, counts, topk); \
                   delta = delta_scratch; } \
     compressed_attention_dq_kernel<DPV><<<gq, 256, 0, s>>>(q, kc, vc, dout, lse, delta, B, Hq, Hkv, T, D, blocks, ratio, dq, selection, counts, topk); \
-    compressed_attention_dkv_kernel<DPV><<<gk, 256, 0, s>>>(q, kc, vc, dout, lse, delta, B, Hq, Hkv, T, D, blocks, ratio, dkc, dvc, selection, counts, topk); } while (0)
+    compressed_attention_dkv_kernel<DPV><<<(unsigned)nkv, 256, 0, s>>>(q, kc, vc, dout, lse, delta, B, Hq, Hkv, T, D, blocks, ratio, dkc, dvc, selection, counts, topk, bits); } while (0)
   if (D <= 32) GN_CA_BWD(32); else if (D <= 64) GN_CA_BWD(64); else GN_CA_BWD(128);
 #undef GN_CA_BWD
   GN_LAUNCH_CHECK();

@@ -84,10 +84,12 @@ int compress_heads_backward_launch(const float* key, const float* value, const f
 // (token t stands at position offset + t: offset > 0 is the cached inference form)
 int compressed_attention_launch(const float* q, const float* kc, const float* vc, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* out, float* lse,
                                 const int32_t* selection, const int32_t* counts, int topk, int offset, cudaStream_t s);
+// (select_bits: optional scratch of B * Hkv * ceil(blocks / 32) * T words for the selected-block form: the selection as bits per token)
 // backward, dense (selection null) or over selected blocks: dq, dkc, dvc are accumulated into; rowcorr nullable (then delta_scratch [B * Hq * T] is used)
 int compressed_attention_backward_launch(const float* q, const float* kc, const float* vc, const float* dout, const float* lse, const float* rowcorr,
                                          float* delta_scratch, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* dq, float* dkc, float* dvc,
-                                         const int32_t* selection, const int32_t* counts, int topk, cudaStream_t s);
+                                         const int32_t* selection, const int32_t* counts, int topk, cudaStream_t s,
+                                         uint32_t* select_bits = nullptr);
 int attention_merge_launch(const float* oa, const float* la, const float* ob, const float* lb, int64_t rows, int D, float* out, float* lse, cudaStream_t s);
 // score part of the indexer's backward: gq [rows, heads, dim], gk [blocks, heads, dim] overwritten, gw [heads] accumulated; wpart [rows, heads] scratch
 int indexer_scores_backward_launch(const float* gs, const float* q, const float* key, const float* w, int rows, int blocks, int heads, int dim, float* gq, float* gk,

@@ -194,9 +194,10 @@ extern "C" int gn_profile_kernel(gn_ctx* ctx, const char* kernel, const int64_t*
       return time_it(s, iters, mean_ms, [&]() { return compressed_attention_launch(q, kc, vc, B, Hq, Hkv, T, D, blocks, ratio, o, lse, sel, cnt, topk, 0, s); });
     GN_CUDA(cudaMemsetAsync(dq, 0, sizeof(float) * nq, s)); GN_CUDA(cudaMemsetAsync(dk, 0, sizeof(float) * nk, s)); GN_CUDA(cudaMemsetAsync(dv, 0, sizeof(float) * nk, s));
     // as in a layer with a sliding-window branch: the row correction dO . O of the merged output comes with the call
+    uint32_t* bits = nullptr; if (sparse) GN_TRY(bufs.get(&bits, (size_t)B * Hkv * T * ((blocks + 31) / 32)));
     float* rowcorr; GN_TRY(bufs.get(&rowcorr, (size_t)nt)); GN_TRY(synth(rowcorr, nt, -1, 1, 25, s));
     return time_it(s, iters, mean_ms, [&]() {
-      return compressed_attention_backward_launch(q, kc, vc, dout, lse, rowcorr, delta, B, Hq, Hkv, T, D, blocks, ratio, dq, dk, dv, sel, cnt, topk, s);
+      return compressed_attention_backward_launch(q, kc, vc, dout, lse, rowcorr, delta, B, Hq, Hkv, T, D, blocks, ratio, dq, dk, dv, sel, cnt, topk, s, bits);
     });
   }
   if (k == "compressed_attention_decode") {
