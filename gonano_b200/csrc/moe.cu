@@ -141,9 +141,67 @@ __global__ void __launch_bounds__(256) indexer_scores_kernel(float* dst, const f
   }
   if (lane == 0) dst[idx] = total;
 }
+// The same for many rows and blocks: a 64 x 64 tile of scores per CTA, 4 x 4 per thread; per head the query and key tiles pass
+// through shared memory 32 dimensions at a time (rows padded to 33 words: no bank conflicts), relu and the head weight are
+// applied when the head's dot products are complete.
+__global__ void __launch_bounds__(256) indexer_scores_tiled_kernel(float* __restrict__ dst, const float* __restrict__ q, const float* __restrict__ key,
+                                                                   const float* __restrict__ w, int rows, int blocks, int heads, int dim) {
+  __shared__ float qs[64][33], ks[64][33];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int r0 = blockIdx.y * 64, b0 = blockIdx.x * 64;
+  float total[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) total[i][j] = 0.0f;
+  for (int h = 0; h < heads; ++h) {
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    for (int d0 = 0; d0 < dim; d0 += 32) {
+      __syncthreads();
+      for (int idx = threadIdx.x; idx < 64 * 32; idx += 256) {
+        const int rr = idx >> 5, dd = idx & 31;
+        const bool dok = d0 + dd < dim;
+        qs[rr][dd] = (dok && r0 + rr < rows) ? q[((int64_t)(r0 + rr) * heads + h) * dim + d0 + dd] : 0.0f;
+        ks[rr][dd] = (dok && b0 + rr < blocks) ? key[((int64_t)(b0 + rr) * heads + h) * dim + d0 + dd] : 0.0f;
+      }
+      __syncthreads();
+#pragma unroll 8
+      for (int dd = 0; dd < 32; ++dd) {
+        float a[4], b[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { a[i] = qs[ty + 16 * i][dd]; b[i] = ks[tx + 16 * i][dd]; }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+      }
+    }
+    const float wh = w[h];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) if (acc[i][j] > 0.0f) total[i][j] += wh * acc[i][j];
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int r = r0 + ty + 16 * i, b = b0 + tx + 16 * j;
+      if (r < rows && b < blocks) dst[(int64_t)r * blocks + b] = total[i][j];
+    }
+}
 int indexer_scores_launch(float* dst, const float* q, const float* k, const float* w, int rows, int blocks, int heads, int dim, cudaStream_t s) {
   int64_t n = (int64_t)rows * blocks;
   if (n <= 0) return GN_OK;
+  if (rows >= 64 && blocks >= 64) {
+    indexer_scores_tiled_kernel<<<dim3(ceil_div(blocks, 64), ceil_div(rows, 64)), 256, 0, s>>>(dst, q, k, w, rows, blocks, heads, dim);
+    GN_LAUNCH_CHECK();
+    return GN_OK;
+  }
   indexer_scores_kernel<<<ceil_div(n, 8), 256, 0, s>>>(dst, q, k, w, rows, blocks, heads, dim);
   GN_LAUNCH_CHECK();
   return GN_OK;

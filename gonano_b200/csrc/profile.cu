@@ -200,6 +200,28 @@ extern "C" int gn_profile_kernel(gn_ctx* ctx, const char* kernel, const int64_t*
       return compressed_attention_backward_launch(q, kc, vc, dout, lse, rowcorr, delta, B, Hq, Hkv, T, D, blocks, ratio, dq, dk, dv, sel, cnt, topk, s, bits);
     });
   }
+  if (k == "indexer_scores") {
+    GN_REQUIRE(n_dims == 4, "%s wants {rows, blocks, heads, dim}", kernel);
+    const int rows = (int)dims[0], blocks = (int)dims[1], heads = (int)dims[2], dim = (int)dims[3];
+    float *q, *kk, *w, *dst;
+    GN_TRY(bufs.get(&q, (size_t)rows * heads * dim)); GN_TRY(bufs.get(&kk, (size_t)blocks * heads * dim)); GN_TRY(bufs.get(&w, (size_t)heads));
+    GN_TRY(bufs.get(&dst, (size_t)rows * blocks));
+    GN_TRY(synth(q, (int64_t)rows * heads * dim, -1, 1, 51, s)); GN_TRY(synth(kk, (int64_t)blocks * heads * dim, -1, 1, 52, s)); GN_TRY(synth(w, heads, 0.5f, 1.5f, 53, s));
+    return time_it(s, iters, mean_ms, [&]() { return indexer_scores_launch(dst, q, kk, w, rows, blocks, heads, dim, s); });
+  }
+  if (k == "select_hierarchical" || k == "select_blocks") {
+    GN_REQUIRE(n_dims >= 4, "%s wants {tokens, blocks, ratio, topk[, pool, budget]}", kernel);
+    const int tokens = (int)dims[0], blocks = (int)dims[1], ratio = (int)dims[2], topk = (int)dims[3];
+    const int pool = n_dims > 4 ? std::max(1, (int)dims[4]) : 1, budget = n_dims > 5 ? (int)dims[5] : 0;
+    const int per_token = std::max(1, (budget + pool - 1) / pool), cap = per_token * pool;
+    float *scores, *gmax; int32_t *sel, *cnt, *cand, *ccnt, *chosen;
+    GN_TRY(bufs.get(&scores, (size_t)tokens * blocks)); GN_TRY(bufs.get(&gmax, (size_t)tokens * ((blocks + pool - 1) / pool)));
+    GN_TRY(bufs.get(&sel, (size_t)tokens * topk)); GN_TRY(bufs.get(&cnt, (size_t)tokens)); GN_TRY(bufs.get(&cand, (size_t)tokens * cap));
+    GN_TRY(bufs.get(&ccnt, (size_t)tokens)); GN_TRY(bufs.get(&chosen, (size_t)tokens * per_token));
+    GN_TRY(synth(scores, (int64_t)tokens * blocks, -1, 1, 61, s));
+    if (k == "select_blocks") return time_it(s, iters, mean_ms, [&]() { return select_blocks_launch(scores, tokens, blocks, 0, ratio, topk, sel, cnt, s); });
+    return time_it(s, iters, mean_ms, [&]() { return select_hierarchical_launch(scores, tokens, blocks, 0, ratio, topk, pool, budget, gmax, chosen, sel, cnt, cand, ccnt, s); });
+  }
   if (k == "compressed_attention_decode") {
     // one decode step of the global branch over a cached compressed sequence: {rows, n_head, n_kv_head, head_dim, blocks}
     GN_REQUIRE(n_dims == 5, "%s wants {rows, n_head, n_kv_head, head_dim, blocks}", kernel);

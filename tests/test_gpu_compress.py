@@ -637,3 +637,15 @@ def test_compress_heads(oracle, bk, B, Hkv, T, d, D, ratio):
     got = bk.compress_backward(x, k, v, w, prob, kc, vc, gkc, gvc, ratio)
     for g, t_ in zip(got, want):
         close(g, t_, 2e-4, 2e-5 * max(1.0, float(np.max(np.abs(t_)))))
+
+
+# Backend.IndexerScores at sizes that take the tiled kernel (64 x 64 scores per CTA): ragged edges, several heads, dims that are not
+# a multiple of the 32-dimension step
+@pytest.mark.parametrize("rows,blocks,heads,dim", [(64, 64, 1, 64), (130, 77, 3, 24), (300, 545, 2, 100), (70, 200, 4, 7)])
+def test_indexer_scores_tiled(oracle, bk, rows, blocks, heads, dim):
+    rng = np.random.default_rng(rows + blocks)
+    q = rng.standard_normal((rows, heads, dim)).astype(np.float32); k = rng.standard_normal((blocks, heads, dim)).astype(np.float32)
+    w = rng.standard_normal(heads).astype(np.float32)
+    want = np.asarray(oracle.Backend(0).indexer_scores(q, k, w, rows, blocks, heads, dim)).reshape(rows, blocks)
+    got = np.asarray(bk.indexer_scores(q, k, w, rows, blocks, heads, dim)).reshape(rows, blocks)
+    close(got, want, 1e-5, 1e-5 * np.sqrt(dim))
