@@ -57,6 +57,30 @@ def test_invalid_arguments_are_rejected(lib):
     assert b"advantage" in lib.gn_last_error()
 
 
+def test_compressed_attention_entry_points_check_their_arguments(lib):
+    """The entry points of the compressed attention layers refuse missing arrays before they touch a device, name themselves
+    in the error text, and treat empty inputs as nothing to do."""
+    import ctypes as C
+    buf = (C.c_float * 64)()
+    ibuf = (C.c_int32 * 16)()
+    p = C.cast(buf, C.c_void_p); ip = C.cast(ibuf, C.c_void_p)
+    assert lib.gn_compressed_attention_forward(None, p, p, 1, 1, 1, 4, 8, 2, 2, p, None) != 0 and b"compressed_attention_forward" in lib.gn_last_error()
+    assert lib.gn_compressed_attention_backward(p, p, p, None, p, None, 1, 1, 1, 4, 8, 2, 2, p, p, p) != 0 and b"compressed_attention_backward" in lib.gn_last_error()
+    assert lib.gn_compressed_attention_sparse_forward(p, p, p, None, ip, 1, 1, 1, 4, 8, 2, 2, p, None) != 0
+    assert lib.gn_compressed_attention_sparse_backward(p, p, p, p, p, None, ip, ip, 1, 1, 1, 4, 8, 2, 0, p, p, p) != 0     # topk 0
+    assert lib.gn_attention_merge(p, p, p, None, 4, 8, p, None) != 0 and b"attention_merge" in lib.gn_last_error()
+    assert lib.gn_select_blocks_hierarchical(p, 4, 4, 0, 0, 2, 2, 4, ip, ip, None, None) != 0                             # ratio 0
+    assert lib.gn_select_blocks_within_pool(p, 4, 4, 0, 2, 2, None, ip, 4, ip, ip) != 0
+    assert lib.gn_indexer_distillation_grad(p, None, None, None, 0, 4, 4, 2, 2, 1.0, p) != 0
+    assert lib.gn_attention_windowed_forward(p, p, p, 1, 3, 2, 4, 8, 0, 2, p, None) != 0                                   # 3 query heads on 2 kv heads
+    assert lib.gn_compress_forward(p, p, p, p, None, 1, 1, 4, 4, 8, 2, p, p, None) != 0 and b"compress_forward" in lib.gn_last_error()
+    # nothing to do: no device is needed
+    assert lib.gn_compressed_attention_forward(None, None, None, 0, 1, 1, 4, 8, 2, 2, None, None) == 0
+    assert lib.gn_attention_merge(None, None, None, None, 0, 8, None, None) == 0
+    assert lib.gn_select_blocks_hierarchical(None, 0, 4, 0, 2, 2, 2, 4, None, None, None, None) == 0
+    assert lib.gn_hierarchical_cap(8, 512) == 512 and lib.gn_hierarchical_cap(8, 0) == 8 and lib.gn_hierarchical_cap(0, 3) == 3
+
+
 def test_build_batch_matches_oracle(oracle):
     from gonano_b200 import session
     rng = np.random.default_rng(0)
