@@ -518,8 +518,10 @@ int gn_indexer_scores_backward(const float* grad_scores, const float* query, con
   float* gq = st.out(grad_query, (size_t)rows * heads * dim); float* gk = st.out(grad_key, (size_t)blocks * heads * dim);
   float* gw = st.out(grad_weight, (size_t)heads, true);
   float* wpart = st.temp<float>((size_t)rows * heads);
+  const int kplanes = rows >= 64 && blocks >= 64 ? 16 : 0;
+  float* kpart = kplanes ? st.temp<float>((size_t)kplanes * blocks * heads * dim) : nullptr;
   if (st.status != GN_OK) return st.status;
-  GN_TRY(indexer_scores_backward_launch(pg, pq, pk, pw, rows, blocks, heads, dim, gq, gk, gw, wpart, s));
+  GN_TRY(indexer_scores_backward_launch(pg, pq, pk, pw, rows, blocks, heads, dim, gq, gk, gw, wpart, s, kpart, kplanes));
   GN_END();
 }
 // distillationTarget (model/compress_attention.go:155-196) for every (batch, kv head)

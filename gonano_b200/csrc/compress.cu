@@ -478,6 +478,128 @@ __global__ void __launch_bounds__(256) indexer_bwd_key_kernel(const float* __res
 #pragma unroll
   for (int i = 0; i < 4; ++i) { const int c = lane + 32 * i; if (c < dim) gk[idx * dim + c] = acc[i]; }
 }
+// The same two gradients for many rows and blocks, in 64 x 64 tiles of scores (4 x 4 per thread, as indexer_scores_tiled_kernel):
+// the tile of q . k is recomputed, G = grad_scores * w_h where the dot product is positive goes through shared memory, and a second
+// small product adds G K (query side: a CTA owns 64 rows and walks the block tiles) or G^T Q (key side: a CTA owns 64 blocks and
+// walks the row tiles) in a fixed order.  Shared memory: the two operand tiles at full dim (rows padded by one word) and G.
+template <bool KEY_SIDE>
+__global__ void __launch_bounds__(256) indexer_bwd_tiled_kernel(const float* __restrict__ gs, const float* __restrict__ q, const float* __restrict__ key,
+                                                                const float* __restrict__ w, int rows, int blocks, int heads, int dim,
+                                                                float* __restrict__ out, float* __restrict__ wpart, int tiles_per_split) {
+  // blockIdx.z: a share of the tiles walked (key side with few block tiles: the shares' partial results, out + z * plane, are added
+  // by a second pass)
+  extern __shared__ float smem[];
+  const int ld = dim + 1;
+  float* Qs = smem; float* Ks = Qs + 64 * ld; float* Gs = Ks + 64 * ld;      // Gs [64 rows][65]
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int h = blockIdx.y, own0 = blockIdx.x * 64;                          // the 64 rows (query side) or blocks (key side) of this CTA
+  const float wh = w[h];
+  const int ncol = (dim + 15) / 16;                                          // output columns per thread: tx, tx + 16, ... (at most 8)
+  float acc_o[4][8], wsum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc_o[i][j] = 0.0f;
+  auto load_tile = [&](float* dst, const float* src, int first, int limit) {
+    for (int idx = threadIdx.x; idx < 64 * dim; idx += 256) {
+      const int rr = idx / dim, dd = idx % dim;
+      dst[rr * ld + dd] = first + rr < limit ? src[((int64_t)(first + rr) * heads + h) * dim + dd] : 0.0f;
+    }
+  };
+  if (KEY_SIDE) load_tile(Ks, key, own0, blocks); else load_tile(Qs, q, own0, rows);
+  const int other_n = KEY_SIDE ? rows : blocks;
+  const int o_begin = blockIdx.z * tiles_per_split * 64, o_end = min(other_n, o_begin + tiles_per_split * 64);
+  out += (int64_t)blockIdx.z * (KEY_SIDE ? blocks : rows) * heads * dim;
+  for (int o0 = o_begin; o0 < o_end; o0 += 64) {
+    __syncthreads();                                                         // the previous tile's second product is done
+    if (KEY_SIDE) load_tile(Qs, q, o0, rows); else load_tile(Ks, key, o0, blocks);
+    __syncthreads();
+    const int r0 = KEY_SIDE ? o0 : own0, b0 = KEY_SIDE ? own0 : o0;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    for (int d = 0; d < dim; ++d) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { a[i] = Qs[(ty + 16 * i) * ld + d]; b[i] = Ks[(tx + 16 * i) * ld + d]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int r = r0 + ty + 16 * i, b = b0 + tx + 16 * j;
+        float g = 0.0f;
+        if (r < rows && b < blocks && acc[i][j] > 0.0f) {
+          const float gsv = gs[(int64_t)r * blocks + b];
+          if (!KEY_SIDE) wsum[i] = fmaf(gsv, acc[i][j], wsum[i]);
+          g = gsv * wh;
+        }
+        Gs[(ty + 16 * i) * 65 + tx + 16 * j] = g;                            // [row of the tile][block of the tile]
+      }
+    __syncthreads();
+    if (!KEY_SIDE) {
+      // grad_query[row, c] += sum_b G[row][b] K[b][c]
+      for (int bb = 0; bb < 64; ++bb) {
+        float gv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) gv[i] = Gs[(ty + 16 * i) * 65 + bb];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (j >= ncol) break;
+          const int c = tx + 16 * j;
+          const float kvv = c < dim ? Ks[bb * ld + c] : 0.0f;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc_o[i][j] = fmaf(gv[i], kvv, acc_o[i][j]);
+        }
+      }
+    } else {
+      // grad_key[block, c] += sum_r G[r][block] Q[r][c]
+      for (int rr = 0; rr < 64; ++rr) {
+        float gv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) gv[i] = Gs[rr * 65 + ty + 16 * i];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (j >= ncol) break;
+          const int c = tx + 16 * j;
+          const float qvv = c < dim ? Qs[rr * ld + c] : 0.0f;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc_o[i][j] = fmaf(gv[i], qvv, acc_o[i][j]);
+        }
+      }
+    }
+  }
+  const int own_n = KEY_SIDE ? blocks : rows;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int o = own0 + ty + 16 * i;
+    if (o < own_n) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { const int c = tx + 16 * j; if (j < ncol && c < dim) out[((int64_t)o * heads + h) * dim + c] = acc_o[i][j]; }
+    }
+    if (!KEY_SIDE) {
+      float v = wsum[i];
+#pragma unroll
+      for (int m = 8; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);   // over the 16 threads that share the row
+      if (tx == 0 && o < own_n) wpart[(int64_t)o * heads + h] = v;
+    }
+  }
+}
+
+// out[i] = sum of the planes part[z][i] in order
+__global__ void __launch_bounds__(256) plane_sum_kernel(const float* __restrict__ part, int planes, int64_t n, float* __restrict__ out) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float acc = 0.0f;
+  for (int z = 0; z < planes; ++z) acc += part[(int64_t)z * n + i];
+  out[i] = acc;
+}
 // grad_weight[h] += sum over rows of wpart[row, h]: one CTA per head, fixed order
 __global__ void __launch_bounds__(256) indexer_bwd_weight_kernel(const float* __restrict__ wpart, int rows, int heads, float* __restrict__ gw) {
   __shared__ double part[256];
@@ -804,9 +926,34 @@ int select_blocks_launch(const float* scores, int tokens, int blocks, int offset
 }
 
 int indexer_scores_backward_launch(const float* gs, const float* q, const float* key, const float* w, int rows, int blocks, int heads, int dim, float* gq, float* gk,
-                                   float* gw, float* wpart, cudaStream_t s) {
+                                   float* gw, float* wpart, cudaStream_t s, float* kpart, int kpart_planes) {
   if (rows <= 0 || blocks <= 0 || heads <= 0) return GN_OK;
   GN_REQUIRE(dim >= 1 && dim <= 128, "indexer backward: dim %d outside [1,128]", dim);
+  if (rows >= 64 && blocks >= 64) {
+    const size_t smem = sizeof(float) * (size_t)(2 * 64 * (dim + 1) + 64 * 65);
+    static PerDeviceOnce configured;
+    if (configured.first()) {
+      GN_CUDA(cudaFuncSetAttribute(indexer_bwd_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(float) * (2 * 64 * 129 + 64 * 65))));
+      GN_CUDA(cudaFuncSetAttribute(indexer_bwd_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(float) * (2 * 64 * 129 + 64 * 65))));
+    }
+    const int row_tiles = ceil_div(rows, 64), block_tiles = ceil_div(blocks, 64);
+    indexer_bwd_tiled_kernel<false><<<dim3(row_tiles, heads), 256, smem, s>>>(gs, q, key, w, rows, blocks, heads, dim, gq, wpart, block_tiles);
+    // key side: few block tiles leave SMs idle, so the row tiles are shared out when the caller gave room for the partial planes
+    int splits = 1;
+    if (kpart && block_tiles * heads < num_sms()) splits = std::max(1, std::min(std::min(row_tiles, kpart_planes), ceil_div(2 * num_sms(), block_tiles * heads)));
+    const int per = ceil_div(row_tiles, splits);
+    splits = ceil_div(row_tiles, per);
+    if (splits > 1) {
+      indexer_bwd_tiled_kernel<true><<<dim3(block_tiles, heads, splits), 256, smem, s>>>(gs, q, key, w, rows, blocks, heads, dim, kpart, nullptr, per);
+      const int64_t n = (int64_t)blocks * heads * dim;
+      plane_sum_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, s>>>(kpart, splits, n, gk);
+    } else {
+      indexer_bwd_tiled_kernel<true><<<dim3(block_tiles, heads), 256, smem, s>>>(gs, q, key, w, rows, blocks, heads, dim, gk, nullptr, row_tiles);
+    }
+    indexer_bwd_weight_kernel<<<heads, 256, 0, s>>>(wpart, rows, heads, gw);
+    GN_LAUNCH_CHECK();
+    return GN_OK;
+  }
   indexer_bwd_query_kernel<<<(unsigned)ceil_div((int64_t)rows * heads, 8), 256, 0, s>>>(gs, q, key, w, rows, blocks, heads, dim, gq, wpart);
   indexer_bwd_key_kernel<<<(unsigned)ceil_div((int64_t)blocks * heads, 8), 256, 0, s>>>(gs, q, key, w, rows, blocks, heads, dim, gk);
   indexer_bwd_weight_kernel<<<heads, 256, 0, s>>>(wpart, rows, heads, gw);

@@ -92,8 +92,9 @@ int compressed_attention_backward_launch(const float* q, const float* kc, const 
                                          uint32_t* select_bits = nullptr);
 int attention_merge_launch(const float* oa, const float* la, const float* ob, const float* lb, int64_t rows, int D, float* out, float* lse, cudaStream_t s);
 // score part of the indexer's backward: gq [rows, heads, dim], gk [blocks, heads, dim] overwritten, gw [heads] accumulated; wpart [rows, heads] scratch
+// (kpart: optional room for kpart_planes partial copies of gk, used when the blocks are too few to fill the machine)
 int indexer_scores_backward_launch(const float* gs, const float* q, const float* key, const float* w, int rows, int blocks, int heads, int dim, float* gq, float* gk,
-                                   float* gw, float* wpart, cudaStream_t s);
+                                   float* gw, float* wpart, cudaStream_t s, float* kpart = nullptr, int kpart_planes = 0);
 // the indexer's distillation: target [B * Hkv, T, blocks] from the main attention logits; grad = (masked softmax(scores) - target) * weight, row r = token r % seq
 int distillation_target_launch(const float* q, const float* kc, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* target, cudaStream_t s);
 int distillation_grad_launch(const float* scores, const float* target, const int32_t* candidates, const int32_t* candidate_counts, int cap, int64_t rows, int blocks,

@@ -209,6 +209,18 @@ extern "C" int gn_profile_kernel(gn_ctx* ctx, const char* kernel, const int64_t*
     GN_TRY(synth(q, (int64_t)rows * heads * dim, -1, 1, 51, s)); GN_TRY(synth(kk, (int64_t)blocks * heads * dim, -1, 1, 52, s)); GN_TRY(synth(w, heads, 0.5f, 1.5f, 53, s));
     return time_it(s, iters, mean_ms, [&]() { return indexer_scores_launch(dst, q, kk, w, rows, blocks, heads, dim, s); });
   }
+  if (k == "indexer_scores_bwd") {
+    GN_REQUIRE(n_dims == 4, "%s wants {rows, blocks, heads, dim}", kernel);
+    const int rows = (int)dims[0], blocks = (int)dims[1], heads = (int)dims[2], dim = (int)dims[3];
+    float *q, *kk, *w, *gs, *gq, *gk, *gw, *wpart;
+    GN_TRY(bufs.get(&q, (size_t)rows * heads * dim)); GN_TRY(bufs.get(&kk, (size_t)blocks * heads * dim)); GN_TRY(bufs.get(&w, (size_t)heads));
+    GN_TRY(bufs.get(&gs, (size_t)rows * blocks)); GN_TRY(bufs.get(&gq, (size_t)rows * heads * dim)); GN_TRY(bufs.get(&gk, (size_t)blocks * heads * dim));
+    GN_TRY(bufs.get(&gw, (size_t)heads)); GN_TRY(bufs.get(&wpart, (size_t)rows * heads));
+    GN_TRY(synth(q, (int64_t)rows * heads * dim, -1, 1, 51, s)); GN_TRY(synth(kk, (int64_t)blocks * heads * dim, -1, 1, 52, s)); GN_TRY(synth(w, heads, 0.5f, 1.5f, 53, s));
+    GN_TRY(synth(gs, (int64_t)rows * blocks, -1, 1, 54, s)); GN_CUDA(cudaMemsetAsync(gw, 0, sizeof(float) * heads, s));
+    float* kpart; GN_TRY(bufs.get(&kpart, (size_t)16 * blocks * heads * dim));
+    return time_it(s, iters, mean_ms, [&]() { return indexer_scores_backward_launch(gs, q, kk, w, rows, blocks, heads, dim, gq, gk, gw, wpart, s, kpart, 16); });
+  }
   if (k == "select_hierarchical" || k == "select_blocks") {
     GN_REQUIRE(n_dims >= 4, "%s wants {tokens, blocks, ratio, topk[, pool, budget]}", kernel);
     const int tokens = (int)dims[0], blocks = (int)dims[1], ratio = (int)dims[2], topk = (int)dims[3];

@@ -357,7 +357,8 @@ def test_hierarchical_selection_unbounded_equals_flat(bk):
 
 
 # the score part of SparseIndexer.Backward (model/indexer.go:107-151)
-@pytest.mark.parametrize("rows,blocks,heads,dim", [(5, 3, 2, 2), (70, 33, 4, 32), (130, 64, 3, 100), (16, 300, 8, 64)])
+@pytest.mark.parametrize("rows,blocks,heads,dim", [(5, 3, 2, 2), (70, 33, 4, 32), (130, 64, 3, 100), (16, 300, 8, 64), (300, 545, 2, 64), (64, 200, 1, 128),
+                                                   (257, 70, 3, 7)])   # from 64 x 64 on: the tiled kernels
 def test_indexer_scores_backward(oracle, bk, rows, blocks, heads, dim):
     rng = np.random.default_rng(rows + dim)
     q = rng.standard_normal((rows, heads, dim)).astype(np.float32); k = rng.standard_normal((blocks, heads, dim)).astype(np.float32)
