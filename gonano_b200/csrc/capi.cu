@@ -533,7 +533,9 @@ int gn_indexer_distillation_target(const float* query, const float* key_c, int b
   const float* pq = st.in(query, (size_t)batch * n_head * seq * head_dim); const float* pk = st.in(key_c, (size_t)batch * n_kv_head * blocks * head_dim);
   float* pt = st.out(target, (size_t)batch * n_kv_head * seq * blocks);
   if (st.status != GN_OK) return st.status;
-  GN_TRY(distillation_target_launch(pq, pk, batch, n_head, n_kv_head, seq, head_dim, blocks, ratio, pt, s));
+  float* qsum = (seq >= 64 && blocks >= 64) ? st.temp<float>((size_t)batch * n_kv_head * seq * head_dim + 1) : nullptr;
+  if (st.status != GN_OK) return st.status;
+  GN_TRY(distillation_target_launch(pq, pk, batch, n_head, n_kv_head, seq, head_dim, blocks, ratio, pt, s, qsum));
   GN_END();
 }
 // the score gradient of indexerDistillationGradient (model/compress_attention.go:120-151) with restrictIndexerToPool (:203-231)

@@ -645,6 +645,36 @@ __global__ void __launch_bounds__(256) distillation_target_kernel(const float* _
   const float ft = (float)total;
   for (int j = lane; j < allowed; j += 32) row[j] /= ft;
 }
+// The long-sequence form of the target: the logits are linear in the query, so the queries of a group are summed first
+// (head_sum_kernel, heads in order), one tiled product per (batch, kv head) gives sum_h q_h . k / heads for every (token, block),
+// and target_softmax_kernel turns each row into the softmax over its allowed blocks (float64 sum, as the reference) and zeroes the rest.
+__global__ void __launch_bounds__(256) head_sum_kernel(const float* __restrict__ q, int B, int Hq, int Hkv, int T, int D, float* __restrict__ qsum) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)B * Hkv * T * D) return;
+  const int c = (int)(idx % D); const int64_t r = idx / D; const int t = (int)(r % T); const int64_t kvh = r / T;
+  const int hk = (int)(kvh % Hkv); const int b = (int)(kvh / Hkv); const int hr = Hq / Hkv;
+  float acc = 0.0f;
+  for (int h = 0; h < hr; ++h) acc += q[((((int64_t)b * Hq + hk * hr + h) * T + t) * D) + c];
+  qsum[idx] = acc;
+}
+__global__ void __launch_bounds__(256) target_softmax_kernel(float* __restrict__ target, int64_t rows, int T, int blocks, int ratio) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t r = (int64_t)blockIdx.x * 8 + warp;
+  if (r >= rows) return;
+  const int allowed = min((int)(r % T) / ratio, blocks);
+  float* row = target + r * blocks;
+  float mx = -INFINITY;
+  for (int j = lane; j < allowed; j += 32) mx = fmaxf(mx, row[j]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  double total = 0.0;
+  for (int j = lane; j < allowed; j += 32) { const double v = exp((double)(row[j] - mx)); row[j] = (float)v; total += v; }
+  total = warp_sum_d(total);
+  const float ft = (float)total;
+  for (int j = lane; j < blocks; j += 32) row[j] = j < allowed ? row[j] / ft : 0.0f;
+}
+__global__ void set_scalar_kernel(float* dst, float v) { *dst = v; }
+
 // (softmax over the allowed blocks - target) * weight, optionally restricted to the row's candidate list
 // (model/compress_attention.go:120-151, 203-231, 266-303): one warp per row; the gradient row doubles as the membership marker.
 __global__ void __launch_bounds__(256) distillation_grad_kernel(const float* __restrict__ scores, const float* __restrict__ target,
@@ -961,10 +991,22 @@ int indexer_scores_backward_launch(const float* gs, const float* q, const float*
   return GN_OK;
 }
 
-int distillation_target_launch(const float* q, const float* kc, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* target, cudaStream_t s) {
+int distillation_target_launch(const float* q, const float* kc, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* target, cudaStream_t s,
+                               float* qsum) {
   const int64_t n = (int64_t)B * Hkv * T;
   if (n <= 0 || blocks <= 0) return GN_OK;
   GN_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && ratio >= 1 && D >= 1, "distillation target: %d query heads, %d kv heads, ratio %d", Hq, Hkv, ratio);
+  if (qsum && T >= 64 && blocks >= 64) {
+    float* scale = qsum + n * D;                 // one float behind the sums: 1 / heads of a group
+    set_scalar_kernel<<<1, 1, 0, s>>>(scale, 1.0f / (float)(Hq / Hkv));
+    head_sum_kernel<<<(unsigned)ceil_div(n * D, 256), 256, 0, s>>>(q, B, Hq, Hkv, T, D, qsum);
+    GN_LAUNCH_CHECK();
+    for (int64_t i = 0; i < (int64_t)B * Hkv; ++i)
+      GN_TRY(dot_scores_launch(target + i * T * blocks, qsum + i * T * D, kc + i * blocks * D, scale, T, blocks, D, s));
+    target_softmax_kernel<<<(unsigned)ceil_div(n, 8), 256, 0, s>>>(target, n, T, blocks, ratio);
+    GN_LAUNCH_CHECK();
+    return GN_OK;
+  }
   distillation_target_kernel<<<(unsigned)ceil_div(n, 8), 256, 0, s>>>(q, kc, B, Hq, Hkv, T, D, blocks, ratio, target);
   GN_LAUNCH_CHECK();
   return GN_OK;

@@ -40,6 +40,8 @@ int grouped_matmul_t_launch(float* dst, const float* input, const float* weight,
                             int64_t total_rows, cudaStream_t s);
 int indexer_scores_launch(float* dst, const float* q, const float* k, const float* w, int rows, int blocks, int heads, int dim, cudaStream_t s);
 int indexer_block_max_launch(float* dst, const float* scores, int rows, int blocks, int group, cudaStream_t s);
+// dst[row, block] = scale[0] * (q[row] . key[block]), q [rows, dim], key [blocks, dim], scale a device scalar
+int dot_scores_launch(float* dst, const float* q, const float* k, const float* scale, int rows, int blocks, int dim, cudaStream_t s);
 
 // --------------------------------------------------------------- attention.cu
 // Strided multi-head attention over token-major tensors.
@@ -96,7 +98,9 @@ int attention_merge_launch(const float* oa, const float* la, const float* ob, co
 int indexer_scores_backward_launch(const float* gs, const float* q, const float* key, const float* w, int rows, int blocks, int heads, int dim, float* gq, float* gk,
                                    float* gw, float* wpart, cudaStream_t s, float* kpart = nullptr, int kpart_planes = 0);
 // the indexer's distillation: target [B * Hkv, T, blocks] from the main attention logits; grad = (masked softmax(scores) - target) * weight, row r = token r % seq
-int distillation_target_launch(const float* q, const float* kc, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* target, cudaStream_t s);
+// (qsum: optional scratch of B * Hkv * T * D + 1 floats: the long-sequence form sums the group's queries first and takes one tiled product per (batch, kv head))
+int distillation_target_launch(const float* q, const float* kc, int B, int Hq, int Hkv, int T, int D, int blocks, int ratio, float* target, cudaStream_t s,
+                               float* qsum = nullptr);
 int distillation_grad_launch(const float* scores, const float* target, const int32_t* candidates, const int32_t* candidate_counts, int cap, int64_t rows, int blocks,
                              int seq, int ratio, float weight, float* grad, cudaStream_t s);
 // two-level selection: gmax [tokens, ceil(blocks / pool)] and chosen [tokens, max(1, ceil(budget / pool))] are scratch; candidates [tokens, that * pool]

@@ -144,6 +144,7 @@ __global__ void __launch_bounds__(256) indexer_scores_kernel(float* dst, const f
 // The same for many rows and blocks: a 64 x 64 tile of scores per CTA, 4 x 4 per thread; per head the query and key tiles pass
 // through shared memory 32 dimensions at a time (rows padded to 33 words: no bank conflicts), relu and the head weight are
 // applied when the head's dot products are complete.
+template <bool GATE>
 __global__ void __launch_bounds__(256) indexer_scores_tiled_kernel(float* __restrict__ dst, const float* __restrict__ q, const float* __restrict__ key,
                                                                    const float* __restrict__ w, int rows, int blocks, int heads, int dim) {
   __shared__ float qs[64][33], ks[64][33];
@@ -184,7 +185,7 @@ __global__ void __launch_bounds__(256) indexer_scores_tiled_kernel(float* __rest
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) if (acc[i][j] > 0.0f) total[i][j] += wh * acc[i][j];
+      for (int j = 0; j < 4; ++j) if (!GATE || acc[i][j] > 0.0f) total[i][j] += wh * acc[i][j];
   }
 #pragma unroll
   for (int i = 0; i < 4; ++i)
@@ -198,11 +199,18 @@ int indexer_scores_launch(float* dst, const float* q, const float* k, const floa
   int64_t n = (int64_t)rows * blocks;
   if (n <= 0) return GN_OK;
   if (rows >= 64 && blocks >= 64) {
-    indexer_scores_tiled_kernel<<<dim3(ceil_div(blocks, 64), ceil_div(rows, 64)), 256, 0, s>>>(dst, q, k, w, rows, blocks, heads, dim);
+    indexer_scores_tiled_kernel<true><<<dim3(ceil_div(blocks, 64), ceil_div(rows, 64)), 256, 0, s>>>(dst, q, k, w, rows, blocks, heads, dim);
     GN_LAUNCH_CHECK();
     return GN_OK;
   }
   indexer_scores_kernel<<<ceil_div(n, 8), 256, 0, s>>>(dst, q, k, w, rows, blocks, heads, dim);
+  GN_LAUNCH_CHECK();
+  return GN_OK;
+}
+// dst[row, block] = scale[0] * (q[row] . key[block]): the tiled kernel above without the gate, one head
+int dot_scores_launch(float* dst, const float* q, const float* k, const float* scale, int rows, int blocks, int dim, cudaStream_t s) {
+  if ((int64_t)rows * blocks <= 0) return GN_OK;
+  indexer_scores_tiled_kernel<false><<<dim3(ceil_div(blocks, 64), ceil_div(rows, 64)), 256, 0, s>>>(dst, q, k, scale, rows, blocks, 1, dim);
   GN_LAUNCH_CHECK();
   return GN_OK;
 }

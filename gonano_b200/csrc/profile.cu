@@ -209,6 +209,16 @@ extern "C" int gn_profile_kernel(gn_ctx* ctx, const char* kernel, const int64_t*
     GN_TRY(synth(q, (int64_t)rows * heads * dim, -1, 1, 51, s)); GN_TRY(synth(kk, (int64_t)blocks * heads * dim, -1, 1, 52, s)); GN_TRY(synth(w, heads, 0.5f, 1.5f, 53, s));
     return time_it(s, iters, mean_ms, [&]() { return indexer_scores_launch(dst, q, kk, w, rows, blocks, heads, dim, s); });
   }
+  if (k == "distillation_target") {
+    GN_REQUIRE(n_dims == 6, "%s wants {batch, n_head, n_kv_head, head_dim, seq, ratio}", kernel);
+    const int B = (int)dims[0], Hq = (int)dims[1], Hkv = (int)dims[2], D = (int)dims[3], T = (int)dims[4], ratio = (int)dims[5];
+    const int blocks = (T + ratio - 1) / ratio;
+    float *q, *kc, *target;
+    GN_TRY(bufs.get(&q, (size_t)B * Hq * T * D)); GN_TRY(bufs.get(&kc, (size_t)B * Hkv * blocks * D)); GN_TRY(bufs.get(&target, (size_t)B * Hkv * T * blocks));
+    GN_TRY(synth(q, (int64_t)B * Hq * T * D, -0.6f, 0.6f, 71, s)); GN_TRY(synth(kc, (int64_t)B * Hkv * blocks * D, -0.6f, 0.6f, 72, s));
+    float* qsum; GN_TRY(bufs.get(&qsum, (size_t)B * Hkv * T * D + 1));
+    return time_it(s, iters, mean_ms, [&]() { return distillation_target_launch(q, kc, B, Hq, Hkv, T, D, blocks, ratio, target, s, qsum); });
+  }
   if (k == "indexer_scores_bwd") {
     GN_REQUIRE(n_dims == 4, "%s wants {rows, blocks, heads, dim}", kernel);
     const int rows = (int)dims[0], blocks = (int)dims[1], heads = (int)dims[2], dim = (int)dims[3];

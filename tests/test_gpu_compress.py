@@ -373,7 +373,7 @@ def test_indexer_scores_backward(oracle, bk, rows, blocks, heads, dim):
 
 # the indexer's distillation: target from the main attention logits and the score gradient, free and restricted to a
 # published candidate list (model/compress_attention.go:120-196, 203-231, 266-303)
-@pytest.mark.parametrize("B,Hq,Hkv,T,D,ratio", [(1, 2, 1, 9, 8, 2), (2, 6, 2, 70, 128, 4), (1, 8, 1, 130, 64, 4)])
+@pytest.mark.parametrize("B,Hq,Hkv,T,D,ratio", [(1, 2, 1, 9, 8, 2), (2, 6, 2, 70, 128, 4), (1, 8, 1, 130, 64, 4), (2, 8, 2, 300, 128, 4), (1, 3, 1, 530, 40, 8)])   # the last two: tiled target
 def test_indexer_distillation(oracle, bk, B, Hq, Hkv, T, D, ratio):
     rng = np.random.default_rng(T + Hq)
     blocks = (T + ratio - 1) // ratio
