@@ -331,6 +331,11 @@ def test_select_blocks_hierarchical(oracle, bk, tokens, blocks, offset, ratio, t
         assert np.array_equal(g, w)
     if tokens == 1:
         assert got[2][0].tolist() == [0, 1] and got[0][0].tolist() == [0]
+    # the candidate list is optional output: without it the selection is the same
+    from gonano_b200._lib import ptr, check
+    sel2 = np.full((tokens, topk), -1, np.int32); cnt2 = np.zeros(tokens, np.int32)
+    check(bk.lib.gn_select_blocks_hierarchical(ptr(scores), tokens, blocks, offset, ratio, topk, pool, budget, ptr(sel2), ptr(cnt2), None, None))
+    assert np.array_equal(sel2, got[0]) and np.array_equal(cnt2, got[1])
     groups = max(1, -(-budget // pool))
     assert got[2].shape[1] == groups * pool and np.all(got[3] <= groups * pool)          # model/indexer_test.go:212-244
     allowed = np.minimum((offset + np.arange(tokens)) // ratio, blocks)
