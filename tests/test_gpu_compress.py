@@ -655,3 +655,10 @@ def test_indexer_scores_tiled(oracle, bk, rows, blocks, heads, dim):
     want = np.asarray(oracle.Backend(0).indexer_scores(q, k, w, rows, blocks, heads, dim)).reshape(rows, blocks)
     got = np.asarray(bk.indexer_scores(q, k, w, rows, blocks, heads, dim)).reshape(rows, blocks)
     close(got, want, 1e-5, 1e-5 * np.sqrt(dim))
+
+
+def test_merged_branches_equal_concatenated_attention_forward_and_backward(bk):
+    """The reference's numerical contract of the merge (model/swa_test.go:14-113) on the device."""
+    from test_oracle_golden import _merge_contract
+    bwd = lambda q, k, v, o, dout, lse, ql, kl, hd, off, win, rc: bk.attention_backward(q, k, v, o, dout, lse, ql, kl, hd, off, win, row_correction=rc)
+    _merge_contract(bk.attention_forward, bwd, bk.attention_merge, np.random.default_rng(7))

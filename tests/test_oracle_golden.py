@@ -442,3 +442,36 @@ def test_distillation_restricted_to_candidates_known_answer(oracle):
         return total
     numeric = (loss(1e-3) - loss(-1e-3)) / 2e-3
     assert abs(float(np.sum(g.astype(np.float64) * d)) - numeric) <= 1e-3 * max(1.0, abs(numeric))
+
+
+def _merge_contract(attn_fwd, attn_bwd, merge, rng):
+    """model/swa_test.go:14-113: two branches merged through their log-sum-exps equal one attention over the concatenated keys,
+    forward and backward (each branch differentiated with the merged log-sum-exp and the merged row correction dO . O)."""
+    ql, hd, na, nb = 5, 8, 6, 4
+    q = rng.standard_normal((ql, hd)).astype(np.float32)
+    ka, va = rng.standard_normal((na, hd)).astype(np.float32), rng.standard_normal((na, hd)).astype(np.float32)
+    kb, vb = rng.standard_normal((nb, hd)).astype(np.float32), rng.standard_normal((nb, hd)).astype(np.float32)
+    off = ql + na + nb                                           # past every key: no causal or window cut
+    oa, la = attn_fwd(q, ka, va, ql, na, hd, off, -1); ob, lb = attn_fwd(q, kb, vb, ql, nb, hd, off, -1)
+    om, lm = merge(np.asarray(oa).reshape(ql, hd), np.asarray(la), np.asarray(ob).reshape(ql, hd), np.asarray(lb))
+    om = np.asarray(om).reshape(ql, hd); lm = np.asarray(lm).reshape(ql)
+    k = np.concatenate([ka, kb]); v = np.concatenate([va, vb])
+    oref, lref = attn_fwd(q, k, v, ql, na + nb, hd, off, -1)
+    oref = np.asarray(oref).reshape(ql, hd); lref = np.asarray(lref).reshape(ql)
+    tol = lambda got, want: np.all(np.abs(got - want) <= 1e-3 * (np.abs(want) + 1e-4))
+    assert tol(om, oref) and tol(lm, lref)
+    dout = rng.standard_normal((ql, hd)).astype(np.float32)
+    rc = np.sum(dout.astype(np.float64) * om.astype(np.float64), axis=1).astype(np.float32)
+    gqa, gka, gva = attn_bwd(q, ka, va, oa, dout, lm, ql, na, hd, off, -1, rc)
+    gqb, gkb, gvb = attn_bwd(q, kb, vb, ob, dout, lm, ql, nb, hd, off, -1, rc)
+    gq, gk, gv = attn_bwd(q, k, v, oref, dout, lref, ql, na + nb, hd, off, -1, None)
+    gq, gk, gv = np.asarray(gq), np.asarray(gk).reshape(na + nb, hd), np.asarray(gv).reshape(na + nb, hd)
+    assert tol(np.asarray(gqa) + np.asarray(gqb), gq)
+    assert tol(np.asarray(gka).reshape(na, hd), gk[:na]) and tol(np.asarray(gkb).reshape(nb, hd), gk[na:])
+    assert tol(np.asarray(gva).reshape(na, hd), gv[:na]) and tol(np.asarray(gvb).reshape(nb, hd), gv[na:])
+
+
+def test_merged_branches_equal_concatenated_attention_forward_and_backward(oracle):
+    bk = oracle.Backend(0)
+    bwd = lambda q, k, v, o, dout, lse, ql, kl, hd, off, win, rc: bk.attention_backward(q, k, v, dout, lse, ql, kl, hd, off, win, row_correction=rc)
+    _merge_contract(bk.attention_forward, bwd, oracle.merge_branches, np.random.default_rng(7))
