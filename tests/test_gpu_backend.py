@@ -256,3 +256,16 @@ def test_few_row_products(oracle, bk, ref, rows, cols, inner):
     assert np.max(np.abs(got - want)) <= 2e-5 * np.max(np.abs(want))
     again = bk.matmul_transposed(left, rt, rows, cols, inner)
     assert np.array_equal(got, again)          # fixed summation order: bit-reproducible
+
+
+def test_wide_product_with_512_rows(bk):
+    """x W^T with 512 rows against a very wide weight matrix (the shape of the decode step's lm_head), and a ragged row count."""
+    rng = np.random.default_rng(5)
+    M, N, K = 512, 16384, 160
+    x = rng.standard_normal((M, K)).astype(np.float32); w = rng.standard_normal((N, K)).astype(np.float32)
+    got = np.asarray(bk.matmul_transposed(x, w, M, N, K)).reshape(M, N)
+    want = x.astype(np.float64) @ w.astype(np.float64).T
+    assert np.max(np.abs(got - want)) <= 1e-5 * np.sqrt(K) * 4
+    M2 = 300                                                   # a ragged last row block
+    got2 = np.asarray(bk.matmul_transposed(x[:M2], w, M2, N, K)).reshape(M2, N)
+    assert np.max(np.abs(got2 - want[:M2])) <= 1e-5 * np.sqrt(K) * 4
