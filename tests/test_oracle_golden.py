@@ -475,3 +475,22 @@ def test_merged_branches_equal_concatenated_attention_forward_and_backward(oracl
     bk = oracle.Backend(0)
     bwd = lambda q, k, v, o, dout, lse, ql, kl, hd, off, win, rc: bk.attention_backward(q, k, v, dout, lse, ql, kl, hd, off, win, row_correction=rc)
     _merge_contract(bk.attention_forward, bwd, oracle.merge_branches, np.random.default_rng(7))
+
+
+# the cached inference form against the full-sequence pass (the invariant inference/inference_test.go:306-440 holds the reference's
+# engine to): the last rows of a full pass equal the continuation computed from the cached blocks at their positions
+def test_cached_compressed_attention_equals_full_pass(oracle):
+    rng = np.random.default_rng(19)
+    B, Hq, Hkv, T, D, ratio, T0 = 2, 4, 2, 23, 8, 4, 9
+    blocks = (T + ratio - 1) // ratio
+    q = (rng.standard_normal((B, Hq, T, D)) * 0.5).astype(np.float32)
+    kc = (rng.standard_normal((B, Hkv, blocks, D)) * 0.5).astype(np.float32); vc = rng.standard_normal((B, Hkv, blocks, D)).astype(np.float32)
+    full, full_l = oracle.compressed_attention_forward(q, kc, vc, ratio)
+    again, again_l = oracle.compressed_attention_forward_at(q, kc, vc, ratio, 0)
+    assert np.array_equal(full, again) and np.array_equal(full_l, again_l)
+    tail, tail_l = oracle.compressed_attention_forward_at(q[:, :, T0:], kc, vc, ratio, T0)
+    assert np.array_equal(tail, full[:, :, T0:]) and np.array_equal(tail_l, full_l[:, :, T0:])
+    for t in range(T0, T):                                     # token by token with only the blocks complete at that time
+        have = (t + 1) // ratio
+        one, one_l = oracle.compressed_attention_forward_at(q[:, :, t:t + 1], kc[:, :, :have], vc[:, :, :have], ratio, t)
+        assert np.allclose(one[:, :, 0], full[:, :, t], atol=1e-6) and np.allclose(one_l[:, :, 0], full_l[:, :, t], atol=1e-6)
